@@ -1,0 +1,362 @@
+// Causal GQA attention forward for sm_100a: ONE kernel for the trainer's packed varlen
+// forward, the engine's (chunked) prefill and the engine's paged decode, so the three
+// sites produce the same bits per (token, head) by construction.
+//
+// Invariance rules (what the reference gets from FlashAttention-3 pinned to num_splits=1 on
+// both sides, ISO/ops/attention/_register.py:15-77):
+//   * keys are consumed in blocks of 128 aligned to position 0 of the sequence, in
+//     ascending order, never split across CTAs; the online-softmax state of a row
+//     (m, l, O) is updated once per block in that order;
+//   * a row of the 128-row tile belongs to one (token, query head); the tcgen05 MMAs and
+//     the per-row softmax never mix rows, so a token's result is the same whether its tile
+//     holds 127 other real rows (prefill / training) or padding (decode);
+//   * a block that is entirely masked for a row leaves that row's state untouched
+//     (alpha = 1, p = 0).
+//
+// Tile rows are GQA-packed: row r = (token r / G, head g0*G + r % G) for one KV head g0,
+// fetched with one 4D TMA box over Q viewed as [T, Hkv, G, D]. K and V come from a slot
+// pool [num_slots, Hkv, D] through a block table (page = 128 slots) or contiguously.
+//
+// Roles (192 threads): warp 0 TMA producer, warp 1 tcgen05.mma issuer, warps 2..5 softmax
+// (thread = row). TMEM: two S buffers (128 cols each) + one O_blk buffer (D cols).
+// Pipeline: S_{j+1} = Q K_{j+1}^T is issued while the softmax of block j runs; O_blk = P V_j
+// is added into the fp32 register accumulator of the row by the softmax threads.
+#include "bw_common.cuh"
+#include "host_util.h"
+
+namespace {
+using namespace bw;
+
+constexpr int kRows = 128;   // tile rows (queries x heads-in-group)
+constexpr int kBlkN = 128;   // keys per block == page size
+constexpr int kAttnThreads = 192;
+
+struct WorkItem {
+  int q_start;   // first query token (row of Q / out)
+  int q_len;     // query tokens in this tile (<= 128 / G)
+  int q_pos0;    // position of the first query token inside its sequence
+  int kv_len;    // keys visible to the sequence (positions 0 .. kv_len-1 exist)
+  int bt_row;    // row of the block table, or -1 for contiguous keys
+  int kv_start;  // contiguous mode: slot of position 0
+  int pad0, pad1;
+};
+
+template <int ND>  // head dim = 64 * ND
+struct AttnSmem {
+  static constexpr int kChunk = kRows * 128;                 // 128 rows x 128 B = 16 KB
+  static constexpr int kQ = ND * kChunk;
+  static constexpr int kKV = ND * kChunk;                    // one K or V block
+  static constexpr int kP = 2 * kChunk;                      // 128 rows x 128 keys bf16
+  static constexpr int offQ = 0;
+  static constexpr int offK = offQ + kQ;
+  static constexpr int offV = offK + 2 * kKV;
+  static constexpr int offP = offV + 2 * kKV;
+  static constexpr int offBar = offP + kP;
+  static constexpr int kBytes = offBar + 256 + 1024;
+};
+
+// bars: 0 Q | 1,2 K_full | 3,4 K_empty | 5,6 V_full | 7,8 V_empty | 9,10 S_full | 11 P_full | 12 O_full
+template <int ND>
+__global__ void __launch_bounds__(kAttnThreads, 1)
+attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                     const __grid_constant__ CUtensorMap tmV, const WorkItem* __restrict__ items,
+                     const int* __restrict__ block_table, int bt_stride, __nv_bfloat16* __restrict__ out,
+                     float* __restrict__ lse_out, int Hq, int Hkv, int G, float scale_log2, int* __restrict__ status) {
+  using SM = AttnSmem<ND>;
+  constexpr int D = 64 * ND;
+  constexpr int kTmemCols = 512;  // S0 | S1 | O  (2*128 + D <= 512, power of two)
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SM::offBar);
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 13);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const WorkItem it = items[blockIdx.x];
+  const int kvh = blockIdx.y;
+  const int TQ = kRows / G;
+  const int q_valid = it.q_len < TQ ? it.q_len : TQ;
+  int kv_hi = it.q_pos0 + q_valid;  // causal: last row sees positions < q_pos0 + q_valid
+  if (kv_hi > it.kv_len) kv_hi = it.kv_len;
+  const int nb = (kv_hi + kBlkN - 1) / kBlkN;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int i = 0; i < 11; ++i) mbar_init(smem_u32(&bars[i]), 1);
+    mbar_init(smem_u32(&bars[11]), 128);
+    mbar_init(smem_u32(&bars[12]), 1);
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc<kTmemCols>(smem_u32(tmem_holder));
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+  const uint32_t tmem_S0 = tmem_base, tmem_O = tmem_base + 256;
+
+  if (nb > 0) {
+    if (warp == 0) {
+      // -------------------------------------------------------------- producer
+      if (elect_one()) {
+        tma_prefetch_desc(&tmQ);
+        tma_prefetch_desc(&tmK);
+        tma_prefetch_desc(&tmV);
+        const uint32_t bq = smem_u32(&bars[0]);
+        mbar_arrive_expect_tx(bq, SM::kQ);
+#pragma unroll
+        for (int dc = 0; dc < ND; ++dc)
+          tma_load_4d(smem_u32(smem + SM::offQ + dc * SM::kChunk), &tmQ, bq, dc * 64, 0, kvh, it.q_start);
+        for (int j = 0; j < nb; ++j) {
+          const int st = j & 1;
+          const uint32_t ph = (j >> 1) & 1;
+          int row;
+          if (it.bt_row >= 0) row = block_table[static_cast<size_t>(it.bt_row) * bt_stride + j] * kBlkN;
+          else row = it.kv_start + j * kBlkN;
+          if (!mbar_wait(smem_u32(&bars[3 + st]), ph ^ 1, abort_flag, status, ST_TIMEOUT_EMPTY)) break;
+          const uint32_t bk = smem_u32(&bars[1 + st]);
+          mbar_arrive_expect_tx(bk, SM::kKV);
+#pragma unroll
+          for (int dc = 0; dc < ND; ++dc)
+            tma_load_2d(smem_u32(smem + SM::offK + st * SM::kKV + dc * SM::kChunk), &tmK, bk, kvh * D + dc * 64, row);
+          if (!mbar_wait(smem_u32(&bars[7 + st]), ph ^ 1, abort_flag, status, ST_TIMEOUT_EMPTY)) break;
+          const uint32_t bv = smem_u32(&bars[5 + st]);
+          mbar_arrive_expect_tx(bv, SM::kKV);
+#pragma unroll
+          for (int dc = 0; dc < ND; ++dc)
+            tma_load_2d(smem_u32(smem + SM::offV + st * SM::kKV + dc * SM::kChunk), &tmV, bv, kvh * D + dc * 64, row);
+        }
+      }
+    } else if (warp == 1) {
+      // -------------------------------------------------------------- MMA issuer
+      if (elect_one()) {
+        constexpr uint32_t idesc_s = make_idesc_bf16(kRows, kBlkN, 0, 0);
+        constexpr uint32_t idesc_o = make_idesc_bf16(kRows, D, 0, 1);  // V is MN-major
+        const uint32_t sQ = smem_u32(smem + SM::offQ);
+        const uint32_t sP = smem_u32(smem + SM::offP);
+        bool ok = mbar_wait(smem_u32(&bars[0]), 0, abort_flag, status, ST_TIMEOUT_FULL);
+        auto issue_qk = [&](int j) -> bool {
+          const int st = j & 1;
+          if (!mbar_wait(smem_u32(&bars[1 + st]), (j >> 1) & 1, abort_flag, status, ST_TIMEOUT_FULL)) return false;
+          tc_fence_after();
+          const uint32_t sK = smem_u32(smem + SM::offK + st * SM::kKV);
+#pragma unroll
+          for (int dc = 0; dc < ND; ++dc)
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+              umma_f16_ss(tmem_S0 + st * 128, make_sw128_desc(sQ + dc * SM::kChunk + k * 32, 16, 1024),
+                          make_sw128_desc(sK + dc * SM::kChunk + k * 32, 16, 1024), idesc_s, (dc | k) != 0 ? 1u : 0u);
+          umma_commit(smem_u32(&bars[3 + st]));   // K stage free
+          umma_commit(smem_u32(&bars[9 + st]));   // S ready
+          return true;
+        };
+        if (ok) ok = issue_qk(0);
+        for (int j = 0; j < nb && ok; ++j) {
+          if (j + 1 < nb) {
+            // S[(j+1)&1] was last read by the softmax of block j-1, which finished before P_full(j-1)
+            if (!issue_qk(j + 1)) { ok = false; break; }
+          }
+          const int st = j & 1;
+          if (!mbar_wait(smem_u32(&bars[11]), j & 1, abort_flag, status, ST_TIMEOUT_MISC)) { ok = false; break; }
+          if (!mbar_wait(smem_u32(&bars[5 + st]), (j >> 1) & 1, abort_flag, status, ST_TIMEOUT_FULL)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sV = smem_u32(smem + SM::offV + st * SM::kKV);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            // A = P (K-major): 64-key atoms 16 KB apart, 32 B per K=16 step inside an atom
+            const uint64_t da = make_sw128_desc(sP + (k >> 2) * SM::kChunk + (k & 3) * 32, 16, 1024);
+            // B = V (MN-major): 16 keys = 2 groups of 8 rows (SBO 1024 B); 64-wide d chunks LBO apart
+            const uint64_t db = make_sw128_desc(sV + k * 2048, SM::kChunk, 1024);
+            umma_f16_ss(tmem_O, da, db, idesc_o, k != 0 ? 1u : 0u);
+          }
+          umma_commit(smem_u32(&bars[7 + st]));  // V stage free
+          umma_commit(smem_u32(&bars[12]));      // O_blk ready, P buffer free
+        }
+      }
+    } else {
+      // -------------------------------------------------------------- softmax / epilogue
+      const int quad = warp & 3;
+      const int r = quad * 32 + lane;             // tile row
+      const int tok = r / G;                      // token inside the tile
+      const int hq = kvh * G + (r % G);
+      const bool row_valid = tok < q_valid;
+      const int q_pos = it.q_pos0 + (row_valid ? tok : q_valid - 1);
+      const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
+      float m = -INFINITY, l = 0.f;
+      float o[D];
+#pragma unroll
+      for (int i = 0; i < D; ++i) o[i] = 0.f;
+      uint8_t* sP = smem + SM::offP;
+      bool ok = true;
+      for (int j = 0; j < nb && ok; ++j) {
+        const int st = j & 1;
+        if (!mbar_wait(smem_u32(&bars[9 + st]), (j >> 1) & 1, abort_flag, status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t tS = tmem_S0 + st * 128 + lane_off;
+        const int key0 = j * kBlkN;
+        int lim = q_pos - key0 + 1;               // keys [0, lim) of this block are visible
+        const int lim2 = it.kv_len - key0;
+        if (lim2 < lim) lim = lim2;
+        // pass 1: row max of the scaled scores
+        float mb = -INFINITY;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t s[32];
+          tmem_ld_32x32(tS + c * 32, s);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float t = __fmul_rn(__uint_as_float(s[i]), scale_log2);
+            if (c * 32 + i < lim) mb = fmaxf(mb, t);
+          }
+        }
+        const float m_new = fmaxf(m, mb);
+        const float alpha = (m == -INFINITY) ? 0.f : exp2f(__fsub_rn(m, m_new));
+        // previous block's P V is done: P buffer is free, O_blk holds block j-1
+        if (j > 0) {
+          if (!mbar_wait(smem_u32(&bars[12]), (j - 1) & 1, abort_flag, status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+          tc_fence_after();
+#pragma unroll
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t v[32];
+            tmem_ld_32x32(tmem_O + lane_off + c * 32, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[c * 32 + i] = __fadd_rn(o[c * 32 + i], __uint_as_float(v[i]));
+          }
+        }
+        if (alpha != 1.f) {
+#pragma unroll
+          for (int i = 0; i < D; ++i) o[i] = __fmul_rn(o[i], alpha);
+          l = __fmul_rn(l, alpha);
+        }
+        m = m_new;
+        // pass 2: p = exp2(t - m), row sum left to right, P -> smem (bf16, 128B swizzle)
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t s[32];
+          tmem_ld_32x32(tS + c * 32, s);
+          tmem_ld_wait();
+          uint32_t pk[16];
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            float p0 = 0.f, p1 = 0.f;
+            if (c * 32 + i < lim) p0 = exp2f(__fsub_rn(__fmul_rn(__uint_as_float(s[i]), scale_log2), m));
+            if (c * 32 + i + 1 < lim) p1 = exp2f(__fsub_rn(__fmul_rn(__uint_as_float(s[i + 1]), scale_log2), m));
+            l = __fadd_rn(l, p0);
+            l = __fadd_rn(l, p1);
+            pk[i >> 1] = pack_bf2(p0, p1);
+          }
+          // columns c*32 .. c*32+31 -> atom (c>>1), 16-byte chunks ((c&1)*4 + q), q = 0..3
+          uint8_t* rowp = sP + (c >> 1) * SM::kChunk + r * 128;
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const int chunk = ((c & 1) * 4 + q) ^ (r & 7);
+            *reinterpret_cast<uint4*>(rowp + chunk * 16) = make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
+          }
+        }
+        tc_fence_before();
+        fence_proxy_async();  // make the generic-proxy writes of P visible to the tensor core
+        mbar_arrive(smem_u32(&bars[11]));
+      }
+      if (ok && mbar_wait(smem_u32(&bars[12]), (nb - 1) & 1, abort_flag, status, ST_TIMEOUT_TMEM_FULL)) {
+        tc_fence_after();
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(tmem_O + lane_off + c * 32, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[c * 32 + i] = __fadd_rn(o[c * 32 + i], __uint_as_float(v[i]));
+        }
+        if (row_valid) {
+          const float inv = __fdiv_rn(1.0f, l);
+          const size_t orow = static_cast<size_t>(it.q_start + tok) * Hq + hq;
+          uint4* dst = reinterpret_cast<uint4*>(out + orow * D);
+#pragma unroll
+          for (int i = 0; i < D / 8; ++i) {
+            uint4 w;
+            w.x = pack_bf2(__fmul_rn(o[8 * i + 0], inv), __fmul_rn(o[8 * i + 1], inv));
+            w.y = pack_bf2(__fmul_rn(o[8 * i + 2], inv), __fmul_rn(o[8 * i + 3], inv));
+            w.z = pack_bf2(__fmul_rn(o[8 * i + 4], inv), __fmul_rn(o[8 * i + 5], inv));
+            w.w = pack_bf2(__fmul_rn(o[8 * i + 6], inv), __fmul_rn(o[8 * i + 7], inv));
+            dst[i] = w;
+          }
+          if (lse_out) lse_out[orow] = (m + log2f(l)) * 0.6931471805599453f;
+        }
+      }
+    }
+  }
+
+  if (*abort_flag) {
+    for (int i = 0; i < 64; ++i) __nanosleep(2000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc<kTmemCols>(tmem_base);
+  }
+}
+
+template <int ND>
+int launch_attn(const void* q, const void* k, const void* v, const void* items, const void* block_table, void* out,
+                void* lse, int num_items, int T, int Hq, int Hkv, int bt_stride, long long num_slots, float scale,
+                cudaStream_t stream, int dev) {
+  using SM = AttnSmem<ND>;
+  constexpr int D = 64 * ND;
+  const int G = Hq / Hkv;
+  const int TQ = kRows / G;
+  CUtensorMap tmQ, tmK, tmV;
+  {
+    uint64_t dims[4] = {static_cast<uint64_t>(D), static_cast<uint64_t>(G), static_cast<uint64_t>(Hkv),
+                        static_cast<uint64_t>(T)};
+    uint64_t strides[3] = {static_cast<uint64_t>(D) * 2, static_cast<uint64_t>(G) * D * 2,
+                           static_cast<uint64_t>(Hq) * D * 2};
+    uint32_t box[4] = {64, static_cast<uint32_t>(G), 1, static_cast<uint32_t>(TQ)};
+    int rc = ixh::make_tmap(&tmQ, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, q, dims, strides, box);
+    if (rc) return rc;
+  }
+  int rc = ixh::make_tmap_bf16_2d(&tmK, k, num_slots, static_cast<uint64_t>(Hkv) * D, static_cast<uint64_t>(Hkv) * D, kBlkN);
+  if (rc) return rc;
+  rc = ixh::make_tmap_bf16_2d(&tmV, v, num_slots, static_cast<uint64_t>(Hkv) * D, static_cast<uint64_t>(Hkv) * D, kBlkN);
+  if (rc) return rc;
+  auto kern = attention_fwd_kernel<ND>;
+  static bool attr_set[64] = {false};
+  if (!attr_set[dev & 63]) {
+    IX_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::kBytes));
+    attr_set[dev & 63] = true;
+  }
+  dim3 grid(num_items, Hkv);
+  const float scale_log2 = scale * 1.4426950408889634f;
+  kern<<<grid, kAttnThreads, SM::kBytes, stream>>>(tmQ, tmK, tmV, static_cast<const WorkItem*>(items),
+                                                   static_cast<const int*>(block_table), bt_stride,
+                                                   static_cast<__nv_bfloat16*>(out), static_cast<float*>(lse), Hq, Hkv,
+                                                   G, scale_log2, ixh::status_word(dev));
+  IX_CUDA(cudaGetLastError());
+  return 0;
+}
+
+}  // namespace
+
+// q: [T, Hq, D] bf16; k, v: [num_slots, Hkv, D] bf16 slot pools (zero-initialised: a masked key
+// still enters P*V with weight 0, so its bytes must be finite); items: [num_items, 8] int32
+// (WorkItem); block_table: [*, bt_stride] int32 page ids (page = 128 slots) or null;
+// out: [T, Hq, D] bf16; lse: [T, Hq] fp32 or null.
+IX_API int ix_attention_fwd(const void* q, const void* k, const void* v, const void* items, const void* block_table,
+                            void* out, void* lse, void* /*reserved*/, int num_items, int T, int Hq, int Hkv, int D,
+                            int bt_stride, long long num_slots, int /*flags*/, float scale, void* /*reserved2*/,
+                            void* stream) {
+  if (num_items <= 0) return 0;
+  if (Hkv <= 0 || Hq % Hkv) return ixh::fail(ixh::IX_EARG, "attention: Hq=%d not a multiple of Hkv=%d", Hq, Hkv);
+  const int G = Hq / Hkv;
+  if (G > 128 || (128 % G)) return ixh::fail(ixh::IX_EARG, "attention: group size %d must divide 128", G);
+  int dev = 0;
+  IX_CUDA(cudaGetDevice(&dev));
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (D == 128) return launch_attn<2>(q, k, v, items, block_table, out, lse, num_items, T, Hq, Hkv, bt_stride, num_slots, scale, s, dev);
+  if (D == 64) return launch_attn<1>(q, k, v, items, block_table, out, lse, num_items, T, Hq, Hkv, bt_stride, num_slots, scale, s, dev);
+  return ixh::fail(ixh::IX_EARG, "attention: head dim %d unsupported (64 or 128)", D);
+}

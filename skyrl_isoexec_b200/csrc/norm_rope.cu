@@ -1,0 +1,406 @@
+// Row-wise normalisation / activation kernels shared by the trainer and the rollout
+// engine. One warp owns one row (or one (token, head) pair), so a row's bits never
+// depend on how many rows the launch has.
+//
+// Rounding chains (each step is one explicit round-to-nearest op, no FMA contraction):
+//   RMSNorm   h = bf16(x + r)                          (only with a residual input)
+//             ss = sum over the row of fp32(h*h): lane l takes 8-element vectors l, l+32, ...
+//                  in ascending order, then a 5-step xor butterfly (16,8,4,2,1)
+//             rstd = 1 / sqrt(ss / N + eps)            (div.rn, sqrt.rn)
+//             n = bf16(h * rstd);  y = bf16(n * g),  g = w or bf16(1 + w) (zero-centred)
+//   RoPE      a = bf16(y*cos)  b = bf16(rot(y)*sin)  out = bf16(a + b)   (three rounds;
+//             the reference pins the same three-round chain, ISO/ops/rope/rope_fused.py:49-105)
+//   SwiGLU    s = bf16(g / (1 + exp(-g)));  out = bf16(s * u)
+//   gated out-norm (GatedDeltaNet): n,y as RMSNorm; out = bf16(y * bf16(silu(z)))
+#include "bw_common.cuh"
+#include "host_util.h"
+
+namespace {
+using namespace bw;
+
+struct alignas(16) BF8 {
+  __nv_bfloat16 v[8];
+};
+
+__device__ __forceinline__ float silu_f32(float g) {
+  return __fdiv_rn(g, __fadd_rn(1.0f, expf(-g)));
+}
+
+// ------------------------------------------------------------------ RMSNorm (+residual)
+template <bool HAS_RES, bool ZERO_CENTERED>
+__global__ void __launch_bounds__(128)
+rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
+               const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
+               __nv_bfloat16* __restrict__ res_out, float* __restrict__ rstd_out, int rows, int N, float eps,
+               long long ldx, long long ldy) {
+  const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const int nvec = N >> 3;
+  const BF8* xr = reinterpret_cast<const BF8*>(x + static_cast<size_t>(row) * ldx);
+  const BF8* rr = HAS_RES ? reinterpret_cast<const BF8*>(res + static_cast<size_t>(row) * N) : nullptr;
+  BF8* ro = HAS_RES ? reinterpret_cast<BF8*>(res_out + static_cast<size_t>(row) * N) : nullptr;
+  float ss = 0.f;
+  for (int v = lane; v < nvec; v += 32) {
+    BF8 a = xr[v];
+    if (HAS_RES) {
+      BF8 b = rr[v];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) a.v[j] = f2bf(__fadd_rn(bf2f(a.v[j]), bf2f(b.v[j])));
+      ro[v] = a;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float f = bf2f(a.v[j]);
+      ss = __fadd_rn(ss, __fmul_rn(f, f));
+    }
+  }
+  ss = warp_sum_butterfly(ss);
+  const float rstd = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, static_cast<float>(N)), eps)));
+  if (rstd_out && lane == 0) rstd_out[row] = rstd;
+  const BF8* hr = HAS_RES ? reinterpret_cast<const BF8*>(res_out + static_cast<size_t>(row) * N) : xr;
+  const BF8* wr = reinterpret_cast<const BF8*>(w);
+  BF8* yr = reinterpret_cast<BF8*>(y + static_cast<size_t>(row) * ldy);
+  for (int v = lane; v < nvec; v += 32) {
+    BF8 a = hr[v];  // same lane wrote it above (HAS_RES), so no cross-thread hazard
+    BF8 g = wr[v];
+    BF8 o;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float n = round_bf(__fmul_rn(bf2f(a.v[j]), rstd));
+      float gg = bf2f(g.v[j]);
+      if (ZERO_CENTERED) gg = round_bf(__fadd_rn(1.0f, gg));
+      o.v[j] = f2bf(__fmul_rn(n, gg));
+    }
+    yr[v] = o;
+  }
+}
+
+// ------------------------------------------------------------------ QK-norm + RoPE + KV write
+// qkv: [T, (Hq + 2*Hkv) * D] as produced by the fused QKV projection (row stride ldqkv).
+// One warp per (token, head). q heads -> q_out[T, Hq, D]; k heads -> k_out[slot, Hkv, D];
+// v heads -> v_out[slot, Hkv, D] with slot = slots ? slots[t] : t (paged cache or packed).
+template <bool QK_NORM, bool ZERO_CENTERED>
+__global__ void __launch_bounds__(128)
+qk_norm_rope_kernel(const __nv_bfloat16* __restrict__ qkv, long long ldqkv, const int* __restrict__ positions,
+                    const long long* __restrict__ slots, const float* __restrict__ cos_tab,
+                    const float* __restrict__ sin_tab, const __nv_bfloat16* __restrict__ qw,
+                    const __nv_bfloat16* __restrict__ kw, __nv_bfloat16* __restrict__ q_out,
+                    __nv_bfloat16* __restrict__ k_out, __nv_bfloat16* __restrict__ v_out, int T, int Hq, int Hkv,
+                    int D, int rot_dim, float eps, int q_gate) {
+  const int Htot = Hq + 2 * Hkv;
+  const long long wid = static_cast<long long>(blockIdx.x) * 4 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (wid >= static_cast<long long>(T) * Htot) return;
+  const int t = static_cast<int>(wid / Htot);
+  const int h = static_cast<int>(wid % Htot);
+  const int nact = D >> 3;  // active lanes (8 elements each)
+  // with an output gate (gated attention) the q block of head h is [q(D) | gate(D)]
+  const int q_stride = q_gate ? 2 * D : D;
+  long long src_off;
+  if (h < Hq) src_off = static_cast<long long>(h) * q_stride;
+  else src_off = static_cast<long long>(Hq) * q_stride + static_cast<long long>(h - Hq) * D;
+  const __nv_bfloat16* src = qkv + static_cast<size_t>(t) * ldqkv + src_off;
+  BF8 a;
+  if (lane < nact) a = reinterpret_cast<const BF8*>(src)[lane];
+  else {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) a.v[j] = f2bf(0.f);
+  }
+  const bool is_v = h >= Hq + Hkv;
+  const long long slot = slots ? slots[t] : t;
+  if (is_v) {
+    if (lane < nact && slot >= 0)
+      reinterpret_cast<BF8*>(v_out + (static_cast<size_t>(slot) * Hkv + (h - Hq - Hkv)) * D)[lane] = a;
+    return;
+  }
+  float y[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) y[j] = bf2f(a.v[j]);
+  if (QK_NORM) {
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) ss = __fadd_rn(ss, __fmul_rn(y[j], y[j]));
+    ss = warp_sum_butterfly(ss);
+    const float rstd = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, static_cast<float>(D)), eps)));
+    const __nv_bfloat16* wsrc = (h < Hq) ? qw : kw;
+    BF8 g;
+    if (lane < nact) g = reinterpret_cast<const BF8*>(wsrc)[lane];
+    else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) g.v[j] = f2bf(0.f);
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float n = round_bf(__fmul_rn(y[j], rstd));
+      float gg = bf2f(g.v[j]);
+      if (ZERO_CENTERED) gg = round_bf(__fadd_rn(1.0f, gg));
+      y[j] = round_bf(__fmul_rn(n, gg));
+    }
+  }
+  // rotate-half over the first rot_dim elements: element i pairs with i +- rot_dim/2
+  const int half = rot_dim >> 1;
+  const int half_lanes = half >> 3;  // lanes per half (rot_dim multiple of 16)
+  const int pos = positions[t];
+  float o[8];
+  const int e0 = lane * 8;
+  const bool in_rot = e0 < rot_dim;
+  const bool first_half = e0 < half;
+  const int partner = first_half ? lane + half_lanes : lane - half_lanes;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const float other = __shfl_sync(0xffffffffu, y[j], (in_rot ? partner : lane) & 31);
+    if (in_rot) {
+      const int fi = (first_half ? e0 : e0 - half) + j;
+      const float c = cos_tab[static_cast<size_t>(pos) * half + fi];
+      const float s = sin_tab[static_cast<size_t>(pos) * half + fi];
+      const float rot = first_half ? __fmul_rn(other, -1.0f) : other;
+      const float p1 = round_bf(__fmul_rn(y[j], c));
+      const float p2 = round_bf(__fmul_rn(rot, s));
+      o[j] = __fadd_rn(p1, p2);
+    } else {
+      o[j] = y[j];
+    }
+  }
+  if (lane < nact) {
+    BF8 r;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) r.v[j] = f2bf(o[j]);
+    if (h < Hq) reinterpret_cast<BF8*>(q_out + (static_cast<size_t>(t) * Hq + h) * D)[lane] = r;
+    else if (slot >= 0) reinterpret_cast<BF8*>(k_out + (static_cast<size_t>(slot) * Hkv + (h - Hq)) * D)[lane] = r;
+  }
+}
+
+// ------------------------------------------------------------------ SwiGLU
+// in: [T, 2F] = [gate | up]; out: [T, F]
+__global__ void __launch_bounds__(256)
+swiglu_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out, long long T, int F,
+              long long ld_in) {
+  const long long nvec_row = F >> 3;
+  const long long total = T * nvec_row;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long t = i / nvec_row;
+    const long long v = i % nvec_row;
+    const BF8 g = reinterpret_cast<const BF8*>(in + t * ld_in)[v];
+    const BF8 u = reinterpret_cast<const BF8*>(in + t * ld_in + F)[v];
+    BF8 o;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float s = round_bf(silu_f32(bf2f(g.v[j])));
+      o.v[j] = f2bf(__fmul_rn(s, bf2f(u.v[j])));
+    }
+    reinterpret_cast<BF8*>(out + t * F)[v] = o;
+  }
+}
+
+// d(gate), d(up) from d(out); recomputes silu. din: [T, 2F]
+__global__ void __launch_bounds__(256)
+swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ in, const __nv_bfloat16* __restrict__ dout,
+                  __nv_bfloat16* __restrict__ din, long long T, int F, long long ld_in) {
+  const long long nvec_row = F >> 3;
+  const long long total = T * nvec_row;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long t = i / nvec_row;
+    const long long v = i % nvec_row;
+    const BF8 g = reinterpret_cast<const BF8*>(in + t * ld_in)[v];
+    const BF8 u = reinterpret_cast<const BF8*>(in + t * ld_in + F)[v];
+    const BF8 d = reinterpret_cast<const BF8*>(dout + t * F)[v];
+    BF8 dg, du;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float gf = bf2f(g.v[j]), uf = bf2f(u.v[j]), df = bf2f(d.v[j]);
+      const float sig = 1.0f / (1.0f + expf(-gf));
+      const float s = gf * sig;
+      du.v[j] = f2bf(df * s);
+      dg.v[j] = f2bf(df * uf * (sig * (1.0f + gf * (1.0f - sig))));
+    }
+    reinterpret_cast<BF8*>(din + t * 2 * F)[v] = dg;
+    reinterpret_cast<BF8*>(din + t * 2 * F + F)[v] = du;
+  }
+}
+
+// ------------------------------------------------------------------ gated multiply: out = bf16(a * bf16(sigmoid(g)))
+// used for the output gate of gated attention. a: [T, H*D] ; g read from qkv block layout.
+__global__ void __launch_bounds__(256)
+sigmoid_gate_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ qkv, long long ldqkv,
+                    __nv_bfloat16* __restrict__ out, long long T, int Hq, int D) {
+  const long long nvec_row = static_cast<long long>(Hq) * D >> 3;
+  const long long total = T * nvec_row;
+  const int vec_per_head = D >> 3;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long t = i / nvec_row;
+    const long long v = i % nvec_row;
+    const int h = static_cast<int>(v / vec_per_head);
+    const int vv = static_cast<int>(v % vec_per_head);
+    const BF8 x = reinterpret_cast<const BF8*>(a + t * Hq * D)[v];
+    const BF8 g = reinterpret_cast<const BF8*>(qkv + t * ldqkv + static_cast<long long>(h) * 2 * D + D)[vv];
+    BF8 o;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float gf = bf2f(g.v[j]);
+      const float s = round_bf(__fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-gf))));
+      o.v[j] = f2bf(__fmul_rn(bf2f(x.v[j]), s));
+    }
+    reinterpret_cast<BF8*>(out + t * Hq * D)[v] = o;
+  }
+}
+
+// ------------------------------------------------------------------ gated out-norm (GDN): per (token, head) over Dv
+// out = bf16( bf16(bf16(o*rstd) * g) * bf16(silu(z)) ),  g = w or bf16(1+w)
+template <bool ZERO_CENTERED>
+__global__ void __launch_bounds__(128)
+gated_outnorm_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ z,
+                     const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ out, long long rows, int D,
+                     float eps) {
+  const long long row = static_cast<long long>(blockIdx.x) * 4 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const int nvec = D >> 3;
+  const BF8* orow = reinterpret_cast<const BF8*>(o + row * D);
+  const BF8* zrow = reinterpret_cast<const BF8*>(z + row * D);
+  float ss = 0.f;
+  for (int v = lane; v < nvec; v += 32) {
+    const BF8 a = orow[v];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float f = bf2f(a.v[j]);
+      ss = __fadd_rn(ss, __fmul_rn(f, f));
+    }
+  }
+  ss = warp_sum_butterfly(ss);
+  const float rstd = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, static_cast<float>(D)), eps)));
+  for (int v = lane; v < nvec; v += 32) {
+    const BF8 a = orow[v];
+    const BF8 zz = zrow[v];
+    const BF8 g = reinterpret_cast<const BF8*>(w)[v];
+    BF8 r;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float n = round_bf(__fmul_rn(bf2f(a.v[j]), rstd));
+      float gg = bf2f(g.v[j]);
+      if (ZERO_CENTERED) gg = round_bf(__fadd_rn(1.0f, gg));
+      const float yv = round_bf(__fmul_rn(n, gg));
+      const float s = round_bf(silu_f32(bf2f(zz.v[j])));
+      r.v[j] = f2bf(__fmul_rn(yv, s));
+    }
+    reinterpret_cast<BF8*>(out + row * D)[v] = r;
+  }
+}
+
+inline int grid_1d(long long total, int block, int cap = 148 * 16) {
+  long long g = (total + block - 1) / block;
+  if (g > cap) g = cap;
+  if (g < 1) g = 1;
+  return static_cast<int>(g);
+}
+
+}  // namespace
+
+IX_API int ix_rmsnorm(const void* x, const void* res, const void* w, void* y, void* res_out, void* rstd_out,
+                      int rows, int N, float eps, int zero_centered, long long ldx, long long ldy, void* stream) {
+  if (rows <= 0) return 0;
+  if (N & 7) return ixh::fail(ixh::IX_EARG, "rmsnorm: N=%d must be a multiple of 8", N);
+  if ((ldx & 7) || (ldy & 7)) return ixh::fail(ixh::IX_EARG, "rmsnorm: ldx/ldy must be multiples of 8");
+  if (res && !res_out) return ixh::fail(ixh::IX_EARG, "rmsnorm: residual input needs res_out");
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const int grid = (rows + 3) / 4;
+  auto X = static_cast<const __nv_bfloat16*>(x);
+  auto R = static_cast<const __nv_bfloat16*>(res);
+  auto W = static_cast<const __nv_bfloat16*>(w);
+  auto Y = static_cast<__nv_bfloat16*>(y);
+  auto RO = static_cast<__nv_bfloat16*>(res_out);
+  auto RS = static_cast<float*>(rstd_out);
+  if (res) {
+    if (zero_centered) rmsnorm_kernel<true, true><<<grid, 128, 0, s>>>(X, R, W, Y, RO, RS, rows, N, eps, ldx, ldy);
+    else rmsnorm_kernel<true, false><<<grid, 128, 0, s>>>(X, R, W, Y, RO, RS, rows, N, eps, ldx, ldy);
+  } else {
+    if (zero_centered) rmsnorm_kernel<false, true><<<grid, 128, 0, s>>>(X, R, W, Y, RO, RS, rows, N, eps, ldx, ldy);
+    else rmsnorm_kernel<false, false><<<grid, 128, 0, s>>>(X, R, W, Y, RO, RS, rows, N, eps, ldx, ldy);
+  }
+  IX_CUDA(cudaGetLastError());
+  return 0;
+}
+
+IX_API int ix_qk_norm_rope(const void* qkv, long long ldqkv, const void* positions, const void* slots,
+                           const void* cos_tab, const void* sin_tab, const void* qw, const void* kw, void* q_out,
+                           void* k_out, void* v_out, int T, int Hq, int Hkv, int D, int rot_dim, float eps,
+                           int qk_norm, int zero_centered, int q_gate, void* stream) {
+  if (T <= 0) return 0;
+  if (D > 256 || (D & 7)) return ixh::fail(ixh::IX_EARG, "qk_norm_rope: head dim %d unsupported", D);
+  if ((rot_dim & 15) || rot_dim > D) return ixh::fail(ixh::IX_EARG, "qk_norm_rope: rot_dim %d unsupported", rot_dim);
+  if (ldqkv & 7) return ixh::fail(ixh::IX_EARG, "qk_norm_rope: ldqkv must be a multiple of 8");
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const long long warps = static_cast<long long>(T) * (Hq + 2 * Hkv);
+  const int grid = static_cast<int>((warps + 3) / 4);
+#define IX_QKR(N_, Z_)                                                                                        \
+  qk_norm_rope_kernel<N_, Z_><<<grid, 128, 0, s>>>(                                                           \
+      static_cast<const __nv_bfloat16*>(qkv), ldqkv, static_cast<const int*>(positions),                      \
+      static_cast<const long long*>(slots), static_cast<const float*>(cos_tab),                               \
+      static_cast<const float*>(sin_tab), static_cast<const __nv_bfloat16*>(qw),                              \
+      static_cast<const __nv_bfloat16*>(kw), static_cast<__nv_bfloat16*>(q_out),                              \
+      static_cast<__nv_bfloat16*>(k_out), static_cast<__nv_bfloat16*>(v_out), T, Hq, Hkv, D, rot_dim, eps, q_gate)
+  if (qk_norm) {
+    if (zero_centered) IX_QKR(true, true);
+    else IX_QKR(true, false);
+  } else {
+    IX_QKR(false, false);
+  }
+#undef IX_QKR
+  IX_CUDA(cudaGetLastError());
+  return 0;
+}
+
+IX_API int ix_swiglu(const void* in, void* out, long long T, int F, long long ld_in, void* stream) {
+  if (T <= 0) return 0;
+  if ((F & 7) || (ld_in & 7)) return ixh::fail(ixh::IX_EARG, "swiglu: F and ld_in must be multiples of 8");
+  swiglu_kernel<<<grid_1d(T * (F >> 3), 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(in), static_cast<__nv_bfloat16*>(out), T, F, ld_in);
+  IX_CUDA(cudaGetLastError());
+  return 0;
+}
+
+IX_API int ix_swiglu_bwd(const void* in, const void* dout, void* din, long long T, int F, long long ld_in,
+                         void* stream) {
+  if (T <= 0) return 0;
+  if ((F & 7) || (ld_in & 7)) return ixh::fail(ixh::IX_EARG, "swiglu_bwd: F and ld_in must be multiples of 8");
+  swiglu_bwd_kernel<<<grid_1d(T * (F >> 3), 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(in), static_cast<const __nv_bfloat16*>(dout),
+      static_cast<__nv_bfloat16*>(din), T, F, ld_in);
+  IX_CUDA(cudaGetLastError());
+  return 0;
+}
+
+IX_API int ix_sigmoid_gate(const void* a, const void* qkv, long long ldqkv, void* out, long long T, int Hq, int D,
+                           void* stream) {
+  if (T <= 0) return 0;
+  if ((D & 7) || (ldqkv & 7)) return ixh::fail(ixh::IX_EARG, "sigmoid_gate: D and ldqkv must be multiples of 8");
+  sigmoid_gate_kernel<<<grid_1d(T * (static_cast<long long>(Hq) * D >> 3), 256), 256, 0,
+                        reinterpret_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(a), static_cast<const __nv_bfloat16*>(qkv), ldqkv,
+      static_cast<__nv_bfloat16*>(out), T, Hq, D);
+  IX_CUDA(cudaGetLastError());
+  return 0;
+}
+
+IX_API int ix_gated_outnorm(const void* o, const void* z, const void* w, void* out, long long rows, int D,
+                            float eps, int zero_centered, void* stream) {
+  if (rows <= 0) return 0;
+  if (D & 7) return ixh::fail(ixh::IX_EARG, "gated_outnorm: D must be a multiple of 8");
+  const int grid = static_cast<int>((rows + 3) / 4);
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (zero_centered)
+    gated_outnorm_kernel<true><<<grid, 128, 0, s>>>(static_cast<const __nv_bfloat16*>(o),
+                                                    static_cast<const __nv_bfloat16*>(z),
+                                                    static_cast<const __nv_bfloat16*>(w),
+                                                    static_cast<__nv_bfloat16*>(out), rows, D, eps);
+  else
+    gated_outnorm_kernel<false><<<grid, 128, 0, s>>>(static_cast<const __nv_bfloat16*>(o),
+                                                     static_cast<const __nv_bfloat16*>(z),
+                                                     static_cast<const __nv_bfloat16*>(w),
+                                                     static_cast<__nv_bfloat16*>(out), rows, D, eps);
+  IX_CUDA(cudaGetLastError());
+  return 0;
+}

@@ -1,0 +1,56 @@
+// Library runtime: per-device status word, last-error string, version.
+#include <stdarg.h>
+
+#include "host_util.h"
+
+namespace ixh {
+
+static int* g_status[64] = {nullptr};
+static std::mutex g_status_mu;
+
+int* status_word(int device) {
+  if (device < 0 || device >= 64) return nullptr;
+  if (g_status[device]) return g_status[device];
+  std::lock_guard<std::mutex> lk(g_status_mu);
+  if (!g_status[device]) {
+    int* p = nullptr;
+    if (cudaMalloc(&p, 64 * sizeof(int)) != cudaSuccess) return nullptr;
+    cudaMemset(p, 0, 64 * sizeof(int));
+    g_status[device] = p;
+  }
+  return g_status[device];
+}
+
+}  // namespace ixh
+
+IX_API const char* ix_last_error() { return ixh::last_error_buf(); }
+
+IX_API int ix_version() { return 1; }
+
+// Allocate the status word of the current device up front (call once per device before
+// any stream capture, since the first use would otherwise allocate inside the capture).
+IX_API int ix_init() {
+  int dev = 0;
+  IX_CUDA(cudaGetDevice(&dev));
+  return ixh::status_word(dev) ? 0 : ixh::fail(ixh::IX_EDRV, "could not allocate status word");
+}
+
+// Read (and clear) the kernel status word of the current device. Synchronises the device.
+// 0 = every kernel since the last read finished without a bounded wait running out.
+IX_API int ix_read_status() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return -1;
+  int* p = ixh::status_word(dev);
+  if (!p) return -1;
+  int v = 0;
+  if (cudaMemcpy(&v, p, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+  if (v != 0) cudaMemset(p, 0, sizeof(int));
+  return v;
+}
+
+// Device pointer of the status word (for kernels launched from other libraries/tests).
+IX_API void* ix_status_ptr() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
+  return ixh::status_word(dev);
+}
