@@ -77,7 +77,8 @@ rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restr
 }
 
 // ------------------------------------------------------------------ QK-norm + RoPE + KV write
-// qkv: [T, (Hq + 2*Hkv) * D] as produced by the fused QKV projection (row stride ldqkv).
+// qkv: [T, (Hq + 2*Hkv) * D] as produced by the fused QKV projection (row stride ldqkv),
+// KV-group major (see below).
 // One warp per (token, head). q heads -> q_out[T, Hq, D]; k heads -> k_out[slot, Hkv, D];
 // v heads -> v_out[slot, Hkv, D] with slot = slots ? slots[t] : t (paged cache or packed).
 template <bool QK_NORM, bool ZERO_CENTERED>
@@ -95,11 +96,16 @@ qk_norm_rope_kernel(const __nv_bfloat16* __restrict__ qkv, long long ldqkv, cons
   const int t = static_cast<int>(wid / Htot);
   const int h = static_cast<int>(wid % Htot);
   const int nact = D >> 3;  // active lanes (8 elements each)
-  // with an output gate (gated attention) the q block of head h is [q(D) | gate(D)]
+  // Row layout is KV-group major: for each KV head g, [its G query heads | k_g | v_g], so a
+  // tensor-parallel shard (whole groups) is a contiguous slice. With an output gate (gated
+  // attention) the block of a query head is [q(D) | gate(D)].
   const int q_stride = q_gate ? 2 * D : D;
+  const int G = Hq / Hkv;
+  const long long grp_stride = static_cast<long long>(G) * q_stride + 2 * D;
   long long src_off;
-  if (h < Hq) src_off = static_cast<long long>(h) * q_stride;
-  else src_off = static_cast<long long>(Hq) * q_stride + static_cast<long long>(h - Hq) * D;
+  if (h < Hq) src_off = (h / G) * grp_stride + static_cast<long long>(h % G) * q_stride;
+  else if (h < Hq + Hkv) src_off = (h - Hq) * grp_stride + static_cast<long long>(G) * q_stride;
+  else src_off = (h - Hq - Hkv) * grp_stride + static_cast<long long>(G) * q_stride + D;
   const __nv_bfloat16* src = qkv + static_cast<size_t>(t) * ldqkv + src_off;
   BF8 a;
   if (lane < nact) a = reinterpret_cast<const BF8*>(src)[lane];
@@ -225,7 +231,9 @@ swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ in, const __nv_bfloat16* __r
 // used for the output gate of gated attention. a: [T, H*D] ; g read from qkv block layout.
 __global__ void __launch_bounds__(256)
 sigmoid_gate_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ qkv, long long ldqkv,
-                    __nv_bfloat16* __restrict__ out, long long T, int Hq, int D) {
+                    __nv_bfloat16* __restrict__ out, long long T, int Hq, int Hkv, int D) {
+  const int G = Hq / Hkv;
+  const long long grp_stride = static_cast<long long>(G) * 2 * D + 2 * D;
   const long long nvec_row = static_cast<long long>(Hq) * D >> 3;
   const long long total = T * nvec_row;
   const int vec_per_head = D >> 3;
@@ -236,7 +244,8 @@ sigmoid_gate_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __
     const int h = static_cast<int>(v / vec_per_head);
     const int vv = static_cast<int>(v % vec_per_head);
     const BF8 x = reinterpret_cast<const BF8*>(a + t * Hq * D)[v];
-    const BF8 g = reinterpret_cast<const BF8*>(qkv + t * ldqkv + static_cast<long long>(h) * 2 * D + D)[vv];
+    const BF8 g = reinterpret_cast<const BF8*>(qkv + t * ldqkv + (h / G) * grp_stride +
+                                                static_cast<long long>(h % G) * 2 * D + D)[vv];
     BF8 o;
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
@@ -373,14 +382,14 @@ IX_API int ix_swiglu_bwd(const void* in, const void* dout, void* din, long long 
   return 0;
 }
 
-IX_API int ix_sigmoid_gate(const void* a, const void* qkv, long long ldqkv, void* out, long long T, int Hq, int D,
-                           void* stream) {
+IX_API int ix_sigmoid_gate(const void* a, const void* qkv, long long ldqkv, void* out, long long T, int Hq, int Hkv,
+                           int D, void* stream) {
   if (T <= 0) return 0;
   if ((D & 7) || (ldqkv & 7)) return ixh::fail(ixh::IX_EARG, "sigmoid_gate: D and ldqkv must be multiples of 8");
   sigmoid_gate_kernel<<<grid_1d(T * (static_cast<long long>(Hq) * D >> 3), 256), 256, 0,
                         reinterpret_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(a), static_cast<const __nv_bfloat16*>(qkv), ldqkv,
-      static_cast<__nv_bfloat16*>(out), T, Hq, D);
+      static_cast<__nv_bfloat16*>(out), T, Hq, Hkv, D);
   IX_CUDA(cudaGetLastError());
   return 0;
 }

@@ -167,8 +167,12 @@ void qk_norm_rope(const T* qkv, long long ldqkv, const int* positions, const lon
 #pragma omp parallel for schedule(static)
   for (long long wid = 0; wid < static_cast<long long>(Tn) * Htot; ++wid) {
     const int t = static_cast<int>(wid / Htot), h = static_cast<int>(wid % Htot);
-    const long long src_off = h < Hq ? static_cast<long long>(h) * q_stride
-                                     : static_cast<long long>(Hq) * q_stride + static_cast<long long>(h - Hq) * D;
+    const int G = Hq / Hkv;
+    const long long grp_stride = static_cast<long long>(G) * q_stride + 2 * D;
+    long long src_off;
+    if (h < Hq) src_off = (h / G) * grp_stride + static_cast<long long>(h % G) * q_stride;
+    else if (h < Hq + Hkv) src_off = (h - Hq) * grp_stride + static_cast<long long>(G) * q_stride;
+    else src_off = (h - Hq - Hkv) * grp_stride + static_cast<long long>(G) * q_stride + D;
     const T* src = qkv + t * ldqkv + src_off;
     const long long slot = slots ? slots[t] : t;
     if (h >= Hq + Hkv) {
@@ -231,12 +235,14 @@ void swiglu(const T* in, T* out, long long Tn, int F, long long ld_in) {
 }
 
 template <typename T>
-void sigmoid_gate(const T* a, const T* qkv, long long ldqkv, T* out, long long Tn, int Hq, int D) {
+void sigmoid_gate(const T* a, const T* qkv, long long ldqkv, T* out, long long Tn, int Hq, int Hkv, int D) {
+  const int G = Hq / Hkv;
+  const long long grp_stride = static_cast<long long>(G) * 2 * D + 2 * D;
 #pragma omp parallel for schedule(static)
   for (long long t = 0; t < Tn; ++t)
     for (int h = 0; h < Hq; ++h)
       for (int i = 0; i < D; ++i) {
-        const float g = ld(qkv, t * ldqkv + static_cast<long long>(h) * 2 * D + D + i);
+        const float g = ld(qkv, t * ldqkv + (h / G) * grp_stride + static_cast<long long>(h % G) * 2 * D + D + i);
         const float s = rnd<T>(1.0f / (1.0f + expf(-g)));
         const long long o = (t * Hq + h) * D + i;
         st(out, o, ld(a, o) * s);
@@ -521,9 +527,9 @@ IXC_API void ixc_swiglu(const void* in, void* out, long long Tn, int F, long lon
   DISPATCH(dtype, swiglu(static_cast<const T*>(in), static_cast<T*>(out), Tn, F, ld_in));
 }
 
-IXC_API void ixc_sigmoid_gate(const void* a, const void* qkv, long long ldqkv, void* out, long long Tn, int Hq, int D,
-                              int dtype) {
-  DISPATCH(dtype, sigmoid_gate(static_cast<const T*>(a), static_cast<const T*>(qkv), ldqkv, static_cast<T*>(out), Tn, Hq, D));
+IXC_API void ixc_sigmoid_gate(const void* a, const void* qkv, long long ldqkv, void* out, long long Tn, int Hq, int Hkv,
+                              int D, int dtype) {
+  DISPATCH(dtype, sigmoid_gate(static_cast<const T*>(a), static_cast<const T*>(qkv), ldqkv, static_cast<T*>(out), Tn, Hq, Hkv, D));
 }
 
 IXC_API void ixc_gated_outnorm(const void* o, const void* z, const void* w, void* out, long long rows, int D, float eps,

@@ -1,0 +1,77 @@
+"""Paged KV cache: a pool of 128-slot pages per attention layer plus a page allocator.
+
+One page == one key block of the attention kernel (ops/functional.PAGE), so a block table
+row is exactly the list of TMA row coordinates the kernel walks. Pools are zero-initialised
+and re-zeroed on wake-up: a masked key still enters P*V with weight 0, so stale bytes must be
+finite (csrc/attention_tcgen05.cu).
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ..models.config import ModelConfig
+from ..ops.functional import PAGE
+
+
+class PageAllocator:
+    def __init__(self, num_pages: int):
+        self.num_pages = num_pages
+        self.free = list(range(num_pages - 1, -1, -1))
+
+    def can_alloc(self, n: int) -> bool:
+        return len(self.free) >= n
+
+    def alloc(self, n: int) -> list[int]:
+        if len(self.free) < n:
+            raise RuntimeError(f"out of KV pages: want {n}, have {len(self.free)}")
+        return [self.free.pop() for _ in range(n)]
+
+    def release(self, pages: list[int]) -> None:
+        self.free.extend(reversed(pages))
+
+    @property
+    def num_free(self) -> int:
+        return len(self.free)
+
+
+class KVCache:
+    """Per attention layer (k_pool, v_pool), each [num_pages*PAGE, Hkv_local, D]; GDN layers get
+    ``None`` here (their state lives in ``engine.gdn_state``)."""
+
+    def __init__(self, cfg: ModelConfig, num_pages: int, device, tp: int = 1, layer_ids: list[int] | None = None):
+        self.cfg = cfg
+        self.num_pages = num_pages
+        self.device = torch.device(device)
+        self.hkv = max(1, cfg.num_kv_heads // tp)
+        self.layer_ids = list(layer_ids if layer_ids is not None else range(cfg.num_layers))
+        self.allocator = PageAllocator(num_pages)
+        self.pools: list | None = None
+        self.wake()
+
+    @staticmethod
+    def bytes_per_page(cfg: ModelConfig, tp: int = 1) -> int:
+        n_attn = sum(1 for i in range(cfg.num_layers) if cfg.layer_type(i) == "attn")
+        elt = 2 if cfg.dtype == "bfloat16" else 4
+        return n_attn * 2 * PAGE * max(1, cfg.num_kv_heads // tp) * cfg.head_dim * elt
+
+    def wake(self) -> None:
+        if self.pools is not None:
+            return
+        dt = self.cfg.torch_dtype
+        shape = (self.num_pages * PAGE, self.hkv, self.cfg.head_dim)
+        self.pools = [
+            (torch.zeros(shape, dtype=dt, device=self.device), torch.zeros(shape, dtype=dt, device=self.device))
+            if self.cfg.layer_type(i) == "attn" else None
+            for i in self.layer_ids
+        ]
+
+    def sleep(self) -> None:
+        """Drop the pools (their memory returns to the allocator for the trainer); contents are
+        never needed after a rollout phase ends."""
+        self.pools = None
+        self.allocator = PageAllocator(self.num_pages)
+
+    def slots_for(self, pages: list[int], start: int, n: int) -> list[int]:
+        """Slots of positions start .. start+n-1 of a sequence whose pages are ``pages``."""
+        return [pages[p // PAGE] * PAGE + p % PAGE for p in range(start, start + n)]

@@ -1,0 +1,308 @@
+"""Rollout engine: continuous batching over a paged KV cache, running the SAME ``DecoderLM``
+the trainer runs (the reference needs vLLM + a Megatron-in-vLLM wrapper for this,
+ISO/runtimes/vllm/gptmodel_vllm.py:642-721; here the engine is ~400 lines around the shared model).
+
+A step is one forward over a flat token batch: the decode tokens of running sequences first,
+then (chunked) prefill tokens of admitted sequences, up to ``max_num_batched_tokens``. Every
+token goes through the same kernels whatever the mix, which is what makes a token's logprob
+independent of the batch it was computed in.
+"""
+
+from __future__ import annotations
+
+import time
+from collections import deque
+from dataclasses import dataclass, field
+
+import torch
+
+from ..models.decoder import DecoderLM, ForwardCtx
+from ..ops import functional as F
+from ..ops.functional import PAGE
+from .kv_cache import KVCache
+from .sampler import Sampler, SamplingParams
+
+
+@dataclass
+class EngineConfig:
+    max_num_seqs: int = 1024
+    max_num_batched_tokens: int = 8192
+    num_kv_pages: int = 0                # 0 = size from gpu_memory_utilization
+    gpu_memory_utilization: float = 0.8
+    max_model_len: int = 0               # 0 = model max_position
+    eos_token_id: int | None = None
+    seed: int = 0
+    enable_prefix_caching: bool = False  # the contract pins this off (state claim engine_prefix_cache)
+    use_cuda_graph: bool = True
+
+
+@dataclass
+class Sequence:
+    seq_id: int
+    prompt_ids: list[int]
+    params: SamplingParams
+    output_ids: list[int] = field(default_factory=list)
+    logprobs: list[float] = field(default_factory=list)
+    pages: list[int] = field(default_factory=list)
+    num_computed: int = 0          # tokens whose K/V are in the cache
+    finished: bool = False
+    stop_reason: str | None = None
+    request_index: int = 0
+    arrival: float = 0.0
+
+    @property
+    def tokens(self) -> list[int]:
+        return self.prompt_ids + self.output_ids
+
+    @property
+    def length(self) -> int:
+        return len(self.prompt_ids) + len(self.output_ids)
+
+
+@dataclass
+class RequestOutput:
+    prompt_ids: list[int]
+    response_ids: list[int]
+    response_logprobs: list[float]
+    stop_reason: str
+
+
+class Scheduler:
+    """Decode-first continuous batching with chunked prefill and recompute-preemption."""
+
+    def __init__(self, cfg: EngineConfig, cache: KVCache):
+        self.cfg = cfg
+        self.cache = cache
+        self.waiting: deque[Sequence] = deque()
+        self.running: list[Sequence] = []
+
+    def add(self, seq: Sequence) -> None:
+        self.waiting.append(seq)
+
+    def has_work(self) -> bool:
+        return bool(self.waiting or self.running)
+
+    def _ensure_pages(self, seq: Sequence, upto: int) -> bool:
+        need = (upto + PAGE - 1) // PAGE - len(seq.pages)
+        if need <= 0:
+            return True
+        if not self.cache.allocator.can_alloc(need):
+            return False
+        seq.pages += self.cache.allocator.alloc(need)
+        return True
+
+    def _preempt(self, seq: Sequence) -> None:
+        self.cache.allocator.release(seq.pages)
+        seq.pages = []
+        seq.num_computed = 0
+        self.waiting.appendleft(seq)
+
+    def schedule(self):
+        """Returns (decode_seqs, prefill list of (seq, start, n))."""
+        budget = self.cfg.max_num_batched_tokens
+        decode: list[Sequence] = []
+        # running sequences that have their whole context cached decode one token
+        running = [s for s in self.running if s.num_computed == s.length - 1]
+        still_prefilling = [s for s in self.running if s.num_computed < s.length - 1]
+        for s in running:
+            while not self._ensure_pages(s, s.length):
+                victims = [v for v in self.running if v is not s and v not in decode]
+                if not victims:
+                    raise RuntimeError("KV cache too small for a single sequence")
+                v = victims[-1]
+                self.running.remove(v)
+                if v in still_prefilling:
+                    still_prefilling.remove(v)
+                self._preempt(v)
+            if s in self.running:
+                decode.append(s)
+                budget -= 1
+        prefill = []
+        for s in still_prefilling:
+            if budget <= 0:
+                break
+            n = min(s.length - s.num_computed, budget)
+            if not self._ensure_pages(s, s.num_computed + n):
+                continue
+            prefill.append((s, s.num_computed, n))
+            budget -= n
+        while self.waiting and budget > 0 and len(self.running) < self.cfg.max_num_seqs:
+            s = self.waiting[0]
+            n = min(s.length - s.num_computed, budget)
+            if not self._ensure_pages(s, s.num_computed + n):
+                break
+            self.waiting.popleft()
+            self.running.append(s)
+            prefill.append((s, s.num_computed, n))
+            budget -= n
+        return decode, prefill
+
+    def finish(self, seq: Sequence) -> None:
+        self.cache.allocator.release(seq.pages)
+        seq.pages = []
+        self.running.remove(seq)
+
+
+class LLMEngine:
+    def __init__(self, model: DecoderLM, cfg: EngineConfig | None = None):
+        self.model = model
+        self.mcfg = model.cfg
+        self.cfg = cfg or EngineConfig()
+        self.device = model.device_
+        self.max_len = self.cfg.max_model_len or self.mcfg.max_position
+        n_pages = self.cfg.num_kv_pages or self._auto_pages()
+        self.cache = KVCache(self.mcfg, n_pages, self.device, tp=model.ps.tp, layer_ids=model.layer_ids)
+        self.scheduler = Scheduler(self.cfg, self.cache)
+        self.sampler = Sampler(self.device, self.cfg.seed, self.mcfg.logprob_leaves)
+        self._next_id = 0
+        self.paused = False
+        self.asleep = False
+        self.stats = {"steps": 0, "tokens": 0, "prefill_tokens": 0, "decode_tokens": 0, "preemptions": 0}
+        self.gdn_state = None
+        if self.mcfg.has_gdn:
+            from .gdn_state import GDNStatePool
+
+            self.gdn_state = GDNStatePool(self.mcfg, self.cfg.max_num_seqs, self.device, tp=model.ps.tp)
+
+    def _auto_pages(self) -> int:
+        per_page = KVCache.bytes_per_page(self.mcfg, self.model.ps.tp)
+        if per_page == 0:
+            return 1
+        if self.device.type == "cuda":
+            free, _total = torch.cuda.mem_get_info(self.device)
+            budget = int(free * self.cfg.gpu_memory_utilization)
+        else:
+            budget = 256 << 20
+        want = self.cfg.max_num_seqs * ((self.max_len + PAGE - 1) // PAGE)
+        return max(2, min(want, budget // per_page))
+
+    # ------------------------------------------------------------------ lifecycle
+    def sleep(self, tags: list[str] | None = None) -> None:
+        """Release the KV pools (and recurrent state). Weights stay resident."""
+        assert not self.scheduler.has_work(), "sleep with requests in flight"
+        self.cache.sleep()
+        if self.gdn_state is not None:
+            self.gdn_state.invalidate("sleep_wake")
+        self.asleep = True
+
+    def wake_up(self, tags: list[str] | None = None) -> None:
+        self.cache.wake()
+        self.asleep = False
+
+    def reset_prefix_cache(self) -> None:
+        """No prefix cache is kept (pinned off by the contract); recurrent state is dropped."""
+        if self.gdn_state is not None:
+            self.gdn_state.invalidate("weight_sync")
+
+    def pause_generation(self) -> None:
+        self.paused = True
+
+    def resume_generation(self) -> None:
+        self.paused = False
+
+    # ------------------------------------------------------------------ requests
+    def add_request(self, prompt_ids: list[int], params: SamplingParams, request_index: int = 0) -> Sequence:
+        if len(prompt_ids) == 0:
+            raise ValueError("empty prompt")
+        if len(prompt_ids) >= self.max_len:
+            raise ValueError(f"prompt of {len(prompt_ids)} tokens exceeds max_model_len={self.max_len}")
+        seq = Sequence(self._next_id, list(prompt_ids), params, request_index=request_index, arrival=time.time())
+        self._next_id += 1
+        self.scheduler.add(seq)
+        return seq
+
+    @torch.no_grad()
+    def step(self) -> list[Sequence]:
+        """Run one scheduler step; returns the sequences that finished in it."""
+        decode, prefill = self.scheduler.schedule()
+        if not decode and not prefill:
+            return []
+        G = self.model.hq // self.model.hkv
+        tq = PAGE // G
+        ids, pos, slots, items, bt_rows, sample_rows, sample_seqs = [], [], [], [], [], [], []
+        row = 0
+        for s in decode:
+            p = s.length - 1
+            ids.append(s.tokens[-1])
+            pos.append(p)
+            slots.append(s.pages[p // PAGE] * PAGE + p % PAGE)
+            items.append((row, 1, p, p + 1, len(bt_rows), 0, 0, 0))
+            bt_rows.append(s.pages)
+            sample_rows.append(row)
+            sample_seqs.append(s)
+            row += 1
+        for s, start, n in prefill:
+            toks = s.tokens
+            ids += toks[start:start + n]
+            pos += range(start, start + n)
+            slots += self.cache.slots_for(s.pages, start, n)
+            bt = len(bt_rows)
+            bt_rows.append(s.pages)
+            for t0 in range(0, n, tq):
+                items.append((row + t0, min(tq, n - t0), start + t0, start + n, bt, 0, 0, 0))
+            if start + n == s.length:
+                sample_rows.append(row + n - 1)
+                sample_seqs.append(s)
+            row += n
+        dev = self.device
+        maxp = max(len(b) for b in bt_rows)
+        bt = torch.zeros(len(bt_rows), maxp, dtype=torch.int32)
+        for i, b in enumerate(bt_rows):
+            bt[i, :len(b)] = torch.tensor(b, dtype=torch.int32)
+        fc = ForwardCtx(
+            positions=torch.tensor(pos, dtype=torch.int32).to(dev, non_blocking=True),
+            meta=F.AttnMeta(torch.tensor(items, dtype=torch.int32).reshape(-1, 8).to(dev, non_blocking=True),
+                            bt.to(dev, non_blocking=True)),
+            slots=torch.tensor(slots, dtype=torch.int64).to(dev, non_blocking=True),
+            kv=self.cache.pools,
+            site="engine_decode" if not prefill else "engine_prefill",
+        )
+        if self.gdn_state is not None:
+            fc.gdn_meta = self.gdn_state.step_meta(decode, prefill)
+            fc.kv = self.gdn_state.merge_into(self.cache.pools)
+        hidden = self.model(torch.tensor(ids, dtype=torch.int64).to(dev, non_blocking=True), fc)
+        for s in decode:
+            s.num_computed += 1
+        for s, start, n in prefill:
+            s.num_computed = start + n
+        self.stats["steps"] += 1
+        self.stats["tokens"] += row
+        self.stats["decode_tokens"] += len(decode)
+        self.stats["prefill_tokens"] += row - len(decode)
+        finished: list[Sequence] = []
+        if sample_rows:
+            rows = torch.tensor(sample_rows, dtype=torch.int64).to(dev)
+            logits = self.model.logits(hidden.index_select(0, rows))
+            if self.model.ps.tp > 1:
+                from ..parallel.tp import column_parallel_gather
+
+                logits = column_parallel_gather(logits, self.model.ps)
+            tokens, lps = self.sampler(logits, [s.params for s in sample_seqs])
+            tokens, lps = tokens.tolist(), lps.tolist()
+            for s, tok, lp in zip(sample_seqs, tokens, lps):
+                s.output_ids.append(tok)
+                s.logprobs.append(lp)
+                eos = self.cfg.eos_token_id
+                if (not s.params.ignore_eos and eos is not None and tok == eos) or tok in s.params.stop_token_ids:
+                    s.finished, s.stop_reason = True, "stop"
+                elif len(s.output_ids) >= s.params.max_generate_length or s.length >= self.max_len:
+                    s.finished, s.stop_reason = True, "length"
+                if s.finished:
+                    if self.gdn_state is not None:
+                        self.gdn_state.release(s.seq_id)
+                    self.scheduler.finish(s)
+                    finished.append(s)
+        return finished
+
+    def generate(self, prompts: list[list[int]], params: SamplingParams | list[SamplingParams]) -> list[RequestOutput]:
+        """Blocking batch generation; outputs are in prompt order."""
+        if self.asleep:
+            raise RuntimeError("engine is asleep; call wake_up() first")
+        plist = params if isinstance(params, list) else [params] * len(prompts)
+        seqs = [self.add_request(p, sp, i) for i, (p, sp) in enumerate(zip(prompts, plist))]
+        while self.scheduler.has_work():
+            if self.paused:
+                time.sleep(0.001)
+                continue
+            self.step()
+        return [RequestOutput(s.prompt_ids, s.output_ids, s.logprobs, s.stop_reason or "length") for s in seqs]

@@ -1,0 +1,97 @@
+"""Token sampling and the rollout log-probabilities.
+
+The log-probability reported for a sampled token is always the one of the RAW logits
+(vLLM's ``raw_logprobs`` mode, which the reference forces under IsoExec,
+ISO/runtimes/vllm/vllm_patches.py:388), computed by the same fixed-leaf kernel the trainer
+scores with (ops/functional.token_logprobs). Temperature / top-k / top-p / min-p only shape
+the distribution the token is drawn from; drawing uses the Gumbel-max trick so one
+generator seed fixes the whole rollout.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import torch
+
+from ..ops import functional as F
+
+
+@dataclass
+class SamplingParams:
+    max_generate_length: int = 1024
+    temperature: float = 1.0
+    top_p: float = 1.0
+    top_k: int = -1
+    min_p: float = 0.0
+    repetition_penalty: float = 1.0
+    logprobs: int | None = 1
+    stop_token_ids: tuple[int, ...] = ()
+    ignore_eos: bool = False
+    seed: int | None = None
+    n: int = 1
+    additional_kwargs: dict = field(default_factory=dict)
+
+    @staticmethod
+    def from_dict(d: dict | None) -> "SamplingParams":
+        d = dict(d or {})
+        if "max_tokens" in d:
+            d["max_generate_length"] = d.pop("max_tokens")
+        if "stop" in d:
+            d.pop("stop")
+        known = {k: v for k, v in d.items() if k in SamplingParams.__dataclass_fields__}
+        if "stop_token_ids" in known and known["stop_token_ids"] is not None:
+            known["stop_token_ids"] = tuple(known["stop_token_ids"])
+        return SamplingParams(**known)
+
+
+def isoexec_sampling_constraints(p: SamplingParams) -> SamplingParams:
+    """Under the execution contract the importance ratio is exactly 1 only if the behaviour policy
+    is the raw model distribution: temperature 1 and no truncation."""
+    if p.temperature != 1.0 or p.top_p != 1.0 or p.top_k not in (-1, 0) or p.min_p != 0.0:
+        raise ValueError("IsoExec rollouts require temperature=1.0, top_p=1.0, top_k=-1, min_p=0.0")
+    return p
+
+
+class Sampler:
+    def __init__(self, device, seed: int = 0, leaves: int = F.DEFAULT_LEAVES):
+        self.device = torch.device(device)
+        self.gen = torch.Generator(device=self.device)
+        self.gen.manual_seed(seed)
+        self.leaves = leaves
+
+    def reseed(self, seed: int) -> None:
+        self.gen.manual_seed(seed)
+
+    @torch.no_grad()
+    def __call__(self, logits: torch.Tensor, params: list[SamplingParams]):
+        """logits [n, V] -> (token ids int64 [n], raw logprobs fp32 [n])."""
+        n, V = logits.shape
+        x = logits.float()
+        uniform = all(p.temperature == 1.0 and p.top_p >= 1.0 and p.top_k <= 0 and p.min_p <= 0.0 for p in params)
+        if not uniform:
+            x = x.clone()
+            for i, p in enumerate(params):
+                if p.temperature == 0.0:
+                    continue
+                row = x[i] / p.temperature
+                if p.top_k and p.top_k > 0 and p.top_k < V:
+                    kth = torch.topk(row, p.top_k).values[-1]
+                    row = row.masked_fill(row < kth, float("-inf"))
+                if p.min_p > 0.0:
+                    probs = torch.softmax(row, -1)
+                    row = row.masked_fill(probs < p.min_p * probs.max(), float("-inf"))
+                if p.top_p < 1.0:
+                    sp, si = torch.sort(torch.softmax(row, -1), descending=True)
+                    keep = (sp.cumsum(-1) - sp) < p.top_p
+                    mask = torch.ones_like(row, dtype=torch.bool)
+                    mask[si[keep]] = False
+                    row = row.masked_fill(mask, float("-inf"))
+                x[i] = row
+        u = torch.rand(x.shape, device=x.device, dtype=torch.float32, generator=self.gen)
+        gumbel = -torch.log(-torch.log(u.clamp_min(1e-20)).clamp_min(1e-20))
+        greedy = torch.tensor([p.temperature == 0.0 for p in params], device=x.device)
+        noisy = torch.where(greedy[:, None], x, x + gumbel)
+        tokens = noisy.argmax(-1)
+        logprobs, _ = F.token_logprobs(logits, tokens, self.leaves)
+        return tokens, logprobs

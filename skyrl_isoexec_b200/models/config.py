@@ -1,0 +1,142 @@
+"""Model configurations: one dataclass covers the four families the framework runs
+(dense Qwen3, Qwen3-MoE, hybrid GatedDeltaNet, and tiny variants of each for tests)."""
+
+from __future__ import annotations
+
+from dataclasses import asdict, dataclass, field, replace
+
+import torch
+
+
+@dataclass(frozen=True)
+class ModelConfig:
+    name: str
+    architecture: str  # HF-style architecture string, keys the execution-contract profile
+    vocab_size: int
+    hidden_size: int
+    num_layers: int
+    num_q_heads: int
+    num_kv_heads: int
+    head_dim: int
+    ffn_size: int
+    rope_theta: float = 1e6
+    rms_eps: float = 1e-6
+    tie_embeddings: bool = False
+    qk_norm: bool = True
+    max_position: int = 8192
+    dtype: str = "bfloat16"
+    # --- MoE (num_experts == 0 -> dense MLP)
+    num_experts: int = 0
+    top_k: int = 0
+    moe_ffn_size: int = 0
+    router: str = "softmax"  # "softmax" | "sigmoid_bias"
+    norm_topk_prob: bool = True
+    shared_expert_ffn: int = 0
+    # --- hybrid GatedDeltaNet
+    layer_types: tuple[str, ...] = ()  # per layer "attn" | "gdn"; empty = all attention
+    gdn_k_heads: int = 0
+    gdn_v_heads: int = 0
+    gdn_head_dim: int = 0
+    gdn_conv_kernel: int = 4
+    gdn_chunk: int = 64
+    attn_output_gate: bool = False
+    zero_centered_norm: bool = False
+    partial_rotary_factor: float = 1.0
+    # --- numerics pins that enter the execution contract
+    logprob_leaves: int = 8
+    pik_leaves: int = 8
+    tp_invariant: bool = False  # row-parallel K reductions use the leaf tree so any TP | pik_leaves gives equal bits
+
+    @property
+    def torch_dtype(self) -> torch.dtype:
+        return {"bfloat16": torch.bfloat16, "float32": torch.float32}[self.dtype]
+
+    @property
+    def rot_dim(self) -> int:
+        r = int(self.head_dim * self.partial_rotary_factor)
+        return r - (r % 16) if r % 16 else r
+
+    @property
+    def has_moe(self) -> bool:
+        return self.num_experts > 0
+
+    @property
+    def has_gdn(self) -> bool:
+        return any(t == "gdn" for t in self.layer_types)
+
+    def layer_type(self, i: int) -> str:
+        return self.layer_types[i] if self.layer_types else "attn"
+
+    def to_dict(self) -> dict:
+        d = asdict(self)
+        d["layer_types"] = list(self.layer_types)
+        return d
+
+    @staticmethod
+    def from_dict(d: dict) -> "ModelConfig":
+        d = dict(d)
+        d["layer_types"] = tuple(d.get("layer_types", ()))
+        return ModelConfig(**d)
+
+    def with_(self, **kw) -> "ModelConfig":
+        return replace(self, **kw)
+
+    def param_count(self) -> int:
+        h, L = self.hidden_size, self.num_layers
+        attn = h * (self.num_q_heads * (2 if self.attn_output_gate else 1) + 2 * self.num_kv_heads) * self.head_dim \
+            + self.num_q_heads * self.head_dim * h
+        if self.has_moe:
+            mlp = self.num_experts * 3 * h * self.moe_ffn_size + h * self.num_experts + 3 * h * self.shared_expert_ffn
+        else:
+            mlp = 3 * h * self.ffn_size
+        emb = self.vocab_size * h * (1 if self.tie_embeddings else 2)
+        return L * (attn + mlp) + emb
+
+
+def _hybrid_pattern(n: int) -> tuple[str, ...]:
+    return tuple("attn" if (i % 4) == 3 else "gdn" for i in range(n))
+
+
+PRESETS: dict[str, ModelConfig] = {
+    # BASELINE config 1: tiny Qwen3-style decoder for the CPU/gloo run
+    "tiny-qwen3": ModelConfig(
+        name="tiny-qwen3", architecture="Qwen3ForCausalLM", vocab_size=2048, hidden_size=256, num_layers=2,
+        num_q_heads=4, num_kv_heads=2, head_dim=64, ffn_size=768, tie_embeddings=True, dtype="float32",
+        max_position=512),
+    "qwen3-8b": ModelConfig(
+        name="qwen3-8b", architecture="Qwen3ForCausalLM", vocab_size=151936, hidden_size=4096, num_layers=36,
+        num_q_heads=32, num_kv_heads=8, head_dim=128, ffn_size=12288, max_position=40960),
+    "qwen3-32b": ModelConfig(
+        name="qwen3-32b", architecture="Qwen3ForCausalLM", vocab_size=151936, hidden_size=5120, num_layers=64,
+        num_q_heads=64, num_kv_heads=8, head_dim=128, ffn_size=25600, max_position=40960),
+    "qwen3-30b-a3b": ModelConfig(
+        name="qwen3-30b-a3b", architecture="Qwen3MoeForCausalLM", vocab_size=151936, hidden_size=2048, num_layers=48,
+        num_q_heads=32, num_kv_heads=4, head_dim=128, ffn_size=0, num_experts=128, top_k=8, moe_ffn_size=768,
+        max_position=40960),
+    # BASELINE config 4: hybrid [GDN, GDN, GDN, gated attention] x 8
+    "qwen3.5-hybrid": ModelConfig(
+        name="qwen3.5-hybrid", architecture="Qwen3NextForCausalLM", vocab_size=151936, hidden_size=2560,
+        num_layers=32, num_q_heads=16, num_kv_heads=4, head_dim=128, ffn_size=9216,
+        layer_types=_hybrid_pattern(32), gdn_k_heads=16, gdn_v_heads=32, gdn_head_dim=128, attn_output_gate=True,
+        zero_centered_norm=True, max_position=40960),
+    # small variants used by tests and smoke runs
+    "tiny-qwen3-bf16": ModelConfig(
+        name="tiny-qwen3-bf16", architecture="Qwen3ForCausalLM", vocab_size=2048, hidden_size=256, num_layers=2,
+        num_q_heads=4, num_kv_heads=2, head_dim=128, ffn_size=768, tie_embeddings=False, max_position=1024),
+    "tiny-moe": ModelConfig(
+        name="tiny-moe", architecture="Qwen3MoeForCausalLM", vocab_size=2048, hidden_size=256, num_layers=2,
+        num_q_heads=4, num_kv_heads=2, head_dim=64, ffn_size=0, num_experts=8, top_k=2, moe_ffn_size=128,
+        dtype="float32", max_position=512),
+    "tiny-hybrid": ModelConfig(
+        name="tiny-hybrid", architecture="Qwen3NextForCausalLM", vocab_size=2048, hidden_size=256, num_layers=4,
+        num_q_heads=4, num_kv_heads=2, head_dim=64, ffn_size=512, layer_types=_hybrid_pattern(4), gdn_k_heads=2,
+        gdn_v_heads=4, gdn_head_dim=64, attn_output_gate=True, zero_centered_norm=True, dtype="float32",
+        max_position=512),
+}
+
+
+def get_config(name: str, **overrides) -> ModelConfig:
+    if name not in PRESETS:
+        raise KeyError(f"unknown model preset {name!r}; known: {sorted(PRESETS)}")
+    cfg = PRESETS[name]
+    return cfg.with_(**overrides) if overrides else cfg

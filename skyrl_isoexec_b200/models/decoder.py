@@ -1,0 +1,308 @@
+"""The one model definition both runtimes execute.
+
+The reference reaches "same function on both sides" by running Megatron's ``GPTModel`` inside
+vLLM (ISO/runtimes/vllm/gptmodel_vllm.py:217-222,278-408). Here trainer and rollout engine
+instantiate this class directly, so the unified model is structural: the forward below is
+the only forward there is, and the only difference between the sites is where K/V live
+(fresh packed tensors with autograd for ``trainer_fwd``; a paged slot pool for the engine
+sites and for ``trainer_score`` when it chooses to).
+
+Weights live in ONE flat buffer per rank (``ParamStore``), Megatron-style, so that the
+optimizer, the DP gradient reduction and the trainer->rollout weight sync each work on a
+single contiguous range instead of hundreds of tensors.
+"""
+
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+import torch.nn as nn
+
+from ..ops import functional as F
+from ..ops import gdn as gdn_ops
+from ..ops import moe as moe_ops
+from ..parallel.state import ParallelState
+from ..parallel import tp as tp_ops
+from .config import ModelConfig
+
+
+# ------------------------------------------------------------------------------------ parameters
+@dataclass
+class ParamSpec:
+    name: str
+    shape: tuple[int, ...]       # local (sharded) shape
+    full_shape: tuple[int, ...]  # unsharded shape
+    shard_dim: int | None        # dim split over TP (None = replicated)
+    init_std: float | None       # None = ones (norm weights), 0.0 = zeros
+    offset: int = 0
+    ep_sharded: bool = False     # leading expert dim split over EP
+    sections: tuple[int, ...] = ()  # sizes of the blocks on shard_dim that are each split over TP
+
+
+class ParamStore:
+    """Flat parameter storage. ``flat`` holds every local parameter back to back (each start
+    aligned to 128 elements so TMA bases stay 16-byte aligned); ``views[name]`` are the tensors
+    the model computes with."""
+
+    ALIGN = 128
+
+    def __init__(self, specs: list[ParamSpec], dtype: torch.dtype, device):
+        off = 0
+        for s in specs:
+            s.offset = off
+            n = math.prod(s.shape)
+            off += (n + self.ALIGN - 1) // self.ALIGN * self.ALIGN
+        self.specs = {s.name: s for s in specs}
+        self.order = [s.name for s in specs]
+        self.numel = off
+        self.flat = torch.zeros(off, dtype=dtype, device=device)
+        self.views = {s.name: self.flat[s.offset:s.offset + math.prod(s.shape)].view(s.shape) for s in specs}
+
+    def init_weights(self, seed: int, tp_rank: int = 0, tp: int = 1, ep_rank: int = 0, ep: int = 1) -> None:
+        """Deterministic init: every parameter is drawn at FULL shape from a generator seeded by
+        (seed, parameter index) and then sliced, so any TP/EP layout holds the same model."""
+        for i, name in enumerate(self.order):
+            s = self.specs[name]
+            v = self.views[name]
+            if s.init_std is None:
+                v.fill_(1.0)
+                continue
+            if s.init_std == 0.0:
+                v.zero_()
+                continue
+            g = torch.Generator(device="cpu").manual_seed(seed * 1000003 + i)
+            full = torch.empty(s.full_shape, dtype=torch.float32).normal_(0.0, s.init_std, generator=g)
+            v.copy_(shard_of(full, s, tp_rank, tp, ep_rank, ep).to(v.dtype))
+
+
+def shard_of(full: torch.Tensor, s: ParamSpec, tp_rank: int, tp: int, ep_rank: int = 0, ep: int = 1) -> torch.Tensor:
+    """Slice a full-shape tensor to the local shard described by ``s``."""
+    t = full
+    if s.ep_sharded and ep > 1:
+        e = t.shape[0] // ep
+        t = t[ep_rank * e:(ep_rank + 1) * e]
+    if s.shard_dim is not None and tp > 1:
+        secs = s.sections or (t.shape[s.shard_dim],)
+        parts, lo = [], 0
+        for sz in secs:
+            parts.append(t.narrow(s.shard_dim, lo + tp_rank * (sz // tp), sz // tp))
+            lo += sz
+        t = parts[0] if len(parts) == 1 else torch.cat(parts, dim=s.shard_dim)
+    return t
+
+
+def _qkv_rows(cfg: ModelConfig) -> int:
+    return (cfg.num_q_heads * (2 if cfg.attn_output_gate else 1) + 2 * cfg.num_kv_heads) * cfg.head_dim
+
+
+def build_param_specs(cfg: ModelConfig, ps: ParallelState, layer_range: range | None = None) -> list[ParamSpec]:
+    """Parameter inventory of this rank. Column-parallel weights are split on dim 0 by whole
+    heads / FFN columns, row-parallel weights on dim 1; MoE experts on the leading expert dim."""
+    tp, h = ps.tp, cfg.hidden_size
+    std = 0.02
+    out_std = 0.02 / math.sqrt(2 * cfg.num_layers)
+    specs: list[ParamSpec] = []
+
+    def add(name, full_shape, shard_dim, init_std, ep_sharded=False, sections=()):
+        shape = list(full_shape)
+        for sz in sections:
+            assert sz % tp == 0, (name, sections, tp)
+        if ep_sharded and ps.ep > 1:
+            assert shape[0] % ps.ep == 0
+            shape[0] //= ps.ep
+        if shard_dim is not None and tp > 1:
+            assert shape[shard_dim] % tp == 0, (name, full_shape, tp)
+            shape[shard_dim] //= tp
+        specs.append(ParamSpec(name, tuple(shape), tuple(full_shape), shard_dim, init_std, ep_sharded=ep_sharded,
+                               sections=tuple(sections)))
+
+    layers = layer_range if layer_range is not None else range(cfg.num_layers)
+    if ps.is_first_pp or cfg.tie_embeddings:
+        add("embed.weight", (cfg.vocab_size, h), None, std)
+    for i in layers:
+        p = f"layers.{i}."
+        add(p + "ln1.weight", (h,), None, 0.0 if cfg.zero_centered_norm else None)
+        if cfg.layer_type(i) == "attn":
+            # stored head-major per KV group so a TP shard holds whole GQA groups: [q-block | k | v] per shard
+            add(p + "attn.qkv.weight", (_qkv_rows(cfg), h), 0, std)
+            add(p + "attn.o.weight", (h, cfg.num_q_heads * cfg.head_dim), 1, out_std)
+            if cfg.qk_norm:
+                add(p + "attn.q_norm.weight", (cfg.head_dim,), None, 0.0 if cfg.zero_centered_norm else None)
+                add(p + "attn.k_norm.weight", (cfg.head_dim,), None, 0.0 if cfg.zero_centered_norm else None)
+        else:
+            kd, vd = cfg.gdn_k_heads * cfg.gdn_head_dim, cfg.gdn_v_heads * cfg.gdn_head_dim
+            # in_proj rows: [q(kd) | k(kd) | v(vd) | z(vd) | b(Hv) | a(Hv)], split over TP by head
+            add(p + "gdn.in_proj.weight", (2 * kd + 2 * vd + 2 * cfg.gdn_v_heads, h), 0, std,
+                sections=(kd, kd, vd, vd, cfg.gdn_v_heads, cfg.gdn_v_heads))
+            add(p + "gdn.conv.weight", (2 * kd + vd, cfg.gdn_conv_kernel), 0, 0.2, sections=(kd, kd, vd))
+            add(p + "gdn.A_log", (cfg.gdn_v_heads,), 0, 0.0)
+            add(p + "gdn.dt_bias", (cfg.gdn_v_heads,), 0, 0.0)
+            add(p + "gdn.out_norm.weight", (cfg.gdn_head_dim,), None, 0.0 if cfg.zero_centered_norm else None)
+            add(p + "gdn.out_proj.weight", (h, vd), 1, out_std)
+        add(p + "ln2.weight", (h,), None, 0.0 if cfg.zero_centered_norm else None)
+        if cfg.has_moe:
+            E, f = cfg.num_experts, cfg.moe_ffn_size
+            add(p + "moe.router.weight", (E, h), None, std)
+            if cfg.router == "sigmoid_bias":
+                add(p + "moe.router.expert_bias", (E,), None, 0.0)
+            add(p + "moe.experts.gate_up", (E, 2 * f, h), None, std, ep_sharded=True)
+            add(p + "moe.experts.down", (E, h, f), None, out_std, ep_sharded=True)
+            if cfg.shared_expert_ffn:
+                add(p + "moe.shared.gate_up.weight", (2 * cfg.shared_expert_ffn, h), 0, std,
+                    sections=(cfg.shared_expert_ffn, cfg.shared_expert_ffn))
+                add(p + "moe.shared.down.weight", (h, cfg.shared_expert_ffn), 1, out_std)
+        else:
+            add(p + "mlp.gate_up.weight", (2 * cfg.ffn_size, h), 0, std, sections=(cfg.ffn_size, cfg.ffn_size))
+            add(p + "mlp.down.weight", (h, cfg.ffn_size), 1, out_std)
+    if ps.is_last_pp:
+        add("final_norm.weight", (h,), None, 0.0 if cfg.zero_centered_norm else None)
+        if not cfg.tie_embeddings:
+            add("lm_head.weight", (cfg.vocab_size, h), 0, std)
+    return specs
+
+
+# ------------------------------------------------------------------------------------ forward context
+@dataclass
+class ForwardCtx:
+    """Per-call inputs of the forward. ``kv`` is None at the differentiable trainer site
+    (K/V are fresh packed tensors) and a list of per-layer state at the engine sites."""
+
+    positions: torch.Tensor            # int32 [T]
+    meta: F.AttnMeta
+    slots: torch.Tensor | None = None  # int64 [T] slot of each token in the KV pools
+    kv: list | None = None             # per attention layer: (k_pool, v_pool); per GDN layer: GDN state handle
+    gdn_meta: object | None = None     # sequence layout for GDN layers (see ops/gdn.py)
+    site: str = "trainer_fwd"          # trainer_fwd | trainer_score | engine_prefill | engine_decode
+
+
+class DecoderLM(nn.Module):
+    def __init__(self, cfg: ModelConfig, ps: ParallelState | None = None, device="cpu", seed: int = 0,
+                 layer_range: range | None = None, init: bool = True):
+        super().__init__()
+        self.cfg = cfg
+        self.ps = ps or ParallelState.single()
+        self.device_ = torch.device(device)
+        self.layer_ids = list(layer_range if layer_range is not None else range(cfg.num_layers))
+        specs = build_param_specs(cfg, self.ps, layer_range)
+        self.store = ParamStore(specs, cfg.torch_dtype, self.device_)
+        if init:
+            self.store.init_weights(seed, self.ps.tp_rank, self.ps.tp, self.ps.ep_rank, self.ps.ep)
+        self.params = nn.ParameterDict()
+        self._p: dict[str, nn.Parameter] = {}
+        for name in self.store.order:
+            p = nn.Parameter(self.store.views[name], requires_grad=True)
+            self._p[name] = p
+            self.params[name.replace(".", "/")] = p
+        self.rope = F.RopeTable(cfg.rot_dim, cfg.max_position, cfg.rope_theta, self.device_)
+        self.scale = F.softmax_scale(cfg.head_dim)
+        tp = self.ps.tp
+        assert cfg.num_kv_heads % tp == 0 or tp == 1, "TP must divide the KV heads"
+        self.hq, self.hkv = cfg.num_q_heads // tp, cfg.num_kv_heads // tp
+
+    # -------------------------------------------------------------------------------- helpers
+    def p(self, name: str) -> torch.Tensor:
+        return self._p[name]
+
+    def named_weights(self):
+        """(name, local tensor) in storage order, the unit of weight sync and checkpoints."""
+        for name in self.store.order:
+            yield name, self.store.views[name]
+
+    def embed(self, input_ids: torch.Tensor) -> torch.Tensor:
+        return torch.nn.functional.embedding(input_ids, self.p("embed.weight"))
+
+    def lm_head_weight(self) -> torch.Tensor:
+        if self.cfg.tie_embeddings:
+            w = self.p("embed.weight")
+            if self.ps.tp > 1:
+                n = w.shape[0] // self.ps.tp
+                return w[self.ps.tp_rank * n:(self.ps.tp_rank + 1) * n]
+            return w
+        return self.p("lm_head.weight")
+
+    # -------------------------------------------------------------------------------- layers
+    def _attn_block(self, i: int, y: torch.Tensor, fc: ForwardCtx, kv_idx: int) -> torch.Tensor:
+        cfg, pfx = self.cfg, f"layers.{i}.attn."
+        T = y.shape[0]
+        qkv = F.linear(y, self.p(pfx + "qkv.weight"))
+        qw = self.p(pfx + "q_norm.weight") if cfg.qk_norm else None
+        kw = self.p(pfx + "k_norm.weight") if cfg.qk_norm else None
+        if fc.kv is None:
+            q, k, v = F.qk_norm_rope_train(qkv, fc.positions, self.rope, qw, kw, self.hq, self.hkv, cfg.head_dim,
+                                           cfg.rms_eps, cfg.qk_norm, cfg.zero_centered_norm, cfg.attn_output_gate)
+            a = F.attention(q, k, v, fc.meta, self.scale)
+        else:
+            k_pool, v_pool = fc.kv[kv_idx]
+            q = F.qk_norm_rope_fwd(qkv, fc.positions, fc.slots, self.rope, qw, kw, k_pool, v_pool, self.hq, self.hkv,
+                                   cfg.head_dim, cfg.rms_eps, cfg.qk_norm, cfg.zero_centered_norm, cfg.attn_output_gate)
+            a, _ = F.attention_fwd(q, k_pool, v_pool, fc.meta, self.scale)
+        if cfg.attn_output_gate:
+            a = _gate_attn(a, qkv, self.hq, self.hkv, cfg.head_dim)
+        return tp_ops.row_parallel_linear(a.reshape(T, self.hq * cfg.head_dim), self.p(pfx + "o.weight"), self.ps, cfg)
+
+    def _mlp_block(self, i: int, y: torch.Tensor) -> torch.Tensor:
+        cfg, pfx = self.cfg, f"layers.{i}."
+        if cfg.has_moe:
+            return moe_ops.moe_block(y, self, i)
+        gu = F.linear(y, self.p(pfx + "mlp.gate_up.weight"))
+        return tp_ops.row_parallel_linear(F.swiglu(gu), self.p(pfx + "mlp.down.weight"), self.ps, cfg)
+
+    def layer(self, i: int, x: torch.Tensor, res: torch.Tensor | None, fc: ForwardCtx, kv_idx: int):
+        cfg = self.cfg
+        y, res = _norm(x, self.p(f"layers.{i}.ln1.weight"), cfg, res)
+        if cfg.layer_type(i) == "attn":
+            o = self._attn_block(i, y, fc, kv_idx)
+        else:
+            o = gdn_ops.gdn_block(y, self, i, fc, kv_idx)
+        y, res = _norm(o, self.p(f"layers.{i}.ln2.weight"), cfg, res)
+        return self._mlp_block(i, y), res
+
+    def forward(self, input_ids: torch.Tensor | None, fc: ForwardCtx, hidden_in: tuple | None = None,
+                checkpoint_layers: bool = False):
+        """Returns the final-norm hidden states [T, hidden] on the last pipeline stage, else the
+        (x, residual) pair to send to the next stage."""
+        if hidden_in is None:
+            x, res = self.embed(input_ids), None
+        else:
+            x, res = hidden_in
+        for kv_idx, i in enumerate(self.layer_ids):
+            if checkpoint_layers and torch.is_grad_enabled():
+                x, res = _ckpt(self, i, x, res, fc, kv_idx)
+            else:
+                x, res = self.layer(i, x, res, fc, kv_idx)
+        if not self.ps.is_last_pp:
+            return x, res
+        y, _ = _norm(x, self.p("final_norm.weight"), self.cfg, res)
+        return y
+
+    def logits(self, hidden: torch.Tensor, out_f32: bool = False) -> torch.Tensor:
+        """Vocabulary logits of the given rows ([rows, V/tp] on this rank)."""
+        return F.linear(hidden, self.lm_head_weight(), out_f32)
+
+
+def _norm(x, w, cfg: ModelConfig, res):
+    y, new_res = F.rmsnorm(x, w, cfg.rms_eps, cfg.zero_centered_norm, residual=res)
+    return y, (new_res if new_res is not None else x)
+
+
+def _gate_attn(a, qkv, hq, hkv, d):
+    if torch.is_grad_enabled() and (a.requires_grad or qkv.requires_grad):
+        T, G = a.shape[0], hq // hkv
+        gate = qkv.view(T, hkv, G * 2 * d + 2 * d)[..., : G * 2 * d].reshape(T, hq, 2 * d)[..., d:]
+        return a * torch.sigmoid(gate.float()).to(a.dtype)
+    return F.sigmoid_gate(a, qkv, hq, hkv, d)
+
+
+def _ckpt(model: DecoderLM, i, x, res, fc, kv_idx):
+    from torch.utils.checkpoint import checkpoint
+
+    if res is None:
+        def run0(x_):
+            return model.layer(i, x_, None, fc, kv_idx)
+        return checkpoint(run0, x, use_reentrant=False)
+
+    def run(x_, r_):
+        return model.layer(i, x_, r_, fc, kv_idx)
+    return checkpoint(run, x, res, use_reentrant=False)

@@ -19,7 +19,7 @@ _SIGS = {
     "ixc_rmsnorm": [_P, _P, _P, _P, _P, _P, _I, _I, _F, _I, _L, _L, _I],
     "ixc_qk_norm_rope": [_P, _L, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _I],
     "ixc_swiglu": [_P, _P, _L, _I, _L, _I],
-    "ixc_sigmoid_gate": [_P, _P, _L, _P, _L, _I, _I, _I],
+    "ixc_sigmoid_gate": [_P, _P, _L, _P, _L, _I, _I, _I, _I],
     "ixc_gated_outnorm": [_P, _P, _P, _P, _L, _I, _F, _I, _I],
     "ixc_logprob_fused": [_P, _L, _I, _I, _I, _P, _P, _P, _P, _I],
     "ixc_logprob_rowmax": [_P, _L, _I, _I, _P, _I],

@@ -32,7 +32,7 @@ _SIGS = {
     "ix_qk_norm_rope": [_P, _L, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P],
     "ix_swiglu": [_P, _P, _L, _I, _L, _P],
     "ix_swiglu_bwd": [_P, _P, _P, _L, _I, _L, _P],
-    "ix_sigmoid_gate": [_P, _P, _L, _P, _L, _I, _I, _P],
+    "ix_sigmoid_gate": [_P, _P, _L, _P, _L, _I, _I, _I, _P],
     "ix_gated_outnorm": [_P, _P, _P, _P, _L, _I, _F, _I, _P],
     "ix_logprob_fused": [_P, _L, _I, _I, _I, _P, _P, _P, _P, _I, _P],
     "ix_logprob_rowmax": [_P, _L, _I, _I, _P, _I, _P],

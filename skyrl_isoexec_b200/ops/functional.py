@@ -233,10 +233,12 @@ class _QKNormRope(torch.autograd.Function):
         qs = 2 * D if q_gate else D
         pos = positions.long()
         cos, sin = rope.cos[pos], rope.sin[pos]
+        G = Hq // Hkv
         dqkv = torch.zeros_like(qkv)
-        qblk = qkv[:, : Hq * qs].reshape(T, Hq, qs)
-        xq = qblk[..., :D].float()
-        xk = qkv[:, Hq * qs: Hq * qs + Hkv * D].reshape(T, Hkv, D).float()
+        grp = qkv.view(T, Hkv, G * qs + 2 * D)  # KV-group major: [G query blocks | k | v]
+        dgrp = dqkv.view(T, Hkv, G * qs + 2 * D)
+        xq = grp[..., : G * qs].reshape(T, Hkv, G, qs)[..., :D].reshape(T, Hq, D).float()
+        xk = grp[..., G * qs: G * qs + D].float()
         dwq = dwk = None
 
         def one(x, dout, w):
@@ -255,10 +257,9 @@ class _QKNormRope(torch.autograd.Function):
 
         dxq, dwq = one(xq, dq, qw)
         dxk, dwk = one(xk, dk, kw)
-        dq_blk = dqkv[:, : Hq * qs].view(T, Hq, qs)
-        dq_blk[..., :D] = dxq.to(qkv.dtype)
-        dqkv[:, Hq * qs: Hq * qs + Hkv * D] = dxk.to(qkv.dtype).reshape(T, Hkv * D)
-        dqkv[:, Hq * qs + Hkv * D:] = dv.reshape(T, Hkv * D)
+        dgrp[..., : G * qs].view(T, Hkv, G, qs)[..., :D] = dxq.to(qkv.dtype).view(T, Hkv, G, D)
+        dgrp[..., G * qs: G * qs + D] = dxk.to(qkv.dtype)
+        dgrp[..., G * qs + D:] = dv
         return dqkv, None, None, dwq, dwk, None, None, None, None, None, None, None
 
 
@@ -416,17 +417,17 @@ def swiglu(x):
 
 
 # --------------------------------------------------------------------------- gated attention output / GDN out-norm
-def sigmoid_gate(a, qkv, Hq, D):
+def sigmoid_gate(a, qkv, Hq, Hkv, D):
     """out[t,h,:] = a[t,h,:] * sigmoid(gate[t,h,:]) with gate read in place from the fused q block."""
     T = a.shape[0]
     out = torch.empty_like(a)
     if T == 0:
         return out
     if _is_cuda(a):
-        _native.check(_native.lib().ix_sigmoid_gate(a.data_ptr(), qkv.data_ptr(), qkv.stride(0), out.data_ptr(), T, Hq, D,
+        _native.check(_native.lib().ix_sigmoid_gate(a.data_ptr(), qkv.data_ptr(), qkv.stride(0), out.data_ptr(), T, Hq, Hkv, D,
                                                     _native.stream()), "ix_sigmoid_gate")
     else:
-        _cpu.lib().ixc_sigmoid_gate(a.data_ptr(), qkv.data_ptr(), qkv.stride(0), out.data_ptr(), T, Hq, D, _cpu.dt(a))
+        _cpu.lib().ixc_sigmoid_gate(a.data_ptr(), qkv.data_ptr(), qkv.stride(0), out.data_ptr(), T, Hq, Hkv, D, _cpu.dt(a))
     return out
 
 

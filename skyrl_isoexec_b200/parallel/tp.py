@@ -1,0 +1,161 @@
+"""Tensor-parallel linears with a TP-invariant reduction ("pik" in the reference,
+ISO/ops/collectives/pik/plan.py:20-36,104-119 and pik/allreduce.py:1018-1168).
+
+The K reduction of a row-parallel linear is fixed as G equal leaves folded by a balanced
+binary fp32 tree (left operand = lower leaf index). A rank at TP degree C owns the G/C
+consecutive leaves of its K slice, i.e. one whole subtree; the cross-rank step is the upper
+levels of the SAME tree. Any C dividing G therefore yields identical bits, and C == G costs
+nothing extra (one leaf per rank = a plain GEMM).
+
+Transports for the upper levels:
+  * ``symm``  - peer-memory kernel (csrc/tree_allreduce.cu): every rank stores its partial in
+                symmetric memory, then reads all peers and folds in tree order (one launch);
+  * ``nccl``  - all_gather of the fp32 partials + local fold (the baseline / fallback);
+  * CPU/gloo  - all_gather + the same fold in torch.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+
+from ..ops import functional as F
+from ..ops import _cpu, _native
+
+
+@dataclass(frozen=True)
+class ReductionPlan:
+    num_leaves: int = 8
+    leaf_dtype: str = "fp32"  # "fp32" | "bf16": optional rounding at the leaf boundary only
+
+    def validate(self, K: int, tp: int) -> None:
+        G = self.num_leaves
+        if G < 1 or G & (G - 1):
+            raise ValueError(f"num_leaves={G} must be a power of two")
+        if G % tp:
+            raise ValueError(f"TP degree {tp} does not divide the {G} leaves")
+        if K % G:
+            raise ValueError(f"K={K} is not divisible into {G} leaves")
+
+    def leaves_per_rank(self, tp: int) -> int:
+        return self.num_leaves // tp
+
+    def contract_string(self, arch: str) -> str:
+        return f"pik-tree:G={self.num_leaves}:leaf={self.leaf_dtype}:arch={arch}"
+
+
+def combine_order(n: int) -> list[tuple[int, int]]:
+    """(dst, src) pairs of the balanced tree over n slots: stride 1, 2, 4, ...; slot[i] += slot[i+stride]."""
+    out, stride = [], 1
+    while stride < n:
+        out += [(i, i + stride) for i in range(0, n, 2 * stride)]
+        stride *= 2
+    return out
+
+
+def tree_fold(parts: torch.Tensor) -> torch.Tensor:
+    """Fold ``parts[n, ...]`` (fp32) along dim 0 in tree order. n must be a power of two."""
+    n = parts.shape[0]
+    buf = [parts[i] for i in range(n)]
+    for dst, src in combine_order(n):
+        buf[dst] = buf[dst] + buf[src]
+    return buf[0]
+
+
+def leaftree_gemm(x: torch.Tensor, w: torch.Tensor, leaves: int, round_leaf: bool = False) -> torch.Tensor:
+    """fp32 [M,N] = tree over ``leaves`` K-slices of x[M,K] @ w[N,K]^T (local subtree of one rank)."""
+    M, K = x.shape
+    N = w.shape[0]
+    assert K % leaves == 0
+    if leaves == 1 and not round_leaf:
+        return F.gemm_nt(x, w, out_f32=True)
+    if x.is_cuda:
+        LK = K // leaves
+        parts = torch.stack([F.gemm_nt(x[:, j * LK:(j + 1) * LK], w[:, j * LK:(j + 1) * LK], out_f32=True)
+                             for j in range(leaves)])
+        if round_leaf:
+            parts = parts.bfloat16().float()
+        return tree_fold(parts)
+    out = torch.empty(M, N, dtype=torch.float32)
+    if M:
+        _cpu.lib().ixc_leaftree_gemm(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, leaves, int(round_leaf),
+                                     x.stride(0), w.stride(0), N, _cpu.dt(x))
+    return out
+
+
+def tree_all_reduce(partial: torch.Tensor, group, tp: int) -> torch.Tensor:
+    """Upper levels of the tree across the TP group: gather every rank's fp32 partial (rank order =
+    leaf order) and fold. All ranks end with identical bits."""
+    if tp == 1:
+        return partial
+    from . import symm
+
+    if partial.is_cuda and symm.enabled(group):
+        return symm.tree_all_reduce(partial, group)
+    gathered = torch.empty((tp,) + tuple(partial.shape), dtype=partial.dtype, device=partial.device)
+    dist.all_gather_into_tensor(gathered, partial.contiguous(), group=group)
+    return tree_fold(gathered)
+
+
+class _RowParallel(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, ps, leaves_local, round_leaf, out_dtype):
+        ctx.save_for_backward(x, w)
+        part = leaftree_gemm(x, w, leaves_local, round_leaf)
+        full = tree_all_reduce(part, ps.tp_group, ps.tp)
+        return full.to(out_dtype)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        dy = dy.to(w.dtype)
+        return torch.matmul(dy, w), torch.matmul(dy.t(), x), None, None, None, None
+
+
+def row_parallel_linear(x: torch.Tensor, w: torch.Tensor, ps, cfg) -> torch.Tensor:
+    """y = x_full @ w_full^T where this rank holds the K slice x[:, K/tp], w[:, K/tp].
+
+    With ``cfg.pik_leaves == 0`` (TP pinned, same degree on both sides) and tp == 1 this is the
+    plain batch-invariant GEMM. Otherwise the leaf tree runs so that every TP degree dividing
+    ``cfg.pik_leaves`` produces the same bits."""
+    G = getattr(cfg, "pik_leaves", 0)
+    if ps.tp == 1 and (G <= 1 or not cfg.tp_invariant):
+        return F.linear(x, w)
+    plan = ReductionPlan(G)
+    plan.validate(w.shape[1] * ps.tp, ps.tp)
+    shp = x.shape
+    x2 = x.reshape(-1, shp[-1])
+    y = _RowParallel.apply(x2, w, ps, plan.leaves_per_rank(ps.tp), plan.leaf_dtype == "bf16", x.dtype)
+    return y.reshape(*shp[:-1], w.shape[0])
+
+
+def column_parallel_gather(y_local: torch.Tensor, ps) -> torch.Tensor:
+    """All-gather the column shards of a column-parallel output along the last dim (byte movement only)."""
+    if ps.tp == 1:
+        return y_local
+    parts = [torch.empty_like(y_local) for _ in range(ps.tp)]
+    dist.all_gather(parts, y_local.contiguous(), group=ps.tp_group)
+    return torch.cat(parts, dim=-1)
+
+
+class _CopyToTP(torch.autograd.Function):
+    """Identity forward, all-reduce backward: input of a column-parallel region."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        return x
+
+    @staticmethod
+    def backward(ctx, g):
+        g = g.contiguous()
+        dist.all_reduce(g, group=ctx.group)
+        return g, None
+
+
+def copy_to_tp(x, ps):
+    if ps.tp == 1 or not (torch.is_grad_enabled() and x.requires_grad):
+        return x
+    return _CopyToTP.apply(x, ps.tp_group)

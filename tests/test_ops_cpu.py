@@ -65,9 +65,11 @@ def test_qk_norm_rope_matches_formula_and_grad():
     q, k, v = F.qk_norm_rope_train(qkv, pos, rope, qw, kw, Hq, Hkv, D, 1e-6)
     (q.square().sum() + k.sum() * 2 + v.sum() * 3).backward()
     a, b, c = (t.detach().clone().requires_grad_() for t in (qkv, qw, kw))
-    xq = a[:, :Hq * D].view(T, Hq, D)
-    xk = a[:, Hq * D:(Hq + Hkv) * D].view(T, Hkv, D)
-    xv = a[:, (Hq + Hkv) * D:].view(T, Hkv, D)
+    G = Hq // Hkv  # rows are KV-group major: [G query heads | k | v] per KV head
+    grp = a.view(T, Hkv, (G + 2) * D)
+    xq = grp[..., :G * D].reshape(T, Hq, D)
+    xk = grp[..., G * D:(G + 1) * D]
+    xv = grp[..., (G + 1) * D:]
     nrm = lambda x, w: x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + 1e-6) * w
     q2, k2 = _rope_ref(nrm(xq, b), pos, rope), _rope_ref(nrm(xk, c), pos, rope)
     (q2.square().sum() + k2.sum() * 2 + xv.sum() * 3).backward()
