@@ -89,7 +89,8 @@ class Sampler:
                     row = row.masked_fill(mask, float("-inf"))
                 x[i] = row
         u = torch.rand(x.shape, device=x.device, dtype=torch.float32, generator=self.gen)
-        gumbel = -torch.log(-torch.log(u.clamp_min(1e-20)).clamp_min(1e-20))
+        expo = -torch.log(u.clamp_min(1e-20))          # Exp(1) samples
+        gumbel = -torch.log(expo.clamp_min(1e-20))     # Gumbel(0, 1) samples
         greedy = torch.tensor([p.temperature == 0.0 for p in params], device=x.device)
         noisy = torch.where(greedy[:, None], x, x + gumbel)
         tokens = noisy.argmax(-1)

@@ -1,0 +1,194 @@
+"""Checkpoint save / resume in the reference's directory layout
+(docs/content/docs/checkpointing-logging/checkpointing.mdx:36-85,116-128; R/train/trainer.py:1858-2036):
+
+    {ckpt_path}/latest_ckpt_global_step.txt
+    {ckpt_path}/global_step_N/policy/metadata.json
+    {ckpt_path}/global_step_N/policy/__{rank}_0.distcp     (one shard file per rank)
+    {ckpt_path}/global_step_N/data.pt                       (dataloader state)
+    {ckpt_path}/global_step_N/trainer_state.pt
+
+A shard file holds the rank's slice of the sharded state dict with the keys ``model`` /
+``optimizer`` / ``lr_scheduler`` / ``rng``; ``metadata.json`` records every parameter's full
+shape, shard dim and sections so a checkpoint written at one TP degree loads at another
+(parameters are reassembled to full shape and re-sliced). The step directory is written under
+a temporary name and renamed, and ``latest_ckpt_global_step.txt`` is replaced last, so a crash
+mid-save never leaves a directory that ``resume_mode=latest`` would pick up.
+"""
+
+from __future__ import annotations
+
+import json
+import os
+import random
+import re
+import shutil
+
+import torch
+import torch.distributed as dist
+
+LATEST = "latest_ckpt_global_step.txt"
+_STEP_RE = re.compile(r"^global_step_(\d+)$")
+
+
+def _barrier():
+    if dist.is_initialized():
+        dist.barrier()
+
+
+def _rank():
+    return dist.get_rank() if dist.is_initialized() else 0
+
+
+def step_dir(ckpt_path: str, step: int) -> str:
+    return os.path.join(ckpt_path, f"global_step_{step}")
+
+
+def save_checkpoint(ckpt_path: str, step: int, policy, data_state: dict, trainer_state: dict, ps, max_to_keep: int = -1) -> str:
+    final = step_dir(ckpt_path, step)
+    tmp = final + ".tmp"
+    rank = _rank()
+    if rank == 0:
+        if os.path.isdir(tmp):
+            shutil.rmtree(tmp)
+        os.makedirs(os.path.join(tmp, "policy"), exist_ok=True)
+    _barrier()
+    model = policy.model
+    shard = {
+        "model": {name: t.detach().cpu().clone() for name, t in model.named_weights()},
+        "optimizer": {k: (v.detach().cpu().clone() if torch.is_tensor(v) else v) for k, v in policy.opt.state_dict().items()},
+        "lr_scheduler": {"step": policy.opt.step_count},
+        "rng": {"torch": torch.get_rng_state(), "python": random.getstate(),
+                "cuda": torch.cuda.get_rng_state() if torch.cuda.is_available() else None},
+        "parallel": {"tp": ps.tp, "tp_rank": ps.tp_rank, "dp_rank": ps.dp_rank, "pp_rank": ps.pp_rank, "ep_rank": ps.ep_rank},
+    }
+    torch.save(shard, os.path.join(tmp, "policy", f"__{rank}_0.distcp"))
+    if rank == 0:
+        meta = {
+            "format": "skyrl_isoexec_b200.sharded.v1", "global_step": step, "world_size": dist.get_world_size() if dist.is_initialized() else 1,
+            "tp": ps.tp, "pp": ps.pp, "dp": ps.dp, "ep": ps.ep, "model_config": model.cfg.to_dict(),
+            "params": {n: {"full_shape": list(s.full_shape), "shard_dim": s.shard_dim, "sections": list(s.sections),
+                           "ep_sharded": s.ep_sharded, "offset": s.offset, "shape": list(s.shape)}
+                       for n, s in model.store.specs.items()},
+        }
+        with open(os.path.join(tmp, "policy", "metadata.json"), "w") as f:
+            json.dump(meta, f, indent=1, sort_keys=True)
+        torch.save(data_state, os.path.join(tmp, "data.pt"))
+        torch.save(trainer_state, os.path.join(tmp, "trainer_state.pt"))
+    _barrier()
+    if rank == 0:
+        if os.path.isdir(final):
+            shutil.rmtree(final)
+        os.replace(tmp, final)
+        with open(os.path.join(ckpt_path, LATEST + ".tmp"), "w") as f:
+            f.write(str(step))
+        os.replace(os.path.join(ckpt_path, LATEST + ".tmp"), os.path.join(ckpt_path, LATEST))
+        cleanup_old_checkpoints(ckpt_path, max_to_keep)
+    _barrier()
+    return final
+
+
+def list_checkpoints(ckpt_path: str) -> list[int]:
+    if not os.path.isdir(ckpt_path):
+        return []
+    steps = []
+    for d in os.listdir(ckpt_path):
+        m = _STEP_RE.match(d)
+        if m and os.path.isdir(os.path.join(ckpt_path, d)):
+            steps.append(int(m.group(1)))
+    return sorted(steps)
+
+
+def cleanup_old_checkpoints(ckpt_path: str, max_to_keep: int) -> list[int]:
+    if max_to_keep is None or max_to_keep < 0:
+        return []
+    steps = list_checkpoints(ckpt_path)
+    drop = steps[:-max_to_keep] if max_to_keep > 0 else steps
+    for s in drop:
+        shutil.rmtree(step_dir(ckpt_path, s), ignore_errors=True)
+    return drop
+
+
+def validate_checkpoint_dir(path: str) -> None:
+    if not _STEP_RE.match(os.path.basename(os.path.normpath(path))):
+        raise ValueError(f"resume_path must be a global_step_N directory, got {path!r}")
+    for need in ("policy/metadata.json", "data.pt", "trainer_state.pt"):
+        if not os.path.exists(os.path.join(path, need)):
+            raise FileNotFoundError(f"checkpoint {path} is incomplete: missing {need}")
+
+
+def resolve_resume_path(ckpt_path: str, resume_mode: str, resume_path: str = "") -> str | None:
+    if resume_mode == "none":
+        return None
+    if resume_mode == "from_path":
+        validate_checkpoint_dir(resume_path)
+        return resume_path
+    latest = os.path.join(ckpt_path, LATEST)
+    if not os.path.exists(latest):
+        return None
+    with open(latest) as f:
+        step = int(f.read().strip())
+    path = step_dir(ckpt_path, step)
+    validate_checkpoint_dir(path)
+    return path
+
+
+def _assemble_full(name: str, meta: dict, shards: list[dict]) -> torch.Tensor:
+    """Rebuild a parameter at full shape from the TP shards of the saved layout (dp_rank 0)."""
+    info = meta["params"][name]
+    parts = [s["model"][name] for s in shards]
+    if info["shard_dim"] is None or len(parts) == 1:
+        return parts[0]
+    d, tp = info["shard_dim"], len(parts)
+    secs = info["sections"] or [info["full_shape"][d]]
+    cols = []
+    for si, sz in enumerate(secs):
+        lo = sum(x // tp for x in secs[:si])
+        cols += [p.narrow(d, lo, sz // tp) for p in parts]
+    return torch.cat(cols, dim=d)
+
+
+def load_checkpoint(path: str, policy, ps) -> tuple[dict, dict]:
+    validate_checkpoint_dir(path)
+    with open(os.path.join(path, "policy", "metadata.json")) as f:
+        meta = json.load(f)
+    model = policy.model
+    rank = _rank()
+    same_layout = (meta["tp"] == ps.tp and meta["pp"] == ps.pp and meta["ep"] == ps.ep
+                   and meta["world_size"] == (dist.get_world_size() if dist.is_initialized() else 1))
+    from ..models.decoder import shard_of
+
+    if same_layout:
+        shard = torch.load(os.path.join(path, "policy", f"__{rank}_0.distcp"), map_location="cpu", weights_only=False)
+        with torch.no_grad():
+            for name, dst in model.named_weights():
+                dst.copy_(shard["model"][name].to(dst.dtype))
+        policy.opt.load_state_dict({k: (v.to(policy.opt.master.device) if torch.is_tensor(v) else v)
+                                    for k, v in shard["optimizer"].items()})
+        torch.set_rng_state(shard["rng"]["torch"])
+        random.setstate(shard["rng"]["python"])
+    else:
+        # reshard: read the TP shards of data-parallel rank 0 of the saved job, rebuild, re-slice
+        files = sorted(f for f in os.listdir(os.path.join(path, "policy")) if f.endswith(".distcp"))
+        shards = [torch.load(os.path.join(path, "policy", f), map_location="cpu", weights_only=False) for f in files]
+        shards = [s for s in shards if s["parallel"]["dp_rank"] == 0 and s["parallel"]["pp_rank"] == 0 and s["parallel"]["ep_rank"] == 0]
+        shards.sort(key=lambda s: s["parallel"]["tp_rank"])
+        with torch.no_grad():
+            for name, dst in model.named_weights():
+                full = _assemble_full(name, meta, shards)
+                dst.copy_(shard_of(full, model.store.specs[name], ps.tp_rank, ps.tp, ps.ep_rank, ps.ep).to(dst.dtype))
+            if policy.opt.low_precision:
+                policy.opt.master.copy_(model.store.flat.float())
+        policy.opt.step_count = int(shards[0]["lr_scheduler"]["step"])
+    data_state = torch.load(os.path.join(path, "data.pt"), weights_only=False)
+    trainer_state = torch.load(os.path.join(path, "trainer_state.pt"), weights_only=False)
+    return data_state, trainer_state
+
+
+def save_hf_export(export_path: str, step: int, model) -> str:
+    """Export full-shape weights + config as ``{export_path}/global_step_N/policy/`` (single-rank layouts)."""
+    out = os.path.join(export_path, f"global_step_{step}", "policy")
+    os.makedirs(out, exist_ok=True)
+    torch.save({n: t.detach().cpu() for n, t in model.named_weights()}, os.path.join(out, "pytorch_model.bin"))
+    with open(os.path.join(out, "config.json"), "w") as f:
+        json.dump({"architectures": [model.cfg.architecture], **model.cfg.to_dict()}, f, indent=1)
+    return out

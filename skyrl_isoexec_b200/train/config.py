@@ -1,0 +1,243 @@
+"""Typed configuration tree with ``key=value`` dotted CLI overrides.
+
+Shape and defaults follow the reference's ``SkyRLTrainConfig`` (R/train/config/config.py:29-1056:
+``trainer.*``, ``generator.*``, ``data.*``, ``environment.*``; defaults at :244-259,421-487,561-639,
+719-833) so existing launch lines carry over. Parsing needs no OmegaConf: a dotted key walks the
+dataclass tree and the value is coerced to the field's type; unknown keys are errors.
+"""
+
+from __future__ import annotations
+
+import dataclasses
+import json
+import typing
+from dataclasses import dataclass, field, fields, is_dataclass
+
+from .algorithms import AlgorithmConfig, OffPolicyCorrection
+from .policy_worker import OptimizerConfig
+
+
+@dataclass
+class PlacementConfig:
+    colocate_all: bool = True
+    policy_num_gpus_per_node: int = 1
+    policy_num_nodes: int = 1
+
+
+@dataclass
+class ParallelConfig:
+    tensor_model_parallel_size: int = 1
+    pipeline_model_parallel_size: int = 1
+    context_parallel_size: int = 1
+    expert_model_parallel_size: int = 1
+    sequence_parallel: bool = False
+
+
+@dataclass
+class PolicyConfig:
+    model: str = "tiny-qwen3"           # preset name or path of a saved config
+    model_overrides: dict = field(default_factory=dict)
+    optimizer_config: OptimizerConfig = field(default_factory=OptimizerConfig)
+    parallel: ParallelConfig = field(default_factory=ParallelConfig)
+    seed: int = 0
+
+
+@dataclass
+class SamplingConfig:
+    max_generate_length: int = 1024
+    repetition_penalty: float = 1.0
+    temperature: float = 1.0
+    top_p: float = 1.0
+    min_p: float = 0.0
+    top_k: int = -1
+    logprobs: int = 1
+    stop: list | None = None
+    ignore_eos: bool = False
+    additional_kwargs: dict = field(default_factory=dict)
+
+
+@dataclass
+class InferenceEngineConfig:
+    backend: str = "native"
+    num_engines: int = 1
+    tensor_parallel_size: int = 1
+    data_parallel_size: int = 1
+    gpu_memory_utilization: float = 0.8
+    max_num_batched_tokens: int = 8192
+    max_num_seqs: int = 1024
+    num_kv_pages: int = 0
+    enforce_eager: bool = False
+    enable_prefix_caching: bool = False
+    weight_sync_backend: str = "nccl"   # nccl | gloo | cuda_ipc | shared
+    run_engines_locally: bool = True
+
+
+@dataclass
+class GeneratorConfig:
+    inference_engine: InferenceEngineConfig = field(default_factory=InferenceEngineConfig)
+    n_samples_per_prompt: int = 5
+    sampling_params: SamplingConfig = field(default_factory=SamplingConfig)
+    eval_sampling_params: SamplingConfig = field(default_factory=lambda: SamplingConfig(temperature=0.0))
+    eval_n_samples_per_prompt: int = 1
+    max_input_length: int = 512
+    batched: bool = True
+    max_turns: int = 1
+    use_conversation_multi_turn: bool = True
+    zero_reward_on_non_stop: bool = False
+    apply_overlong_filtering: bool = False
+
+
+@dataclass
+class DataConfig:
+    train_data: list = field(default_factory=list)
+    val_data: list = field(default_factory=list)
+    synthetic_prompts: int = 0          # >0: uniform-random token prompts (no dataset needed)
+    synthetic_prompt_len: int = 32
+
+
+@dataclass
+class EnvironmentConfig:
+    env_class: str = "even_tokens"
+    env_kwargs: dict = field(default_factory=dict)
+
+
+@dataclass
+class IsoExecConfig:
+    enabled: bool = True
+    gate_mean_limit: float = 1.0e-5     # forward-gate limits of the reference (R/train/utils/trainer_utils.py:45-46)
+    gate_max_limit: float = 1.0e-4
+    require_bitwise: bool = True        # the contract claims tolerance 0: any nonzero diff refuses
+    strict: bool = True
+    contract_path: str = ""
+    debug_trace: str = ""
+
+
+@dataclass
+class TrainerConfig:
+    placement: PlacementConfig = field(default_factory=PlacementConfig)
+    policy: PolicyConfig = field(default_factory=PolicyConfig)
+    algorithm: AlgorithmConfig = field(default_factory=AlgorithmConfig)
+    isoexec: IsoExecConfig = field(default_factory=IsoExecConfig)
+    strategy: str = "native"
+    epochs: int = 1
+    train_batch_size: int = 1024
+    policy_mini_batch_size: int = 256
+    micro_train_batch_size_per_gpu: int = 1
+    micro_forward_batch_size_per_gpu: int = 1
+    max_tokens_per_microbatch: int = 8192
+    update_epochs_per_batch: int = 1
+    max_prompt_length: int = 512
+    eval_batch_size: int = 1024
+    eval_before_train: bool = False
+    eval_interval: int = -1
+    ckpt_path: str = ""
+    ckpt_interval: int = 10
+    max_ckpts_to_keep: int = -1
+    resume_mode: str = "latest"         # none | latest | from_path
+    resume_path: str = ""
+    export_path: str = ""
+    hf_save_interval: int = -1
+    logger: str = "console"
+    project_name: str = "skyrl_isoexec_b200"
+    run_name: str = "run"
+    seed: int = 42
+    recompute_old_logprobs_per_minibatch: bool = False
+    dump_data_batch: bool = False
+    num_steps: int = -1                 # stop after this many global steps (-1: run the epochs out)
+
+
+@dataclass
+class SkyRLTrainConfig:
+    trainer: TrainerConfig = field(default_factory=TrainerConfig)
+    generator: GeneratorConfig = field(default_factory=GeneratorConfig)
+    data: DataConfig = field(default_factory=DataConfig)
+    environment: EnvironmentConfig = field(default_factory=EnvironmentConfig)
+
+    @classmethod
+    def from_cli_overrides(cls, argv: list[str]) -> "SkyRLTrainConfig":
+        cfg = cls()
+        for arg in argv:
+            if "=" not in arg:
+                raise ValueError(f"override {arg!r} is not key=value")
+            if arg.startswith("+"):
+                raise ValueError("the '+key=value' syntax is not supported; every key already exists in the config tree")
+            key, val = arg.split("=", 1)
+            set_by_path(cfg, key.strip(), val.strip())
+        return cfg
+
+    def to_dict(self) -> dict:
+        return dataclasses.asdict(self)
+
+    def dumps(self) -> str:
+        return json.dumps(self.to_dict(), indent=1, sort_keys=True, default=str)
+
+
+def _coerce(val: str, tp):
+    origin = typing.get_origin(tp)
+    if origin is typing.Union or str(origin) == "types.UnionType" or origin is getattr(__import__("types"), "UnionType", None):
+        args = [a for a in typing.get_args(tp) if a is not type(None)]
+        if val.lower() in ("null", "none"):
+            return None
+        return _coerce(val, args[0])
+    if tp is bool:
+        if val.lower() in ("true", "1", "yes"):
+            return True
+        if val.lower() in ("false", "0", "no"):
+            return False
+        raise ValueError(f"{val!r} is not a bool")
+    if tp is int:
+        return int(val)
+    if tp is float:
+        return float(val)
+    if tp is str:
+        return val.strip("\"'")
+    if tp in (list, dict) or origin in (list, dict, tuple):
+        out = json.loads(val.replace("'", '"'))
+        return tuple(out) if origin is tuple else out
+    return val
+
+
+def set_by_path(cfg, key: str, val: str) -> None:
+    parts = key.split(".")
+    obj = cfg
+    for p in parts[:-1]:
+        if not is_dataclass(obj) or p not in {f.name for f in fields(obj)}:
+            raise KeyError(f"unknown config key {key!r} (at {p!r})")
+        obj = getattr(obj, p)
+    leaf = parts[-1]
+    if isinstance(obj, dict):
+        obj[leaf] = json.loads(val) if val[:1] in "[{0123456789-tfn\"" else val
+        return
+    fmap = {f.name: f for f in fields(obj)} if is_dataclass(obj) else {}
+    if leaf not in fmap:
+        raise KeyError(f"unknown config key {key!r}")
+    hints = typing.get_type_hints(type(obj))
+    setattr(obj, leaf, _coerce(val, hints[leaf]))
+
+
+def validate_cfg(cfg: SkyRLTrainConfig, world_size: int = 1) -> None:
+    """Cross-field checks done before anything is built (reference: R/train/utils/utils.py:230)."""
+    t, g = cfg.trainer, cfg.generator
+    p = t.policy.parallel
+    mp = p.tensor_model_parallel_size * p.pipeline_model_parallel_size * p.context_parallel_size
+    if world_size % mp:
+        raise ValueError(f"world size {world_size} is not divisible by tp*pp*cp={mp}")
+    dp = world_size // mp
+    if t.train_batch_size % t.policy_mini_batch_size:
+        raise ValueError("train_batch_size must be a multiple of policy_mini_batch_size")
+    if (t.policy_mini_batch_size * g.n_samples_per_prompt) % dp:
+        raise ValueError(f"policy_mini_batch_size * n_samples_per_prompt must be divisible by the DP size {dp}")
+    if t.algorithm.policy_loss_type not in __import__("skyrl_isoexec_b200.train.algorithms", fromlist=["x"]).POLICY_LOSSES:
+        raise ValueError(f"unknown policy_loss_type {t.algorithm.policy_loss_type!r}")
+    if t.algorithm.advantage_estimator not in __import__("skyrl_isoexec_b200.train.algorithms", fromlist=["x"]).ADVANTAGE_ESTIMATORS:
+        raise ValueError(f"unknown advantage_estimator {t.algorithm.advantage_estimator!r}")
+    if t.resume_mode not in ("none", "latest", "from_path"):
+        raise ValueError(f"resume_mode {t.resume_mode!r} must be none|latest|from_path")
+    if t.isoexec.enabled:
+        s = g.sampling_params
+        if s.temperature != 1.0 or s.top_p != 1.0 or s.top_k not in (-1, 0) or s.min_p != 0.0:
+            raise ValueError("isoexec.enabled requires temperature=1.0, top_p=1.0, top_k=-1, min_p=0.0 for rollouts")
+        if g.inference_engine.enable_prefix_caching:
+            raise ValueError("isoexec.enabled pins enable_prefix_caching=false")
+    if g.inference_engine.tensor_parallel_size < 1 or g.inference_engine.num_engines < 1:
+        raise ValueError("inference engine sizes must be >= 1")

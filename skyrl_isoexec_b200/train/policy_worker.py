@@ -1,0 +1,407 @@
+"""Trainer-side worker: owns the policy model, its flat optimizer state and the three verbs
+the controller drives (``forward`` for scoring, ``forward_backward`` per mini-batch,
+``optim_step``), like the reference's ``PolicyWorkerBase`` (B/workers/worker.py:776-1073) and
+its Megatron wrapper (B/workers/megatron/megatron_model_wrapper.py:185-711) - without Megatron:
+padding is removed and sequences are packed back to back, micro-batches are cut by a token
+budget, and the LM head + log-softmax run chunked and are recomputed in the backward so a
+[tokens, vocab] tensor is never kept alive.
+"""
+
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+
+import torch
+import torch.distributed as dist
+
+from ..models.decoder import DecoderLM, ForwardCtx
+from ..ops import _native
+from ..ops import functional as F
+from ..parallel.state import ParallelState
+from . import algorithms as alg
+from .batch import TrainingInputBatch
+
+
+@dataclass
+class OptimizerConfig:
+    lr: float = 1e-6
+    beta1: float = 0.9
+    beta2: float = 0.999
+    eps: float = 1e-8
+    weight_decay: float = 0.01
+    max_grad_norm: float = 1.0
+    num_warmup_steps: int = 0
+    scheduler: str = "constant_with_warmup"  # | "cosine" | "linear"
+    total_steps: int = 0
+    min_lr_ratio: float = 0.0
+
+
+@dataclass
+class WorkerConfig:
+    max_tokens_per_microbatch: int = 8192
+    logprob_chunk_rows: int = 8192
+    checkpoint_layers: bool = True
+    want_entropy: bool = False
+    optimizer: OptimizerConfig = field(default_factory=OptimizerConfig)
+
+
+# ------------------------------------------------------------------------------------ LM head + logprob (chunked, recomputed)
+class _LMHeadLogprob(torch.autograd.Function):
+    """logprob/entropy of ``targets`` from hidden rows, one vocabulary GEMM chunk at a time.
+    Saves only the hidden rows and the per-row lse; the backward recomputes each logits chunk,
+    turns it into d(logits) in place and feeds the two library GEMMs."""
+
+    @staticmethod
+    def forward(ctx, hidden, weight, targets, leaves, chunk, want_entropy):
+        n = hidden.shape[0]
+        lp = torch.empty(n, device=hidden.device, dtype=torch.float32)
+        lse = torch.empty_like(lp)
+        ent = torch.empty_like(lp) if want_entropy else None
+        for lo in range(0, n, chunk):
+            hi = min(n, lo + chunk)
+            logits = F.gemm_nt(hidden[lo:hi], weight)
+            a, b, c = F.logprob_fused_fwd(logits, targets[lo:hi], leaves, want_entropy)
+            lp[lo:hi], lse[lo:hi] = a, b
+            if want_entropy:
+                ent[lo:hi] = c
+            del logits
+        ctx.save_for_backward(hidden, weight, targets, lse, ent if want_entropy else lse)
+        ctx.cfg = (leaves, chunk, want_entropy)
+        if not want_entropy:
+            ent = torch.zeros_like(lp)
+            ctx.mark_non_differentiable(ent)
+        return lp, ent
+
+    @staticmethod
+    def backward(ctx, g_lp, g_ent):
+        hidden, weight, targets, lse, ent = ctx.saved_tensors
+        leaves, chunk, want_entropy = ctx.cfg
+        n = hidden.shape[0]
+        g_lp = g_lp.contiguous().float()
+        ge = g_ent.contiguous().float() if want_entropy and g_ent is not None else None
+        dh = torch.empty_like(hidden)
+        dw = torch.zeros_like(weight)
+        for lo in range(0, n, chunk):
+            hi = min(n, lo + chunk)
+            logits = F.gemm_nt(hidden[lo:hi], weight)
+            d = F.logprob_bwd(logits, targets[lo:hi], lse[lo:hi], g_lp[lo:hi], None if ge is None else ge[lo:hi],
+                              ent[lo:hi] if ge is not None else None, inplace=True)
+            dh[lo:hi] = torch.matmul(d, weight)
+            dw.addmm_(d.t(), hidden[lo:hi])
+            del logits, d
+        return dh, dw, None, None, None, None
+
+
+def lm_head_logprobs(model: DecoderLM, hidden_rows, targets, chunk: int, want_entropy: bool = False):
+    w = model.lm_head_weight()
+    leaves = model.cfg.logprob_leaves
+    if model.ps.tp > 1:
+        from ..parallel.vocab_parallel import vocab_parallel_logprobs
+
+        return vocab_parallel_logprobs(model, hidden_rows, targets, chunk, want_entropy)
+    if torch.is_grad_enabled() and (hidden_rows.requires_grad or w.requires_grad):
+        return _LMHeadLogprob.apply(hidden_rows, w, targets, leaves, chunk, want_entropy)
+    n = hidden_rows.shape[0]
+    lp = torch.empty(n, device=hidden_rows.device, dtype=torch.float32)
+    ent = torch.zeros_like(lp)
+    for lo in range(0, n, chunk):
+        hi = min(n, lo + chunk)
+        a, _, c = F.logprob_fused_fwd(F.gemm_nt(hidden_rows[lo:hi], w), targets[lo:hi], leaves, want_entropy)
+        lp[lo:hi] = a
+        if want_entropy:
+            ent[lo:hi] = c
+    return lp, ent
+
+
+# ------------------------------------------------------------------------------------ packing
+@dataclass
+class PackedMicroBatch:
+    seq_index: list[int]          # rows of the mini-batch in this micro-batch
+    ids: torch.Tensor             # int64 [T]
+    positions: torch.Tensor       # int32 [T]
+    seq_lens: list[int]
+    pred_rows: torch.Tensor       # int64 [Nr] hidden rows that predict a response token
+    targets: torch.Tensor         # int64 [Nr]
+    out_index: torch.Tensor       # int64 [Nr] flat index into [len(seq_index) * R]
+
+
+def pack_microbatches(sequences: torch.Tensor, attention_mask: torch.Tensor, num_actions: int,
+                      max_tokens: int) -> list[PackedMicroBatch]:
+    """Remove padding, pack sequences back to back and cut micro-batches by a token budget."""
+    B, S = sequences.shape
+    P = S - num_actions
+    att = attention_mask.bool()
+    lens = att.sum(1).tolist()
+    first = att.float().argmax(1).tolist()
+    groups, cur, cur_tok = [], [], 0
+    for b in range(B):
+        if cur and cur_tok + lens[b] > max_tokens:
+            groups.append(cur)
+            cur, cur_tok = [], 0
+        cur.append(b)
+        cur_tok += lens[b]
+    if cur:
+        groups.append(cur)
+    out = []
+    for grp in groups:
+        ids, pos, pred, tgt, oidx, seq_lens = [], [], [], [], [], []
+        base = 0
+        for j, b in enumerate(grp):
+            n, f = lens[b], first[b]
+            if n == 0:
+                continue
+            ids.append(sequences[b, f:f + n])
+            pos.append(torch.arange(n, dtype=torch.int32))
+            plen = P - f                      # real prompt tokens
+            rlen = n - plen                   # real response tokens
+            if rlen > 0 and plen > 0:
+                k = torch.arange(rlen)
+                pred.append(base + plen - 1 + k)
+                tgt.append(sequences[b, P:P + rlen])
+                oidx.append(j * num_actions + k)
+            seq_lens.append(n)
+            base += n
+        z = torch.zeros(0, dtype=torch.long)
+        out.append(PackedMicroBatch(grp, torch.cat(ids), torch.cat(pos), seq_lens,
+                                    torch.cat(pred) if pred else z, torch.cat(tgt) if tgt else z,
+                                    torch.cat(oidx) if oidx else z))
+    return out
+
+
+# ------------------------------------------------------------------------------------ optimizer
+class FlatAdamW:
+    """AdamW over the model's flat parameter buffer: fp32 master weights, moments and main
+    gradients are four flat buffers, updated by one kernel launch (csrc/loss_optim.cu). Gradient
+    norm and clip coefficient are computed on the device in a fixed order; nothing syncs with
+    the host unless the caller reads the norm."""
+
+    def __init__(self, model: DecoderLM, cfg: OptimizerConfig):
+        self.model, self.cfg = model, cfg
+        flat = model.store.flat
+        self.n = flat.numel()
+        dev = flat.device
+        self.low_precision = flat.dtype != torch.float32
+        self.master = flat.detach().float().clone() if self.low_precision else flat.detach()
+        self.exp_avg = torch.zeros(self.n, dtype=torch.float32, device=dev)
+        self.exp_avg_sq = torch.zeros(self.n, dtype=torch.float32, device=dev)
+        self.main_grad = torch.zeros(self.n, dtype=torch.float32, device=dev)
+        self.step_count = 0
+        self._sq = torch.zeros(1, dtype=torch.float32, device=dev)
+        self._coef = torch.ones(1, dtype=torch.float32, device=dev)
+        self._norm = torch.zeros(1, dtype=torch.float32, device=dev)
+        self._scratch = None
+        self._hooks = []
+        for name in model.store.order:
+            spec = model.store.specs[name]
+            p = model.p(name)
+            view = self.main_grad[spec.offset:spec.offset + p.numel()].view(p.shape)
+            self._hooks.append(p.register_post_accumulate_grad_hook(self._make_hook(view)))
+
+    @staticmethod
+    def _make_hook(view):
+        def hook(p):
+            view.add_(p.grad)
+            p.grad = None
+        return hook
+
+    def zero_grad(self):
+        self.main_grad.zero_()
+
+    def lr_at(self, step: int) -> float:
+        c = self.cfg
+        if c.num_warmup_steps and step < c.num_warmup_steps:
+            return c.lr * (step + 1) / c.num_warmup_steps
+        if c.scheduler == "cosine" and c.total_steps > c.num_warmup_steps:
+            t = (step - c.num_warmup_steps) / (c.total_steps - c.num_warmup_steps)
+            return c.lr * (c.min_lr_ratio + (1 - c.min_lr_ratio) * 0.5 * (1 + math.cos(math.pi * min(1.0, t))))
+        if c.scheduler == "linear" and c.total_steps > c.num_warmup_steps:
+            t = (step - c.num_warmup_steps) / (c.total_steps - c.num_warmup_steps)
+            return c.lr * max(c.min_lr_ratio, 1 - t)
+        return c.lr
+
+    def grad_sq_norm(self, ps: ParallelState) -> torch.Tensor:
+        """Squared L2 norm of the full gradient. Replicated parameters are counted once."""
+        self._sq = F.reduce_sum_fixed(self.main_grad, square=True, out=self._sq, scratch=self._scratch)
+        if ps.tp > 1:
+            # sharded parameters add across TP; replicated ones are identical on every rank, so
+            # count them on TP rank 0 only
+            rep = torch.zeros_like(self._sq)
+            for name in self.model.store.order:
+                s = self.model.store.specs[name]
+                if s.shard_dim is None:
+                    g = self.main_grad[s.offset:s.offset + math.prod(s.shape)]
+                    rep += g.square().sum()
+            local = self._sq - (rep if ps.tp_rank != 0 else 0)
+            dist.all_reduce(local, group=ps.tp_group)
+            self._sq = local
+        return self._sq
+
+    def step(self, ps: ParallelState) -> torch.Tensor:
+        """Clip by global norm and apply AdamW. Returns the gradient norm (device scalar)."""
+        c = self.cfg
+        sq = self.grad_sq_norm(ps)
+        self.step_count += 1
+        lr = self.lr_at(self.step_count - 1)
+        flat = self.model.store.flat
+        if flat.is_cuda:
+            L = _native.lib()
+            _native.check(L.ix_clip_coef(sq.data_ptr(), c.max_grad_norm, self._coef.data_ptr(), self._norm.data_ptr(),
+                                         _native.stream()), "ix_clip_coef")
+            _native.check(L.ix_adamw(self.master.data_ptr(), self.exp_avg.data_ptr(), self.exp_avg_sq.data_ptr(),
+                                     self.main_grad.data_ptr(), flat.data_ptr() if self.low_precision else None,
+                                     self.n, 1, lr, c.beta1, c.beta2, c.eps, c.weight_decay, self.step_count,
+                                     self._coef.data_ptr(), _native.stream()), "ix_adamw")
+        else:
+            norm = sq.sqrt()
+            self._norm.copy_(norm)
+            coef = torch.clamp(c.max_grad_norm / (norm + 1e-6), max=1.0) if c.max_grad_norm > 0 else torch.ones(1)
+            g = self.main_grad * coef
+            self.exp_avg.mul_(c.beta1).add_(g, alpha=1 - c.beta1)
+            self.exp_avg_sq.mul_(c.beta2).addcmul_(g, g, value=1 - c.beta2)
+            bc1, bc2 = 1 - c.beta1 ** self.step_count, 1 - c.beta2 ** self.step_count
+            with torch.no_grad():
+                self.master.mul_(1 - lr * c.weight_decay)
+                self.master.addcdiv_(self.exp_avg / bc1, (self.exp_avg_sq / bc2).sqrt() + c.eps, value=-lr)
+                if self.low_precision:
+                    flat.copy_(self.master.to(flat.dtype))
+        self.zero_grad()
+        return self._norm
+
+    def state_dict(self) -> dict:
+        return {"master": self.master, "exp_avg": self.exp_avg, "exp_avg_sq": self.exp_avg_sq,
+                "step": self.step_count}
+
+    def load_state_dict(self, sd: dict) -> None:
+        with torch.no_grad():
+            self.master.copy_(sd["master"])
+            self.exp_avg.copy_(sd["exp_avg"])
+            self.exp_avg_sq.copy_(sd["exp_avg_sq"])
+            self.step_count = int(sd["step"])
+            if self.low_precision:
+                self.model.store.flat.copy_(self.master.to(self.model.store.flat.dtype))
+
+    def offload(self):
+        """Move optimizer state to pinned host memory (the colocated rollout phase needs the HBM)."""
+        for n in ("master", "exp_avg", "exp_avg_sq", "main_grad"):
+            t = getattr(self, n)
+            if t.is_cuda and not (n == "master" and not self.low_precision):
+                setattr(self, n, t.to("cpu", non_blocking=False).pin_memory())
+
+    def backload(self, device):
+        for n in ("master", "exp_avg", "exp_avg_sq", "main_grad"):
+            t = getattr(self, n)
+            if not t.is_cuda and torch.device(device).type == "cuda":
+                setattr(self, n, t.to(device, non_blocking=True))
+
+
+# ------------------------------------------------------------------------------------ worker
+class PolicyWorker:
+    def __init__(self, model: DecoderLM, cfg: WorkerConfig | None = None, algo: alg.AlgorithmConfig | None = None):
+        self.model = model
+        self.cfg = cfg or WorkerConfig()
+        self.algo = algo or alg.AlgorithmConfig()
+        self.ps = model.ps
+        self.device = model.device_
+        self.opt = FlatAdamW(model, self.cfg.optimizer)
+        self.launch_count = 0
+
+    # ---------------------------------------------------------------- forward pieces
+    def _run_model(self, mb: PackedMicroBatch, site: str):
+        dev = self.device
+        fc = ForwardCtx(positions=mb.positions.to(dev, non_blocking=True),
+                        meta=F.AttnMeta.packed(mb.seq_lens, self.model.hq, self.model.hkv, dev), site=site)
+        if self.model.cfg.has_gdn:
+            from ..ops.gdn import GDNMeta
+
+            fc.gdn_meta = GDNMeta.packed(mb.seq_lens, dev)
+        hidden = self.model(mb.ids.to(dev, non_blocking=True), fc,
+                            checkpoint_layers=self.cfg.checkpoint_layers and torch.is_grad_enabled())
+        return hidden
+
+    def _logprobs(self, mb: PackedMicroBatch, hidden, want_entropy: bool):
+        dev = self.device
+        rows = mb.pred_rows.to(dev, non_blocking=True)
+        tg = mb.targets.to(dev, non_blocking=True)
+        return lm_head_logprobs(self.model, hidden.index_select(0, rows), tg, self.cfg.logprob_chunk_rows, want_entropy)
+
+    # ---------------------------------------------------------------- verbs
+    @torch.no_grad()
+    def forward(self, batch: TrainingInputBatch) -> torch.Tensor:
+        """Scoring forward: log-probabilities of the response tokens, ``[B, max_response]`` fp32 (CPU)."""
+        R = batch["response_mask"].shape[1] if batch.get("response_mask") is not None else batch.metadata["response_length"]
+        seqs, att = batch["sequences"], batch["attention_mask"]
+        out = torch.zeros(seqs.shape[0], R, dtype=torch.float32)
+        for mb in pack_microbatches(seqs, att, R, self.cfg.max_tokens_per_microbatch):
+            hidden = self._run_model(mb, "trainer_score")
+            lp, _ = self._logprobs(mb, hidden, False)
+            flat = torch.zeros(len(mb.seq_index) * R, dtype=torch.float32, device=lp.device)
+            flat[mb.out_index.to(lp.device)] = lp
+            out[torch.tensor(mb.seq_index)] = flat.view(-1, R).cpu()
+        return out
+
+    def forward_backward(self, batch: TrainingInputBatch) -> dict:
+        """Accumulate the gradient of the (sum-reduced, advantage-pre-scaled) policy loss of a
+        mini-batch shard. Returns metrics (python floats)."""
+        algo = self.algo
+        R = batch["response_mask"].shape[1]
+        seqs, att = batch["sequences"], batch["attention_mask"]
+        loss_fn = alg.get_policy_loss(algo.policy_loss_type)
+        want_ent = self.cfg.want_entropy or algo.use_entropy_loss
+        tot = {"loss": 0.0, "clip_ratio_num": 0.0, "tokens": 0.0, "entropy_sum": 0.0, "kl_sum": 0.0}
+        dev = self.device
+        for mb in pack_microbatches(seqs, att, R, self.cfg.max_tokens_per_microbatch):
+            idx = torch.tensor(mb.seq_index)
+            hidden = self._run_model(mb, "trainer_fwd")
+            lp_flat, ent_flat = self._logprobs(mb, hidden, want_ent)
+            oi = mb.out_index.to(dev)
+            nb = len(mb.seq_index)
+
+            def to2d(x):
+                return torch.zeros(nb * R, dtype=torch.float32, device=dev).index_put((oi,), x).view(nb, R)
+
+            lp2d = to2d(lp_flat)
+            get = lambda k: (batch[k][idx].to(dev).float() if batch.get(k) is not None else None)
+            mask = get("loss_mask") if batch.get("loss_mask") is not None else get("response_mask")
+            old = get("action_log_probs")
+            if old is None:
+                old = lp2d.detach()
+            loss, m = loss_fn(lp2d, old, get("advantages"), algo, loss_mask=mask, rollout_logprobs=get("rollout_logprobs"))
+            ntok = mask.sum()
+            if algo.use_kl_loss and batch.get("base_action_log_probs") is not None:
+                kl = alg.compute_approx_kl(lp2d, get("base_action_log_probs"), mask, algo.kl_estimator_type)
+                scale = batch.metadata.get("aux_loss_scale", 1.0)
+                loss = loss + algo.kl_loss_coef * scale * (kl * mask).sum()
+                tot["kl_sum"] += float((kl * mask).sum().detach())
+            if want_ent:
+                ent2d = to2d(ent_flat)
+                tot["entropy_sum"] += float((ent2d * mask).sum().detach())
+                if algo.use_entropy_loss:
+                    scale = batch.metadata.get("aux_loss_scale", 1.0)
+                    loss = loss - algo.entropy_loss_coef * scale * (ent2d * mask).sum()
+            loss.backward()
+            tot["loss"] += float(loss.detach())
+            tot["clip_ratio_num"] += float(m.get("clip_ratio", 0.0)) * float(ntok)
+            tot["tokens"] += float(ntok)
+        n = max(1.0, tot["tokens"])
+        return {"policy_loss": tot["loss"], "ppo_clip_ratio": tot["clip_ratio_num"] / n, "loss_tokens": tot["tokens"],
+                "policy_entropy": tot["entropy_sum"] / n, "policy_kl": tot["kl_sum"] / n}
+
+    def reduce_gradients(self) -> None:
+        """Sum the main gradients over the data-parallel group (fixed bucket order)."""
+        if self.ps.dp > 1:
+            from ..parallel.dp import reduce_main_grads
+
+            reduce_main_grads(self.opt.main_grad, self.ps)
+
+    def optim_step(self) -> float:
+        self.reduce_gradients()
+        norm = self.opt.step(self.ps)
+        return float(norm.item())
+
+    # ---------------------------------------------------------------- memory residency (colocated runs)
+    def offload_optimizer(self):
+        self.opt.offload()
+
+    def backload_optimizer(self):
+        self.opt.backload(self.device)

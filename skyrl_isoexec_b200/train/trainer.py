@@ -1,0 +1,403 @@
+"""The RL controller: one GRPO/PPO step = generate -> score -> advantages -> update -> sync.
+
+Mirrors ``RayPPOTrainer.train`` (R/train/trainer.py:309-635) as an SPMD program: every rank (one
+process per GPU) runs this loop on its own shard of the prompts with a colocated rollout engine
+and policy worker; prompt groups never straddle ranks, so advantages need no communication, and
+the only cross-rank traffic of a step is the token-count / metric all-reduce and the gradient
+reduction. Ray is not needed.
+
+IsoExec hooks, as in the reference: contract built and installed on both sides at model
+construction (R/train/trainer.py:223), hash exchanged on the weight-sync init message and
+checked again on every sync, rollout-vs-train logprob gate after scoring (trainer.py:455-475,
+1540-1588; R/train/utils/trainer_utils.py:199-267).
+"""
+
+from __future__ import annotations
+
+import asyncio
+import os
+import random
+import time
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+
+from ..core import ledger as L
+from ..core import process as P
+from ..core.adapter import ContractAdapter, served_ops_of
+from ..core.testing import count_bit_mismatches
+from ..engine.interface import NativeInferenceEngine
+from ..engine.llm_engine import EngineConfig, LLMEngine
+from ..models.config import get_config
+from ..models.decoder import DecoderLM
+from ..parallel.state import ParallelState
+from ..sync import strategies as S
+from ..utils.tracking import Timer, Tracking
+from . import algorithms as alg
+from . import checkpoint as ckpt
+from .batch import TrainingInputBatch, build_sequences, pad_training_input_batch
+from .config import SkyRLTrainConfig, validate_cfg
+from .generator import GeneratorInput, GeneratorOutput, SkyRLGymGenerator
+from .policy_worker import PolicyWorker, WorkerConfig
+
+
+class ForwardGateError(RuntimeError):
+    pass
+
+
+def validate_isoexec_forward_gate(diff_abs: torch.Tensor, mask: torch.Tensor, mismatches: int, cfg) -> dict:
+    """Rollout-vs-train logprob gate. Under the contract the tolerance claim is zero, so any bit
+    mismatch refuses; the reference's mean/max envelope (1e-5 / 1e-4) is kept as a second line."""
+    n = mask.sum().clamp(min=1)
+    mean = float((diff_abs * mask).sum() / n)
+    mx = float((diff_abs * mask).max()) if diff_abs.numel() else 0.0
+    ok = mean <= cfg.gate_mean_limit and mx <= cfg.gate_max_limit and (mismatches == 0 or not cfg.require_bitwise)
+    return {"ok": ok, "mean": mean, "max": mx, "mismatches": mismatches}
+
+
+class SyntheticPromptDataset:
+    """Uniform-random token prompts with a fixed seed (the benchmark configurations use synthetic data)."""
+
+    def __init__(self, num_prompts: int, prompt_len: int, vocab_size: int, seed: int, env_class: str):
+        g = torch.Generator().manual_seed(seed)
+        self.prompts = [torch.randint(0, vocab_size, (prompt_len,), generator=g).tolist() for _ in range(num_prompts)]
+        self.env_class = env_class
+
+    def __len__(self):
+        return len(self.prompts)
+
+    def __getitem__(self, i):
+        return {"prompt": self.prompts[i], "env_class": self.env_class, "env_extras": {}, "uid": f"p{i}"}
+
+
+class PromptDataLoader:
+    """Shuffling batch iterator with a resumable state (epoch, cursor, rng)."""
+
+    def __init__(self, dataset, batch_size: int, seed: int, shuffle: bool = True, drop_last: bool = True):
+        self.ds, self.bs, self.seed, self.shuffle, self.drop_last = dataset, batch_size, seed, shuffle, drop_last
+        self.epoch, self.cursor = 0, 0
+        self._order = self._make_order()
+
+    def _make_order(self):
+        idx = list(range(len(self.ds)))
+        if self.shuffle:
+            random.Random(self.seed + self.epoch).shuffle(idx)
+        return idx
+
+    def __len__(self):
+        return len(self.ds) // self.bs if self.drop_last else (len(self.ds) + self.bs - 1) // self.bs
+
+    def __iter__(self):
+        while self.cursor + (self.bs if self.drop_last else 1) <= len(self._order):
+            batch = [self.ds[i] for i in self._order[self.cursor:self.cursor + self.bs]]
+            self.cursor += self.bs
+            yield batch
+        self.epoch += 1
+        self.cursor = 0
+        self._order = self._make_order()
+
+    def state_dict(self):
+        return {"epoch": self.epoch, "cursor": self.cursor, "seed": self.seed}
+
+    def load_state_dict(self, sd):
+        self.epoch, self.cursor, self.seed = sd["epoch"], sd["cursor"], sd["seed"]
+        self._order = self._make_order()
+
+
+class RayPPOTrainer:
+    """Name kept for API parity; no Ray involved."""
+
+    def __init__(self, cfg: SkyRLTrainConfig, ps: ParallelState | None = None, device: str | None = None,
+                 dataset=None, tokenizer=None, tracker: Tracking | None = None):
+        self.cfg = cfg
+        self.ps = ps or ParallelState.single()
+        self.rank = dist.get_rank() if dist.is_initialized() else 0
+        self.world = dist.get_world_size() if dist.is_initialized() else 1
+        validate_cfg(cfg, self.world)
+        self.device = torch.device(device or ("cuda" if torch.cuda.is_available() else "cpu"))
+        self.tokenizer = tokenizer
+        self.global_step = 0
+        self.all_metrics: dict = {}
+        self.all_timings: dict = {}
+        t = cfg.trainer
+        self.tracker = tracker or (Tracking(t.project_name, t.run_name, t.logger, cfg.to_dict()) if self.rank == 0 else None)
+        self.dataset = dataset
+        self.policy: PolicyWorker | None = None
+        self.engine: LLMEngine | None = None
+        self.generator: SkyRLGymGenerator | None = None
+        self.kl_ctrl = alg.get_kl_controller(t.algorithm)
+
+    # ------------------------------------------------------------------ build
+    def build_models(self) -> None:
+        t, g = self.cfg.trainer, self.cfg.generator
+        mcfg = get_config(t.policy.model, **t.policy.model_overrides)
+        model = DecoderLM(mcfg, self.ps, self.device, seed=t.policy.seed)
+        wcfg = WorkerConfig(max_tokens_per_microbatch=t.max_tokens_per_microbatch, optimizer=t.policy.optimizer_config,
+                            want_entropy=t.algorithm.use_entropy_loss)
+        algo = t.algorithm
+        if not algo.max_seq_len:
+            algo.max_seq_len = t.max_prompt_length + g.sampling_params.max_generate_length
+        self.policy = PolicyWorker(model, wcfg, algo)
+        ie = g.inference_engine
+        ecfg = EngineConfig(max_num_seqs=ie.max_num_seqs, max_num_batched_tokens=ie.max_num_batched_tokens,
+                            num_kv_pages=ie.num_kv_pages, gpu_memory_utilization=ie.gpu_memory_utilization,
+                            seed=t.seed + 7919 * self.rank, enable_prefix_caching=ie.enable_prefix_caching,
+                            use_cuda_graph=not ie.enforce_eager,
+                            max_model_len=min(mcfg.max_position, t.max_prompt_length + g.sampling_params.max_generate_length + 1))
+        # colocated, same TP layout: the engine computes with the trainer's flat parameter buffer
+        self.engine = LLMEngine(model, ecfg)
+        self.infer = NativeInferenceEngine(self.engine, self.tokenizer)
+        self.generator = SkyRLGymGenerator(self.infer, self.tokenizer, max_turns=g.max_turns, batched=g.batched,
+                                           env_config=self.cfg.environment.env_kwargs,
+                                           zero_reward_on_non_stop=g.zero_reward_on_non_stop,
+                                           apply_overlong_filtering=g.apply_overlong_filtering)
+        if t.isoexec.enabled:
+            self.adapter_trainer = ContractAdapter("trainer", model, self.rank, engine_tp=ie.tensor_parallel_size
+                                                   if not ie.run_engines_locally else self.ps.tp)
+            self.adapter_trainer.run_install()
+            self.adapter_engine = ContractAdapter("engine", model, self.rank)
+            self.adapter_engine.run_install()
+        if self.dataset is None:
+            d = self.cfg.data
+            n = d.synthetic_prompts or t.train_batch_size * 4
+            self.dataset = SyntheticPromptDataset(n, d.synthetic_prompt_len, mcfg.vocab_size, t.seed,
+                                                  self.cfg.environment.env_class)
+        per_rank = t.train_batch_size // self.ps.dp if self.ps.dp > 1 else t.train_batch_size
+        self.loader = PromptDataLoader(self.dataset, per_rank, t.seed + self.ps.dp_rank)
+        self.init_weight_sync_state()
+
+    def init_weight_sync_state(self) -> None:
+        """Stamp the trainer's contract hash on the init message; the engine's receiver refuses a mismatch."""
+        info = S.create_init_info("shared") if self.cfg.trainer.isoexec.enabled else S.SharedInitInfo(contract_hash=None)
+        self.sync_info = info
+        if self.cfg.trainer.isoexec.enabled:
+            self.receiver = S.create_receiver(info, self.engine.model)
+        self.sender = S.create_sender(info, self.policy.model)
+
+    # ------------------------------------------------------------------ one step, phase by phase
+    def prepare_generator_input(self, rows: list[dict]) -> tuple[GeneratorInput, list[str]]:
+        n = self.cfg.generator.n_samples_per_prompt
+        sp = self.cfg.generator.sampling_params
+        prompts, envs, extras, uids = [], [], [], []
+        for r in rows:
+            for _ in range(n):
+                prompts.append(r["prompt"])
+                envs.append(r["env_class"])
+                extras.append(r.get("env_extras") or {})
+                uids.append(r["uid"])
+        gi: GeneratorInput = {"prompts": prompts, "env_classes": envs, "env_extras": extras,
+                              "sampling_params": {"max_generate_length": sp.max_generate_length, "temperature": sp.temperature,
+                                                  "top_p": sp.top_p, "top_k": sp.top_k, "min_p": sp.min_p,
+                                                  "ignore_eos": sp.ignore_eos},
+                              "trajectory_ids": None, "batch_metadata": {"global_step": self.global_step}}
+        return gi, uids
+
+    def generate(self, gi: GeneratorInput) -> GeneratorOutput:
+        return asyncio.run(self.generator.generate(gi))
+
+    def convert_to_training_input(self, go: GeneratorOutput, uids: list[str]) -> TrainingInputBatch:
+        seq, att, rmask = build_sequences(go["prompt_token_ids"], go["response_ids"])
+        B, R = rmask.shape
+        loss_mask = torch.zeros(B, R)
+        rewards = torch.zeros(B, R)
+        rollout_lp = torch.zeros(B, R)
+        for i in range(B):
+            n = len(go["response_ids"][i])
+            loss_mask[i, :n] = torch.tensor(go["loss_masks"][i], dtype=torch.float32)
+            r = go["rewards"][i]
+            if isinstance(r, (list, tuple)):
+                rewards[i, :n] = torch.tensor(r, dtype=torch.float32)
+            elif n > 0:
+                rewards[i, n - 1] = float(r)     # outcome reward sits on the last response token
+            if go.get("rollout_logprobs") is not None:
+                rollout_lp[i, :n] = torch.tensor(go["rollout_logprobs"][i], dtype=torch.float32)
+        b = TrainingInputBatch({"sequences": seq, "attention_mask": att, "response_mask": rmask, "loss_mask": loss_mask,
+                                "rewards": rewards, "rollout_logprobs": rollout_lp})
+        lens = rmask.sum(1)
+        b.metadata = {"uids": list(uids), "response_length": R, "avg_response_length": float(lens.mean()),
+                      "max_response_length": int(lens.max())}
+        return b
+
+    def fwd_logprobs_values_reward(self, batch: TrainingInputBatch) -> TrainingInputBatch:
+        lp = self.policy.forward(batch)
+        batch["action_log_probs"] = lp
+        mask = batch["response_mask"]
+        ro = batch["rollout_logprobs"]
+        diff = (lp - ro).abs() * mask
+        n = mask.sum().clamp(min=1)
+        mean = diff.sum() / n
+        std = ((diff - mean).pow(2) * mask).sum().div(n).sqrt()
+        mism = count_bit_mismatches((lp * mask).contiguous(), (ro * mask).contiguous())
+        self.all_metrics.update({
+            "policy/rollout_train_logprobs_abs_diff_max": float(diff.max()) if diff.numel() else 0.0,
+            "policy/rollout_train_logprobs_abs_diff_min": float(diff[mask > 0].min()) if mask.sum() > 0 else 0.0,
+            "policy/rollout_train_logprobs_abs_diff_mean": float(mean),
+            "policy/rollout_train_logprobs_abs_diff_std": float(std),
+            "policy/rollout_train_logprob_bit_mismatches": mism,
+        })
+        iso = self.cfg.trainer.isoexec
+        if iso.enabled:
+            gate = validate_isoexec_forward_gate(diff, mask, mism, iso)
+            if self.global_step <= 1 and hasattr(self, "adapter_trainer"):
+                self.adapter_trainer.on_gate(gate["ok"], f"mean={gate['mean']:.3e} max={gate['max']:.3e} "
+                                                           f"mismatches={gate['mismatches']}")
+            if not gate["ok"]:
+                msg = (f"IsoExec forward gate refused at step {self.global_step}: mean={gate['mean']:.3e} "
+                       f"max={gate['max']:.3e} bit mismatches={gate['mismatches']}")
+                if iso.strict:
+                    raise ForwardGateError(msg)
+                print("[warn] " + msg)
+        return batch
+
+    def compute_advantages_and_returns(self, batch: TrainingInputBatch) -> TrainingInputBatch:
+        a = self.cfg.trainer.algorithm
+        adv, ret = alg.compute_advantages_and_returns(batch["rewards"], batch["response_mask"], batch.metadata["uids"],
+                                                      a.advantage_estimator, a, values=batch.get("values"))
+        batch["advantages"], batch["returns"] = adv, ret
+        m = batch["response_mask"]
+        scores = batch["rewards"].sum(-1)
+        self.all_metrics.update({"reward/avg_raw_reward": float(scores.mean()),
+                                 "reward/avg_pass_rate": float((scores > 0).float().mean()),
+                                 "policy/avg_advantage_abs": float((adv.abs() * m).sum() / m.sum().clamp(min=1))})
+        return batch
+
+    def _global_sum(self, x: float) -> float:
+        if self.ps.dp > 1:
+            t = torch.tensor([x], dtype=torch.float64, device=self.device if self.device.type == "cuda" else "cpu")
+            dist.all_reduce(t, group=self.ps.dp_group)
+            return float(t.item())
+        return x
+
+    def train_critic_and_policy(self, batch: TrainingInputBatch) -> dict:
+        t, a = self.cfg.trainer, self.cfg.trainer.algorithm
+        n_samples = self.cfg.generator.n_samples_per_prompt
+        mb_seqs = (t.policy_mini_batch_size * n_samples) // max(1, self.ps.dp)
+        B = batch.batch_size
+        out = {"policy_loss": 0.0, "ppo_clip_ratio": 0.0, "grad_norm": 0.0, "policy_entropy": 0.0}
+        n_updates = 0
+        for _epoch in range(t.update_epochs_per_batch):
+            for lo in range(0, B, mb_seqs):
+                mb = batch.slice(lo, min(B, lo + mb_seqs))
+                lm = mb["loss_mask"]
+                # mean-type reductions by advantage pre-scaling, with GLOBAL mini-batch statistics
+                if a.loss_reduction == "token_mean":
+                    tot = self._global_sum(float(lm.sum()))
+                    mb["advantages"] = mb["advantages"] / max(1.0, tot)
+                    mb.metadata["aux_loss_scale"] = 1.0 / max(1.0, tot)
+                else:
+                    gB = int(self._global_sum(float(mb.batch_size)))
+                    scaled = alg.apply_loss_reduction_to_advantages(mb["advantages"], lm, a.loss_reduction,
+                                                                    t.micro_train_batch_size_per_gpu, a.max_seq_len)
+                    mb["advantages"] = scaled * (mb.batch_size / max(1, gB))
+                    mb.metadata["aux_loss_scale"] = 1.0 / max(1.0, self._global_sum(float(lm.sum())))
+                m = self.policy.forward_backward(mb)
+                gn = self.policy.optim_step()
+                out["policy_loss"] += m["policy_loss"]
+                out["ppo_clip_ratio"] += m["ppo_clip_ratio"]
+                out["policy_entropy"] += m["policy_entropy"]
+                out["grad_norm"] += gn
+                n_updates += 1
+        for k in out:
+            out[k] /= max(1, n_updates)
+        out["policy_loss"] = self._global_sum(out["policy_loss"])
+        self.all_metrics.update({f"policy/{k}": v for k, v in out.items()})
+        self.all_metrics["policy/policy_lr"] = self.policy.opt.lr_at(max(0, self.policy.opt.step_count - 1))
+        return out
+
+    def sync_weights(self) -> None:
+        """Trainer -> rollout. Same process and layout: the flat buffer is shared, so the transfer is
+        the handshake, the state invalidation and the verification that the alias still holds."""
+        iso = self.cfg.trainer.isoexec.enabled
+        req = self.sender.send_chunks(S.extract_native_weights(self.policy.model, None))
+        if iso:
+            n = S.load_weights(self.engine.model, ((k, v) for k, v in self.receiver.receive_weights(req)))
+            assert n == len(req.names)
+            self.adapter_engine.on_weight_sync(self.sync_info.contract_hash, [s.state_id for s in
+                                                                               self.adapter_engine.contract.claims.state])
+            self.adapter_trainer.on_weight_sync(P.contract_hash(self.adapter_engine.contract))
+        self.engine.reset_prefix_cache()
+
+    # ------------------------------------------------------------------ the loop
+    def train_step(self, rows: list[dict]) -> dict:
+        """One full RL step on this rank's prompt shard. Returns the step's metrics."""
+        self.all_metrics, self.all_timings = {}, {}
+        self.global_step += 1
+        T = self.all_timings
+        with Timer("step", T):
+            with Timer("prepare_input", T):
+                gi, uids = self.prepare_generator_input(rows)
+            with Timer("wake", T):
+                self.engine.wake_up()
+            with Timer("generate", T):
+                go = self.generate(gi)
+            with Timer("sleep", T):
+                self.engine.sleep()
+            with Timer("convert", T):
+                batch = self.convert_to_training_input(go, uids)
+            if self.global_step == 1 and hasattr(self, "adapter_engine"):
+                for ad in (self.adapter_engine,):
+                    ad.note_served(served_ops_of(self.policy.model.cfg))
+                    ad.on_first_forward()
+            with Timer("fwd_logprobs", T):
+                batch = self.fwd_logprobs_values_reward(batch)
+            if self.global_step == 1 and hasattr(self, "adapter_trainer"):
+                self.adapter_trainer.note_served(served_ops_of(self.policy.model.cfg))
+                self.adapter_trainer.on_first_forward()
+            with Timer("advantages", T):
+                batch = self.compute_advantages_and_returns(batch)
+            with Timer("policy_train", T):
+                self.train_critic_and_policy(batch)
+            with Timer("sync_weights", T):
+                self.sync_weights()
+        t = self.cfg.trainer
+        if t.ckpt_path and t.ckpt_interval > 0 and self.global_step % t.ckpt_interval == 0:
+            with Timer("save_checkpoints", T):
+                self.save_checkpoints()
+        self.all_metrics.update(go.get("rollout_metrics") or {})
+        ntok = sum(len(r) for r in go["response_ids"])
+        self.all_metrics["generate/response_tokens"] = ntok
+        self.all_metrics["generate/tokens_per_s"] = ntok / max(1e-9, T["generate"])
+        self.all_metrics.update({f"timing/{k}": v for k, v in T.items()})
+        if self.tracker is not None:
+            self.tracker.log(self.all_metrics, self.global_step)
+        return dict(self.all_metrics)
+
+    def train(self) -> None:
+        if self.policy is None:
+            self.build_models()
+        t = self.cfg.trainer
+        if t.ckpt_path and t.resume_mode != "none":
+            self.load_checkpoints()
+        self.sync_weights()
+        try:
+            for _epoch in range(t.epochs):
+                for rows in self.loader:
+                    self.train_step(rows)
+                    if 0 < t.num_steps <= self.global_step:
+                        return
+        except BaseException as e:  # noqa: BLE001
+            if self.tracker is not None:
+                self.tracker.log_exception(e, self.global_step)
+            raise
+        finally:
+            if t.isoexec.enabled and t.ckpt_path and hasattr(self, "adapter_trainer"):
+                self.adapter_trainer.ledger.write_verdict(t.ckpt_path)
+                self.adapter_engine.ledger.write_verdict(t.ckpt_path)
+
+    # ------------------------------------------------------------------ checkpoints
+    def save_checkpoints(self) -> str:
+        t = self.cfg.trainer
+        return ckpt.save_checkpoint(t.ckpt_path, self.global_step, self.policy, self.loader.state_dict(),
+                                    {"global_step": self.global_step, "config": self.cfg.to_dict()}, self.ps,
+                                    max_to_keep=t.max_ckpts_to_keep)
+
+    def load_checkpoints(self) -> int:
+        t = self.cfg.trainer
+        path = ckpt.resolve_resume_path(t.ckpt_path, t.resume_mode, t.resume_path)
+        if path is None:
+            return 0
+        data_state, trainer_state = ckpt.load_checkpoint(path, self.policy, self.ps)
+        self.loader.load_state_dict(data_state)
+        self.global_step = int(trainer_state["global_step"])
+        return self.global_step
