@@ -157,7 +157,8 @@ class LLMEngine:
         self._next_id = 0
         self.paused = False
         self.asleep = False
-        self.stats = {"steps": 0, "tokens": 0, "prefill_tokens": 0, "decode_tokens": 0, "preemptions": 0}
+        self.stats = {"steps": 0, "tokens": 0, "prefill_tokens": 0, "decode_tokens": 0, "preemptions": 0,
+                      "h2d_bytes": 0, "d2h_bytes": 0}
         self.gdn_state = None
         if self.mcfg.has_gdn:
             from .gdn_state import GDNStatePool
@@ -175,6 +176,13 @@ class LLMEngine:
             budget = 256 << 20
         want = self.cfg.max_num_seqs * ((self.max_len + PAGE - 1) // PAGE)
         return max(2, min(want, budget // per_page))
+
+    def _h2d(self, t: torch.Tensor) -> torch.Tensor:
+        """Stage a host tensor in pinned memory and copy it to the engine's device (counted)."""
+        self.stats["h2d_bytes"] += t.numel() * t.element_size()
+        if self.device.type != "cuda":
+            return t
+        return t.pin_memory().to(self.device, non_blocking=True)
 
     # ------------------------------------------------------------------ lifecycle
     def sleep(self, tags: list[str] | None = None) -> None:
@@ -244,23 +252,21 @@ class LLMEngine:
                 sample_rows.append(row + n - 1)
                 sample_seqs.append(s)
             row += n
-        dev = self.device
         maxp = max(len(b) for b in bt_rows)
         bt = torch.zeros(len(bt_rows), maxp, dtype=torch.int32)
         for i, b in enumerate(bt_rows):
             bt[i, :len(b)] = torch.tensor(b, dtype=torch.int32)
         fc = ForwardCtx(
-            positions=torch.tensor(pos, dtype=torch.int32).to(dev, non_blocking=True),
-            meta=F.AttnMeta(torch.tensor(items, dtype=torch.int32).reshape(-1, 8).to(dev, non_blocking=True),
-                            bt.to(dev, non_blocking=True)),
-            slots=torch.tensor(slots, dtype=torch.int64).to(dev, non_blocking=True),
+            positions=self._h2d(torch.tensor(pos, dtype=torch.int32)),
+            meta=F.AttnMeta(self._h2d(torch.tensor(items, dtype=torch.int32).reshape(-1, 8)), self._h2d(bt)),
+            slots=self._h2d(torch.tensor(slots, dtype=torch.int64)),
             kv=self.cache.pools,
             site="engine_decode" if not prefill else "engine_prefill",
         )
         if self.gdn_state is not None:
             fc.gdn_meta = self.gdn_state.step_meta(decode, prefill)
             fc.kv = self.gdn_state.merge_into(self.cache.pools)
-        hidden = self.model(torch.tensor(ids, dtype=torch.int64).to(dev, non_blocking=True), fc)
+        hidden = self.model(self._h2d(torch.tensor(ids, dtype=torch.int64)), fc)
         for s in decode:
             s.num_computed += 1
         for s, start, n in prefill:
@@ -271,13 +277,14 @@ class LLMEngine:
         self.stats["prefill_tokens"] += row - len(decode)
         finished: list[Sequence] = []
         if sample_rows:
-            rows = torch.tensor(sample_rows, dtype=torch.int64).to(dev)
+            rows = self._h2d(torch.tensor(sample_rows, dtype=torch.int64))
             logits = self.model.logits(hidden.index_select(0, rows))
             if self.model.ps.tp > 1:
                 from ..parallel.tp import column_parallel_gather
 
                 logits = column_parallel_gather(logits, self.model.ps)
             tokens, lps = self.sampler(logits, [s.params for s in sample_seqs])
+            self.stats["d2h_bytes"] += tokens.numel() * 8 + lps.numel() * 4
             tokens, lps = tokens.tolist(), lps.tolist()
             for s, tok, lp in zip(sample_seqs, tokens, lps):
                 s.output_ids.append(tok)

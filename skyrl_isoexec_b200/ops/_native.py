@@ -78,7 +78,17 @@ def lib():
     return h
 
 
+_launches = 0
+
+
+def launch_count() -> int:
+    """Number of native launcher calls made by this process (every launcher result passes through ``check``)."""
+    return _launches
+
+
 def check(rc: int, what: str) -> None:
+    global _launches
+    _launches += 1
     if rc != 0:
         msg = lib().ix_last_error()
         raise NativeError(f"{what} failed (rc={rc}): {msg.decode() if msg else ''}")

@@ -1,0 +1,254 @@
+"""sm_100a kernels against (a) a plain PyTorch fp32 reference of the same op and (b) the C++ CPU
+restatement with the same reduction order (bitwise where the chain has no transcendental
+function). Also the invariance properties the execution contract claims."""
+import math
+
+import pytest
+import torch
+
+from skyrl_isoexec_b200.core.testing import bitwise_equal, count_bit_mismatches
+from skyrl_isoexec_b200.ops import _native
+from skyrl_isoexec_b200.ops import functional as F
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+@pytest.fixture(autouse=True)
+def _status_clean():
+    yield
+    assert _native.read_status() == 0, "a kernel's bounded wait ran out"
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (1000, 4096, 1024), (8, 4096, 4096), (333, 1000, 776), (1, 2048, 256)])
+def test_gemm_matches_fp32_and_is_invariant(M, N, K):
+    torch.manual_seed(0)
+    x = (torch.randn(M, K, device=DEV) * 0.5).bfloat16()
+    w = (torch.randn(N, K, device=DEV) * 0.05).bfloat16()
+    ref = x.float() @ w.float().T
+    outs = {bn: F.gemm_nt(x, w, bn=bn) for bn in (32, 64, 128, 256)}
+    for o in outs.values():
+        assert (o.float() - ref).abs().max() <= 1e-2 * ref.abs().max() + 1e-3
+    assert all(bitwise_equal(outs[32], outs[b]) for b in (64, 128, 256))       # N-tile invariance
+    k = min(M, 3)
+    assert bitwise_equal(F.gemm_nt(x[:k].contiguous(), w), outs[256][:k])        # row-count invariance
+    f32 = F.gemm_nt(x, w, out_f32=True)
+    assert (f32 - ref).abs().max() <= 2e-4 * max(1.0, ref.abs().max().item())
+    assert bitwise_equal(f32.bfloat16(), outs[256])                               # bf16 out = one round of the fp32 acc
+
+
+def test_gemm_strided_input_rows():
+    torch.manual_seed(1)
+    big = (torch.randn(64, 512, device=DEV)).bfloat16()
+    x = big[:, 128:384]                      # row stride 512, K = 256
+    w = (torch.randn(96, 256, device=DEV) * 0.1).bfloat16()
+    assert bitwise_equal(F.gemm_nt(x, w), F.gemm_nt(x.contiguous(), w))
+
+
+@pytest.mark.parametrize("zero_centered", [False, True])
+@pytest.mark.parametrize("N", [128, 4096, 2560])
+def test_rmsnorm_bitwise_vs_cpu_oracle(N, zero_centered):
+    torch.manual_seed(2)
+    x, r, w = (torch.randn(37, N) * 2).bfloat16(), torch.randn(37, N).bfloat16(), torch.randn(N).bfloat16()
+    y_c, res_c, _ = F.rmsnorm_fwd(x, w, 1e-6, zero_centered, r)
+    y_g, res_g, _ = F.rmsnorm_fwd(x.to(DEV), w.to(DEV), 1e-6, zero_centered, r.to(DEV))
+    assert bitwise_equal(res_g.cpu(), res_c) and bitwise_equal(y_g.cpu(), y_c)
+    h = x.float() + r.float()
+    g = (1 + w.float()) if zero_centered else w.float()
+    ref = h.bfloat16().float() * torch.rsqrt(h.bfloat16().float().pow(2).mean(-1, keepdim=True) + 1e-6) * g
+    assert (y_g.cpu().float() - ref).abs().max() <= 0.05 * ref.abs().max()
+
+
+@pytest.mark.parametrize("Hq,Hkv,D,gate", [(8, 2, 128, False), (4, 2, 64, False), (4, 2, 128, True)])
+def test_qk_norm_rope_bitwise_vs_cpu_oracle(Hq, Hkv, D, gate):
+    torch.manual_seed(3)
+    T = 53
+    rows = (Hq * (2 if gate else 1) + 2 * Hkv) * D
+    qkv = torch.randn(T, rows).bfloat16()
+    qw, kw = torch.randn(D).bfloat16(), torch.randn(D).bfloat16()
+    pos = torch.randint(0, 1000, (T,), dtype=torch.int32)
+    slots = torch.randperm(256)[:T].to(torch.int64)
+    outs = []
+    for dev in ("cpu", DEV):
+        rope = F.RopeTable(D, 1024, 1e6, dev)
+        kp, vp = torch.zeros(256, Hkv, D, dtype=torch.bfloat16, device=dev), torch.zeros(256, Hkv, D, dtype=torch.bfloat16, device=dev)
+        q = F.qk_norm_rope_fwd(qkv.to(dev), pos.to(dev), slots.to(dev), rope, qw.to(dev), kw.to(dev), kp, vp, Hq, Hkv, D, 1e-6,
+                               True, False, gate)
+        outs.append((q.cpu(), kp.cpu(), vp.cpu()))
+    for a, b in zip(*outs):
+        assert bitwise_equal(a, b)
+
+
+def _attn_ref(q, k, v, lens, scale):
+    outs, s = [], 0
+    G = q.shape[1] // k.shape[1]
+    for n in lens:
+        qs = q[s:s + n].float().transpose(0, 1)
+        ks = k[s:s + n].float().repeat_interleave(G, 1).transpose(0, 1)
+        vs = v[s:s + n].float().repeat_interleave(G, 1).transpose(0, 1)
+        sc = (qs @ ks.transpose(1, 2)) * scale
+        sc = sc.masked_fill(~torch.ones(n, n, dtype=torch.bool, device=q.device).tril(), float("-inf"))
+        outs.append((sc.softmax(-1) @ vs).transpose(0, 1))
+        s += n
+    return torch.cat(outs, 0)
+
+
+@pytest.mark.parametrize("Hq,Hkv,D", [(8, 2, 128), (4, 2, 64), (32, 8, 128), (16, 2, 128)])
+def test_attention_packed_vs_fp32_and_cpu_oracle(Hq, Hkv, D):
+    torch.manual_seed(4)
+    lens = [300, 17, 129, 128]
+    T = sum(lens)
+    q, k, v = (torch.randn(T, h, D, device=DEV).bfloat16() for h in (Hq, Hkv, Hkv))
+    scale = 1 / math.sqrt(D)
+    out, lse = F.attention_fwd(q, k, v, F.AttnMeta.packed(lens, Hq, Hkv, DEV), scale, want_lse=True)
+    ref = _attn_ref(q, k, v, lens, scale)
+    assert (out.float() - ref).abs().max() < 2e-2
+    oc, lc = F.attention_fwd(q.cpu(), k.cpu(), v.cpu(), F.AttnMeta.packed(lens, Hq, Hkv, "cpu"), scale, want_lse=True)
+    assert (out.cpu().float() - oc.float()).abs().max() < 2e-2 and (lse.cpu() - lc).abs().max() < 1e-3
+
+
+def test_attention_decode_and_chunk_equal_prefill_bitwise_paged():
+    torch.manual_seed(5)
+    Hq, Hkv, D, S = 32, 8, 128, 700
+    q, k, v = (torch.randn(S, h, D, device=DEV).bfloat16() for h in (Hq, Hkv, Hkv))
+    scale = 1 / math.sqrt(D)
+    full, _ = F.attention_fwd(q, k, v, F.AttnMeta.packed([S], Hq, Hkv, DEV), scale)
+    nblk = (S + 127) // 128
+    perm = torch.randperm(nblk + 4)[:nblk]
+    kc = torch.zeros((nblk + 4) * 128, Hkv, D, device=DEV, dtype=torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    for b, p in enumerate(perm.tolist()):
+        lo, hi = b * 128, min(S, b * 128 + 128)
+        kc[p * 128:p * 128 + hi - lo], vc[p * 128:p * 128 + hi - lo] = k[lo:hi], v[lo:hi]
+    bt = perm.to(torch.int32).view(1, -1).to(DEV)
+    for t in (0, 127, 128, 511, S - 1):                       # single-token decode at several positions
+        items = torch.tensor([[0, 1, t, t + 1, 0, 0, 0, 0]], dtype=torch.int32, device=DEV)
+        o, _ = F.attention_fwd(q[t:t + 1].contiguous(), kc, vc, F.AttnMeta(items, bt), scale)
+        assert bitwise_equal(o[0], full[t])
+    items = torch.tensor([[0, 32, S - 45, S - 13, 0, 0, 0, 0], [32, 13, S - 13, S, 0, 0, 0, 0]], dtype=torch.int32, device=DEV)
+    o, _ = F.attention_fwd(q[S - 45:].contiguous(), kc, vc, F.AttnMeta(items, bt), scale)   # chunked prefill
+    assert bitwise_equal(o, full[S - 45:])
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_logprobs_vs_fp32_cpu_oracle_and_row_invariance(dtype):
+    torch.manual_seed(6)
+    V = 151936
+    logits = (torch.randn(9, V, device=DEV) * 3).to(dtype)
+    tg = torch.randint(0, V, (9,), device=DEV)
+    lp, lse, ent = F.logprob_fused_fwd(logits, tg, 8, want_entropy=True)
+    ref = torch.log_softmax(logits.float(), -1)
+    assert (lp - ref.gather(1, tg[:, None])[:, 0]).abs().max() < 3e-6
+    assert (ent - (-(ref.exp() * ref).sum(-1))).abs().max() < 1e-3
+    lp1, _, _ = F.logprob_fused_fwd(logits[4:5].contiguous(), tg[4:5], 8)
+    assert bitwise_equal(lp1, lp[4:5])
+    lpc, lsec, _ = F.logprob_fused_fwd(logits.cpu(), tg.cpu(), 8)
+    assert (lp.cpu() - lpc).abs().max() < 2e-6 and (lse.cpu() - lsec).abs().max() < 2e-6
+
+
+def test_logprob_staged_equals_fused_bitwise():
+    """TP path: row max / leaf sums / finalize over two vocabulary shards == the fused kernel."""
+    torch.manual_seed(7)
+    V, G, rows = 4096, 8, 11
+    logits = (torch.randn(rows, V, device=DEV) * 2).bfloat16()
+    tg = torch.randint(0, V, (rows,), device=DEV)
+    lp, lse, _ = F.logprob_fused_fwd(logits, tg, G)
+    L = _native.lib()
+    s = _native.stream()
+    mx = torch.empty(2, rows, device=DEV)
+    leaf = torch.empty(rows, G, device=DEV)
+    tl = torch.zeros(2, rows, device=DEV)
+    half = V // 2
+    shards = [logits[:, :half].contiguous(), logits[:, half:].contiguous()]
+    for r, sh in enumerate(shards):
+        _native.check(L.ix_logprob_rowmax(sh.data_ptr(), half, rows, half, mx[r].data_ptr(), 0, s), "rowmax")
+    m = torch.maximum(mx[0], mx[1])
+    for r, sh in enumerate(shards):
+        _native.check(L.ix_logprob_leafsum(sh.data_ptr(), half, rows, half, G // 2, G, r * (G // 2), m.data_ptr(),
+                                           leaf.data_ptr(), None, 0, s), "leafsum")
+        _native.check(L.ix_logprob_gather_target(sh.data_ptr(), half, rows, half, r * half, tg.data_ptr(), tl[r].data_ptr(), 0, s), "gather")
+    t_logit = tl[0] + tl[1]
+    lp2, lse2 = torch.empty(rows, device=DEV), torch.empty(rows, device=DEV)
+    _native.check(L.ix_logprob_finalize(leaf.data_ptr(), None, m.data_ptr(), t_logit.data_ptr(), tg.data_ptr(), lp2.data_ptr(),
+                                        lse2.data_ptr(), None, rows, G, s), "finalize")
+    assert bitwise_equal(lp2, lp) and bitwise_equal(lse2, lse)
+
+
+def test_logprob_backward_matches_autograd():
+    torch.manual_seed(8)
+    V = 4096
+    logits = (torch.randn(7, V, device=DEV) * 2).bfloat16().requires_grad_()
+    tg = torch.randint(0, V, (7,), device=DEV)
+    lp, ent = F.token_logprobs(logits, tg, 8, want_entropy=True)
+    w = torch.arange(1, 8.0, device=DEV)
+    ((lp * w).sum() + 0.3 * ent.sum()).backward()
+    l2 = logits.detach().float().requires_grad_()
+    ls = torch.log_softmax(l2, -1)
+    ((ls.gather(1, tg[:, None])[:, 0] * w).sum() + 0.3 * (-(ls.exp() * ls).sum(-1)).sum()).backward()
+    assert (logits.grad.float() - l2.grad).abs().max() < 2e-2
+
+
+def test_swiglu_and_reduce_and_adamw():
+    torch.manual_seed(9)
+    x = torch.randn(33, 512, device=DEV).bfloat16()
+    y = F.swiglu_fwd(x)
+    ref = torch.nn.functional.silu(x[:, :256].float()).bfloat16().float() * x[:, 256:].float()
+    assert (y.float() - ref).abs().max() < 2e-2
+    yc = F.swiglu_fwd(x.cpu())
+    assert count_bit_mismatches(y.cpu(), yc) <= 0.001 * y.numel()          # expf implementations may differ in the last ulp
+    g = torch.randn(100003, device=DEV)
+    a = F.reduce_sum_fixed(g, square=True)
+    assert bitwise_equal(a.cpu(), F.reduce_sum_fixed(g.cpu(), square=True))
+    assert abs(a.item() - g.double().pow(2).sum().item()) < 1e-1
+
+
+def test_ppo_loss_kernel_matches_torch():
+    from skyrl_isoexec_b200.train import algorithms as alg
+
+    torch.manual_seed(10)
+    cfg = alg.AlgorithmConfig()
+    lp = (torch.randn(6, 40) * 0.3 - 2).requires_grad_()
+    old = lp.detach() + torch.randn(6, 40) * 0.2
+    adv, mask = torch.randn(6, 40), (torch.rand(6, 40) > 0.2).float()
+    for name in ("regular", "dual_clip"):
+        fn = alg.get_policy_loss(name)
+        l_cpu, m_cpu = fn(lp, old, adv, cfg, loss_mask=mask)
+        (g_cpu,) = torch.autograd.grad(l_cpu, lp)
+        lpg = lp.detach().to(DEV).requires_grad_()
+        l_gpu, m_gpu = fn(lpg, old.to(DEV), adv.to(DEV), cfg, loss_mask=mask.to(DEV))
+        (g_gpu,) = torch.autograd.grad(l_gpu, lpg)
+        assert abs(l_cpu.item() - l_gpu.item()) < 1e-3 * max(1.0, abs(l_cpu.item()))
+        assert (g_cpu - g_gpu.cpu()).abs().max() < 1e-4
+        assert abs(float(m_cpu["clip_ratio"]) - float(m_gpu["clip_ratio"])) < 1e-6
+
+
+def test_engine_and_trainer_logprobs_bitwise_on_gpu_and_step():
+    """The flagship claim on the GPU: rollout logprobs == trainer scoring logprobs, bit for bit,
+    with chunked prefill and a batch mix that changes every step; then one optimizer step and again."""
+    from skyrl_isoexec_b200.engine.llm_engine import EngineConfig, LLMEngine
+    from skyrl_isoexec_b200.engine.sampler import SamplingParams
+    from skyrl_isoexec_b200.models.config import get_config
+    from skyrl_isoexec_b200.models.decoder import DecoderLM
+    from skyrl_isoexec_b200.train.batch import TrainingInputBatch, build_sequences
+    from skyrl_isoexec_b200.train.policy_worker import PolicyWorker, WorkerConfig
+
+    cfg = get_config("tiny-qwen3-bf16")
+    model = DecoderLM(cfg, device=DEV, seed=0)
+    eng = LLMEngine(model, EngineConfig(max_num_seqs=16, num_kv_pages=64, max_num_batched_tokens=96))
+    worker = PolicyWorker(model, WorkerConfig(max_tokens_per_microbatch=700))
+    worker.cfg.optimizer.lr = 1e-3
+    g = torch.Generator().manual_seed(0)
+    for _round in range(2):
+        prompts = [torch.randint(0, cfg.vocab_size, (int(n),), generator=g).tolist() for n in torch.randint(20, 200, (10,), generator=g)]
+        outs = eng.generate(prompts, SamplingParams(max_generate_length=40, ignore_eos=True))
+        seq, att, rmask = build_sequences([o.prompt_ids for o in outs], [o.response_ids for o in outs])
+        batch = TrainingInputBatch({"sequences": seq, "attention_mask": att, "response_mask": rmask, "loss_mask": rmask.clone(),
+                                    "advantages": torch.randn_like(rmask) / rmask.sum()})
+        lp = worker.forward(batch)
+        ro = torch.zeros_like(lp)
+        for i, o in enumerate(outs):
+            ro[i, :len(o.response_logprobs)] = torch.tensor(o.response_logprobs)
+        assert count_bit_mismatches((lp * rmask).contiguous(), (ro * rmask).contiguous()) == 0
+        batch["action_log_probs"] = lp
+        worker.forward_backward(batch)
+        assert worker.optim_step() > 0
