@@ -58,6 +58,10 @@ class Sequence:
     def length(self) -> int:
         return len(self.prompt_ids) + len(self.output_ids)
 
+    @property
+    def last_token(self) -> int:
+        return self.output_ids[-1] if self.output_ids else self.prompt_ids[-1]
+
 
 @dataclass
 class RequestOutput:
@@ -159,6 +163,11 @@ class LLMEngine:
         self.asleep = False
         self.stats = {"steps": 0, "tokens": 0, "prefill_tokens": 0, "decode_tokens": 0, "preemptions": 0,
                       "h2d_bytes": 0, "d2h_bytes": 0}
+        self._graphs: dict = {}
+        if self.device.type == "cuda":
+            from ..ops import _native
+
+            _native.lib().ix_init()   # status word allocated before any stream capture
         self.gdn_state = None
         if self.mcfg.has_gdn:
             from .gdn_state import GDNStatePool
@@ -188,6 +197,7 @@ class LLMEngine:
     def sleep(self, tags: list[str] | None = None) -> None:
         """Release the KV pools (and recurrent state). Weights stay resident."""
         assert not self.scheduler.has_work(), "sleep with requests in flight"
+        self._graphs.clear()      # graphs hold the pool addresses; they are re-captured after wake-up
         self.cache.sleep()
         if self.gdn_state is not None:
             self.gdn_state.invalidate("sleep_wake")
@@ -225,13 +235,21 @@ class LLMEngine:
         decode, prefill = self.scheduler.schedule()
         if not decode and not prefill:
             return []
+        if not prefill and self._graphs_enabled():
+            logits = self._decode_with_graph(decode)
+            for s in decode:
+                s.num_computed += 1
+            self.stats["steps"] += 1
+            self.stats["tokens"] += len(decode)
+            self.stats["decode_tokens"] += len(decode)
+            return self._sample_and_finish(logits, decode)
         G = self.model.hq // self.model.hkv
         tq = PAGE // G
         ids, pos, slots, items, bt_rows, sample_rows, sample_seqs = [], [], [], [], [], [], []
         row = 0
         for s in decode:
             p = s.length - 1
-            ids.append(s.tokens[-1])
+            ids.append(s.last_token)
             pos.append(p)
             slots.append(s.pages[p // PAGE] * PAGE + p % PAGE)
             items.append((row, 1, p, p + 1, len(bt_rows), 0, 0, 0))
@@ -275,31 +293,63 @@ class LLMEngine:
         self.stats["tokens"] += row
         self.stats["decode_tokens"] += len(decode)
         self.stats["prefill_tokens"] += row - len(decode)
-        finished: list[Sequence] = []
-        if sample_rows:
-            rows = self._h2d(torch.tensor(sample_rows, dtype=torch.int64))
-            logits = self.model.logits(hidden.index_select(0, rows))
-            if self.model.ps.tp > 1:
-                from ..parallel.tp import column_parallel_gather
+        if not sample_rows:
+            return []
+        rows = self._h2d(torch.tensor(sample_rows, dtype=torch.int64))
+        logits = self.model.logits(hidden.index_select(0, rows))
+        return self._sample_and_finish(logits, sample_seqs)
 
-                logits = column_parallel_gather(logits, self.model.ps)
-            tokens, lps = self.sampler(logits, [s.params for s in sample_seqs])
-            self.stats["d2h_bytes"] += tokens.numel() * 8 + lps.numel() * 4
-            tokens, lps = tokens.tolist(), lps.tolist()
-            for s, tok, lp in zip(sample_seqs, tokens, lps):
-                s.output_ids.append(tok)
-                s.logprobs.append(lp)
-                eos = self.cfg.eos_token_id
-                if (not s.params.ignore_eos and eos is not None and tok == eos) or tok in s.params.stop_token_ids:
-                    s.finished, s.stop_reason = True, "stop"
-                elif len(s.output_ids) >= s.params.max_generate_length or s.length >= self.max_len:
-                    s.finished, s.stop_reason = True, "length"
-                if s.finished:
-                    if self.gdn_state is not None:
-                        self.gdn_state.release(s.seq_id)
-                    self.scheduler.finish(s)
-                    finished.append(s)
+    def _sample_and_finish(self, logits: torch.Tensor, sample_seqs: list[Sequence]) -> list[Sequence]:
+        if self.model.ps.tp > 1:
+            from ..parallel.tp import column_parallel_gather
+
+            logits = column_parallel_gather(logits, self.model.ps)
+        tokens, lps = self.sampler(logits, [s.params for s in sample_seqs])
+        self.stats["d2h_bytes"] += tokens.numel() * 8 + lps.numel() * 4
+        tokens, lps = tokens.tolist(), lps.tolist()
+        finished: list[Sequence] = []
+        eos = self.cfg.eos_token_id
+        for s, tok, lp in zip(sample_seqs, tokens, lps):
+            s.output_ids.append(tok)
+            s.logprobs.append(lp)
+            if (not s.params.ignore_eos and eos is not None and tok == eos) or tok in s.params.stop_token_ids:
+                s.finished, s.stop_reason = True, "stop"
+            elif len(s.output_ids) >= s.params.max_generate_length or s.length >= self.max_len:
+                s.finished, s.stop_reason = True, "length"
+            if s.finished:
+                if self.gdn_state is not None:
+                    self.gdn_state.release(s.seq_id)
+                self.scheduler.finish(s)
+                finished.append(s)
         return finished
+
+    # ------------------------------------------------------------------ CUDA-graph decode
+    def _graphs_enabled(self) -> bool:
+        return (self.cfg.use_cuda_graph and self.device.type == "cuda" and not self.mcfg.has_moe
+                and not self.mcfg.has_gdn and self.model.ps.tp == 1)
+
+    def _decode_with_graph(self, decode: list[Sequence]) -> torch.Tensor:
+        from .cuda_graph import DecodeGraph
+
+        B = len(decode)
+        W = (self.max_len + PAGE - 1) // PAGE
+        g = self._graphs.get(B)
+        if g is None:
+            g = DecodeGraph(self, B, W)
+            self._graphs[B] = g
+        ids, pos, slots, items, bt_rows = [], [], [], [], []
+        for i, s in enumerate(decode):
+            p = s.length - 1
+            ids.append(s.last_token)
+            pos.append(p)
+            slots.append(s.pages[p // PAGE] * PAGE + p % PAGE)
+            items.append((i, 1, p, p + 1, i, 0, 0, 0))
+            bt_rows.append(s.pages)
+        g.fill(ids, pos, slots, items, bt_rows)
+        if g.graph is None:
+            g.dev.copy_(g.host)
+            g.capture()
+        return g.run()
 
     def generate(self, prompts: list[list[int]], params: SamplingParams | list[SamplingParams]) -> list[RequestOutput]:
         """Blocking batch generation; outputs are in prompt order."""

@@ -20,6 +20,7 @@ from dataclasses import dataclass
 import torch
 import torch.nn as nn
 
+from ..debug import trace as _trace
 from ..ops import functional as F
 from ..ops import gdn as gdn_ops
 from ..ops import moe as moe_ops
@@ -272,9 +273,13 @@ class DecoderLM(nn.Module):
                 x, res = _ckpt(self, i, x, res, fc, kv_idx)
             else:
                 x, res = self.layer(i, x, res, fc, kv_idx)
+            if _trace.active() is not None:   # region door: residual-stream contribution of layer i
+                _trace.record(f"layer{i}.out", x)
         if not self.ps.is_last_pp:
             return x, res
         y, _ = _norm(x, self.p("final_norm.weight"), self.cfg, res)
+        if _trace.active() is not None:
+            _trace.record("final_norm", y)
         return y
 
     def logits(self, hidden: torch.Tensor, out_f32: bool = False) -> torch.Tensor:
