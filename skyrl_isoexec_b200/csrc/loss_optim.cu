@@ -275,3 +275,70 @@ IX_API int ix_accum_bf16_to_f32(void* dst, const void* src, long long n, int acc
   IX_CUDA(cudaGetLastError());
   return 0;
 }
+
+// ------------------------------------------------------------------ allocation-free reduction
+// See ix_noalloc.h for who needs this and what the limits are.
+#include "ix_noalloc.h"
+
+namespace {
+
+// Partial sums of stage 1 live here instead of in caller-provided memory. One copy of this
+// array exists on every GPU whose context loads the library, from load until process exit.
+static __device__ __align__(256) float g_noalloc_partials[IX_NOALLOC_MAX_PARTIALS];
+
+// Device address of the array above, per device ordinal. In host code the symbol's name is
+// only a handle for the runtime; the address a kernel can dereference comes from
+// cudaGetSymbolAddress, taken with that device current.
+float* g_noalloc_ptr[64] = {nullptr};
+
+int noalloc_scratch(int dev, float** out) {
+  if (dev < 0 || dev >= 64) return ixh::fail(ixh::IX_EARG, "reduce_sum_noalloc: device ordinal %d out of range", dev);
+  if (g_noalloc_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    IX_CUDA(cudaGetSymbolAddress(&p, g_noalloc_partials));
+    g_noalloc_ptr[dev] = static_cast<float*>(p);
+  }
+  *out = g_noalloc_ptr[dev];
+  return 0;
+}
+
+}  // namespace
+
+IX_API long long ix_reduce_sum_noalloc_max_elems() {
+  return static_cast<long long>(IX_NOALLOC_MAX_PARTIALS) * kRedChunk;
+}
+
+IX_API int ix_reduce_sum_noalloc(const void* in, long long n, int dtype, int square, void* out, int accumulate,
+                                 void* stream) {
+  if (n < 0) return ixh::fail(ixh::IX_EARG, "reduce_sum_noalloc: negative length %lld", n);
+  if (n > ix_reduce_sum_noalloc_max_elems())
+    return ixh::fail(ixh::IX_ESIZE,
+                     "reduce_sum_noalloc: %lld elements exceed the built-in scratch (max %lld); use ix_reduce_sum with "
+                     "caller-provided scratch for larger inputs",
+                     n, ix_reduce_sum_noalloc_max_elems());
+  if (dtype != 0 && dtype != 1) return ixh::fail(ixh::IX_EARG, "reduce_sum_noalloc: dtype must be 0 (bf16) or 1 (fp32)");
+  int dev = 0;
+  IX_CUDA(cudaGetDevice(&dev));
+  float* part = nullptr;
+  int rc = noalloc_scratch(dev, &part);
+  if (rc) return rc;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (n == 0) {
+    if (!accumulate) IX_CUDA(cudaMemsetAsync(out, 0, sizeof(float), s));
+    return 0;
+  }
+  // Nothing in the scratch has to start at zero: stage 1 overwrites partials [0, np) and
+  // stage 2 reads exactly those, so whatever an earlier call left behind is never read.
+  const long long np = (n + kRedChunk - 1) / kRedChunk;
+  const int grid = static_cast<int>(np < 148 * 8 ? np : 148 * 8);
+  if (dtype == 0) {
+    if (square) reduce_stage1_kernel<__nv_bfloat16, true><<<grid, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(in), n, part);
+    else reduce_stage1_kernel<__nv_bfloat16, false><<<grid, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(in), n, part);
+  } else {
+    if (square) reduce_stage1_kernel<float, true><<<grid, 256, 0, s>>>(static_cast<const float*>(in), n, part);
+    else reduce_stage1_kernel<float, false><<<grid, 256, 0, s>>>(static_cast<const float*>(in), n, part);
+  }
+  reduce_stage2_kernel<<<1, 256, 0, s>>>(part, np, static_cast<float*>(out), accumulate);
+  IX_CUDA(cudaGetLastError());
+  return 0;
+}
