@@ -1,0 +1,60 @@
+"""Small, self-terminating kernel workloads for ncu captures (one kernel family per mode).
+
+    python profiles/run_kernels.py attn_decode | attn_prefill | gemm_large | gemm_decode | logprob | rmsnorm
+
+Each mode allocates well under 1 GB, launches the kernel a handful of times and exits.
+"""
+import math
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+import torch  # noqa: E402
+
+from skyrl_isoexec_b200.ops import _native, functional as F  # noqa: E402
+
+mode = sys.argv[1] if len(sys.argv) > 1 else "attn_decode"
+dev = "cuda"
+_native.lib().ix_init()
+torch.manual_seed(0)
+if mode in ("attn_decode", "attn_prefill"):
+    Hq, Hkv, D = 32, 8, 128
+    if mode == "attn_decode":
+        B, kv_len = 64, 1536
+        npg = (kv_len + 127) // 128
+        kc = torch.randn(B * npg * 128, Hkv, D, device=dev).bfloat16()
+        vc = torch.randn_like(kc)
+        q = torch.randn(B, Hq, D, device=dev).bfloat16()
+        bt = torch.arange(B * npg, dtype=torch.int32, device=dev).view(B, npg)
+        items = torch.tensor([[i, 1, kv_len - 1, kv_len, i, 0, 0, 0] for i in range(B)], dtype=torch.int32, device=dev)
+        meta = F.AttnMeta(items, bt)
+    else:
+        lens = [2560, 2560, 2560, 512]
+        T = sum(lens)
+        q = torch.randn(T, Hq, D, device=dev).bfloat16()
+        kc = torch.randn(T, Hkv, D, device=dev).bfloat16()
+        vc = torch.randn_like(kc)
+        meta = F.AttnMeta.packed(lens, Hq, Hkv, dev)
+    for _ in range(4):
+        F.attention_fwd(q, kc, vc, meta, 1 / math.sqrt(D))
+elif mode in ("gemm_large", "gemm_decode"):
+    M, N, K = (8192, 4096, 4096) if mode == "gemm_large" else (64, 24576, 4096)
+    x = torch.randn(M, K, device=dev).bfloat16()
+    w = (torch.randn(N, K, device=dev) * 0.02).bfloat16()
+    for _ in range(4):
+        F.gemm_nt(x, w)
+elif mode == "logprob":
+    V = 151936
+    lg = torch.randn(1024, V, device=dev).bfloat16()
+    tg = torch.randint(0, V, (1024,), device=dev)
+    for _ in range(4):
+        F.logprob_fused_fwd(lg, tg, 8)
+elif mode == "rmsnorm":
+    x = torch.randn(16384, 4096, device=dev).bfloat16()
+    r = torch.randn_like(x)
+    w = torch.ones(4096, device=dev).bfloat16()
+    for _ in range(4):
+        F.rmsnorm_fwd(x, w, 1e-6, False, r)
+torch.cuda.synchronize()
+assert _native.read_status() == 0
+print("ok", mode)

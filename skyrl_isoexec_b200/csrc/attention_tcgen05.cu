@@ -19,8 +19,10 @@
 //
 // Roles (192 threads): warp 0 TMA producer, warp 1 tcgen05.mma issuer, warps 2..5 softmax
 // (thread = row). TMEM: two S buffers (128 cols each) + one O_blk buffer (D cols).
-// Pipeline: S_{j+1} = Q K_{j+1}^T is issued while the softmax of block j runs; O_blk = P V_j
-// is added into the fp32 register accumulator of the row by the softmax threads.
+// Pipeline: S_{j+1} = Q K_{j+1}^T is issued while the softmax of block j runs; O += P V_j
+// accumulates in TMEM. The exponent reference m of a row moves lazily (only when the running
+// maximum grew by more than 8 in log2 units), so the softmax threads rescale O in TMEM rarely
+// and otherwise only read the scores once, exponentiate and hand P to the tensor core.
 #include "bw_common.cuh"
 #include "host_util.h"
 
@@ -169,7 +171,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
             const uint64_t da = make_sw128_desc(sP + (k >> 2) * SM::kChunk + (k & 3) * 32, 16, 1024);
             // B = V (MN-major): 16 keys = 2 groups of 8 rows (SBO 1024 B); 64-wide d chunks LBO apart
             const uint64_t db = make_sw128_desc(sV + k * 2048, SM::kChunk, 1024);
-            umma_f16_ss(tmem_O, da, db, idesc_o, k != 0 ? 1u : 0u);
+            umma_f16_ss(tmem_O, da, db, idesc_o, (j | k) != 0 ? 1u : 0u);   // O accumulates over blocks in TMEM
           }
           umma_commit(smem_u32(&bars[7 + st]));  // V stage free
           umma_commit(smem_u32(&bars[12]));      // O_blk ready, P buffer free
@@ -184,10 +186,11 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       const bool row_valid = tok < q_valid;
       const int q_pos = it.q_pos0 + (row_valid ? tok : q_valid - 1);
       const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
+      // m is the exponent reference of the row. It follows the running maximum lazily: it only moves
+      // when the maximum has grown by more than 8 (log2 units) since it was last set, so O (which
+      // accumulates in TMEM) is rescaled rarely. p = exp2(t - m) is then at most 2^8; l and O are
+      // both relative to the same m, so O / l is exact softmax. The rule is per row.
       float m = -INFINITY, l = 0.f;
-      float o[D];
-#pragma unroll
-      for (int i = 0; i < D; ++i) o[i] = 0.f;
       uint8_t* sP = smem + SM::offP;
       bool ok = true;
       for (int j = 0; j < nb && ok; ++j) {
@@ -199,91 +202,115 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         int lim = q_pos - key0 + 1;               // keys [0, lim) of this block are visible
         const int lim2 = it.kv_len - key0;
         if (lim2 < lim) lim = lim2;
-        // pass 1: row max of the scaled scores
-        float mb = -INFINITY;
-#pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          uint32_t s[32];
-          tmem_ld_32x32(tS + c * 32, s);
-          tmem_ld_wait();
+        // the whole score row goes to registers once: four loads in flight, then the waits
+        uint32_t s0[32], s1[32], s2[32], s3[32];
+        tmem_ld_32x32(tS, s0);
+        tmem_ld_32x32(tS + 32, s1);
+        tmem_ld_32x32(tS + 64, s2);
+        tmem_ld_32x32(tS + 96, s3);
+        tmem_ld_wait_dep(s0);
+        tmem_ld_wait_dep(s1);
+        tmem_ld_wait_dep(s2);
+        tmem_ld_wait_dep(s3);
+        // Row maximum on the raw scores (scale > 0, so max(s)*scale == max(s*scale)); a block that is
+        // fully visible to every row of the warp skips the per-element mask test.
+        const bool full_blk = __all_sync(0xffffffffu, lim >= kBlkN);
+        float mraw = -INFINITY;
+        if (full_blk) {
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
-            const float t = __fmul_rn(__uint_as_float(s[i]), scale_log2);
-            if (c * 32 + i < lim) mb = fmaxf(mb, t);
+            mraw = fmaxf(mraw, fmaxf(fmaxf(__uint_as_float(s0[i]), __uint_as_float(s1[i])),
+                                     fmaxf(__uint_as_float(s2[i]), __uint_as_float(s3[i]))));
           }
+        } else {
+#define IX_MASK_MAX(S_, C_)                                                         \
+  _Pragma("unroll") for (int i = 0; i < 32; ++i) {                                  \
+    if ((C_) * 32 + i >= lim) S_[i] = 0xff800000u; /* -inf */                       \
+    mraw = fmaxf(mraw, __uint_as_float(S_[i]));                                     \
+  }
+          IX_MASK_MAX(s0, 0)
+          IX_MASK_MAX(s1, 1)
+          IX_MASK_MAX(s2, 2)
+          IX_MASK_MAX(s3, 3)
+#undef IX_MASK_MAX
         }
+        const float mb = __fmul_rn(mraw, scale_log2);
         const float m_new = fmaxf(m, mb);
-        const float alpha = (m == -INFINITY) ? 0.f : exp2f(__fsub_rn(m, m_new));
-        // previous block's P V is done: P buffer is free, O_blk holds block j-1
+        float alpha = 1.f;
+        if (__fsub_rn(m_new, m) > 8.0f) {         // also true for the first visible block (m = -inf)
+          alpha = (m == -INFINITY) ? 0.f : ex2_approx(__fsub_rn(m, m_new));
+          m = m_new;
+        }
+        const bool any_rescale = __any_sync(0xffffffffu, alpha != 1.f);
+        // P V of block j-1 must have finished: the P buffer is reused and O may be rescaled
         if (j > 0) {
           if (!mbar_wait(smem_u32(&bars[12]), (j - 1) & 1, abort_flag, status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
           tc_fence_after();
-#pragma unroll
-          for (int c = 0; c < D / 32; ++c) {
-            uint32_t v[32];
-            tmem_ld_32x32(tmem_O + lane_off + c * 32, v);
-            tmem_ld_wait();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) o[c * 32 + i] = __fadd_rn(o[c * 32 + i], __uint_as_float(v[i]));
-          }
-        }
-        if (alpha != 1.f) {
-#pragma unroll
-          for (int i = 0; i < D; ++i) o[i] = __fmul_rn(o[i], alpha);
-          l = __fmul_rn(l, alpha);
-        }
-        m = m_new;
-        // pass 2: p = exp2(t - m), row sum left to right, P -> smem (bf16, 128B swizzle)
+          if (any_rescale) {
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          uint32_t s[32];
-          tmem_ld_32x32(tS + c * 32, s);
-          tmem_ld_wait();
-          uint32_t pk[16];
+            for (int c = 0; c < D / 32; ++c) {
+              uint32_t v[32];
+              tmem_ld_32x32(tmem_O + lane_off + c * 32, v);
+              tmem_ld_wait_dep(v);
 #pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            float p0 = 0.f, p1 = 0.f;
-            if (c * 32 + i < lim) p0 = exp2f(__fsub_rn(__fmul_rn(__uint_as_float(s[i]), scale_log2), m));
-            if (c * 32 + i + 1 < lim) p1 = exp2f(__fsub_rn(__fmul_rn(__uint_as_float(s[i + 1]), scale_log2), m));
-            l = __fadd_rn(l, p0);
-            l = __fadd_rn(l, p1);
-            pk[i >> 1] = pack_bf2(p0, p1);
-          }
-          // columns c*32 .. c*32+31 -> atom (c>>1), 16-byte chunks ((c&1)*4 + q), q = 0..3
-          uint8_t* rowp = sP + (c >> 1) * SM::kChunk + r * 128;
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            const int chunk = ((c & 1) * 4 + q) ^ (r & 7);
-            *reinterpret_cast<uint4*>(rowp + chunk * 16) = make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
+              for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__fmul_rn(__uint_as_float(v[i]), alpha));
+              tmem_st_32x32(tmem_O + lane_off + c * 32, v);
+            }
+            tmem_st_wait();
           }
         }
+        if (alpha != 1.f) l = __fmul_rn(l, alpha);
+        // p = exp2(s*scale - m): one FMA and one ex2.approx per element (masked scores are -inf -> p = 0);
+        // the row sum adds the pair (p_i + p_{i+1}) left to right
+        const float neg_m = -m;
+#define IX_EXP_STORE(S_, C_)                                                                         \
+  {                                                                                                  \
+    uint32_t pk[16];                                                                                 \
+    _Pragma("unroll") for (int i = 0; i < 32; i += 2) {                                              \
+      const float p0 = ex2_approx(__fmaf_rn(__uint_as_float(S_[i]), scale_log2, neg_m));             \
+      const float p1 = ex2_approx(__fmaf_rn(__uint_as_float(S_[i + 1]), scale_log2, neg_m));         \
+      l = __fadd_rn(l, __fadd_rn(p0, p1));                                                           \
+      pk[i >> 1] = pack_bf2(p0, p1);                                                                 \
+    }                                                                                                \
+    uint8_t* rowp = sP + ((C_) >> 1) * SM::kChunk + r * 128;                                         \
+    _Pragma("unroll") for (int q = 0; q < 4; ++q) {                                                  \
+      const int chunk = (((C_) & 1) * 4 + q) ^ (r & 7);                                              \
+      *reinterpret_cast<uint4*>(rowp + chunk * 16) =                                                 \
+          make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);                        \
+    }                                                                                                \
+  }
+        IX_EXP_STORE(s0, 0)
+        IX_EXP_STORE(s1, 1)
+        IX_EXP_STORE(s2, 2)
+        IX_EXP_STORE(s3, 3)
+#undef IX_EXP_STORE
         tc_fence_before();
         fence_proxy_async();  // make the generic-proxy writes of P visible to the tensor core
         mbar_arrive(smem_u32(&bars[11]));
       }
       if (ok && mbar_wait(smem_u32(&bars[12]), (nb - 1) & 1, abort_flag, status, ST_TIMEOUT_TMEM_FULL)) {
         tc_fence_after();
-#pragma unroll
+        const float inv = __fdiv_rn(1.0f, l);
+        const size_t orow = static_cast<size_t>(it.q_start + (row_valid ? tok : 0)) * Hq + hq;
+#pragma unroll 1
         for (int c = 0; c < D / 32; ++c) {
           uint32_t v[32];
           tmem_ld_32x32(tmem_O + lane_off + c * 32, v);
-          tmem_ld_wait();
+          tmem_ld_wait_dep(v);
+          if (row_valid) {
+            uint4* dst = reinterpret_cast<uint4*>(out + orow * D + c * 32);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) o[c * 32 + i] = __fadd_rn(o[c * 32 + i], __uint_as_float(v[i]));
+            for (int i = 0; i < 4; ++i) {
+              uint4 w;
+              w.x = pack_bf2(__fmul_rn(__uint_as_float(v[8 * i + 0]), inv), __fmul_rn(__uint_as_float(v[8 * i + 1]), inv));
+              w.y = pack_bf2(__fmul_rn(__uint_as_float(v[8 * i + 2]), inv), __fmul_rn(__uint_as_float(v[8 * i + 3]), inv));
+              w.z = pack_bf2(__fmul_rn(__uint_as_float(v[8 * i + 4]), inv), __fmul_rn(__uint_as_float(v[8 * i + 5]), inv));
+              w.w = pack_bf2(__fmul_rn(__uint_as_float(v[8 * i + 6]), inv), __fmul_rn(__uint_as_float(v[8 * i + 7]), inv));
+              dst[i] = w;
+            }
+          }
         }
         if (row_valid) {
-          const float inv = __fdiv_rn(1.0f, l);
-          const size_t orow = static_cast<size_t>(it.q_start + tok) * Hq + hq;
-          uint4* dst = reinterpret_cast<uint4*>(out + orow * D);
-#pragma unroll
-          for (int i = 0; i < D / 8; ++i) {
-            uint4 w;
-            w.x = pack_bf2(__fmul_rn(o[8 * i + 0], inv), __fmul_rn(o[8 * i + 1], inv));
-            w.y = pack_bf2(__fmul_rn(o[8 * i + 2], inv), __fmul_rn(o[8 * i + 3], inv));
-            w.z = pack_bf2(__fmul_rn(o[8 * i + 4], inv), __fmul_rn(o[8 * i + 5], inv));
-            w.w = pack_bf2(__fmul_rn(o[8 * i + 6], inv), __fmul_rn(o[8 * i + 7], inv));
-            dst[i] = w;
-          }
           if (lse_out) lse_out[orow] = (m + log2f(l)) * 0.6931471805599453f;
         }
       }

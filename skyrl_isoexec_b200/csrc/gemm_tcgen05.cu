@@ -30,25 +30,35 @@ constexpr int BM = 128;
 constexpr int BK = 64;
 constexpr int kThreads = 192;
 
+constexpr int kMaxStages = 16;
+constexpr int kPipeBytes = 200 * 1024;   // shared memory given to the TMA pipeline
+
+// The A stage holds only the rows that exist: a_rows = min(128, M rounded up to 8). The MMA still
+// reads 128 rows (whatever follows in shared memory, never stored), so a decode-sized M spends its
+// shared memory on more weight stages in flight instead of on zero padding.
 template <int BN>
 struct GemmCfg {
-  static constexpr int kStageBytesA = BM * BK * 2;
   static constexpr int kStageBytesB = BN * BK * 2;
-  static constexpr int kStageBytes = kStageBytesA + kStageBytesB;
-  static constexpr int kStages = (BN >= 256) ? 4 : (BN >= 128 ? 6 : 8);
   static constexpr int kTmemCols = (2 * BN < 32) ? 32 : 2 * BN;
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int kSmemBytes = kPipeBytes + BM * BK * 2 /*tail the last stage's MMA may read*/ + 1024 /*align*/ + 512 /*barriers*/;
+  static int stage_bytes(int a_rows) { return a_rows * BK * 2 + kStageBytesB; }
+  static int stages(int a_rows) {
+    int s = kPipeBytes / stage_bytes(a_rows);
+    return s > kMaxStages ? kMaxStages : s;
+  }
 };
 
 template <int BN, bool OUT_F32>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                    void* __restrict__ Cout, int M, int N, int K, int ldc, int* __restrict__ status) {
+                    void* __restrict__ Cout, int M, int N, int K, int ldc, int a_rows, int S,
+                    int* __restrict__ status) {
   using Cfg = GemmCfg<BN>;
-  constexpr int S = Cfg::kStages;
+  const int stage_bytes_a = a_rows * BK * 2;
+  const int stage_bytes = stage_bytes_a + Cfg::kStageBytesB;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S * Cfg::kStageBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kPipeBytes + BM * BK * 2);
   // bars: [0,S) full, [S,2S) empty, [2S,2S+2) tmem_full, [2S+2,2S+4) tmem_empty
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * S + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
@@ -97,10 +107,10 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             break;
           }
           const uint32_t full = smem_u32(&bars[stage]);
-          mbar_arrive_expect_tx(full, Cfg::kStageBytes);
-          const uint32_t sa = smem_u32(smem + stage * Cfg::kStageBytes);
+          mbar_arrive_expect_tx(full, stage_bytes);
+          const uint32_t sa = smem_u32(smem + stage * stage_bytes);
           tma_load_2d(sa, &tmA, full, kb * BK, m_blk * BM);
-          tma_load_2d(sa + Cfg::kStageBytesA, &tmB, full, kb * BK, n_blk * BN);
+          tma_load_2d(sa + stage_bytes_a, &tmB, full, kb * BK, n_blk * BN);
           if (++stage == S) {
             stage = 0;
             phase ^= 1;
@@ -131,9 +141,9 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             break;
           }
           tc_fence_after();
-          const uint32_t sa = smem_u32(smem + stage * Cfg::kStageBytes);
+          const uint32_t sa = smem_u32(smem + stage * stage_bytes);
           const uint64_t da = make_sw128_desc(sa, 16, 1024);
-          const uint64_t db = make_sw128_desc(sa + Cfg::kStageBytesA, 16, 1024);
+          const uint64_t db = make_sw128_desc(sa + stage_bytes_a, 16, 1024);
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k) {
             // +32 bytes per K=16 step inside the 128-byte swizzle atom (address field is >>4)
@@ -236,7 +246,10 @@ int launch_gemm(const void* A, const void* B, void* C, int M, int N, int K, int 
                 int max_ctas, cudaStream_t stream, int dev) {
   using Cfg = GemmCfg<BN>;
   CUtensorMap tmA, tmB;
-  int rc = ixh::make_tmap_bf16_2d(&tmA, A, M, K, lda, BM);
+  int a_rows = (M + 7) & ~7;
+  if (a_rows > BM) a_rows = BM;
+  const int S = Cfg::stages(a_rows);
+  int rc = ixh::make_tmap_bf16_2d(&tmA, A, M, K, lda, a_rows);
   if (rc) return rc;
   rc = ixh::make_tmap_bf16_2d(&tmB, B, N, K, ldb, BN);
   if (rc) return rc;
@@ -250,7 +263,7 @@ int launch_gemm(const void* A, const void* B, void* C, int M, int N, int K, int 
   int grid = num_sms(dev);
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
   if (tiles < grid) grid = tiles;
-  kern<<<grid, kThreads, Cfg::kSmemBytes, stream>>>(tmA, tmB, C, M, N, K, ldc, ixh::status_word(dev));
+  kern<<<grid, kThreads, Cfg::kSmemBytes, stream>>>(tmA, tmB, C, M, N, K, ldc, a_rows, S, ixh::status_word(dev));
   IX_CUDA(cudaGetLastError());
   return ixh::IX_OK;
 }
@@ -273,7 +286,7 @@ IX_API int ix_gemm_bf16_nt(const void* A, const void* B, void* C, int M, int N, 
     const int sms = num_sms(dev);
     const int tm = (M + BM - 1) / BM;
     bn = 256;
-    while (bn > 32 && tm * ((N + bn - 1) / bn) < sms) bn >>= 1;
+    while (bn > 32 && tm * ((N + bn - 1) / bn) * 5 < sms * 3) bn >>= 1;   // widest tile that still gives >= 0.6 CTAs per SM
   }
 #define IX_GEMM_CASE(BN_)                                                                                     \
   case BN_:                                                                                                   \

@@ -41,18 +41,33 @@ rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restr
   const BF8* rr = HAS_RES ? reinterpret_cast<const BF8*>(res + static_cast<size_t>(row) * N) : nullptr;
   BF8* ro = HAS_RES ? reinterpret_cast<BF8*>(res_out + static_cast<size_t>(row) * N) : nullptr;
   float ss = 0.f;
-  for (int v = lane; v < nvec; v += 32) {
-    BF8 a = xr[v];
-    if (HAS_RES) {
-      BF8 b = rr[v];
+  // four vectors per lane are loaded before any is consumed (memory-level parallelism); the sum
+  // still visits the lane's vectors in ascending order
+  for (int v0 = lane; v0 < nvec; v0 += 128) {
+    BF8 a[4], b[4];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) a.v[j] = f2bf(__fadd_rn(bf2f(a.v[j]), bf2f(b.v[j])));
-      ro[v] = a;
+    for (int u = 0; u < 4; ++u) {
+      const int v = v0 + 32 * u;
+      if (v < nvec) {
+        a[u] = xr[v];
+        if (HAS_RES) b[u] = rr[v];
+      }
     }
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const float f = bf2f(a.v[j]);
-      ss = __fadd_rn(ss, __fmul_rn(f, f));
+    for (int u = 0; u < 4; ++u) {
+      const int v = v0 + 32 * u;
+      if (v < nvec) {
+        if (HAS_RES) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) a[u].v[j] = f2bf(__fadd_rn(bf2f(a[u].v[j]), bf2f(b[u].v[j])));
+          ro[v] = a[u];
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float f = bf2f(a[u].v[j]);
+          ss = __fadd_rn(ss, __fmul_rn(f, f));
+        }
+      }
     }
   }
   ss = warp_sum_butterfly(ss);
@@ -61,18 +76,31 @@ rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restr
   const BF8* hr = HAS_RES ? reinterpret_cast<const BF8*>(res_out + static_cast<size_t>(row) * N) : xr;
   const BF8* wr = reinterpret_cast<const BF8*>(w);
   BF8* yr = reinterpret_cast<BF8*>(y + static_cast<size_t>(row) * ldy);
-  for (int v = lane; v < nvec; v += 32) {
-    BF8 a = hr[v];  // same lane wrote it above (HAS_RES), so no cross-thread hazard
-    BF8 g = wr[v];
-    BF8 o;
+  for (int v0 = lane; v0 < nvec; v0 += 128) {
+    BF8 a[4], g[4];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const float n = round_bf(__fmul_rn(bf2f(a.v[j]), rstd));
-      float gg = bf2f(g.v[j]);
-      if (ZERO_CENTERED) gg = round_bf(__fadd_rn(1.0f, gg));
-      o.v[j] = f2bf(__fmul_rn(n, gg));
+    for (int u = 0; u < 4; ++u) {
+      const int v = v0 + 32 * u;
+      if (v < nvec) {
+        a[u] = hr[v];  // same lane wrote it above (HAS_RES), so no cross-thread hazard
+        g[u] = wr[v];
+      }
     }
-    yr[v] = o;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int v = v0 + 32 * u;
+      if (v < nvec) {
+        BF8 o;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float n = round_bf(__fmul_rn(bf2f(a[u].v[j]), rstd));
+          float gg = bf2f(g[u].v[j]);
+          if (ZERO_CENTERED) gg = round_bf(__fadd_rn(1.0f, gg));
+          o.v[j] = f2bf(__fmul_rn(n, gg));
+        }
+        yr[v] = o;
+      }
+    }
   }
 }
 

@@ -420,24 +420,24 @@ void attention_fwd(const T* q, const T* k, const T* v, const WorkItem* items, co
               mb = fmaxf(mb, s[c]);
             }
             const float m_new = fmaxf(m, mb);
-            const float alpha = (m == -INFINITY) ? 0.f : exp2f(m - m_new);
-            if (j > 0)
-              for (int d = 0; d < D; ++d) o[d] = o[d] + ob[d];
+            // lazy exponent reference: m only moves when the maximum grew by more than 8 (log2 units)
+            float alpha = 1.f;
+            if (m_new - m > 8.0f) {
+              alpha = (m == -INFINITY) ? 0.f : exp2f(m - m_new);
+              m = m_new;
+            }
             if (alpha != 1.f) {
               for (int d = 0; d < D; ++d) o[d] = o[d] * alpha;
               l = l * alpha;
             }
-            m = m_new;
-            std::fill(ob.begin(), ob.end(), 0.f);
             for (int c = 0; c < 128 && c < lim; ++c) {
               const float pv = exp2f(s[c] - m);
               l = l + pv;
               const float pr = rnd<T>(pv);
               const T* vr = v + ((row0 + c) * Hkv + kvh) * D;
-              for (int d = 0; d < D; ++d) ob[d] = ob[d] + pr * ld(vr, d);
+              for (int d = 0; d < D; ++d) o[d] = o[d] + pr * ld(vr, d);
             }
           }
-          for (int d = 0; d < D; ++d) o[d] = o[d] + ob[d];
           const float inv = 1.0f / l;
           const long long orow = static_cast<long long>(it.q_start + tok) * Hq + hq;
           for (int d = 0; d < D; ++d) st(out, orow * D + d, o[d] * inv);
@@ -589,4 +589,209 @@ IXC_API float ixc_reduce_sum(const void* in, long long n, int dtype, int square)
                                 : reduce_sum<uint16_t, false>(static_cast<const uint16_t*>(in), n);
   return square ? reduce_sum<float, true>(static_cast<const float*>(in), n)
                 : reduce_sum<float, false>(static_cast<const float*>(in), n);
+}
+
+// ------------------------------------------------------------------ MoE router (same order as csrc/moe.cu)
+IXC_API void ixc_router_topk(const void* logits_, long long ldl, const void* bias_, int Tn, int E, int K, int sigmoid_bias,
+                             int norm_topk, void* idx_out_, void* w_out_, void* probs_out_) {
+  const float* logits = static_cast<const float*>(logits_);
+  const float* bias = static_cast<const float*>(bias_);
+  int* idx_out = static_cast<int*>(idx_out_);
+  float* w_out = static_cast<float*>(w_out_);
+  float* probs_out = static_cast<float*>(probs_out_);
+#pragma omp parallel for schedule(static)
+  for (int t = 0; t < Tn; ++t) {
+    const float* x = logits + t * ldl;
+    std::vector<float> score(E), gate(E);
+    if (!sigmoid_bias) {
+      float m = -INFINITY;
+      for (int e = 0; e < E; ++e) m = fmaxf(m, x[e]);
+      float lane[32];
+      for (int l = 0; l < 32; ++l) {
+        float part = 0.f;
+        for (int e = l; e < E; e += 32) {
+          gate[e] = expf(x[e] - m);
+          part = part + gate[e];
+        }
+        lane[l] = part;
+      }
+      const float S = butterfly32(lane);
+      for (int e = 0; e < E; ++e) {
+        gate[e] = gate[e] / S;
+        score[e] = gate[e];
+      }
+    } else {
+      for (int e = 0; e < E; ++e) {
+        gate[e] = 1.0f / (1.0f + expf(-x[e]));
+        score[e] = bias ? gate[e] + bias[e] : gate[e];
+      }
+    }
+    if (probs_out)
+      for (int e = 0; e < E; ++e) probs_out[static_cast<long long>(t) * E + e] = gate[e];
+    float wsum = 0.f;
+    for (int r = 0; r < K; ++r) {
+      int bi = -1;
+      float bv = -INFINITY;
+      for (int e = 0; e < E; ++e)
+        if (score[e] > bv) {
+          bv = score[e];
+          bi = e;
+        }
+      idx_out[static_cast<long long>(t) * K + r] = bi;
+      w_out[static_cast<long long>(t) * K + r] = gate[bi];
+      wsum = wsum + gate[bi];
+      score[bi] = -INFINITY;
+    }
+    if (norm_topk)
+      for (int r = 0; r < K; ++r) w_out[static_cast<long long>(t) * K + r] = w_out[static_cast<long long>(t) * K + r] / wsum;
+  }
+}
+
+// ------------------------------------------------------------------ GatedDeltaNet (same order as csrc/gdn.cu)
+namespace {
+struct ScanChunk {
+  int tok_start, n_tok, pos0, pad;
+  long long row_in, row_out;
+};
+
+template <typename T>
+void gdn_conv(const T* x, long long ldx, const T* w, const int* tok_back, const long long* state_row, const T* conv_state,
+              T* out, long long Tn, int C, int W) {
+#pragma omp parallel for schedule(static)
+  for (long long t = 0; t < Tn; ++t)
+    for (int c = 0; c < C; ++c) {
+      const int back = tok_back[t];
+      const long long srow = state_row ? state_row[t] : -1;
+      float acc = 0.f;
+      for (int j = 0; j < W; ++j) {
+        const int d = W - 1 - j;
+        float xv;
+        if (d <= back) xv = ld(x, (t - d) * ldx + c);
+        else if (srow >= 0) xv = ld(conv_state, (srow * C + c) * (W - 1) + (W - 1) - (d - back));
+        else xv = 0.f;
+        acc = fmaf(ld(w, static_cast<long long>(c) * W + j), xv, acc);
+      }
+      st(out, t * C + c, acc / (1.0f + expf(-acc)));
+    }
+}
+
+template <typename T>
+void gdn_conv_state(const T* x, long long ldx, const ScanChunk* chunks, T* conv_state, int n_chunks, int C, int W) {
+  for (int ch = 0; ch < n_chunks; ++ch) {
+    const ScanChunk sc = chunks[ch];
+    if (sc.row_out < 0) continue;
+    for (int c = 0; c < C; ++c) {
+      float nv[3];
+      for (int j = 0; j < W - 1; ++j) {
+        const int d = W - 1 - j;
+        if (d <= sc.n_tok) nv[j] = ld(x, static_cast<long long>(sc.tok_start + sc.n_tok - d) * ldx + c);
+        else if (sc.row_in >= 0) nv[j] = ld(conv_state, (sc.row_in * C + c) * (W - 1) + j + sc.n_tok);
+        else nv[j] = 0.f;
+      }
+      for (int j = 0; j < W - 1; ++j) st(conv_state, (sc.row_out * C + c) * (W - 1) + j, nv[j]);
+    }
+  }
+}
+
+template <typename T>
+void gdn_gate(const T* a, const T* b, long long ldab, const T* A_log, const T* dt_bias, float* g, float* beta, long long Tn, int H) {
+#pragma omp parallel for schedule(static)
+  for (long long t = 0; t < Tn; ++t)
+    for (int h = 0; h < H; ++h) {
+      const float x = ld(a, t * ldab + h) + ld(dt_bias, h);
+      const float sp = x > 20.f ? x : log1pf(expf(x));
+      g[t * H + h] = -expf(ld(A_log, h)) * sp;
+      beta[t * H + h] = 1.0f / (1.0f + expf(-ld(b, t * ldab + h)));
+    }
+}
+
+template <typename T>
+void gdn_l2norm(const T* in, long long ldin, T* out_q, T* out_k, long long Tn, int Hk, int D, float eps, float q_scale) {
+#pragma omp parallel for schedule(static)
+  for (long long wid = 0; wid < Tn * 2 * Hk; ++wid) {
+    const long long t = wid / (2 * Hk);
+    const int hh = static_cast<int>(wid % (2 * Hk));
+    const bool is_k = hh >= Hk;
+    const int h = is_k ? hh - Hk : hh;
+    const T* src = in + t * ldin + (is_k ? static_cast<long long>(Hk) * D : 0) + static_cast<long long>(h) * D;
+    float lane[32];
+    for (int l = 0; l < 32; ++l) {
+      float ss = 0.f;
+      for (int v = l; v < D / 8; v += 32)
+        for (int j = 0; j < 8; ++j) {
+          const float f = ld(src, v * 8 + j);
+          ss = ss + f * f;
+        }
+      lane[l] = ss;
+    }
+    const float rstd = 1.0f / sqrtf(butterfly32(lane) + eps);
+    T* dst = (is_k ? out_k : out_q) + (t * Hk + h) * D;
+    for (int i = 0; i < D; ++i) {
+      float n = rnd<T>(ld(src, i) * rstd);
+      if (!is_k) n = rnd<T>(n * q_scale);
+      st(dst, i, n);
+    }
+  }
+}
+
+template <typename T>
+void gdn_scan(const T* q, const T* k, const T* v, const float* g, const float* beta, const ScanChunk* chunks, float* state,
+              T* out, int n_chunks, int Hk, int Hv, int DK, int DV, int snapshot_every) {
+#pragma omp parallel for schedule(dynamic) collapse(2)
+  for (int ch = 0; ch < n_chunks; ++ch)
+    for (int hv = 0; hv < Hv; ++hv) {
+      const ScanChunk sc = chunks[ch];
+      const int hk = hv / (Hv / Hk);
+      std::vector<float> S(static_cast<size_t>(DV) * DK, 0.f);
+      if (sc.row_in >= 0) memcpy(S.data(), state + (sc.row_in * Hv + hv) * DV * DK, sizeof(float) * DV * DK);
+      for (int tt = 0; tt < sc.n_tok; ++tt) {
+        const long long t = sc.tok_start + tt;
+        const float decay = expf(g[t * Hv + hv]), bt = beta[t * Hv + hv];
+        const T* kr = k + (t * Hk + hk) * DK;
+        const T* qr = q + (t * Hk + hk) * DK;
+        for (int j = 0; j < DV; ++j) {
+          float* Sj = &S[static_cast<size_t>(j) * DK];
+          float kv = 0.f;
+          for (int i = 0; i < DK; ++i) {
+            Sj[i] = Sj[i] * decay;
+            kv = fmaf(Sj[i], ld(kr, i), kv);
+          }
+          const float d = (ld(v, (t * Hv + hv) * DV + j) - kv) * bt;
+          float o = 0.f;
+          for (int i = 0; i < DK; ++i) {
+            Sj[i] = fmaf(d, ld(kr, i), Sj[i]);
+            o = fmaf(Sj[i], ld(qr, i), o);
+          }
+          st(out, (t * Hv + hv) * DV + j, o);
+          if (snapshot_every > 0 && ((sc.pos0 + tt + 1) % snapshot_every) == 0)
+            for (int i = 0; i < DK; ++i) Sj[i] = round_bf(Sj[i]);
+        }
+      }
+      if (sc.row_out >= 0) memcpy(state + (sc.row_out * Hv + hv) * DV * DK, S.data(), sizeof(float) * DV * DK);
+    }
+}
+}  // namespace
+
+IXC_API void ixc_gdn_conv(const void* x, long long ldx, const void* w, const void* tok_back, const void* state_row,
+                          const void* conv_state, void* out, long long Tn, int C, int W, int dtype) {
+  DISPATCH(dtype, gdn_conv(static_cast<const T*>(x), ldx, static_cast<const T*>(w), static_cast<const int*>(tok_back),
+                           static_cast<const long long*>(state_row), static_cast<const T*>(conv_state), static_cast<T*>(out), Tn, C, W));
+}
+IXC_API void ixc_gdn_conv_state(const void* x, long long ldx, const void* chunks, void* conv_state, int n_chunks, int C, int W, int dtype) {
+  DISPATCH(dtype, gdn_conv_state(static_cast<const T*>(x), ldx, static_cast<const ScanChunk*>(chunks), static_cast<T*>(conv_state), n_chunks, C, W));
+}
+IXC_API void ixc_gdn_gate(const void* a, const void* b, long long ldab, const void* A_log, const void* dt_bias, void* g, void* beta,
+                          long long Tn, int H, int dtype) {
+  DISPATCH(dtype, gdn_gate(static_cast<const T*>(a), static_cast<const T*>(b), ldab, static_cast<const T*>(A_log),
+                           static_cast<const T*>(dt_bias), static_cast<float*>(g), static_cast<float*>(beta), Tn, H));
+}
+IXC_API void ixc_gdn_l2norm(const void* in, long long ldin, void* out_q, void* out_k, long long Tn, int Hk, int D, float eps,
+                            float q_scale, int dtype) {
+  DISPATCH(dtype, gdn_l2norm(static_cast<const T*>(in), ldin, static_cast<T*>(out_q), static_cast<T*>(out_k), Tn, Hk, D, eps, q_scale));
+}
+IXC_API void ixc_gdn_scan(const void* q, const void* k, const void* v, const void* g, const void* beta, const void* chunks,
+                          void* state, void* out, int n_chunks, int Hk, int Hv, int DK, int DV, int snapshot_every, int dtype) {
+  DISPATCH(dtype, gdn_scan(static_cast<const T*>(q), static_cast<const T*>(k), static_cast<const T*>(v), static_cast<const float*>(g),
+                           static_cast<const float*>(beta), static_cast<const ScanChunk*>(chunks), static_cast<float*>(state),
+                           static_cast<T*>(out), n_chunks, Hk, Hv, DK, DV, snapshot_every));
 }

@@ -79,6 +79,7 @@ class Scheduler:
         self.cache = cache
         self.waiting: deque[Sequence] = deque()
         self.running: list[Sequence] = []
+        self.preemptions = 0
 
     def add(self, seq: Sequence) -> None:
         self.waiting.append(seq)
@@ -109,14 +110,20 @@ class Scheduler:
         running = [s for s in self.running if s.num_computed == s.length - 1]
         still_prefilling = [s for s in self.running if s.num_computed < s.length - 1]
         for s in running:
-            while not self._ensure_pages(s, s.length):
-                victims = [v for v in self.running if v is not s and v not in decode]
-                if not victims:
+            while s in self.running and not self._ensure_pages(s, s.length):
+                # out of pages: preempt the most recently admitted sequence (possibly s itself);
+                # it is recomputed from its tokens when pages free up
+                victims = [v for v in self.running if v.pages]
+                if len(victims) <= 1 and victims == [s]:
                     raise RuntimeError("KV cache too small for a single sequence")
                 v = victims[-1]
                 self.running.remove(v)
                 if v in still_prefilling:
                     still_prefilling.remove(v)
+                if v in decode:
+                    decode.remove(v)
+                    budget += 1
+                self.preemptions += 1
                 self._preempt(v)
             if s in self.running:
                 decode.append(s)

@@ -25,6 +25,7 @@ _SIGS = {
     "ixc_logprob_rowmax": [_P, _L, _I, _I, _P, _I],
     "ixc_logprob_leafsum": [_P, _L, _I, _I, _I, _I, _I, _P, _P, _P, _I],
     "ixc_logprob_finalize": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I],
+    "ixc_router_topk": [_P, _L, _P, _I, _I, _I, _I, _I, _P, _P, _P],
     "ixc_attention_fwd": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I],
 }
 

@@ -45,6 +45,9 @@ _SIGS = {
     "ix_clip_coef": [_P, _F, _P, _P, _P],
     "ix_adamw": [_P, _P, _P, _P, _P, _L, _I, _F, _F, _F, _F, _F, _I, _P, _P],
     "ix_accum_bf16_to_f32": [_P, _P, _L, _I, _P],
+    "ix_router_topk": [_P, _L, _P, _I, _I, _I, _I, _I, _P, _P, _P, _P],
+    "ix_moe_combine": [_P, _P, _P, _P, _I, _I, _I, _I, _P],
+    "ix_scale_rows": [_P, _P, _L, _I, _P],
     "ix_attention_fwd": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _L, _I, _F, _P, _P],
 }
 _RESTYPE = {"ix_reduce_scratch_elems": C.c_longlong}

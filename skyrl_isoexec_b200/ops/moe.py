@@ -1,2 +1,198 @@
-def moe_block(y, model, i):
-    raise NotImplementedError("MoE block is provided by ops/moe.py")
+"""Mixture-of-experts block with batch-, EP- and order-invariant numerics.
+
+Recipe (the reference's deterministic MoE, ISO/ops/moe/moe_batch_invariant.py:276-321,744-887 and
+moe_batched_experts.py:152-298, restated without Megatron):
+  router   fp32 logits from the batch-invariant GEMM; per-token top-k with lower-index ties;
+           gate weights optionally renormalised over the k picks (csrc/moe.cu)
+  dispatch (token, slot) rows ordered by (expert, token, slot): a stable counting sort, integers only
+  experts  per expert row group: fc1 -> SwiGLU -> x gate weight (one round) -> fc2 with fp32 output,
+           each through the batch-invariant GEMM, so a row's value does not depend on its group size
+  combine  per token: fp32 sum of its k expert rows in ASCENDING EXPERT INDEX, one round, then the
+           shared expert (if any) is added
+With expert parallelism the rows travel to the expert's owner and back by all-to-all (bytes only);
+the sum order is a property of the token, not of where its experts live, so EP never changes bits.
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from . import _cpu, _native
+from . import functional as F
+
+
+# ------------------------------------------------------------------------------------ router
+def router_topk_fwd(logits: torch.Tensor, k: int, bias: torch.Tensor | None, sigmoid_bias: bool, norm_topk: bool,
+                    want_probs: bool = False):
+    """logits fp32 [T, E] -> (idx int32 [T, k], weights fp32 [T, k], probs [T, E] | None)."""
+    T, E = logits.shape
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1
+    idx = torch.empty(T, k, dtype=torch.int32, device=logits.device)
+    w = torch.empty(T, k, dtype=torch.float32, device=logits.device)
+    probs = torch.empty(T, E, dtype=torch.float32, device=logits.device) if want_probs else None
+    if T == 0:
+        return idx, w, probs
+    if logits.is_cuda:
+        _native.check(_native.lib().ix_router_topk(logits.data_ptr(), logits.stride(0), _native.ptr(bias), T, E, k,
+                                                   int(sigmoid_bias), int(norm_topk), idx.data_ptr(), w.data_ptr(),
+                                                   _native.ptr(probs), _native.stream()), "ix_router_topk")
+    else:
+        _cpu.lib().ixc_router_topk(logits.data_ptr(), logits.stride(0), _cpu.ptr(bias), T, E, k, int(sigmoid_bias),
+                                   int(norm_topk), idx.data_ptr(), w.data_ptr(), _cpu.ptr(probs))
+    return idx, w, probs
+
+
+class _RouterTopK(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, logits, k, bias, sigmoid_bias, norm_topk):
+        idx, w, _ = router_topk_fwd(logits, k, bias, sigmoid_bias, norm_topk)
+        ctx.save_for_backward(logits, idx)
+        ctx.cfg = (sigmoid_bias, norm_topk)
+        ctx.mark_non_differentiable(idx)
+        return idx, w
+
+    @staticmethod
+    def backward(ctx, _g_idx, g_w):
+        logits, idx = ctx.saved_tensors
+        sigmoid_bias, norm_topk = ctx.cfg
+        with torch.enable_grad():
+            x = logits.detach().requires_grad_(True)
+            p = torch.sigmoid(x) if sigmoid_bias else torch.softmax(x, -1)
+            w = p.gather(1, idx.long())
+            if norm_topk:
+                w = w / w.sum(-1, keepdim=True)
+            (gx,) = torch.autograd.grad(w, x, g_w)
+        return gx, None, None, None, None
+
+
+def route(logits, k, bias=None, sigmoid_bias=False, norm_topk=True):
+    if torch.is_grad_enabled() and logits.requires_grad:
+        return _RouterTopK.apply(logits, k, bias, sigmoid_bias, norm_topk)
+    idx, w, _ = router_topk_fwd(logits, k, bias, sigmoid_bias, norm_topk)
+    return idx, w
+
+
+# ------------------------------------------------------------------------------------ dispatch / combine
+def build_dispatch(idx: torch.Tensor, num_experts: int):
+    """Integer routing mechanics. idx int32 [T, k]. Returns
+    order   int64 [T*k]  flat (token*k + slot) ids sorted by (expert, token, slot),
+    counts  int64 [E]    rows per expert,
+    pos     int64 [T, k] for each token, the dispatch row of its experts in ASCENDING expert index."""
+    T, k = idx.shape
+    flat = idx.reshape(-1).long()
+    order = torch.sort(flat, stable=True).indices            # stable: ties keep (token, slot) order
+    counts = torch.bincount(flat, minlength=num_experts)
+    inv = torch.empty_like(order)
+    inv[order] = torch.arange(order.numel(), device=idx.device)
+    by_expert = torch.sort(idx.long(), dim=1, stable=True).indices   # slots of a token by ascending expert
+    pos = inv.view(T, k).gather(1, by_expert)
+    return order, counts, pos
+
+
+def combine_fixed_order(rows: torch.Tensor, pos: torch.Tensor, out_dtype, shared: torch.Tensor | None = None):
+    """out[t] = round(sum_j rows[pos[t, j]]) with j over ascending expert index (fp32), + shared after the round."""
+    T, k = pos.shape
+    H = rows.shape[1]
+    if rows.is_cuda and out_dtype in (torch.bfloat16, torch.float32) and not (torch.is_grad_enabled() and rows.requires_grad):
+        out = torch.empty(T, H, dtype=out_dtype, device=rows.device)
+        if T:
+            _native.check(_native.lib().ix_moe_combine(rows.data_ptr(), pos.data_ptr(), _native.ptr(shared), out.data_ptr(), T, H,
+                                                       k, int(out_dtype == torch.bfloat16), _native.stream()), "ix_moe_combine")
+        return out
+    acc = rows.index_select(0, pos[:, 0])
+    for j in range(1, k):
+        acc = acc + rows.index_select(0, pos[:, j])
+    out = acc.to(out_dtype)
+    if shared is not None:
+        out = (out.float() + shared.float()).to(out_dtype)
+    return out
+
+
+class _AllToAll(torch.autograd.Function):
+    """Variable-split all-to-all of rows over the EP group (bytes only); backward is the reverse exchange."""
+
+    @staticmethod
+    def forward(ctx, x, send_counts, recv_counts, group):
+        ctx.cfg = (send_counts, recv_counts, group)
+        out = x.new_empty((sum(recv_counts),) + tuple(x.shape[1:]))
+        dist.all_to_all_single(out, x.contiguous(), output_split_sizes=recv_counts, input_split_sizes=send_counts, group=group)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        send_counts, recv_counts, group = ctx.cfg
+        out = g.new_empty((sum(send_counts),) + tuple(g.shape[1:]))
+        dist.all_to_all_single(out, g.contiguous(), output_split_sizes=send_counts, input_split_sizes=recv_counts, group=group)
+        return out, None, None, None
+
+
+# ------------------------------------------------------------------------------------ experts
+def _expert_rows(x_rows, w_rows, counts, gate_up, down):
+    """Rows grouped by local expert -> fp32 expert outputs, one GEMM pair per non-empty group."""
+    outs = []
+    lo = 0
+    for e, n in enumerate(counts):
+        if n == 0:
+            continue
+        xe = x_rows[lo:lo + n]
+        h1 = F.linear(xe, gate_up[e])
+        a = F.swiglu(h1)
+        if a.is_cuda and a.dtype == torch.bfloat16 and not (torch.is_grad_enabled() and a.requires_grad):
+            _native.check(_native.lib().ix_scale_rows(a.data_ptr(), w_rows[lo:lo + n].contiguous().data_ptr(), n, a.shape[1],
+                                                      _native.stream()), "ix_scale_rows")
+        else:
+            a = (a.float() * w_rows[lo:lo + n, None]).to(a.dtype)
+        outs.append(F.linear(a, down[e], out_f32=True))
+        lo += n
+    if not outs:
+        return x_rows.new_zeros((0, down.shape[1]), dtype=torch.float32)
+    return torch.cat(outs, 0)
+
+
+def moe_block(y: torch.Tensor, model, i: int) -> torch.Tensor:
+    cfg, ps = model.cfg, model.ps
+    pfx = f"layers.{i}.moe."
+    T, h = y.shape
+    E, k = cfg.num_experts, cfg.top_k
+    logits = F.linear(y, model.p(pfx + "router.weight"), out_f32=True).float()
+    bias = model.p(pfx + "router.expert_bias").float() if cfg.router == "sigmoid_bias" else None
+    idx, w = route(logits, k, bias, cfg.router == "sigmoid_bias", cfg.norm_topk_prob)
+    order, counts, pos = build_dispatch(idx, E)
+    tok_of_row = torch.div(order, k, rounding_mode="floor")
+    x_rows = y.index_select(0, tok_of_row)
+    w_rows = w.reshape(-1).index_select(0, order)
+    gate_up, down = model.p(pfx + "experts.gate_up"), model.p(pfx + "experts.down")
+    if ps.ep > 1:
+        e_loc = E // ps.ep
+        counts_l = counts.tolist()
+        send = [sum(counts_l[r * e_loc:(r + 1) * e_loc]) for r in range(ps.ep)]
+        # exchange per-expert counts so every owner knows its incoming group sizes
+        cnt_in = torch.empty(ps.ep * e_loc, dtype=counts.dtype, device=counts.device)
+        dist.all_to_all_single(cnt_in, counts.contiguous(), group=ps.ep_group)
+        cnt_in_l = cnt_in.view(ps.ep, e_loc).tolist()
+        recv = [sum(c) for c in cnt_in_l]
+        xr = _AllToAll.apply(x_rows, send, recv, ps.ep_group)
+        wr = _AllToAll.apply(w_rows, send, recv, ps.ep_group)
+        # received rows are grouped by (source rank, expert); regroup by expert, keeping source order
+        segs, base = [], 0
+        for r in range(ps.ep):
+            for e in range(e_loc):
+                segs.append((e, r, base, cnt_in_l[r][e]))
+                base += cnt_in_l[r][e]
+        perm = torch.cat([torch.arange(b, b + n, device=y.device) for e, r, b, n in sorted(segs) if n] or
+                         [torch.zeros(0, dtype=torch.long, device=y.device)])
+        loc_counts = [sum(cnt_in_l[r][e] for r in range(ps.ep)) for e in range(e_loc)]
+        out_rows = _expert_rows(xr.index_select(0, perm), wr.index_select(0, perm), loc_counts, gate_up, down)
+        back = torch.empty_like(out_rows)
+        back[perm] = out_rows
+        rows = _AllToAll.apply(back, recv, send, ps.ep_group)
+    else:
+        rows = _expert_rows(x_rows, w_rows, counts.tolist(), gate_up, down)
+    shared = None
+    if cfg.shared_expert_ffn:
+        from ..parallel import tp as tp_ops
+
+        gu = F.linear(y, model.p(pfx + "shared.gate_up.weight"))
+        shared = tp_ops.row_parallel_linear(F.swiglu(gu), model.p(pfx + "shared.down.weight"), ps, cfg)
+    return combine_fixed_order(rows, pos, y.dtype, shared)

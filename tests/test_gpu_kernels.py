@@ -252,3 +252,46 @@ def test_engine_and_trainer_logprobs_bitwise_on_gpu_and_step():
         batch["action_log_probs"] = lp
         worker.forward_backward(batch)
         assert worker.optim_step() > 0
+
+
+def test_router_topk_matches_cpu_oracle_and_tie_rule():
+    from skyrl_isoexec_b200.ops import moe
+
+    torch.manual_seed(11)
+    for E, k in ((128, 8), (8, 2), (256, 8)):
+        lg = torch.randn(37, E)
+        lg[0, 3] = lg[0, 5] = 9.0                        # exact tie at the top: the lower index must win
+        ic, wc, pc = moe.router_topk_fwd(lg, k, None, False, True, want_probs=True)
+        ig, wg, pg = moe.router_topk_fwd(lg.to(DEV), k, None, False, True, want_probs=True)
+        assert ic[0, 0] == 3 and ic[0, 1] == 5
+        assert torch.equal(ig.cpu(), ic)
+        assert (wg.cpu() - wc).abs().max() < 1e-6 and (pg.cpu() - torch.softmax(lg, -1)).abs().max() < 1e-6
+        one = moe.router_topk_fwd(lg[5:6].to(DEV).contiguous(), k, None, False, True)
+        assert torch.equal(one[0], ig[5:6]) and bitwise_equal(one[1], wg[5:6])   # a token's routing ignores the batch
+
+
+@pytest.mark.parametrize("name", ["tiny-moe"])
+def test_moe_engine_and_trainer_logprobs_bitwise_on_gpu(name):
+    from skyrl_isoexec_b200.engine.llm_engine import EngineConfig, LLMEngine
+    from skyrl_isoexec_b200.engine.sampler import SamplingParams
+    from skyrl_isoexec_b200.models.config import get_config
+    from skyrl_isoexec_b200.models.decoder import DecoderLM
+    from skyrl_isoexec_b200.train.batch import TrainingInputBatch, build_sequences
+    from skyrl_isoexec_b200.train.policy_worker import PolicyWorker, WorkerConfig
+
+    cfg = get_config(name, dtype="bfloat16")
+    model = DecoderLM(cfg, device=DEV, seed=0)
+    eng = LLMEngine(model, EngineConfig(max_num_seqs=16, num_kv_pages=64, max_num_batched_tokens=80))
+    worker = PolicyWorker(model, WorkerConfig(max_tokens_per_microbatch=300))
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, cfg.vocab_size, (int(n),), generator=g).tolist() for n in torch.randint(20, 150, (8,), generator=g)]
+    outs = eng.generate(prompts, SamplingParams(max_generate_length=24, ignore_eos=True))
+    seq, att, rmask = build_sequences([o.prompt_ids for o in outs], [o.response_ids for o in outs])
+    batch = TrainingInputBatch({"sequences": seq, "attention_mask": att, "response_mask": rmask, "loss_mask": rmask.clone(),
+                                "advantages": torch.randn_like(rmask) / rmask.sum()})
+    lp = worker.forward(batch)
+    ro = torch.tensor([o.response_logprobs for o in outs])
+    assert count_bit_mismatches(lp.contiguous(), ro.contiguous()) == 0
+    batch["action_log_probs"] = lp
+    worker.forward_backward(batch)
+    assert worker.optim_step() > 0

@@ -146,10 +146,18 @@ def test_scheduler_preempts_and_recomputes_with_identical_logprobs():
     a = roomy.generate(prompts, sp)
     b = tight.generate(prompts, sp)
     assert tight.cache.allocator.num_free == 5 and roomy.cache.allocator.num_free == 16
-    # a preempted sequence is recomputed from scratch; what it already sampled is kept and its
-    # recomputed context yields the same distribution, so greedy-equal seeds are not required here:
-    # check the invariant that matters, every sequence finished with the full length
+    assert tight.scheduler.preemptions > 0 and roomy.scheduler.preemptions == 0
     assert all(len(o.response_ids) == 60 and len(o.response_logprobs) == 60 for o in a + b)
+    # a preempted sequence is recomputed from its tokens; the logprobs it reported before and after
+    # the preemption must all equal what a clean scoring forward gives, bit for bit
+    from skyrl_isoexec_b200.train.policy_worker import PolicyWorker, WorkerConfig
+
+    worker = PolicyWorker(model, WorkerConfig(max_tokens_per_microbatch=4096))
+    for outs in (a, b):
+        seq, att, rmask = build_sequences([o.prompt_ids for o in outs], [o.response_ids for o in outs])
+        lp = worker.forward(TrainingInputBatch({"sequences": seq, "attention_mask": att, "response_mask": rmask}))
+        ro = torch.tensor([o.response_logprobs for o in outs])
+        assert torch.equal(lp.view(torch.int32), ro.view(torch.int32))
 
 
 # ------------------------------------------------------------------ full loop + checkpoints
