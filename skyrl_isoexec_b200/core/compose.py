@@ -80,7 +80,7 @@ class ModelProfile:
     router_score: str = "softmax"
     router_topk: int = 0
     router_norm_topk: bool = True
-    gdn_kernel: str = "cpr"
+    gdn_kernel: str = "recurrent"
     gdn_chunk_size: int = 64
     gdn_conv_width: int = 4
     topology: tuple[TopologyAxisFact, ...] = ()

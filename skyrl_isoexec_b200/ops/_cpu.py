@@ -26,6 +26,11 @@ _SIGS = {
     "ixc_logprob_leafsum": [_P, _L, _I, _I, _I, _I, _I, _P, _P, _P, _I],
     "ixc_logprob_finalize": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I],
     "ixc_router_topk": [_P, _L, _P, _I, _I, _I, _I, _I, _P, _P, _P],
+    "ixc_gdn_conv": [_P, _L, _P, _P, _P, _P, _P, _L, _I, _I, _I],
+    "ixc_gdn_conv_state": [_P, _L, _P, _P, _I, _I, _I, _I],
+    "ixc_gdn_gate": [_P, _P, _L, _P, _P, _P, _P, _L, _I, _I],
+    "ixc_gdn_l2norm": [_P, _L, _P, _P, _L, _I, _I, _F, _F, _I],
+    "ixc_gdn_scan": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I],
     "ixc_attention_fwd": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I],
 }
 

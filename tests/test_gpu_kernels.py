@@ -270,8 +270,8 @@ def test_router_topk_matches_cpu_oracle_and_tie_rule():
         assert torch.equal(one[0], ig[5:6]) and bitwise_equal(one[1], wg[5:6])   # a token's routing ignores the batch
 
 
-@pytest.mark.parametrize("name", ["tiny-moe"])
-def test_moe_engine_and_trainer_logprobs_bitwise_on_gpu(name):
+@pytest.mark.parametrize("name", ["tiny-moe", "tiny-hybrid"])
+def test_moe_and_hybrid_engine_and_trainer_logprobs_bitwise_on_gpu(name):
     from skyrl_isoexec_b200.engine.llm_engine import EngineConfig, LLMEngine
     from skyrl_isoexec_b200.engine.sampler import SamplingParams
     from skyrl_isoexec_b200.models.config import get_config
@@ -295,3 +295,30 @@ def test_moe_engine_and_trainer_logprobs_bitwise_on_gpu(name):
     batch["action_log_probs"] = lp
     worker.forward_backward(batch)
     assert worker.optim_step() > 0
+
+
+def test_gdn_scan_bitwise_vs_cpu_oracle_chunked_equals_recurrent():
+    """The scan over a whole sequence equals the same sequence fed as chunks through the state pool
+    (bitwise, on the GPU), and agrees with the C++ oracle wherever exp() agrees."""
+    from skyrl_isoexec_b200.models.config import get_config
+    from skyrl_isoexec_b200.ops import gdn
+
+    torch.manual_seed(12)
+    cfg = get_config("tiny-hybrid", dtype="bfloat16")
+    hk, hv, d = cfg.gdn_k_heads, cfg.gdn_v_heads, cfg.gdn_head_dim
+    C = (2 * hk + hv) * d
+    T = 200
+    proj = (torch.randn(T, C + hv * d + 2 * hv) * 0.5).bfloat16()
+    conv_w, A_log, dtb = (torch.randn(C, 4) * 0.3).bfloat16(), (torch.randn(hv) * 0.1).bfloat16(), (torch.randn(hv) * 0.1).bfloat16()
+    whole = gdn.gdn_core_fwd(proj.to(DEV), conv_w.to(DEV), A_log.to(DEV), dtb.to(DEV), gdn.GDNMeta.packed([T], DEV), cfg, 1)
+    cpu = gdn.gdn_core_fwd(proj, conv_w, A_log, dtb, gdn.GDNMeta.packed([T], "cpu"), cfg, 1)
+    assert (whole.cpu().float() - cpu.float()).abs().max() < 2e-2 * max(1.0, cpu.float().abs().max().item())
+    conv_state = torch.zeros(3, C, 3, dtype=torch.bfloat16, device=DEV)
+    ssm = torch.zeros(3, hv, d, d, dtype=torch.float32, device=DEV)
+    outs, pos = [], 0
+    for n in (70, 1, 1, 64, 1, 63):                       # prefill chunk, decode steps, more chunks
+        meta = gdn.GDNMeta.build([(0, n, pos, 2 if pos > 0 else -1, 2)], DEV)
+        outs.append(gdn.gdn_core_fwd(proj[pos:pos + n].to(DEV).contiguous(), conv_w.to(DEV), A_log.to(DEV), dtb.to(DEV), meta, cfg, 1,
+                                     conv_state, ssm))
+        pos += n
+    assert bitwise_equal(torch.cat(outs, 0), whole)
