@@ -109,6 +109,11 @@ def main():
     torch.cuda.set_device(local)
     _native.lib().ix_init()
     ps = ParallelState.build(tp=1) if world > 1 else ParallelState.single()
+    if world > 1:
+        # data-parallel gradient reduction runs on the peer-memory kernels (csrc/peer_collectives.cu)
+        from skyrl_isoexec_b200.parallel.symm_runtime import SymmGroup
+
+        SymmGroup(ps.dp_group, staging_bytes=512 << 20)
     P, S = args.prompts_per_gpu, args.samples
     ov = [
         f"trainer.policy.model={args.model}", f"trainer.train_batch_size={P * world}",

@@ -40,6 +40,7 @@ class ParamSpec:
     offset: int = 0
     ep_sharded: bool = False     # leading expert dim split over EP
     sections: tuple[int, ...] = ()  # sizes of the blocks on shard_dim that are each split over TP
+    tp_grad_sum: bool = False    # replicated weight used by the LOCAL heads only: its gradient is summed over TP
 
 
 class ParamStore:
@@ -116,8 +117,9 @@ def build_param_specs(cfg: ModelConfig, ps: ParallelState, layer_range: range | 
         if shard_dim is not None and tp > 1:
             assert shape[shard_dim] % tp == 0, (name, full_shape, tp)
             shape[shard_dim] //= tp
+        per_head = name.endswith(("q_norm.weight", "k_norm.weight", "gdn.out_norm.weight"))
         specs.append(ParamSpec(name, tuple(shape), tuple(full_shape), shard_dim, init_std, ep_sharded=ep_sharded,
-                               sections=tuple(sections)))
+                               sections=tuple(sections), tp_grad_sum=per_head))
 
     layers = layer_range if layer_range is not None else range(cfg.num_layers)
     if ps.is_first_pp or cfg.tie_embeddings:
@@ -218,8 +220,7 @@ class DecoderLM(nn.Module):
         if self.cfg.tie_embeddings:
             w = self.p("embed.weight")
             if self.ps.tp > 1:
-                n = w.shape[0] // self.ps.tp
-                return w[self.ps.tp_rank * n:(self.ps.tp_rank + 1) * n]
+                return tp_ops.tied_head_slice(w, self.ps)
             return w
         return self.p("lm_head.weight")
 
@@ -227,7 +228,7 @@ class DecoderLM(nn.Module):
     def _attn_block(self, i: int, y: torch.Tensor, fc: ForwardCtx, kv_idx: int) -> torch.Tensor:
         cfg, pfx = self.cfg, f"layers.{i}.attn."
         T = y.shape[0]
-        qkv = F.linear(y, self.p(pfx + "qkv.weight"))
+        qkv = F.linear(tp_ops.copy_to_tp(y, self.ps), self.p(pfx + "qkv.weight"))
         qw = self.p(pfx + "q_norm.weight") if cfg.qk_norm else None
         kw = self.p(pfx + "k_norm.weight") if cfg.qk_norm else None
         if fc.kv is None:
@@ -247,7 +248,7 @@ class DecoderLM(nn.Module):
         cfg, pfx = self.cfg, f"layers.{i}."
         if cfg.has_moe:
             return moe_ops.moe_block(y, self, i)
-        gu = F.linear(y, self.p(pfx + "mlp.gate_up.weight"))
+        gu = F.linear(tp_ops.copy_to_tp(y, self.ps), self.p(pfx + "mlp.gate_up.weight"))
         return tp_ops.row_parallel_linear(F.swiglu(gu), self.p(pfx + "mlp.down.weight"), self.ps, cfg)
 
     def layer(self, i: int, x: torch.Tensor, res: torch.Tensor | None, fc: ForwardCtx, kv_idx: int):

@@ -214,7 +214,7 @@ def gdn_block(y, model, i: int, fc, kv_idx: int):
     pfx = f"layers.{i}.gdn."
     hk, hv, d, kd, vd = _dims(cfg, ps.tp)
     C = 2 * kd + vd
-    proj = F.linear(y, model.p(pfx + "in_proj.weight"))
+    proj = F.linear(tp_ops.copy_to_tp(y, ps), model.p(pfx + "in_proj.weight"))
     meta = fc.gdn_meta
     assert meta is not None, "GDN layers need ForwardCtx.gdn_meta"
     conv_w, A_log, dt_bias = model.p(pfx + "conv.weight"), model.p(pfx + "A_log"), model.p(pfx + "dt_bias")

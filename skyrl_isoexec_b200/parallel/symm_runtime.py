@@ -34,10 +34,6 @@ def _rendezvous(t: torch.Tensor, group):
     import torch.distributed._symmetric_memory as sm
 
     name = group.group_name if group is not None else dist.group.WORLD.group_name
-    try:
-        sm.enable_symm_mem_for_group(name)
-    except Exception:  # noqa: BLE001 - newer versions enable groups implicitly
-        pass
     return sm.rendezvous(t, group=name)
 
 

@@ -94,9 +94,10 @@ def tree_all_reduce(partial: torch.Tensor, group, tp: int) -> torch.Tensor:
 
     if partial.is_cuda and symm.enabled(group):
         return symm.tree_all_reduce(partial, group)
-    gathered = torch.empty((tp,) + tuple(partial.shape), dtype=partial.dtype, device=partial.device)
-    dist.all_gather_into_tensor(gathered, partial.contiguous(), group=group)
-    return tree_fold(gathered)
+    part = partial.contiguous().view(-1)
+    gathered = torch.empty(tp * part.numel(), dtype=partial.dtype, device=partial.device)
+    dist.all_gather_into_tensor(gathered, part, group=group)
+    return tree_fold(gathered.view((tp,) + tuple(partial.shape)))
 
 
 class _RowParallel(torch.autograd.Function):
@@ -159,3 +160,31 @@ def copy_to_tp(x, ps):
     if ps.tp == 1 or not (torch.is_grad_enabled() and x.requires_grad):
         return x
     return _CopyToTP.apply(x, ps.tp_group)
+
+
+class _TiedHeadSlice(torch.autograd.Function):
+    """Vocabulary shard of a replicated (tied) embedding used as the LM head. Backward returns the
+    full-size gradient with every rank's shard filled in (sum over TP), so the replicated parameter
+    receives the same gradient on every rank."""
+
+    @staticmethod
+    def forward(ctx, w, ps):
+        ctx.ps = ps
+        n = w.shape[0] // ps.tp
+        return w[ps.tp_rank * n:(ps.tp_rank + 1) * n]
+
+    @staticmethod
+    def backward(ctx, g):
+        ps = ctx.ps
+        n = g.shape[0]
+        full = g.new_zeros((n * ps.tp,) + tuple(g.shape[1:]))
+        full[ps.tp_rank * n:(ps.tp_rank + 1) * n] = g
+        dist.all_reduce(full, group=ps.tp_group)
+        return full, None
+
+
+def tied_head_slice(w, ps):
+    if torch.is_grad_enabled() and w.requires_grad:
+        return _TiedHeadSlice.apply(w, ps)
+    n = w.shape[0] // ps.tp
+    return w[ps.tp_rank * n:(ps.tp_rank + 1) * n]

@@ -388,7 +388,14 @@ class PolicyWorker:
                 "policy_entropy": tot["entropy_sum"] / n, "policy_kl": tot["kl_sum"] / n}
 
     def reduce_gradients(self) -> None:
-        """Sum the main gradients over the data-parallel group (fixed bucket order)."""
+        """Sum the main gradients over the data-parallel group (fixed bucket order); before that,
+        weights that are replicated over TP but only see the local heads get their gradient summed over TP."""
+        if self.ps.tp > 1:
+            store = self.model.store
+            for name in store.order:
+                s = store.specs[name]
+                if s.tp_grad_sum:
+                    dist.all_reduce(self.opt.main_grad[s.offset:s.offset + math.prod(s.shape)], group=self.ps.tp_group)
         if self.ps.dp > 1:
             from ..parallel.dp import reduce_main_grads
 
