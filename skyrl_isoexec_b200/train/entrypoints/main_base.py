@@ -1,0 +1,72 @@
+"""Training entry point (reference: R/train/entrypoints/main_base.py:134-452).
+
+    python -m skyrl_isoexec_b200.train.entrypoints.main_base trainer.policy.model=qwen3-8b key=value ...
+    torchrun --nproc-per-node 8 -m skyrl_isoexec_b200.train.entrypoints.main_base ... (one process per GPU)
+
+``BasePPOExp`` keeps the reference's extension hooks (``get_trainer``, ``get_generator``,
+``get_inference_client``, ``get_train_dataset``, ``get_tracker``) so an experiment subclass can swap a piece
+without touching the loop. No Ray: under torchrun every rank runs the same program.
+"""
+
+from __future__ import annotations
+
+import sys
+
+import torch
+
+from ...parallel.state import ParallelState, init_distributed
+from ..config import SkyRLTrainConfig, validate_cfg
+from ..trainer import RayPPOTrainer
+
+
+class BasePPOExp:
+    def __init__(self, cfg: SkyRLTrainConfig):
+        self.cfg = cfg
+        self.rank, self.world, self.local_rank = init_distributed()
+        validate_cfg(cfg, self.world)
+        p = cfg.trainer.policy.parallel
+        self.ps = ParallelState.build(tp=p.tensor_model_parallel_size, pp=p.pipeline_model_parallel_size,
+                                      ep=p.expert_model_parallel_size, cp=p.context_parallel_size) if self.world > 1 \
+            else ParallelState.single()
+        self.device = f"cuda:{self.local_rank}" if torch.cuda.is_available() else "cpu"
+        if torch.cuda.is_available():
+            torch.cuda.set_device(self.local_rank)
+
+    # ---- hooks
+    def get_tokenizer(self):
+        return None
+
+    def get_train_dataset(self):
+        from ..dataset import PromptDataset
+
+        d = self.cfg.data
+        if d.train_data:
+            return PromptDataset(d.train_data, tokenizer=self.get_tokenizer(), max_prompt_length=self.cfg.trainer.max_prompt_length,
+                                 env_class=self.cfg.environment.env_class)
+        return None   # the trainer falls back to synthetic prompts
+
+    def get_tracker(self):
+        return None
+
+    def get_trainer(self) -> RayPPOTrainer:
+        return RayPPOTrainer(self.cfg, ps=self.ps, device=self.device, dataset=self.get_train_dataset(),
+                             tokenizer=self.get_tokenizer(), tracker=self.get_tracker())
+
+    def run(self):
+        trainer = self.get_trainer()
+        trainer.build_models()
+        if self.world > 1 and torch.cuda.is_available() and self.ps.dp > 1:
+            from ...parallel.symm_runtime import SymmGroup
+
+            SymmGroup(self.ps.dp_group)
+        trainer.train()
+        return trainer
+
+
+def main(argv=None) -> None:
+    cfg = SkyRLTrainConfig.from_cli_overrides(list(sys.argv[1:] if argv is None else argv))
+    BasePPOExp(cfg).run()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,43 @@
+"""Evaluation: generate on a validation set with the eval sampling parameters and report reward
+statistics and pass@k (reference: R/train/evaluate.py)."""
+
+from __future__ import annotations
+
+import asyncio
+from collections import defaultdict
+
+from .generator import GeneratorInput
+
+
+def pass_at_k(n: int, c: int, k: int) -> float:
+    """Unbiased estimator of pass@k from n samples with c correct (Chen et al., 2021)."""
+    if n - c < k:
+        return 1.0
+    p = 1.0
+    for i in range(n - c + 1, n + 1):
+        p *= 1.0 - k / i
+    return 1.0 - p
+
+
+def evaluate(generator, rows: list[dict], sampling_params: dict, n_samples: int = 1, ks=(1,), batch_size: int = 1024) -> dict:
+    """rows: dataset rows ({prompt, env_class, env_extras, uid}). Returns eval/* metrics."""
+    by_uid: dict = defaultdict(list)
+    lens = []
+    for lo in range(0, len(rows), batch_size):
+        chunk = rows[lo:lo + batch_size]
+        gi: GeneratorInput = {"prompts": [r["prompt"] for r in chunk for _ in range(n_samples)],
+                              "env_classes": [r["env_class"] for r in chunk for _ in range(n_samples)],
+                              "env_extras": [r.get("env_extras") or {} for r in chunk for _ in range(n_samples)],
+                              "sampling_params": sampling_params, "trajectory_ids": None, "batch_metadata": {"eval": True}}
+        go = asyncio.run(generator.generate(gi))
+        uids = [r["uid"] for r in chunk for _ in range(n_samples)]
+        for uid, rew, resp in zip(uids, go["rewards"], go["response_ids"]):
+            by_uid[uid].append(float(sum(rew)) if isinstance(rew, (list, tuple)) else float(rew))
+            lens.append(len(resp))
+    allr = [r for v in by_uid.values() for r in v]
+    out = {"eval/avg_reward": sum(allr) / max(1, len(allr)), "eval/num_prompts": len(by_uid),
+           "eval/avg_response_length": sum(lens) / max(1, len(lens))}
+    for k in ks:
+        if k <= n_samples:
+            out[f"eval/pass_at_{k}"] = sum(pass_at_k(len(v), sum(1 for r in v if r > 0), k) for v in by_uid.values()) / max(1, len(by_uid))
+    return out

@@ -1,0 +1,171 @@
+"""Flag table, lifecycle ordering checks, dataset/packing/replay helpers, SFT, evaluation, the
+fully-asynchronous trainer and the entry point, all on CPU."""
+import json
+import threading
+
+import pytest
+import torch
+
+from skyrl_isoexec_b200.core import flags, lifecycle
+from skyrl_isoexec_b200.train import dataset as D
+from skyrl_isoexec_b200.train.config import SkyRLTrainConfig
+from skyrl_isoexec_b200.train.evaluate import evaluate, pass_at_k
+from skyrl_isoexec_b200.train.fully_async_trainer import (AsyncConfig, AsyncPromptSource, FullyAsyncTrainer, GenerationGroupQueue,
+                                                           StalenessManager)
+from skyrl_isoexec_b200.train.sft_trainer import SFTConfig, SFTTrainer
+from skyrl_isoexec_b200.train.trainer import RayPPOTrainer
+
+
+def test_flag_table_is_consistent_and_detects_split_brain():
+    assert flags.check_table() == []
+    snap = flags.snapshot({})
+    assert set(snap) == {f.name for f in flags.FLAGS}
+    fn = flags.function_flags()
+    assert fn and all(f.selects for f in fn)
+    both = [f for f in fn if flags.TRAIN in f.sides and flags.ENGINE in f.sides]
+    assert both, "at least one function flag is read by both sides"
+    f = both[0]
+    other = "1" if f.get({}) != "1" else "0"
+    out = flags.latent_split_brain({}, {f.name: other})
+    assert len(out) == 1 and f.name in out[0]
+    assert flags.latent_split_brain({f.name: other}, {f.name: other}) == []
+    assert f.name in flags.actor_forwarding_list(flags.ENGINE)
+
+
+def test_lifecycle_checks_flag_wrong_orders():
+    good = lifecycle.LifecycleLog()
+    for name, d in (("handshake_ok", {}), ("engine_wake", {"tags": ["weights"]}), ("sync_begin", {}), ("weight_sync", {}),
+                    ("sync_end", {}), ("state_invalidated", {}), ("engine_wake", {"tags": ["kv_cache"]}), ("generate", {}),
+                    ("engine_sleep", {"level": 1})):
+        good.add(name, **d)
+    assert lifecycle.run_all(good) == []
+    bad = lifecycle.LifecycleLog()
+    for name, d in (("engine_sleep", {"level": 2}), ("sync_begin", {}), ("weight_sync", {}), ("generate", {}), ("handshake_ok", {})):
+        bad.add(name, **d)
+    errs = lifecycle.run_all(bad)
+    # asleep during sync, transfer still open at generate, state not invalidated, handshake after the first sync
+    assert len(errs) == 4, errs
+    dropped = lifecycle.LifecycleLog()
+    dropped.add("engine_sleep", level=2)
+    dropped.add("generate")
+    assert lifecycle.check_sleep_tag_scoping(dropped)
+
+
+def test_packing_boundaries_and_replay_buffer():
+    lens = [700, 300, 300, 200, 512, 100, 50]
+    bins = D.pack_first_fit_decreasing(lens, 1024)
+    assert sorted(i for b in bins for i in b) == list(range(len(lens)))
+    assert all(sum(lens[i] for i in b) <= 1024 for b in bins) and len(bins) == 3
+    assert D.pack_first_fit_decreasing([2000, 10], 1024) == [[0], [1]]      # an oversize sequence gets its own bin
+    bal = D.pack_balanced(lens, 2)
+    loads = [sum(lens[i] for i in b) for b in bal]
+    assert sorted(i for b in bal for i in b) == list(range(len(lens))) and abs(loads[0] - loads[1]) <= 200
+    uids = ["a", "a", "b", "b", "b", "c"]
+    assert D.compute_prompt_boundaries(uids) == [(0, 2), (2, 5), (5, 6)]
+    assert D.compute_prompt_mini_batch_boundaries(uids, 2) == [(0, 5), (5, 6)]
+    rb = D.ReplayBuffer(capacity=4, max_staleness=1)
+    for v, item in enumerate("wxyz"):
+        rb.add(item, version=v)
+    rb.add("q", version=3)                 # over capacity: the oldest goes
+    assert len(rb) == 4
+    assert rb.evict_stale(current_version=3) == 1   # versions 1 is staler than 1 step; 2, 3, 3 stay
+    got = rb.pop_batch(2, current_version=3)
+    assert got == [("y", 2), ("z", 3)] and len(rb) == 1
+
+
+def test_prompt_dataset_reads_jsonl_and_filters(tmp_path):
+    p = tmp_path / "train.jsonl"
+    rows = [{"prompt": list(range(5)), "env_class": "even_tokens"}, {"prompt": list(range(50)), "env_class": "even_tokens"},
+            {"prompt": [1, 2, 3], "reward_spec": {"ground_truth": "7"}}]
+    p.write_text("\n".join(json.dumps(r) for r in rows))
+    ds = D.PromptDataset([str(p)], max_prompt_length=10, env_class="gsm8k")
+    assert len(ds) == 2
+    assert ds[0]["env_class"] == "even_tokens" and ds[1]["env_class"] == "gsm8k"
+    assert ds[0]["uid"] != ds[1]["uid"]
+
+
+def test_pass_at_k_matches_closed_forms():
+    assert pass_at_k(10, 0, 1) == 0.0 and pass_at_k(10, 10, 3) == 1.0
+    assert abs(pass_at_k(10, 3, 1) - 0.3) < 1e-12
+    assert abs(pass_at_k(4, 2, 2) - (1 - (2 / 4) * (1 / 3))) < 1e-12
+
+
+def _rl_cfg(tmp, steps, *extra):
+    return SkyRLTrainConfig.from_cli_overrides([
+        "trainer.policy.model=tiny-qwen3", "trainer.train_batch_size=4", "trainer.policy_mini_batch_size=4",
+        "generator.n_samples_per_prompt=4", "generator.sampling_params.max_generate_length=16",
+        "generator.sampling_params.ignore_eos=true", "data.synthetic_prompt_len=12", "data.synthetic_prompts=32",
+        "trainer.max_prompt_length=12", "generator.inference_engine.num_kv_pages=64",
+        "trainer.policy.optimizer_config.lr=1e-3", f"trainer.num_steps={steps}", f"trainer.ckpt_path={tmp}",
+        "trainer.ckpt_interval=0", "trainer.logger=jsonl", *extra])
+
+
+def test_evaluate_reports_reward_and_pass_at_k(tmp_path):
+    tr = RayPPOTrainer(_rl_cfg(str(tmp_path), 1), device="cpu")
+    tr.build_models()
+    tr.engine.wake_up()
+    rows = [tr.dataset[i] for i in range(3)]
+    out = evaluate(tr.generator, rows, {"max_generate_length": 8, "ignore_eos": True}, n_samples=4, ks=(1, 4))
+    assert out["eval/num_prompts"] == 3 and out["eval/avg_response_length"] == 8
+    assert 0.0 <= out["eval/pass_at_1"] <= out["eval/pass_at_4"] <= 1.0
+
+
+def test_sft_lowers_the_loss_on_a_fixed_batch():
+    g = torch.Generator().manual_seed(0)
+    ex = [{"prompt_ids": torch.randint(0, 200, (6,), generator=g).tolist(),
+           "response_ids": torch.randint(0, 200, (10,), generator=g).tolist()} for _ in range(8)]
+    cfg = SFTConfig(model="tiny-qwen3", batch_size=8, logger="jsonl")
+    cfg.optimizer.lr = 3e-3
+    cfg.optimizer.num_warmup_steps = 0
+    tr = SFTTrainer(cfg, ex, device="cpu")
+    losses = [tr.train_step(ex)["sft/loss"] for _ in range(6)]
+    assert losses[-1] < losses[0] * 0.9, losses
+    assert tr.global_step == 6
+
+
+def test_staleness_manager_bounds_rollouts_in_flight():
+    sm = StalenessManager(max_staleness_steps=1, mini_batch_prompts=2)
+    assert sm.capacity == 4
+    assert all(sm.acquire(timeout=0.0) for _ in range(4))
+    assert not sm.acquire(timeout=0.01)
+    sm.finished()
+    sm.finished()
+    assert not sm.acquire(timeout=0.01)          # buffered groups still count against the budget
+    sm.consumed(2)
+    assert sm.acquire(timeout=0.0) and sm.acquire(timeout=0.0) and not sm.acquire(timeout=0.0)
+    q = GenerationGroupQueue()
+    t = threading.Timer(0.05, lambda: [q.put(1), q.put(2)])
+    t.start()
+    assert q.get_many(2, timeout=2.0) == [1, 2]
+    with pytest.raises(TimeoutError):
+        q.get_many(1, timeout=0.01)
+    src = AsyncPromptSource([{"uid": i} for i in range(3)])
+    assert [src.next()["uid"] for _ in range(4)] == [0, 1, 2, 0] and src.epoch == 1
+    src.mark_consumed(1)
+    sd = src.state_dict()
+    src2 = AsyncPromptSource([{"uid": i} for i in range(3)])
+    src2.load_state_dict(sd)
+    assert src2.cursor == 1 and src2.consumed == {1}
+
+
+def test_fully_async_trainer_runs_with_bounded_staleness(tmp_path):
+    cfg = _rl_cfg(str(tmp_path), 3, "trainer.isoexec.strict=false")
+    tr = FullyAsyncTrainer(cfg, AsyncConfig(max_staleness_steps=1, num_parallel_generation_workers=3, mini_batch_prompts=4), device="cpu")
+    tr.train()
+    assert tr.global_step == 3 and tr.stale.version == 3
+    assert 0 <= tr.all_metrics["async/staleness_max"] <= 2
+    assert tr.all_metrics["policy/grad_norm"] > 0
+    assert len(tr.source.consumed) >= 4
+
+
+def test_entrypoint_runs_one_step(tmp_path, capsys):
+    from skyrl_isoexec_b200.train.entrypoints import main_base
+
+    ov = ["trainer.policy.model=tiny-qwen3", "trainer.train_batch_size=2", "trainer.policy_mini_batch_size=2",
+          "generator.n_samples_per_prompt=2", "generator.sampling_params.max_generate_length=8",
+          "generator.sampling_params.ignore_eos=true", "data.synthetic_prompt_len=8", "data.synthetic_prompts=8",
+          "trainer.max_prompt_length=8", "generator.inference_engine.num_kv_pages=16", "trainer.num_steps=1",
+          f"trainer.ckpt_path={tmp_path}", "trainer.ckpt_interval=0", "trainer.logger=jsonl"]
+    exp = main_base.BasePPOExp(SkyRLTrainConfig.from_cli_overrides(ov))
+    trainer = exp.run()
+    assert trainer.global_step == 1
