@@ -48,6 +48,7 @@ _SIGS = {
     "ix_router_topk": [_P, _L, _P, _I, _I, _I, _I, _I, _P, _P, _P, _P],
     "ix_moe_combine": [_P, _P, _P, _P, _I, _I, _I, _I, _P],
     "ix_scale_rows": [_P, _P, _L, _I, _P],
+    "ix_moe_grouped_gemm": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     "ix_gdn_conv": [_P, _L, _P, _P, _P, _P, _P, _L, _I, _I, _I, _P],
     "ix_gdn_conv_state": [_P, _L, _P, _P, _I, _I, _I, _I, _P],
     "ix_gdn_gate": [_P, _P, _L, _P, _P, _P, _P, _L, _I, _I, _P],

@@ -150,6 +150,44 @@ def _expert_rows(x_rows, w_rows, counts, gate_up, down):
     return torch.cat(outs, 0)
 
 
+EPI_BF16, EPI_F32, EPI_GLU = 0, 1, 2
+
+
+def grouped_gemm(x_rows: torch.Tensor, w: torch.Tensor, offs: torch.Tensor, epi: int, w_rows: torch.Tensor | None = None,
+                 row_dst: torch.Tensor | None = None, out: torch.Tensor | None = None, bn: int = 0) -> torch.Tensor:
+    """One launch over all experts (csrc/moe_grouped_gemm.cu). x_rows [R, K] bf16 sorted by expert, offs int32 [E+1]
+    on the device, w [E, N or 2N, K]. epi: EPI_BF16 | EPI_F32 plain output, EPI_GLU = SwiGLU x gate weight.
+    ``row_dst`` (int64 [R] device addresses) scatters the output rows, possibly into peer memory."""
+    R, K = x_rows.shape
+    E = w.shape[0]
+    N = w.shape[1] // 2 if epi == EPI_GLU else w.shape[1]
+    assert x_rows.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.is_contiguous() and x_rows.stride(1) == 1
+    assert offs.dtype == torch.int32 and offs.numel() == E + 1
+    if out is None and row_dst is None:
+        out = torch.empty(R, N, dtype=torch.float32 if epi == EPI_F32 else torch.bfloat16, device=x_rows.device)
+    _native.check(_native.lib().ix_moe_grouped_gemm(x_rows.data_ptr(), w.data_ptr(), _native.ptr(out), offs.data_ptr(),
+                                                    _native.ptr(w_rows), _native.ptr(row_dst), R, E, N, K, x_rows.stride(0), N,
+                                                    epi, bn, _native.stream()), "ix_moe_grouped_gemm")
+    return out
+
+
+def expert_rows_grouped(x_rows, w_rows, offs, gate_up, down, row_dst=None):
+    """fc1 + SwiGLU + gate weight in one grouped launch, fc2 (fp32 out) in a second; no host round trip."""
+    a = grouped_gemm(x_rows, gate_up, offs, EPI_GLU, w_rows=w_rows.contiguous())
+    return grouped_gemm(a, down, offs, EPI_F32, row_dst=row_dst)
+
+
+def _grouped_ok(x_rows, gate_up, down) -> bool:
+    return (x_rows.is_cuda and x_rows.dtype == torch.bfloat16 and not torch.is_grad_enabled() and gate_up.shape[2] % 64 == 0
+            and down.shape[2] % 64 == 0 and down.shape[1] % 32 == 0 and (gate_up.shape[1] // 2) % 32 == 0 and gate_up.shape[0] <= 512)
+
+
+def counts_to_offsets(counts: torch.Tensor) -> torch.Tensor:
+    offs = torch.zeros(counts.numel() + 1, dtype=torch.int32, device=counts.device)
+    offs[1:] = torch.cumsum(counts, 0)
+    return offs
+
+
 def moe_block(y: torch.Tensor, model, i: int) -> torch.Tensor:
     cfg, ps = model.cfg, model.ps
     pfx = f"layers.{i}.moe."
@@ -163,7 +201,15 @@ def moe_block(y: torch.Tensor, model, i: int) -> torch.Tensor:
     x_rows = y.index_select(0, tok_of_row)
     w_rows = w.reshape(-1).index_select(0, order)
     gate_up, down = model.p(pfx + "experts.gate_up"), model.p(pfx + "experts.down")
-    if ps.ep > 1:
+    peer = None
+    if ps.ep > 1 and y.is_cuda and not torch.is_grad_enabled():
+        from . import moe_ep
+
+        peer = moe_ep.get(ps.ep_group)
+    if peer is not None:
+        # dispatch, expert GEMMs and the return of the rows as our own kernels over peer memory
+        rows, pos = peer.forward(y, idx, w, gate_up, down)
+    elif ps.ep > 1:
         e_loc = E // ps.ep
         counts_l = counts.tolist()
         send = [sum(counts_l[r * e_loc:(r + 1) * e_loc]) for r in range(ps.ep)]
@@ -183,10 +229,17 @@ def moe_block(y: torch.Tensor, model, i: int) -> torch.Tensor:
         perm = torch.cat([torch.arange(b, b + n, device=y.device) for e, r, b, n in sorted(segs) if n] or
                          [torch.zeros(0, dtype=torch.long, device=y.device)])
         loc_counts = [sum(cnt_in_l[r][e] for r in range(ps.ep)) for e in range(e_loc)]
-        out_rows = _expert_rows(xr.index_select(0, perm), wr.index_select(0, perm), loc_counts, gate_up, down)
+        xs, wsr = xr.index_select(0, perm), wr.index_select(0, perm)
+        if _grouped_ok(xs, gate_up, down):
+            offs = counts_to_offsets(torch.tensor(loc_counts, dtype=torch.int64, device=y.device))
+            out_rows = expert_rows_grouped(xs, wsr, offs, gate_up, down)
+        else:
+            out_rows = _expert_rows(xs, wsr, loc_counts, gate_up, down)
         back = torch.empty_like(out_rows)
         back[perm] = out_rows
         rows = _AllToAll.apply(back, recv, send, ps.ep_group)
+    elif _grouped_ok(x_rows, gate_up, down):
+        rows = expert_rows_grouped(x_rows, w_rows, counts_to_offsets(counts), gate_up, down)
     else:
         rows = _expert_rows(x_rows, w_rows, counts.tolist(), gate_up, down)
     shared = None

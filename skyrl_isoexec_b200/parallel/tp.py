@@ -104,6 +104,16 @@ class _RowParallel(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, ps, leaves_local, round_leaf, out_dtype):
         ctx.save_for_backward(x, w)
+        if x.is_cuda and not round_leaf and x.dtype == torch.bfloat16 and x.stride(-1) == 1 and x.stride(0) % 8 == 0:
+            from . import tp_fused
+
+            if tp_fused.fused_ok(x.shape[0], w.shape[0], x.shape[1], leaves_local):
+                # one kernel: leaf accumulators in TMEM, leaf tree in the epilogue, rank tree over peer memory
+                if ps.tp == 1:
+                    return tp_fused.leaftree_gemm_fused(x, w, leaves_local, out_f32=out_dtype == torch.float32).to(out_dtype)
+                rt = tp_fused.get(ps.tp_group)
+                if rt is not None:
+                    return rt.row_parallel(x, w, leaves_local, out_dtype=out_dtype if out_dtype == torch.float32 else torch.bfloat16).to(out_dtype)
         part = leaftree_gemm(x, w, leaves_local, round_leaf)
         full = tree_all_reduce(part, ps.tp_group, ps.tp)
         return full.to(out_dtype)

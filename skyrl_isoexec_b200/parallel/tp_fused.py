@@ -1,0 +1,187 @@
+"""Host side of the fused tensor-parallel GEMMs (csrc/tp_gemm_fused.cu): symmetric-memory buffers,
+epochs, tile-width choice and the five entry points.
+
+  * ``leaftree_gemm_fused(x, w, leaves)``           single rank: G-leaf tree GEMM in one launch;
+  * ``FusedTP.row_parallel(x, w, leaves, ...)``     GEMM -> all-reduce (one-shot for decode-sized M,
+                                                    two-shot otherwise) or GEMM -> reduce-scatter;
+  * ``FusedTP.allgather_linear(x_local, w)``        all-gather -> GEMM for a sequence-parallel input.
+
+Every rank of the group calls the same methods in the same order; each call advances a shared epoch
+and flips the staging half. A call can be captured in a CUDA graph only together with its epoch, so
+the tensor-parallel engine runs these eagerly.
+
+Why a buffer half is free again two calls later: a rank finishes call e+1 only after it has waited
+for data that EVERY peer produced in call e+1, and a peer launches e+1 after its own kernel e (and the
+copy-out that follows it on the same stream) has completed; so when a rank starts call e+2 and writes
+into the halves of parity e, no peer still reads them.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+import torch.distributed as dist
+
+from ..ops import _native
+
+TP_LOCAL, TP_AR1, TP_AR2, TP_RS, TP_AG = 0, 1, 2, 3, 4
+_SMS = 148
+
+
+def _sig(lib):
+    if getattr(lib, "_tp_sig", False):
+        return
+    lib.ix_tp_gemm_fused.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p] + [C.c_int] * 6 + [C.c_int] * 6 + [C.c_uint] + \
+        [C.c_void_p] * 4 + [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p]
+    lib.ix_tp_stage_floats.argtypes = [C.c_int] * 5
+    lib.ix_tp_stage_floats.restype = C.c_longlong
+    lib._tp_sig = True
+
+
+def pick_bn(M: int, N: int, leaves: int) -> int:
+    """Widest tile allowed by TMEM (2*leaves*bn <= 512 columns, bn <= 128) that still gives most SMs a tile."""
+    bn = min(128, 256 // leaves)
+    tiles_m = (M + 127) // 128
+    while bn > 32 and (N % bn or tiles_m * (N // bn) * 5 < _SMS * 3):
+        bn //= 2
+    if N % bn:
+        raise ValueError(f"N={N} is not a multiple of the narrowest tile (32)")
+    return bn
+
+
+def fused_ok(M: int, N: int, K: int, leaves: int) -> bool:
+    return leaves in (1, 2, 4, 8) and K % (64 * leaves) == 0 and N % 32 == 0 and M > 0
+
+
+def leaftree_gemm_fused(x: torch.Tensor, w: torch.Tensor, leaves: int, out_f32: bool = True) -> torch.Tensor:
+    """[M,N] = balanced fp32 tree over ``leaves`` equal K slices of x @ w^T, one kernel, no peers."""
+    lib = _native.lib()
+    _sig(lib)
+    M, K = x.shape
+    N = w.shape[0]
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.stride(1) == 1 and w.stride(1) == 1
+    out = torch.empty(M, N, dtype=torch.float32 if out_f32 else torch.bfloat16, device=x.device)
+    bn = pick_bn(M, N, leaves)
+    _native.check(lib.ix_tp_gemm_fused(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, x.stride(0), w.stride(0), N,
+                                       TP_LOCAL, leaves, bn, int(out_f32), 0, 1, 0, None, None, None, None, None, None, 0, 0,
+                                       _native.stream()), "ix_tp_gemm_fused")
+    return out
+
+
+class FusedTP:
+    def __init__(self, group, stage_bytes: int = 160 << 20, out_bytes: int = 80 << 20, gather_bytes: int = 80 << 20, device=None):
+        import torch.distributed._symmetric_memory as sm
+
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.W = dist.get_world_size(group)
+        assert self.W & (self.W - 1) == 0 and self.W <= 8, "fused TP kernels support 1, 2, 4 or 8 ranks"
+        self.device = torch.device(device or f"cuda:{torch.cuda.current_device()}")
+        self.stage_floats = stage_bytes // 4
+        self.out_elems = out_bytes // 2           # bf16 elements per half
+        self.gather_elems = gather_bytes // 2
+        self.n_flags = 1 << 16
+        name = group.group_name if group is not None else dist.group.WORLD.group_name
+        self.stage = sm.empty(2 * self.stage_floats, dtype=torch.float32, device=self.device)
+        self.outring = sm.empty(2 * self.out_elems, dtype=torch.bfloat16, device=self.device)
+        self.gather = sm.empty(2 * self.gather_elems, dtype=torch.bfloat16, device=self.device)
+        self.flags = sm.empty(2 * self.n_flags + 64, dtype=torch.int32, device=self.device)   # [2 halves of tile flags | done flags]
+        self.flags.zero_()
+        self.ctr = torch.zeros(4, dtype=torch.int32, device=self.device)
+        torch.cuda.synchronize()
+        hs = [sm.rendezvous(t, group=name) for t in (self.stage, self.outring, self.gather, self.flags)]
+        dist.barrier(group=group)
+        self.p_stage, self.p_out, self.p_gather, self.p_flags = ([int(p) for p in h.buffer_ptrs] for h in hs)
+        self._handles = hs
+        self.calls = 0
+        self.epoch = 0
+        self.lib = _native.lib()
+        _sig(self.lib)
+
+    def _arr(self, ptrs, off_bytes):
+        return (C.c_longlong * self.W)(*[p + off_bytes for p in ptrs])
+
+    def _next(self):
+        parity = self.calls & 1
+        self.calls += 1
+        self.epoch += 1
+        return parity
+
+    def check(self) -> None:
+        st = _native.read_status()
+        if st != 0:
+            raise RuntimeError(f"a fused tensor-parallel kernel gave up on a wait (kernel status {st}): a rank of the group did not arrive")
+
+    # ------------------------------------------------------------------ GEMM -> all-reduce / reduce-scatter
+    def row_parallel(self, x: torch.Tensor, w: torch.Tensor, leaves: int = 1, mode: str = "auto",
+                     out_dtype=torch.bfloat16) -> torch.Tensor:
+        """x [M, K/W], w [N, K/W] (this rank's K slice). Returns the tree-ordered sum over ranks:
+        ``allreduce``/``auto`` -> [M, N] on every rank; ``reduce_scatter`` -> this rank's [M/W, N] row block."""
+        M, K = x.shape
+        N = w.shape[0]
+        W = self.W
+        if mode == "auto":
+            mode = "allreduce"
+        code = TP_RS if mode == "reduce_scatter" else (TP_AR1 if M <= 256 else TP_AR2)
+        bn = pick_bn(M, N, leaves)
+        need = int(self.lib.ix_tp_stage_floats(M, N, code, W, bn))
+        tiles = ((M + 127) // 128) * (N // bn)
+        if need > self.stage_floats or tiles * W > self.n_flags:
+            raise ValueError(f"row_parallel {M}x{N}: needs {need * 4} B of staging (have {self.stage_floats * 4})")
+        parity = self._next()
+        out_f32 = out_dtype == torch.float32
+        esz = 4 if out_f32 else 2
+        stage = self._arr(self.p_stage, parity * self.stage_floats * 4)
+        flags = self._arr(self.p_flags, parity * self.n_flags * 4)
+        done = self._arr(self.p_flags, (2 * self.n_flags + parity * 16) * 4)
+        peer_out, out_local, ret = None, None, None
+        if code == TP_AR2:
+            if M * N * esz > self.out_elems * 2:
+                raise ValueError(f"row_parallel {M}x{N}: output exceeds the symmetric output ring")
+            peer_out = self._arr(self.p_out, parity * self.out_elems * 2)
+            ring = self.outring[parity * self.out_elems:(parity + 1) * self.out_elems]
+            view = (ring.view(torch.float32) if out_f32 else ring)[:M * N].view(M, N)
+        elif code == TP_RS:
+            ret = torch.empty(M // W, N, dtype=out_dtype, device=x.device)
+            out_local = ret.data_ptr()
+        else:
+            ret = torch.empty(M, N, dtype=out_dtype, device=x.device)
+            out_local = ret.data_ptr()
+        _native.check(self.lib.ix_tp_gemm_fused(x.data_ptr(), w.data_ptr(), out_local, M, N, K, x.stride(0), w.stride(0), N,
+                                                code, leaves, bn, int(out_f32), self.rank, W, self.epoch, stage, flags, peer_out, done,
+                                                self.ctr.data_ptr(), None, 0, 0, _native.stream()), "ix_tp_gemm_fused")
+        if code == TP_AR2:
+            ret = view.clone()       # the ring half is rewritten two calls from now
+        return ret
+
+    # ------------------------------------------------------------------ all-gather -> GEMM
+    def allgather_linear(self, x_local: torch.Tensor, w: torch.Tensor, out_dtype=torch.bfloat16) -> torch.Tensor:
+        """x_local [M/W, K] (this rank's rows), w [N_local, K]. Returns [M, N_local] = all_gather(x) @ w^T."""
+        Ml, K = x_local.shape
+        N = w.shape[0]
+        W = self.W
+        M = Ml * W
+        if M * K > self.gather_elems:
+            raise ValueError(f"allgather_linear: gathered input {M}x{K} exceeds the symmetric gather buffer")
+        bn = pick_bn(M, N, 1)
+        parity = self._next()
+        flags = self._arr(self.p_flags, parity * self.n_flags * 4)
+        gat = self._arr(self.p_gather, parity * self.gather_elems * 2)
+        a_gathered = self.p_gather[self.rank] + parity * self.gather_elems * 2
+        out = torch.empty(M, N, dtype=out_dtype, device=x_local.device)
+        _native.check(self.lib.ix_tp_gemm_fused(a_gathered, w.data_ptr(), out.data_ptr(), M, N, K, K, w.stride(0), N, TP_AG, 1, bn,
+                                                int(out_dtype == torch.float32), self.rank, W, self.epoch, None, flags, gat, None,
+                                                None, x_local.data_ptr(), x_local.stride(0), Ml, _native.stream()), "ix_tp_gemm_fused")
+        return out
+
+
+_registry: dict = {}
+
+
+def register(group, rt: FusedTP) -> None:
+    _registry[group] = rt
+
+
+def get(group):
+    return _registry.get(group)

@@ -45,6 +45,65 @@ def test_gemm_strided_input_rows():
     assert bitwise_equal(F.gemm_nt(x, w), F.gemm_nt(x.contiguous(), w))
 
 
+@pytest.mark.parametrize("T,E,k", [(7, 8, 2), (700, 16, 4)])
+def test_grouped_expert_gemm_equals_per_expert_loop_bitwise(T, E, k):
+    """One grouped launch (fc1 + SwiGLU + gate weight fused; fc2 with fp32 out, plain and scattered) gives the bits
+    of the per-expert loop over the dense kernels, including empty experts and ragged last tiles."""
+    from skyrl_isoexec_b200.ops import moe
+
+    torch.manual_seed(5)
+    H, Fd = 256, 192
+    x = torch.randn(T, H, device=DEV).bfloat16()
+    gate_up = (torch.randn(E, 2 * Fd, H, device=DEV) * 0.06).bfloat16()
+    down = (torch.randn(E, H, Fd, device=DEV) * 0.06).bfloat16()
+    idx = torch.stack([torch.randperm(E - 1, device=DEV)[:k] for _ in range(T)]).int()      # the last expert stays empty
+    order, counts, pos = moe.build_dispatch(idx, E)
+    assert int(counts[-1]) == 0
+    x_rows = x.index_select(0, torch.div(order, k, rounding_mode="floor"))
+    w_rows = torch.rand(T * k, device=DEV)
+    with torch.no_grad():
+        want = moe._expert_rows(x_rows, w_rows, counts.tolist(), gate_up, down)
+        offs = moe.counts_to_offsets(counts)
+        got = moe.expert_rows_grouped(x_rows, w_rows, offs, gate_up, down)
+        assert bitwise_equal(got, want)
+        for bn in (32, 64):
+            a = moe.grouped_gemm(x_rows, gate_up, offs, moe.EPI_GLU, w_rows=w_rows, bn=bn)
+            assert bitwise_equal(moe.grouped_gemm(a, down, offs, moe.EPI_F32, bn=bn), want)
+        # scattered epilogue: rows land at the addresses given, here a permutation of a local buffer
+        a = moe.grouped_gemm(x_rows, gate_up, offs, moe.EPI_GLU, w_rows=w_rows)
+        dest = torch.zeros(T * k, H, device=DEV)
+        perm = torch.randperm(T * k, device=DEV)
+        row_dst = dest.data_ptr() + perm * (H * 4)
+        moe.grouped_gemm(a, down, offs, moe.EPI_F32, row_dst=row_dst)
+        assert bitwise_equal(dest[perm], want)
+        h1 = moe.grouped_gemm(x_rows, gate_up, offs, moe.EPI_BF16)
+        lo = int(offs[1])
+        assert bitwise_equal(h1[:lo], F.gemm_nt(x_rows[:lo].contiguous(), gate_up[0])) if lo else True
+
+
+@pytest.mark.parametrize("M", [5, 300])
+def test_leaftree_gemm_one_kernel_equals_leaf_loop_bitwise(M):
+    """Leaves accumulate in separate TMEM accumulators and fold in the epilogue: same bits as one GEMM per
+    leaf followed by the balanced tree in fp32, for every leaf count; one leaf is the plain GEMM."""
+    from skyrl_isoexec_b200.parallel.tp import tree_fold
+    from skyrl_isoexec_b200.parallel.tp_fused import leaftree_gemm_fused
+
+    torch.manual_seed(3)
+    N, K = 384, 1024
+    x = torch.randn(M, K, device=DEV).bfloat16()
+    w = (torch.randn(N, K, device=DEV) * 0.05).bfloat16()
+    assert bitwise_equal(leaftree_gemm_fused(x, w, 1), F.gemm_nt(x, w, out_f32=True))
+    for L in (2, 4, 8):
+        LK = K // L
+        parts = torch.stack([F.gemm_nt(x[:, j * LK:(j + 1) * LK], w[:, j * LK:(j + 1) * LK], out_f32=True) for j in range(L)])
+        want = tree_fold(parts)
+        got = leaftree_gemm_fused(x, w, L)
+        assert bitwise_equal(got, want), f"L={L}"
+        assert bitwise_equal(leaftree_gemm_fused(x, w, L, out_f32=False), want.bfloat16())
+    ref = x.float() @ w.float().T
+    assert (leaftree_gemm_fused(x, w, 8) - ref).abs().max() <= 2e-4 * max(1.0, ref.abs().max().item())
+
+
 @pytest.mark.parametrize("zero_centered", [False, True])
 @pytest.mark.parametrize("N", [128, 4096, 2560])
 def test_rmsnorm_bitwise_vs_cpu_oracle(N, zero_centered):

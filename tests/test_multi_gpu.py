@@ -128,3 +128,234 @@ def test_bounded_wait_reports_instead_of_hanging():
     assert _native.read_status() == 0                          # cleared by the read
     x = torch.ones(8, device="cuda")
     assert float(x.sum()) == 8.0                               # the context is still healthy
+
+
+def _tp_worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank), NCCL_NVLS_ENABLE="0")
+    import torch.distributed as dist
+
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from skyrl_isoexec_b200.core.testing import bitwise_equal
+        from skyrl_isoexec_b200.ops import _native, functional as F
+        from skyrl_isoexec_b200.parallel.tp_fused import FusedTP, leaftree_gemm_fused
+
+        _native.lib().ix_init()
+        rt = FusedTP(dist.group.WORLD, stage_bytes=192 << 20, out_bytes=96 << 20, gather_bytes=96 << 20)
+        res = {}
+        G, N, K = 8, 512, 2048
+        Kr = K // world
+        ok = {"ar1": True, "ar2": True, "rs": True, "ag": True}
+        for it in range(3):                                    # three rounds: both staging halves get reused
+            g = torch.Generator(device="cuda").manual_seed(11 + it)
+            w_full = (torch.randn(N, K, device="cuda", generator=g) * 0.05).bfloat16()
+            ws = w_full[:, rank * Kr:(rank + 1) * Kr].contiguous()
+            for M, key in ((40, "ar1"), (640, "ar2"), (128 * world * 2, "rs")):
+                x_full = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+                xs = x_full[:, rank * Kr:(rank + 1) * Kr].contiguous()
+                want = leaftree_gemm_fused(x_full, w_full, G, out_f32=False)          # the single-rank member of the family
+                got = rt.row_parallel(xs, ws, G // world, mode="reduce_scatter" if key == "rs" else "allreduce")
+                if key == "rs":
+                    want = want[rank * (M // world):(rank + 1) * (M // world)]
+                ok[key] &= bool(bitwise_equal(got, want))
+            # all-gather -> GEMM: every rank contributes different rows
+            gl = torch.Generator(device="cuda").manual_seed(1000 * it + rank)
+            x_loc = torch.randn(256, 1024, device="cuda", generator=gl).bfloat16()
+            w_col = (torch.randn(384, 1024, device="cuda", generator=g) * 0.05).bfloat16()
+            gathered = torch.empty(world * 256, 1024, device="cuda", dtype=torch.bfloat16)
+            dist.all_gather_into_tensor(gathered, x_loc)
+            ok["ag"] &= bool(bitwise_equal(rt.allgather_linear(x_loc, w_col), F.gemm_nt(gathered, w_col)))
+        rt.check()
+        res.update({f"fused_{k}_bitwise": v for k, v in ok.items()})
+
+        # ---- timing, device clock, max over ranks: down-projection of Qwen3-8B at TP=world, 8192 tokens
+        def timed(fn, n=5):
+            for _ in range(2):
+                fn()
+            torch.cuda.synchronize()
+            dist.barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(n):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            t = torch.tensor([e0.elapsed_time(e1) / n], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return float(t)
+
+        M, N, Kr = 8192, 4096, 12288 // world
+        x = torch.randn(M, Kr, device="cuda").bfloat16()
+        w = (torch.randn(N, Kr, device="cuda") * 0.02).bfloat16()
+
+        def unfused():
+            y = torch.matmul(x, w.t())
+            dist.all_reduce(y)
+            return y
+
+        res["fused_ar2_ms"] = timed(lambda: rt.row_parallel(x, w, 1))
+        res["fused_rs_ms"] = timed(lambda: rt.row_parallel(x, w, 1, mode="reduce_scatter"))
+        res["cublas_nccl_allreduce_ms"] = timed(unfused)
+        res["gemm_only_ms"] = timed(lambda: F.gemm_nt(x, w))
+        xl = torch.randn(M // world, 4096, device="cuda").bfloat16()
+        wq = (torch.randn(6144 // world, 4096, device="cuda") * 0.02).bfloat16()
+        gath = torch.empty(M, 4096, device="cuda", dtype=torch.bfloat16)
+
+        def unfused_ag():
+            dist.all_gather_into_tensor(gath, xl)
+            return torch.matmul(gath, wq.t())
+
+        res["fused_ag_ms"] = timed(lambda: rt.allgather_linear(xl, wq))
+        res["nccl_allgather_cublas_ms"] = timed(unfused_ag)
+        xd = torch.randn(64, Kr, device="cuda").bfloat16()
+        res["fused_ar1_decode_ms"] = timed(lambda: rt.row_parallel(xd, w, 1), n=20)
+
+        def unfused_dec():
+            y = torch.matmul(xd, w.t())
+            dist.all_reduce(y)
+            return y
+
+        res["cublas_nccl_decode_ms"] = timed(unfused_dec, n=20)
+        rt.check()
+        res["status"] = _native.read_status()
+        if rank == 0:
+            q.put(res)
+    finally:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+@pytest.mark.timeout(600)
+def test_fused_tp_gemm_matches_single_rank_tree_bitwise():
+    """GEMM -> all-reduce (one- and two-shot), GEMM -> reduce-scatter and all-gather -> GEMM, each one kernel
+    over peer memory, reproduce the bits of the single-rank 8-leaf tree GEMM at TP = 2 (and 4)."""
+    world = 2 if _ngpu() < 4 else 4
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_tp_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = q.get(timeout=500)
+    for p in procs:
+        p.join(timeout=120)
+    print("fused tp gemm:", res)
+    assert res["fused_ar1_bitwise"] and res["fused_ar2_bitwise"] and res["fused_rs_bitwise"] and res["fused_ag_bitwise"]
+    assert res["status"] == 0
+
+
+def test_fused_tp_kernel_gives_up_when_a_peer_never_arrives():
+    """One GPU plays rank 0 of 2; 'rank 1' is a set of local buffers that nothing writes. The reducer warps'
+    wait for rank 1's tile flags runs out, the kernel frees its TMEM and returns, the status word reports it."""
+    import ctypes as C
+
+    from skyrl_isoexec_b200.ops import _native
+    from skyrl_isoexec_b200.parallel import tp_fused
+
+    lib = _native.lib()
+    lib.ix_init()
+    tp_fused._sig(lib)
+    M, N, K, bn = 16, 256, 256, 32
+    x = torch.randn(M, K, device="cuda").bfloat16()
+    w = torch.randn(N, K, device="cuda").bfloat16()
+    out = torch.zeros(M, N, device="cuda", dtype=torch.bfloat16)
+    nfl = int(lib.ix_tp_stage_floats(M, N, tp_fused.TP_AR1, 2, bn))
+    stage = [torch.zeros(nfl, device="cuda") for _ in range(2)]
+    flags = [torch.zeros(4096, dtype=torch.int32, device="cuda") for _ in range(2)]
+    arr = lambda ts: (C.c_longlong * 2)(*[t.data_ptr() for t in ts])  # noqa: E731
+    assert _native.read_status() == 0
+    _native.check(lib.ix_tp_gemm_fused(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, K, K, N, tp_fused.TP_AR1, 1, bn, 0,
+                                       0, 2, 1, arr(stage), arr(flags), None, None, None, None, 0, 0, _native.stream()), "tp_gemm")
+    torch.cuda.synchronize()
+    assert _native.read_status() == 105
+    assert int(flags[1].view(-1, 2)[: N // bn, 0].min()) == 1        # rank 0 did publish its tiles to the 'peer'
+    y = torch.ones(4, device="cuda")
+    assert float(y.sum()) == 4.0
+
+
+def _ep_worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank), NCCL_NVLS_ENABLE="0")
+    import torch.distributed as dist
+
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from skyrl_isoexec_b200.core.testing import bitwise_equal
+        from skyrl_isoexec_b200.ops import _native, moe
+        from skyrl_isoexec_b200.ops.moe_ep import EPPeer
+
+        _native.lib().ix_init()
+        res = {}
+        E, k, H, Fd, T = 16, 4, 256, 192, 300 + 17 * rank          # ranks hold different numbers of tokens
+        g = torch.Generator(device="cuda").manual_seed(1)
+        gate_up = (torch.randn(E, 2 * Fd, H, device="cuda", generator=g) * 0.06).bfloat16()
+        down = (torch.randn(E, H, Fd, device="cuda", generator=g) * 0.06).bfloat16()
+        e_loc = E // world
+        gu_l, dn_l = gate_up[rank * e_loc:(rank + 1) * e_loc].contiguous(), down[rank * e_loc:(rank + 1) * e_loc].contiguous()
+        rt = EPPeer(dist.group.WORLD, H, E, max_rows_local=400 * k)
+        ok = True
+        with torch.no_grad():
+            for it in range(3):
+                gl = torch.Generator(device="cuda").manual_seed(100 * it + rank)
+                y = torch.randn(T, H, device="cuda", generator=gl).bfloat16()
+                idx = torch.stack([torch.randperm(E, device="cuda", generator=gl)[:k] for _ in range(T)]).int()
+                w = torch.rand(T, k, device="cuda", generator=gl)
+                rows, pos = rt.forward(y, idx, w, gu_l, dn_l)
+                got = moe.combine_fixed_order(rows, pos, torch.bfloat16)
+                order, counts, pos1 = moe.build_dispatch(idx, E)
+                x_rows = y.index_select(0, torch.div(order, k, rounding_mode="floor"))
+                w_rows = w.reshape(-1).index_select(0, order)
+                rows1 = moe.expert_rows_grouped(x_rows, w_rows, moe.counts_to_offsets(counts), gate_up, down)
+                ok &= bool(bitwise_equal(got, moe.combine_fixed_order(rows1, pos1, torch.bfloat16)))
+        res["ep_peer_equals_single_rank_bitwise"] = ok
+        # ---- one Qwen3-30B-A3B-sized layer: 4096 tokens per rank, 128 experts, top-8 (device time, max over ranks)
+        E, k, H, Fd, T = 128, 8, 2048, 768, 4096
+        e_loc = E // world
+        gu = (torch.randn(e_loc, 2 * Fd, H, device="cuda") * 0.03).bfloat16()
+        dn = (torch.randn(e_loc, H, Fd, device="cuda") * 0.03).bfloat16()
+        rt2 = EPPeer(dist.group.WORLD, H, E, max_rows_local=T * k, capacity_rows=T * k * 2)
+        y = torch.randn(T, H, device="cuda").bfloat16()
+        idx = torch.stack([torch.randperm(E, device="cuda")[:k] for _ in range(T)]).int()
+        w = torch.rand(T, k, device="cuda")
+        with torch.no_grad():
+            for _ in range(2):
+                rt2.forward(y, idx, w, gu, dn)
+            torch.cuda.synchronize()
+            dist.barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(5):
+                rows, pos = rt2.forward(y, idx, w, gu, dn)
+                moe.combine_fixed_order(rows, pos, torch.bfloat16)
+            e1.record()
+            torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / 5], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        res["ep_layer_ms_4096tok_per_rank"] = float(t)
+        res["status"] = _native.read_status()
+        if rank == 0:
+            q.put(res)
+    finally:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+@pytest.mark.timeout(600)
+def test_expert_parallel_over_peer_memory_equals_single_rank_bitwise():
+    world = 2 if _ngpu() < 4 else 4
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_ep_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = q.get(timeout=500)
+    for p in procs:
+        p.join(timeout=120)
+    print("expert parallel over peer memory:", res)
+    assert res["ep_peer_equals_single_rank_bitwise"] and res["status"] == 0
