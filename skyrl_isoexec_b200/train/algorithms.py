@@ -92,6 +92,18 @@ class AlgorithmConfig:
     sapo_tau_neg: float = 1.05
     cispo_eps_clip_low: float = 0.0
     cispo_eps_clip_high: float = 5.0
+    dppo_type: str = "binary_tv"           # binary_tv | binary_kl
+    dppo_delta_low: float = 0.2
+    dppo_delta_high: float = 0.2
+    clip_cov_ratio: float = 0.0002
+    clip_cov_lb: float = 1.0
+    clip_cov_ub: float = 5.0
+    clip_cov_seed: int = 0
+    kl_cov_frac: float = 0.2
+    kl_cov_ppo_kl_coef: float = 1.0
+    dynamic_sampling_type: str = ""        # "" | filter | replace
+    dynamic_sampling_max_sample_batches: int = 30
+    dynamic_sampling_min_replace_ratio: float = 0.3
     max_seq_len: int = 0
     off_policy_correction: OffPolicyCorrection = field(default_factory=OffPolicyCorrection)
 
@@ -433,6 +445,92 @@ def cispo_policy_loss(log_probs, old_log_probs, advantages, cfg, loss_mask=None,
     loss = -advantages * ratio.clamp(lo, hi).detach() * log_probs
     metrics = {"clip_ratio": masked_mean(((ratio < lo) | (ratio > hi)).float(), loss_mask).detach()}
     return _finish(loss, old_log_probs, rollout_logprobs, loss_mask, cfg, metrics)
+
+
+@register_policy_loss("rollout_is")
+def rollout_is_policy_loss(log_probs, old_log_probs, advantages, cfg, loss_mask=None, rollout_logprobs=None):
+    """CISPO against the ROLLOUT distribution, with a hard zero outside (1-eps_low, 1+eps_high): usable when
+    the trainer's own old logprobs do not exist (asynchronous training).
+    Reference: B/utils/ppo_utils.py:752-792."""
+    if rollout_logprobs is None:
+        raise ValueError("rollout_is needs the rollout logprobs")
+    ratio = torch.exp(torch.clamp(log_probs - rollout_logprobs, -20.0, 20.0))
+    keep = (ratio > 1 - cfg.eps_clip_low) & (ratio < 1 + cfg.eps_clip_high)
+    coef = torch.where(keep, ratio, torch.zeros_like(ratio)).detach()
+    metrics = {"clip_ratio": masked_mean((~keep).float(), loss_mask).detach()}
+    return _finish(-coef * advantages * log_probs, old_log_probs, rollout_logprobs, loss_mask, cfg, metrics)
+
+
+@register_policy_loss("dppo")
+def dppo_policy_loss(log_probs, old_log_probs, advantages, cfg, loss_mask=None, rollout_logprobs=None):
+    """Divergence-proximal PPO: a token leaves the objective when moving its PROBABILITY further in the
+    direction the advantage asks for would exceed a divergence budget (binary total-variation or binary KL
+    between behaviour and current token probability). Reference: B/utils/ppo_utils.py:794-864."""
+    mu = rollout_logprobs if rollout_logprobs is not None else old_log_probs
+    ratio = torch.exp(torch.clamp(log_probs - mu, -20.0, 20.0))
+    with torch.no_grad():
+        p, q = torch.exp(log_probs), torch.exp(mu)
+        diff = p - q
+        up, down = advantages > 0, advantages < 0
+        if cfg.dppo_type == "binary_tv":
+            drop = (up & (diff > cfg.dppo_delta_high)) | (down & (-diff > cfg.dppo_delta_low))
+        elif cfg.dppo_type == "binary_kl":
+            eps = 1e-8
+            bkl = q * (mu - log_probs) + (1 - q) * torch.log((1 - q + eps) / (1 - p + eps))
+            drop = (up & (diff > 0) & (bkl > cfg.dppo_delta_high)) | (down & (diff < 0) & (bkl > cfg.dppo_delta_low))
+        else:
+            raise ValueError(f"unknown dppo_type {cfg.dppo_type!r} (binary_tv | binary_kl)")
+        keep = (~drop).to(ratio.dtype)
+    metrics = {"clip_ratio": masked_mean(1.0 - keep, loss_mask).detach()}
+    return _finish(-ratio * advantages * keep, old_log_probs, rollout_logprobs, loss_mask, cfg, metrics)
+
+
+def _token_covariance(log_probs, advantages, loss_mask):
+    return (advantages - masked_mean(advantages, loss_mask)) * (log_probs.detach() - masked_mean(log_probs.detach(), loss_mask))
+
+
+@register_policy_loss("clip_cov")
+def clip_cov_policy_loss(log_probs, old_log_probs, advantages, cfg, loss_mask=None, rollout_logprobs=None):
+    """PPO clip plus covariance clipping: among tokens the ratio clip left alone, a random sample (a fixed
+    fraction of the batch) of those whose advantage/logprob covariance lies in [lb, ub] is detached from
+    the objective. The sample is drawn from a generator seeded by ``cfg.clip_cov_seed`` so DP ranks and
+    re-runs agree. Reference: B/utils/ppo_utils.py:866-927."""
+    ratio = torch.exp(log_probs - old_log_probs)
+    l1 = -advantages * ratio
+    l2 = -advantages * ratio.clamp(1 - cfg.eps_clip_low, 1 + cfg.eps_clip_high)
+    valid = loss_mask > 0
+    clipped = (l2 > l1) & valid
+    cov = _token_covariance(log_probs, advantages, loss_mask)
+    cand = valid & ~clipped & (cov > cfg.clip_cov_lb) & (cov < cfg.clip_cov_ub)
+    budget = max(1, int(cfg.clip_cov_ratio * float(loss_mask.sum())))
+    flat = torch.nonzero(cand.reshape(-1)).squeeze(-1)
+    corr = torch.ones_like(advantages).reshape(-1)
+    if flat.numel():
+        g = torch.Generator().manual_seed(int(cfg.clip_cov_seed))
+        pick = flat[torch.randperm(flat.numel(), generator=g)[:budget].to(flat.device)]
+        corr[pick] = 0.0
+    corr = corr.view_as(advantages)
+    metrics = {"clip_ratio": masked_mean((corr == 0).float(), loss_mask).detach()}
+    return (torch.maximum(l1, l2) * corr * loss_mask).sum(), metrics
+
+
+@register_policy_loss("kl_cov")
+def kl_cov_policy_loss(log_probs, old_log_probs, advantages, cfg, loss_mask=None, rollout_logprobs=None):
+    """Unclipped policy gradient, with a |log ratio| penalty on the ``kl_cov_frac`` of tokens whose
+    advantage/logprob covariance is largest. Reference: B/utils/ppo_utils.py:929-982."""
+    delta = log_probs - old_log_probs
+    base = -advantages * torch.exp(delta)
+    valid = loss_mask > 0
+    n = int(valid.sum())
+    if n == 0:
+        return (base * loss_mask).sum(), {"clip_ratio": 0.0}
+    cov = _token_covariance(log_probs, advantages, loss_mask).masked_fill(~valid, float("-inf")).reshape(-1)
+    k = max(1, min(n, int(n * cfg.kl_cov_frac)))
+    top = torch.topk(cov, k, largest=True).indices
+    pen = torch.zeros_like(cov)
+    pen[top] = 1.0
+    loss = base + cfg.kl_cov_ppo_kl_coef * delta.abs() * pen.view_as(base)
+    return (loss * loss_mask).sum(), {"clip_ratio": 0.0}
 
 
 @register_policy_loss("cross_entropy")

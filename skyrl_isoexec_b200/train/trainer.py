@@ -139,6 +139,15 @@ class RayPPOTrainer:
         if not algo.max_seq_len:
             algo.max_seq_len = t.max_prompt_length + g.sampling_params.max_generate_length
         self.policy = PolicyWorker(model, wcfg, algo)
+        self.ref = self.critic = None
+        if algo.use_kl_loss or algo.use_kl_in_reward:
+            from .ref_critic import RefWorker
+
+            self.ref = RefWorker.from_policy(model, wcfg)
+        if algo.advantage_estimator == "gae":
+            from .ref_critic import CriticWorker
+
+            self.critic = CriticWorker(DecoderLM(mcfg, self.ps, self.device, seed=t.policy.seed + 1), wcfg, algo)
         ie = g.inference_engine
         ecfg = EngineConfig(max_num_seqs=ie.max_num_seqs, max_num_batched_tokens=ie.max_num_batched_tokens,
                             num_kv_pages=ie.num_kv_pages, gpu_memory_utilization=ie.gpu_memory_utilization,
@@ -236,6 +245,17 @@ class RayPPOTrainer:
             "policy/rollout_train_logprobs_abs_diff_std": float(std),
             "policy/rollout_train_logprob_bit_mismatches": mism,
         })
+        a = self.cfg.trainer.algorithm
+        if getattr(self, "ref", None) is not None:
+            batch["base_action_log_probs"] = self.ref.forward(batch)
+            if a.use_kl_in_reward:
+                kl = alg.compute_approx_kl(lp, batch["base_action_log_probs"], mask, a.kl_estimator_type) * mask
+                batch["rewards"] = batch["rewards"] - self.kl_ctrl.value * kl
+                cur = float(kl.sum() / n)
+                self.kl_ctrl.update(cur, int(mask.shape[0]))
+                self.all_metrics.update({"reward/kl": cur, "reward/kl_coef": self.kl_ctrl.value})
+        if getattr(self, "critic", None) is not None:
+            batch["values"] = self.critic.forward(batch) * mask
         iso = self.cfg.trainer.isoexec
         if iso.enabled:
             gate = validate_isoexec_forward_gate(diff, mask, mism, iso)
@@ -274,8 +294,15 @@ class RayPPOTrainer:
         n_samples = self.cfg.generator.n_samples_per_prompt
         mb_seqs = (t.policy_mini_batch_size * n_samples) // max(1, self.ps.dp)
         B = batch.batch_size
-        out = {"policy_loss": 0.0, "ppo_clip_ratio": 0.0, "grad_norm": 0.0, "policy_entropy": 0.0}
+        out = {"policy_loss": 0.0, "ppo_clip_ratio": 0.0, "grad_norm": 0.0, "policy_entropy": 0.0, "policy_kl": 0.0}
         n_updates = 0
+        if getattr(self, "critic", None) is not None:
+            closs = 0.0
+            for lo in range(0, B, mb_seqs):
+                cm = self.critic.forward_backward(batch.slice(lo, min(B, lo + mb_seqs)))
+                self.critic.optim_step()
+                closs += cm["critic_loss"]
+            self.all_metrics["critic/critic_loss"] = closs / max(1, (B + mb_seqs - 1) // mb_seqs)
         for _epoch in range(t.update_epochs_per_batch):
             for lo in range(0, B, mb_seqs):
                 mb = batch.slice(lo, min(B, lo + mb_seqs))
@@ -296,6 +323,7 @@ class RayPPOTrainer:
                 out["policy_loss"] += m["policy_loss"]
                 out["ppo_clip_ratio"] += m["ppo_clip_ratio"]
                 out["policy_entropy"] += m["policy_entropy"]
+                out["policy_kl"] += m["policy_kl"]
                 out["grad_norm"] += gn
                 n_updates += 1
         for k in out:
@@ -331,6 +359,20 @@ class RayPPOTrainer:
                 self.engine.wake_up()
             with Timer("generate", T):
                 go = self.generate(gi)
+                a = self.cfg.trainer.algorithm
+                if a.dynamic_sampling_type:
+                    from .trainer_utils import handle_dynamic_sampling
+
+                    state: dict = {}
+                    it = iter(self.loader)
+                    while True:
+                        go2, uids2, more = handle_dynamic_sampling(go, uids, a, state, len(rows), self.cfg.generator.n_samples_per_prompt,
+                                                                   seed=self.cfg.trainer.seed + self.global_step)
+                        if not more:
+                            go, uids = go2, uids2
+                            break
+                        gi, uids = self.prepare_generator_input(next(it))
+                        go = self.generate(gi)
             with Timer("sleep", T):
                 self.engine.sleep()
             with Timer("convert", T):

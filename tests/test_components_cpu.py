@@ -169,3 +169,95 @@ def test_entrypoint_runs_one_step(tmp_path, capsys):
     exp = main_base.BasePPOExp(SkyRLTrainConfig.from_cli_overrides(ov))
     trainer = exp.run()
     assert trainer.global_step == 1
+
+
+# ------------------------------------------------------------------ more policy losses, dynamic sampling, ref / critic
+def test_rollout_is_dppo_clip_cov_kl_cov_losses():
+    from skyrl_isoexec_b200.train import algorithms as alg
+
+    torch.manual_seed(0)
+    cfg = alg.AlgorithmConfig(clip_cov_ratio=0.2, clip_cov_lb=-10.0, clip_cov_ub=10.0)
+    lp = (torch.randn(4, 9) * 0.3 - 1.0).requires_grad_()
+    old = lp.detach() + torch.randn(4, 9) * 0.3
+    adv, mask = torch.randn(4, 9), (torch.rand(4, 9) > 0.2).float()
+    # rollout_is: gradient coefficient is the ratio inside the band and zero outside
+    loss, m = alg.get_policy_loss("rollout_is")(lp, old, adv, cfg, loss_mask=mask, rollout_logprobs=old)
+    (g,) = torch.autograd.grad(loss, lp)
+    ratio = torch.exp(lp.detach() - old)
+    keep = (ratio > 0.8) & (ratio < 1.2)
+    assert torch.allclose(g, -(torch.where(keep, ratio, torch.zeros_like(ratio)) * adv * mask), atol=1e-6)
+    assert 0.0 <= float(m["clip_ratio"]) <= 1.0
+    with pytest.raises(ValueError):
+        alg.get_policy_loss("rollout_is")(lp, old, adv, cfg, loss_mask=mask)
+    # dppo: dropped tokens carry no gradient; both divergence types run
+    for kind in ("binary_tv", "binary_kl"):
+        cfg.dppo_type, cfg.dppo_delta_low, cfg.dppo_delta_high = kind, 0.02, 0.02
+        loss, m = alg.get_policy_loss("dppo")(lp, old, adv, cfg, loss_mask=mask, rollout_logprobs=old)
+        (g,) = torch.autograd.grad(loss, lp)
+        assert float(m["clip_ratio"]) > 0 and int((g == 0).sum()) >= int((mask == 0).sum())
+    # clip_cov: deterministic given the seed; detached tokens have zero gradient
+    l1, m1 = alg.get_policy_loss("clip_cov")(lp, old, adv, cfg, loss_mask=mask)
+    l2, _ = alg.get_policy_loss("clip_cov")(lp, old, adv, cfg, loss_mask=mask)
+    assert torch.equal(l1, l2) and float(m1["clip_ratio"]) > 0
+    # kl_cov: equals the unclipped objective plus the penalty on exactly k tokens
+    cfg.kl_cov_frac, cfg.kl_cov_ppo_kl_coef = 0.25, 2.0
+    lk, _ = alg.get_policy_loss("kl_cov")(lp, old, adv, cfg, loss_mask=mask)
+    base = (-adv * torch.exp(lp - old) * mask).sum()
+    k = max(1, int(int(mask.sum()) * 0.25))
+    extra = float(lk - base) / 2.0
+    topk_sum = None
+    cov = alg._token_covariance(lp, adv, mask).masked_fill(mask == 0, float("-inf")).reshape(-1)
+    topk_sum = float((lp - old).abs().reshape(-1)[torch.topk(cov, k).indices].sum())
+    assert abs(extra - topk_sum) < 1e-4
+
+
+def test_dynamic_sampling_filter_and_replace():
+    from skyrl_isoexec_b200.train import algorithms as alg
+    from skyrl_isoexec_b200.train.trainer_utils import cleanup_old_checkpoints, handle_dynamic_sampling, informative_groups, list_checkpoints
+
+    def batch(tag, rewards):
+        n = len(rewards)
+        return ({"prompt_token_ids": [[1]] * n, "response_ids": [[tag, i] for i in range(n)], "rewards": rewards,
+                 "loss_masks": [[1, 1]] * n, "rollout_logprobs": [[0.0, 0.0]] * n},
+                [f"{tag}{i // 2}" for i in range(n)])
+
+    go, uids = batch("a", [1.0, 0.0, 1.0, 1.0, 0.0, 0.0, 0.5, 0.2])      # groups a0 (mixed) a1 (all 1) a2 (all 0) a3 (mixed)
+    good, bad = informative_groups(go, uids)
+    assert good == ["a0", "a3"] and bad == ["a1", "a2"]
+    cfg = alg.AlgorithmConfig(dynamic_sampling_type="filter", dynamic_sampling_max_sample_batches=3)
+    st: dict = {}
+    out, u, more = handle_dynamic_sampling(go, uids, cfg, st, prompts_needed=3, n_samples=2)
+    assert more and out is None and st["batches"] == 1
+    go2, uids2 = batch("b", [0.0, 1.0, 1.0, 1.0])                          # b0 mixed, b1 flat
+    out, u, more = handle_dynamic_sampling(go2, uids2, cfg, st, prompts_needed=3, n_samples=2)
+    assert not more and u == ["a0", "a0", "a3", "a3", "b0", "b0"] and out["rewards"] == [1.0, 0.0, 0.5, 0.2, 0.0, 1.0]
+    assert st == {}
+    cfg2 = alg.AlgorithmConfig(dynamic_sampling_type="filter", dynamic_sampling_max_sample_batches=1)
+    with pytest.raises(RuntimeError, match="informative"):
+        handle_dynamic_sampling(go2, uids2, cfg2, {}, prompts_needed=5, n_samples=2)
+    cfg3 = alg.AlgorithmConfig(dynamic_sampling_type="replace", dynamic_sampling_min_replace_ratio=0.5)
+    out, u, more = handle_dynamic_sampling(go, uids, cfg3, {}, prompts_needed=4, n_samples=2, seed=1)
+    assert not more and len(u) == 8 and informative_groups(out, u)[1] == []
+    cfg3.dynamic_sampling_min_replace_ratio = 0.9
+    out, u, more = handle_dynamic_sampling(go, uids, cfg3, {}, prompts_needed=4, n_samples=2)
+    assert out is go                                                        # too few informative groups: left alone
+    import os
+    import tempfile
+
+    with tempfile.TemporaryDirectory() as d:
+        for s in (1, 2, 3, 10):
+            os.makedirs(os.path.join(d, f"global_step_{s}"))
+        assert cleanup_old_checkpoints(d, 2) == [1, 2] and list_checkpoints(d) == [3, 10]
+
+
+def test_ppo_with_critic_and_reference_kl_runs(tmp_path):
+    cfg = _rl_cfg(str(tmp_path), 2, "trainer.algorithm.advantage_estimator=gae", "trainer.algorithm.use_kl_loss=true",
+                  "trainer.algorithm.kl_loss_coef=0.01", "trainer.algorithm.lambd=0.95")
+    tr = RayPPOTrainer(cfg, device="cpu")
+    tr.train()
+    assert tr.critic is not None and tr.ref is not None and tr.global_step == 2
+    m = tr.all_metrics
+    assert m["critic/critic_loss"] > 0 and m["policy/rollout_train_logprob_bit_mismatches"] == 0
+    assert m["policy/policy_kl"] >= 0 and m["policy/grad_norm"] > 0
+    # the reference stayed frozen while the policy moved
+    assert not torch.equal(tr.ref.model.store.flat, tr.policy.model.store.flat)
