@@ -36,7 +36,10 @@ constexpr int BK = 64;
 constexpr int kThreads = 320;
 constexpr int kMaxRanks = 16;
 constexpr int kMaxStages = 16;
-constexpr int kPipeBytes = 196 * 1024;
+constexpr int kCopySplit = 4;   // AG: a 128-row block travels as four 32-row pieces, each with its own flag
+constexpr int kSmemLimit = 227 * 1024 - 64;     // dynamic shared memory a CTA may ask for, minus this kernel's static bytes
+constexpr int kFixedBytes = 1024 /*align*/ + 512 /*barriers*/;
+constexpr int kTbufFloatsPerWarp = 32 * 36;   // epilogue transpose buffer: 32 rows x (32 + 4 pad) floats per warp
 
 enum Mode { TP_LOCAL = 0, TP_AR1 = 1, TP_AR2 = 2, TP_RS = 3, TP_AG = 4 };
 
@@ -189,12 +192,12 @@ __device__ __forceinline__ void reduce_tile(const TpParams& p, int slot, int m_b
   constexpr int kVecPerRow = BN / 4;
   const int row_base = (p.mode == TP_RS) ? (m_blk - p.rank * ((M + BM - 1) / BM / W)) * BM : m_blk * BM;
   const int rows_valid = min(BM, M - m_blk * BM);
-  for (int idx = tid; idx < BM * kVecPerRow; idx += 128) {
+#pragma unroll 2
+  for (int idx = tid; idx < rows_valid * kVecPerRow; idx += 128) {
     const int r = idx / kVecPerRow, c4 = idx % kVecPerRow;
-    if (r >= rows_valid) break;
     float4 v[W];
 #pragma unroll
-    for (int s = 0; s < W; ++s) v[s] = reinterpret_cast<const float4*>(base + static_cast<size_t>(s) * (BM * BN))[idx];
+    for (int s = 0; s < W; ++s) v[s] = __ldcs(reinterpret_cast<const float4*>(base + static_cast<size_t>(s) * (BM * BN)) + idx);
     fold_ranks<W>(v);
     const size_t off = static_cast<size_t>(row_base + r) * ldc + n_blk * BN + c4 * 4;
     if (p.mode == TP_AR2) {
@@ -222,8 +225,8 @@ __device__ __forceinline__ void reduce_tile(const TpParams& p, int slot, int m_b
 
 template <int BN, int L>
 __global__ void __launch_bounds__(kThreads, 1)
-tp_gemm_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                     const __grid_constant__ TpParams p, void* __restrict__ c_local, int M, int N, int K, int ldc, int a_rows,
+tp_gemm_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmA2,
+                     const __grid_constant__ CUtensorMap tmB, const __grid_constant__ TpParams p, void* __restrict__ c_local, int M, int N, int K, int ldc, int a_rows,
                      int S, int* __restrict__ status) {
   constexpr int kAccCols = L * BN;
   constexpr int kNumAcc = (2 * kAccCols <= 512) ? 2 : 1;
@@ -233,10 +236,12 @@ tp_gemm_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
   const int stage_bytes = stage_bytes_a + BN * BK * 2;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kPipeBytes + BM * BK * 2);
+  // [S stages][tail: what the last stage's MMA may read beyond a short A box][barriers 512 B][epilogue transpose buffers]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S * stage_bytes + (BM - a_rows) * BK * 2);
   // bars: [0,S) full, [S,2S) empty, [2S,2S+2) tmem_full, [2S+2,2S+4) tmem_empty, [2S+4] tile stored
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * S + 5);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+  float* tbuf_all = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(bars) + 512);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -277,6 +282,7 @@ tp_gemm_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     // ------------------------------------------------------------ TMA producer
     if (elect_one()) {
       tma_prefetch_desc(&tmA);
+      tma_prefetch_desc(&tmA2);
       tma_prefetch_desc(&tmB);
       int stage = 0;
       uint32_t phase = 0;
@@ -284,11 +290,17 @@ tp_gemm_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
       for (int q = blockIdx.x; q < num_q && ok; q += gridDim.x) {
         int m_blk, n_blk, owner, slot;
         if (!tm.decode(q, m_blk, n_blk, owner, slot)) continue;
-        if (p.mode == TP_AG) {
-          // rows of this block were written by rank `owner`'s copier warps (generic proxy, possibly remote)
-          if (!wait_flag(p.flags[p.rank] + owner * tm.nb + slot, p.epoch, abort_flag, status)) break;
+        const bool local_rows = p.mode == TP_AG && owner == p.rank;   // AG: own rows come straight from a_local (tmA2)
+        if (p.mode == TP_AG && !local_rows) {
+          // rows of this block were pushed by rank `owner`'s copier warps (generic proxy, remote) in kCopySplit pieces
+          bool arrived = true;
+          for (int sub = 0; sub < kCopySplit && arrived; ++sub)
+            arrived = wait_flag(p.flags[p.rank] + (owner * tm.nb + slot) * kCopySplit + sub, p.epoch, abort_flag, status);
+          if (!arrived) break;
           fence_proxy_async_global();
         }
+        const CUtensorMap* ta = local_rows ? &tmA2 : &tmA;
+        const int a_row = local_rows ? slot * BM : m_blk * BM;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(smem_u32(&bars[S + stage]), phase ^ 1, abort_flag, status, ST_TIMEOUT_EMPTY)) {
             ok = false;
@@ -297,7 +309,7 @@ tp_gemm_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
           const uint32_t full = smem_u32(&bars[stage]);
           mbar_arrive_expect_tx(full, stage_bytes);
           const uint32_t sa = smem_u32(smem + stage * stage_bytes);
-          tma_load_2d(sa, &tmA, full, kb * BK, m_blk * BM);
+          tma_load_2d(sa, ta, full, kb * BK, a_row);
           tma_load_2d(sa + stage_bytes_a, &tmB, full, kb * BK, n_blk * BN);
           if (++stage == S) {
             stage = 0;
@@ -388,15 +400,30 @@ tp_gemm_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
               }
             }
           }
-        } else if (row < M) {
-          // partial tile -> staging slot (slot*W + rank) at the owner (AR2/RS) or at every rank (AR1)
-          const size_t off = (static_cast<size_t>(slot) * p.W + p.rank) * (BM * BN) + static_cast<size_t>(row_in) * BN + c * CW;
-          const int d0 = (p.mode == TP_AR1) ? 0 : owner, d1 = (p.mode == TP_AR1) ? p.W : owner + 1;
-#pragma unroll 1
-          for (int d = d0; d < d1; ++d) {
-            float* dst = p.stage[d] + off;
+        } else {
+          // partial tile -> staging slot (slot*W + rank) at the owner (AR2/RS) or at every rank (AR1). A lane holds CW
+          // columns of ONE row; through a per-warp shared-memory transpose the warp instead stores whole row segments
+          // (CW*4 contiguous bytes each), which is what NVLink and DRAM want.
+          constexpr int kUnits = CW / 4;            // float4 per row segment
+          constexpr int kRowsPerIt = 32 / kUnits;
+          float* tb = tbuf_all + (warp - 2) * kTbufFloatsPerWarp;
+          __syncwarp();
 #pragma unroll
-            for (int j = 0; j < CW / 4; ++j) reinterpret_cast<float4*>(dst)[j] = make_float4(f[4 * j], f[4 * j + 1], f[4 * j + 2], f[4 * j + 3]);
+          for (int j = 0; j < kUnits; ++j)
+            *reinterpret_cast<float4*>(tb + lane * 36 + 4 * j) = make_float4(f[4 * j], f[4 * j + 1], f[4 * j + 2], f[4 * j + 3]);
+          __syncwarp();
+          const size_t tile_off = (static_cast<size_t>(slot) * p.W + p.rank) * (BM * BN) + c * CW;
+          const int d0 = (p.mode == TP_AR1) ? 0 : owner, d1 = (p.mode == TP_AR1) ? p.W : owner + 1;
+          const int u = lane % kUnits, rs = lane / kUnits;
+#pragma unroll
+          for (int it = 0; it < kUnits; ++it) {
+            const int r = it * kRowsPerIt + rs;     // row within this warp's 32
+            const float4 v = *reinterpret_cast<const float4*>(tb + r * 36 + 4 * u);
+            if (m_blk * BM + quad * 32 + r < M) {
+              const size_t off = tile_off + static_cast<size_t>(quad * 32 + r) * BN + 4 * u;
+#pragma unroll 1
+              for (int d = d0; d < d1; ++d) __stcs(reinterpret_cast<float4*>(p.stage[d] + off), v);   // streaming: keep A/B tiles in L2
+            }
           }
         }
       }
@@ -430,21 +457,33 @@ tp_gemm_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     // ------------------------------------------------------------ warps 6..9: reducer or copier
     const int tid = threadIdx.x - 192;
     if (p.mode == TP_AG) {
-      const int units = tm.nb * p.W;
+      // units of (128-row block, quarter, destination peer); own rows are not copied (the GEMM reads them in place)
+      constexpr int kRows = BM / kCopySplit;
+      const int units = tm.nb * kCopySplit * (p.W - 1);
       const int vec_per_row = K / 8;
+      const int n_vec = kRows * vec_per_row;
       for (int u = blockIdx.x; u < units; u += gridDim.x) {
-        const int d = (p.rank + u / tm.nb) % p.W, b = u % tm.nb;
-        const __nv_bfloat16* src = static_cast<const __nv_bfloat16*>(p.a_local) + static_cast<size_t>(b) * BM * p.lda_local;
-        __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.peer_out[d]) + (static_cast<size_t>(p.rank) * p.m_local + b * BM) * K;
-        for (int idx = tid; idx < BM * vec_per_row; idx += 128) {
-          const int r = idx / vec_per_row, c = idx % vec_per_row;
-          reinterpret_cast<uint4*>(dst + static_cast<size_t>(r) * K)[c] =
-              reinterpret_cast<const uint4*>(src + static_cast<size_t>(r) * p.lda_local)[c];
+        const int d = (p.rank + 1 + u / (tm.nb * kCopySplit)) % p.W;
+        const int b = (u / kCopySplit) % tm.nb, sub = u % kCopySplit;
+        const __nv_bfloat16* src = static_cast<const __nv_bfloat16*>(p.a_local) + (static_cast<size_t>(b) * BM + sub * kRows) * p.lda_local;
+        __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.peer_out[d]) + (static_cast<size_t>(p.rank) * p.m_local + b * BM + sub * kRows) * K;
+        for (int base = tid; base < n_vec; base += 128 * 8) {
+          uint4 v[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {      // eight loads in flight per thread before the first remote store
+            const int idx = base + j * 128;
+            if (idx < n_vec) v[j] = reinterpret_cast<const uint4*>(src + static_cast<size_t>(idx / vec_per_row) * p.lda_local)[idx % vec_per_row];
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int idx = base + j * 128;
+            if (idx < n_vec) reinterpret_cast<uint4*>(dst + static_cast<size_t>(idx / vec_per_row) * K)[idx % vec_per_row] = v[j];
+          }
         }
         named_bar(2, 128);
         if (tid == 0) {
           __threadfence_system();
-          st_release_sys(p.flags[d] + p.rank * tm.nb + b, p.epoch);
+          st_release_sys(p.flags[d] + (p.rank * tm.nb + b) * kCopySplit + sub, p.epoch);
         }
       }
     } else if (p.mode != TP_LOCAL) {
@@ -506,20 +545,23 @@ int sm_count(int dev) {
 }
 
 template <int BN, int L>
-int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const TpParams& p, void* c_local, int M, int N, int K, int ldc,
+int launch(const CUtensorMap& tmA, const CUtensorMap& tmA2, const CUtensorMap& tmB, const TpParams& p, void* c_local, int M, int N, int K, int ldc,
            int a_rows, int num_q, cudaStream_t stream, int dev) {
-  constexpr int kSmem = kPipeBytes + BM * BK * 2 + 1024 + 512;
-  int S = kPipeBytes / (a_rows * BK * 2 + BN * BK * 2);
+  const int stage_bytes = a_rows * BK * 2 + BN * BK * 2;
+  const int tail = (BM - a_rows) * BK * 2;
+  const int tbuf = 4 * kTbufFloatsPerWarp * 4;
+  int S = (kSmemLimit - kFixedBytes - tail - tbuf) / stage_bytes;
   if (S > kMaxStages) S = kMaxStages;
+  const int kSmem = S * stage_bytes + tail + kFixedBytes + tbuf;
   auto kern = tp_gemm_fused_kernel<BN, L>;
   static bool attr_set[64] = {false};
   if (!attr_set[dev & 63]) {
-    IX_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem));
+    IX_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
     attr_set[dev & 63] = true;
   }
   int grid = sm_count(dev);
   if (num_q < grid) grid = num_q;
-  kern<<<grid, kThreads, kSmem, stream>>>(tmA, tmB, p, c_local, M, N, K, ldc, a_rows, S, ixh::status_word(dev));
+  kern<<<grid, kThreads, kSmem, stream>>>(tmA, tmA2, tmB, p, c_local, M, N, K, ldc, a_rows, S, ixh::status_word(dev));
   IX_CUDA(cudaGetLastError());
   return 0;
 }
@@ -567,8 +609,11 @@ IX_API int ix_tp_gemm_fused(const void* A, const void* B, void* c_local, int M, 
   p.rank = rank, p.W = W, p.mode = mode, p.out_f32 = out_f32, p.epoch = epoch;
   int a_rows = (M + 7) & ~7;
   if (a_rows > BM) a_rows = BM;
-  CUtensorMap tmA, tmB;
+  CUtensorMap tmA, tmA2, tmB;
   int rc = ixh::make_tmap_bf16_2d(&tmA, A, M, K, lda, a_rows);
+  if (rc) return rc;
+  if (mode == TP_AG) rc = ixh::make_tmap_bf16_2d(&tmA2, a_local, m_local, K, lda_local, a_rows);
+  else tmA2 = tmA;
   if (rc) return rc;
   rc = ixh::make_tmap_bf16_2d(&tmB, B, N, K, ldb, bn);
   if (rc) return rc;
@@ -576,8 +621,8 @@ IX_API int ix_tp_gemm_fused(const void* A, const void* B, void* c_local, int M, 
   const int num_q = (mode == TP_AR2) ? ((T + W - 1) / W) * W : T;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
 #define IX_TP(BN_, L_) \
-  if (bn == BN_ && leaves == L_) return launch<BN_, L_>(tmA, tmB, p, c_local, M, N, K, ldc, a_rows, num_q, s, dev);
-  IX_TP(128, 1) IX_TP(128, 2) IX_TP(64, 1) IX_TP(64, 2) IX_TP(64, 4) IX_TP(32, 1) IX_TP(32, 2) IX_TP(32, 4) IX_TP(32, 8)
+  if (bn == BN_ && leaves == L_) return launch<BN_, L_>(tmA, tmA2, tmB, p, c_local, M, N, K, ldc, a_rows, num_q, s, dev);
+  IX_TP(256, 1) IX_TP(128, 1) IX_TP(128, 2) IX_TP(64, 1) IX_TP(64, 2) IX_TP(64, 4) IX_TP(32, 1) IX_TP(32, 2) IX_TP(32, 4) IX_TP(32, 8)
 #undef IX_TP
   return ixh::fail(ixh::IX_EARG, "tp_gemm: no kernel for bn=%d leaves=%d (need 2*leaves*bn <= 512)", bn, leaves);
 }

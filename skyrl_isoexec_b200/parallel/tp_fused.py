@@ -40,8 +40,8 @@ def _sig(lib):
 
 
 def pick_bn(M: int, N: int, leaves: int) -> int:
-    """Widest tile allowed by TMEM (2*leaves*bn <= 512 columns, bn <= 128) that still gives most SMs a tile."""
-    bn = min(128, 256 // leaves)
+    """Widest tile allowed by TMEM (2*leaves*bn <= 512 columns) that still gives most SMs a tile."""
+    bn = 256 // leaves
     tiles_m = (M + 127) // 128
     while bn > 32 and (N % bn or tiles_m * (N // bn) * 5 < _SMS * 3):
         bn //= 2

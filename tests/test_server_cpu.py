@@ -1,0 +1,89 @@
+"""HTTP inference server + remote client on CPU (127.0.0.1, ephemeral ports)."""
+import asyncio
+import threading
+import time
+
+import pytest
+import torch
+
+from skyrl_isoexec_b200.engine.llm_engine import EngineConfig, LLMEngine
+from skyrl_isoexec_b200.engine.server import InferenceServer, RemoteInferenceClient, ServerGroup
+from skyrl_isoexec_b200.models.config import get_config
+from skyrl_isoexec_b200.models.decoder import DecoderLM
+
+
+def _engine(seed=0):
+    cfg = get_config("tiny-qwen3")
+    return LLMEngine(DecoderLM(cfg, seed=seed), EngineConfig(max_num_seqs=16, num_kv_pages=32, seed=3))
+
+
+def test_server_data_and_control_plane(tmp_path):
+    e1, e2 = _engine(), _engine()
+    group = ServerGroup([e1, e2])
+    urls = group.start()
+    try:
+        cl = RemoteInferenceClient(urls, max_retries=1, backoff_s=0.01, timeout_s=60)
+        infos = cl.server_info()
+        assert len(infos) == 2 and infos[0]["tp_size"] == 1 and cl.dp_size() == 2
+        g = torch.Generator().manual_seed(0)
+        prompts = [torch.randint(0, 2048, (9,), generator=g).tolist() for _ in range(5)]
+        sp = {"max_generate_length": 7, "ignore_eos": True}
+        out = asyncio.run(cl.generate({"prompt_token_ids": prompts, "sampling_params": sp, "session_ids": list("abcde")}))
+        assert all(len(r) == 7 for r in out["response_ids"]) and all(len(l) == 7 for l in out["response_logprobs"])
+        assert sum(i["requests_served"] for i in cl.server_info()) == 5
+        # the logprobs the server reports are the model's: a clean scoring pass reproduces them bit for bit
+        from skyrl_isoexec_b200.train.batch import TrainingInputBatch, build_sequences
+        from skyrl_isoexec_b200.train.policy_worker import PolicyWorker
+
+        seq, att, rmask = build_sequences(prompts, out["response_ids"])
+        lp = PolicyWorker(e1.model).forward(TrainingInputBatch({"sequences": seq, "attention_mask": att, "response_mask": rmask}))
+        assert torch.equal(lp, torch.tensor(out["response_logprobs"]))
+        # OpenAI-style completion with token-id prompts
+        r = asyncio.run(cl.completion({"prompt": prompts[0], "max_tokens": 4, "n": 2, "logprobs": 1, "ignore_eos": True}))
+        assert len(r["choices"]) == 2 and r["usage"]["completion_tokens"] == 8 and len(r["choices"][0]["logprobs"]["token_logprobs"]) == 4
+        # weights from a file: after the update server 0 computes with the new weights
+        new = DecoderLM(get_config("tiny-qwen3"), seed=9)
+        path = str(tmp_path / "w.pt")
+        torch.save({"model": dict(new.named_weights())}, path)
+        asyncio.run(cl.pause_generation("finish"))
+        asyncio.run(cl.update_named_weights({"path": path}))
+        asyncio.run(cl.resume_generation())
+        assert torch.equal(e1.model.store.flat, new.store.flat)
+        # a dead URL: transient errors are retried, then reported
+        dead = RemoteInferenceClient(["http://127.0.0.1:9"], max_retries=2, backoff_s=0.001, timeout_s=1)
+        with pytest.raises(ConnectionError):
+            dead.server_info()
+        assert dead.retries == 3
+    finally:
+        group.shutdown()
+
+
+def test_pause_abort_ends_running_requests_and_keep_resumes():
+    srv = InferenceServer(_engine()).start()
+    try:
+        cl = RemoteInferenceClient([srv.url], timeout_s=60)
+        res = {}
+
+        def long_call():
+            res["out"] = asyncio.run(cl.generate({"prompt_token_ids": [[1, 2, 3]], "sampling_params": {"max_generate_length": 100000, "ignore_eos": True}}))
+
+        t = threading.Thread(target=long_call)
+        t.start()
+        time.sleep(0.3)
+        asyncio.run(cl.pause_generation("keep"))
+        n1 = len(srv._pending[0].seqs[0].output_ids)
+        time.sleep(0.1)
+        assert len(srv._pending[0].seqs[0].output_ids) == n1 and n1 > 0      # parked, not lost
+        asyncio.run(cl.resume_generation())
+        time.sleep(0.1)
+        r = asyncio.run(cl.pause_generation("abort"))
+        t.join(timeout=20)
+        assert r[0]["aborted"] == 1 and res["out"]["stop_reasons"][0] == "abort"
+        assert len(res["out"]["response_ids"][0]) > n1
+        with pytest.raises(RuntimeError, match="paused"):
+            asyncio.run(cl.generate({"prompt_token_ids": [[1, 2, 3]], "sampling_params": {"max_generate_length": 2}}))
+        asyncio.run(cl.resume_generation())
+        out = asyncio.run(cl.generate({"prompt_token_ids": [[1, 2, 3]], "sampling_params": {"max_generate_length": 2, "ignore_eos": True}}))
+        assert len(out["response_ids"][0]) == 2
+    finally:
+        srv.shutdown()
