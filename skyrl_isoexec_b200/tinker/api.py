@@ -1,0 +1,179 @@
+"""HTTP front end of the Tinker-style API (reference: R/tinker/api.py FastAPI app + SQLModel tables, R/tinker/engine.py).
+
+Every mutating call returns a ``request_id`` at once; the work is queued in a SQLite table (so queued requests
+survive a restart of the front end) and executed in order by one engine thread; ``/api/v1/retrieve_future`` returns
+``{status: pending|completed|failed, result}``.
+
+  POST /api/v1/create_model        {base_model, model_overrides?, lr?}   -> {model_id}
+  POST /api/v1/forward_backward    {model_id, data, loss_fn}
+  POST /api/v1/forward             {model_id, data}
+  POST /api/v1/optim_step          {model_id, adam_params}
+  POST /api/v1/asample             {model_id, prompt_ids, num_samples, sampling_params}
+  POST /api/v1/save_weights | load_weights {model_id, path}
+  POST /api/v1/retrieve_future     {request_id}
+  GET  /api/v1/healthz, /api/v1/get_server_capabilities
+"""
+
+from __future__ import annotations
+
+import json
+import sqlite3
+import threading
+import time
+import uuid
+from http.server import BaseHTTPRequestHandler, ThreadingHTTPServer
+
+from .backend import LOSS_FNS, SkyRLTrainBackend
+
+_ROUTES = {"forward_backward": "forward_backward", "forward": "forward", "optim_step": "optim_step", "asample": "sample",
+           "save_weights": "save_weights", "load_weights": "load_weights"}
+
+
+class TinkerServer:
+    def __init__(self, db_path: str = ":memory:", host: str = "127.0.0.1", port: int = 0, device: str | None = None):
+        self.db = sqlite3.connect(db_path, check_same_thread=False)
+        self.db.execute("create table if not exists futures (id text primary key, seq integer, model_id text, payload text, "
+                        "status text, result text, created real)")
+        self.db.execute("create table if not exists models (id text primary key, spec text)")
+        self._dblock = threading.Lock()
+        self.device = device
+        self.models: dict[str, SkyRLTrainBackend] = {}
+        self._stop = threading.Event()
+        self._wake = threading.Event()
+        self._seq = 0
+        outer = self
+
+        class H(BaseHTTPRequestHandler):
+            def log_message(self, *a):
+                pass
+
+            def _reply(self, code, obj):
+                body = json.dumps(obj).encode()
+                self.send_response(code)
+                self.send_header("Content-Type", "application/json")
+                self.send_header("Content-Length", str(len(body)))
+                self.end_headers()
+                self.wfile.write(body)
+
+            def do_GET(self):
+                if self.path == "/api/v1/healthz":
+                    return self._reply(200, {"status": "ok"})
+                if self.path == "/api/v1/get_server_capabilities":
+                    from ..models.config import PRESETS
+
+                    return self._reply(200, {"supported_models": sorted(PRESETS), "loss_fns": sorted(LOSS_FNS)})
+                self._reply(404, {"error": "no route"})
+
+            def do_POST(self):
+                n = int(self.headers.get("Content-Length") or 0)
+                try:
+                    body = json.loads(self.rfile.read(n) or b"{}")
+                    self._reply(200, outer.post(self.path, body))
+                except KeyError as e:
+                    self._reply(404, {"error": f"unknown {e}"})
+                except Exception as e:  # noqa: BLE001
+                    self._reply(400, {"error": f"{type(e).__name__}: {e}"})
+
+        self.httpd = ThreadingHTTPServer((host, port), H)
+        self.httpd.daemon_threads = True
+        self.url = "http://%s:%d" % self.httpd.server_address[:2]
+        self._threads = [threading.Thread(target=self.httpd.serve_forever, daemon=True), threading.Thread(target=self._loop, daemon=True)]
+
+    def start(self):
+        for t in self._threads:
+            t.start()
+        return self
+
+    def shutdown(self):
+        self._stop.set()
+        self._wake.set()
+        self.httpd.shutdown()
+        self.httpd.server_close()
+
+    # ------------------------------------------------------------------ front end
+    def post(self, path: str, body: dict) -> dict:
+        verb = path.rsplit("/", 1)[-1]
+        if verb == "create_model":
+            mid = "model-" + uuid.uuid4().hex[:10]
+            spec = {"base_model": body.get("base_model", "tiny-qwen3"), "model_overrides": body.get("model_overrides") or {},
+                    "lr": body.get("lr", 1e-5), "seed": body.get("seed", 0)}
+            self.models[mid] = SkyRLTrainBackend(spec["base_model"], spec["model_overrides"], self.device, spec["lr"], spec["seed"])
+            with self._dblock:
+                self.db.execute("insert into models values (?, ?)", (mid, json.dumps(spec)))
+                self.db.commit()
+            return {"model_id": mid}
+        if verb == "retrieve_future":
+            with self._dblock:
+                row = self.db.execute("select status, result from futures where id = ?", (body["request_id"],)).fetchone()
+            if row is None:
+                raise KeyError(body["request_id"])
+            return {"status": row[0], "result": json.loads(row[1]) if row[1] else None}
+        if verb not in _ROUTES:
+            raise KeyError(path)
+        if body.get("model_id") not in self.models:
+            raise KeyError(f"model_id {body.get('model_id')!r}")
+        rid = "req-" + uuid.uuid4().hex[:12]
+        payload = dict(body, type=_ROUTES[verb])
+        with self._dblock:
+            self._seq += 1
+            self.db.execute("insert into futures values (?, ?, ?, ?, 'pending', null, ?)",
+                            (rid, self._seq, body["model_id"], json.dumps(payload), time.time()))
+            self.db.commit()
+        self._wake.set()
+        return {"request_id": rid}
+
+    # ------------------------------------------------------------------ engine loop: strictly in arrival order
+    def _loop(self) -> None:
+        while not self._stop.is_set():
+            with self._dblock:
+                row = self.db.execute("select id, model_id, payload from futures where status = 'pending' order by seq limit 1").fetchone()
+            if row is None:
+                self._wake.wait(0.05)
+                self._wake.clear()
+                continue
+            rid, mid, payload = row
+            try:
+                res, status = self.models[mid].handle(json.loads(payload)), "completed"
+            except Exception as e:  # noqa: BLE001
+                res, status = {"error": f"{type(e).__name__}: {e}"}, "failed"
+            with self._dblock:
+                self.db.execute("update futures set status = ?, result = ? where id = ?", (status, json.dumps(res), rid))
+                self.db.commit()
+
+
+class TinkerClient:
+    """Blocking convenience client (stdlib only)."""
+
+    def __init__(self, url: str, poll_s: float = 0.01, timeout_s: float = 600.0):
+        self.url, self.poll_s, self.timeout_s = url, poll_s, timeout_s
+
+    def _post(self, verb: str, body: dict) -> dict:
+        import urllib.error
+        import urllib.request
+
+        req = urllib.request.Request(f"{self.url}/api/v1/{verb}", data=json.dumps(body).encode(), headers={"Content-Type": "application/json"})
+        try:
+            with urllib.request.urlopen(req, timeout=self.timeout_s) as r:
+                return json.loads(r.read())
+        except urllib.error.HTTPError as e:
+            raise RuntimeError(f"{verb}: HTTP {e.code}: {e.read().decode(errors='replace')[:300]}") from None
+
+    def create_model(self, **kw) -> str:
+        return self._post("create_model", kw)["model_id"]
+
+    def submit(self, verb: str, **body) -> str:
+        return self._post(verb, body)["request_id"]
+
+    def result(self, request_id: str) -> dict:
+        t0 = time.time()
+        while time.time() - t0 < self.timeout_s:
+            r = self._post("retrieve_future", {"request_id": request_id})
+            if r["status"] == "completed":
+                return r["result"]
+            if r["status"] == "failed":
+                raise RuntimeError(r["result"]["error"])
+            time.sleep(self.poll_s)
+        raise TimeoutError(request_id)
+
+    def call(self, verb: str, **body) -> dict:
+        return self.result(self.submit(verb, **body))

@@ -1,0 +1,98 @@
+"""The compute side of the Tinker API: one model (policy worker + colocated engine) driven by typed requests
+(reference: R/backends/skyrl_train_backend.py ``SkyRLTrainBackend``; R/tinker/engine.py request loop).
+
+Requests are plain dicts, processed strictly in arrival order:
+  forward_backward {data: [{prompt_ids, response_ids, advantages?, logprobs?}], loss_fn}  -> per-sequence logprobs, loss
+  forward          {data}                                                                 -> per-sequence logprobs
+  optim_step       {adam_params: {learning_rate}}                                         -> grad norm
+  sample           {prompt_ids, num_samples, sampling_params}                             -> sequences + logprobs
+  save_weights / load_weights {path}
+"""
+
+from __future__ import annotations
+
+import os
+
+import torch
+
+from ..engine.llm_engine import EngineConfig, LLMEngine
+from ..engine.sampler import SamplingParams
+from ..models.config import get_config
+from ..models.decoder import DecoderLM
+from ..train import algorithms as alg
+from ..train.batch import TrainingInputBatch, build_sequences
+from ..train.policy_worker import OptimizerConfig, PolicyWorker, WorkerConfig
+
+LOSS_FNS = {"cross_entropy": "cross_entropy", "importance_sampling": "importance_sampling", "ppo": "regular", "cispo": "cispo"}
+
+
+class SkyRLTrainBackend:
+    def __init__(self, base_model: str = "tiny-qwen3", model_overrides: dict | None = None, device: str | None = None,
+                 lr: float = 1e-5, seed: int = 0, num_kv_pages: int = 64):
+        dev = device or ("cuda" if torch.cuda.is_available() else "cpu")
+        self.cfg = get_config(base_model, **(model_overrides or {}))
+        self.model = DecoderLM(self.cfg, device=dev, seed=seed)
+        self.algo = alg.AlgorithmConfig(policy_loss_type="cross_entropy")
+        self.worker = PolicyWorker(self.model, WorkerConfig(optimizer=OptimizerConfig(lr=lr, num_warmup_steps=0)), self.algo)
+        self.engine = LLMEngine(self.model, EngineConfig(max_num_seqs=64, num_kv_pages=num_kv_pages, seed=seed + 1))
+        self.step_count = 0
+
+    def _batch(self, data: list[dict]) -> TrainingInputBatch:
+        seq, att, rmask = build_sequences([d["prompt_ids"] for d in data], [d["response_ids"] for d in data])
+        B, R = rmask.shape
+        adv, old = torch.zeros(B, R), torch.zeros(B, R)
+        for i, d in enumerate(data):
+            n = len(d["response_ids"])
+            a = d.get("advantages", 1.0)
+            adv[i, :n] = torch.tensor(a, dtype=torch.float32) if isinstance(a, (list, tuple)) else float(a)
+            if d.get("logprobs") is not None:
+                old[i, :n] = torch.tensor(d["logprobs"], dtype=torch.float32)
+        return TrainingInputBatch({"sequences": seq, "attention_mask": att, "response_mask": rmask, "loss_mask": rmask.clone(),
+                                   "advantages": adv, "action_log_probs": old, "rollout_logprobs": old.clone()})
+
+    def handle(self, req: dict) -> dict:
+        kind = req["type"]
+        if kind in ("forward", "forward_backward"):
+            b = self._batch(req["data"])
+            lens = [len(d["response_ids"]) for d in req["data"]]
+            if kind == "forward":
+                lp = self.worker.forward(b)
+                return {"logprobs": [lp[i, :n].tolist() for i, n in enumerate(lens)]}
+            loss_fn = req.get("loss_fn", "cross_entropy")
+            if loss_fn not in LOSS_FNS:
+                raise ValueError(f"loss_fn {loss_fn!r} not in {sorted(LOSS_FNS)}")
+            self.algo.policy_loss_type = LOSS_FNS[loss_fn]
+            if loss_fn == "cross_entropy" or all(d.get("logprobs") is None for d in req["data"]):
+                b.pop("action_log_probs")
+            m = self.worker.forward_backward(b)
+            return {"loss": m["policy_loss"], "num_tokens": m["loss_tokens"], "clip_ratio": m["ppo_clip_ratio"]}
+        if kind == "optim_step":
+            lr = (req.get("adam_params") or {}).get("learning_rate")
+            if lr is not None:
+                self.worker.opt.cfg.lr = float(lr)
+            gn = self.worker.optim_step()
+            self.step_count += 1
+            self.engine.reset_prefix_cache()
+            return {"grad_norm": gn, "step": self.step_count}
+        if kind == "sample":
+            sp = SamplingParams.from_dict(req.get("sampling_params"))
+            n = int(req.get("num_samples", 1))
+            if self.engine.asleep:
+                self.engine.wake_up()
+            outs = self.engine.generate([list(req["prompt_ids"])] * n, sp)
+            return {"sequences": [{"tokens": o.response_ids, "logprobs": o.response_logprobs, "stop_reason": o.stop_reason} for o in outs]}
+        if kind == "save_weights":
+            os.makedirs(os.path.dirname(req["path"]) or ".", exist_ok=True)
+            torch.save({"model": {k: v.detach().cpu() for k, v in self.model.named_weights()}, "step": self.step_count,
+                        "optimizer": self.worker.opt.state_dict()}, req["path"])
+            return {"path": req["path"]}
+        if kind == "load_weights":
+            from ..sync.strategies import load_weights
+
+            sd = torch.load(req["path"], weights_only=False, map_location="cpu")
+            load_weights(self.model, sd["model"].items())
+            if sd.get("optimizer") is not None and req.get("with_optimizer", True):
+                self.worker.opt.load_state_dict(sd["optimizer"])
+            self.step_count = int(sd.get("step", 0))
+            return {"step": self.step_count}
+        raise ValueError(f"unknown request type {kind!r}")

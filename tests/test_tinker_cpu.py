@@ -1,0 +1,45 @@
+"""Tinker-style API end to end on CPU: futures, ordering, a supervised step that lowers the loss, sampling,
+RL-style importance-sampling update, save / load."""
+import pytest
+import torch
+
+from skyrl_isoexec_b200.tinker.api import TinkerClient, TinkerServer
+
+
+def test_tinker_training_loop_over_http(tmp_path):
+    srv = TinkerServer(db_path=str(tmp_path / "q.db"), device="cpu").start()
+    try:
+        cl = TinkerClient(srv.url)
+        mid = cl.create_model(base_model="tiny-qwen3", lr=3e-3)
+        g = torch.Generator().manual_seed(0)
+        data = [{"prompt_ids": torch.randint(0, 500, (5,), generator=g).tolist(),
+                 "response_ids": torch.randint(0, 500, (8,), generator=g).tolist()} for _ in range(4)]
+        # queue several requests before any result is read: they run in order
+        ids = []
+        for _ in range(4):
+            ids.append(cl.submit("forward_backward", model_id=mid, data=data, loss_fn="cross_entropy"))
+            ids.append(cl.submit("optim_step", model_id=mid, adam_params={"learning_rate": 3e-3}))
+        res = [cl.result(i) for i in ids]
+        losses = [r["loss"] for r in res[0::2]]
+        assert [r["step"] for r in res[1::2]] == [1, 2, 3, 4] and losses[-1] < losses[0]
+        assert res[0]["num_tokens"] == 32
+        # sample, then an RL update on the samples with their own logprobs (ratio 1 at the start)
+        s = cl.call("asample", model_id=mid, prompt_ids=data[0]["prompt_ids"], num_samples=3,
+                    sampling_params={"max_generate_length": 6, "ignore_eos": True})
+        assert len(s["sequences"]) == 3 and all(len(x["tokens"]) == 6 and len(x["logprobs"]) == 6 for x in s["sequences"])
+        rl = [{"prompt_ids": data[0]["prompt_ids"], "response_ids": x["tokens"], "logprobs": x["logprobs"], "advantages": a}
+              for x, a in zip(s["sequences"], (1.0, -0.5, 0.25))]
+        fwd = cl.call("forward", model_id=mid, data=rl)
+        assert fwd["logprobs"] == [x["logprobs"] for x in s["sequences"]]            # engine == trainer, bit for bit
+        out = cl.call("forward_backward", model_id=mid, data=rl, loss_fn="importance_sampling")
+        assert abs(out["loss"] - (-(1.0 - 0.5 + 0.25) * 6)) < 1e-4                    # sum of -ratio*A with ratio == 1
+        path = str(tmp_path / "w" / "ckpt.pt")
+        cl.call("save_weights", model_id=mid, path=path)
+        cl.call("optim_step", model_id=mid, adam_params={})
+        assert cl.call("load_weights", model_id=mid, path=path)["step"] == 4
+        with pytest.raises(RuntimeError, match="loss_fn"):
+            cl.call("forward_backward", model_id=mid, data=rl, loss_fn="nope")
+        with pytest.raises(RuntimeError, match="404"):
+            cl.submit("optim_step", model_id="model-missing")
+    finally:
+        srv.shutdown()
