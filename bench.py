@@ -38,6 +38,7 @@ def parse():
     ap.add_argument("--prompt-len", type=int, default=512)
     ap.add_argument("--response-len", type=int, default=2048)
     ap.add_argument("--micro-tokens", type=int, default=8192)
+    ap.add_argument("--keep-last-layers", type=int, default=0, help="layers not recomputed in the backward (uses spare HBM)")
     ap.add_argument("--layers", type=int, default=0, help="debug only: truncate the model (marks the run invalid)")
     return ap.parse_args()
 
@@ -124,7 +125,7 @@ def main():
         f"generator.inference_engine.max_num_seqs={P * S}", "generator.inference_engine.max_num_batched_tokens=8192",
         f"generator.inference_engine.num_kv_pages={P * S * ((args.prompt_len + args.response_len) // 128 + 2)}",
         "trainer.policy.optimizer_config.lr=1e-6", "trainer.logger=console" if os.environ.get("BENCH_VERBOSE") else "trainer.logger=jsonl",
-        "environment.env_class=even_tokens", "trainer.resume_mode=none",
+        "environment.env_class=even_tokens", "trainer.resume_mode=none", f"trainer.policy.keep_last_layers={args.keep_last_layers}",
     ]
     if args.layers:
         ov.append(f'trainer.policy.model_overrides={{"num_layers": {args.layers}}}')
@@ -192,7 +193,7 @@ def main():
                        "l2": "working set (16 GB of weights per pass) exceeds L2; no explicit flush"},
             "clocks": sampler.summary(),
             "e2e": {"value": tokens / (wall_ms / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)},
-            "gpu_launches": int(launches),
+            "gpu_launches": int(launches), "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2**30, 1),
         }
         print(json.dumps(out))
     if world > 1:

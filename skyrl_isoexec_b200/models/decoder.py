@@ -64,8 +64,10 @@ class ParamStore:
 
     def init_weights(self, seed: int, tp_rank: int = 0, tp: int = 1, ep_rank: int = 0, ep: int = 1) -> None:
         """Deterministic init: every parameter is drawn at FULL shape from a generator seeded by
-        (seed, parameter index) and then sliced, so any TP/EP layout holds the same model."""
-        for i, name in enumerate(self.order):
+        (seed, parameter name) and then sliced, so any TP/EP/PP layout holds the same model."""
+        import zlib
+
+        for name in self.order:
             s = self.specs[name]
             v = self.views[name]
             if s.init_std is None:
@@ -74,7 +76,7 @@ class ParamStore:
             if s.init_std == 0.0:
                 v.zero_()
                 continue
-            g = torch.Generator(device="cpu").manual_seed(seed * 1000003 + i)
+            g = torch.Generator(device="cpu").manual_seed(seed * 1000003 + zlib.crc32(name.encode()))
             full = torch.empty(s.full_shape, dtype=torch.float32).normal_(0.0, s.init_std, generator=g)
             v.copy_(shard_of(full, s, tp_rank, tp, ep_rank, ep).to(v.dtype))
 
@@ -262,15 +264,18 @@ class DecoderLM(nn.Module):
         return self._mlp_block(i, y), res
 
     def forward(self, input_ids: torch.Tensor | None, fc: ForwardCtx, hidden_in: tuple | None = None,
-                checkpoint_layers: bool = False):
+                checkpoint_layers: bool | int = False):
         """Returns the final-norm hidden states [T, hidden] on the last pipeline stage, else the
         (x, residual) pair to send to the next stage."""
         if hidden_in is None:
             x, res = self.embed(input_ids), None
         else:
             x, res = hidden_in
+        # checkpoint_layers: True = recompute every layer in the backward; an int n = recompute only the first n
+        # layers of this stage (the last layers' activations are consumed first, so keeping them costs the least time)
+        n_ckpt = len(self.layer_ids) if checkpoint_layers is True else int(checkpoint_layers)
         for kv_idx, i in enumerate(self.layer_ids):
-            if checkpoint_layers and torch.is_grad_enabled():
+            if kv_idx < n_ckpt and torch.is_grad_enabled():
                 x, res = _ckpt(self, i, x, res, fc, kv_idx)
             else:
                 x, res = self.layer(i, x, res, fc, kv_idx)

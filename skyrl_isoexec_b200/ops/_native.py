@@ -30,6 +30,9 @@ _SIGS = {
     "ix_gemm_bf16_nt": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     "ix_rmsnorm": [_P, _P, _P, _P, _P, _P, _I, _I, _F, _I, _L, _L, _P],
     "ix_qk_norm_rope": [_P, _L, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P],
+    "ix_rmsnorm_bwd": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P],
+    "ix_qk_norm_rope_bwd": [_P, _L, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P],
+    "ix_bwd_num_partials": [],
     "ix_swiglu": [_P, _P, _L, _I, _L, _P],
     "ix_swiglu_bwd": [_P, _P, _P, _L, _I, _L, _P],
     "ix_sigmoid_gate": [_P, _P, _L, _P, _L, _I, _I, _I, _P],

@@ -128,6 +128,19 @@ class _RMSNorm(torch.autograd.Function):
     def backward(ctx, dy, dres):
         h, w, rstd = ctx.saved_tensors
         N = h.shape[-1]
+        if _is_cuda(h) and h.dtype == torch.bfloat16 and N % 8 == 0 and N <= 8192:
+            # one pass over the activations (csrc/norm_rope_bwd.cu); weight gradient folded in a fixed order
+            L = _native.lib()
+            rows = h.shape[0]
+            dy2 = dy.reshape(-1, N).contiguous()
+            dr2 = dres.reshape(-1, N).contiguous() if dres is not None else None
+            dh = torch.empty_like(h)
+            part = torch.empty(L.ix_bwd_num_partials(), N, dtype=torch.float32, device=h.device)
+            dw = torch.empty_like(w) if ctx.needs_input_grad[1] else None
+            _native.check(L.ix_rmsnorm_bwd(h.data_ptr(), w.data_ptr(), rstd.data_ptr(), dy2.data_ptr(), _native.ptr(dr2), dh.data_ptr(),
+                                           part.data_ptr(), _native.ptr(dw), rows, N, int(ctx.zero_centered), _native.stream()), "ix_rmsnorm_bwd")
+            dh = dh.reshape(ctx.shp)
+            return dh, dw, (dh if ctx.has_res else None), None, None
         hf = h.float()
         g = w.float()
         if ctx.zero_centered:
@@ -230,6 +243,18 @@ class _QKNormRope(torch.autograd.Function):
         Hq, Hkv, D, eps, qk_norm, zero_centered, q_gate = ctx.cfg
         rope = ctx.rope
         T = qkv.shape[0]
+        if _is_cuda(qkv) and qkv.dtype == torch.bfloat16 and D % 8 == 0 and D <= 256 and rope.rot_dim % 16 == 0 and qkv.stride(1) == 1:
+            L = _native.lib()
+            dqkv = torch.zeros_like(qkv) if q_gate else torch.empty_like(qkv)
+            part = torch.empty(L.ix_bwd_num_partials(), 2, D, dtype=torch.float32, device=qkv.device)
+            dw = torch.empty(2, D, dtype=qw.dtype, device=qkv.device) if qk_norm else None
+            _native.check(L.ix_qk_norm_rope_bwd(qkv.data_ptr(), qkv.stride(0), positions.data_ptr(), rope.cos.data_ptr(), rope.sin.data_ptr(),
+                                                _native.ptr(qw), _native.ptr(kw), dq.contiguous().data_ptr(), dk.contiguous().data_ptr(),
+                                                dv.contiguous().data_ptr(), dqkv.data_ptr(), part.data_ptr(), _native.ptr(dw),
+                                                (dw[1].data_ptr() if dw is not None else None), T, Hq, Hkv, D, rope.rot_dim, eps,
+                                                int(qk_norm), int(zero_centered), int(q_gate), _native.stream()), "ix_qk_norm_rope_bwd")
+            return (dqkv, None, None, (dw[0] if dw is not None else None), (dw[1] if dw is not None else None),
+                    None, None, None, None, None, None, None)
         qs = 2 * D if q_gate else D
         pos = positions.long()
         cos, sin = rope.cos[pos], rope.sin[pos]

@@ -40,6 +40,7 @@ class PolicyConfig:
     optimizer_config: OptimizerConfig = field(default_factory=OptimizerConfig)
     parallel: ParallelConfig = field(default_factory=ParallelConfig)
     seed: int = 0
+    keep_last_layers: int = 0           # layers whose activations are kept instead of recomputed in the backward
 
 
 @dataclass

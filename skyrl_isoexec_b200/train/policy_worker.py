@@ -42,6 +42,7 @@ class WorkerConfig:
     max_tokens_per_microbatch: int = 8192
     logprob_chunk_rows: int = 8192
     checkpoint_layers: bool = True
+    keep_last_layers: int = 0          # do not recompute the last n layers (trades activation memory for one forward of them)
     want_entropy: bool = False
     optimizer: OptimizerConfig = field(default_factory=OptimizerConfig)
 
@@ -201,7 +202,13 @@ class FlatAdamW:
     @staticmethod
     def _make_hook(view):
         def hook(p):
-            view.add_(p.grad)
+            g = p.grad
+            if g.is_cuda and g.dtype == torch.bfloat16 and g.is_contiguous() and g.numel() % 8 == 0:
+                # main_grad += float(grad), vectorised (csrc/loss_optim.cu); torch's mixed-dtype add_ runs at a quarter of the bandwidth
+                _native.check(_native.lib().ix_accum_bf16_to_f32(view.data_ptr(), g.data_ptr(), g.numel(), 1, _native.stream()),
+                              "ix_accum_bf16_to_f32")
+            else:
+                view.add_(g)
             p.grad = None
         return hook
 
@@ -307,6 +314,12 @@ class PolicyWorker:
         self.launch_count = 0
 
     # ---------------------------------------------------------------- forward pieces
+    def _ckpt_arg(self):
+        if not (self.cfg.checkpoint_layers and torch.is_grad_enabled()):
+            return False
+        keep = getattr(self.cfg, "keep_last_layers", 0)
+        return True if keep <= 0 else max(0, len(self.model.layer_ids) - keep)
+
     def _run_model(self, mb: PackedMicroBatch, site: str):
         dev = self.device
         fc = ForwardCtx(positions=mb.positions.to(dev, non_blocking=True),
@@ -316,7 +329,7 @@ class PolicyWorker:
 
             fc.gdn_meta = GDNMeta.packed(mb.seq_lens, dev)
         hidden = self.model(mb.ids.to(dev, non_blocking=True), fc,
-                            checkpoint_layers=self.cfg.checkpoint_layers and torch.is_grad_enabled())
+                            checkpoint_layers=self._ckpt_arg())
         return hidden
 
     def _logprobs(self, mb: PackedMicroBatch, hidden, want_entropy: bool):

@@ -45,6 +45,53 @@ def test_gemm_strided_input_rows():
     assert bitwise_equal(F.gemm_nt(x, w), F.gemm_nt(x.contiguous(), w))
 
 
+@pytest.mark.parametrize("zero_centered,with_res", [(False, True), (True, False)])
+def test_rmsnorm_backward_kernel_matches_fp32_autograd(zero_centered, with_res):
+    torch.manual_seed(2)
+    rows, N = 333, 1024
+    x = torch.randn(rows, N, device=DEV).bfloat16().requires_grad_()
+    res = torch.randn(rows, N, device=DEV).bfloat16().requires_grad_() if with_res else None
+    w = (torch.randn(N, device=DEV) * 0.2 + (0.0 if zero_centered else 1.0)).bfloat16().requires_grad_()
+    gy, gr = torch.randn(rows, N, device=DEV).bfloat16(), torch.randn(rows, N, device=DEV).bfloat16()
+    y, r = F.rmsnorm(x, w, 1e-6, zero_centered, res)
+    loss = (y.float() * gy.float()).sum() + ((r.float() * gr.float()).sum() if with_res else 0.0)
+    dx, dw = torch.autograd.grad(loss, [x, w])
+    # fp32 reference of the same function
+    xf = x.detach().float().requires_grad_()
+    wf = w.detach().float().requires_grad_()
+    h = (xf + res.detach().float()) if with_res else xf
+    n = h * torch.rsqrt(h.pow(2).mean(-1, keepdim=True) + 1e-6)
+    yf = n * ((1.0 + wf) if zero_centered else wf)
+    lf = (yf * gy.float()).sum() + ((h * gr.float()).sum() if with_res else 0.0)
+    dxf, dwf = torch.autograd.grad(lf, [xf, wf])
+    assert (dx.float() - dxf).abs().max() <= 2e-2 * dxf.abs().max()
+    assert (dw.float() - dwf).abs().max() <= 2e-2 * dwf.abs().max()
+    # fixed-order weight-gradient fold: two runs, same bits
+    y2, r2 = F.rmsnorm(x, w, 1e-6, zero_centered, res)
+    loss2 = (y2.float() * gy.float()).sum() + ((r2.float() * gr.float()).sum() if with_res else 0.0)
+    assert bitwise_equal(torch.autograd.grad(loss2, [w])[0], dw)
+
+
+@pytest.mark.parametrize("gate", [False, True])
+def test_qk_norm_rope_backward_kernel_matches_cpu_composite(gate):
+    torch.manual_seed(4)
+    T, Hq, Hkv, D = 77, 8, 2, 128
+    width = (Hq * (2 * D if gate else D)) + 2 * Hkv * D
+    rope = {d: F.RopeTable(D, 256, 1e6, d) for d in ("cpu", DEV)}
+    qkv0 = torch.randn(T, width).bfloat16()
+    qw0, kw0 = (torch.randn(D) * 0.2 + 1).bfloat16(), (torch.randn(D) * 0.2 + 1).bfloat16()
+    pos0 = torch.randint(0, 256, (T,), dtype=torch.int32)
+    gq, gk, gv = torch.randn(T, Hq, D).bfloat16(), torch.randn(T, Hkv, D).bfloat16(), torch.randn(T, Hkv, D).bfloat16()
+    grads = {}
+    for d in ("cpu", DEV):
+        qkv, qw, kw = (t.to(d).requires_grad_() for t in (qkv0, qw0, kw0))
+        q, k, v = F.qk_norm_rope_train(qkv, pos0.to(d), rope[d], qw, kw, Hq, Hkv, D, 1e-6, True, False, gate)
+        loss = (q.float() * gq.to(d).float()).sum() + (k.float() * gk.to(d).float()).sum() + (v.float() * gv.to(d).float()).sum()
+        grads[d] = [g.cpu().float() for g in torch.autograd.grad(loss, [qkv, qw, kw])]
+    for a, b in zip(grads[DEV], grads["cpu"]):
+        assert (a - b).abs().max() <= 2e-2 * b.abs().max() + 1e-3
+
+
 @pytest.mark.parametrize("T,E,k", [(7, 8, 2), (700, 16, 4)])
 def test_grouped_expert_gemm_equals_per_expert_loop_bitwise(T, E, k):
     """One grouped launch (fc1 + SwiGLU + gate weight fused; fc2 with fp32 out, plain and scattered) gives the bits
