@@ -39,7 +39,7 @@ template <int BN, int EPI>
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     void* __restrict__ Cout, const int* __restrict__ offs, const float* __restrict__ w_rows,
-                    const long long* __restrict__ row_dst, int E, int N, int K, int ldc, int rows_b_per_expert,
+                    const long long* __restrict__ row_dst, int R, int E, int N, int K, int ldc, int rows_b_per_expert,
                     int a_rows, int S, int* __restrict__ status) {
   constexpr int kMmaN = (EPI == EPI_GLU) ? 2 * BN : BN;
   constexpr int kTmemCols = (2 * kMmaN < 32) ? 32 : 2 * kMmaN;
@@ -59,7 +59,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   const int tiles_n = N / BN;
   const int num_kb = K / BK;
 
-  for (int e = threadIdx.x; e <= E; e += kThreads) s_row_start[e] = offs[e];
+  // offs == nullptr: one group made of all R rows (the dense MLP uses this kernel for its fused GLU epilogue)
+  for (int e = threadIdx.x; e <= E; e += kThreads) s_row_start[e] = offs ? offs[e] : (e == 0 ? 0 : R);
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     for (int i = 0; i < S; ++i) {
@@ -183,7 +184,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       const bool valid = row < row_end;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * kMmaN;
       float wr = 1.0f;
-      if (EPI == EPI_GLU && valid) wr = w_rows[row];
+      if (EPI == EPI_GLU && valid && w_rows != nullptr) wr = w_rows[row];   // no weights: x 1.0 leaves the bf16 value as it is
       uint8_t* dst_row = nullptr;
       if (valid) {
         if (row_dst != nullptr) dst_row = reinterpret_cast<uint8_t*>(row_dst[row]);
@@ -294,7 +295,7 @@ int launch_grouped(const void* A, const void* B, void* C, const int* offs, const
   }
   int grid = sms_of(dev);
   if (max_tiles > 0 && max_tiles < grid) grid = max_tiles;
-  kern<<<grid, kThreads, kSmem, stream>>>(tmA, tmB, C, offs, w_rows, row_dst, E, N, K, ldc, rows_b, a_rows, S, ixh::status_word(dev));
+  kern<<<grid, kThreads, kSmem, stream>>>(tmA, tmB, C, offs, w_rows, row_dst, R, E, N, K, ldc, rows_b, a_rows, S, ixh::status_word(dev));
   IX_CUDA(cudaGetLastError());
   return 0;
 }
@@ -309,7 +310,7 @@ IX_API int ix_moe_grouped_gemm(const void* A, const void* B, void* C, const void
   if (R <= 0) return 0;
   if (E < 1 || E > kMaxExperts) return ixh::fail(ixh::IX_EARG, "grouped gemm: E=%d unsupported (1..%d)", E, kMaxExperts);
   if ((K % BK) || (lda & 7) || (ldc & 7)) return ixh::fail(ixh::IX_EARG, "grouped gemm: K must be a multiple of 64, lda/ldc of 8");
-  if (epi == EPI_GLU && w_rows == nullptr) return ixh::fail(ixh::IX_EARG, "grouped gemm: the GLU epilogue needs the per-row gate weights");
+  if (offs == nullptr && E != 1) return ixh::fail(ixh::IX_EARG, "grouped gemm: row offsets may only be omitted for a single group");
   int dev = 0;
   IX_CUDA(cudaGetDevice(&dev));
   if (bn == 0) {

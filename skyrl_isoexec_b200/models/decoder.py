@@ -250,8 +250,14 @@ class DecoderLM(nn.Module):
         cfg, pfx = self.cfg, f"layers.{i}."
         if cfg.has_moe:
             return moe_ops.moe_block(y, self, i)
-        gu = F.linear(tp_ops.copy_to_tp(y, self.ps), self.p(pfx + "mlp.gate_up.weight"))
-        return tp_ops.row_parallel_linear(F.swiglu(gu), self.p(pfx + "mlp.down.weight"), self.ps, cfg)
+        wgu = self.p(pfx + "mlp.gate_up.weight")
+        if y.is_cuda and y.dtype == torch.bfloat16 and not torch.is_grad_enabled() and (wgu.shape[0] // 2) % 32 == 0 and y.dim() == 2:
+            # gate_up GEMM with the SwiGLU applied in its epilogue (one launch, no [T, 2F] intermediate). The epilogue
+            # repeats the roundings of the separate kernels, so this and the differentiable path below agree bit for bit.
+            a = moe_ops.grouped_gemm(y, wgu.unsqueeze(0), None, moe_ops.EPI_GLU)
+        else:
+            a = F.swiglu(F.linear(tp_ops.copy_to_tp(y, self.ps), wgu))
+        return tp_ops.row_parallel_linear(a, self.p(pfx + "mlp.down.weight"), self.ps, cfg)
 
     def layer(self, i: int, x: torch.Tensor, res: torch.Tensor | None, fc: ForwardCtx, kv_idx: int):
         cfg = self.cfg

@@ -162,10 +162,10 @@ def grouped_gemm(x_rows: torch.Tensor, w: torch.Tensor, offs: torch.Tensor, epi:
     E = w.shape[0]
     N = w.shape[1] // 2 if epi == EPI_GLU else w.shape[1]
     assert x_rows.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.is_contiguous() and x_rows.stride(1) == 1
-    assert offs.dtype == torch.int32 and offs.numel() == E + 1
+    assert offs is None or (offs.dtype == torch.int32 and offs.numel() == E + 1)
     if out is None and row_dst is None:
         out = torch.empty(R, N, dtype=torch.float32 if epi == EPI_F32 else torch.bfloat16, device=x_rows.device)
-    _native.check(_native.lib().ix_moe_grouped_gemm(x_rows.data_ptr(), w.data_ptr(), _native.ptr(out), offs.data_ptr(),
+    _native.check(_native.lib().ix_moe_grouped_gemm(x_rows.data_ptr(), w.data_ptr(), _native.ptr(out), _native.ptr(offs),
                                                     _native.ptr(w_rows), _native.ptr(row_dst), R, E, N, K, x_rows.stride(0), N,
                                                     epi, bn, _native.stream()), "ix_moe_grouped_gemm")
     return out
