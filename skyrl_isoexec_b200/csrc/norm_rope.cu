@@ -4,8 +4,10 @@
 //
 // Rounding chains (each step is one explicit round-to-nearest op, no FMA contraction):
 //   RMSNorm   h = bf16(x + r)                          (only with a residual input)
-//             ss = sum over the row of fp32(h*h): lane l takes 8-element vectors l, l+32, ...
-//                  in ascending order, then a 5-step xor butterfly (16,8,4,2,1)
+//             ss = sum over the row of fp32(h*h): lane l keeps four chains, chain u over the 8-element
+//                  vectors l+32u, l+32u+128, ... in ascending order, folds them as (c0+c1)+(c2+c3),
+//                  then a 5-step xor butterfly (16,8,4,2,1) over the lanes. The same order is produced
+//                  by the warp-per-row kernel and by the CTA-per-row kernel used for few rows.
 //             rstd = 1 / sqrt(ss / N + eps)            (div.rn, sqrt.rn)
 //             n = bf16(h * rstd);  y = bf16(n * g),  g = w or bf16(1 + w) (zero-centred)
 //   RoPE      a = bf16(y*cos)  b = bf16(rot(y)*sin)  out = bf16(a + b)   (three rounds;
@@ -40,9 +42,9 @@ rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restr
   const BF8* xr = reinterpret_cast<const BF8*>(x + static_cast<size_t>(row) * ldx);
   const BF8* rr = HAS_RES ? reinterpret_cast<const BF8*>(res + static_cast<size_t>(row) * N) : nullptr;
   BF8* ro = HAS_RES ? reinterpret_cast<BF8*>(res_out + static_cast<size_t>(row) * N) : nullptr;
-  float ss = 0.f;
-  // four vectors per lane are loaded before any is consumed (memory-level parallelism); the sum
-  // still visits the lane's vectors in ascending order
+  float c[4] = {0.f, 0.f, 0.f, 0.f};
+  // four vectors per lane are loaded before any is consumed (memory-level parallelism); vector u of a
+  // batch feeds chain u
   for (int v0 = lane; v0 < nvec; v0 += 128) {
     BF8 a[4], b[4];
 #pragma unroll
@@ -65,12 +67,12 @@ rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restr
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           const float f = bf2f(a[u].v[j]);
-          ss = __fadd_rn(ss, __fmul_rn(f, f));
+          c[u] = __fadd_rn(c[u], __fmul_rn(f, f));
         }
       }
     }
   }
-  ss = warp_sum_butterfly(ss);
+  const float ss = warp_sum_butterfly(__fadd_rn(__fadd_rn(c[0], c[1]), __fadd_rn(c[2], c[3])));
   const float rstd = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, static_cast<float>(N)), eps)));
   if (rstd_out && lane == 0) rstd_out[row] = rstd;
   const BF8* hr = HAS_RES ? reinterpret_cast<const BF8*>(res_out + static_cast<size_t>(row) * N) : xr;
@@ -100,6 +102,68 @@ rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restr
         }
         yr[v] = o;
       }
+    }
+  }
+}
+
+// Same function and the same bits, for launches with few rows (decode): one CTA of 128 threads per row, warp u
+// computes chain u of every lane, the row stays in registers between the two phases. N <= 8192.
+template <bool HAS_RES, bool ZERO_CENTERED>
+__global__ void __launch_bounds__(128)
+rmsnorm_cta_row_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
+                       const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
+                       __nv_bfloat16* __restrict__ res_out, float* __restrict__ rstd_out, int N, float eps,
+                       long long ldx, long long ldy) {
+  __shared__ float s_c[4][32];
+  const int row = blockIdx.x;
+  const int u = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nvec = N >> 3;
+  const BF8* xr = reinterpret_cast<const BF8*>(x + static_cast<size_t>(row) * ldx);
+  BF8 a[8], g[8];
+  float c = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {           // vector l + 32u + 128 i: chain u of lane l, ascending
+    const int v = lane + 32 * u + 128 * i;
+    if (v < nvec) {
+      a[i] = xr[v];
+      g[i] = reinterpret_cast<const BF8*>(w)[v];
+      if (HAS_RES) {
+        const BF8 b = reinterpret_cast<const BF8*>(res + static_cast<size_t>(row) * N)[v];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) a[i].v[j] = f2bf(__fadd_rn(bf2f(a[i].v[j]), bf2f(b.v[j])));
+        reinterpret_cast<BF8*>(res_out + static_cast<size_t>(row) * N)[v] = a[i];
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    if (lane + 32 * u + 128 * i < nvec) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float f = bf2f(a[i].v[j]);
+        c = __fadd_rn(c, __fmul_rn(f, f));
+      }
+    }
+  }
+  s_c[u][lane] = c;
+  __syncthreads();
+  const float ss = warp_sum_butterfly(__fadd_rn(__fadd_rn(s_c[0][lane], s_c[1][lane]), __fadd_rn(s_c[2][lane], s_c[3][lane])));
+  const float rstd = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, static_cast<float>(N)), eps)));
+  if (rstd_out && threadIdx.x == 0) rstd_out[row] = rstd;
+  BF8* yr = reinterpret_cast<BF8*>(y + static_cast<size_t>(row) * ldy);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int v = lane + 32 * u + 128 * i;
+    if (v < nvec) {
+      BF8 o;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float n = round_bf(__fmul_rn(bf2f(a[i].v[j]), rstd));
+        float gg = bf2f(g[i].v[j]);
+        if (ZERO_CENTERED) gg = round_bf(__fadd_rn(1.0f, gg));
+        o.v[j] = f2bf(__fmul_rn(n, gg));
+      }
+      yr[v] = o;
     }
   }
 }
@@ -350,6 +414,18 @@ IX_API int ix_rmsnorm(const void* x, const void* res, const void* w, void* y, vo
   auto Y = static_cast<__nv_bfloat16*>(y);
   auto RO = static_cast<__nv_bfloat16*>(res_out);
   auto RS = static_cast<float*>(rstd_out);
+  if (rows <= 1024 && N <= 8192) {
+    // few rows: a CTA per row (more threads per row, one memory round trip); same bits as the warp-per-row kernel
+    if (res) {
+      if (zero_centered) rmsnorm_cta_row_kernel<true, true><<<rows, 128, 0, s>>>(X, R, W, Y, RO, RS, N, eps, ldx, ldy);
+      else rmsnorm_cta_row_kernel<true, false><<<rows, 128, 0, s>>>(X, R, W, Y, RO, RS, N, eps, ldx, ldy);
+    } else {
+      if (zero_centered) rmsnorm_cta_row_kernel<false, true><<<rows, 128, 0, s>>>(X, R, W, Y, RO, RS, N, eps, ldx, ldy);
+      else rmsnorm_cta_row_kernel<false, false><<<rows, 128, 0, s>>>(X, R, W, Y, RO, RS, N, eps, ldx, ldy);
+    }
+    IX_CUDA(cudaGetLastError());
+    return 0;
+  }
   if (res) {
     if (zero_centered) rmsnorm_kernel<true, true><<<grid, 128, 0, s>>>(X, R, W, Y, RO, RS, rows, N, eps, ldx, ldy);
     else rmsnorm_kernel<true, false><<<grid, 128, 0, s>>>(X, R, W, Y, RO, RS, rows, N, eps, ldx, ldy);

@@ -137,13 +137,15 @@ void rmsnorm(const T* x, const T* res, const T* w, T* y, T* res_out, float* rstd
     }
     float lane[32];
     for (int l = 0; l < 32; ++l) {
-      float ss = 0.f;
-      for (int v = l; v < nvec; v += 32)
-        for (int j = 0; j < 8; ++j) {
-          const float f = h[v * 8 + j];
-          ss = ss + f * f;
-        }
-      lane[l] = ss;
+      // four interleaved chains per lane (chain u takes vectors l + 32u, l + 32u + 128, ...), folded as (c0+c1)+(c2+c3)
+      float c[4] = {0.f, 0.f, 0.f, 0.f};
+      for (int u = 0; u < 4; ++u)
+        for (int v = l + 32 * u; v < nvec; v += 128)
+          for (int j = 0; j < 8; ++j) {
+            const float f = h[v * 8 + j];
+            c[u] = c[u] + f * f;
+          }
+      lane[l] = (c[0] + c[1]) + (c[2] + c[3]);
     }
     const float rstd = rstd_of(butterfly32(lane), N, eps);
     if (rstd_out) rstd_out[r] = rstd;

@@ -171,6 +171,9 @@ class LLMEngine:
         self.stats = {"steps": 0, "tokens": 0, "prefill_tokens": 0, "decode_tokens": 0, "preemptions": 0,
                       "h2d_bytes": 0, "d2h_bytes": 0}
         self._graphs: dict = {}
+        self._inflight: dict | None = None        # a decode step launched but not yet read back
+        self._res_host: list = [None, None]       # pinned result buffers, alternating
+        self._res_parity = 0
         if self.device.type == "cuda":
             from ..ops import _native
 
@@ -203,6 +206,7 @@ class LLMEngine:
     # ------------------------------------------------------------------ lifecycle
     def sleep(self, tags: list[str] | None = None) -> None:
         """Release the KV pools (and recurrent state). Weights stay resident."""
+        self._drain_inflight()
         assert not self.scheduler.has_work(), "sleep with requests in flight"
         self._graphs.clear()      # graphs hold the pool addresses; they are re-captured after wake-up
         self.cache.sleep()
@@ -238,18 +242,23 @@ class LLMEngine:
 
     @torch.no_grad()
     def step(self) -> list[Sequence]:
-        """Run one scheduler step; returns the sequences that finished in it."""
+        """Run one scheduler step; returns the sequences that finished in it.
+
+        Graph-replayed decode steps run ONE STEP AHEAD of the host: the step's sampled tokens stay on the device and
+        feed the next replay directly, which is launched before the host reads them back; the host then appends the
+        previous step's tokens while the GPU is already busy. A sequence that turns out to have stopped (EOS) has one
+        surplus token computed, which is dropped. Results therefore come back one call later than they were launched."""
+        if self._inflight is not None:
+            prev = self._inflight
+            nxt = self._launch_ahead(prev) if self._can_run_ahead(prev) else None
+            self._inflight = nxt
+            return self._finalize(prev)
         decode, prefill = self.scheduler.schedule()
         if not decode and not prefill:
             return []
         if not prefill and self._graphs_enabled():
-            logits = self._decode_with_graph(decode)
-            for s in decode:
-                s.num_computed += 1
-            self.stats["steps"] += 1
-            self.stats["tokens"] += len(decode)
-            self.stats["decode_tokens"] += len(decode)
-            return self._sample_and_finish(logits, decode)
+            self._inflight = self._launch_decode(decode, ahead=False)
+            return []
         G = self.model.hq // self.model.hkv
         tq = PAGE // G
         ids, pos, slots, items, bt_rows, sample_rows, sample_seqs = [], [], [], [], [], [], []
@@ -335,7 +344,10 @@ class LLMEngine:
         return (self.cfg.use_cuda_graph and self.device.type == "cuda" and not self.mcfg.has_moe
                 and not self.mcfg.has_gdn and self.model.ps.tp == 1)
 
-    def _decode_with_graph(self, decode: list[Sequence]) -> torch.Tensor:
+    def _launch_decode(self, decode: list[Sequence], ahead: bool) -> dict:
+        """Enqueue (copy, graph replay, sampling, device-side token feedback, D2H of the results) for one decode step
+        and return without waiting. ``ahead``: a token of every sequence is still in flight, so positions are one
+        further than the host's view and the input tokens are already in the graph's id buffer."""
         from .cuda_graph import DecodeGraph
 
         B = len(decode)
@@ -344,19 +356,82 @@ class LLMEngine:
         if g is None:
             g = DecodeGraph(self, B, W)
             self._graphs[B] = g
-        ids, pos, slots, items, bt_rows = [], [], [], [], []
+        off = 1 if ahead else 0
+        pos, slots, items, bt_rows = [], [], [], []
         for i, s in enumerate(decode):
-            p = s.length - 1
-            ids.append(s.last_token)
+            p = s.length - 1 + off
             pos.append(p)
             slots.append(s.pages[p // PAGE] * PAGE + p % PAGE)
             items.append((i, 1, p, p + 1, i, 0, 0, 0))
             bt_rows.append(s.pages)
-        g.fill(ids, pos, slots, items, bt_rows)
+        g.fill(None if ahead else [s.last_token for s in decode], pos, slots, items, bt_rows)
         if g.graph is None:
             g.dev.copy_(g.host)
             g.capture()
-        return g.run()
+        logits = g.run()
+        tokens, lps = self.sampler(logits, [s.params for s in decode])
+        g.ids.copy_(tokens)                       # next replay's input, device to device
+        k = self._res_parity = self._res_parity ^ 1
+        if self._res_host[k] is None or self._res_host[k][0].numel() < B:
+            self._res_host[k] = (torch.zeros(max(B, 64), dtype=torch.int64).pin_memory(), torch.zeros(max(B, 64), dtype=torch.float32).pin_memory())
+        ht, hl = self._res_host[k]
+        ht[:B].copy_(tokens, non_blocking=True)
+        hl[:B].copy_(lps, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self.stats["steps"] += 1
+        self.stats["tokens"] += B
+        self.stats["decode_tokens"] += B
+        self.stats["d2h_bytes"] += B * 12
+        return {"seqs": list(decode), "tokens": ht, "lps": hl, "event": ev, "B": B}
+
+    def _can_run_ahead(self, prev: dict) -> bool:
+        """The next step may be launched before the previous one is read back only if its batch is known now: nothing
+        waits to be admitted, no sequence ends by length with the token in flight, and every sequence has a KV slot for it."""
+        if self.paused or self.scheduler.waiting or not self._graphs_enabled():
+            return False
+        seqs = prev["seqs"]
+        if len(seqs) != len(self.scheduler.running) or any(s.finished for s in seqs):
+            return False
+        for s in seqs:
+            if len(s.output_ids) + 1 >= s.params.max_generate_length or s.length + 1 >= self.max_len:
+                return False
+        for s in seqs:
+            if not self.scheduler._ensure_pages(s, s.length + 1):
+                return False
+        return True
+
+    def _launch_ahead(self, prev: dict) -> dict:
+        return self._launch_decode(prev["seqs"], ahead=True)
+
+    def _finalize(self, rec: dict) -> list[Sequence]:
+        """Wait for a launched step's results and apply them (append token, stop checks, release)."""
+        rec["event"].synchronize()
+        B = rec["B"]
+        tokens, lps = rec["tokens"][:B].tolist(), rec["lps"][:B].tolist()
+        finished: list[Sequence] = []
+        eos = self.cfg.eos_token_id
+        for s, tok, lp in zip(rec["seqs"], tokens, lps):
+            if s.finished:                      # stopped (or was aborted) while this surplus step was in flight
+                continue
+            s.num_computed += 1                 # the step cached the K/V of the token it consumed
+            s.output_ids.append(tok)
+            s.logprobs.append(lp)
+            if (not s.params.ignore_eos and eos is not None and tok == eos) or tok in s.params.stop_token_ids:
+                s.finished, s.stop_reason = True, "stop"
+            elif len(s.output_ids) >= s.params.max_generate_length or s.length >= self.max_len:
+                s.finished, s.stop_reason = True, "length"
+            if s.finished:
+                if self.gdn_state is not None:
+                    self.gdn_state.release(s.seq_id)
+                self.scheduler.finish(s)
+                finished.append(s)
+        return finished
+
+    def _drain_inflight(self) -> None:
+        if self._inflight is not None:
+            rec, self._inflight = self._inflight, None
+            self._finalize(rec)
 
     def generate(self, prompts: list[list[int]], params: SamplingParams | list[SamplingParams]) -> list[RequestOutput]:
         """Blocking batch generation; outputs are in prompt order."""

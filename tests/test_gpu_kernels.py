@@ -45,6 +45,21 @@ def test_gemm_strided_input_rows():
     assert bitwise_equal(F.gemm_nt(x, w), F.gemm_nt(x.contiguous(), w))
 
 
+@pytest.mark.parametrize("N", [4096, 2560, 1000 * 8])
+def test_rmsnorm_few_rows_kernel_equals_many_rows_kernel_bitwise(N):
+    """Decode-sized launches use a CTA per row, large ones a warp per row: one reduction order, same bits."""
+    torch.manual_seed(6)
+    x = torch.randn(1500, N, device=DEV).bfloat16()
+    r = torch.randn(1500, N, device=DEV).bfloat16()
+    w = (torch.randn(N, device=DEV) * 0.1 + 1).bfloat16()
+    y_big, res_big, rstd_big = F.rmsnorm_fwd(x, w, 1e-6, False, r, want_rstd=True)            # 1500 rows: warp per row
+    y_small, res_small, rstd_small = F.rmsnorm_fwd(x[:64].contiguous(), w, 1e-6, False, r[:64].contiguous(), want_rstd=True)
+    assert bitwise_equal(y_small, y_big[:64]) and bitwise_equal(res_small, res_big[:64]) and bitwise_equal(rstd_small, rstd_big[:64])
+    y1, _, _ = F.rmsnorm_fwd(x[:3].contiguous(), w, 1e-6, True)
+    y2, _, _ = F.rmsnorm_fwd(x[:1100].contiguous(), w, 1e-6, True)
+    assert bitwise_equal(y1, y2[:3])
+
+
 @pytest.mark.parametrize("zero_centered,with_res", [(False, True), (True, False)])
 def test_rmsnorm_backward_kernel_matches_fp32_autograd(zero_centered, with_res):
     torch.manual_seed(2)
@@ -358,6 +373,47 @@ def test_engine_and_trainer_logprobs_bitwise_on_gpu_and_step():
         batch["action_log_probs"] = lp
         worker.forward_backward(batch)
         assert worker.optim_step() > 0
+
+
+def test_run_ahead_decode_with_stops_and_mixed_lengths_stays_bitwise():
+    """Graph decode runs one step ahead of the host. Sequences stop at different times (stop tokens, different
+    length limits), so surplus tokens are computed and dropped and the batch keeps changing: what is reported must
+    still be exactly the tokens up to the stop, and their logprobs must equal a clean scoring pass bit for bit."""
+    from skyrl_isoexec_b200.engine.llm_engine import EngineConfig, LLMEngine
+    from skyrl_isoexec_b200.engine.sampler import SamplingParams
+    from skyrl_isoexec_b200.models.config import get_config
+    from skyrl_isoexec_b200.models.decoder import DecoderLM
+    from skyrl_isoexec_b200.train.batch import TrainingInputBatch, build_sequences
+    from skyrl_isoexec_b200.train.policy_worker import PolicyWorker, WorkerConfig
+
+    cfg = get_config("tiny-qwen3-bf16")
+    model = DecoderLM(cfg, device=DEV, seed=3)
+    eng = LLMEngine(model, EngineConfig(max_num_seqs=12, num_kv_pages=64, max_num_batched_tokens=256, seed=5))
+    g = torch.Generator().manual_seed(1)
+    prompts = [torch.randint(0, cfg.vocab_size, (int(n),), generator=g).tolist() for n in torch.randint(5, 120, (12,), generator=g)]
+    stops = tuple(range(0, cfg.vocab_size, 16))                       # one token in 16 ends a sequence
+    params = [SamplingParams(max_generate_length=20 + 9 * i, stop_token_ids=stops if i % 3 else ()) for i in range(12)]
+    outs = eng.generate(prompts, params)
+    assert eng.stats["steps"] > 0 and not eng.scheduler.has_work() and eng._inflight is None
+    assert eng.cache.allocator.num_free == 64
+    n_stop = 0
+    for o, p in zip(outs, params):
+        assert len(o.response_ids) == len(o.response_logprobs) and 1 <= len(o.response_ids) <= p.max_generate_length
+        body = o.response_ids[:-1]
+        assert not any(t in stops for t in body) or not p.stop_token_ids        # nothing after a stop token
+        if o.stop_reason == "stop":
+            assert o.response_ids[-1] in stops
+            n_stop += 1
+        else:
+            assert len(o.response_ids) == p.max_generate_length
+    assert n_stop >= 3
+    seq, att, rmask = build_sequences([o.prompt_ids for o in outs], [o.response_ids for o in outs])
+    lp = PolicyWorker(model, WorkerConfig(max_tokens_per_microbatch=600)).forward(
+        TrainingInputBatch({"sequences": seq, "attention_mask": att, "response_mask": rmask}))
+    ro = torch.zeros_like(lp)
+    for i, o in enumerate(outs):
+        ro[i, :len(o.response_logprobs)] = torch.tensor(o.response_logprobs)
+    assert count_bit_mismatches((lp * rmask).contiguous(), (ro * rmask).contiguous()) == 0
 
 
 def test_router_topk_matches_cpu_oracle_and_tie_rule():
