@@ -28,7 +28,7 @@ constexpr int BM = 128;
 constexpr int BK = 64;
 constexpr int kThreads = 192;
 constexpr int kMaxStages = 12;
-constexpr int kPipeBytes = 192 * 1024;
+constexpr int kSmemLimit = 227 * 1024 - 4352;   // dynamic shared memory budget: the CTA limit minus this kernel's static tables
 constexpr int kMaxExperts = 512;
 
 enum { EPI_BF16 = 0, EPI_F32 = 1, EPI_GLU = 2 };
@@ -48,7 +48,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   const int stage_bytes = stage_bytes_a + kMmaN * BK * 2;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kPipeBytes + BM * BK * 2);
+  // [S stages][tail: what the last stage's MMA may read past a short A box][barriers]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S * stage_bytes + (BM - a_rows) * BK * 2);
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * S + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
   __shared__ int s_tile_start[kMaxExperts + 1];   // first m-tile index of each expert; [E] = total m-tiles
@@ -276,10 +277,12 @@ template <int BN, int EPI>
 int launch_grouped(const void* A, const void* B, void* C, const int* offs, const float* w_rows, const long long* row_dst,
                    int R, int E, int N, int K, int lda, int ldb, int ldc, int max_tiles, cudaStream_t stream, int dev) {
   constexpr int kMmaN = (EPI == EPI_GLU) ? 2 * BN : BN;
-  constexpr int kSmem = kPipeBytes + BM * BK * 2 + 1024 + 512;
+  constexpr int kFixed = 1024 /*align*/ + 512 /*barriers*/;
   int a_rows = (R + 7) & ~7;
   if (a_rows > BM) a_rows = BM;
-  int S = kPipeBytes / (a_rows * BK * 2 + kMmaN * BK * 2);
+  const int stage_bytes = a_rows * BK * 2 + kMmaN * BK * 2;
+  const int tail = (BM - a_rows) * BK * 2;
+  int S = (kSmemLimit - kFixed - tail) / stage_bytes;
   if (S > kMaxStages) S = kMaxStages;
   const int rows_b = (EPI == EPI_GLU) ? 2 * N : N;
   CUtensorMap tmA, tmB;
@@ -290,11 +293,12 @@ int launch_grouped(const void* A, const void* B, void* C, const int* offs, const
   auto kern = grouped_gemm_kernel<BN, EPI>;
   static bool attr_set[64] = {false};
   if (!attr_set[dev & 63]) {
-    IX_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem));
+    IX_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
     attr_set[dev & 63] = true;
   }
   int grid = sms_of(dev);
   if (max_tiles > 0 && max_tiles < grid) grid = max_tiles;
+  const int kSmem = S * stage_bytes + tail + kFixed;
   kern<<<grid, kThreads, kSmem, stream>>>(tmA, tmB, C, offs, w_rows, row_dst, R, E, N, K, ldc, rows_b, a_rows, S, ixh::status_word(dev));
   IX_CUDA(cudaGetLastError());
   return 0;

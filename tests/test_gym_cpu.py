@@ -1,0 +1,57 @@
+"""Text environments and tools (offline: SQLite in memory, local corpus, subprocess python)."""
+from skyrl_isoexec_b200 import gym
+from skyrl_isoexec_b200.gym.envs import aime
+
+
+def test_registered_environments():
+    assert {"aime", "gsm8k", "lcb", "search", "searchcode", "sql", "multiply", "even_tokens"} <= set(gym.registered_envs())
+
+
+def test_aime_scoring():
+    assert aime.compute_score("so the result is \\boxed{042}", "42") == 1.0
+    assert aime.compute_score("... \\boxed{\\frac{1}{2}} then \\boxed{7}.", 7) == 1.0
+    assert aime.compute_score("Answer: 1,234", "1234") == 1.0 and aime.compute_score("no answer", "3") == 0.0
+    env = gym.make("aime", {}, {"reward_spec": {"ground_truth": "113"}})
+    assert env.step("thus \\boxed{113}")["reward"] == 1.0 and env.step("\\boxed{114}")["reward"] == 0.0
+
+
+def test_sql_env_multi_turn():
+    schema = "create table t (id integer, name text, score real); insert into t values (1,'a',2.5),(2,'b',4.0),(3,'c',1.0);"
+    ex = {"reward_spec": {"ground_truth": "select name from t where score > 2 order by name"}, "schema_sql": schema, "max_turns": 3}
+    env = gym.make("sql", {}, ex)
+    o = env.step("let me look <sql>select * from t</sql>")
+    assert not o["done"] and "2.5" in o["observations"][0]["content"]
+    o = env.step("<sql>selec nonsense</sql>")
+    assert not o["done"] and "error" in o["observations"][0]["content"]
+    o = env.step("<solution>select name from t where score >= 2.5</solution>")
+    assert o["done"] and o["reward"] == 1.0
+    env2 = gym.make("sql", {}, ex)
+    assert env2.step("<solution>select name from t</solution>")["reward"] == 0.0
+    env3 = gym.make("sql", {}, dict(ex, max_turns=1))
+    assert env3.step("thinking...")["done"]
+
+
+def test_search_env_and_bm25():
+    corpus = ["The capital of France is Paris.", "Berlin is the capital of Germany.", "Bananas are rich in potassium."]
+    env = gym.make("search", {"topk": 2}, {"reward_spec": {"ground_truth": ["Paris"]}, "corpus": corpus})
+    o = env.step("<search>capital of France</search>")
+    assert not o["done"] and o["observations"][0]["content"].startswith("<observation>Doc 1: The capital of France")
+    assert env.step("<answer>the Paris.</answer>")["reward"] == 1.0
+    env = gym.make("search", {}, {"reward_spec": {"ground_truth": "Paris"}, "corpus": corpus, "max_turns": 2})
+    env.step("<search>zzz</search>")
+    assert env.step("<search>qqq</search>")["done"]
+
+
+def test_code_envs_run_tests_in_a_subprocess():
+    tests = [{"input": "3 4\n", "output": "7"}, {"input": "10 -2\n", "output": "8"}]
+    good = "```python\na, b = map(int, input().split())\nprint(a + b)\n```"
+    bad = "```python\nprint(0)\n```"
+    env = gym.make("lcb", {"timeout_s": 10}, {"reward_spec": {"ground_truth": tests}})
+    assert env.step(good)["reward"] == 1.0 and env.step(bad)["reward"] == 0.0 and env.step("no code")["reward"] == 0.0
+    loop = "```python\nwhile True: pass\n```"
+    assert gym.make("lcb", {"timeout_s": 0.5}, {"reward_spec": {"ground_truth": tests}}).step(loop)["reward"] == 0.0
+    sc = gym.make("searchcode", {}, {"reward_spec": {"ground_truth": "x", "tests": [{"assert": "assert add(2, 3) == 5"}]},
+                                    "corpus": ["def add(a, b): return a + b  # adds two numbers"]})
+    o = sc.step("<search>add two numbers</search>")
+    assert "def add" in o["observations"][0]["content"]
+    assert sc.step("```python\ndef add(a, b):\n    return a + b\n```")["reward"] == 1.0

@@ -359,3 +359,77 @@ def test_expert_parallel_over_peer_memory_equals_single_rank_bitwise():
         p.join(timeout=120)
     print("expert parallel over peer memory:", res)
     assert res["ep_peer_equals_single_rank_bitwise"] and res["status"] == 0
+
+
+def _tp_model_worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank), NCCL_NVLS_ENABLE="0")
+    import torch.distributed as dist
+
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from skyrl_isoexec_b200.core.testing import count_bit_mismatches
+        from skyrl_isoexec_b200.engine.llm_engine import EngineConfig, LLMEngine
+        from skyrl_isoexec_b200.engine.sampler import SamplingParams
+        from skyrl_isoexec_b200.models.config import get_config
+        from skyrl_isoexec_b200.models.decoder import DecoderLM
+        from skyrl_isoexec_b200.ops import _native
+        from skyrl_isoexec_b200.parallel import tp_fused
+        from skyrl_isoexec_b200.parallel.state import ParallelState
+        from skyrl_isoexec_b200.train.batch import TrainingInputBatch, build_sequences
+        from skyrl_isoexec_b200.train.policy_worker import PolicyWorker, WorkerConfig
+
+        _native.lib().ix_init()
+        ps = ParallelState.build(tp=world)
+        tp_fused.register(ps.tp_group, tp_fused.FusedTP(ps.tp_group, stage_bytes=64 << 20, out_bytes=32 << 20, gather_bytes=8 << 20))
+        cfg = get_config("tiny-qwen3-bf16", hidden_size=1024, num_q_heads=8, num_kv_heads=4, head_dim=128, ffn_size=2048,
+                         num_layers=2, tp_invariant=True, pik_leaves=8)
+        model = DecoderLM(cfg, ps, "cuda", seed=2)
+        eng = LLMEngine(model, EngineConfig(max_num_seqs=8, num_kv_pages=48, max_num_batched_tokens=512, seed=9))
+        g = torch.Generator().manual_seed(0)
+        prompts = [torch.randint(0, cfg.vocab_size, (int(n),), generator=g).tolist() for n in (300, 40, 150, 90, 210, 33)]
+        outs = eng.generate(prompts, SamplingParams(max_generate_length=24, ignore_eos=True))
+        seq, att, rmask = build_sequences([o.prompt_ids for o in outs], [o.response_ids for o in outs])
+        batch = TrainingInputBatch({"sequences": seq, "attention_mask": att, "response_mask": rmask, "loss_mask": rmask.clone(),
+                                    "advantages": torch.randn(rmask.shape, generator=g) * 1e-3})
+        worker = PolicyWorker(model, WorkerConfig(max_tokens_per_microbatch=700))
+        lp = worker.forward(batch)
+        ro = torch.zeros_like(lp)
+        for i, o in enumerate(outs):
+            ro[i, :len(o.response_logprobs)] = torch.tensor(o.response_logprobs)
+        res = {"engine_vs_trainer_mismatches_tp": count_bit_mismatches((lp * rmask).contiguous(), (ro * rmask).contiguous())}
+        batch["action_log_probs"] = lp
+        worker.forward_backward(batch)
+        res["grad_norm_tp"] = worker.optim_step()
+        tp_fused.get(ps.tp_group).check()
+        if rank == 0:
+            # the same model on ONE rank (8 leaves in one kernel) scores the same sequences: TP must not change a bit
+            single = DecoderLM(cfg, ParallelState.single(), "cuda", seed=2)
+            w1 = PolicyWorker(single, WorkerConfig(max_tokens_per_microbatch=700))
+            lp1 = w1.forward(batch)
+            res["tp2_vs_tp1_mismatches"] = count_bit_mismatches((lp1 * rmask).contiguous(), (ro * rmask).contiguous())
+            res["status"] = _native.read_status()
+            q.put(res)
+    finally:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+@pytest.mark.timeout(600)
+def test_tensor_parallel_model_with_fused_kernels_is_bitwise_tp_invariant():
+    """Engine and trainer at TP=2, their row-parallel linears running as the fused GEMM->all-reduce kernel:
+    rollout logprobs == trainer logprobs == the logprobs of the same model on a single rank, bit for bit."""
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_tp_model_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = q.get(timeout=500)
+    for p in procs:
+        p.join(timeout=120)
+    print("tp model:", res)
+    assert res["engine_vs_trainer_mismatches_tp"] == 0 and res["tp2_vs_tp1_mismatches"] == 0
+    assert res["grad_norm_tp"] > 0 and res["status"] == 0
