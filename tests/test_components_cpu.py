@@ -261,3 +261,85 @@ def test_ppo_with_critic_and_reference_kl_runs(tmp_path):
     assert m["policy/policy_kl"] >= 0 and m["policy/grad_norm"] > 0
     # the reference stayed frozen while the policy moved
     assert not torch.equal(tr.ref.model.store.flat, tr.policy.model.store.flat)
+
+
+def test_lora_adapter_store_merges_exactly_and_trains():
+    from skyrl_isoexec_b200.models.config import get_config
+    from skyrl_isoexec_b200.models.decoder import DecoderLM
+    from skyrl_isoexec_b200.train import algorithms as alg
+    from skyrl_isoexec_b200.train.batch import TrainingInputBatch, build_sequences
+    from skyrl_isoexec_b200.train.lora import AdapterStore, LoRAAdapter, LoRAConfig, LoRATrainer
+    from skyrl_isoexec_b200.train.policy_worker import PolicyWorker, WorkerConfig
+
+    model = DecoderLM(get_config("tiny-qwen3"), seed=1)
+    base = model.store.flat.clone()
+    store = AdapterStore(model)
+    a1 = LoRAAdapter.init(model, LoRAConfig(rank=4, lr=5e-3, seed=1))
+    a2 = LoRAAdapter.init(model, LoRAConfig(rank=2, seed=2))
+    for b in a2.B.values():
+        b.normal_(0, 0.02)
+    store.register("tenant1", a1)
+    store.register("tenant2", a2)
+    store.activate("tenant2")
+    assert not torch.equal(model.store.flat, base)
+    store.activate("tenant1")                          # B = 0: a fresh adapter is a no-op, and tenant2 is fully removed
+    assert torch.equal(model.store.flat, base)
+    # train tenant1 on a fixed SFT batch; the loss goes down, the base does not move
+    g = torch.Generator().manual_seed(0)
+    ex = [(torch.randint(0, 300, (6,), generator=g).tolist(), torch.randint(0, 300, (9,), generator=g).tolist()) for _ in range(6)]
+    seq, att, rmask = build_sequences([p for p, _ in ex], [r for _, r in ex])
+    batch = TrainingInputBatch({"sequences": seq, "attention_mask": att, "response_mask": rmask, "loss_mask": rmask.clone(),
+                                "advantages": torch.zeros_like(rmask)})
+    worker = PolicyWorker(model, WorkerConfig(), alg.AlgorithmConfig(policy_loss_type="cross_entropy"))
+    tr = LoRATrainer(worker, store, "tenant1")
+    losses = []
+    for _ in range(8):
+        losses.append(worker.forward_backward(batch)["policy_loss"])
+        assert tr.optim_step() > 0
+    assert losses[-1] < losses[0] * 0.97, losses
+    store.deactivate()
+    assert torch.equal(model.store.flat, base)
+    sd = a1.state_dict()
+    a1b = LoRAAdapter.from_state_dict(sd)
+    assert a1b.num_parameters() == a1.num_parameters() and torch.equal(a1b.B["layers.0.attn.o.weight"], a1.B["layers.0.attn.o.weight"].cpu())
+
+
+def test_fusion_ledger_digest_and_checkers():
+    from skyrl_isoexec_b200.core import fusion_ledger as FL
+
+    d = FL.ledger_digest()
+    assert len(d) == 24 and d == FL.ledger_digest()
+    assert FL.ledger_digest(FL.REGIONS[:-1]) != d                       # a different fusion set is a different contract
+    res = FL.run_checkers("cpu")
+    assert res["rmsnorm+residual"] is True and res["logprob_fused"] is True
+    x = FL.hazard_population((64, 64), torch.float32, "cpu")
+    assert (x == 0).any() and (x.abs() > 1e30).any() and (x.abs() < 1e-35).logical_and(x != 0).any()
+
+
+def test_moe_utils_io_and_nccl_capabilities(tmp_path):
+    from skyrl_isoexec_b200.parallel import nccl_runtime
+    from skyrl_isoexec_b200.train.moe_utils import RouterReplay, balanced_dp_assignment, imbalance
+    from skyrl_isoexec_b200.utils import io
+
+    lens = [900, 40, 800, 60, 700, 100, 650, 120]
+    a = balanced_dp_assignment(lens, 2)
+    assert sorted(i for r in a for i in r) == list(range(8)) and len(a[0]) == len(a[1]) == 4
+    assert imbalance(lens, a) < 1.05 < imbalance(lens, [[0, 2, 4, 6], [1, 3, 5, 7]])
+    rr = RouterReplay()
+    rr.mode = "record"
+    idx = torch.tensor([[0, 3], [1, 2], [2, 0]])
+    assert rr.route(5, idx) is idx
+    rr.mode = "replay"
+    other = torch.tensor([[3, 0], [1, 3], [2, 0]])                         # same set in row 0 (order differs), a flip in row 1
+    got = rr.route(5, other)
+    assert torch.equal(got, idx) and rr.flips == 1
+    p = str(tmp_path / "a" / "marker.txt")
+    with io.atomic_write(p) as f:
+        f.write("7")
+    assert io.exists(p) and io.list_dir(str(tmp_path / "a")) == ["marker.txt"] and io.scheme("s3://b/k") == "s3"
+    with pytest.raises(RuntimeError, match="s3"):
+        io.exists("s3://bucket/key")
+    caps = nccl_runtime.capabilities()
+    assert caps["backend"] in ("none", "gloo", "nccl") and "peer_access" in caps
+    with pytest.raises(RuntimeError):
+        nccl_runtime.require({"peer_access": False}, "peer_access")
