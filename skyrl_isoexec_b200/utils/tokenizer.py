@@ -1,0 +1,35 @@
+"""A dependency-free byte-level tokenizer with a chat template, for text environments, the HTTP server and tests when
+no pretrained tokenizer files are available (there is no network here). Ids 0..255 are bytes; specials follow."""
+
+from __future__ import annotations
+
+
+class ByteTokenizer:
+    BOS, EOS, IM_START, IM_END, PAD = 256, 257, 258, 259, 260
+    vocab_size = 261
+
+    def __init__(self):
+        self.eos_token_id, self.pad_token_id, self.bos_token_id = self.EOS, self.PAD, self.BOS
+
+    def encode(self, text: str, add_special_tokens: bool = False) -> list[int]:
+        ids = list(text.encode("utf-8"))
+        return ([self.BOS] + ids) if add_special_tokens else ids
+
+    def decode(self, ids, skip_special_tokens: bool = True) -> str:
+        out = bytearray()
+        names = {self.BOS: "<s>", self.EOS: "</s>", self.IM_START: "<|im_start|>", self.IM_END: "<|im_end|>", self.PAD: ""}
+        for t in ids:
+            t = int(t)
+            if t < 256:
+                out.append(t)
+            elif not skip_special_tokens:
+                out += names.get(t, "").encode()
+        return out.decode("utf-8", errors="replace")
+
+    def apply_chat_template(self, messages: list[dict], add_generation_prompt: bool = True, tokenize: bool = True):
+        ids: list[int] = []
+        for m in messages:
+            ids += [self.IM_START] + self.encode(f"{m['role']}\n{m['content']}") + [self.IM_END] + self.encode("\n")
+        if add_generation_prompt:
+            ids += [self.IM_START] + self.encode("assistant\n")
+        return ids if tokenize else self.decode(ids, skip_special_tokens=False)
