@@ -171,6 +171,8 @@ class LLMEngine:
         self.stats = {"steps": 0, "tokens": 0, "prefill_tokens": 0, "decode_tokens": 0, "preemptions": 0,
                       "h2d_bytes": 0, "d2h_bytes": 0}
         self._graphs: dict = {}
+        self._ep_lockstep = model.ps.ep > 1 and self.mcfg.has_moe
+        self._global_work = False
         self._inflight: dict | None = None        # a decode step launched but not yet read back
         self._res_host: list = [None, None]       # pinned result buffers, alternating
         self._res_parity = 0
@@ -248,6 +250,16 @@ class LLMEngine:
         feed the next replay directly, which is launched before the host reads them back; the host then appends the
         previous step's tokens while the GPU is already busy. A sequence that turns out to have stopped (EOS) has one
         surplus token computed, which is dropped. Results therefore come back one call later than they were launched."""
+        if self._ep_lockstep:
+            # every MoE layer is a collective over the EP group: ranks step together, and a rank with nothing to do
+            # still serves its experts to the others
+            mine = self.scheduler.has_work()
+            self._global_work = self._ep_vote(mine)
+            if not self._global_work:
+                return []
+            if not mine:
+                self.model.ep_idle_forward()
+                return []
         if self._inflight is not None:
             prev = self._inflight
             nxt = self._launch_ahead(prev) if self._can_run_ahead(prev) else None
@@ -428,6 +440,13 @@ class LLMEngine:
                 finished.append(s)
         return finished
 
+    def _ep_vote(self, have: bool) -> bool:
+        import torch.distributed as dist
+
+        t = torch.tensor([1 if have else 0], dtype=torch.int32, device=self.device if self.device.type == "cuda" else "cpu")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.model.ps.ep_group)
+        return bool(int(t))
+
     def _drain_inflight(self) -> None:
         if self._inflight is not None:
             rec, self._inflight = self._inflight, None
@@ -439,9 +458,13 @@ class LLMEngine:
             raise RuntimeError("engine is asleep; call wake_up() first")
         plist = params if isinstance(params, list) else [params] * len(prompts)
         seqs = [self.add_request(p, sp, i) for i, (p, sp) in enumerate(zip(prompts, plist))]
-        while self.scheduler.has_work():
+        while True:
             if self.paused:
                 time.sleep(0.001)
                 continue
+            if not self._ep_lockstep and not self.scheduler.has_work():
+                break
             self.step()
+            if self._ep_lockstep and not self._global_work:
+                break
         return [RequestOutput(s.prompt_ids, s.output_ids, s.logprobs, s.stop_reason or "length") for s in seqs]

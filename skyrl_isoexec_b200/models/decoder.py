@@ -294,6 +294,16 @@ class DecoderLM(nn.Module):
             _trace.record("final_norm", y)
         return y
 
+    @torch.no_grad()
+    def ep_idle_forward(self) -> None:
+        """A step with zero tokens under expert parallelism: take part in every MoE layer's collectives (and run this
+        rank's experts on the rows the other ranks send) without doing anything else."""
+        if not self.cfg.has_moe:
+            return
+        y = torch.empty(0, self.cfg.hidden_size, dtype=self.cfg.torch_dtype, device=self.device_)
+        for i in self.layer_ids:
+            moe_ops.moe_block(y, self, i)
+
     def logits(self, hidden: torch.Tensor, out_f32: bool = False) -> torch.Tensor:
         """Vocabulary logits of the given rows ([rows, V/tp] on this rank)."""
         return F.linear(hidden, self.lm_head_weight(), out_f32)

@@ -31,10 +31,13 @@ class ParallelState:
     pp_group: object = None
     dp_group: object = None
     ep_group: object = None
+    edp_group: object = None      # ranks that hold the SAME expert shard (expert data parallel)
     cp_group: object = None
     tp_ranks: list = field(default_factory=lambda: [0])
     dp_ranks: list = field(default_factory=lambda: [0])
     ep_ranks: list = field(default_factory=lambda: [0])
+    edp_ranks: list = field(default_factory=lambda: [0])
+    edp_rank: int = 0
     pp_ranks: list = field(default_factory=lambda: [0])
     cp_ranks: list = field(default_factory=lambda: [0])
 
@@ -93,6 +96,12 @@ class ParallelState:
                 assert len(s) % ep == 0, f"stage size {len(s)} not divisible by ep={ep}"
                 groups += [s[i:i + ep] for i in range(0, len(s), ep)]
             mk(groups, "ep_group", "ep_ranks", "ep_rank")
+            # ranks with the same position in their EP group hold the same experts: their expert gradients are summed
+            edp = []
+            for p in range(pp):
+                s = stage(p)
+                edp += [[s[i + r] for i in range(0, len(s), ep)] for r in range(ep)]
+            mk(edp, "edp_group", "edp_ranks", "edp_rank")
         return st
 
 

@@ -128,8 +128,9 @@ class PackedMicroBatch:
 
 
 def pack_microbatches(sequences: torch.Tensor, attention_mask: torch.Tensor, num_actions: int,
-                      max_tokens: int) -> list[PackedMicroBatch]:
-    """Remove padding, pack sequences back to back and cut micro-batches by a token budget."""
+                      max_tokens: int, min_groups: int = 0) -> list[PackedMicroBatch]:
+    """Remove padding, pack sequences back to back and cut micro-batches by a token budget. ``min_groups``: produce at
+    least that many micro-batches (ranks that share collectives per layer must run the same number of them)."""
     B, S = sequences.shape
     P = S - num_actions
     att = attention_mask.bool()
@@ -144,6 +145,12 @@ def pack_microbatches(sequences: torch.Tensor, attention_mask: torch.Tensor, num
         cur_tok += lens[b]
     if cur:
         groups.append(cur)
+    while len(groups) < min_groups:
+        big = max(range(len(groups)), key=lambda i: len(groups[i]))
+        if len(groups[big]) < 2:
+            raise ValueError(f"cannot cut {B} sequences into {min_groups} micro-batches; give every rank at least that many sequences")
+        g = groups.pop(big)
+        groups[big:big] = [g[:len(g) // 2], g[len(g) // 2:]]
     out = []
     for grp in groups:
         ids, pos, pred, tgt, oidx, seq_lens = [], [], [], [], [], []
@@ -242,6 +249,16 @@ class FlatAdamW:
             local = self._sq - (rep if ps.tp_rank != 0 else 0)
             dist.all_reduce(local, group=ps.tp_group)
             self._sq = local
+        if ps.ep > 1 and self.model.cfg.has_moe:
+            # expert shards are distinct parameters on every rank of the EP group: add them up; the rest is replicated
+            ex = torch.zeros_like(self._sq)
+            for name in self.model.store.order:
+                s = self.model.store.specs[name]
+                if s.ep_sharded:
+                    ex += self.main_grad[s.offset:s.offset + math.prod(s.shape)].square().sum()
+            tot = ex.clone()
+            dist.all_reduce(tot, group=ps.ep_group)
+            self._sq = self._sq - ex + tot
         return self._sq
 
     def step(self, ps: ParallelState) -> torch.Tensor:
@@ -332,6 +349,17 @@ class PolicyWorker:
                             checkpoint_layers=self._ckpt_arg())
         return hidden
 
+    def _pack(self, seqs, att, R):
+        """Micro-batches of this rank. Under expert parallelism every rank of the EP group runs the same number of them
+        (each MoE layer is a collective), so the count is agreed on first."""
+        mbs = pack_microbatches(seqs, att, R, self.cfg.max_tokens_per_microbatch)
+        if self.ps.ep > 1 and self.model.cfg.has_moe:
+            n = torch.tensor([len(mbs)], dtype=torch.int64, device=self.device if self.device.type == "cuda" else "cpu")
+            dist.all_reduce(n, op=dist.ReduceOp.MAX, group=self.ps.ep_group)
+            if int(n) > len(mbs):
+                mbs = pack_microbatches(seqs, att, R, self.cfg.max_tokens_per_microbatch, min_groups=int(n))
+        return mbs
+
     def _logprobs(self, mb: PackedMicroBatch, hidden, want_entropy: bool):
         dev = self.device
         rows = mb.pred_rows.to(dev, non_blocking=True)
@@ -345,7 +373,7 @@ class PolicyWorker:
         R = batch["response_mask"].shape[1] if batch.get("response_mask") is not None else batch.metadata["response_length"]
         seqs, att = batch["sequences"], batch["attention_mask"]
         out = torch.zeros(seqs.shape[0], R, dtype=torch.float32)
-        for mb in pack_microbatches(seqs, att, R, self.cfg.max_tokens_per_microbatch):
+        for mb in self._pack(seqs, att, R):
             hidden = self._run_model(mb, "trainer_score")
             lp, _ = self._logprobs(mb, hidden, False)
             flat = torch.zeros(len(mb.seq_index) * R, dtype=torch.float32, device=lp.device)
@@ -363,7 +391,7 @@ class PolicyWorker:
         want_ent = self.cfg.want_entropy or algo.use_entropy_loss
         tot = {"loss": 0.0, "clip_ratio_num": 0.0, "tokens": 0.0, "entropy_sum": 0.0, "kl_sum": 0.0}
         dev = self.device
-        for mb in pack_microbatches(seqs, att, R, self.cfg.max_tokens_per_microbatch):
+        for mb in self._pack(seqs, att, R):
             idx = torch.tensor(mb.seq_index)
             hidden = self._run_model(mb, "trainer_fwd")
             lp_flat, ent_flat = self._logprobs(mb, hidden, want_ent)
@@ -410,9 +438,15 @@ class PolicyWorker:
                 if s.tp_grad_sum:
                     dist.all_reduce(self.opt.main_grad[s.offset:s.offset + math.prod(s.shape)], group=self.ps.tp_group)
         if self.ps.dp > 1:
-            from ..parallel.dp import reduce_main_grads
+            from ..parallel.dp import reduce_main_grads, split_ranges_by_expert_sharding
 
-            reduce_main_grads(self.opt.main_grad, self.ps)
+            if self.ps.ep > 1 and self.model.cfg.has_moe:
+                # expert shards differ from rank to rank inside an EP group: only ranks holding the same shard sum them
+                dense, expert = split_ranges_by_expert_sharding(self.model.store)
+                reduce_main_grads(self.opt.main_grad, self.ps, ranges=dense)
+                reduce_main_grads(self.opt.main_grad, self.ps, ranges=expert, group=self.ps.edp_group)
+            else:
+                reduce_main_grads(self.opt.main_grad, self.ps)
 
     def optim_step(self) -> float:
         self.reduce_gradients()
