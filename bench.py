@@ -38,6 +38,7 @@ def parse():
     ap.add_argument("--prompt-len", type=int, default=512)
     ap.add_argument("--response-len", type=int, default=2048)
     ap.add_argument("--micro-tokens", type=int, default=8192)
+    ap.add_argument("--tp", type=int, default=1, help="tensor-parallel degree of trainer and engine (fused GEMM+collective kernels)")
     ap.add_argument("--keep-last-layers", type=int, default=0, help="layers not recomputed in the backward (uses spare HBM)")
     ap.add_argument("--layers", type=int, default=0, help="debug only: truncate the model (marks the run invalid)")
     return ap.parse_args()
@@ -109,26 +110,33 @@ def main():
     assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}"
     torch.cuda.set_device(local)
     _native.lib().ix_init()
-    ps = ParallelState.build(tp=1) if world > 1 else ParallelState.single()
+    ps = ParallelState.build(tp=args.tp) if world > 1 else ParallelState.single()
     if world > 1:
-        # data-parallel gradient reduction runs on the peer-memory kernels (csrc/peer_collectives.cu)
-        from skyrl_isoexec_b200.parallel.symm_runtime import SymmGroup
+        # peer-memory transports: DP gradient sum (csrc/peer_collectives.cu), fused TP GEMMs (csrc/tp_gemm_fused.cu)
+        from skyrl_isoexec_b200.models.config import get_config
+        from skyrl_isoexec_b200.parallel.transports import setup_transports
 
-        SymmGroup(ps.dp_group, staging_bytes=512 << 20)
-    P, S = args.prompts_per_gpu, args.samples
+        setup_transports(ps, get_config(args.model, tp_invariant=args.tp > 1) if args.tp > 1 else None, max_tokens=args.micro_tokens)
+    P, S = args.prompts_per_gpu * args.tp, args.samples
     ov = [
-        f"trainer.policy.model={args.model}", f"trainer.train_batch_size={P * world}",
-        f"trainer.policy_mini_batch_size={P * world}", f"generator.n_samples_per_prompt={S}",
+        f"trainer.policy.model={args.model}", f"trainer.train_batch_size={P * ps.dp}",
+        f"trainer.policy_mini_batch_size={P * ps.dp}", f"generator.n_samples_per_prompt={S}",
         f"generator.sampling_params.max_generate_length={args.response_len}", "generator.sampling_params.ignore_eos=true",
-        f"data.synthetic_prompt_len={args.prompt_len}", f"data.synthetic_prompts={P * world * (args.steps + args.warmup + 1)}",
+        f"data.synthetic_prompt_len={args.prompt_len}", f"data.synthetic_prompts={P * ps.dp * (args.steps + args.warmup + 1)}",
         f"trainer.max_prompt_length={args.prompt_len}", f"trainer.max_tokens_per_microbatch={args.micro_tokens}",
         f"generator.inference_engine.max_num_seqs={P * S}", "generator.inference_engine.max_num_batched_tokens=8192",
         f"generator.inference_engine.num_kv_pages={P * S * ((args.prompt_len + args.response_len) // 128 + 2)}",
         "trainer.policy.optimizer_config.lr=1e-6", "trainer.logger=console" if os.environ.get("BENCH_VERBOSE") else "trainer.logger=jsonl",
         "environment.env_class=even_tokens", "trainer.resume_mode=none", f"trainer.policy.keep_last_layers={args.keep_last_layers}",
     ]
+    mo = {}
     if args.layers:
-        ov.append(f'trainer.policy.model_overrides={{"num_layers": {args.layers}}}')
+        mo["num_layers"] = args.layers
+    if args.tp > 1:
+        mo["tp_invariant"] = True
+        ov.append(f"generator.inference_engine.tensor_parallel_size={args.tp}")
+    if mo:
+        ov.append("trainer.policy.model_overrides=" + json.dumps(mo))
     cfg = SkyRLTrainConfig.from_cli_overrides(ov)
     trainer = RayPPOTrainer(cfg, ps=ps, device=f"cuda:{local}")
     trainer.build_models()
@@ -171,7 +179,7 @@ def main():
         sm = stats.clone()
         dist.all_reduce(sm, op=dist.ReduceOp.SUM)
         dev_ms, wall_ms, gen_s = float(mx[0]), float(mx[1]), float(mx[4])
-        tokens, mism = float(sm[2]), float(sm[3])
+        tokens, mism = float(sm[2]) / args.tp, float(sm[3]) / args.tp   # every rank of a TP group reports the same sequences
     else:
         wall_ms = wall * 1e3
     status = _native.read_status()
@@ -187,9 +195,10 @@ def main():
             "grpo_steps_per_s": args.steps / (dev_ms / 1e3), "rollout_tok_per_s": tokens / max(1e-9, gen_s),
             "logprob_mismatches": int(mism), "kernel_status": status,
             "config": {"model": args.model + (f"[layers={args.layers} INVALID-DEBUG]" if args.layers else ""),
-                       "global_batch": P * S * world, "prompts": P * world, "samples_per_prompt": S,
+                       "global_batch": P * S * ps.dp, "prompts": P * ps.dp, "samples_per_prompt": S,
                        "prompt_len": args.prompt_len, "seq_len": args.prompt_len + args.response_len,
-                       "parallelism": f"dp{world}" if world > 1 else "single", "engine": "colocated, 1 engine per GPU, TP1",
+                       "parallelism": (f"dp{ps.dp}" + (f"xtp{args.tp}" if args.tp > 1 else "")) if world > 1 else "single",
+                       "engine": f"colocated, 1 engine per TP group, TP{args.tp}",
                        "l2": "working set (16 GB of weights per pass) exceeds L2; no explicit flush"},
             "clocks": sampler.summary(),
             "e2e": {"value": tokens / (wall_ms / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)},

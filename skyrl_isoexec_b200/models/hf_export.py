@@ -1,0 +1,137 @@
+"""Export to / import from the Hugging Face checkpoint layout (``config.json`` + ``model.safetensors``), the
+format ``trainer.export_path`` / ``hf_save_interval`` write (reference: B/workers/.../save_hf_model paths and the
+Megatron<->HF bridges in B/workers/megatron/model_bridges.py).
+
+Internally QKV and gate/up are fused and QKV rows are stored KV-group major; the export un-fuses them into
+``q_proj / k_proj / v_proj`` and ``gate_proj / up_proj`` with the usual Qwen3 names, and the import does the reverse.
+Only full (unsharded) models are handled here; sharded runs gather through ``sync.strategies.gather_full`` first.
+"""
+
+from __future__ import annotations
+
+import json
+import os
+
+import torch
+
+from .config import ModelConfig
+from .decoder import DecoderLM
+
+
+def _split_qkv(w: torch.Tensor, cfg: ModelConfig):
+    """[G-major fused rows, h] -> (q [Hq*D, h], k [Hkv*D, h], v [Hkv*D, h]) in head order."""
+    Hq, Hkv, D = cfg.num_q_heads, cfg.num_kv_heads, cfg.head_dim
+    G = Hq // Hkv
+    qs = 2 * D if cfg.attn_output_gate else D
+    grp = w.view(Hkv, G * qs + 2 * D, -1)
+    q = grp[:, :G * qs].reshape(Hkv * G, qs, -1)
+    k = grp[:, G * qs:G * qs + D].reshape(Hkv * D, -1)
+    v = grp[:, G * qs + D:].reshape(Hkv * D, -1)
+    return q.reshape(Hq * qs, -1), k, v
+
+
+def _fuse_qkv(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cfg: ModelConfig) -> torch.Tensor:
+    Hq, Hkv, D = cfg.num_q_heads, cfg.num_kv_heads, cfg.head_dim
+    G = Hq // Hkv
+    qs = 2 * D if cfg.attn_output_gate else D
+    h = q.shape[-1]
+    return torch.cat([q.view(Hkv, G * qs, h), k.view(Hkv, D, h), v.view(Hkv, D, h)], 1).reshape(-1, h)
+
+
+def to_hf_state_dict(model: DecoderLM) -> dict[str, torch.Tensor]:
+    cfg = model.cfg
+    assert model.ps.tp == 1 and model.ps.ep == 1 and model.ps.pp == 1, "gather the shards before exporting"
+    out: dict[str, torch.Tensor] = {}
+    for name, t in model.named_weights():
+        t = t.detach().cpu().contiguous()
+        if name == "embed.weight":
+            out["model.embed_tokens.weight"] = t
+        elif name == "lm_head.weight":
+            out["lm_head.weight"] = t
+        elif name == "final_norm.weight":
+            out["model.norm.weight"] = t
+        else:
+            _, i, rest = name.split(".", 2)
+            p = f"model.layers.{i}."
+            if rest == "attn.qkv.weight":
+                q, k, v = _split_qkv(t, cfg)
+                out[p + "self_attn.q_proj.weight"], out[p + "self_attn.k_proj.weight"], out[p + "self_attn.v_proj.weight"] = \
+                    q.contiguous(), k.contiguous(), v.contiguous()
+            elif rest == "mlp.gate_up.weight":
+                f = t.shape[0] // 2
+                out[p + "mlp.gate_proj.weight"], out[p + "mlp.up_proj.weight"] = t[:f].contiguous(), t[f:].contiguous()
+            elif rest == "moe.experts.gate_up":
+                f = t.shape[1] // 2
+                for e in range(t.shape[0]):
+                    out[p + f"mlp.experts.{e}.gate_proj.weight"] = t[e, :f].contiguous()
+                    out[p + f"mlp.experts.{e}.up_proj.weight"] = t[e, f:].contiguous()
+            elif rest == "moe.experts.down":
+                for e in range(t.shape[0]):
+                    out[p + f"mlp.experts.{e}.down_proj.weight"] = t[e].contiguous()
+            else:
+                ren = {"ln1.weight": "input_layernorm.weight", "ln2.weight": "post_attention_layernorm.weight",
+                       "attn.o.weight": "self_attn.o_proj.weight", "attn.q_norm.weight": "self_attn.q_norm.weight",
+                       "attn.k_norm.weight": "self_attn.k_norm.weight", "mlp.down.weight": "mlp.down_proj.weight",
+                       "moe.router.weight": "mlp.gate.weight"}
+                out[p + ren.get(rest, rest)] = t
+    return out
+
+
+def hf_config(cfg: ModelConfig) -> dict:
+    arch = "Qwen3MoeForCausalLM" if cfg.has_moe else ("Qwen3NextForCausalLM" if cfg.has_gdn else "Qwen3ForCausalLM")
+    d = {"architectures": [arch], "hidden_size": cfg.hidden_size, "num_hidden_layers": cfg.num_layers,
+         "num_attention_heads": cfg.num_q_heads, "num_key_value_heads": cfg.num_kv_heads, "head_dim": cfg.head_dim,
+         "intermediate_size": cfg.ffn_size, "vocab_size": cfg.vocab_size, "rope_theta": cfg.rope_theta, "rms_norm_eps": cfg.rms_eps,
+         "tie_word_embeddings": cfg.tie_embeddings, "max_position_embeddings": cfg.max_position, "torch_dtype": cfg.dtype,
+         "hidden_act": "silu"}
+    if cfg.has_moe:
+        d.update({"num_experts": cfg.num_experts, "num_experts_per_tok": cfg.top_k, "moe_intermediate_size": cfg.moe_ffn_size,
+                  "norm_topk_prob": cfg.norm_topk_prob})
+    return d
+
+
+def save_hf(model: DecoderLM, path: str) -> None:
+    from safetensors.torch import save_file
+
+    os.makedirs(path, exist_ok=True)
+    save_file(to_hf_state_dict(model), os.path.join(path, "model.safetensors"), metadata={"format": "pt"})
+    with open(os.path.join(path, "config.json"), "w") as f:
+        json.dump(hf_config(model.cfg), f, indent=1)
+
+
+def load_hf(model: DecoderLM, path: str) -> int:
+    """Load ``model.safetensors`` written by ``save_hf`` (or any checkpoint with the same names) into ``model``."""
+    from safetensors.torch import load_file
+
+    sd = load_file(os.path.join(path, "model.safetensors"))
+    cfg = model.cfg
+    n = 0
+    with torch.no_grad():
+        for name, t in model.named_weights():
+            if name == "embed.weight":
+                src = sd["model.embed_tokens.weight"]
+            elif name == "lm_head.weight":
+                src = sd["lm_head.weight"]
+            elif name == "final_norm.weight":
+                src = sd["model.norm.weight"]
+            else:
+                _, i, rest = name.split(".", 2)
+                p = f"model.layers.{i}."
+                if rest == "attn.qkv.weight":
+                    src = _fuse_qkv(sd[p + "self_attn.q_proj.weight"], sd[p + "self_attn.k_proj.weight"], sd[p + "self_attn.v_proj.weight"], cfg)
+                elif rest == "mlp.gate_up.weight":
+                    src = torch.cat([sd[p + "mlp.gate_proj.weight"], sd[p + "mlp.up_proj.weight"]], 0)
+                elif rest == "moe.experts.gate_up":
+                    src = torch.stack([torch.cat([sd[p + f"mlp.experts.{e}.gate_proj.weight"], sd[p + f"mlp.experts.{e}.up_proj.weight"]], 0)
+                                       for e in range(t.shape[0])])
+                elif rest == "moe.experts.down":
+                    src = torch.stack([sd[p + f"mlp.experts.{e}.down_proj.weight"] for e in range(t.shape[0])])
+                else:
+                    ren = {"ln1.weight": "input_layernorm.weight", "ln2.weight": "post_attention_layernorm.weight",
+                           "attn.o.weight": "self_attn.o_proj.weight", "attn.q_norm.weight": "self_attn.q_norm.weight",
+                           "attn.k_norm.weight": "self_attn.k_norm.weight", "mlp.down.weight": "mlp.down_proj.weight",
+                           "moe.router.weight": "mlp.gate.weight"}
+                    src = sd[p + ren.get(rest, rest)]
+            t.copy_(src.to(t.dtype).view(t.shape))
+            n += 1
+    return n

@@ -152,7 +152,7 @@ class RayPPOTrainer:
         ie = g.inference_engine
         ecfg = EngineConfig(max_num_seqs=ie.max_num_seqs, max_num_batched_tokens=ie.max_num_batched_tokens,
                             num_kv_pages=ie.num_kv_pages, gpu_memory_utilization=ie.gpu_memory_utilization,
-                            seed=t.seed + 7919 * self.rank, enable_prefix_caching=ie.enable_prefix_caching,
+                            seed=t.seed + 7919 * self.ps.dp_rank, enable_prefix_caching=ie.enable_prefix_caching,   # one sampler stream per DP replica
                             use_cuda_graph=not ie.enforce_eager,
                             max_model_len=min(mcfg.max_position, t.max_prompt_length + g.sampling_params.max_generate_length + 1))
         # colocated, same TP layout: the engine computes with the trainer's flat parameter buffer
@@ -414,9 +414,15 @@ class RayPPOTrainer:
             self.load_checkpoints()
         self.sync_weights()
         try:
+            if t.eval_before_train:
+                self.eval()
             for _epoch in range(t.epochs):
                 for rows in self.loader:
                     self.train_step(rows)
+                    if t.eval_interval > 0 and self.global_step % t.eval_interval == 0:
+                        self.eval()
+                    if t.export_path and t.hf_save_interval > 0 and self.global_step % t.hf_save_interval == 0:
+                        self.export_hf()
                     if 0 < t.num_steps <= self.global_step:
                         return
         except BaseException as e:  # noqa: BLE001
@@ -427,6 +433,40 @@ class RayPPOTrainer:
             if t.isoexec.enabled and t.ckpt_path and hasattr(self, "adapter_trainer"):
                 self.adapter_trainer.ledger.write_verdict(t.ckpt_path)
                 self.adapter_engine.ledger.write_verdict(t.ckpt_path)
+
+    # ------------------------------------------------------------------ evaluation / export
+    def eval(self) -> dict:
+        """Generate on the validation prompts (``eval_dataset`` or the first ``eval_batch_size`` training prompts) with the
+        eval sampling parameters and log reward statistics and pass@k."""
+        from .evaluate import evaluate
+
+        g = self.cfg.generator
+        ds = getattr(self, "eval_dataset", None) or self.dataset
+        rows = [ds[i] for i in range(min(len(ds), self.cfg.trainer.eval_batch_size))]
+        sp = g.eval_sampling_params
+        params = {"max_generate_length": sp.max_generate_length, "temperature": sp.temperature, "top_p": sp.top_p, "top_k": sp.top_k,
+                  "min_p": sp.min_p, "ignore_eos": sp.ignore_eos}
+        was_asleep = self.engine.asleep
+        if was_asleep:
+            self.engine.wake_up()
+        n = max(1, g.eval_n_samples_per_prompt)
+        out = evaluate(self.generator, rows, params, n_samples=n, ks=tuple(sorted({1, n})))
+        if was_asleep:
+            self.engine.sleep()
+        if self.tracker is not None:
+            self.tracker.log(out, self.global_step)
+        self.last_eval = out
+        return out
+
+    def export_hf(self) -> str | None:
+        """Write the policy in the Hugging Face layout under ``export_path/global_step_N`` (unsharded runs; rank 0)."""
+        from ..models import hf_export
+
+        if self.ps.tp > 1 or self.ps.ep > 1 or self.ps.pp > 1 or self.rank != 0:
+            return None
+        path = os.path.join(self.cfg.trainer.export_path, f"global_step_{self.global_step}")
+        hf_export.save_hf(self.policy.model, path)
+        return path
 
     # ------------------------------------------------------------------ checkpoints
     def save_checkpoints(self) -> str:

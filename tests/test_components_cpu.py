@@ -343,3 +343,50 @@ def test_moe_utils_io_and_nccl_capabilities(tmp_path):
     assert caps["backend"] in ("none", "gloo", "nccl") and "peer_access" in caps
     with pytest.raises(RuntimeError):
         nccl_runtime.require({"peer_access": False}, "peer_access")
+
+
+def test_hf_export_roundtrip_and_dispatch_helpers(tmp_path):
+    from safetensors.torch import load_file
+
+    from skyrl_isoexec_b200.models import hf_export
+    from skyrl_isoexec_b200.models.config import get_config
+    from skyrl_isoexec_b200.models.decoder import DecoderLM
+    from skyrl_isoexec_b200.parallel import dispatch
+    from skyrl_isoexec_b200.parallel.state import ParallelState
+
+    for preset in ("tiny-qwen3", "tiny-moe"):
+        cfg = get_config(preset)
+        m = DecoderLM(cfg, seed=3)
+        d = str(tmp_path / preset)
+        hf_export.save_hf(m, d)
+        sd = load_file(d + "/model.safetensors")
+        Hq, Hkv, D = cfg.num_q_heads, cfg.num_kv_heads, cfg.head_dim
+        assert sd["model.layers.0.self_attn.q_proj.weight"].shape == (Hq * D, cfg.hidden_size)
+        assert sd["model.layers.0.self_attn.k_proj.weight"].shape == (Hkv * D, cfg.hidden_size)
+        # q head h of the export is the h-th query head of the fused, group-major storage
+        G = Hq // Hkv
+        fused = m.p("layers.0.attn.qkv.weight").detach().view(Hkv, G * D + 2 * D, -1)
+        assert torch.equal(sd["model.layers.0.self_attn.q_proj.weight"].view(Hq, D, -1)[G], fused[1, :D])
+        m2 = DecoderLM(cfg, seed=99)
+        assert hf_export.load_hf(m2, d) == len(m.store.order) and torch.equal(m2.store.flat, m.store.flat)
+        assert json.load(open(d + "/config.json"))["num_hidden_layers"] == cfg.num_layers
+    ps = ParallelState.single()
+    assert dispatch.dp_slice(12, 1, 3) == slice(4, 8)
+    with pytest.raises(ValueError):
+        dispatch.dp_slice(10, 0, 3)
+    assert dispatch.reduce_metrics({"a": 1.0, "s": "x"}, ps) == {"a": 1.0, "s": "x"}
+    x = torch.arange(6).view(3, 2)
+    assert dispatch.gather_rows(x, ps) is x
+
+
+def test_trainer_eval_and_hf_export_hooks(tmp_path):
+    cfg = _rl_cfg(str(tmp_path / "ck"), 2, "trainer.eval_interval=1", "trainer.eval_before_train=true", "trainer.eval_batch_size=3",
+                  "generator.eval_n_samples_per_prompt=2", "generator.eval_sampling_params.max_generate_length=6",
+                  "generator.eval_sampling_params.temperature=1.0", "generator.eval_sampling_params.ignore_eos=true",
+                  f"trainer.export_path={tmp_path / 'hf'}", "trainer.hf_save_interval=2")
+    tr = RayPPOTrainer(cfg, device="cpu")
+    tr.train()
+    assert tr.last_eval["eval/num_prompts"] == 3 and "eval/pass_at_2" in tr.last_eval
+    import os
+
+    assert sorted(os.listdir(tmp_path / "hf" / "global_step_2")) == ["config.json", "model.safetensors"]

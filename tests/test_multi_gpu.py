@@ -433,3 +433,74 @@ def test_tensor_parallel_model_with_fused_kernels_is_bitwise_tp_invariant():
     print("tp model:", res)
     assert res["engine_vs_trainer_mismatches_tp"] == 0 and res["tp2_vs_tp1_mismatches"] == 0
     assert res["grad_norm_tp"] > 0 and res["status"] == 0
+
+
+def _ep_model_worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank), NCCL_NVLS_ENABLE="0")
+    import torch.distributed as dist
+
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from skyrl_isoexec_b200.core.testing import count_bit_mismatches
+        from skyrl_isoexec_b200.engine.llm_engine import EngineConfig, LLMEngine
+        from skyrl_isoexec_b200.engine.sampler import SamplingParams
+        from skyrl_isoexec_b200.models.config import get_config
+        from skyrl_isoexec_b200.models.decoder import DecoderLM
+        from skyrl_isoexec_b200.ops import _native
+        from skyrl_isoexec_b200.parallel.state import ParallelState
+        from skyrl_isoexec_b200.parallel.transports import setup_transports
+        from skyrl_isoexec_b200.train.batch import TrainingInputBatch, build_sequences
+        from skyrl_isoexec_b200.train.policy_worker import PolicyWorker, WorkerConfig
+
+        _native.lib().ix_init()
+        ps = ParallelState.build(ep=world)
+        cfg = get_config("tiny-moe", dtype="bfloat16", hidden_size=512, num_q_heads=4, num_kv_heads=2,
+                         head_dim=128, moe_ffn_size=256, num_experts=16, top_k=4)
+        reg = setup_transports(ps, cfg, max_tokens=1024)
+        model = DecoderLM(cfg, ps, "cuda", seed=4)
+        eng = LLMEngine(model, EngineConfig(max_num_seqs=8, num_kv_pages=40, max_num_batched_tokens=512, seed=20 + rank))
+        g = torch.Generator().manual_seed(rank)                      # every rank has its own prompts and its own lengths
+        prompts = [torch.randint(0, cfg.vocab_size, (int(n),), generator=g).tolist() for n in torch.randint(20, 200, (4 + rank,), generator=g)]
+        outs = eng.generate(prompts, SamplingParams(max_generate_length=12 + 7 * rank, ignore_eos=True))
+        seq, att, rmask = build_sequences([o.prompt_ids for o in outs], [o.response_ids for o in outs])
+        batch = TrainingInputBatch({"sequences": seq, "attention_mask": att, "response_mask": rmask, "loss_mask": rmask.clone(),
+                                    "advantages": torch.randn(rmask.shape, generator=g) * 1e-3})
+        worker = PolicyWorker(model, WorkerConfig(max_tokens_per_microbatch=300 if rank == 0 else 1000))
+        lp = worker.forward(batch)
+        ro = torch.zeros_like(lp)
+        for i, o in enumerate(outs):
+            ro[i, :len(o.response_logprobs)] = torch.tensor(o.response_logprobs)
+        mism = count_bit_mismatches((lp * rmask).contiguous(), (ro * rmask).contiguous())
+        batch["action_log_probs"] = lp
+        worker.forward_backward(batch)
+        gn = worker.optim_step()
+        res = torch.tensor([float(mism), gn, float(_native.read_status())], device="cuda", dtype=torch.float64)
+        allr = [torch.zeros_like(res) for _ in range(world)]
+        dist.all_gather(allr, res)
+        if rank == 0:
+            q.put({"registered": reg, "mismatches": [int(r[0]) for r in allr], "grad_norms": [float(r[1]) for r in allr],
+                   "status": [int(r[2]) for r in allr]})
+    finally:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+@pytest.mark.timeout(600)
+def test_moe_model_with_expert_parallelism_over_peer_memory():
+    """MoE engine and trainer at EP=2: dispatch / grouped GEMMs / return over peer memory in the no-grad passes, NCCL
+    all-to-all under autograd; ranks hold different prompts and step in lockstep. Rollout == trainer, bit for bit."""
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_ep_model_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = q.get(timeout=500)
+    for p in procs:
+        p.join(timeout=120)
+    print("moe ep model:", res)
+    assert res["registered"]["ep"] and res["mismatches"] == [0, 0] and res["status"] == [0, 0]
+    assert res["grad_norms"][0] == res["grad_norms"][1] > 0
