@@ -17,8 +17,9 @@
 // fetched with one 4D TMA box over Q viewed as [T, Hkv, G, D]. K and V come from a slot
 // pool [num_slots, Hkv, D] through a block table (page = 128 slots) or contiguously.
 //
+// Persistent CTAs (one per SM) walk the (tile, KV head) work list; the producer runs ahead across work items.
 // Roles (192 threads): warp 0 TMA producer, warp 1 tcgen05.mma issuer, warps 2..5 softmax
-// (thread = row). TMEM: two S buffers (128 cols each) + one O_blk buffer (D cols).
+// (thread = row). TMEM: two S buffers (128 cols each) + one O buffer (D cols).
 // Pipeline: S_{j+1} = Q K_{j+1}^T is issued while the softmax of block j runs; O += P V_j
 // accumulates in TMEM. The exponent reference m of a row moves lazily (only when the running
 // maximum grew by more than 8 in log2 units), so the softmax threads rescale O in TMEM rarely
@@ -49,19 +50,41 @@ struct AttnSmem {
   static constexpr int kQ = ND * kChunk;
   static constexpr int kKV = ND * kChunk;                    // one K or V block
   static constexpr int kP = 2 * kChunk;                      // 128 rows x 128 keys bf16
-  static constexpr int offQ = 0;
-  static constexpr int offK = offQ + kQ;
+  static constexpr int offQ = 0;                             // two Q tiles: the next work item's Q loads during this one
+  static constexpr int offK = offQ + 2 * kQ;
   static constexpr int offV = offK + 2 * kKV;
   static constexpr int offP = offV + 2 * kKV;
   static constexpr int offBar = offP + kP;
   static constexpr int kBytes = offBar + 256 + 1024;
 };
 
-// bars: 0 Q | 1,2 K_full | 3,4 K_empty | 5,6 V_full | 7,8 V_empty | 9,10 S_full | 11 P_full | 12 O_full
+// Barriers. Stage rings (K, V, S) and the once-per-block barriers (P, O_full) are indexed by a block counter that
+// runs across the work items of a CTA; Q and O_empty by the item counter.
+enum { B_QF = 0, B_QE = 2, B_KF = 4, B_KE = 6, B_VF = 8, B_VE = 10, B_SF = 12, B_PF = 14, B_OF = 15, B_OE = 16, kNumBars = 17 };
+
+struct ItemGeom {
+  WorkItem it;
+  int kvh, q_valid, nb;
+};
+
+__device__ __forceinline__ ItemGeom item_geom(const WorkItem* items, int w, int num_items, int TQ) {
+  ItemGeom g;
+  g.it = items[w % num_items];      // items vary fastest: neighbouring CTAs work on the same KV head of neighbouring tiles
+  g.kvh = w / num_items;
+  g.q_valid = g.it.q_len < TQ ? g.it.q_len : TQ;
+  int kv_hi = g.it.q_pos0 + g.q_valid;  // causal: last row sees positions < q_pos0 + q_valid
+  if (kv_hi > g.it.kv_len) kv_hi = g.it.kv_len;
+  g.nb = (kv_hi + kBlkN - 1) / kBlkN;
+  return g;
+}
+
+// Persistent: a CTA walks the (tile, KV head) work list with stride gridDim.x. The producer runs ahead across work
+// items (the next item's Q and first K/V blocks load while the current item's last blocks and epilogue run), so an SM
+// keeps streaming K/V instead of draining and refilling its pipeline for every item.
 template <int ND>
 __global__ void __launch_bounds__(kAttnThreads, 1)
 attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                     const __grid_constant__ CUtensorMap tmV, const WorkItem* __restrict__ items,
+                     const __grid_constant__ CUtensorMap tmV, const WorkItem* __restrict__ items, int num_items,
                      const int* __restrict__ block_table, int bt_stride, __nv_bfloat16* __restrict__ out,
                      float* __restrict__ lse_out, int Hq, int Hkv, int G, float scale_log2, int* __restrict__ status) {
   using SM = AttnSmem<ND>;
@@ -70,23 +93,16 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SM::offBar);
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 13);
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + kNumBars);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const WorkItem it = items[blockIdx.x];
-  const int kvh = blockIdx.y;
   const int TQ = kRows / G;
-  const int q_valid = it.q_len < TQ ? it.q_len : TQ;
-  int kv_hi = it.q_pos0 + q_valid;  // causal: last row sees positions < q_pos0 + q_valid
-  if (kv_hi > it.kv_len) kv_hi = it.kv_len;
-  const int nb = (kv_hi + kBlkN - 1) / kBlkN;
+  const int total = num_items * Hkv;
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
-    for (int i = 0; i < 11; ++i) mbar_init(smem_u32(&bars[i]), 1);
-    mbar_init(smem_u32(&bars[11]), 128);
-    mbar_init(smem_u32(&bars[12]), 1);
+    for (int i = 0; i < kNumBars; ++i) mbar_init(smem_u32(&bars[i]), (i == B_PF || i == B_OE) ? 128 : 1);
     fence_mbar_init();
   }
   if (warp == 1) {
@@ -99,49 +115,65 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   const uint32_t tmem_base = *tmem_holder;
   const uint32_t tmem_S0 = tmem_base, tmem_O = tmem_base + 256;
 
-  if (nb > 0) {
-    if (warp == 0) {
-      // -------------------------------------------------------------- producer
-      if (elect_one()) {
-        tma_prefetch_desc(&tmQ);
-        tma_prefetch_desc(&tmK);
-        tma_prefetch_desc(&tmV);
-        const uint32_t bq = smem_u32(&bars[0]);
+  if (warp == 0) {
+    // -------------------------------------------------------------- producer
+    if (elect_one()) {
+      tma_prefetch_desc(&tmQ);
+      tma_prefetch_desc(&tmK);
+      tma_prefetch_desc(&tmV);
+      uint32_t jb = 0, qi = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; w < total && ok; w += gridDim.x) {
+        const ItemGeom g = item_geom(items, w, num_items, TQ);
+        if (g.nb == 0) continue;
+        const int qs = qi & 1;
+        if (!mbar_wait(smem_u32(&bars[B_QE + qs]), ((qi >> 1) & 1) ^ 1, abort_flag, status, ST_TIMEOUT_EMPTY)) break;
+        const uint32_t bq = smem_u32(&bars[B_QF + qs]);
         mbar_arrive_expect_tx(bq, SM::kQ);
 #pragma unroll
         for (int dc = 0; dc < ND; ++dc)
-          tma_load_4d(smem_u32(smem + SM::offQ + dc * SM::kChunk), &tmQ, bq, dc * 64, 0, kvh, it.q_start);
-        for (int j = 0; j < nb; ++j) {
-          const int st = j & 1;
-          const uint32_t ph = (j >> 1) & 1;
+          tma_load_4d(smem_u32(smem + SM::offQ + qs * SM::kQ + dc * SM::kChunk), &tmQ, bq, dc * 64, 0, g.kvh, g.it.q_start);
+        for (int j = 0; j < g.nb; ++j, ++jb) {
+          const int st = jb & 1;
+          const uint32_t ph = (jb >> 1) & 1;
           int row;
-          if (it.bt_row >= 0) row = block_table[static_cast<size_t>(it.bt_row) * bt_stride + j] * kBlkN;
-          else row = it.kv_start + j * kBlkN;
-          if (!mbar_wait(smem_u32(&bars[3 + st]), ph ^ 1, abort_flag, status, ST_TIMEOUT_EMPTY)) break;
-          const uint32_t bk = smem_u32(&bars[1 + st]);
+          if (g.it.bt_row >= 0) row = block_table[static_cast<size_t>(g.it.bt_row) * bt_stride + j] * kBlkN;
+          else row = g.it.kv_start + j * kBlkN;
+          if (!mbar_wait(smem_u32(&bars[B_KE + st]), ph ^ 1, abort_flag, status, ST_TIMEOUT_EMPTY)) { ok = false; break; }
+          const uint32_t bk = smem_u32(&bars[B_KF + st]);
           mbar_arrive_expect_tx(bk, SM::kKV);
 #pragma unroll
           for (int dc = 0; dc < ND; ++dc)
-            tma_load_2d(smem_u32(smem + SM::offK + st * SM::kKV + dc * SM::kChunk), &tmK, bk, kvh * D + dc * 64, row);
-          if (!mbar_wait(smem_u32(&bars[7 + st]), ph ^ 1, abort_flag, status, ST_TIMEOUT_EMPTY)) break;
-          const uint32_t bv = smem_u32(&bars[5 + st]);
+            tma_load_2d(smem_u32(smem + SM::offK + st * SM::kKV + dc * SM::kChunk), &tmK, bk, g.kvh * D + dc * 64, row);
+          if (!mbar_wait(smem_u32(&bars[B_VE + st]), ph ^ 1, abort_flag, status, ST_TIMEOUT_EMPTY)) { ok = false; break; }
+          const uint32_t bv = smem_u32(&bars[B_VF + st]);
           mbar_arrive_expect_tx(bv, SM::kKV);
 #pragma unroll
           for (int dc = 0; dc < ND; ++dc)
-            tma_load_2d(smem_u32(smem + SM::offV + st * SM::kKV + dc * SM::kChunk), &tmV, bv, kvh * D + dc * 64, row);
+            tma_load_2d(smem_u32(smem + SM::offV + st * SM::kKV + dc * SM::kChunk), &tmV, bv, g.kvh * D + dc * 64, row);
         }
+        ++qi;
       }
-    } else if (warp == 1) {
-      // -------------------------------------------------------------- MMA issuer
-      if (elect_one()) {
-        constexpr uint32_t idesc_s = make_idesc_bf16(kRows, kBlkN, 0, 0);
-        constexpr uint32_t idesc_o = make_idesc_bf16(kRows, D, 0, 1);  // V is MN-major
-        const uint32_t sQ = smem_u32(smem + SM::offQ);
-        const uint32_t sP = smem_u32(smem + SM::offP);
-        bool ok = mbar_wait(smem_u32(&bars[0]), 0, abort_flag, status, ST_TIMEOUT_FULL);
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------------- MMA issuer
+    if (elect_one()) {
+      constexpr uint32_t idesc_s = make_idesc_bf16(kRows, kBlkN, 0, 0);
+      constexpr uint32_t idesc_o = make_idesc_bf16(kRows, D, 0, 1);  // V is MN-major
+      const uint32_t sP = smem_u32(smem + SM::offP);
+      uint32_t jb0 = 0, qi = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; w < total && ok; w += gridDim.x) {
+        const ItemGeom g = item_geom(items, w, num_items, TQ);
+        if (g.nb == 0) continue;
+        const int nb = g.nb;
+        const int qs = qi & 1;
+        const uint32_t sQ = smem_u32(smem + SM::offQ + qs * SM::kQ);
+        ok = mbar_wait(smem_u32(&bars[B_QF + qs]), (qi >> 1) & 1, abort_flag, status, ST_TIMEOUT_FULL);
         auto issue_qk = [&](int j) -> bool {
-          const int st = j & 1;
-          if (!mbar_wait(smem_u32(&bars[1 + st]), (j >> 1) & 1, abort_flag, status, ST_TIMEOUT_FULL)) return false;
+          const uint32_t b = jb0 + j;
+          const int st = b & 1;
+          if (!mbar_wait(smem_u32(&bars[B_KF + st]), (b >> 1) & 1, abort_flag, status, ST_TIMEOUT_FULL)) return false;
           tc_fence_after();
           const uint32_t sK = smem_u32(smem + SM::offK + st * SM::kKV);
 #pragma unroll
@@ -150,19 +182,25 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
             for (int k = 0; k < 4; ++k)
               umma_f16_ss(tmem_S0 + st * 128, make_sw128_desc(sQ + dc * SM::kChunk + k * 32, 16, 1024),
                           make_sw128_desc(sK + dc * SM::kChunk + k * 32, 16, 1024), idesc_s, (dc | k) != 0 ? 1u : 0u);
-          umma_commit(smem_u32(&bars[3 + st]));   // K stage free
-          umma_commit(smem_u32(&bars[9 + st]));   // S ready
+          umma_commit(smem_u32(&bars[B_KE + st]));   // K stage free
+          umma_commit(smem_u32(&bars[B_SF + st]));   // S ready
+          if (j == nb - 1) umma_commit(smem_u32(&bars[B_QE + qs]));   // last use of this Q tile
           return true;
         };
+        // S[b & 1] was last read by the softmax of block b - 2, which finished before P_full(b - 2): waited below
         if (ok) ok = issue_qk(0);
         for (int j = 0; j < nb && ok; ++j) {
           if (j + 1 < nb) {
-            // S[(j+1)&1] was last read by the softmax of block j-1, which finished before P_full(j-1)
             if (!issue_qk(j + 1)) { ok = false; break; }
           }
-          const int st = j & 1;
-          if (!mbar_wait(smem_u32(&bars[11]), j & 1, abort_flag, status, ST_TIMEOUT_MISC)) { ok = false; break; }
-          if (!mbar_wait(smem_u32(&bars[5 + st]), (j >> 1) & 1, abort_flag, status, ST_TIMEOUT_FULL)) { ok = false; break; }
+          const uint32_t b = jb0 + j;
+          const int st = b & 1;
+          if (!mbar_wait(smem_u32(&bars[B_PF]), b & 1, abort_flag, status, ST_TIMEOUT_MISC)) { ok = false; break; }
+          if (!mbar_wait(smem_u32(&bars[B_VF + st]), (b >> 1) & 1, abort_flag, status, ST_TIMEOUT_FULL)) { ok = false; break; }
+          if (j == 0 && qi > 0) {
+            // the first P V of an item overwrites O: the previous item's epilogue must have read it out
+            if (!mbar_wait(smem_u32(&bars[B_OE]), (qi - 1) & 1, abort_flag, status, ST_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
+          }
           tc_fence_after();
           const uint32_t sV = smem_u32(smem + SM::offV + st * SM::kKV);
 #pragma unroll
@@ -171,31 +209,41 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
             const uint64_t da = make_sw128_desc(sP + (k >> 2) * SM::kChunk + (k & 3) * 32, 16, 1024);
             // B = V (MN-major): 16 keys = 2 groups of 8 rows (SBO 1024 B); 64-wide d chunks LBO apart
             const uint64_t db = make_sw128_desc(sV + k * 2048, SM::kChunk, 1024);
-            umma_f16_ss(tmem_O, da, db, idesc_o, (j | k) != 0 ? 1u : 0u);   // O accumulates over blocks in TMEM
+            umma_f16_ss(tmem_O, da, db, idesc_o, (j | k) != 0 ? 1u : 0u);   // O accumulates over the item's blocks in TMEM
           }
-          umma_commit(smem_u32(&bars[7 + st]));  // V stage free
-          umma_commit(smem_u32(&bars[12]));      // O_blk ready, P buffer free
+          umma_commit(smem_u32(&bars[B_VE + st]));  // V stage free
+          umma_commit(smem_u32(&bars[B_OF]));       // O_blk ready, P buffer free
         }
+        jb0 += nb;
+        ++qi;
       }
-    } else {
-      // -------------------------------------------------------------- softmax / epilogue
-      const int quad = warp & 3;
-      const int r = quad * 32 + lane;             // tile row
-      const int tok = r / G;                      // token inside the tile
-      const int hq = kvh * G + (r % G);
+    }
+  } else {
+    // -------------------------------------------------------------- softmax / epilogue
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;             // tile row
+    const int tok = r / G;                      // token inside the tile
+    const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
+    uint8_t* sP = smem + SM::offP;
+    uint32_t jb0 = 0;
+    bool ok = true;
+    for (int w = blockIdx.x; w < total && ok; w += gridDim.x) {
+      const ItemGeom g = item_geom(items, w, num_items, TQ);
+      if (g.nb == 0) continue;
+      const WorkItem& it = g.it;
+      const int nb = g.nb, q_valid = g.q_valid;
+      const int hq = g.kvh * G + (r % G);
       const bool row_valid = tok < q_valid;
       const int q_pos = it.q_pos0 + (row_valid ? tok : q_valid - 1);
-      const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
       // m is the exponent reference of the row. It follows the running maximum lazily: it only moves
       // when the maximum has grown by more than 8 (log2 units) since it was last set, so O (which
       // accumulates in TMEM) is rescaled rarely. p = exp2(t - m) is then at most 2^8; l and O are
       // both relative to the same m, so O / l is exact softmax. The rule is per row.
       float m = -INFINITY, l = 0.f;
-      uint8_t* sP = smem + SM::offP;
-      bool ok = true;
       for (int j = 0; j < nb && ok; ++j) {
-        const int st = j & 1;
-        if (!mbar_wait(smem_u32(&bars[9 + st]), (j >> 1) & 1, abort_flag, status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+        const uint32_t b = jb0 + j;
+        const int st = b & 1;
+        if (!mbar_wait(smem_u32(&bars[B_SF + st]), (b >> 1) & 1, abort_flag, status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
         tc_fence_after();
         const uint32_t tS = tmem_S0 + st * 128 + lane_off;
         const int key0 = j * kBlkN;
@@ -242,9 +290,10 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           m = m_new;
         }
         const bool any_rescale = __any_sync(0xffffffffu, alpha != 1.f);
-        // P V of block j-1 must have finished: the P buffer is reused and O may be rescaled
+        // P V of block j-1 must have finished: the P buffer is reused and O may be rescaled. (For j == 0 the buffer
+        // was last read by the previous item's last P V, which this thread waited for in that item's epilogue.)
         if (j > 0) {
-          if (!mbar_wait(smem_u32(&bars[12]), (j - 1) & 1, abort_flag, status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+          if (!mbar_wait(smem_u32(&bars[B_OF]), (b - 1) & 1, abort_flag, status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
           tc_fence_after();
           if (any_rescale) {
 #pragma unroll 1
@@ -286,34 +335,40 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 #undef IX_EXP_STORE
         tc_fence_before();
         fence_proxy_async();  // make the generic-proxy writes of P visible to the tensor core
-        mbar_arrive(smem_u32(&bars[11]));
+        mbar_arrive(smem_u32(&bars[B_PF]));
       }
-      if (ok && mbar_wait(smem_u32(&bars[12]), (nb - 1) & 1, abort_flag, status, ST_TIMEOUT_TMEM_FULL)) {
-        tc_fence_after();
-        const float inv = __fdiv_rn(1.0f, l);
-        const size_t orow = static_cast<size_t>(it.q_start + (row_valid ? tok : 0)) * Hq + hq;
+      if (!ok) break;
+      if (!mbar_wait(smem_u32(&bars[B_OF]), (jb0 + nb - 1) & 1, abort_flag, status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+      tc_fence_after();
+      const float inv = __fdiv_rn(1.0f, l);
+      const size_t orow = static_cast<size_t>(it.q_start + (row_valid ? tok : 0)) * Hq + hq;
 #pragma unroll 1
-        for (int c = 0; c < D / 32; ++c) {
-          uint32_t v[32];
-          tmem_ld_32x32(tmem_O + lane_off + c * 32, v);
-          tmem_ld_wait_dep(v);
-          if (row_valid) {
-            uint4* dst = reinterpret_cast<uint4*>(out + orow * D + c * 32);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              uint4 w;
-              w.x = pack_bf2(__fmul_rn(__uint_as_float(v[8 * i + 0]), inv), __fmul_rn(__uint_as_float(v[8 * i + 1]), inv));
-              w.y = pack_bf2(__fmul_rn(__uint_as_float(v[8 * i + 2]), inv), __fmul_rn(__uint_as_float(v[8 * i + 3]), inv));
-              w.z = pack_bf2(__fmul_rn(__uint_as_float(v[8 * i + 4]), inv), __fmul_rn(__uint_as_float(v[8 * i + 5]), inv));
-              w.w = pack_bf2(__fmul_rn(__uint_as_float(v[8 * i + 6]), inv), __fmul_rn(__uint_as_float(v[8 * i + 7]), inv));
-              dst[i] = w;
-            }
-          }
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(tmem_O + lane_off + c * 32, v);
+        tmem_ld_wait_dep(v);
+        if (c == D / 32 - 1) {
+          // O is in registers: the next item's first P V may overwrite the accumulator
+          tc_fence_before();
+          mbar_arrive(smem_u32(&bars[B_OE]));
         }
         if (row_valid) {
-          if (lse_out) lse_out[orow] = (m + log2f(l)) * 0.6931471805599453f;
+          uint4* dst = reinterpret_cast<uint4*>(out + orow * D + c * 32);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint4 wv;
+            wv.x = pack_bf2(__fmul_rn(__uint_as_float(v[8 * i + 0]), inv), __fmul_rn(__uint_as_float(v[8 * i + 1]), inv));
+            wv.y = pack_bf2(__fmul_rn(__uint_as_float(v[8 * i + 2]), inv), __fmul_rn(__uint_as_float(v[8 * i + 3]), inv));
+            wv.z = pack_bf2(__fmul_rn(__uint_as_float(v[8 * i + 4]), inv), __fmul_rn(__uint_as_float(v[8 * i + 5]), inv));
+            wv.w = pack_bf2(__fmul_rn(__uint_as_float(v[8 * i + 6]), inv), __fmul_rn(__uint_as_float(v[8 * i + 7]), inv));
+            dst[i] = wv;
+          }
         }
       }
+      if (row_valid) {
+        if (lse_out) lse_out[orow] = (m + log2f(l)) * 0.6931471805599453f;
+      }
+      jb0 += nb;
     }
   }
 
@@ -356,9 +411,12 @@ int launch_attn(const void* q, const void* k, const void* v, const void* items, 
     IX_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::kBytes));
     attr_set[dev & 63] = true;
   }
-  dim3 grid(num_items, Hkv);
+  int sms = 0;
+  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+  const long long total = static_cast<long long>(num_items) * Hkv;
+  const int grid = static_cast<int>(total < sms ? total : sms);       // persistent: one CTA per SM walks the work list
   const float scale_log2 = scale * 1.4426950408889634f;
-  kern<<<grid, kAttnThreads, SM::kBytes, stream>>>(tmQ, tmK, tmV, static_cast<const WorkItem*>(items),
+  kern<<<grid, kAttnThreads, SM::kBytes, stream>>>(tmQ, tmK, tmV, static_cast<const WorkItem*>(items), num_items,
                                                    static_cast<const int*>(block_table), bt_stride,
                                                    static_cast<__nv_bfloat16*>(out), static_cast<float*>(lse), Hq, Hkv,
                                                    G, scale_log2, ixh::status_word(dev));
