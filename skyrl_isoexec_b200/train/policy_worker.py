@@ -44,6 +44,7 @@ class WorkerConfig:
     checkpoint_layers: bool = True
     keep_last_layers: int = 0          # do not recompute the last n layers (trades activation memory for one forward of them)
     want_entropy: bool = False
+    overlap_grad_reduce: bool = True   # sum gradient buckets over DP during the last micro-batch's backward
     optimizer: OptimizerConfig = field(default_factory=OptimizerConfig)
 
 
@@ -204,10 +205,66 @@ class FlatAdamW:
             spec = model.store.specs[name]
             p = model.p(name)
             view = self.main_grad[spec.offset:spec.offset + p.numel()].view(p.shape)
-            self._hooks.append(p.register_post_accumulate_grad_hook(self._make_hook(view)))
+            self._hooks.append(p.register_post_accumulate_grad_hook(self._make_hook(view, name)))
+        self._ov = None
 
-    @staticmethod
-    def _make_hook(view):
+    # ---- data-parallel reduction overlapped with the backward -------------------------------------------------
+    def setup_overlap(self, ps, bucket_elems: int = 64 << 20) -> None:
+        """Cut the flat gradient buffer into buckets of whole parameters (storage order). During the LAST micro-batch's
+        backward a bucket is summed over the data-parallel group, on a side stream, as soon as its last gradient has
+        been accumulated, so the reduction hides behind the remaining backward instead of following it."""
+        buckets, cur_lo, cur_names, end = [], None, [], 0
+        for name in self.model.store.order:
+            s = self.model.store.specs[name]
+            if cur_lo is None:
+                cur_lo = s.offset
+            cur_names.append(name)
+            end = s.offset + math.prod(s.shape)
+            if end - cur_lo >= bucket_elems:
+                buckets.append((cur_lo, end, cur_names))
+                cur_lo, cur_names = None, []
+        if cur_names:
+            buckets.append((cur_lo, end, cur_names))
+        self._ov = {"ps": ps, "buckets": buckets, "of": {n: i for i, b in enumerate(buckets) for n in b[2]},
+                    "pending": [0] * len(buckets), "done": set(), "active": False,
+                    "side": torch.cuda.Stream() if self.main_grad.is_cuda else None}
+
+    def begin_overlap(self) -> None:
+        ov = self._ov
+        if ov is None:
+            return
+        ov["pending"] = [len(b[2]) for b in ov["buckets"]]
+        ov["done"], ov["active"] = set(), True
+
+    def _bucket_ready(self, i: int) -> None:
+        from ..parallel.dp import reduce_main_grads
+
+        ov = self._ov
+        lo, hi, _ = ov["buckets"][i]
+        if ov["side"] is not None:
+            ev = torch.cuda.Event()
+            ev.record()
+            with torch.cuda.stream(ov["side"]):
+                ov["side"].wait_event(ev)
+                reduce_main_grads(self.main_grad, ov["ps"], ranges=[(lo, hi)])
+        else:
+            reduce_main_grads(self.main_grad, ov["ps"], ranges=[(lo, hi)])
+        ov["done"].add(i)
+
+    def finish_overlap(self) -> bool:
+        """Reduce whatever the backward did not trigger, join the side stream. False if no overlap was running."""
+        ov = self._ov
+        if ov is None or not ov["active"]:
+            return False
+        for i in range(len(ov["buckets"]) - 1, -1, -1):      # same order on every rank
+            if i not in ov["done"]:
+                self._bucket_ready(i)
+        if ov["side"] is not None:
+            torch.cuda.current_stream().wait_stream(ov["side"])
+        ov["active"] = False
+        return True
+
+    def _make_hook(self, view, name):
         def hook(p):
             g = p.grad
             if g.is_cuda and g.dtype == torch.bfloat16 and g.is_contiguous() and g.numel() % 8 == 0:
@@ -217,6 +274,12 @@ class FlatAdamW:
             else:
                 view.add_(g)
             p.grad = None
+            ov = self._ov
+            if ov is not None and ov["active"]:
+                b = ov["of"][name]
+                ov["pending"][b] -= 1
+                if ov["pending"][b] == 0:
+                    self._bucket_ready(b)
         return hook
 
     def zero_grad(self):
@@ -391,7 +454,10 @@ class PolicyWorker:
         want_ent = self.cfg.want_entropy or algo.use_entropy_loss
         tot = {"loss": 0.0, "clip_ratio_num": 0.0, "tokens": 0.0, "entropy_sum": 0.0, "kl_sum": 0.0}
         dev = self.device
-        for mb in self._pack(seqs, att, R):
+        mbs = self._pack(seqs, att, R)
+        for mi, mb in enumerate(mbs):
+            if mi == len(mbs) - 1 and self._overlap_ok():
+                self.opt.begin_overlap()          # gradients of this backward are final: reduce them bucket by bucket
             idx = torch.tensor(mb.seq_index)
             hidden = self._run_model(mb, "trainer_fwd")
             lp_flat, ent_flat = self._logprobs(mb, hidden, want_ent)
@@ -428,9 +494,20 @@ class PolicyWorker:
         return {"policy_loss": tot["loss"], "ppo_clip_ratio": tot["clip_ratio_num"] / n, "loss_tokens": tot["tokens"],
                 "policy_entropy": tot["entropy_sum"] / n, "policy_kl": tot["kl_sum"] / n}
 
+    def _overlap_ok(self) -> bool:
+        """Overlap applies to plain data parallelism (no TP/EP-specific reductions to order before the DP sum)."""
+        ps = self.ps
+        if not (ps.dp > 1 and ps.tp == 1 and ps.ep == 1 and self.cfg.overlap_grad_reduce):
+            return False
+        if self.opt._ov is None:
+            self.opt.setup_overlap(ps)
+        return True
+
     def reduce_gradients(self) -> None:
         """Sum the main gradients over the data-parallel group (fixed bucket order); before that,
         weights that are replicated over TP but only see the local heads get their gradient summed over TP."""
+        if self.opt.finish_overlap():
+            return
         if self.ps.tp > 1:
             store = self.model.store
             for name in store.order:
