@@ -114,6 +114,8 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
   const uint32_t tmem_S0 = tmem_base, tmem_O = tmem_base + 256;
+  pdl_launch_dependents();
+  pdl_wait();   // Q, the K/V slots of this step and the work list come from the kernels before this one
 
   if (warp == 0) {
     // -------------------------------------------------------------- producer
@@ -416,10 +418,9 @@ int launch_attn(const void* q, const void* k, const void* v, const void* items, 
   const long long total = static_cast<long long>(num_items) * Hkv;
   const int grid = static_cast<int>(total < sms ? total : sms);       // persistent: one CTA per SM walks the work list
   const float scale_log2 = scale * 1.4426950408889634f;
-  kern<<<grid, kAttnThreads, SM::kBytes, stream>>>(tmQ, tmK, tmV, static_cast<const WorkItem*>(items), num_items,
-                                                   static_cast<const int*>(block_table), bt_stride,
-                                                   static_cast<__nv_bfloat16*>(out), static_cast<float*>(lse), Hq, Hkv,
-                                                   G, scale_log2, ixh::status_word(dev));
+  IX_CUDA(ixh::launch_pdl(kern, dim3(grid), dim3(kAttnThreads), static_cast<size_t>(SM::kBytes), stream, tmQ, tmK, tmV,
+                          static_cast<const WorkItem*>(items), num_items, static_cast<const int*>(block_table), bt_stride,
+                          static_cast<__nv_bfloat16*>(out), static_cast<float*>(lse), Hq, Hkv, G, scale_log2, ixh::status_word(dev)));
   IX_CUDA(cudaGetLastError());
   return 0;
 }

@@ -39,7 +39,7 @@ constexpr int kPipeBytes = 200 * 1024;   // shared memory given to the TMA pipel
 template <int BN>
 struct GemmCfg {
   static constexpr int kStageBytesB = BN * BK * 2;
-  static constexpr int kTmemCols = (2 * BN < 32) ? 32 : 2 * BN;
+  static constexpr int kTmemCols = tmem_cols_pow2(2 * BN);
   static constexpr int kSmemBytes = kPipeBytes + BM * BK * 2 /*tail the last stage's MMA may read*/ + 1024 /*align*/ + 512 /*barriers*/;
   static int stage_bytes(int a_rows) { return a_rows * BK * 2 + kStageBytesB; }
   static int stages(int a_rows) {
@@ -90,25 +90,49 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
+  pdl_launch_dependents();
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (elect_one()) {
       tma_prefetch_desc(&tmA);
       tma_prefetch_desc(&tmB);
+      // Before waiting for the previous kernel: the WEIGHT half of the first stages of this CTA's first tile (nothing
+      // in a step writes weights). The activation half follows after pdl_wait().
+      int pre = 0;
+      if (static_cast<int>(blockIdx.x) < num_tiles) {
+        pre = num_kb < S ? num_kb : S;
+        const int n_blk0 = blockIdx.x / tiles_m;
+        for (int kb = 0; kb < pre; ++kb) {
+          const uint32_t full = smem_u32(&bars[kb]);
+          mbar_arrive_expect_tx(full, stage_bytes);
+          tma_load_2d(smem_u32(smem + kb * stage_bytes) + stage_bytes_a, &tmB, full, kb * BK, n_blk0 * BN);
+        }
+      }
+      pdl_wait();
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
         const int m_blk = t % tiles_m, n_blk = t / tiles_m;
         for (int kb = 0; kb < num_kb; ++kb) {
+          const uint32_t full = smem_u32(&bars[stage]);
+          const uint32_t sa = smem_u32(smem + stage * stage_bytes);
+          if (pre > 0) {
+            // this stage's barrier is armed and its weights are on their way: add the activations
+            --pre;
+            tma_load_2d(sa, &tmA, full, kb * BK, m_blk * BM);
+            if (++stage == S) {
+              stage = 0;
+              phase ^= 1;
+            }
+            continue;
+          }
           if (!mbar_wait(smem_u32(&bars[S + stage]), phase ^ 1, abort_flag, status, ST_TIMEOUT_EMPTY)) {
             ok = false;
             break;
           }
-          const uint32_t full = smem_u32(&bars[stage]);
           mbar_arrive_expect_tx(full, stage_bytes);
-          const uint32_t sa = smem_u32(smem + stage * stage_bytes);
           tma_load_2d(sa, &tmA, full, kb * BK, m_blk * BM);
           tma_load_2d(sa + stage_bytes_a, &tmB, full, kb * BK, n_blk * BN);
           if (++stage == S) {
@@ -163,6 +187,7 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
   } else {
     // ------------------------------------------------------------ epilogue (warps 2..5)
+    pdl_wait();                 // C may still be read by the previous kernel
     const int quad = warp & 3;  // TMEM lane quadrant this warp may read
     int acc = 0;
     uint32_t acc_phase = 0;
@@ -172,28 +197,33 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       tc_fence_after();
       const int row = m_blk * BM + quad * 32 + lane;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN;
+      constexpr int CW = (BN % 32 == 0) ? 32 : 16;   // columns per TMEM load (tiles of 48, 208, ... columns use 16)
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(taddr + c * 32, r);
-        tmem_ld_wait();
-        const int col0 = n_blk * BN + c * 32;
+      for (int c = 0; c < BN / CW; ++c) {
+        uint32_t r[CW];
+        if constexpr (CW == 32) {
+          tmem_ld_32x32(taddr + c * CW, r);
+          tmem_ld_wait_dep(r);
+        } else {
+          tmem_ld_32x16_sync(taddr + c * CW, r);
+        }
+        const int col0 = n_blk * BN + c * CW;
         if (row < M) {
           if constexpr (OUT_F32) {
             float* dst = reinterpret_cast<float*>(Cout) + static_cast<size_t>(row) * ldc + col0;
-            if (col0 + 32 <= N && (ldc & 3) == 0) {
+            if (col0 + CW <= N && (ldc & 3) == 0) {
 #pragma unroll
-              for (int j = 0; j < 8; ++j)
+              for (int j = 0; j < CW / 4; ++j)
                 reinterpret_cast<uint4*>(dst)[j] = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
             } else {
-              for (int j = 0; j < 32; ++j)
+              for (int j = 0; j < CW; ++j)
                 if (col0 + j < N) dst[j] = __uint_as_float(r[j]);
             }
           } else {
             __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(Cout) + static_cast<size_t>(row) * ldc + col0;
-            if (col0 + 32 <= N && (ldc & 7) == 0) {
+            if (col0 + CW <= N && (ldc & 7) == 0) {
 #pragma unroll
-              for (int j = 0; j < 4; ++j) {
+              for (int j = 0; j < CW / 8; ++j) {
                 uint4 v;
                 v.x = pack_bf2(__uint_as_float(r[8 * j + 0]), __uint_as_float(r[8 * j + 1]));
                 v.y = pack_bf2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
@@ -202,7 +232,7 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 reinterpret_cast<uint4*>(dst)[j] = v;
               }
             } else {
-              for (int j = 0; j < 32; ++j)
+              for (int j = 0; j < CW; ++j)
                 if (col0 + j < N) dst[j] = f2bf(__uint_as_float(r[j]));
             }
           }
@@ -263,8 +293,7 @@ int launch_gemm(const void* A, const void* B, void* C, int M, int N, int K, int 
   int grid = num_sms(dev);
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
   if (tiles < grid) grid = tiles;
-  kern<<<grid, kThreads, Cfg::kSmemBytes, stream>>>(tmA, tmB, C, M, N, K, ldc, a_rows, S, ixh::status_word(dev));
-  IX_CUDA(cudaGetLastError());
+  IX_CUDA(ixh::launch_pdl(kern, dim3(grid), dim3(kThreads), Cfg::kSmemBytes, stream, tmA, tmB, C, M, N, K, ldc, a_rows, S, ixh::status_word(dev)));
   return ixh::IX_OK;
 }
 
@@ -272,7 +301,7 @@ int launch_gemm(const void* A, const void* B, void* C, int M, int N, int K, int 
 
 // C[M,N] = A[M,K] * B[N,K]^T. A, B bf16 row-major with leading dims lda/ldb (elements,
 // multiples of 8); C bf16 (out_f32=0) or fp32 (out_f32=1) with leading dim ldc.
-// bn selects the N tile (32/64/128/256; 0 = choose from the shape).
+// bn selects the N tile (32/48/64/128/208/256; 0 = choose from the shape).
 IX_API int ix_gemm_bf16_nt(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb,
                            int ldc, int out_f32, int bn, int max_ctas, void* stream) {
   if (M <= 0 || N <= 0 || K <= 0) return ixh::fail(ixh::IX_EARG, "gemm: empty problem %dx%dx%d", M, N, K);
@@ -286,7 +315,24 @@ IX_API int ix_gemm_bf16_nt(const void* A, const void* B, void* C, int M, int N, 
     const int sms = num_sms(dev);
     const int tm = (M + BM - 1) / BM;
     bn = 256;
-    while (bn > 32 && tm * ((N + bn - 1) / bn) * 5 < sms * 3) bn >>= 1;   // widest tile that still gives >= 0.6 CTAs per SM
+    if (tm > 1) {
+      // training / prefill sizes: the widest tile that still gives >= 0.6 CTAs per SM
+      while (bn > 32 && tm * ((N + bn - 1) / bn) * 5 < sms * 3) bn >>= 1;
+    } else {
+      // decode sizes (one row of tiles, weight streaming): of the widths below, the one that keeps the most SMs busy
+      // over whole waves; ties go to the wider tile, which re-reads the activations least. A pure function of N.
+      const int cand[6] = {256, 208, 128, 64, 48, 32};
+      double best = -1.0;
+      for (int i = 0; i < 6; ++i) {
+        const long long tiles = (N + cand[i] - 1) / cand[i];
+        const long long waves = (tiles + sms - 1) / sms;
+        const double util = static_cast<double>(tiles) / static_cast<double>(waves * sms);
+        if (util > best + 1e-9) {
+          best = util;
+          bn = cand[i];
+        }
+      }
+    }
   }
 #define IX_GEMM_CASE(BN_)                                                                                     \
   case BN_:                                                                                                   \
@@ -294,8 +340,10 @@ IX_API int ix_gemm_bf16_nt(const void* A, const void* B, void* C, int M, int N, 
                    : launch_gemm<BN_, false>(A, B, C, M, N, K, lda, ldb, ldc, max_ctas, s, dev);
   switch (bn) {
     IX_GEMM_CASE(32)
+    IX_GEMM_CASE(48)
     IX_GEMM_CASE(64)
     IX_GEMM_CASE(128)
+    IX_GEMM_CASE(208)
     IX_GEMM_CASE(256)
     default:
       return ixh::fail(ixh::IX_EARG, "gemm: unsupported bn=%d", bn);

@@ -42,7 +42,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     const long long* __restrict__ row_dst, int R, int E, int N, int K, int ldc, int rows_b_per_expert,
                     int a_rows, int S, int* __restrict__ status) {
   constexpr int kMmaN = (EPI == EPI_GLU) ? 2 * BN : BN;
-  constexpr int kTmemCols = (2 * kMmaN < 32) ? 32 : 2 * kMmaN;
+  constexpr int kTmemCols = tmem_cols_pow2(2 * kMmaN);
   static_assert(kTmemCols <= 512, "accumulators exceed TMEM");
   const int stage_bytes_a = a_rows * BK * 2;
   const int stage_bytes = stage_bytes_a + kMmaN * BK * 2;
@@ -60,6 +60,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   const int tiles_n = N / BN;
   const int num_kb = K / BK;
 
+  pdl_launch_dependents();
+  if (offs != nullptr) pdl_wait();   // the row offsets come from the routing kernels that precede this one
   // offs == nullptr: one group made of all R rows (the dense MLP uses this kernel for its fused GLU epilogue)
   for (int e = threadIdx.x; e <= E; e += kThreads) s_row_start[e] = offs ? offs[e] : (e == 0 ? 0 : R);
   if (threadIdx.x == 0) {
@@ -112,6 +114,22 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     if (elect_one()) {
       tma_prefetch_desc(&tmA);
       tma_prefetch_desc(&tmB);
+      // weights of the first stages of this CTA's first tile go out before the wait for the previous kernel
+      int pre = 0;
+      if (static_cast<int>(blockIdx.x) < num_tiles) {
+        int e, row0, row_end, n_blk;
+        decode(blockIdx.x, e, row0, row_end, n_blk);
+        const int b_row = e * rows_b_per_expert + n_blk * BN;
+        pre = num_kb < S ? num_kb : S;
+        for (int kb = 0; kb < pre; ++kb) {
+          const uint32_t full = smem_u32(&bars[kb]);
+          mbar_arrive_expect_tx(full, stage_bytes);
+          const uint32_t sb = smem_u32(smem + kb * stage_bytes) + stage_bytes_a;
+          tma_load_2d(sb, &tmB, full, kb * BK, b_row);
+          if (EPI == EPI_GLU) tma_load_2d(sb + BN * BK * 2, &tmB, full, kb * BK, b_row + N);
+        }
+      }
+      pdl_wait();
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -120,13 +138,22 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         decode(t, e, row0, row_end, n_blk);
         const int b_row = e * rows_b_per_expert + n_blk * BN;
         for (int kb = 0; kb < num_kb; ++kb) {
+          const uint32_t full = smem_u32(&bars[stage]);
+          const uint32_t sa = smem_u32(smem + stage * stage_bytes);
+          if (pre > 0) {
+            --pre;
+            tma_load_2d(sa, &tmA, full, kb * BK, row0);
+            if (++stage == S) {
+              stage = 0;
+              phase ^= 1;
+            }
+            continue;
+          }
           if (!mbar_wait(smem_u32(&bars[S + stage]), phase ^ 1, abort_flag, status, ST_TIMEOUT_EMPTY)) {
             ok = false;
             break;
           }
-          const uint32_t full = smem_u32(&bars[stage]);
           mbar_arrive_expect_tx(full, stage_bytes);
-          const uint32_t sa = smem_u32(smem + stage * stage_bytes);
           tma_load_2d(sa, &tmA, full, kb * BK, row0);
           tma_load_2d(sa + stage_bytes_a, &tmB, full, kb * BK, b_row);
           if (EPI == EPI_GLU) tma_load_2d(sa + stage_bytes_a + BN * BK * 2, &tmB, full, kb * BK, b_row + N);
@@ -173,6 +200,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       }
     }
   } else {
+    pdl_wait();   // outputs (and the per-row weights / destinations) belong to the previous kernels until they finish
     const int quad = warp & 3;
     int acc = 0;
     uint32_t acc_phase = 0;
@@ -299,8 +327,8 @@ int launch_grouped(const void* A, const void* B, void* C, const int* offs, const
   int grid = sms_of(dev);
   if (max_tiles > 0 && max_tiles < grid) grid = max_tiles;
   const int kSmem = S * stage_bytes + tail + kFixed;
-  kern<<<grid, kThreads, kSmem, stream>>>(tmA, tmB, C, offs, w_rows, row_dst, R, E, N, K, ldc, rows_b, a_rows, S, ixh::status_word(dev));
-  IX_CUDA(cudaGetLastError());
+  IX_CUDA(ixh::launch_pdl(kern, dim3(grid), dim3(kThreads), static_cast<size_t>(kSmem), stream, tmA, tmB, C, offs, w_rows, row_dst, R, E, N, K, ldc,
+                          rows_b, a_rows, S, ixh::status_word(dev)));
   return 0;
 }
 
@@ -318,10 +346,22 @@ IX_API int ix_moe_grouped_gemm(const void* A, const void* B, void* C, const void
   int dev = 0;
   IX_CUDA(cudaGetDevice(&dev));
   if (bn == 0) {
-    bn = 128;
-    // an upper bound of the m-tiles: every expert may add one ragged tile
-    const long long mt = (static_cast<long long>(R) + BM - 1) / BM + E;
-    while (bn > 32 && (N % bn || mt * (N / bn) < sms_of(dev))) bn >>= 1;
+    // an upper bound of the m-tiles: every expert may add one ragged tile (exact for a single group)
+    const long long mt = (static_cast<long long>(R) + BM - 1) / BM + (offs ? E : 0);
+    const int sms = sms_of(dev);
+    const int cand[4] = {128, 96, 64, 32};
+    double best = -1.0;
+    bn = 32;
+    for (int i = 0; i < 4; ++i) {
+      if (N % cand[i]) continue;
+      const long long tiles = mt * (N / cand[i]);
+      const long long waves = (tiles + sms - 1) / sms;
+      const double util = static_cast<double>(tiles) / static_cast<double>(waves * sms);
+      if (util > best + 1e-9) {       // most SMs busy over whole waves; ties go to the wider tile
+        best = util;
+        bn = cand[i];
+      }
+    }
   }
   if (N % bn) return ixh::fail(ixh::IX_EARG, "grouped gemm: N=%d is not a multiple of the tile width %d", N, bn);
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
@@ -332,7 +372,8 @@ IX_API int ix_moe_grouped_gemm(const void* A, const void* B, void* C, const void
   const int max_tiles = max_tiles_ll > 1 << 30 ? 1 << 30 : static_cast<int>(max_tiles_ll);
 #define IX_GG(BN_, EPI_) \
   if (bn == BN_ && epi == EPI_) return launch_grouped<BN_, EPI_>(A, B, C, o, w, rd, R, E, N, K, lda, K, ldc, max_tiles, s, dev);
-  IX_GG(128, 0) IX_GG(64, 0) IX_GG(32, 0) IX_GG(128, 1) IX_GG(64, 1) IX_GG(32, 1) IX_GG(128, 2) IX_GG(64, 2) IX_GG(32, 2)
+  IX_GG(128, 0) IX_GG(96, 0) IX_GG(64, 0) IX_GG(32, 0) IX_GG(128, 1) IX_GG(96, 1) IX_GG(64, 1) IX_GG(32, 1)
+  IX_GG(128, 2) IX_GG(96, 2) IX_GG(64, 2) IX_GG(32, 2)
 #undef IX_GG
   return ixh::fail(ixh::IX_EARG, "grouped gemm: no kernel for bn=%d epi=%d", bn, epi);
 }

@@ -115,6 +115,8 @@ rmsnorm_cta_row_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16*
                        __nv_bfloat16* __restrict__ res_out, float* __restrict__ rstd_out, int N, float eps,
                        long long ldx, long long ldy) {
   __shared__ float s_c[4][32];
+  pdl_launch_dependents();
+  pdl_wait();
   const int row = blockIdx.x;
   const int u = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nvec = N >> 3;
@@ -181,6 +183,8 @@ qk_norm_rope_kernel(const __nv_bfloat16* __restrict__ qkv, long long ldqkv, cons
                     const __nv_bfloat16* __restrict__ kw, __nv_bfloat16* __restrict__ q_out,
                     __nv_bfloat16* __restrict__ k_out, __nv_bfloat16* __restrict__ v_out, int T, int Hq, int Hkv,
                     int D, int rot_dim, float eps, int q_gate) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int Htot = Hq + 2 * Hkv;
   const long long wid = static_cast<long long>(blockIdx.x) * 4 + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
@@ -417,11 +421,11 @@ IX_API int ix_rmsnorm(const void* x, const void* res, const void* w, void* y, vo
   if (rows <= 1024 && N <= 8192) {
     // few rows: a CTA per row (more threads per row, one memory round trip); same bits as the warp-per-row kernel
     if (res) {
-      if (zero_centered) rmsnorm_cta_row_kernel<true, true><<<rows, 128, 0, s>>>(X, R, W, Y, RO, RS, N, eps, ldx, ldy);
-      else rmsnorm_cta_row_kernel<true, false><<<rows, 128, 0, s>>>(X, R, W, Y, RO, RS, N, eps, ldx, ldy);
+      if (zero_centered) IX_CUDA(ixh::launch_pdl(rmsnorm_cta_row_kernel<true, true>, dim3(rows), dim3(128), 0, s, X, R, W, Y, RO, RS, N, eps, ldx, ldy));
+      else IX_CUDA(ixh::launch_pdl(rmsnorm_cta_row_kernel<true, false>, dim3(rows), dim3(128), 0, s, X, R, W, Y, RO, RS, N, eps, ldx, ldy));
     } else {
-      if (zero_centered) rmsnorm_cta_row_kernel<false, true><<<rows, 128, 0, s>>>(X, R, W, Y, RO, RS, N, eps, ldx, ldy);
-      else rmsnorm_cta_row_kernel<false, false><<<rows, 128, 0, s>>>(X, R, W, Y, RO, RS, N, eps, ldx, ldy);
+      if (zero_centered) IX_CUDA(ixh::launch_pdl(rmsnorm_cta_row_kernel<false, true>, dim3(rows), dim3(128), 0, s, X, R, W, Y, RO, RS, N, eps, ldx, ldy));
+      else IX_CUDA(ixh::launch_pdl(rmsnorm_cta_row_kernel<false, false>, dim3(rows), dim3(128), 0, s, X, R, W, Y, RO, RS, N, eps, ldx, ldy));
     }
     IX_CUDA(cudaGetLastError());
     return 0;
@@ -448,13 +452,13 @@ IX_API int ix_qk_norm_rope(const void* qkv, long long ldqkv, const void* positio
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   const long long warps = static_cast<long long>(T) * (Hq + 2 * Hkv);
   const int grid = static_cast<int>((warps + 3) / 4);
-#define IX_QKR(N_, Z_)                                                                                        \
-  qk_norm_rope_kernel<N_, Z_><<<grid, 128, 0, s>>>(                                                           \
-      static_cast<const __nv_bfloat16*>(qkv), ldqkv, static_cast<const int*>(positions),                      \
-      static_cast<const long long*>(slots), static_cast<const float*>(cos_tab),                               \
-      static_cast<const float*>(sin_tab), static_cast<const __nv_bfloat16*>(qw),                              \
-      static_cast<const __nv_bfloat16*>(kw), static_cast<__nv_bfloat16*>(q_out),                              \
-      static_cast<__nv_bfloat16*>(k_out), static_cast<__nv_bfloat16*>(v_out), T, Hq, Hkv, D, rot_dim, eps, q_gate)
+#define IX_QKR(N_, Z_)                                                                                                  \
+  IX_CUDA(ixh::launch_pdl(qk_norm_rope_kernel<N_, Z_>, dim3(grid), dim3(128), 0, s, static_cast<const __nv_bfloat16*>(qkv), \
+                          ldqkv, static_cast<const int*>(positions), static_cast<const long long*>(slots),              \
+                          static_cast<const float*>(cos_tab), static_cast<const float*>(sin_tab),                       \
+                          static_cast<const __nv_bfloat16*>(qw), static_cast<const __nv_bfloat16*>(kw),                 \
+                          static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(k_out),                       \
+                          static_cast<__nv_bfloat16*>(v_out), T, Hq, Hkv, D, rot_dim, eps, q_gate))
   if (qk_norm) {
     if (zero_centered) IX_QKR(true, true);
     else IX_QKR(true, false);

@@ -54,3 +54,14 @@ IX_API void* ix_status_ptr() {
   if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
   return ixh::status_word(dev);
 }
+
+namespace ixh {
+static int g_pdl = 1;
+bool pdl_enabled() { return g_pdl != 0; }
+}  // namespace ixh
+
+// 1 (default): kernels that support it are launched with programmatic stream serialization; 0: plain stream order.
+IX_API int ix_set_pdl(int on) {
+  ixh::g_pdl = on ? 1 : 0;
+  return 0;
+}

@@ -59,14 +59,46 @@ class Sampler:
         self.gen = torch.Generator(device=self.device)
         self.gen.manual_seed(seed)
         self.leaves = leaves
+        self.seed = int(seed)
+        self.calls = 0
+        self._temp_cache: dict = {}
 
     def reseed(self, seed: int) -> None:
         self.gen.manual_seed(seed)
+        self.seed, self.calls = int(seed), 0
+
+    def _fused(self, logits: torch.Tensor, params: list[SamplingParams]):
+        """One pass over the bf16 logits (csrc/sampler.cu): Gumbel-max with counter-based noise, then the chosen tokens'
+        log-probabilities from the row-invariant kernel the trainer uses."""
+        from ..ops import _native
+
+        n, V = logits.shape
+        key = tuple(p.temperature for p in params)
+        inv = self._temp_cache.get(key)
+        if inv is None:
+            if len(self._temp_cache) > 64:
+                self._temp_cache.clear()
+            inv = torch.tensor([0.0 if t == 0.0 else 1.0 / t for t in key], dtype=torch.float32, device=logits.device)
+            self._temp_cache[key] = inv
+        L = _native.lib()
+        m = L.ix_sampler_scratch_elems(n)
+        sv = torch.empty(m, dtype=torch.float32, device=logits.device)
+        si = torch.empty(m, dtype=torch.int32, device=logits.device)
+        tokens = torch.empty(n, dtype=torch.int64, device=logits.device)
+        self.calls += 1
+        _native.check(L.ix_sample_gumbel(logits.data_ptr(), logits.stride(0), n, V, inv.data_ptr(), self.seed & 0xFFFFFFFFFFFFFFFF,
+                                         self.calls & 0xFFFFFFFF, sv.data_ptr(), si.data_ptr(), tokens.data_ptr(), _native.stream()),
+                      "ix_sample_gumbel")
+        logprobs, _ = F.token_logprobs(logits, tokens, self.leaves)
+        return tokens, logprobs
 
     @torch.no_grad()
     def __call__(self, logits: torch.Tensor, params: list[SamplingParams]):
         """logits [n, V] -> (token ids int64 [n], raw logprobs fp32 [n])."""
         n, V = logits.shape
+        untruncated = all(p.top_p >= 1.0 and p.top_k <= 0 and p.min_p <= 0.0 for p in params)
+        if untruncated and logits.is_cuda and logits.dtype == torch.bfloat16 and logits.stride(1) == 1 and logits.stride(0) % 8 == 0:
+            return self._fused(logits, params)
         x = logits.float()
         uniform = all(p.temperature == 1.0 and p.top_p >= 1.0 and p.top_k <= 0 and p.min_p <= 0.0 for p in params)
         if not uniform:

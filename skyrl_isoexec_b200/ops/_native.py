@@ -25,6 +25,7 @@ _P, _I, _L, _F = C.c_void_p, C.c_int, C.c_longlong, C.c_float
 
 _SIGS = {
     "ix_init": [],
+    "ix_set_pdl": [_I],
     "ix_read_status": [],
     "ix_version": [],
     "ix_gemm_bf16_nt": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P],
@@ -51,6 +52,8 @@ _SIGS = {
     "ix_router_topk": [_P, _L, _P, _I, _I, _I, _I, _I, _P, _P, _P, _P],
     "ix_moe_combine": [_P, _P, _P, _P, _I, _I, _I, _I, _P],
     "ix_scale_rows": [_P, _P, _L, _I, _P],
+    "ix_sampler_scratch_elems": [_I],
+    "ix_sample_gumbel": [_P, _L, _I, _I, _P, C.c_ulonglong, C.c_uint, _P, _P, _P, _P],
     "ix_moe_grouped_gemm": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     "ix_gdn_conv": [_P, _L, _P, _P, _P, _P, _P, _L, _I, _I, _I, _P],
     "ix_gdn_conv_state": [_P, _L, _P, _P, _I, _I, _I, _I, _P],
@@ -86,6 +89,8 @@ def lib():
             continue
         fn.argtypes = sig
         fn.restype = C.c_int
+    if os.environ.get("ISOEXEC_B200_PDL", "1") == "0" and hasattr(h, "ix_set_pdl"):
+        h.ix_set_pdl(0)          # plain stream order instead of programmatic dependent launches
     _lib = h
     return h
 

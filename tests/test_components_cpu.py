@@ -390,3 +390,14 @@ def test_trainer_eval_and_hf_export_hooks(tmp_path):
     import os
 
     assert sorted(os.listdir(tmp_path / "hf" / "global_step_2")) == ["config.json", "model.safetensors"]
+
+
+def test_preflight_gate_ready_and_blocks_on_a_missing_kernel(monkeypatch, capsys):
+    from skyrl_isoexec_b200.core import preflight
+
+    assert preflight.main(["--model", "qwen3-8b"]) == 0
+    assert "PREFLIGHT: READY" in capsys.readouterr().out
+    monkeypatch.setattr(preflight, "check_native", lambda: ["libisoexec_b200.so is missing"])
+    assert preflight.main(["--model", "tiny-qwen3"]) == 1
+    out = capsys.readouterr().out
+    assert "PREFLIGHT: BLOCKED" in out and "native         BLOCKED" in out
