@@ -1,6 +1,7 @@
 """Small, self-terminating kernel workloads for ncu captures (one kernel family per mode).
 
-    python profiles/run_kernels.py attn_decode | attn_prefill | gemm_large | gemm_decode | logprob | rmsnorm
+    python profiles/run_kernels.py attn_decode | attn_prefill | gemm_large | gemm_decode | logprob | rmsnorm |
+                                   glu_decode | moe_grouped | rmsnorm_decode | sampler | rmsnorm_bwd
 
 Each mode allocates well under 1 GB, launches the kernel a handful of times and exits.
 """
@@ -55,6 +56,48 @@ elif mode == "rmsnorm":
     w = torch.ones(4096, device=dev).bfloat16()
     for _ in range(4):
         F.rmsnorm_fwd(x, w, 1e-6, False, r)
+elif mode == "glu_decode":
+    # dense MLP in a decode step: gate_up GEMM with the SwiGLU epilogue (grouped kernel, one group), 64 tokens
+    from skyrl_isoexec_b200.ops import moe
+    x = torch.randn(64, 4096, device=dev).bfloat16()
+    w = (torch.randn(1, 24576, 4096, device=dev) * 0.02).bfloat16()
+    with torch.no_grad():
+        for _ in range(4):
+            moe.grouped_gemm(x, w, None, moe.EPI_GLU)
+elif mode == "moe_grouped":
+    # one Qwen3-30B-A3B expert layer: 4096 tokens x top-8 over 128 experts (fc1 + SwiGLU x gate weight, then fc2)
+    from skyrl_isoexec_b200.ops import moe
+    T, E, k, H, Fd = 4096, 128, 8, 2048, 768
+    gate_up = (torch.randn(E, 2 * Fd, H, device=dev) * 0.03).bfloat16()
+    down = (torch.randn(E, H, Fd, device=dev) * 0.03).bfloat16()
+    y = torch.randn(T, H, device=dev).bfloat16()
+    idx = torch.stack([torch.randperm(E, device=dev)[:k] for _ in range(T)]).int()
+    order, counts, pos = moe.build_dispatch(idx, E)
+    x_rows = y.index_select(0, torch.div(order, k, rounding_mode="floor"))
+    w_rows = torch.rand(T * k, device=dev)
+    offs = moe.counts_to_offsets(counts)
+    with torch.no_grad():
+        for _ in range(4):
+            moe.expert_rows_grouped(x_rows, w_rows, offs, gate_up, down)
+elif mode == "rmsnorm_decode":
+    x = torch.randn(64, 4096, device=dev).bfloat16()
+    r = torch.randn_like(x)
+    w = torch.ones(4096, device=dev).bfloat16()
+    for _ in range(4):
+        F.rmsnorm_fwd(x, w, 1e-6, False, r)
+elif mode == "rmsnorm_bwd":
+    x = torch.randn(8192, 4096, device=dev).bfloat16().requires_grad_()
+    r = torch.randn(8192, 4096, device=dev).bfloat16().requires_grad_()
+    w = torch.ones(4096, device=dev).bfloat16().requires_grad_()
+    for _ in range(3):
+        y, h = F.rmsnorm(x, w, 1e-6, False, r)
+        (y.float().sum() + h.float().sum()).backward()
+elif mode == "sampler":
+    from skyrl_isoexec_b200.engine.sampler import Sampler, SamplingParams
+    lg = torch.randn(64, 151936, device=dev).bfloat16()
+    sm = Sampler(dev, 0)
+    for _ in range(4):
+        sm(lg, [SamplingParams()] * 64)
 torch.cuda.synchronize()
 assert _native.read_status() == 0
 print("ok", mode)

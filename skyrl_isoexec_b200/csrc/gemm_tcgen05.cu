@@ -322,14 +322,17 @@ IX_API int ix_gemm_bf16_nt(const void* A, const void* B, void* C, int M, int N, 
       // decode sizes (one row of tiles, weight streaming): of the widths below, the one that keeps the most SMs busy
       // over whole waves; ties go to the wider tile, which re-reads the activations least. A pure function of N.
       const int cand[6] = {256, 208, 128, 64, 48, 32};
-      double best = -1.0;
+      double util[6], best = -1.0;
       for (int i = 0; i < 6; ++i) {
         const long long tiles = (N + cand[i] - 1) / cand[i];
         const long long waves = (tiles + sms - 1) / sms;
-        const double util = static_cast<double>(tiles) / static_cast<double>(waves * sms);
-        if (util > best + 1e-9) {
-          best = util;
+        util[i] = static_cast<double>(tiles) / static_cast<double>(waves * sms);
+        if (util[i] > best) best = util[i];
+      }
+      for (int i = 0; i < 6; ++i) {
+        if (util[i] >= best - 0.05) {   // the widest tile within 5% of the best utilisation
           bn = cand[i];
+          break;
         }
       }
     }

@@ -350,16 +350,21 @@ IX_API int ix_moe_grouped_gemm(const void* A, const void* B, void* C, const void
     const long long mt = (static_cast<long long>(R) + BM - 1) / BM + (offs ? E : 0);
     const int sms = sms_of(dev);
     const int cand[4] = {128, 96, 64, 32};
-    double best = -1.0;
-    bn = 32;
+    double util[4], best = -1.0;
     for (int i = 0; i < 4; ++i) {
+      util[i] = -1.0;
       if (N % cand[i]) continue;
       const long long tiles = mt * (N / cand[i]);
       const long long waves = (tiles + sms - 1) / sms;
-      const double util = static_cast<double>(tiles) / static_cast<double>(waves * sms);
-      if (util > best + 1e-9) {       // most SMs busy over whole waves; ties go to the wider tile
-        best = util;
+      util[i] = static_cast<double>(tiles) / static_cast<double>(waves * sms);
+      if (util[i] > best) best = util[i];
+    }
+    // the widest tile within 5% of the best whole-wave utilisation: narrow tiles only where they fill the machine
+    bn = 32;
+    for (int i = 0; i < 4; ++i) {
+      if (util[i] >= 0.0 && util[i] >= best - 0.05) {
         bn = cand[i];
+        break;
       }
     }
   }
