@@ -129,6 +129,11 @@ def contract_hash(contract: M.ExecutionContract | None = None) -> str:
     return h
 
 
+def contract_hash_or_none() -> str | None:
+    """The stamped hash, or None in a process that has built no contract (tools, unit tests of a transport)."""
+    return contract_hash() if _process_contract is not None else None
+
+
 def assert_contract_agreement(mine: str, theirs: str | None, who: str = "peer") -> None:
     if theirs is None:
         raise ContractMismatch(f"{who} sent no contract hash: refusing to run without a handshake")

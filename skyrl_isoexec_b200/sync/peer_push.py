@@ -41,7 +41,7 @@ def export_engine_buffer(model, contract_hash: str | None = None) -> PeerPushIni
     flat = model.store.flat
     assert flat.is_cuda, "peer push needs the engine's parameters on a GPU"
     handle = flat.untyped_storage()._share_cuda_()
-    return PeerPushInitInfo(contract_hash if contract_hash is not None else P.contract_hash(), flat.numel(),
+    return PeerPushInitInfo(contract_hash if contract_hash is not None else P.contract_hash_or_none(), flat.numel(),
                             str(flat.dtype).replace("torch.", ""), handle)
 
 
@@ -88,7 +88,7 @@ class PeerPushSender:
 
 class PeerPushReceiver:
     def __init__(self, info: PeerPushInitInfo, model):
-        mine = P.contract_hash()
+        mine = P.contract_hash_or_none()
         if info.contract_hash is not None and mine is not None and info.contract_hash != mine:
             raise RuntimeError(f"weight sync refused: trainer contract {info.contract_hash} != engine contract {mine}")
         self.model = model

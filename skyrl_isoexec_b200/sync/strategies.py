@@ -241,7 +241,13 @@ class BroadcastReceiver:
 
 # ------------------------------------------------------------------------------------ factory
 def create_init_info(strategy: str, **kw) -> WeightSyncInitInfo:
-    kw.setdefault("contract_hash", P.contract_hash())
+    """``peer`` (CUDA-IPC push) is built on the ENGINE rank from its model: ``create_init_info("peer", model=m)``."""
+    if strategy == "peer":
+        from .peer_push import export_engine_buffer
+
+        return export_engine_buffer(kw["model"], kw.get("contract_hash"))
+    if "contract_hash" not in kw:
+        kw["contract_hash"] = P.contract_hash()
     if strategy == "shared":
         return SharedInitInfo(**kw)
     if strategy in ("broadcast", "nccl", "gloo"):
@@ -249,9 +255,21 @@ def create_init_info(strategy: str, **kw) -> WeightSyncInitInfo:
     raise ValueError(f"unknown weight sync strategy {strategy!r}")
 
 
-def create_sender(init_info: WeightSyncInitInfo, model):
-    return {"shared": SharedSender, "broadcast": BroadcastSender}[init_info.strategy_type()](init_info, model)
+def _peer_classes():
+    from .peer_push import PeerPushReceiver, PeerPushSender
+
+    return PeerPushSender, PeerPushReceiver
+
+
+def create_sender(init_info: WeightSyncInitInfo, model, **kw):
+    kind = init_info.strategy_type()
+    if kind == "peer":
+        return _peer_classes()[0](init_info, model, **kw)
+    return {"shared": SharedSender, "broadcast": BroadcastSender}[kind](init_info, model)
 
 
 def create_receiver(init_info: WeightSyncInitInfo, model):
-    return {"shared": SharedReceiver, "broadcast": BroadcastReceiver}[init_info.strategy_type()](init_info, model)
+    kind = init_info.strategy_type()
+    if kind == "peer":
+        return _peer_classes()[1](init_info, model)
+    return {"shared": SharedReceiver, "broadcast": BroadcastReceiver}[kind](init_info, model)

@@ -177,7 +177,7 @@ def load_checkpoint(path: str, policy, ps) -> tuple[dict, dict]:
                 full = _assemble_full(name, meta, shards)
                 dst.copy_(shard_of(full, model.store.specs[name], ps.tp_rank, ps.tp, ps.ep_rank, ps.ep).to(dst.dtype))
             if policy.opt.low_precision:
-                policy.opt.master.copy_(model.store.flat.float())
+                policy.opt.master.copy_(model.store.flat[policy.opt.lo:policy.opt.hi].float())
         policy.opt.step_count = int(shards[0]["lr_scheduler"]["step"])
     data_state = torch.load(os.path.join(path, "data.pt"), weights_only=False)
     trainer_state = torch.load(os.path.join(path, "trainer_state.pt"), weights_only=False)

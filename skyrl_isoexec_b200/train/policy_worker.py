@@ -42,9 +42,11 @@ class WorkerConfig:
     max_tokens_per_microbatch: int = 8192
     logprob_chunk_rows: int = 8192
     checkpoint_layers: bool = True
-    keep_last_layers: int = 0          # do not recompute the last n layers (trades activation memory for one forward of them)
+    keep_last_layers: int = 0          # do not recompute the last n layers (trades activation memory for one forward of
+                                       # them); -1 = as many as the free HBM allows (only with a sharded optimizer)
     want_entropy: bool = False
     overlap_grad_reduce: bool = True   # sum gradient buckets over DP during the last micro-batch's backward
+    shard_optimizer: bool = True       # fp32 master weights and Adam moments are cut over the data-parallel group
     optimizer: OptimizerConfig = field(default_factory=OptimizerConfig)
 
 
@@ -185,15 +187,29 @@ class FlatAdamW:
     norm and clip coefficient are computed on the device in a fixed order; nothing syncs with
     the host unless the caller reads the norm."""
 
-    def __init__(self, model: DecoderLM, cfg: OptimizerConfig):
+    def __init__(self, model: DecoderLM, cfg: OptimizerConfig, shard: tuple | None = None):
+        """``shard = (index, count, process group)``: this rank keeps the fp32 master weights and both moments of one
+        contiguous slice of the flat buffer only (the distributed optimizer of the reference's Megatron backend,
+        B/distributed/megatron/megatron_strategy.py:281-323, and what FSDP2 does to optimizer state). Gradients are still
+        summed in full, so the norm, the clip coefficient and every updated weight have the bits of the unsharded run;
+        after the update each rank broadcasts its slice of the new low-precision weights."""
         self.model, self.cfg = model, cfg
         flat = model.store.flat
         self.n = flat.numel()
         dev = flat.device
         self.low_precision = flat.dtype != torch.float32
-        self.master = flat.detach().float().clone() if self.low_precision else flat.detach()
-        self.exp_avg = torch.zeros(self.n, dtype=torch.float32, device=dev)
-        self.exp_avg_sq = torch.zeros(self.n, dtype=torch.float32, device=dev)
+        self.shard = shard if shard is not None and shard[1] > 1 else None
+        if self.shard is not None:
+            idx, cnt, _ = self.shard
+            per = (-(-self.n // cnt) + 63) // 64 * 64          # slices start on 256-byte boundaries
+            self.slices = [(min(self.n, r * per), min(self.n, (r + 1) * per)) for r in range(cnt)]
+            self.lo, self.hi = self.slices[idx]
+        else:
+            self.slices, self.lo, self.hi = [(0, self.n)], 0, self.n
+        own = flat.detach()[self.lo:self.hi]
+        self.master = own.float().clone() if self.low_precision else own
+        self.exp_avg = torch.zeros(self.hi - self.lo, dtype=torch.float32, device=dev)
+        self.exp_avg_sq = torch.zeros(self.hi - self.lo, dtype=torch.float32, device=dev)
         self.main_grad = torch.zeros(self.n, dtype=torch.float32, device=dev)
         self.step_count = 0
         self._sq = torch.zeros(1, dtype=torch.float32, device=dev)
@@ -335,15 +351,17 @@ class FlatAdamW:
             L = _native.lib()
             _native.check(L.ix_clip_coef(sq.data_ptr(), c.max_grad_norm, self._coef.data_ptr(), self._norm.data_ptr(),
                                          _native.stream()), "ix_clip_coef")
-            _native.check(L.ix_adamw(self.master.data_ptr(), self.exp_avg.data_ptr(), self.exp_avg_sq.data_ptr(),
-                                     self.main_grad.data_ptr(), flat.data_ptr() if self.low_precision else None,
-                                     self.n, 1, lr, c.beta1, c.beta2, c.eps, c.weight_decay, self.step_count,
-                                     self._coef.data_ptr(), _native.stream()), "ix_adamw")
+            if self.hi > self.lo:
+                _native.check(L.ix_adamw(self.master.data_ptr(), self.exp_avg.data_ptr(), self.exp_avg_sq.data_ptr(),
+                                         self.main_grad.data_ptr() + 4 * self.lo,
+                                         flat.data_ptr() + flat.element_size() * self.lo if self.low_precision else None,
+                                         self.hi - self.lo, 1, lr, c.beta1, c.beta2, c.eps, c.weight_decay, self.step_count,
+                                         self._coef.data_ptr(), _native.stream()), "ix_adamw")
         else:
             norm = sq.sqrt()
             self._norm.copy_(norm)
             coef = torch.clamp(c.max_grad_norm / (norm + 1e-6), max=1.0) if c.max_grad_norm > 0 else torch.ones(1)
-            g = self.main_grad * coef
+            g = self.main_grad[self.lo:self.hi] * coef
             self.exp_avg.mul_(c.beta1).add_(g, alpha=1 - c.beta1)
             self.exp_avg_sq.mul_(c.beta2).addcmul_(g, g, value=1 - c.beta2)
             bc1, bc2 = 1 - c.beta1 ** self.step_count, 1 - c.beta2 ** self.step_count
@@ -351,22 +369,41 @@ class FlatAdamW:
                 self.master.mul_(1 - lr * c.weight_decay)
                 self.master.addcdiv_(self.exp_avg / bc1, (self.exp_avg_sq / bc2).sqrt() + c.eps, value=-lr)
                 if self.low_precision:
-                    flat.copy_(self.master.to(flat.dtype))
+                    flat[self.lo:self.hi].copy_(self.master.to(flat.dtype))
+        self._gather_weights()
         self.zero_grad()
         return self._norm
 
+    def _gather_weights(self) -> None:
+        """Sharded optimizer: every rank sends the slice it has just updated to the others."""
+        if self.shard is None:
+            return
+        _, cnt, group = self.shard
+        flat = self.model.store.flat.detach()
+        for r in range(cnt):
+            lo, hi = self.slices[r]
+            if hi > lo:
+                dist.broadcast(flat[lo:hi], src=dist.get_global_rank(group, r) if group is not None else r, group=group)
+
     def state_dict(self) -> dict:
         return {"master": self.master, "exp_avg": self.exp_avg, "exp_avg_sq": self.exp_avg_sq,
-                "step": self.step_count}
+                "step": self.step_count, "slice": (self.lo, self.hi, self.n)}
 
     def load_state_dict(self, sd: dict) -> None:
+        """Accepts the state of the same slice, or a full (unsharded) state, which is cut to this rank's slice."""
+        lo, hi, n = sd.get("slice", (0, self.n, self.n))
+        if n != self.n or not (lo <= self.lo and self.hi <= hi):
+            raise ValueError(f"optimizer state covers [{lo}, {hi}) of {n}; this rank needs [{self.lo}, {self.hi}) of {self.n}")
+        cut = slice(self.lo - lo, self.hi - lo)
         with torch.no_grad():
-            self.master.copy_(sd["master"])
-            self.exp_avg.copy_(sd["exp_avg"])
-            self.exp_avg_sq.copy_(sd["exp_avg_sq"])
+            self.master.copy_(sd["master"][cut])
+            self.exp_avg.copy_(sd["exp_avg"][cut])
+            self.exp_avg_sq.copy_(sd["exp_avg_sq"][cut])
             self.step_count = int(sd["step"])
             if self.low_precision:
-                self.model.store.flat.copy_(self.master.to(self.model.store.flat.dtype))
+                flat = self.model.store.flat
+                flat[self.lo:self.hi].copy_(self.master.to(flat.dtype))
+        self._gather_weights()
 
     def offload(self):
         """Move optimizer state to pinned host memory (the colocated rollout phase needs the HBM)."""
@@ -390,15 +427,61 @@ class PolicyWorker:
         self.algo = algo or alg.AlgorithmConfig()
         self.ps = model.ps
         self.device = model.device_
-        self.opt = FlatAdamW(model, self.cfg.optimizer)
+        ps = self.ps
+        shard = None
+        if self.cfg.shard_optimizer and ps.dp > 1 and ps.ep == 1 and ps.pp == 1 and dist.is_initialized():
+            shard = (ps.dp_rank, ps.dp, ps.dp_group)
+        self.opt = FlatAdamW(model, self.cfg.optimizer, shard=shard)
+        self._auto_keep = None
         self.launch_count = 0
 
     # ---------------------------------------------------------------- forward pieces
     def _ckpt_arg(self):
         if not (self.cfg.checkpoint_layers and torch.is_grad_enabled()):
             return False
-        keep = getattr(self.cfg, "keep_last_layers", 0)
+        keep = self.keep_layers()
         return True if keep <= 0 else max(0, len(self.model.layer_ids) - keep)
+
+    def keep_layers(self) -> int:
+        """Layers whose activations stay alive for the backward instead of being recomputed. ``-1`` in the config means
+        "what the spare HBM allows": 0 until one whole step has run with full recompute, then fixed from that step's
+        measured peak (see ``_calibrate_keep``)."""
+        keep = getattr(self.cfg, "keep_last_layers", 0)
+        if keep >= 0:
+            return keep
+        return self._auto_keep or 0
+
+    def activation_bytes_per_layer(self, tokens: int) -> int:
+        """What autograd keeps alive for one dense layer that is not recomputed: layer input, both residual sums, both
+        normed inputs, the o-projection output, fused QKV, rotated Q/K, attention output, gate|up and the activation."""
+        c = self.model.cfg
+        tp = max(1, self.ps.tp)
+        qkv = (c.num_q_heads * (2 if c.attn_output_gate else 1) + 2 * c.num_kv_heads) * c.head_dim // tp
+        qk = (c.num_q_heads + c.num_kv_heads) * c.head_dim // tp
+        attn = c.num_q_heads * c.head_dim // tp
+        per_token = 6 * c.hidden_size + qkv + qk + attn + 3 * c.ffn_size // tp
+        return 2 * per_token * tokens
+
+    def _calibrate_keep(self) -> None:
+        """After the first full step (rollout, scoring and update have each run once with full recompute): the HBM the
+        step never touched, less a margin, is given to activations of the last layers. Dense attention models on a
+        GPU only; every data-parallel rank takes the smallest answer so that steps stay balanced."""
+        if getattr(self.cfg, "keep_last_layers", 0) >= 0 or self._auto_keep is not None:
+            return
+        n = 0
+        c = self.model.cfg
+        if self.device.type == "cuda" and not c.has_moe and not c.has_gdn and self.cfg.checkpoint_layers:
+            total = torch.cuda.get_device_properties(self.device).total_memory
+            free_now, _ = torch.cuda.mem_get_info(self.device)
+            outside = total - free_now - torch.cuda.memory_reserved(self.device)   # context, NCCL, symmetric memory
+            headroom = total - outside - torch.cuda.max_memory_reserved(self.device)
+            per_layer = int(1.25 * self.activation_bytes_per_layer(self.cfg.max_tokens_per_microbatch))
+            n = max(0, min(len(self.model.layer_ids), int((headroom - (10 << 30)) // per_layer)))
+        if dist.is_initialized() and dist.get_world_size() > 1:
+            t = torch.tensor([n], dtype=torch.int64, device=self.device if self.device.type == "cuda" else "cpu")
+            dist.all_reduce(t, op=dist.ReduceOp.MIN)
+            n = int(t.item())
+        self._auto_keep = n
 
     def _run_model(self, mb: PackedMicroBatch, site: str):
         dev = self.device
@@ -528,7 +611,9 @@ class PolicyWorker:
     def optim_step(self) -> float:
         self.reduce_gradients()
         norm = self.opt.step(self.ps)
-        return float(norm.item())
+        out = float(norm.item())
+        self._calibrate_keep()
+        return out
 
     # ---------------------------------------------------------------- memory residency (colocated runs)
     def offload_optimizer(self):

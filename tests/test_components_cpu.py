@@ -401,3 +401,27 @@ def test_preflight_gate_ready_and_blocks_on_a_missing_kernel(monkeypatch, capsys
     assert preflight.main(["--model", "tiny-qwen3"]) == 1
     out = capsys.readouterr().out
     assert "PREFLIGHT: BLOCKED" in out and "native         BLOCKED" in out
+
+
+def test_weight_sync_factory_dispatches_the_peer_strategy(monkeypatch):
+    from skyrl_isoexec_b200.sync import peer_push, strategies
+
+    made = []
+
+    class _S:
+        def __init__(self, info, model, **kw):
+            made.append(("sender", kw))
+
+    class _R:
+        def __init__(self, info, model):
+            made.append(("receiver", {}))
+
+    monkeypatch.setattr(peer_push, "PeerPushSender", _S)
+    monkeypatch.setattr(peer_push, "PeerPushReceiver", _R)
+    info = peer_push.PeerPushInitInfo("h", 8, "bfloat16", None)
+    assert info.strategy_type() == "peer"
+    strategies.create_sender(info, None, from_master=None)
+    strategies.create_receiver(info, None)
+    assert made == [("sender", {"from_master": None}), ("receiver", {})]
+    with pytest.raises(ValueError):
+        strategies.create_init_info("carrier-pigeon", contract_hash="h")

@@ -1,5 +1,6 @@
 """Peer-memory collectives and tensor/data parallel paths on 2+ GPUs (skipped on smaller boxes).
 Ranks are child processes, one per GPU, over NCCL on 127.0.0.1; every kernel-side wait is bounded."""
+import datetime
 import os
 import socket
 
@@ -8,6 +9,9 @@ import torch
 import torch.multiprocessing as mp
 
 pytestmark = pytest.mark.gpu
+
+# a rank that raised leaves its peers in a collective: the process group gives up after this long instead of ten minutes
+_PG_TIMEOUT = datetime.timedelta(seconds=120)
 
 
 def _free_port():
@@ -28,7 +32,7 @@ def _worker(rank, world, port, q):
     import torch.distributed as dist
 
     torch.cuda.set_device(rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank), timeout=_PG_TIMEOUT)
     try:
         from skyrl_isoexec_b200.core.testing import bitwise_equal
         from skyrl_isoexec_b200.ops import _native
@@ -136,7 +140,7 @@ def _tp_worker(rank, world, port, q):
     import torch.distributed as dist
 
     torch.cuda.set_device(rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank), timeout=_PG_TIMEOUT)
     try:
         from skyrl_isoexec_b200.core.testing import bitwise_equal
         from skyrl_isoexec_b200.ops import _native, functional as F
@@ -282,7 +286,7 @@ def _ep_worker(rank, world, port, q):
     import torch.distributed as dist
 
     torch.cuda.set_device(rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank), timeout=_PG_TIMEOUT)
     try:
         from skyrl_isoexec_b200.core.testing import bitwise_equal
         from skyrl_isoexec_b200.ops import _native, moe
@@ -367,7 +371,7 @@ def _tp_model_worker(rank, world, port, q):
     import torch.distributed as dist
 
     torch.cuda.set_device(rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank), timeout=_PG_TIMEOUT)
     try:
         from skyrl_isoexec_b200.core.testing import count_bit_mismatches
         from skyrl_isoexec_b200.engine.llm_engine import EngineConfig, LLMEngine
@@ -441,7 +445,7 @@ def _ep_model_worker(rank, world, port, q):
     import torch.distributed as dist
 
     torch.cuda.set_device(rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank), timeout=_PG_TIMEOUT)
     try:
         from skyrl_isoexec_b200.core.testing import count_bit_mismatches
         from skyrl_isoexec_b200.engine.llm_engine import EngineConfig, LLMEngine
@@ -512,7 +516,7 @@ def _push_worker(rank, world, port, q):
     import torch.distributed as dist
 
     torch.cuda.set_device(rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank), timeout=_PG_TIMEOUT)
     try:
         from skyrl_isoexec_b200.models.config import get_config
         from skyrl_isoexec_b200.models.decoder import DecoderLM
@@ -545,6 +549,9 @@ def _push_worker(rank, world, port, q):
             master = model.store.flat.float() * 1.5
             PeerPushSender(box[0], model, from_master=master).send()
             q.put({"bytes": nbytes, "ms": e0.elapsed_time(e1)})
+    except Exception as e:  # noqa: BLE001
+        q.put({f"error_rank{rank}": repr(e)})
+        raise
     finally:
         dist.barrier()
         dist.destroy_process_group()
@@ -567,4 +574,5 @@ def test_weight_push_into_the_engine_over_peer_memory():
     for p in procs:
         p.join(timeout=60)
     print("weight push:", res)
+    assert not [k for k in res if k.startswith("error")], res
     assert res["same_bf16"] and res["same_cast"] and res["bytes"] > 0
