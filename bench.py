@@ -39,7 +39,8 @@ def parse():
     ap.add_argument("--response-len", type=int, default=2048)
     ap.add_argument("--micro-tokens", type=int, default=8192)
     ap.add_argument("--tp", type=int, default=1, help="tensor-parallel degree of trainer and engine (fused GEMM+collective kernels)")
-    ap.add_argument("--keep-last-layers", type=int, default=0, help="layers not recomputed in the backward (uses spare HBM)")
+    ap.add_argument("--keep-last-layers", type=int, default=0,
+                    help="layers not recomputed in the backward (uses spare HBM); -1 = as many as the first step's measured peak leaves room for")
     ap.add_argument("--layers", type=int, default=0, help="debug only: truncate the model (marks the run invalid)")
     return ap.parse_args()
 
@@ -203,6 +204,8 @@ def main():
             "clocks": sampler.summary(),
             "e2e": {"value": tokens / (wall_ms / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)},
             "gpu_launches": int(launches), "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2**30, 1),
+            "peak_reserved_gb": round(torch.cuda.max_memory_reserved() / 2**30, 1),
+            "layers_not_recomputed": int(trainer.policy.keep_layers()), "optimizer_sharded": trainer.policy.opt.shard is not None,
         }
         print(json.dumps(out))
     if world > 1:
