@@ -55,7 +55,11 @@ class PeerPushSender:
             raise ValueError(f"engine buffer ({info.numel} x {info.dtype}) does not match the trainer's layout "
                              f"({mine.numel()} x {mine.dtype}); use the broadcast strategy to reshard")
         storage = torch.UntypedStorage._new_shared_cuda(*info.ipc_handle)
-        self.remote = torch.tensor([], dtype=mine.dtype, device=mine.device).set_(storage, 0, (info.numel,))
+        # the mapping lives on the engine's device; this process reaches it by peer access, which torch turns on between
+        # two devices at their first direct copy
+        self.remote = torch.tensor([], dtype=mine.dtype, device=storage.device).set_(storage, 0, (info.numel,))
+        if self.remote.device != mine.device:
+            self.remote[:8].to(mine.device)
         self.src = from_master if from_master is not None else mine
         self.src_f32 = self.src.dtype == torch.float32
         if self.src_f32 and mine.dtype != torch.bfloat16:
