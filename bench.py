@@ -39,7 +39,7 @@ def parse():
     ap.add_argument("--response-len", type=int, default=2048)
     ap.add_argument("--micro-tokens", type=int, default=8192)
     ap.add_argument("--tp", type=int, default=1, help="tensor-parallel degree of trainer and engine (fused GEMM+collective kernels)")
-    ap.add_argument("--keep-last-layers", type=int, default=0,
+    ap.add_argument("--keep-last-layers", type=int, default=-1,
                     help="layers not recomputed in the backward (uses spare HBM); -1 = as many as the first step's measured peak leaves room for")
     ap.add_argument("--layers", type=int, default=0, help="debug only: truncate the model (marks the run invalid)")
     return ap.parse_args()

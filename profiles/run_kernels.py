@@ -1,7 +1,7 @@
 """Small, self-terminating kernel workloads for ncu captures (one kernel family per mode).
 
     python profiles/run_kernels.py attn_decode | attn_prefill | gemm_large | gemm_decode | logprob | rmsnorm |
-                                   glu_decode | moe_grouped | rmsnorm_decode | sampler | rmsnorm_bwd
+                                   glu_decode | moe_grouped | rmsnorm_decode | sampler | rmsnorm_bwd | attn_bwd
 
 Each mode allocates well under 1 GB, launches the kernel a handful of times and exits.
 """
@@ -92,6 +92,37 @@ elif mode == "rmsnorm_bwd":
     for _ in range(3):
         y, h = F.rmsnorm(x, w, 1e-6, False, r)
         (y.float().sum() + h.float().sum()).backward()
+elif mode == "attn_bwd":
+    # one micro-batch of the flagship step: 8192 packed tokens, Qwen3-8B heads; prints device time of the three
+    # backward kernels together and, for scale, of the library path they replace (SDPA forward + backward on padded
+    # [B, H, S, D])
+    Hq, Hkv, D = 32, 8, 128
+    lens = [2560, 2560, 2560, 512]
+    T = sum(lens)
+    q, kc, vc = (torch.randn(T, h, D, device=dev).bfloat16().requires_grad_(True) for h in (Hq, Hkv, Hkv))
+    dout = torch.randn(T, Hq, D, device=dev).bfloat16()
+    meta = F.AttnMeta.packed(lens, Hq, Hkv, dev)
+    out = F.attention(q, kc, vc, meta, 1 / math.sqrt(D))
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for it in range(4):
+        if it == 1:
+            e0.record()
+        torch.autograd.grad(out, (q, kc, vc), dout, retain_graph=True)
+    e1.record()
+    torch.cuda.synchronize()
+    print(f"attention backward (delta + dK/dV + dQ kernels): {e0.elapsed_time(e1) / 3 * 1000:.1f} us per call")
+    if len(sys.argv) > 2 and sys.argv[2] == "compare":
+        B, S = 3, 2560
+        qp, kp, vp = (torch.randn(B, h, S, D, device=dev).bfloat16().requires_grad_(True) for h in (Hq, Hkv, Hkv))
+        do = torch.randn(B, Hq, S, D, device=dev).bfloat16()
+        for it in range(4):
+            if it == 1:
+                e0.record()
+            o = torch.nn.functional.scaled_dot_product_attention(qp, kp, vp, is_causal=True, enable_gqa=True)
+            torch.autograd.grad(o, (qp, kp, vp), do)
+        e1.record()
+        torch.cuda.synchronize()
+        print(f"library SDPA forward + backward, 3 x 2560 tokens (7680 of the 8192): {e0.elapsed_time(e1) / 3 * 1000:.1f} us per call")
 elif mode == "sampler":
     from skyrl_isoexec_b200.engine.sampler import Sampler, SamplingParams
     lg = torch.randn(64, 151936, device=dev).bfloat16()

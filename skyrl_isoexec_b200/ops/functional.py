@@ -301,6 +301,26 @@ class AttnMeta:
     items: torch.Tensor
     block_table: torch.Tensor | None = None
     seq_lens: list[int] = field(default_factory=list)  # packed training layout only (for the backward)
+    _bwd: tuple | None = None
+
+    def bwd_items(self, Hq: int, Hkv: int, device):
+        """Work lists of the backward kernels (int32 [n, 8]: first row, sequence start, sequence end, 0...): one item
+        per query tile of 128 / G tokens for dQ, one per block of 128 keys for dK / dV; the heaviest items come first
+        so that the long ones do not start last."""
+        if self._bwd is None:
+            tq = PAGE // (Hq // Hkv)
+            qi, ki = [], []
+            start = 0
+            for n in self.seq_lens:
+                for t0 in range(0, n, tq):
+                    qi.append((-(t0 + min(tq, n - t0)), start + t0, start, start + n))
+                for k0 in range(0, n, PAGE):
+                    ki.append((-(n - k0), start + k0, start, start + n))
+                start += n
+            mk = lambda rows: torch.tensor([(a, b, c, 0, 0, 0, 0, 0) for _, a, b, c in sorted(rows)],
+                                           dtype=torch.int32).reshape(-1, 8).to(device)
+            self._bwd = (mk(qi), mk(ki))
+        return self._bwd
 
     @staticmethod
     def packed(seq_lens, Hq, Hkv, device) -> "AttnMeta":
@@ -345,15 +365,38 @@ def attention_fwd(q, k, v, meta: AttnMeta, scale: float, want_lse: bool = False)
 class _Attention(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, meta, scale):
-        out, _ = attention_fwd(q, k, v, meta, scale)
-        ctx.save_for_backward(q, k, v)
+        native = _is_cuda(q) and q.dtype == torch.bfloat16
+        out, lse = attention_fwd(q, k, v, meta, scale, want_lse=native)
+        if native:
+            ctx.save_for_backward(q, k, v, out, lse)
+        else:
+            ctx.save_for_backward(q, k, v)
+        ctx.native = native
         ctx.meta = meta
         ctx.scale = scale
         return out
 
     @staticmethod
     def backward(ctx, dout):
-        # Outside the bitwise contract: recompute per sequence with the library attention and
+        if ctx.native:
+            # csrc/attention_bwd_tcgen05.cu: delta, dK/dV (key-stationary) and dQ (query-stationary), no atomics
+            q, k, v, out, lse = ctx.saved_tensors
+            T, Hq, D = q.shape
+            Hkv = k.shape[1]
+            assert k.shape[0] == T and k.is_contiguous() and v.is_contiguous(), "the backward needs the packed contiguous layout"
+            dout = dout.contiguous()
+            dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+            delta = torch.empty(T, Hq, device=q.device, dtype=torch.float32)
+            iq, ik = ctx.meta.bwd_items(Hq, Hkv, q.device)
+            _native.check(
+                _native.lib().ix_attention_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(),
+                                               dout.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), delta.data_ptr(),
+                                               iq.data_ptr(), iq.shape[0], ik.data_ptr(), ik.shape[0], T, Hq, Hkv, D,
+                                               ctx.scale, _native.stream()),
+                "ix_attention_bwd",
+            )
+            return dq, dk, dv, None, None
+        # CPU / fp32 configuration: recompute per sequence with the library attention and
         # differentiate it (right padding is harmless under a causal mask).
         q, k, v = ctx.saved_tensors
         lens = ctx.meta.seq_lens

@@ -419,6 +419,15 @@ class FlatAdamW:
                 setattr(self, n, t.to(device, non_blocking=True))
 
 
+def layers_that_fit(headroom_bytes: int, bytes_per_layer: int, num_layers: int, margin_bytes: int = 10 << 30,
+                    safety: float = 1.25) -> int:
+    """How many layers' activations fit into HBM that a whole step never touched: the estimate per layer is inflated
+    by ``safety`` and ``margin_bytes`` stay free for fragmentation and for anything the first step did not show."""
+    if bytes_per_layer <= 0:
+        return 0
+    return max(0, min(num_layers, int((headroom_bytes - margin_bytes) // int(safety * bytes_per_layer))))
+
+
 # ------------------------------------------------------------------------------------ worker
 class PolicyWorker:
     def __init__(self, model: DecoderLM, cfg: WorkerConfig | None = None, algo: alg.AlgorithmConfig | None = None):
@@ -475,8 +484,8 @@ class PolicyWorker:
             free_now, _ = torch.cuda.mem_get_info(self.device)
             outside = total - free_now - torch.cuda.memory_reserved(self.device)   # context, NCCL, symmetric memory
             headroom = total - outside - torch.cuda.max_memory_reserved(self.device)
-            per_layer = int(1.25 * self.activation_bytes_per_layer(self.cfg.max_tokens_per_microbatch))
-            n = max(0, min(len(self.model.layer_ids), int((headroom - (10 << 30)) // per_layer)))
+            n = layers_that_fit(headroom, self.activation_bytes_per_layer(self.cfg.max_tokens_per_microbatch),
+                                len(self.model.layer_ids))
         if dist.is_initialized() and dist.get_world_size() > 1:
             t = torch.tensor([n], dtype=torch.int64, device=self.device if self.device.type == "cuda" else "cpu")
             dist.all_reduce(t, op=dist.ReduceOp.MIN)

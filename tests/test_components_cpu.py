@@ -425,3 +425,24 @@ def test_weight_sync_factory_dispatches_the_peer_strategy(monkeypatch):
     assert made == [("sender", {"from_master": None}), ("receiver", {})]
     with pytest.raises(ValueError):
         strategies.create_init_info("carrier-pigeon", contract_hash="h")
+
+
+def test_kept_layer_budget_and_activation_estimate():
+    from skyrl_isoexec_b200.models.config import get_config
+    from skyrl_isoexec_b200.models.decoder import DecoderLM
+    from skyrl_isoexec_b200.parallel.state import ParallelState
+    from skyrl_isoexec_b200.train.policy_worker import PolicyWorker, WorkerConfig, layers_that_fit
+
+    gb = 1 << 30
+    assert layers_that_fit(5 * gb, gb, 36) == 0                       # under the margin: recompute everything
+    assert layers_that_fit(10 * gb + 5 * gb, gb, 36) == 4             # 5 GB over the margin, 1.25 GB per layer
+    assert layers_that_fit(500 * gb, gb, 36) == 36                    # never more than the model has
+    assert layers_that_fit(50 * gb, 0, 36) == 0
+    w = PolicyWorker(DecoderLM(get_config("tiny-qwen3"), ParallelState.single(), seed=0), WorkerConfig(keep_last_layers=-1))
+    c = w.model.cfg
+    per_tok = 6 * c.hidden_size + (c.num_q_heads + 2 * c.num_kv_heads) * c.head_dim + (c.num_q_heads + c.num_kv_heads) * c.head_dim \
+        + c.num_q_heads * c.head_dim + 3 * c.ffn_size
+    assert w.activation_bytes_per_layer(100) == 2 * per_tok * 100
+    assert w.keep_layers() == 0 and w._ckpt_arg() in (True, False)    # auto: nothing kept before the first step calibrates
+    w._calibrate_keep()                                               # CPU: calibrates to 0 and stays there
+    assert w._auto_keep == 0 and w.keep_layers() == 0
