@@ -174,6 +174,25 @@ accum_bf16_to_f32_kernel(float* __restrict__ dst, const __nv_bfloat16* __restric
   }
 }
 
+// Same, eight elements per thread and iteration (one 16-byte load of the source, two of the destination)
+__global__ void __launch_bounds__(256)
+accum_bf16_to_f32_vec8_kernel(float4* __restrict__ dst, const uint4* __restrict__ src, long long n8, int accumulate) {
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n8;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const uint4 s = __ldcs(src + i);                       // the bf16 gradient is dead after this read
+    const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&s);
+    float4 a = make_float4(__low2float(p[0]), __high2float(p[0]), __low2float(p[1]), __high2float(p[1]));
+    float4 b = make_float4(__low2float(p[2]), __high2float(p[2]), __low2float(p[3]), __high2float(p[3]));
+    if (accumulate) {
+      const float4 x = dst[2 * i], y = dst[2 * i + 1];
+      a.x += x.x; a.y += x.y; a.z += x.z; a.w += x.w;
+      b.x += y.x; b.y += y.y; b.z += y.z; b.w += y.w;
+    }
+    dst[2 * i] = a;
+    dst[2 * i + 1] = b;
+  }
+}
+
 inline int grid_1d(long long total, int block, int cap = 148 * 8) {
   long long g = (total + block - 1) / block;
   if (g > cap) g = cap;
@@ -270,6 +289,12 @@ IX_API int ix_adamw(void* master, void* m, void* v, const void* grad, void* para
 
 IX_API int ix_accum_bf16_to_f32(void* dst, const void* src, long long n, int accumulate, void* stream) {
   if (n <= 0) return 0;
+  if ((n & 7) == 0 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0 && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+    accum_bf16_to_f32_vec8_kernel<<<grid_1d(n / 8, 256, 148 * 16), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+        static_cast<float4*>(dst), static_cast<const uint4*>(src), n / 8, accumulate);
+    IX_CUDA(cudaGetLastError());
+    return 0;
+  }
   accum_bf16_to_f32_kernel<<<grid_1d(n, 256, 148 * 16), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       static_cast<float*>(dst), static_cast<const __nv_bfloat16*>(src), n, accumulate);
   IX_CUDA(cudaGetLastError());

@@ -182,15 +182,19 @@ qk_norm_rope_kernel(const __nv_bfloat16* __restrict__ qkv, long long ldqkv, cons
                     const float* __restrict__ sin_tab, const __nv_bfloat16* __restrict__ qw,
                     const __nv_bfloat16* __restrict__ kw, __nv_bfloat16* __restrict__ q_out,
                     __nv_bfloat16* __restrict__ k_out, __nv_bfloat16* __restrict__ v_out, int T, int Hq, int Hkv,
-                    int D, int rot_dim, float eps, int q_gate) {
+                    int D, int rot_dim, float eps, int q_gate, int wpt) {
   pdl_launch_dependents();
   pdl_wait();
+  // wpt warps share a token: warp w of the token takes heads w, w + wpt, ... The rotation constants and the norm
+  // weights of a lane are the same for every head of a token and are fetched once. wpt = Hq + 2 Hkv (one head per
+  // warp) for decode-sized T, where parallelism matters more than the table traffic. A head's arithmetic does not
+  // depend on wpt.
   const int Htot = Hq + 2 * Hkv;
   const long long wid = static_cast<long long>(blockIdx.x) * 4 + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
-  if (wid >= static_cast<long long>(T) * Htot) return;
-  const int t = static_cast<int>(wid / Htot);
-  const int h = static_cast<int>(wid % Htot);
+  if (wid >= static_cast<long long>(T) * wpt) return;
+  const int t = static_cast<int>(wid / wpt);
+  const int h0 = static_cast<int>(wid % wpt);
   const int nact = D >> 3;  // active lanes (8 elements each)
   // Row layout is KV-group major: for each KV head g, [its G query heads | k_g | v_g], so a
   // tensor-parallel shard (whole groups) is a contiguous slice. With an output gate (gated
@@ -198,78 +202,88 @@ qk_norm_rope_kernel(const __nv_bfloat16* __restrict__ qkv, long long ldqkv, cons
   const int q_stride = q_gate ? 2 * D : D;
   const int G = Hq / Hkv;
   const long long grp_stride = static_cast<long long>(G) * q_stride + 2 * D;
-  long long src_off;
-  if (h < Hq) src_off = (h / G) * grp_stride + static_cast<long long>(h % G) * q_stride;
-  else if (h < Hq + Hkv) src_off = (h - Hq) * grp_stride + static_cast<long long>(G) * q_stride;
-  else src_off = (h - Hq - Hkv) * grp_stride + static_cast<long long>(G) * q_stride + D;
-  const __nv_bfloat16* src = qkv + static_cast<size_t>(t) * ldqkv + src_off;
-  BF8 a;
-  if (lane < nact) a = reinterpret_cast<const BF8*>(src)[lane];
-  else {
-#pragma unroll
-    for (int j = 0; j < 8; ++j) a.v[j] = f2bf(0.f);
-  }
-  const bool is_v = h >= Hq + Hkv;
   const long long slot = slots ? slots[t] : t;
-  if (is_v) {
-    if (lane < nact && slot >= 0)
-      reinterpret_cast<BF8*>(v_out + (static_cast<size_t>(slot) * Hkv + (h - Hq - Hkv)) * D)[lane] = a;
-    return;
-  }
-  float y[8];
-#pragma unroll
-  for (int j = 0; j < 8; ++j) y[j] = bf2f(a.v[j]);
-  if (QK_NORM) {
-    float ss = 0.f;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) ss = __fadd_rn(ss, __fmul_rn(y[j], y[j]));
-    ss = warp_sum_butterfly(ss);
-    const float rstd = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, static_cast<float>(D)), eps)));
-    const __nv_bfloat16* wsrc = (h < Hq) ? qw : kw;
-    BF8 g;
-    if (lane < nact) g = reinterpret_cast<const BF8*>(wsrc)[lane];
-    else {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) g.v[j] = f2bf(0.f);
-    }
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const float n = round_bf(__fmul_rn(y[j], rstd));
-      float gg = bf2f(g.v[j]);
-      if (ZERO_CENTERED) gg = round_bf(__fadd_rn(1.0f, gg));
-      y[j] = round_bf(__fmul_rn(n, gg));
-    }
-  }
   // rotate-half over the first rot_dim elements: element i pairs with i +- rot_dim/2
   const int half = rot_dim >> 1;
   const int half_lanes = half >> 3;  // lanes per half (rot_dim multiple of 16)
   const int pos = positions[t];
-  float o[8];
   const int e0 = lane * 8;
   const bool in_rot = e0 < rot_dim;
   const bool first_half = e0 < half;
   const int partner = first_half ? lane + half_lanes : lane - half_lanes;
+  float cs[8], sn[8];
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
-    const float other = __shfl_sync(0xffffffffu, y[j], (in_rot ? partner : lane) & 31);
+    cs[j] = 1.f;
+    sn[j] = 0.f;
     if (in_rot) {
       const int fi = (first_half ? e0 : e0 - half) + j;
-      const float c = cos_tab[static_cast<size_t>(pos) * half + fi];
-      const float s = sin_tab[static_cast<size_t>(pos) * half + fi];
-      const float rot = first_half ? __fmul_rn(other, -1.0f) : other;
-      const float p1 = round_bf(__fmul_rn(y[j], c));
-      const float p2 = round_bf(__fmul_rn(rot, s));
-      o[j] = __fadd_rn(p1, p2);
-    } else {
-      o[j] = y[j];
+      cs[j] = cos_tab[static_cast<size_t>(pos) * half + fi];
+      sn[j] = sin_tab[static_cast<size_t>(pos) * half + fi];
     }
   }
-  if (lane < nact) {
-    BF8 r;
+  BF8 gq, gk;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) r.v[j] = f2bf(o[j]);
-    if (h < Hq) reinterpret_cast<BF8*>(q_out + (static_cast<size_t>(t) * Hq + h) * D)[lane] = r;
-    else if (slot >= 0) reinterpret_cast<BF8*>(k_out + (static_cast<size_t>(slot) * Hkv + (h - Hq)) * D)[lane] = r;
+  for (int j = 0; j < 8; ++j) gq.v[j] = gk.v[j] = f2bf(0.f);
+  if (QK_NORM && lane < nact) {
+    gq = reinterpret_cast<const BF8*>(qw)[lane];
+    gk = reinterpret_cast<const BF8*>(kw)[lane];
+  }
+  for (int h = h0; h < Htot; h += wpt) {
+    long long src_off;
+    if (h < Hq) src_off = (h / G) * grp_stride + static_cast<long long>(h % G) * q_stride;
+    else if (h < Hq + Hkv) src_off = (h - Hq) * grp_stride + static_cast<long long>(G) * q_stride;
+    else src_off = (h - Hq - Hkv) * grp_stride + static_cast<long long>(G) * q_stride + D;
+    const __nv_bfloat16* src = qkv + static_cast<size_t>(t) * ldqkv + src_off;
+    BF8 a;
+    if (lane < nact) a = reinterpret_cast<const BF8*>(src)[lane];
+    else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) a.v[j] = f2bf(0.f);
+    }
+    if (h >= Hq + Hkv) {   // a value head: copy
+      if (lane < nact && slot >= 0)
+        reinterpret_cast<BF8*>(v_out + (static_cast<size_t>(slot) * Hkv + (h - Hq - Hkv)) * D)[lane] = a;
+      continue;
+    }
+    float y[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) y[j] = bf2f(a.v[j]);
+    if (QK_NORM) {
+      float ss = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss = __fadd_rn(ss, __fmul_rn(y[j], y[j]));
+      ss = warp_sum_butterfly(ss);
+      const float rstd = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, static_cast<float>(D)), eps)));
+      const BF8& g = (h < Hq) ? gq : gk;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float n = round_bf(__fmul_rn(y[j], rstd));
+        float gg = bf2f(g.v[j]);
+        if (ZERO_CENTERED) gg = round_bf(__fadd_rn(1.0f, gg));
+        y[j] = round_bf(__fmul_rn(n, gg));
+      }
+    }
+    float o[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float other = __shfl_sync(0xffffffffu, y[j], (in_rot ? partner : lane) & 31);
+      if (in_rot) {
+        const float rot = first_half ? __fmul_rn(other, -1.0f) : other;
+        const float p1 = round_bf(__fmul_rn(y[j], cs[j]));
+        const float p2 = round_bf(__fmul_rn(rot, sn[j]));
+        o[j] = __fadd_rn(p1, p2);
+      } else {
+        o[j] = y[j];
+      }
+    }
+    if (lane < nact) {
+      BF8 r;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) r.v[j] = f2bf(o[j]);
+      if (h < Hq) reinterpret_cast<BF8*>(q_out + (static_cast<size_t>(t) * Hq + h) * D)[lane] = r;
+      else if (slot >= 0) reinterpret_cast<BF8*>(k_out + (static_cast<size_t>(slot) * Hkv + (h - Hq)) * D)[lane] = r;
+    }
   }
 }
 
@@ -450,7 +464,11 @@ IX_API int ix_qk_norm_rope(const void* qkv, long long ldqkv, const void* positio
   if ((rot_dim & 15) || rot_dim > D) return ixh::fail(ixh::IX_EARG, "qk_norm_rope: rot_dim %d unsupported", rot_dim);
   if (ldqkv & 7) return ixh::fail(ixh::IX_EARG, "qk_norm_rope: ldqkv must be a multiple of 8");
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  const long long warps = static_cast<long long>(T) * (Hq + 2 * Hkv);
+  // decode-sized T: one head per warp; otherwise a warp walks several heads of its token and reuses the per-token constants
+  const int Htot = Hq + 2 * Hkv;
+  int wpt = Htot;
+  if (T > 1024) wpt = (Htot % 8 == 0) ? 8 : (Htot % 4 == 0) ? 4 : Htot;
+  const long long warps = static_cast<long long>(T) * wpt;
   const int grid = static_cast<int>((warps + 3) / 4);
 #define IX_QKR(N_, Z_)                                                                                                  \
   IX_CUDA(ixh::launch_pdl(qk_norm_rope_kernel<N_, Z_>, dim3(grid), dim3(128), 0, s, static_cast<const __nv_bfloat16*>(qkv), \
@@ -458,7 +476,7 @@ IX_API int ix_qk_norm_rope(const void* qkv, long long ldqkv, const void* positio
                           static_cast<const float*>(cos_tab), static_cast<const float*>(sin_tab),                       \
                           static_cast<const __nv_bfloat16*>(qw), static_cast<const __nv_bfloat16*>(kw),                 \
                           static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(k_out),                       \
-                          static_cast<__nv_bfloat16*>(v_out), T, Hq, Hkv, D, rot_dim, eps, q_gate))
+                          static_cast<__nv_bfloat16*>(v_out), T, Hq, Hkv, D, rot_dim, eps, q_gate, wpt))
   if (qk_norm) {
     if (zero_centered) IX_QKR(true, true);
     else IX_QKR(true, false);

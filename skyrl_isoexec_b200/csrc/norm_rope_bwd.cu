@@ -119,7 +119,7 @@ qk_norm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ qkv, long long ldqkv, 
                         const __nv_bfloat16* __restrict__ qw, const __nv_bfloat16* __restrict__ kw,
                         const __nv_bfloat16* __restrict__ dq, const __nv_bfloat16* __restrict__ dk,
                         const __nv_bfloat16* __restrict__ dv, __nv_bfloat16* __restrict__ dqkv, float* __restrict__ dw_partial,
-                        int T, int Hq, int Hkv, int D, int rot_dim, float eps, int q_gate) {
+                        int T, int Hq, int Hkv, int D, int rot_dim, float eps, int q_gate, int wpt) {
   __shared__ float s_w[4][2][256];            // per warp: [q | k][D] weight-gradient accumulators
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int Htot = Hq + 2 * Hkv;
@@ -134,9 +134,36 @@ qk_norm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ qkv, long long ldqkv, 
   const int half = rot_dim >> 1, half_lanes = half >> 3;
   const bool in_rot = e0 < rot_dim, first_half = e0 < half;
   const int partner = first_half ? lane + half_lanes : lane - half_lanes;
-  const long long total = static_cast<long long>(T) * Htot;
+  // wpt warps share a token and each walks heads h0, h0 + wpt, ...: the rotation constants of a lane are fetched once
+  // per token, the norm weights once per warp
+  float gq[8], gk[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) gq[j] = gk[j] = 0.f;
+  if (QK_NORM && lane < nact) {
+    const BF8 a = reinterpret_cast<const BF8*>(qw)[lane], b = reinterpret_cast<const BF8*>(kw)[lane];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      gq[j] = bf2f(a.v[j]);
+      gk[j] = bf2f(b.v[j]);
+      if (ZERO_CENTERED) gq[j] = round_bf(1.0f + gq[j]), gk[j] = round_bf(1.0f + gk[j]);
+    }
+  }
+  const long long total = static_cast<long long>(T) * wpt;
   for (long long wid = static_cast<long long>(blockIdx.x) * 4 + warp; wid < total; wid += static_cast<long long>(gridDim.x) * 4) {
-    const int t = static_cast<int>(wid / Htot), h = static_cast<int>(wid % Htot);
+   const int t = static_cast<int>(wid / wpt), h0 = static_cast<int>(wid % wpt);
+   const int pos = positions[t];
+   float cs[8], sn[8];
+#pragma unroll
+   for (int j = 0; j < 8; ++j) {
+     cs[j] = 1.f;
+     sn[j] = 0.f;
+     if (in_rot) {
+       const int fi = (first_half ? e0 : e0 - half) + j;
+       cs[j] = cos_tab[static_cast<size_t>(pos) * half + fi];
+       sn[j] = sin_tab[static_cast<size_t>(pos) * half + fi];
+     }
+   }
+   for (int h = h0; h < Htot; h += wpt) {
     long long off;
     if (h < Hq) off = (h / G) * grp_stride + static_cast<long long>(h % G) * q_stride;
     else if (h < Hq + Hkv) off = (h - Hq) * grp_stride + static_cast<long long>(G) * q_stride;
@@ -158,14 +185,12 @@ qk_norm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ qkv, long long ldqkv, 
       for (int j = 0; j < 8; ++j) d[j] = x[j] = 0.f;
     }
     // transpose of the rotation: dy_i = do_i c + do_{i+half} s ; dy_{i+half} = do_{i+half} c - do_i s
-    const int pos = positions[t];
     float dy[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       const float other = __shfl_sync(0xffffffffu, d[j], (in_rot ? partner : lane) & 31);
       if (in_rot) {
-        const int fi = (first_half ? e0 : e0 - half) + j;
-        const float c = cos_tab[static_cast<size_t>(pos) * half + fi], s = sin_tab[static_cast<size_t>(pos) * half + fi];
+        const float c = cs[j], s = sn[j];
         dy[j] = first_half ? d[j] * c + other * s : d[j] * c - other * s;
       } else {
         dy[j] = d[j];
@@ -178,19 +203,7 @@ qk_norm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ qkv, long long ldqkv, 
       for (int j = 0; j < 8; ++j) ss += x[j] * x[j];
       ss = warp_sum_butterfly(ss);
       const float rs = rsqrtf(ss / static_cast<float>(D) + eps);
-      const __nv_bfloat16* wsrc = (h < Hq) ? qw : kw;
-      float g[8];
-      if (lane < nact) {
-        const BF8 g8 = reinterpret_cast<const BF8*>(wsrc)[lane];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          g[j] = bf2f(g8.v[j]);
-          if (ZERO_CENTERED) g[j] = round_bf(1.0f + g[j]);
-        }
-      } else {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) g[j] = 0.f;
-      }
+      const float (&g)[8] = (h < Hq) ? gq : gk;
       float dot = 0.f;
 #pragma unroll
       for (int j = 0; j < 8; ++j) dot += dy[j] * g[j] * (x[j] * rs);
@@ -211,6 +224,7 @@ qk_norm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ qkv, long long ldqkv, 
       for (int j = 0; j < 8; ++j) o.v[j] = f2bf(dx[j]);
       reinterpret_cast<BF8*>(dst)[lane] = o;
     }
+   }
   }
   if (QK_NORM) {
     if (lane < nact) {
@@ -269,14 +283,16 @@ IX_API int ix_qk_norm_rope_bwd(const void* qkv, long long ldqkv, const void* pos
   if (T <= 0) return 0;
   if ((D & 7) || D > 256 || (rot_dim & 15) || rot_dim > D) return ixh::fail(ixh::IX_EARG, "qk_norm_rope_bwd: D=%d rot_dim=%d unsupported", D, rot_dim);
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  const long long total = static_cast<long long>(T) * (Hq + 2 * Hkv);
+  const int Htot = Hq + 2 * Hkv;
+  const int wpt = (Htot % 8 == 0) ? 8 : (Htot % 4 == 0) ? 4 : Htot;
+  const long long total = static_cast<long long>(T) * wpt;
   int grid = static_cast<int>((total + 3) / 4 > kQkBwdCtas ? kQkBwdCtas : (total + 3) / 4);
 #define IX_QB(QN, ZC)                                                                                                          \
   qk_norm_rope_bwd_kernel<QN, ZC><<<grid, 128, 0, s>>>(                                                                        \
       static_cast<const __nv_bfloat16*>(qkv), ldqkv, static_cast<const int*>(positions), static_cast<const float*>(cos_tab),   \
       static_cast<const float*>(sin_tab), static_cast<const __nv_bfloat16*>(qw), static_cast<const __nv_bfloat16*>(kw),        \
       static_cast<const __nv_bfloat16*>(dq), static_cast<const __nv_bfloat16*>(dk), static_cast<const __nv_bfloat16*>(dv),     \
-      static_cast<__nv_bfloat16*>(dqkv), static_cast<float*>(dw_partial), T, Hq, Hkv, D, rot_dim, eps, q_gate);
+      static_cast<__nv_bfloat16*>(dqkv), static_cast<float*>(dw_partial), T, Hq, Hkv, D, rot_dim, eps, q_gate, wpt);
   if (qk_norm) {
     if (zero_centered) IX_QB(true, true) else IX_QB(true, false)
   } else {

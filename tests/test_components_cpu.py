@@ -446,3 +446,28 @@ def test_kept_layer_budget_and_activation_estimate():
     assert w.keep_layers() == 0 and w._ckpt_arg() in (True, False)    # auto: nothing kept before the first step calibrates
     w._calibrate_keep()                                               # CPU: calibrates to 0 and stays there
     assert w._auto_keep == 0 and w.keep_layers() == 0
+
+
+def test_attention_backward_work_lists_cover_every_tile_once_heaviest_first():
+    from skyrl_isoexec_b200.ops import functional as F
+
+    lens = [300, 17, 129, 128, 513]
+    Hq, Hkv = 8, 2
+    tq = 128 // (Hq // Hkv)
+    meta = F.AttnMeta.packed(lens, Hq, Hkv, "cpu")
+    iq, ik = meta.bwd_items(Hq, Hkv, "cpu")
+    assert meta.bwd_items(Hq, Hkv, "cpu")[0] is iq                       # built once
+    starts, s = [], 0
+    for n in lens:
+        starts.append((s, s + n))
+        s += n
+    want_q = {(a + t0, a, b) for a, b in starts for t0 in range(0, b - a, tq)}
+    want_k = {(a + k0, a, b) for a, b in starts for k0 in range(0, b - a, 128)}
+    got_q = [tuple(r[:3]) for r in iq.tolist()]
+    got_k = [tuple(r[:3]) for r in ik.tolist()]
+    assert len(got_q) == len(want_q) and set(got_q) == want_q
+    assert len(got_k) == len(want_k) and set(got_k) == want_k
+    # dQ work grows with the tile's last position, dK/dV work with the distance to the end of the sequence
+    wq = [min(t + tq, b) - a for t, a, b in got_q]
+    wk = [b - t for t, a, b in got_k]
+    assert wq == sorted(wq, reverse=True) and wk == sorted(wk, reverse=True)

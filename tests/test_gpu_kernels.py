@@ -251,6 +251,42 @@ def test_attention_backward_kernels_match_fp32_autograd(Hq, Hkv, D):
     assert all(bitwise_equal(a, b) for a, b in zip(got, again))
 
 
+@pytest.mark.parametrize("n", [8 * 1000, 8 * 1000 + 3, 1 << 22])
+def test_gradient_accumulation_kernel_bf16_into_fp32(n):
+    from skyrl_isoexec_b200.ops import _native
+
+    torch.manual_seed(21)
+    g = torch.randn(n, device=DEV).bfloat16()
+    acc = torch.randn(n, device=DEV)
+    want = acc + g.float()
+    L = _native.lib()
+    _native.check(L.ix_accum_bf16_to_f32(acc.data_ptr(), g.data_ptr(), n, 1, _native.stream()), "accum")
+    assert bitwise_equal(acc, want)
+    _native.check(L.ix_accum_bf16_to_f32(acc.data_ptr(), g.data_ptr(), n, 0, _native.stream()), "accum")
+    assert bitwise_equal(acc, g.float())
+
+
+def test_qk_norm_rope_many_tokens_path_equals_few_tokens_path_bitwise():
+    """Above 1024 tokens a warp walks several heads of its token (per-token constants fetched once); a token's bits
+    must not depend on which path ran."""
+    torch.manual_seed(31)
+    Hq, Hkv, D, T = 32, 8, 128, 1500
+    qkv = torch.randn(T, (Hq + 2 * Hkv) * D, device=DEV).bfloat16()
+    qw, kw = torch.randn(D, device=DEV).bfloat16(), torch.randn(D, device=DEV).bfloat16()
+    pos = torch.randint(0, 1000, (T,), dtype=torch.int32, device=DEV)
+    rope = F.RopeTable(D, 1024, 1e6, DEV)
+    mk = lambda: (torch.zeros(T, Hkv, D, dtype=torch.bfloat16, device=DEV), torch.zeros(T, Hkv, D, dtype=torch.bfloat16, device=DEV))
+    k1, v1 = mk()
+    q1 = F.qk_norm_rope_fwd(qkv, pos, None, rope, qw, kw, k1, v1, Hq, Hkv, D, 1e-6)
+    k2, v2 = mk()
+    q2 = torch.empty_like(q1)
+    for lo in range(0, T, 700):
+        hi = min(T, lo + 700)
+        slots = torch.arange(lo, hi, device=DEV, dtype=torch.int64)
+        q2[lo:hi] = F.qk_norm_rope_fwd(qkv[lo:hi], pos[lo:hi], slots, rope, qw, kw, k2, v2, Hq, Hkv, D, 1e-6)
+    assert bitwise_equal(q1, q2) and bitwise_equal(k1, k2) and bitwise_equal(v1, v2)
+
+
 def test_attention_decode_and_chunk_equal_prefill_bitwise_paged():
     torch.manual_seed(5)
     Hq, Hkv, D, S = 32, 8, 128, 700
