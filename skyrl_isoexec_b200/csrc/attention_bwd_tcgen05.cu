@@ -145,15 +145,28 @@ __device__ __forceinline__ void store_acc_row(uint32_t taddr, __nv_bfloat16* dst
   }
 }
 
+// A shared-memory descriptor is linear in the start address (field = address >> 4, 14 bits, and all of shared memory
+// fits in them), so the descriptors of a tile's K steps are the tile's base descriptor plus constants: one 64-bit add
+// per operand instead of rebuilding the descriptor in the single thread that issues every MMA.
+__device__ __forceinline__ uint64_t desc_k(uint32_t smem_addr) { return make_sw128_desc(smem_addr, 16, 1024); }          // K-major
+__device__ __forceinline__ uint64_t desc_mn(uint32_t smem_addr) { return make_sw128_desc(smem_addr, kChunk, 1024); }     // M/N-major
+
 // S (or dP) = A[128 x D] B[128 x D]^T, both K-major tiles of ND 64-wide chunks
 template <int ND>
-__device__ __forceinline__ void mma_nt_128(uint32_t d_tmem, uint32_t sA, uint32_t sB, uint32_t idesc) {
+__device__ __forceinline__ void mma_nt_128(uint32_t d_tmem, uint64_t dA, uint64_t dB, uint32_t idesc) {
 #pragma unroll
   for (int dc = 0; dc < ND; ++dc)
 #pragma unroll
-    for (int k = 0; k < 4; ++k)
-      umma_f16_ss(d_tmem, make_sw128_desc(sA + dc * kChunk + k * 32, 16, 1024), make_sw128_desc(sB + dc * kChunk + k * 32, 16, 1024),
-                  idesc, (dc | k) != 0 ? 1u : 0u);
+    for (int k = 0; k < 4; ++k) {
+      const uint64_t off = static_cast<uint64_t>((dc * kChunk + k * 32) >> 4);
+      umma_f16_ss(d_tmem, dA + off, dB + off, idesc, (dc | k) != 0 ? 1u : 0u);
+    }
+}
+// acc (+)= A^T-ish[128 x 128 rows] B[128 rows x N]: both operands M/N-major, the reduction runs over the 128 tile rows
+// in 8 steps of 16 rows (2048 B)
+__device__ __forceinline__ void mma_tn_128(uint32_t d_tmem, uint64_t dA, uint64_t dB, uint32_t idesc, bool first) {
+#pragma unroll
+  for (int k = 0; k < 8; ++k) umma_f16_ss(d_tmem, dA + static_cast<uint64_t>(k * 128), dB + static_cast<uint64_t>(k * 128), idesc, (first && k == 0) ? 0u : 1u);
 }
 
 // ------------------------------------------------------------------------------------------------ dQ
@@ -244,7 +257,8 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     if (elect_one() && nb > 0) {
       constexpr uint32_t idesc_s = make_idesc_bf16(kRows, kBlkN, 0, 0);
       constexpr uint32_t idesc_q = make_idesc_bf16(kRows, D, 0, 1);       // B = K read MN-major (keys are the reduction)
-      const uint32_t sQ = smem_u32(smem + SM::offQ), sdO = smem_u32(smem + SM::offdO), sdS = smem_u32(smem + SM::offdS);
+      const uint64_t dQd = desc_k(smem_u32(smem + SM::offQ)), ddO = desc_k(smem_u32(smem + SM::offdO));
+      const uint64_t ddS = desc_k(smem_u32(smem + SM::offdS));
       // S and dP of block j into TMEM (their columns are free once the softmax warps hold block j-1 in registers)
       auto front = [&](int j) -> bool {
         const int st = j & 1;
@@ -252,8 +266,8 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         if (!mbar_wait(smem_u32(&bars[Q_KF + st]), ph, abort_flag, status, ST_TIMEOUT_FULL)) return false;
         if (!mbar_wait(smem_u32(&bars[Q_VF + st]), ph, abort_flag, status, ST_TIMEOUT_FULL)) return false;
         tc_fence_after();
-        mma_nt_128<ND>(tmem_S, sQ, smem_u32(smem + SM::offK + st * SM::kT), idesc_s);
-        mma_nt_128<ND>(tmem_dP, sdO, smem_u32(smem + SM::offV + st * SM::kT), idesc_s);
+        mma_nt_128<ND>(tmem_S, dQd, desc_k(smem_u32(smem + SM::offK + st * SM::kT)), idesc_s);
+        mma_nt_128<ND>(tmem_dP, ddO, desc_k(smem_u32(smem + SM::offV + st * SM::kT)), idesc_s);
         umma_commit(smem_u32(&bars[Q_VE + st]));
         umma_commit(smem_u32(&bars[Q_SF]));
         return true;
@@ -268,11 +282,12 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         }
         if (!mbar_wait(smem_u32(&bars[Q_DSF]), j & 1, abort_flag, status, ST_TIMEOUT_MISC)) break;
         tc_fence_after();
-        const uint32_t sK = smem_u32(smem + SM::offK + st * SM::kT);
+        // A = dS, K-major (two 64-key chunks); B = K block read M/N-major (16 keys = 2048 B per step)
+        const uint64_t dKm = desc_mn(smem_u32(smem + SM::offK + st * SM::kT));
 #pragma unroll
         for (int k = 0; k < 8; ++k)
-          umma_f16_ss(tmem_dQ, make_sw128_desc(sdS + (k >> 2) * kChunk + (k & 3) * 32, 16, 1024),
-                      make_sw128_desc(sK + k * 2048, kChunk, 1024), idesc_q, (j | k) != 0 ? 1u : 0u);
+          umma_f16_ss(tmem_dQ, ddS + static_cast<uint64_t>(((k >> 2) * kChunk + (k & 3) * 32) >> 4), dKm + static_cast<uint64_t>(k * 128),
+                      idesc_q, (j | k) != 0 ? 1u : 0u);
         umma_commit(smem_u32(&bars[Q_KE + st]));
         umma_commit(smem_u32(&bars[Q_DQF]));
       }
@@ -300,7 +315,7 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       int lim = q_pos - key0 + 1;
       if (seq_len - key0 < lim) lim = seq_len - key0;
       if (!row_valid) lim = 0;
-      uint32_t s0[32], s1[32], d0[32], d1[32], dk[16];
+      uint32_t s0[32], s1[32], d0[32], d1[32], dk[16], dk2[16];
       tmem_ld_32x32(tmem_S + lane_off + chalf * 64, s0);
       tmem_ld_32x32(tmem_S + lane_off + chalf * 64 + 32, s1);
       tmem_ld_32x32(tmem_dP + lane_off + chalf * 64, d0);
@@ -311,14 +326,15 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       tmem_ld_wait_dep(d1);
       tc_fence_before();
       mbar_arrive(smem_u32(&bars[Q_SR]));       // S and dP are in registers: the next block's MMAs may overwrite them
+      // both chunks are computed before the first store, so the wait for the buffer comes as late as possible
       chunk_ds(s0, d0, chalf * 64, lim, scale_log2, neg_lse2, scale, neg_dscale, dk);
+      chunk_ds(s1, d1, chalf * 64 + 32, lim, scale_log2, neg_lse2, scale, neg_dscale, dk2);
       if (j > 0) {
         // the dS buffer is still the A operand of dQ += dS K of block j-1
         if (!mbar_wait(smem_u32(&bars[Q_DQF]), (j - 1) & 1, abort_flag, status, ST_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
       }
       store_row_chunk(sdS, r, chalf * 2, dk);
-      chunk_ds(s1, d1, chalf * 64 + 32, lim, scale_log2, neg_lse2, scale, neg_dscale, dk);
-      store_row_chunk(sdS, r, chalf * 2 + 1, dk);
+      store_row_chunk(sdS, r, chalf * 2 + 1, dk2);
       tc_fence_before();
       fence_proxy_async();
       mbar_arrive(smem_u32(&bars[Q_DSF]));
@@ -429,7 +445,8 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     if (elect_one() && nq > 0) {
       constexpr uint32_t idesc_s = make_idesc_bf16(kRows, kBlkN, 0, 0);
       constexpr uint32_t idesc_t = make_idesc_bf16(kRows, D, 1, 1);       // A = P^T / dS^T and B = dO / Q, both M/N-major
-      const uint32_t sK = smem_u32(smem + SM::offK), sV = smem_u32(smem + SM::offV), sP = smem_u32(smem + SM::offP);
+      const uint64_t dKd = desc_k(smem_u32(smem + SM::offK)), dVd = desc_k(smem_u32(smem + SM::offV));
+      const uint64_t dPm = desc_mn(smem_u32(smem + SM::offP));
       // S (and dP) of tile i; dV: Q is free after S. dK: dO is free after dP.
       auto front = [&](int i) -> bool {
         const int st = i & 1;
@@ -437,9 +454,9 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         if (!mbar_wait(smem_u32(&bars[K_QF + st]), ph, abort_flag, status, ST_TIMEOUT_FULL)) return false;
         if (kDK && !mbar_wait(smem_u32(&bars[K_OF + st]), ph, abort_flag, status, ST_TIMEOUT_FULL)) return false;
         tc_fence_after();
-        mma_nt_128<ND>(tmem_S, smem_u32(smem + SM::offQ + st * SM::kT), sK, idesc_s);
+        mma_nt_128<ND>(tmem_S, desc_k(smem_u32(smem + SM::offQ + st * SM::kT)), dKd, idesc_s);
         if (kDK) {
-          mma_nt_128<ND>(tmem_dP, smem_u32(smem + SM::offdO + st * SM::kT), sV, idesc_s);
+          mma_nt_128<ND>(tmem_dP, desc_k(smem_u32(smem + SM::offdO + st * SM::kT)), dVd, idesc_s);
           umma_commit(smem_u32(&bars[K_OE + st]));
         } else {
           umma_commit(smem_u32(&bars[K_QE + st]));
@@ -447,26 +464,25 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         umma_commit(smem_u32(&bars[K_SF]));
         return true;
       };
+      // acc += (P or dS of tile i)^T (dO or Q of tile i)
+      auto back = [&](int i) -> bool {
+        const int st = i & 1;
+        if (!mbar_wait(smem_u32(&bars[K_PF]), i & 1, abort_flag, status, ST_TIMEOUT_MISC)) return false;
+        if (!kDK && !mbar_wait(smem_u32(&bars[K_OF + st]), (i >> 1) & 1, abort_flag, status, ST_TIMEOUT_FULL)) return false;
+        tc_fence_after();
+        mma_tn_128(tmem_acc, dPm, desc_mn(smem_u32(smem + (kDK ? SM::offQ : SM::offdO) + st * SM::kT)), idesc_t, i == 0);
+        umma_commit(smem_u32(&bars[(kDK ? K_QE : K_OE) + st]));
+        umma_commit(smem_u32(&bars[K_PE]));
+        return true;
+      };
       bool ok = mbar_wait(smem_u32(&bars[K_KVF]), 0, abort_flag, status, ST_TIMEOUT_FULL);
       if (ok) ok = front(0);
       for (int i = 0; i < nq && ok; ++i) {
-        const int st = i & 1;
         if (i + 1 < nq) {
           if (!mbar_wait(smem_u32(&bars[K_SR]), i & 1, abort_flag, status, ST_TIMEOUT_MISC)) break;
           if (!front(i + 1)) break;
         }
-        if (!mbar_wait(smem_u32(&bars[K_PF]), i & 1, abort_flag, status, ST_TIMEOUT_MISC)) break;
-        if (!kDK && !mbar_wait(smem_u32(&bars[K_OF + st]), (i >> 1) & 1, abort_flag, status, ST_TIMEOUT_FULL)) break;
-        tc_fence_after();
-        // the reduction runs over the 128 tile rows: 8 steps of 16 rows (2048 B); the 64-key halves of P / dS and the
-        // 64-wide d chunks of dO / Q are one chunk apart
-        const uint32_t sB = smem_u32(smem + (kDK ? SM::offQ : SM::offdO) + st * SM::kT);
-#pragma unroll
-        for (int k = 0; k < 8; ++k)
-          umma_f16_ss(tmem_acc, make_sw128_desc(sP + k * 2048, kChunk, 1024), make_sw128_desc(sB + k * 2048, kChunk, 1024),
-                      idesc_t, (i | k) != 0 ? 1u : 0u);
-        umma_commit(smem_u32(&bars[(kDK ? K_QE : K_OE) + st]));
-        umma_commit(smem_u32(&bars[K_PE]));
+        if (!back(i)) break;
       }
     }
   } else {
@@ -479,19 +495,28 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const float scale_log2 = scale * kLog2e;
     uint8_t* sP = smem + SM::offP;
     bool ok = nq > 0;
+    // row statistics of tile i + 1 are fetched while tile i is being processed (a global load per tile would
+    // otherwise sit in front of every tile's exponentials)
+    auto row_stats = [&](int i, float& l2, float& ds) {
+      const int t = it.tok0 + i * TQ + tok;
+      const bool valid = i < nq && t < it.seq_end;
+      const size_t srow = static_cast<size_t>(valid ? t : it.tok0) * Hq + hq;
+      l2 = valid ? -lse[srow] * kLog2e : 0.f;
+      ds = (kDK && valid) ? -delta[srow] * scale : 0.f;
+    };
+    float nxt_lse2 = 0.f, nxt_dscale = 0.f;
+    row_stats(0, nxt_lse2, nxt_dscale);
     for (int i = 0; i < nq && ok; ++i) {
       const int t = it.tok0 + i * TQ + tok;                 // this row's token
       const bool row_valid = t < it.seq_end;
-      const size_t srow = static_cast<size_t>(row_valid ? t : it.tok0) * Hq + hq;
-      const float neg_lse2 = row_valid ? -lse[srow] * kLog2e : 0.f;
-      float neg_dscale = 0.f;
-      if (kDK) neg_dscale = row_valid ? -delta[srow] * scale : 0.f;
+      const float neg_lse2 = nxt_lse2, neg_dscale = nxt_dscale;
+      row_stats(i + 1, nxt_lse2, nxt_dscale);
       int lim = (t - it.seq_start) - key_pos0 + 1;          // keys [0, lim) of the block are visible to this row
       if (n_keys < lim) lim = n_keys;
       if (!row_valid) lim = 0;
       if (!mbar_wait(smem_u32(&bars[K_SF]), i & 1, abort_flag, status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
       tc_fence_after();
-      uint32_t s0[32], s1[32], pk[16];
+      uint32_t s0[32], s1[32], pk[16], pk2[16];
       tmem_ld_32x32(tmem_S + lane_off + chalf * 64, s0);
       tmem_ld_32x32(tmem_S + lane_off + chalf * 64 + 32, s1);
       if (kDK) {
@@ -505,24 +530,24 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         tc_fence_before();
         mbar_arrive(smem_u32(&bars[K_SR]));
         chunk_ds(s0, d0, chalf * 64, lim, scale_log2, neg_lse2, scale, neg_dscale, pk);
+        chunk_ds(s1, d1, chalf * 64 + 32, lim, scale_log2, neg_lse2, scale, neg_dscale, pk2);
         if (i > 0) {
           if (!mbar_wait(smem_u32(&bars[K_PE]), (i - 1) & 1, abort_flag, status, ST_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
         }
         store_row_chunk(sP, r, chalf * 2, pk);
-        chunk_ds(s1, d1, chalf * 64 + 32, lim, scale_log2, neg_lse2, scale, neg_dscale, pk);
-        store_row_chunk(sP, r, chalf * 2 + 1, pk);
+        store_row_chunk(sP, r, chalf * 2 + 1, pk2);
       } else {
         tmem_ld_wait_dep(s0);
         tmem_ld_wait_dep(s1);
         tc_fence_before();
         mbar_arrive(smem_u32(&bars[K_SR]));
         chunk_p(s0, chalf * 64, lim, scale_log2, neg_lse2, pk);
+        chunk_p(s1, chalf * 64 + 32, lim, scale_log2, neg_lse2, pk2);
         if (i > 0) {
           if (!mbar_wait(smem_u32(&bars[K_PE]), (i - 1) & 1, abort_flag, status, ST_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
         }
         store_row_chunk(sP, r, chalf * 2, pk);
-        chunk_p(s1, chalf * 64 + 32, lim, scale_log2, neg_lse2, pk);
-        store_row_chunk(sP, r, chalf * 2 + 1, pk);
+        store_row_chunk(sP, r, chalf * 2 + 1, pk2);
       }
       tc_fence_before();
       fence_proxy_async();
