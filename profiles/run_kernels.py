@@ -1,7 +1,7 @@
 """Small, self-terminating kernel workloads for ncu captures (one kernel family per mode).
 
     python profiles/run_kernels.py attn_decode | attn_prefill | gemm_large | gemm_decode | logprob | rmsnorm |
-                                   glu_decode | moe_grouped | rmsnorm_decode | sampler | rmsnorm_bwd | attn_bwd
+                                   glu_decode | moe_grouped | rmsnorm_decode | sampler | rmsnorm_bwd | attn_bwd | train_small
 
 Each mode allocates well under 1 GB, launches the kernel a handful of times and exits.
 """
@@ -123,6 +123,39 @@ elif mode == "attn_bwd":
         e1.record()
         torch.cuda.synchronize()
         print(f"library SDPA forward + backward, 3 x 2560 tokens (7680 of the 8192): {e0.elapsed_time(e1) / 3 * 1000:.1f} us per call")
+elif mode == "train_small":
+    # elementwise kernels of one training micro-batch (8192 tokens, Qwen3-8B shapes): CUDA-event time and bytes moved
+    T, Hq, Hkv, D = 8192, 32, 8, 128
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def timed(fn, n=5):
+        for _ in range(2):
+            fn()
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n * 1000
+
+    qkv = torch.randn(T, (Hq + 2 * Hkv) * D, device=dev).bfloat16().requires_grad_(True)
+    qw, kw = (torch.randn(D, device=dev).bfloat16().requires_grad_(True) for _ in range(2))
+    pos = (torch.arange(T, device=dev, dtype=torch.int32) % 2560).contiguous()
+    rope = F.RopeTable(D, 4096, 1e6, dev)
+    kc, vc = (torch.zeros(T, Hkv, D, device=dev, dtype=torch.bfloat16) for _ in range(2))
+    us = timed(lambda: F.qk_norm_rope_fwd(qkv.detach(), pos, None, rope, qw.detach(), kw.detach(), kc, vc, Hq, Hkv, D, 1e-6))
+    nbytes = 2 * qkv.numel() * 2
+    print(f"qk_norm_rope forward: {us:.1f} us, {nbytes / us / 1e6:.2f} TB/s (read + write of the fused QKV)")
+    q, k, v = F.qk_norm_rope_train(qkv, pos, rope, qw, kw, Hq, Hkv, D, 1e-6)
+    gq, gk, gv = torch.randn_like(q), torch.randn_like(k), torch.randn_like(v)
+    us = timed(lambda: torch.autograd.grad((q, k, v), (qkv, qw, kw), (gq, gk, gv), retain_graph=True))
+    print(f"qk_norm_rope backward (+ weight-gradient fold): {us:.1f} us, {3 * qkv.numel() * 2 / us / 1e6:.2f} TB/s (dq|dk|dv + qkv read, dqkv written)")
+    n = 4096 * 12288
+    g = torch.randn(n, device=dev).bfloat16()
+    acc = torch.zeros(n, device=dev)
+    L = _native.lib()
+    us = timed(lambda: _native.check(L.ix_accum_bf16_to_f32(acc.data_ptr(), g.data_ptr(), n, 1, _native.stream()), "accum"))
+    print(f"gradient accumulation bf16 -> fp32, {n} elements: {us:.1f} us, {n * 10 / us / 1e6:.2f} TB/s")
 elif mode == "sampler":
     from skyrl_isoexec_b200.engine.sampler import Sampler, SamplingParams
     lg = torch.randn(64, 151936, device=dev).bfloat16()

@@ -61,6 +61,10 @@ _SIGS = {
     "ix_gdn_l2norm": [_P, _L, _P, _P, _L, _I, _I, _F, _F, _I, _P],
     "ix_gdn_scan": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
     "ix_attention_fwd": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _L, _I, _F, _P, _P],
+    "ix_enable_peer_access": [_I],
+    "ix_ipc_open": [_P, _P],
+    "ix_ipc_close": [_P],
+    "ix_pointer_device": [_P],
     "ix_attention_bwd": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _F, _P],
 }
 _RESTYPE = {"ix_reduce_scratch_elems": C.c_longlong}

@@ -25,6 +25,9 @@ from ..core import process as P
 from ..ops import _native
 
 
+_OPENED: dict = {}     # IPC handle bytes -> base address of the mapping in this process
+
+
 @dataclass
 class PeerPushInitInfo:
     contract_hash: str | None
@@ -54,12 +57,23 @@ class PeerPushSender:
         if info.numel != mine.numel() or info.dtype != str(mine.dtype).replace("torch.", ""):
             raise ValueError(f"engine buffer ({info.numel} x {info.dtype}) does not match the trainer's layout "
                              f"({mine.numel()} x {mine.dtype}); use the broadcast strategy to reshard")
-        storage = torch.UntypedStorage._new_shared_cuda(*info.ipc_handle)
-        # the mapping lives on the engine's device; this process reaches it by peer access, which torch turns on between
-        # two devices at their first direct copy
-        self.remote = torch.tensor([], dtype=mine.dtype, device=storage.device).set_(storage, 0, (info.numel,))
-        if self.remote.device != mine.device:
-            self.remote[:8].to(mine.device)
+        # The handle is opened HERE, natively, with the trainer's device current and lazy peer access: a mapping made
+        # in the context of the device that owns the memory (what torch's own importer does) cannot be dereferenced by
+        # kernels of another device. A handle can be opened once per process, so mappings are cached.
+        lib = _native.lib()
+        owner_device, handle, _size_bytes, offset_bytes = info.ipc_handle[:4]
+        key = bytes(handle)
+        if key not in _OPENED:
+            base = C.c_void_p()
+            with torch.cuda.device(mine.device):
+                if owner_device != mine.device.index:
+                    _native.check(lib.ix_enable_peer_access(int(owner_device)), "ix_enable_peer_access")
+                _native.check(lib.ix_ipc_open(C.c_char_p(key), C.byref(base)), "ix_ipc_open")
+            _OPENED[key] = base.value
+        self.remote_ptr = _OPENED[key] + int(offset_bytes)
+        where = lib.ix_pointer_device(C.c_void_p(self.remote_ptr))
+        if where != int(owner_device):
+            raise RuntimeError(f"the engine's buffer is not a device allocation on GPU {owner_device} (got {where})")
         self.src = from_master if from_master is not None else mine
         self.src_f32 = self.src.dtype == torch.float32
         if self.src_f32 and mine.dtype != torch.bfloat16:
@@ -73,7 +87,7 @@ class PeerPushSender:
             for d in s.shape:
                 n *= d
             n_al = (n + 7) // 8 * 8
-            recs.append(struct.pack("<QQqii", self.src.data_ptr() + s.offset * esz_src, self.remote.data_ptr() + s.offset * mine.element_size(),
+            recs.append(struct.pack("<QQqii", self.src.data_ptr() + s.offset * esz_src, self.remote_ptr + s.offset * mine.element_size(),
                                     n_al, int(self.src_f32), 0))
         self.n_desc = len(recs)
         self.descs = torch.frombuffer(bytearray(b"".join(recs)), dtype=torch.uint8).to(mine.device)

@@ -508,71 +508,3 @@ def test_moe_model_with_expert_parallelism_over_peer_memory():
     print("moe ep model:", res)
     assert res["registered"]["ep"] and res["mismatches"] == [0, 0] and res["status"] == [0, 0]
     assert res["grad_norms"][0] == res["grad_norms"][1] > 0
-
-
-def _push_worker(rank, world, port, q):
-    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
-                      LOCAL_RANK=str(rank), NCCL_NVLS_ENABLE="0")
-    import torch.distributed as dist
-
-    torch.cuda.set_device(rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank), timeout=_PG_TIMEOUT)
-    try:
-        from skyrl_isoexec_b200.models.config import get_config
-        from skyrl_isoexec_b200.models.decoder import DecoderLM
-        from skyrl_isoexec_b200.ops import _native
-        from skyrl_isoexec_b200.sync.peer_push import PeerPushReceiver, PeerPushSender, export_engine_buffer
-
-        _native.lib().ix_init()
-        cfg = get_config("tiny-qwen3-bf16", hidden_size=1024, num_layers=4, ffn_size=4096)
-        if rank == 1:                                        # the engine: different weights until the push arrives
-            model = DecoderLM(cfg, device="cuda", seed=77)
-            info = export_engine_buffer(model, contract_hash=None)
-            dist.broadcast_object_list([info], src=1)
-            rx = PeerPushReceiver(info, model)
-            rx.receive()
-            ref = DecoderLM(cfg, device="cuda", seed=5)
-            same_bf16 = bool(torch.equal(model.store.flat, ref.store.flat))
-            rx.receive()                                     # second push: from the fp32 master copy, rounded in flight
-            same_cast = bool(torch.equal(model.store.flat, (ref.store.flat.float() * 1.5).bfloat16()))
-            q.put({"same_bf16": same_bf16, "same_cast": same_cast})
-        else:                                                # the trainer
-            model = DecoderLM(cfg, device="cuda", seed=5)
-            box = [None]
-            dist.broadcast_object_list(box, src=1)
-            tx = PeerPushSender(box[0], model)
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            nbytes = tx.send()
-            e1.record()
-            torch.cuda.synchronize()
-            master = model.store.flat.float() * 1.5
-            PeerPushSender(box[0], model, from_master=master).send()
-            q.put({"bytes": nbytes, "ms": e0.elapsed_time(e1)})
-    except Exception as e:  # noqa: BLE001
-        q.put({f"error_rank{rank}": repr(e)})
-        raise
-    finally:
-        dist.barrier()
-        dist.destroy_process_group()
-
-
-@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
-@pytest.mark.timeout(300)
-def test_weight_push_into_the_engine_over_peer_memory():
-    """Trainer on GPU 0 writes its parameters straight into the engine's buffer on GPU 1 (mapped through CUDA IPC) with
-    one kernel; a second push casts the fp32 master copy to bf16 on the way."""
-    ctx = mp.get_context("spawn")
-    q = ctx.Queue()
-    port = _free_port()
-    procs = [ctx.Process(target=_push_worker, args=(r, 2, port, q)) for r in range(2)]
-    for p in procs:
-        p.start()
-    res = {}
-    for _ in range(2):
-        res.update(q.get(timeout=240))
-    for p in procs:
-        p.join(timeout=60)
-    print("weight push:", res)
-    assert not [k for k in res if k.startswith("error")], res
-    assert res["same_bf16"] and res["same_cast"] and res["bytes"] > 0
