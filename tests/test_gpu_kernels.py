@@ -287,6 +287,33 @@ def test_qk_norm_rope_many_tokens_path_equals_few_tokens_path_bitwise():
     assert bitwise_equal(q1, q2) and bitwise_equal(k1, k2) and bitwise_equal(v1, v2)
 
 
+def test_descriptor_driven_push_copy_kernel_copies_and_casts_on_one_gpu():
+    """The kernel behind the peer weight push, run on local memory: several ranges in one launch, bf16 -> bf16 byte
+    equality and fp32 -> bf16 round-to-nearest, ragged tail included."""
+    import ctypes as C
+    import struct
+
+    from skyrl_isoexec_b200.ops import _native
+
+    torch.manual_seed(17)
+    sizes = [4096, 8 * 1000 + 5, 128, 1 << 20]
+    src_bf = [torch.randn(n, device=DEV).bfloat16() for n in sizes]
+    src_f32 = [torch.randn(n, device=DEV) for n in sizes]
+    dst_a = [torch.zeros(n, device=DEV, dtype=torch.bfloat16) for n in sizes]
+    dst_b = [torch.zeros(n, device=DEV, dtype=torch.bfloat16) for n in sizes]
+    recs = [struct.pack("<QQqii", s.data_ptr(), d.data_ptr(), s.numel(), 0, 0) for s, d in zip(src_bf, dst_a)]
+    recs += [struct.pack("<QQqii", s.data_ptr(), d.data_ptr(), s.numel(), 1, 0) for s, d in zip(src_f32, dst_b)]
+    descs = torch.frombuffer(bytearray(b"".join(recs)), dtype=torch.uint8).to(DEV)
+    lib = _native.lib()
+    lib.ix_push_copy.argtypes = [C.c_void_p, C.c_int, C.c_void_p]
+    _native.check(lib.ix_push_copy(descs.data_ptr(), len(recs), _native.stream()), "ix_push_copy")
+    torch.cuda.synchronize()
+    for s_, d in zip(src_bf, dst_a):
+        assert bitwise_equal(s_, d)
+    for s_, d in zip(src_f32, dst_b):
+        assert bitwise_equal(s_.bfloat16(), d)
+
+
 def test_attention_decode_and_chunk_equal_prefill_bitwise_paged():
     torch.manual_seed(5)
     Hq, Hkv, D, S = 32, 8, 128, 700
