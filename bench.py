@@ -41,6 +41,9 @@ def parse():
     ap.add_argument("--tp", type=int, default=1, help="tensor-parallel degree of trainer and engine (fused GEMM+collective kernels)")
     ap.add_argument("--keep-last-layers", type=int, default=-1,
                     help="layers not recomputed in the backward (uses spare HBM); -1 = as many as the first step's measured peak leaves room for")
+    ap.add_argument("--reuse-rollout-logprobs", action="store_true",
+                    help="variant, not the headline: skip the scoring forward and take the engine's logprobs as the old-policy "
+                         "logprobs (same bits under the contract); the gate then compares the training forward with the rollout")
     ap.add_argument("--layers", type=int, default=0, help="debug only: truncate the model (marks the run invalid)")
     return ap.parse_args()
 
@@ -130,6 +133,8 @@ def main():
         "trainer.policy.optimizer_config.lr=1e-6", "trainer.logger=console" if os.environ.get("BENCH_VERBOSE") else "trainer.logger=jsonl",
         "environment.env_class=even_tokens", "trainer.resume_mode=none", f"trainer.policy.keep_last_layers={args.keep_last_layers}",
     ]
+    if args.reuse_rollout_logprobs:
+        ov.append("trainer.isoexec.reuse_rollout_logprobs=true")
     mo = {}
     if args.layers:
         mo["num_layers"] = args.layers
@@ -200,6 +205,7 @@ def main():
                        "prompt_len": args.prompt_len, "seq_len": args.prompt_len + args.response_len,
                        "parallelism": (f"dp{ps.dp}" + (f"xtp{args.tp}" if args.tp > 1 else "")) if world > 1 else "single",
                        "engine": f"colocated, 1 engine per TP group, TP{args.tp}",
+                       "scoring_forward": "skipped: rollout logprobs reused (VARIANT, not the reference's step)" if args.reuse_rollout_logprobs else "run",
                        "l2": "working set (16 GB of weights per pass) exceeds L2; no explicit flush"},
             "clocks": sampler.summary(),
             "e2e": {"value": tokens / (wall_ms / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)},

@@ -109,6 +109,11 @@ class IsoExecConfig:
     gate_max_limit: float = 1.0e-4
     require_bitwise: bool = True        # the contract claims tolerance 0: any nonzero diff refuses
     strict: bool = True
+    # Strictly on-policy steps (one optimizer step per rollout batch): take the engine's sampled-token logprobs as the
+    # old-policy logprobs instead of recomputing them with a scoring forward. Under the contract the two are the same
+    # bits; the forward gate then compares the TRAINING forward's logprobs with the rollout's, before the optimizer
+    # step. Off by default (the reference always runs the scoring forward).
+    reuse_rollout_logprobs: bool = False
     contract_path: str = ""
     debug_trace: str = ""
 

@@ -545,6 +545,10 @@ class PolicyWorker:
         loss_fn = alg.get_policy_loss(algo.policy_loss_type)
         want_ent = self.cfg.want_entropy or algo.use_entropy_loss
         tot = {"loss": 0.0, "clip_ratio_num": 0.0, "tokens": 0.0, "entropy_sum": 0.0, "kl_sum": 0.0}
+        # optional: compare this forward's logprobs with the rollout's, bit for bit (the forward gate when the scoring
+        # forward is skipped)
+        check_bits = bool(batch.metadata.get("check_rollout_bits")) and batch.get("rollout_logprobs") is not None
+        bits = {"mismatches": 0, "abs_sum": 0.0, "abs_max": 0.0, "tokens": 0.0}
         dev = self.device
         mbs = self._pack(seqs, att, R)
         for mi, mb in enumerate(mbs):
@@ -567,6 +571,16 @@ class PolicyWorker:
                 old = lp2d.detach()
             loss, m = loss_fn(lp2d, old, get("advantages"), algo, loss_mask=mask, rollout_logprobs=get("rollout_logprobs"))
             ntok = mask.sum()
+            if check_bits:
+                from ..core.testing import count_bit_mismatches
+
+                rm = get("response_mask")
+                a_, b_ = (lp2d.detach() * rm).contiguous(), (get("rollout_logprobs") * rm).contiguous()
+                d_ = (a_ - b_).abs()
+                bits["mismatches"] += count_bit_mismatches(a_, b_)
+                bits["abs_sum"] += float(d_.sum())
+                bits["abs_max"] = max(bits["abs_max"], float(d_.max()) if d_.numel() else 0.0)
+                bits["tokens"] += float(rm.sum())
             if algo.use_kl_loss and batch.get("base_action_log_probs") is not None:
                 kl = alg.compute_approx_kl(lp2d, get("base_action_log_probs"), mask, algo.kl_estimator_type)
                 scale = batch.metadata.get("aux_loss_scale", 1.0)
@@ -583,8 +597,11 @@ class PolicyWorker:
             tot["clip_ratio_num"] += float(m.get("clip_ratio", 0.0)) * float(ntok)
             tot["tokens"] += float(ntok)
         n = max(1.0, tot["tokens"])
-        return {"policy_loss": tot["loss"], "ppo_clip_ratio": tot["clip_ratio_num"] / n, "loss_tokens": tot["tokens"],
-                "policy_entropy": tot["entropy_sum"] / n, "policy_kl": tot["kl_sum"] / n}
+        out = {"policy_loss": tot["loss"], "ppo_clip_ratio": tot["clip_ratio_num"] / n, "loss_tokens": tot["tokens"],
+               "policy_entropy": tot["entropy_sum"] / n, "policy_kl": tot["kl_sum"] / n}
+        if check_bits:
+            out["rollout_bits"] = bits
+        return out
 
     def _overlap_ok(self) -> bool:
         """Overlap applies to plain data parallelism (no TP/EP-specific reductions to order before the DP sum)."""

@@ -229,8 +229,21 @@ class RayPPOTrainer:
                       "max_response_length": int(lens.max())}
         return b
 
+    def _reuse_rollout_logprobs(self) -> bool:
+        """The scoring forward may be dropped only when the rollout policy IS the policy being updated: contract
+        enforced, one optimizer step per rollout batch."""
+        t = self.cfg.trainer
+        return bool(t.isoexec.enabled and t.isoexec.reuse_rollout_logprobs and t.update_epochs_per_batch == 1
+                    and t.policy_mini_batch_size >= t.train_batch_size)
+
     def fwd_logprobs_values_reward(self, batch: TrainingInputBatch) -> TrainingInputBatch:
-        lp = self.policy.forward(batch)
+        self._gate_in_update = self._reuse_rollout_logprobs()
+        if self._gate_in_update:
+            # old-policy logprobs = the engine's, which the contract makes the trainer's bit for bit; the gate runs on the
+            # training forward (train_critic_and_policy), before the optimizer step
+            lp = batch["rollout_logprobs"].clone()
+        else:
+            lp = self.policy.forward(batch)
         batch["action_log_probs"] = lp
         mask = batch["response_mask"]
         ro = batch["rollout_logprobs"]
@@ -258,7 +271,7 @@ class RayPPOTrainer:
         if getattr(self, "critic", None) is not None:
             batch["values"] = self.critic.forward(batch) * mask
         iso = self.cfg.trainer.isoexec
-        if iso.enabled:
+        if iso.enabled and not self._gate_in_update:
             gate = validate_isoexec_forward_gate(diff, mask, mism, iso)
             if self.global_step <= 1 and hasattr(self, "adapter_trainer"):
                 self.adapter_trainer.on_gate(gate["ok"], f"mean={gate['mean']:.3e} max={gate['max']:.3e} "
@@ -319,7 +332,11 @@ class RayPPOTrainer:
                                                                     t.micro_train_batch_size_per_gpu, a.max_seq_len)
                     mb["advantages"] = scaled * (mb.batch_size / max(1, gB))
                     mb.metadata["aux_loss_scale"] = 1.0 / max(1.0, self._global_sum(float(lm.sum())))
+                if getattr(self, "_gate_in_update", False):
+                    mb.metadata["check_rollout_bits"] = True
                 m = self.policy.forward_backward(mb)
+                if getattr(self, "_gate_in_update", False):
+                    self._gate_on_training_forward(m["rollout_bits"])      # raises before the weights move
                 gn = self.policy.optim_step()
                 out["policy_loss"] += m["policy_loss"]
                 out["ppo_clip_ratio"] += m["ppo_clip_ratio"]
@@ -333,6 +350,31 @@ class RayPPOTrainer:
         self.all_metrics.update({f"policy/{k}": v for k, v in out.items()})
         self.all_metrics["policy/policy_lr"] = self.policy.opt.lr_at(max(0, self.policy.opt.step_count - 1))
         return out
+
+    def _gate_on_training_forward(self, bits: dict) -> None:
+        """Forward gate when the scoring forward is skipped: the training forward's logprobs against the rollout's."""
+        iso = self.cfg.trainer.isoexec
+        mism = int(self._global_sum(float(bits["mismatches"])))
+        ntok = max(1.0, self._global_sum(bits["tokens"]))
+        mean = self._global_sum(bits["abs_sum"]) / ntok
+        mx = bits["abs_max"]
+        if self.ps.dp > 1:
+            t = torch.tensor([mx], dtype=torch.float64, device=self.device if self.device.type == "cuda" else "cpu")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.ps.dp_group)
+            mx = float(t)
+        self.all_metrics.update({"policy/rollout_train_logprob_bit_mismatches": mism,
+                                 "policy/rollout_train_logprobs_abs_diff_mean": mean,
+                                 "policy/rollout_train_logprobs_abs_diff_max": mx,
+                                 "policy/scoring_forward_skipped": 1})
+        ok = mean <= iso.gate_mean_limit and mx <= iso.gate_max_limit and (mism == 0 or not iso.require_bitwise)
+        if self.global_step <= 1 and hasattr(self, "adapter_trainer"):
+            self.adapter_trainer.on_gate(ok, f"mean={mean:.3e} max={mx:.3e} mismatches={mism} (training forward)")
+        if not ok:
+            msg = (f"IsoExec forward gate refused at step {self.global_step} (training forward vs rollout): mean={mean:.3e} "
+                   f"max={mx:.3e} bit mismatches={mism}")
+            if iso.strict:
+                raise ForwardGateError(msg)
+            print("[warn] " + msg)
 
     def sync_weights(self) -> None:
         """Trainer -> rollout. Same process and layout: the flat buffer is shared, so the transfer is

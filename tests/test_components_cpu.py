@@ -471,3 +471,49 @@ def test_attention_backward_work_lists_cover_every_tile_once_heaviest_first():
     wq = [min(t + tq, b) - a for t, a, b in got_q]
     wk = [b - t for t, a, b in got_k]
     assert wq == sorted(wq, reverse=True) and wk == sorted(wk, reverse=True)
+
+
+def test_scoring_forward_can_be_skipped_on_policy_with_the_same_weights_bit_for_bit(tmp_path):
+    """With the contract enforced and one optimizer step per rollout batch, the engine's logprobs are the old-policy
+    logprobs: skipping the scoring forward leaves the updated weights unchanged bit for bit, the gate still runs (on
+    the training forward), and a rollout logprob that is off by one ulp is refused BEFORE the weights move."""
+    from skyrl_isoexec_b200.train.entrypoints import main_base
+    from skyrl_isoexec_b200.core.ledger import ContractViolation
+    from skyrl_isoexec_b200.train.trainer import ForwardGateError
+
+    def run(reuse, tamper=False):
+        ov = ["trainer.policy.model=tiny-qwen3", "trainer.train_batch_size=2", "trainer.policy_mini_batch_size=2",
+              "generator.n_samples_per_prompt=2", "generator.sampling_params.max_generate_length=8",
+              "generator.sampling_params.ignore_eos=true", "data.synthetic_prompt_len=8", "data.synthetic_prompts=8",
+              "trainer.max_prompt_length=8", "generator.inference_engine.num_kv_pages=16", "trainer.num_steps=2",
+              f"trainer.ckpt_path={tmp_path}/r{int(reuse)}{int(tamper)}", "trainer.ckpt_interval=0", "trainer.logger=jsonl",
+              "trainer.policy.optimizer_config.lr=1e-3", f"trainer.isoexec.reuse_rollout_logprobs={'true' if reuse else 'false'}"]
+        exp = main_base.BasePPOExp(SkyRLTrainConfig.from_cli_overrides(ov))
+        tr = exp.get_trainer()
+        tr.build_models()
+        tr.sync_weights()
+        it = iter(tr.loader)
+        if tamper:
+            orig = tr.convert_to_training_input
+
+            def bent(go, uids):
+                b = orig(go, uids)
+                ro = b["rollout_logprobs"]
+                ro[0, -1] = torch.nextafter(ro[0, -1], torch.tensor(0.0))
+                return b
+
+            tr.convert_to_training_input = bent
+        before = tr.policy.model.store.flat.detach().clone()
+        m = [tr.train_step(next(it)) for _ in range(2)] if not tamper else None
+        return tr, m, before
+
+    tr_a, m_a, _ = run(False)
+    tr_b, m_b, _ = run(True)
+    assert torch.equal(tr_a.policy.model.store.flat.detach(), tr_b.policy.model.store.flat.detach())
+    assert all(m["policy/rollout_train_logprob_bit_mismatches"] == 0 for m in m_a + m_b)
+    assert all(m.get("policy/scoring_forward_skipped") == 1 for m in m_b) and "policy/scoring_forward_skipped" not in m_a[0]
+    assert m_b[0]["timing/fwd_logprobs"] < m_a[0]["timing/fwd_logprobs"]
+    tr_c, _, before = run(True, tamper=True)
+    with pytest.raises((ForwardGateError, ContractViolation)):      # the ledger refuses at step 1, the gate afterwards
+        tr_c.train_step(next(iter(tr_c.loader)))
+    assert torch.equal(tr_c.policy.model.store.flat.detach(), before)       # refused before the optimizer step
