@@ -173,8 +173,15 @@ rmsnorm_cta_row_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16*
 // ------------------------------------------------------------------ QK-norm + RoPE + KV write
 // qkv: [T, (Hq + 2*Hkv) * D] as produced by the fused QKV projection (row stride ldqkv),
 // KV-group major (see below).
-// One warp per (token, head). q heads -> q_out[T, Hq, D]; k heads -> k_out[slot, Hkv, D];
-// v heads -> v_out[slot, Hkv, D] with slot = slots ? slots[t] : t (paged cache or packed).
+// q heads -> q_out[T, Hq, D]; k heads -> k_out[slot, Hkv, D]; v heads -> v_out[slot, Hkv, D] with
+// slot = slots ? slots[t] : t (paged cache or packed).
+//
+// Work layout. A head occupies nact = D / 8 lanes (8 elements each; the 8-per-lane split is part of the pinned
+// summation order). hpw = 32 / nact heads share a warp when nact is a power of two (two heads for D = 128), each in
+// its own aligned lane group; the row sum then runs over the group only, which gives the bits of the full-warp
+// butterfly over one head padded with zero lanes, because the skipped steps only ever added +0. wpt warps share a
+// token; the warp with index w takes heads w, w + wpt, w + 2 wpt, ..., hpw at a time, and fetches the rotation
+// constants and norm weights of its lanes once. A head's arithmetic depends on neither hpw nor wpt.
 template <bool QK_NORM, bool ZERO_CENTERED>
 __global__ void __launch_bounds__(128)
 qk_norm_rope_kernel(const __nv_bfloat16* __restrict__ qkv, long long ldqkv, const int* __restrict__ positions,
@@ -182,20 +189,19 @@ qk_norm_rope_kernel(const __nv_bfloat16* __restrict__ qkv, long long ldqkv, cons
                     const float* __restrict__ sin_tab, const __nv_bfloat16* __restrict__ qw,
                     const __nv_bfloat16* __restrict__ kw, __nv_bfloat16* __restrict__ q_out,
                     __nv_bfloat16* __restrict__ k_out, __nv_bfloat16* __restrict__ v_out, int T, int Hq, int Hkv,
-                    int D, int rot_dim, float eps, int q_gate, int wpt) {
+                    int D, int rot_dim, float eps, int q_gate, int wpt, int hpw, int red_width) {
   pdl_launch_dependents();
   pdl_wait();
-  // wpt warps share a token: warp w of the token takes heads w, w + wpt, ... The rotation constants and the norm
-  // weights of a lane are the same for every head of a token and are fetched once. wpt = Hq + 2 Hkv (one head per
-  // warp) for decode-sized T, where parallelism matters more than the table traffic. A head's arithmetic does not
-  // depend on wpt.
   const int Htot = Hq + 2 * Hkv;
   const long long wid = static_cast<long long>(blockIdx.x) * 4 + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (wid >= static_cast<long long>(T) * wpt) return;
   const int t = static_cast<int>(wid / wpt);
   const int h0 = static_cast<int>(wid % wpt);
-  const int nact = D >> 3;  // active lanes (8 elements each)
+  const int nact = D >> 3;                 // lanes per head
+  const int sub = lane / nact;             // which of the warp's head slots this lane belongs to
+  const int sl = lane - sub * nact;        // lane within the head
+  const bool lane_on = sub < hpw;
   // Row layout is KV-group major: for each KV head g, [its G query heads | k_g | v_g], so a
   // tensor-parallel shard (whole groups) is a contiguous slice. With an output gate (gated
   // attention) the block of a query head is [q(D) | gate(D)].
@@ -207,10 +213,10 @@ qk_norm_rope_kernel(const __nv_bfloat16* __restrict__ qkv, long long ldqkv, cons
   const int half = rot_dim >> 1;
   const int half_lanes = half >> 3;  // lanes per half (rot_dim multiple of 16)
   const int pos = positions[t];
-  const int e0 = lane * 8;
-  const bool in_rot = e0 < rot_dim;
+  const int e0 = sl * 8;
+  const bool in_rot = lane_on && e0 < rot_dim;
   const bool first_half = e0 < half;
-  const int partner = first_half ? lane + half_lanes : lane - half_lanes;
+  const int partner = sub * nact + (first_half ? sl + half_lanes : sl - half_lanes);
   float cs[8], sn[8];
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
@@ -225,26 +231,25 @@ qk_norm_rope_kernel(const __nv_bfloat16* __restrict__ qkv, long long ldqkv, cons
   BF8 gq, gk;
 #pragma unroll
   for (int j = 0; j < 8; ++j) gq.v[j] = gk.v[j] = f2bf(0.f);
-  if (QK_NORM && lane < nact) {
-    gq = reinterpret_cast<const BF8*>(qw)[lane];
-    gk = reinterpret_cast<const BF8*>(kw)[lane];
+  if (QK_NORM && lane_on) {
+    gq = reinterpret_cast<const BF8*>(qw)[sl];
+    gk = reinterpret_cast<const BF8*>(kw)[sl];
   }
-  for (int h = h0; h < Htot; h += wpt) {
-    long long src_off;
-    if (h < Hq) src_off = (h / G) * grp_stride + static_cast<long long>(h % G) * q_stride;
-    else if (h < Hq + Hkv) src_off = (h - Hq) * grp_stride + static_cast<long long>(G) * q_stride;
-    else src_off = (h - Hq - Hkv) * grp_stride + static_cast<long long>(G) * q_stride + D;
-    const __nv_bfloat16* src = qkv + static_cast<size_t>(t) * ldqkv + src_off;
+  for (int hb = h0; hb < Htot; hb += wpt * hpw) {     // the same trip count for every lane of the warp
+    const int h = hb + sub * wpt;
+    const bool on = lane_on && h < Htot;
+    const bool is_v = h >= Hq + Hkv;
     BF8 a;
-    if (lane < nact) a = reinterpret_cast<const BF8*>(src)[lane];
-    else {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) a.v[j] = f2bf(0.f);
-    }
-    if (h >= Hq + Hkv) {   // a value head: copy
-      if (lane < nact && slot >= 0)
-        reinterpret_cast<BF8*>(v_out + (static_cast<size_t>(slot) * Hkv + (h - Hq - Hkv)) * D)[lane] = a;
-      continue;
+    for (int j = 0; j < 8; ++j) a.v[j] = f2bf(0.f);
+    if (on) {
+      long long src_off;
+      if (h < Hq) src_off = (h / G) * grp_stride + static_cast<long long>(h % G) * q_stride;
+      else if (!is_v) src_off = (h - Hq) * grp_stride + static_cast<long long>(G) * q_stride;
+      else src_off = (h - Hq - Hkv) * grp_stride + static_cast<long long>(G) * q_stride + D;
+      a = reinterpret_cast<const BF8*>(qkv + static_cast<size_t>(t) * ldqkv + src_off)[sl];
+      if (is_v && slot >= 0)   // a value head: copy (its lanes still take part in the shuffles below)
+        reinterpret_cast<BF8*>(v_out + (static_cast<size_t>(slot) * Hkv + (h - Hq - Hkv)) * D)[sl] = a;
     }
     float y[8];
 #pragma unroll
@@ -253,7 +258,10 @@ qk_norm_rope_kernel(const __nv_bfloat16* __restrict__ qkv, long long ldqkv, cons
       float ss = 0.f;
 #pragma unroll
       for (int j = 0; j < 8; ++j) ss = __fadd_rn(ss, __fmul_rn(y[j], y[j]));
-      ss = warp_sum_butterfly(ss);
+      // the steps of warp_sum_butterfly that stay inside the head's lane group, in the same order (16, 8, 4, 2, 1)
+#pragma unroll
+      for (int off = 16; off >= 1; off >>= 1)
+        if (off < red_width) ss = __fadd_rn(ss, __shfl_xor_sync(0xffffffffu, ss, off));
       const float rstd = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, static_cast<float>(D)), eps)));
       const BF8& g = (h < Hq) ? gq : gk;
 #pragma unroll
@@ -277,12 +285,12 @@ qk_norm_rope_kernel(const __nv_bfloat16* __restrict__ qkv, long long ldqkv, cons
         o[j] = y[j];
       }
     }
-    if (lane < nact) {
+    if (on && !is_v) {
       BF8 r;
 #pragma unroll
       for (int j = 0; j < 8; ++j) r.v[j] = f2bf(o[j]);
-      if (h < Hq) reinterpret_cast<BF8*>(q_out + (static_cast<size_t>(t) * Hq + h) * D)[lane] = r;
-      else if (slot >= 0) reinterpret_cast<BF8*>(k_out + (static_cast<size_t>(slot) * Hkv + (h - Hq)) * D)[lane] = r;
+      if (h < Hq) reinterpret_cast<BF8*>(q_out + (static_cast<size_t>(t) * Hq + h) * D)[sl] = r;
+      else if (slot >= 0) reinterpret_cast<BF8*>(k_out + (static_cast<size_t>(slot) * Hkv + (h - Hq)) * D)[sl] = r;
     }
   }
 }
@@ -464,10 +472,17 @@ IX_API int ix_qk_norm_rope(const void* qkv, long long ldqkv, const void* positio
   if ((rot_dim & 15) || rot_dim > D) return ixh::fail(ixh::IX_EARG, "qk_norm_rope: rot_dim %d unsupported", rot_dim);
   if (ldqkv & 7) return ixh::fail(ixh::IX_EARG, "qk_norm_rope: ldqkv must be a multiple of 8");
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  // decode-sized T: one head per warp; otherwise a warp walks several heads of its token and reuses the per-token constants
+  // lanes per head, heads per warp (power-of-two lane groups only), width of the row-sum butterfly
   const int Htot = Hq + 2 * Hkv;
-  int wpt = Htot;
-  if (T > 1024) wpt = (Htot % 8 == 0) ? 8 : (Htot % 4 == 0) ? 4 : Htot;
+  const int nact = D >> 3;
+  const bool pow2 = (nact & (nact - 1)) == 0;
+  const int hpw = (pow2 && nact <= 16) ? 32 / nact : 1;
+  int red_width = 1;
+  while (red_width < nact) red_width <<= 1;
+  // decode-sized T: every warp makes one pass (hpw heads); otherwise a warp walks several heads of its token and
+  // reuses the per-token constants
+  int wpt = (Htot + hpw - 1) / hpw;
+  if (T > 1024 && wpt > 8) wpt = 8;
   const long long warps = static_cast<long long>(T) * wpt;
   const int grid = static_cast<int>((warps + 3) / 4);
 #define IX_QKR(N_, Z_)                                                                                                  \
@@ -476,7 +491,7 @@ IX_API int ix_qk_norm_rope(const void* qkv, long long ldqkv, const void* positio
                           static_cast<const float*>(cos_tab), static_cast<const float*>(sin_tab),                       \
                           static_cast<const __nv_bfloat16*>(qw), static_cast<const __nv_bfloat16*>(kw),                 \
                           static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(k_out),                       \
-                          static_cast<__nv_bfloat16*>(v_out), T, Hq, Hkv, D, rot_dim, eps, q_gate, wpt))
+                          static_cast<__nv_bfloat16*>(v_out), T, Hq, Hkv, D, rot_dim, eps, q_gate, wpt, hpw, red_width))
   if (qk_norm) {
     if (zero_centered) IX_QKR(true, true);
     else IX_QKR(true, false);

@@ -110,8 +110,10 @@ __global__ void __launch_bounds__(256) fold_partials_kernel(const float* __restr
   out[c] = f2bf(s);
 }
 
-// Backward of qk_norm_rope: one warp per (token, head). dq [T,Hq,D], dk/dv [T,Hkv,D] -> dqkv in the KV-group-major
-// fused layout; the gate half of a gated query block is not touched here (its gradient comes from the gate op).
+// Backward of qk_norm_rope. dq [T,Hq,D], dk/dv [T,Hkv,D] -> dqkv in the KV-group-major fused layout; the gate half of
+// a gated query block is not touched here (its gradient comes from the gate op). Work layout as in the forward
+// (csrc/norm_rope.cu): a head takes nact = D / 8 lanes, hpw heads share a warp when nact is a power of two, wpt warps
+// share a token and walk its heads, fetching the rotation constants once per token and the norm weights once.
 template <bool QK_NORM, bool ZERO_CENTERED>
 __global__ void __launch_bounds__(128)
 qk_norm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ qkv, long long ldqkv, const int* __restrict__ positions,
@@ -119,12 +121,14 @@ qk_norm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ qkv, long long ldqkv, 
                         const __nv_bfloat16* __restrict__ qw, const __nv_bfloat16* __restrict__ kw,
                         const __nv_bfloat16* __restrict__ dq, const __nv_bfloat16* __restrict__ dk,
                         const __nv_bfloat16* __restrict__ dv, __nv_bfloat16* __restrict__ dqkv, float* __restrict__ dw_partial,
-                        int T, int Hq, int Hkv, int D, int rot_dim, float eps, int q_gate, int wpt) {
+                        int T, int Hq, int Hkv, int D, int rot_dim, float eps, int q_gate, int wpt, int hpw, int red_width) {
   __shared__ float s_w[4][2][256];            // per warp: [q | k][D] weight-gradient accumulators
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int Htot = Hq + 2 * Hkv;
   const int nact = D >> 3;
-  const int e0 = lane * 8;
+  const int sub = lane / nact, sl = lane - sub * nact;
+  const bool lane_on = sub < hpw;
+  const int e0 = sl * 8;
   float accq[8], acck[8];
 #pragma unroll
   for (int j = 0; j < 8; ++j) accq[j] = acck[j] = 0.f;
@@ -132,15 +136,13 @@ qk_norm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ qkv, long long ldqkv, 
   const int G = Hq / Hkv;
   const long long grp_stride = static_cast<long long>(G) * q_stride + 2 * D;
   const int half = rot_dim >> 1, half_lanes = half >> 3;
-  const bool in_rot = e0 < rot_dim, first_half = e0 < half;
-  const int partner = first_half ? lane + half_lanes : lane - half_lanes;
-  // wpt warps share a token and each walks heads h0, h0 + wpt, ...: the rotation constants of a lane are fetched once
-  // per token, the norm weights once per warp
+  const bool in_rot = lane_on && e0 < rot_dim, first_half = e0 < half;
+  const int partner = sub * nact + (first_half ? sl + half_lanes : sl - half_lanes);
   float gq[8], gk[8];
 #pragma unroll
   for (int j = 0; j < 8; ++j) gq[j] = gk[j] = 0.f;
-  if (QK_NORM && lane < nact) {
-    const BF8 a = reinterpret_cast<const BF8*>(qw)[lane], b = reinterpret_cast<const BF8*>(kw)[lane];
+  if (QK_NORM && lane_on) {
+    const BF8 a = reinterpret_cast<const BF8*>(qw)[sl], b = reinterpret_cast<const BF8*>(kw)[sl];
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       gq[j] = bf2f(a.v[j]);
@@ -148,85 +150,106 @@ qk_norm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ qkv, long long ldqkv, 
       if (ZERO_CENTERED) gq[j] = round_bf(1.0f + gq[j]), gk[j] = round_bf(1.0f + gk[j]);
     }
   }
+  // sum over the lanes of one head (group-local butterfly)
+  auto group_sum = [&](float v) {
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1)
+      if (off < red_width) v += __shfl_xor_sync(0xffffffffu, v, off);
+    return v;
+  };
   const long long total = static_cast<long long>(T) * wpt;
   for (long long wid = static_cast<long long>(blockIdx.x) * 4 + warp; wid < total; wid += static_cast<long long>(gridDim.x) * 4) {
-   const int t = static_cast<int>(wid / wpt), h0 = static_cast<int>(wid % wpt);
-   const int pos = positions[t];
-   float cs[8], sn[8];
-#pragma unroll
-   for (int j = 0; j < 8; ++j) {
-     cs[j] = 1.f;
-     sn[j] = 0.f;
-     if (in_rot) {
-       const int fi = (first_half ? e0 : e0 - half) + j;
-       cs[j] = cos_tab[static_cast<size_t>(pos) * half + fi];
-       sn[j] = sin_tab[static_cast<size_t>(pos) * half + fi];
-     }
-   }
-   for (int h = h0; h < Htot; h += wpt) {
-    long long off;
-    if (h < Hq) off = (h / G) * grp_stride + static_cast<long long>(h % G) * q_stride;
-    else if (h < Hq + Hkv) off = (h - Hq) * grp_stride + static_cast<long long>(G) * q_stride;
-    else off = (h - Hq - Hkv) * grp_stride + static_cast<long long>(G) * q_stride + D;
-    __nv_bfloat16* dst = dqkv + static_cast<size_t>(t) * ldqkv + off;
-    if (h >= Hq + Hkv) {
-      if (lane < nact) reinterpret_cast<BF8*>(dst)[lane] = reinterpret_cast<const BF8*>(dv + (static_cast<size_t>(t) * Hkv + (h - Hq - Hkv)) * D)[lane];
-      continue;
-    }
-    const __nv_bfloat16* dsrc = (h < Hq) ? dq + (static_cast<size_t>(t) * Hq + h) * D : dk + (static_cast<size_t>(t) * Hkv + (h - Hq)) * D;
-    float d[8], x[8];
-    if (lane < nact) {
-      const BF8 a = reinterpret_cast<const BF8*>(dsrc)[lane];
-      const BF8 b = reinterpret_cast<const BF8*>(qkv + static_cast<size_t>(t) * ldqkv + off)[lane];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) d[j] = bf2f(a.v[j]), x[j] = bf2f(b.v[j]);
-    } else {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) d[j] = x[j] = 0.f;
-    }
-    // transpose of the rotation: dy_i = do_i c + do_{i+half} s ; dy_{i+half} = do_{i+half} c - do_i s
-    float dy[8];
+    const int t = static_cast<int>(wid / wpt), h0 = static_cast<int>(wid % wpt);
+    const int pos = positions[t];
+    float cs[8], sn[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      const float other = __shfl_sync(0xffffffffu, d[j], (in_rot ? partner : lane) & 31);
+      cs[j] = 1.f;
+      sn[j] = 0.f;
       if (in_rot) {
-        const float c = cs[j], s = sn[j];
-        dy[j] = first_half ? d[j] * c + other * s : d[j] * c - other * s;
-      } else {
-        dy[j] = d[j];
+        const int fi = (first_half ? e0 : e0 - half) + j;
+        cs[j] = cos_tab[static_cast<size_t>(pos) * half + fi];
+        sn[j] = sin_tab[static_cast<size_t>(pos) * half + fi];
       }
     }
-    float dx[8];
-    if (QK_NORM) {
-      float ss = 0.f;
+    for (int hb = h0; hb < Htot; hb += wpt * hpw) {       // the same trip count for every lane of the warp
+      const int h = hb + sub * wpt;
+      const bool on = lane_on && h < Htot;
+      const bool is_v = h >= Hq + Hkv;
+      long long off = 0;
+      if (h < Hq) off = (h / G) * grp_stride + static_cast<long long>(h % G) * q_stride;
+      else if (!is_v) off = (h - Hq) * grp_stride + static_cast<long long>(G) * q_stride;
+      else off = (h - Hq - Hkv) * grp_stride + static_cast<long long>(G) * q_stride + D;
+      float d[8], x[8];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) ss += x[j] * x[j];
-      ss = warp_sum_butterfly(ss);
-      const float rs = rsqrtf(ss / static_cast<float>(D) + eps);
-      const float (&g)[8] = (h < Hq) ? gq : gk;
-      float dot = 0.f;
+      for (int j = 0; j < 8; ++j) d[j] = x[j] = 0.f;
+      if (on) {
+        __nv_bfloat16* dst = dqkv + static_cast<size_t>(t) * ldqkv + off;
+        if (is_v) {
+          reinterpret_cast<BF8*>(dst)[sl] = reinterpret_cast<const BF8*>(dv + (static_cast<size_t>(t) * Hkv + (h - Hq - Hkv)) * D)[sl];
+        } else {
+          const __nv_bfloat16* dsrc = (h < Hq) ? dq + (static_cast<size_t>(t) * Hq + h) * D : dk + (static_cast<size_t>(t) * Hkv + (h - Hq)) * D;
+          const BF8 a = reinterpret_cast<const BF8*>(dsrc)[sl];
+          const BF8 b = reinterpret_cast<const BF8*>(qkv + static_cast<size_t>(t) * ldqkv + off)[sl];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) dot += dy[j] * g[j] * (x[j] * rs);
-      dot = warp_sum_butterfly(dot) / static_cast<float>(D);
+          for (int j = 0; j < 8; ++j) d[j] = bf2f(a.v[j]), x[j] = bf2f(b.v[j]);
+        }
+      }
+      // transpose of the rotation: dy_i = do_i c + do_{i+half} s ; dy_{i+half} = do_{i+half} c - do_i s
+      float dy[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        const float n = x[j] * rs;
-        dx[j] = rs * (dy[j] * g[j] - n * dot);
-        if (h < Hq) accq[j] += dy[j] * n; else acck[j] += dy[j] * n;
+        const float other = __shfl_sync(0xffffffffu, d[j], (in_rot ? partner : lane) & 31);
+        if (in_rot) {
+          const float c = cs[j], s = sn[j];
+          dy[j] = first_half ? d[j] * c + other * s : d[j] * c - other * s;
+        } else {
+          dy[j] = d[j];
+        }
       }
-    } else {
+      float dx[8];
+      if (QK_NORM) {
+        float ss = 0.f;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) dx[j] = dy[j];
-    }
-    if (lane < nact) {
-      BF8 o;
+        for (int j = 0; j < 8; ++j) ss += x[j] * x[j];
+        ss = group_sum(ss);
+        const float rs = rsqrtf(ss / static_cast<float>(D) + eps);
+        const bool is_q = h < Hq;
+        float dot = 0.f;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) o.v[j] = f2bf(dx[j]);
-      reinterpret_cast<BF8*>(dst)[lane] = o;
+        for (int j = 0; j < 8; ++j) dot += dy[j] * (is_q ? gq[j] : gk[j]) * (x[j] * rs);
+        dot = group_sum(dot) / static_cast<float>(D);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float n = x[j] * rs;
+          dx[j] = rs * (dy[j] * (is_q ? gq[j] : gk[j]) - n * dot);
+          if (on && !is_v) {
+            if (is_q) accq[j] += dy[j] * n; else acck[j] += dy[j] * n;
+          }
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) dx[j] = dy[j];
+      }
+      if (on && !is_v) {
+        BF8 o;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o.v[j] = f2bf(dx[j]);
+        reinterpret_cast<BF8*>(dqkv + static_cast<size_t>(t) * ldqkv + off)[sl] = o;
+      }
     }
-   }
   }
   if (QK_NORM) {
+    // the head slots of a warp accumulated the same elements: fold them into slot 0
+    if (hpw > 1) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        for (int o2 = nact; o2 < 32; o2 <<= 1) {
+          accq[j] += __shfl_xor_sync(0xffffffffu, accq[j], o2);
+          acck[j] += __shfl_xor_sync(0xffffffffu, acck[j], o2);
+        }
+      }
+    }
     if (lane < nact) {
 #pragma unroll
       for (int j = 0; j < 8; ++j) s_w[warp][0][e0 + j] = accq[j], s_w[warp][1][e0 + j] = acck[j];
@@ -284,7 +307,13 @@ IX_API int ix_qk_norm_rope_bwd(const void* qkv, long long ldqkv, const void* pos
   if ((D & 7) || D > 256 || (rot_dim & 15) || rot_dim > D) return ixh::fail(ixh::IX_EARG, "qk_norm_rope_bwd: D=%d rot_dim=%d unsupported", D, rot_dim);
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   const int Htot = Hq + 2 * Hkv;
-  const int wpt = (Htot % 8 == 0) ? 8 : (Htot % 4 == 0) ? 4 : Htot;
+  const int nact = D >> 3;
+  const bool pow2 = (nact & (nact - 1)) == 0;
+  const int hpw = (pow2 && nact <= 16) ? 32 / nact : 1;
+  int red_width = 1;
+  while (red_width < nact) red_width <<= 1;
+  int wpt = (Htot + hpw - 1) / hpw;
+  if (wpt > 8) wpt = 8;
   const long long total = static_cast<long long>(T) * wpt;
   int grid = static_cast<int>((total + 3) / 4 > kQkBwdCtas ? kQkBwdCtas : (total + 3) / 4);
 #define IX_QB(QN, ZC)                                                                                                          \
@@ -292,7 +321,7 @@ IX_API int ix_qk_norm_rope_bwd(const void* qkv, long long ldqkv, const void* pos
       static_cast<const __nv_bfloat16*>(qkv), ldqkv, static_cast<const int*>(positions), static_cast<const float*>(cos_tab),   \
       static_cast<const float*>(sin_tab), static_cast<const __nv_bfloat16*>(qw), static_cast<const __nv_bfloat16*>(kw),        \
       static_cast<const __nv_bfloat16*>(dq), static_cast<const __nv_bfloat16*>(dk), static_cast<const __nv_bfloat16*>(dv),     \
-      static_cast<__nv_bfloat16*>(dqkv), static_cast<float*>(dw_partial), T, Hq, Hkv, D, rot_dim, eps, q_gate, wpt);
+      static_cast<__nv_bfloat16*>(dqkv), static_cast<float*>(dw_partial), T, Hq, Hkv, D, rot_dim, eps, q_gate, wpt, hpw, red_width);
   if (qk_norm) {
     if (zero_centered) IX_QB(true, true) else IX_QB(true, false)
   } else {
