@@ -16,6 +16,8 @@ Transports for the upper levels:
 
 from __future__ import annotations
 
+import os
+from collections import Counter
 from dataclasses import dataclass
 
 import torch
@@ -100,6 +102,63 @@ def tree_all_reduce(partial: torch.Tensor, group, tp: int) -> torch.Tensor:
     return tree_fold(gathered.view((tp,) + tuple(partial.shape)))
 
 
+# ------------------------------------------------------------------------------------ census and admission
+# Which transport served how many calls (reference: the pik transport census, ISO/ops/collectives/pik/allreduce.py:213-226,
+# 719-808), and the per-shape admission of the fused kernel (reference: pik/allreduce.py:476-486,1018-1068): the first
+# call of a shape runs BOTH the fused kernel and the plain path (leaf-tree GEMM, then the tree all-reduce), compares the
+# bits, and every rank of the group takes the worst answer (MIN all-reduce). A shape that is not admitted stays on
+# the plain path for the life of the process.
+_CENSUS: Counter = Counter()
+_ADMITTED: dict = {}
+
+
+def transport_census(reset: bool = False) -> dict:
+    """{(operation, transport): calls served}. Transports: ``fused_peer`` (GEMM + collective in one kernel),
+    ``peer_tree`` (stand-alone tree all-reduce over peer memory), ``nccl`` / ``gloo`` (all-gather + local fold),
+    ``local`` (tp = 1), ``refused`` (a shape whose probe failed, served by the plain path)."""
+    out = {f"{op}/{tr}": n for (op, tr), n in sorted(_CENSUS.items())}
+    if reset:
+        _CENSUS.clear()
+    return out
+
+
+def admitted_shapes() -> dict:
+    return dict(_ADMITTED)
+
+
+def _plain_row_parallel(x, w, ps, leaves_local, round_leaf):
+    part = leaftree_gemm(x, w, leaves_local, round_leaf)
+    return tree_all_reduce(part, ps.tp_group, ps.tp)
+
+
+def admit_fused_row_parallel(rt, ps, x, w, leaves_local, fused_dtype):
+    """Returns (admitted, result of THIS call or None). The probe runs once per (group, size class, N, K, leaves,
+    dtype); ``ISOEXEC_B200_TP_ADMISSION=0`` admits without probing."""
+    from ..core.testing import bitwise_equal
+
+    M = x.shape[0]
+    key = (id(ps.tp_group), "small" if M <= 256 else "large", w.shape[0], x.shape[1], leaves_local, str(fused_dtype))
+    if key in _ADMITTED:
+        return _ADMITTED[key], None
+    if os.environ.get("ISOEXEC_B200_TP_ADMISSION", "1") == "0":
+        _ADMITTED[key] = True
+        return True, None
+    want = _plain_row_parallel(x, w, ps, leaves_local, False).to(fused_dtype)
+    ok = True
+    try:
+        got = rt.row_parallel(x, w, leaves_local, out_dtype=fused_dtype)
+        rt.check()
+        ok = bool(bitwise_equal(got, want))
+    except Exception:  # noqa: BLE001 - a probe that cannot run is a refusal, not a crash
+        ok = False
+    if ps.tp > 1 and dist.is_initialized():
+        flag = torch.tensor([1 if ok else 0], dtype=torch.int32, device=x.device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=ps.tp_group)
+        ok = bool(int(flag.item()))
+    _ADMITTED[key] = ok
+    return ok, want       # the plain result has the same bits when admitted and is the fallback when not
+
+
 class _RowParallel(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, ps, leaves_local, round_leaf, out_dtype):
@@ -110,12 +169,23 @@ class _RowParallel(torch.autograd.Function):
             if tp_fused.fused_ok(x.shape[0], w.shape[0], x.shape[1], leaves_local):
                 # one kernel: leaf accumulators in TMEM, leaf tree in the epilogue, rank tree over peer memory
                 if ps.tp == 1:
+                    _CENSUS[("row_parallel", "local")] += 1
                     return tp_fused.leaftree_gemm_fused(x, w, leaves_local, out_f32=out_dtype == torch.float32).to(out_dtype)
                 rt = tp_fused.get(ps.tp_group)
                 if rt is not None:
-                    return rt.row_parallel(x, w, leaves_local, out_dtype=out_dtype if out_dtype == torch.float32 else torch.bfloat16).to(out_dtype)
-        part = leaftree_gemm(x, w, leaves_local, round_leaf)
-        full = tree_all_reduce(part, ps.tp_group, ps.tp)
+                    fdt = out_dtype if out_dtype == torch.float32 else torch.bfloat16
+                    ok, first = admit_fused_row_parallel(rt, ps, x, w, leaves_local, fdt)
+                    _CENSUS[("row_parallel", "fused_peer" if ok else "refused")] += 1
+                    if first is None:
+                        first = rt.row_parallel(x, w, leaves_local, out_dtype=fdt) if ok else _plain_row_parallel(x, w, ps, leaves_local, False)
+                    return first.to(out_dtype)
+        full = _plain_row_parallel(x, w, ps, leaves_local, round_leaf)
+        if ps.tp > 1:
+            from . import symm
+
+            _CENSUS[("row_parallel", "peer_tree" if (x.is_cuda and symm.enabled(ps.tp_group)) else str(dist.get_backend(ps.tp_group)))] += 1
+        else:
+            _CENSUS[("row_parallel", "local")] += 1
         return full.to(out_dtype)
 
     @staticmethod

@@ -517,3 +517,55 @@ def test_scoring_forward_can_be_skipped_on_policy_with_the_same_weights_bit_for_
     with pytest.raises((ForwardGateError, ContractViolation)):      # the ledger refuses at step 1, the gate afterwards
         tr_c.train_step(next(iter(tr_c.loader)))
     assert torch.equal(tr_c.policy.model.store.flat.detach(), before)       # refused before the optimizer step
+
+
+def test_fused_tp_admission_probe_and_transport_census():
+    """A shape is admitted to the fused GEMM+collective kernel only if its first call reproduces the plain path bit
+    for bit; a refused shape stays on the plain path; the census says who served what."""
+    from types import SimpleNamespace
+
+    from skyrl_isoexec_b200.parallel import tp
+
+    ps = SimpleNamespace(tp=1, tp_group=None)
+    torch.manual_seed(0)
+    x, w = torch.randn(12, 64), torch.randn(16, 64)
+    want = tp.leaftree_gemm(x, w, 4, False)
+
+    class Good:
+        calls = 0
+
+        def row_parallel(self, x, w, leaves, out_dtype=torch.float32):
+            Good.calls += 1
+            return tp.leaftree_gemm(x, w, leaves, False).to(out_dtype)
+
+        def check(self):
+            pass
+
+    class Bad(Good):
+        def row_parallel(self, x, w, leaves, out_dtype=torch.float32):
+            out = super().row_parallel(x, w, leaves, out_dtype).clone()
+            out[0, 0] = torch.nextafter(out[0, 0], torch.tensor(float("inf")))      # one ulp off
+            return out
+
+    class Broken(Good):
+        def check(self):
+            raise RuntimeError("a wait ran out")
+
+    tp._ADMITTED.clear()
+    ok, first = tp.admit_fused_row_parallel(Good(), ps, x, w, 4, torch.float32)
+    assert ok and torch.equal(first, want)
+    ok2, first2 = tp.admit_fused_row_parallel(Good(), ps, x, w, 4, torch.float32)
+    assert ok2 and first2 is None and Good.calls == 1                          # probed once per shape
+    ok3, first3 = tp.admit_fused_row_parallel(Bad(), ps, x, w[:8], 4, torch.float32)
+    assert not ok3 and torch.equal(first3, tp.leaftree_gemm(x, w[:8], 4, False))   # refused: the plain result is served
+    ok4, _ = tp.admit_fused_row_parallel(Broken(), ps, x, w[:4], 4, torch.float32)
+    assert not ok4
+    assert sorted(tp.admitted_shapes().values()) == [False, False, True]
+    tp._CENSUS.clear()
+    cfg = SimpleNamespace(pik_leaves=4, tp_invariant=True)
+    from skyrl_isoexec_b200.parallel.state import ParallelState
+
+    y = tp.row_parallel_linear(x, w, ParallelState.single(), cfg)
+    assert torch.equal(y, want)
+    assert tp.transport_census(reset=True) == {"row_parallel/local": 1} and tp.transport_census() == {}
+    tp._ADMITTED.clear()

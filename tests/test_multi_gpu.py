@@ -414,6 +414,10 @@ def _tp_model_worker(rank, world, port, q):
             lp1 = w1.forward(batch)
             res["tp2_vs_tp1_mismatches"] = count_bit_mismatches((lp1 * rmask).contiguous(), (ro * rmask).contiguous())
             res["status"] = _native.read_status()
+            from skyrl_isoexec_b200.parallel import tp as tp_ops
+
+            res["census"] = tp_ops.transport_census()
+            res["admitted"] = sorted(tp_ops.admitted_shapes().values())
             q.put(res)
     finally:
         dist.barrier()
@@ -437,6 +441,9 @@ def test_tensor_parallel_model_with_fused_kernels_is_bitwise_tp_invariant():
     print("tp model:", res)
     assert res["engine_vs_trainer_mismatches_tp"] == 0 and res["tp2_vs_tp1_mismatches"] == 0
     assert res["grad_norm_tp"] > 0 and res["status"] == 0
+    # every row-parallel shape passed its bitwise admission probe and was then served by the fused kernel
+    assert res["admitted"] and all(res["admitted"]), res["admitted"]
+    assert res["census"].get("row_parallel/fused_peer", 0) > 0 and "row_parallel/refused" not in res["census"], res["census"]
 
 
 def _ep_model_worker(rank, world, port, q):
