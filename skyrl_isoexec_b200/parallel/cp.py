@@ -1,8 +1,9 @@
 """Long-context sequence parallelism for attention: Ulysses-style head/sequence all-to-all and an all-gather
 form (reference: B/distributed/ulysses/utils.py:66-240 ``SeqAllToAll`` / gather helpers; the context-parallel
-all-gather autograd of B/distributed/megatron/model_utils.py:1438-1540). No ring or blockwise attention
-exists in the reference either; both forms below move bytes only, so the attention kernel sees complete
-sequences and the single-split, fixed-block numerics are untouched.
+all-gather autograd of B/distributed/megatron/model_utils.py:1438-1540). Those two forms move bytes only, so the
+attention kernel sees complete sequences and the single-split, fixed-block numerics are untouched. A ring /
+blockwise variant (absent from the reference) is at the end of the file: chunks of K/V travel around the ranks and
+the per-chunk results are folded in one fixed order; it is outside the bitwise contract.
 
 Layout: the packed token dimension is cut into ``cp`` contiguous, equal chunks (pad the micro-batch to a
 multiple of ``cp`` tokens); rank r holds chunk r of every per-token tensor.
@@ -114,3 +115,94 @@ def gather_sequence(x, ps):
 
 def scatter_sequence(x, ps):
     return shard_sequence(x, ps.cp_rank, ps.cp) if ps.cp > 1 else x
+
+
+# ------------------------------------------------------------------------------------ ring / blockwise attention
+# The K/V chunks travel around the ring of context-parallel ranks; every rank attends its local queries to one chunk
+# per step. The per-chunk results (o_b, lse_b) are kept and folded at the end in ASCENDING chunk order, whatever order
+# they arrived in, so the block-combine order is one fixed function of the layout. This variant is outside the bitwise
+# contract (the contract's attention consumes keys in 128-wide blocks with one running state); it exists for
+# sequences whose K/V do not fit one GPU and whose head count does not divide for the all-to-all form.
+class _RingShift(torch.autograd.Function):
+    """Forward: pass ``x`` to the next rank of the ring and return what the previous rank passed. Backward: the
+    gradient travels the other way."""
+
+    @staticmethod
+    def forward(ctx, x, ranks, me, group):
+        ctx.ranks, ctx.me, ctx.group = ranks, me, group
+        return _ring_exchange(x, ranks[(me + 1) % len(ranks)], ranks[(me - 1) % len(ranks)], group, me)
+
+    @staticmethod
+    def backward(ctx, g):
+        ranks, me = ctx.ranks, ctx.me
+        return _ring_exchange(g.contiguous(), ranks[(me - 1) % len(ranks)], ranks[(me + 1) % len(ranks)], ctx.group, me), None, None, None
+
+
+def _ring_exchange(x, dst, src, group, me):
+    x = x.contiguous()
+    out = torch.empty_like(x)
+    if dst == src and len({dst}) == 1 and dst == dist.get_rank():      # ring of one
+        return x.clone()
+    # even positions send first, odd positions receive first: no rank waits on a peer that is also waiting to send
+    if me % 2 == 0:
+        dist.send(x, dst, group=group)
+        dist.recv(out, src, group=group)
+    else:
+        dist.recv(out, src, group=group)
+        dist.send(x, dst, group=group)
+    return out
+
+
+def _chunk_attention(q, k, v, scale, q_off: int, k_off: int, causal: bool):
+    """Local queries against ONE chunk of keys. q [n, Hq, D], k/v [m, Hkv, D]. Returns (o [n, Hq, D] fp32 normalised
+    inside the chunk, lse [n, Hq] fp32; rows that see no key of the chunk get lse = -inf and o = 0)."""
+    n, Hq, _ = q.shape
+    m, Hkv, _ = k.shape
+    G = Hq // Hkv
+    qf = q.float().transpose(0, 1)                                   # [Hq, n, D]
+    kf = k.float().repeat_interleave(G, 1).transpose(0, 1)           # [Hq, m, D]
+    vf = v.float().repeat_interleave(G, 1).transpose(0, 1)
+    s = (qf @ kf.transpose(1, 2)) * scale                            # [Hq, n, m]
+    if causal:
+        qi = torch.arange(q_off, q_off + n, device=q.device)[:, None]
+        ki = torch.arange(k_off, k_off + m, device=q.device)[None, :]
+        s = s.masked_fill((ki > qi)[None], float("-inf"))
+    lse = torch.logsumexp(s, dim=-1)                                 # -inf where the whole row is masked
+    p = torch.exp(s - torch.where(torch.isinf(lse), torch.zeros_like(lse), lse)[..., None])
+    p = torch.where(torch.isinf(lse)[..., None], torch.zeros_like(p), p)
+    return (p @ vf).transpose(0, 1), lse.transpose(0, 1)
+
+
+def ring_attention(q, k, v, scale: float, ps, causal: bool = True):
+    """Blockwise attention over ONE sequence cut into ``cp`` equal contiguous chunks; this rank holds chunk
+    ``ps.cp_rank`` of q [n, Hq, D] and k, v [n, Hkv, D]. Differentiable (the ring shift carries gradients back).
+    Returns this rank's [n, Hq, D] in q's dtype."""
+    cp, r = ps.cp, ps.cp_rank
+    n = q.shape[0]
+    if cp == 1:
+        o, _ = _chunk_attention(q, k, v, scale, 0, 0, causal)
+        return o.to(q.dtype)
+    parts = {}
+    kv = torch.stack([k, v])                                          # one tensor, one shift per step: the backward
+    for step in range(cp):                                            # of the ring is then a single chain on every rank
+        src = (r - step) % cp                                         # whose chunk this rank holds at this step
+        if not causal or src <= r:
+            parts[src] = _chunk_attention(q, kv[0], kv[1], scale, r * n, src * n, causal)
+        if step + 1 < cp:                                             # every rank shifts, also those that skipped
+            kv = _RingShift.apply(kv, tuple(ps.cp_ranks), r, ps.cp_group)
+    # fold in ascending chunk order: out = sum_b exp(lse_b - lse) o_b
+    order = sorted(parts)
+    lse = parts[order[0]][1]
+    for b in order[1:]:
+        lse = torch.logaddexp(lse, parts[b][1])
+    out = None
+    for b in order:
+        o_b, lse_b = parts[b]
+        w = torch.exp(lse_b - lse)
+        w = torch.where(torch.isinf(lse_b), torch.zeros_like(w), w)
+        term = o_b * w[..., None]
+        out = term if out is None else out + term
+    # A rank that skipped the later chunks (causal) still has to take part in the backward of every shift: tie the last
+    # shifted tensor to the output with weight zero so that autograd walks the whole chain everywhere.
+    out = out + kv.sum() * 0.0
+    return out.to(q.dtype)
