@@ -40,7 +40,9 @@ class PolicyConfig:
     optimizer_config: OptimizerConfig = field(default_factory=OptimizerConfig)
     parallel: ParallelConfig = field(default_factory=ParallelConfig)
     seed: int = 0
-    keep_last_layers: int = 0           # layers whose activations are kept instead of recomputed in the backward
+    keep_last_layers: int = 0           # layers whose activations are kept instead of recomputed in the backward;
+                                        # -1 = as many as the first step's measured memory peak leaves room for
+    shard_optimizer: bool = True        # dp > 1: fp32 master weights and Adam moments are cut over the data-parallel ranks
 
 
 @dataclass

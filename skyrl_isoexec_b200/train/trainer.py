@@ -134,7 +134,7 @@ class RayPPOTrainer:
         mcfg = get_config(t.policy.model, **t.policy.model_overrides)
         model = DecoderLM(mcfg, self.ps, self.device, seed=t.policy.seed)
         wcfg = WorkerConfig(max_tokens_per_microbatch=t.max_tokens_per_microbatch, optimizer=t.policy.optimizer_config,
-                            keep_last_layers=t.policy.keep_last_layers,
+                            keep_last_layers=t.policy.keep_last_layers, shard_optimizer=t.policy.shard_optimizer,
                             want_entropy=t.algorithm.use_entropy_loss)
         algo = t.algorithm
         if not algo.max_seq_len:
