@@ -119,6 +119,15 @@ PRESETS: dict[str, ModelConfig] = {
         num_layers=32, num_q_heads=16, num_kv_heads=4, head_dim=128, ffn_size=9216,
         layer_types=_hybrid_pattern(32), gdn_k_heads=16, gdn_v_heads=32, gdn_head_dim=128, attn_output_gate=True,
         zero_centered_norm=True, max_position=40960),
+    # Llama-3 style dense decoder (the reference's tx model zoo, R/tx/models/llama3.py): no QK-norm, untied head
+    "llama3-8b": ModelConfig(
+        name="llama3-8b", architecture="LlamaForCausalLM", vocab_size=128256, hidden_size=4096, num_layers=32,
+        num_q_heads=32, num_kv_heads=8, head_dim=128, ffn_size=14336, qk_norm=False, rope_theta=5e5, rms_eps=1e-5,
+        max_position=8192),
+    "tiny-llama": ModelConfig(
+        name="tiny-llama", architecture="LlamaForCausalLM", vocab_size=2048, hidden_size=256, num_layers=2,
+        num_q_heads=4, num_kv_heads=2, head_dim=64, ffn_size=768, qk_norm=False, rope_theta=5e5, rms_eps=1e-5,
+        tie_embeddings=False, dtype="float32", max_position=512),
     # small variants used by tests and smoke runs
     "tiny-qwen3-bf16": ModelConfig(
         name="tiny-qwen3-bf16", architecture="Qwen3ForCausalLM", vocab_size=2048, hidden_size=256, num_layers=2,

@@ -79,6 +79,8 @@ def to_hf_state_dict(model: DecoderLM) -> dict[str, torch.Tensor]:
 
 def hf_config(cfg: ModelConfig) -> dict:
     arch = "Qwen3MoeForCausalLM" if cfg.has_moe else ("Qwen3NextForCausalLM" if cfg.has_gdn else "Qwen3ForCausalLM")
+    if not (cfg.has_moe or cfg.has_gdn or cfg.qk_norm):
+        arch = "LlamaForCausalLM"       # dense, no QK-norm: the Llama checkpoint layout (same tensor names minus q_norm / k_norm)
     d = {"architectures": [arch], "hidden_size": cfg.hidden_size, "num_hidden_layers": cfg.num_layers,
          "num_attention_heads": cfg.num_q_heads, "num_key_value_heads": cfg.num_kv_heads, "head_dim": cfg.head_dim,
          "intermediate_size": cfg.ffn_size, "vocab_size": cfg.vocab_size, "rope_theta": cfg.rope_theta, "rms_norm_eps": cfg.rms_eps,

@@ -354,7 +354,7 @@ def test_hf_export_roundtrip_and_dispatch_helpers(tmp_path):
     from skyrl_isoexec_b200.parallel import dispatch
     from skyrl_isoexec_b200.parallel.state import ParallelState
 
-    for preset in ("tiny-qwen3", "tiny-moe"):
+    for preset in ("tiny-qwen3", "tiny-moe", "tiny-llama"):
         cfg = get_config(preset)
         m = DecoderLM(cfg, seed=3)
         d = str(tmp_path / preset)
@@ -569,3 +569,21 @@ def test_fused_tp_admission_probe_and_transport_census():
     assert torch.equal(y, want)
     assert tp.transport_census(reset=True) == {"row_parallel/local": 1} and tp.transport_census() == {}
     tp._ADMITTED.clear()
+
+
+def test_llama_style_decoder_runs_one_rl_step_with_bitwise_rollout_logprobs(tmp_path):
+    """The dense family without QK-norm (Llama-3 style preset): one full step on CPU, engine == trainer bit for bit."""
+    from skyrl_isoexec_b200.models.config import get_config
+    from skyrl_isoexec_b200.train.entrypoints import main_base
+
+    assert get_config("llama3-8b").param_count() > 7.5e9 and not get_config("llama3-8b").qk_norm
+    ov = ["trainer.policy.model=tiny-llama", "trainer.train_batch_size=2", "trainer.policy_mini_batch_size=2",
+          "generator.n_samples_per_prompt=2", "generator.sampling_params.max_generate_length=8",
+          "generator.sampling_params.ignore_eos=true", "data.synthetic_prompt_len=8", "data.synthetic_prompts=8",
+          "trainer.max_prompt_length=8", "generator.inference_engine.num_kv_pages=16", "trainer.num_steps=1",
+          f"trainer.ckpt_path={tmp_path}", "trainer.ckpt_interval=0", "trainer.logger=jsonl"]
+    tr = main_base.BasePPOExp(SkyRLTrainConfig.from_cli_overrides(ov)).get_trainer()
+    tr.build_models()
+    tr.sync_weights()
+    m = tr.train_step(next(iter(tr.loader)))
+    assert m["policy/rollout_train_logprob_bit_mismatches"] == 0 and m["policy/grad_norm"] > 0
