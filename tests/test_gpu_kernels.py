@@ -180,8 +180,9 @@ def test_rmsnorm_bitwise_vs_cpu_oracle(N, zero_centered):
     assert (y_g.cpu().float() - ref).abs().max() <= 0.05 * ref.abs().max()
 
 
+@pytest.mark.parametrize("qk_norm", [True, False])
 @pytest.mark.parametrize("Hq,Hkv,D,gate", [(8, 2, 128, False), (4, 2, 64, False), (4, 2, 128, True)])
-def test_qk_norm_rope_bitwise_vs_cpu_oracle(Hq, Hkv, D, gate):
+def test_qk_norm_rope_bitwise_vs_cpu_oracle(Hq, Hkv, D, gate, qk_norm):
     torch.manual_seed(3)
     T = 53
     rows = (Hq * (2 if gate else 1) + 2 * Hkv) * D
@@ -194,7 +195,7 @@ def test_qk_norm_rope_bitwise_vs_cpu_oracle(Hq, Hkv, D, gate):
         rope = F.RopeTable(D, 1024, 1e6, dev)
         kp, vp = torch.zeros(256, Hkv, D, dtype=torch.bfloat16, device=dev), torch.zeros(256, Hkv, D, dtype=torch.bfloat16, device=dev)
         q = F.qk_norm_rope_fwd(qkv.to(dev), pos.to(dev), slots.to(dev), rope, qw.to(dev), kw.to(dev), kp, vp, Hq, Hkv, D, 1e-6,
-                               True, False, gate)
+                               qk_norm, False, gate)
         outs.append((q.cpu(), kp.cpu(), vp.cpu()))
     for a, b in zip(*outs):
         assert bitwise_equal(a, b)
