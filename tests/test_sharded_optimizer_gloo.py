@@ -86,3 +86,69 @@ def test_sharded_optimizer_matches_unsharded_bit_for_bit():
         assert same, f"rank {rank}: sharded and unsharded weights differ"
         assert cut_ok, f"rank {rank}: state did not round-trip"
         assert refused, f"rank {rank}: a state of another slice was accepted"
+
+
+def _ckpt_worker(rank, world, port, q, tmp):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    import torch.distributed as dist
+
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from skyrl_isoexec_b200.models.config import get_config
+        from skyrl_isoexec_b200.models.decoder import DecoderLM
+        from skyrl_isoexec_b200.parallel.state import ParallelState
+        from skyrl_isoexec_b200.train import checkpoint as ckpt
+        from skyrl_isoexec_b200.train.batch import TrainingInputBatch, build_sequences
+        from skyrl_isoexec_b200.train.policy_worker import OptimizerConfig, PolicyWorker, WorkerConfig
+
+        ps = ParallelState.build()
+        g = torch.Generator().manual_seed(40 + rank)
+        prompts = [torch.randint(0, 2048, (8,), generator=g).tolist() for _ in range(4)]
+        resp = [torch.randint(0, 2048, (10,), generator=g).tolist() for _ in range(4)]
+        seq, att, rmask = build_sequences(prompts, resp)
+        batch = TrainingInputBatch({"sequences": seq, "attention_mask": att, "response_mask": rmask, "loss_mask": rmask.clone(),
+                                    "advantages": torch.randn(rmask.shape, generator=g)})
+
+        def worker(seed):
+            return PolicyWorker(DecoderLM(get_config("tiny-qwen3"), ps, seed=seed),
+                                WorkerConfig(max_tokens_per_microbatch=64, optimizer=OptimizerConfig(lr=1e-2)))
+
+        def step(w):
+            w.forward_backward(batch)
+            w.optim_step()
+
+        a = worker(5)                                  # uninterrupted: three steps
+        for _ in range(3):
+            step(a)
+        b = worker(5)                                  # two steps, save, resume into a fresh worker, one more step
+        for _ in range(2):
+            step(b)
+        ckpt.save_checkpoint(tmp, 2, b, {"pos": 2}, {"global_step": 2}, ps)
+        c = worker(77)
+        assert c.opt.shard is not None
+        data_state, trainer_state = ckpt.load_checkpoint(ckpt.step_dir(tmp, 2), c, ps)
+        resumed_same = bool(torch.equal(c.model.store.flat.detach(), b.model.store.flat.detach())
+                            and torch.equal(c.opt.exp_avg, b.opt.exp_avg) and c.opt.step_count == 2)
+        step(c)
+        q.put((rank, resumed_same, bool(torch.equal(c.model.store.flat.detach(), a.model.store.flat.detach())),
+               data_state["pos"], trainer_state["global_step"]))
+    finally:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+@pytest.mark.timeout(300)
+def test_checkpoint_resume_with_a_sharded_optimizer_continues_bit_for_bit(tmp_path):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_ckpt_worker, args=(r, 2, port, q, str(tmp_path))) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = [q.get(timeout=200) for _ in range(2)]
+    for p in procs:
+        p.join(timeout=60)
+    for rank, resumed_same, continued_same, pos, step in got:
+        assert resumed_same, f"rank {rank}: the resumed worker does not hold the saved state"
+        assert continued_same, f"rank {rank}: save + resume + step differs from three uninterrupted steps"
+        assert pos == 2 and step == 2
