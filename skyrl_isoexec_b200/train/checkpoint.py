@@ -147,6 +147,28 @@ def _assemble_full(name: str, meta: dict, shards: list[dict]) -> torch.Tensor:
     return torch.cat(cols, dim=d)
 
 
+def _assemble_optimizer_state(shards: list[dict]) -> dict | None:
+    """Full optimizer state of one (tp, pp, ep) position from what its data-parallel ranks saved: either every rank
+    saved everything (take one), or each saved one slice of the flat buffer (concatenate in slice order)."""
+    pieces = {}
+    for s in shards:
+        o = s["optimizer"]
+        lo, hi, n = o.get("slice", (0, o["master"].numel(), o["master"].numel()))
+        pieces[(lo, hi)] = (o, n)
+    if not pieces:
+        return None
+    n = next(iter(pieces.values()))[1]
+    if (0, n) in pieces:
+        return dict(pieces[(0, n)][0])
+    spans = sorted(k for k in pieces if k[1] > k[0])
+    if not spans or spans[0][0] != 0 or spans[-1][1] != n or any(a[1] != b[0] for a, b in zip(spans, spans[1:])):
+        return None                                   # slices do not tile the buffer: leave the optimizer fresh
+    out = {k: torch.cat([pieces[sp][0][k] for sp in spans]) for k in ("master", "exp_avg", "exp_avg_sq")}
+    out["step"] = pieces[spans[0]][0]["step"]
+    out["slice"] = (0, n, n)
+    return out
+
+
 def load_checkpoint(path: str, policy, ps) -> tuple[dict, dict]:
     validate_checkpoint_dir(path)
     with open(os.path.join(path, "policy", "metadata.json")) as f:
@@ -169,8 +191,8 @@ def load_checkpoint(path: str, policy, ps) -> tuple[dict, dict]:
     else:
         # reshard: read the TP shards of data-parallel rank 0 of the saved job, rebuild, re-slice
         files = sorted(f for f in os.listdir(os.path.join(path, "policy")) if f.endswith(".distcp"))
-        shards = [torch.load(os.path.join(path, "policy", f), map_location="cpu", weights_only=False) for f in files]
-        shards = [s for s in shards if s["parallel"]["dp_rank"] == 0 and s["parallel"]["pp_rank"] == 0 and s["parallel"]["ep_rank"] == 0]
+        every = [torch.load(os.path.join(path, "policy", f), map_location="cpu", weights_only=False) for f in files]
+        shards = [s for s in every if s["parallel"]["dp_rank"] == 0 and s["parallel"]["pp_rank"] == 0 and s["parallel"]["ep_rank"] == 0]
         shards.sort(key=lambda s: s["parallel"]["tp_rank"])
         with torch.no_grad():
             for name, dst in model.named_weights():
@@ -179,6 +201,13 @@ def load_checkpoint(path: str, policy, ps) -> tuple[dict, dict]:
             if policy.opt.low_precision:
                 policy.opt.master.copy_(model.store.flat[policy.opt.lo:policy.opt.hi].float())
         policy.opt.step_count = int(shards[0]["lr_scheduler"]["step"])
+        if meta["tp"] == ps.tp and meta["pp"] == ps.pp and meta["ep"] == ps.ep:
+            # only the data-parallel degree changed: the flat layout of this rank is the saved one, so the optimizer
+            # state (whole, or the slices a sharded optimizer wrote) is put back together and cut again
+            full = _assemble_optimizer_state([s for s in every if s["parallel"]["tp_rank"] == ps.tp_rank
+                                              and s["parallel"]["pp_rank"] == ps.pp_rank and s["parallel"]["ep_rank"] == ps.ep_rank])
+            if full is not None:
+                policy.opt.load_state_dict({k: (v.to(policy.opt.master.device) if torch.is_tensor(v) else v) for k, v in full.items()})
     data_state = torch.load(os.path.join(path, "data.pt"), weights_only=False)
     trainer_state = torch.load(os.path.join(path, "trainer_state.pt"), weights_only=False)
     return data_state, trainer_state

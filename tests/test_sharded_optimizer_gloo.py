@@ -152,3 +152,19 @@ def test_checkpoint_resume_with_a_sharded_optimizer_continues_bit_for_bit(tmp_pa
         assert resumed_same, f"rank {rank}: the resumed worker does not hold the saved state"
         assert continued_same, f"rank {rank}: save + resume + step differs from three uninterrupted steps"
         assert pos == 2 and step == 2
+    # the same checkpoint read by ONE process (the data-parallel degree changed): weights, step count and the Adam
+    # state put back together from the two slices
+    from skyrl_isoexec_b200.models.config import get_config
+    from skyrl_isoexec_b200.models.decoder import DecoderLM
+    from skyrl_isoexec_b200.parallel.state import ParallelState
+    from skyrl_isoexec_b200.train import checkpoint as ckpt
+    from skyrl_isoexec_b200.train.policy_worker import PolicyWorker, WorkerConfig
+
+    ps1 = ParallelState.single()
+    w = PolicyWorker(DecoderLM(get_config("tiny-qwen3"), ps1, seed=1), WorkerConfig())
+    ckpt.load_checkpoint(ckpt.step_dir(str(tmp_path), 2), w, ps1)
+    shards = [torch.load(f"{ckpt.step_dir(str(tmp_path), 2)}/policy/__{r}_0.distcp", weights_only=False) for r in range(2)]
+    want = torch.cat([s["optimizer"]["exp_avg"] for s in shards])
+    assert w.opt.shard is None and w.opt.step_count == 2
+    assert w.opt.exp_avg.numel() == w.opt.n and torch.equal(w.opt.exp_avg, want) and float(want.abs().sum()) > 0
+    assert torch.equal(w.opt.master, w.model.store.flat.detach().float())
