@@ -13,6 +13,7 @@ import json
 import typing
 from dataclasses import dataclass, field, fields, is_dataclass
 
+from ..utils.profiler import ProfilerConfig
 from .algorithms import AlgorithmConfig, OffPolicyCorrection
 from .policy_worker import OptimizerConfig
 
@@ -152,6 +153,9 @@ class TrainerConfig:
     recompute_old_logprobs_per_minibatch: bool = False
     dump_data_batch: bool = False
     num_steps: int = -1                 # stop after this many global steps (-1: run the epochs out)
+    profiler: ProfilerConfig = field(default_factory=ProfilerConfig)    # torch.profiler over a window of steps
+    nvtx: bool = False                  # NVTX range around every phase of a step (for timeline tools)
+    record_memory: str = ""             # directory: allocator history on, one snapshot after each policy update
 
 
 @dataclass

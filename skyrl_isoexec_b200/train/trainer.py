@@ -390,9 +390,22 @@ class RayPPOTrainer:
         self.engine.reset_prefix_cache()
 
     # ------------------------------------------------------------------ the loop
+    def _observability(self):
+        """Profiler window, NVTX ranges and allocator history, as configured (all off by default)."""
+        if getattr(self, "_prof", None) is None:
+            from ..utils.profiler import Profiler, start_memory_history
+
+            t = self.cfg.trainer
+            self._prof = Profiler(t.profiler, self.rank)
+            Timer.nvtx = bool(t.nvtx)
+            if t.record_memory:
+                start_memory_history()
+        return self._prof
+
     def train_step(self, rows: list[dict]) -> dict:
         """One full RL step on this rank's prompt shard. Returns the step's metrics."""
         self.all_metrics, self.all_timings = {}, {}
+        self._observability().step()
         self.global_step += 1
         T = self.all_timings
         with Timer("step", T):
@@ -433,6 +446,10 @@ class RayPPOTrainer:
                 batch = self.compute_advantages_and_returns(batch)
             with Timer("policy_train", T):
                 self.train_critic_and_policy(batch)
+            if self.cfg.trainer.record_memory:
+                from ..utils.profiler import save_memory_snapshot
+
+                save_memory_snapshot(self.cfg.trainer.record_memory, f"step{self.global_step}_policy_train", self.rank)
             with Timer("sync_weights", T):
                 self.sync_weights()
         t = self.cfg.trainer

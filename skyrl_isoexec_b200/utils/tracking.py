@@ -18,12 +18,19 @@ class Timer:
         self.name, self.sink, self.cuda_sync = name, sink, cuda_sync
         self.elapsed = 0.0
 
+    nvtx = False        # process-wide switch: every timed phase is also an NVTX range
+
     def __enter__(self):
         if self.cuda_sync:
             import torch
 
             if torch.cuda.is_available():
                 torch.cuda.synchronize()
+        if Timer.nvtx:
+            import torch
+
+            if torch.cuda.is_available():
+                torch.cuda.nvtx.range_push(self.name)
         self.t0 = time.perf_counter()
         return self
 
@@ -34,6 +41,11 @@ class Timer:
             if torch.cuda.is_available():
                 torch.cuda.synchronize()
         self.elapsed = time.perf_counter() - self.t0
+        if Timer.nvtx:
+            import torch
+
+            if torch.cuda.is_available():
+                torch.cuda.nvtx.range_pop()
         if self.sink is not None:
             self.sink[self.name] = self.sink.get(self.name, 0.0) + self.elapsed
         return False

@@ -587,3 +587,22 @@ def test_llama_style_decoder_runs_one_rl_step_with_bitwise_rollout_logprobs(tmp_
     tr.sync_weights()
     m = tr.train_step(next(iter(tr.loader)))
     assert m["policy/rollout_train_logprob_bit_mismatches"] == 0 and m["policy/grad_norm"] > 0
+
+
+def test_profiler_window_and_phase_timers_are_wired_into_the_step(tmp_path):
+    from skyrl_isoexec_b200.train.entrypoints import main_base
+
+    ov = ["trainer.policy.model=tiny-qwen3", "trainer.train_batch_size=2", "trainer.policy_mini_batch_size=2",
+          "generator.n_samples_per_prompt=2", "generator.sampling_params.max_generate_length=4",
+          "generator.sampling_params.ignore_eos=true", "data.synthetic_prompt_len=8", "data.synthetic_prompts=12",
+          "trainer.max_prompt_length=8", "generator.inference_engine.num_kv_pages=16", "trainer.num_steps=3",
+          f"trainer.ckpt_path={tmp_path}", "trainer.ckpt_interval=0", "trainer.logger=jsonl",
+          "trainer.profiler.enable=true", "trainer.profiler.start_step=1", "trainer.profiler.end_step=2",
+          f"trainer.profiler.save_path={tmp_path}/prof", "trainer.nvtx=true"]
+    tr = main_base.BasePPOExp(SkyRLTrainConfig.from_cli_overrides(ov)).run()
+    assert tr.global_step == 3
+    assert (tmp_path / "prof" / "trace_rank0.json").stat().st_size > 1000      # the window [1, 2) was captured
+    assert {"timing/generate", "timing/fwd_logprobs", "timing/policy_train"} <= set(tr.all_metrics)
+    from skyrl_isoexec_b200.utils.tracking import Timer
+
+    Timer.nvtx = False
