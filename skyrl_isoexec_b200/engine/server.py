@@ -7,7 +7,7 @@ engine and does continuous batching across all connections.
   data plane     POST /generate               token-in / token-out ({prompt_token_ids, sampling_params, session_id})
                  POST /v1/completions         OpenAI-compatible (``prompt`` may be text or token ids)
                  POST /v1/chat/completions    OpenAI-compatible (needs a tokenizer with a chat template)
-  control plane  GET  /health, /get_server_info
+  control plane  GET  /health, /get_server_info, /metrics (Prometheus text format)
                  POST /pause {mode: abort|keep|finish}, /resume, /sleep, /wake_up, /reset_prefix_cache,
                       /update_weights {path} (a checkpoint directory or a flat .pt), /shutdown
 
@@ -69,6 +69,14 @@ class InferenceServer:
                     return self._reply(200, outer.info())
                 if self.path == "/v1/models":
                     return self._reply(200, {"object": "list", "data": [{"id": outer.model_name, "object": "model"}]})
+                if self.path == "/metrics":
+                    body = outer.metrics_text().encode()
+                    self.send_response(200)
+                    self.send_header("Content-Type", "text/plain; version=0.0.4")
+                    self.send_header("Content-Length", str(len(body)))
+                    self.end_headers()
+                    self.wfile.write(body)
+                    return None
                 self._reply(404, {"error": f"no route {self.path}"})
 
             def do_POST(self):
@@ -103,6 +111,26 @@ class InferenceServer:
         return {"model": self.model_name, "tp_size": ps.tp, "dp_size": 1, "pp_size": 1, "paused": self._paused_mode,
                 "asleep": bool(getattr(self.llm, "asleep", False)), "requests_served": self.requests_served,
                 "max_model_len": self.llm.max_len}
+
+    def metrics_text(self) -> str:
+        """Engine counters in the Prometheus text format (the reference scrapes vLLM's /metrics into its tracker,
+        R/train/utils/vllm_metrics_scraper.py). Counters are cumulative since the server started."""
+        st = dict(getattr(self.llm, "stats", {}) or {})
+        rows = [("isoexec_requests_served_total", "counter", self.requests_served),
+                ("isoexec_engine_steps_total", "counter", st.get("steps", 0)),
+                ("isoexec_tokens_total", "counter", st.get("tokens", 0)),
+                ("isoexec_prefill_tokens_total", "counter", st.get("prefill_tokens", 0)),
+                ("isoexec_decode_tokens_total", "counter", st.get("decode_tokens", 0)),
+                ("isoexec_h2d_bytes_total", "counter", st.get("h2d_bytes", 0)),
+                ("isoexec_d2h_bytes_total", "counter", st.get("d2h_bytes", 0)),
+                ("isoexec_requests_running", "gauge", len(getattr(self.llm, "running", []) or [])),
+                ("isoexec_requests_waiting", "gauge", len(getattr(self.llm, "waiting", []) or [])),
+                ("isoexec_paused", "gauge", 0 if self._paused_mode in (None, "", "none") else 1)]
+        out = []
+        for name, kind, val in rows:
+            out.append(f"# TYPE {name} {kind}")
+            out.append(f'{name}{{model="{self.model_name}"}} {float(val):g}')
+        return "\n".join(out) + "\n"
 
     # ------------------------------------------------------------------ the engine loop (one thread owns the engine)
     def _engine_loop(self) -> None:
@@ -286,6 +314,20 @@ class RemoteInferenceClient(InferenceEngineInterface):
                 self.retries += 1
                 time.sleep(self.backoff_s * (2 ** attempt))
         raise ConnectionError(f"{url}{path}: no answer after {self.max_retries + 1} attempts: {last}")
+
+    def scrape_metrics(self) -> dict:
+        """GET /metrics of every server, summed per metric name: ``{"engine/<name>": value}`` for the tracker."""
+        import urllib.request
+
+        tot: dict = {}
+        for u in self.urls:
+            with urllib.request.urlopen(u + "/metrics", timeout=10) as r:
+                for line in r.read().decode().splitlines():
+                    if line and not line.startswith("#"):
+                        name, val = line.rsplit(" ", 1)
+                        key = "engine/" + name.split("{", 1)[0]
+                        tot[key] = tot.get(key, 0.0) + float(val)
+        return tot
 
     def _pick(self, session_id=None) -> str:
         if session_id is not None:

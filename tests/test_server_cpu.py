@@ -31,6 +31,10 @@ def test_server_data_and_control_plane(tmp_path):
         out = asyncio.run(cl.generate({"prompt_token_ids": prompts, "sampling_params": sp, "session_ids": list("abcde")}))
         assert all(len(r) == 7 for r in out["response_ids"]) and all(len(l) == 7 for l in out["response_logprobs"])
         assert sum(i["requests_served"] for i in cl.server_info()) == 5
+        # Prometheus-style counters, summed over the servers
+        m = cl.scrape_metrics()
+        assert m["engine/isoexec_requests_served_total"] == 5 and m["engine/isoexec_decode_tokens_total"] >= 5 * 6
+        assert m["engine/isoexec_prefill_tokens_total"] == 5 * 9 and m["engine/isoexec_requests_running"] == 0
         # the logprobs the server reports are the model's: a clean scoring pass reproduces them bit for bit
         from skyrl_isoexec_b200.train.batch import TrainingInputBatch, build_sequences
         from skyrl_isoexec_b200.train.policy_worker import PolicyWorker
