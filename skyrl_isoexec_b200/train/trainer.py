@@ -400,6 +400,12 @@ class RayPPOTrainer:
             Timer.nvtx = bool(t.nvtx)
             if t.record_memory:
                 start_memory_history()
+            self._gpu_mon = None
+            if t.gpu_monitor and self.device.type == "cuda":
+                from ..utils.gpu_monitor import GpuMonitor
+
+                self._gpu_mon = GpuMonitor(self.device.index or 0, period_s=0.5)
+                self._gpu_mon.start()
         return self._prof
 
     def train_step(self, rows: list[dict]) -> dict:
@@ -461,6 +467,9 @@ class RayPPOTrainer:
         self.all_metrics["generate/response_tokens"] = ntok
         self.all_metrics["generate/tokens_per_s"] = ntok / max(1e-9, T["generate"])
         self.all_metrics.update({f"timing/{k}": v for k, v in T.items()})
+        if getattr(self, "_gpu_mon", None) is not None:
+            g = self._gpu_mon.summary(reset=True)
+            self.all_metrics.update({f"gpu/{k}": (",".join(v) if isinstance(v, list) else v) for k, v in g.items()})
         if self.tracker is not None:
             self.tracker.log(self.all_metrics, self.global_step)
         return dict(self.all_metrics)

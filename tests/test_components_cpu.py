@@ -606,3 +606,22 @@ def test_profiler_window_and_phase_timers_are_wired_into_the_step(tmp_path):
     from skyrl_isoexec_b200.utils.tracking import Timer
 
     Timer.nvtx = False
+
+
+def test_gpu_monitor_parses_and_summarises_with_a_fake_query():
+    import time
+
+    from skyrl_isoexec_b200.utils.gpu_monitor import GpuMonitor, parse_row
+
+    assert parse_row("garbage") is None and parse_row("a, b, c, d, e, f") is None
+    r = parse_row("1740, 1965, 985.2, 99, 160000, Not Active, Not Active, Not Active, Active")
+    assert r["sm_mhz"] == 1740 and r["reasons"] == {"sw_power_cap"}
+    lines = iter(["1700, 1965, 900.0, 98, 1000, Not Active, Not Active, Not Active, Active",
+                  "1800, 1965, 950.0, 99, 2000, Not Active, Not Active, Not Active, Not Active",
+                  "1750, 1965, 990.0, 97, 1500, Not Active, Active, Not Active, Active"] + ["bad"] * 1000)
+    mon = GpuMonitor(0, period_s=0.01, runner=lambda: next(lines))
+    mon.start()
+    time.sleep(0.3)
+    s = mon.stop()
+    assert s["samples"] == 3 and s["sm_mhz"] == 1750 and s["sm_max_mhz"] == 1965 and s["mem_mib"] == 2000
+    assert s["reasons"] == ["hw_thermal_slowdown", "sw_power_cap"]
