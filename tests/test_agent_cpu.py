@@ -72,3 +72,26 @@ def test_agent_trajectories_train_through_the_real_engine(tmp_path):
     mask = batch["loss_mask"]
     assert torch.equal((lp * mask), (batch["rollout_logprobs"] * mask))           # model tokens: bitwise on-policy
     assert float(mask.sum()) == 4 * 24 and (batch["response_mask"].sum() > mask.sum())
+
+
+def test_codeact_agent_runs_code_keeps_state_between_snippets_and_masks_observations():
+    from skyrl_isoexec_b200.agent.codeact import CodeActAgent
+
+    tok = ByteTokenizer()
+    script = ["First the data.\n<execute_python>\nxs = [3, 4, 5]\nprint(sum(xs))\n</execute_python>",
+              "<execute_python>\nprint(1 / 0)\n</execute_python>",                       # an error: not added to the prelude
+              "<execute_python>\nprint(sum(x * x for x in xs))\n</execute_python>",      # xs persists; the earlier print does not repeat
+              "<execute_bash>ls</execute_bash>",
+              "<finish>50</finish>"]
+    agent = CodeActAgent(ScriptedEngine(tok, script), tok, max_turns=6)
+    inst = [{"id": "c1", "task": "Sum of squares of 3, 4, 5?", "judge": lambda ans, tr: 1.0 if ans == "50" else 0.0}]
+    (t,) = asyncio.run(AsyncDispatcher(agent, max_parallel=1).run(inst))
+    assert t.finish == "50" and t.reward == 1.0 and t.turns == 5 and t.tool_calls == ["python", "python", "python"]
+    text = tok.decode(t.response_ids)
+    assert "ZeroDivisionError" in text and "bash is not available" in text
+    first = text.index("</execute_python>")
+    third_obs = text[text.rindex("</execute_python>"):]
+    assert "12" in text[first:first + 80] and "50" in third_obs and "12" not in third_obs.split("<finish>")[0].split("execute_bash")[0]
+    assert len(t.response_ids) == len(t.loss_mask) == len(t.logprobs) and 0 < sum(t.loss_mask) < len(t.loss_mask)
+    go, uids = to_generator_output([t])
+    assert uids == ["c1"] and sum(go["rewards"][0]) == 1.0
