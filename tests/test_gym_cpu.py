@@ -4,7 +4,7 @@ from skyrl_isoexec_b200.gym.envs import aime
 
 
 def test_registered_environments():
-    assert {"aime", "gsm8k", "lcb", "search", "searchcode", "sql", "multiply", "even_tokens"} <= set(gym.registered_envs())
+    assert {"aime", "gsm8k", "lcb", "rlm", "search", "searchcode", "sql", "multiply", "even_tokens"} <= set(gym.registered_envs())
 
 
 def test_aime_scoring():
@@ -55,3 +55,30 @@ def test_code_envs_run_tests_in_a_subprocess():
     o = sc.step("<search>add two numbers</search>")
     assert "def add" in o["observations"][0]["content"]
     assert sc.step("```python\ndef add(a, b):\n    return a + b\n```")["reward"] == 1.0
+
+
+def test_rlm_env_repl_over_a_long_context():
+    lines = [f"row {i}: filler" for i in range(2000)]
+    lines[1234] = "row 1234: the invoice total is 987.50 EUR"
+    ctx = "\n".join(lines)
+    mk = lambda **kw: gym.make("rlm", {}, {"context": ctx, "reward_spec": {"ground_truth": "987.50"}, "max_turns": 5, **kw})
+    env = mk()
+    prompt, info = env.init([{"role": "user", "content": "What is the invoice total?"}])
+    assert prompt[0]["role"] == "system" and "length" in prompt[0]["content"] and info["context_len"] == len(ctx)
+    assert ctx[:50] not in prompt[0]["content"]                       # the context itself is NOT in the prompt
+    r = env.step("Let me look.\n```repl\nhits = [l for l in context.splitlines() if 'invoice' in l]\nprint(hits)\n```")
+    assert not r["done"] and "987.50 EUR" in r["observations"][0]["content"]
+    r = env.step("```repl\nprint(1/0)\n```")                          # an error is shown and not kept
+    assert not r["done"] and "ZeroDivisionError" in r["observations"][0]["content"]
+    r = env.step("```repl\ntotal = hits[0].split('is ')[1].split()[0]\nprint(SHOW_VARS())\n```")    # hits persists
+    assert "'hits'" in r["observations"][0]["content"] and "'total'" in r["observations"][0]["content"]
+    r = env.step("FINAL_VAR(total)")
+    assert r["done"] and r["reward"] == 1.0 and r["metadata"]["how"] == "FINAL_VAR"
+    assert env.get_metrics() == {"rlm/turns": 4, "rlm/blocks_run": 3, "rlm/block_errors": 1}
+    # direct answers, wrong answers, the turn limit, a variable that does not exist
+    assert mk().step("FINAL(987.50)")["reward"] == 1.0 and mk().step("FINAL(12)")["reward"] == 0.0
+    assert mk(reward_spec={"ground_truth": "987.50", "match": "contains"}).step("FINAL(it is 987.50 EUR)")["reward"] == 1.0
+    e = mk(max_turns=2)
+    assert "FINAL_VAR failed" in e.step("FINAL_VAR(nope)")["observations"][0]["content"]
+    out = e.step("no code here")
+    assert out["done"] and out["reward"] == 0.0 and out["metadata"]["how"] == "turn limit"
