@@ -41,13 +41,16 @@ class SkyRLTrainBackend:
         seq, att, rmask = build_sequences([d["prompt_ids"] for d in data], [d["response_ids"] for d in data])
         B, R = rmask.shape
         adv, old = torch.zeros(B, R), torch.zeros(B, R)
+        lmask = rmask.clone()
         for i, d in enumerate(data):
             n = len(d["response_ids"])
             a = d.get("advantages", 1.0)
             adv[i, :n] = torch.tensor(a, dtype=torch.float32) if isinstance(a, (list, tuple)) else float(a)
             if d.get("logprobs") is not None:
                 old[i, :n] = torch.tensor(d["logprobs"], dtype=torch.float32)
-        return TrainingInputBatch({"sequences": seq, "attention_mask": att, "response_mask": rmask, "loss_mask": rmask.clone(),
+            if d.get("loss_mask") is not None:          # multi-turn data: observation tokens carry weight 0
+                lmask[i, :n] = torch.tensor(d["loss_mask"], dtype=lmask.dtype)
+        return TrainingInputBatch({"sequences": seq, "attention_mask": att, "response_mask": rmask, "loss_mask": lmask,
                                    "advantages": adv, "action_log_probs": old, "rollout_logprobs": old.clone()})
 
     def handle(self, req: dict) -> dict:

@@ -95,3 +95,33 @@ def test_codeact_agent_runs_code_keeps_state_between_snippets_and_masks_observat
     assert len(t.response_ids) == len(t.loss_mask) == len(t.logprobs) and 0 < sum(t.loss_mask) < len(t.loss_mask)
     go, uids = to_generator_output([t])
     assert uids == ["c1"] and sum(go["rewards"][0]) == 1.0
+
+
+def test_agents_run_against_a_tinker_service_and_train_it_on_their_trajectories(tmp_path):
+    """The model that a Tinker-style service is training serves the agent's turns; the trajectories go back as
+    forward_backward data with observation tokens masked, and the service's forward reproduces the sampled logprobs
+    on the model tokens bit for bit."""
+    from skyrl_isoexec_b200.agent.integrations import TinkerSamplingEngine, trajectories_to_tinker_batch
+    from skyrl_isoexec_b200.tinker.api import TinkerClient, TinkerServer
+
+    srv = TinkerServer(db_path=str(tmp_path / "q.db"), device="cpu").start()
+    try:
+        cl = TinkerClient(srv.url)
+        mid = cl.create_model(base_model="tiny-qwen3", lr=1e-3)
+        tok = ByteTokenizer()
+        tools = ToolRegistry()
+        tools.register("echo", lambda **kw: kw, "returns its arguments")
+        eng = TinkerSamplingEngine(cl, mid)
+        agent = ReActAgent(eng, tok, tools, max_turns=2, sampling_params={"max_generate_length": 10, "ignore_eos": True})
+        inst = [{"id": f"t{i}", "task": f"task {i}", "judge": lambda ans, t: float(t.response_ids[0] % 2)} for i in range(2)]
+        trajs = asyncio.run(AsyncDispatcher(agent, max_parallel=2).run(inst, n_samples=1))
+        assert eng.calls == 4 and all(t.turns == 2 and sum(t.loss_mask) == 20 < len(t.loss_mask) for t in trajs)
+        batch = trajectories_to_tinker_batch(trajs)
+        fwd = cl.call("forward", model_id=mid, **batch)
+        for t, lp in zip(trajs, fwd["logprobs"]):
+            assert [a for a, m in zip(lp, t.loss_mask) if m] == [a for a, m in zip(t.logprobs, t.loss_mask) if m]
+        out = cl.call("forward_backward", model_id=mid, loss_fn="importance_sampling", **batch)
+        assert out["num_tokens"] == 40                                   # only the model tokens carry loss
+        assert cl.call("optim_step", model_id=mid, adam_params={})["step"] == 1
+    finally:
+        srv.shutdown()
