@@ -283,6 +283,8 @@ class FlatAdamW:
     def _make_hook(self, view, name):
         def hook(p):
             g = p.grad
+            if g is None:          # another optimizer on the same parameters has already taken it
+                return
             if g.is_cuda and g.dtype == torch.bfloat16 and g.is_contiguous() and g.numel() % 8 == 0:
                 # main_grad += float(grad), vectorised (csrc/loss_optim.cu); torch's mixed-dtype add_ runs at a quarter of the bandwidth
                 _native.check(_native.lib().ix_accum_bf16_to_f32(view.data_ptr(), g.data_ptr(), g.numel(), 1, _native.stream()),

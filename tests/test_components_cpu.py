@@ -625,3 +625,12 @@ def test_gpu_monitor_parses_and_summarises_with_a_fake_query():
     s = mon.stop()
     assert s["samples"] == 3 and s["sm_mhz"] == 1750 and s["sm_max_mhz"] == 1965 and s["mem_mib"] == 2000
     assert s["reasons"] == ["hw_thermal_slowdown", "sw_power_cap"]
+
+
+def test_tinker_and_memory_sweep_benchmarks_run_on_cpu():
+    from skyrl_isoexec_b200.benchmarks import bench_tinker, memory_sweep
+
+    r = bench_tinker.run("tiny-qwen3", requests=2, device="cpu", prompt_len=6, response_len=4)
+    assert r["sample"]["tokens_per_s"] > 0 and r["train"]["steps_per_s"] > 0
+    rows = memory_sweep.run("tiny-qwen3", 0, [64, 128], 32, "cpu")
+    assert [x["tokens"] for x in rows] == [64, 128] and all(x["tokens_per_s"] > 0 and x["estimate_gib"] >= 0 for x in rows)
