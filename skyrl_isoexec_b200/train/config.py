@@ -178,11 +178,63 @@ class SkyRLTrainConfig:
             set_by_path(cfg, key.strip(), val.strip())
         return cfg
 
+    @classmethod
+    def from_file(cls, path: str, overrides: list[str] | None = None) -> "SkyRLTrainConfig":
+        """A YAML or JSON file with the nested config tree (any subset of keys), then ``key=value`` overrides on top.
+        Keys of older config files are translated first (``LEGACY_KEYS``; reference: the legacy YAML translation of
+        R/train/config/config.py:1001-1056)."""
+        with open(path) as f:
+            text = f.read()
+        if path.endswith(".json"):
+            tree = json.loads(text)
+        else:
+            import yaml
+
+            tree = yaml.safe_load(text) or {}
+        if not isinstance(tree, dict):
+            raise ValueError(f"{path}: the top level of a config file must be a mapping")
+        cfg = cls()
+        for key, val in _flatten(tree):
+            key = LEGACY_KEYS.get(key, key)
+            text_val = val if isinstance(val, str) else json.dumps(val)
+            if text_val == "null":
+                text_val = "none"
+            set_by_path(cfg, key, text_val)
+        for arg in overrides or []:
+            if "=" not in arg:
+                raise ValueError(f"override {arg!r} is not key=value")
+            k, v = arg.split("=", 1)
+            set_by_path(cfg, LEGACY_KEYS.get(k.strip(), k.strip()), v.strip())
+        return cfg
+
     def to_dict(self) -> dict:
         return dataclasses.asdict(self)
 
     def dumps(self) -> str:
         return json.dumps(self.to_dict(), indent=1, sort_keys=True, default=str)
+
+
+# old key -> current key (files written for earlier layouts of the tree keep working)
+LEGACY_KEYS = {
+    "trainer.policy.model.path": "trainer.policy.model",
+    "trainer.policy_mini_batch": "trainer.policy_mini_batch_size",
+    "trainer.algorithm.eps_clip": "trainer.algorithm.eps_clip_low",
+    "generator.num_samples": "generator.n_samples_per_prompt",
+    "generator.max_generate_length": "generator.sampling_params.max_generate_length",
+    "generator.temperature": "generator.sampling_params.temperature",
+    "trainer.keep_last_layers": "trainer.policy.keep_last_layers",
+}
+
+
+def _flatten(tree: dict, prefix: str = ""):
+    """Nested mapping -> (dotted key, leaf) pairs. A mapping under a key whose config field is itself a dict (for
+    instance ``trainer.policy.model_overrides``) is a leaf."""
+    for k, v in tree.items():
+        key = f"{prefix}{k}"
+        if isinstance(v, dict) and not key.endswith(("model_overrides", "additional_kwargs", "env_extras")):
+            yield from _flatten(v, key + ".")
+        else:
+            yield key, v
 
 
 def _coerce(val: str, tp):

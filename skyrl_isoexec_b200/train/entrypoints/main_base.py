@@ -64,7 +64,14 @@ class BasePPOExp:
 
 
 def main(argv=None) -> None:
-    cfg = SkyRLTrainConfig.from_cli_overrides(list(sys.argv[1:] if argv is None else argv))
+    """``main_base [--config file.yaml] key=value ...``: an optional YAML / JSON config file, then overrides."""
+    args = list(sys.argv[1:] if argv is None else argv)
+    path = None
+    if args and args[0] in ("--config", "-c"):
+        path, args = args[1], args[2:]
+    elif args and args[0].startswith("--config="):
+        path, args = args[0].split("=", 1)[1], args[1:]
+    cfg = SkyRLTrainConfig.from_file(path, args) if path else SkyRLTrainConfig.from_cli_overrides(args)
     BasePPOExp(cfg).run()
 
 

@@ -634,3 +634,35 @@ def test_tinker_and_memory_sweep_benchmarks_run_on_cpu():
     assert r["sample"]["tokens_per_s"] > 0 and r["train"]["steps_per_s"] > 0
     rows = memory_sweep.run("tiny-qwen3", 0, [64, 128], 32, "cpu")
     assert [x["tokens"] for x in rows] == [64, 128] and all(x["tokens_per_s"] > 0 and x["estimate_gib"] >= 0 for x in rows)
+
+
+def test_config_file_with_nested_keys_legacy_names_and_overrides(tmp_path):
+    p = tmp_path / "run.yaml"
+    p.write_text("""
+trainer:
+  train_batch_size: 4
+  policy_mini_batch: 2            # legacy name
+  policy:
+    model: tiny-moe
+    model_overrides: {num_layers: 1}
+  algorithm:
+    eps_clip: 0.3                 # legacy name
+  isoexec:
+    reuse_rollout_logprobs: true
+generator:
+  num_samples: 2                  # legacy name
+  sampling_params:
+    stop: null
+""")
+    cfg = SkyRLTrainConfig.from_file(str(p), ["trainer.train_batch_size=8", "generator.temperature=0.5"])
+    t = cfg.trainer
+    assert t.train_batch_size == 8 and t.policy_mini_batch_size == 2 and t.policy.model == "tiny-moe"
+    assert t.policy.model_overrides == {"num_layers": 1} and t.algorithm.eps_clip_low == 0.3 and t.isoexec.reuse_rollout_logprobs
+    assert cfg.generator.n_samples_per_prompt == 2 and cfg.generator.sampling_params.temperature == 0.5
+    j = tmp_path / "run.json"
+    j.write_text(json.dumps({"trainer": {"epochs": 3}}))
+    assert SkyRLTrainConfig.from_file(str(j)).trainer.epochs == 3
+    bad = tmp_path / "bad.yaml"
+    bad.write_text("trainer:\n  no_such_key: 1\n")
+    with pytest.raises(KeyError):
+        SkyRLTrainConfig.from_file(str(bad))
