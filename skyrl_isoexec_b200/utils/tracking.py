@@ -119,8 +119,22 @@ class _MlflowAdapter:
         self.mlflow.end_run()
 
 
+class _SwanlabAdapter:
+    def __init__(self, project, name, config):
+        import swanlab  # raises if swanlab is missing
+
+        self.swanlab = swanlab
+        swanlab.init(project=project, experiment_name=name, config=config)
+
+    def log(self, data, step):
+        self.swanlab.log({k: v for k, v in data.items() if isinstance(v, (int, float))}, step=step)
+
+    def finish(self):
+        self.swanlab.finish()
+
+
 class Tracking:
-    SUPPORTED = ("console", "jsonl", "tensorboard", "wandb", "mlflow")
+    SUPPORTED = ("console", "jsonl", "tensorboard", "wandb", "mlflow", "swanlab")
 
     def __init__(self, project_name: str, experiment_name: str, backends="console", config: dict | None = None,
                  log_dir: str = "runs"):
@@ -141,6 +155,8 @@ class Tracking:
                 self.loggers[b] = _WandbAdapter(project_name, experiment_name, config)
             elif b == "mlflow":
                 self.loggers[b] = _MlflowAdapter(project_name, experiment_name, config)
+            elif b == "swanlab":
+                self.loggers[b] = _SwanlabAdapter(project_name, experiment_name, config)
 
     def log(self, data: dict, step: int, commit: bool = True):
         for lg in self.loggers.values():
