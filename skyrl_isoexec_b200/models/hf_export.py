@@ -4,7 +4,8 @@ Megatron<->HF bridges in B/workers/megatron/model_bridges.py).
 
 Internally QKV and gate/up are fused and QKV rows are stored KV-group major; the export un-fuses them into
 ``q_proj / k_proj / v_proj`` and ``gate_proj / up_proj`` with the usual Qwen3 names, and the import does the reverse.
-Only full (unsharded) models are handled here; sharded runs gather through ``sync.strategies.gather_full`` first.
+Tensor-parallel models are gathered on the way out (``sync.strategies.gather_full``); the import slices full tensors
+to the local shard.
 """
 
 from __future__ import annotations
@@ -38,11 +39,26 @@ def _fuse_qkv(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cfg: ModelConfi
     return torch.cat([q.view(Hkv, G * qs, h), k.view(Hkv, D, h), v.view(Hkv, D, h)], 1).reshape(-1, h)
 
 
-def to_hf_state_dict(model: DecoderLM) -> dict[str, torch.Tensor]:
-    cfg = model.cfg
-    assert model.ps.tp == 1 and model.ps.ep == 1 and model.ps.pp == 1, "gather the shards before exporting"
-    out: dict[str, torch.Tensor] = {}
+def full_named_weights(model: DecoderLM):
+    """(name, full-shape tensor) for every parameter. Under tensor parallelism the sharded ones are all-gathered over the
+    TP group, so EVERY rank of the group has to iterate (in lock step)."""
+    from ..sync.strategies import gather_full
+
+    ps = model.ps
     for name, t in model.named_weights():
+        spec = model.store.specs[name]
+        if ps.tp > 1 and spec.shard_dim is not None:
+            t = gather_full(t.detach(), spec, ps)
+        yield name, t
+
+
+def to_hf_state_dict(model: DecoderLM) -> dict[str, torch.Tensor]:
+    """Un-fused, Hugging Face named tensors of the whole model. Tensor-parallel models are gathered (a collective over the
+    TP group); expert- and pipeline-parallel models are not handled here."""
+    cfg = model.cfg
+    assert model.ps.ep == 1 and model.ps.pp == 1, "expert- / pipeline-parallel shards are not gathered by the exporter"
+    out: dict[str, torch.Tensor] = {}
+    for name, t in full_named_weights(model):
         t = t.detach().cpu().contiguous()
         if name == "embed.weight":
             out["model.embed_tokens.weight"] = t
@@ -92,11 +108,15 @@ def hf_config(cfg: ModelConfig) -> dict:
     return d
 
 
-def save_hf(model: DecoderLM, path: str) -> None:
+def save_hf(model: DecoderLM, path: str, write: bool = True) -> None:
+    """Every rank of a tensor-parallel group calls this (the gather is a collective); ``write=False`` on all but one."""
     from safetensors.torch import save_file
 
+    sd = to_hf_state_dict(model)
+    if not write:
+        return
     os.makedirs(path, exist_ok=True)
-    save_file(to_hf_state_dict(model), os.path.join(path, "model.safetensors"), metadata={"format": "pt"})
+    save_file(sd, os.path.join(path, "model.safetensors"), metadata={"format": "pt"})
     with open(os.path.join(path, "config.json"), "w") as f:
         json.dump(hf_config(model.cfg), f, indent=1)
 
@@ -134,6 +154,11 @@ def load_hf(model: DecoderLM, path: str) -> int:
                            "attn.k_norm.weight": "self_attn.k_norm.weight", "mlp.down.weight": "mlp.down_proj.weight",
                            "moe.router.weight": "mlp.gate.weight"}
                     src = sd[p + ren.get(rest, rest)]
-            t.copy_(src.to(t.dtype).view(t.shape))
+            spec = model.store.specs[name]
+            if tuple(src.shape) != tuple(t.shape) and src.numel() != t.numel():
+                from .decoder import shard_of     # a full tensor for a sharded parameter: cut this rank's part
+
+                src = shard_of(src.view(spec.full_shape), spec, model.ps.tp_rank, model.ps.tp, model.ps.ep_rank, model.ps.ep)
+            t.copy_(src.to(t.dtype).reshape(t.shape))
             n += 1
     return n

@@ -53,11 +53,25 @@ def _worker(rank, port, q):
                 return lp, gsq, model
 
             lp2, g2, m2 = run(ps2)
+            # Hugging Face export from the tensor-parallel model (a collective over the TP group) and import back
+            from skyrl_isoexec_b200.models import hf_export
+
+            hf2 = hf_export.to_hf_state_dict(m2)
             if rank == 0:
                 lp1, g1, m1 = run(ParallelState.single())
-                out[name] = (int((lp1.view(torch.int32) != lp2.view(torch.int32)).sum()), g1, g2)
+                hf1 = hf_export.to_hf_state_dict(m1)
+                same_export = sorted(hf1) == sorted(hf2) and all(torch.equal(hf1[k], hf2[k]) for k in hf1)
+                out[name] = (int((lp1.view(torch.int32) != lp2.view(torch.int32)).sum()), g1, g2, same_export)
             else:
                 out[name] = None
+            import tempfile
+
+            d = tempfile.gettempdir() + f"/hf_tp_{port}_{name}"
+            hf_export.save_hf(m2, d, write=rank == 0)
+            dist.barrier()
+            m3 = DecoderLM(cfg, ps2, seed=99)
+            hf_export.load_hf(m3, d)
+            assert torch.equal(m3.store.flat, m2.store.flat), f"{name}: import into TP shards differs on rank {rank}"
         if rank == 0:
             q.put(out)
     finally:
@@ -76,6 +90,7 @@ def test_tp2_equals_tp1_bitwise_on_cpu():
     out = q.get(timeout=240)
     for p in procs:
         p.join(timeout=60)
-    for name, (mism, g1, g2) in out.items():
+    for name, (mism, g1, g2, same_export) in out.items():
         assert mism == 0, f"{name}: {mism} logprob bits differ between TP=1 and TP=2"
+        assert same_export, f"{name}: the export gathered from TP=2 differs from the TP=1 export"
         assert abs(g1 - g2) <= 2e-3 * max(g1, 1e-12), f"{name}: grad norms {g1} vs {g2}"
