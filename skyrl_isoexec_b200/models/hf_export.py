@@ -14,6 +14,7 @@ import json
 import os
 
 import torch
+import torch.distributed as dist
 
 from .config import ModelConfig
 from .decoder import DecoderLM
@@ -40,8 +41,8 @@ def _fuse_qkv(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cfg: ModelConfi
 
 
 def full_named_weights(model: DecoderLM):
-    """(name, full-shape tensor) for every parameter. Under tensor parallelism the sharded ones are all-gathered over the
-    TP group, so EVERY rank of the group has to iterate (in lock step)."""
+    """(name, full-shape tensor) for every parameter. Under tensor / expert parallelism the sharded ones are all-gathered
+    over the TP / EP group, so EVERY rank of those groups has to iterate (in lock step)."""
     from ..sync.strategies import gather_full
 
     ps = model.ps
@@ -49,14 +50,18 @@ def full_named_weights(model: DecoderLM):
         spec = model.store.specs[name]
         if ps.tp > 1 and spec.shard_dim is not None:
             t = gather_full(t.detach(), spec, ps)
+        if ps.ep > 1 and spec.ep_sharded:                # experts of the other expert-parallel ranks, in rank order
+            parts = [torch.empty_like(t) for _ in range(ps.ep)]
+            dist.all_gather(parts, t.detach().contiguous(), group=ps.ep_group)
+            t = torch.cat(parts, dim=0)
         yield name, t
 
 
 def to_hf_state_dict(model: DecoderLM) -> dict[str, torch.Tensor]:
     """Un-fused, Hugging Face named tensors of the whole model. Tensor-parallel models are gathered (a collective over the
-    TP group); expert- and pipeline-parallel models are not handled here."""
+    TP and EP groups); pipeline-parallel models are not handled here."""
     cfg = model.cfg
-    assert model.ps.ep == 1 and model.ps.pp == 1, "expert- / pipeline-parallel shards are not gathered by the exporter"
+    assert model.ps.pp == 1, "pipeline-parallel stages are not gathered by the exporter"
     out: dict[str, torch.Tensor] = {}
     for name, t in full_named_weights(model):
         t = t.detach().cpu().contiguous()

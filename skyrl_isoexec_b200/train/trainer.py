@@ -528,15 +528,17 @@ class RayPPOTrainer:
 
     def export_hf(self) -> str | None:
         """Write the policy in the Hugging Face layout under ``export_path/global_step_N``. Tensor-parallel shards are
-        gathered (every rank of data-parallel replica 0 takes part, its TP rank 0 writes); expert- and pipeline-parallel
+        and expert-parallel shards are gathered (collectives over those groups), global rank 0 writes; pipeline-parallel
         runs are not exported."""
         from ..models import hf_export
 
-        if self.ps.ep > 1 or self.ps.pp > 1 or self.ps.dp_rank != 0:
+        if self.ps.pp > 1:
+            return None
+        if self.ps.ep == 1 and self.ps.dp_rank != 0:      # plain data-parallel replicas hold copies: one is enough
             return None
         path = os.path.join(self.cfg.trainer.export_path, f"global_step_{self.global_step}")
-        hf_export.save_hf(self.policy.model, path, write=self.ps.tp_rank == 0)
-        return path if self.ps.tp_rank == 0 else None
+        hf_export.save_hf(self.policy.model, path, write=self.rank == 0)
+        return path if self.rank == 0 else None
 
     # ------------------------------------------------------------------ checkpoints
     def save_checkpoints(self) -> str:

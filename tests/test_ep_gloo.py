@@ -42,8 +42,17 @@ def _worker(rank, world, port, q, tmp):
         it = iter(tr.loader)
         m1 = tr.train_step(next(it))
         m2 = tr.train_step(next(it))
+        # Hugging Face export: every rank contributes its experts, the result has all of them and both ranks agree
+        from skyrl_isoexec_b200.models import hf_export
+
+        sd = hf_export.to_hf_state_dict(tr.policy.model)
+        n_exp = len([k for k in sd if k.startswith("model.layers.0.mlp.experts.") and k.endswith("down_proj.weight")])
+        mine = tr.policy.model.p("layers.0.moe.experts.down").detach()
+        per = mine.shape[0]
+        own_ok = all(torch.equal(sd[f"model.layers.0.mlp.experts.{rank * per + e}.down_proj.weight"], mine[e]) for e in range(per))
+        digest = float(sum(v.double().sum() for v in sd.values()))
         q.put((rank, m1["policy/rollout_train_logprob_bit_mismatches"], m2["policy/rollout_train_logprob_bit_mismatches"],
-               m1["policy/grad_norm"], m2["policy/grad_norm"], int(tr.engine.stats["steps"])))
+               m1["policy/grad_norm"], m2["policy/grad_norm"], int(tr.engine.stats["steps"]), n_exp, own_ok, digest))
     finally:
         dist.barrier()
         dist.destroy_process_group()
@@ -66,3 +75,4 @@ def test_grpo_loop_with_expert_parallelism(tmp_path):
     for r in (0, 1):
         assert got[r][0] == 0 and got[r][1] == 0
     assert got[0][2] == got[1][2] > 0 and got[0][3] == got[1][3] > 0          # one global gradient norm, seen by both
+    assert got[0][5] == got[1][5] == 8 and got[0][6] and got[1][6] and got[0][7] == got[1][7]     # export: all 8 experts, same on both
