@@ -150,9 +150,9 @@ def load_hf(model: DecoderLM, path: str) -> int:
                     src = torch.cat([sd[p + "mlp.gate_proj.weight"], sd[p + "mlp.up_proj.weight"]], 0)
                 elif rest == "moe.experts.gate_up":
                     src = torch.stack([torch.cat([sd[p + f"mlp.experts.{e}.gate_proj.weight"], sd[p + f"mlp.experts.{e}.up_proj.weight"]], 0)
-                                       for e in range(t.shape[0])])
+                                       for e in range(cfg.num_experts)])      # all experts; cut to this rank's below
                 elif rest == "moe.experts.down":
-                    src = torch.stack([sd[p + f"mlp.experts.{e}.down_proj.weight"] for e in range(t.shape[0])])
+                    src = torch.stack([sd[p + f"mlp.experts.{e}.down_proj.weight"] for e in range(cfg.num_experts)])
                 else:
                     ren = {"ln1.weight": "input_layernorm.weight", "ln2.weight": "post_attention_layernorm.weight",
                            "attn.o.weight": "self_attn.o_proj.weight", "attn.q_norm.weight": "self_attn.q_norm.weight",

@@ -51,6 +51,13 @@ def _worker(rank, world, port, q, tmp):
         per = mine.shape[0]
         own_ok = all(torch.equal(sd[f"model.layers.0.mlp.experts.{rank * per + e}.down_proj.weight"], mine[e]) for e in range(per))
         digest = float(sum(v.double().sum() for v in sd.values()))
+        # ... and the import cuts the full expert stack back to this rank's experts
+        hf_export.save_hf(tr.policy.model, f"{tmp}/hf", write=rank == 0)
+        dist.barrier()
+        before = tr.policy.model.store.flat.detach().clone()
+        tr.policy.model.store.flat.detach().zero_()
+        hf_export.load_hf(tr.policy.model, f"{tmp}/hf")
+        own_ok = own_ok and bool(torch.equal(tr.policy.model.store.flat.detach(), before))
         q.put((rank, m1["policy/rollout_train_logprob_bit_mismatches"], m2["policy/rollout_train_logprob_bit_mismatches"],
                m1["policy/grad_norm"], m2["policy/grad_norm"], int(tr.engine.stats["steps"]), n_exp, own_ok, digest))
     finally:
