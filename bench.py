@@ -114,7 +114,12 @@ def main():
     assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}"
     torch.cuda.set_device(local)
     _native.lib().ix_init()
-    ps = ParallelState.build(tp=args.tp) if world > 1 else ParallelState.single()
+    if world > 1:
+        from skyrl_isoexec_b200.models.config import get_config as _gc
+
+        ps = ParallelState.build(tp=args.tp, kv_rep=max(1, args.tp // _gc(args.model).num_kv_heads))
+    else:
+        ps = ParallelState.single()
     if world > 1:
         # peer-memory transports: DP gradient sum (csrc/peer_collectives.cu), fused TP GEMMs (csrc/tp_gemm_fused.cu)
         from skyrl_isoexec_b200.models.config import get_config

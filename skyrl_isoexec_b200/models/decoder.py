@@ -41,6 +41,9 @@ class ParamSpec:
     ep_sharded: bool = False     # leading expert dim split over EP
     sections: tuple[int, ...] = ()  # sizes of the blocks on shard_dim that are each split over TP
     tp_grad_sum: bool = False    # replicated weight used by the LOCAL heads only: its gradient is summed over TP
+    kv_rep: int = 1              # fused QKV when tp > num_kv_heads: kv_rep consecutive TP ranks share one KV head (each
+                                 # holds a slice of its query heads plus a full copy of k and v)
+    kv_layout: tuple[int, ...] = ()   # (Hkv, G, rows per query head, D) of the full fused QKV
 
 
 class ParamStore:
@@ -81,9 +84,34 @@ class ParamStore:
             v.copy_(shard_of(full, s, tp_rank, tp, ep_rank, ep).to(v.dtype))
 
 
+def kv_rows(s: ParamSpec) -> tuple[int, int]:
+    """(first row, number of rows) of the replicated k|v block inside a local fused-QKV shard with ``kv_rep > 1``."""
+    Hkv, G, qs, D = s.kv_layout
+    return (G // s.kv_rep) * qs, 2 * D
+
+
+def unshard_kv_rep(parts: list[torch.Tensor], s: ParamSpec) -> torch.Tensor:
+    """Full fused QKV from the shards of all TP ranks (rank order) when KV heads are replicated: per KV group the query
+    slices of its ``kv_rep`` ranks, then k|v taken from the first of them."""
+    Hkv, G, qs, D = s.kv_layout
+    rep = s.kv_rep
+    q_rows = (G // rep) * qs
+    out = []
+    for g in range(Hkv):
+        mine = parts[g * rep:(g + 1) * rep]
+        out += [m[:q_rows] for m in mine] + [mine[0][q_rows:]]
+    return torch.cat(out, dim=0)
+
+
 def shard_of(full: torch.Tensor, s: ParamSpec, tp_rank: int, tp: int, ep_rank: int = 0, ep: int = 1) -> torch.Tensor:
     """Slice a full-shape tensor to the local shard described by ``s``."""
     t = full
+    if s.kv_rep > 1 and tp > 1:
+        Hkv, G, qs, D = s.kv_layout
+        rep = s.kv_rep
+        g, j, gl = tp_rank // rep, tp_rank % rep, G // rep
+        grp = t.reshape(Hkv, G * qs + 2 * D, -1)[g]
+        return torch.cat([grp[j * gl * qs:(j + 1) * gl * qs], grp[G * qs:]], dim=0)
     if s.ep_sharded and ep > 1:
         e = t.shape[0] // ep
         t = t[ep_rank * e:(ep_rank + 1) * e]
@@ -131,7 +159,17 @@ def build_param_specs(cfg: ModelConfig, ps: ParallelState, layer_range: range | 
         add(p + "ln1.weight", (h,), None, 0.0 if cfg.zero_centered_norm else None)
         if cfg.layer_type(i) == "attn":
             # stored head-major per KV group so a TP shard holds whole GQA groups: [q-block | k | v] per shard
-            add(p + "attn.qkv.weight", (_qkv_rows(cfg), h), 0, std)
+            if tp > cfg.num_kv_heads:
+                # more TP ranks than KV heads: tp / Hkv consecutive ranks share a KV head; each keeps a slice of the
+                # group's query heads and a full copy of its k and v rows (their gradients are summed over those ranks)
+                Hkv, D = cfg.num_kv_heads, cfg.head_dim
+                G, qs = cfg.num_q_heads // Hkv, (2 * D if cfg.attn_output_gate else D)
+                assert tp % Hkv == 0 and G % (tp // Hkv) == 0, f"tp={tp} cannot replicate {Hkv} KV heads of {G}-head groups"
+                rep = tp // Hkv
+                specs.append(ParamSpec(p + "attn.qkv.weight", ((G // rep) * qs + 2 * D, h), (_qkv_rows(cfg), h), 0, std,
+                                       kv_rep=rep, kv_layout=(Hkv, G, qs, D)))
+            else:
+                add(p + "attn.qkv.weight", (_qkv_rows(cfg), h), 0, std)
             add(p + "attn.o.weight", (h, cfg.num_q_heads * cfg.head_dim), 1, out_std)
             if cfg.qk_norm:
                 add(p + "attn.q_norm.weight", (cfg.head_dim,), None, 0.0 if cfg.zero_centered_norm else None)
@@ -203,8 +241,12 @@ class DecoderLM(nn.Module):
         self.rope = F.RopeTable(cfg.rot_dim, cfg.max_position, cfg.rope_theta, self.device_)
         self.scale = F.softmax_scale(cfg.head_dim)
         tp = self.ps.tp
-        assert cfg.num_kv_heads % tp == 0 or tp == 1, "TP must divide the KV heads"
-        self.hq, self.hkv = cfg.num_q_heads // tp, cfg.num_kv_heads // tp
+        assert cfg.num_kv_heads % tp == 0 or tp % cfg.num_kv_heads == 0, "TP must divide, or be a multiple of, the KV heads"
+        self.hq, self.hkv = cfg.num_q_heads // tp, max(1, cfg.num_kv_heads // tp)
+        self.kv_rep = max(1, tp // cfg.num_kv_heads)
+        if self.kv_rep > 1 and any(t == "attn" for t in (cfg.layer_type(i) for i in self.layer_ids)):
+            assert getattr(self.ps, "kvr_ranks", None) and len(self.ps.kvr_ranks) == self.kv_rep, \
+                f"KV heads are replicated over {self.kv_rep} ranks: build the process groups with kv_rep={self.kv_rep}"
 
     # -------------------------------------------------------------------------------- helpers
     def p(self, name: str) -> torch.Tensor:

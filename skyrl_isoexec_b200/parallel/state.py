@@ -32,6 +32,9 @@ class ParallelState:
     dp_group: object = None
     ep_group: object = None
     edp_group: object = None      # ranks that hold the SAME expert shard (expert data parallel)
+    kvr_group: object = None      # consecutive TP ranks that share one (replicated) KV head, when tp > num_kv_heads
+    kvr_ranks: list = field(default_factory=lambda: [0])
+    kvr_rank: int = 0
     cp_group: object = None
     tp_ranks: list = field(default_factory=lambda: [0])
     dp_ranks: list = field(default_factory=lambda: [0])
@@ -54,7 +57,7 @@ class ParallelState:
         return self.pp_rank == self.pp - 1
 
     @staticmethod
-    def build(tp: int = 1, pp: int = 1, ep: int = 1, cp: int = 1, ranks: list[int] | None = None) -> "ParallelState":
+    def build(tp: int = 1, pp: int = 1, ep: int = 1, cp: int = 1, ranks: list[int] | None = None, kv_rep: int = 1) -> "ParallelState":
         """Create the groups for a job (or for the sub-job made of ``ranks``). Every process of the
         default group must call this with the same arguments (``new_group`` is collective)."""
         if not dist.is_initialized():
@@ -87,6 +90,11 @@ class ParallelState:
            "pp_group", "pp_ranks", "pp_rank")
         mk([[idx(p, d, c, t) for c in range(cp)] for p in range(pp) for d in range(dp) for t in range(tp)],
            "cp_group", "cp_ranks", "cp_rank")
+        if kv_rep > 1:
+            # tp > num_kv_heads: kv_rep consecutive TP ranks hold copies of one KV head (models/decoder.py)
+            assert tp % kv_rep == 0, (tp, kv_rep)
+            mk([[idx(p, d, c, t0 + t) for t in range(kv_rep)] for p in range(pp) for d in range(dp) for c in range(cp)
+                for t0 in range(0, tp, kv_rep)], "kvr_group", "kvr_ranks", "kvr_rank")
         if ep > 1:
             # expert parallel spans (dp x tp) ranks of one pipeline stage, ep consecutive ranks per group
             stage = lambda p: [idx(p, d, c, t) for d in range(dp) for c in range(cp) for t in range(tp)]

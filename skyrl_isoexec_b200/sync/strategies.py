@@ -127,6 +127,10 @@ def gather_full(t: torch.Tensor, spec, ps) -> torch.Tensor:
     """All-gather a TP-sharded tensor to its full shape, undoing the per-section split."""
     parts = [torch.empty_like(t) for _ in range(ps.tp)]
     dist.all_gather(parts, t.contiguous(), group=ps.tp_group)
+    if getattr(spec, "kv_rep", 1) > 1:
+        from ..models.decoder import unshard_kv_rep
+
+        return unshard_kv_rep(parts, spec)
     if not spec.sections:
         return torch.cat(parts, dim=spec.shard_dim)
     secs = [s // ps.tp for s in spec.sections]

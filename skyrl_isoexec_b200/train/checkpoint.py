@@ -67,7 +67,8 @@ def save_checkpoint(ckpt_path: str, step: int, policy, data_state: dict, trainer
             "format": "skyrl_isoexec_b200.sharded.v1", "global_step": step, "world_size": dist.get_world_size() if dist.is_initialized() else 1,
             "tp": ps.tp, "pp": ps.pp, "dp": ps.dp, "ep": ps.ep, "model_config": model.cfg.to_dict(),
             "params": {n: {"full_shape": list(s.full_shape), "shard_dim": s.shard_dim, "sections": list(s.sections),
-                           "ep_sharded": s.ep_sharded, "offset": s.offset, "shape": list(s.shape)}
+                           "ep_sharded": s.ep_sharded, "offset": s.offset, "shape": list(s.shape),
+                           "kv_rep": s.kv_rep, "kv_layout": list(s.kv_layout)}
                        for n, s in model.store.specs.items()},
         }
         with open(os.path.join(tmp, "policy", "metadata.json"), "w") as f:
@@ -138,6 +139,12 @@ def _assemble_full(name: str, meta: dict, shards: list[dict]) -> torch.Tensor:
     parts = [s["model"][name] for s in shards]
     if info["shard_dim"] is None or len(parts) == 1:
         return parts[0]
+    if info.get("kv_rep", 1) > 1:
+        from types import SimpleNamespace
+
+        from ..models.decoder import unshard_kv_rep
+
+        return unshard_kv_rep(parts, SimpleNamespace(kv_rep=info["kv_rep"], kv_layout=tuple(info["kv_layout"])))
     d, tp = info["shard_dim"], len(parts)
     secs = info["sections"] or [info["full_shape"][d]]
     cols = []

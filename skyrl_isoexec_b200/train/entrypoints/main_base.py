@@ -25,8 +25,15 @@ class BasePPOExp:
         self.rank, self.world, self.local_rank = init_distributed()
         validate_cfg(cfg, self.world)
         p = cfg.trainer.policy.parallel
+        kv_rep = 1
+        if self.world > 1 and p.tensor_model_parallel_size > 1:
+            from ...models.config import get_config
+
+            # more tensor-parallel ranks than KV heads: consecutive ranks share (replicate) a KV head
+            m = get_config(cfg.trainer.policy.model, **cfg.trainer.policy.model_overrides)
+            kv_rep = max(1, p.tensor_model_parallel_size // m.num_kv_heads)
         self.ps = ParallelState.build(tp=p.tensor_model_parallel_size, pp=p.pipeline_model_parallel_size,
-                                      ep=p.expert_model_parallel_size, cp=p.context_parallel_size) if self.world > 1 \
+                                      ep=p.expert_model_parallel_size, cp=p.context_parallel_size, kv_rep=kv_rep) if self.world > 1 \
             else ParallelState.single()
         self.device = f"cuda:{self.local_rank}" if torch.cuda.is_available() else "cpu"
         if torch.cuda.is_available():

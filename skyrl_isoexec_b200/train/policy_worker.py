@@ -328,6 +328,16 @@ class FlatAdamW:
                     g = self.main_grad[s.offset:s.offset + math.prod(s.shape)]
                     rep += g.square().sum()
             local = self._sq - (rep if ps.tp_rank != 0 else 0)
+            if getattr(ps, "kvr_rank", 0) != 0:
+                # copies of a replicated KV head: counted once, on the first rank of the sharing group
+                from ..models.decoder import kv_rows
+
+                for name in self.model.store.order:
+                    s = self.model.store.specs[name]
+                    if s.kv_rep > 1:
+                        r0, nr = kv_rows(s)
+                        lo = s.offset + r0 * s.shape[1]
+                        local = local - self.main_grad[lo:lo + nr * s.shape[1]].square().sum()
             dist.all_reduce(local, group=ps.tp_group)
             self._sq = local
         if ps.ep > 1 and self.model.cfg.has_moe:
@@ -614,6 +624,14 @@ class PolicyWorker:
             self.opt.setup_overlap(ps)
         return True
 
+    @staticmethod
+    def _kv_range(s) -> tuple[int, int]:
+        """(first element, count) of the replicated k|v rows of a fused-QKV shard inside the flat buffer."""
+        from ..models.decoder import kv_rows
+
+        r0, nr = kv_rows(s)
+        return s.offset + r0 * s.shape[1], nr * s.shape[1]
+
     def reduce_gradients(self) -> None:
         """Sum the main gradients over the data-parallel group (fixed bucket order); before that,
         weights that are replicated over TP but only see the local heads get their gradient summed over TP."""
@@ -625,6 +643,10 @@ class PolicyWorker:
                 s = store.specs[name]
                 if s.tp_grad_sum:
                     dist.all_reduce(self.opt.main_grad[s.offset:s.offset + math.prod(s.shape)], group=self.ps.tp_group)
+                if s.kv_rep > 1:
+                    # the ranks that share a KV head each saw the gradient from their own query heads only
+                    lo, n = self._kv_range(s)
+                    dist.all_reduce(self.opt.main_grad[lo:lo + n], group=self.ps.kvr_group)
         if self.ps.dp > 1:
             from ..parallel.dp import reduce_main_grads, split_ranges_by_expert_sharding
 
