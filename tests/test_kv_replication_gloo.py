@@ -19,7 +19,7 @@ def _free_port():
     return p
 
 
-def _worker(rank, port, q, tmp):
+def _worker(rank, port, q, tmp, gate):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE="4")
     torch.set_num_threads(2)
     dist.init_process_group("gloo", rank=rank, world_size=4)
@@ -32,7 +32,7 @@ def _worker(rank, port, q, tmp):
         from skyrl_isoexec_b200.train.batch import TrainingInputBatch, build_sequences
         from skyrl_isoexec_b200.train.policy_worker import OptimizerConfig, PolicyWorker, WorkerConfig
 
-        cfg = get_config("tiny-qwen3", tp_invariant=True)             # 4 query heads, 2 KV heads
+        cfg = get_config("tiny-qwen3", tp_invariant=True, attn_output_gate=gate)      # 4 query heads, 2 KV heads
         ps4 = ParallelState.build(tp=4, kv_rep=2)
         assert ps4.kvr_ranks == [2 * (rank // 2), 2 * (rank // 2) + 1] and ps4.kvr_rank == rank % 2
         g = torch.Generator().manual_seed(1)
@@ -85,11 +85,12 @@ def _worker(rank, port, q, tmp):
 
 
 @pytest.mark.timeout(600)
-def test_tp4_with_two_kv_heads_equals_tp1(tmp_path):
+@pytest.mark.parametrize("gate", [False, True])          # plain query heads, and [q | output gate] blocks per head
+def test_tp4_with_two_kv_heads_equals_tp1(tmp_path, gate):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, port, q, str(tmp_path))) for r in range(4)]
+    procs = [ctx.Process(target=_worker, args=(r, port, q, str(tmp_path), gate)) for r in range(4)]
     for p in procs:
         p.start()
     got = [q.get(timeout=400) for _ in range(4)]
