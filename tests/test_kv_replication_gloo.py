@@ -64,6 +64,20 @@ def _worker(rank, port, q, tmp, gate):
         both = [torch.empty_like(mine) for _ in range(2)]
         dist.all_gather(both, mine, group=ps4.kvr_group)
         kv_same = bool(torch.equal(both[0], both[1]))
+        # the rollout engine on the same tensor-parallel model: one KV head per rank in its paged cache, and the sampled
+        # tokens' logprobs equal a trainer forward bit for bit
+        from skyrl_isoexec_b200.core.testing import count_bit_mismatches
+        from skyrl_isoexec_b200.engine.llm_engine import EngineConfig, LLMEngine
+        from skyrl_isoexec_b200.engine.sampler import SamplingParams
+
+        eng = LLMEngine(m4, EngineConfig(max_num_seqs=4, num_kv_pages=16, max_num_batched_tokens=128, seed=9))
+        outs = eng.generate(prompts, SamplingParams(max_generate_length=6, ignore_eos=True))
+        seq_e, att_e, rm_e = build_sequences([o.prompt_ids for o in outs], [o.response_ids for o in outs])
+        lp_e = w4.forward(TrainingInputBatch({"sequences": seq_e, "attention_mask": att_e, "response_mask": rm_e}))
+        ro = torch.zeros_like(lp_e)
+        for i, o in enumerate(outs):
+            ro[i, :len(o.response_logprobs)] = torch.tensor(o.response_logprobs)
+        engine_mism = count_bit_mismatches((lp_e * rm_e).contiguous(), (ro * rm_e).contiguous())
         hf4 = hf_export.to_hf_state_dict(m4)                          # gathers (collective over the TP group)
         ckpt.save_checkpoint(tmp, 1, w4, {}, {"global_step": 1}, ps4)
         res = None
@@ -78,7 +92,7 @@ def _worker(rank, port, q, tmp, gate):
             resharded = bool(torch.equal(hf_export.to_hf_state_dict(m_r)["model.layers.0.self_attn.k_proj.weight"],
                                          hf4["model.layers.0.self_attn.k_proj.weight"]))
             res = (int((lp1.view(torch.int32) != lp4.view(torch.int32)).sum()), g1, g4, worst, sorted(hf1) == sorted(hf4), resharded)
-        q.put((rank, kv_same, res))
+        q.put((rank, kv_same and engine_mism == 0, res))
     finally:
         dist.barrier()
         dist.destroy_process_group()
