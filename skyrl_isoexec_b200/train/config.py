@@ -296,6 +296,18 @@ def validate_cfg(cfg: SkyRLTrainConfig, world_size: int = 1) -> None:
         raise ValueError(f"unknown policy_loss_type {t.algorithm.policy_loss_type!r}")
     if t.algorithm.advantage_estimator not in __import__("skyrl_isoexec_b200.train.algorithms", fromlist=["x"]).ADVANTAGE_ESTIMATORS:
         raise ValueError(f"unknown advantage_estimator {t.algorithm.advantage_estimator!r}")
+    tp = p.tensor_model_parallel_size
+    if tp > 1:
+        from ..models.config import PRESETS, get_config
+
+        if t.policy.model in PRESETS:
+            m = get_config(t.policy.model, **t.policy.model_overrides)
+            hkv, hq = m.num_kv_heads, m.num_q_heads
+            if hq % tp:
+                raise ValueError(f"tensor parallel size {tp} does not divide the {hq} query heads of {t.policy.model}")
+            if hkv % tp and (tp % hkv or (hq // hkv) % (tp // hkv)):
+                raise ValueError(f"tensor parallel size {tp} must divide the {hkv} KV heads, or be a multiple of them that "
+                                 f"also divides each group of {hq // hkv} query heads (KV heads are then replicated)")
     if t.resume_mode not in ("none", "latest", "from_path"):
         raise ValueError(f"resume_mode {t.resume_mode!r} must be none|latest|from_path")
     if t.isoexec.enabled:
