@@ -26,7 +26,7 @@ from http.server import BaseHTTPRequestHandler, ThreadingHTTPServer
 from .backend import LOSS_FNS, SkyRLTrainBackend
 
 _ROUTES = {"forward_backward": "forward_backward", "forward": "forward", "optim_step": "optim_step", "asample": "sample",
-           "save_weights": "save_weights", "load_weights": "load_weights"}
+           "save_weights": "save_weights", "load_weights": "load_weights", "save_weights_for_sampler": "save_weights_for_sampler"}
 
 
 class TinkerServer:
@@ -35,6 +35,8 @@ class TinkerServer:
         self.db.execute("create table if not exists futures (id text primary key, seq integer, model_id text, payload text, "
                         "status text, result text, created real)")
         self.db.execute("create table if not exists models (id text primary key, spec text)")
+        self.db.execute("create table if not exists sessions (id text primary key, kind text, model_id text, meta text, "
+                        "created real, heartbeat real)")
         self._dblock = threading.Lock()
         self.device = device
         self.models: dict[str, SkyRLTrainBackend] = {}
@@ -93,6 +95,55 @@ class TinkerServer:
     # ------------------------------------------------------------------ front end
     def post(self, path: str, body: dict) -> dict:
         verb = path.rsplit("/", 1)[-1]
+        # ---- sessions: bookkeeping only (who is connected, which sampler weights a sampling session reads)
+        if verb in ("create_session", "create_sampling_session"):
+            if verb == "create_sampling_session" and body.get("model_id") not in self.models:
+                raise KeyError(f"model_id {body.get('model_id')!r}")
+            sid = ("sess-" if verb == "create_session" else "samp-") + uuid.uuid4().hex[:10]
+            now = time.time()
+            with self._dblock:
+                self.db.execute("insert into sessions values (?, ?, ?, ?, ?, ?)",
+                                (sid, verb[len("create_"):], body.get("model_id"), json.dumps({k: v for k, v in body.items() if k != "model_id"}), now, now))
+                self.db.commit()
+            return {"session_id": sid}
+        if verb == "session_heartbeat":
+            with self._dblock:
+                cur = self.db.execute("update sessions set heartbeat = ? where id = ?", (time.time(), body["session_id"]))
+                self.db.commit()
+            if cur.rowcount == 0:
+                raise KeyError(body["session_id"])
+            return {"ok": True}
+        if verb == "get_info":
+            if body.get("model_id") not in self.models:
+                raise KeyError(f"model_id {body.get('model_id')!r}")
+            with self._dblock:
+                spec = json.loads(self.db.execute("select spec from models where id = ?", (body["model_id"],)).fetchone()[0])
+                pending = self.db.execute("select count(*) from futures where model_id = ? and status = 'pending'", (body["model_id"],)).fetchone()[0]
+            b = self.models[body["model_id"]]
+            return {"model_id": body["model_id"], "spec": spec, "step": b.step_count, "pending_requests": pending,
+                    "num_parameters": int(b.model.store.flat.numel()), "sampler_version": getattr(b, "sampler_version", 0)}
+        if verb == "unload_model":
+            if body.get("model_id") not in self.models:
+                raise KeyError(f"model_id {body.get('model_id')!r}")
+            with self._dblock:
+                busy = self.db.execute("select count(*) from futures where model_id = ? and status = 'pending'", (body["model_id"],)).fetchone()[0]
+            if busy:
+                raise RuntimeError(f"{busy} requests of {body['model_id']} are still pending")
+            del self.models[body["model_id"]]
+            with self._dblock:
+                self.db.execute("delete from models where id = ?", (body["model_id"],))
+                self.db.commit()
+            return {"unloaded": body["model_id"]}
+        if verb == "training_runs":
+            with self._dblock:
+                rows = self.db.execute("select id, spec from models").fetchall()
+            return {"training_runs": [{"model_id": i, "spec": json.loads(sp), "step": self.models[i].step_count} for i, sp in rows if i in self.models]}
+        if verb == "weights_info":
+            import torch
+
+            sd = torch.load(body["path"], weights_only=False, map_location="cpu")
+            return {"path": body["path"], "step": int(sd.get("step", 0)), "num_tensors": len(sd["model"]),
+                    "num_parameters": int(sum(v.numel() for v in sd["model"].values())), "has_optimizer": sd.get("optimizer") is not None}
         if verb == "create_model":
             mid = "model-" + uuid.uuid4().hex[:10]
             spec = {"base_model": body.get("base_model", "tiny-qwen3"), "model_overrides": body.get("model_overrides") or {},

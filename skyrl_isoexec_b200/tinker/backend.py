@@ -84,6 +84,17 @@ class SkyRLTrainBackend:
                 self.engine.wake_up()
             outs = self.engine.generate([list(req["prompt_ids"])] * n, sp)
             return {"sequences": [{"tokens": o.response_ids, "logprobs": o.response_logprobs, "stop_reason": o.stop_reason} for o in outs]}
+        if kind == "save_weights_for_sampler":
+            # the sampler IS this backend's engine and reads the trainer's parameter buffer: publishing new weights is a
+            # version bump plus dropping what the engine cached under the old ones (optionally also a file for others)
+            self.sampler_version = getattr(self, "sampler_version", 0) + 1
+            self.engine.reset_prefix_cache()
+            out = {"sampler_version": self.sampler_version, "step": self.step_count}
+            if req.get("path"):
+                os.makedirs(os.path.dirname(req["path"]) or ".", exist_ok=True)
+                torch.save({"model": {k: v.detach().cpu() for k, v in self.model.named_weights()}, "step": self.step_count}, req["path"])
+                out["path"] = req["path"]
+            return out
         if kind == "save_weights":
             os.makedirs(os.path.dirname(req["path"]) or ".", exist_ok=True)
             torch.save({"model": {k: v.detach().cpu() for k, v in self.model.named_weights()}, "step": self.step_count,

@@ -37,9 +37,26 @@ def test_tinker_training_loop_over_http(tmp_path):
         cl.call("save_weights", model_id=mid, path=path)
         cl.call("optim_step", model_id=mid, adam_params={})
         assert cl.call("load_weights", model_id=mid, path=path)["step"] == 4
+        # sessions, sampler publication, introspection
+        sess = cl._post("create_session", {"user": "t"})["session_id"]
+        assert cl._post("session_heartbeat", {"session_id": sess})["ok"]
+        samp = cl._post("create_sampling_session", {"model_id": mid, "base": "latest"})["session_id"]
+        assert sess.startswith("sess-") and samp.startswith("samp-")
+        pub = cl.call("save_weights_for_sampler", model_id=mid, path=str(tmp_path / "w" / "sampler.pt"))
+        assert pub["sampler_version"] == 1 and pub["step"] == 4
+        info = cl._post("get_info", {"model_id": mid})
+        assert info["step"] == 4 and info["sampler_version"] == 1 and info["pending_requests"] == 0 and info["num_parameters"] > 0
+        wi = cl._post("weights_info", {"path": path})
+        assert wi["step"] == 4 and wi["has_optimizer"] and wi["num_parameters"] > 0
+        assert not cl._post("weights_info", {"path": pub["path"]})["has_optimizer"]
+        assert [r["model_id"] for r in cl._post("training_runs", {})["training_runs"]] == [mid]
         with pytest.raises(RuntimeError, match="loss_fn"):
             cl.call("forward_backward", model_id=mid, data=rl, loss_fn="nope")
         with pytest.raises(RuntimeError, match="404"):
             cl.submit("optim_step", model_id="model-missing")
+        assert cl._post("unload_model", {"model_id": mid})["unloaded"] == mid
+        assert cl._post("training_runs", {})["training_runs"] == []
+        with pytest.raises(RuntimeError, match="404"):
+            cl._post("get_info", {"model_id": mid})
     finally:
         srv.shutdown()
