@@ -666,3 +666,48 @@ generator:
     bad.write_text("trainer:\n  no_such_key: 1\n")
     with pytest.raises(KeyError):
         SkyRLTrainConfig.from_file(str(bad))
+
+
+def test_worker_dispatch_verbs_staging_lcm_and_residency(tmp_path):
+    from types import SimpleNamespace
+
+    from skyrl_isoexec_b200.models.config import get_config
+    from skyrl_isoexec_b200.models.decoder import DecoderLM
+    from skyrl_isoexec_b200.parallel.state import ParallelState
+    from skyrl_isoexec_b200.train.batch import TrainingInputBatch, build_sequences
+    from skyrl_isoexec_b200.train.policy_worker import PolicyWorker, WorkerConfig
+    from skyrl_isoexec_b200.train.worker_dispatch import WorkerDispatch
+
+    ps = ParallelState.single()
+    policy = PolicyWorker(DecoderLM(get_config("tiny-qwen3"), ps, seed=1), WorkerConfig(max_tokens_per_microbatch=64))
+    critic = PolicyWorker(DecoderLM(get_config("tiny-qwen3"), ps, seed=2), WorkerConfig(max_tokens_per_microbatch=64))
+    ref = SimpleNamespace(ps=SimpleNamespace(dp=3), opt=None, forward=lambda b: "ref-forward")
+    synced = []
+    d = WorkerDispatch({"policy": policy, "critic": critic, "ref": ref, "absent": None}, sync_fn=lambda: synced.append(1))
+    assert sorted(d.workers) == ["critic", "policy", "ref"] and d.get_lcm_dp_size() == 3
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, 2048, (6,), generator=g).tolist() for _ in range(4)]
+    resp = [torch.randint(0, 2048, (5,), generator=g).tolist() for _ in range(4)]
+    seq, att, rmask = build_sequences(prompts, resp)
+    batch = TrainingInputBatch({"sequences": seq, "attention_mask": att, "response_mask": rmask, "loss_mask": rmask.clone(),
+                                "advantages": torch.ones(rmask.shape)})
+    assert d.pad_batch(batch).batch_size == 6                           # 4 rows -> next multiple of 3
+    assert d.forward("ref", batch) == "ref-forward"
+    key = d.stage_data(batch)
+    m1 = d.forward_backward_from_staged("policy", key, 0, 2)
+    m2 = d.forward_backward_from_staged("policy", key, 2, 4)
+    assert m1["loss_tokens"] == m2["loss_tokens"] == 10 and d.optim_step("policy") > 0
+    assert d.residency == {"policy": "gpu", "critic": "cpu", "ref": "gpu"}     # the critic's state was parked, the ref has none
+    d.forward_backward("critic", batch)
+    assert d.residency["policy"] == "cpu" and d.residency["critic"] == "gpu"
+    assert d.transitions == [("critic", "cpu"), ("policy", "cpu"), ("critic", "gpu")]
+    d.offload_all()
+    assert d.residency["critic"] == "cpu"
+    d.drop_staged(key)
+    with pytest.raises(KeyError):
+        d.forward_backward_from_staged("policy", key, 0, 1)
+    d.save_weights_for_sampler()
+    assert synced == [1]
+    path = d.save_checkpoint(str(tmp_path), 1, {"pos": 1}, {"global_step": 1})
+    ds, ts = d.load_checkpoint(path)
+    assert ds["pos"] == 1 and ts["global_step"] == 1 and d.residency["policy"] == "gpu"
