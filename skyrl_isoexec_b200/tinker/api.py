@@ -228,3 +228,26 @@ class TinkerClient:
 
     def call(self, verb: str, **body) -> dict:
         return self.result(self.submit(verb, **body))
+
+
+def main(argv=None) -> None:
+    """``python -m skyrl_isoexec_b200.tinker.api [--host 127.0.0.1] [--port 8000] [--db tinker.db] [--device cuda]``"""
+    import argparse
+
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--host", default="127.0.0.1")
+    ap.add_argument("--port", type=int, default=8000)
+    ap.add_argument("--db", default=":memory:")
+    ap.add_argument("--device", default=None)
+    a = ap.parse_args(argv)
+    srv = TinkerServer(db_path=a.db, host=a.host, port=a.port, device=a.device).start()
+    print(f"tinker API at {srv.url}/api/v1", flush=True)
+    try:
+        while True:
+            time.sleep(3600)
+    except KeyboardInterrupt:
+        srv.shutdown()
+
+
+if __name__ == "__main__":
+    main()

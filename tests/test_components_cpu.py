@@ -711,3 +711,33 @@ def test_worker_dispatch_verbs_staging_lcm_and_residency(tmp_path):
     path = d.save_checkpoint(str(tmp_path), 1, {"pos": 1}, {"global_step": 1})
     ds, ts = d.load_checkpoint(path)
     assert ds["pos"] == 1 and ts["global_step"] == 1 and d.residency["policy"] == "gpu"
+
+
+def test_generate_sft_and_serve_entry_points(tmp_path):
+    import urllib.request
+
+    from skyrl_isoexec_b200.train.entrypoints import main_generate, main_sft, serve
+
+    ov = ["trainer.policy.model=tiny-qwen3", "trainer.train_batch_size=2", "trainer.policy_mini_batch_size=2",
+          "generator.n_samples_per_prompt=2", "generator.eval_n_samples_per_prompt=2", "generator.eval_sampling_params.max_generate_length=4",
+          "generator.eval_sampling_params.ignore_eos=true", "data.synthetic_prompt_len=8", "data.synthetic_prompts=8",
+          "trainer.max_prompt_length=8", "generator.inference_engine.num_kv_pages=16", "trainer.eval_batch_size=3",
+          f"trainer.ckpt_path={tmp_path}/ck", "trainer.resume_mode=none", "trainer.logger=jsonl", f"trainer.export_path={tmp_path}/out"]
+    out = main_generate.run(SkyRLTrainConfig.from_cli_overrides(ov))
+    assert any(k.startswith("eval/") for k in out) and json.load(open(tmp_path / "out" / "eval.json")) == out
+    data = tmp_path / "sft.jsonl"
+    g = torch.Generator().manual_seed(0)
+    with open(data, "w") as f:
+        for _ in range(6):
+            f.write(json.dumps({"prompt_ids": torch.randint(0, 500, (5,), generator=g).tolist(),
+                                "response_ids": torch.randint(0, 500, (7,), generator=g).tolist()}) + "\n")
+    tr = main_sft.main(["--data", str(data), "--batch-size", "3", "--num-steps", "2", "--lr", "1e-3", "--logger", "jsonl"])
+    assert tr.global_step == 2
+    srv = serve.build(["--model", "tiny-qwen3", "--num-kv-pages", "16", "--device", "cpu"]).start()
+    try:
+        with urllib.request.urlopen(srv.url + "/health", timeout=10) as r:
+            assert json.loads(r.read())["status"] == "ok"
+        with urllib.request.urlopen(srv.url + "/metrics", timeout=10) as r:
+            assert b"isoexec_requests_served_total" in r.read()
+    finally:
+        srv.shutdown()
