@@ -741,3 +741,19 @@ def test_generate_sft_and_serve_entry_points(tmp_path):
             assert b"isoexec_requests_served_total" in r.read()
     finally:
         srv.shutdown()
+
+
+def test_example_configs_load_and_validate():
+    import glob
+    import os
+
+    from skyrl_isoexec_b200.train.config import validate_cfg
+
+    root = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "examples")
+    files = sorted(glob.glob(os.path.join(root, "*.yaml")))
+    assert len(files) >= 3
+    for f in files:
+        cfg = SkyRLTrainConfig.from_file(f)
+        validate_cfg(cfg, 8 if "8gpu" in f else 1)
+    big = SkyRLTrainConfig.from_file(os.path.join(root, "qwen3_8b_grpo_8gpu.yaml"))
+    assert big.trainer.policy.model == "qwen3-8b" and big.trainer.policy.keep_last_layers == -1 and big.generator.n_samples_per_prompt == 8
