@@ -12,9 +12,9 @@ from skyrl_isoexec_b200.models.config import get_config
 from skyrl_isoexec_b200.models.decoder import DecoderLM
 
 
-def _engine(seed=0):
-    cfg = get_config("tiny-qwen3")
-    return LLMEngine(DecoderLM(cfg, seed=seed), EngineConfig(max_num_seqs=16, num_kv_pages=32, seed=3))
+def _engine(seed=0, max_position=512, pages=32):
+    cfg = get_config("tiny-qwen3", max_position=max_position)
+    return LLMEngine(DecoderLM(cfg, seed=seed), EngineConfig(max_num_seqs=16, num_kv_pages=pages, seed=3))
 
 
 def test_server_data_and_control_plane(tmp_path):
@@ -63,7 +63,8 @@ def test_server_data_and_control_plane(tmp_path):
 
 
 def test_pause_abort_ends_running_requests_and_keep_resumes():
-    srv = InferenceServer(_engine()).start()
+    # a context long enough that the request cannot run into the length limit before the test aborts it
+    srv = InferenceServer(_engine(max_position=16384, pages=160)).start()
     try:
         cl = RemoteInferenceClient([srv.url], timeout_s=60)
         res = {}
