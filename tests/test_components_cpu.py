@@ -621,7 +621,9 @@ def test_gpu_monitor_parses_and_summarises_with_a_fake_query():
                   "1750, 1965, 990.0, 97, 1500, Not Active, Active, Not Active, Active"] + ["bad"] * 1000)
     mon = GpuMonitor(0, period_s=0.01, runner=lambda: next(lines))
     mon.start()
-    time.sleep(0.3)
+    t0 = time.time()
+    while len(mon.rows) < 3 and time.time() - t0 < 10:
+        time.sleep(0.02)
     s = mon.stop()
     assert s["samples"] == 3 and s["sm_mhz"] == 1750 and s["sm_max_mhz"] == 1965 and s["mem_mib"] == 2000
     assert s["reasons"] == ["hw_thermal_slowdown", "sw_power_cap"]

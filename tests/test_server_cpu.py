@@ -74,7 +74,9 @@ def test_pause_abort_ends_running_requests_and_keep_resumes():
 
         t = threading.Thread(target=long_call)
         t.start()
-        time.sleep(0.3)
+        t0 = time.time()
+        while time.time() - t0 < 20 and not (srv._pending and srv._pending[0].seqs and len(srv._pending[0].seqs[0].output_ids) > 2):
+            time.sleep(0.02)                      # wait until the request is really decoding, however slow the machine
         asyncio.run(cl.pause_generation("keep"))
         n1 = len(srv._pending[0].seqs[0].output_ids)
         time.sleep(0.1)
