@@ -87,6 +87,8 @@ class NativeInferenceEngine(InferenceEngineInterface):
     def __init__(self, llm: LLMEngine, tokenizer=None):
         self.llm = llm
         self.tokenizer = tokenizer
+        if tokenizer is not None and llm.detokenize is None:
+            llm.detokenize = tokenizer.decode          # stop strings are matched on decoded text
         self.receiver = None
 
     async def generate(self, input_batch: InferenceEngineInput) -> InferenceEngineOutput:

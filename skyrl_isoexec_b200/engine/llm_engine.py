@@ -166,6 +166,7 @@ class LLMEngine:
         self.scheduler = Scheduler(self.cfg, self.cache)
         self.sampler = Sampler(self.device, self.cfg.seed, self.mcfg.logprob_leaves)
         self._next_id = 0
+        self.detokenize = None          # ids -> text, set by whoever owns a tokenizer; needed only for stop STRINGS
         self.paused = False
         self.asleep = False
         self.stats = {"steps": 0, "tokens": 0, "prefill_tokens": 0, "decode_tokens": 0, "preemptions": 0,
@@ -340,7 +341,8 @@ class LLMEngine:
         for s, tok, lp in zip(sample_seqs, tokens, lps):
             s.output_ids.append(tok)
             s.logprobs.append(lp)
-            if (not s.params.ignore_eos and eos is not None and tok == eos) or tok in s.params.stop_token_ids:
+            if (not s.params.ignore_eos and eos is not None and tok == eos) or tok in s.params.stop_token_ids \
+                    or self._hit_stop_string(s):
                 s.finished, s.stop_reason = True, "stop"
             elif len(s.output_ids) >= s.params.max_generate_length or s.length >= self.max_len:
                 s.finished, s.stop_reason = True, "length"
@@ -416,6 +418,16 @@ class LLMEngine:
     def _launch_ahead(self, prev: dict) -> dict:
         return self._launch_decode(prev["seqs"], ahead=True)
 
+    def _hit_stop_string(self, s) -> bool:
+        """Stop strings: decode a tail of the output long enough to contain the longest stop string and look for them.
+        Needs ``self.detokenize`` (ids -> text); the matched text stays in the output, as with a stop token."""
+        stops = s.params.stop
+        if not stops or self.detokenize is None:
+            return False
+        longest = max(len(x) for x in stops)
+        tail = s.output_ids[-min(len(s.output_ids), 4 * longest + 8):]        # generous: a token is at least one character
+        return any(x in self.detokenize(tail) for x in stops)
+
     def _finalize(self, rec: dict) -> list[Sequence]:
         """Wait for a launched step's results and apply them (append token, stop checks, release)."""
         rec["event"].synchronize()
@@ -429,7 +441,8 @@ class LLMEngine:
             s.num_computed += 1                 # the step cached the K/V of the token it consumed
             s.output_ids.append(tok)
             s.logprobs.append(lp)
-            if (not s.params.ignore_eos and eos is not None and tok == eos) or tok in s.params.stop_token_ids:
+            if (not s.params.ignore_eos and eos is not None and tok == eos) or tok in s.params.stop_token_ids \
+                    or self._hit_stop_string(s):
                 s.finished, s.stop_reason = True, "stop"
             elif len(s.output_ids) >= s.params.max_generate_length or s.length >= self.max_len:
                 s.finished, s.stop_reason = True, "length"

@@ -27,6 +27,7 @@ class SamplingParams:
     repetition_penalty: float = 1.0
     logprobs: int | None = 1
     stop_token_ids: tuple[int, ...] = ()
+    stop: tuple[str, ...] = ()          # stop strings (need a detokenizer on the engine: ``LLMEngine.detokenize``)
     ignore_eos: bool = False
     seed: int | None = None
     n: int = 1
@@ -38,7 +39,8 @@ class SamplingParams:
         if "max_tokens" in d:
             d["max_generate_length"] = d.pop("max_tokens")
         if "stop" in d:
-            d.pop("stop")
+            st = d.pop("stop")
+            d["stop"] = () if not st else ((st,) if isinstance(st, str) else tuple(st))
         known = {k: v for k, v in d.items() if k in SamplingParams.__dataclass_fields__}
         if "stop_token_ids" in known and known["stop_token_ids"] is not None:
             known["stop_token_ids"] = tuple(known["stop_token_ids"])

@@ -202,3 +202,30 @@ def test_checkpoint_helpers(tmp_path):
     assert ckpt.cleanup_old_checkpoints(d, 2) == [1] and ckpt.list_checkpoints(d) == [2, 3]
     with pytest.raises(FileNotFoundError):
         ckpt.validate_checkpoint_dir(f"{d}/global_step_3")
+
+
+def test_engine_stop_strings_end_a_sequence_at_the_first_match():
+    from skyrl_isoexec_b200.engine.llm_engine import EngineConfig, LLMEngine
+    from skyrl_isoexec_b200.engine.sampler import SamplingParams
+    from skyrl_isoexec_b200.models.config import get_config
+    from skyrl_isoexec_b200.models.decoder import DecoderLM
+
+    assert SamplingParams.from_dict({"stop": "END"}).stop == ("END",) and SamplingParams.from_dict({"stop": None}).stop == ()
+    prompt = [5, 6, 7, 8]
+
+    def fresh():
+        eng = LLMEngine(DecoderLM(get_config("tiny-qwen3"), seed=0), EngineConfig(max_num_seqs=4, num_kv_pages=16, seed=11))
+        eng.detokenize = lambda ids: "".join(f"<{i}>" for i in ids)
+        return eng
+
+    free = fresh().generate([prompt], SamplingParams(max_generate_length=12, ignore_eos=True))[0]
+    assert len(free.response_ids) == 12 and free.stop_reason == "length"
+    target = free.response_ids[4]
+    first = free.response_ids.index(target)
+    out = fresh().generate([prompt], SamplingParams(max_generate_length=12, ignore_eos=True, stop=(f"<{target}>", "<never>")))[0]
+    assert out.stop_reason == "stop" and out.response_ids == free.response_ids[:first + 1]      # same samples, cut at the match
+    assert out.response_logprobs == free.response_logprobs[:first + 1]
+    # without a detokenizer stop strings cannot be matched and are ignored
+    eng = fresh()
+    eng.detokenize = None
+    assert len(eng.generate([prompt], SamplingParams(max_generate_length=6, ignore_eos=True, stop=(f"<{target}>",)))[0].response_ids) == 6
