@@ -42,6 +42,12 @@ class ModelConfig:
     attn_output_gate: bool = False
     zero_centered_norm: bool = False
     partial_rotary_factor: float = 1.0
+    # --- multi-head latent attention (DeepSeek-V2/V3 style); on when kv_lora_rank > 0. Every query head has its own key
+    # and value head (num_kv_heads == num_q_heads); head_dim = qk_rope_dim + the un-rotated part; v_head_dim <= head_dim
+    kv_lora_rank: int = 0
+    q_lora_rank: int = 0         # 0 = a plain query projection
+    qk_rope_dim: int = 0
+    v_head_dim: int = 0
     # --- numerics pins that enter the execution contract
     logprob_leaves: int = 8
     pik_leaves: int = 8
@@ -52,7 +58,17 @@ class ModelConfig:
         return {"bfloat16": torch.bfloat16, "float32": torch.float32}[self.dtype]
 
     @property
+    def is_mla(self) -> bool:
+        return self.kv_lora_rank > 0
+
+    @property
+    def qk_nope_dim(self) -> int:
+        return self.head_dim - self.qk_rope_dim
+
+    @property
     def rot_dim(self) -> int:
+        if self.is_mla:
+            return self.qk_rope_dim
         r = int(self.head_dim * self.partial_rotary_factor)
         return r - (r % 16) if r % 16 else r
 
@@ -85,6 +101,11 @@ class ModelConfig:
         h, L = self.hidden_size, self.num_layers
         attn = h * (self.num_q_heads * (2 if self.attn_output_gate else 1) + 2 * self.num_kv_heads) * self.head_dim \
             + self.num_q_heads * self.head_dim * h
+        if self.is_mla:
+            H, D = self.num_q_heads, self.head_dim
+            q = (h * self.q_lora_rank + self.q_lora_rank * H * D) if self.q_lora_rank else h * H * D
+            attn = q + h * (self.kv_lora_rank + self.qk_rope_dim) + self.kv_lora_rank * H * (self.qk_nope_dim + self.v_head_dim) \
+                + H * self.v_head_dim * h
         if self.has_moe:
             mlp = self.num_experts * 3 * h * self.moe_ffn_size + h * self.num_experts + 3 * h * self.shared_expert_ffn
         else:
@@ -128,6 +149,23 @@ PRESETS: dict[str, ModelConfig] = {
         name="tiny-llama", architecture="LlamaForCausalLM", vocab_size=2048, hidden_size=256, num_layers=2,
         num_q_heads=4, num_kv_heads=2, head_dim=64, ffn_size=768, qk_norm=False, rope_theta=5e5, rms_eps=1e-5,
         tie_embeddings=False, dtype="float32", max_position=512),
+    # DeepSeek-V3 style (the reference's tx model zoo, R/tx/models/deepseekv3.py): latent attention with low-rank query
+    # and key/value projections, sigmoid router with a selection bias, one shared expert. Sized so that the query/key head
+    # (rotated 64 + un-rotated 64) fits the 128-wide attention kernels
+    "deepseek-mla-16b": ModelConfig(
+        name="deepseek-mla-16b", architecture="DeepseekV3ForCausalLM", vocab_size=129280, hidden_size=2048, num_layers=27,
+        num_q_heads=16, num_kv_heads=16, head_dim=128, ffn_size=0, qk_norm=False, rope_theta=1e4, kv_lora_rank=512,
+        q_lora_rank=768, qk_rope_dim=64, v_head_dim=128, num_experts=64, top_k=6, moe_ffn_size=1408, router="sigmoid_bias",
+        shared_expert_ffn=2816, max_position=16384),
+    "tiny-mla": ModelConfig(
+        name="tiny-mla", architecture="DeepseekV3ForCausalLM", vocab_size=2048, hidden_size=256, num_layers=2,
+        num_q_heads=4, num_kv_heads=4, head_dim=64, ffn_size=768, qk_norm=False, rope_theta=1e4, kv_lora_rank=64,
+        q_lora_rank=96, qk_rope_dim=32, v_head_dim=48, dtype="float32", max_position=512),
+    "tiny-deepseek": ModelConfig(
+        name="tiny-deepseek", architecture="DeepseekV3ForCausalLM", vocab_size=2048, hidden_size=256, num_layers=2,
+        num_q_heads=4, num_kv_heads=4, head_dim=64, ffn_size=0, qk_norm=False, rope_theta=1e4, kv_lora_rank=64,
+        q_lora_rank=0, qk_rope_dim=32, v_head_dim=64, num_experts=8, top_k=2, moe_ffn_size=128, router="sigmoid_bias",
+        shared_expert_ffn=128, dtype="float32", max_position=512),
     # small variants used by tests and smoke runs
     "tiny-qwen3-bf16": ModelConfig(
         name="tiny-qwen3-bf16", architecture="Qwen3ForCausalLM", vocab_size=2048, hidden_size=256, num_layers=2,

@@ -157,7 +157,23 @@ def build_param_specs(cfg: ModelConfig, ps: ParallelState, layer_range: range | 
     for i in layers:
         p = f"layers.{i}."
         add(p + "ln1.weight", (h,), None, 0.0 if cfg.zero_centered_norm else None)
-        if cfg.layer_type(i) == "attn":
+        if cfg.layer_type(i) == "attn" and cfg.is_mla:
+            # latent attention: low-rank query and key/value projections. The down-projections and their norms are
+            # replicated; the up-projections and the output projection are cut over TP by whole heads.
+            H, D, dn, dr, dv = cfg.num_q_heads, cfg.head_dim, cfg.qk_nope_dim, cfg.qk_rope_dim, cfg.v_head_dim
+            assert cfg.num_kv_heads == H and 0 < dr < D and 0 < dv <= D and not cfg.qk_norm and not cfg.attn_output_gate, \
+                "latent attention: one KV head per query head, qk_rope_dim < head_dim, v_head_dim <= head_dim, no QK-norm or gate"
+            if cfg.q_lora_rank:
+                add(p + "attn.q_a.weight", (cfg.q_lora_rank, h), None, std)
+                add(p + "attn.q_a_norm.weight", (cfg.q_lora_rank,), None, None)
+                add(p + "attn.q_b.weight", (H * D, cfg.q_lora_rank), 0, std)           # per head: [rotated dr | un-rotated dn]
+            else:
+                add(p + "attn.q_b.weight", (H * D, h), 0, std)
+            add(p + "attn.kv_a.weight", (cfg.kv_lora_rank + dr, h), None, std)           # [latent | shared rotated key]
+            add(p + "attn.kv_a_norm.weight", (cfg.kv_lora_rank,), None, None)
+            add(p + "attn.kv_b.weight", (H * (dn + dv), cfg.kv_lora_rank), 0, std)       # per head: [un-rotated key dn | value dv]
+            add(p + "attn.o.weight", (h, H * dv), 1, out_std)
+        elif cfg.layer_type(i) == "attn":
             # stored head-major per KV group so a TP shard holds whole GQA groups: [q-block | k | v] per shard
             if tp > cfg.num_kv_heads:
                 # more TP ranks than KV heads: tp / Hkv consecutive ranks share a KV head; each keeps a slice of the
@@ -288,6 +304,39 @@ class DecoderLM(nn.Module):
             a = _gate_attn(a, qkv, self.hq, self.hkv, cfg.head_dim)
         return tp_ops.row_parallel_linear(a.reshape(T, self.hq * cfg.head_dim), self.p(pfx + "o.weight"), self.ps, cfg)
 
+    def _mla_block(self, i: int, y: torch.Tensor, fc: ForwardCtx, kv_idx: int) -> torch.Tensor:
+        """Multi-head latent attention (reference model: R/tx/models/deepseekv3.py) in its materialised form: the latent
+        is expanded to per-head keys and values, which are laid out as an ordinary fused [q | k | v] row per head
+        (rotated dims first, values zero-padded to the query/key width), so rotary, KV pool and the attention kernels are
+        the ones every other family uses. The padding contributes exact zeros to every dot product; the padded output
+        columns are dropped before the output projection. The KV pool therefore holds full keys and values, not the latent."""
+        cfg, pfx, ps = self.cfg, f"layers.{i}.attn.", self.ps
+        T, H, D, dn, dr, dv, r = y.shape[0], self.hq, cfg.head_dim, cfg.qk_nope_dim, cfg.qk_rope_dim, cfg.v_head_dim, cfg.kv_lora_rank
+        if cfg.q_lora_rank:
+            qa, _ = F.rmsnorm(F.linear(y, self.p(pfx + "q_a.weight")), self.p(pfx + "q_a_norm.weight"), cfg.rms_eps, False)
+        else:
+            qa = y
+        q = F.linear(tp_ops.copy_to_tp(qa, ps), self.p(pfx + "q_b.weight")).view(T, H, D)
+        kva = F.linear(y, self.p(pfx + "kv_a.weight"))
+        c, _ = F.rmsnorm(kva[:, :r].contiguous(), self.p(pfx + "kv_a_norm.weight"), cfg.rms_eps, False)
+        k_rot = tp_ops.copy_to_tp(kva[:, r:].contiguous(), ps)                  # one rotated key shared by all heads
+        kvb = F.linear(tp_ops.copy_to_tp(c, ps), self.p(pfx + "kv_b.weight")).view(T, H, dn + dv)
+        k = torch.cat([k_rot.unsqueeze(1).expand(T, H, dr), kvb[..., :dn]], dim=-1)
+        v = kvb[..., dn:]
+        if dv < D:
+            v = torch.nn.functional.pad(v, (0, D - dv))
+        qkv = torch.cat([q, k, v], dim=-1).reshape(T, H * 3 * D)
+        if fc.kv is None:
+            q, k, v = F.qk_norm_rope_train(qkv, fc.positions, self.rope, None, None, H, H, D, cfg.rms_eps, False, False, False)
+            a = F.attention(q, k, v, fc.meta, self.scale)
+        else:
+            k_pool, v_pool = fc.kv[kv_idx]
+            q = F.qk_norm_rope_fwd(qkv, fc.positions, fc.slots, self.rope, None, None, k_pool, v_pool, H, H, D, cfg.rms_eps,
+                                   False, False, False)
+            a, _ = F.attention_fwd(q, k_pool, v_pool, fc.meta, self.scale)
+        a = a[..., :dv].reshape(T, H * dv) if dv < D else a.reshape(T, H * D)
+        return tp_ops.row_parallel_linear(a, self.p(pfx + "o.weight"), ps, cfg)
+
     def _mlp_block(self, i: int, y: torch.Tensor) -> torch.Tensor:
         cfg, pfx = self.cfg, f"layers.{i}."
         if cfg.has_moe:
@@ -305,7 +354,7 @@ class DecoderLM(nn.Module):
         cfg = self.cfg
         y, res = _norm(x, self.p(f"layers.{i}.ln1.weight"), cfg, res)
         if cfg.layer_type(i) == "attn":
-            o = self._attn_block(i, y, fc, kv_idx)
+            o = self._mla_block(i, y, fc, kv_idx) if cfg.is_mla else self._attn_block(i, y, fc, kv_idx)
         else:
             o = gdn_ops.gdn_block(y, self, i, fc, kv_idx)
         y, res = _norm(o, self.p(f"layers.{i}.ln2.weight"), cfg, res)

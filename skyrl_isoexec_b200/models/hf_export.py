@@ -2,6 +2,9 @@
 format ``trainer.export_path`` / ``hf_save_interval`` write (reference: B/workers/.../save_hf_model paths and the
 Megatron<->HF bridges in B/workers/megatron/model_bridges.py).
 
+Latent-attention (DeepSeek-style) models export ``q_a_proj / q_b_proj / kv_a_proj_with_mqa / kv_b_proj`` with the rotated
+dims re-interleaved and moved behind the un-rotated ones, the order those checkpoints use.
+
 Internally QKV and gate/up are fused and QKV rows are stored KV-group major; the export un-fuses them into
 ``q_proj / k_proj / v_proj`` and ``gate_proj / up_proj`` with the usual Qwen3 names, and the import does the reverse.
 Tensor-parallel models are gathered on the way out (``sync.strategies.gather_full``); the import slices full tensors
@@ -38,6 +41,37 @@ def _fuse_qkv(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cfg: ModelConfi
     qs = 2 * D if cfg.attn_output_gate else D
     h = q.shape[-1]
     return torch.cat([q.view(Hkv, G * qs, h), k.view(Hkv, D, h), v.view(Hkv, D, h)], 1).reshape(-1, h)
+
+
+def _rope_perm(dr: int, to_hf: bool) -> torch.Tensor:
+    """Row permutation between the rotate-half order of the rotated dims kept here ([first halves | second halves]) and the
+    interleaved (pair-adjacent) order of DeepSeek checkpoints."""
+    half = torch.arange(dr // 2)
+    to = torch.stack([half, half + dr // 2], 1).reshape(-1)          # hf[2j] = ours[j], hf[2j + 1] = ours[dr/2 + j]
+    return to if to_hf else torch.argsort(to)
+
+
+def _mla_q_rows(w: torch.Tensor, cfg: ModelConfig, to_hf: bool) -> torch.Tensor:
+    """Query up-projection rows per head: [rotated | un-rotated] here, [un-rotated | rotated, interleaved] in the checkpoint."""
+    H, D, dr = cfg.num_q_heads, cfg.head_dim, cfg.qk_rope_dim
+    g = w.view(H, D, -1)
+    if to_hf:
+        return torch.cat([g[:, dr:], g[:, :dr][:, _rope_perm(dr, True)]], 1).reshape(H * D, -1)
+    dn = D - dr
+    return torch.cat([g[:, dn:][:, _rope_perm(dr, False)], g[:, :dn]], 1).reshape(H * D, -1)
+
+
+def _mla_kv_a_rows(w: torch.Tensor, cfg: ModelConfig, to_hf: bool) -> torch.Tensor:
+    r = cfg.kv_lora_rank
+    return torch.cat([w[:r], w[r:][_rope_perm(cfg.qk_rope_dim, to_hf)]], 0)
+
+
+_MLA_NAMES = {"attn.q_a.weight": "self_attn.q_a_proj.weight", "attn.q_a_norm.weight": "self_attn.q_a_layernorm.weight",
+              "attn.kv_a_norm.weight": "self_attn.kv_a_layernorm.weight", "attn.kv_b.weight": "self_attn.kv_b_proj.weight"}
+
+
+def _shared_prefix(cfg: ModelConfig) -> str:
+    return "mlp.shared_experts." if cfg.is_mla else "mlp.shared_expert."
 
 
 def full_named_weights(model: DecoderLM):
@@ -78,9 +112,17 @@ def to_hf_state_dict(model: DecoderLM) -> dict[str, torch.Tensor]:
                 q, k, v = _split_qkv(t, cfg)
                 out[p + "self_attn.q_proj.weight"], out[p + "self_attn.k_proj.weight"], out[p + "self_attn.v_proj.weight"] = \
                     q.contiguous(), k.contiguous(), v.contiguous()
+            elif rest == "attn.q_b.weight":
+                out[p + ("self_attn.q_b_proj.weight" if cfg.q_lora_rank else "self_attn.q_proj.weight")] = _mla_q_rows(t, cfg, True).contiguous()
+            elif rest == "attn.kv_a.weight":
+                out[p + "self_attn.kv_a_proj_with_mqa.weight"] = _mla_kv_a_rows(t, cfg, True).contiguous()
             elif rest == "mlp.gate_up.weight":
                 f = t.shape[0] // 2
                 out[p + "mlp.gate_proj.weight"], out[p + "mlp.up_proj.weight"] = t[:f].contiguous(), t[f:].contiguous()
+            elif rest == "moe.shared.gate_up.weight":
+                f = t.shape[0] // 2
+                out[p + _shared_prefix(cfg) + "gate_proj.weight"], out[p + _shared_prefix(cfg) + "up_proj.weight"] = \
+                    t[:f].contiguous(), t[f:].contiguous()
             elif rest == "moe.experts.gate_up":
                 f = t.shape[1] // 2
                 for e in range(t.shape[0]):
@@ -93,7 +135,8 @@ def to_hf_state_dict(model: DecoderLM) -> dict[str, torch.Tensor]:
                 ren = {"ln1.weight": "input_layernorm.weight", "ln2.weight": "post_attention_layernorm.weight",
                        "attn.o.weight": "self_attn.o_proj.weight", "attn.q_norm.weight": "self_attn.q_norm.weight",
                        "attn.k_norm.weight": "self_attn.k_norm.weight", "mlp.down.weight": "mlp.down_proj.weight",
-                       "moe.router.weight": "mlp.gate.weight"}
+                       "moe.router.weight": "mlp.gate.weight", "moe.router.expert_bias": "mlp.gate.e_score_correction_bias",
+                       "moe.shared.down.weight": _shared_prefix(cfg) + "down_proj.weight", **_MLA_NAMES}
                 out[p + ren.get(rest, rest)] = t
     return out
 
@@ -107,6 +150,13 @@ def hf_config(cfg: ModelConfig) -> dict:
          "intermediate_size": cfg.ffn_size, "vocab_size": cfg.vocab_size, "rope_theta": cfg.rope_theta, "rms_norm_eps": cfg.rms_eps,
          "tie_word_embeddings": cfg.tie_embeddings, "max_position_embeddings": cfg.max_position, "torch_dtype": cfg.dtype,
          "hidden_act": "silu"}
+    if cfg.is_mla:
+        d["architectures"] = ["DeepseekV3ForCausalLM"]
+        d.update({"kv_lora_rank": cfg.kv_lora_rank, "q_lora_rank": cfg.q_lora_rank or None, "qk_rope_head_dim": cfg.qk_rope_dim,
+                  "qk_nope_head_dim": cfg.qk_nope_dim, "v_head_dim": cfg.v_head_dim})
+        if cfg.has_moe:
+            d.update({"n_routed_experts": cfg.num_experts, "n_shared_experts": 1 if cfg.shared_expert_ffn else 0,
+                      "scoring_func": "sigmoid" if cfg.router == "sigmoid_bias" else "softmax"})
     if cfg.has_moe:
         d.update({"num_experts": cfg.num_experts, "num_experts_per_tok": cfg.top_k, "moe_intermediate_size": cfg.moe_ffn_size,
                   "norm_topk_prob": cfg.norm_topk_prob})
@@ -146,8 +196,14 @@ def load_hf(model: DecoderLM, path: str) -> int:
                 p = f"model.layers.{i}."
                 if rest == "attn.qkv.weight":
                     src = _fuse_qkv(sd[p + "self_attn.q_proj.weight"], sd[p + "self_attn.k_proj.weight"], sd[p + "self_attn.v_proj.weight"], cfg)
+                elif rest == "attn.q_b.weight":
+                    src = _mla_q_rows(sd[p + ("self_attn.q_b_proj.weight" if cfg.q_lora_rank else "self_attn.q_proj.weight")], cfg, False)
+                elif rest == "attn.kv_a.weight":
+                    src = _mla_kv_a_rows(sd[p + "self_attn.kv_a_proj_with_mqa.weight"], cfg, False)
                 elif rest == "mlp.gate_up.weight":
                     src = torch.cat([sd[p + "mlp.gate_proj.weight"], sd[p + "mlp.up_proj.weight"]], 0)
+                elif rest == "moe.shared.gate_up.weight":
+                    src = torch.cat([sd[p + _shared_prefix(cfg) + "gate_proj.weight"], sd[p + _shared_prefix(cfg) + "up_proj.weight"]], 0)
                 elif rest == "moe.experts.gate_up":
                     src = torch.stack([torch.cat([sd[p + f"mlp.experts.{e}.gate_proj.weight"], sd[p + f"mlp.experts.{e}.up_proj.weight"]], 0)
                                        for e in range(cfg.num_experts)])      # all experts; cut to this rank's below
@@ -157,7 +213,8 @@ def load_hf(model: DecoderLM, path: str) -> int:
                     ren = {"ln1.weight": "input_layernorm.weight", "ln2.weight": "post_attention_layernorm.weight",
                            "attn.o.weight": "self_attn.o_proj.weight", "attn.q_norm.weight": "self_attn.q_norm.weight",
                            "attn.k_norm.weight": "self_attn.k_norm.weight", "mlp.down.weight": "mlp.down_proj.weight",
-                           "moe.router.weight": "mlp.gate.weight"}
+                           "moe.router.weight": "mlp.gate.weight", "moe.router.expert_bias": "mlp.gate.e_score_correction_bias",
+                           "moe.shared.down.weight": _shared_prefix(cfg) + "down_proj.weight", **_MLA_NAMES}
                     src = sd[p + ren.get(rest, rest)]
             spec = model.store.specs[name]
             if tuple(src.shape) != tuple(t.shape) and src.numel() != t.numel():

@@ -246,6 +246,6 @@ def moe_block(y: torch.Tensor, model, i: int) -> torch.Tensor:
     if cfg.shared_expert_ffn:
         from ..parallel import tp as tp_ops
 
-        gu = F.linear(y, model.p(pfx + "shared.gate_up.weight"))
+        gu = F.linear(tp_ops.copy_to_tp(y, ps), model.p(pfx + "shared.gate_up.weight"))   # column-parallel: sum the input grads
         shared = tp_ops.row_parallel_linear(F.swiglu(gu), model.p(pfx + "shared.down.weight"), ps, cfg)
     return combine_fixed_order(rows, pos, y.dtype, shared)

@@ -15,7 +15,7 @@ from dataclasses import dataclass, field
 
 import torch
 
-DEFAULT_TARGETS = ("attn.qkv.weight", "attn.o.weight", "mlp.gate_up.weight", "mlp.down.weight")
+DEFAULT_TARGETS = ("attn.qkv.weight", "attn.q_b.weight", "attn.kv_b.weight", "attn.o.weight", "mlp.gate_up.weight", "mlp.down.weight")
 
 
 @dataclass

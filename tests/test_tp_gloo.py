@@ -32,7 +32,7 @@ def _worker(rank, port, q):
 
         ps2 = ParallelState.build(tp=2)
         out = {}
-        for name in ("tiny-qwen3", "tiny-moe", "tiny-hybrid"):
+        for name in ("tiny-qwen3", "tiny-moe", "tiny-hybrid", "tiny-mla", "tiny-deepseek"):
             cfg = get_config(name, tp_invariant=True)
             g = torch.Generator().manual_seed(1)
             prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (20, 33, 9)]
