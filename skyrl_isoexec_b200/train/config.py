@@ -89,6 +89,7 @@ class GeneratorConfig:
     use_conversation_multi_turn: bool = True
     zero_reward_on_non_stop: bool = False
     apply_overlong_filtering: bool = False
+    rate_limit: dict = field(default_factory=dict)   # enabled / trajectories_per_second / max_concurrency (multi-turn trajectories)
 
 
 @dataclass

@@ -79,7 +79,10 @@ def concatenate_generator_outputs(outs: list[GeneratorOutput]) -> GeneratorOutpu
 class SkyRLGymGenerator(GeneratorInterface):
     def __init__(self, engine: InferenceEngineInterface, tokenizer=None, max_turns: int = 1, batched: bool = True,
                  max_input_length: int = 1 << 30, env_config: dict | None = None, zero_reward_on_non_stop: bool = False,
-                 apply_overlong_filtering: bool = False):
+                 apply_overlong_filtering: bool = False, rate_limit=None):
+        from ..utils.rate_limiter import create_rate_limiter
+
+        self.rate_limiter = create_rate_limiter(rate_limit)      # brackets every multi-turn trajectory (start rate, in flight)
         self.engine = engine
         self.tokenizer = tokenizer
         self.max_turns = max_turns
@@ -184,9 +187,12 @@ class SkyRLGymGenerator(GeneratorInterface):
         if self.batched and self.max_turns == 1:
             return await self.generate_batched(input_batch)
         extras = input_batch.get("env_extras") or [{}] * n
-        res = await asyncio.gather(*[
-            self.agent_loop(input_batch["prompts"][i], input_batch["env_classes"][i], extras[i],
-                            input_batch.get("sampling_params")) for i in range(n)])
+        async def one(i):
+            async with self.rate_limiter:
+                return await self.agent_loop(input_batch["prompts"][i], input_batch["env_classes"][i], extras[i],
+                                             input_batch.get("sampling_params"))
+
+        res = await asyncio.gather(*[one(i) for i in range(n)])
         out: GeneratorOutput = {
             "prompt_token_ids": [r[0] for r in res], "response_ids": [r[1] for r in res], "rewards": [r[2] for r in res],
             "loss_masks": [r[3] for r in res], "stop_reasons": [r[4] for r in res], "rollout_logprobs": [r[5] for r in res],

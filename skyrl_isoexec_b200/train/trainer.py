@@ -109,7 +109,12 @@ class RayPPOTrainer:
     """Name kept for API parity; no Ray involved."""
 
     def __init__(self, cfg: SkyRLTrainConfig, ps: ParallelState | None = None, device: str | None = None,
-                 dataset=None, tokenizer=None, tracker: Tracking | None = None):
+                 dataset=None, tokenizer=None, tracker: Tracking | None = None, callbacks=None):
+        from .callbacks import CallbackHandler, TrainingControl
+
+        self.callbacks = CallbackHandler(callbacks)
+        self.control = TrainingControl()
+        self.epoch = 0
         self.cfg = cfg
         self.ps = ps or ParallelState.single()
         self.rank = dist.get_rank() if dist.is_initialized() else 0
@@ -127,6 +132,17 @@ class RayPPOTrainer:
         self.engine: LLMEngine | None = None
         self.generator: SkyRLGymGenerator | None = None
         self.kl_ctrl = alg.get_kl_controller(t.algorithm)
+
+    def _fire(self, event: str, **fields) -> None:
+        """Dispatch one callback event (R/train/utils/callbacks.py:117-162) with a fresh snapshot of the run's position."""
+        if not self.callbacks:
+            return
+        from .callbacks import CallbackInput
+
+        per_epoch = len(self.loader) if getattr(self, "loader", None) is not None else 0
+        t = self.cfg.trainer
+        total = t.num_steps if t.num_steps > 0 else per_epoch * t.epochs
+        getattr(self.callbacks, event)(self, CallbackInput(self.global_step, self.epoch, total, per_epoch, **fields), self.control)
 
     # ------------------------------------------------------------------ build
     def build_models(self) -> None:
@@ -161,7 +177,8 @@ class RayPPOTrainer:
         self.generator = SkyRLGymGenerator(self.infer, self.tokenizer, max_turns=g.max_turns, batched=g.batched,
                                            env_config=self.cfg.environment.env_kwargs,
                                            zero_reward_on_non_stop=g.zero_reward_on_non_stop,
-                                           apply_overlong_filtering=g.apply_overlong_filtering)
+                                           apply_overlong_filtering=g.apply_overlong_filtering,
+                                           rate_limit=g.rate_limit or None)
         if t.isoexec.enabled:
             self.adapter_trainer = ContractAdapter("trainer", model, self.rank, engine_tp=ie.tensor_parallel_size
                                                    if not ie.run_engines_locally else self.ps.tp)
@@ -470,6 +487,7 @@ class RayPPOTrainer:
         if getattr(self, "_gpu_mon", None) is not None:
             g = self._gpu_mon.summary(reset=True)
             self.all_metrics.update({f"gpu/{k}": (",".join(v) if isinstance(v, list) else v) for k, v in g.items()})
+        self._fire("on_log", logs=self.all_metrics)
         if self.tracker is not None:
             self.tracker.log(self.all_metrics, self.global_step)
         return dict(self.all_metrics)
@@ -482,17 +500,32 @@ class RayPPOTrainer:
             self.load_checkpoints()
         self.sync_weights()
         try:
+            self._fire("on_train_start")
             if t.eval_before_train:
                 self.eval()
-            for _epoch in range(t.epochs):
+            done = False
+            for self.epoch in range(t.epochs):
+                self._fire("on_epoch_start")
                 for rows in self.loader:
-                    self.train_step(rows)
-                    if t.eval_interval > 0 and self.global_step % t.eval_interval == 0:
+                    self._fire("on_step_start", batch=rows)
+                    metrics = self.train_step(rows)
+                    self._fire("on_step_end", batch=rows, metrics=metrics)
+                    # the control flags are read once per step, here, and cleared
+                    want_save, want_eval = self.control.should_save, self.control.should_evaluate
+                    self.control.reset()
+                    if want_save and t.ckpt_path and not (t.ckpt_interval > 0 and self.global_step % t.ckpt_interval == 0):
+                        self.save_checkpoints()
+                    if want_eval or (t.eval_interval > 0 and self.global_step % t.eval_interval == 0):
                         self.eval()
                     if t.export_path and t.hf_save_interval > 0 and self.global_step % t.hf_save_interval == 0:
                         self.export_hf()
-                    if 0 < t.num_steps <= self.global_step:
-                        return
+                    if 0 < t.num_steps <= self.global_step or self.control.should_stop:
+                        done = True
+                        break
+                self._fire("on_epoch_end")
+                if done:
+                    break
+            self._fire("on_train_end")
         except BaseException as e:  # noqa: BLE001
             if self.tracker is not None:
                 self.tracker.log_exception(e, self.global_step)
@@ -518,12 +551,14 @@ class RayPPOTrainer:
         if was_asleep:
             self.engine.wake_up()
         n = max(1, g.eval_n_samples_per_prompt)
+        self._fire("on_eval_start")
         out = evaluate(self.generator, rows, params, n_samples=n, ks=tuple(sorted({1, n})))
         if was_asleep:
             self.engine.sleep()
         if self.tracker is not None:
             self.tracker.log(out, self.global_step)
         self.last_eval = out
+        self._fire("on_eval_end", metrics=out)
         return out
 
     def export_hf(self) -> str | None:
@@ -543,9 +578,11 @@ class RayPPOTrainer:
     # ------------------------------------------------------------------ checkpoints
     def save_checkpoints(self) -> str:
         t = self.cfg.trainer
-        return ckpt.save_checkpoint(t.ckpt_path, self.global_step, self.policy, self.loader.state_dict(),
+        path = ckpt.save_checkpoint(t.ckpt_path, self.global_step, self.policy, self.loader.state_dict(),
                                     {"global_step": self.global_step, "config": self.cfg.to_dict()}, self.ps,
                                     max_to_keep=t.max_ckpts_to_keep)
+        self._fire("on_save", ckpt_path=path)
+        return path
 
     def load_checkpoints(self) -> int:
         t = self.cfg.trainer

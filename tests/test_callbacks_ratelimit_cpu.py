@@ -1,0 +1,142 @@
+"""Trainer callbacks (events, control flags, log mutation, early stop) and the trajectory rate / concurrency limiter."""
+
+import asyncio
+import json
+import os
+
+import pytest
+
+from skyrl_isoexec_b200.train.callbacks import CallbackHandler, TrainingCallback
+from skyrl_isoexec_b200.train.config import SkyRLTrainConfig
+from skyrl_isoexec_b200.train.trainer import RayPPOTrainer
+from skyrl_isoexec_b200.utils.rate_limiter import (AsyncRateLimiter, NoOpRateLimiter, RateLimiterConfig, create_rate_limiter)
+
+
+def _cfg(tmp, steps, *extra):
+    return SkyRLTrainConfig.from_cli_overrides([
+        "trainer.policy.model=tiny-qwen3", "trainer.train_batch_size=2", "trainer.policy_mini_batch_size=2",
+        "generator.n_samples_per_prompt=2", "generator.sampling_params.max_generate_length=4",
+        "generator.sampling_params.ignore_eos=true", "data.synthetic_prompt_len=8", "data.synthetic_prompts=16",
+        "trainer.max_prompt_length=8", "generator.inference_engine.num_kv_pages=16", f"trainer.num_steps={steps}",
+        f"trainer.ckpt_path={tmp}", "trainer.ckpt_interval=0", "trainer.logger=jsonl", "trainer.eval_batch_size=2",
+        "generator.eval_sampling_params.max_generate_length=4", "generator.eval_sampling_params.ignore_eos=true", *extra])
+
+
+class _Recorder(TrainingCallback):
+    def __init__(self):
+        self.events = []
+
+    def on_train_start(self, trainer, ci, control):
+        self.events.append(("train_start", ci.global_step, ci.total_steps))
+
+    def on_epoch_start(self, trainer, ci, control):
+        self.events.append(("epoch_start", ci.epoch))
+
+    def on_step_start(self, trainer, ci, control):
+        assert ci.batch is not None and ci.metrics is None
+        self.events.append(("step_start", ci.global_step))
+
+    def on_step_end(self, trainer, ci, control):
+        assert "policy/grad_norm" in ci.metrics
+        self.events.append(("step_end", ci.global_step))
+        if ci.global_step == 1:
+            control.should_save = control.should_evaluate = True     # neither is scheduled by the config
+        if ci.global_step == 2:
+            control.should_stop = True
+
+    def on_eval_start(self, trainer, ci, control):
+        self.events.append(("eval_start", ci.global_step))
+
+    def on_eval_end(self, trainer, ci, control):
+        assert "eval/num_prompts" in ci.metrics
+        self.events.append(("eval_end", ci.global_step))
+
+    def on_save(self, trainer, ci, control):
+        assert os.path.isdir(ci.ckpt_path)
+        self.events.append(("save", ci.global_step))
+
+    def on_log(self, trainer, ci, control):
+        ci.logs["custom/seen_by_callback"] = float(ci.global_step)
+
+    def on_train_end(self, trainer, ci, control):
+        self.events.append(("train_end", ci.global_step))
+
+
+def test_trainer_fires_callbacks_and_honours_control_flags(tmp_path):
+    rec, other = _Recorder(), TrainingCallback()
+    tr = RayPPOTrainer(_cfg(str(tmp_path), 5), device="cpu", callbacks=[CallbackHandler([rec]), other])   # handlers nest
+    tr.train()
+    assert tr.global_step == 2, "should_stop ends the run after step 2 although five steps were configured"
+    assert rec.events == [("train_start", 0, 5), ("epoch_start", 0), ("step_start", 0), ("step_end", 1), ("save", 1),
+                          ("eval_start", 1), ("eval_end", 1), ("step_start", 1), ("step_end", 2), ("train_end", 2)]
+    assert not tr.control.should_save and not tr.control.should_evaluate
+    assert tr.all_metrics["custom/seen_by_callback"] == 2.0
+    logged = [json.loads(ln) for ln in open(_jsonl(tr))]
+    assert any(r.get("custom/seen_by_callback") == 1.0 for r in logged), "the field a callback added reaches the tracker"
+
+
+def _jsonl(tr):
+    return tr.tracker.loggers["jsonl"].f.name
+
+
+def test_rate_limiter_config_and_factory():
+    with pytest.raises(ValueError):
+        RateLimiterConfig(True, 0.5, None)
+    with pytest.raises(ValueError):
+        AsyncRateLimiter(None, 0)
+    assert isinstance(create_rate_limiter(None), NoOpRateLimiter)
+    assert isinstance(create_rate_limiter({"enabled": False, "max_concurrency": 2}), NoOpRateLimiter)
+    assert isinstance(create_rate_limiter({"enabled": True}), NoOpRateLimiter)
+    lim = create_rate_limiter(RateLimiterConfig(True, 2.0, 3))
+    assert isinstance(lim, AsyncRateLimiter) and lim.rate == 2.0 and lim.max_concurrency == 3
+
+
+def test_rate_limiter_token_bucket_on_virtual_time_and_concurrency_cap():
+    now = [0.0]
+
+    async def fake_sleep(dt):
+        now[0] += dt
+        await asyncio.sleep(0)
+
+    async def run():
+        lim = AsyncRateLimiter(rate=4.0, clock=lambda: now[0], sleep=fake_sleep)
+        stamps = []
+        for _ in range(10):
+            await lim.acquire()
+            stamps.append(now[0])
+            lim.release()
+        # a full bucket lets four through at once, then one start every quarter second
+        assert stamps[:4] == [0.0] * 4
+        assert [round(s, 6) for s in stamps[4:]] == [0.25, 0.5, 0.75, 1.0, 1.25, 1.5]
+
+        cap = AsyncRateLimiter(max_concurrency=3)
+        live = [0]
+
+        async def traj():
+            async with cap:
+                live[0] += 1
+                assert live[0] <= 3
+                await asyncio.sleep(0.001)
+                live[0] -= 1
+
+        await asyncio.gather(*[traj() for _ in range(12)])
+        assert cap.peak_in_flight == 3 and cap.in_flight == 0 and cap.started == 12
+
+        # an exception inside the bracket still frees the slot
+        with pytest.raises(RuntimeError):
+            async with cap:
+                raise RuntimeError("trajectory failed")
+        assert cap.in_flight == 0
+
+    asyncio.run(run())
+
+
+def test_generator_brackets_multi_turn_trajectories_with_the_limiter(tmp_path):
+    tr = RayPPOTrainer(_cfg(str(tmp_path), 1, "generator.batched=false", "generator.rate_limit.enabled=true",
+                            "generator.rate_limit.max_concurrency=2"), device="cpu")
+    tr.build_models()
+    tr.sync_weights()
+    m = tr.train_step(next(iter(tr.loader)))
+    lim = tr.generator.rate_limiter
+    assert isinstance(lim, AsyncRateLimiter) and lim.started == 4 and lim.peak_in_flight <= 2 and lim.in_flight == 0
+    assert m["policy/rollout_train_logprob_bit_mismatches"] == 0
