@@ -157,6 +157,7 @@ class TrainerConfig:
     profiler: ProfilerConfig = field(default_factory=ProfilerConfig)    # torch.profiler over a window of steps
     nvtx: bool = False                  # NVTX range around every phase of a step (for timeline tools)
     record_memory: str = ""             # directory: allocator history on, one snapshot after each policy update
+    log_example_interval: int = 0        # > 0: print the first rollout of the step every this many steps
     gpu_monitor: bool = False           # poll nvidia-smi (read-only) and log gpu/* per step: clocks, power, throttle reasons
 
 

@@ -454,6 +454,12 @@ class RayPPOTrainer:
                         go = self.generate(gi)
             with Timer("sleep", T):
                 self.engine.sleep()
+            every = self.cfg.trainer.log_example_interval
+            if every > 0 and self.rank == 0 and self.global_step % every == 0 and go["response_ids"]:
+                from ..utils.tracking import log_example
+
+                dec = self.tokenizer.decode if self.tokenizer is not None else str
+                log_example(dec(list(go["prompt_token_ids"][0])), dec(list(go["response_ids"][0])), go["rewards"][0])
             with Timer("convert", T):
                 batch = self.convert_to_training_input(go, uids)
             if self.global_step == 1 and hasattr(self, "adapter_engine"):

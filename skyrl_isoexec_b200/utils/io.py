@@ -73,3 +73,43 @@ def local_work_dir(path: str):
     p = _local(path)
     os.makedirs(p, exist_ok=True)
     yield p
+
+
+# ----------------------------------------------------------------------------- archives (reference: R/utils/storage.py)
+@contextlib.contextmanager
+def pack_and_upload(dest: str, rank: int | None = None):
+    """Yield an empty temporary directory; on a clean exit its content becomes the archive ``dest`` (tar inside gzip at
+    level 0: checkpoint tensors do not compress, speed matters). With ``rank`` given and a ``dest + ".probe"`` file
+    present, the filesystem is shared between the ranks and only rank 0 writes. The archive appears atomically."""
+    import gzip
+    import tarfile
+
+    with tempfile.TemporaryDirectory() as tmp:
+        yield tmp
+        if rank not in (None, 0) and exists(dest + ".probe"):
+            return
+        with atomic_write(dest, "wb") as f:
+            with gzip.GzipFile(fileobj=f, mode="wb", compresslevel=0) as gz:
+                with tarfile.open(fileobj=gz, mode="w:") as tar:
+                    tar.add(tmp, arcname="")
+
+
+@contextlib.contextmanager
+def download_and_unpack(source: str):
+    """Yield a temporary directory holding the content of the archive ``source``. Members that would land outside the
+    directory, links and device files are refused (tarfile's ``data`` filter)."""
+    import tarfile
+
+    with tempfile.TemporaryDirectory() as tmp:
+        with open_file(source, "rb") as f:
+            with tarfile.open(fileobj=f, mode="r:gz") as tar:
+                tar.extractall(tmp, filter="data")
+        yield tmp
+
+
+def download_file(source: str):
+    """The whole file as an in-memory binary stream positioned at 0."""
+    import io as _io
+
+    with open_file(source, "rb") as f:
+        return _io.BytesIO(f.read())

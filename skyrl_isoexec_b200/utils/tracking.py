@@ -51,6 +51,30 @@ class Timer:
         return False
 
 
+_ANSI = {"green": "\033[32m", "yellow": "\033[33m", "cyan": "\033[36m"}
+
+
+def log_example(prompt, response, reward=None, stream=None, color: bool | None = None) -> str:
+    """Print one rollout (reference: R/train/utils/logging_utils.py:35-84): the prompt in cyan, the response in green when
+    its total reward is positive and yellow otherwise, line by line so that a pager or a log collector that cuts at line
+    ends keeps the colours. ``reward`` may be a number or per-token rewards (summed). Returns the text that was written."""
+    import sys
+
+    stream = stream or sys.stdout
+    if color is None:
+        color = bool(getattr(stream, "isatty", lambda: False)())
+    total = None if reward is None else float(sum(reward)) if isinstance(reward, (list, tuple)) else float(reward)
+
+    def block(text, name):
+        lines = str(text).splitlines() or [""]
+        return "\n".join(f"{_ANSI[name]}{ln}\033[0m" if color else ln for ln in lines)
+
+    text = (f"Example:\n  Input: {block(prompt, 'cyan')}\n  Output (Total Reward: {'N/A' if total is None else format(total, '.4f')}):\n"
+            f"{block(response, 'green' if total is not None and total > 0 else 'yellow')}\n")
+    stream.write(text)
+    return text
+
+
 class ConsoleLogger:
     def log(self, data: dict, step: int):
         keys = sorted(data)

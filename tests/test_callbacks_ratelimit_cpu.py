@@ -140,3 +140,48 @@ def test_generator_brackets_multi_turn_trajectories_with_the_limiter(tmp_path):
     lim = tr.generator.rate_limiter
     assert isinstance(lim, AsyncRateLimiter) and lim.started == 4 and lim.peak_in_flight <= 2 and lim.in_flight == 0
     assert m["policy/rollout_train_logprob_bit_mismatches"] == 0
+
+
+def test_archives_round_trip_and_shared_filesystem_probe(tmp_path):
+    from skyrl_isoexec_b200.utils import io as xio
+
+    dest = str(tmp_path / "out" / "ckpt.tar.gz")
+    with xio.pack_and_upload(dest) as d:
+        os.makedirs(os.path.join(d, "sub"))
+        open(os.path.join(d, "sub", "a.bin"), "wb").write(b"\x00\x01" * 1000)
+        open(os.path.join(d, "meta.json"), "w").write("{}")
+    with xio.download_and_unpack(dest) as d:
+        assert open(os.path.join(d, "sub", "a.bin"), "rb").read() == b"\x00\x01" * 1000 and os.path.exists(os.path.join(d, "meta.json"))
+    assert xio.download_file(dest).read(2) == b"\x1f\x8b"                       # a gzip stream
+    # shared filesystem (probe file present): ranks other than 0 leave the archive alone
+    other = str(tmp_path / "shared.tar.gz")
+    open(other + ".probe", "w").close()
+    with xio.pack_and_upload(other, rank=1) as d:
+        open(os.path.join(d, "x"), "w").write("1")
+    assert not os.path.exists(other)
+    with xio.pack_and_upload(other, rank=0) as d:
+        open(os.path.join(d, "x"), "w").write("1")
+    assert os.path.exists(other)
+    # a failure inside the block writes nothing
+    bad = str(tmp_path / "bad.tar.gz")
+    with pytest.raises(RuntimeError):
+        with xio.pack_and_upload(bad) as d:
+            raise RuntimeError("save failed")
+    assert not os.path.exists(bad)
+
+
+def test_log_example_formats_reward_and_colours(tmp_path, capsys):
+    import io
+
+    from skyrl_isoexec_b200.utils.tracking import log_example
+
+    buf = io.StringIO()
+    text = log_example([{"role": "user", "content": "2+2?"}], "line one\nline two", [0.0, 1.0], stream=buf, color=True)
+    assert buf.getvalue() == text and "Total Reward: 1.0000" in text
+    assert text.count("\033[32m") == 2 and "\033[36m" in text                     # both response lines green, prompt cyan
+    text = log_example("p", "r", None, stream=buf, color=False)
+    assert "Total Reward: N/A" in text and "\033[" not in text
+    assert "\033[33m" in log_example("p", "r", -1.0, stream=buf, color=True)     # non-positive reward: yellow
+    tr = RayPPOTrainer(_cfg(str(tmp_path), 1, "trainer.log_example_interval=1"), device="cpu")
+    tr.train()
+    assert "Example:\n  Input: " in capsys.readouterr().out
