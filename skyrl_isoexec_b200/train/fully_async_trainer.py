@@ -33,6 +33,10 @@ class AsyncConfig:
     max_staleness_steps: int = 1
     num_parallel_generation_workers: int = 4      # prompt groups in flight
     mini_batch_prompts: int = 8
+    # simulated trainer (FullyAsyncTrainerSim): no trainer components, sleeps stand in for the update and the weight sync
+    simulate_training: bool = False
+    simulate_training_step_seconds: float = 0.0
+    simulate_weight_sync_seconds: float = 0.0
 
 
 class AsyncPromptSource:
@@ -178,11 +182,27 @@ class FullyAsyncTrainer(RayPPOTrainer):
             self.groups.put_error()
 
     # ------------------------------------------------------------------ training side
+    def _run_training(self, batch, fresh: bool) -> None:
+        """Scoring forward, advantages and the policy update on one mini-batch of finished groups."""
+        iso = self.cfg.trainer.isoexec
+        strict_before = iso.strict
+        if not fresh:
+            iso.strict = False          # stale samples are off-policy by construction
+        try:
+            batch = self.fwd_logprobs_values_reward(batch)
+        finally:
+            iso.strict = strict_before
+        batch = self.compute_advantages_and_returns(batch)
+        self.train_critic_and_policy(batch)
+
+    def _publish_weights(self) -> None:
+        self.sync_weights()
+
     def train(self) -> None:
-        if self.policy is None:
+        if self.engine is None:
             self.build_models()
         self.source = AsyncPromptSource(self.dataset, self.cfg.trainer.seed)
-        self.sync_weights()
+        self._publish_weights()
         self.engine.wake_up()
         th = threading.Thread(target=self._generation_loop, daemon=True)
         th.start()
@@ -202,18 +222,8 @@ class FullyAsyncTrainer(RayPPOTrainer):
                 batch = self.convert_to_training_input(go, uids)
                 staleness = [self.stale.version - g["version"] for g in groups]
                 with self._engine_lock:             # scoring + update exclude engine steps: one flat buffer, one writer
-                    fresh = all(s == 0 for s in staleness)
-                    iso = self.cfg.trainer.isoexec
-                    strict_before = iso.strict
-                    if not fresh:
-                        iso.strict = False          # stale samples are off-policy by construction
-                    try:
-                        batch = self.fwd_logprobs_values_reward(batch)
-                    finally:
-                        iso.strict = strict_before
-                    batch = self.compute_advantages_and_returns(batch)
-                    self.train_critic_and_policy(batch)
-                    self.sync_weights()
+                    self._run_training(batch, all(s == 0 for s in staleness))
+                    self._publish_weights()
                     self.stale.bump_version()
                 for g in groups:
                     self.source.mark_consumed(g["uid"])
@@ -224,3 +234,65 @@ class FullyAsyncTrainer(RayPPOTrainer):
         finally:
             self._stop.set()
             th.join(timeout=30)
+
+
+class FullyAsyncTrainerSim(FullyAsyncTrainer):
+    """The fully-async loop with a SIMULATED trainer (reference: R/train/fully_async_trainer_sim.py:55-115): the engine,
+    the generation thread, the staleness budget and the pause around a weight update are real; the update itself is a
+    sleep of ``simulate_training_step_seconds`` and the weight sync a sleep of ``simulate_weight_sync_seconds`` during
+    which generation is paused. No policy worker, optimizer state, reference or critic model is built, so the
+    generation side can be measured at a model size whose training state would not fit. Evaluation, checkpoints and
+    exports are refused; nothing is resumed."""
+
+    def __init__(self, cfg, async_cfg: AsyncConfig | None = None, **kw):
+        super().__init__(cfg, async_cfg, **kw)
+        t = self.cfg.trainer
+        assert self.acfg.simulate_training, "FullyAsyncTrainerSim needs AsyncConfig.simulate_training=True"
+        assert t.eval_interval <= 0 and t.ckpt_interval <= 0 and t.hf_save_interval <= 0, \
+            "the simulated trainer has no model state: evaluation, checkpoints and exports must be off (it never resumes)"
+
+    def build_models(self) -> None:
+        """Engine side only: the model's parameters (random init or whatever the caller loads into them), the engine and
+        the generator."""
+        from ..engine.interface import NativeInferenceEngine
+        from ..engine.llm_engine import EngineConfig, LLMEngine
+        from ..models.config import get_config
+        from ..models.decoder import DecoderLM
+        from .generator import SkyRLGymGenerator
+        from .trainer import PromptDataLoader, SyntheticPromptDataset
+
+        t, g = self.cfg.trainer, self.cfg.generator
+        mcfg = get_config(t.policy.model, **t.policy.model_overrides)
+        model = DecoderLM(mcfg, self.ps, self.device, seed=t.policy.seed)
+        for p in model.parameters():
+            p.requires_grad_(False)
+        ie = g.inference_engine
+        ecfg = EngineConfig(max_num_seqs=ie.max_num_seqs, max_num_batched_tokens=ie.max_num_batched_tokens,
+                            num_kv_pages=ie.num_kv_pages, gpu_memory_utilization=ie.gpu_memory_utilization,
+                            seed=t.seed + 7919 * self.ps.dp_rank, enable_prefix_caching=ie.enable_prefix_caching,
+                            use_cuda_graph=not ie.enforce_eager,
+                            max_model_len=min(mcfg.max_position, t.max_prompt_length + g.sampling_params.max_generate_length + 1))
+        self.engine = LLMEngine(model, ecfg)
+        self.infer = NativeInferenceEngine(self.engine, self.tokenizer)
+        self.generator = SkyRLGymGenerator(self.infer, self.tokenizer, max_turns=g.max_turns, batched=g.batched,
+                                           env_config=self.cfg.environment.env_kwargs)
+        if self.dataset is None:
+            d = self.cfg.data
+            self.dataset = SyntheticPromptDataset(d.synthetic_prompts or t.train_batch_size * 4, d.synthetic_prompt_len,
+                                                  mcfg.vocab_size, t.seed, self.cfg.environment.env_class)
+        self.loader = PromptDataLoader(self.dataset, t.train_batch_size, t.seed)
+        self.sim_steps: list[dict] = []
+
+    def convert_to_training_input(self, go, uids):
+        return {"num_sequences": len(go["response_ids"]), "response_tokens": sum(len(r) for r in go["response_ids"])}
+
+    def _run_training(self, batch, fresh: bool) -> None:
+        time.sleep(self.acfg.simulate_training_step_seconds)
+        self.sim_steps.append({"step": self.global_step, "fresh": fresh, **batch})
+        self.all_metrics.update({"sim/step_seconds": self.acfg.simulate_training_step_seconds,
+                                 "sim/response_tokens": batch["response_tokens"]})
+
+    def _publish_weights(self) -> None:
+        """Called with the engine lock held (generation is paused), as a real weight update would be."""
+        if self.acfg.simulate_weight_sync_seconds > 0:
+            time.sleep(self.acfg.simulate_weight_sync_seconds)

@@ -185,3 +185,23 @@ def test_log_example_formats_reward_and_colours(tmp_path, capsys):
     tr = RayPPOTrainer(_cfg(str(tmp_path), 1, "trainer.log_example_interval=1"), device="cpu")
     tr.train()
     assert "Example:\n  Input: " in capsys.readouterr().out
+
+
+def test_simulated_async_trainer_builds_no_trainer_state_and_keeps_the_generation_dynamics(tmp_path):
+    from skyrl_isoexec_b200.train.fully_async_trainer import AsyncConfig, FullyAsyncTrainerSim
+
+    cfg = _cfg(str(tmp_path), 3)
+    with pytest.raises(AssertionError):
+        FullyAsyncTrainerSim(cfg, AsyncConfig(mini_batch_prompts=2), device="cpu")          # simulate_training is off
+    with pytest.raises(AssertionError):
+        FullyAsyncTrainerSim(_cfg(str(tmp_path), 3, "trainer.ckpt_interval=1"),
+                             AsyncConfig(mini_batch_prompts=2, simulate_training=True), device="cpu")
+    ac = AsyncConfig(max_staleness_steps=1, num_parallel_generation_workers=3, mini_batch_prompts=2, simulate_training=True,
+                     simulate_training_step_seconds=0.01, simulate_weight_sync_seconds=0.005)
+    tr = FullyAsyncTrainerSim(cfg, ac, device="cpu")
+    tr.train()
+    assert tr.policy is None and tr.global_step == 3 and len(tr.sim_steps) == 3
+    assert all(s["num_sequences"] == 4 and s["response_tokens"] == 16 for s in tr.sim_steps)   # 2 prompts x 2 samples x 4 tokens
+    assert tr.stale.version == 3 and 0 <= tr.all_metrics["async/staleness_max"] <= 2
+    assert tr.all_metrics["sim/response_tokens"] == 16
+    assert not any(p.requires_grad for p in tr.engine.model.parameters())
