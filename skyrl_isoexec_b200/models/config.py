@@ -32,6 +32,7 @@ class ModelConfig:
     router: str = "softmax"  # "softmax" | "sigmoid_bias"
     norm_topk_prob: bool = True
     shared_expert_ffn: int = 0
+    shared_expert_gate: bool = False   # the shared expert's output is scaled by sigmoid(x . w_gate), one scalar per token
     # --- hybrid GatedDeltaNet
     layer_types: tuple[str, ...] = ()  # per layer "attn" | "gdn"; empty = all attention
     gdn_k_heads: int = 0
@@ -140,6 +141,20 @@ PRESETS: dict[str, ModelConfig] = {
         num_layers=32, num_q_heads=16, num_kv_heads=4, head_dim=128, ffn_size=9216,
         layer_types=_hybrid_pattern(32), gdn_k_heads=16, gdn_v_heads=32, gdn_head_dim=128, attn_output_gate=True,
         zero_centered_norm=True, max_position=40960),
+    # the reference's own manifest model (ISO/models/qwen3_5.py:120-134): hybrid GDN + gated attention, 256 routed experts
+    # plus a gated shared expert. Its 256-wide attention heads have no instance in the attention kernels yet (64 and 128
+    # only), so on a GPU this preset builds and shards but does not run; the tiny variant below runs everywhere.
+    "qwen3.5-35b-a3b": ModelConfig(
+        name="qwen3.5-35b-a3b", architecture="Qwen3_5MoeForCausalLM", vocab_size=248320, hidden_size=2048, num_layers=40,
+        num_q_heads=16, num_kv_heads=2, head_dim=256, ffn_size=0, layer_types=_hybrid_pattern(40), gdn_k_heads=16,
+        gdn_v_heads=32, gdn_head_dim=128, attn_output_gate=True, zero_centered_norm=True, partial_rotary_factor=0.25,
+        num_experts=256, top_k=8, moe_ffn_size=512, shared_expert_ffn=512, shared_expert_gate=True, max_position=40960),
+    "tiny-hybrid-moe": ModelConfig(
+        name="tiny-hybrid-moe", architecture="Qwen3_5MoeForCausalLM", vocab_size=2048, hidden_size=256, num_layers=4,
+        num_q_heads=4, num_kv_heads=2, head_dim=64, ffn_size=0, layer_types=_hybrid_pattern(4), gdn_k_heads=2,
+        gdn_v_heads=4, gdn_head_dim=64, attn_output_gate=True, zero_centered_norm=True, partial_rotary_factor=0.25,
+        num_experts=8, top_k=2, moe_ffn_size=128, shared_expert_ffn=128, shared_expert_gate=True, dtype="float32",
+        max_position=512),
     # Llama-3 style dense decoder (the reference's tx model zoo, R/tx/models/llama3.py): no QK-norm, untied head
     "llama3-8b": ModelConfig(
         name="llama3-8b", architecture="LlamaForCausalLM", vocab_size=128256, hidden_size=4096, num_layers=32,

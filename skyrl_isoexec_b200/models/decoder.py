@@ -212,6 +212,8 @@ def build_param_specs(cfg: ModelConfig, ps: ParallelState, layer_range: range | 
                 add(p + "moe.shared.gate_up.weight", (2 * cfg.shared_expert_ffn, h), 0, std,
                     sections=(cfg.shared_expert_ffn, cfg.shared_expert_ffn))
                 add(p + "moe.shared.down.weight", (h, cfg.shared_expert_ffn), 1, out_std)
+                if cfg.shared_expert_gate:
+                    add(p + "moe.shared.gate.weight", (1, h), None, std)
         else:
             add(p + "mlp.gate_up.weight", (2 * cfg.ffn_size, h), 0, std, sections=(cfg.ffn_size, cfg.ffn_size))
             add(p + "mlp.down.weight", (h, cfg.ffn_size), 1, out_std)

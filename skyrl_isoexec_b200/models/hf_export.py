@@ -136,7 +136,8 @@ def to_hf_state_dict(model: DecoderLM) -> dict[str, torch.Tensor]:
                        "attn.o.weight": "self_attn.o_proj.weight", "attn.q_norm.weight": "self_attn.q_norm.weight",
                        "attn.k_norm.weight": "self_attn.k_norm.weight", "mlp.down.weight": "mlp.down_proj.weight",
                        "moe.router.weight": "mlp.gate.weight", "moe.router.expert_bias": "mlp.gate.e_score_correction_bias",
-                       "moe.shared.down.weight": _shared_prefix(cfg) + "down_proj.weight", **_MLA_NAMES}
+                       "moe.shared.down.weight": _shared_prefix(cfg) + "down_proj.weight",
+                       "moe.shared.gate.weight": "mlp.shared_expert_gate.weight", **_MLA_NAMES}
                 out[p + ren.get(rest, rest)] = t
     return out
 
@@ -214,7 +215,8 @@ def load_hf(model: DecoderLM, path: str) -> int:
                            "attn.o.weight": "self_attn.o_proj.weight", "attn.q_norm.weight": "self_attn.q_norm.weight",
                            "attn.k_norm.weight": "self_attn.k_norm.weight", "mlp.down.weight": "mlp.down_proj.weight",
                            "moe.router.weight": "mlp.gate.weight", "moe.router.expert_bias": "mlp.gate.e_score_correction_bias",
-                           "moe.shared.down.weight": _shared_prefix(cfg) + "down_proj.weight", **_MLA_NAMES}
+                           "moe.shared.down.weight": _shared_prefix(cfg) + "down_proj.weight",
+                       "moe.shared.gate.weight": "mlp.shared_expert_gate.weight", **_MLA_NAMES}
                     src = sd[p + ren.get(rest, rest)]
             spec = model.store.specs[name]
             if tuple(src.shape) != tuple(t.shape) and src.numel() != t.numel():

@@ -248,4 +248,11 @@ def moe_block(y: torch.Tensor, model, i: int) -> torch.Tensor:
 
         gu = F.linear(tp_ops.copy_to_tp(y, ps), model.p(pfx + "shared.gate_up.weight"))   # column-parallel: sum the input grads
         shared = tp_ops.row_parallel_linear(F.swiglu(gu), model.p(pfx + "shared.down.weight"), ps, cfg)
+        if cfg.shared_expert_gate:        # one scalar per token: sigmoid(y . w_gate), applied in fp32, one round
+            gl = F.linear(y, model.p(pfx + "shared.gate.weight"), out_f32=True).float()
+            if not gl.is_cuda:
+                # the CPU sigmoid rounds a vector lane and a scalar tail differently, so a [T, 1] tensor's values would depend
+                # on T; at full row width every element sits in a whole vector and a token's value is the same in any batch
+                gl = gl.expand(-1, shared.shape[-1]).contiguous()
+            shared = (shared.float() * torch.sigmoid(gl)).to(y.dtype)
     return combine_fixed_order(rows, pos, y.dtype, shared)

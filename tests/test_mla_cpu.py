@@ -120,3 +120,64 @@ def test_latent_attention_checkpoint_layout_round_trips(tmp_path, preset):
     assert hf_export.load_hf(m2, d) == len(m.store.order) and torch.equal(m2.store.flat, m.store.flat)
     c = json.load(open(d + "/config.json"))
     assert c["architectures"] == ["DeepseekV3ForCausalLM"] and c["kv_lora_rank"] == r and c["qk_rope_head_dim"] == dr
+
+
+def test_gemm_census_matches_the_manifest_model_and_the_parameter_inventory():
+    """The census of the 35B-A3B hybrid reproduces the reference manifest's widths (ISO/models/qwen3_5.py:120-155), and
+    for every preset each column / row / replicated site agrees with the shape of the parameter that serves it."""
+    from skyrl_isoexec_b200.models.census import census_table, gemm_census
+    from skyrl_isoexec_b200.models.config import PRESETS
+    from skyrl_isoexec_b200.models.decoder import build_param_specs
+    from skyrl_isoexec_b200.parallel.state import ParallelState
+
+    cfg = get_config("qwen3.5-35b-a3b")
+    by = {s.name: s for s in gemm_census(cfg, tp=1)}
+    assert (by["gdn.in_proj"].k, by["gdn.in_proj"].n, by["gdn.in_proj"].calls) == (2048, 12352, 30)
+    assert (by["attn.qkv"].n, by["attn.qkv"].calls) == (9216, 10)
+    assert (by["moe.router"].n, by["moe.router"].out_dtype, by["moe.router"].calls) == (256, "fp32", 40)
+    assert by["moe.shared.gate"].n == 1 and by["moe.shared.fc1"].n == 1024 and by["lm_head"].n == 248320
+    by2 = {s.name: s for s in gemm_census(cfg, tp=2, ep=8)}
+    assert by2["gdn.in_proj"].n == 6176 and by2["attn.qkv"].n == 4608 and by2["lm_head"].n == 124160
+    assert by2["moe.router"].n == 256 and by2["moe.experts.fc1"].count == 32 and by2["attn.o"].k == 16 * 256 // 2
+    assert "moe.experts.fc2" in census_table(cfg, 2, 8)
+    names = {"attn.qkv": "attn.qkv.weight", "attn.o": "attn.o.weight", "gdn.in_proj": "gdn.in_proj.weight",
+             "gdn.out_proj": "gdn.out_proj.weight", "moe.router": "moe.router.weight", "moe.shared.gate": "moe.shared.gate.weight",
+             "moe.shared.fc1": "moe.shared.gate_up.weight", "moe.shared.fc2": "moe.shared.down.weight", "mlp.fc1": "mlp.gate_up.weight",
+             "mlp.fc2": "mlp.down.weight", "attn.q_a": "attn.q_a.weight", "attn.q_b": "attn.q_b.weight", "attn.kv_a": "attn.kv_a.weight",
+             "attn.kv_b": "attn.kv_b.weight"}
+    for preset, c in PRESETS.items():
+        if c.vocab_size > 4096:
+            continue                                   # the tiny presets cover every family; skip building big inventories
+        specs = {s.name: s for s in build_param_specs(c, ParallelState.single())}
+        for site in gemm_census(c):
+            if site.grouped or site.name == "lm_head":
+                continue
+            layer = next(i for i in range(c.num_layers) if f"layers.{i}.{names[site.name]}" in specs)
+            assert specs[f"layers.{layer}.{names[site.name]}"].shape == (site.n, site.k), (preset, site)
+
+
+def test_gated_shared_expert_hybrid_moe_runs_a_full_rl_step_with_bitwise_rollout_logprobs(tmp_path):
+    from skyrl_isoexec_b200.train.entrypoints import main_base
+
+    cfg = get_config("tiny-hybrid-moe")
+    m = DecoderLM(cfg, seed=1)
+    assert m.p("layers.0.moe.shared.gate.weight").shape == (1, cfg.hidden_size)
+    ov = ["trainer.policy.model=tiny-hybrid-moe", "trainer.train_batch_size=2", "trainer.policy_mini_batch_size=2",
+          "generator.n_samples_per_prompt=2", "generator.sampling_params.max_generate_length=8",
+          "generator.sampling_params.ignore_eos=true", "data.synthetic_prompt_len=8", "data.synthetic_prompts=8",
+          "trainer.max_prompt_length=8", "generator.inference_engine.num_kv_pages=16", "trainer.num_steps=1",
+          f"trainer.ckpt_path={tmp_path}", "trainer.ckpt_interval=0", "trainer.logger=jsonl"]
+    tr = main_base.BasePPOExp(SkyRLTrainConfig.from_cli_overrides(ov)).get_trainer()
+    tr.build_models()
+    tr.sync_weights()
+    met = tr.train_step(next(iter(tr.loader)))
+    assert met["policy/rollout_train_logprob_bit_mismatches"] == 0 and met["policy/grad_norm"] > 0
+    g = tr.policy.model.p("layers.0.moe.shared.gate.weight")
+    d = str(tmp_path / "hf")
+    hf_export.save_hf(tr.policy.model, d)
+    from safetensors.torch import load_file
+
+    assert torch.equal(load_file(d + "/model.safetensors")["model.layers.0.mlp.shared_expert_gate.weight"], g.detach())
+    m2 = DecoderLM(cfg, seed=9)
+    hf_export.load_hf(m2, d)
+    assert torch.equal(m2.store.flat, tr.policy.model.store.flat)
