@@ -753,9 +753,33 @@ def test_example_configs_load_and_validate():
 
     root = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "examples")
     files = sorted(glob.glob(os.path.join(root, "*.yaml")))
-    assert len(files) >= 3
+    assert len(files) >= 8
     for f in files:
         cfg = SkyRLTrainConfig.from_file(f)
-        validate_cfg(cfg, 8 if "8gpu" in f else 1)
+        validate_cfg(cfg, 8 if ("8gpu" in f or "ep8" in f) else 2 if "tp2" in f else 1)
     big = SkyRLTrainConfig.from_file(os.path.join(root, "qwen3_8b_grpo_8gpu.yaml"))
     assert big.trainer.policy.model == "qwen3-8b" and big.trainer.policy.keep_last_layers == -1 and big.generator.n_samples_per_prompt == 8
+
+
+def test_runnable_examples_run(tmp_path):
+    """The two CPU-sized example configs that bring their own algorithm variant run their steps; the callbacks example
+    stops early and checkpoints on a new best."""
+    import importlib.util
+    import os
+
+    from skyrl_isoexec_b200.train.entrypoints import main_base
+
+    root = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "examples")
+    for name in ("ppo_gae_critic.yaml", "off_policy_tis_correction.yaml"):
+        cfg = SkyRLTrainConfig.from_file(os.path.join(root, name), [f"trainer.ckpt_path={tmp_path / name}", "trainer.logger=jsonl"])
+        tr = main_base.BasePPOExp(cfg).run()
+        assert tr.global_step == 2 and tr.all_metrics["policy/grad_norm"] >= 0
+    spec = importlib.util.spec_from_file_location("callbacks_early_stop", os.path.join(root, "callbacks_early_stop.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    tr = mod.main(str(tmp_path / "cb"), num_steps=12)
+    cb = tr.callbacks.callbacks[0]
+    assert 1 <= tr.global_step <= 12 and cb.best > float("-inf")
+    assert tr.global_step == 12 or cb.since >= cb.patience
+    assert any(d.startswith("global_step_") for d in os.listdir(tmp_path / "cb")), "a new best wrote a checkpoint"
+    assert "early_stop/best_reward" in tr.all_metrics
