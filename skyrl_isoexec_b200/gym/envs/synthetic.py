@@ -35,5 +35,28 @@ class TokenSumParityEnv(Env):
         return {"observations": [], "reward": r, "done": True, "metadata": {}}
 
 
+class EvenTokensTurnsEnv(Env):
+    """Several model turns without observations: the episode ends after ``max_turns`` turns and the outcome reward
+    (fraction of even token ids over ALL turns) arrives with the last one. A token-level stand-in for a multi-turn task."""
+
+    accepts_tokens = True
+
+    def __init__(self, env_config=None, extras=None):
+        self.max_turns = int((extras or {}).get("max_turns", 2))
+        self.toks: list[int] = []
+        self.turns = 0
+
+    def step(self, action):
+        self.toks += list(action)
+        self.turns += 1
+        done = self.turns >= self.max_turns
+        frac = (sum(1 for t in self.toks if t % 2 == 0) / len(self.toks)) if self.toks else 0.0
+        return {"observations": [], "reward": frac if done else 0.0, "done": done, "metadata": {}}
+
+    def get_metrics(self):
+        return {"turns": self.turns}
+
+
 register("even_tokens", lambda c, e: EvenTokensEnv(c, e))
+register("even_tokens_turns", lambda c, e: EvenTokensTurnsEnv(c, e))
 register("token_sum_parity", lambda c, e: TokenSumParityEnv(c, e))

@@ -89,6 +89,7 @@ class GeneratorConfig:
     use_conversation_multi_turn: bool = True
     zero_reward_on_non_stop: bool = False
     apply_overlong_filtering: bool = False
+    step_wise_trajectories: bool = False   # every model turn of a multi-turn trajectory is a training sample of its own
     rate_limit: dict = field(default_factory=dict)   # enabled / trajectories_per_second / max_concurrency (multi-turn trajectories)
 
 
@@ -290,6 +291,12 @@ def validate_cfg(cfg: SkyRLTrainConfig, world_size: int = 1) -> None:
     if world_size % mp:
         raise ValueError(f"world size {world_size} is not divisible by tp*pp*cp={mp}")
     dp = world_size // mp
+    if g.step_wise_trajectories:
+        if g.batched and g.max_turns == 1:
+            raise ValueError("generator.step_wise_trajectories needs the multi-turn agent loop (generator.batched=false)")
+        if t.algorithm.advantage_estimator not in ("grpo", "rloo", "maxrl"):
+            raise ValueError("step-wise trajectories take their advantage from the last step's outcome reward: "
+                             "advantage_estimator must be grpo, rloo or maxrl")
     if t.train_batch_size % t.policy_mini_batch_size:
         raise ValueError("train_batch_size must be a multiple of policy_mini_batch_size")
     if (t.policy_mini_batch_size * g.n_samples_per_prompt) % dp:

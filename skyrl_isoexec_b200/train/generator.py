@@ -40,6 +40,7 @@ class GeneratorOutput(TypedDict, total=False):
     trajectory_generation_times: list[float] | None
     rollout_expert_indices: Any
     is_last_step: list[bool] | None
+    step_source: list[int] | None
     env_metrics: list[dict] | None
 
 
@@ -79,10 +80,15 @@ def concatenate_generator_outputs(outs: list[GeneratorOutput]) -> GeneratorOutpu
 class SkyRLGymGenerator(GeneratorInterface):
     def __init__(self, engine: InferenceEngineInterface, tokenizer=None, max_turns: int = 1, batched: bool = True,
                  max_input_length: int = 1 << 30, env_config: dict | None = None, zero_reward_on_non_stop: bool = False,
-                 apply_overlong_filtering: bool = False, rate_limit=None):
+                 apply_overlong_filtering: bool = False, rate_limit=None, step_wise: bool = False):
         from ..utils.rate_limiter import create_rate_limiter
 
         self.rate_limiter = create_rate_limiter(rate_limit)      # brackets every multi-turn trajectory (start rate, in flight)
+        # step-wise trajectories (R/train/generators/skyrl_gym_generator.py:361-580): every model turn of a multi-turn
+        # trajectory becomes a training sample of its own (prompt = the whole context before the turn, response = the turn)
+        self.step_wise = step_wise
+        if step_wise and batched and max_turns == 1:
+            raise ValueError("step-wise trajectories need the multi-turn agent loop: set generator.batched=false")
         self.engine = engine
         self.tokenizer = tokenizer
         self.max_turns = max_turns
@@ -150,6 +156,7 @@ class SkyRLGymGenerator(GeneratorInterface):
         prompt_ids = self._encode_prompt(prompt)
         ctx = list(prompt_ids)
         resp, mask, lps, rew = [], [], [], []
+        steps: list[dict] = []
         stop = "stop"
         t0 = time.time()
         for _turn in range(self.max_turns):
@@ -161,6 +168,9 @@ class SkyRLGymGenerator(GeneratorInterface):
             rlp = (out.get("response_logprobs") or [[0.0] * len(rid)])[0]
             stop = out["stop_reasons"][0]
             step = env.step(rid if env.accepts_tokens else self._decode(rid))
+            if self.step_wise and rid:
+                steps.append({"prompt": list(ctx), "response": list(rid), "logprobs": list(rlp), "stop": stop,
+                              "rewards": [0.0] * (len(rid) - 1) + [float(step["reward"])]})
             resp += rid
             mask += [1] * len(rid)
             lps += rlp
@@ -180,7 +190,38 @@ class SkyRLGymGenerator(GeneratorInterface):
                 ctx += obs_ids
         metrics = env.get_metrics()
         env.close()
+        if self.step_wise:
+            return steps, time.time() - t0, metrics
         return prompt_ids, resp, rew, mask, stop, lps, time.time() - t0, metrics
+
+    def _flatten_steps(self, res, input_batch: GeneratorInput) -> GeneratorOutput:
+        """One row per model turn, the turns of a trajectory adjacent and in order; ``is_last_step`` marks a trajectory's
+        final turn and ``step_source`` gives the index of the trajectory (the row of the generator input) a step came from."""
+        keys = ("prompt_token_ids", "response_ids", "rewards", "loss_masks", "stop_reasons", "rollout_logprobs", "is_last_step",
+                "step_source", "trajectory_generation_times", "env_metrics")
+        out: GeneratorOutput = {k: [] for k in keys}
+        tids = input_batch.get("trajectory_ids")
+        out["trajectory_ids"] = [] if tids is not None else None
+        for i, (steps, secs, metrics) in enumerate(res):
+            for j, st in enumerate(steps):
+                out["prompt_token_ids"].append(st["prompt"])
+                out["response_ids"].append(st["response"])
+                out["rewards"].append(st["rewards"])
+                out["loss_masks"].append([1] * len(st["response"]))
+                out["stop_reasons"].append(st["stop"])
+                out["rollout_logprobs"].append(st["logprobs"])
+                out["is_last_step"].append(j == len(steps) - 1)
+                out["step_source"].append(i)
+                out["trajectory_generation_times"].append(secs)
+                out["env_metrics"].append(metrics)
+                if tids is not None:
+                    out["trajectory_ids"].append(tids[i])
+        out["rollout_expert_indices"] = None
+        last = [k for k, f in enumerate(out["is_last_step"]) if f]
+        out["rollout_metrics"] = get_rollout_metrics([out["response_ids"][k] for k in last], [out["rewards"][k] for k in last],
+                                                     [out["env_metrics"][k] for k in last])
+        out["rollout_metrics"]["generate/steps_per_trajectory"] = len(out["is_last_step"]) / max(1, len(last))
+        return out
 
     async def generate(self, input_batch: GeneratorInput) -> GeneratorOutput:
         n = len(input_batch["prompts"])
@@ -193,6 +234,8 @@ class SkyRLGymGenerator(GeneratorInterface):
                                              input_batch.get("sampling_params"))
 
         res = await asyncio.gather(*[one(i) for i in range(n)])
+        if self.step_wise:
+            return self._flatten_steps(res, input_batch)
         out: GeneratorOutput = {
             "prompt_token_ids": [r[0] for r in res], "response_ids": [r[1] for r in res], "rewards": [r[2] for r in res],
             "loss_masks": [r[3] for r in res], "stop_reasons": [r[4] for r in res], "rollout_logprobs": [r[5] for r in res],

@@ -178,7 +178,7 @@ class RayPPOTrainer:
                                            env_config=self.cfg.environment.env_kwargs,
                                            zero_reward_on_non_stop=g.zero_reward_on_non_stop,
                                            apply_overlong_filtering=g.apply_overlong_filtering,
-                                           rate_limit=g.rate_limit or None)
+                                           rate_limit=g.rate_limit or None, step_wise=g.step_wise_trajectories)
         if t.isoexec.enabled:
             self.adapter_trainer = ContractAdapter("trainer", model, self.rank, engine_tp=ie.tensor_parallel_size
                                                    if not ie.run_engines_locally else self.ps.tp)
@@ -244,6 +244,9 @@ class RayPPOTrainer:
         lens = rmask.sum(1)
         b.metadata = {"uids": list(uids), "response_length": R, "avg_response_length": float(lens.mean()),
                       "max_response_length": int(lens.max())}
+        if go.get("step_source") is not None:       # step-wise: one row per model turn; a row inherits its trajectory's uid
+            b.metadata["uids"] = [uids[i] for i in go["step_source"]]
+            b.metadata["is_last_step"] = list(go["is_last_step"])
         return b
 
     def _reuse_rollout_logprobs(self) -> bool:
@@ -303,11 +306,28 @@ class RayPPOTrainer:
 
     def compute_advantages_and_returns(self, batch: TrainingInputBatch) -> TrainingInputBatch:
         a = self.cfg.trainer.algorithm
-        adv, ret = alg.compute_advantages_and_returns(batch["rewards"], batch["response_mask"], batch.metadata["uids"],
-                                                      a.advantage_estimator, a, values=batch.get("values"))
+        last = batch.metadata.get("is_last_step")
+        if last is not None:
+            # step-wise (R/train/trainer.py:1179-1218): the advantage of a trajectory comes from its LAST step's reward,
+            # compared within the prompt's group, and is given to every response token of every step of that trajectory
+            is_last = torch.tensor(last, dtype=torch.bool)
+            assert bool(is_last[-1]), "the last row must close a trajectory"
+            uids = batch.metadata["uids"]
+            adv_l, ret_l = alg.compute_advantages_and_returns(
+                batch["rewards"][is_last], torch.ones_like(batch["response_mask"][is_last], dtype=torch.float32),
+                [u for u, f in zip(uids, last) if f], a.advantage_estimator, a, values=None)
+            traj = torch.cat([torch.zeros(1, dtype=torch.bool), is_last[:-1]]).long().cumsum(0)
+            assert int(traj[-1]) + 1 == adv_l.shape[0]
+            rm = batch["response_mask"].to(adv_l.dtype)
+            adv, ret = adv_l[traj] * rm, ret_l[traj] * rm
+        else:
+            adv, ret = alg.compute_advantages_and_returns(batch["rewards"], batch["response_mask"], batch.metadata["uids"],
+                                                          a.advantage_estimator, a, values=batch.get("values"))
         batch["advantages"], batch["returns"] = adv, ret
         m = batch["response_mask"]
         scores = batch["rewards"].sum(-1)
+        if last is not None:
+            scores = scores[torch.tensor(last, dtype=torch.bool)]
         self.all_metrics.update({"reward/avg_raw_reward": float(scores.mean()),
                                  "reward/avg_pass_rate": float((scores > 0).float().mean()),
                                  "policy/avg_advantage_abs": float((adv.abs() * m).sum() / m.sum().clamp(min=1))})

@@ -205,3 +205,47 @@ def test_simulated_async_trainer_builds_no_trainer_state_and_keeps_the_generatio
     assert tr.stale.version == 3 and 0 <= tr.all_metrics["async/staleness_max"] <= 2
     assert tr.all_metrics["sim/response_tokens"] == 16
     assert not any(p.requires_grad for p in tr.engine.model.parameters())
+
+
+def test_step_wise_trajectories_train_each_turn_with_the_trajectory_advantage(tmp_path):
+    import torch
+
+    from skyrl_isoexec_b200.train.config import validate_cfg
+
+    with pytest.raises(ValueError):
+        validate_cfg(_cfg(str(tmp_path), 1, "generator.step_wise_trajectories=true"))                     # batched single turn
+    with pytest.raises(ValueError):
+        validate_cfg(_cfg(str(tmp_path), 1, "generator.step_wise_trajectories=true", "generator.batched=false",
+                          "trainer.algorithm.advantage_estimator=gae"))
+    cfg = _cfg(str(tmp_path), 1, "generator.step_wise_trajectories=true", "generator.batched=false", "generator.max_turns=3",
+               "environment.env_class=even_tokens_turns", "generator.inference_engine.num_kv_pages=32", "trainer.max_prompt_length=24")
+    tr = RayPPOTrainer(cfg, device="cpu")
+    tr.build_models()
+    tr.sync_weights()
+    rows = next(iter(tr.loader))
+    gi, uids = tr.prepare_generator_input(rows)
+    tr.engine.wake_up()
+    go = tr.generate(gi)
+    tr.engine.sleep()
+    # 2 prompts x 2 samples = 4 trajectories of 3 turns: 12 rows, turns adjacent, the third of each closes the trajectory
+    assert len(go["response_ids"]) == 12 and go["is_last_step"] == [False, False, True] * 4
+    assert go["step_source"] == [0] * 3 + [1] * 3 + [2] * 3 + [3] * 3
+    for k in range(0, 12, 3):
+        p0, p1, p2 = (go["prompt_token_ids"][k + j] for j in range(3))
+        assert p1 == p0 + go["response_ids"][k] and p2 == p1 + go["response_ids"][k + 1], "a step's prompt is the whole context so far"
+        assert sum(go["rewards"][k]) == 0 and sum(go["rewards"][k + 1]) == 0          # the outcome reward arrives with the last turn
+    assert go["rollout_metrics"]["generate/steps_per_trajectory"] == 3.0
+    batch = tr.convert_to_training_input(go, uids)
+    assert batch.metadata["uids"] == [uids[i] for i in go["step_source"]] and batch.batch_size == 12
+    tr.all_metrics = {}
+    batch = tr.compute_advantages_and_returns(batch)
+    adv, rm = batch["advantages"], batch["response_mask"]
+    for k in range(0, 12, 3):
+        vals = [adv[k + j][rm[k + j].bool()] for j in range(3)]
+        assert all(torch.equal(v, vals[2][:1].expand_as(v)) for v in vals), "every turn carries its trajectory's one advantage"
+    # the group baseline is over trajectories (last steps), not over rows: two trajectories per prompt sum to zero
+    a_traj = torch.stack([adv[k + 2][0] for k in range(0, 12, 3)])
+    assert abs(float(a_traj[0] + a_traj[1])) < 1e-5 and abs(float(a_traj[2] + a_traj[3])) < 1e-5
+    # and the whole step runs through the trainer with the forward gate on
+    m = tr.train_step(next(iter(tr.loader)))
+    assert m["policy/rollout_train_logprob_bit_mismatches"] == 0 and m["policy/grad_norm"] > 0
