@@ -226,6 +226,13 @@ def rloo_advantage(token_level_rewards, response_mask, index, **kw):
     return adv, adv
 
 
+@register_advantage_estimator("no_op")
+def no_op_advantage(token_level_rewards, response_mask, index=None, **kw):
+    """The token-level rewards ARE the advantages (dense per-token signals such as a distillation reward)."""
+    adv = (token_level_rewards * response_mask).detach()
+    return adv, adv
+
+
 @register_advantage_estimator("maxrl")
 def maxrl_advantage(token_level_rewards, response_mask, index, epsilon=1e-6, **kw):
     """(score - group mean) / (group mean + eps)."""

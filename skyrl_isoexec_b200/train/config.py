@@ -35,6 +35,15 @@ class ParallelConfig:
 
 
 @dataclass
+class RefConfig:
+    """The frozen reference / teacher model. Empty ``model``: a copy of the policy's initial weights."""
+    model: str = ""                     # preset name; must share the policy's vocabulary
+    model_overrides: dict = field(default_factory=dict)
+    seed: int = 0                       # random init seed when no weights are given
+    hf_path: str = ""                   # directory with model.safetensors in the Hugging Face layout
+
+
+@dataclass
 class PolicyConfig:
     model: str = "tiny-qwen3"           # preset name or path of a saved config
     model_overrides: dict = field(default_factory=dict)
@@ -127,6 +136,7 @@ class IsoExecConfig:
 class TrainerConfig:
     placement: PlacementConfig = field(default_factory=PlacementConfig)
     policy: PolicyConfig = field(default_factory=PolicyConfig)
+    ref: RefConfig = field(default_factory=RefConfig)
     algorithm: AlgorithmConfig = field(default_factory=AlgorithmConfig)
     isoexec: IsoExecConfig = field(default_factory=IsoExecConfig)
     strategy: str = "native"

@@ -160,7 +160,17 @@ class RayPPOTrainer:
         if algo.use_kl_loss or algo.use_kl_in_reward:
             from .ref_critic import RefWorker
 
-            self.ref = RefWorker.from_policy(model, wcfg)
+            if t.ref.model:           # a different frozen model (a teacher): same vocabulary, its own weights
+                from ..models import hf_export
+
+                rcfg = get_config(t.ref.model, **t.ref.model_overrides)
+                assert rcfg.vocab_size == mcfg.vocab_size, "the reference / teacher model must share the policy's vocabulary"
+                rmodel = DecoderLM(rcfg, self.ps, self.device, seed=t.ref.seed)
+                if t.ref.hf_path:
+                    hf_export.load_hf(rmodel, t.ref.hf_path)
+                self.ref = RefWorker(rmodel, wcfg)
+            else:
+                self.ref = RefWorker.from_policy(model, wcfg)
         if algo.advantage_estimator == "gae":
             from .ref_critic import CriticWorker
 
@@ -283,11 +293,8 @@ class RayPPOTrainer:
         if getattr(self, "ref", None) is not None:
             batch["base_action_log_probs"] = self.ref.forward(batch)
             if a.use_kl_in_reward:
-                kl = alg.compute_approx_kl(lp, batch["base_action_log_probs"], mask, a.kl_estimator_type) * mask
-                batch["rewards"] = batch["rewards"] - self.kl_ctrl.value * kl
-                cur = float(kl.sum() / n)
-                self.kl_ctrl.update(cur, int(mask.shape[0]))
-                self.all_metrics.update({"reward/kl": cur, "reward/kl_coef": self.kl_ctrl.value})
+                batch["action_log_probs"] = lp
+                batch = self.apply_reward_kl_penalty(batch)
         if getattr(self, "critic", None) is not None:
             batch["values"] = self.critic.forward(batch) * mask
         iso = self.cfg.trainer.isoexec
@@ -302,6 +309,18 @@ class RayPPOTrainer:
                 if iso.strict:
                     raise ForwardGateError(msg)
                 print("[warn] " + msg)
+        return batch
+
+    def apply_reward_kl_penalty(self, batch: TrainingInputBatch) -> TrainingInputBatch:
+        """Subtract ``kl_coef * KL(policy || reference)`` per token from the rewards (R/train/trainer.py
+        ``apply_reward_kl_penalty``); a seam that subclasses replace (on-policy distillation makes it THE reward)."""
+        a = self.cfg.trainer.algorithm
+        lp, mask = batch["action_log_probs"], batch["response_mask"]
+        kl = alg.compute_approx_kl(lp, batch["base_action_log_probs"], mask, a.kl_estimator_type) * mask
+        batch["rewards"] = batch["rewards"] - self.kl_ctrl.value * kl
+        cur = float(kl.sum() / mask.sum().clamp(min=1))
+        self.kl_ctrl.update(cur, int(mask.shape[0]))
+        self.all_metrics.update({"reward/kl": cur, "reward/kl_coef": self.kl_ctrl.value})
         return batch
 
     def compute_advantages_and_returns(self, batch: TrainingInputBatch) -> TrainingInputBatch:

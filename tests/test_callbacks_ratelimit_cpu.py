@@ -249,3 +249,40 @@ def test_step_wise_trajectories_train_each_turn_with_the_trajectory_advantage(tm
     # and the whole step runs through the trainer with the forward gate on
     m = tr.train_step(next(iter(tr.loader)))
     assert m["policy/rollout_train_logprob_bit_mismatches"] == 0 and m["policy/grad_norm"] > 0
+
+
+def test_on_policy_distillation_rewards_are_the_teacher_gap_and_pull_the_student_toward_the_teacher(tmp_path):
+    import torch
+
+    from skyrl_isoexec_b200.train.distill import OnPolicyDistillationTrainer
+
+    cfg = _cfg(str(tmp_path), 3, "trainer.ref.model=tiny-qwen3", "trainer.ref.seed=7", "trainer.policy.optimizer_config.lr=1e-3",
+               "trainer.train_batch_size=4", "trainer.policy_mini_batch_size=4", "generator.sampling_params.max_generate_length=8",
+               "data.synthetic_prompts=64")
+    tr = OnPolicyDistillationTrainer(cfg, device="cpu")
+    assert cfg.trainer.algorithm.advantage_estimator == "no_op" and cfg.trainer.algorithm.use_kl_in_reward
+    tr.build_models()
+    assert tr.ref is not None and not torch.equal(tr.ref.model.store.flat, tr.policy.model.store.flat), "the teacher has its own weights"
+    tr.sync_weights()
+    rows = next(iter(tr.loader))
+    gi, uids = tr.prepare_generator_input(rows)
+    tr.engine.wake_up()
+    go = tr.generate(gi)
+    tr.engine.sleep()
+    tr.all_metrics = {}
+    batch = tr.fwd_logprobs_values_reward(tr.convert_to_training_input(go, uids))
+    want = -(batch["action_log_probs"] - batch["base_action_log_probs"]) * batch["loss_mask"]
+    assert torch.equal(batch["rewards"], want) and float(want.abs().sum()) > 0
+    batch = tr.compute_advantages_and_returns(batch)
+    assert torch.equal(batch["advantages"], want * batch["response_mask"]), "no_op: the dense rewards are the advantages"
+    assert tr.all_metrics["distill/reverse_kl"] > 0
+    # one update on this batch moves the student the right way: tokens the teacher likes more than the student (positive
+    # advantage) gain probability, the others lose it -- to first order sum(adv * delta logprob) > 0
+    before, adv, mask = batch["action_log_probs"].clone(), batch["advantages"].clone(), batch["response_mask"]
+    tr.train_critic_and_policy(batch)
+    after = tr.policy.forward(batch)
+    assert float((adv * (after - before) * mask).sum()) > 0
+    tr.sync_weights()
+    tr.train()
+    assert tr.global_step == 3 and tr.all_metrics["policy/rollout_train_logprob_bit_mismatches"] == 0
+    assert tr.all_metrics["distill/reverse_kl"] == tr.all_metrics["distill/reverse_kl"]          # finite, logged every step
