@@ -82,3 +82,66 @@ def test_rlm_env_repl_over_a_long_context():
     assert "FINAL_VAR failed" in e.step("FINAL_VAR(nope)")["observations"][0]["content"]
     out = e.step("no code here")
     assert out["done"] and out["reward"] == 0.0 and out["metadata"]["how"] == "turn limit"
+
+
+def test_llm_judge_env_parses_scores_retries_and_counts_broken_replies():
+    import http.server
+    import json
+    import threading
+
+    import pytest
+
+    from skyrl_isoexec_b200 import gym
+    from skyrl_isoexec_b200.gym.envs.llm_judge import parse_judge_reply
+
+    assert parse_judge_reply("thinking...\n### Final Score: 1") == 1.0 and parse_judge_reply("### Final Score: 0.0\n") == 0.0
+    assert parse_judge_reply("1") == 1.0 and parse_judge_reply("maybe") is None
+    assert parse_judge_reply("### Final Score: 0\nsecond thoughts\n### Final Score: 1") == 1.0      # the last verdict counts
+    ex = {"reward_spec": {"ground_truth": "#### 42"}}
+    with pytest.raises(ValueError):
+        gym.make("llm_judge", {}, ex)
+    with pytest.raises(ValueError):
+        gym.make("llm_judge", {"judge_fn": lambda m: "1"}, {})
+    seen = []
+
+    def judge(messages):
+        seen.append(messages[0]["content"])
+        return "The numbers agree.\n### Final Score: 1" if "#### 42" in messages[0]["content"].split("PREDICTED SOLUTION:")[1] else "### Final Score: 0"
+
+    env = gym.make("llm_judge", {"judge_fn": judge}, ex)
+    out = env.step("so the answer is\n#### 42")
+    assert out["reward"] == 1.0 and out["done"] and "GOLD SOLUTION:\n#### 42" in seen[0]
+    assert gym.make("llm_judge", {"judge_fn": judge}, ex).step("#### 41")["reward"] == 0.0
+    bad = gym.make("llm_judge", {"judge_fn": lambda m: "no idea"}, ex)
+    assert bad.step("x")["reward"] == 0.0 and bad.get_metrics()["judge_unparsed"] == 1
+    calls = []
+
+    def flaky(messages):
+        calls.append(1)
+        if len(calls) < 3:
+            raise ConnectionError("judge down")
+        return "1"
+
+    fl = gym.make("llm_judge", {"judge_fn": flaky, "retries": 2}, ex)
+    assert fl.step("x")["reward"] == 1.0 and fl.get_metrics() == {"judge_calls": 3, "judge_unparsed": 0, "judge_errors": 2}
+
+    class H(http.server.BaseHTTPRequestHandler):          # an OpenAI-compatible grader endpoint
+        def do_POST(self):
+            body = json.loads(self.rfile.read(int(self.headers["Content-Length"])))
+            ok = self.path == "/v1/chat/completions" and body["messages"][0]["role"] == "user" and body["temperature"] == 0.0
+            data = json.dumps({"choices": [{"message": {"role": "assistant", "content": f"### Final Score: {int(ok)}"}}]}).encode()
+            self.send_response(200)
+            self.send_header("Content-Length", str(len(data)))
+            self.end_headers()
+            self.wfile.write(data)
+
+        def log_message(self, *a):
+            pass
+
+    srv = http.server.ThreadingHTTPServer(("127.0.0.1", 0), H)
+    threading.Thread(target=srv.serve_forever, daemon=True).start()
+    try:
+        env = gym.make("llm_judge", {"base_url": f"http://127.0.0.1:{srv.server_address[1]}"}, ex)
+        assert env.step("#### 42")["reward"] == 1.0
+    finally:
+        srv.shutdown()
