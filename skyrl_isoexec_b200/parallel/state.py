@@ -113,10 +113,14 @@ class ParallelState:
         return st
 
 
-def init_distributed(backend: str | None = None, timeout_s: int = 600) -> tuple[int, int, int]:
+def init_distributed(backend: str | None = None, timeout_s: int | None = None) -> tuple[int, int, int]:
     """Initialise the default process group from the torchrun environment. Returns
-    (rank, world_size, local_rank). A no-op for a single process without RANK set."""
+    (rank, world_size, local_rank). A no-op for a single process without RANK set. The collective timeout is
+    ``timeout_s``, else ``SKYRL_WORKER_NCCL_TIMEOUT_IN_S`` (reference: R/env_vars.py:22), else 600 s."""
     import datetime
+
+    if timeout_s is None:
+        timeout_s = int(os.environ.get("SKYRL_WORKER_NCCL_TIMEOUT_IN_S", "600"))
 
     if "RANK" not in os.environ or int(os.environ.get("WORLD_SIZE", "1")) == 1:
         return 0, 1, int(os.environ.get("LOCAL_RANK", "0"))

@@ -783,3 +783,28 @@ def test_runnable_examples_run(tmp_path):
     assert tr.global_step == 12 or cb.since >= cb.patience
     assert any(d.startswith("global_step_") for d in os.listdir(tmp_path / "cb")), "a new best wrote a checkpoint"
     assert "early_stop/best_reward" in tr.all_metrics
+
+
+def test_process_group_timeout_follows_the_environment_flag(monkeypatch):
+    """``init_distributed`` takes its collective timeout from SKYRL_WORKER_NCCL_TIMEOUT_IN_S unless told otherwise."""
+    import datetime
+
+    import torch.distributed as dist
+
+    from skyrl_isoexec_b200.parallel import state
+
+    seen = {}
+    monkeypatch.setattr(dist, "is_initialized", lambda: False)
+    monkeypatch.setattr(dist, "init_process_group", lambda **kw: seen.update(kw))
+    for k, v in (("RANK", "1"), ("WORLD_SIZE", "2"), ("LOCAL_RANK", "1")):
+        monkeypatch.setenv(k, v)
+    monkeypatch.delenv("SKYRL_WORKER_NCCL_TIMEOUT_IN_S", raising=False)
+    assert state.init_distributed(backend="gloo") == (1, 2, 1) and seen["timeout"] == datetime.timedelta(seconds=600)
+    monkeypatch.setenv("SKYRL_WORKER_NCCL_TIMEOUT_IN_S", "45")
+    state.init_distributed(backend="gloo")
+    assert seen["timeout"] == datetime.timedelta(seconds=45)
+    state.init_distributed(backend="gloo", timeout_s=7)
+    assert seen["timeout"] == datetime.timedelta(seconds=7)
+    monkeypatch.setenv("WORLD_SIZE", "1")
+    seen.clear()
+    assert state.init_distributed() == (0, 1, 1) and not seen
