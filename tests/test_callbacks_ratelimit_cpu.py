@@ -286,3 +286,52 @@ def test_on_policy_distillation_rewards_are_the_teacher_gap_and_pull_the_student
     tr.train()
     assert tr.global_step == 3 and tr.all_metrics["policy/rollout_train_logprob_bit_mismatches"] == 0
     assert tr.all_metrics["distill/reverse_kl"] == tr.all_metrics["distill/reverse_kl"]          # finite, logged every step
+
+
+def test_tracking_backends_against_fake_clients(tmp_path, monkeypatch, capsys):
+    """Every tracker backend, driven through stand-ins for the client packages (none of which is installed here): each gets
+    the run's identity at construction, scalar metrics per step and a closing call; unknown names and missing packages fail
+    at construction, not at the first log call; a crash report reaches every backend."""
+    import sys
+    import types
+
+    from skyrl_isoexec_b200.utils.tracking import Tracking
+
+    calls = []
+
+    def fake(name, **fns):
+        m = types.ModuleType(name)
+        for k, f in fns.items():
+            setattr(m, k, f)
+        monkeypatch.setitem(sys.modules, name, m)
+
+    fake("wandb", init=lambda **kw: calls.append(("wandb.init", kw["project"], kw["name"])),
+         log=lambda d, step: calls.append(("wandb.log", dict(d), step)), finish=lambda: calls.append(("wandb.finish",)))
+    fake("mlflow", set_experiment=lambda p: calls.append(("mlflow.exp", p)), start_run=lambda run_name: calls.append(("mlflow.run", run_name)),
+         log_params=lambda p: calls.append(("mlflow.params", p)), log_metrics=lambda d, step: calls.append(("mlflow.log", dict(d), step)),
+         end_run=lambda: calls.append(("mlflow.end",)))
+    fake("swanlab", init=lambda **kw: calls.append(("swanlab.init", kw["experiment_name"])),
+         log=lambda d, step: calls.append(("swanlab.log", dict(d), step)), finish=lambda: calls.append(("swanlab.finish",)))
+    tr = Tracking("proj", "run1", "['wandb', 'mlflow', 'swanlab', 'console', 'jsonl']", config={"lr": 1e-6, "nested": {"a": 1}},
+                  log_dir=str(tmp_path))
+    assert list(tr.loggers) == ["wandb", "mlflow", "swanlab", "console", "jsonl"]
+    tr.log({"loss": 0.5, "note": "text", "n": 3}, step=7)
+    assert ("wandb.log", {"loss": 0.5, "note": "text", "n": 3}, 7) in calls
+    assert ("mlflow.log", {"loss": 0.5, "n": 3.0}, 7) in calls and ("swanlab.log", {"loss": 0.5, "n": 3}, 7) in calls   # scalars only
+    assert ("mlflow.params", {"lr": "1e-06", "nested": "{'a': 1}"}) in calls
+    assert "[step 7]" in capsys.readouterr().out
+    try:
+        raise RuntimeError("boom")
+    except RuntimeError as e:
+        tr.log_exception(e, step=8)
+    crash = [c for c in calls if c[0] == "wandb.log" and "crash/traceback" in c[1]]
+    assert crash and "RuntimeError: boom" in crash[0][1]["crash/traceback"] and crash[0][1]["crash/type"] == "RuntimeError"
+    tr.finish()
+    assert all(c in calls for c in (("wandb.finish",), ("mlflow.end",), ("swanlab.finish",)))
+    lines = [json.loads(ln) for ln in open(tmp_path / "proj" / "run1.jsonl")]
+    assert lines[0]["step"] == 7 and lines[0]["loss"] == 0.5 and lines[1]["crash/type"] == "RuntimeError"
+    with pytest.raises(ValueError):
+        Tracking("p", "r", "console,comet")
+    monkeypatch.setitem(sys.modules, "wandb", None)                          # "import wandb" now fails
+    with pytest.raises(ImportError):
+        Tracking("p", "r", "wandb")
