@@ -28,7 +28,12 @@ LOSS_FNS = {"cross_entropy": "cross_entropy", "importance_sampling": "importance
 
 class SkyRLTrainBackend:
     def __init__(self, base_model: str = "tiny-qwen3", model_overrides: dict | None = None, device: str | None = None,
-                 lr: float = 1e-5, seed: int = 0, num_kv_pages: int = 64):
+                 lr: float = 1e-5, seed: int = 0, num_kv_pages: int = 64, external_inference_url: str | None = None,
+                 external_inference_model: str = "policy", external_timeout_s: float = 600.0):
+        # sampling can be served by a separate OpenAI-compatible server (reference: R/tinker/extra/external_inference.py):
+        # token-id prompts to POST {url}/v1/completions, sampled ids and logprobs back; training stays in this process
+        self.external_url = external_inference_url.rstrip("/") if external_inference_url else None
+        self.external_model, self.external_timeout_s = external_inference_model, external_timeout_s
         dev = device or ("cuda" if torch.cuda.is_available() else "cpu")
         self.cfg = get_config(base_model, **(model_overrides or {}))
         self.model = DecoderLM(self.cfg, device=dev, seed=seed)
@@ -36,6 +41,31 @@ class SkyRLTrainBackend:
         self.worker = PolicyWorker(self.model, WorkerConfig(optimizer=OptimizerConfig(lr=lr, num_warmup_steps=0)), self.algo)
         self.engine = LLMEngine(self.model, EngineConfig(max_num_seqs=64, num_kv_pages=num_kv_pages, seed=seed + 1))
         self.step_count = 0
+
+    def _sample_external(self, prompt_ids: list[int], sp, n: int) -> dict:
+        import json
+        import urllib.request
+
+        body = {"model": self.external_model, "prompt": prompt_ids, "n": n, "max_tokens": sp.max_generate_length,
+                "temperature": sp.temperature, "top_p": sp.top_p, "logprobs": 1}
+        if sp.top_k and sp.top_k > 0:
+            body["top_k"] = sp.top_k
+        if sp.stop_token_ids:
+            body["stop_token_ids"] = list(sp.stop_token_ids)
+        if sp.ignore_eos:
+            body["ignore_eos"] = True
+        req = urllib.request.Request(self.external_url + "/v1/completions", data=json.dumps(body).encode(),
+                                     headers={"Content-Type": "application/json"})
+        with urllib.request.urlopen(req, timeout=self.external_timeout_s) as r:
+            out = json.loads(r.read())
+        seqs = []
+        for c in out["choices"]:
+            if "token_ids" not in c:
+                raise RuntimeError("the external server's completion carries no token_ids: training needs the sampled ids")
+            lps = (c.get("logprobs") or {}).get("token_logprobs") or [0.0] * len(c["token_ids"])
+            seqs.append({"tokens": list(c["token_ids"]), "logprobs": list(lps),
+                         "stop_reason": "length" if c.get("finish_reason") == "length" else "stop"})
+        return {"sequences": seqs}
 
     def _batch(self, data: list[dict]) -> TrainingInputBatch:
         seq, att, rmask = build_sequences([d["prompt_ids"] for d in data], [d["response_ids"] for d in data])
@@ -80,6 +110,8 @@ class SkyRLTrainBackend:
         if kind == "sample":
             sp = SamplingParams.from_dict(req.get("sampling_params"))
             n = int(req.get("num_samples", 1))
+            if self.external_url:
+                return self._sample_external(list(req["prompt_ids"]), sp, n)
             if self.engine.asleep:
                 self.engine.wake_up()
             outs = self.engine.generate([list(req["prompt_ids"])] * n, sp)

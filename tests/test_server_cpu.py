@@ -94,3 +94,25 @@ def test_pause_abort_ends_running_requests_and_keep_resumes():
         assert len(out["response_ids"][0]) == 2
     finally:
         srv.shutdown()
+
+
+def test_tinker_backend_samples_through_an_external_server_and_trains_on_the_result():
+    """The training backend forwards ``sample`` to an OpenAI-compatible server (here: this framework's own, holding the
+    same weights) and gets back ids and logprobs that its own forward reproduces bit for bit."""
+    from skyrl_isoexec_b200.tinker.backend import SkyRLTrainBackend
+
+    srv = InferenceServer(_engine(seed=0)).start()
+    try:
+        be = SkyRLTrainBackend("tiny-qwen3", device="cpu", seed=0, external_inference_url=srv.url + "/", lr=1e-3)
+        assert torch.equal(be.model.store.flat, srv.llm.model.store.flat), "same preset and seed: same weights on both sides"
+        prompt = list(range(5, 17))
+        out = be.handle({"type": "sample", "prompt_ids": prompt, "num_samples": 3,
+                         "sampling_params": {"max_generate_length": 6, "ignore_eos": True, "temperature": 1.0}})
+        seqs = out["sequences"]
+        assert len(seqs) == 3 and all(len(s["tokens"]) == 6 == len(s["logprobs"]) and s["stop_reason"] == "length" for s in seqs)
+        data = [{"prompt_ids": prompt, "response_ids": s["tokens"], "advantages": [1.0] * 6, "logprobs": s["logprobs"]} for s in seqs]
+        fwd = be.handle({"type": "forward", "data": data, "loss_fn": "importance_sampling"})
+        for got, s in zip(fwd["logprobs"], seqs):
+            assert got == s["logprobs"], "the external engine's logprobs are the trainer's, bit for bit"
+    finally:
+        srv.shutdown()
