@@ -31,6 +31,17 @@ def evaluate(generator, rows: list[dict], sampling_params: dict, n_samples: int 
                               "sampling_params": sampling_params, "trajectory_ids": None, "batch_metadata": {"eval": True}}
         go = asyncio.run(generator.generate(gi))
         uids = [r["uid"] for r in chunk for _ in range(n_samples)]
+        if go.get("step_source") is not None:
+            # step-wise output (one row per model turn; R/train/evaluate.py ``evaluate_step_wise``): a trajectory is scored by
+            # its LAST step's reward, and its length is the sum over its turns
+            total = defaultdict(int)
+            for src, resp in zip(go["step_source"], go["response_ids"]):
+                total[src] += len(resp)
+            for src, rew, last in zip(go["step_source"], go["rewards"], go["is_last_step"]):
+                if last:
+                    by_uid[uids[src]].append(float(sum(rew)) if isinstance(rew, (list, tuple)) else float(rew))
+                    lens.append(total[src])
+            continue
         for uid, rew, resp in zip(uids, go["rewards"], go["response_ids"]):
             by_uid[uid].append(float(sum(rew)) if isinstance(rew, (list, tuple)) else float(rew))
             lens.append(len(resp))

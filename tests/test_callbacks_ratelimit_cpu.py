@@ -218,7 +218,8 @@ def test_step_wise_trajectories_train_each_turn_with_the_trajectory_advantage(tm
         validate_cfg(_cfg(str(tmp_path), 1, "generator.step_wise_trajectories=true", "generator.batched=false",
                           "trainer.algorithm.advantage_estimator=gae"))
     cfg = _cfg(str(tmp_path), 1, "generator.step_wise_trajectories=true", "generator.batched=false", "generator.max_turns=3",
-               "environment.env_class=even_tokens_turns", "generator.inference_engine.num_kv_pages=32", "trainer.max_prompt_length=24")
+               "environment.env_class=even_tokens_turns", "generator.inference_engine.num_kv_pages=32", "trainer.max_prompt_length=24",
+               "generator.eval_n_samples_per_prompt=2", "generator.eval_sampling_params.temperature=1.0")
     tr = RayPPOTrainer(cfg, device="cpu")
     tr.build_models()
     tr.sync_weights()
@@ -249,6 +250,9 @@ def test_step_wise_trajectories_train_each_turn_with_the_trajectory_advantage(tm
     # and the whole step runs through the trainer with the forward gate on
     m = tr.train_step(next(iter(tr.loader)))
     assert m["policy/rollout_train_logprob_bit_mismatches"] == 0 and m["policy/grad_norm"] > 0
+    # evaluation scores TRAJECTORIES (last steps), not rows: 2 prompts x 2 samples, each 3 turns of 4 tokens
+    ev = tr.eval()
+    assert ev["eval/num_prompts"] == 2 and ev["eval/avg_response_length"] == 12.0 and 0.0 <= ev["eval/avg_reward"] <= 1.0
 
 
 def test_on_policy_distillation_rewards_are_the_teacher_gap_and_pull_the_student_toward_the_teacher(tmp_path):
