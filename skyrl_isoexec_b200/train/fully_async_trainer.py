@@ -207,6 +207,7 @@ class FullyAsyncTrainer(RayPPOTrainer):
         th = threading.Thread(target=self._generation_loop, daemon=True)
         th.start()
         n_steps = self.cfg.trainer.num_steps if self.cfg.trainer.num_steps > 0 else 1
+        self._fire("on_train_start")
         try:
             for _ in range(n_steps):
                 t0 = time.perf_counter()
@@ -229,8 +230,14 @@ class FullyAsyncTrainer(RayPPOTrainer):
                     self.source.mark_consumed(g["uid"])
                 self.all_metrics.update({"async/staleness_max": max(staleness), "async/staleness_mean": sum(staleness) / len(staleness),
                                          "async/buffered_groups": len(self.groups), "timing/step": time.perf_counter() - t0})
+                self._fire("on_step_end", metrics=dict(self.all_metrics))
+                self._fire("on_log", logs=self.all_metrics)
                 if self.tracker is not None:
                     self.tracker.log(self.all_metrics, self.global_step)
+                self.control.reset()
+                if self.control.should_stop:
+                    break
+            self._fire("on_train_end")
         finally:
             self._stop.set()
             th.join(timeout=30)

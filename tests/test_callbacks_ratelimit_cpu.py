@@ -206,6 +206,26 @@ def test_simulated_async_trainer_builds_no_trainer_state_and_keeps_the_generatio
     assert tr.all_metrics["sim/response_tokens"] == 16
     assert not any(p.requires_grad for p in tr.engine.model.parameters())
 
+    class StopAfterTwo(TrainingCallback):
+        seen = []
+
+        def on_train_start(self, trainer, ci, control):
+            self.seen.append("start")
+
+        def on_step_end(self, trainer, ci, control):
+            self.seen.append(ci.global_step)
+            control.should_stop = ci.global_step >= 2
+
+        def on_log(self, trainer, ci, control):
+            ci.logs["custom/async"] = 1.0
+
+        def on_train_end(self, trainer, ci, control):
+            self.seen.append("end")
+
+    tr = FullyAsyncTrainerSim(_cfg(str(tmp_path), 5), ac, device="cpu", callbacks=[StopAfterTwo()])
+    tr.train()
+    assert StopAfterTwo.seen == ["start", 1, 2, "end"] and tr.global_step == 2 and tr.all_metrics["custom/async"] == 1.0
+
 
 def test_step_wise_trajectories_train_each_turn_with_the_trajectory_advantage(tmp_path):
     import torch
