@@ -1,0 +1,172 @@
+"""Small, self-terminating kernel workloads for ncu captures (one kernel family per mode).
+
+    python skyrl_isoexec_b200/benchmarks/profile_kernels.py attn_decode | attn_prefill | gemm_large | gemm_decode | logprob | rmsnorm |
+                                   glu_decode | moe_grouped | rmsnorm_decode | sampler | rmsnorm_bwd | attn_bwd | train_small
+
+Each mode allocates well under 1 GB, launches the kernel a handful of times and exits.
+"""
+import math
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
+import torch  # noqa: E402
+
+from skyrl_isoexec_b200.ops import _native, functional as F  # noqa: E402
+
+
+def main(mode: str = "attn_decode") -> None:
+    dev = "cuda"
+    _native.lib().ix_init()
+    torch.manual_seed(0)
+    if mode in ("attn_decode", "attn_prefill"):
+        Hq, Hkv, D = 32, 8, 128
+        if mode == "attn_decode":
+            B, kv_len = 64, 1536
+            npg = (kv_len + 127) // 128
+            kc = torch.randn(B * npg * 128, Hkv, D, device=dev).bfloat16()
+            vc = torch.randn_like(kc)
+            q = torch.randn(B, Hq, D, device=dev).bfloat16()
+            bt = torch.arange(B * npg, dtype=torch.int32, device=dev).view(B, npg)
+            items = torch.tensor([[i, 1, kv_len - 1, kv_len, i, 0, 0, 0] for i in range(B)], dtype=torch.int32, device=dev)
+            meta = F.AttnMeta(items, bt)
+        else:
+            lens = [2560, 2560, 2560, 512]
+            T = sum(lens)
+            q = torch.randn(T, Hq, D, device=dev).bfloat16()
+            kc = torch.randn(T, Hkv, D, device=dev).bfloat16()
+            vc = torch.randn_like(kc)
+            meta = F.AttnMeta.packed(lens, Hq, Hkv, dev)
+        for _ in range(4):
+            F.attention_fwd(q, kc, vc, meta, 1 / math.sqrt(D))
+    elif mode in ("gemm_large", "gemm_decode"):
+        M, N, K = (8192, 4096, 4096) if mode == "gemm_large" else (64, 24576, 4096)
+        x = torch.randn(M, K, device=dev).bfloat16()
+        w = (torch.randn(N, K, device=dev) * 0.02).bfloat16()
+        for _ in range(4):
+            F.gemm_nt(x, w)
+    elif mode == "logprob":
+        V = 151936
+        lg = torch.randn(1024, V, device=dev).bfloat16()
+        tg = torch.randint(0, V, (1024,), device=dev)
+        for _ in range(4):
+            F.logprob_fused_fwd(lg, tg, 8)
+    elif mode == "rmsnorm":
+        x = torch.randn(16384, 4096, device=dev).bfloat16()
+        r = torch.randn_like(x)
+        w = torch.ones(4096, device=dev).bfloat16()
+        for _ in range(4):
+            F.rmsnorm_fwd(x, w, 1e-6, False, r)
+    elif mode == "glu_decode":
+        # dense MLP in a decode step: gate_up GEMM with the SwiGLU epilogue (grouped kernel, one group), 64 tokens
+        from skyrl_isoexec_b200.ops import moe
+        x = torch.randn(64, 4096, device=dev).bfloat16()
+        w = (torch.randn(1, 24576, 4096, device=dev) * 0.02).bfloat16()
+        with torch.no_grad():
+            for _ in range(4):
+                moe.grouped_gemm(x, w, None, moe.EPI_GLU)
+    elif mode == "moe_grouped":
+        # one Qwen3-30B-A3B expert layer: 4096 tokens x top-8 over 128 experts (fc1 + SwiGLU x gate weight, then fc2)
+        from skyrl_isoexec_b200.ops import moe
+        T, E, k, H, Fd = 4096, 128, 8, 2048, 768
+        gate_up = (torch.randn(E, 2 * Fd, H, device=dev) * 0.03).bfloat16()
+        down = (torch.randn(E, H, Fd, device=dev) * 0.03).bfloat16()
+        y = torch.randn(T, H, device=dev).bfloat16()
+        idx = torch.stack([torch.randperm(E, device=dev)[:k] for _ in range(T)]).int()
+        order, counts, pos = moe.build_dispatch(idx, E)
+        x_rows = y.index_select(0, torch.div(order, k, rounding_mode="floor"))
+        w_rows = torch.rand(T * k, device=dev)
+        offs = moe.counts_to_offsets(counts)
+        with torch.no_grad():
+            for _ in range(4):
+                moe.expert_rows_grouped(x_rows, w_rows, offs, gate_up, down)
+    elif mode == "rmsnorm_decode":
+        x = torch.randn(64, 4096, device=dev).bfloat16()
+        r = torch.randn_like(x)
+        w = torch.ones(4096, device=dev).bfloat16()
+        for _ in range(4):
+            F.rmsnorm_fwd(x, w, 1e-6, False, r)
+    elif mode == "rmsnorm_bwd":
+        x = torch.randn(8192, 4096, device=dev).bfloat16().requires_grad_()
+        r = torch.randn(8192, 4096, device=dev).bfloat16().requires_grad_()
+        w = torch.ones(4096, device=dev).bfloat16().requires_grad_()
+        for _ in range(3):
+            y, h = F.rmsnorm(x, w, 1e-6, False, r)
+            (y.float().sum() + h.float().sum()).backward()
+    elif mode == "attn_bwd":
+        # one micro-batch of the flagship step: 8192 packed tokens, Qwen3-8B heads; prints device time of the three
+        # backward kernels together and, for scale, of the library path they replace (SDPA forward + backward on padded
+        # [B, H, S, D])
+        Hq, Hkv, D = 32, 8, 128
+        lens = [2560, 2560, 2560, 512]
+        T = sum(lens)
+        q, kc, vc = (torch.randn(T, h, D, device=dev).bfloat16().requires_grad_(True) for h in (Hq, Hkv, Hkv))
+        dout = torch.randn(T, Hq, D, device=dev).bfloat16()
+        meta = F.AttnMeta.packed(lens, Hq, Hkv, dev)
+        out = F.attention(q, kc, vc, meta, 1 / math.sqrt(D))
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for it in range(4):
+            if it == 1:
+                e0.record()
+            torch.autograd.grad(out, (q, kc, vc), dout, retain_graph=True)
+        e1.record()
+        torch.cuda.synchronize()
+        print(f"attention backward (delta + dK/dV + dQ kernels): {e0.elapsed_time(e1) / 3 * 1000:.1f} us per call")
+        if len(sys.argv) > 2 and sys.argv[2] == "compare":
+            B, S = 3, 2560
+            qp, kp, vp = (torch.randn(B, h, S, D, device=dev).bfloat16().requires_grad_(True) for h in (Hq, Hkv, Hkv))
+            do = torch.randn(B, Hq, S, D, device=dev).bfloat16()
+            for it in range(4):
+                if it == 1:
+                    e0.record()
+                o = torch.nn.functional.scaled_dot_product_attention(qp, kp, vp, is_causal=True, enable_gqa=True)
+                torch.autograd.grad(o, (qp, kp, vp), do)
+            e1.record()
+            torch.cuda.synchronize()
+            print(f"library SDPA forward + backward, 3 x 2560 tokens (7680 of the 8192): {e0.elapsed_time(e1) / 3 * 1000:.1f} us per call")
+    elif mode == "train_small":
+        # elementwise kernels of one training micro-batch (8192 tokens, Qwen3-8B shapes): CUDA-event time and bytes moved
+        T, Hq, Hkv, D = 8192, 32, 8, 128
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+        def timed(fn, n=5):
+            for _ in range(2):
+                fn()
+            e0.record()
+            for _ in range(n):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            return e0.elapsed_time(e1) / n * 1000
+
+        qkv = torch.randn(T, (Hq + 2 * Hkv) * D, device=dev).bfloat16().requires_grad_(True)
+        qw, kw = (torch.randn(D, device=dev).bfloat16().requires_grad_(True) for _ in range(2))
+        pos = (torch.arange(T, device=dev, dtype=torch.int32) % 2560).contiguous()
+        rope = F.RopeTable(D, 4096, 1e6, dev)
+        kc, vc = (torch.zeros(T, Hkv, D, device=dev, dtype=torch.bfloat16) for _ in range(2))
+        us = timed(lambda: F.qk_norm_rope_fwd(qkv.detach(), pos, None, rope, qw.detach(), kw.detach(), kc, vc, Hq, Hkv, D, 1e-6))
+        nbytes = 2 * qkv.numel() * 2
+        print(f"qk_norm_rope forward: {us:.1f} us, {nbytes / us / 1e6:.2f} TB/s (read + write of the fused QKV)")
+        q, k, v = F.qk_norm_rope_train(qkv, pos, rope, qw, kw, Hq, Hkv, D, 1e-6)
+        gq, gk, gv = torch.randn_like(q), torch.randn_like(k), torch.randn_like(v)
+        us = timed(lambda: torch.autograd.grad((q, k, v), (qkv, qw, kw), (gq, gk, gv), retain_graph=True))
+        print(f"qk_norm_rope backward (+ weight-gradient fold): {us:.1f} us, {3 * qkv.numel() * 2 / us / 1e6:.2f} TB/s (dq|dk|dv + qkv read, dqkv written)")
+        n = 4096 * 12288
+        g = torch.randn(n, device=dev).bfloat16()
+        acc = torch.zeros(n, device=dev)
+        L = _native.lib()
+        us = timed(lambda: _native.check(L.ix_accum_bf16_to_f32(acc.data_ptr(), g.data_ptr(), n, 1, _native.stream()), "accum"))
+        print(f"gradient accumulation bf16 -> fp32, {n} elements: {us:.1f} us, {n * 10 / us / 1e6:.2f} TB/s")
+    elif mode == "sampler":
+        from skyrl_isoexec_b200.engine.sampler import Sampler, SamplingParams
+        lg = torch.randn(64, 151936, device=dev).bfloat16()
+        sm = Sampler(dev, 0)
+        for _ in range(4):
+            sm(lg, [SamplingParams()] * 64)
+    torch.cuda.synchronize()
+    assert _native.read_status() == 0
+    print("ok", mode)
+
+
+if __name__ == "__main__":
+    main(sys.argv[1] if len(sys.argv) > 1 else "attn_decode")
