@@ -1,5 +1,5 @@
 // Blackwell (sm_100a) device primitives shared by every kernel in this library:
-// mbarrier, TMA (cp.async.bulk.tensor, never with cluster multicast), tcgen05
+// mbarrier, TMA (cp.async.bulk.tensor), tcgen05
 // (TMEM alloc / mma / commit / ld) and the bounded-wait protocol.
 //
 // Bounded waits: every spin in this library (mbarrier or flag) gives up after a

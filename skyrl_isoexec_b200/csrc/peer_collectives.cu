@@ -16,7 +16,7 @@
 // before every peer has started it, and a peer starts it only after finishing epoch e, so a buffer
 // is never overwritten (by the producer of epoch e+2) while a peer still reads epoch e.
 //
-// No TMA and no cluster multicast is used on peer memory: remote data arrives by ld.global.
+// No TMA is used on peer memory: remote data arrives by ld.global.
 #include "bw_common.cuh"
 #include "host_util.h"
 

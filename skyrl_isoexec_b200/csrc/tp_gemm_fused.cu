@@ -24,7 +24,7 @@
 //   warps 6..9  reducer (AR1/AR2/RS): wait for a tile's W flags, fold over ranks, write/push the result
 //               copier  (AG): push local rows to the peers' gathered buffers
 // Remote traffic is plain st.global / ld.global on peer-mapped memory; TMA only ever reads this GPU's memory
-// and no cluster multicast is used. Flags are st.release.sys / ld.acquire.sys epochs; every wait is bounded.
+// Flags are st.release.sys / ld.acquire.sys epochs; every wait is bounded.
 #include "bw_common.cuh"
 #include "host_util.h"
 
