@@ -161,6 +161,12 @@ class FixedKLController:
     def update(self, current, n_steps):
         pass
 
+    def state_dict(self):
+        return {"value": self.value}
+
+    def load_state_dict(self, sd):
+        self.value = float(sd["value"])
+
 
 class AdaptiveKLController:
     """Proportional controller on the observed KL (Ziegler et al.), clipped to +-20% per update."""
@@ -171,6 +177,12 @@ class AdaptiveKLController:
     def update(self, current, n_steps):
         err = min(max(current / self.target - 1, -0.2), 0.2)
         self.value *= 1 + err * n_steps / self.horizon
+
+    def state_dict(self):
+        return {"value": self.value}
+
+    def load_state_dict(self, sd):
+        self.value = float(sd["value"])
 
 
 def get_kl_controller(cfg: AlgorithmConfig):
@@ -221,7 +233,8 @@ def rloo_advantage(token_level_rewards, response_mask, index, **kw):
         gid = _group_ids(index)
         cnt, mean, _ = _group_stats(scores, gid)
         n = cnt[gid]
-        adv = torch.where(n > 1, scores * n / (n - 1).clamp(min=1) - mean[gid] * n / (n - 1).clamp(min=1), scores)
+        # a group of one has no "others": its advantage is 0 (R/backends/skyrl_train/utils/ppo_utils.py:1231-1234)
+        adv = torch.where(n > 1, scores * n / (n - 1).clamp(min=1) - mean[gid] * n / (n - 1).clamp(min=1), torch.zeros_like(scores))
         adv = adv.to(response_mask.device)[:, None] * response_mask
     return adv, adv
 
@@ -317,7 +330,8 @@ def compute_off_policy_correction(old_log_probs, rollout_logprobs, loss_mask, op
     the trainer's old logprobs and the rollout engine's. Returns (weights|None, new_mask, metrics)."""
     metrics: dict[str, float] = {}
     if rollout_logprobs is None or (opc.tis_ratio_type is None and opc.sequence_mask_metric is None
-                                    and opc.outlier_token_is_threshold_low is None):
+                                    and opc.outlier_token_is_threshold_low is None
+                                    and opc.outlier_token_is_threshold_high is None):
         return None, loss_mask, metrics
     with torch.no_grad():
         lr = (old_log_probs.float() - rollout_logprobs.float()) * loss_mask

@@ -8,7 +8,10 @@
     {ckpt_path}/global_step_N/trainer_state.pt
 
 A shard file holds the rank's slice of the sharded state dict with the keys ``model`` /
-``optimizer`` / ``lr_scheduler`` / ``rng``; ``metadata.json`` records every parameter's full
+``optimizer`` / ``lr_scheduler`` / ``rng``. The files follow the naming of torch's distributed
+checkpoints but are ``torch.save`` pickles with a JSON index: they are NOT readable by
+``torch.distributed.checkpoint`` or Megatron's dist-checkpointing tools (use the HF export for
+interchange). A critic, when there is one, is saved the same way under ``critic/``. ``metadata.json`` records every parameter's full
 shape, shard dim and sections so a checkpoint written at one TP degree loads at another
 (parameters are reassembled to full shape and re-sliced). The step directory is written under
 a temporary name and renamed, and ``latest_ckpt_global_step.txt`` is replaced last, so a crash
@@ -43,7 +46,9 @@ def step_dir(ckpt_path: str, step: int) -> str:
     return os.path.join(ckpt_path, f"global_step_{step}")
 
 
-def save_checkpoint(ckpt_path: str, step: int, policy, data_state: dict, trainer_state: dict, ps, max_to_keep: int = -1) -> str:
+def save_checkpoint(ckpt_path: str, step: int, policy, data_state: dict, trainer_state: dict, ps, max_to_keep: int = -1,
+                    extra_shards: dict | None = None) -> str:
+    """``extra_shards``: ``{folder: this rank's state}`` written as ``{folder}/__{rank}_0.distcp`` beside ``policy/``."""
     final = step_dir(ckpt_path, step)
     tmp = final + ".tmp"
     rank = _rank()
@@ -62,6 +67,9 @@ def save_checkpoint(ckpt_path: str, step: int, policy, data_state: dict, trainer
         "parallel": {"tp": ps.tp, "tp_rank": ps.tp_rank, "dp_rank": ps.dp_rank, "pp_rank": ps.pp_rank, "ep_rank": ps.ep_rank},
     }
     torch.save(shard, os.path.join(tmp, "policy", f"__{rank}_0.distcp"))
+    for folder, state in (extra_shards or {}).items():
+        os.makedirs(os.path.join(tmp, folder), exist_ok=True)
+        torch.save(state, os.path.join(tmp, folder, f"__{rank}_0.distcp"))
     if rank == 0:
         meta = {
             "format": "skyrl_isoexec_b200.sharded.v1", "global_step": step, "world_size": dist.get_world_size() if dist.is_initialized() else 1,
@@ -134,24 +142,48 @@ def resolve_resume_path(ckpt_path: str, resume_mode: str, resume_path: str = "")
 
 
 def _assemble_full(name: str, meta: dict, shards: list[dict]) -> torch.Tensor:
-    """Rebuild a parameter at full shape from the TP shards of the saved layout (dp_rank 0)."""
+    """Rebuild a parameter at full shape from the shards of one data-parallel replica of the saved layout.
+    ``shards``: the saved shard dicts of one pipeline stage; TP shards are joined on the shard dim (per section),
+    expert-parallel shards on the leading expert dim."""
     info = meta["params"][name]
-    parts = [s["model"][name] for s in shards]
-    if info["shard_dim"] is None or len(parts) == 1:
-        return parts[0]
-    if info.get("kv_rep", 1) > 1:
-        from types import SimpleNamespace
 
-        from ..models.decoder import unshard_kv_rep
+    def join_tp(parts):
+        if info["shard_dim"] is None or len(parts) == 1:
+            return parts[0]
+        if info.get("kv_rep", 1) > 1:
+            from types import SimpleNamespace
 
-        return unshard_kv_rep(parts, SimpleNamespace(kv_rep=info["kv_rep"], kv_layout=tuple(info["kv_layout"])))
-    d, tp = info["shard_dim"], len(parts)
-    secs = info["sections"] or [info["full_shape"][d]]
-    cols = []
-    for si, sz in enumerate(secs):
-        lo = sum(x // tp for x in secs[:si])
-        cols += [p.narrow(d, lo, sz // tp) for p in parts]
-    return torch.cat(cols, dim=d)
+            from ..models.decoder import unshard_kv_rep
+
+            return unshard_kv_rep(parts, SimpleNamespace(kv_rep=info["kv_rep"], kv_layout=tuple(info["kv_layout"])))
+        d, tp = info["shard_dim"], len(parts)
+        secs = info["sections"] or [info["full_shape"][d]]
+        cols = []
+        for si, sz in enumerate(secs):
+            lo = sum(x // tp for x in secs[:si])
+            cols += [p.narrow(d, lo, sz // tp) for p in parts]
+        return torch.cat(cols, dim=d)
+
+    if info.get("ep_sharded") and meta.get("ep", 1) > 1:
+        # one (tp-joined) block per saved expert-parallel rank, concatenated on the expert dim
+        blocks = []
+        for e in range(meta["ep"]):
+            mine = sorted((s for s in shards if s["parallel"]["ep_rank"] == e), key=lambda s: s["parallel"]["tp_rank"])
+            seen, uniq = set(), []
+            for s in mine:                       # ranks of other expert-data-parallel replicas hold copies
+                if s["parallel"]["tp_rank"] not in seen:
+                    seen.add(s["parallel"]["tp_rank"])
+                    uniq.append(s)
+            if not uniq:
+                raise KeyError(f"checkpoint has no shard of expert-parallel rank {e} for {name}")
+            blocks.append(join_tp([s["model"][name] for s in uniq]))
+        return torch.cat(blocks, dim=0)
+    seen, parts = set(), []
+    for s in sorted(shards, key=lambda s: s["parallel"]["tp_rank"]):
+        if s["parallel"]["tp_rank"] not in seen:
+            seen.add(s["parallel"]["tp_rank"])
+            parts.append(s["model"][name])
+    return join_tp(parts)
 
 
 def _assemble_optimizer_state(shards: list[dict]) -> dict | None:
@@ -169,14 +201,33 @@ def _assemble_optimizer_state(shards: list[dict]) -> dict | None:
         return dict(pieces[(0, n)][0])
     spans = sorted(k for k in pieces if k[1] > k[0])
     if not spans or spans[0][0] != 0 or spans[-1][1] != n or any(a[1] != b[0] for a, b in zip(spans, spans[1:])):
-        return None                                   # slices do not tile the buffer: leave the optimizer fresh
+        return None                                   # slices do not tile the buffer
     out = {k: torch.cat([pieces[sp][0][k] for sp in spans]) for k in ("master", "exp_avg", "exp_avg_sq")}
     out["step"] = pieces[spans[0]][0]["step"]
     out["slice"] = (0, n, n)
     return out
 
 
+def load_extra_shard(path: str, folder: str):
+    """This rank's file of an extra folder written by ``save_checkpoint(extra_shards=...)``; None if absent."""
+    f = os.path.join(path, folder, f"__{_rank()}_0.distcp")
+    return torch.load(f, map_location="cpu", weights_only=False) if os.path.exists(f) else None
+
+
+def _restore_rng(rng: dict) -> None:
+    torch.set_rng_state(rng["torch"])
+    random.setstate(rng["python"])
+    if rng.get("cuda") is not None and torch.cuda.is_available():
+        torch.cuda.set_rng_state(rng["cuda"])
+
+
 def load_checkpoint(path: str, policy, ps) -> tuple[dict, dict]:
+    """Load the policy (weights, optimizer, RNG) saved under ``path`` into this job's layout.
+
+    Same layout: every rank reads its own file. A different tensor-, expert- or data-parallel degree: parameters are
+    rebuilt at full shape from one saved replica and re-sliced; the optimizer state carries over only when the flat
+    layout of a rank is unchanged (data-parallel degree changed alone) and is otherwise started fresh, with a warning.
+    A different pipeline-parallel degree is refused (a stage's file holds its own layers only)."""
     validate_checkpoint_dir(path)
     with open(os.path.join(path, "policy", "metadata.json")) as f:
         meta = json.load(f)
@@ -193,28 +244,38 @@ def load_checkpoint(path: str, policy, ps) -> tuple[dict, dict]:
                 dst.copy_(shard["model"][name].to(dst.dtype))
         policy.opt.load_state_dict({k: (v.to(policy.opt.master.device) if torch.is_tensor(v) else v)
                                     for k, v in shard["optimizer"].items()})
-        torch.set_rng_state(shard["rng"]["torch"])
-        random.setstate(shard["rng"]["python"])
+        _restore_rng(shard["rng"])
     else:
-        # reshard: read the TP shards of data-parallel rank 0 of the saved job, rebuild, re-slice
+        if meta["pp"] != ps.pp:
+            raise ValueError(f"checkpoint was written with pipeline_parallel={meta['pp']}; this job uses {ps.pp}. Resharding "
+                             f"covers tensor-, expert- and data-parallel changes only")
         files = sorted(f for f in os.listdir(os.path.join(path, "policy")) if f.endswith(".distcp"))
         every = [torch.load(os.path.join(path, "policy", f), map_location="cpu", weights_only=False) for f in files]
-        shards = [s for s in every if s["parallel"]["dp_rank"] == 0 and s["parallel"]["pp_rank"] == 0 and s["parallel"]["ep_rank"] == 0]
-        shards.sort(key=lambda s: s["parallel"]["tp_rank"])
+        stage = [s for s in every if s["parallel"]["pp_rank"] == ps.pp_rank]
+        if not stage:
+            raise KeyError(f"checkpoint holds no shard of pipeline stage {ps.pp_rank}")
         with torch.no_grad():
             for name, dst in model.named_weights():
-                full = _assemble_full(name, meta, shards)
+                full = _assemble_full(name, meta, stage)
+                want = tuple(model.store.specs[name].full_shape)
+                if tuple(full.shape) != want:
+                    raise ValueError(f"{name}: rebuilt shape {tuple(full.shape)} from the checkpoint, expected {want}")
                 dst.copy_(shard_of(full, model.store.specs[name], ps.tp_rank, ps.tp, ps.ep_rank, ps.ep).to(dst.dtype))
             if policy.opt.low_precision:
                 policy.opt.master.copy_(model.store.flat[policy.opt.lo:policy.opt.hi].float())
-        policy.opt.step_count = int(shards[0]["lr_scheduler"]["step"])
-        if meta["tp"] == ps.tp and meta["pp"] == ps.pp and meta["ep"] == ps.ep:
+        policy.opt.step_count = int(stage[0]["lr_scheduler"]["step"])
+        carried = False
+        if meta["tp"] == ps.tp and meta["ep"] == ps.ep:
             # only the data-parallel degree changed: the flat layout of this rank is the saved one, so the optimizer
             # state (whole, or the slices a sharded optimizer wrote) is put back together and cut again
-            full = _assemble_optimizer_state([s for s in every if s["parallel"]["tp_rank"] == ps.tp_rank
-                                              and s["parallel"]["pp_rank"] == ps.pp_rank and s["parallel"]["ep_rank"] == ps.ep_rank])
+            full = _assemble_optimizer_state([s for s in stage if s["parallel"]["tp_rank"] == ps.tp_rank
+                                              and s["parallel"]["ep_rank"] == ps.ep_rank])
             if full is not None:
                 policy.opt.load_state_dict({k: (v.to(policy.opt.master.device) if torch.is_tensor(v) else v) for k, v in full.items()})
+                carried = True
+        if not carried and rank == 0:
+            print(f"[warn] checkpoint layout (tp={meta['tp']} ep={meta['ep']} dp={meta['dp']}) differs from this job's "
+                  f"(tp={ps.tp} ep={ps.ep} dp={ps.dp}): weights were resharded, Adam moments start from zero")
     data_state = torch.load(os.path.join(path, "data.pt"), weights_only=False)
     trainer_state = torch.load(os.path.join(path, "trainer_state.pt"), weights_only=False)
     return data_state, trainer_state

@@ -587,7 +587,10 @@ class PolicyWorker:
                 from ..core.testing import count_bit_mismatches
 
                 rm = get("response_mask")
-                a_, b_ = (lp2d.detach() * rm).contiguous(), (get("rollout_logprobs") * rm).contiguous()
+                if batch.get("loss_mask") is not None:     # trained tokens only: observation tokens carry no rollout logprob
+                    rm = rm * (get("loss_mask") > 0).to(rm.dtype)
+                z_ = torch.zeros_like(rm)
+                a_, b_ = torch.where(rm > 0, lp2d.detach(), z_).contiguous(), torch.where(rm > 0, get("rollout_logprobs"), z_).contiguous()
                 d_ = (a_ - b_).abs()
                 bits["mismatches"] += count_bit_mismatches(a_, b_)
                 bits["abs_sum"] += float(d_.sum())

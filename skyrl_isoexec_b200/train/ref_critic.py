@@ -16,7 +16,7 @@ import torch.distributed as dist
 from ..models.decoder import DecoderLM
 from . import algorithms as alg
 from .batch import TrainingInputBatch
-from .policy_worker import FlatAdamW, PolicyWorker, WorkerConfig, pack_microbatches
+from .policy_worker import PolicyWorker, WorkerConfig, pack_microbatches
 
 
 class RefWorker(PolicyWorker):
@@ -50,14 +50,15 @@ class CriticWorker:
         self.cfg = cfg or WorkerConfig()
         self.algo = algo or alg.AlgorithmConfig()
         self.ps, self.device = model.ps, model.device_
-        self.opt = FlatAdamW(model, self.cfg.optimizer)
+        # a complete policy-style worker around the backbone: packing, recompute policy, the (possibly DP-sharded) flat
+        # optimizer and the TP / KV-replica / DP gradient reductions are the policy worker's own
+        self._policy_like = PolicyWorker(model, self.cfg, self.algo)
+        self.opt = self._policy_like.opt
         g = torch.Generator().manual_seed(1234)
         h = model.cfg.hidden_size
         self.v_weight = torch.nn.Parameter((torch.randn(h, generator=g) * (1.0 / h ** 0.5)).to(self.device))
         self.v_bias = torch.nn.Parameter(torch.zeros(1, device=self.device))
         self.head_opt = torch.optim.AdamW([self.v_weight, self.v_bias], lr=self.cfg.optimizer.lr, weight_decay=0.0)
-        self._policy_like = PolicyWorker.__new__(PolicyWorker)
-        self._policy_like.model, self._policy_like.cfg, self._policy_like.device = model, self.cfg, self.device
 
     def _values(self, mb, hidden) -> torch.Tensor:
         rows = mb.pred_rows.to(self.device, non_blocking=True)
@@ -104,10 +105,8 @@ class CriticWorker:
         return {"critic_loss": tot["loss"], "values_clip_ratio": tot["clip"] / max(1, tot["n"])}
 
     def optim_step(self) -> float:
+        self._policy_like.reduce_gradients()          # TP sums of per-head norm weights, KV replicas, then DP
         if self.ps.dp > 1:
-            from ..parallel.dp import reduce_main_grads
-
-            reduce_main_grads(self.opt.main_grad, self.ps)
             for p in (self.v_weight, self.v_bias):
                 if p.grad is not None:
                     dist.all_reduce(p.grad, group=self.ps.dp_group)
@@ -115,3 +114,22 @@ class CriticWorker:
         self.head_opt.step()
         self.head_opt.zero_grad(set_to_none=True)
         return float(norm.item())
+
+    # ---------------------------------------------------------------- checkpoint
+    def state_dict(self) -> dict:
+        """This rank's critic state: backbone shard, value head, both optimizers (reference: the ``critic/`` folder of a
+        step directory, R/train/trainer.py:1858-1930)."""
+        cpu = lambda t: t.detach().cpu().clone()
+        return {"model": {n: cpu(t) for n, t in self.model.named_weights()},
+                "optimizer": {k: (cpu(v) if torch.is_tensor(v) else v) for k, v in self.opt.state_dict().items()},
+                "head": {"weight": cpu(self.v_weight), "bias": cpu(self.v_bias)}, "head_optimizer": self.head_opt.state_dict()}
+
+    def load_state_dict(self, sd: dict) -> None:
+        with torch.no_grad():
+            for n, dst in self.model.named_weights():
+                dst.copy_(sd["model"][n].to(dst.dtype))
+            self.v_weight.copy_(sd["head"]["weight"])
+            self.v_bias.copy_(sd["head"]["bias"])
+        dev = self.opt.master.device
+        self.opt.load_state_dict({k: (v.to(dev) if torch.is_tensor(v) else v) for k, v in sd["optimizer"].items()})
+        self.head_opt.load_state_dict(sd["head_optimizer"])

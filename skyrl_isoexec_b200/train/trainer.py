@@ -72,10 +72,16 @@ class SyntheticPromptDataset:
 
 
 class PromptDataLoader:
-    """Shuffling batch iterator with a resumable state (epoch, cursor, rng)."""
+    """Shuffling batch iterator with a resumable state (epoch, cursor, seed).
 
-    def __init__(self, dataset, batch_size: int, seed: int, shuffle: bool = True, drop_last: bool = True):
+    Data parallelism: every rank walks the SAME global order (one seed for the job) and takes slice ``part`` of
+    ``parts`` out of each global batch of ``batch_size * parts`` prompts, so the shards of one step are disjoint, an
+    epoch visits every prompt once across the job, and the state is identical on every rank (one rank saves it for all)."""
+
+    def __init__(self, dataset, batch_size: int, seed: int, shuffle: bool = True, drop_last: bool = True,
+                 part: int = 0, parts: int = 1):
         self.ds, self.bs, self.seed, self.shuffle, self.drop_last = dataset, batch_size, seed, shuffle, drop_last
+        self.part, self.parts = part, max(1, parts)
         self.epoch, self.cursor = 0, 0
         self._order = self._make_order()
 
@@ -85,23 +91,33 @@ class PromptDataLoader:
             random.Random(self.seed + self.epoch).shuffle(idx)
         return idx
 
+    @property
+    def _global_bs(self) -> int:
+        return self.bs * self.parts
+
     def __len__(self):
-        return len(self.ds) // self.bs if self.drop_last else (len(self.ds) + self.bs - 1) // self.bs
+        g = self._global_bs
+        return len(self.ds) // g if self.drop_last else (len(self.ds) + g - 1) // g
 
     def __iter__(self):
-        while self.cursor + (self.bs if self.drop_last else 1) <= len(self._order):
-            batch = [self.ds[i] for i in self._order[self.cursor:self.cursor + self.bs]]
-            self.cursor += self.bs
+        g = self._global_bs
+        while self.cursor + (g if self.drop_last else 1) <= len(self._order):
+            whole = self._order[self.cursor:self.cursor + g]
+            batch = [self.ds[i] for i in whole[self.part * self.bs:(self.part + 1) * self.bs]]
+            self.cursor += g
             yield batch
         self.epoch += 1
         self.cursor = 0
         self._order = self._make_order()
 
     def state_dict(self):
-        return {"epoch": self.epoch, "cursor": self.cursor, "seed": self.seed}
+        return {"epoch": self.epoch, "cursor": self.cursor, "seed": self.seed, "parts": self.parts, "batch_size": self.bs}
 
     def load_state_dict(self, sd):
-        self.epoch, self.cursor, self.seed = sd["epoch"], sd["cursor"], sd["seed"]
+        self.epoch, self.seed = sd["epoch"], sd["seed"]
+        # the cursor counts prompts of the global order, so it survives a change of the data-parallel degree as long
+        # as the global batch is the same
+        self.cursor = sd["cursor"]
         self._order = self._make_order()
 
 
@@ -201,7 +217,7 @@ class RayPPOTrainer:
             self.dataset = SyntheticPromptDataset(n, d.synthetic_prompt_len, mcfg.vocab_size, t.seed,
                                                   self.cfg.environment.env_class)
         per_rank = t.train_batch_size // self.ps.dp if self.ps.dp > 1 else t.train_batch_size
-        self.loader = PromptDataLoader(self.dataset, per_rank, t.seed + self.ps.dp_rank)
+        self.loader = PromptDataLoader(self.dataset, per_rank, t.seed, part=self.ps.dp_rank, parts=self.ps.dp)
         self.init_weight_sync_state()
 
     def init_weight_sync_state(self) -> None:
@@ -275,16 +291,23 @@ class RayPPOTrainer:
         else:
             lp = self.policy.forward(batch)
         batch["action_log_probs"] = lp
-        mask = batch["response_mask"]
+        rmask = batch["response_mask"]
+        # the gate and the diff metrics look at the tokens the loss trains on (R/train/trainer.py:1544-1546): observation
+        # tokens of a multi-turn rollout sit inside response_mask with a placeholder rollout logprob of 0 and loss mask 0
+        lm = batch.get("loss_mask")
+        mask = ((lm > 0) & (rmask > 0)).to(lp.dtype) if lm is not None else rmask
         ro = batch["rollout_logprobs"]
         diff = (lp - ro).abs() * mask
+        nsel = float(mask.sum())
         n = mask.sum().clamp(min=1)
         mean = diff.sum() / n
         std = ((diff - mean).pow(2) * mask).sum().div(n).sqrt()
-        mism = count_bit_mismatches((lp * mask).contiguous(), (ro * mask).contiguous())
+        sel = mask > 0            # select, do not multiply: -x * 0 is -0.0, whose bits differ from the placeholder +0.0
+        z = torch.zeros_like(lp)
+        mism = count_bit_mismatches(torch.where(sel, lp, z).contiguous(), torch.where(sel, ro, z).contiguous()) if nsel > 0 else 0
         self.all_metrics.update({
-            "policy/rollout_train_logprobs_abs_diff_max": float(diff.max()) if diff.numel() else 0.0,
-            "policy/rollout_train_logprobs_abs_diff_min": float(diff[mask > 0].min()) if mask.sum() > 0 else 0.0,
+            "policy/rollout_train_logprobs_abs_diff_max": float(diff.max()) if diff.numel() and nsel > 0 else 0.0,
+            "policy/rollout_train_logprobs_abs_diff_min": float(diff[mask > 0].min()) if nsel > 0 else 0.0,
             "policy/rollout_train_logprobs_abs_diff_mean": float(mean),
             "policy/rollout_train_logprobs_abs_diff_std": float(std),
             "policy/rollout_train_logprob_bit_mismatches": mism,
@@ -296,7 +319,7 @@ class RayPPOTrainer:
                 batch["action_log_probs"] = lp
                 batch = self.apply_reward_kl_penalty(batch)
         if getattr(self, "critic", None) is not None:
-            batch["values"] = self.critic.forward(batch) * mask
+            batch["values"] = self.critic.forward(batch) * rmask
         iso = self.cfg.trainer.isoexec
         if iso.enabled and not self._gate_in_update:
             gate = validate_isoexec_forward_gate(diff, mask, mism, iso)
@@ -384,8 +407,14 @@ class RayPPOTrainer:
                     mb.metadata["aux_loss_scale"] = 1.0 / max(1.0, tot)
                 else:
                     gB = int(self._global_sum(float(mb.batch_size)))
+                    pb = None
+                    if a.loss_reduction == "prompt_mean":
+                        from .dataset import compute_prompt_boundaries
+
+                        pb = compute_prompt_boundaries(batch.metadata["uids"][lo:min(B, lo + mb_seqs)])
                     scaled = alg.apply_loss_reduction_to_advantages(mb["advantages"], lm, a.loss_reduction,
-                                                                    t.micro_train_batch_size_per_gpu, a.max_seq_len)
+                                                                    t.micro_train_batch_size_per_gpu, a.max_seq_len,
+                                                                    prompt_boundaries=pb)
                     mb["advantages"] = scaled * (mb.batch_size / max(1, gB))
                     mb.metadata["aux_loss_scale"] = 1.0 / max(1.0, self._global_sum(float(lm.sum())))
                 if getattr(self, "_gate_in_update", False):
@@ -464,6 +493,23 @@ class RayPPOTrainer:
                 self._gpu_mon.start()
         return self._prof
 
+    def _extra_prompts(self, n: int) -> list[dict]:
+        """More prompts for dynamic sampling, drawn from a stream of their own (the epoch iterator that feeds
+        ``train()`` is not touched): a seeded walk over the dataset, disjoint across data-parallel ranks, that wraps around."""
+        if getattr(self, "_extra_rng", None) is None:
+            self._extra_rng = random.Random(self.cfg.trainer.seed + 7_654_321)
+            self._extra_pool: list[int] = []
+        out = []
+        while len(out) < n:
+            if len(self._extra_pool) < self.ps.dp:
+                idx = list(range(len(self.dataset)))
+                self._extra_rng.shuffle(idx)
+                self._extra_pool += idx
+            take = self._extra_pool[:self.ps.dp]           # every rank draws the same numbers and keeps its own column
+            del self._extra_pool[:self.ps.dp]
+            out.append(self.dataset[take[self.ps.dp_rank]])
+        return out
+
     def train_step(self, rows: list[dict]) -> dict:
         """One full RL step on this rank's prompt shard. Returns the step's metrics."""
         self.all_metrics, self.all_timings = {}, {}
@@ -482,14 +528,13 @@ class RayPPOTrainer:
                     from .trainer_utils import handle_dynamic_sampling
 
                     state: dict = {}
-                    it = iter(self.loader)
                     while True:
                         go2, uids2, more = handle_dynamic_sampling(go, uids, a, state, len(rows), self.cfg.generator.n_samples_per_prompt,
                                                                    seed=self.cfg.trainer.seed + self.global_step)
                         if not more:
                             go, uids = go2, uids2
                             break
-                        gi, uids = self.prepare_generator_input(next(it))
+                        gi, uids = self.prepare_generator_input(self._extra_prompts(len(rows)))
                         go = self.generate(gi)
             with Timer("sleep", T):
                 self.engine.sleep()
@@ -549,7 +594,7 @@ class RayPPOTrainer:
             if t.eval_before_train:
                 self.eval()
             done = False
-            for self.epoch in range(t.epochs):
+            for self.epoch in range(getattr(self, "_start_epoch", 0), t.epochs):
                 self._fire("on_epoch_start")
                 for rows in self.loader:
                     self._fire("on_step_start", batch=rows)
@@ -623,9 +668,11 @@ class RayPPOTrainer:
     # ------------------------------------------------------------------ checkpoints
     def save_checkpoints(self) -> str:
         t = self.cfg.trainer
+        extra = {"critic": self.critic.state_dict()} if getattr(self, "critic", None) is not None else None
         path = ckpt.save_checkpoint(t.ckpt_path, self.global_step, self.policy, self.loader.state_dict(),
-                                    {"global_step": self.global_step, "config": self.cfg.to_dict()}, self.ps,
-                                    max_to_keep=t.max_ckpts_to_keep)
+                                    {"global_step": self.global_step, "epoch": self.epoch, "kl_ctrl": self.kl_ctrl.state_dict(),
+                                     "config": self.cfg.to_dict()}, self.ps,
+                                    max_to_keep=t.max_ckpts_to_keep, extra_shards=extra)
         self._fire("on_save", ckpt_path=path)
         return path
 
@@ -637,4 +684,13 @@ class RayPPOTrainer:
         data_state, trainer_state = ckpt.load_checkpoint(path, self.policy, self.ps)
         self.loader.load_state_dict(data_state)
         self.global_step = int(trainer_state["global_step"])
+        self.epoch = self._start_epoch = int(trainer_state.get("epoch", data_state.get("epoch", 0)))
+        if trainer_state.get("kl_ctrl") is not None:
+            self.kl_ctrl.load_state_dict(trainer_state["kl_ctrl"])
+        if getattr(self, "critic", None) is not None:
+            sd = ckpt.load_extra_shard(path, "critic")
+            if sd is None:
+                print("[warn] checkpoint has no critic state for this rank: the critic restarts from its initial weights")
+            else:
+                self.critic.load_state_dict(sd)
         return self.global_step

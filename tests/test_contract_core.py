@@ -72,18 +72,18 @@ def test_identity_projections():
 
 
 @pytest.mark.parametrize("mutate,needle", [
-    (lambda c, e: dataclasses.replace(c, composition=()), "empty composition"),
-    (lambda c, e: dataclasses.replace(c, composition=(dataclasses.replace(e, route="fast"),)), "unknown route"),
-    (lambda c, e: dataclasses.replace(c, composition=(dataclasses.replace(e, cases=("nope",)),)), "unknown case"),
-    (lambda c, e: dataclasses.replace(c, composition=(dataclasses.replace(e, route="reference_preserving"),)), "requires a reference"),
-    (lambda c, e: dataclasses.replace(c, composition=(dataclasses.replace(e, route="composition_defining"),)), "requires an artifact"),
-    (lambda c, e: dataclasses.replace(c, composition=(dataclasses.replace(e, half="deployment"),)), "neutrality_proof"),
-    (lambda c, e: dataclasses.replace(c, composition=(e, dataclasses.replace(e, impl=M.ImplRef("other", 1, "sm100"), cases=("trainer_score",)),)), "duplicate (region, case)"),
-    (lambda c, e: dataclasses.replace(c, composition=(dataclasses.replace(e, cases=("trainer_score",)), dataclasses.replace(e, impl=M.ImplRef("other", 1, "sm100"), cases=("engine_decode",)))), "asymmetric region requires a discharge"),
-    (lambda c, e: dataclasses.replace(c, claims=M.Claims(tolerances=(M.ToleranceClaim(("engine_decode", "trainer_score"), {"max": "inf"}),))), "not a finite threshold"),
-    (lambda c, e: dataclasses.replace(c, claims=M.Claims(state=(M.StateClaim("kv", ("reboot",), False, "x::y"),))), "unknown lifecycle event"),
-    (lambda c, e: dataclasses.replace(c, claims=M.Claims(topology=(M.TopologyClaim("tp", "invariant", domain=(2,), proof="p"),))), "tautology"),
-    (lambda c, e: dataclasses.replace(c, claims=M.Claims(topology=(M.TopologyClaim("tp", "pinned"),))), "pinned requires degree"),
+    (lambda c, e: dataclasses.replace(c, composition=()), "[C-EMPTY]"),
+    (lambda c, e: dataclasses.replace(c, composition=(dataclasses.replace(e, route="fast"),)), "[E-ROUTE]"),
+    (lambda c, e: dataclasses.replace(c, composition=(dataclasses.replace(e, cases=("nope",)),)), "[E-CASE]"),
+    (lambda c, e: dataclasses.replace(c, composition=(dataclasses.replace(e, route="reference_preserving"),)), "[E-REFERENCE]"),
+    (lambda c, e: dataclasses.replace(c, composition=(dataclasses.replace(e, route="composition_defining"),)), "[E-ARTIFACT]"),
+    (lambda c, e: dataclasses.replace(c, composition=(dataclasses.replace(e, half="deployment"),)), "[E-DEPLOY]"),
+    (lambda c, e: dataclasses.replace(c, composition=(e, dataclasses.replace(e, impl=M.ImplRef("other", 1, "sm100"), cases=("trainer_score",)),)), "[P-DUP]"),
+    (lambda c, e: dataclasses.replace(c, composition=(dataclasses.replace(e, cases=("trainer_score",)), dataclasses.replace(e, impl=M.ImplRef("other", 1, "sm100"), cases=("engine_decode",)))), "[P-ASYM]"),
+    (lambda c, e: dataclasses.replace(c, claims=M.Claims(tolerances=(M.ToleranceClaim(("engine_decode", "trainer_score"), {"max": "inf"}),))), "[T-BOUND]"),
+    (lambda c, e: dataclasses.replace(c, claims=M.Claims(state=(M.StateClaim("kv", ("reboot",), False, "x::y"),))), "[S-EVENT]"),
+    (lambda c, e: dataclasses.replace(c, claims=M.Claims(topology=(M.TopologyClaim("tp", "invariant", domain=(2,), proof="p"),))), "[A-SINGLE]"),
+    (lambda c, e: dataclasses.replace(c, claims=M.Claims(topology=(M.TopologyClaim("tp", "pinned"),))), "[A-PINNED]"),
 ])
 def test_validator_refusals(mutate, needle):
     c = _fixture()
@@ -95,7 +95,7 @@ def test_validator_refusals(mutate, needle):
 def test_stale_identities_are_caught():
     c = _fixture()
     bad = dataclasses.replace(c, identities=M.Identities("0" * 64, c.identities.numerical_policy, c.identities.deployment))
-    assert any("stored identities" in v for v in rules.validate(bad))
+    assert any("[C-IDENT]" in v for v in rules.validate(bad))
 
 
 def test_rounding_schedule_pins():

@@ -34,7 +34,7 @@ def test_rloo_maxrl_reinforcepp_gae():
     r[:, 1] = torch.tensor([1.0, 2.0, 3.0, 6.0])
     m = torch.ones(4, 2)
     adv, _ = alg.rloo_advantage(r, m, ["a", "a", "a", "b"])
-    assert torch.allclose(adv[0, 0], torch.tensor(1.0 - 2.5)) and adv[3, 0] == 6.0
+    assert torch.allclose(adv[0, 0], torch.tensor(1.0 - 2.5)) and adv[3, 0] == 0.0     # a group of one: advantage 0
     adv, _ = alg.maxrl_advantage(r, m, ["a", "a", "a", "b"])
     assert torch.allclose(adv[2, 0], torch.tensor((3.0 - 2.0) / (2.0 + 1e-6)))
     adv, ret = alg.reinforce_pp_advantage(r, m, gamma=1.0)
@@ -229,3 +229,37 @@ def test_engine_stop_strings_end_a_sequence_at_the_first_match():
     eng = fresh()
     eng.detokenize = None
     assert len(eng.generate([prompt], SamplingParams(max_generate_length=6, ignore_eos=True, stop=(f"<{target}>",)))[0].response_ids) == 6
+
+
+def test_forward_gate_ignores_observation_tokens_of_a_multi_turn_rollout(tmp_path):
+    """Observation tokens sit inside response_mask with a placeholder rollout logprob of 0 and loss mask 0
+    (train/generator.py agent_loop); the rollout-vs-train gate and its metrics must look at trained tokens only."""
+    tr = RayPPOTrainer(_cfg(str(tmp_path / "ck"), 1, ["trainer.ckpt_interval=0"]), device="cpu")
+    tr.build_models()
+    tr.sync_weights()
+    tr.engine.wake_up()
+    gi, uids = tr.prepare_generator_input(next(iter(tr.loader)))
+    go = tr.generate(gi)
+    tr.engine.sleep()
+    # splice an "observation" into the middle of every response: the tokens stay, their rollout logprob becomes the
+    # placeholder 0.0 and their loss mask 0, exactly what the multi-turn loop emits
+    for i in range(len(go["response_ids"])):
+        for j in range(5, 9):
+            go["loss_masks"][i][j] = 0
+            go["rollout_logprobs"][i][j] = 0.0
+    batch = tr.convert_to_training_input(go, uids)
+    tr.global_step = 1
+    batch = tr.fwd_logprobs_values_reward(batch)         # strict gate: would raise ForwardGateError on a mismatch
+    m = tr.all_metrics
+    assert m["policy/rollout_train_logprob_bit_mismatches"] == 0 and m["policy/rollout_train_logprobs_abs_diff_max"] == 0.0
+    # all-masked batch: nothing to compare, nothing refuses
+    batch["loss_mask"].zero_()
+    tr.fwd_logprobs_values_reward(batch)
+    assert tr.all_metrics["policy/rollout_train_logprob_bit_mismatches"] == 0
+    # the training-forward variant of the gate (scoring forward skipped) masks the same way
+    batch = tr.convert_to_training_input(go, uids)
+    batch["action_log_probs"] = batch["rollout_logprobs"].clone()
+    batch["advantages"] = torch.zeros_like(batch["rollout_logprobs"])
+    batch.metadata["check_rollout_bits"] = True
+    out = tr.policy.forward_backward(batch)
+    assert out["rollout_bits"]["mismatches"] == 0 and out["rollout_bits"]["tokens"] == float((batch["loss_mask"] > 0).sum())
