@@ -9,7 +9,18 @@ Prints ONE JSON line on rank 0. ``value`` is the whole-job aggregate of response
 second through complete GRPO steps, timed on the device with CUDA events (max over ranks);
 ``e2e`` is the same quantity from the host clock around ``RayPPOTrainer.train_step`` (prompts
 enter from pinned host memory, sampled tokens / logprobs / loss come back to the host every
-step). Weak scaling: each GPU keeps 8 prompts x 8 samples, 512-token prompts, 2048-token responses.
+step). Weak scaling: each GPU keeps 8 prompts x 8 samples, 512-token prompts, 2048-token responses,
+so 8 GPUs run the named configuration (64 prompts x 8 samples).
+
+Layout per GPU count (``--tp`` / ``--engine-tp`` override it, ``--layout dp`` forces plain data parallelism):
+
+    1 GPU    one trainer, one engine on the trainer's weights
+    2 GPUs   trainer TP2,        two engines at TP1
+    4 GPUs   trainer TP4,        two engines at TP2
+    8 GPUs   trainer TP4 x DP2,  four engines at TP2      (the named configuration)
+
+With more than one GPU the engines have their own layout and every step ends with a resharding weight sync
+(trainer shards -> engine shards over peer memory), reported as ``sync_ms_per_step``.
 """
 
 from __future__ import annotations
@@ -38,7 +49,9 @@ def parse():
     ap.add_argument("--prompt-len", type=int, default=512)
     ap.add_argument("--response-len", type=int, default=2048)
     ap.add_argument("--micro-tokens", type=int, default=8192)
-    ap.add_argument("--tp", type=int, default=1, help="tensor-parallel degree of trainer and engine (fused GEMM+collective kernels)")
+    ap.add_argument("--tp", type=int, default=0, help="trainer tensor-parallel degree (0 = by GPU count: 1, 2, 4, 4)")
+    ap.add_argument("--engine-tp", type=int, default=0, help="engine tensor-parallel degree (0 = by GPU count: 1, 1, 2, 2)")
+    ap.add_argument("--layout", default="named", choices=["named", "dp"], help="dp: plain data parallelism, engines on the trainer's weights")
     ap.add_argument("--keep-last-layers", type=int, default=-1,
                     help="layers not recomputed in the backward (uses spare HBM); -1 = as many as the first step's measured peak leaves room for")
     ap.add_argument("--reuse-rollout-logprobs", action="store_true",
@@ -114,27 +127,28 @@ def main():
     assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}"
     torch.cuda.set_device(local)
     _native.lib().ix_init()
+    if args.layout == "dp":
+        args.tp = args.tp or 1
+        args.engine_tp = args.engine_tp or args.tp
+    else:
+        args.tp = args.tp or {1: 1, 2: 2, 4: 4}.get(world, 4)
+        args.engine_tp = args.engine_tp or {1: 1, 2: 1}.get(world, 2)
     if world > 1:
         from skyrl_isoexec_b200.models.config import get_config as _gc
 
         ps = ParallelState.build(tp=args.tp, kv_rep=max(1, args.tp // _gc(args.model).num_kv_heads))
     else:
         ps = ParallelState.single()
-    if world > 1:
-        # peer-memory transports: DP gradient sum (csrc/peer_collectives.cu), fused TP GEMMs (csrc/tp_gemm_fused.cu)
-        from skyrl_isoexec_b200.models.config import get_config
-        from skyrl_isoexec_b200.parallel.transports import setup_transports
-
-        setup_transports(ps, get_config(args.model, tp_invariant=args.tp > 1) if args.tp > 1 else None, max_tokens=args.micro_tokens)
     P, S = args.prompts_per_gpu * args.tp, args.samples
+    per_engine = P * S // max(1, args.tp // args.engine_tp)       # sequences one engine serves per step
     ov = [
         f"trainer.policy.model={args.model}", f"trainer.train_batch_size={P * ps.dp}",
         f"trainer.policy_mini_batch_size={P * ps.dp}", f"generator.n_samples_per_prompt={S}",
         f"generator.sampling_params.max_generate_length={args.response_len}", "generator.sampling_params.ignore_eos=true",
         f"data.synthetic_prompt_len={args.prompt_len}", f"data.synthetic_prompts={P * ps.dp * (args.steps + args.warmup + 1)}",
         f"trainer.max_prompt_length={args.prompt_len}", f"trainer.max_tokens_per_microbatch={args.micro_tokens}",
-        f"generator.inference_engine.max_num_seqs={P * S}", "generator.inference_engine.max_num_batched_tokens=8192",
-        f"generator.inference_engine.num_kv_pages={P * S * ((args.prompt_len + args.response_len) // 128 + 2)}",
+        f"generator.inference_engine.max_num_seqs={per_engine}", "generator.inference_engine.max_num_batched_tokens=8192",
+        f"generator.inference_engine.num_kv_pages={per_engine * ((args.prompt_len + args.response_len) // 128 + 2)}",
         "trainer.policy.optimizer_config.lr=1e-6", "trainer.logger=console" if os.environ.get("BENCH_VERBOSE") else "trainer.logger=jsonl",
         "environment.env_class=even_tokens", "trainer.resume_mode=none", f"trainer.policy.keep_last_layers={args.keep_last_layers}",
     ]
@@ -143,9 +157,9 @@ def main():
     mo = {}
     if args.layers:
         mo["num_layers"] = args.layers
-    if args.tp > 1:
+    if args.tp > 1 or args.engine_tp > 1:
         mo["tp_invariant"] = True
-        ov.append(f"generator.inference_engine.tensor_parallel_size={args.tp}")
+    ov.append(f"generator.inference_engine.tensor_parallel_size={args.engine_tp}")
     if mo:
         ov.append("trainer.policy.model_overrides=" + json.dumps(mo))
     cfg = SkyRLTrainConfig.from_cli_overrides(ov)
@@ -169,7 +183,8 @@ def main():
     h2d0, d2h0 = trainer.engine.stats.get("h2d_bytes", 0), trainer.engine.stats.get("d2h_bytes", 0)
     tokens = 0
     mism = 0
-    gen_s = 0.0
+    gen_s = sync_s = 0.0
+    sync_bytes = 0
     t0 = time.perf_counter()
     e0.record()
     for _ in range(args.steps):
@@ -177,19 +192,21 @@ def main():
         tokens += int(m["generate/response_tokens"])
         mism += int(m["policy/rollout_train_logprob_bit_mismatches"])
         gen_s += float(m["timing/generate"])
+        sync_s += float(m["timing/sync_weights"])
+        sync_bytes = int(m.get("sync/bytes", 0))
     e1.record()
     sync_all()
     wall = time.perf_counter() - t0
     sampler.stop_flag = True
     sampler.join(timeout=2)
     dev_ms = e0.elapsed_time(e1)
-    stats = torch.tensor([dev_ms, wall * 1e3, float(tokens), float(mism), gen_s], dtype=torch.float64, device="cuda")
+    stats = torch.tensor([dev_ms, wall * 1e3, float(tokens), float(mism), gen_s, sync_s], dtype=torch.float64, device="cuda")
     if world > 1:
         mx = stats.clone()
         dist.all_reduce(mx, op=dist.ReduceOp.MAX)
         sm = stats.clone()
         dist.all_reduce(sm, op=dist.ReduceOp.SUM)
-        dev_ms, wall_ms, gen_s = float(mx[0]), float(mx[1]), float(mx[4])
+        dev_ms, wall_ms, gen_s, sync_s = float(mx[0]), float(mx[1]), float(mx[4]), float(mx[5])
         tokens, mism = float(sm[2]) / args.tp, float(sm[3]) / args.tp   # every rank of a TP group reports the same sequences
     else:
         wall_ms = wall * 1e3
@@ -205,11 +222,13 @@ def main():
             "dtype": "bf16", "data": "synthetic (uniform-random prompt tokens, even-token reward, random-init weights)",
             "grpo_steps_per_s": args.steps / (dev_ms / 1e3), "rollout_tok_per_s": tokens / max(1e-9, gen_s),
             "logprob_mismatches": int(mism), "kernel_status": status,
+            "sync_ms_per_step": 1e3 * sync_s / args.steps, "sync_bytes_per_rank": sync_bytes,
             "config": {"model": args.model + (f"[layers={args.layers} INVALID-DEBUG]" if args.layers else ""),
                        "global_batch": P * S * ps.dp, "prompts": P * ps.dp, "samples_per_prompt": S,
                        "prompt_len": args.prompt_len, "seq_len": args.prompt_len + args.response_len,
                        "parallelism": (f"dp{ps.dp}" + (f"xtp{args.tp}" if args.tp > 1 else "")) if world > 1 else "single",
-                       "engine": f"colocated, 1 engine per TP group, TP{args.tp}",
+                       "engine": (f"colocated, {world // args.engine_tp} engines x TP{args.engine_tp}, own layout, resharding weight sync every step"
+                                  if trainer.separate_engine else f"colocated, {world // args.tp} engines x TP{args.tp} on the trainer's weights"),
                        "scoring_forward": "skipped: rollout logprobs reused (VARIANT, not the reference's step)" if args.reuse_rollout_logprobs else "run",
                        "l2": "working set (16 GB of weights per pass) exceeds L2; no explicit flush"},
             "clocks": sampler.summary(),

@@ -53,7 +53,9 @@ class ParamStore:
 
     ALIGN = 128
 
-    def __init__(self, specs: list[ParamSpec], dtype: torch.dtype, device):
+    def __init__(self, specs: list[ParamSpec], dtype: torch.dtype, device, alloc=None):
+        """``alloc(numel, dtype, device)`` supplies the flat buffer (e.g. from symmetric memory, so that peers can read
+        the weights during a resharding weight sync); default: an ordinary zero-filled tensor."""
         off = 0
         for s in specs:
             s.offset = off
@@ -62,7 +64,8 @@ class ParamStore:
         self.specs = {s.name: s for s in specs}
         self.order = [s.name for s in specs]
         self.numel = off
-        self.flat = torch.zeros(off, dtype=dtype, device=device)
+        self.flat = alloc(off, dtype, device) if alloc is not None else torch.zeros(off, dtype=dtype, device=device)
+        assert self.flat.numel() >= off and self.flat.dtype == dtype
         self.views = {s.name: self.flat[s.offset:s.offset + math.prod(s.shape)].view(s.shape) for s in specs}
 
     def init_weights(self, seed: int, tp_rank: int = 0, tp: int = 1, ep_rank: int = 0, ep: int = 1) -> None:
@@ -240,14 +243,14 @@ class ForwardCtx:
 
 class DecoderLM(nn.Module):
     def __init__(self, cfg: ModelConfig, ps: ParallelState | None = None, device="cpu", seed: int = 0,
-                 layer_range: range | None = None, init: bool = True):
+                 layer_range: range | None = None, init: bool = True, flat_alloc=None):
         super().__init__()
         self.cfg = cfg
         self.ps = ps or ParallelState.single()
         self.device_ = torch.device(device)
         self.layer_ids = list(layer_range if layer_range is not None else range(cfg.num_layers))
         specs = build_param_specs(cfg, self.ps, layer_range)
-        self.store = ParamStore(specs, cfg.torch_dtype, self.device_)
+        self.store = ParamStore(specs, cfg.torch_dtype, self.device_, alloc=flat_alloc)
         if init:
             self.store.init_weights(seed, self.ps.tp_rank, self.ps.tp, self.ps.ep_rank, self.ps.ep)
         self.params = nn.ParameterDict()

@@ -90,6 +90,15 @@ class SharedInitInfo(WeightSyncInitInfo):
 
 
 @dataclass
+class ReshardInitInfo(WeightSyncInitInfo):
+    """Colocated engines at another tensor-parallel degree than the trainer (``sync/reshard.py``)."""
+    trainer_tp: int = 1
+
+    def strategy_type(self) -> str:
+        return "reshard"
+
+
+@dataclass
 class BroadcastInitInfo(WeightSyncInitInfo):
     group_ranks: list[int] = field(default_factory=list)   # global ranks: [trainer src] + engine ranks
     src_rank: int = 0

@@ -53,6 +53,7 @@ class PolicyConfig:
     keep_last_layers: int = 0           # layers whose activations are kept instead of recomputed in the backward;
                                         # -1 = as many as the first step's measured memory peak leaves room for
     shard_optimizer: bool = True        # dp > 1: fp32 master weights and Adam moments are cut over the data-parallel ranks
+    peer_transports: bool = True        # GPUs with peer access: fused TP GEMM+collective kernels, peer-memory DP / EP transports
 
 
 @dataclass
@@ -72,8 +73,9 @@ class SamplingConfig:
 @dataclass
 class InferenceEngineConfig:
     backend: str = "native"
-    num_engines: int = 1
-    tensor_parallel_size: int = 1
+    num_engines: int = 0                # 0 = as many as fit the job: world size / tensor_parallel_size
+    tensor_parallel_size: int = 0       # 0 = the trainer's tensor-parallel degree (engine computes with the trainer's buffer);
+                                        # another degree gives colocated engines of their own layout, fed by a resharding sync
     data_parallel_size: int = 1
     gpu_memory_utilization: float = 0.8
     max_num_batched_tokens: int = 8192
@@ -335,5 +337,15 @@ def validate_cfg(cfg: SkyRLTrainConfig, world_size: int = 1) -> None:
             raise ValueError("isoexec.enabled requires temperature=1.0, top_p=1.0, top_k=-1, min_p=0.0 for rollouts")
         if g.inference_engine.enable_prefix_caching:
             raise ValueError("isoexec.enabled pins enable_prefix_caching=false")
-    if g.inference_engine.tensor_parallel_size < 1 or g.inference_engine.num_engines < 1:
-        raise ValueError("inference engine sizes must be >= 1")
+    ie = g.inference_engine
+    if ie.tensor_parallel_size < 0 or ie.num_engines < 0:
+        raise ValueError("inference engine sizes must be >= 0 (0 = derived from the trainer layout)")
+    etp = ie.tensor_parallel_size or tp
+    if etp != tp:
+        if tp % etp:
+            raise ValueError(f"colocated engines of tensor-parallel size {etp} must nest inside the trainer's tensor-parallel "
+                             f"groups of size {tp} (the trainer degree has to be a multiple of the engine degree)")
+        if p.pipeline_model_parallel_size > 1 or p.context_parallel_size > 1 or p.expert_model_parallel_size > 1:
+            raise ValueError("engines with their own tensor-parallel degree need pp = cp = ep = 1 on the trainer")
+    if ie.num_engines not in (0, 1) and ie.num_engines * etp != world_size:
+        raise ValueError(f"num_engines={ie.num_engines} x tensor_parallel_size={etp} must cover the {world_size} GPUs of a colocated job")

@@ -135,6 +135,10 @@ class RayPPOTrainer:
         self.ps = ps or ParallelState.single()
         self.rank = dist.get_rank() if dist.is_initialized() else 0
         self.world = dist.get_world_size() if dist.is_initialized() else 1
+        if ps is not None:        # the process groups that exist are the truth; the config follows them
+            pc = cfg.trainer.policy.parallel
+            pc.tensor_model_parallel_size, pc.pipeline_model_parallel_size = self.ps.tp, self.ps.pp
+            pc.context_parallel_size, pc.expert_model_parallel_size = self.ps.cp, self.ps.ep
         validate_cfg(cfg, self.world)
         self.device = torch.device(device or ("cuda" if torch.cuda.is_available() else "cpu"))
         self.tokenizer = tokenizer
@@ -161,10 +165,60 @@ class RayPPOTrainer:
         getattr(self.callbacks, event)(self, CallbackInput(self.global_step, self.epoch, total, per_epoch, **fields), self.control)
 
     # ------------------------------------------------------------------ build
+    def _engine_layout(self, mcfg):
+        """Decide how the rollout engines are laid out. Same tensor-parallel degree as the trainer: the engine computes
+        with the trainer's own flat buffer (one engine per trainer TP group). Another degree (BASELINE-style "trainer TP4 x
+        DP2 feeding four TP2 engines"): every GPU also holds a shard of an engine of that degree, engines nest inside
+        trainer TP groups, and each sync reshards the weights (sync/reshard.py). Collective: every rank calls it."""
+        ie = self.cfg.generator.inference_engine
+        tp_e = ie.tensor_parallel_size or self.ps.tp
+        self.separate_engine = tp_e != self.ps.tp
+        self.engine_ps = self.ps
+        self.engines_per_replica = 1
+        if self.separate_engine:
+            if self.ps.tp % tp_e or self.ps.pp > 1 or self.ps.cp > 1 or self.ps.ep > 1:
+                raise ValueError(f"engine TP {tp_e} must divide trainer TP {self.ps.tp}, with pp = cp = ep = 1")
+            self.engine_ps = ParallelState.build(tp=tp_e, kv_rep=max(1, tp_e // mcfg.num_kv_heads)) if tp_e > 1 or self.world > 1 \
+                else ParallelState.single()
+            self.engines_per_replica = self.ps.tp // tp_e
+        return tp_e
+
+    def _setup_transports(self, mcfg) -> None:
+        """Peer-memory transports for every group this job computes over (GPUs with peer access only)."""
+        self.transports = {}
+        t = self.cfg.trainer
+        if self.world == 1 or self.device.type != "cuda" or not getattr(t.policy, "peer_transports", True):
+            return
+        from ..parallel import tp_fused
+        from ..parallel.transports import setup_transports
+
+        if tp_fused.get(self.ps.tp_group) is None:          # a caller may have registered them already
+            self.transports["trainer"] = setup_transports(self.ps, mcfg, max_tokens=t.max_tokens_per_microbatch)
+        if self.separate_engine and self.engine_ps.tp > 1 and tp_fused.get(self.engine_ps.tp_group) is None:
+            from ..parallel.state import ParallelState as _PS
+
+            only_tp = _PS(tp=self.engine_ps.tp, tp_rank=self.engine_ps.tp_rank, tp_group=self.engine_ps.tp_group,
+                          tp_ranks=self.engine_ps.tp_ranks)
+            self.transports["engine"] = setup_transports(only_tp, mcfg, max_tokens=self.cfg.generator.inference_engine.max_num_batched_tokens)
+
     def build_models(self) -> None:
         t, g = self.cfg.trainer, self.cfg.generator
-        mcfg = get_config(t.policy.model, **t.policy.model_overrides)
-        model = DecoderLM(mcfg, self.ps, self.device, seed=t.policy.seed)
+        mo = dict(t.policy.model_overrides)
+        tp_e_cfg = g.inference_engine.tensor_parallel_size or self.ps.tp
+        if tp_e_cfg != self.ps.tp:
+            mo.setdefault("tp_invariant", True)     # two degrees, one set of bits: the K reductions use the leaf tree
+        mcfg = get_config(t.policy.model, **mo)
+        tp_e = self._engine_layout(mcfg)
+        self._setup_transports(mcfg)
+        flat_alloc = self._flat_rendezvous = None
+        if self.separate_engine and self.device.type == "cuda" and self.ps.tp > 1 and g.inference_engine.weight_sync_backend != "nccl_gather":
+            from ..parallel import nccl_runtime
+
+            if nccl_runtime.capabilities()["symmetric_memory"]:
+                from ..sync.reshard import symmetric_flat_allocator
+
+                flat_alloc, self._flat_rendezvous = symmetric_flat_allocator(self.ps.tp_group)
+        model = DecoderLM(mcfg, self.ps, self.device, seed=t.policy.seed, flat_alloc=flat_alloc)
         wcfg = WorkerConfig(max_tokens_per_microbatch=t.max_tokens_per_microbatch, optimizer=t.policy.optimizer_config,
                             keep_last_layers=t.policy.keep_last_layers, shard_optimizer=t.policy.shard_optimizer,
                             want_entropy=t.algorithm.use_entropy_loss)
@@ -194,11 +248,18 @@ class RayPPOTrainer:
         ie = g.inference_engine
         ecfg = EngineConfig(max_num_seqs=ie.max_num_seqs, max_num_batched_tokens=ie.max_num_batched_tokens,
                             num_kv_pages=ie.num_kv_pages, gpu_memory_utilization=ie.gpu_memory_utilization,
-                            seed=t.seed + 7919 * self.ps.dp_rank, enable_prefix_caching=ie.enable_prefix_caching,   # one sampler stream per DP replica
+                            # one sampler stream per engine; the ranks of one engine share it
+                            seed=t.seed + 7919 * (self.engine_ps.dp_rank if self.separate_engine else self.ps.dp_rank),
+                            enable_prefix_caching=ie.enable_prefix_caching,
                             use_cuda_graph=not ie.enforce_eager,
                             max_model_len=min(mcfg.max_position, t.max_prompt_length + g.sampling_params.max_generate_length + 1))
-        # colocated, same TP layout: the engine computes with the trainer's flat parameter buffer
-        self.engine = LLMEngine(model, ecfg)
+        if self.separate_engine:
+            # engines of their own layout: a second set of (sharded) weights per GPU, filled by the resharding sync
+            emodel = DecoderLM(mcfg, self.engine_ps, self.device, seed=t.policy.seed, init=False)
+            self.engine = LLMEngine(emodel, ecfg)
+        else:
+            # colocated, same TP layout: the engine computes with the trainer's flat parameter buffer
+            self.engine = LLMEngine(model, ecfg)
         self.infer = NativeInferenceEngine(self.engine, self.tokenizer)
         self.generator = SkyRLGymGenerator(self.infer, self.tokenizer, max_turns=g.max_turns, batched=g.batched,
                                            env_config=self.cfg.environment.env_kwargs,
@@ -206,10 +267,9 @@ class RayPPOTrainer:
                                            apply_overlong_filtering=g.apply_overlong_filtering,
                                            rate_limit=g.rate_limit or None, step_wise=g.step_wise_trajectories)
         if t.isoexec.enabled:
-            self.adapter_trainer = ContractAdapter("trainer", model, self.rank, engine_tp=ie.tensor_parallel_size
-                                                   if not ie.run_engines_locally else self.ps.tp)
+            self.adapter_trainer = ContractAdapter("trainer", model, self.rank, trainer_tp=self.ps.tp, engine_tp=tp_e)
             self.adapter_trainer.run_install()
-            self.adapter_engine = ContractAdapter("engine", model, self.rank)
+            self.adapter_engine = ContractAdapter("engine", self.engine.model, self.rank, trainer_tp=self.ps.tp, engine_tp=tp_e)
             self.adapter_engine.run_install()
         if self.dataset is None:
             d = self.cfg.data
@@ -222,9 +282,24 @@ class RayPPOTrainer:
 
     def init_weight_sync_state(self) -> None:
         """Stamp the trainer's contract hash on the init message; the engine's receiver refuses a mismatch."""
-        info = S.create_init_info("shared") if self.cfg.trainer.isoexec.enabled else S.SharedInitInfo(contract_hash=None)
+        iso = self.cfg.trainer.isoexec.enabled
+        self.resharder = None
+        if self.separate_engine:
+            from ..sync import reshard as R
+
+            info = S.ReshardInitInfo(contract_hash=P.contract_hash() if iso else None, engine_tp=self.engine_ps.tp, trainer_tp=self.ps.tp)
+            if iso:
+                P.assert_init_info_contract(info)          # engine side of the handshake
+            if self._flat_rendezvous is not None:
+                ptrs, self._flat_handle = self._flat_rendezvous(self.policy.model.store.flat)
+                self.resharder = R.PeerPullResharder(self.policy.model, self.engine.model, self.ps.tp_group, self.ps.tp_rank, ptrs)
+            else:
+                self.resharder = R.CollectiveResharder(self.policy.model, self.engine.model, self.ps.tp_group, self.ps.tp_rank)
+            self.sync_info = info
+            return
+        info = S.create_init_info("shared") if iso else S.SharedInitInfo(contract_hash=None)
         self.sync_info = info
-        if self.cfg.trainer.isoexec.enabled:
+        if iso:
             self.receiver = S.create_receiver(info, self.engine.model)
         self.sender = S.create_sender(info, self.policy.model)
 
@@ -247,7 +322,34 @@ class RayPPOTrainer:
         return gi, uids
 
     def generate(self, gi: GeneratorInput) -> GeneratorOutput:
-        return asyncio.run(self.generator.generate(gi))
+        if self.engines_per_replica == 1:
+            return asyncio.run(self.generator.generate(gi))
+        # several engines serve one trainer replica: each takes a contiguous slice of the replica's requests, then the
+        # slices are exchanged inside the trainer's tensor-parallel group so that every rank trains on the whole batch
+        from .generator import get_rollout_metrics
+        from .trainer_utils import _cat, _take
+
+        k, n = self.engines_per_replica, len(gi["prompts"])
+        e = self.ps.tp_rank // self.engine_ps.tp
+        lo, hi = e * n // k, (e + 1) * n // k
+        part = dict(gi)
+        for key in ("prompts", "env_classes", "env_extras", "trajectory_ids"):
+            if isinstance(gi.get(key), list):
+                part[key] = gi[key][lo:hi]
+        go = asyncio.run(self.generator.generate(part))
+        go.pop("rollout_metrics", None)
+        box = [None] * self.ps.tp
+        dist.all_gather_object(box, go if self.engine_ps.tp_rank == 0 else None, group=self.ps.tp_group)
+        merged = None
+        for g_ in box:
+            if g_ is not None:
+                merged = _cat(merged, g_)
+        assert merged is not None and len(merged["response_ids"]) == n or self.cfg.generator.step_wise_trajectories
+        last = merged.get("is_last_step") or [True] * len(merged["response_ids"])
+        sel = [i for i, f in enumerate(last) if f]
+        merged["rollout_metrics"] = get_rollout_metrics([merged["response_ids"][i] for i in sel], [merged["rewards"][i] for i in sel],
+                                                        [merged["env_metrics"][i] for i in sel] if merged.get("env_metrics") else None)
+        return merged
 
     def convert_to_training_input(self, go: GeneratorOutput, uids: list[str]) -> TrainingInputBatch:
         seq, att, rmask = build_sequences(go["prompt_token_ids"], go["response_ids"])
@@ -465,6 +567,15 @@ class RayPPOTrainer:
         """Trainer -> rollout. Same process and layout: the flat buffer is shared, so the transfer is
         the handshake, the state invalidation and the verification that the alias still holds."""
         iso = self.cfg.trainer.isoexec.enabled
+        if self.separate_engine:
+            self.all_metrics["sync/bytes"] = self.resharder.sync()
+            self.all_metrics["sync/bytes_from_peers"] = self.resharder.remote_bytes
+            if iso:
+                h = P.contract_hash(self.adapter_trainer.contract)
+                self.adapter_engine.on_weight_sync(self.sync_info.contract_hash, [s.state_id for s in self.adapter_engine.contract.claims.state])
+                self.adapter_trainer.on_weight_sync(P.contract_hash(self.adapter_engine.contract) if h else None)
+            self.engine.reset_prefix_cache()
+            return
         req = self.sender.send_chunks(S.extract_native_weights(self.policy.model, None))
         if iso:
             n = S.load_weights(self.engine.model, ((k, v) for k, v in self.receiver.receive_weights(req)))
