@@ -79,7 +79,7 @@ __global__ void __launch_bounds__(256) reshard_pull_kernel(const ReshardDesc* __
 
 }  // namespace
 
-// descs: DEVICE array of n_desc records laid out as ReshardDesc (48 bytes each). Every address is valid in this
+// descs: DEVICE array of n_desc records laid out as ReshardDesc (56 bytes each). Every address is valid in this
 // process on the current device (local memory or peer-mapped symmetric memory). Pieces must not overlap in the
 // destination. Returns 0 or an error code.
 IX_API int ix_reshard_pull(const void* descs, int n_desc, void* stream) {

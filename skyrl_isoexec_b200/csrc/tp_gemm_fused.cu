@@ -52,7 +52,14 @@ struct TpParams {
   const void* a_local;          // AG: this rank's rows of A (bf16 [Ml, lda_local])
   int lda_local, m_local;       // AG
   int rank, W, mode, out_f32;
-  uint32_t epoch;
+  uint32_t epoch;               // the call's epoch; with epoch_word set, an OFFSET added to the value of that word
+  // A call recorded in a CUDA graph cannot carry its epoch as an argument (a replay would repeat it). Such a call
+  // passes the address of a device word that the host sets before every replay, the call's position in the graph as
+  // `epoch`, BASE addresses of the double-buffered staging and flag arrays, and the sizes of one half; the kernel
+  // derives the epoch and the half from the word. One-shot all-reduce (AR1) only.
+  const uint32_t* epoch_word;
+  long long stage_half;         // floats per staging half
+  long long flags_half;         // flags per half
 };
 
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
@@ -186,9 +193,9 @@ __device__ __forceinline__ void fold_leaves(uint32_t taddr, int leaf_stride, flo
 
 // Reducer body for one tile, W ranks: out = tree over ranks of the W staged partials.
 template <int BN, int W>
-__device__ __forceinline__ void reduce_tile(const TpParams& p, int slot, int m_blk, int n_blk, int M, int ldc, void* c_local,
-                                            int tid) {
-  const float* base = p.stage[p.rank] + static_cast<size_t>(slot) * W * (BM * BN);
+__device__ __forceinline__ void reduce_tile(const TpParams& p, size_t st_off, int slot, int m_blk, int n_blk, int M, int ldc,
+                                            void* c_local, int tid) {
+  const float* base = p.stage[p.rank] + st_off + static_cast<size_t>(slot) * W * (BM * BN);
   constexpr int kVecPerRow = BN / 4;
   const int row_base = (p.mode == TP_RS) ? (m_blk - p.rank * ((M + BM - 1) / BM / W)) * BM : m_blk * BM;
   const int rows_valid = min(BM, M - m_blk * BM);
@@ -253,6 +260,10 @@ tp_gemm_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
   tm.rows_per = tm.tiles_m / p.W;
   tm.nb = p.m_local / BM;
   const int num_q = tm.num_q();
+  // epoch and staging half of this call (see TpParams::epoch_word); the half of call e is (e - 1) & 1 in both forms
+  const uint32_t epoch = p.epoch_word ? (*p.epoch_word + p.epoch) : p.epoch;
+  const size_t st_off = p.epoch_word ? static_cast<size_t>((epoch - 1u) & 1u) * static_cast<size_t>(p.stage_half) : 0;
+  const size_t fl_off = p.epoch_word ? static_cast<size_t>((epoch - 1u) & 1u) * static_cast<size_t>(p.flags_half) : 0;
   const int num_kb = K / BK;
   const int kb_per_leaf = num_kb / L;
 
@@ -295,7 +306,7 @@ tp_gemm_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
           // rows of this block were pushed by rank `owner`'s copier warps (generic proxy, remote) in kCopySplit pieces
           bool arrived = true;
           for (int sub = 0; sub < kCopySplit && arrived; ++sub)
-            arrived = wait_flag(p.flags[p.rank] + (owner * tm.nb + slot) * kCopySplit + sub, p.epoch, abort_flag, status);
+            arrived = wait_flag(p.flags[p.rank] + fl_off + (owner * tm.nb + slot) * kCopySplit + sub, epoch, abort_flag, status);
           if (!arrived) break;
           fence_proxy_async_global();
         }
@@ -422,7 +433,7 @@ tp_gemm_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
             if (m_blk * BM + quad * 32 + r < M) {
               const size_t off = tile_off + static_cast<size_t>(quad * 32 + r) * BN + 4 * u;
 #pragma unroll 1
-              for (int d = d0; d < d1; ++d) __stcs(reinterpret_cast<float4*>(p.stage[d] + off), v);   // streaming: keep A/B tiles in L2
+              for (int d = d0; d < d1; ++d) __stcs(reinterpret_cast<float4*>(p.stage[d] + st_off + off), v);   // streaming: keep A/B tiles in L2
             }
           }
         }
@@ -440,7 +451,7 @@ tp_gemm_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
           const int d0 = (p.mode == TP_AR1) ? 0 : owner, d1 = (p.mode == TP_AR1) ? p.W : owner + 1;
           if (stored && lane < d1 - d0) {
             __threadfence_system();
-            st_release_sys(p.flags[d0 + lane] + slot * p.W + p.rank, p.epoch);
+            st_release_sys(p.flags[d0 + lane] + fl_off + slot * p.W + p.rank, epoch);
           }
           if (!stored) break;
         }
@@ -483,7 +494,7 @@ tp_gemm_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         named_bar(2, 128);
         if (tid == 0) {
           __threadfence_system();
-          st_release_sys(p.flags[d] + (p.rank * tm.nb + b) * kCopySplit + sub, p.epoch);
+          st_release_sys(p.flags[d] + fl_off + (p.rank * tm.nb + b) * kCopySplit + sub, epoch);
         }
       }
     } else if (p.mode != TP_LOCAL) {
@@ -493,14 +504,14 @@ tp_gemm_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         if (!tm.owned(i, m_blk, n_blk)) break;
         if (tid == 0) s_ok = 1;
         named_bar(2, 128);
-        if (tid < p.W && !wait_flag(p.flags[p.rank] + i * p.W + tid, p.epoch, abort_flag, status)) s_ok = 0;
+        if (tid < p.W && !wait_flag(p.flags[p.rank] + fl_off + i * p.W + tid, epoch, abort_flag, status)) s_ok = 0;
         named_bar(2, 128);
         if (!s_ok) break;
         switch (p.W) {
-          case 1: reduce_tile<BN, 1>(p, i, m_blk, n_blk, M, ldc, c_local, tid); break;
-          case 2: reduce_tile<BN, 2>(p, i, m_blk, n_blk, M, ldc, c_local, tid); break;
-          case 4: reduce_tile<BN, 4>(p, i, m_blk, n_blk, M, ldc, c_local, tid); break;
-          case 8: reduce_tile<BN, 8>(p, i, m_blk, n_blk, M, ldc, c_local, tid); break;
+          case 1: reduce_tile<BN, 1>(p, st_off, i, m_blk, n_blk, M, ldc, c_local, tid); break;
+          case 2: reduce_tile<BN, 2>(p, st_off, i, m_blk, n_blk, M, ldc, c_local, tid); break;
+          case 4: reduce_tile<BN, 4>(p, st_off, i, m_blk, n_blk, M, ldc, c_local, tid); break;
+          case 8: reduce_tile<BN, 8>(p, st_off, i, m_blk, n_blk, M, ldc, c_local, tid); break;
           default: break;
         }
       }
@@ -513,10 +524,10 @@ tp_gemm_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
           if (arrived + 1 == gridDim.x) {
             *p.local_ctr = 0;
             __threadfence_system();
-            for (int d = 0; d < p.W; ++d) st_release_sys(p.done[d] + p.rank, p.epoch);
+            for (int d = 0; d < p.W; ++d) st_release_sys(p.done[d] + p.rank, epoch);
           }
         }
-        if (blockIdx.x == 0 && tid < p.W) wait_flag(p.done[p.rank] + tid, p.epoch, abort_flag, status);
+        if (blockIdx.x == 0 && tid < p.W) wait_flag(p.done[p.rank] + tid, epoch, abort_flag, status);
       }
     }
   }
@@ -581,10 +592,13 @@ IX_API long long ix_tp_stage_floats(int M, int N, int mode, int W, int bn) {
 // AG: ignored, rows come from a_local through the gathered buffers), B: this rank's weight shard [N, K].
 // stage/flags/peer_out/done: W device addresses each (as mapped in THIS process), already offset to the call's
 // parity half. leaves: L (K / 64 must be divisible by L). bn: 32/64/128 with 2*L*bn <= 512.
-IX_API int ix_tp_gemm_fused(const void* A, const void* B, void* c_local, int M, int N, int K, int lda, int ldb, int ldc,
+static int tp_gemm_fused_impl(const void* A, const void* B, void* c_local, int M, int N, int K, int lda, int ldb, int ldc,
                             int mode, int leaves, int bn, int out_f32, int rank, int W, unsigned epoch,
                             const long long* stage, const long long* flags, const long long* peer_out, const long long* done,
-                            void* local_ctr, const void* a_local, int lda_local, int m_local, void* stream) {
+                            void* local_ctr, const void* a_local, int lda_local, int m_local, void* stream,
+                            const void* epoch_word, long long stage_half, long long flags_half) {
+  if (epoch_word != nullptr && mode != TP_AR1)
+    return ixh::fail(ixh::IX_EARG, "tp_gemm: a device epoch word (graph capture) is supported by the one-shot all-reduce only");
   if (M <= 0 || N <= 0 || K <= 0) return ixh::fail(ixh::IX_EARG, "tp_gemm: empty problem");
   if ((lda & 7) || (ldb & 7) || (ldc & 7) || leaves < 1 || (K % (BK * leaves)) != 0) return ixh::fail(ixh::IX_EARG, "tp_gemm: K=%d must split into %d leaves of whole 64-blocks", K, leaves);
   if (N % bn) return ixh::fail(ixh::IX_EARG, "tp_gemm: N=%d not a multiple of the tile width %d", N, bn);
@@ -607,6 +621,7 @@ IX_API int ix_tp_gemm_fused(const void* A, const void* B, void* c_local, int M, 
   p.local_ctr = static_cast<unsigned int*>(local_ctr);
   p.a_local = a_local, p.lda_local = lda_local, p.m_local = m_local > 0 ? m_local : BM;
   p.rank = rank, p.W = W, p.mode = mode, p.out_f32 = out_f32, p.epoch = epoch;
+  p.epoch_word = static_cast<const uint32_t*>(epoch_word), p.stage_half = stage_half, p.flags_half = flags_half;
   int a_rows = (M + 7) & ~7;
   if (a_rows > BM) a_rows = BM;
   CUtensorMap tmA, tmA2, tmB;
@@ -625,4 +640,36 @@ IX_API int ix_tp_gemm_fused(const void* A, const void* B, void* c_local, int M, 
   IX_TP(256, 1) IX_TP(128, 1) IX_TP(128, 2) IX_TP(64, 1) IX_TP(64, 2) IX_TP(64, 4) IX_TP(32, 1) IX_TP(32, 2) IX_TP(32, 4) IX_TP(32, 8)
 #undef IX_TP
   return ixh::fail(ixh::IX_EARG, "tp_gemm: no kernel for bn=%d leaves=%d (need 2*leaves*bn <= 512)", bn, leaves);
+}
+
+IX_API int ix_tp_gemm_fused(const void* A, const void* B, void* c_local, int M, int N, int K, int lda, int ldb, int ldc,
+                            int mode, int leaves, int bn, int out_f32, int rank, int W, unsigned epoch,
+                            const long long* stage, const long long* flags, const long long* peer_out, const long long* done,
+                            void* local_ctr, const void* a_local, int lda_local, int m_local, void* stream) {
+  return tp_gemm_fused_impl(A, B, c_local, M, N, K, lda, ldb, ldc, mode, leaves, bn, out_f32, rank, W, epoch, stage, flags, peer_out,
+                            done, local_ctr, a_local, lda_local, m_local, stream, nullptr, 0, 0);
+}
+
+// One-shot GEMM -> all-reduce in a form that a CUDA graph can record: the epoch of the call is
+// *epoch_word + epoch_offset, read on the device; stage/flags are the BASE addresses of the double-buffered arrays
+// (W each) and stage_half / flags_half the element counts of one half. The host sets the word (ix_tp_set_epoch) to the
+// epoch of the last call made before the replay and then accounts for the calls the graph contains.
+IX_API int ix_tp_gemm_ar1_graph(const void* A, const void* B, void* c_local, int M, int N, int K, int lda, int ldb, int ldc,
+                                int leaves, int bn, int out_f32, int rank, int W, const void* epoch_word, unsigned epoch_offset,
+                                const long long* stage, const long long* flags, long long stage_half, long long flags_half,
+                                void* stream) {
+  if (epoch_word == nullptr) return ixh::fail(ixh::IX_EARG, "tp_gemm_ar1_graph: no epoch word");
+  return tp_gemm_fused_impl(A, B, c_local, M, N, K, lda, ldb, ldc, TP_AR1, leaves, bn, out_f32, rank, W, epoch_offset, stage, flags,
+                            nullptr, nullptr, nullptr, nullptr, 0, 0, stream, epoch_word, stage_half, flags_half);
+}
+
+namespace {
+__global__ void set_word_kernel(uint32_t* w, uint32_t v) { *w = v; }
+}  // namespace
+
+IX_API int ix_tp_set_epoch(void* epoch_word, unsigned value, void* stream) {
+  if (epoch_word == nullptr) return ixh::fail(ixh::IX_EARG, "tp_set_epoch: null word");
+  set_word_kernel<<<1, 1, 0, reinterpret_cast<cudaStream_t>(stream)>>>(static_cast<uint32_t*>(epoch_word), value);
+  IX_CUDA(cudaGetLastError());
+  return 0;
 }

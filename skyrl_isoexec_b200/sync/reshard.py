@@ -200,10 +200,11 @@ class PeerPullResharder(_Base):
         self.lib = _native.lib()
         self.lib.ix_reshard_pull.argtypes = [C.c_void_p, C.c_int, C.c_void_p]
         self.lib.ix_reshard_pull.restype = C.c_int
-        assert self.lib.ix_reshard_desc_bytes() == 48
+        fmt = "<QQqqqqii"
+        assert self.lib.ix_reshard_desc_bytes() == struct.calcsize(fmt), "descriptor layout differs between host and kernel"
         es = self.e.store.flat.element_size()
         dst0 = self.e.store.flat.data_ptr()
-        recs = [struct.pack("<QQqqqqii", peer_ptrs[p.src_rank] + p.src_off * es, dst0 + p.dst_off * es, p.rows, p.row_elems * es,
+        recs = [struct.pack(fmt, peer_ptrs[p.src_rank] + p.src_off * es, dst0 + p.dst_off * es, p.rows, p.row_elems * es,
                             p.src_pitch * es, p.dst_pitch * es, 0, 0) for p in self.pieces]
         self.n_desc = len(recs)
         self.descs = torch.frombuffer(bytearray(b"".join(recs)), dtype=torch.uint8).to(self.e.store.flat.device)

@@ -22,6 +22,23 @@ def _free_port():
     return p
 
 
+def _collect(q, procs, n=1, timeout=500):
+    """n results from the ranks' queue; gives up at once when a rank has died instead of waiting out the timeout."""
+    import queue as _queue
+    import time as _time
+
+    out, t0 = [], _time.time()
+    while len(out) < n:
+        try:
+            out.append(q.get(timeout=2))
+        except _queue.Empty:
+            if any((not p.is_alive()) and p.exitcode not in (0, None) for p in procs):
+                raise AssertionError("a rank exited with an error: " + str([p.exitcode for p in procs]))
+            if _time.time() - t0 > timeout:
+                raise AssertionError("timed out waiting for the ranks")
+    return out
+
+
 def _ngpu():
     return torch.cuda.device_count() if torch.cuda.is_available() else 0
 
@@ -105,7 +122,7 @@ def test_peer_collectives_two_ranks():
     procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
     for p in procs:
         p.start()
-    res = q.get(timeout=500)
+    res = _collect(q, procs, 1, 500)[0]
     for p in procs:
         p.join(timeout=120)
     print("peer collectives:", res)
@@ -243,7 +260,7 @@ def test_fused_tp_gemm_matches_single_rank_tree_bitwise():
     procs = [ctx.Process(target=_tp_worker, args=(r, world, port, q)) for r in range(world)]
     for p in procs:
         p.start()
-    res = q.get(timeout=500)
+    res = _collect(q, procs, 1, 500)[0]
     for p in procs:
         p.join(timeout=120)
     print("fused tp gemm:", res)
@@ -358,7 +375,7 @@ def test_expert_parallel_over_peer_memory_equals_single_rank_bitwise():
     procs = [ctx.Process(target=_ep_worker, args=(r, world, port, q)) for r in range(world)]
     for p in procs:
         p.start()
-    res = q.get(timeout=500)
+    res = _collect(q, procs, 1, 500)[0]
     for p in procs:
         p.join(timeout=120)
     print("expert parallel over peer memory:", res)
@@ -435,7 +452,7 @@ def test_tensor_parallel_model_with_fused_kernels_is_bitwise_tp_invariant():
     procs = [ctx.Process(target=_tp_model_worker, args=(r, 2, port, q)) for r in range(2)]
     for p in procs:
         p.start()
-    res = q.get(timeout=500)
+    res = _collect(q, procs, 1, 500)[0]
     for p in procs:
         p.join(timeout=120)
     print("tp model:", res)
@@ -509,9 +526,79 @@ def test_moe_model_with_expert_parallelism_over_peer_memory():
     procs = [ctx.Process(target=_ep_model_worker, args=(r, 2, port, q)) for r in range(2)]
     for p in procs:
         p.start()
-    res = q.get(timeout=500)
+    res = _collect(q, procs, 1, 500)[0]
     for p in procs:
         p.join(timeout=120)
     print("moe ep model:", res)
     assert res["registered"]["ep"] and res["mismatches"] == [0, 0] and res["status"] == [0, 0]
     assert res["grad_norms"][0] == res["grad_norms"][1] > 0
+
+
+def _separate_engine_worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank), NCCL_NVLS_ENABLE="0")
+    import torch.distributed as dist
+
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank), timeout=_PG_TIMEOUT)
+    try:
+        import json
+
+        from skyrl_isoexec_b200.ops import _native
+        from skyrl_isoexec_b200.parallel.state import ParallelState
+        from skyrl_isoexec_b200.sync.reshard import PeerPullResharder
+        from skyrl_isoexec_b200.train.config import SkyRLTrainConfig
+        from skyrl_isoexec_b200.train.trainer import RayPPOTrainer
+
+        _native.lib().ix_init()
+        ps = ParallelState.build(tp=world)
+        mo = {"hidden_size": 1024, "num_q_heads": 8, "num_kv_heads": 4, "head_dim": 128, "ffn_size": 2048, "num_layers": 2, "pik_leaves": 8}
+        cfg = SkyRLTrainConfig.from_cli_overrides([
+            "trainer.policy.model=tiny-qwen3-bf16", "trainer.policy.model_overrides=" + json.dumps(mo),
+            "trainer.train_batch_size=4", "trainer.policy_mini_batch_size=4", "generator.n_samples_per_prompt=4",
+            "generator.sampling_params.max_generate_length=40", "generator.sampling_params.ignore_eos=true",
+            "data.synthetic_prompt_len=200", "data.synthetic_prompts=32", "trainer.max_prompt_length=200",
+            "generator.inference_engine.num_kv_pages=64", "generator.inference_engine.max_num_batched_tokens=1024",
+            "trainer.max_tokens_per_microbatch=1024", "trainer.policy.optimizer_config.lr=1e-3", "trainer.logger=jsonl",
+            f"generator.inference_engine.tensor_parallel_size={world // 2}"])
+        tr = RayPPOTrainer(cfg, ps=ps, device=f"cuda:{rank}")
+        tr.build_models()
+        tr.sync_weights()
+        it = iter(tr.loader)
+        out = {"mism": [], "bytes": [], "far": [], "sync_s": [], "peer_pull": isinstance(tr.resharder, PeerPullResharder),
+               "engines": tr.engines_per_replica}
+        for _ in range(3):
+            m = tr.train_step(next(it))
+            out["mism"].append(int(m["policy/rollout_train_logprob_bit_mismatches"]))
+            out["bytes"].append(int(m["sync/bytes"]))
+            out["far"].append(int(m["sync/bytes_from_peers"]))
+            out["sync_s"].append(float(m["timing/sync_weights"]))
+        out["status"] = _native.read_status()
+        q.put((rank, out))
+    finally:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+@pytest.mark.timeout(600)
+def test_trainer_tp_feeds_engines_of_half_the_degree_through_the_peer_pull_sync():
+    """Trainer at TP = all GPUs, engines at half that degree (TP2 -> two TP1 engines on 2 GPUs, TP4 -> two TP2 engines on
+    4): three full GRPO steps; every step reshards the updated weights with ONE pull kernel over peer memory, and the
+    engines' rollout logprobs equal the trainer's scoring forward bit for bit."""
+    world = 2 if _ngpu() < 4 else 4
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_separate_engine_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = dict(_collect(q, procs, world))
+    for p in procs:
+        p.join(timeout=120)
+    print("separate engines:", res[0])
+    for r in range(world):
+        o = res[r]
+        assert o["peer_pull"] and o["engines"] == 2 and o["status"] == 0
+        assert o["mism"] == [0, 0, 0], (r, o["mism"])
+        assert all(b > 0 for b in o["bytes"]) and all(0 < f < b for f, b in zip(o["far"], o["bytes"]))
