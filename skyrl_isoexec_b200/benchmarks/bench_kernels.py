@@ -79,6 +79,15 @@ def main(argv=None):
             t = timeit(lambda: F.gemm_nt(xl, w), do_flush=False)
             tf = 2 * M * N * K / t / 1e6
             rows.append({"kernel": "gemm_train", "case": f"{name} M={M} N={N} K={K}", "us": t, "tflops": tf, "frac_of_measured": tf / peaks["bf16_tflops"]})
+            # the two gradients of the same layer: dX = dY @ W (NN), dW = dY^T @ X (TN); library time beside ours
+            dy = torch.randn(M, N, device=dev).bfloat16()
+            for kern, ours, lib in (("gemm_bwd_dx", lambda: F.gemm_nn(dy, w), lambda: torch.matmul(dy, w)),
+                                    ("gemm_bwd_dw", lambda: F.gemm_tn(dy, xl), lambda: torch.matmul(dy.t(), xl))):
+                t, tl = timeit(ours, do_flush=False), timeit(lib, do_flush=False)
+                tf = 2 * M * N * K / t / 1e6
+                rows.append({"kernel": kern, "case": f"{name} M={M} N={N} K={K}", "us": t, "tflops": tf,
+                             "frac_of_measured": tf / peaks["bf16_tflops"], "library_us": tl})
+            del dy
     for kv_len in (512, 1536, 2560):
         npg = (kv_len + 127) // 128
         kc = torch.randn(B * npg * 128, Hkv, D, device=dev).bfloat16()
@@ -111,6 +120,8 @@ def main(argv=None):
     for row in rows:
         extra = f"{row['tbs']:.2f} TB/s" if "tbs" in row else (f"{row['tflops']:.0f} TFLOP/s" if "tflops" in row else "")
         frac = f"  {row['frac_of_measured']:.2f} of measured" if "frac_of_measured" in row else ""
+        if "library_us" in row:
+            frac += f"  (torch.matmul {row['library_us']:.1f} us)"
         print(f"{row['kernel']:18s} {row['case']:36s} {row['us']:9.1f} us  {extra}{frac}")
     assert _native.read_status() == 0
     if args.json:

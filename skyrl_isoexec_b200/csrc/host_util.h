@@ -98,6 +98,13 @@ inline int make_tmap(CUtensorMap* out, CUtensorMapDataType dt, int rank, const v
   }
   CUresult r = fn(out, dt, rank, const_cast<void*>(base), d, s, b, es, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r == CUDA_ERROR_INVALID_CONTEXT || r == CUDA_ERROR_NOT_INITIALIZED) {
+    // a thread that has made no runtime call yet (an autograd worker's first op) has no context bound: bind the
+    // device's primary context and encode again
+    cudaFree(nullptr);
+    r = fn(out, dt, rank, const_cast<void*>(base), d, s, b, es, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
+           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  }
   if (r != CUDA_SUCCESS) return fail(IX_EDRV, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
   return IX_OK;
 }

@@ -48,6 +48,7 @@ class DecodeGraph:
         self.ids = d[self.o_ids:]
         self.graph = None
         self.logits = None
+        self.tp_calls = 0
 
     @property
     def host(self):
@@ -60,17 +61,33 @@ class DecodeGraph:
         hidden = eng.model(self.ids, fc)
         return eng.model.logits(hidden)
 
+    def _fused_tp(self):
+        """The engine's fused tensor-parallel runtime, if its row-parallel GEMMs run as GEMM -> all-reduce kernels."""
+        ps = self.engine.model.ps
+        if ps.tp == 1:
+            return None
+        from ..parallel import tp_fused
+
+        return tp_fused.get(ps.tp_group)
+
     def capture(self):
-        # warm-up on a side stream (sets function attributes, fills allocator pools), then capture
+        # warm-up on a side stream (sets function attributes, fills allocator pools, runs the per-shape admission probes
+        # of the fused tensor-parallel kernels, which compare on the host), then capture
         s = torch.cuda.Stream(device=self.engine.device)
         s.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(s), torch.no_grad():
             self._forward()
         torch.cuda.current_stream().wait_stream(s)
         torch.cuda.synchronize()
+        rt = self._fused_tp()
         self.graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(self.graph), torch.no_grad():
-            self.logits = self._forward()
+        if rt is not None:
+            rt.begin_capture()       # calls are recorded with their epoch read from a device word
+        try:
+            with torch.cuda.graph(self.graph), torch.no_grad():
+                self.logits = self._forward()
+        finally:
+            self.tp_calls = rt.end_capture() if rt is not None else 0
 
     def fill(self, ids, pos, slots, items, bt_rows):
         """Write the next step's inputs into the free staging buffer. ``ids`` None: the tokens are on the device."""
@@ -91,5 +108,7 @@ class DecodeGraph:
         n = self.words if self._with_ids else self.o_ids
         self.dev[:n].copy_(self.hosts[self.parity][:n], non_blocking=True)
         self.engine.stats["h2d_bytes"] += n * 4
+        if self.tp_calls:
+            self._fused_tp().before_replay(self.tp_calls)
         self.graph.replay()
         return self.logits

@@ -355,8 +355,18 @@ class LLMEngine:
 
     # ------------------------------------------------------------------ CUDA-graph decode
     def _graphs_enabled(self) -> bool:
-        return (self.cfg.use_cuda_graph and self.device.type == "cuda" and not self.mcfg.has_moe
-                and not self.mcfg.has_gdn and self.model.ps.tp == 1)
+        """Decode steps are replayed from a CUDA graph unless the model has a layer whose decode is not host-free yet
+        (MoE routing with host-side counts, GatedDeltaNet state slots). Tensor parallelism: the row-parallel GEMMs must be
+        served by the fused peer-memory kernel (its graph form reads the epoch from a device word); with the NCCL
+        transport the step stays eager."""
+        if not (self.cfg.use_cuda_graph and self.device.type == "cuda") or self.mcfg.has_moe or self.mcfg.has_gdn:
+            return False
+        ps = self.model.ps
+        if ps.tp > 1:
+            from ..parallel import tp_fused
+
+            return tp_fused.get(ps.tp_group) is not None and bool(getattr(self.mcfg, "tp_invariant", False))
+        return True
 
     def _launch_decode(self, decode: list[Sequence], ahead: bool) -> dict:
         """Enqueue (copy, graph replay, sampling, device-side token feedback, D2H of the results) for one decode step
@@ -383,6 +393,10 @@ class LLMEngine:
             g.dev.copy_(g.host)
             g.capture()
         logits = g.run()
+        if self.model.ps.tp > 1:          # vocabulary shards -> full rows (bytes only; outside the graph)
+            from ..parallel.tp import column_parallel_gather
+
+            logits = column_parallel_gather(logits, self.model.ps)
         tokens, lps = self.sampler(logits, [s.params for s in decode])
         g.ids.copy_(tokens)                       # next replay's input, device to device
         k = self._res_parity = self._res_parity ^ 1

@@ -29,6 +29,8 @@ _SIGS = {
     "ix_read_status": [],
     "ix_version": [],
     "ix_gemm_bf16_nt": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P],
+    "ix_gemm_bf16_nn": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
+    "ix_gemm_bf16_tn": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
     "ix_rmsnorm": [_P, _P, _P, _P, _P, _P, _I, _I, _F, _I, _L, _L, _P],
     "ix_qk_norm_rope": [_P, _L, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P],
     "ix_rmsnorm_bwd": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P],

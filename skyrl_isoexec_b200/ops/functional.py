@@ -5,7 +5,8 @@ fallback on a GPU: a missing native library raises.
 
 Forward passes are the bitwise-gated half (trainer == engine). Backward passes are outside
 the contract (as in the reference, whose backward runs on stock cuBLAS,
-ISO/ops/mm/mm_fwd_scope.py:75-147) and are written with torch ops.
+ISO/ops/mm/mm_fwd_scope.py:75-147); their GEMMs are the NN / TN tcgen05 kernels of
+csrc/gemm_bwd_tcgen05.cu on a GPU and torch ops on CPU.
 """
 
 from __future__ import annotations
@@ -54,6 +55,59 @@ def gemm_nt(x: torch.Tensor, w: torch.Tensor, out_f32: bool = False, bn: int = 0
     return out
 
 
+def _bwd_gemm_ok(*ts) -> bool:
+    return all(t.is_cuda and t.dtype == torch.bfloat16 and t.dim() == 2 for t in ts)
+
+
+def gemm_nn(a: torch.Tensor, b: torch.Tensor, out_f32: bool = False) -> torch.Tensor:
+    """``a[M,R] @ b[R,N]`` (the input gradient ``dY @ W``): tcgen05 kernel reading ``b`` M/N-major, no transposed copy
+    (csrc/gemm_bwd_tcgen05.cu). CPU tensors and odd shapes use torch."""
+    M, R = a.shape
+    N = b.shape[1]
+    if not (_bwd_gemm_ok(a, b) and M > 0 and R % 8 == 0 and N % 8 == 0):
+        return torch.matmul(a, b).to(torch.float32 if out_f32 else a.dtype)
+    if a.stride(1) != 1 or a.stride(0) % 8:
+        a = a.contiguous()
+    if b.stride(1) != 1 or b.stride(0) % 8:
+        b = b.contiguous()
+    out = torch.empty(M, N, device=a.device, dtype=torch.float32 if out_f32 else torch.bfloat16)
+    _native.check(_native.lib().ix_gemm_bf16_nn(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, R, a.stride(0), b.stride(0), N,
+                                                int(out_f32), _native.stream()), "ix_gemm_bf16_nn")
+    return out
+
+
+def gemm_tn(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, accumulate: bool = False,
+            out_f32: bool = False) -> torch.Tensor:
+    """``a[R,M]^T @ b[R,N]`` (the weight gradient ``dY^T @ X``): both operands read M/N-major by the tcgen05 kernel.
+    ``out`` (fp32, contiguous [M,N]) with ``accumulate=True``: the product is ADDED to it in the epilogue."""
+    R, M = a.shape
+    N = b.shape[1]
+    ok = _bwd_gemm_ok(a, b) and R > 0 and M % 8 == 0 and N % 8 == 0
+    if out is not None:
+        assert out.dtype == torch.float32 and out.shape == (M, N) and out.is_contiguous()
+    if not ok:
+        res = torch.matmul(a.t(), b)
+        if out is None:
+            return res.to(torch.float32 if out_f32 else a.dtype)
+        if accumulate:
+            out.add_(res)
+        else:
+            out.copy_(res)
+        return out
+    if a.stride(1) != 1 or a.stride(0) % 8:
+        a = a.contiguous()
+    if b.stride(1) != 1 or b.stride(0) % 8:
+        b = b.contiguous()
+    if out is None:
+        out = torch.empty(M, N, device=a.device, dtype=torch.float32 if out_f32 else torch.bfloat16)
+        mode = int(out_f32)
+    else:
+        mode = 2 if accumulate else 1
+    _native.check(_native.lib().ix_gemm_bf16_tn(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, R, a.stride(0), b.stride(0), N, mode,
+                                                _native.stream()), "ix_gemm_bf16_tn")
+    return out
+
+
 class _Linear(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, out_f32):
@@ -69,14 +123,14 @@ class _Linear(torch.autograd.Function):
         dy2 = dy.reshape(-1, dy.shape[-1]).to(w.dtype)
         dx = dw = None
         if ctx.needs_input_grad[0]:
-            dx = torch.matmul(dy2, w).reshape(ctx.shp)
+            dx = gemm_nn(dy2, w).reshape(ctx.shp)
         if ctx.needs_input_grad[1]:
-            dw = torch.matmul(dy2.t(), x2)
+            dw = gemm_tn(dy2, x2)
         return dx, dw, None
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, out_f32: bool = False) -> torch.Tensor:
-    """``x[..., K] @ w[N, K]^T``. Forward: batch-invariant GEMM. Backward: library GEMMs."""
+    """``x[..., K] @ w[N, K]^T``. Forward: batch-invariant GEMM. Backward: the NN / TN tcgen05 GEMMs."""
     if torch.is_grad_enabled() and (x.requires_grad or w.requires_grad):
         return _Linear.apply(x, w, out_f32)
     shp = x.shape

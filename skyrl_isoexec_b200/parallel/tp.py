@@ -192,7 +192,7 @@ class _RowParallel(torch.autograd.Function):
     def backward(ctx, dy):
         x, w = ctx.saved_tensors
         dy = dy.to(w.dtype)
-        return torch.matmul(dy, w), torch.matmul(dy.t(), x), None, None, None, None
+        return F.gemm_nn(dy, w), F.gemm_tn(dy, x), None, None, None, None
 
 
 def row_parallel_linear(x: torch.Tensor, w: torch.Tensor, ps, cfg) -> torch.Tensor:

@@ -7,8 +7,13 @@ epochs, tile-width choice and the five entry points.
   * ``FusedTP.allgather_linear(x_local, w)``        all-gather -> GEMM for a sequence-parallel input.
 
 Every rank of the group calls the same methods in the same order; each call advances a shared epoch
-and flips the staging half. A call can be captured in a CUDA graph only together with its epoch, so
-the tensor-parallel engine runs these eagerly.
+and flips the staging half.
+
+CUDA graphs: a recorded kernel argument would repeat the same epoch at every replay, so while a graph is being
+captured (``begin_capture`` .. ``end_capture``) the decode-sized GEMM -> all-reduce is recorded in a form that reads
+its epoch from a device word: epoch = word + position of the call in the graph. ``before_replay(n)`` sets the word to
+the epoch reached so far (a one-thread kernel on the stream, outside the graph) and accounts for the n calls of the
+replay, so eager calls and replays can be mixed freely and every rank stays on the same count.
 
 Why a buffer half is free again two calls later: a rank finishes call e+1 only after it has waited
 for data that EVERY peer produced in call e+1, and a peer launches e+1 after its own kernel e (and the
@@ -36,6 +41,9 @@ def _sig(lib):
         [C.c_void_p] * 4 + [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p]
     lib.ix_tp_stage_floats.argtypes = [C.c_int] * 5
     lib.ix_tp_stage_floats.restype = C.c_longlong
+    lib.ix_tp_gemm_ar1_graph.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p] + [C.c_int] * 6 + [C.c_int] * 5 + \
+        [C.c_void_p, C.c_uint, C.c_void_p, C.c_void_p, C.c_longlong, C.c_longlong, C.c_void_p]
+    lib.ix_tp_set_epoch.argtypes = [C.c_void_p, C.c_uint, C.c_void_p]
     lib._tp_sig = True
 
 
@@ -98,6 +106,27 @@ class FusedTP:
         self.epoch = 0
         self.lib = _native.lib()
         _sig(self.lib)
+        self.epoch_word = torch.zeros(4, dtype=torch.int32, device=self.device)
+        self._cap = None            # while a CUDA graph is being captured: {"n": calls recorded so far}
+        self._base_stage = (C.c_longlong * self.W)(*self.p_stage)
+        self._base_flags = (C.c_longlong * self.W)(*self.p_flags)
+
+    # ------------------------------------------------------------------ CUDA-graph capture
+    def begin_capture(self) -> None:
+        self._cap = {"n": 0}
+
+    def end_capture(self) -> int:
+        """Number of fused calls the captured graph contains."""
+        n, self._cap = self._cap["n"], None
+        return n
+
+    def before_replay(self, n_calls: int) -> None:
+        """Call on the replay's stream right before ``graph.replay()``."""
+        if n_calls <= 0:
+            return
+        _native.check(self.lib.ix_tp_set_epoch(self.epoch_word.data_ptr(), self.epoch, _native.stream()), "ix_tp_set_epoch")
+        self.epoch += n_calls
+        self.calls += n_calls
 
     def _arr(self, ptrs, off_bytes):
         return (C.c_longlong * self.W)(*[p + off_bytes for p in ptrs])
@@ -129,8 +158,18 @@ class FusedTP:
         tiles = ((M + 127) // 128) * (N // bn)
         if need > self.stage_floats or tiles * W > self.n_flags:
             raise ValueError(f"row_parallel {M}x{N}: needs {need * 4} B of staging (have {self.stage_floats * 4})")
-        parity = self._next()
         out_f32 = out_dtype == torch.float32
+        if self._cap is not None:
+            if code != TP_AR1:
+                raise ValueError(f"a CUDA graph can record the decode-sized GEMM -> all-reduce only (M <= 256); got M={M}, mode={mode}")
+            self._cap["n"] += 1
+            ret = torch.empty(M, N, dtype=out_dtype, device=x.device)
+            _native.check(self.lib.ix_tp_gemm_ar1_graph(x.data_ptr(), w.data_ptr(), ret.data_ptr(), M, N, K, x.stride(0), w.stride(0), N,
+                                                        leaves, bn, int(out_f32), self.rank, W, self.epoch_word.data_ptr(), self._cap["n"],
+                                                        self._base_stage, self._base_flags, self.stage_floats, self.n_flags,
+                                                        _native.stream()), "ix_tp_gemm_ar1_graph")
+            return ret
+        parity = self._next()
         esz = 4 if out_f32 else 2
         stage = self._arr(self.p_stage, parity * self.stage_floats * 4)
         flags = self._arr(self.p_flags, parity * self.n_flags * 4)

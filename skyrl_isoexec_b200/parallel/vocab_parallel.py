@@ -90,17 +90,22 @@ class _VocabParallelLogprob(torch.autograd.Function):
         g_lp = g_lp.contiguous().float()
         ge = g_ent.contiguous().float() if want_entropy and g_ent is not None else None
         dh = torch.empty_like(hidden)
-        dw = torch.zeros_like(weight)
+        own = hidden.is_cuda and hidden.dtype == torch.bfloat16 and weight.shape[0] % 8 == 0 and weight.shape[1] % 8 == 0
+        dwf = torch.zeros(weight.shape, dtype=torch.float32, device=weight.device) if own else None
+        dw = None if own else torch.zeros_like(weight)
         for lo in range(0, n, chunk):
             hi = min(n, lo + chunk)
             logits = F.gemm_nt(hidden[lo:hi], weight)
             d = F.logprob_bwd(logits, targets[lo:hi].to(torch.int64).contiguous(), lse[lo:hi], g_lp[lo:hi],
                               None if ge is None else ge[lo:hi], ent[lo:hi] if ge is not None else None,
                               col_base=ps.tp_rank * vloc, inplace=True)
-            dh[lo:hi] = torch.matmul(d, weight)
-            dw.addmm_(d.t(), hidden[lo:hi])
+            dh[lo:hi] = F.gemm_nn(d, weight)
+            if dwf is not None:
+                F.gemm_tn(d, hidden[lo:hi], out=dwf, accumulate=True)
+            else:
+                dw.addmm_(d.t(), hidden[lo:hi])
         dist.all_reduce(dh, group=ps.tp_group)       # sum of the vocabulary shards' contributions
-        return dh, dw, None, None, None, None, None
+        return dh, (dwf.to(weight.dtype) if dwf is not None else dw), None, None, None, None, None
 
 
 def vocab_parallel_logprobs(model, hidden_rows, targets, chunk: int, want_entropy: bool = False):

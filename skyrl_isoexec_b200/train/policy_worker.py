@@ -54,7 +54,7 @@ class WorkerConfig:
 class _LMHeadLogprob(torch.autograd.Function):
     """logprob/entropy of ``targets`` from hidden rows, one vocabulary GEMM chunk at a time.
     Saves only the hidden rows and the per-row lse; the backward recomputes each logits chunk,
-    turns it into d(logits) in place and feeds the two library GEMMs."""
+    turns it into d(logits) in place and feeds the NN / TN gradient GEMMs."""
 
     @staticmethod
     def forward(ctx, hidden, weight, targets, leaves, chunk, want_entropy):
@@ -85,16 +85,22 @@ class _LMHeadLogprob(torch.autograd.Function):
         g_lp = g_lp.contiguous().float()
         ge = g_ent.contiguous().float() if want_entropy and g_ent is not None else None
         dh = torch.empty_like(hidden)
-        dw = torch.zeros_like(weight)
+        # the weight gradient of all chunks is summed in fp32 by the TN GEMM's accumulating epilogue (GPU, bf16)
+        own = hidden.is_cuda and hidden.dtype == torch.bfloat16 and weight.shape[0] % 8 == 0 and weight.shape[1] % 8 == 0
+        dwf = torch.zeros(weight.shape, dtype=torch.float32, device=weight.device) if own else None
+        dw = None if own else torch.zeros_like(weight)
         for lo in range(0, n, chunk):
             hi = min(n, lo + chunk)
             logits = F.gemm_nt(hidden[lo:hi], weight)
             d = F.logprob_bwd(logits, targets[lo:hi], lse[lo:hi], g_lp[lo:hi], None if ge is None else ge[lo:hi],
                               ent[lo:hi] if ge is not None else None, inplace=True)
-            dh[lo:hi] = torch.matmul(d, weight)
-            dw.addmm_(d.t(), hidden[lo:hi])
+            dh[lo:hi] = F.gemm_nn(d, weight)
+            if dwf is not None:
+                F.gemm_tn(d, hidden[lo:hi], out=dwf, accumulate=True)
+            else:
+                dw.addmm_(d.t(), hidden[lo:hi])
             del logits, d
-        return dh, dw, None, None, None, None
+        return dh, (dwf.to(weight.dtype) if dwf is not None else dw), None, None, None, None
 
 
 def lm_head_logprobs(model: DecoderLM, hidden_rows, targets, chunk: int, want_entropy: bool = False):

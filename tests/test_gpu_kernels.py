@@ -37,6 +37,56 @@ def test_gemm_matches_fp32_and_is_invariant(M, N, K):
     assert bitwise_equal(f32.bfloat16(), outs[256])                               # bf16 out = one round of the fp32 acc
 
 
+@pytest.mark.parametrize("M,N,R", [(300, 512, 1024), (8192, 4096, 1536), (1, 264, 64), (4097, 12288, 4096), (640, 72, 8)])
+def test_input_gradient_gemm_nn_matches_fp32(M, N, R):
+    """dX = dY[M,R] @ W[R,N]: W is read M/N-major by the MMA (no transposed copy), against an fp32 product."""
+    torch.manual_seed(2)
+    dy = (torch.randn(M, R, device=DEV) * 0.5).bfloat16()
+    w = (torch.randn(R, N, device=DEV) * 0.05).bfloat16()
+    ref = dy.float() @ w.float()
+    got = F.gemm_nn(dy, w, out_f32=True)
+    assert (got - ref).abs().max() <= 2e-4 * max(1.0, ref.abs().max().item())
+    assert bitwise_equal(F.gemm_nn(dy, w), got.bfloat16())
+    assert bitwise_equal(F.gemm_nn(dy, w), F.gemm_nn(dy, w))
+    big = torch.zeros(M, R + 64, device=DEV, dtype=torch.bfloat16)
+    big[:, 32:32 + R] = dy
+    assert bitwise_equal(F.gemm_nn(big[:, 32:32 + R], w), got.bfloat16()) if (R + 64) % 8 == 0 else True     # strided rows
+
+
+@pytest.mark.parametrize("M,N,R", [(512, 1024, 300), (4096, 1536, 8192), (264, 64, 1), (12288, 4096, 4097), (72, 8, 640)])
+def test_weight_gradient_gemm_tn_matches_fp32_and_accumulates(M, N, R):
+    """dW[M,N] = dY[R,M]^T @ X[R,N] with both operands read M/N-major; R (the token count) need not be a multiple of
+    anything. The accumulating form adds the product to an fp32 buffer in the epilogue."""
+    torch.manual_seed(3)
+    dy = (torch.randn(R, M, device=DEV) * 0.5).bfloat16()
+    x = (torch.randn(R, N, device=DEV) * 0.25).bfloat16()
+    ref = dy.float().T @ x.float()
+    got = F.gemm_tn(dy, x, out_f32=True)
+    tol = 2e-4 * max(1.0, ref.abs().max().item())
+    assert (got - ref).abs().max() <= tol
+    assert bitwise_equal(F.gemm_tn(dy, x), got.bfloat16())
+    base = torch.randn(M, N, device=DEV)
+    acc = base.clone()
+    F.gemm_tn(dy, x, out=acc, accumulate=True)
+    assert bitwise_equal(acc, base + got)
+    F.gemm_tn(dy, x, out=acc, accumulate=False)
+    assert bitwise_equal(acc, got)
+
+
+def test_linear_backward_uses_own_gemms_and_matches_fp32_autograd():
+    torch.manual_seed(4)
+    x = (torch.randn(777, 1024, device=DEV) * 0.5).bfloat16().requires_grad_()
+    w = (torch.randn(2048, 1024, device=DEV) * 0.05).bfloat16().requires_grad_()
+    g = (torch.randn(777, 2048, device=DEV) * 0.1).bfloat16()
+    n0 = F._native.launch_count()
+    F.linear(x, w).backward(g)
+    assert F._native.launch_count() - n0 == 3                       # forward NT, input-gradient NN, weight-gradient TN
+    xf, wf = x.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    (xf @ wf.T).backward(g.float())
+    assert (x.grad.float() - xf.grad).abs().max() <= 1e-2 * xf.grad.abs().max()
+    assert (w.grad.float() - wf.grad).abs().max() <= 1e-2 * wf.grad.abs().max()
+
+
 def test_gemm_strided_input_rows():
     torch.manual_seed(1)
     big = (torch.randn(64, 512, device=DEV)).bfloat16()
