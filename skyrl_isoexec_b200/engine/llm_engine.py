@@ -356,12 +356,23 @@ class LLMEngine:
     # ------------------------------------------------------------------ CUDA-graph decode
     def _graphs_enabled(self) -> bool:
         """Decode steps are replayed from a CUDA graph unless the model has a layer whose decode is not host-free yet
-        (MoE routing with host-side counts, GatedDeltaNet state slots). Tensor parallelism: the row-parallel GEMMs must be
+        (expert-parallel MoE, GatedDeltaNet state slots). Tensor parallelism: the row-parallel GEMMs must be
         served by the fused peer-memory kernel (its graph form reads the epoch from a device word); with the NCCL
         transport the step stays eager."""
-        if not (self.cfg.use_cuda_graph and self.device.type == "cuda") or self.mcfg.has_moe or self.mcfg.has_gdn:
+        if not (self.cfg.use_cuda_graph and self.device.type == "cuda") or self.mcfg.has_gdn:
             return False
         ps = self.model.ps
+        if self.mcfg.has_moe:
+            # single-rank experts build their routing tables on the device (ops/moe.py DispatchPlan): host-free.
+            # Expert parallelism exchanges counts through handshakes whose epochs are kernel arguments: eager.
+            from ..ops import moe as moe_ops
+
+            i = next((j for j in self.model.layer_ids if self.mcfg.has_moe), None)
+            if ps.ep > 1 or i is None:
+                return False
+            gu, dn = self.model.p(f"layers.{i}.moe.experts.gate_up"), self.model.p(f"layers.{i}.moe.experts.down")
+            if not moe_ops._experts_fn_ok(gu, gu, dn):
+                return False
         if ps.tp > 1:
             from ..parallel import tp_fused
 

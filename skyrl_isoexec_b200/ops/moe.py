@@ -18,8 +18,12 @@ from __future__ import annotations
 import torch
 import torch.distributed as dist
 
+from collections import Counter
+
 from . import _cpu, _native
 from . import functional as F
+
+_SERVED: Counter = Counter()       # which expert path served how many MoE blocks (read by the contract ledger)
 
 
 # ------------------------------------------------------------------------------------ router
@@ -182,6 +186,150 @@ def _grouped_ok(x_rows, gate_up, down) -> bool:
             and down.shape[2] % 64 == 0 and down.shape[1] % 32 == 0 and (gate_up.shape[1] // 2) % 32 == 0 and gate_up.shape[0] <= 512)
 
 
+# ------------------------------------------------------------------------------------ device-side routing plan + expert VJP
+class DispatchPlan:
+    """Routing tables built on the device without a host round trip (csrc/moe_dispatch.cu): rows ordered by (expert,
+    token, slot); every expert's group padded to a multiple of ``pad`` rows (zero rows)."""
+
+    def __init__(self, idx: torch.Tensor, num_experts: int, pad: int):
+        import ctypes as C
+
+        T, k = idx.shape
+        self.T, self.k, self.E, self.pad = T, k, num_experts, pad
+        dev = idx.device
+        self.r_cap = ((T * k + num_experts * (pad - 1)) + 63) // 64 * 64 if pad > 1 else max(1, T * k)
+        self.offs = torch.empty(num_experts + 1, dtype=torch.int32, device=dev)
+        self.row_of = torch.empty(max(1, T * k), dtype=torch.int32, device=dev)
+        self.src_of_row = torch.empty(self.r_cap, dtype=torch.int32, device=dev)
+        self.pos = torch.empty(T, k, dtype=torch.int64, device=dev)
+        scratch = torch.empty(T * k + num_experts, dtype=torch.int32, device=dev)
+        lib = _native.lib()
+        if not getattr(lib, "_moe_plan_sig", False):
+            P, I, L = C.c_void_p, C.c_int, C.c_longlong
+            lib.ix_moe_dispatch_plan.argtypes = [P, I, I, I, I, P, P, P, I, P, P, P]
+            lib.ix_moe_gather_rows.argtypes = [P, L, P, P, P, I, I, I, P, P, P]
+            lib.ix_moe_scatter_rows.argtypes = [P, L, P, P, I, I, I, P, P]
+            lib.ix_moe_glu_scale_bwd.argtypes = [P, P, P, P, I, I, P, P, P]
+            lib.ix_moe_grouped_gemm_nn.argtypes = [P, P, P, P, I, I, I, I, I, I, I, P]
+            lib.ix_moe_grouped_gemm_tn.argtypes = [P, P, P, P, I, I, I, I, I, I, I, P]
+            lib._moe_plan_sig = True
+        self.lib = lib
+        _native.check(lib.ix_moe_dispatch_plan(idx.contiguous().data_ptr(), T, k, num_experts, pad, self.offs.data_ptr(),
+                                               self.row_of.data_ptr(), self.src_of_row.data_ptr(), self.r_cap, self.pos.data_ptr(),
+                                               scratch.data_ptr(), _native.stream()), "ix_moe_dispatch_plan")
+
+    def gather(self, y: torch.Tensor, w_flat: torch.Tensor | None):
+        """(x_rows bf16 [r_cap, H], w_rows fp32 [r_cap]) in dispatch order; padding rows are zero."""
+        H = y.shape[1]
+        x_rows = torch.empty(self.r_cap, H, dtype=y.dtype, device=y.device)
+        w_rows = torch.empty(self.r_cap, dtype=torch.float32, device=y.device)
+        _native.check(self.lib.ix_moe_gather_rows(y.data_ptr(), y.stride(0), _native.ptr(w_flat), self.src_of_row.data_ptr(),
+                                                  self.offs.data_ptr(), self.E, self.k, H, x_rows.data_ptr(), w_rows.data_ptr(),
+                                                  _native.stream()), "ix_moe_gather_rows")
+        return x_rows, w_rows
+
+    def scatter(self, g: torch.Tensor) -> torch.Tensor:
+        """d_rows[r] = g[token of r] (zero for padding): backward of the combine."""
+        H = g.shape[1]
+        out = torch.empty(self.r_cap, H, dtype=g.dtype, device=g.device)
+        _native.check(self.lib.ix_moe_scatter_rows(g.data_ptr(), g.stride(0), self.src_of_row.data_ptr(), self.offs.data_ptr(), self.E,
+                                                   self.k, H, out.data_ptr(), _native.stream()), "ix_moe_scatter_rows")
+        return out
+
+
+def grouped_gemm_nn(a: torch.Tensor, w: torch.Tensor, plan: DispatchPlan, out_f32: bool = False) -> torch.Tensor:
+    """out[r] = a[r] @ w[e(r)] for w [E, Kred, N] (the input gradient of a grouped linear)."""
+    R, Kred = a.shape
+    E, _, N = w.shape
+    out = torch.empty(R, N, dtype=torch.float32 if out_f32 else torch.bfloat16, device=a.device)
+    _native.check(plan.lib.ix_moe_grouped_gemm_nn(a.data_ptr(), w.data_ptr(), out.data_ptr(), plan.offs.data_ptr(), R, E, N, Kred,
+                                                  a.stride(0), N, int(out_f32), _native.stream()), "ix_moe_grouped_gemm_nn")
+    return out
+
+
+def grouped_gemm_tn(a: torch.Tensor, b: torch.Tensor, plan: DispatchPlan, out: torch.Tensor | None = None,
+                    accumulate: bool = False) -> torch.Tensor:
+    """out[e] (+)= a[rows of e]^T @ b[rows of e] -> [E, M, N] (the weight gradient of a grouped linear)."""
+    R, M = a.shape
+    N = b.shape[1]
+    if out is None:
+        out = torch.empty(plan.E, M, N, dtype=torch.bfloat16, device=a.device)
+        mode = 0
+    else:
+        assert out.dtype == torch.float32 and out.is_contiguous() and tuple(out.shape) == (plan.E, M, N)
+        mode = 2 if accumulate else 1
+    _native.check(plan.lib.ix_moe_grouped_gemm_tn(a.data_ptr(), b.data_ptr(), out.data_ptr(), plan.offs.data_ptr(), R, plan.E, M, N,
+                                                  a.stride(0), b.stride(0), mode, _native.stream()), "ix_moe_grouped_gemm_tn")
+    return out
+
+
+def _glu_scale(h: torch.Tensor, w_rows: torch.Tensor) -> torch.Tensor:
+    """a2 = bf16(bf16(bf16(silu(g)) * u) * w_row): the two kernels whose roundings the fused GLU epilogue repeats."""
+    a = F.swiglu_fwd(h)
+    _native.check(_native.lib().ix_scale_rows(a.data_ptr(), w_rows.data_ptr(), a.shape[0], a.shape[1], _native.stream()), "ix_scale_rows")
+    return a
+
+
+class _ExpertsFn(torch.autograd.Function):
+    """All experts of one layer, differentiable, as grouped tcgen05 launches with no host synchronisation:
+    forward = plan, gather, grouped fc1, GLU x gate weight, grouped fc2 (fp32), fixed-order combine;
+    backward = scatter of the output gradient, grouped NN / TN GEMMs for both linears, the GLU x weight VJP, and the
+    fixed-order sum of the k row gradients of every token (no atomics)
+    (reference: ISO/ops/moe/moe_batched_experts.py:301-400, moe_backward_kernel.py:254-401, moe_combine_backward.py:80-231)."""
+
+    @staticmethod
+    def forward(ctx, y, w, gate_up, down, idx, shared):
+        E = gate_up.shape[0]
+        plan = DispatchPlan(idx, E, 64)
+        x_rows, w_rows = plan.gather(y, w.reshape(-1).contiguous())
+        h = grouped_gemm(x_rows, gate_up, plan.offs, EPI_BF16)
+        a2 = _glu_scale(h, w_rows)
+        rows = grouped_gemm(a2, down, plan.offs, EPI_F32)
+        out = torch.empty(y.shape[0], down.shape[1], dtype=y.dtype, device=y.device)
+        if y.shape[0]:
+            _native.check(_native.lib().ix_moe_combine(rows.data_ptr(), plan.pos.data_ptr(), _native.ptr(shared), out.data_ptr(),
+                                                       y.shape[0], out.shape[1], plan.k, int(y.dtype == torch.bfloat16),
+                                                       _native.stream()), "ix_moe_combine")
+        ctx.plan = plan
+        ctx.has_shared = shared is not None
+        ctx.save_for_backward(y, h, w_rows, gate_up, down)
+        ctx.mark_non_differentiable(idx)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        y, h, w_rows, gate_up, down = ctx.saved_tensors
+        plan: DispatchPlan = ctx.plan
+        g = g.contiguous()
+        d_rows = plan.scatter(g)                                    # [R, H]
+        a2 = _glu_scale(h, w_rows)                                  # recomputed (an elementwise pass) instead of kept
+        d_a2 = grouped_gemm_nn(d_rows, down, plan)                  # [R, F]      down [E, H, F]
+        d_down = grouped_gemm_tn(d_rows, a2, plan)                  # [E, H, F]
+        del a2
+        d_h = torch.empty_like(h)
+        d_w_rows = torch.empty_like(w_rows)
+        _native.check(plan.lib.ix_moe_glu_scale_bwd(h.data_ptr(), w_rows.data_ptr(), d_a2.data_ptr(), plan.offs.data_ptr(), plan.E,
+                                                    h.shape[1] // 2, d_h.data_ptr(), d_w_rows.data_ptr(), _native.stream()),
+                      "ix_moe_glu_scale_bwd")
+        del d_a2
+        x_rows, _ = plan.gather(y, None)
+        d_gate_up = grouped_gemm_tn(d_h, x_rows, plan)              # [E, 2F, H]
+        del x_rows
+        d_x_rows = grouped_gemm_nn(d_h, gate_up, plan, out_f32=True)     # [R, H] fp32
+        d_y = torch.empty_like(y)
+        if y.shape[0]:
+            _native.check(_native.lib().ix_moe_combine(d_x_rows.data_ptr(), plan.pos.data_ptr(), None, d_y.data_ptr(), y.shape[0],
+                                                       y.shape[1], plan.k, int(y.dtype == torch.bfloat16), _native.stream()),
+                          "ix_moe_combine")
+        d_w = d_w_rows.index_select(0, plan.row_of[:plan.T * plan.k].long()).view(plan.T, plan.k)
+        return d_y, d_w, d_gate_up, d_down, None, (g if ctx.has_shared else None)
+
+
+def _experts_fn_ok(y, gate_up, down) -> bool:
+    return (y.is_cuda and y.dtype == torch.bfloat16 and gate_up.shape[2] % 64 == 0 and down.shape[2] % 64 == 0
+            and down.shape[1] % 64 == 0 and (gate_up.shape[1] // 2) % 32 == 0 and gate_up.shape[0] <= 512)
+
+
 def counts_to_offsets(counts: torch.Tensor) -> torch.Tensor:
     offs = torch.zeros(counts.numel() + 1, dtype=torch.int32, device=counts.device)
     offs[1:] = torch.cumsum(counts, 0)
@@ -196,11 +344,23 @@ def moe_block(y: torch.Tensor, model, i: int) -> torch.Tensor:
     logits = F.linear(y, model.p(pfx + "router.weight"), out_f32=True).float()
     bias = model.p(pfx + "router.expert_bias").float() if cfg.router == "sigmoid_bias" else None
     idx, w = route(logits, k, bias, cfg.router == "sigmoid_bias", cfg.norm_topk_prob)
+    gate_up, down = model.p(pfx + "experts.gate_up"), model.p(pfx + "experts.down")
+    if ps.ep == 1 and _experts_fn_ok(y, gate_up, down):
+        # single-rank experts on a GPU: routing tables, expert GEMMs and (with autograd) their VJPs are all kernels,
+        # and nothing in the block reads a value back to the host
+        shared = _shared_expert(y, model, pfx) if cfg.shared_expert_ffn else None
+        if torch.is_grad_enabled() and (y.requires_grad or gate_up.requires_grad):
+            _SERVED["moe.experts/grouped_autograd"] += 1
+            return _ExpertsFn.apply(y, w, gate_up, down, idx, shared)
+        _SERVED["moe.experts/grouped"] += 1
+        plan = DispatchPlan(idx, E, 1)
+        x_rows, w_rows = plan.gather(y, w.reshape(-1).contiguous())
+        rows = expert_rows_grouped(x_rows, w_rows, plan.offs, gate_up, down)
+        return combine_fixed_order(rows, plan.pos, y.dtype, shared)
     order, counts, pos = build_dispatch(idx, E)
     tok_of_row = torch.div(order, k, rounding_mode="floor")
     x_rows = y.index_select(0, tok_of_row)
     w_rows = w.reshape(-1).index_select(0, order)
-    gate_up, down = model.p(pfx + "experts.gate_up"), model.p(pfx + "experts.down")
     peer = None
     if ps.ep > 1 and y.is_cuda and not torch.is_grad_enabled():
         from . import moe_ep
@@ -242,17 +402,22 @@ def moe_block(y: torch.Tensor, model, i: int) -> torch.Tensor:
         rows = expert_rows_grouped(x_rows, w_rows, counts_to_offsets(counts), gate_up, down)
     else:
         rows = _expert_rows(x_rows, w_rows, counts.tolist(), gate_up, down)
-    shared = None
-    if cfg.shared_expert_ffn:
-        from ..parallel import tp as tp_ops
-
-        gu = F.linear(tp_ops.copy_to_tp(y, ps), model.p(pfx + "shared.gate_up.weight"))   # column-parallel: sum the input grads
-        shared = tp_ops.row_parallel_linear(F.swiglu(gu), model.p(pfx + "shared.down.weight"), ps, cfg)
-        if cfg.shared_expert_gate:        # one scalar per token: sigmoid(y . w_gate), applied in fp32, one round
-            gl = F.linear(y, model.p(pfx + "shared.gate.weight"), out_f32=True).float()
-            if not gl.is_cuda:
-                # the CPU sigmoid rounds a vector lane and a scalar tail differently, so a [T, 1] tensor's values would depend
-                # on T; at full row width every element sits in a whole vector and a token's value is the same in any batch
-                gl = gl.expand(-1, shared.shape[-1]).contiguous()
-            shared = (shared.float() * torch.sigmoid(gl)).to(y.dtype)
+    _SERVED["moe.experts/" + ("peer" if peer is not None else "looped_or_nccl")] += 1
+    shared = _shared_expert(y, model, pfx) if cfg.shared_expert_ffn else None
     return combine_fixed_order(rows, pos, y.dtype, shared)
+
+
+def _shared_expert(y, model, pfx):
+    from ..parallel import tp as tp_ops
+
+    cfg, ps = model.cfg, model.ps
+    gu = F.linear(tp_ops.copy_to_tp(y, ps), model.p(pfx + "shared.gate_up.weight"))   # column-parallel: sum the input grads
+    shared = tp_ops.row_parallel_linear(F.swiglu(gu), model.p(pfx + "shared.down.weight"), ps, cfg)
+    if cfg.shared_expert_gate:        # one scalar per token: sigmoid(y . w_gate), applied in fp32, one round
+        gl = F.linear(y, model.p(pfx + "shared.gate.weight"), out_f32=True).float()
+        if not gl.is_cuda:
+            # the CPU sigmoid rounds a vector lane and a scalar tail differently, so a [T, 1] tensor's values would depend
+            # on T; at full row width every element sits in a whole vector and a token's value is the same in any batch
+            gl = gl.expand(-1, shared.shape[-1]).contiguous()
+        shared = (shared.float() * torch.sigmoid(gl)).to(y.dtype)
+    return shared

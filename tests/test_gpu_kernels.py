@@ -656,3 +656,77 @@ def test_fused_gumbel_sampler_distribution_greedy_and_determinism():
     assert g.tolist() == [5, 5, 5, 5]
     cold, _ = Sampler(DEV, seed=3)(logits, [SamplingParams(temperature=0.25)] * n)
     assert (cold == 5).float().mean() > 0.85
+
+
+def test_moe_dispatch_plan_is_the_stable_counting_sort():
+    """The device-built routing tables equal the torch sort / bincount construction; with padding every expert's group
+    starts on a multiple of 64 rows and the padding rows are marked empty."""
+    from skyrl_isoexec_b200.ops import moe
+
+    g = torch.Generator().manual_seed(5)
+    for T, E, k in ((1, 8, 2), (333, 8, 2), (4096, 128, 8), (77, 16, 4)):
+        idx = torch.stack([torch.randperm(E, generator=g)[:k] for _ in range(T)]).int().to(DEV)
+        order, counts, pos = moe.build_dispatch(idx, E)
+        plan = moe.DispatchPlan(idx, E, 1)
+        assert torch.equal(plan.src_of_row[:T * k].long(), order) and torch.equal(plan.pos, pos)
+        assert torch.equal(plan.offs.long(), moe.counts_to_offsets(counts).long())
+        pp = moe.DispatchPlan(idx, E, 64)
+        offs = pp.offs.tolist()
+        assert all(o % 64 == 0 for o in offs) and offs[-1] <= pp.r_cap
+        src = pp.src_of_row.tolist()
+        cl = counts.tolist()
+        for e in range(E):
+            seg = src[offs[e]:offs[e + 1]]
+            assert seg[:cl[e]] == order[sum(cl[:e]):sum(cl[:e + 1])].tolist() and all(v == -1 for v in seg[cl[e]:])
+        y = torch.randn(T, 64, device=DEV).bfloat16()
+        w = torch.rand(T * k, device=DEV)
+        xr, wr = pp.gather(y, w)
+        for e in (0, E - 1):
+            n = cl[e]
+            rows = order[sum(cl[:e]):sum(cl[:e]) + n]
+            assert torch.equal(xr[offs[e]:offs[e] + n], y[rows // k]) and torch.equal(wr[offs[e]:offs[e] + n], w[rows])
+            assert not xr[offs[e] + n:offs[e + 1]].any() and not wr[offs[e] + n:offs[e + 1]].any()
+
+
+def test_moe_experts_autograd_function_matches_fp32_autograd_and_the_fused_forward():
+    """One MoE layer's experts as grouped kernels with a kernel VJP: the forward has the bits of the fused inference
+    path, the gradients of input, gate weights and both expert weights agree with fp32 autograd of the same math."""
+    from skyrl_isoexec_b200.ops import moe
+
+    torch.manual_seed(7)
+    T, E, k, H, Fd = 500, 8, 2, 256, 128
+    y = (torch.randn(T, H, device=DEV) * 0.5).bfloat16().requires_grad_()
+    gate_up = (torch.randn(E, 2 * Fd, H, device=DEV) * 0.05).bfloat16().requires_grad_()
+    down = (torch.randn(E, H, Fd, device=DEV) * 0.05).bfloat16().requires_grad_()
+    logits = torch.randn(T, E, device=DEV)
+    idx, w0, _ = moe.router_topk_fwd(logits, k, None, False, True)
+    w = w0.clone().requires_grad_()
+    gout = (torch.randn(T, H, device=DEV) * 0.1).bfloat16()
+    out = moe._ExpertsFn.apply(y, w, gate_up, down, idx, None)
+    out.backward(gout)
+    # forward bits: the inference path (fused GLU epilogue, unpadded plan)
+    with torch.no_grad():
+        plan = moe.DispatchPlan(idx, E, 1)
+        xr, wr = plan.gather(y.detach(), w0.reshape(-1).contiguous())
+        rows = moe.expert_rows_grouped(xr, wr, plan.offs, gate_up.detach(), down.detach())
+        assert bitwise_equal(moe.combine_fixed_order(rows, plan.pos, torch.bfloat16), out.detach())
+    # fp32 reference of the same function
+    yf, wf = y.detach().float().requires_grad_(), w0.clone().requires_grad_()
+    guf, df = gate_up.detach().float().requires_grad_(), down.detach().float().requires_grad_()
+    ref = torch.zeros(T, H, device=DEV)
+    for e in range(E):
+        tok, slot = (idx == e).nonzero(as_tuple=True)
+        if tok.numel() == 0:
+            continue
+        h = yf[tok] @ guf[e].T
+        a = torch.nn.functional.silu(h[:, :Fd]) * h[:, Fd:] * wf[tok, slot][:, None]
+        ref = ref.index_add(0, tok, a @ df[e].T)
+    ref.backward(gout.float())
+    rel = lambda a, b: float((a.float() - b).abs().max() / b.abs().max().clamp(min=1e-6))
+    assert rel(out.detach(), ref.detach()) < 2e-2
+    assert rel(y.grad, yf.grad) < 3e-2 and rel(w.grad, wf.grad) < 3e-2
+    assert rel(gate_up.grad, guf.grad) < 3e-2 and rel(down.grad, df.grad) < 3e-2
+    # an expert that received no token gets an exactly zero gradient
+    empty = [e for e in range(E) if not bool((idx == e).any())]
+    for e in empty:
+        assert not gate_up.grad[e].any() and not down.grad[e].any()
