@@ -141,22 +141,32 @@ class ContractAdapter:
             lg.report("hook_exists", f"state:{s.state_id}", ok, "" if ok else f"hook {s.ref!r} does not resolve")
 
     def install(self) -> None:
-        """Record the implementation each (op, site) of this side dispatches to on this device."""
+        """Record, per (op, site) of this side, what the library on the model's device can really serve: the contract's
+        implementation id only if every entry point that implements it resolves in the loaded library of that device
+        kind (a CPU model under an sm100 contract, or a library built without a kernel, records a marker instead and
+        the comparison with the contract fails). The library's version and export digest are pinned in the record."""
         from ..ops import _cpu, _native
+        from . import observe
 
         gpu = self.model.device_.type == "cuda"
         lib = _native.lib() if gpu else _cpu.lib()     # raises if the library is missing: no silent fallback
+        self.library = observe.library_fingerprint(lib, gpu)
         role = {c.id: c.runtime_role for c in self.contract.cases}
-        for (op, site), sel in self.selections.items():
-            if role[site] != self.side:
-                continue
-            self.fingerprint.record_install(op, site, sel.impl_id, obj=lib, pinned=dict(sel.pins))
-        for e in self.contract.composition:   # subsumed ops are installed by the op that fuses them
+        for e in self.contract.composition:
             for cid in e.cases:
-                if role[cid] == self.side:
-                    for op in e.region:
-                        if (op, cid) not in self.fingerprint.records:
-                            self.fingerprint.record_install(op, cid, e.impl.id, obj=lib)
+                if role[cid] != self.side:
+                    continue
+                seen = observe.installed_impl(lib, e.impl.id, gpu)
+                for op in e.region:             # the ops a fused implementation subsumes are installed with it
+                    self.fingerprint.record_install(op, cid, seen, obj=lib, pinned={})
+        # pins: what this process would run with, read from the live model configuration
+        live = {k: dict(s.pins) for k, s in derive_selections(
+            profile_from_model_config(self.model.cfg, self.trainer_tp, self.engine_tp, self.model.ps.pp, self.model.ps.cp,
+                                      self.model.ps.ep), self.arch).items()}
+        for (op, site), pins in live.items():
+            rec = self.fingerprint.records.get((op, site))
+            if rec is not None:
+                rec.pinned = pins
 
     def run_install(self) -> M.ExecutionContract:
         try:
@@ -186,24 +196,64 @@ class ContractAdapter:
 
     # ------------------------------------------------------------------ FIRST_FORWARD
     def note_served(self, ops) -> None:
+        """Manual credit (tests, external runtimes). The trainer feeds ``on_first_forward`` with an observed census instead."""
         for op in ops:
             self.served[op] += 1
 
-    def on_first_forward(self) -> None:
+    def expected_impls(self) -> dict[str, set]:
+        """{op: implementation ids the contract names for it on this side}; subsumed ops map to their fused entry's id."""
+        role = {c.id: c.runtime_role for c in self.contract.cases}
+        out: dict[str, set] = {}
+        for e in self.contract.composition:
+            if any(role[c] == self.side for c in e.cases):
+                for op in e.region:
+                    out.setdefault(op, set()).add(e.impl.id)
+        return out
+
+    def on_first_forward(self, census=None) -> None:
+        """Close FIRST_FORWARD. ``census``: {(op, impl id): calls} observed by the op layer during the forward being
+        judged (``core.observe.diff``). An op is served iff something ran for it and everything that ran for it is an
+        implementation the contract names; an op that a fused kernel subsumes is served when its owner is."""
+        from . import observe
+
         lg = self.ledger
+        want = self.expected_impls()
+        primary = {op for (op, site) in (self.selections or {})}
+        owner: dict[str, str] = {}
+        for e in self.contract.composition:
+            own = next((op for op in e.region if op in primary), e.region[0])
+            for op in e.region:
+                owner.setdefault(op, own)
         for o in [o for o in lg.plan if o.phase == "FIRST_FORWARD" and o.kind == "served"]:
-            n = self.served.get(o.key, 0)
-            lg.report("served", o.key, n > 0, "" if n > 0 else "declared but never executed in the first forward")
+            if census is None:
+                n = self.served.get(o.key, 0)
+                lg.report("served", o.key, n > 0, "" if n > 0 else "declared but never executed in the first forward")
+                continue
+            op = owner.get(o.key, o.key)
+            got = observe.ran(census, op)
+            if not got and self.served.get(o.key, 0) > 0:
+                got = {next(iter(want.get(op, {"?"}))): self.served[o.key]}
+            bad = sorted(set(got) - want.get(op, set()))
+            if not got:
+                lg.report("served", o.key, False, f"nothing ran for {op!r} during the first forward")
+            elif bad:
+                lg.report("served", o.key, False, f"{op!r} was served by {bad}, the contract names {sorted(want.get(op, set()))}")
+            else:
+                lg.report("served", o.key, True, ",".join(f"{k}x{v}" for k, v in sorted(got.items())))
         lg.close_phase("FIRST_FORWARD")
 
     # ------------------------------------------------------------------ WEIGHT_SYNC / STEP1
-    def on_weight_sync(self, peer_hash: str | None, invalidated: list[str] | None = None) -> None:
+    def on_weight_sync(self, peer_hash: str | None, invalidated=None) -> None:
         lg = self.ledger
         mine = P.contract_hash(self.contract)
         ok = peer_hash == mine
         lg.report("handshake", "contract_hash", ok, "" if ok else f"peer {str(peer_hash)[:12]} != local {mine[:12]}")
-        for sid in invalidated or []:
-            lg.report("installed_backstop", f"invalidate:{sid}", True)
+        # ``invalidated``: {state id: observed} from the invalidation hooks' own counters (a list of ids is read as
+        # "the caller vouches", kept for runtimes that cannot observe)
+        obs = invalidated if isinstance(invalidated, dict) else {sid: True for sid in (invalidated or [])}
+        for sid, seen in obs.items():
+            lg.report("installed_backstop", f"invalidate:{sid}", bool(seen),
+                      "" if seen else "the state's invalidation hook did not run for this weight sync")
         if "WEIGHT_SYNC" not in lg.closed:
             lg.close_phase("WEIGHT_SYNC")
 

@@ -122,7 +122,7 @@ def profile_from_model_config(cfg: ModelConfig, trainer_tp: int = 1, engine_tp: 
         zero_centered_norms=cfg.zero_centered_norm, activation_dtype="bf16" if cfg.dtype == "bfloat16" else "fp32",
         rms_eps=cfg.rms_eps, rope_theta=cfg.rope_theta, rot_dim=cfg.rot_dim, logprob_leaves=cfg.logprob_leaves,
         pik_leaves=G, router_score=cfg.router, router_topk=cfg.top_k, router_norm_topk=cfg.norm_topk_prob,
-        gdn_chunk_size=cfg.gdn_chunk, gdn_conv_width=cfg.gdn_conv_kernel, topology=tuple(topo), states=tuple(states),
+        gdn_kernel="cpr" if getattr(cfg, "gdn_snapshot", False) else "recurrent", gdn_chunk_size=cfg.gdn_chunk, gdn_conv_width=cfg.gdn_conv_kernel, topology=tuple(topo), states=tuple(states),
         tolerances=tol)
 
 

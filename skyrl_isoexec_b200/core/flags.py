@@ -37,11 +37,11 @@ FLAGS: tuple[Flag, ...] = (
          "trainer.isoexec.enabled"),
     Flag("SKYRL_ISOEXEC_MANIFEST_STRICT", "1", (TRAIN, ENGINE), "deployment", "0 demotes contract refusals to warnings"),
     Flag("SKYRL_ISOEXEC_DEBUG_TRACE", "", (TRAIN, ENGINE), "diagnostic", "directory for per-region digest traces (also demotes refusals)"),
-    Flag("SKYRL_ISOEXEC_GDN_KERNEL", "recurrent", (TRAIN, ENGINE), "function", "recurrent | cpr: bf16 snapshots of the GDN state at chunk boundaries",
+    Flag("SKYRL_ISOEXEC_GDN_KERNEL", "recurrent", (TRAIN, ENGINE), "function", "recurrent | cpr: bf16 snapshots of the GDN state at chunk boundaries (read by models/config.py::get_config)",
          "gdn.core:kernel"),
-    Flag("SKYRL_ISOEXEC_PIK_LEAVES", "8", (TRAIN, ENGINE), "function", "number of K leaves of the TP-invariant reduction tree",
+    Flag("SKYRL_ISOEXEC_PIK_LEAVES", "8", (TRAIN, ENGINE), "function", "number of K leaves of the TP-invariant reduction tree (read by models/config.py::get_config)",
          "collectives.tree_all_reduce:leaves"),
-    Flag("SKYRL_ISOEXEC_LOGPROB_LEAVES", "8", (TRAIN, ENGINE), "function", "number of vocabulary leaves of the log-softmax",
+    Flag("SKYRL_ISOEXEC_LOGPROB_LEAVES", "8", (TRAIN, ENGINE), "function", "number of vocabulary leaves of the log-softmax (read by models/config.py::get_config)",
          "logprobs.log_softmax:leaves"),
     Flag("ISOEXEC_CONTRACT_PATH", "", (TRAIN, ENGINE), "deployment", "write the built contract here (artifact)"),
     Flag("ISOEXEC_CONTRACT_HASH", "", (TRAIN, ENGINE), "deployment", "expected numerical_policy; a different built or loaded contract is refused"),
@@ -49,7 +49,7 @@ FLAGS: tuple[Flag, ...] = (
     Flag("ISOEXEC_B200_FORCE_CPU", "0", (TRAIN, ENGINE), "deployment", "treat the process as GPU-less (tests)"),
     Flag("SKYRL_WORKER_NCCL_TIMEOUT_IN_S", "600", (TRAIN, ENGINE), "deployment", "process-group timeout"),
     Flag("NCCL_NVLS_ENABLE", "", (TRAIN, ENGINE), "deployment", "NVLS on/off for NCCL; no NCCL reduction is on the logprob path"),
-    Flag("SKYRL_ISOEXEC_PIK_P2P", "1", (TRAIN, ENGINE), "deployment", "0 forces the NCCL all-gather transport for tree reductions (same bits)"),
+    Flag("SKYRL_ISOEXEC_PIK_P2P", "1", (TRAIN, ENGINE), "deployment", "0 forces the NCCL all-gather transport for tree reductions (same bits; read by parallel/transports.py)"),
     Flag("SKYRL_ISOEXEC_TRAINER_SP", "0", (TRAIN,), "dead", "sequence-parallel trainer variant of the reference; SP here never changes bits"),
     Flag("VLLM_BATCH_INVARIANT", "", (ENGINE,), "dead", "vLLM switch of the reference; there is no vLLM here"),
 )

@@ -21,7 +21,7 @@ from typing import Callable
 class FusedRegion:
     name: str                    # kernel / entry point
     replaces: tuple              # the unfused op chain it must equal bit for bit
-    equality: str                # "bitwise" | "pair" (two fused sites must equal each other, not an eager chain)
+    equality: str                # "bitwise" | "pair" (two fused sites must equal each other, not an eager chain) | "close"
     note: str = ""
 
 
@@ -38,7 +38,8 @@ REGIONS: tuple[FusedRegion, ...] = (
     FusedRegion("attention (prefill | decode | chunk)", ("attention(prefill)",), "pair", "decode and chunked prefill equal full prefill"),
     FusedRegion("rmsnorm (cta-per-row | warp-per-row)", ("rmsnorm",), "pair", "two launch geometries, one reduction order"),
     FusedRegion("gdn_scan (chunked | recurrent)", ("gdn_scan(sequential)",), "pair"),
-    FusedRegion("ppo_loss_fused", ("ratio", "clip", "min", "mask", "sum"), "bitwise"),
+    FusedRegion("ppo_loss_fused", ("ratio", "clip", "min", "mask", "sum"), "close",
+                "outside the logprob path: equal to the torch chain up to fp32 summation order, bit-identical run to run"),
 )
 
 
@@ -71,10 +72,15 @@ def checker(name: str):
     return deco
 
 
-def run_checkers(device: str) -> dict[str, bool]:
-    """Run every registered bit-equality checker on ``device``; a region without a checker is reported as absent,
-    which the ledger obligation treats as unproven."""
-    return {r.name: (_CHECKERS[r.name](device) if r.name in _CHECKERS else None) for r in REGIONS}
+def run_checkers(device: str) -> dict[str, bool | None]:
+    """Run every region's checker on ``device``: True / False, or None when the comparison needs another device
+    (deferred, not proven). A region WITHOUT a checker raises: an unproven fusion must not pass silently."""
+    from . import fusion_checks  # noqa: F401  (registers the checkers)
+
+    missing = [r.name for r in REGIONS if r.name not in _CHECKERS]
+    if missing:
+        raise LookupError(f"fused regions without a bit-equality checker: {missing}")
+    return {r.name: _CHECKERS[r.name](device) for r in REGIONS}
 
 
 @checker("rmsnorm+residual")

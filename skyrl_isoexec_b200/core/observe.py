@@ -84,24 +84,34 @@ IMPL_SYMBOLS: dict[str, tuple[str, ...]] = {
 }
 
 
+def _names(is_gpu: bool) -> list[str]:
+    pre = "ix_" if is_gpu else "ixc_"
+    return sorted({n for syms in IMPL_SYMBOLS.values() for n in syms if n.startswith(pre) and n.startswith("ixc_") != is_gpu})
+
+
 def library_fingerprint(lib, is_gpu: bool) -> dict:
     """Version symbol and a digest over which of the known entry points the loaded library exports."""
-    prefix = "ix_" if is_gpu else "ixc_"
-    names = sorted({s for syms in IMPL_SYMBOLS.values() for s in syms if s.startswith(prefix) and (is_gpu or s.startswith("ixc_"))
-                    and (not is_gpu or not s.startswith("ixc_"))})
-    present = [(n, hasattr(lib, n)) for n in names]
+    present = [(n, hasattr(lib, n)) for n in _names(is_gpu)]
     ver = getattr(lib, "ix_version" if is_gpu else "ixc_version")()
-    h = hashlib.sha256(repr((ver, present)).encode()).hexdigest()[:24]
+    h = hashlib.sha256(repr((int(ver), present)).encode()).hexdigest()[:24]
     return {"version": int(ver), "exports_digest": h, "missing": [n for n, ok in present if not ok]}
 
 
+# implementations whose id is the same on both kinds of device (their kernels exist in both libraries)
+_BOTH = {"cpr_chunk_scan": "gdn_scan", "cpr_recurrent_step": "gdn_scan", "shifted_sum_conv": "gdn_conv",
+         "fp32_gating": "gdn_gate", "slot_pool": "gdn_conv_state"}
+
+
 def installed_impl(lib, impl_id: str, is_gpu: bool) -> str:
-    """The id under which ``impl_id`` is recorded as installed: itself when the library on this device exports every
-    entry point it needs, else a marker that can never equal a contract entry."""
+    """The id under which ``impl_id`` is recorded as installed: itself when the library of the device the model lives
+    on exports every entry point it needs; otherwise a marker that can never equal a contract entry."""
+    if impl_id in _BOTH:
+        sym = ("ix_" if is_gpu else "ixc_") + _BOTH[impl_id]
+        return impl_id if hasattr(lib, sym) else f"missing:{impl_id}:{sym}"
     syms = IMPL_SYMBOLS.get(impl_id)
     if syms is None:
         return f"unknown:{impl_id}"
-    if impl_id.startswith("cpu_") == is_gpu and impl_id not in ("cpr_chunk_scan", "cpr_recurrent_step", "shifted_sum_conv", "fp32_gating", "slot_pool"):
+    if impl_id.startswith("cpu_") == is_gpu:
         return f"wrong-device:{impl_id}"
-    missing = [s for s in syms if (s.startswith("ixc_") != (not is_gpu)) is False and not hasattr(lib, s)]
+    missing = [n for n in syms if not hasattr(lib, n)]
     return impl_id if not missing else f"missing:{impl_id}:{','.join(missing)}"

@@ -83,7 +83,11 @@ def check_flags() -> list[str]:
 def check_fusion_ledger() -> list[str]:
     from . import fusion_ledger as FL
 
-    return [f"fused region {name!r} differs from its unfused chain" for name, ok in FL.run_checkers("cpu").items() if ok is False]
+    try:
+        res = FL.run_checkers("cpu")
+    except LookupError as e:
+        return [str(e)]
+    return [f"fused region {name!r} differs from its unfused chain" for name, ok in res.items() if ok is False]
 
 
 def check_native() -> list[str]:

@@ -30,6 +30,7 @@ class GDNStatePool:
         self.free = list(range(self.rows - 1, 0, -1))
         self.row_of: dict[int, int] = {}
         self.epoch = 0
+        self.invalidations = {"weight_sync": 0, "sleep_wake": 0}
 
     def _row(self, seq_id: int) -> int:
         if seq_id not in self.row_of:
@@ -49,6 +50,7 @@ class GDNStatePool:
         self.free = list(range(self.rows - 1, 0, -1))
         self.row_of.clear()
         self.epoch += 1
+        self.invalidations[event] += 1
 
     def step_meta(self, decode, prefill) -> GDNMeta:
         """Chunks in batch order: decode tokens first (one token each), then the prefill chunks. A chunk

@@ -47,6 +47,7 @@ class KVCache:
         self.layer_ids = list(layer_ids if layer_ids is not None else range(cfg.num_layers))
         self.allocator = PageAllocator(num_pages)
         self.pools: list | None = None
+        self.invalidations = {"weight_sync": 0, "sleep_wake": 0}     # how often each lifecycle event really emptied the cache
         self.wake()
 
     @staticmethod
@@ -71,6 +72,20 @@ class KVCache:
         never needed after a rollout phase ends."""
         self.pools = None
         self.allocator = PageAllocator(self.num_pages)
+        self.invalidations["sleep_wake"] += 1
+
+    def invalidate(self, event: str) -> bool:
+        """A weight sync makes every cached key and value stale. No prefix is kept across requests, so the cache is clean
+        exactly when no page is in use at that moment. Returns whether it was, and counts clean invalidations so that
+        the contract ledger sees that the event really emptied the cache instead of taking it on trust. (A sync while
+        paused requests keep their pages, the in-flight update mode, is counted under ``stale_syncs``.)"""
+        assert event in self.invalidations
+        clean = self.pools is None or self.allocator.num_free == self.num_pages
+        if clean:
+            self.invalidations[event] += 1
+        else:
+            self.stale_syncs = getattr(self, "stale_syncs", 0) + 1
+        return clean
 
     def slots_for(self, pages: list[int], start: int, n: int) -> list[int]:
         """Slots of positions start .. start+n-1 of a sequence whose pages are ``pages``."""

@@ -160,6 +160,8 @@ class LLMEngine:
         self.mcfg = model.cfg
         self.cfg = cfg or EngineConfig()
         self.device = model.device_
+        if self.cfg.enable_prefix_caching:
+            raise ValueError("this engine keeps no prefix cache (the execution contract pins it off); set enable_prefix_caching=false")
         self.max_len = self.cfg.max_model_len or self.mcfg.max_position
         n_pages = self.cfg.num_kv_pages or self._auto_pages()
         self.cache = KVCache(self.mcfg, n_pages, self.device, tp=model.ps.tp, layer_ids=model.layer_ids)
@@ -222,9 +224,19 @@ class LLMEngine:
         self.asleep = False
 
     def reset_prefix_cache(self) -> None:
-        """No prefix cache is kept (pinned off by the contract); recurrent state is dropped."""
+        """Called at every weight sync. No prefix cache is kept (pinned off by the contract): the KV cache checks that no
+        page holds old-weight state; recurrent state is dropped."""
+        self._drain_inflight()
+        self.cache.invalidate("weight_sync")
         if self.gdn_state is not None:
             self.gdn_state.invalidate("weight_sync")
+
+    def invalidation_counts(self) -> dict:
+        """{state id of the contract: {event: times the state was really invalidated}}."""
+        out = {"engine_kv_cache": dict(self.cache.invalidations)}
+        if self.gdn_state is not None:
+            out["gdn_recurrent_state"] = dict(self.gdn_state.invalidations)
+        return out
 
     def pause_generation(self) -> None:
         self.paused = True
@@ -236,6 +248,8 @@ class LLMEngine:
     def add_request(self, prompt_ids: list[int], params: SamplingParams, request_index: int = 0) -> Sequence:
         if len(prompt_ids) == 0:
             raise ValueError("empty prompt")
+        if getattr(params, "repetition_penalty", 1.0) not in (1.0, None):
+            raise ValueError("repetition_penalty is not implemented by this engine; leave it at 1.0")
         if len(prompt_ids) >= self.max_len:
             raise ValueError(f"prompt of {len(prompt_ids)} tokens exceeds max_model_len={self.max_len}")
         seq = Sequence(self._next_id, list(prompt_ids), params, request_index=request_index, arrival=time.time())

@@ -40,6 +40,7 @@ class ModelConfig:
     gdn_head_dim: int = 0
     gdn_conv_kernel: int = 4
     gdn_chunk: int = 64
+    gdn_snapshot: bool = False         # "cpr" scan: the fp32 state is rounded to the activation dtype at every chunk boundary
     attn_output_gate: bool = False
     zero_centered_norm: bool = False
     partial_rotary_factor: float = 1.0
@@ -201,4 +202,21 @@ def get_config(name: str, **overrides) -> ModelConfig:
     if name not in PRESETS:
         raise KeyError(f"unknown model preset {name!r}; known: {sorted(PRESETS)}")
     cfg = PRESETS[name]
-    return cfg.with_(**overrides) if overrides else cfg
+    # function flags of the environment select contract pins (core/flags.py); an explicit override wins over the flag
+    import os
+
+    env = {}
+    k = os.environ.get("SKYRL_ISOEXEC_GDN_KERNEL", "")
+    if k:
+        if k not in ("recurrent", "cpr"):
+            raise ValueError(f"SKYRL_ISOEXEC_GDN_KERNEL={k!r}: expected recurrent or cpr")
+        env["gdn_snapshot"] = k == "cpr"
+    for flag, field_ in (("SKYRL_ISOEXEC_PIK_LEAVES", "pik_leaves"), ("SKYRL_ISOEXEC_LOGPROB_LEAVES", "logprob_leaves")):
+        v = os.environ.get(flag, "")
+        if v:
+            n = int(v)
+            if n < 1 or n & (n - 1):
+                raise ValueError(f"{flag}={v}: the number of leaves must be a power of two")
+            env[field_] = n
+    env.update(overrides)
+    return cfg.with_(**env) if env else cfg

@@ -20,6 +20,7 @@ from dataclasses import dataclass
 import torch
 import torch.nn as nn
 
+from ..core import observe as _obs
 from ..debug import trace as _trace
 from ..ops import functional as F
 from ..ops import gdn as gdn_ops
@@ -350,6 +351,8 @@ class DecoderLM(nn.Module):
         if y.is_cuda and y.dtype == torch.bfloat16 and not torch.is_grad_enabled() and (wgu.shape[0] // 2) % 32 == 0 and y.dim() == 2:
             # gate_up GEMM with the SwiGLU applied in its epilogue (one launch, no [T, 2F] intermediate). The epilogue
             # repeats the roundings of the separate kernels, so this and the differentiable path below agree bit for bit.
+            _obs.note("mm", "tcgen05_batch_invariant")
+            _obs.note("activation.swiglu", "fused_swiglu")
             a = moe_ops.grouped_gemm(y, wgu.unsqueeze(0), None, moe_ops.EPI_GLU)
         else:
             a = F.swiglu(F.linear(tp_ops.copy_to_tp(y, self.ps), wgu))

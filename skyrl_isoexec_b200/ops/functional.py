@@ -16,6 +16,7 @@ from dataclasses import dataclass, field
 
 import torch
 
+from ..core import observe as _obs
 from . import _cpu, _native
 
 PAGE = 128  # keys per attention block == slots per KV page
@@ -39,6 +40,7 @@ def gemm_nt(x: torch.Tensor, w: torch.Tensor, out_f32: bool = False, bn: int = 0
         out = torch.empty(M, N, device=x.device, dtype=torch.float32 if out_f32 else torch.bfloat16)
         if M == 0:
             return out
+        _obs.note("mm", "tcgen05_batch_invariant")
         L = _native.lib()
         _native.check(
             L.ix_gemm_bf16_nt(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, x.stride(0), w.stride(0), N,
@@ -50,6 +52,7 @@ def gemm_nt(x: torch.Tensor, w: torch.Tensor, out_f32: bool = False, bn: int = 0
     out = torch.empty(M, N, dtype=out_dtype)
     if M == 0:
         return out
+    _obs.note("mm", "cpu_sequential_k")
     _cpu.lib().ixc_gemm_nt(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, x.stride(0), w.stride(0), N,
                            _cpu.dt(x), int(out_dtype == torch.float32))
     return out
@@ -150,6 +153,7 @@ def rmsnorm_fwd(x, w, eps, zero_centered=False, residual=None, want_rstd=False):
     if residual is not None:
         residual = residual.contiguous()
     if _is_cuda(x):
+        _obs.note("norms.rms", "fused_add_rmsnorm")
         L = _native.lib()
         _native.check(
             L.ix_rmsnorm(x.data_ptr(), _native.ptr(residual), w.data_ptr(), y.data_ptr(), _native.ptr(res_out),
@@ -157,6 +161,7 @@ def rmsnorm_fwd(x, w, eps, zero_centered=False, residual=None, want_rstd=False):
             "ix_rmsnorm",
         )
     else:
+        _obs.note("norms.rms", "cpu_add_rmsnorm")
         _cpu.lib().ixc_rmsnorm(x.data_ptr(), _cpu.ptr(residual), w.data_ptr(), y.data_ptr(), _cpu.ptr(res_out),
                                _cpu.ptr(rstd), rows, N, eps, int(zero_centered), x.stride(0), N, _cpu.dt(x))
     return y, res_out, rstd
@@ -246,6 +251,7 @@ def qk_norm_rope_fwd(qkv, positions, slots, rope: RopeTable, qw, kw, k_out, v_ou
     if T == 0:
         return q
     assert positions.dtype == torch.int32 and (slots is None or slots.dtype == torch.int64)
+    _obs.note("rope.rope", "fused_qknorm_rope_kvwrite" if _is_cuda(qkv) else "cpu_fused_qknorm_rope")
     if _is_cuda(qkv):
         L = _native.lib()
         _native.check(
@@ -401,6 +407,7 @@ def attention_fwd(q, k, v, meta: AttnMeta, scale: float, want_lse: bool = False)
         return out, lse
     bt = meta.block_table
     assert q.is_contiguous() and k.is_contiguous() and v.is_contiguous() and meta.items.is_contiguous()
+    _obs.note("attention.varlen", "tcgen05_unified" if _is_cuda(q) else "cpu_blockwise")
     if _is_cuda(q):
         L = _native.lib()
         _native.check(
@@ -500,6 +507,7 @@ def swiglu_fwd(x):
     out = torch.empty(T, F, device=x.device, dtype=x.dtype)
     if T == 0:
         return out
+    _obs.note("activation.swiglu", "fused_swiglu" if _is_cuda(x) else "cpu_swiglu")
     assert x.stride(1) == 1
     if _is_cuda(x):
         _native.check(_native.lib().ix_swiglu(x.data_ptr(), out.data_ptr(), T, F, x.stride(0), _native.stream()), "ix_swiglu")
@@ -542,6 +550,7 @@ def swiglu(x):
 def sigmoid_gate(a, qkv, Hq, Hkv, D):
     """out[t,h,:] = a[t,h,:] * sigmoid(gate[t,h,:]) with gate read in place from the fused q block."""
     T = a.shape[0]
+    _obs.note("activation.attn_gate", "fused_sigmoid_gate" if _is_cuda(a) else "cpu_sigmoid_gate")
     out = torch.empty_like(a)
     if T == 0:
         return out
@@ -561,6 +570,7 @@ def gated_outnorm(o, z, w, eps=1e-6, zero_centered=False):
     out = torch.empty_like(o2)
     if o2.shape[0] == 0:
         return out.reshape(shp)
+    _obs.note("norms.gated_out", "fused_gated_outnorm" if _is_cuda(o2) else "cpu_gated_outnorm")
     if _is_cuda(o2):
         _native.check(_native.lib().ix_gated_outnorm(o2.data_ptr(), z2.data_ptr(), w.data_ptr(), out.data_ptr(),
                                                      o2.shape[0], D, eps, int(zero_centered), _native.stream()),
@@ -585,6 +595,7 @@ def logprob_fused_fwd(logits, targets, leaves=DEFAULT_LEAVES, want_entropy=False
     ent = torch.empty_like(lp) if want_entropy else None
     if rows == 0:
         return lp, lse, ent
+    _obs.note("logprobs.log_softmax", "rowinv_leaftree" if _is_cuda(logits) else "cpu_rowinv_leaftree")
     targets = targets.to(torch.int64).contiguous()
     is_f32 = int(logits.dtype == torch.float32)
     if _is_cuda(logits):

@@ -20,6 +20,7 @@ from dataclasses import dataclass
 import numpy as np
 import torch
 
+from ..core import observe as _obs
 from . import _cpu, _native
 from . import functional as F
 
@@ -97,6 +98,12 @@ def gdn_core_fwd(proj, conv_w, A_log, dt_bias, meta: GDNMeta, cfg, tp, conv_stat
     if ssm_state is None:
         ssm_state = torch.empty(0, dtype=torch.float32, device=dev)
     args_cs = None if conv_state is None else conv_state.data_ptr()
+    # one token per chunk with a state row behind it is the recurrent decode step; anything longer is the scan
+    _obs.note("gdn.core", "cpr_recurrent_step" if (meta.uses_state and T == meta.n_chunks) else "cpr_chunk_scan")
+    _obs.note("gdn.conv", "shifted_sum_conv")
+    _obs.note("gdn.gating", "fp32_gating")
+    if meta.uses_state:
+        _obs.note("gdn.state", "slot_pool")
     if proj.is_cuda:
         L, s, f32 = _native.lib(), _native.stream(), _is_f32(proj)
         ck = _native.check

@@ -20,6 +20,7 @@ import torch.distributed as dist
 
 from collections import Counter
 
+from ..core import observe as _obs
 from . import _cpu, _native
 from . import functional as F
 
@@ -37,6 +38,7 @@ def router_topk_fwd(logits: torch.Tensor, k: int, bias: torch.Tensor | None, sig
     probs = torch.empty(T, E, dtype=torch.float32, device=logits.device) if want_probs else None
     if T == 0:
         return idx, w, probs
+    _obs.note("moe.router", "deterministic_topk" if logits.is_cuda else "cpu_deterministic_topk")
     if logits.is_cuda:
         _native.check(_native.lib().ix_router_topk(logits.data_ptr(), logits.stride(0), _native.ptr(bias), T, E, k,
                                                    int(sigmoid_bias), int(norm_topk), idx.data_ptr(), w.data_ptr(),
@@ -84,6 +86,11 @@ def build_dispatch(idx: torch.Tensor, num_experts: int):
     counts  int64 [E]    rows per expert,
     pos     int64 [T, k] for each token, the dispatch row of its experts in ASCENDING expert index."""
     T, k = idx.shape
+    if idx.is_cuda and idx.dtype == torch.int32 and k <= 16:
+        # the counting-sort kernels (csrc/moe_dispatch.cu): same tables, no sort, no host round trip
+        plan = DispatchPlan(idx, num_experts, 1)
+        return plan.src_of_row[:T * k].long(), (plan.offs[1:] - plan.offs[:-1]).long(), plan.pos
+    _obs.note("moe.dispatch", "cpu_index_build" if not idx.is_cuda else "torch_sort_index_build")
     flat = idx.reshape(-1).long()
     order = torch.sort(flat, stable=True).indices            # stable: ties keep (token, slot) order
     counts = torch.bincount(flat, minlength=num_experts)
@@ -98,6 +105,7 @@ def combine_fixed_order(rows: torch.Tensor, pos: torch.Tensor, out_dtype, shared
     """out[t] = round(sum_j rows[pos[t, j]]) with j over ascending expert index (fp32), + shared after the round."""
     T, k = pos.shape
     H = rows.shape[1]
+    _obs.note("moe.combine", "fixed_order" if rows.is_cuda else "cpu_fixed_order")
     if rows.is_cuda and out_dtype in (torch.bfloat16, torch.float32) and not (torch.is_grad_enabled() and rows.requires_grad):
         out = torch.empty(T, H, dtype=out_dtype, device=rows.device)
         if T:
@@ -134,6 +142,7 @@ class _AllToAll(torch.autograd.Function):
 # ------------------------------------------------------------------------------------ experts
 def _expert_rows(x_rows, w_rows, counts, gate_up, down):
     """Rows grouped by local expert -> fp32 expert outputs, one GEMM pair per non-empty group."""
+    _obs.note("moe.experts", "cpu_grouped_gemm" if not x_rows.is_cuda else "looped_experts")
     outs = []
     lo = 0
     for e, n in enumerate(counts):
@@ -177,6 +186,7 @@ def grouped_gemm(x_rows: torch.Tensor, w: torch.Tensor, offs: torch.Tensor, epi:
 
 def expert_rows_grouped(x_rows, w_rows, offs, gate_up, down, row_dst=None):
     """fc1 + SwiGLU + gate weight in one grouped launch, fc2 (fp32 out) in a second; no host round trip."""
+    _obs.note("moe.experts", "grouped_gemm")
     a = grouped_gemm(x_rows, gate_up, offs, EPI_GLU, w_rows=w_rows.contiguous())
     return grouped_gemm(a, down, offs, EPI_F32, row_dst=row_dst)
 
@@ -195,6 +205,7 @@ class DispatchPlan:
         import ctypes as C
 
         T, k = idx.shape
+        _obs.note("moe.dispatch", "index_build")
         self.T, self.k, self.E, self.pad = T, k, num_experts, pad
         dev = idx.device
         self.r_cap = ((T * k + num_experts * (pad - 1)) + 63) // 64 * 64 if pad > 1 else max(1, T * k)
@@ -280,6 +291,8 @@ class _ExpertsFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, y, w, gate_up, down, idx, shared):
         E = gate_up.shape[0]
+        _obs.note("moe.experts", "grouped_gemm")
+        _obs.note("moe.combine", "fixed_order")
         plan = DispatchPlan(idx, E, 64)
         x_rows, w_rows = plan.gather(y, w.reshape(-1).contiguous())
         h = grouped_gemm(x_rows, gate_up, plan.offs, EPI_BF16)

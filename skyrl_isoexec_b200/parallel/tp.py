@@ -23,6 +23,7 @@ from dataclasses import dataclass
 import torch
 import torch.distributed as dist
 
+from ..core import observe as _obs
 from ..ops import functional as F
 from ..ops import _cpu, _native
 
@@ -202,6 +203,10 @@ def row_parallel_linear(x: torch.Tensor, w: torch.Tensor, ps, cfg) -> torch.Tens
     plain batch-invariant GEMM. Otherwise the leaf tree runs so that every TP degree dividing
     ``cfg.pik_leaves`` produces the same bits."""
     G = getattr(cfg, "pik_leaves", 0)
+    # one op in the contract's eyes whatever the degree: a tree whose cross-rank levels are empty at tp = 1
+    impl = "pik_tree" if x.is_cuda else "cpu_pik_tree"
+    _obs.note("collectives.row_parallel", impl)
+    _obs.note("collectives.tree_all_reduce", impl)
     if ps.tp == 1 and (G <= 1 or not cfg.tp_invariant):
         return F.linear(x, w)
     plan = ReductionPlan(G)

@@ -22,6 +22,10 @@ def setup_transports(ps, model_cfg=None, max_tokens: int = 8192, dp_staging_byte
     caps = nccl_runtime.capabilities()
     if not caps["symmetric_memory"]:
         return out
+    import os
+
+    if os.environ.get("SKYRL_ISOEXEC_PIK_P2P", "1") == "0":
+        return out          # forced onto the NCCL all-gather transport of the tree reductions (same bits, other wire)
     if ps.dp > 1 and ps.dp & (ps.dp - 1) == 0 and ps.dp <= 16:
         from .symm_runtime import SymmGroup
 

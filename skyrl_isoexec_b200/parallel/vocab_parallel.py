@@ -13,6 +13,7 @@ from __future__ import annotations
 import torch
 import torch.distributed as dist
 
+from ..core import observe as _obs
 from ..ops import _cpu, _native
 from ..ops import functional as F
 
@@ -27,6 +28,7 @@ def _staged_forward(logits, targets, G, tp, tp_rank, group, want_entropy):
     leafpx = torch.zeros(rows, G, dtype=torch.float32, device=dev) if want_entropy else None
     tl = torch.empty(rows, dtype=torch.float32, device=dev)
     targets = targets.to(torch.int64).contiguous()
+    _obs.note("logprobs.log_softmax", "rowinv_leaftree" if logits.is_cuda else "cpu_rowinv_leaftree")
     if logits.is_cuda:
         L, s, ck = _native.lib(), _native.stream(), _native.check
         ck(L.ix_logprob_rowmax(logits.data_ptr(), logits.stride(0), rows, vloc, rmax.data_ptr(), is_f32, s), "rowmax")

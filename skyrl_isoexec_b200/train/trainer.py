@@ -24,6 +24,7 @@ import torch
 import torch.distributed as dist
 
 from ..core import ledger as L
+from ..core import observe as _observe
 from ..core import process as P
 from ..core.adapter import ContractAdapter, served_ops_of
 from ..core.testing import count_bit_mismatches
@@ -279,6 +280,7 @@ class RayPPOTrainer:
         per_rank = t.train_batch_size // self.ps.dp if self.ps.dp > 1 else t.train_batch_size
         self.loader = PromptDataLoader(self.dataset, per_rank, t.seed, part=self.ps.dp_rank, parts=self.ps.dp)
         self.init_weight_sync_state()
+        self._census0 = _observe.snapshot()
 
     def init_weight_sync_state(self) -> None:
         """Stamp the trainer's contract hash on the init message; the engine's receiver refuses a mismatch."""
@@ -567,23 +569,23 @@ class RayPPOTrainer:
         """Trainer -> rollout. Same process and layout: the flat buffer is shared, so the transfer is
         the handshake, the state invalidation and the verification that the alias still holds."""
         iso = self.cfg.trainer.isoexec.enabled
+        before = self.engine.invalidation_counts()
         if self.separate_engine:
             self.all_metrics["sync/bytes"] = self.resharder.sync()
             self.all_metrics["sync/bytes_from_peers"] = self.resharder.remote_bytes
+        else:
+            req = self.sender.send_chunks(S.extract_native_weights(self.policy.model, None))
             if iso:
-                h = P.contract_hash(self.adapter_trainer.contract)
-                self.adapter_engine.on_weight_sync(self.sync_info.contract_hash, [s.state_id for s in self.adapter_engine.contract.claims.state])
-                self.adapter_trainer.on_weight_sync(P.contract_hash(self.adapter_engine.contract) if h else None)
-            self.engine.reset_prefix_cache()
-            return
-        req = self.sender.send_chunks(S.extract_native_weights(self.policy.model, None))
-        if iso:
-            n = S.load_weights(self.engine.model, ((k, v) for k, v in self.receiver.receive_weights(req)))
-            assert n == len(req.names)
-            self.adapter_engine.on_weight_sync(self.sync_info.contract_hash, [s.state_id for s in
-                                                                               self.adapter_engine.contract.claims.state])
-            self.adapter_trainer.on_weight_sync(P.contract_hash(self.adapter_engine.contract))
+                n = S.load_weights(self.engine.model, ((k, v) for k, v in self.receiver.receive_weights(req)))
+                assert n == len(req.names)
         self.engine.reset_prefix_cache()
+        if iso:
+            # what the invalidation hooks themselves counted during this sync, per state claim of the contract
+            after = self.engine.invalidation_counts()
+            observed = {s.state_id: after.get(s.state_id, {}).get("weight_sync", 0) > before.get(s.state_id, {}).get("weight_sync", 0)
+                        for s in self.adapter_engine.contract.claims.state if "weight_sync" in s.invalidated_by}
+            self.adapter_engine.on_weight_sync(self.sync_info.contract_hash, observed)
+            self.adapter_trainer.on_weight_sync(P.contract_hash(self.adapter_engine.contract))
 
     # ------------------------------------------------------------------ the loop
     def _observability(self):
@@ -658,18 +660,25 @@ class RayPPOTrainer:
             with Timer("convert", T):
                 batch = self.convert_to_training_input(go, uids)
             if self.global_step == 1 and hasattr(self, "adapter_engine"):
-                for ad in (self.adapter_engine,):
-                    ad.note_served(served_ops_of(self.policy.model.cfg))
-                    ad.on_first_forward()
+                # everything the op layer ran since the models were built was the engine's (generation)
+                self.adapter_engine.on_first_forward(_observe.diff(self._census0))
+            c1 = _observe.snapshot()
             with Timer("fwd_logprobs", T):
                 batch = self.fwd_logprobs_values_reward(batch)
             if self.global_step == 1 and hasattr(self, "adapter_trainer"):
-                self.adapter_trainer.note_served(served_ops_of(self.policy.model.cfg))
-                self.adapter_trainer.on_first_forward()
+                if self._reuse_rollout_logprobs():
+                    # no scoring forward on this configuration: the trainer's first forward is the training forward,
+                    # judged after the update below
+                    self._pending_trainer_census = c1
+                else:
+                    self.adapter_trainer.on_first_forward(_observe.diff(c1))
             with Timer("advantages", T):
                 batch = self.compute_advantages_and_returns(batch)
             with Timer("policy_train", T):
                 self.train_critic_and_policy(batch)
+            if getattr(self, "_pending_trainer_census", None) is not None:
+                self.adapter_trainer.on_first_forward(_observe.diff(self._pending_trainer_census))
+                self._pending_trainer_census = None
             if self.cfg.trainer.record_memory:
                 from ..utils.profiler import save_memory_snapshot
 

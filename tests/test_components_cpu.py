@@ -311,7 +311,24 @@ def test_fusion_ledger_digest_and_checkers():
     assert len(d) == 24 and d == FL.ledger_digest()
     assert FL.ledger_digest(FL.REGIONS[:-1]) != d                       # a different fusion set is a different contract
     res = FL.run_checkers("cpu")
-    assert res["rmsnorm+residual"] is True and res["logprob_fused"] is True
+    assert set(res) == {r.name for r in FL.REGIONS}                     # every fused region has a checker
+    cpu_checkable = ("rmsnorm+residual", "logprob_fused", "qk_norm+rope+kv_write", "leaftree_gemm (LOCAL)",
+                     "attention (prefill | decode | chunk)", "gdn_scan (chunked | recurrent)")
+    assert all(res[n] is True for n in cpu_checkable), res
+    assert all(v is not False for v in res.values())                    # the rest is deferred to a GPU, never "differs"
+    # a region nobody can prove blocks the preflight instead of passing as "unknown"
+    extra = FL.REGIONS + (FL.FusedRegion("made_up_fusion", ("a", "b"), "bitwise"),)
+    old_regions, FL.REGIONS = FL.REGIONS, extra
+    try:
+        import pytest as _pt
+
+        with _pt.raises(LookupError):
+            FL.run_checkers("cpu")
+        from skyrl_isoexec_b200.core import preflight
+
+        assert any("made_up_fusion" in e for e in preflight.check_fusion_ledger())
+    finally:
+        FL.REGIONS = old_regions
     x = FL.hazard_population((64, 64), torch.float32, "cpu")
     assert (x == 0).any() and (x.abs() > 1e30).any() and (x.abs() < 1e-35).logical_and(x != 0).any()
 

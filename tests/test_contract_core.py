@@ -251,3 +251,74 @@ def test_signature_table_needs_proof():
     t.admit("m", "h", "sm100", (0.0, 0.0), proof_ref="tests/test_gpu_kernels.py::test_engine_and_trainer")
     assert t.check("m", "h", "sm100", 0.0)[0] and not t.check("m", "h", "sm100", 1e-7)[0]
     assert not t.check("m", "other", "sm100", 0.0)[0]
+
+
+def _tiny_trainer(tmp_path, model="tiny-qwen3"):
+    from skyrl_isoexec_b200.train.config import SkyRLTrainConfig
+    from skyrl_isoexec_b200.train.trainer import RayPPOTrainer
+
+    cfg = SkyRLTrainConfig.from_cli_overrides([
+        f"trainer.policy.model={model}", "trainer.train_batch_size=2", "trainer.policy_mini_batch_size=2",
+        "generator.n_samples_per_prompt=2", "generator.sampling_params.max_generate_length=6",
+        "generator.sampling_params.ignore_eos=true", "data.synthetic_prompt_len=8", "data.synthetic_prompts=8",
+        "trainer.max_prompt_length=8", "generator.inference_engine.num_kv_pages=8", "trainer.logger=jsonl",
+        f"trainer.ckpt_path={tmp_path}", "trainer.ckpt_interval=0"])
+    tr = RayPPOTrainer(cfg, device="cpu")
+    tr.build_models()
+    tr.sync_weights()
+    return tr
+
+
+def test_ledger_refuses_when_an_op_is_served_by_another_path(tmp_path, monkeypatch):
+    """Enforcement observes: the served records come from what the op layer really dispatched. An activation that is
+    quietly computed by torch instead of the contract's kernel makes the first forward refuse."""
+    import torch
+
+    from skyrl_isoexec_b200.core import ledger as LG
+    from skyrl_isoexec_b200.core import observe
+    from skyrl_isoexec_b200.ops import functional as F
+
+    tr = _tiny_trainer(tmp_path)
+    m = tr.train_step(next(iter(tr.loader)))                       # the honest run closes every phase
+    assert m["policy/rollout_train_logprob_bit_mismatches"] == 0
+    assert tr.adapter_trainer.ledger.verdict()["ok"] and tr.adapter_engine.ledger.verdict()["ok"]
+    rec = tr.adapter_engine.ledger.verdict()["records"]
+    assert "cpu_swiglu" in rec["FIRST_FORWARD/served/activation.swiglu"]["detail"]      # observed, with the impl that ran
+
+    def eager_swiglu(x):                                           # same maths, another implementation
+        observe.note("activation.swiglu", "torch_eager")
+        f = x.shape[1] // 2
+        return (torch.nn.functional.silu(x[:, :f].float()) * x[:, f:].float()).to(x.dtype)
+
+    monkeypatch.setattr(F, "swiglu_fwd", eager_swiglu)
+    tr2 = _tiny_trainer(tmp_path)
+    with pytest.raises(LG.ContractViolation) as ei:
+        tr2.train_step(next(iter(tr2.loader)))
+    assert "activation.swiglu" in str(ei.value) and "torch_eager" in str(ei.value)
+
+
+def test_ledger_sees_a_weight_sync_that_did_not_invalidate_the_cache(tmp_path, monkeypatch):
+    """The installed_backstop records come from the invalidation hooks' own counters, not from the caller's word."""
+    tr = _tiny_trainer(tmp_path)
+    tr.train_step(next(iter(tr.loader)))
+    assert tr.adapter_engine.ledger.verdict()["ok"]
+    monkeypatch.setattr(tr.engine.cache, "invalidate", lambda event: False)           # a hook that no longer does its job
+    tr.sync_weights()
+    v = tr.adapter_engine.ledger.verdict()
+    assert not v["ok"] and any("invalidate:engine_kv_cache" in m for m in v["violations"])
+
+
+def test_install_fingerprint_is_taken_from_the_library_on_the_models_device(tmp_path):
+    """A contract that names sm100 kernels cannot be attested by a model that lives on the CPU."""
+    from skyrl_isoexec_b200.core import ledger as LG
+    from skyrl_isoexec_b200.core.adapter import ContractAdapter
+    from skyrl_isoexec_b200.models.config import get_config
+    from skyrl_isoexec_b200.models.decoder import DecoderLM
+
+    model = DecoderLM(get_config("tiny-qwen3"), device="cpu", seed=0)
+    ok = ContractAdapter("trainer", model)
+    ok.run_install()
+    assert ok.library["version"] >= 1 and not ok.library["missing"] and ok.ledger.verdict()["ok"]
+    with pytest.raises(LG.ContractViolation) as ei:
+        ContractAdapter("trainer", model, arch="sm100").run_install()
+    assert "wrong-device" in str(ei.value)

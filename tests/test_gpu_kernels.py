@@ -730,3 +730,13 @@ def test_moe_experts_autograd_function_matches_fp32_autograd_and_the_fused_forwa
     empty = [e for e in range(E) if not bool((idx == e).any())]
     for e in empty:
         assert not gate_up.grad[e].any() and not down.grad[e].any()
+
+
+def test_every_fused_region_equals_its_unfused_chain_on_hazard_inputs():
+    """The fusion ledger's checkers on the GPU: everything except the multi-GPU kernels is decided here."""
+    from skyrl_isoexec_b200.core import fusion_ledger as FL
+
+    res = FL.run_checkers(DEV)
+    multi = {"tp_gemm_fused (AR1/AR2/RS)", "tp_gemm_fused (AG)"}
+    assert all(res[n] is True for n in res if n not in multi), res
+    assert all(res[n] is not False for n in multi)
