@@ -272,6 +272,12 @@ class RayPPOTrainer:
             self.adapter_trainer.run_install()
             self.adapter_engine = ContractAdapter("engine", self.engine.model, self.rank, trainer_tp=self.ps.tp, engine_tp=tp_e)
             self.adapter_engine.run_install()
+            # the admitted steady-state signature of this (model, contract, arch): under the contract the band of the
+            # mean |rollout - train| logprob difference is exactly zero (R/.../isoexec/core/signatures.py:48-131)
+            from ..core.signatures import bitwise_table
+
+            self._sig_key = (mcfg.name, self.adapter_trainer.contract.identities.numerical_policy, self.adapter_trainer.arch)
+            self.signatures = bitwise_table(*self._sig_key, proof_ref="tests/test_train_cpu.py::test_grpo_loop_is_bitwise_on_policy_and_resumes")
         if self.dataset is None:
             d = self.cfg.data
             n = d.synthetic_prompts or t.train_batch_size * 4
@@ -427,6 +433,11 @@ class RayPPOTrainer:
         iso = self.cfg.trainer.isoexec
         if iso.enabled and not self._gate_in_update:
             gate = validate_isoexec_forward_gate(diff, mask, mism, iso)
+            if iso.require_bitwise and getattr(self, "signatures", None) is not None:
+                sig_ok, why = self.signatures.check(*self._sig_key, gate["mean"])
+                if not sig_ok:
+                    gate["ok"] = False
+                    gate["signature"] = why
             if self.global_step <= 1 and hasattr(self, "adapter_trainer"):
                 self.adapter_trainer.on_gate(gate["ok"], f"mean={gate['mean']:.3e} max={gate['max']:.3e} "
                                                            f"mismatches={gate['mismatches']}")
