@@ -101,13 +101,14 @@ def resolve_ref(ref: str) -> bool:
 
 class ContractAdapter:
     def __init__(self, side: str, model, rank: int = 0, trainer_tp: int | None = None, engine_tp: int | None = None,
-                 arch: str | None = None):
+                 arch: str | None = None, trainer_pp: int | None = None):
         self.side = side
         self.model = model
         self.rank = rank
         ps = model.ps
         self.trainer_tp = trainer_tp if trainer_tp is not None else ps.tp
         self.engine_tp = engine_tp if engine_tp is not None else ps.tp
+        self.trainer_pp = trainer_pp if trainer_pp is not None else ps.pp
         self.arch = arch or detect_arch(model.device_)
         self.fingerprint = Fingerprint()
         self.served: Counter = Counter()
@@ -118,7 +119,7 @@ class ContractAdapter:
     # ------------------------------------------------------------------ INSTALL
     def build_contract(self) -> M.ExecutionContract:
         cfg, ps = self.model.cfg, self.model.ps
-        profile = profile_from_model_config(cfg, self.trainer_tp, self.engine_tp, ps.pp, ps.cp, ps.ep)
+        profile = profile_from_model_config(cfg, self.trainer_tp, self.engine_tp, self.trainer_pp, ps.cp, ps.ep)
         reg = build_registry()
         self.selections = derive_selections(profile, self.arch)
         return build_execution_contract(profile, reg, self.selections, self.arch)
@@ -161,7 +162,7 @@ class ContractAdapter:
                     self.fingerprint.record_install(op, cid, seen, obj=lib, pinned={})
         # pins: what this process would run with, read from the live model configuration
         live = {k: dict(s.pins) for k, s in derive_selections(
-            profile_from_model_config(self.model.cfg, self.trainer_tp, self.engine_tp, self.model.ps.pp, self.model.ps.cp,
+            profile_from_model_config(self.model.cfg, self.trainer_tp, self.engine_tp, self.trainer_pp, self.model.ps.cp,
                                       self.model.ps.ep), self.arch).items()}
         for (op, site), pins in live.items():
             rec = self.fingerprint.records.get((op, site))
@@ -210,10 +211,11 @@ class ContractAdapter:
                     out.setdefault(op, set()).add(e.impl.id)
         return out
 
-    def on_first_forward(self, census=None) -> None:
+    def on_first_forward(self, census=None, not_on_this_rank=()) -> None:
         """Close FIRST_FORWARD. ``census``: {(op, impl id): calls} observed by the op layer during the forward being
         judged (``core.observe.diff``). An op is served iff something ran for it and everything that ran for it is an
-        implementation the contract names; an op that a fused kernel subsumes is served when its owner is."""
+        implementation the contract names; an op that a fused kernel subsumes is served when its owner is.
+        ``not_on_this_rank``: ops that belong to layers another pipeline stage holds."""
         from . import observe
 
         lg = self.ledger
@@ -230,6 +232,10 @@ class ContractAdapter:
                 lg.report("served", o.key, n > 0, "" if n > 0 else "declared but never executed in the first forward")
                 continue
             op = owner.get(o.key, o.key)
+            if op in not_on_this_rank or o.key in not_on_this_rank:
+                # a pipeline stage owns a subset of the layers: ops of layers it does not hold run on another stage
+                lg.report("served", o.key, True, "served by another pipeline stage")
+                continue
             got = observe.ran(census, op)
             if not got and self.served.get(o.key, 0) > 0:
                 got = {next(iter(want.get(op, {"?"}))): self.served[o.key]}

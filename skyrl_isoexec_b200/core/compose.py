@@ -104,7 +104,10 @@ def profile_from_model_config(cfg: ModelConfig, trainer_tp: int = 1, engine_tp: 
         tp_fact = TopologyAxisFact("tp", "pinned", degree=trainer_tp,
                                    collective_plan=f"pik-tree:G={G}:leaf=fp32" if trainer_tp > 1 else "none")
     topo = [tp_fact,
-            TopologyAxisFact("pp", "pinned", degree=pp, collective_plan="nccl-p2p-bytes-only"),
+            # a stage boundary moves the (x, residual) pair as bytes: with a pipelined trainer the engines (pp = 1) and the
+            # trainer (pp stages) compute the same function, which the claim states as invariance over both degrees
+            (TopologyAxisFact("pp", "pinned", degree=1, collective_plan="nccl-p2p-bytes-only") if pp == 1 else
+             TopologyAxisFact("pp", "invariant", domain=(1, pp), proof="skyrl_isoexec_b200/parallel/pp.py::PipelinePolicyWorker")),
             TopologyAxisFact("cp", "pinned", degree=cp, collective_plan="none" if cp == 1 else "ulysses-a2a-bytes-only")]
     if cfg.has_moe:
         topo.append(TopologyAxisFact("ep", "invariant", domain=(1, 2, 4, 8),

@@ -239,3 +239,54 @@ def symmetric_flat_allocator(group):
         return [int(p) for p in h.buffer_ptrs], h
 
     return alloc, rendezvous
+
+
+class PipelineStageSync:
+    """Trainer with pipeline parallelism, engines without: every pipeline stage holds the parameters of its own layers,
+    every engine needs all of them. Stage by stage, the owning rank broadcasts its flat buffer inside the pipeline
+    group and every rank copies that stage's parameters into its engine model (same tensor-parallel layout on both
+    sides, so each parameter is one contiguous copy). Reference: the Megatron backend gathers across pipeline ranks
+    when it exports weights for the engines, B/workers/megatron/megatron_worker.py:569-571."""
+
+    def __init__(self, trainer_model, engine_model, ps):
+        from ..models.decoder import ParamStore, build_param_specs
+        from ..parallel.pp import stage_layers
+        import copy
+
+        self.t, self.e, self.ps = trainer_model, engine_model, ps
+        if engine_model.ps.tp != ps.tp or engine_model.ps.ep != ps.ep:
+            raise ValueError("with a pipelined trainer the engines use the trainer's tensor- and expert-parallel degrees")
+        cfg = trainer_model.cfg
+        self.stages = []          # per stage: (numel of its flat buffer, [(name, offset, numel)])
+        for s in range(ps.pp):
+            ps_s = copy.copy(ps)
+            ps_s.pp_rank = s
+            specs = build_param_specs(cfg, ps_s, stage_layers(cfg.num_layers, ps.pp, s))
+            off, items = 0, []
+            for sp in specs:
+                n = math.prod(sp.shape)
+                items.append((sp.name, off, n))
+                off += (n + ParamStore.ALIGN - 1) // ParamStore.ALIGN * ParamStore.ALIGN
+            self.stages.append((off, items))
+        assert self.stages[ps.pp_rank][0] == trainer_model.store.numel, "stage layout differs from the live parameter store"
+        self.total_bytes = sum(n for n, _ in self.stages) * trainer_model.store.flat.element_size()
+        self.remote_bytes = self.total_bytes - self.stages[ps.pp_rank][0] * trainer_model.store.flat.element_size()
+
+    @torch.no_grad()
+    def sync(self) -> int:
+        ps = self.ps
+        mine = self.t.store.flat.detach()
+        done = set()
+        for s, (numel, items) in enumerate(self.stages):
+            buf = mine if s == ps.pp_rank else torch.empty(numel, dtype=mine.dtype, device=mine.device)
+            dist.broadcast(buf, src=ps.pp_ranks[s], group=ps.pp_group)
+            for name, off, n in items:
+                if name in done or name not in self.e.store.views:      # a tied embedding lives on two stages: first wins
+                    continue
+                dst = self.e.store.views[name]
+                dst.copy_(buf[off:off + n].view(dst.shape))
+                done.add(name)
+        missing = [n for n in self.e.store.order if n not in done]
+        if missing:
+            raise KeyError(f"no pipeline stage delivered {missing[:4]}")
+        return self.total_bytes

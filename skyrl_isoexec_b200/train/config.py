@@ -347,5 +347,7 @@ def validate_cfg(cfg: SkyRLTrainConfig, world_size: int = 1) -> None:
                              f"groups of size {tp} (the trainer degree has to be a multiple of the engine degree)")
         if p.pipeline_model_parallel_size > 1 or p.context_parallel_size > 1 or p.expert_model_parallel_size > 1:
             raise ValueError("engines with their own tensor-parallel degree need pp = cp = ep = 1 on the trainer")
+    if p.pipeline_model_parallel_size > 1 and (p.context_parallel_size > 1 or p.expert_model_parallel_size > 1):
+        raise ValueError("a pipelined trainer (pipeline_model_parallel_size > 1) supports tensor and data parallelism only")
     if ie.num_engines not in (0, 1) and ie.num_engines * etp != world_size:
         raise ValueError(f"num_engines={ie.num_engines} x tensor_parallel_size={etp} must cover the {world_size} GPUs of a colocated job")

@@ -356,6 +356,15 @@ class FlatAdamW:
             tot = ex.clone()
             dist.all_reduce(tot, group=ps.ep_group)
             self._sq = self._sq - ex + tot
+        if ps.pp > 1:
+            # every pipeline stage holds its own layers: the global norm is the sum over stages (a tied embedding sits on
+            # the first and the last stage with the same, already summed, gradient: counted on the first only)
+            local = self._sq.clone()
+            if self.model.cfg.tie_embeddings and ps.is_last_pp and not ps.is_first_pp and "embed.weight" in self.model.store.specs:
+                s = self.model.store.specs["embed.weight"]
+                local = local - self.main_grad[s.offset:s.offset + math.prod(s.shape)].square().sum()
+            dist.all_reduce(local, group=ps.pp_group)
+            self._sq = local
         return self._sq
 
     def step(self, ps: ParallelState) -> torch.Tensor:

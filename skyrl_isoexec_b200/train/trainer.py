@@ -176,6 +176,20 @@ class RayPPOTrainer:
         self.separate_engine = tp_e != self.ps.tp
         self.engine_ps = self.ps
         self.engines_per_replica = 1
+        self.replica_group, self.replica_size, self.replica_rank = self.ps.tp_group, self.ps.tp, self.ps.tp_rank
+        if self.ps.pp > 1:
+            # pipelined trainer: every rank also holds an un-pipelined engine of the trainer's TP degree; the pp engines of
+            # a replica split its requests and swap rollouts inside the pipeline group; the sync gathers the stages
+            if tp_e != self.ps.tp or self.ps.cp > 1:
+                raise ValueError("a pipelined trainer feeds engines of its own tensor-parallel degree (cp = 1)")
+            import copy
+
+            self.separate_engine = True
+            self.engine_ps = copy.copy(self.ps)
+            self.engine_ps.pp, self.engine_ps.pp_rank, self.engine_ps.pp_group, self.engine_ps.pp_ranks = 1, 0, None, [self.ps.rank]
+            self.engines_per_replica = self.ps.pp
+            self.replica_group, self.replica_size, self.replica_rank = self.ps.pp_group, self.ps.pp, self.ps.pp_rank
+            return tp_e
         if self.separate_engine:
             if self.ps.tp % tp_e or self.ps.pp > 1 or self.ps.cp > 1 or self.ps.ep > 1:
                 raise ValueError(f"engine TP {tp_e} must divide trainer TP {self.ps.tp}, with pp = cp = ep = 1")
@@ -183,6 +197,12 @@ class RayPPOTrainer:
                 else ParallelState.single()
             self.engines_per_replica = self.ps.tp // tp_e
         return tp_e
+
+    def _engine_index(self) -> int:
+        """Global index of the engine this rank belongs to (all ranks of one engine share a sampler stream)."""
+        if self.ps.pp > 1:
+            return self.ps.dp_rank * self.ps.pp + self.ps.pp_rank
+        return self.engine_ps.dp_rank if self.separate_engine else self.ps.dp_rank
 
     def _setup_transports(self, mcfg) -> None:
         """Peer-memory transports for every group this job computes over (GPUs with peer access only)."""
@@ -219,14 +239,24 @@ class RayPPOTrainer:
                 from ..sync.reshard import symmetric_flat_allocator
 
                 flat_alloc, self._flat_rendezvous = symmetric_flat_allocator(self.ps.tp_group)
-        model = DecoderLM(mcfg, self.ps, self.device, seed=t.policy.seed, flat_alloc=flat_alloc)
+        if self.ps.pp > 1:
+            from ..parallel.pp import build_stage_model
+
+            model = build_stage_model(mcfg, self.ps, self.device, seed=t.policy.seed)
+        else:
+            model = DecoderLM(mcfg, self.ps, self.device, seed=t.policy.seed, flat_alloc=flat_alloc)
         wcfg = WorkerConfig(max_tokens_per_microbatch=t.max_tokens_per_microbatch, optimizer=t.policy.optimizer_config,
                             keep_last_layers=t.policy.keep_last_layers, shard_optimizer=t.policy.shard_optimizer,
                             want_entropy=t.algorithm.use_entropy_loss)
         algo = t.algorithm
         if not algo.max_seq_len:
             algo.max_seq_len = t.max_prompt_length + g.sampling_params.max_generate_length
-        self.policy = PolicyWorker(model, wcfg, algo)
+        if self.ps.pp > 1:
+            from ..parallel.pp import PipelinePolicyWorker
+
+            self.policy = PipelinePolicyWorker(model, wcfg, algo)
+        else:
+            self.policy = PolicyWorker(model, wcfg, algo)
         self.ref = self.critic = None
         if algo.use_kl_loss or algo.use_kl_in_reward:
             from .ref_critic import RefWorker
@@ -250,7 +280,7 @@ class RayPPOTrainer:
         ecfg = EngineConfig(max_num_seqs=ie.max_num_seqs, max_num_batched_tokens=ie.max_num_batched_tokens,
                             num_kv_pages=ie.num_kv_pages, gpu_memory_utilization=ie.gpu_memory_utilization,
                             # one sampler stream per engine; the ranks of one engine share it
-                            seed=t.seed + 7919 * (self.engine_ps.dp_rank if self.separate_engine else self.ps.dp_rank),
+                            seed=t.seed + 7919 * self._engine_index(),
                             enable_prefix_caching=ie.enable_prefix_caching,
                             use_cuda_graph=not ie.enforce_eager,
                             max_model_len=min(mcfg.max_position, t.max_prompt_length + g.sampling_params.max_generate_length + 1))
@@ -268,9 +298,10 @@ class RayPPOTrainer:
                                            apply_overlong_filtering=g.apply_overlong_filtering,
                                            rate_limit=g.rate_limit or None, step_wise=g.step_wise_trajectories)
         if t.isoexec.enabled:
-            self.adapter_trainer = ContractAdapter("trainer", model, self.rank, trainer_tp=self.ps.tp, engine_tp=tp_e)
+            self.adapter_trainer = ContractAdapter("trainer", model, self.rank, trainer_tp=self.ps.tp, engine_tp=tp_e, trainer_pp=self.ps.pp)
             self.adapter_trainer.run_install()
-            self.adapter_engine = ContractAdapter("engine", self.engine.model, self.rank, trainer_tp=self.ps.tp, engine_tp=tp_e)
+            self.adapter_engine = ContractAdapter("engine", self.engine.model, self.rank, trainer_tp=self.ps.tp, engine_tp=tp_e,
+                                                  trainer_pp=self.ps.pp)
             self.adapter_engine.run_install()
             # the admitted steady-state signature of this (model, contract, arch): under the contract the band of the
             # mean |rollout - train| logprob difference is exactly zero (R/.../isoexec/core/signatures.py:48-131)
@@ -298,7 +329,9 @@ class RayPPOTrainer:
             info = S.ReshardInitInfo(contract_hash=P.contract_hash() if iso else None, engine_tp=self.engine_ps.tp, trainer_tp=self.ps.tp)
             if iso:
                 P.assert_init_info_contract(info)          # engine side of the handshake
-            if self._flat_rendezvous is not None:
+            if self.ps.pp > 1:
+                self.resharder = R.PipelineStageSync(self.policy.model, self.engine.model, self.ps)
+            elif self._flat_rendezvous is not None:
                 ptrs, self._flat_handle = self._flat_rendezvous(self.policy.model.store.flat)
                 self.resharder = R.PeerPullResharder(self.policy.model, self.engine.model, self.ps.tp_group, self.ps.tp_rank, ptrs)
             else:
@@ -338,7 +371,7 @@ class RayPPOTrainer:
         from .trainer_utils import _cat, _take
 
         k, n = self.engines_per_replica, len(gi["prompts"])
-        e = self.ps.tp_rank // self.engine_ps.tp
+        e = self.replica_rank if self.ps.pp > 1 else self.ps.tp_rank // self.engine_ps.tp
         lo, hi = e * n // k, (e + 1) * n // k
         part = dict(gi)
         for key in ("prompts", "env_classes", "env_extras", "trajectory_ids"):
@@ -346,8 +379,9 @@ class RayPPOTrainer:
                 part[key] = gi[key][lo:hi]
         go = asyncio.run(self.generator.generate(part))
         go.pop("rollout_metrics", None)
-        box = [None] * self.ps.tp
-        dist.all_gather_object(box, go if self.engine_ps.tp_rank == 0 else None, group=self.ps.tp_group)
+        box = [None] * self.replica_size
+        lead = True if self.ps.pp > 1 else self.engine_ps.tp_rank == 0      # one copy per engine
+        dist.all_gather_object(box, go if lead else None, group=self.replica_group)
         merged = None
         for g_ in box:
             if g_ is not None:
@@ -617,6 +651,21 @@ class RayPPOTrainer:
                 self._gpu_mon.start()
         return self._prof
 
+    def _ops_of_other_stages(self) -> tuple:
+        """Contract ops that this pipeline stage does not execute because the layers that use them live elsewhere."""
+        if self.ps.pp == 1:
+            return ()
+        cfg, ids = self.policy.model.cfg, self.policy.model.layer_ids
+        out = []
+        if not self.ps.is_last_pp:
+            out += ["logprobs.log_softmax", "logprobs.lm_head_slice"]
+        kinds = {cfg.layer_type(i) for i in ids}
+        if "attn" not in kinds:
+            out += ["attention.varlen", "rope.rope", "norms.qk", "activation.attn_gate"]
+        if "gdn" not in kinds:
+            out += ["gdn.core", "gdn.conv", "gdn.gating", "gdn.state", "norms.gated_out"]
+        return tuple(out)
+
     def _extra_prompts(self, n: int) -> list[dict]:
         """More prompts for dynamic sampling, drawn from a stream of their own (the epoch iterator that feeds
         ``train()`` is not touched): a seeded walk over the dataset, disjoint across data-parallel ranks, that wraps around."""
@@ -682,13 +731,13 @@ class RayPPOTrainer:
                     # judged after the update below
                     self._pending_trainer_census = c1
                 else:
-                    self.adapter_trainer.on_first_forward(_observe.diff(c1))
+                    self.adapter_trainer.on_first_forward(_observe.diff(c1), self._ops_of_other_stages())
             with Timer("advantages", T):
                 batch = self.compute_advantages_and_returns(batch)
             with Timer("policy_train", T):
                 self.train_critic_and_policy(batch)
             if getattr(self, "_pending_trainer_census", None) is not None:
-                self.adapter_trainer.on_first_forward(_observe.diff(self._pending_trainer_census))
+                self.adapter_trainer.on_first_forward(_observe.diff(self._pending_trainer_census), self._ops_of_other_stages())
                 self._pending_trainer_census = None
             if self.cfg.trainer.record_memory:
                 from ..utils.profiler import save_memory_snapshot
