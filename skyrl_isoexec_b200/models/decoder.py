@@ -300,7 +300,14 @@ class DecoderLM(nn.Module):
         if fc.kv is None:
             q, k, v = F.qk_norm_rope_train(qkv, fc.positions, self.rope, qw, kw, self.hq, self.hkv, cfg.head_dim,
                                            cfg.rms_eps, cfg.qk_norm, cfg.zero_centered_norm, cfg.attn_output_gate)
-            a = F.attention(q, k, v, fc.meta, self.scale)
+            if self.ps.cp > 1:
+                # context parallelism: tokens are cut over the cp ranks; an all-to-all gives every rank all tokens of a
+                # slice of the heads for the attention kernel and the inverse brings the result back (bytes only)
+                from ..parallel import cp as cp_ops
+
+                a = cp_ops.ulysses_attention(q, k, v, fc.meta, self.scale, self.ps)
+            else:
+                a = F.attention(q, k, v, fc.meta, self.scale)
         else:
             k_pool, v_pool = fc.kv[kv_idx]
             q = F.qk_norm_rope_fwd(qkv, fc.positions, fc.slots, self.rope, qw, kw, k_pool, v_pool, self.hq, self.hkv,

@@ -521,6 +521,8 @@ class PolicyWorker:
 
     def _run_model(self, mb: PackedMicroBatch, site: str):
         dev = self.device
+        if self.ps.cp > 1:
+            return self._run_model_cp(mb, site)
         fc = ForwardCtx(positions=mb.positions.to(dev, non_blocking=True),
                         meta=F.AttnMeta.packed(mb.seq_lens, self.model.hq, self.model.hkv, dev), site=site)
         if self.model.cfg.has_gdn:
@@ -530,6 +532,36 @@ class PolicyWorker:
         hidden = self.model(mb.ids.to(dev, non_blocking=True), fc,
                             checkpoint_layers=self._ckpt_arg())
         return hidden
+
+    # ---------------------------------------------------------------- context parallelism
+    def _cp_span(self, mb: PackedMicroBatch) -> tuple[int, int, int]:
+        """(padded token count, first token, one past the last token) of this rank's contiguous share of a micro-batch."""
+        cp = self.ps.cp
+        Tp = (int(mb.ids.numel()) + cp - 1) // cp * cp
+        n = Tp // cp
+        return Tp, self.ps.cp_rank * n, (self.ps.cp_rank + 1) * n
+
+    def _run_model_cp(self, mb: PackedMicroBatch, site: str):
+        """The packed micro-batch is padded to a multiple of cp tokens (the padding forms a sequence of its own, so no real
+        token attends to it) and cut into cp contiguous shares; this rank runs the model on its share and the attention
+        layers exchange heads for tokens (``parallel/cp.py::ulysses_attention``). Returns the hidden rows of the share.
+        Reference: B/distributed/megatron/model_utils.py:1438-1540, B/distributed/ulysses/utils.py:66-240."""
+        c = self.model.cfg
+        if c.has_gdn:
+            raise ValueError("context parallelism cuts sequences across ranks; GatedDeltaNet layers scan a sequence in order and are not supported with it")
+        cp, dev = self.ps.cp, self.device
+        if self.model.hq % cp or self.model.hkv % cp:
+            raise ValueError(f"context_parallel_size={cp} must divide the local query ({self.model.hq}) and KV ({self.model.hkv}) head counts")
+        T = int(mb.ids.numel())
+        Tp, lo, hi = self._cp_span(mb)
+        ids, pos, lens = mb.ids, mb.positions, list(mb.seq_lens)
+        if Tp > T:
+            ids = torch.cat([ids, ids.new_zeros(Tp - T)])
+            pos = torch.cat([pos, torch.arange(Tp - T, dtype=pos.dtype)])
+            lens.append(Tp - T)
+        fc = ForwardCtx(positions=pos[lo:hi].contiguous().to(dev, non_blocking=True),
+                        meta=F.AttnMeta.packed(lens, self.model.hq // cp, self.model.hkv // cp, dev), site=site)
+        return self.model(ids[lo:hi].contiguous().to(dev, non_blocking=True), fc, checkpoint_layers=self._ckpt_arg())
 
     def _pack(self, seqs, att, R):
         """Micro-batches of this rank. Under expert parallelism every rank of the EP group runs the same number of them
@@ -543,10 +575,18 @@ class PolicyWorker:
         return mbs
 
     def _logprobs(self, mb: PackedMicroBatch, hidden, want_entropy: bool):
+        """(logprobs, entropies, flat output index) of the response tokens this rank predicts: all of the micro-batch's, or
+        under context parallelism those whose predicting row lies in this rank's share of the tokens."""
         dev = self.device
-        rows = mb.pred_rows.to(dev, non_blocking=True)
-        tg = mb.targets.to(dev, non_blocking=True)
-        return lm_head_logprobs(self.model, hidden.index_select(0, rows), tg, self.cfg.logprob_chunk_rows, want_entropy)
+        rows, tg, oi = mb.pred_rows, mb.targets, mb.out_index
+        if self.ps.cp > 1:
+            _, lo, hi = self._cp_span(mb)
+            mine = (rows >= lo) & (rows < hi)
+            rows, tg, oi = rows[mine] - lo, tg[mine], oi[mine]
+        rows = rows.to(dev, non_blocking=True)
+        tg = tg.to(dev, non_blocking=True)
+        lp, ent = lm_head_logprobs(self.model, hidden.index_select(0, rows), tg, self.cfg.logprob_chunk_rows, want_entropy)
+        return lp, ent, oi.to(dev)
 
     # ---------------------------------------------------------------- verbs
     @torch.no_grad()
@@ -557,10 +597,15 @@ class PolicyWorker:
         out = torch.zeros(seqs.shape[0], R, dtype=torch.float32)
         for mb in self._pack(seqs, att, R):
             hidden = self._run_model(mb, "trainer_score")
-            lp, _ = self._logprobs(mb, hidden, False)
+            lp, _, oi = self._logprobs(mb, hidden, False)
             flat = torch.zeros(len(mb.seq_index) * R, dtype=torch.float32, device=lp.device)
-            flat[mb.out_index.to(lp.device)] = lp
+            flat[oi] = lp
             out[torch.tensor(mb.seq_index)] = flat.view(-1, R).cpu()
+        if self.ps.cp > 1:
+            # every rank filled the tokens of its own share and left zeros elsewhere: a sum is an exact merge
+            t = out.to(self.device) if self.device.type == "cuda" else out
+            dist.all_reduce(t, group=self.ps.cp_group)
+            out = t.cpu()
         return out
 
     def forward_backward(self, batch: TrainingInputBatch) -> dict:
@@ -583,8 +628,7 @@ class PolicyWorker:
                 self.opt.begin_overlap()          # gradients of this backward are final: reduce them bucket by bucket
             idx = torch.tensor(mb.seq_index)
             hidden = self._run_model(mb, "trainer_fwd")
-            lp_flat, ent_flat = self._logprobs(mb, hidden, want_ent)
-            oi = mb.out_index.to(dev)
+            lp_flat, ent_flat, oi = self._logprobs(mb, hidden, want_ent)
             nb = len(mb.seq_index)
 
             def to2d(x):
@@ -593,6 +637,12 @@ class PolicyWorker:
             lp2d = to2d(lp_flat)
             get = lambda k: (batch[k][idx].to(dev).float() if batch.get(k) is not None else None)
             mask = get("loss_mask") if batch.get("loss_mask") is not None else get("response_mask")
+            if self.ps.cp > 1:
+                # the loss is a sum over tokens: each context-parallel rank takes the tokens it predicted, the gradient
+                # sum over the cp group (reduce_gradients) puts the pieces together
+                if algo.policy_loss_type in ("gspo", "sapo"):
+                    raise ValueError(f"policy_loss_type={algo.policy_loss_type!r} needs whole-sequence statistics and is not supported with context parallelism")
+                mask = mask * to2d(torch.ones_like(lp_flat))
             old = get("action_log_probs")
             if old is None:
                 old = lp2d.detach()
@@ -626,6 +676,11 @@ class PolicyWorker:
             tot["loss"] += float(loss.detach())
             tot["clip_ratio_num"] += float(m.get("clip_ratio", 0.0)) * float(ntok)
             tot["tokens"] += float(ntok)
+        if self.ps.cp > 1:
+            keys = sorted(tot)
+            t = torch.tensor([tot[k] for k in keys], dtype=torch.float64, device=dev if dev.type == "cuda" else "cpu")
+            dist.all_reduce(t, group=self.ps.cp_group)
+            tot = {k: float(v) for k, v in zip(keys, t.tolist())}
         n = max(1.0, tot["tokens"])
         out = {"policy_loss": tot["loss"], "ppo_clip_ratio": tot["clip_ratio_num"] / n, "loss_tokens": tot["tokens"],
                "policy_entropy": tot["entropy_sum"] / n, "policy_kl": tot["kl_sum"] / n}
@@ -665,6 +720,11 @@ class PolicyWorker:
                     # the ranks that share a KV head each saw the gradient from their own query heads only
                     lo, n = self._kv_range(s)
                     dist.all_reduce(self.opt.main_grad[lo:lo + n], group=self.ps.kvr_group)
+        if self.ps.cp > 1:
+            # every context-parallel rank saw a share of the tokens: parameter gradients are partial sums
+            from ..parallel.dp import reduce_main_grads
+
+            reduce_main_grads(self.opt.main_grad, self.ps, group=self.ps.cp_group)
         if self.ps.dp > 1:
             from ..parallel.dp import reduce_main_grads, split_ranges_by_expert_sharding
 

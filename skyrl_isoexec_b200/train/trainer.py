@@ -177,7 +177,18 @@ class RayPPOTrainer:
         self.engine_ps = self.ps
         self.engines_per_replica = 1
         self.replica_group, self.replica_size, self.replica_rank = self.ps.tp_group, self.ps.tp, self.ps.tp_rank
+        self._every_rank_leads = False
+        if self.ps.cp > 1 and self.ps.pp == 1:
+            # context-parallel trainer: parameters are not cut by cp, so every cp rank runs an engine on the trainer's own
+            # weights; the cp engines of a replica split its requests and swap rollouts inside the cp group
+            if tp_e != self.ps.tp:
+                raise ValueError("a context-parallel trainer feeds engines of its own tensor-parallel degree")
+            self.engines_per_replica = self.ps.cp
+            self.replica_group, self.replica_size, self.replica_rank = self.ps.cp_group, self.ps.cp, self.ps.cp_rank
+            self._every_rank_leads = True
+            return tp_e
         if self.ps.pp > 1:
+            self._every_rank_leads = True
             # pipelined trainer: every rank also holds an un-pipelined engine of the trainer's TP degree; the pp engines of
             # a replica split its requests and swap rollouts inside the pipeline group; the sync gathers the stages
             if tp_e != self.ps.tp or self.ps.cp > 1:
@@ -202,6 +213,8 @@ class RayPPOTrainer:
         """Global index of the engine this rank belongs to (all ranks of one engine share a sampler stream)."""
         if self.ps.pp > 1:
             return self.ps.dp_rank * self.ps.pp + self.ps.pp_rank
+        if self.ps.cp > 1:
+            return self.ps.dp_rank * self.ps.cp + self.ps.cp_rank
         return self.engine_ps.dp_rank if self.separate_engine else self.ps.dp_rank
 
     def _setup_transports(self, mcfg) -> None:
@@ -371,7 +384,7 @@ class RayPPOTrainer:
         from .trainer_utils import _cat, _take
 
         k, n = self.engines_per_replica, len(gi["prompts"])
-        e = self.replica_rank if self.ps.pp > 1 else self.ps.tp_rank // self.engine_ps.tp
+        e = self.replica_rank if self._every_rank_leads else self.ps.tp_rank // self.engine_ps.tp
         lo, hi = e * n // k, (e + 1) * n // k
         part = dict(gi)
         for key in ("prompts", "env_classes", "env_extras", "trajectory_ids"):
@@ -380,7 +393,7 @@ class RayPPOTrainer:
         go = asyncio.run(self.generator.generate(part))
         go.pop("rollout_metrics", None)
         box = [None] * self.replica_size
-        lead = True if self.ps.pp > 1 else self.engine_ps.tp_rank == 0      # one copy per engine
+        lead = True if self._every_rank_leads else self.engine_ps.tp_rank == 0      # one copy per engine
         dist.all_gather_object(box, go if lead else None, group=self.replica_group)
         merged = None
         for g_ in box:
