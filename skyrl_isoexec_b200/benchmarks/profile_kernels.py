@@ -1,7 +1,8 @@
 """Small, self-terminating kernel workloads for ncu captures (one kernel family per mode).
 
     python skyrl_isoexec_b200/benchmarks/profile_kernels.py attn_decode | attn_prefill | gemm_large | gemm_decode | logprob | rmsnorm |
-                                   glu_decode | moe_grouped | rmsnorm_decode | sampler | rmsnorm_bwd | attn_bwd | train_small
+                                   glu_decode | moe_grouped | rmsnorm_decode | sampler | rmsnorm_bwd | attn_bwd | train_small |
+                                   gemm_bwd_dx | gemm_bwd_dw | moe_train | reshard
 
 Each mode allocates well under 1 GB, launches the kernel a handful of times and exits.
 """
@@ -157,6 +158,43 @@ def main(mode: str = "attn_decode") -> None:
         L = _native.lib()
         us = timed(lambda: _native.check(L.ix_accum_bf16_to_f32(acc.data_ptr(), g.data_ptr(), n, 1, _native.stream()), "accum"))
         print(f"gradient accumulation bf16 -> fp32, {n} elements: {us:.1f} us, {n * 10 / us / 1e6:.2f} TB/s")
+    elif mode in ("gemm_bwd_dx", "gemm_bwd_dw"):
+        # the two gradients of the gate|up projection of Qwen3-8B for an 8192-token micro-batch
+        M, N, K = 8192, 24576, 4096
+        dy = torch.randn(M, N, device=dev).bfloat16()
+        w = (torch.randn(N, K, device=dev) * 0.02).bfloat16()
+        x = torch.randn(M, K, device=dev).bfloat16()
+        for _ in range(4):
+            F.gemm_nn(dy, w) if mode == "gemm_bwd_dx" else F.gemm_tn(dy, x)
+    elif mode == "moe_train":
+        # one MoE layer of Qwen3-30B-A3B (128 experts, top-8, hidden 2048, expert FFN 768), 4096 tokens: forward and
+        # backward through the grouped kernels (dispatch plan, fc1, GLU x weight, fc2, combine and their VJPs)
+        from skyrl_isoexec_b200.ops import moe
+        T, E, k, H, Fd = 4096, 128, 8, 2048, 768
+        y = (torch.randn(T, H, device=dev) * 0.5).bfloat16().requires_grad_()
+        gu = (torch.randn(E, 2 * Fd, H, device=dev) * 0.02).bfloat16().requires_grad_()
+        dn = (torch.randn(E, H, Fd, device=dev) * 0.02).bfloat16().requires_grad_()
+        idx, w0, _ = moe.router_topk_fwd(torch.randn(T, E, device=dev), k, None, False, True)
+        g = (torch.randn(T, H, device=dev) * 0.1).bfloat16()
+        for _ in range(3):
+            w = w0.clone().requires_grad_()
+            moe._ExpertsFn.apply(y, w, gu, dn, idx, None).backward(g)
+            y.grad = gu.grad = dn.grad = None
+    elif mode == "reshard":
+        # the pull kernel of the resharding weight sync on local memory: column-split and row-split pieces of a 1 GB buffer
+        import ctypes as C
+        import struct
+        lib = _native.lib()
+        lib.ix_reshard_pull.argtypes = [C.c_void_p, C.c_int, C.c_void_p]
+        src = torch.randn(512 << 20, device=dev).bfloat16()
+        dst = torch.empty(256 << 20, device=dev, dtype=torch.bfloat16)
+        recs, off = [], 0
+        for i in range(64):          # 64 matrices [4096, 2048] taken as the left half of [4096, 4096] sources
+            recs.append(struct.pack("<QQqqqqii", src.data_ptr() + i * 4096 * 4096 * 2, dst.data_ptr() + off, 4096, 2048 * 2, 4096 * 2, 2048 * 2, 0, 0))
+            off += 4096 * 2048 * 2
+        d = torch.frombuffer(bytearray(b"".join(recs)), dtype=torch.uint8).to(dev)
+        for _ in range(4):
+            _native.check(lib.ix_reshard_pull(d.data_ptr(), len(recs), _native.stream()), "ix_reshard_pull")
     elif mode == "sampler":
         from skyrl_isoexec_b200.engine.sampler import Sampler, SamplingParams
         lg = torch.randn(64, 151936, device=dev).bfloat16()

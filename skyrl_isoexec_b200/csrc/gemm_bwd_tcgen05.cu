@@ -447,8 +447,21 @@ grouped_bwd_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
             }
           } else {
             float* dst = reinterpret_cast<float*>(Cout) + cbase + static_cast<size_t>(row) * ldc + col0;
-            for (int j = 0; j < 32; ++j)
-              if (col0 + j < N) dst[j] = (OUT == OUT_F32_ACC) ? __fadd_rn(dst[j], __uint_as_float(r[j])) : __uint_as_float(r[j]);
+            if (whole && (ldc & 3) == 0) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                float4 v = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]), __uint_as_float(r[4 * j + 2]),
+                                       __uint_as_float(r[4 * j + 3]));
+                if constexpr (OUT == OUT_F32_ACC) {
+                  const float4 o = reinterpret_cast<const float4*>(dst)[j];
+                  v.x = __fadd_rn(o.x, v.x), v.y = __fadd_rn(o.y, v.y), v.z = __fadd_rn(o.z, v.z), v.w = __fadd_rn(o.w, v.w);
+                }
+                reinterpret_cast<float4*>(dst)[j] = v;
+              }
+            } else {
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < N) dst[j] = (OUT == OUT_F32_ACC) ? __fadd_rn(dst[j], __uint_as_float(r[j])) : __uint_as_float(r[j]);
+            }
           }
         }
       }
