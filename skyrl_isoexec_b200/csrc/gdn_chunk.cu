@@ -145,7 +145,7 @@ gdn_chunk_prep_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* 
     }
     umma_commit(smem_u32(bar));
   }
-  const bool ok_a = mma_done(smem_u32(bar), ph, abort_flag, status);
+  const bool ok_a = __syncthreads_and(mma_done(smem_u32(bar), ph, abort_flag, status)) != 0;
   ph ^= 1;
   tc_fence_after();
   {
@@ -239,7 +239,7 @@ gdn_chunk_prep_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* 
     for (int ks = 0; ks < 4; ++ks) umma_f16_ss(tmem, da + 2 * ks, db + 128 * ks, idesc, ks != 0 ? 1u : 0u);
     umma_commit(smem_u32(bar));
   }
-  const bool ok_b = mma_done(smem_u32(bar), ph, abort_flag, status);
+  const bool ok_b = __syncthreads_and(mma_done(smem_u32(bar), ph, abort_flag, status)) != 0;
   tc_fence_after();
   if (tid < 64 && ok_b) {
     const int t = tid;
@@ -399,7 +399,7 @@ gdn_chunk_state_kernel(const __nv_bfloat16* __restrict__ q, const GdnChunk* __re
       }
       umma_commit(smem_u32(bar));
     }
-    ok = mma_done(smem_u32(bar), ph, abort_flag, status);
+    ok = __syncthreads_and(mma_done(smem_u32(bar), ph, abort_flag, status)) != 0;   // one answer for the whole CTA
     ph ^= 1;
     tc_fence_after();
     // (4) rows 0..63: D_t = U_t - X_t, rounded to bf16, into the M/N-major tile
@@ -443,22 +443,24 @@ gdn_chunk_state_kernel(const __nv_bfloat16* __restrict__ q, const GdnChunk* __re
       for (int ks = 0; ks < 4; ++ks) umma_f16_ss(tmem, dd + 128 * ks, dk + 128 * ks, idesc_s, 1u);
       umma_commit(smem_u32(bar));
     }
-    ok = mma_done(smem_u32(bar), ph, abort_flag, status);
+    ok = __syncthreads_and(mma_done(smem_u32(bar), ph, abort_flag, status)) != 0;   // one answer for the whole CTA
     ph ^= 1;
     tc_fence_after();
-    // (6) rows 64..127: o_t = e^{G_t} (Q S^T)_t + (P D)_t
+    // (6) rows 64..127: o_t = e^{G_t} (Q S^T)_t + (P D)_t. The TMEM loads are warp-wide instructions: every lane of the
+    // two warps executes them, only the stores are predicated on the row holding a token.
     if (tid >= 64 && ok) {
       const int t = tid - 64;
-      if (t < ck.n_tok) {
-        const float eg = eG[ch * 64 + t];
-        __nv_bfloat16* dst = out + (static_cast<long long>(ck.tok_start + t) * Hv + hv) * D;
+      const bool live = t < ck.n_tok;
+      const float eg = eG[ch * 64 + t];
+      __nv_bfloat16* dst = out + (static_cast<long long>(ck.tok_start + (live ? t : 0)) * Hv + hv) * D;
 #pragma unroll 1
-        for (int c0 = 0; c0 < D; c0 += 32) {
-          uint32_t x[32], o[32];
-          tmem_ld_32x32(accX + c0, x);
-          tmem_ld_32x32(accO + c0, o);
-          tmem_ld_wait_dep(x);
-          tmem_ld_wait_dep(o);
+      for (int c0 = 0; c0 < D; c0 += 32) {
+        uint32_t x[32], o[32];
+        tmem_ld_32x32(accX + c0, x);
+        tmem_ld_32x32(accO + c0, o);
+        tmem_ld_wait_dep(x);
+        tmem_ld_wait_dep(o);
+        if (live) {
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             uint4 w;
@@ -469,16 +471,6 @@ gdn_chunk_state_kernel(const __nv_bfloat16* __restrict__ q, const GdnChunk* __re
                                __fmaf_rn(eg, __uint_as_float(x[8 * j + 2 * e + 1]), __uint_as_float(o[8 * j + 2 * e + 1])));
             reinterpret_cast<uint4*>(dst + c0)[j] = w;
           }
-        }
-      } else {
-        // keep the warp's TMEM loads converged: the loads are warp-wide instructions
-#pragma unroll 1
-        for (int c0 = 0; c0 < D; c0 += 32) {
-          uint32_t x[32], o[32];
-          tmem_ld_32x32(accX + c0, x);
-          tmem_ld_32x32(accO + c0, o);
-          tmem_ld_wait_dep(x);
-          tmem_ld_wait_dep(o);
         }
       }
     }

@@ -134,6 +134,53 @@ def gdn_core_fwd(proj, conv_w, A_log, dt_bias, meta: GDNMeta, cfg, tp, conv_stat
     return o
 
 
+# ------------------------------------------------------------------------------------ chunked scan on the tensor cores
+CHUNK = 64
+_CHUNK_DT = np.dtype([("tok_start", "<i4"), ("n_tok", "<i4")])
+_CHAIN_DT = np.dtype([("chunk_begin", "<i4"), ("chunk_end", "<i4"), ("row_in", "<i8"), ("row_out", "<i8")])
+
+
+def chunk_tables(segments, device):
+    """Device tables for ``gdn_chunk_scan``. ``segments``: [(tok_start, n_tok, row_in, row_out)], one per sequence, each
+    starting ON a chunk boundary of its sequence (position multiple of 64). Returns (chunks, chains, n_chunks, n_chains)."""
+    ch, cn = [], []
+    for ts, n, rin, rout in segments:
+        b = len(ch)
+        for lo in range(0, n, CHUNK):
+            ch.append((ts + lo, min(CHUNK, n - lo)))
+        cn.append((b, len(ch), rin, rout))
+    a = np.array(ch, dtype=_CHUNK_DT)
+    c = np.array(cn, dtype=_CHAIN_DT)
+    return (torch.from_numpy(a.view(np.uint8).copy()).to(device), torch.from_numpy(c.view(np.uint8).copy()).to(device), len(ch), len(cn))
+
+
+def gdn_chunk_scan(qn, kn, v, g, beta, segments, state=None):
+    """Gated delta rule over packed sequences by the chunked tcgen05 kernels (csrc/gdn_chunk.cu).
+    qn, kn: [T, Hk, D] bf16 (normalised), v: [T, Hv, D] bf16, g, beta: [T, Hv] fp32; ``segments`` as in ``chunk_tables``;
+    ``state``: fp32 pool [rows, Hv, D, D] read at ``row_in`` and written at ``row_out`` (after the last complete chunk)."""
+    import ctypes as C
+
+    T, Hk, D = qn.shape
+    Hv = v.shape[1]
+    assert qn.dtype == torch.bfloat16 and qn.is_contiguous() and kn.is_contiguous() and v.is_contiguous()
+    assert g.dtype == torch.float32 and g.is_contiguous() and beta.is_contiguous()
+    out = torch.empty(T, Hv, D, dtype=torch.bfloat16, device=qn.device)
+    if T == 0:
+        return out
+    chunks, chains, n_chunks, n_chains = chunk_tables(segments, qn.device)
+    lib = _native.lib()
+    if not getattr(lib, "_gdn_chunk_sig", False):
+        lib.ix_gdn_chunk_scratch_bytes.argtypes = [C.c_int, C.c_int, C.c_int]
+        lib.ix_gdn_chunk_scratch_bytes.restype = C.c_longlong
+        lib.ix_gdn_chunk_fwd.argtypes = [C.c_void_p] * 6 + [C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int] + [C.c_void_p] * 4
+        lib._gdn_chunk_sig = True
+    scratch = torch.empty(int(lib.ix_gdn_chunk_scratch_bytes(n_chunks, Hv, D)), dtype=torch.uint8, device=qn.device)
+    _native.check(lib.ix_gdn_chunk_fwd(qn.data_ptr(), kn.data_ptr(), v.data_ptr(), g.data_ptr(), beta.data_ptr(), chunks.data_ptr(),
+                                       n_chunks, chains.data_ptr(), n_chains, Hk, Hv, D, scratch.data_ptr(), _native.ptr(state),
+                                       out.data_ptr(), _native.stream()), "ix_gdn_chunk_fwd")
+    return out
+
+
 # ------------------------------------------------------------------------------------ torch formulation (backward only)
 def chunk_gated_delta_rule_torch(q, k, v, g, beta, chunk: int = 64):
     """q, k: [H, T, Dk] (already normalised / scaled), v: [H, T, Dv], g, beta: [H, T] fp32.

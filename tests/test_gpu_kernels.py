@@ -740,3 +740,59 @@ def test_every_fused_region_equals_its_unfused_chain_on_hazard_inputs():
     multi = {"tp_gemm_fused (AR1/AR2/RS)", "tp_gemm_fused (AG)"}
     assert all(res[n] is True for n in res if n not in multi), res
     assert all(res[n] is not False for n in multi)
+
+
+def _gdn_recurrence_fp32(q, k, v, g, beta):
+    """Token-by-token gated delta rule in fp32: q, k [T, Hk, D], v [T, Hv, D], g, beta [T, Hv] -> o [T, Hv, D]."""
+    T, Hk, D = q.shape
+    Hv = v.shape[1]
+    rep = Hv // Hk
+    qf, kf = q.float().repeat_interleave(rep, 1), k.float().repeat_interleave(rep, 1)
+    S = torch.zeros(Hv, D, D, device=q.device)                   # [Hv, Dv, Dk]
+    out = torch.empty(T, Hv, D, device=q.device)
+    for t in range(T):
+        S = S * g[t].exp()[:, None, None]
+        kv = torch.einsum("hvk,hk->hv", S, kf[t])
+        d = (v[t].float() - kv) * beta[t][:, None]
+        S = S + d[:, :, None] * kf[t][:, None, :]
+        out[t] = torch.einsum("hvk,hk->hv", S, qf[t])
+    return out
+
+
+@pytest.mark.parametrize("D", [64, 128])
+def test_gdn_chunked_tensor_core_scan_matches_the_fp32_recurrence_and_decode_is_bitwise(D):
+    """The chunked tcgen05 form of the gated delta rule: close to the fp32 token recurrence, and bit-identical whether a
+    sequence is scanned whole, or as a prefill piece, single decode tokens and further pieces that each re-run the open
+    chunk from the state at the last chunk boundary."""
+    from skyrl_isoexec_b200.ops import gdn
+
+    torch.manual_seed(21)
+    T, Hk, Hv = 300, 2, 4
+    q = torch.nn.functional.normalize(torch.randn(T, Hk, D, device=DEV), dim=-1) * D ** -0.5
+    k = torch.nn.functional.normalize(torch.randn(T, Hk, D, device=DEV), dim=-1)
+    v = torch.randn(T, Hv, D, device=DEV) * 0.5
+    g = -torch.rand(T, Hv, device=DEV) * 0.2
+    beta = torch.rand(T, Hv, device=DEV)
+    qb, kb, vb = q.bfloat16().contiguous(), k.bfloat16().contiguous(), v.bfloat16().contiguous()
+    whole = gdn.gdn_chunk_scan(qb, kb, vb, g, beta, [(0, T, -1, -1)])
+    ref = _gdn_recurrence_fp32(qb, kb, vb, g, beta)
+    err = (whole.float() - ref).abs().max().item()
+    assert err < 3e-2 * max(1.0, ref.abs().max().item()), err
+    # two sequences packed back to back give the rows of each scanned alone
+    both = gdn.gdn_chunk_scan(qb, kb, vb, g, beta, [(0, 130, -1, -1), (130, T - 130, -1, -1)])
+    assert bitwise_equal(both[:130], whole[:130])
+    alone = gdn.gdn_chunk_scan(qb[130:].contiguous(), kb[130:].contiguous(), vb[130:].contiguous(), g[130:].contiguous(),
+                               beta[130:].contiguous(), [(0, T - 130, -1, -1)])
+    assert bitwise_equal(both[130:], alone)
+    # engine-style walk: every call re-runs the open chunk from the state at the last boundary (row 1 of a pool)
+    state = torch.zeros(2, Hv, D, D, device=DEV)
+    outs, pos, have_state = [], 0, False
+    for n in (70, 1, 1, 57, 1, 100, 1, T - 231):
+        c0 = pos // 64 * 64                                   # the open chunk starts here
+        sl = slice(c0, pos + n)
+        o = gdn.gdn_chunk_scan(qb[sl].contiguous(), kb[sl].contiguous(), vb[sl].contiguous(), g[sl].contiguous(), beta[sl].contiguous(),
+                               [(0, pos + n - c0, 1 if have_state else -1, 1)], state)
+        outs.append(o[pos - c0:])
+        pos += n
+        have_state = pos >= 64
+    assert pos == T and bitwise_equal(torch.cat(outs, 0), whole)
