@@ -187,10 +187,11 @@ def _chk_gdn(device: str):
     whole = gdn.gdn_core_fwd(proj, conv_w, A_log, dtb, gdn.GDNMeta.packed([T], device), cfg, 1)
     conv_state = torch.zeros(3, C, cfg.gdn_conv_kernel - 1, dtype=dt, device=device)
     ssm = torch.zeros(3, hv, d, d, dtype=torch.float32, device=device)
+    open_chunk = gdn.new_chunk_buffers(3, hk, hv, d, dt, device) if gdn.chunked_ok(proj, d) else None
     outs, pos = [], 0
     for n in (70, 1, 1, 64, 1, 3):
         meta = gdn.GDNMeta.build([(0, n, pos, 2 if pos > 0 else -1, 2)], device)
-        outs.append(gdn.gdn_core_fwd(proj[pos:pos + n].contiguous(), conv_w, A_log, dtb, meta, cfg, 1, conv_state, ssm))
+        outs.append(gdn.gdn_core_fwd(proj[pos:pos + n].contiguous(), conv_w, A_log, dtb, meta, cfg, 1, conv_state, ssm, open_chunk))
         pos += n
     return _same(torch.cat(outs, 0), whole)
 

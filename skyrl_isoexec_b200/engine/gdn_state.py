@@ -22,9 +22,15 @@ class GDNStatePool:
         C, W = (2 * hk + hv) * d, cfg.gdn_conv_kernel
         self.layer_ids = list(layer_ids if layer_ids is not None else range(cfg.num_layers))
         dt = cfg.torch_dtype
+        from ..ops.gdn import chunked_ok, new_chunk_buffers
+
+        # per layer: conv tail, fp32 recurrent state at the sequence's last chunk boundary and, where the scan is the
+        # chunked tensor-core form, the tokens of the sequence's open chunk (re-run in front of every new token)
+        probe = torch.empty(0, dtype=dt, device=self.device)
         self.states = {
             i: (torch.zeros(self.rows, C, W - 1, dtype=dt, device=self.device),
                 torch.zeros(self.rows, hv, d, d, dtype=torch.float32, device=self.device))
+            + ((new_chunk_buffers(self.rows, hk, hv, d, dt, self.device),) if chunked_ok(probe, d) else ())
             for i in self.layer_ids if cfg.layer_type(i) == "gdn"
         }
         self.free = list(range(self.rows - 1, 0, -1))

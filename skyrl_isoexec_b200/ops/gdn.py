@@ -42,6 +42,8 @@ class GDNMeta:
     lens: list[int]
     n_chunks: int
     uses_state: bool = False
+    host_chunks: list | None = None       # the (tok_start, n_tok, pos0, row_in, row_out) tuples the tables were built from
+    plan: dict | None = None              # index tensors of the chunked scan, built by the first GDN layer of a step
 
     @staticmethod
     def build(chunk_list, device) -> "GDNMeta":
@@ -57,7 +59,7 @@ class GDNMeta:
         uses = any(c[3] >= 0 or c[4] >= 0 for c in chunk_list)
         ch = torch.from_numpy(arr.view(np.uint8).copy())
         return GDNMeta(ch.to(device), torch.from_numpy(back).to(device), torch.from_numpy(srow).to(device) if uses else None,
-                       [c[1] for c in chunk_list], len(chunk_list), uses)
+                       [c[1] for c in chunk_list], len(chunk_list), uses, host_chunks=[tuple(int(x) for x in c) for c in chunk_list])
 
     @staticmethod
     def packed(seq_lens, device) -> "GDNMeta":
@@ -78,9 +80,75 @@ def _is_f32(t):
     return int(t.dtype == torch.float32)
 
 
-def gdn_core_fwd(proj, conv_w, A_log, dt_bias, meta: GDNMeta, cfg, tp, conv_state=None, ssm_state=None):
+def _chunk_plan(meta: GDNMeta, rows: int, device) -> dict:
+    """Index tensors that lay the open chunk of every sequence (kept tokens since its last chunk boundary) in front of
+    the sequence's new tokens, and that write the new open chunk back. Same for every GDN layer of a step."""
+    if meta.plan is not None:
+        return meta.plan
+    T = sum(c[1] for c in meta.host_chunks)
+    gather, segs, new_rows, keep_src, keep_dst = [], [], [], [], []
+    base = 0
+    for tok, n, pos0, rin, rout in meta.host_chunks:
+        fill = pos0 % CHUNK
+        row = rout if rout >= 0 else rin
+        if fill and row < 0:
+            raise ValueError("a sequence continues inside a chunk but has no state row holding its open chunk")
+        gather += [row * CHUNK + j for j in range(fill)] + [rows * CHUNK + tok + j for j in range(n)]
+        c0 = pos0 - fill
+        segs.append((base, fill + n, rin if c0 > 0 else -1, rout))
+        new_rows += [base + fill + j for j in range(n)]
+        nfill = (pos0 + n) % CHUNK
+        if rout >= 0 and nfill:
+            keep_src += [base + fill + n - nfill + j for j in range(nfill)]
+            keep_dst += [rout * CHUNK + j for j in range(nfill)]
+        base += fill + n
+    mk = lambda x: torch.tensor(x, dtype=torch.int64, device=device)
+    meta.plan = {"gather": mk(gather), "segments": segs, "new_rows": mk(new_rows), "keep_src": mk(keep_src), "keep_dst": mk(keep_dst),
+                 "identity": not meta.uses_state, "T": T}
+    return meta.plan
+
+
+def _chunked_core(qn, kn, vv, g, beta, meta: GDNMeta, ssm_state, chunk_buf):
+    """The scan by the chunked tensor-core kernels. Trainer: packed whole sequences. Engine: every sequence's open chunk is
+    kept in ``chunk_buf`` (post-conv q, k, v and the gates of up to 63 tokens) and is re-run in front of the new tokens,
+    from the fp32 state at its chunk boundary, so a decode step computes the very row a whole-sequence scan computes."""
+    if not meta.uses_state:
+        segs, s0 = [], 0
+        for n in meta.lens:
+            segs.append((s0, n, -1, -1))
+            s0 += n
+        return gdn_chunk_scan(qn, kn, vv, g, beta, segs, None)
+    rows = ssm_state.shape[0]
+    plan = _chunk_plan(meta, rows, qn.device)
+    names = ("q", "k", "v", "g", "b")
+    new = dict(zip(names, (qn, kn, vv, g, beta)))
+    full = {}
+    for nm in names:
+        buf = chunk_buf[nm]
+        both = torch.cat([buf.reshape((rows * CHUNK,) + tuple(buf.shape[2:])), new[nm]], 0)
+        full[nm] = both.index_select(0, plan["gather"]).contiguous()
+    out = gdn_chunk_scan(full["q"], full["k"], full["v"], full["g"], full["b"], plan["segments"], ssm_state)
+    if plan["keep_src"].numel():
+        for nm in names:
+            buf = chunk_buf[nm]
+            buf.reshape((rows * CHUNK,) + tuple(buf.shape[2:])).index_copy_(0, plan["keep_dst"], full[nm].index_select(0, plan["keep_src"]))
+    return out.index_select(0, plan["new_rows"])
+
+
+def new_chunk_buffers(rows: int, hk: int, hv: int, d: int, dtype, device) -> dict:
+    """Per state row: the tokens of the sequence's open chunk (q, k [64, Hk, D], v [64, Hv, D], log-decay and beta [64, Hv])."""
+    z = lambda *shape, dt=dtype: torch.zeros(rows, CHUNK, *shape, dtype=dt, device=device)
+    return {"q": z(hk, d), "k": z(hk, d), "v": z(hv, d), "g": z(hv, dt=torch.float32), "b": z(hv, dt=torch.float32)}
+
+
+def chunked_ok(proj, d: int) -> bool:
+    return proj.is_cuda and proj.dtype == torch.bfloat16 and d in (64, 128)
+
+
+def gdn_core_fwd(proj, conv_w, A_log, dt_bias, meta: GDNMeta, cfg, tp, conv_state=None, ssm_state=None, chunk_buf=None):
     """proj: [T, 2kd+2vd+2Hv] (in_proj output). Returns o [T, Hv, Dv]. Updates the state pools in place
-    when ``meta`` names state rows."""
+    when ``meta`` names state rows. On a GPU in bf16 the scan is the chunked tensor-core form (``_chunked_core``); with
+    state rows it needs ``chunk_buf`` (``new_chunk_buffers``). CPU / fp32: the sequential scan."""
     hk, hv, d, kd, vd = _dims(cfg, tp)
     T = proj.shape[0]
     C, W = 2 * kd + vd, cfg.gdn_conv_kernel
@@ -116,8 +184,11 @@ def gdn_core_fwd(proj, conv_w, A_log, dt_bias, meta: GDNMeta, cfg, tp, conv_stat
                          beta.data_ptr(), T, hv, f32, s), "ix_gdn_gate")
         ck(L.ix_gdn_l2norm(qkv.data_ptr(), C, qn.data_ptr(), kn.data_ptr(), T, hk, d, 1e-6, d ** -0.5, f32, s), "ix_gdn_l2norm")
         vv = qkv[:, 2 * kd:].contiguous()          # the scan indexes v as packed [T, Hv, Dv]
-        ck(L.ix_gdn_scan(qn.data_ptr(), kn.data_ptr(), vv.data_ptr(), g.data_ptr(), beta.data_ptr(), meta.chunks.data_ptr(),
-                         ssm_state.data_ptr(), o.data_ptr(), meta.n_chunks, hk, hv, d, d, snap, f32, s), "ix_gdn_scan")
+        if chunked_ok(proj, d) and (not meta.uses_state or chunk_buf is not None):
+            o = _chunked_core(qn, kn, vv.view(T, hv, d), g, beta, meta, ssm_state if meta.uses_state else None, chunk_buf)
+        else:
+            ck(L.ix_gdn_scan(qn.data_ptr(), kn.data_ptr(), vv.data_ptr(), g.data_ptr(), beta.data_ptr(), meta.chunks.data_ptr(),
+                             ssm_state.data_ptr(), o.data_ptr(), meta.n_chunks, hk, hv, d, d, snap, f32, s), "ix_gdn_scan")
     else:
         L, dt = _cpu.lib(), _cpu.dt(proj)
         L.ixc_gdn_conv(proj.data_ptr(), proj.stride(0), conv_w.data_ptr(), meta.tok_back.data_ptr(), _cpu.ptr(meta.state_row), args_cs,
@@ -278,8 +349,9 @@ def gdn_block(y, model, i: int, fc, kv_idx: int):
         else:
             o = gdn_core_fwd(proj, conv_w, A_log, dt_bias, meta, cfg, ps.tp)
     else:
-        conv_state, ssm_state = fc.kv[kv_idx]
-        o = gdn_core_fwd(proj, conv_w, A_log, dt_bias, meta, cfg, ps.tp, conv_state, ssm_state)
+        st = fc.kv[kv_idx]
+        conv_state, ssm_state = st[0], st[1]
+        o = gdn_core_fwd(proj, conv_w, A_log, dt_bias, meta, cfg, ps.tp, conv_state, ssm_state, st[2] if len(st) > 2 else None)
     z = proj[:, C:C + vd].reshape(-1, hv, d)
     if torch.is_grad_enabled() and (o.requires_grad or proj.requires_grad):
         w = model.p(pfx + "out_norm.weight").float()

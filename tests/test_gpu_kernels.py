@@ -614,11 +614,12 @@ def test_gdn_scan_bitwise_vs_cpu_oracle_chunked_equals_recurrent():
     assert (whole.cpu().float() - cpu.float()).abs().max() < 2e-2 * max(1.0, cpu.float().abs().max().item())
     conv_state = torch.zeros(3, C, 3, dtype=torch.bfloat16, device=DEV)
     ssm = torch.zeros(3, hv, d, d, dtype=torch.float32, device=DEV)
+    open_chunk = gdn.new_chunk_buffers(3, hk, hv, d, torch.bfloat16, DEV)      # tokens since the last chunk boundary, per state row
     outs, pos = [], 0
     for n in (70, 1, 1, 64, 1, 63):                       # prefill chunk, decode steps, more chunks
         meta = gdn.GDNMeta.build([(0, n, pos, 2 if pos > 0 else -1, 2)], DEV)
         outs.append(gdn.gdn_core_fwd(proj[pos:pos + n].to(DEV).contiguous(), conv_w.to(DEV), A_log.to(DEV), dtb.to(DEV), meta, cfg, 1,
-                                     conv_state, ssm))
+                                     conv_state, ssm, open_chunk))
         pos += n
     assert bitwise_equal(torch.cat(outs, 0), whole)
 
