@@ -159,6 +159,9 @@ def main():
         mo["num_layers"] = args.layers
     if args.tp > 1 or args.engine_tp > 1:
         mo["tp_invariant"] = True
+        # leaves of the TP-invariant reduction tree: the largest tensor-parallel degree of the deployment (a contract pin
+        # shared by trainer and engines); fewer leaves mean wider GEMM tiles on every rank
+        mo["pik_leaves"] = max(2, args.tp, args.engine_tp)
     ov.append(f"generator.inference_engine.tensor_parallel_size={args.engine_tp}")
     if mo:
         ov.append("trainer.policy.model_overrides=" + json.dumps(mo))
@@ -229,6 +232,7 @@ def main():
                        "parallelism": (f"dp{ps.dp}" + (f"xtp{args.tp}" if args.tp > 1 else "")) if world > 1 else "single",
                        "engine": (f"colocated, {world // args.engine_tp} engines x TP{args.engine_tp}, own layout, resharding weight sync every step"
                                   if trainer.separate_engine else f"colocated, {world // args.tp} engines x TP{args.tp} on the trainer's weights"),
+                       "pik_leaves": mo.get("pik_leaves", 0),
                        "scoring_forward": "skipped: rollout logprobs reused (VARIANT, not the reference's step)" if args.reuse_rollout_logprobs else "run",
                        "l2": "working set (16 GB of weights per pass) exceeds L2; no explicit flush"},
             "clocks": sampler.summary(),

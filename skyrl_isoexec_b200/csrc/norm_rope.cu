@@ -377,30 +377,51 @@ sigmoid_gate_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __
 
 // ------------------------------------------------------------------ gated out-norm (GDN): per (token, head) over Dv
 // out = bf16( bf16(bf16(o*rstd) * g) * bf16(silu(z)) ),  g = w or bf16(1+w)
-template <bool ZERO_CENTERED>
+// HALF: rows of at most 128 elements need 16 lanes, so a warp takes two rows. The 16-lane butterfly has the bits of the
+// 32-lane one over a row padded with zero lanes (the skipped first step only ever added +0), so both forms agree with
+// each other and with the CPU oracle.
+template <bool ZERO_CENTERED, bool HALF>
 __global__ void __launch_bounds__(128)
 gated_outnorm_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ z,
                      const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ out, long long rows, int D,
                      float eps) {
-  const long long row = static_cast<long long>(blockIdx.x) * 4 + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31;
-  if (row >= rows) return;
+  constexpr int L = HALF ? 16 : 32;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long row = HALF ? (static_cast<long long>(blockIdx.x) * 8 + warp * 2 + (lane >> 4))
+                             : (static_cast<long long>(blockIdx.x) * 4 + warp);
+  const int sub = lane & (L - 1);
+  const bool live = row < rows;
   const int nvec = D >> 3;
-  const BF8* orow = reinterpret_cast<const BF8*>(o + row * D);
-  const BF8* zrow = reinterpret_cast<const BF8*>(z + row * D);
+  const BF8* orow = reinterpret_cast<const BF8*>(o + (live ? row : 0) * D);
+  const BF8* zrow = reinterpret_cast<const BF8*>(z + (live ? row : 0) * D);
   float ss = 0.f;
-  for (int v = lane; v < nvec; v += 32) {
-    const BF8 a = orow[v];
+  BF8 a0;                                   // the common case (D <= 8 * L) keeps the row's vector in registers
+  const bool one = nvec <= L;
+  if (one) {
+    if (sub < nvec && live) {
+      a0 = orow[sub];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const float f = bf2f(a.v[j]);
-      ss = __fadd_rn(ss, __fmul_rn(f, f));
+      for (int j = 0; j < 8; ++j) {
+        const float f = bf2f(a0.v[j]);
+        ss = __fadd_rn(ss, __fmul_rn(f, f));
+      }
+    }
+  } else {
+    for (int v = sub; v < nvec && live; v += L) {
+      const BF8 a = orow[v];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float f = bf2f(a.v[j]);
+        ss = __fadd_rn(ss, __fmul_rn(f, f));
+      }
     }
   }
-  ss = warp_sum_butterfly(ss);
+#pragma unroll
+  for (int off = L / 2; off >= 1; off >>= 1) ss = __fadd_rn(ss, __shfl_xor_sync(0xffffffffu, ss, off));
+  if (!live) return;
   const float rstd = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, static_cast<float>(D)), eps)));
-  for (int v = lane; v < nvec; v += 32) {
-    const BF8 a = orow[v];
+  for (int v = sub; v < nvec; v += L) {
+    const BF8 a = one ? a0 : orow[v];
     const BF8 zz = zrow[v];
     const BF8 g = reinterpret_cast<const BF8*>(w)[v];
     BF8 r;
@@ -539,18 +560,20 @@ IX_API int ix_gated_outnorm(const void* o, const void* z, const void* w, void* o
                             float eps, int zero_centered, void* stream) {
   if (rows <= 0) return 0;
   if (D & 7) return ixh::fail(ixh::IX_EARG, "gated_outnorm: D must be a multiple of 8");
-  const int grid = static_cast<int>((rows + 3) / 4);
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  if (zero_centered)
-    gated_outnorm_kernel<true><<<grid, 128, 0, s>>>(static_cast<const __nv_bfloat16*>(o),
-                                                    static_cast<const __nv_bfloat16*>(z),
-                                                    static_cast<const __nv_bfloat16*>(w),
-                                                    static_cast<__nv_bfloat16*>(out), rows, D, eps);
-  else
-    gated_outnorm_kernel<false><<<grid, 128, 0, s>>>(static_cast<const __nv_bfloat16*>(o),
-                                                     static_cast<const __nv_bfloat16*>(z),
-                                                     static_cast<const __nv_bfloat16*>(w),
-                                                     static_cast<__nv_bfloat16*>(out), rows, D, eps);
+  auto O = static_cast<const __nv_bfloat16*>(o);
+  auto Z = static_cast<const __nv_bfloat16*>(z);
+  auto W = static_cast<const __nv_bfloat16*>(w);
+  auto Y = static_cast<__nv_bfloat16*>(out);
+  if (D <= 128) {
+    const int grid = static_cast<int>((rows + 7) / 8);
+    if (zero_centered) gated_outnorm_kernel<true, true><<<grid, 128, 0, s>>>(O, Z, W, Y, rows, D, eps);
+    else gated_outnorm_kernel<false, true><<<grid, 128, 0, s>>>(O, Z, W, Y, rows, D, eps);
+  } else {
+    const int grid = static_cast<int>((rows + 3) / 4);
+    if (zero_centered) gated_outnorm_kernel<true, false><<<grid, 128, 0, s>>>(O, Z, W, Y, rows, D, eps);
+    else gated_outnorm_kernel<false, false><<<grid, 128, 0, s>>>(O, Z, W, Y, rows, D, eps);
+  }
   IX_CUDA(cudaGetLastError());
   return 0;
 }

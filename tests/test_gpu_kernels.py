@@ -797,3 +797,25 @@ def test_gdn_chunked_tensor_core_scan_matches_the_fp32_recurrence_and_decode_is_
         pos += n
         have_state = pos >= 64
     assert pos == T and bitwise_equal(torch.cat(outs, 0), whole)
+
+
+@pytest.mark.parametrize("D,zc", [(64, True), (128, True), (128, False), (256, True)])
+def test_gated_outnorm_matches_the_cpu_oracle_and_the_formula(D, zc):
+    """rms_norm(o) * gamma * silu(z) per (token, head) row. Rows of up to 128 elements are handled two per warp; the result
+    must equal the C++ restatement (same roundings; only exp() may differ in its last bit) and the fp32 formula."""
+    torch.manual_seed(5)
+    rows = 777
+    o = torch.randn(rows, D).bfloat16()
+    z = torch.randn(rows, D).bfloat16()
+    w = (torch.randn(D) * 0.1).bfloat16()
+    cpu = F.gated_outnorm(o, z, w, 1e-6, zc)
+    gpu = F.gated_outnorm(o.to(DEV), z.to(DEV), w.to(DEV), 1e-6, zc).cpu()
+    diff = (gpu.float() - cpu.float()).abs()
+    assert float((diff > 0).float().mean()) < 0.02                      # exp() rounding only
+    assert float((diff / cpu.float().abs().clamp(min=1e-3)).max()) < 2e-2
+    of, zf = o.float(), z.float()
+    ref = of * torch.rsqrt(of.pow(2).mean(-1, keepdim=True) + 1e-6) * ((1 + w.float()) if zc else w.float()) * torch.nn.functional.silu(zf)
+    assert float((gpu.float() - ref).abs().max()) < 3e-2 * max(1.0, float(ref.abs().max()))
+    # a row's bits do not depend on how many rows the launch has (odd counts leave half a warp idle)
+    one = F.gated_outnorm(o[:1].to(DEV), z[:1].to(DEV), w.to(DEV), 1e-6, zc).cpu()
+    assert bitwise_equal(one, gpu[:1])
