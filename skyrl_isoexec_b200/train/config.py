@@ -21,6 +21,8 @@ from .policy_worker import OptimizerConfig
 @dataclass
 class PlacementConfig:
     colocate_all: bool = True
+    offload_optimizer: bool = False     # colocated jobs: at most one model's optimizer state on the GPU at a time, and none of
+                                        # them during rollout (parked in pinned host memory; costs a PCIe round trip per switch)
     policy_num_gpus_per_node: int = 1
     policy_num_nodes: int = 1
 

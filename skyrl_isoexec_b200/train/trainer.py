@@ -289,6 +289,12 @@ class RayPPOTrainer:
             from .ref_critic import CriticWorker
 
             self.critic = CriticWorker(DecoderLM(mcfg, self.ps, self.device, seed=t.policy.seed + 1), wcfg, algo)
+        # the controller drives its workers through one dispatch object (verbs + residency of optimizer state)
+        from .worker_dispatch import WorkerDispatch
+
+        self.dispatch = WorkerDispatch({"policy": self.policy, "critic": self.critic, "ref": self.ref},
+                                       colocate_all=bool(t.placement.colocate_all and t.placement.offload_optimizer),
+                                       sync_fn=self.sync_weights)
         ie = g.inference_engine
         ecfg = EngineConfig(max_num_seqs=ie.max_num_seqs, max_num_batched_tokens=ie.max_num_batched_tokens,
                             num_kv_pages=ie.num_kv_pages, gpu_memory_utilization=ie.gpu_memory_utilization,
@@ -446,7 +452,7 @@ class RayPPOTrainer:
             # training forward (train_critic_and_policy), before the optimizer step
             lp = batch["rollout_logprobs"].clone()
         else:
-            lp = self.policy.forward(batch)
+            lp = self.dispatch.forward("policy", batch)
         batch["action_log_probs"] = lp
         rmask = batch["response_mask"]
         # the gate and the diff metrics look at the tokens the loss trains on (R/train/trainer.py:1544-1546): observation
@@ -471,12 +477,12 @@ class RayPPOTrainer:
         })
         a = self.cfg.trainer.algorithm
         if getattr(self, "ref", None) is not None:
-            batch["base_action_log_probs"] = self.ref.forward(batch)
+            batch["base_action_log_probs"] = self.dispatch.forward("ref", batch)
             if a.use_kl_in_reward:
                 batch["action_log_probs"] = lp
                 batch = self.apply_reward_kl_penalty(batch)
         if getattr(self, "critic", None) is not None:
-            batch["values"] = self.critic.forward(batch) * rmask
+            batch["values"] = self.dispatch.forward("critic", batch) * rmask
         iso = self.cfg.trainer.isoexec
         if iso.enabled and not self._gate_in_update:
             gate = validate_isoexec_forward_gate(diff, mask, mism, iso)
@@ -554,8 +560,8 @@ class RayPPOTrainer:
         if getattr(self, "critic", None) is not None:
             closs = 0.0
             for lo in range(0, B, mb_seqs):
-                cm = self.critic.forward_backward(batch.slice(lo, min(B, lo + mb_seqs)))
-                self.critic.optim_step()
+                cm = self.dispatch.forward_backward("critic", batch.slice(lo, min(B, lo + mb_seqs)))
+                self.dispatch.optim_step("critic")
                 closs += cm["critic_loss"]
             self.all_metrics["critic/critic_loss"] = closs / max(1, (B + mb_seqs - 1) // mb_seqs)
         for _epoch in range(t.update_epochs_per_batch):
@@ -581,10 +587,10 @@ class RayPPOTrainer:
                     mb.metadata["aux_loss_scale"] = 1.0 / max(1.0, self._global_sum(float(lm.sum())))
                 if getattr(self, "_gate_in_update", False):
                     mb.metadata["check_rollout_bits"] = True
-                m = self.policy.forward_backward(mb)
+                m = self.dispatch.forward_backward("policy", mb)
                 if getattr(self, "_gate_in_update", False):
                     self._gate_on_training_forward(m["rollout_bits"])      # raises before the weights move
-                gn = self.policy.optim_step()
+                gn = self.dispatch.optim_step("policy")
                 out["policy_loss"] += m["policy_loss"]
                 out["ppo_clip_ratio"] += m["ppo_clip_ratio"]
                 out["policy_entropy"] += m["policy_entropy"]
@@ -706,6 +712,8 @@ class RayPPOTrainer:
             with Timer("prepare_input", T):
                 gi, uids = self.prepare_generator_input(rows)
             with Timer("wake", T):
+                if self.dispatch.colocate_all:
+                    self.dispatch.offload_all()           # rollout gets the HBM the optimizer states held
                 self.engine.wake_up()
             with Timer("generate", T):
                 go = self.generate(gi)

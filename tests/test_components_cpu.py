@@ -825,3 +825,34 @@ def test_process_group_timeout_follows_the_environment_flag(monkeypatch):
     monkeypatch.setenv("WORLD_SIZE", "1")
     seen.clear()
     assert state.init_distributed() == (0, 1, 1) and not seen
+
+
+def test_controller_drives_workers_through_the_dispatch_with_optimizer_residency(tmp_path):
+    """The trainer reaches policy, critic and reference through WorkerDispatch; with ``placement.offload_optimizer`` only
+    the model being trained keeps its optimizer state resident and nothing is resident during rollout."""
+    from skyrl_isoexec_b200.train.config import SkyRLTrainConfig
+    from skyrl_isoexec_b200.train.trainer import RayPPOTrainer
+    from skyrl_isoexec_b200.train.worker_dispatch import WorkerDispatch
+
+    cfg = SkyRLTrainConfig.from_cli_overrides([
+        "trainer.policy.model=tiny-qwen3", "trainer.train_batch_size=2", "trainer.policy_mini_batch_size=2",
+        "generator.n_samples_per_prompt=2", "generator.sampling_params.max_generate_length=6",
+        "generator.sampling_params.ignore_eos=true", "data.synthetic_prompt_len=8", "data.synthetic_prompts=8",
+        "trainer.max_prompt_length=8", "generator.inference_engine.num_kv_pages=8", "trainer.logger=jsonl",
+        "trainer.algorithm.advantage_estimator=gae", "trainer.algorithm.use_kl_loss=true", "trainer.placement.offload_optimizer=true"])
+    tr = RayPPOTrainer(cfg, device="cpu")
+    tr.build_models()
+    assert isinstance(tr.dispatch, WorkerDispatch) and set(tr.dispatch.workers) == {"policy", "critic", "ref"}
+    calls = []
+    for verb in ("forward", "forward_backward", "optim_step"):
+        orig = getattr(tr.dispatch, verb)
+        setattr(tr.dispatch, verb, (lambda o, v: (lambda name, *a: (calls.append((v, name)), o(name, *a))[1]))(orig, verb))
+    tr.sync_weights()
+    m = tr.train_step(next(iter(tr.loader)))
+    assert m["policy/rollout_train_logprob_bit_mismatches"] == 0 and m["policy/grad_norm"] > 0
+    assert {("forward", "policy"), ("forward", "ref"), ("forward", "critic"), ("forward_backward", "critic"), ("optim_step", "critic"),
+            ("forward_backward", "policy"), ("optim_step", "policy")} <= set(calls)
+    tl = tr.dispatch.transitions
+    # rollout first: both optimizers parked; then the critic trains (its state comes back), then the policy (critic parked again)
+    assert tl[:2] == [("policy", "cpu"), ("critic", "cpu")] and ("critic", "gpu") in tl and tl[-1] == ("policy", "gpu")
+    assert tr.dispatch.residency == {"policy": "gpu", "critic": "cpu", "ref": "gpu"}
