@@ -188,6 +188,7 @@ def main():
     mism = 0
     gen_s = sync_s = 0.0
     sync_bytes = 0
+    phases = {"generate": 0.0, "fwd_logprobs": 0.0, "policy_train": 0.0, "sync_weights": 0.0, "convert": 0.0, "advantages": 0.0}
     t0 = time.perf_counter()
     e0.record()
     for _ in range(args.steps):
@@ -197,6 +198,8 @@ def main():
         gen_s += float(m["timing/generate"])
         sync_s += float(m["timing/sync_weights"])
         sync_bytes = int(m.get("sync/bytes", 0))
+        for k in phases:
+            phases[k] += float(m.get(f"timing/{k}", 0.0))
     e1.record()
     sync_all()
     wall = time.perf_counter() - t0
@@ -226,6 +229,7 @@ def main():
             "grpo_steps_per_s": args.steps / (dev_ms / 1e3), "rollout_tok_per_s": tokens / max(1e-9, gen_s),
             "logprob_mismatches": int(mism), "kernel_status": status,
             "sync_ms_per_step": 1e3 * sync_s / args.steps, "sync_bytes_per_rank": sync_bytes,
+            "phase_s_per_step_rank0": {k: round(v / args.steps, 3) for k, v in phases.items()},
             "config": {"model": args.model + (f"[layers={args.layers} INVALID-DEBUG]" if args.layers else ""),
                        "global_batch": P * S * ps.dp, "prompts": P * ps.dp, "samples_per_prompt": S,
                        "prompt_len": args.prompt_len, "seq_len": args.prompt_len + args.response_len,
