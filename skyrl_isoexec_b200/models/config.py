@@ -198,10 +198,65 @@ PRESETS: dict[str, ModelConfig] = {
 }
 
 
+def config_from_hf(path: str) -> ModelConfig:
+    """Resolve a model from a Hugging Face style directory (or its ``config.json``): ``architectures[0]`` selects the family,
+    the size fields fill the rest (reference: the model-resolution step that reads ``config.json`` from a path or the HF
+    cache before choosing a manifest, ISO/models/resolve.py). Families: Qwen3, Qwen3-MoE, Qwen3-Next / Qwen3.5 hybrids,
+    Llama, DeepSeek-V3."""
+    import json
+    import os
+
+    f = os.path.join(path, "config.json") if os.path.isdir(path) else path
+    with open(f) as fh:
+        c = json.load(fh)
+    c = {**c.get("text_config", {}), **{k: v for k, v in c.items() if k != "text_config"}}
+    arch = (c.get("architectures") or ["?"])[0]
+    fam = {"Qwen3ForCausalLM": "dense", "Qwen2ForCausalLM": "dense", "LlamaForCausalLM": "dense", "MistralForCausalLM": "dense",
+           "Qwen3MoeForCausalLM": "moe", "Qwen3NextForCausalLM": "hybrid", "Qwen3_5MoeForCausalLM": "hybrid",
+           "Qwen3_5ForCausalLM": "hybrid", "DeepseekV3ForCausalLM": "mla", "DeepseekV2ForCausalLM": "mla"}.get(arch)
+    if fam is None:
+        raise KeyError(f"{f}: architecture {arch!r} has no decoder family here (known: Qwen3, Qwen3-MoE, Qwen3-Next/3.5, Llama, DeepSeek-V3)")
+    h, L, Hq = c["hidden_size"], c["num_hidden_layers"], c["num_attention_heads"]
+    kw = dict(name=os.path.basename(os.path.dirname(os.path.abspath(f))) or arch, architecture=arch, vocab_size=c["vocab_size"],
+              hidden_size=h, num_layers=L, num_q_heads=Hq, num_kv_heads=c.get("num_key_value_heads", Hq),
+              head_dim=c.get("head_dim") or h // Hq, ffn_size=c.get("intermediate_size", 0), rope_theta=float(c.get("rope_theta", 1e4)),
+              rms_eps=float(c.get("rms_norm_eps", 1e-6)), tie_embeddings=bool(c.get("tie_word_embeddings", False)),
+              qk_norm=arch.startswith("Qwen3"), max_position=int(c.get("max_position_embeddings", 8192)),
+              dtype={"float32": "float32"}.get(str(c.get("torch_dtype", "bfloat16")), "bfloat16"))
+    if fam in ("moe", "hybrid", "mla") and (c.get("num_experts") or c.get("n_routed_experts")):
+        kw.update(num_experts=c.get("num_experts") or c["n_routed_experts"], top_k=c["num_experts_per_tok"],
+                  moe_ffn_size=c["moe_intermediate_size"], norm_topk_prob=bool(c.get("norm_topk_prob", True)), ffn_size=0)
+        if c.get("shared_expert_intermediate_size"):
+            kw.update(shared_expert_ffn=c["shared_expert_intermediate_size"], shared_expert_gate=True)
+    if fam == "hybrid":
+        types = c.get("layer_types")
+        if types:
+            types = tuple("gdn" if t in ("linear_attention", "gdn") else "attn" for t in types)
+        else:
+            every = int(c.get("full_attention_interval", 4))
+            types = tuple("attn" if (i % every) == every - 1 else "gdn" for i in range(L))
+        kw.update(layer_types=types, gdn_k_heads=c["linear_num_key_heads"], gdn_v_heads=c["linear_num_value_heads"],
+                  gdn_head_dim=c.get("linear_key_head_dim", 128), gdn_conv_kernel=c.get("linear_conv_kernel_dim", 4),
+                  attn_output_gate=True, zero_centered_norm=True, partial_rotary_factor=float(c.get("partial_rotary_factor", 1.0)))
+    if fam == "mla":
+        dr, dn = c["qk_rope_head_dim"], c["qk_nope_head_dim"]
+        kw.update(kv_lora_rank=c["kv_lora_rank"], q_lora_rank=c.get("q_lora_rank") or 0, qk_rope_dim=dr, head_dim=dr + dn,
+                  v_head_dim=c["v_head_dim"], num_kv_heads=Hq, qk_norm=False,
+                  router="sigmoid_bias" if c.get("scoring_func") == "sigmoid" else "softmax")
+        if c.get("n_shared_experts"):
+            kw.update(shared_expert_ffn=c["moe_intermediate_size"] * c["n_shared_experts"])
+    return ModelConfig(**kw)
+
+
 def get_config(name: str, **overrides) -> ModelConfig:
-    if name not in PRESETS:
-        raise KeyError(f"unknown model preset {name!r}; known: {sorted(PRESETS)}")
-    cfg = PRESETS[name]
+    import os as _os
+
+    if name not in PRESETS and (_os.path.isdir(name) or name.endswith("config.json")):
+        cfg = config_from_hf(name)       # a checkpoint directory instead of a preset name
+    elif name not in PRESETS:
+        raise KeyError(f"unknown model preset {name!r}; known: {sorted(PRESETS)} (or pass a directory holding a config.json)")
+    else:
+        cfg = PRESETS[name]
     # function flags of the environment select contract pins (core/flags.py); an explicit override wins over the flag
     import os
 

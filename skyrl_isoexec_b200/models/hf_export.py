@@ -161,6 +161,15 @@ def hf_config(cfg: ModelConfig) -> dict:
     if cfg.has_moe:
         d.update({"num_experts": cfg.num_experts, "num_experts_per_tok": cfg.top_k, "moe_intermediate_size": cfg.moe_ffn_size,
                   "norm_topk_prob": cfg.norm_topk_prob})
+        if cfg.shared_expert_ffn and not cfg.is_mla:
+            d["shared_expert_intermediate_size"] = cfg.shared_expert_ffn
+    if cfg.has_gdn:
+        d.update({"layer_types": ["linear_attention" if t == "gdn" else "full_attention" for t in cfg.layer_types],
+                  "linear_num_key_heads": cfg.gdn_k_heads, "linear_num_value_heads": cfg.gdn_v_heads,
+                  "linear_key_head_dim": cfg.gdn_head_dim, "linear_value_head_dim": cfg.gdn_head_dim,
+                  "linear_conv_kernel_dim": cfg.gdn_conv_kernel, "partial_rotary_factor": cfg.partial_rotary_factor})
+        if cfg.has_moe:
+            d["architectures"] = ["Qwen3_5MoeForCausalLM"]
     return d
 
 

@@ -858,3 +858,27 @@ def test_controller_drives_workers_through_the_dispatch_with_optimizer_residency
     # rollout first: both optimizers parked; then the critic trains (its state comes back), then the policy (critic parked again)
     assert tl[:2] == [("policy", "cpu"), ("critic", "cpu")] and ("critic", "gpu") in tl and tl[-1] == ("policy", "gpu")
     assert tr.dispatch.residency == {"policy": "gpu", "critic": "cpu", "ref": "gpu"}
+
+
+def test_model_resolution_from_a_hf_style_directory_round_trips(tmp_path):
+    """``trainer.policy.model`` may name a checkpoint directory: ``config.json``'s architecture picks the family and the
+    exported weights load back bit for bit."""
+    from skyrl_isoexec_b200.models import hf_export
+    from skyrl_isoexec_b200.models.config import get_config
+    from skyrl_isoexec_b200.models.decoder import DecoderLM
+
+    for preset in ("tiny-qwen3", "tiny-moe", "tiny-llama", "tiny-hybrid"):
+        src = DecoderLM(get_config(preset), device="cpu", seed=5)
+        d = str(tmp_path / preset)
+        hf_export.save_hf(src, d)
+        cfg = get_config(d)
+        ref = get_config(preset)
+        for f in ("hidden_size", "num_layers", "num_q_heads", "num_kv_heads", "head_dim", "ffn_size", "vocab_size", "num_experts",
+                  "top_k", "moe_ffn_size", "qk_norm", "tie_embeddings"):
+            assert getattr(cfg, f) == getattr(ref, f), (preset, f, getattr(cfg, f), getattr(ref, f))
+        assert cfg.layer_types == ref.layer_types and cfg.gdn_v_heads == ref.gdn_v_heads
+        dst = DecoderLM(cfg.with_(dtype=ref.dtype), device="cpu", seed=9)
+        hf_export.load_hf(dst, d)
+        assert torch.equal(dst.store.flat, src.store.flat)
+    with pytest.raises(KeyError):
+        get_config(str(tmp_path / "nowhere"))
