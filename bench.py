@@ -157,11 +157,12 @@ def main():
     mo = {}
     if args.layers:
         mo["num_layers"] = args.layers
-    if args.tp > 1 or args.engine_tp > 1:
-        mo["tp_invariant"] = True
-        # leaves of the TP-invariant reduction tree: the largest tensor-parallel degree of the deployment (a contract pin
-        # shared by trainer and engines); fewer leaves mean wider GEMM tiles on every rank
-        mo["pik_leaves"] = max(2, args.tp, args.engine_tp)
+    # leaves of the TP-invariant reduction tree: the largest tensor-parallel degree of the deployment (a contract pin
+    # shared by trainer and engines; fewer leaves mean wider GEMM tiles on every rank), and at least 2 everywhere: the
+    # tree is a K split whose order is part of the contract, so a decode-sized row-parallel GEMM (o, down) gives each
+    # leaf its own CTA and folds them through a cluster's shared memory instead of walking all of K in one CTA
+    mo["tp_invariant"] = True
+    mo["pik_leaves"] = max(2, args.tp, args.engine_tp)
     ov.append(f"generator.inference_engine.tensor_parallel_size={args.engine_tp}")
     if mo:
         ov.append("trainer.policy.model_overrides=" + json.dumps(mo))

@@ -2,7 +2,7 @@
 
     python skyrl_isoexec_b200/benchmarks/profile_kernels.py attn_decode | attn_prefill | gemm_large | gemm_decode | logprob | rmsnorm |
                                    glu_decode | moe_grouped | rmsnorm_decode | sampler | rmsnorm_bwd | attn_bwd | train_small |
-                                   gemm_bwd_dx | gemm_bwd_dw | moe_train | reshard
+                                   gemm_bwd_dx | gemm_bwd_dw | moe_train | reshard | gdn_chunk | gated_outnorm
 
 Each mode allocates well under 1 GB, launches the kernel a handful of times and exits.
 """
@@ -195,6 +195,42 @@ def main(mode: str = "attn_decode") -> None:
         d = torch.frombuffer(bytearray(b"".join(recs)), dtype=torch.uint8).to(dev)
         for _ in range(4):
             _native.check(lib.ix_reshard_pull(d.data_ptr(), len(recs), _native.stream()), "ix_reshard_pull")
+    elif mode == "gdn_chunk":
+        # chunked gated delta rule: 8 sequences x 2048 tokens, 16 key heads, 32 value heads of 128 (the hybrid preset's shape)
+        from skyrl_isoexec_b200.ops import gdn
+        T, Hk, Hv, D = 16384, 16, 32, 128
+        qn = torch.nn.functional.normalize(torch.randn(T, Hk, D, device=dev), dim=-1).bfloat16()
+        kn = torch.nn.functional.normalize(torch.randn(T, Hk, D, device=dev), dim=-1).bfloat16()
+        v = torch.randn(T, Hv, D, device=dev).bfloat16()
+        g = -torch.rand(T, Hv, device=dev) * 0.1
+        beta = torch.rand(T, Hv, device=dev)
+        segs = [(i * 2048, 2048, -1, -1) for i in range(8)]
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for i in range(4):
+            if i == 3:
+                e0.record()
+            gdn.gdn_chunk_scan(qn, kn, v, g, beta, segs)
+        e1.record()
+        torch.cuda.synchronize()
+        print(f"gdn_chunk_scan T={T} Hk={Hk} Hv={Hv} D={D}: {e0.elapsed_time(e1) * 1e3:.1f} us (both kernels)")
+        # the token-by-token scan the chunked form replaces on this path (fp32 state in registers, one CTA per head)
+        meta = gdn.GDNMeta.packed([2048] * 8, dev)
+        o = torch.empty(T, Hv, D, device=dev, dtype=torch.bfloat16)
+        ssm = torch.empty(0, dtype=torch.float32, device=dev)
+        lib = _native.lib()
+        for i in range(3):
+            if i == 2:
+                e0.record()
+            _native.check(lib.ix_gdn_scan(qn.data_ptr(), kn.data_ptr(), v.data_ptr(), g.data_ptr(), beta.data_ptr(), meta.chunks.data_ptr(),
+                                          ssm.data_ptr(), o.data_ptr(), meta.n_chunks, Hk, Hv, D, D, 0, 0, _native.stream()), "ix_gdn_scan")
+        e1.record()
+        torch.cuda.synchronize()
+        print(f"sequential gdn_scan, same input: {e0.elapsed_time(e1) * 1e3:.1f} us")
+    elif mode == "gated_outnorm":
+        o, z = torch.randn(8192, 32, 128, device=dev).bfloat16(), torch.randn(8192, 32, 128, device=dev).bfloat16()
+        w = (torch.randn(128, device=dev) * 0.1).bfloat16()
+        for _ in range(4):
+            F.gated_outnorm(o, z, w, 1e-6, True)
     elif mode == "sampler":
         from skyrl_isoexec_b200.engine.sampler import Sampler, SamplingParams
         lg = torch.randn(64, 151936, device=dev).bfloat16()

@@ -591,7 +591,8 @@ IX_API long long ix_tp_stage_floats(int M, int N, int mode, int W, int bn) {
 // The fused tensor-parallel GEMM. A: this rank's operand (row-parallel modes: [M, K] with K = this rank's slice;
 // AG: ignored, rows come from a_local through the gathered buffers), B: this rank's weight shard [N, K].
 // stage/flags/peer_out/done: W device addresses each (as mapped in THIS process), already offset to the call's
-// parity half. leaves: L (K / 64 must be divisible by L). bn: 32/64/128 with 2*L*bn <= 512.
+// parity half. leaves: L (K / 64 must be divisible by L). bn: 32/64/128/256 with L*bn <= 512
+// (two accumulator sets, so that the epilogue of one tile overlaps the MMAs of the next, when 2*L*bn <= 512).
 static int tp_gemm_fused_impl(const void* A, const void* B, void* c_local, int M, int N, int K, int lda, int ldb, int ldc,
                             int mode, int leaves, int bn, int out_f32, int rank, int W, unsigned epoch,
                             const long long* stage, const long long* flags, const long long* peer_out, const long long* done,
@@ -638,8 +639,9 @@ static int tp_gemm_fused_impl(const void* A, const void* B, void* c_local, int M
 #define IX_TP(BN_, L_) \
   if (bn == BN_ && leaves == L_) return launch<BN_, L_>(tmA, tmA2, tmB, p, c_local, M, N, K, ldc, a_rows, num_q, s, dev);
   IX_TP(256, 1) IX_TP(128, 1) IX_TP(128, 2) IX_TP(64, 1) IX_TP(64, 2) IX_TP(64, 4) IX_TP(32, 1) IX_TP(32, 2) IX_TP(32, 4) IX_TP(32, 8)
+  IX_TP(256, 2) IX_TP(128, 4) IX_TP(64, 8)   // all 512 columns hold ONE tile's leaves: wider MMAs, no overlap of epilogue and next tile
 #undef IX_TP
-  return ixh::fail(ixh::IX_EARG, "tp_gemm: no kernel for bn=%d leaves=%d (need 2*leaves*bn <= 512)", bn, leaves);
+  return ixh::fail(ixh::IX_EARG, "tp_gemm: no kernel for bn=%d leaves=%d (need leaves*bn <= 512)", bn, leaves);
 }
 
 IX_API int ix_tp_gemm_fused(const void* A, const void* B, void* c_local, int M, int N, int K, int lda, int ldb, int ldc,

@@ -286,10 +286,13 @@ class _ExpertsFn(torch.autograd.Function):
     forward = plan, gather, grouped fc1, GLU x gate weight, grouped fc2 (fp32), fixed-order combine;
     backward = scatter of the output gradient, grouped NN / TN GEMMs for both linears, the GLU x weight VJP, and the
     fixed-order sum of the k row gradients of every token (no atomics)
-    (reference: ISO/ops/moe/moe_batched_experts.py:301-400, moe_backward_kernel.py:254-401, moe_combine_backward.py:80-231)."""
+    (reference: ISO/ops/moe/moe_batched_experts.py:301-400, moe_backward_kernel.py:254-401, moe_combine_backward.py:80-231).
+
+    ``raw=True`` is the form the expert-parallel owner runs on the rows it received: one expert per input row (k = 1),
+    the result stays fp32 and unrounded so that the SOURCE rank does the fixed-order sum and the single rounding."""
 
     @staticmethod
-    def forward(ctx, y, w, gate_up, down, idx, shared):
+    def forward(ctx, y, w, gate_up, down, idx, shared, raw=False):
         E = gate_up.shape[0]
         _obs.note("moe.experts", "grouped_gemm")
         _obs.note("moe.combine", "fixed_order")
@@ -298,10 +301,10 @@ class _ExpertsFn(torch.autograd.Function):
         h = grouped_gemm(x_rows, gate_up, plan.offs, EPI_BF16)
         a2 = _glu_scale(h, w_rows)
         rows = grouped_gemm(a2, down, plan.offs, EPI_F32)
-        out = torch.empty(y.shape[0], down.shape[1], dtype=y.dtype, device=y.device)
+        out = torch.empty(y.shape[0], down.shape[1], dtype=torch.float32 if raw else y.dtype, device=y.device)
         if y.shape[0]:
             _native.check(_native.lib().ix_moe_combine(rows.data_ptr(), plan.pos.data_ptr(), _native.ptr(shared), out.data_ptr(),
-                                                       y.shape[0], out.shape[1], plan.k, int(y.dtype == torch.bfloat16),
+                                                       y.shape[0], out.shape[1], plan.k, int(out.dtype == torch.bfloat16),
                                                        _native.stream()), "ix_moe_combine")
         ctx.plan = plan
         ctx.has_shared = shared is not None
@@ -313,7 +316,7 @@ class _ExpertsFn(torch.autograd.Function):
     def backward(ctx, g):
         y, h, w_rows, gate_up, down = ctx.saved_tensors
         plan: DispatchPlan = ctx.plan
-        g = g.contiguous()
+        g = g.to(y.dtype).contiguous()
         d_rows = plan.scatter(g)                                    # [R, H]
         a2 = _glu_scale(h, w_rows)                                  # recomputed (an elementwise pass) instead of kept
         d_a2 = grouped_gemm_nn(d_rows, down, plan)                  # [R, F]      down [E, H, F]
@@ -335,7 +338,7 @@ class _ExpertsFn(torch.autograd.Function):
                                                        y.shape[1], plan.k, int(y.dtype == torch.bfloat16), _native.stream()),
                           "ix_moe_combine")
         d_w = d_w_rows.index_select(0, plan.row_of[:plan.T * plan.k].long()).view(plan.T, plan.k)
-        return d_y, d_w, d_gate_up, d_down, None, (g if ctx.has_shared else None)
+        return d_y, d_w, d_gate_up, d_down, None, (g if ctx.has_shared else None), None
 
 
 def _experts_fn_ok(y, gate_up, down) -> bool:
@@ -393,6 +396,16 @@ def moe_block(y: torch.Tensor, model, i: int) -> torch.Tensor:
         recv = [sum(c) for c in cnt_in_l]
         xr = _AllToAll.apply(x_rows, send, recv, ps.ep_group)
         wr = _AllToAll.apply(w_rows, send, recv, ps.ep_group)
+        if torch.is_grad_enabled() and xr.shape[0] and _experts_fn_ok(xr, gate_up, down):
+            # under autograd on a GPU the owner runs its experts and their VJPs as grouped launches: the device plan sorts
+            # the received rows by expert (stable, so source order is kept inside an expert) and pads every group
+            _SERVED["moe.experts/nccl_grouped_autograd"] += 1
+            own = torch.repeat_interleave(torch.arange(e_loc, device=y.device, dtype=torch.int32).repeat(ps.ep), cnt_in.view(-1),
+                                          output_size=xr.shape[0])
+            out_rows = _ExpertsFn.apply(xr, wr.view(-1, 1), gate_up, down, own.view(-1, 1), None, True)
+            rows = _AllToAll.apply(out_rows, recv, send, ps.ep_group)
+            shared = _shared_expert(y, model, pfx) if cfg.shared_expert_ffn else None
+            return combine_fixed_order(rows, pos, y.dtype, shared)
         # received rows are grouped by (source rank, expert); regroup by expert, keeping source order
         segs, base = [], 0
         for r in range(ps.ep):

@@ -44,12 +44,15 @@ def _sig(lib):
     lib.ix_tp_gemm_ar1_graph.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p] + [C.c_int] * 6 + [C.c_int] * 5 + \
         [C.c_void_p, C.c_uint, C.c_void_p, C.c_void_p, C.c_longlong, C.c_longlong, C.c_void_p]
     lib.ix_tp_set_epoch.argtypes = [C.c_void_p, C.c_uint, C.c_void_p]
+    lib.ix_leaf_split_bn.argtypes = [C.c_int] * 4
+    lib.ix_leaf_split_gemm.argtypes = [C.c_void_p] * 3 + [C.c_int] * 9 + [C.c_void_p]
     lib._tp_sig = True
 
 
 def pick_bn(M: int, N: int, leaves: int) -> int:
-    """Widest tile allowed by TMEM (2*leaves*bn <= 512 columns) that still gives most SMs a tile."""
-    bn = 256 // leaves
+    """Widest tile whose ``leaves`` accumulators fit the 512 TMEM columns (a tcgen05.mma of 128 columns costs what one of
+    32 does, so width beats keeping a second accumulator set for epilogue overlap) that still gives most SMs a tile."""
+    bn = min(256, 512 // leaves)
     tiles_m = (M + 127) // 128
     while bn > 32 and (N % bn or tiles_m * (N // bn) * 5 < _SMS * 3):
         bn //= 2
@@ -62,15 +65,25 @@ def fused_ok(M: int, N: int, K: int, leaves: int) -> bool:
     return leaves in (1, 2, 4, 8) and K % (64 * leaves) == 0 and N % 32 == 0 and M > 0
 
 
-def leaftree_gemm_fused(x: torch.Tensor, w: torch.Tensor, leaves: int, out_f32: bool = True) -> torch.Tensor:
-    """[M,N] = balanced fp32 tree over ``leaves`` equal K slices of x @ w^T, one kernel, no peers."""
+def leaftree_gemm_fused(x: torch.Tensor, w: torch.Tensor, leaves: int, out_f32: bool = True, bn: int | None = None,
+                        split: bool | None = None) -> torch.Tensor:
+    """[M,N] = balanced fp32 tree over ``leaves`` equal K slices of x @ w^T, one kernel, no peers. Decode-sized M runs
+    the leaf-parallel form (one CTA per leaf, folded through a cluster's shared memory; csrc/leaf_split_gemm.cu), larger
+    M the form that keeps every leaf's accumulator in one CTA's TMEM; both give the same bits. ``bn`` / ``split``
+    override the choice (benchmarks and tests)."""
     lib = _native.lib()
     _sig(lib)
     M, K = x.shape
     N = w.shape[0]
     assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.stride(1) == 1 and w.stride(1) == 1
     out = torch.empty(M, N, dtype=torch.float32 if out_f32 else torch.bfloat16, device=x.device)
-    bn = pick_bn(M, N, leaves)
+    if split is None:
+        split = bn is None and N % 4 == 0 and lib.ix_leaf_split_bn(M, N, K, leaves) > 0
+    if split:
+        _native.check(lib.ix_leaf_split_gemm(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, x.stride(0), w.stride(0), N,
+                                             leaves, bn or 0, int(out_f32), _native.stream()), "ix_leaf_split_gemm")
+        return out
+    bn = bn or pick_bn(M, N, leaves)
     _native.check(lib.ix_tp_gemm_fused(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, x.stride(0), w.stride(0), N,
                                        TP_LOCAL, leaves, bn, int(out_f32), 0, 1, 0, None, None, None, None, None, None, 0, 0,
                                        _native.stream()), "ix_tp_gemm_fused")

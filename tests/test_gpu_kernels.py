@@ -193,6 +193,36 @@ def test_grouped_expert_gemm_equals_per_expert_loop_bitwise(T, E, k):
         assert bitwise_equal(h1[:lo], F.gemm_nt(x_rows[:lo].contiguous(), gate_up[0])) if lo else True
 
 
+@pytest.mark.parametrize("M", [1, 64, 130, 256])
+def test_leaf_parallel_gemm_over_a_cluster_equals_the_one_cta_form_bitwise(M):
+    """Decode-sized leaf-tree GEMM with one CTA per leaf, folded through the cluster's shared memory: same bits as the
+    form that keeps all leaves in one CTA's TMEM and as the leaf loop, for every leaf count, tile width and output type;
+    a strided activation view is taken as it is."""
+    from skyrl_isoexec_b200.ops import _native
+    from skyrl_isoexec_b200.parallel.tp import tree_fold
+    from skyrl_isoexec_b200.parallel.tp_fused import leaftree_gemm_fused
+
+    torch.manual_seed(5)
+    N, K = 512, 2048
+    xs = torch.randn(M, K + 64, device=DEV).bfloat16()
+    x = xs[:, :K]                                               # row stride K + 64
+    w = (torch.randn(N, K, device=DEV) * 0.05).bfloat16()
+    for L in (2, 4, 8):
+        LK = K // L
+        parts = torch.stack([F.gemm_nt(x[:, j * LK:(j + 1) * LK], w[:, j * LK:(j + 1) * LK], out_f32=True) for j in range(L)])
+        want = tree_fold(parts)
+        assert bitwise_equal(leaftree_gemm_fused(x, w, L, split=False), want)
+        assert _native.lib().ix_leaf_split_bn(M, N, K, L) > 0
+        assert bitwise_equal(leaftree_gemm_fused(x, w, L), want), f"default form, L={L}"
+        for bn in (32, 64, 128):
+            if bn // L < 4:
+                continue
+            assert bitwise_equal(leaftree_gemm_fused(x, w, L, bn=bn, split=True), want), f"L={L} bn={bn}"
+            assert bitwise_equal(leaftree_gemm_fused(x, w, L, out_f32=False, bn=bn, split=True), want.bfloat16())
+    assert _native.read_status() == 0
+    assert _native.lib().ix_leaf_split_bn(4096, N, K, 2) == 0    # training sizes keep the one-CTA form
+
+
 @pytest.mark.parametrize("M", [5, 300])
 def test_leaftree_gemm_one_kernel_equals_leaf_loop_bitwise(M):
     """Leaves accumulate in separate TMEM accumulators and fold in the epilogue: same bits as one GEMM per
@@ -731,6 +761,35 @@ def test_moe_experts_autograd_function_matches_fp32_autograd_and_the_fused_forwa
     empty = [e for e in range(E) if not bool((idx == e).any())]
     for e in empty:
         assert not gate_up.grad[e].any() and not down.grad[e].any()
+
+
+def test_moe_experts_raw_form_equals_the_rows_of_the_combined_form():
+    """The form an expert-parallel owner runs (one expert per received row, fp32 rows returned unrounded): summing its
+    rows in the source's fixed order gives the bits of the single-rank experts function, and its gradients agree."""
+    from skyrl_isoexec_b200.ops import moe
+
+    torch.manual_seed(9)
+    T, E, k, H, Fd = 300, 8, 2, 256, 128
+    y0 = (torch.randn(T, H, device=DEV) * 0.5).bfloat16()
+    gu0 = (torch.randn(E, 2 * Fd, H, device=DEV) * 0.05).bfloat16()
+    dn0 = (torch.randn(E, H, Fd, device=DEV) * 0.05).bfloat16()
+    idx, w0, _ = moe.router_topk_fwd(torch.randn(T, E, device=DEV), k, None, False, True)
+    gout = (torch.randn(T, H, device=DEV) * 0.1).bfloat16()
+    y, w, gu, dn = y0.clone().requires_grad_(), w0.clone().requires_grad_(), gu0.clone().requires_grad_(), dn0.clone().requires_grad_()
+    moe._ExpertsFn.apply(y, w, gu, dn, idx, None).backward(gout)
+    want = moe._ExpertsFn.apply(y0, w0, gu0, dn0, idx, None)
+    # the same work as an owner sees it: T*k rows in (token, slot) order, each naming its expert
+    y2, w2, gu2, dn2 = y0.clone().requires_grad_(), w0.clone().requires_grad_(), gu0.clone().requires_grad_(), dn0.clone().requires_grad_()
+    rows_in = y2.repeat_interleave(k, 0)
+    raw = moe._ExpertsFn.apply(rows_in, w2.reshape(-1, 1), gu2, dn2, idx.reshape(-1, 1).contiguous(), None, True)
+    assert raw.dtype == torch.float32 and raw.shape == (T * k, H)
+    pos = torch.arange(T * k, device=DEV).view(T, k)
+    got = moe.combine_fixed_order(raw, pos, torch.bfloat16)
+    assert bitwise_equal(got.detach(), want)
+    got.backward(gout)
+    rel = lambda a, b: float((a.float() - b.float()).abs().max() / b.float().abs().max().clamp(min=1e-6))
+    assert rel(gu2.grad, gu.grad) < 1e-2 and rel(dn2.grad, dn.grad) < 1e-2
+    assert rel(y2.grad, y.grad) < 2e-2 and rel(w2.grad, w.grad) < 2e-2
 
 
 def test_every_fused_region_equals_its_unfused_chain_on_hazard_inputs():

@@ -502,14 +502,19 @@ def _ep_model_worker(rank, world, port, q):
             ro[i, :len(o.response_logprobs)] = torch.tensor(o.response_logprobs)
         mism = count_bit_mismatches((lp * rmask).contiguous(), (ro * rmask).contiguous())
         batch["action_log_probs"] = lp
-        worker.forward_backward(batch)
+        batch["rollout_logprobs"] = ro                               # the backward pass's own forward is compared as well
+        batch.metadata["check_rollout_bits"] = True
+        fb = worker.forward_backward(batch)
         gn = worker.optim_step()
-        res = torch.tensor([float(mism), gn, float(_native.read_status())], device="cuda", dtype=torch.float64)
+        from skyrl_isoexec_b200.ops import moe as moe_ops
+        res = torch.tensor([float(mism), gn, float(_native.read_status()), float(fb["rollout_bits"]["mismatches"]),
+                            float(moe_ops._SERVED["moe.experts/nccl_grouped_autograd"])], device="cuda", dtype=torch.float64)
         allr = [torch.zeros_like(res) for _ in range(world)]
         dist.all_gather(allr, res)
         if rank == 0:
             q.put({"registered": reg, "mismatches": [int(r[0]) for r in allr], "grad_norms": [float(r[1]) for r in allr],
-                   "status": [int(r[2]) for r in allr]})
+                   "status": [int(r[2]) for r in allr], "train_mismatches": [int(r[3]) for r in allr],
+                   "grouped_autograd_blocks": [int(r[4]) for r in allr]})
     finally:
         dist.barrier()
         dist.destroy_process_group()
@@ -531,6 +536,7 @@ def test_moe_model_with_expert_parallelism_over_peer_memory():
         p.join(timeout=120)
     print("moe ep model:", res)
     assert res["registered"]["ep"] and res["mismatches"] == [0, 0] and res["status"] == [0, 0]
+    assert res["train_mismatches"] == [0, 0] and min(res["grouped_autograd_blocks"]) > 0
     assert res["grad_norms"][0] == res["grad_norms"][1] > 0
 
 
