@@ -38,8 +38,14 @@ def main(mode: str = "attn_decode") -> None:
             kc = torch.randn(T, Hkv, D, device=dev).bfloat16()
             vc = torch.randn_like(kc)
             meta = F.AttnMeta.packed(lens, Hq, Hkv, dev)
-        for _ in range(4):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for i in range(4):
+            if i == 1:
+                e0.record()
             F.attention_fwd(q, kc, vc, meta, 1 / math.sqrt(D))
+        e1.record()
+        torch.cuda.synchronize()
+        print(f"{mode}: {e0.elapsed_time(e1) / 3 * 1e3:.1f} us per call (3 calls back to back; K+V {2 * kc.numel() * 2 / 1e6:.0f} MB)")
     elif mode in ("gemm_large", "gemm_decode"):
         M, N, K = (8192, 4096, 4096) if mode == "gemm_large" else (64, 24576, 4096)
         x = torch.randn(M, K, device=dev).bfloat16()

@@ -11,13 +11,26 @@ survive a restart of the front end) and executed in order by one engine thread; 
   POST /api/v1/asample             {model_id, prompt_ids, num_samples, sampling_params}
   POST /api/v1/save_weights | load_weights {model_id, path}
   POST /api/v1/retrieve_future     {request_id}
+  POST /api/v1/list_checkpoints    {model_id}                            -> every completed save of the model
+  POST /api/v1/checkpoint_archive  {model_id, path}                      -> {archive_id, bytes, sha256}: a .tar.gz of the save
+  GET  /api/v1/download/<archive_id>                                     -> the archive's bytes
+  GET  /api/v1/telemetry                                                 -> per-verb counts / failures / latency, queue depth
   GET  /api/v1/healthz, /api/v1/get_server_capabilities
+
+A front end restarted on an existing database file reloads its models from their stored specs, re-applies the last
+completed ``save_weights`` of each when the file is still there, and keeps queued requests; requests that were
+pending for a model that cannot be rebuilt are marked failed with that reason
+(reference: R/tinker/api.py:730-1375, checkpoint archive and download routes, request telemetry).
 """
 
 from __future__ import annotations
 
+import hashlib
 import json
+import os
 import sqlite3
+import tarfile
+import tempfile
 import threading
 import time
 import uuid
@@ -37,12 +50,20 @@ class TinkerServer:
         self.db.execute("create table if not exists models (id text primary key, spec text)")
         self.db.execute("create table if not exists sessions (id text primary key, kind text, model_id text, meta text, "
                         "created real, heartbeat real)")
+        self.db.execute("create table if not exists checkpoints (model_id text, path text, kind text, step integer, bytes integer, "
+                        "created real)")
+        self.db.execute("create table if not exists archives (id text primary key, model_id text, src text, file text, bytes integer, "
+                        "sha256 text, created real)")
+        cols = [r[1] for r in self.db.execute("pragma table_info(futures)")]
+        if "finished" not in cols:
+            self.db.execute("alter table futures add column finished real")
         self._dblock = threading.Lock()
         self.device = device
         self.models: dict[str, SkyRLTrainBackend] = {}
         self._stop = threading.Event()
         self._wake = threading.Event()
-        self._seq = 0
+        self._seq = int(self.db.execute("select coalesce(max(seq), 0) from futures").fetchone()[0])
+        self.recovered = self._recover()
         outer = self
 
         class H(BaseHTTPRequestHandler):
@@ -64,6 +85,23 @@ class TinkerServer:
                     from ..models.config import PRESETS
 
                     return self._reply(200, {"supported_models": sorted(PRESETS), "loss_fns": sorted(LOSS_FNS)})
+                if self.path == "/api/v1/telemetry":
+                    return self._reply(200, outer.telemetry())
+                if self.path.startswith("/api/v1/download/"):
+                    f = outer.archive_file(self.path.rsplit("/", 1)[-1])
+                    if f is None:
+                        return self._reply(404, {"error": "unknown archive"})
+                    self.send_response(200)
+                    self.send_header("Content-Type", "application/gzip")
+                    self.send_header("Content-Length", str(os.path.getsize(f)))
+                    self.end_headers()
+                    with open(f, "rb") as fh:
+                        while True:
+                            buf = fh.read(1 << 20)
+                            if not buf:
+                                break
+                            self.wfile.write(buf)
+                    return None
                 self._reply(404, {"error": "no route"})
 
             def do_POST(self):
@@ -92,9 +130,76 @@ class TinkerServer:
         self.httpd.shutdown()
         self.httpd.server_close()
 
+    # ------------------------------------------------------------------ restart, checkpoints, telemetry
+    def _recover(self) -> dict:
+        """Rebuild the models a previous front end left in the database; fail what cannot continue."""
+        out = {"models": [], "failed_requests": 0}
+        for mid, spec in self.db.execute("select id, spec from models").fetchall():
+            sp = json.loads(spec)
+            try:
+                b = SkyRLTrainBackend(sp["base_model"], sp["model_overrides"], self.device, sp["lr"], sp["seed"])
+                last = self.db.execute("select path from checkpoints where model_id = ? and kind = 'save_weights' order by created desc limit 1",
+                                       (mid,)).fetchone()
+                if last and os.path.exists(last[0]):
+                    b.handle({"type": "load_weights", "path": last[0]})
+                self.models[mid] = b
+                out["models"].append(mid)
+            except Exception as e:  # noqa: BLE001
+                cur = self.db.execute("update futures set status = 'failed', result = ?, finished = ? where model_id = ? and status = 'pending'",
+                                      (json.dumps({"error": f"front end restarted and the model could not be rebuilt: {type(e).__name__}: {e}"}),
+                                       time.time(), mid))
+                out["failed_requests"] += cur.rowcount
+        self.db.commit()
+        return out
+
+    def archive_file(self, archive_id: str) -> str | None:
+        with self._dblock:
+            row = self.db.execute("select file from archives where id = ?", (archive_id,)).fetchone()
+        return row[0] if row and os.path.exists(row[0]) else None
+
+    def telemetry(self) -> dict:
+        with self._dblock:
+            rows = self.db.execute("select payload, status, created, finished from futures").fetchall()
+            sessions = self.db.execute("select count(*) from sessions").fetchone()[0]
+        per: dict = {}
+        for payload, status, created, finished in rows:
+            kind = json.loads(payload).get("type", "?")
+            d = per.setdefault(kind, {"count": 0, "pending": 0, "failed": 0, "latency_s_sum": 0.0, "latency_s_max": 0.0})
+            d["count"] += 1
+            d["pending"] += status == "pending"
+            d["failed"] += status == "failed"
+            if finished:
+                d["latency_s_sum"] += finished - created
+                d["latency_s_max"] = max(d["latency_s_max"], finished - created)
+        return {"requests": per, "queue_depth": sum(d["pending"] for d in per.values()), "models": len(self.models), "sessions": sessions}
+
     # ------------------------------------------------------------------ front end
     def post(self, path: str, body: dict) -> dict:
         verb = path.rsplit("/", 1)[-1]
+        if verb == "list_checkpoints":
+            with self._dblock:
+                rows = self.db.execute("select path, kind, step, bytes, created from checkpoints where model_id = ? order by created",
+                                       (body["model_id"],)).fetchall()
+            return {"checkpoints": [dict(path=p_, kind=k, step=st, bytes=b, created=c, exists=os.path.exists(p_)) for p_, k, st, b, c in rows]}
+        if verb == "checkpoint_archive":
+            with self._dblock:
+                known = self.db.execute("select 1 from checkpoints where model_id = ? and path = ?", (body["model_id"], body["path"])).fetchone()
+            if not known or not os.path.exists(body["path"]):
+                raise KeyError(f"checkpoint {body['path']!r} of {body['model_id']!r}")       # only recorded saves are served
+            aid = "arc-" + uuid.uuid4().hex[:12]
+            fd, tmp = tempfile.mkstemp(prefix=aid + "-", suffix=".tar.gz")
+            os.close(fd)
+            with tarfile.open(tmp, "w:gz") as tf:
+                tf.add(body["path"], arcname=os.path.basename(body["path"].rstrip("/")))
+            h = hashlib.sha256()
+            with open(tmp, "rb") as fh:
+                for buf in iter(lambda: fh.read(1 << 20), b""):
+                    h.update(buf)
+            size = os.path.getsize(tmp)
+            with self._dblock:
+                self.db.execute("insert into archives values (?, ?, ?, ?, ?, ?, ?)", (aid, body["model_id"], body["path"], tmp, size, h.hexdigest(), time.time()))
+                self.db.commit()
+            return {"archive_id": aid, "bytes": size, "sha256": h.hexdigest(), "download": f"/api/v1/download/{aid}"}
         # ---- sessions: bookkeeping only (who is connected, which sampler weights a sampling session reads)
         if verb in ("create_session", "create_sampling_session"):
             if verb == "create_sampling_session" and body.get("model_id") not in self.models:
@@ -167,7 +272,7 @@ class TinkerServer:
         payload = dict(body, type=_ROUTES[verb])
         with self._dblock:
             self._seq += 1
-            self.db.execute("insert into futures values (?, ?, ?, ?, 'pending', null, ?)",
+            self.db.execute("insert into futures (id, seq, model_id, payload, status, result, created) values (?, ?, ?, ?, 'pending', null, ?)",
                             (rid, self._seq, body["model_id"], json.dumps(payload), time.time()))
             self.db.commit()
         self._wake.set()
@@ -183,12 +288,19 @@ class TinkerServer:
                 self._wake.clear()
                 continue
             rid, mid, payload = row
+            req = json.loads(payload)
             try:
-                res, status = self.models[mid].handle(json.loads(payload)), "completed"
+                res, status = self.models[mid].handle(req), "completed"
             except Exception as e:  # noqa: BLE001
                 res, status = {"error": f"{type(e).__name__}: {e}"}, "failed"
             with self._dblock:
-                self.db.execute("update futures set status = ?, result = ? where id = ?", (status, json.dumps(res), rid))
+                self.db.execute("update futures set status = ?, result = ?, finished = ? where id = ?", (status, json.dumps(res), time.time(), rid))
+                if status == "completed" and req["type"] in ("save_weights", "save_weights_for_sampler") and req.get("path"):
+                    p_ = req["path"]
+                    size = os.path.getsize(p_) if os.path.isfile(p_) else sum(
+                        os.path.getsize(os.path.join(d, f)) for d, _, fs in os.walk(p_) for f in fs) if os.path.exists(p_) else 0
+                    self.db.execute("insert into checkpoints values (?, ?, ?, ?, ?, ?)",
+                                    (mid, p_, req["type"], int(self.models[mid].step_count), int(size), time.time()))
                 self.db.commit()
 
 

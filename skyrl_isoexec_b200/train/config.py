@@ -132,6 +132,9 @@ class IsoExecConfig:
     # bits; the forward gate then compares the TRAINING forward's logprobs with the rollout's, before the optimizer
     # step. Off by default (the reference always runs the scoring forward).
     reuse_rollout_logprobs: bool = False
+    # At start-up on a GPU, prove on every GEMM shape of the model's census that the provider's rows do not depend on
+    # the batch they are computed in (and that the two leaf-tree forms agree); a shape that fails refuses the launch.
+    mm_admission: bool = True
     contract_path: str = ""
     debug_trace: str = ""
 

@@ -328,6 +328,16 @@ class RayPPOTrainer:
 
             self._sig_key = (mcfg.name, self.adapter_trainer.contract.identities.numerical_policy, self.adapter_trainer.arch)
             self.signatures = bitwise_table(*self._sig_key, proof_ref="tests/test_train_cpu.py::test_grpo_loop_is_bitwise_on_policy_and_resumes")
+        if t.isoexec.enabled and t.isoexec.mm_admission and self.device.type == "cuda":
+            from ..core import mm_admission
+
+            self.mm_admitted = {}
+            for deg in sorted({self.ps.tp, self.engine_ps.tp if self.separate_engine else self.ps.tp}):
+                rep = mm_admission.admit(mcfg, str(self.device), tp=deg, ep=self.ps.ep)
+                self.mm_admitted[deg] = rep
+                bad = mm_admission.refused(rep)
+                if bad:
+                    raise RuntimeError(f"GEMM admission refused at tp={deg}: rows of {bad} depend on the batch they are computed in")
         if self.dataset is None:
             d = self.cfg.data
             n = d.synthetic_prompts or t.train_batch_size * 4

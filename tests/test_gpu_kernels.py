@@ -878,3 +878,47 @@ def test_gated_outnorm_matches_the_cpu_oracle_and_the_formula(D, zc):
     # a row's bits do not depend on how many rows the launch has (odd counts leave half a warp idle)
     one = F.gated_outnorm(o[:1].to(DEV), z[:1].to(DEV), w.to(DEV), 1e-6, zc).cpu()
     assert bitwise_equal(one, gpu[:1])
+
+
+def test_gemm_admission_on_the_model_census_and_its_negative_control(monkeypatch):
+    """Start-up admission: every GEMM shape of a model's census gives batch-independent rows (and the two leaf-tree
+    forms agree); a provider whose rows depend on the batch is refused by name."""
+    from skyrl_isoexec_b200.core import mm_admission
+    from skyrl_isoexec_b200.models.config import get_config
+
+    cfg = get_config("qwen3-8b", dtype="bfloat16", tp_invariant=True, pik_leaves=2, num_layers=2, vocab_size=32768)
+    rep = mm_admission.admit(cfg, "cuda")
+    assert rep and all(v is True for v in rep.values()), rep
+    assert {"attn.qkv", "attn.o", "mlp.fc1", "mlp.fc2", "lm_head"} <= set(rep)
+    assert mm_admission.refused(rep) == []
+    rep2 = mm_admission.admit(cfg, "cuda", tp=2)
+    assert all(v is True for v in rep2.values()), rep2
+    # negative control: a "provider" that picks a different summation for small batches
+    real = F.gemm_nt
+    monkeypatch.setattr(F, "gemm_nt", lambda a, w, out_f32=False, **kw: real(a, w, out_f32=out_f32, **kw) if a.shape[0] > 100
+                        else (a.float() @ w.float().T).to(torch.float32 if out_f32 else torch.bfloat16))
+    mm_admission._REPORTS.clear()
+    bad = mm_admission.admit(cfg, "cuda")
+    assert "mlp.fc2" in mm_admission.refused(bad) or "attn.qkv" in mm_admission.refused(bad)
+    mm_admission._REPORTS.clear()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_trace_digest_kernel_equals_the_integer_torch_formulation(dtype):
+    """Row digests of every ladder level from one kernel pass: the same 64-bit numbers as the CPU integer ops, so a
+    trace taken on a GPU compares with one taken on a CPU; invariant to the order of the rows."""
+    from skyrl_isoexec_b200.debug import thash
+
+    torch.manual_seed(2)
+    x = torch.randn(37, 5, 129).to(dtype)
+    x[3, 0, 0], x[4, 1, 1] = 0.0, -0.0
+    xg = x.to(DEV)
+    for k in thash.LADDER:
+        assert torch.equal(thash.row_digests(xg, k).cpu(), thash.row_digests(x, k)), k
+    assert thash.ladder(xg) == thash.ladder(x) and thash.row_ladder(xg) == thash.row_ladder(x)
+    perm = torch.randperm(37)
+    assert thash.ladder(xg[perm.to(DEV)]) == thash.ladder(xg)
+    y = xg.clone()
+    y.view(torch.int16 if dtype == torch.bfloat16 else torch.int32)[5, 2, 7] ^= 1      # flip the last mantissa bit of one element
+    la, lb = thash.ladder(xg), thash.ladder(y)
+    assert la["0"] != lb["0"] and la["1"] == lb["1"]

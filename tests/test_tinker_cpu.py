@@ -60,3 +60,51 @@ def test_tinker_training_loop_over_http(tmp_path):
             cl._post("get_info", {"model_id": mid})
     finally:
         srv.shutdown()
+
+
+def test_tinker_checkpoint_archive_download_telemetry_and_restart(tmp_path):
+    """Saves are recorded, can be packed and downloaded; telemetry counts requests; a front end restarted on the same
+    database file rebuilds the model from its last save and keeps serving it."""
+    import hashlib
+    import io
+    import json
+    import tarfile
+    import urllib.request
+
+    db = str(tmp_path / "t.db")
+    srv = TinkerServer(db_path=db, device="cpu").start()
+    try:
+        cl = TinkerClient(srv.url)
+        mid = cl.create_model(base_model="tiny-qwen3", lr=3e-3)
+        data = [{"prompt_ids": [5, 6, 7], "response_ids": [8, 9, 10, 11]}]
+        cl.call("forward_backward", model_id=mid, data=data, loss_fn="cross_entropy")
+        cl.call("optim_step", model_id=mid)
+        path = str(tmp_path / "w1.pt")
+        cl.call("save_weights", model_id=mid, path=path)
+        want = cl.call("forward", model_id=mid, data=data)["logprobs"]
+        cks = cl._post("list_checkpoints", {"model_id": mid})["checkpoints"]
+        assert len(cks) == 1 and cks[0]["path"] == path and cks[0]["step"] == 1 and cks[0]["bytes"] > 0 and cks[0]["exists"]
+        with pytest.raises(RuntimeError):
+            cl._post("checkpoint_archive", {"model_id": mid, "path": str(tmp_path / "not_a_save.pt")})     # only recorded saves are served
+        arc = cl._post("checkpoint_archive", {"model_id": mid, "path": path})
+        with urllib.request.urlopen(srv.url + arc["download"]) as r:
+            blob = r.read()
+        assert len(blob) == arc["bytes"] and hashlib.sha256(blob).hexdigest() == arc["sha256"]
+        with tarfile.open(fileobj=io.BytesIO(blob), mode="r:gz") as tf:
+            assert tf.getnames() == ["w1.pt"]
+        with urllib.request.urlopen(srv.url + "/api/v1/telemetry") as r:
+            tel = json.loads(r.read())
+        assert tel["requests"]["forward_backward"]["count"] == 1 and tel["requests"]["save_weights"]["failed"] == 0
+        assert tel["queue_depth"] == 0 and tel["models"] == 1 and tel["requests"]["optim_step"]["latency_s_max"] > 0
+    finally:
+        srv.shutdown()
+    srv2 = TinkerServer(db_path=db, device="cpu").start()
+    try:
+        assert srv2.recovered["models"] == [mid]
+        cl2 = TinkerClient(srv2.url)
+        got = cl2.call("forward", model_id=mid, data=data)["logprobs"]
+        assert got == want                                   # the rebuilt model carries the saved weights
+        info = cl2._post("get_info", {"model_id": mid})
+        assert info["step"] == 1
+    finally:
+        srv2.shutdown()

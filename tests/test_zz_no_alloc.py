@@ -64,6 +64,28 @@ def test_noalloc_reduce_matches_regular_entry_point_twice_in_a_row():
     assert out.item() == 5002.0
 
 
+def test_noalloc_reduce_of_bf16_squares_and_of_an_empty_input():
+    lib, fn = _bind()
+    dev = "cuda"
+    torch.manual_seed(1)
+    x = torch.randn(123_457, device=dev).bfloat16()
+    out = torch.full((1,), float("nan"), device=dev)
+    assert fn(x.data_ptr(), x.numel(), 0, 1, out.data_ptr(), 0, _native.stream()) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(out.view(torch.int32), _reference(lib, x, True).view(torch.int32))
+    ref64 = (x.double() ** 2).sum().item()
+    assert abs(out.item() - ref64) <= 1e-4 * ref64
+    # no elements: the output is set to zero, or left alone when accumulating; the input pointer is not read
+    out = torch.tensor([7.5], device=dev)
+    assert fn(None, 0, 1, 0, out.data_ptr(), 1, _native.stream()) == 0
+    torch.cuda.synchronize()
+    assert out.item() == 7.5
+    assert fn(None, 0, 1, 0, out.data_ptr(), 0, _native.stream()) == 0
+    torch.cuda.synchronize()
+    assert out.item() == 0.0
+    assert fn(x.data_ptr(), -1, 0, 0, out.data_ptr(), 0, _native.stream()) != 0
+
+
 def test_noalloc_reduce_rejects_oversized_input():
     lib, fn = _bind()
     limit = lib.ix_reduce_sum_noalloc_max_elems()
