@@ -462,7 +462,8 @@ IX_API int ix_rmsnorm(const void* x, const void* res, const void* w, void* y, vo
   auto RO = static_cast<__nv_bfloat16*>(res_out);
   auto RS = static_cast<float*>(rstd_out);
   if (rows <= 1024 && N <= 8192) {
-    // few rows: a CTA per row (more threads per row, one memory round trip); same bits as the warp-per-row kernel
+    // few rows: a CTA per row (more threads per row, one memory round trip); same bits as the warp-per-row kernel.
+    // At thousands of rows this form measured 2x slower than the warp-per-row kernel (16384 x 4096: 180 us against 94 us)
     if (res) {
       if (zero_centered) IX_CUDA(ixh::launch_pdl(rmsnorm_cta_row_kernel<true, true>, dim3(rows), dim3(128), 0, s, X, R, W, Y, RO, RS, N, eps, ldx, ldy));
       else IX_CUDA(ixh::launch_pdl(rmsnorm_cta_row_kernel<true, false>, dim3(rows), dim3(128), 0, s, X, R, W, Y, RO, RS, N, eps, ldx, ldy));

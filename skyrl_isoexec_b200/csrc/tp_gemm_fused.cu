@@ -60,6 +60,10 @@ struct TpParams {
   const uint32_t* epoch_word;
   long long stage_half;         // floats per staging half
   long long flags_half;         // flags per half
+  // LOCAL: an fp32 [M, ld_add] tensor added to the folded tile before the store (the lower half of a leaf tree that was
+  // computed by an earlier launch: out = lower + fold(this launch's leaves), the root of the same balanced tree)
+  const float* addend;
+  int ld_add;
 };
 
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
@@ -394,6 +398,17 @@ tp_gemm_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         const int col0 = n_blk * BN + c * CW;
         if (p.mode == TP_LOCAL || p.mode == TP_AG) {
           if (row < M) {
+            if (p.addend != nullptr) {
+              const float4* ad = reinterpret_cast<const float4*>(p.addend + static_cast<size_t>(row) * p.ld_add + col0);
+#pragma unroll
+              for (int j = 0; j < CW / 4; ++j) {
+                const float4 a = __ldcs(ad + j);
+                f[4 * j] = __fadd_rn(a.x, f[4 * j]);
+                f[4 * j + 1] = __fadd_rn(a.y, f[4 * j + 1]);
+                f[4 * j + 2] = __fadd_rn(a.z, f[4 * j + 2]);
+                f[4 * j + 3] = __fadd_rn(a.w, f[4 * j + 3]);
+              }
+            }
             if (p.out_f32) {
               float* dst = static_cast<float*>(c_local) + static_cast<size_t>(row) * ldc + col0;
 #pragma unroll
@@ -597,7 +612,10 @@ static int tp_gemm_fused_impl(const void* A, const void* B, void* c_local, int M
                             int mode, int leaves, int bn, int out_f32, int rank, int W, unsigned epoch,
                             const long long* stage, const long long* flags, const long long* peer_out, const long long* done,
                             void* local_ctr, const void* a_local, int lda_local, int m_local, void* stream,
-                            const void* epoch_word, long long stage_half, long long flags_half) {
+                            const void* epoch_word, long long stage_half, long long flags_half, const void* addend = nullptr,
+                            int ld_add = 0) {
+  if (addend != nullptr && (mode != TP_LOCAL || (ld_add & 3)))
+    return ixh::fail(ixh::IX_EARG, "tp_gemm: an addend is taken by the single-rank leaf-tree GEMM only (ld_add a multiple of 4)");
   if (epoch_word != nullptr && mode != TP_AR1)
     return ixh::fail(ixh::IX_EARG, "tp_gemm: a device epoch word (graph capture) is supported by the one-shot all-reduce only");
   if (M <= 0 || N <= 0 || K <= 0) return ixh::fail(ixh::IX_EARG, "tp_gemm: empty problem");
@@ -623,6 +641,7 @@ static int tp_gemm_fused_impl(const void* A, const void* B, void* c_local, int M
   p.a_local = a_local, p.lda_local = lda_local, p.m_local = m_local > 0 ? m_local : BM;
   p.rank = rank, p.W = W, p.mode = mode, p.out_f32 = out_f32, p.epoch = epoch;
   p.epoch_word = static_cast<const uint32_t*>(epoch_word), p.stage_half = stage_half, p.flags_half = flags_half;
+  p.addend = static_cast<const float*>(addend), p.ld_add = ld_add;
   int a_rows = (M + 7) & ~7;
   if (a_rows > BM) a_rows = BM;
   CUtensorMap tmA, tmA2, tmB;
@@ -650,6 +669,15 @@ IX_API int ix_tp_gemm_fused(const void* A, const void* B, void* c_local, int M, 
                             void* local_ctr, const void* a_local, int lda_local, int m_local, void* stream) {
   return tp_gemm_fused_impl(A, B, c_local, M, N, K, lda, ldb, ldc, mode, leaves, bn, out_f32, rank, W, epoch, stage, flags, peer_out,
                             done, local_ctr, a_local, lda_local, m_local, stream, nullptr, 0, 0);
+}
+
+// Single-rank leaf-tree GEMM whose folded tile is added to `addend` (fp32 [M, ld_add]) before the store: the upper half
+// of a tree whose lower half an earlier launch left in `addend`. Two launches of 4 leaves with 128-wide tiles are the
+// 8-leaf tree, bit for bit, at twice the tile width the 8 accumulators of one launch would allow.
+IX_API int ix_leaftree_gemm_add(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc, int leaves,
+                                int bn, int out_f32, const void* addend, int ld_add, void* stream) {
+  return tp_gemm_fused_impl(A, B, C, M, N, K, lda, ldb, ldc, TP_LOCAL, leaves, bn, out_f32, 0, 1, 0, nullptr, nullptr, nullptr, nullptr,
+                            nullptr, nullptr, 0, 0, stream, nullptr, 0, 0, addend, ld_add);
 }
 
 // One-shot GEMM -> all-reduce in a form that a CUDA graph can record: the epoch of the call is

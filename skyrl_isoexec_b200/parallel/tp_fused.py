@@ -44,6 +44,7 @@ def _sig(lib):
     lib.ix_tp_gemm_ar1_graph.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p] + [C.c_int] * 6 + [C.c_int] * 5 + \
         [C.c_void_p, C.c_uint, C.c_void_p, C.c_void_p, C.c_longlong, C.c_longlong, C.c_void_p]
     lib.ix_tp_set_epoch.argtypes = [C.c_void_p, C.c_uint, C.c_void_p]
+    lib.ix_leaftree_gemm_add.argtypes = [C.c_void_p] * 3 + [C.c_int] * 9 + [C.c_void_p, C.c_int, C.c_void_p]
     lib.ix_leaf_split_bn.argtypes = [C.c_int] * 4
     lib.ix_leaf_split_gemm.argtypes = [C.c_void_p] * 3 + [C.c_int] * 9 + [C.c_void_p]
     lib._tp_sig = True
@@ -82,6 +83,20 @@ def leaftree_gemm_fused(x: torch.Tensor, w: torch.Tensor, leaves: int, out_f32: 
     if split:
         _native.check(lib.ix_leaf_split_gemm(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, x.stride(0), w.stride(0), N,
                                              leaves, bn or 0, int(out_f32), _native.stream()), "ix_leaf_split_gemm")
+        return out
+    if leaves == 8 and bn is None and M > 256 and N % 128 == 0 and K % 512 == 0:
+        # training sizes: 8 accumulators in one CTA's TMEM leave 64 columns each. The two halves of the tree as two
+        # launches of 4 leaves keep 128-wide tiles; the second adds the first's fp32 result before its store, which is
+        # the root of the same balanced tree
+        half = K // 2
+        esz = x.element_size()
+        low = torch.empty(M, N, dtype=torch.float32, device=x.device)
+        _native.check(lib.ix_tp_gemm_fused(x.data_ptr(), w.data_ptr(), low.data_ptr(), M, N, half, x.stride(0), w.stride(0), N,
+                                           TP_LOCAL, 4, 128, 1, 0, 1, 0, None, None, None, None, None, None, 0, 0,
+                                           _native.stream()), "ix_tp_gemm_fused")
+        _native.check(lib.ix_leaftree_gemm_add(x.data_ptr() + half * esz, w.data_ptr() + half * esz, out.data_ptr(), M, N, half,
+                                               x.stride(0), w.stride(0), N, 4, 128, int(out_f32), low.data_ptr(), N,
+                                               _native.stream()), "ix_leaftree_gemm_add")
         return out
     bn = bn or pick_bn(M, N, leaves)
     _native.check(lib.ix_tp_gemm_fused(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, x.stride(0), w.stride(0), N,
