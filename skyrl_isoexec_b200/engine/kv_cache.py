@@ -15,9 +15,13 @@ from ..ops.functional import PAGE
 
 
 class PageAllocator:
+    """Free list with reference counts: a page shared by several sequences (the common prompt of the samples of one
+    request group) returns to the free list when its last holder releases it."""
+
     def __init__(self, num_pages: int):
         self.num_pages = num_pages
         self.free = list(range(num_pages - 1, -1, -1))
+        self.refs = [0] * num_pages
 
     def can_alloc(self, n: int) -> bool:
         return len(self.free) >= n
@@ -25,10 +29,22 @@ class PageAllocator:
     def alloc(self, n: int) -> list[int]:
         if len(self.free) < n:
             raise RuntimeError(f"out of KV pages: want {n}, have {len(self.free)}")
-        return [self.free.pop() for _ in range(n)]
+        out = [self.free.pop() for _ in range(n)]
+        for p in out:
+            self.refs[p] = 1
+        return out
+
+    def share(self, pages: list[int]) -> None:
+        for p in pages:
+            assert self.refs[p] > 0, f"page {p} is not in use"
+            self.refs[p] += 1
 
     def release(self, pages: list[int]) -> None:
-        self.free.extend(reversed(pages))
+        for p in reversed(pages):
+            self.refs[p] -= 1
+            assert self.refs[p] >= 0, f"page {p} released twice"
+            if self.refs[p] == 0:
+                self.free.append(p)
 
     @property
     def num_free(self) -> int:

@@ -34,6 +34,7 @@ class EngineConfig:
     seed: int = 0
     enable_prefix_caching: bool = False  # the contract pins this off (state claim engine_prefix_cache)
     use_cuda_graph: bool = True
+    share_prompt_pages: bool = True      # samples of one prompt share its full KV pages (not a cache: freed with the requests)
 
 
 @dataclass
@@ -49,6 +50,10 @@ class Sequence:
     stop_reason: str | None = None
     request_index: int = 0
     arrival: float = 0.0
+    # Samples of one prompt: a sequence whose prompt equals an earlier one's of the same generate() call takes the
+    # leader's full prompt pages (all but the page holding the last prompt token) instead of recomputing them.
+    leader: "Sequence | None" = None
+    shared_tokens: int = 0
 
     @property
     def tokens(self) -> list[int]:
@@ -80,6 +85,7 @@ class Scheduler:
         self.waiting: deque[Sequence] = deque()
         self.running: list[Sequence] = []
         self.preemptions = 0
+        self.shared_prompt_tokens = 0       # prompt tokens taken from a leader's pages instead of being prefilled
 
     def add(self, seq: Sequence) -> None:
         self.waiting.append(seq)
@@ -100,6 +106,7 @@ class Scheduler:
         self.cache.allocator.release(seq.pages)
         seq.pages = []
         seq.num_computed = 0
+        seq.leader = None
         self.waiting.appendleft(seq)
 
     def schedule(self):
@@ -137,12 +144,26 @@ class Scheduler:
                 continue
             prefill.append((s, s.num_computed, n))
             budget -= n
-        while self.waiting and budget > 0 and len(self.running) < self.cfg.max_num_seqs:
-            s = self.waiting[0]
+        i = 0
+        while i < len(self.waiting) and budget > 0 and len(self.running) < self.cfg.max_num_seqs:
+            s = self.waiting[i]
+            if s.leader is not None:
+                ld = s.leader
+                if s.pages or s.num_computed or ld.finished or len(ld.pages) * PAGE < s.shared_tokens:
+                    s.leader = None                      # the leader's pages are gone (or s was preempted): on its own
+                elif ld.num_computed < s.shared_tokens:
+                    i += 1                               # the shared prompt pages are not written yet: later sequences first
+                    continue
+                else:
+                    s.pages = list(ld.pages[:s.shared_tokens // PAGE])
+                    self.cache.allocator.share(s.pages)
+                    s.num_computed = s.shared_tokens
+                    s.leader = None
+                    self.shared_prompt_tokens += s.shared_tokens
             n = min(s.length - s.num_computed, budget)
             if not self._ensure_pages(s, s.num_computed + n):
                 break
-            self.waiting.popleft()
+            del self.waiting[i]
             self.running.append(s)
             prefill.append((s, s.num_computed, n))
             budget -= n
@@ -510,6 +531,16 @@ class LLMEngine:
             raise RuntimeError("engine is asleep; call wake_up() first")
         plist = params if isinstance(params, list) else [params] * len(prompts)
         seqs = [self.add_request(p, sp, i) for i, (p, sp) in enumerate(zip(prompts, plist))]
+        if self.cfg.share_prompt_pages and not self.mcfg.has_gdn:
+            # the n samples of a prompt: K/V rows do not depend on the batch they are computed in, so the later samples
+            # read the first one's full prompt pages (same bits) and prefill only the page with the last prompt token
+            leaders: dict = {}
+            for s in seqs:
+                key = tuple(s.prompt_ids)
+                ld = leaders.setdefault(key, s)
+                shared = ((len(s.prompt_ids) - 1) // PAGE) * PAGE
+                if ld is not s and shared > 0:
+                    s.leader, s.shared_tokens = ld, shared
         while True:
             if self.paused:
                 time.sleep(0.001)

@@ -199,6 +199,7 @@ class PeerPullResharder(_Base):
 
         self.lib = _native.lib()
         self.lib.ix_reshard_pull.argtypes = [C.c_void_p, C.c_int, C.c_void_p]
+        self.lib.ix_reshard_desc_bytes.restype = C.c_int
         self.lib.ix_reshard_pull.restype = C.c_int
         fmt = "<QQqqqqii"
         assert self.lib.ix_reshard_desc_bytes() == struct.calcsize(fmt), "descriptor layout differs between host and kernel"

@@ -882,3 +882,50 @@ def test_model_resolution_from_a_hf_style_directory_round_trips(tmp_path):
         assert torch.equal(dst.store.flat, src.store.flat)
     with pytest.raises(KeyError):
         get_config(str(tmp_path / "nowhere"))
+
+
+def test_samples_of_one_prompt_share_its_full_kv_pages_with_the_same_bits():
+    """The n samples of a prompt take the first sample's full prompt pages instead of recomputing them: greedy outputs and
+    logprobs equal the unshared run bit for bit, sampled-token logprobs equal the trainer's forward, fewer tokens are
+    prefilled, every page is free afterwards, and a pool tight enough to preempt still ends clean."""
+    from skyrl_isoexec_b200.core.testing import count_bit_mismatches
+    from skyrl_isoexec_b200.engine.llm_engine import EngineConfig, LLMEngine
+    from skyrl_isoexec_b200.engine.sampler import SamplingParams
+    from skyrl_isoexec_b200.models.config import get_config
+    from skyrl_isoexec_b200.models.decoder import DecoderLM
+    from skyrl_isoexec_b200.train.batch import TrainingInputBatch, build_sequences
+    from skyrl_isoexec_b200.train.policy_worker import PolicyWorker, WorkerConfig
+
+    cfg = get_config("tiny-qwen3")
+    model = DecoderLM(cfg, device="cpu", seed=3)
+    g = torch.Generator().manual_seed(5)
+    base = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (380, 250, 129)]
+    prompts = [p for p in base for _ in range(3)]                 # 3 samples each; 129 tokens: one full page to share
+
+    def run(share, pages, sp):
+        eng = LLMEngine(model, EngineConfig(max_num_seqs=9, num_kv_pages=pages, max_num_batched_tokens=512, share_prompt_pages=share))
+        outs = eng.generate(prompts, sp)
+        assert eng.cache.allocator.num_free == pages and not any(eng.cache.allocator.refs)
+        return eng, outs
+
+    greedy = SamplingParams(max_generate_length=10, ignore_eos=True, temperature=0.0)
+    e0, o0 = run(False, 40, greedy)
+    e1, o1 = run(True, 40, greedy)
+    assert [o.response_ids for o in o0] == [o.response_ids for o in o1]
+    assert [o.response_logprobs for o in o0] == [o.response_logprobs for o in o1]
+    assert e1.scheduler.shared_prompt_tokens == 2 * (256 + 128 + 128) and e0.scheduler.shared_prompt_tokens == 0
+    assert e1.stats["prefill_tokens"] == e0.stats["prefill_tokens"] - e1.scheduler.shared_prompt_tokens
+    # sampled rollout with sharing: the trainer's forward gives the same logprob bits
+    e2, o2 = run(True, 40, SamplingParams(max_generate_length=12, ignore_eos=True))
+    seq, att, rmask = build_sequences([o.prompt_ids for o in o2], [o.response_ids for o in o2])
+    batch = TrainingInputBatch({"sequences": seq, "attention_mask": att, "response_mask": rmask})
+    lp = PolicyWorker(model, WorkerConfig(max_tokens_per_microbatch=1024)).forward(batch)
+    ro = torch.zeros_like(lp)
+    for i, o in enumerate(o2):
+        ro[i, :len(o.response_logprobs)] = torch.tensor(o.response_logprobs)
+    assert count_bit_mismatches((lp * rmask).contiguous(), (ro * rmask).contiguous()) == 0
+    # a pool that cannot hold all nine sequences once the longest cross a page boundary (19 pages with sharing, 27
+    # without): preemptions happen, reference counts still balance, the greedy outputs do not change
+    e3, o3 = run(True, 17, greedy)
+    assert e3.scheduler.preemptions > 0
+    assert [o.response_ids for o in o3] == [o.response_ids for o in o0]
