@@ -108,7 +108,7 @@ class PipelinePolicyWorker(PolicyWorker):
                 x, res = y
                 self.p2p.send(x, res if res is not None else torch.zeros_like(x), self.p2p.next)
             else:
-                lp, _ = self._logprobs(mb, y, False)
+                lp, _, _ = self._logprobs(mb, y, False)
                 flat = torch.zeros(len(mb.seq_index) * R, dtype=torch.float32, device=lp.device)
                 flat[mb.out_index.to(lp.device)] = lp
                 out[torch.tensor(mb.seq_index)] = flat.view(-1, R).cpu()

@@ -85,6 +85,7 @@ class InferenceEngineConfig:
     num_kv_pages: int = 0
     enforce_eager: bool = False
     enable_prefix_caching: bool = False
+    share_prompt_pages: bool = True     # the n samples of a prompt read one copy of its full KV pages (same bits; not a cache)
     weight_sync_backend: str = "nccl"   # nccl | gloo | cuda_ipc | shared
     run_engines_locally: bool = True
 
