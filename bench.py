@@ -51,6 +51,7 @@ def parse():
     ap.add_argument("--micro-tokens", type=int, default=8192)
     ap.add_argument("--tp", type=int, default=0, help="trainer tensor-parallel degree (0 = by GPU count: 1, 2, 4, 4)")
     ap.add_argument("--engine-tp", type=int, default=0, help="engine tensor-parallel degree (0 = by GPU count: 1, 1, 2, 2)")
+    ap.add_argument("--ep", type=int, default=1, help="expert-parallel degree (MoE models; trainer and engines share it, tp = 1)")
     ap.add_argument("--layout", default="named", choices=["named", "dp"], help="dp: plain data parallelism, engines on the trainer's weights")
     ap.add_argument("--keep-last-layers", type=int, default=-1,
                     help="layers not recomputed in the backward (uses spare HBM); -1 = as many as the first step's measured peak leaves room for")
@@ -127,6 +128,8 @@ def main():
     assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}"
     torch.cuda.set_device(local)
     _native.lib().ix_init()
+    if args.ep > 1:
+        args.tp, args.engine_tp, args.layout = 1, 1, "dp"
     if args.layout == "dp":
         args.tp = args.tp or 1
         args.engine_tp = args.engine_tp or args.tp
@@ -136,7 +139,7 @@ def main():
     if world > 1:
         from skyrl_isoexec_b200.models.config import get_config as _gc
 
-        ps = ParallelState.build(tp=args.tp, kv_rep=max(1, args.tp // _gc(args.model).num_kv_heads))
+        ps = ParallelState.build(tp=args.tp, ep=args.ep, kv_rep=max(1, args.tp // _gc(args.model).num_kv_heads))
     else:
         ps = ParallelState.single()
     P, S = args.prompts_per_gpu * args.tp, args.samples
@@ -234,7 +237,7 @@ def main():
             "config": {"model": args.model + (f"[layers={args.layers} INVALID-DEBUG]" if args.layers else ""),
                        "global_batch": P * S * ps.dp, "prompts": P * ps.dp, "samples_per_prompt": S,
                        "prompt_len": args.prompt_len, "seq_len": args.prompt_len + args.response_len,
-                       "parallelism": (f"dp{ps.dp}" + (f"xtp{args.tp}" if args.tp > 1 else "")) if world > 1 else "single",
+                       "parallelism": (f"dp{ps.dp}" + (f"xtp{args.tp}" if args.tp > 1 else "") + (f"xep{args.ep}" if args.ep > 1 else "")) if world > 1 else "single",
                        "engine": (f"colocated, {world // args.engine_tp} engines x TP{args.engine_tp}, own layout, resharding weight sync every step"
                                   if trainer.separate_engine else f"colocated, {world // args.tp} engines x TP{args.tp} on the trainer's weights"),
                        "pik_leaves": mo.get("pik_leaves", 0),
