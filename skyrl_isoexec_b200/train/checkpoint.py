@@ -10,8 +10,8 @@
 A shard file holds the rank's slice of the sharded state dict with the keys ``model`` /
 ``optimizer`` / ``lr_scheduler`` / ``rng``. The files follow the naming of torch's distributed
 checkpoints but are ``torch.save`` pickles with a JSON index: they are NOT readable by
-``torch.distributed.checkpoint`` or Megatron's dist-checkpointing tools (use the HF export for
-interchange). A critic, when there is one, is saved the same way under ``critic/``. ``metadata.json`` records every parameter's full
+``torch.distributed.checkpoint`` or Megatron's dist-checkpointing tools; for interchange there are the
+torch.distributed.checkpoint export (``train/dcp_checkpoint.py``, ``trainer.dcp_save_interval``) and the HF export. A critic, when there is one, is saved the same way under ``critic/``. ``metadata.json`` records every parameter's full
 shape, shard dim and sections so a checkpoint written at one TP degree loads at another
 (parameters are reassembled to full shape and re-sliced). The step directory is written under
 a temporary name and renamed, and ``latest_ckpt_global_step.txt`` is replaced last, so a crash
@@ -118,6 +118,8 @@ def cleanup_old_checkpoints(ckpt_path: str, max_to_keep: int) -> list[int]:
 
 
 def validate_checkpoint_dir(path: str) -> None:
+    if os.path.exists(os.path.join(path, ".metadata")):
+        return                     # a torch.distributed.checkpoint directory (train/dcp_checkpoint.py)
     if not _STEP_RE.match(os.path.basename(os.path.normpath(path))):
         raise ValueError(f"resume_path must be a global_step_N directory, got {path!r}")
     for need in ("policy/metadata.json", "data.pt", "trainer_state.pt"):

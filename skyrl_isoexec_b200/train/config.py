@@ -166,6 +166,7 @@ class TrainerConfig:
     resume_path: str = ""
     export_path: str = ""
     hf_save_interval: int = -1
+    dcp_save_interval: int = -1         # every N steps: a torch.distributed.checkpoint directory under export_path/global_step_N/dcp
     logger: str = "console"
     project_name: str = "skyrl_isoexec_b200"
     run_name: str = "run"

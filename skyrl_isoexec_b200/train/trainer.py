@@ -820,6 +820,8 @@ class RayPPOTrainer:
                         self.eval()
                     if t.export_path and t.hf_save_interval > 0 and self.global_step % t.hf_save_interval == 0:
                         self.export_hf()
+                    if t.export_path and t.dcp_save_interval > 0 and self.global_step % t.dcp_save_interval == 0:
+                        self.export_dcp()
                     if 0 < t.num_steps <= self.global_step or self.control.should_stop:
                         done = True
                         break
@@ -876,6 +878,15 @@ class RayPPOTrainer:
         hf_export.save_hf(self.policy.model, path, write=self.rank == 0)
         return path if self.rank == 0 else None
 
+    def export_dcp(self) -> str:
+        """Policy weights and optimizer state at full shapes as a ``torch.distributed.checkpoint`` directory
+        (``export_path/global_step_N/dcp``), readable by torch's own tools and loadable at any layout
+        (``trainer.resume_mode=from_path`` with that directory resumes weights, optimizer and the step counter)."""
+        from . import dcp_checkpoint
+
+        path = os.path.join(self.cfg.trainer.export_path, f"global_step_{self.global_step}", "dcp")
+        return dcp_checkpoint.save_dcp(self.policy, path, self.ps, step=self.global_step)
+
     # ------------------------------------------------------------------ checkpoints
     def save_checkpoints(self) -> str:
         t = self.cfg.trainer
@@ -892,6 +903,13 @@ class RayPPOTrainer:
         path = ckpt.resolve_resume_path(t.ckpt_path, t.resume_mode, t.resume_path)
         if path is None:
             return 0
+        if os.path.exists(os.path.join(path, ".metadata")):
+            # a torch.distributed.checkpoint directory: weights, optimizer state and the step; the data order restarts
+            from . import dcp_checkpoint
+
+            info = dcp_checkpoint.load_dcp(self.policy, path)
+            self.global_step = int(info["global_step"])
+            return self.global_step
         data_state, trainer_state = ckpt.load_checkpoint(path, self.policy, self.ps)
         self.loader.load_state_dict(data_state)
         self.global_step = int(trainer_state["global_step"])

@@ -263,3 +263,27 @@ def test_forward_gate_ignores_observation_tokens_of_a_multi_turn_rollout(tmp_pat
     batch.metadata["check_rollout_bits"] = True
     out = tr.policy.forward_backward(batch)
     assert out["rollout_bits"]["mismatches"] == 0 and out["rollout_bits"]["tokens"] == float((batch["loss_mask"] > 0).sum())
+
+
+def test_trainer_exports_a_dcp_checkpoint_and_resumes_from_it(tmp_path):
+    """``trainer.dcp_save_interval`` writes a torch.distributed.checkpoint directory; ``resume_mode=from_path`` on it brings
+    back the weights, the optimizer state and the step counter."""
+    from skyrl_isoexec_b200.train.config import SkyRLTrainConfig
+    from skyrl_isoexec_b200.train.trainer import RayPPOTrainer
+
+    ov = ["trainer.policy.model=tiny-qwen3", "trainer.train_batch_size=4", "trainer.policy_mini_batch_size=4",
+          "generator.n_samples_per_prompt=2", "generator.sampling_params.max_generate_length=8", "data.synthetic_prompt_len=12",
+          "trainer.num_steps=2", "trainer.logger=jsonl", f"trainer.export_path={tmp_path}/export", "trainer.dcp_save_interval=2",
+          f"trainer.ckpt_path={tmp_path}/ckpt", "trainer.ckpt_interval=0", "environment.env_class=even_tokens"]
+    tr = RayPPOTrainer(SkyRLTrainConfig.from_cli_overrides(ov), device="cpu")
+    tr.build_models()
+    tr.train()
+    d = tmp_path / "export" / "global_step_2" / "dcp"
+    assert (d / ".metadata").exists()
+    tr2 = RayPPOTrainer(SkyRLTrainConfig.from_cli_overrides(ov + ["trainer.resume_mode=from_path", f"trainer.resume_path={d}",
+                                                                  "trainer.policy.seed=99"]), device="cpu")
+    tr2.build_models()
+    assert tr2.load_checkpoints() == 2 and tr2.policy.opt.step_count == tr.policy.opt.step_count
+    for (n, a), (_, b) in zip(tr.policy.model.named_weights(), tr2.policy.model.named_weights()):
+        assert torch.equal(a, b), n
+    assert torch.equal(tr.policy.opt.exp_avg_sq, tr2.policy.opt.exp_avg_sq)
