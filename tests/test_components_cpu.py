@@ -929,3 +929,69 @@ def test_samples_of_one_prompt_share_its_full_kv_pages_with_the_same_bits():
     e3, o3 = run(True, 17, greedy)
     assert e3.scheduler.preemptions > 0
     assert [o.response_ids for o in o3] == [o.response_ids for o in o0]
+
+
+def test_sft_chat_records_loss_masks_eval_callbacks_export_and_cache(tmp_path):
+    """Chat records with tool calls are tokenized with assistant-only loss masks (all turns or the last one), cached on
+    disk, trained on; the held-out loss falls; callbacks fire; the Hugging Face export is written at the end."""
+    from skyrl_isoexec_b200.train import sft_data
+    from skyrl_isoexec_b200.train.policy_worker import OptimizerConfig
+
+    class ByteTok:
+        vocab_size = 256
+        name_or_path = "bytes"
+
+        def encode(self, text):
+            return list(text.encode())
+
+    tok = ByteTok()
+    chat = {"messages": [{"role": "system", "content": "be brief"}, {"role": "user", "content": "2+2?"},
+                         {"role": "assistant", "content": "", "tool_calls": '{"function": {"name": "calc", "arguments": "{\\"e\\": \\"2+2\\"}"}}'},
+                         {"role": "tool", "name": "calc", "content": "4"}, {"role": "assistant", "content": "four"}],
+            "tools": '{"name": "calc"}'}
+    row_all = sft_data.tokenize_chat(chat, tok, 4096, "all")
+    row_last = sft_data.tokenize_chat(chat, tok, 4096, "last")
+    full = row_all["prompt_ids"] + row_all["response_ids"]
+    assert full == row_last["prompt_ids"] + row_last["response_ids"]              # same sequence, different split
+    assert bytes(row_last["response_ids"]).decode() == "<|assistant|>\nfour<|end|>\n" and all(row_last["loss_mask"])
+    text = bytes(row_all["response_ids"]).decode()
+    masked_out = bytes(t for t, m in zip(row_all["response_ids"], row_all["loss_mask"]) if not m).decode()
+    assert text.startswith("<|assistant|>") and "calc" in text and masked_out == "<|tool|>\n4<|end|>\n"   # only the tool turn carries no loss
+    assert sft_data.tokenize_chat({"messages": [{"role": "user", "content": "x"}]}, tok, 4096) is None      # nothing to learn
+    recs = [chat, {"instruction": "add", "input": "1 2", "output": "3"}, {"prompt_ids": [1, 2, 3], "response_ids": [4, 5]},
+            {"instruction": "long", "output": "y" * 5000}]
+    rows, st = sft_data.tokenize_dataset(recs, tok, 512, "all", str(tmp_path / "cache"))
+    assert st["rows"] == 3 and st["dropped"] == 1 and st["cache"] == "miss" and st["len_max"] <= 512
+    assert sft_data.tokenize_dataset(recs, tok, 512, "all", str(tmp_path / "cache"))[1]["cache"] == "hit"
+    assert sft_data.tokenize_dataset(recs, tok, 512, "last", str(tmp_path / "cache"))[1]["cache"] == "miss"  # another key
+
+    events = []
+
+    class Spy:
+        def on_train_begin(self, **kw):
+            events.append("begin")
+
+        def on_step_end(self, metrics, **kw):
+            events.append(("step", round(metrics["sft/loss"], 3)))
+
+        def on_eval_end(self, metrics, **kw):
+            events.append(("eval", metrics["eval/loss"]))
+
+        def on_train_end(self, **kw):
+            events.append("end")
+
+    train = [dict(chat), {"instruction": "add", "input": "1 2", "output": "3"}] * 4
+    cfg = SFTConfig(model="tiny-qwen3", batch_size=4, num_steps=6, epochs=10, max_seq_len=512, train_on="all", logger="jsonl",
+                    eval_interval=3, export_path=str(tmp_path / "export"), tokenize_cache_dir=str(tmp_path / "cache"),
+                    optimizer=OptimizerConfig(lr=2e-3))
+    tr = SFTTrainer(cfg, train, device="cpu", tokenizer=tok, eval_examples=[chat], callbacks=[Spy()])
+    assert tr.data_stats["rows"] == 8
+    tr.train()
+    evals = [e[1] for e in events if isinstance(e, tuple) and e[0] == "eval"]
+    assert events[0] == "begin" and events[-1] == "end" and len(evals) == 3 and evals[-1] < evals[0]
+    assert sum(1 for e in events if isinstance(e, tuple) and e[0] == "step") == 6
+    assert (tmp_path / "export" / "global_step_6" / "model.safetensors").exists()
+    # timing mode: synthetic rows, no data
+    tr2 = SFTTrainer(SFTConfig(model="tiny-qwen3", batch_size=2, max_seq_len=64, dummy_steps=2, logger="jsonl"), [], device="cpu")
+    tr2.train()
+    assert tr2.global_step == 2
