@@ -179,6 +179,8 @@ class InferenceServer:
             return 200, {"ok": True}
         if path == "/update_weights":
             return 200, self._update_weights(body)
+        if path == "/update_weights_layerwise":
+            return 200, self._update_weights_layerwise(body)
         if path == "/shutdown":
             threading.Thread(target=self.shutdown, daemon=True).start()
             return 200, {"ok": True}
@@ -225,6 +227,34 @@ class InferenceServer:
             n = load_weights(self.llm.model, sd.items())
             self.llm.reset_prefix_cache()
         return {"ok": True, "tensors": n}
+
+    def _update_weights_layerwise(self, body: dict) -> dict:
+        """Reload from a ``.safetensors`` file with this model's parameter names, a group of layers at a time: only
+        ``layers_per_step`` layers' tensors are held on the host at once (a full ``torch.load`` holds the whole model),
+        and full-shape tensors are cut to this engine's shard as they are read."""
+        from safetensors import safe_open
+
+        from ..sync.strategies import load_weights
+
+        per = max(1, int(body.get("layers_per_step", 4)))
+        with self._lock:
+            if self.llm.scheduler.has_work() and self._paused_mode is None:
+                raise RuntimeError("pause the server before updating weights")
+            n, steps, peak = 0, 0, 0
+            with safe_open(body["path"], framework="pt", device="cpu") as f:
+                groups: dict = {}
+                for k in f.keys():
+                    parts = k.split(".")
+                    g = int(parts[1]) // per if parts[0] == "layers" and len(parts) > 1 and parts[1].isdigit() else -1
+                    groups.setdefault(g, []).append(k)
+                for g in sorted(groups):
+                    held = {k: f.get_tensor(k) for k in groups[g]}
+                    peak = max(peak, sum(t.numel() * t.element_size() for t in held.values()))
+                    n += load_weights(self.llm.model, held.items())
+                    steps += 1
+                    del held
+            self.llm.reset_prefix_cache()
+        return {"ok": True, "tensors": n, "steps": steps, "peak_host_bytes": peak}
 
     def _encode(self, prompt):
         if isinstance(prompt, list) and (not prompt or isinstance(prompt[0], int)):

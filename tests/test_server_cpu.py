@@ -116,3 +116,74 @@ def test_tinker_backend_samples_through_an_external_server_and_trains_on_the_res
             assert got == s["logprobs"], "the external engine's logprobs are the trainer's, bit for bit"
     finally:
         srv.shutdown()
+
+
+def test_router_routes_pins_sessions_fans_out_control_and_survives_a_dead_backend(tmp_path):
+    """One address in front of two engine servers: conversations stick to a backend, a batch is split and joined in
+    order, control calls reach every backend, a layer-wise reload changes the weights of both, and a backend that went
+    away is skipped (and the call that found it dead is retried elsewhere)."""
+    import json
+    import urllib.request
+
+    from safetensors.torch import save_file
+
+    from skyrl_isoexec_b200.engine.router import Router
+
+    def call(url, path, body=None, headers=None):
+        req = urllib.request.Request(url + path, data=None if body is None else json.dumps(body).encode(),
+                                     method="GET" if body is None else "POST", headers={"Content-Type": "application/json", **(headers or {})})
+        try:
+            with urllib.request.urlopen(req, timeout=60) as r:
+                raw = r.read()
+                return r.status, (json.loads(raw) if r.headers.get("Content-Type", "").startswith("application/json") else raw.decode())
+        except urllib.error.HTTPError as e:
+            return e.code, json.loads(e.read())
+
+    e1, e2 = _engine(seed=0), _engine(seed=0)
+    group = ServerGroup([e1, e2])
+    urls = group.start()
+    router = Router(urls, probe_s=0.2, timeout_s=60).start()
+    try:
+        g = torch.Generator().manual_seed(1)
+        prompts = [torch.randint(0, 2048, (8,), generator=g).tolist() for _ in range(6)]
+        sp = {"max_generate_length": 5, "ignore_eos": True, "temperature": 0.0}
+        code, out = call(router.url, "/generate", {"prompt_token_ids": prompts, "sampling_params": sp})
+        assert code == 200 and len(out["response_ids"]) == 6
+        code, one = call(router.url, "/generate", {"prompt_token_ids": [prompts[4]], "sampling_params": sp})
+        assert one["response_ids"][0] == out["response_ids"][4]                     # split and joined in order
+        assert sorted(router.served.values()) == [2, 2] or sum(router.served.values()) == 3
+        # a conversation stays on one backend
+        before = dict(router.served)
+        for _ in range(3):
+            assert call(router.url, "/generate", {"prompt_token_ids": [prompts[0]], "sampling_params": sp, "session_id": "conv-7"})[0] == 200
+        assert call(router.url, "/generate", {"prompt_token_ids": [prompts[1]], "sampling_params": sp}, {"X-Session-Id": "conv-7"})[0] == 200
+        grown = [router.served[b] - before[b] for b in router.backends]
+        assert sorted(grown) == [0, 4]
+        # control plane: every backend, and a failure of one is a failure of the call
+        code, res = call(router.url, "/pause", {"mode": "keep"})
+        assert code == 200 and res["ok"] and len(res["backends"]) == 2
+        donor = DecoderLM(get_config("tiny-qwen3", max_position=512), seed=42)
+        wfile = str(tmp_path / "w.safetensors")
+        save_file({n: t.detach().clone().contiguous() for n, t in donor.named_weights()}, wfile)
+        code, res = call(router.url, "/update_weights_layerwise", {"path": wfile, "layers_per_step": 1})
+        assert code == 200 and all(r["reply"]["steps"] >= 3 and r["reply"]["tensors"] == len(list(donor.named_weights()))
+                                   for r in res["backends"].values())
+        total = sum(t.numel() * t.element_size() for _, t in donor.named_weights())
+        assert all(r["reply"]["peak_host_bytes"] < total for r in res["backends"].values())      # never the whole model at once
+        assert call(router.url, "/resume", {})[0] == 200
+        for e in (e1, e2):
+            assert all(torch.equal(a, b) for (_, a), (_, b) in zip(e.model.named_weights(), donor.named_weights()))
+        code, res = call(router.url, "/update_weights", {"path": str(tmp_path / "missing.pt")})
+        assert code == 502 and not res["ok"]
+        code, text = call(router.url, "/metrics")
+        assert code == 200 and "router_requests_served" in text and "isoexec_requests_served_total" in text
+        assert call(router.url, "/get_server_info")[1]["router"]["sessions"] == 1
+        # one backend goes away: the data plane keeps answering from the other
+        group.servers[0].shutdown()
+        dead = group.servers[0].url if hasattr(group.servers[0], "url") else urls[0]
+        for _ in range(4):
+            assert call(router.url, "/generate", {"prompt_token_ids": [prompts[2]], "sampling_params": sp})[0] == 200
+        assert router.healthy[dead.rstrip("/")] is False and call(router.url, "/health")[1]["healthy_backends"] == 1
+    finally:
+        router.shutdown()
+        group.shutdown()
