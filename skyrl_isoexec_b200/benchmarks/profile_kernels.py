@@ -2,7 +2,7 @@
 
     python skyrl_isoexec_b200/benchmarks/profile_kernels.py attn_decode | attn_prefill | gemm_large | gemm_decode | logprob | rmsnorm |
                                    glu_decode | moe_grouped | rmsnorm_decode | sampler | rmsnorm_bwd | attn_bwd | train_small |
-                                   gemm_bwd_dx | gemm_bwd_dw | moe_train | reshard | gdn_chunk | gated_outnorm
+                                   gemm_bwd_dx | gemm_bwd_dw | moe_train | reshard | gdn_chunk | gated_outnorm | small_train
 
 Each mode allocates well under 1 GB, launches the kernel a handful of times and exits.
 """
@@ -237,6 +237,60 @@ def main(mode: str = "attn_decode") -> None:
         w = (torch.randn(128, device=dev) * 0.1).bfloat16()
         for _ in range(4):
             F.gated_outnorm(o, z, w, 1e-6, True)
+    elif mode == "small_train":
+        # the small kernels of a training step at Qwen3-8B / 30B-A3B / hybrid sizes: router top-k, PPO loss forward +
+        # backward, clip-norm + AdamW over a flat buffer, GatedDeltaNet conv / gating / L2 norm. CUDA-event times printed.
+        from skyrl_isoexec_b200.models.config import get_config
+        from skyrl_isoexec_b200.models.decoder import DecoderLM
+        from skyrl_isoexec_b200.ops import gdn, moe
+        from skyrl_isoexec_b200.train import algorithms as alg
+        from skyrl_isoexec_b200.train.policy_worker import PolicyWorker, WorkerConfig
+
+        def timed(name, fn, n=4):
+            fn()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(n):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            print(f"{name}: {e0.elapsed_time(e1) / n * 1e3:.1f} us")
+
+        logits = torch.randn(8192, 128, device=dev)
+        timed("router_topk 8192 tokens x 128 experts, top-8", lambda: moe.router_topk_fwd(logits, 8, None, False, True))
+        acfg = alg.AlgorithmConfig()
+        loss_fn = alg.get_policy_loss("regular")
+        lp0 = torch.randn(64, 2048, device=dev) * 0.3 - 2
+        old, adv = lp0 + torch.randn_like(lp0) * 0.1, torch.randn(64, 2048, device=dev)
+        mask = (torch.rand(64, 2048, device=dev) > 0.1).float()
+
+        def ppo():
+            a = lp0.clone().requires_grad_()
+            loss, _ = loss_fn(a, old, adv, acfg, loss_mask=mask)
+            loss.backward()
+
+        timed("ppo_loss forward + backward, 64 x 2048 tokens (with the autograd call)", ppo)
+        cfg = get_config("qwen3-8b", dtype="bfloat16", num_layers=2, vocab_size=32768)
+        w = PolicyWorker(DecoderLM(cfg, device=dev, seed=0), WorkerConfig())
+        n = w.opt.n
+        w.opt.main_grad.normal_()
+
+        def adam():
+            w.optim_step()
+            w.opt.main_grad.normal_()
+
+        timed(f"grad-norm + clip + AdamW + bf16 write-back over {n / 1e6:.0f} M parameters (incl. refilling the gradient)", adam)
+        hcfg = get_config("qwen3.5-hybrid", dtype="bfloat16")
+        hk, hv, d = hcfg.gdn_k_heads, hcfg.gdn_v_heads, hcfg.gdn_head_dim
+        C = (2 * hk + hv) * d
+        T = 8192
+        proj = (torch.randn(T, C + hv * d + 2 * hv, device=dev) * 0.5).bfloat16()
+        conv_w = (torch.randn(C, hcfg.gdn_conv_kernel, device=dev) * 0.3).bfloat16()
+        A_log, dtb = (torch.randn(hv, device=dev) * 0.1).bfloat16(), (torch.randn(hv, device=dev) * 0.1).bfloat16()
+        meta = gdn.GDNMeta.packed([2048] * 4, dev)
+        timed(f"GatedDeltaNet core forward (conv + gate + l2norm + chunk scan), {T} tokens, {hk}/{hv} heads of {d}",
+              lambda: gdn.gdn_core_fwd(proj, conv_w, A_log, dtb, meta, hcfg, 1))
     elif mode == "sampler":
         from skyrl_isoexec_b200.engine.sampler import Sampler, SamplingParams
         lg = torch.randn(64, 151936, device=dev).bfloat16()

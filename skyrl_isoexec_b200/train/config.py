@@ -356,5 +356,23 @@ def validate_cfg(cfg: SkyRLTrainConfig, world_size: int = 1) -> None:
             raise ValueError("engines with their own tensor-parallel degree need pp = cp = ep = 1 on the trainer")
     if p.pipeline_model_parallel_size > 1 and (p.context_parallel_size > 1 or p.expert_model_parallel_size > 1):
         raise ValueError("a pipelined trainer (pipeline_model_parallel_size > 1) supports tensor and data parallelism only")
+    # keys of the reference's config that have no meaning in a one-process-per-GPU job: refuse values that would be ignored
+    if p.sequence_parallel:
+        raise ValueError("sequence_parallel=true is not supported: the residual stream stays whole on every tensor-parallel rank "
+                         "(the GEMM -> reduce-scatter / all-gather -> GEMM kernels exist in parallel/tp_fused.py but the decoder does not use them)")
+    if ie.data_parallel_size != 1:
+        raise ValueError("inference_engine.data_parallel_size: engines are replicated by num_engines, not by an inner data-parallel degree")
+    if not ie.run_engines_locally:
+        raise ValueError("run_engines_locally=false: remote engines are reached through engine/server.py + RemoteInferenceClient, not through this key")
+    if not g.use_conversation_multi_turn:
+        raise ValueError("use_conversation_multi_turn=false (token-append multi-turn without re-rendering) is not supported; "
+                         "observations are always appended as rendered turns")
+    pl = t.placement
+    if world_size > 1 and pl.policy_num_nodes * pl.policy_num_gpus_per_node not in (1, world_size):
+        raise ValueError(f"placement asks for {pl.policy_num_nodes} x {pl.policy_num_gpus_per_node} policy GPUs but the job has {world_size} ranks")
+    if t.micro_forward_batch_size_per_gpu != 1:
+        import warnings
+
+        warnings.warn("micro_forward_batch_size_per_gpu is ignored: micro-batches are cut by trainer.max_tokens_per_microbatch", stacklevel=2)
     if ie.num_engines not in (0, 1) and ie.num_engines * etp != world_size:
         raise ValueError(f"num_engines={ie.num_engines} x tensor_parallel_size={etp} must cover the {world_size} GPUs of a colocated job")

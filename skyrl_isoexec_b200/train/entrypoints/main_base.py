@@ -52,6 +52,15 @@ class BasePPOExp:
                                  env_class=self.cfg.environment.env_class)
         return None   # the trainer falls back to synthetic prompts
 
+    def get_eval_dataset(self):
+        from ..dataset import PromptDataset
+
+        d = self.cfg.data
+        if d.val_data:
+            return PromptDataset(d.val_data, tokenizer=self.get_tokenizer(), max_prompt_length=self.cfg.trainer.max_prompt_length,
+                                 env_class=self.cfg.environment.env_class)
+        return None   # evaluation then uses the first training prompts
+
     def get_tracker(self):
         return None
 
@@ -61,6 +70,9 @@ class BasePPOExp:
 
     def run(self):
         trainer = self.get_trainer()
+        ev = self.get_eval_dataset()
+        if ev is not None:
+            trainer.eval_dataset = ev
         trainer.build_models()
         if self.world > 1 and torch.cuda.is_available() and self.ps.dp > 1:
             from ...parallel.symm_runtime import SymmGroup

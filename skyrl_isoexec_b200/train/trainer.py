@@ -242,6 +242,11 @@ class RayPPOTrainer:
         if tp_e_cfg != self.ps.tp:
             mo.setdefault("tp_invariant", True)     # two degrees, one set of bits: the K reductions use the leaf tree
         mcfg = get_config(t.policy.model, **mo)
+        if t.isoexec.debug_trace:
+            # region digests of both sides of every forward, one file per rank, for debug/compare.py
+            from ..debug import trace as _trace
+
+            _trace.install("trainer", self.rank, t.isoexec.debug_trace)
         tp_e = self._engine_layout(mcfg)
         self._setup_transports(mcfg)
         flat_alloc = self._flat_rendezvous = None
@@ -322,6 +327,11 @@ class RayPPOTrainer:
             self.adapter_engine = ContractAdapter("engine", self.engine.model, self.rank, trainer_tp=self.ps.tp, engine_tp=tp_e,
                                                   trainer_pp=self.ps.pp)
             self.adapter_engine.run_install()
+            if t.isoexec.contract_path and self.rank == 0:
+                # the frozen contract as an artifact beside the run (R/.../isoexec/core/process.py write_contract)
+                from ..core import process as _process
+
+                _process.write_contract(self.adapter_trainer.contract, t.isoexec.contract_path)
             # the admitted steady-state signature of this (model, contract, arch): under the contract the band of the
             # mean |rollout - train| logprob difference is exactly zero (R/.../isoexec/core/signatures.py:48-131)
             from ..core.signatures import bitwise_table
@@ -597,6 +607,10 @@ class RayPPOTrainer:
                     mb.metadata["aux_loss_scale"] = 1.0 / max(1.0, self._global_sum(float(lm.sum())))
                 if getattr(self, "_gate_in_update", False):
                     mb.metadata["check_rollout_bits"] = True
+                if t.recompute_old_logprobs_per_minibatch and n_updates > 0:
+                    # the policy has moved since the batch was scored: take the old-policy logprobs of this mini-batch
+                    # from the CURRENT weights, so the ratio of its first update is exactly 1 (R/train/trainer.py:1610-1640)
+                    mb["action_log_probs"] = self.dispatch.forward("policy", mb)
                 m = self.dispatch.forward_backward("policy", mb)
                 if getattr(self, "_gate_in_update", False):
                     self._gate_on_training_forward(m["rollout_bits"])      # raises before the weights move
@@ -750,6 +764,11 @@ class RayPPOTrainer:
                 log_example(dec(list(go["prompt_token_ids"][0])), dec(list(go["response_ids"][0])), go["rewards"][0])
             with Timer("convert", T):
                 batch = self.convert_to_training_input(go, uids)
+            if self.cfg.trainer.dump_data_batch and self.cfg.trainer.ckpt_path:
+                d = os.path.join(self.cfg.trainer.ckpt_path, "dumped_data")
+                os.makedirs(d, exist_ok=True)
+                torch.save({"tensors": {k: v for k, v in batch.items() if torch.is_tensor(v)}, "uids": list(uids)},
+                           os.path.join(d, f"global_step_{self.global_step}_rank{self.rank}.pt"))
             if self.global_step == 1 and hasattr(self, "adapter_engine"):
                 # everything the op layer ran since the models were built was the engine's (generation)
                 self.adapter_engine.on_first_forward(_observe.diff(self._census0))

@@ -287,3 +287,42 @@ def test_trainer_exports_a_dcp_checkpoint_and_resumes_from_it(tmp_path):
     for (n, a), (_, b) in zip(tr.policy.model.named_weights(), tr2.policy.model.named_weights()):
         assert torch.equal(a, b), n
     assert torch.equal(tr.policy.opt.exp_avg_sq, tr2.policy.opt.exp_avg_sq)
+
+
+def test_reference_config_keys_are_wired_or_refused(tmp_path):
+    """Keys carried over from the reference's config either do something or are refused: the contract artifact, the batch
+    dump, per-mini-batch old logprobs, the debug trace; values that would be silently ignored raise."""
+    import json
+
+    from skyrl_isoexec_b200.train.config import SkyRLTrainConfig, validate_cfg
+    from skyrl_isoexec_b200.train.trainer import RayPPOTrainer
+
+    base = ["trainer.policy.model=tiny-qwen3", "trainer.train_batch_size=4", "trainer.policy_mini_batch_size=2",
+            "generator.n_samples_per_prompt=2", "generator.sampling_params.max_generate_length=6", "data.synthetic_prompt_len=10",
+            "trainer.num_steps=1", "trainer.logger=jsonl", f"trainer.ckpt_path={tmp_path}/ckpt", "trainer.ckpt_interval=0",
+            "environment.env_class=even_tokens"]
+    ov = base + [f"trainer.isoexec.contract_path={tmp_path}/contract.json", "trainer.dump_data_batch=true",
+                 "trainer.recompute_old_logprobs_per_minibatch=true", f"trainer.isoexec.debug_trace={tmp_path}/trace"]
+    tr = RayPPOTrainer(SkyRLTrainConfig.from_cli_overrides(ov), device="cpu")
+    tr.build_models()
+    calls = []
+    real = tr.dispatch.forward
+    tr.dispatch.forward = lambda name, b: (calls.append((name, b.batch_size)), real(name, b))[1]
+    tr.train()
+    from skyrl_isoexec_b200.debug import trace as _trace
+
+    _trace.uninstall()
+    doc = json.loads((tmp_path / "contract.json").read_text())
+    assert doc and tr.adapter_trainer.contract is not None
+    dumped = torch.load(tmp_path / "ckpt" / "dumped_data" / "global_step_1_rank0.pt", weights_only=False)
+    assert dumped["tensors"]["sequences"].shape[0] == 8 and len(dumped["uids"]) == 8
+    # two mini-batches: the batch is scored once, and the second mini-batch is re-scored under the moved policy
+    assert calls == [("policy", 8), ("policy", 4)]
+    assert any((tmp_path / "trace").iterdir())
+    for bad in (["trainer.policy.parallel.sequence_parallel=true"], ["generator.inference_engine.data_parallel_size=2"],
+                ["generator.inference_engine.run_engines_locally=false"], ["generator.use_conversation_multi_turn=false"]):
+        with pytest.raises(ValueError):
+            validate_cfg(SkyRLTrainConfig.from_cli_overrides(base + bad), 1)
+    with pytest.raises(ValueError):
+        validate_cfg(SkyRLTrainConfig.from_cli_overrides(base + ["trainer.placement.policy_num_gpus_per_node=4",
+                                                                 "trainer.policy.parallel.tensor_model_parallel_size=1"]), 2)
