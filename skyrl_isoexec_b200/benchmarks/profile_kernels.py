@@ -246,7 +246,7 @@ def main(mode: str = "attn_decode") -> None:
         from skyrl_isoexec_b200.train import algorithms as alg
         from skyrl_isoexec_b200.train.policy_worker import PolicyWorker, WorkerConfig
 
-        def timed(name, fn, n=4):
+        def timed(name, fn, n=1 if os.environ.get("IX_PROFILE_ONCE") else 4):     # IX_PROFILE_ONCE=1: one launch each (ncu)
             fn()
             torch.cuda.synchronize()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

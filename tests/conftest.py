@@ -19,3 +19,14 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+def finish_rank(dist) -> None:
+    """End of a gloo / NCCL worker's ``finally`` block. The closing barrier runs only when the body succeeded: a rank
+    that raised leaves with its traceback instead of parking in a barrier (or making its peers wait for one), so a
+    broken test fails at the parent's first poll with the cause on stderr, not at a timeout."""
+    import sys
+
+    if sys.exc_info()[0] is None:
+        dist.barrier()
+    dist.destroy_process_group()

@@ -47,8 +47,9 @@ def _worker(rank, world, port, q_out):
         ok_gather = torch.equal(kg, k)
         q_out.put((rank, o.detach().numpy(), ql.grad.numpy(), kl.grad.numpy(), vl.grad.numpy(), ok_gather))
     finally:
-        dist.barrier()
-        dist.destroy_process_group()
+        from conftest import finish_rank
+
+        finish_rank(dist)
 
 
 @pytest.mark.timeout(240)
@@ -99,8 +100,9 @@ def _ring_worker(rank, world, port, q_out):
         (o * CP.shard_sequence(go, rank, world)).sum().backward()
         q_out.put((rank, o.detach().numpy(), ql.grad.numpy(), kl.grad.numpy(), vl.grad.numpy()))
     finally:
-        dist.barrier()
-        dist.destroy_process_group()
+        from conftest import finish_rank
+
+        finish_rank(dist)
 
 
 @pytest.mark.timeout(240)

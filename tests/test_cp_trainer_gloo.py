@@ -71,8 +71,9 @@ def _worker(rank, world, port, q):
         diff = float((solo.store.flat - tr.policy.model.store.flat).abs().max())
         q.put((rank, mism, same_lp, diff, float(m["policy/grad_norm"]), gn1, int(m["generate/response_tokens"])))
     finally:
-        dist.barrier()
-        dist.destroy_process_group()
+        from conftest import finish_rank
+
+        finish_rank(dist)
 
 
 @pytest.mark.timeout(600)

@@ -52,8 +52,9 @@ def _worker(rank, world, port, q):
         wl.forward_backward(batch)
         q.put((rank, bool(torch.equal(grads[True], grads[False])), wl.opt.main_grad.numpy(), grads[True].numpy()))
     finally:
-        dist.barrier()
-        dist.destroy_process_group()
+        from conftest import finish_rank
+
+        finish_rank(dist)
 
 
 @pytest.mark.timeout(240)

@@ -61,8 +61,9 @@ def _worker(rank, world, port, q, tmp):
         q.put((rank, m1["policy/rollout_train_logprob_bit_mismatches"], m2["policy/rollout_train_logprob_bit_mismatches"],
                m1["policy/grad_norm"], m2["policy/grad_norm"], int(tr.engine.stats["steps"]), n_exp, own_ok, digest))
     finally:
-        dist.barrier()
-        dist.destroy_process_group()
+        from conftest import finish_rank
+
+        finish_rank(dist)
 
 
 @pytest.mark.timeout(300)

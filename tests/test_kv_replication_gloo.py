@@ -94,8 +94,9 @@ def _worker(rank, port, q, tmp, gate):
             res = (int((lp1.view(torch.int32) != lp4.view(torch.int32)).sum()), g1, g4, worst, sorted(hf1) == sorted(hf4), resharded)
         q.put((rank, kv_same and engine_mism == 0, res))
     finally:
-        dist.barrier()
-        dist.destroy_process_group()
+        from conftest import finish_rank
+
+        finish_rank(dist)
 
 
 @pytest.mark.timeout(600)

@@ -52,8 +52,9 @@ def _worker(rank, world, port, q):
                  for n, v in model.named_weights() for s in [model.store.specs[n]]}
         q.put((rank, lp.numpy(), m["policy_loss"], {n: g.numpy() for n, g in grads.items()}))   # by value: the child may exit first
     finally:
-        dist.barrier()
-        dist.destroy_process_group()
+        from conftest import finish_rank
+
+        finish_rank(dist)
 
 
 @pytest.mark.timeout(240)

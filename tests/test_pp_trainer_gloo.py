@@ -54,8 +54,9 @@ def _worker(rank, world, port, q):
         full = {n: t.clone().numpy() for n, t in tr.engine.model.named_weights()}      # by value: the rank exits right after
         q.put((rank, mism, toks, full))
     finally:
-        dist.barrier()
-        dist.destroy_process_group()
+        from conftest import finish_rank
+
+        finish_rank(dist)
 
 
 @pytest.mark.timeout(600)

@@ -71,8 +71,9 @@ def _worker(rank, world, port, d, q):
         resumed = list(seen)
         q.put((rank, full, resumed, ok_critic, ok_kl, ok_epoch, ok_opt, tr2.global_step))
     finally:
-        dist.barrier()
-        dist.destroy_process_group()
+        from conftest import finish_rank
+
+        finish_rank(dist)
 
 
 @pytest.mark.timeout(600)

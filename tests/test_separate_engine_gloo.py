@@ -69,8 +69,9 @@ def _worker(rank, world, port, tp_t, tp_e, q):
             ok = ok and torch.equal(want, tr.engine.model.store.views[name])
         q.put((rank, mism, moved, changed, ok, tr.engines_per_replica))
     finally:
-        dist.barrier()
-        dist.destroy_process_group()
+        from conftest import finish_rank
+
+        finish_rank(dist)
 
 
 def _run(world, tp_t, tp_e):

@@ -67,8 +67,9 @@ def _worker(rank, world, port, q):
             refused = True
         q.put((rank, same, cut_ok, refused))
     finally:
-        dist.barrier()
-        dist.destroy_process_group()
+        from conftest import finish_rank
+
+        finish_rank(dist)
 
 
 @pytest.mark.timeout(240)
@@ -133,8 +134,9 @@ def _ckpt_worker(rank, world, port, q, tmp):
         q.put((rank, resumed_same, bool(torch.equal(c.model.store.flat.detach(), a.model.store.flat.detach())),
                data_state["pos"], trainer_state["global_step"]))
     finally:
-        dist.barrier()
-        dist.destroy_process_group()
+        from conftest import finish_rank
+
+        finish_rank(dist)
 
 
 @pytest.mark.timeout(300)

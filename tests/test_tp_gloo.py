@@ -75,8 +75,9 @@ def _worker(rank, port, q):
         if rank == 0:
             q.put(out)
     finally:
-        dist.barrier()
-        dist.destroy_process_group()
+        from conftest import finish_rank
+
+        finish_rank(dist)
 
 
 @pytest.mark.timeout(900)
