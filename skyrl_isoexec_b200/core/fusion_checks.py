@@ -101,6 +101,27 @@ def _chk_leaftree(device: str):
     return _same(got, want)
 
 
+@checker("leaftree_gemm (one CTA per leaf | two 4-leaf launches | one CTA)")
+def _chk_leaf_forms(device: str):
+    """The three schedules of the single-rank leaf-tree GEMM give one set of bits: a cluster with one CTA per leaf
+    (decode sizes), two launches of four leaves joined by the addend epilogue (8 leaves at training sizes), and all
+    leaves in one CTA's TMEM."""
+    if device == "cpu":
+        return None             # one schedule on the CPU
+    from ..parallel import tp_fused
+
+    w = hazard_population((256, 1024), torch.bfloat16, device, 21).clamp(-1, 1)
+    ok = True
+    for M in (40, 300):
+        x = hazard_population((M, 1024), torch.bfloat16, device, 22 + M).clamp(-8, 8)
+        for L in (2, 8):
+            one = tp_fused.leaftree_gemm_fused(x, w, L, out_f32=True, bn=32, split=False)       # every leaf in one CTA
+            ok = ok and _same(tp_fused.leaftree_gemm_fused(x, w, L, out_f32=True), one)           # the form the size selects
+            if M <= 256:
+                ok = ok and _same(tp_fused.leaftree_gemm_fused(x, w, L, out_f32=True, split=True), one)
+    return ok
+
+
 def _admitted(kind: str):
     """The fused GEMM+collective kernels are compared with their unfused chain by the admission probe that runs on the
     first call of every shape (parallel/tp.py::admit_fused_row_parallel). Without a multi-GPU job there is nothing to

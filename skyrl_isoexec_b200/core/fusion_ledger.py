@@ -32,6 +32,8 @@ REGIONS: tuple[FusedRegion, ...] = (
                 "the epilogue repeats the three roundings of the separate kernels"),
     FusedRegion("grouped_gemm(experts)", ("loop over experts: gemm_nt",), "bitwise"),
     FusedRegion("leaftree_gemm (LOCAL)", ("per-leaf gemm_nt fp32", "tree_fold"), "bitwise"),
+    FusedRegion("leaftree_gemm (one CTA per leaf | two 4-leaf launches | one CTA)", ("leaftree_gemm (LOCAL)",), "pair",
+                "the decode-sized cluster form and the split 8-leaf training form equal the single-CTA form"),
     FusedRegion("tp_gemm_fused (AR1/AR2/RS)", ("leaftree_gemm", "tree_all_reduce"), "bitwise"),
     FusedRegion("tp_gemm_fused (AG)", ("all_gather", "gemm_nt"), "bitwise"),
     FusedRegion("logprob_fused", ("rowmax", "leafsum", "finalize", "gather_target"), "bitwise"),

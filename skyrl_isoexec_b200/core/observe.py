@@ -54,7 +54,7 @@ IMPL_SYMBOLS: dict[str, tuple[str, ...]] = {
     "fused_gated_outnorm": ("ix_gated_outnorm",),
     "rowinv_leaftree": ("ix_logprob_fused", "ix_logprob_rowmax", "ix_logprob_leafsum", "ix_logprob_finalize"),
     "sampled_rows": ("ix_gemm_bf16_nt",),
-    "cpr_chunk_scan": ("ix_gdn_scan",),
+    "cpr_chunk_scan": ("ix_gdn_scan", "ix_gdn_chunk_fwd"),
     "cpr_recurrent_step": ("ix_gdn_scan",),
     "shifted_sum_conv": ("ix_gdn_conv",),
     "fp32_gating": ("ix_gdn_gate", "ix_gdn_l2norm"),
@@ -63,7 +63,7 @@ IMPL_SYMBOLS: dict[str, tuple[str, ...]] = {
     "index_build": ("ix_moe_dispatch_plan", "ix_moe_gather_rows"),
     "grouped_gemm": ("ix_moe_grouped_gemm",),
     "fixed_order": ("ix_moe_combine",),
-    "pik_tree": ("ix_tp_gemm_fused", "ix_peer_tree_reduce"),
+    "pik_tree": ("ix_tp_gemm_fused", "ix_peer_tree_reduce", "ix_leaf_split_gemm", "ix_leaftree_gemm_add"),
     "bytes_only": (),
     # C++ CPU library (lib/libisoexec_cpu.so)
     "cpu_sequential_k": ("ixc_gemm_nt",),
