@@ -52,8 +52,9 @@ def admit(cfg, device: str = "cuda", tp: int = 1, ep: int = 1) -> dict:
         if not on_gpu or cfg.dtype != "bfloat16" or site.grouped or site.k % 8 or site.n % 8:
             report[site.name] = seen[shape] = None      # expert matrices are covered by the grouped-GEMM region check
             continue
-        x = (torch.randn(320, site.k, generator=g, device=device) * 0.5).bfloat16()
-        w = (torch.randn(site.n, site.k, generator=g, device=device) * 0.05).bfloat16()
+        # drawn in bf16 and scaled in place: the LM head's probe weight is 1.2 GB, an fp32 detour would hold 6 GB for a moment
+        x = torch.randn(320, site.k, generator=g, device=device, dtype=torch.bfloat16).mul_(0.5)
+        w = torch.randn(site.n, site.k, generator=g, device=device, dtype=torch.bfloat16).mul_(0.05)
         f32 = site.out_dtype == "fp32"
         ok = _rows_agree(lambda a: F.gemm_nt(a, w, out_f32=f32), x)
         leaves = getattr(cfg, "pik_leaves", 0) // max(1, tp) if getattr(cfg, "tp_invariant", False) else 0
