@@ -922,3 +922,30 @@ def test_trace_digest_kernel_equals_the_integer_torch_formulation(dtype):
     y.view(torch.int16 if dtype == torch.bfloat16 else torch.int32)[5, 2, 7] ^= 1      # flip the last mantissa bit of one element
     la, lb = thash.ladder(xg), thash.ladder(y)
     assert la["0"] != lb["0"] and la["1"] == lb["1"]
+
+
+def test_gdn_conv_eight_channels_per_thread_equals_the_scalar_kernel_bitwise():
+    """The vectorised causal conv (16-byte loads, taken when the row stride is a multiple of 8) and the scalar kernel (any
+    stride) give the same bits, with taps that reach into the conv state and with a zero history."""
+    from skyrl_isoexec_b200.ops import _native, gdn
+
+    torch.manual_seed(4)
+    T, C, W = 150, 256, 4
+    lens = [70, 80]
+    x = (torch.randn(T, C, device=DEV) * 0.7).bfloat16()
+    w = (torch.randn(C, W, device=DEV) * 0.3).bfloat16()
+    conv_state = (torch.randn(3, C, W - 1, device=DEV) * 0.5).bfloat16()
+    # sequence 0 continues from state row 2 (its first taps read the state), sequence 1 starts from nothing
+    meta = gdn.GDNMeta.build([(0, lens[0], 5, 2, 2), (lens[0], lens[1], 0, -1, 1)], DEV)
+    lib = _native.lib()
+
+    def run(xin, ldx):
+        out = torch.empty(T, C, device=DEV, dtype=torch.bfloat16)
+        _native.check(lib.ix_gdn_conv(xin.data_ptr(), ldx, w.data_ptr(), meta.tok_back.data_ptr(), _native.ptr(meta.state_row),
+                                      conv_state.data_ptr(), out.data_ptr(), T, C, W, 0, _native.stream()), "ix_gdn_conv")
+        return out
+
+    wide = torch.zeros(T, C + 3, device=DEV, dtype=torch.bfloat16)            # row stride 259: the scalar kernel
+    wide[:, :C] = x
+    assert bitwise_equal(run(x, C), run(wide, C + 3))
+    assert _native.read_status() == 0
