@@ -187,6 +187,7 @@ def grouped_gemm(x_rows: torch.Tensor, w: torch.Tensor, offs: torch.Tensor, epi:
 def expert_rows_grouped(x_rows, w_rows, offs, gate_up, down, row_dst=None):
     """fc1 + SwiGLU + gate weight in one grouped launch, fc2 (fp32 out) in a second; no host round trip."""
     _obs.note("moe.experts", "grouped_gemm")
+    _obs.note("activation.swiglu", "fused_swiglu")          # applied in the fc1 epilogue
     a = grouped_gemm(x_rows, gate_up, offs, EPI_GLU, w_rows=w_rows.contiguous())
     return grouped_gemm(a, down, offs, EPI_F32, row_dst=row_dst)
 

@@ -19,6 +19,7 @@ import ctypes as C
 import torch
 import torch.distributed as dist
 
+from ..core import observe as _obs
 from . import _native
 from . import moe as M
 
@@ -79,6 +80,8 @@ class EPPeer:
         if R > self.max_rows:
             raise ValueError(f"{R} dispatch rows exceed the {self.max_rows} the peer buffers were sized for")
         st = _native.stream()
+        _obs.note("moe.experts", "grouped_gemm")                # the owner's fc1 (SwiGLU x gate weight epilogue) and fc2
+        _obs.note("activation.swiglu", "fused_swiglu")
         order, counts, pos = M.build_dispatch(idx, self.E)
         tok_of_row = torch.div(order, k, rounding_mode="floor")
         expert_of_row = idx.reshape(-1).index_select(0, order).contiguous()
