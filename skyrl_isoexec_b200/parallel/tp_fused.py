@@ -50,10 +50,13 @@ def _sig(lib):
     lib._tp_sig = True
 
 
-def pick_bn(M: int, N: int, leaves: int) -> int:
-    """Widest tile whose ``leaves`` accumulators fit the 512 TMEM columns (a tcgen05.mma of 128 columns costs what one of
-    32 does, so width beats keeping a second accumulator set for epilogue overlap) that still gives most SMs a tile."""
-    bn = min(256, 512 // leaves)
+def pick_bn(M: int, N: int, leaves: int, peers: bool = False) -> int:
+    """Widest tile that still gives most SMs a tile. Single rank: the ``leaves`` accumulators may fill all 512 TMEM
+    columns (a tcgen05.mma of 128 columns costs what one of 32 does, so width beats keeping a second accumulator set for
+    epilogue overlap: 843 us against 1640 us at 4 leaves, 8192 x 4096 x 12288). With peers the epilogue also pushes the
+    tile over NVLink, the overlap matters as much as the width (measured equal at 2 ranks), and the rule stays at two
+    accumulator sets (2 * leaves * bn <= 512)."""
+    bn = min(256, (256 if peers else 512) // leaves)
     tiles_m = (M + 127) // 128
     while bn > 32 and (N % bn or tiles_m * (N // bn) * 5 < _SMS * 3):
         bn //= 2
@@ -181,7 +184,7 @@ class FusedTP:
         if mode == "auto":
             mode = "allreduce"
         code = TP_RS if mode == "reduce_scatter" else (TP_AR1 if M <= 256 else TP_AR2)
-        bn = pick_bn(M, N, leaves)
+        bn = pick_bn(M, N, leaves, peers=True)
         need = int(self.lib.ix_tp_stage_floats(M, N, code, W, bn))
         tiles = ((M + 127) // 128) * (N // bn)
         if need > self.stage_floats or tiles * W > self.n_flags:
