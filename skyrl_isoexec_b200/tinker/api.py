@@ -16,6 +16,10 @@ survive a restart of the front end) and executed in order by one engine thread; 
   GET  /api/v1/download/<archive_id>                                     -> the archive's bytes
   GET  /api/v1/telemetry                                                 -> per-verb counts / failures / latency, queue depth
   GET  /api/v1/healthz, /api/v1/get_server_capabilities
+  REST-style forms of the same, with the reference's paths: GET / ; POST /api/v1/client/config ; GET /api/v1/samplers/<id> ;
+  GET /api/v1/training_runs[/<model_id>] ; GET /api/v1/training_runs/<model_id>/checkpoints and /api/v1/models/<model_id>/checkpoints ;
+  GET /api/v1/training_runs/<model_id>/checkpoints/<checkpoint>/archive | download (<checkpoint>: file name or index of the
+  save) ; POST /api/v1/telemetry (events a client reports; stored, counted in GET /api/v1/telemetry)
 
 A front end restarted on an existing database file reloads its models from their stored specs, re-applies the last
 completed ``save_weights`` of each when the file is still there, and keeps queued requests; requests that were
@@ -54,6 +58,7 @@ class TinkerServer:
                         "created real)")
         self.db.execute("create table if not exists archives (id text primary key, model_id text, src text, file text, bytes integer, "
                         "sha256 text, created real)")
+        self.db.execute("create table if not exists client_events (session_id text, name text, payload text, created real)")
         cols = [r[1] for r in self.db.execute("pragma table_info(futures)")]
         if "finished" not in cols:
             self.db.execute("alter table futures add column finished real")
@@ -87,6 +92,16 @@ class TinkerServer:
                     return self._reply(200, {"supported_models": sorted(PRESETS), "loss_fns": sorted(LOSS_FNS)})
                 if self.path == "/api/v1/telemetry":
                     return self._reply(200, outer.telemetry())
+                if self.path == "/":
+                    return self._reply(200, {"name": "skyrl_isoexec_b200 tinker API", "api": "/api/v1", "models": len(outer.models)})
+                rest = outer.rest_get(self.path)
+                if rest is not None:
+                    kind, val = rest
+                    if kind == "json":
+                        return self._reply(200, val)
+                    if kind == "missing":
+                        return self._reply(404, {"error": val})
+                    self.path = "/api/v1/download/" + val          # kind == "download": stream the archive below
                 if self.path.startswith("/api/v1/download/"):
                     f = outer.archive_file(self.path.rsplit("/", 1)[-1])
                     if f is None:
@@ -152,6 +167,50 @@ class TinkerServer:
         self.db.commit()
         return out
 
+    def _checkpoint_of(self, model_id: str, ref: str) -> str | None:
+        """A recorded save of the model named by its file / directory name or by its index in save order."""
+        with self._dblock:
+            rows = [r[0] for r in self.db.execute("select path from checkpoints where model_id = ? order by created", (model_id,))]
+        if ref.lstrip("-").isdigit() and -len(rows) <= int(ref) < len(rows):
+            return rows[int(ref)]
+        for p_ in reversed(rows):
+            if os.path.basename(p_.rstrip("/")) == ref:
+                return p_
+        return None
+
+    def rest_get(self, path: str):
+        """The reference's REST paths. Returns None (not one of them), ("json", obj), ("missing", why) or ("download", archive id)."""
+        parts = [x for x in path.split("?")[0].split("/") if x]
+        if parts[:2] != ["api", "v1"]:
+            return None
+        parts = parts[2:]
+        try:
+            if parts == ["training_runs"]:
+                return "json", self.post("/api/v1/training_runs", {})
+            if len(parts) == 2 and parts[0] == "training_runs":
+                runs = [r for r in self.post("/api/v1/training_runs", {})["training_runs"] if r["model_id"] == parts[1]]
+                return ("json", runs[0]) if runs else ("missing", f"no training run {parts[1]!r}")
+            if len(parts) == 3 and parts[0] in ("training_runs", "models") and parts[2] == "checkpoints":
+                return "json", self.post("/api/v1/list_checkpoints", {"model_id": parts[1]})
+            if len(parts) == 5 and parts[0] == "training_runs" and parts[2] == "checkpoints" and parts[4] in ("archive", "download"):
+                ck = self._checkpoint_of(parts[1], parts[3])
+                if ck is None:
+                    return "missing", f"no checkpoint {parts[3]!r} of {parts[1]!r}"
+                arc = self.post("/api/v1/checkpoint_archive", {"model_id": parts[1], "path": ck})
+                return ("json", arc) if parts[4] == "archive" else ("download", arc["archive_id"])
+            if len(parts) == 2 and parts[0] == "samplers":
+                with self._dblock:
+                    row = self.db.execute("select model_id, meta, created, heartbeat from sessions where id = ? and kind = 'sampling_session'",
+                                          (parts[1],)).fetchone()
+                if row is None:
+                    return "missing", f"no sampler {parts[1]!r}"
+                b = self.models.get(row[0])
+                return "json", {"sampler_id": parts[1], "model_id": row[0], "created": row[2], "heartbeat": row[3], **json.loads(row[1]),
+                                "sampler_version": getattr(b, "sampler_version", 0) if b is not None else None}
+        except KeyError as e:
+            return "missing", f"unknown {e}"
+        return None
+
     def archive_file(self, archive_id: str) -> str | None:
         with self._dblock:
             row = self.db.execute("select file from archives where id = ?", (archive_id,)).fetchone()
@@ -171,11 +230,24 @@ class TinkerServer:
             if finished:
                 d["latency_s_sum"] += finished - created
                 d["latency_s_max"] = max(d["latency_s_max"], finished - created)
-        return {"requests": per, "queue_depth": sum(d["pending"] for d in per.values()), "models": len(self.models), "sessions": sessions}
+        with self._dblock:
+            events = dict(self.db.execute("select name, count(*) from client_events group by name").fetchall())
+        return {"requests": per, "queue_depth": sum(d["pending"] for d in per.values()), "models": len(self.models), "sessions": sessions,
+                "client_events": events}
 
     # ------------------------------------------------------------------ front end
     def post(self, path: str, body: dict) -> dict:
         verb = path.rsplit("/", 1)[-1]
+        if path.endswith("/client/config"):
+            return {"poll_interval_s": 0.01, "request_timeout_s": 600.0, "future_retention": "database", "api_prefix": "/api/v1"}
+        if verb == "telemetry":
+            evs = body.get("events") or ([body] if body.get("name") else [])
+            with self._dblock:
+                for ev in evs:
+                    self.db.execute("insert into client_events values (?, ?, ?, ?)",
+                                    (body.get("session_id"), str(ev.get("name", "event")), json.dumps(ev), time.time()))
+                self.db.commit()
+            return {"status": "accepted", "events": len(evs)}
         if verb == "list_checkpoints":
             with self._dblock:
                 rows = self.db.execute("select path, kind, step, bytes, created from checkpoints where model_id = ? order by created",

@@ -108,3 +108,46 @@ def test_tinker_checkpoint_archive_download_telemetry_and_restart(tmp_path):
         assert info["step"] == 1
     finally:
         srv2.shutdown()
+
+
+def test_tinker_rest_paths_of_the_reference(tmp_path):
+    """The REST-style routes: runs, checkpoints by name or index with archive / download, sampler lookup, client config,
+    client-reported telemetry."""
+    import io
+    import json
+    import tarfile
+    import urllib.error
+    import urllib.request
+
+    srv = TinkerServer(db_path=str(tmp_path / "r.db"), device="cpu").start()
+
+    def get(path):
+        with urllib.request.urlopen(srv.url + path, timeout=60) as r:
+            raw = r.read()
+            return json.loads(raw) if r.headers.get("Content-Type", "").startswith("application/json") else raw
+
+    try:
+        cl = TinkerClient(srv.url)
+        mid = cl.create_model(base_model="tiny-qwen3")
+        cl.call("save_weights", model_id=mid, path=str(tmp_path / "a.pt"))
+        cl.call("save_weights", model_id=mid, path=str(tmp_path / "b.pt"))
+        assert get("/")["models"] == 1
+        assert [r["model_id"] for r in get("/api/v1/training_runs")["training_runs"]] == [mid]
+        assert get(f"/api/v1/training_runs/{mid}")["model_id"] == mid
+        cks = get(f"/api/v1/training_runs/{mid}/checkpoints")["checkpoints"]
+        assert [c["path"].rsplit("/", 1)[-1] for c in cks] == ["a.pt", "b.pt"] == [c["path"].rsplit("/", 1)[-1] for c in get(f"/api/v1/models/{mid}/checkpoints")["checkpoints"]]
+        arc = get(f"/api/v1/training_runs/{mid}/checkpoints/b.pt/archive")
+        blob = get(f"/api/v1/training_runs/{mid}/checkpoints/-1/download")            # the last save, by index
+        with tarfile.open(fileobj=io.BytesIO(blob), mode="r:gz") as tf:
+            assert tf.getnames() == ["b.pt"]
+        assert arc["bytes"] > 0 and arc["download"].startswith("/api/v1/download/")
+        with pytest.raises(urllib.error.HTTPError):
+            get(f"/api/v1/training_runs/{mid}/checkpoints/zzz.pt/archive")
+        sid = cl._post("create_sampling_session", {"model_id": mid, "base_model": "tiny-qwen3"})["session_id"]
+        smp = get(f"/api/v1/samplers/{sid}")
+        assert smp["model_id"] == mid and smp["sampler_version"] == 0
+        assert cl._post("client/config", {})["api_prefix"] == "/api/v1"
+        assert cl._post("telemetry", {"session_id": sid, "events": [{"name": "step"}, {"name": "step"}, {"name": "error", "msg": "x"}]})["events"] == 3
+        assert get("/api/v1/telemetry")["client_events"] == {"step": 2, "error": 1}
+    finally:
+        srv.shutdown()
