@@ -773,7 +773,7 @@ def test_example_configs_load_and_validate():
     assert len(files) >= 8
     for f in files:
         cfg = SkyRLTrainConfig.from_file(f)
-        validate_cfg(cfg, 8 if ("8gpu" in f or "ep8" in f or "tp4dp2" in f) else 2 if "tp2" in f else 1)
+        validate_cfg(cfg, 8 if any(k in f for k in ("8gpu", "ep8", "tp4dp2", "tp2dp4", "tp8")) else 2 if "tp2" in f else 1)
     named = SkyRLTrainConfig.from_file(os.path.join(root, "qwen3_8b_tp4dp2_engines_tp2.yaml"))
     assert named.trainer.policy.parallel.tensor_model_parallel_size == 4 and named.generator.inference_engine.tensor_parallel_size == 2
     big = SkyRLTrainConfig.from_file(os.path.join(root, "qwen3_8b_grpo_8gpu.yaml"))
