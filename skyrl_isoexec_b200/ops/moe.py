@@ -122,21 +122,25 @@ def combine_fixed_order(rows: torch.Tensor, pos: torch.Tensor, out_dtype, shared
 
 
 class _AllToAll(torch.autograd.Function):
-    """Variable-split all-to-all of rows over the EP group (bytes only); backward is the reverse exchange."""
+    """Variable-split all-to-all of rows over the EP group (bytes only); backward is the reverse exchange. The forward
+    payload keeps its dtype (the returned expert rows must reach the source unrounded: fp32). ``grad_wire``: dtype the
+    GRADIENT rows travel in; bf16 halves the backward exchange of the fp32 rows and is outside the bitwise contract
+    (reference: the bf16 all-to-all wire of the MoE backward, ISO/ops/moe/moe_combine_backward.py)."""
 
     @staticmethod
-    def forward(ctx, x, send_counts, recv_counts, group):
-        ctx.cfg = (send_counts, recv_counts, group)
+    def forward(ctx, x, send_counts, recv_counts, group, grad_wire=None):
+        ctx.cfg = (send_counts, recv_counts, group, grad_wire)
         out = x.new_empty((sum(recv_counts),) + tuple(x.shape[1:]))
         dist.all_to_all_single(out, x.contiguous(), output_split_sizes=recv_counts, input_split_sizes=send_counts, group=group)
         return out
 
     @staticmethod
     def backward(ctx, g):
-        send_counts, recv_counts, group = ctx.cfg
-        out = g.new_empty((sum(send_counts),) + tuple(g.shape[1:]))
-        dist.all_to_all_single(out, g.contiguous(), output_split_sizes=send_counts, input_split_sizes=recv_counts, group=group)
-        return out, None, None, None
+        send_counts, recv_counts, group, grad_wire = ctx.cfg
+        wire = g.to(grad_wire) if grad_wire is not None and g.dtype != grad_wire else g
+        out = wire.new_empty((sum(send_counts),) + tuple(g.shape[1:]))
+        dist.all_to_all_single(out, wire.contiguous(), output_split_sizes=send_counts, input_split_sizes=recv_counts, group=group)
+        return out.to(g.dtype), None, None, None, None
 
 
 # ------------------------------------------------------------------------------------ experts
@@ -404,7 +408,7 @@ def moe_block(y: torch.Tensor, model, i: int) -> torch.Tensor:
             own = torch.repeat_interleave(torch.arange(e_loc, device=y.device, dtype=torch.int32).repeat(ps.ep), cnt_in.view(-1),
                                           output_size=xr.shape[0])
             out_rows = _ExpertsFn.apply(xr, wr.view(-1, 1), gate_up, down, own.view(-1, 1), None, True)
-            rows = _AllToAll.apply(out_rows, recv, send, ps.ep_group)
+            rows = _AllToAll.apply(out_rows, recv, send, ps.ep_group, torch.bfloat16 if y.dtype == torch.bfloat16 else None)
             shared = _shared_expert(y, model, pfx) if cfg.shared_expert_ffn else None
             return combine_fixed_order(rows, pos, y.dtype, shared)
         # received rows are grouped by (source rank, expert); regroup by expert, keeping source order
@@ -424,7 +428,7 @@ def moe_block(y: torch.Tensor, model, i: int) -> torch.Tensor:
             out_rows = _expert_rows(xs, wsr, loc_counts, gate_up, down)
         back = torch.empty_like(out_rows)
         back[perm] = out_rows
-        rows = _AllToAll.apply(back, recv, send, ps.ep_group)
+        rows = _AllToAll.apply(back, recv, send, ps.ep_group, torch.bfloat16 if y.dtype == torch.bfloat16 else None)
     elif _grouped_ok(x_rows, gate_up, down):
         rows = expert_rows_grouped(x_rows, w_rows, counts_to_offsets(counts), gate_up, down)
     else:
