@@ -54,6 +54,7 @@ class ModelConfig:
     logprob_leaves: int = 8
     pik_leaves: int = 8
     tp_invariant: bool = False  # row-parallel K reductions use the leaf tree so any TP | pik_leaves gives equal bits
+    sequence_parallel: bool = False  # trainer forward: residual stream, norms and adds on T / tp rows per rank (dense attention models)
 
     @property
     def torch_dtype(self) -> torch.dtype:

@@ -240,6 +240,7 @@ class ForwardCtx:
     kv: list | None = None             # per attention layer: (k_pool, v_pool); per GDN layer: GDN state handle
     gdn_meta: object | None = None     # sequence layout for GDN layers (see ops/gdn.py)
     site: str = "trainer_fwd"          # trainer_fwd | trainer_score | engine_prefill | engine_decode
+    sp_T: int | None = None            # set by the forward when sequence parallelism is on: total rows of the micro-batch
 
 
 class DecoderLM(nn.Module):
@@ -293,8 +294,8 @@ class DecoderLM(nn.Module):
     # -------------------------------------------------------------------------------- layers
     def _attn_block(self, i: int, y: torch.Tensor, fc: ForwardCtx, kv_idx: int) -> torch.Tensor:
         cfg, pfx = self.cfg, f"layers.{i}.attn."
-        T = y.shape[0]
-        qkv = F.linear(tp_ops.copy_to_tp(y, self.ps), self.p(pfx + "qkv.weight"))
+        T = fc.sp_T if fc.sp_T is not None else y.shape[0]
+        qkv = F.linear(tp_ops.copy_to_tp(y, self.ps, fc.sp_T), self.p(pfx + "qkv.weight"))
         qw = self.p(pfx + "q_norm.weight") if cfg.qk_norm else None
         kw = self.p(pfx + "k_norm.weight") if cfg.qk_norm else None
         if fc.kv is None:
@@ -315,7 +316,8 @@ class DecoderLM(nn.Module):
             a, _ = F.attention_fwd(q, k_pool, v_pool, fc.meta, self.scale)
         if cfg.attn_output_gate:
             a = _gate_attn(a, qkv, self.hq, self.hkv, cfg.head_dim)
-        return tp_ops.row_parallel_linear(a.reshape(T, self.hq * cfg.head_dim), self.p(pfx + "o.weight"), self.ps, cfg)
+        return tp_ops.row_parallel_linear(a.reshape(T, self.hq * cfg.head_dim), self.p(pfx + "o.weight"), self.ps, cfg,
+                                          sp=fc.sp_T is not None)
 
     def _mla_block(self, i: int, y: torch.Tensor, fc: ForwardCtx, kv_idx: int) -> torch.Tensor:
         """Multi-head latent attention (reference model: R/tx/models/deepseekv3.py) in its materialised form: the latent
@@ -350,11 +352,14 @@ class DecoderLM(nn.Module):
         a = a[..., :dv].reshape(T, H * dv) if dv < D else a.reshape(T, H * D)
         return tp_ops.row_parallel_linear(a, self.p(pfx + "o.weight"), ps, cfg)
 
-    def _mlp_block(self, i: int, y: torch.Tensor) -> torch.Tensor:
+    def _mlp_block(self, i: int, y: torch.Tensor, fc: ForwardCtx | None = None) -> torch.Tensor:
         cfg, pfx = self.cfg, f"layers.{i}."
         if cfg.has_moe:
             return moe_ops.moe_block(y, self, i)
         wgu = self.p(pfx + "mlp.gate_up.weight")
+        sp_T = fc.sp_T if fc is not None else None
+        if sp_T is not None:
+            y = tp_ops.copy_to_tp(y, self.ps, sp_T)              # all rows for the column-parallel gate|up GEMM
         if y.is_cuda and y.dtype == torch.bfloat16 and not torch.is_grad_enabled() and (wgu.shape[0] // 2) % 32 == 0 and y.dim() == 2:
             # gate_up GEMM with the SwiGLU applied in its epilogue (one launch, no [T, 2F] intermediate). The epilogue
             # repeats the roundings of the separate kernels, so this and the differentiable path below agree bit for bit.
@@ -362,8 +367,8 @@ class DecoderLM(nn.Module):
             _obs.note("activation.swiglu", "fused_swiglu")
             a = moe_ops.grouped_gemm(y, wgu.unsqueeze(0), None, moe_ops.EPI_GLU)
         else:
-            a = F.swiglu(F.linear(tp_ops.copy_to_tp(y, self.ps), wgu))
-        return tp_ops.row_parallel_linear(a, self.p(pfx + "mlp.down.weight"), self.ps, cfg)
+            a = F.swiglu(F.linear(y if sp_T is not None else tp_ops.copy_to_tp(y, self.ps), wgu))
+        return tp_ops.row_parallel_linear(a, self.p(pfx + "mlp.down.weight"), self.ps, cfg, sp=sp_T is not None)
 
     def layer(self, i: int, x: torch.Tensor, res: torch.Tensor | None, fc: ForwardCtx, kv_idx: int):
         cfg = self.cfg
@@ -373,7 +378,7 @@ class DecoderLM(nn.Module):
         else:
             o = gdn_ops.gdn_block(y, self, i, fc, kv_idx)
         y, res = _norm(o, self.p(f"layers.{i}.ln2.weight"), cfg, res)
-        return self._mlp_block(i, y), res
+        return self._mlp_block(i, y, fc), res
 
     def forward(self, input_ids: torch.Tensor | None, fc: ForwardCtx, hidden_in: tuple | None = None,
                 checkpoint_layers: bool | int = False):
@@ -383,6 +388,13 @@ class DecoderLM(nn.Module):
             x, res = self.embed(input_ids), None
         else:
             x, res = hidden_in
+        fc.sp_T = None
+        if self._sequence_parallel(fc, hidden_in):
+            # Megatron-style sequence parallelism (trainer sites): from here to the final norm every rank carries its
+            # T / tp rows of the residual stream; the tensor-parallel regions gather rows on entry and keep this rank's
+            # rows of the tree sum on exit. Same kernels on the same rows: the forward bits do not change.
+            fc.sp_T = int(x.shape[0])
+            x = tp_ops.sp_scatter(x, self.ps)
         # checkpoint_layers: True = recompute every layer in the backward; an int n = recompute only the first n
         # layers of this stage (the last layers' activations are consumed first, so keeping them costs the least time)
         n_ckpt = len(self.layer_ids) if checkpoint_layers is True else int(checkpoint_layers)
@@ -396,9 +408,16 @@ class DecoderLM(nn.Module):
         if not self.ps.is_last_pp:
             return x, res
         y, _ = _norm(x, self.p("final_norm.weight"), self.cfg, res)
+        if fc.sp_T is not None:
+            y = tp_ops.sp_gather(y, fc.sp_T, self.ps, summed=False)     # the LM head's input gradient is already summed over TP
         if _trace.active() is not None:
             _trace.record("final_norm", y)
         return y
+
+    def _sequence_parallel(self, fc: ForwardCtx, hidden_in) -> bool:
+        c, ps = self.cfg, self.ps
+        return bool(getattr(c, "sequence_parallel", False) and ps.tp > 1 and ps.cp == 1 and ps.pp == 1 and hidden_in is None
+                    and fc.kv is None and not (c.has_moe or c.has_gdn or c.is_mla))
 
     @torch.no_grad()
     def ep_idle_forward(self) -> None:

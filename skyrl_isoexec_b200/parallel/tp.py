@@ -196,7 +196,7 @@ class _RowParallel(torch.autograd.Function):
         return F.gemm_nn(dy, w), F.gemm_tn(dy, x), None, None, None, None
 
 
-def row_parallel_linear(x: torch.Tensor, w: torch.Tensor, ps, cfg) -> torch.Tensor:
+def row_parallel_linear(x: torch.Tensor, w: torch.Tensor, ps, cfg, sp: bool = False) -> torch.Tensor:
     """y = x_full @ w_full^T where this rank holds the K slice x[:, K/tp], w[:, K/tp].
 
     With ``cfg.pik_leaves == 0`` (TP pinned, same degree on both sides) and tp == 1 this is the
@@ -214,6 +214,9 @@ def row_parallel_linear(x: torch.Tensor, w: torch.Tensor, ps, cfg) -> torch.Tens
     shp = x.shape
     x2 = x.reshape(-1, shp[-1])
     y = _RowParallel.apply(x2, w, ps, plan.leaves_per_rank(ps.tp), plan.leaf_dtype == "bf16", x.dtype)
+    if ps.tp > 1 and sp:
+        # sequence parallelism: this rank continues with its rows of the tree sum (the same bits as the all-reduced rows)
+        return _KeepRows.apply(y, ps)
     return y.reshape(*shp[:-1], w.shape[0])
 
 
@@ -241,10 +244,84 @@ class _CopyToTP(torch.autograd.Function):
         return g, None
 
 
-def copy_to_tp(x, ps):
+def copy_to_tp(x, ps, sp_T: int | None = None):
+    """Input of a column-parallel region. ``sp_T``: sequence parallelism is on, ``x`` holds this rank's rows of ``sp_T``
+    and is gathered (backward: the ranks' partial input gradients are summed and this rank's rows are kept)."""
+    if ps.tp > 1 and sp_T is not None:
+        return _GatherRows.apply(x, sp_T, ps, True)
     if ps.tp == 1 or not (torch.is_grad_enabled() and x.requires_grad):
         return x
     return _CopyToTP.apply(x, ps.tp_group)
+
+
+# ------------------------------------------------------------------------------------ sequence parallelism
+# Megatron-style sequence parallelism for the differentiable trainer forward: between the tensor-parallel regions the
+# residual stream, the norms and the residual adds live on T / tp rows per rank instead of being repeated on every rank.
+# A column-parallel region is entered by gathering the rows (backward: the partial input gradients of the ranks are
+# summed and scattered), a row-parallel region is left by keeping this rank's rows of the tree sum (backward: the row
+# gradients of all ranks are gathered). Every row is computed by the same kernels from the same inputs as without it,
+# so the forward bits do not change (reference: B/workers/megatron sequence_parallel; ISO/ops/collectives/pik tree
+# reduce-scatter, pik/allreduce.py:476-486).
+def sp_rows(T: int, ps) -> tuple[int, int]:
+    """[lo, hi) of the T rows that tensor-parallel rank ``ps.tp_rank`` keeps: equal shares, the remainder on the last ranks."""
+    base, rem = divmod(T, ps.tp)
+    start = lambda r: r * base + max(0, r - (ps.tp - rem))
+    return start(ps.tp_rank), start(ps.tp_rank + 1)
+
+
+def _gather_rows(x_loc: torch.Tensor, T: int, ps) -> torch.Tensor:
+    base, rem = divmod(T, ps.tp)
+    sizes = [base + (1 if r >= ps.tp - rem else 0) for r in range(ps.tp)]
+    mx = max(sizes)
+    pad = x_loc if x_loc.shape[0] == mx else torch.cat([x_loc, x_loc.new_zeros((mx - x_loc.shape[0],) + tuple(x_loc.shape[1:]))])
+    parts = [torch.empty_like(pad) for _ in range(ps.tp)]
+    dist.all_gather(parts, pad.contiguous(), group=ps.tp_group)
+    return torch.cat([p[:n] for p, n in zip(parts, sizes)], 0)
+
+
+class _GatherRows(torch.autograd.Function):
+    """Rows of every rank -> all T rows. ``summed``: the incoming gradient is a per-rank PARTIAL (input of a
+    column-parallel region): sum over ranks, keep this rank's rows. Otherwise it is already the same on every rank
+    (output of the final norm): keep this rank's rows."""
+
+    @staticmethod
+    def forward(ctx, x_loc, T, ps, summed):
+        ctx.cfg = (T, ps, summed)
+        return _gather_rows(x_loc, T, ps)
+
+    @staticmethod
+    def backward(ctx, g):
+        T, ps, summed = ctx.cfg
+        if summed:
+            g = g.clone()
+            dist.all_reduce(g, group=ps.tp_group)
+        lo, hi = sp_rows(T, ps)
+        return g[lo:hi], None, None, None
+
+
+class _KeepRows(torch.autograd.Function):
+    """All T rows (the same on every rank) -> this rank's rows; backward gathers the row gradients of all ranks, which is
+    the full gradient every rank would have had without sequence parallelism."""
+
+    @staticmethod
+    def forward(ctx, x, ps):
+        ctx.cfg = (x.shape[0], ps)
+        lo, hi = sp_rows(x.shape[0], ps)
+        return x[lo:hi]
+
+    @staticmethod
+    def backward(ctx, g):
+        T, ps = ctx.cfg
+        return _gather_rows(g.contiguous(), T, ps), None
+
+
+def sp_scatter(x: torch.Tensor, ps) -> torch.Tensor:
+    """Replicated rows -> this rank's share (entering the sequence-parallel stream, e.g. after the embedding)."""
+    return _KeepRows.apply(x, ps)
+
+
+def sp_gather(x_loc: torch.Tensor, T: int, ps, summed: bool) -> torch.Tensor:
+    return _GatherRows.apply(x_loc, T, ps, summed)
 
 
 class _TiedHeadSlice(torch.autograd.Function):

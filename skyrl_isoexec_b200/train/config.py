@@ -357,9 +357,8 @@ def validate_cfg(cfg: SkyRLTrainConfig, world_size: int = 1) -> None:
     if p.pipeline_model_parallel_size > 1 and (p.context_parallel_size > 1 or p.expert_model_parallel_size > 1):
         raise ValueError("a pipelined trainer (pipeline_model_parallel_size > 1) supports tensor and data parallelism only")
     # keys of the reference's config that have no meaning in a one-process-per-GPU job: refuse values that would be ignored
-    if p.sequence_parallel:
-        raise ValueError("sequence_parallel=true is not supported: the residual stream stays whole on every tensor-parallel rank "
-                         "(the GEMM -> reduce-scatter / all-gather -> GEMM kernels exist in parallel/tp_fused.py but the decoder does not use them)")
+    if p.sequence_parallel and (p.pipeline_model_parallel_size > 1 or p.context_parallel_size > 1 or p.expert_model_parallel_size > 1):
+        raise ValueError("sequence_parallel=true goes with tensor parallelism only (pp = cp = ep = 1)")
     if ie.data_parallel_size != 1:
         raise ValueError("inference_engine.data_parallel_size: engines are replicated by num_engines, not by an inner data-parallel degree")
     if not ie.run_engines_locally:

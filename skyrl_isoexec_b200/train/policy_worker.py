@@ -712,9 +712,12 @@ class PolicyWorker:
             return
         if self.ps.tp > 1:
             store = self.model.store
+            sp = bool(getattr(self.model.cfg, "sequence_parallel", False))
             for name in store.order:
                 s = store.specs[name]
-                if s.tp_grad_sum:
+                # under sequence parallelism the norm weights between the tensor-parallel regions saw this rank's rows only
+                sp_partial = sp and s.shard_dim is None and name.endswith(("ln1.weight", "ln2.weight", "final_norm.weight"))
+                if s.tp_grad_sum or sp_partial:
                     dist.all_reduce(self.opt.main_grad[s.offset:s.offset + math.prod(s.shape)], group=self.ps.tp_group)
                 if s.kv_rep > 1:
                     # the ranks that share a KV head each saw the gradient from their own query heads only

@@ -421,6 +421,21 @@ def _tp_model_worker(rank, world, port, q):
             ro[i, :len(o.response_logprobs)] = torch.tensor(o.response_logprobs)
         res = {"engine_vs_trainer_mismatches_tp": count_bit_mismatches((lp * rmask).contiguous(), (ro * rmask).contiguous())}
         batch["action_log_probs"] = lp
+        # the same weights with the residual stream cut over the two ranks (sequence parallelism): same logprob bits,
+        # and the same gradients up to the order in which the norm weights' partial sums meet
+        import dataclasses
+
+        sp_model = DecoderLM(dataclasses.replace(cfg, sequence_parallel=True), ps, "cuda", seed=2)
+        sp_worker = PolicyWorker(sp_model, WorkerConfig(max_tokens_per_microbatch=700))
+        lp_sp = sp_worker.forward(batch)
+        res["sp_mismatches"] = count_bit_mismatches((lp_sp * rmask).contiguous(), (lp * rmask).contiguous())
+        sp_worker.forward_backward(batch)
+        sp_worker.reduce_gradients()
+        worker.forward_backward(batch)
+        worker.reduce_gradients()
+        ga, gb = worker.opt.main_grad, sp_worker.opt.main_grad
+        res["sp_grad_rel_diff"] = float((ga - gb).abs().max() / ga.abs().max().clamp(min=1e-12))
+        worker.opt.zero_grad()                                   # the step below reduces its own gradients
         worker.forward_backward(batch)
         res["grad_norm_tp"] = worker.optim_step()
         tp_fused.get(ps.tp_group).check()
@@ -457,6 +472,7 @@ def test_tensor_parallel_model_with_fused_kernels_is_bitwise_tp_invariant():
         p.join(timeout=120)
     print("tp model:", res)
     assert res["engine_vs_trainer_mismatches_tp"] == 0 and res["tp2_vs_tp1_mismatches"] == 0
+    assert res["sp_mismatches"] == 0 and res["sp_grad_rel_diff"] < 2e-2
     assert res["grad_norm_tp"] > 0 and res["status"] == 0
     # every row-parallel shape passed its bitwise admission probe and was then served by the fused kernel
     assert res["admitted"] and all(res["admitted"]), res["admitted"]

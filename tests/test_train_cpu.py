@@ -319,7 +319,8 @@ def test_reference_config_keys_are_wired_or_refused(tmp_path):
     # two mini-batches: the batch is scored once, and the second mini-batch is re-scored under the moved policy
     assert calls == [("policy", 8), ("policy", 4)]
     assert any((tmp_path / "trace").iterdir())
-    for bad in (["trainer.policy.parallel.sequence_parallel=true"], ["generator.inference_engine.data_parallel_size=2"],
+    for bad in (["trainer.policy.parallel.sequence_parallel=true", "trainer.policy.parallel.context_parallel_size=2"],
+                ["generator.inference_engine.data_parallel_size=2"],
                 ["generator.inference_engine.run_engines_locally=false"], ["generator.use_conversation_multi_turn=false"]):
         with pytest.raises(ValueError):
             validate_cfg(SkyRLTrainConfig.from_cli_overrides(base + bad), 1)
