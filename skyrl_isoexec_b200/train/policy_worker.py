@@ -510,7 +510,12 @@ class PolicyWorker:
             total = torch.cuda.get_device_properties(self.device).total_memory
             free_now, _ = torch.cuda.mem_get_info(self.device)
             outside = total - free_now - torch.cuda.memory_reserved(self.device)   # context, NCCL, symmetric memory
-            headroom = total - outside - torch.cuda.max_memory_reserved(self.device)
+            if getattr(self, "_peak_armed", False):
+                # the peak of the scoring and training phases alone: a colocated engine's KV pools (asleep by now, their
+                # blocks back in the allocator's cache) set the step's overall peak but never coexist with activations
+                headroom = total - outside - torch.cuda.max_memory_allocated(self.device)
+            else:
+                headroom = total - outside - torch.cuda.max_memory_reserved(self.device)
             n = layers_that_fit(headroom, self.activation_bytes_per_layer(self.cfg.max_tokens_per_microbatch),
                                 len(self.model.layer_ids))
         if dist.is_initialized() and dist.get_world_size() > 1:
@@ -518,6 +523,14 @@ class PolicyWorker:
             dist.all_reduce(t, op=dist.ReduceOp.MIN)
             n = int(t.item())
         self._auto_keep = n
+
+    def _arm_peak(self) -> None:
+        """First scoring / training call of a run that sizes the kept layers itself: start the peak-memory statistics
+        here, so that ``_calibrate_keep`` sees what these phases need, not what the rollout before them needed."""
+        if (self.device.type == "cuda" and getattr(self.cfg, "keep_last_layers", 0) < 0 and self._auto_keep is None
+                and not getattr(self, "_peak_armed", False)):
+            torch.cuda.reset_peak_memory_stats(self.device)
+            self._peak_armed = True
 
     def _run_model(self, mb: PackedMicroBatch, site: str):
         dev = self.device
@@ -592,6 +605,7 @@ class PolicyWorker:
     @torch.no_grad()
     def forward(self, batch: TrainingInputBatch) -> torch.Tensor:
         """Scoring forward: log-probabilities of the response tokens, ``[B, max_response]`` fp32 (CPU)."""
+        self._arm_peak()
         R = batch["response_mask"].shape[1] if batch.get("response_mask") is not None else batch.metadata["response_length"]
         seqs, att = batch["sequences"], batch["attention_mask"]
         out = torch.zeros(seqs.shape[0], R, dtype=torch.float32)
@@ -612,6 +626,7 @@ class PolicyWorker:
         """Accumulate the gradient of the (sum-reduced, advantage-pre-scaled) policy loss of a
         mini-batch shard. Returns metrics (python floats)."""
         algo = self.algo
+        self._arm_peak()
         R = batch["response_mask"].shape[1]
         seqs, att = batch["sequences"], batch["attention_mask"]
         loss_fn = alg.get_policy_loss(algo.policy_loss_type)
