@@ -43,6 +43,8 @@ FLAGS: tuple[Flag, ...] = (
          "collectives.tree_all_reduce:leaves"),
     Flag("SKYRL_ISOEXEC_LOGPROB_LEAVES", "8", (TRAIN, ENGINE), "function", "number of vocabulary leaves of the log-softmax (read by models/config.py::get_config)",
          "logprobs.log_softmax:leaves"),
+    Flag("SKYRL_ISOEXEC_TRAINER_SP", "0", (TRAIN,), "deployment", "1: sequence parallelism in the tensor-parallel trainer (rows of the residual stream cut over the ranks; the logprob "
+         "bits do not change, so this is a deployment choice, not a numerical pin; read by train/trainer.py::build_models)"),
     Flag("ISOEXEC_CONTRACT_PATH", "", (TRAIN, ENGINE), "deployment", "write the built contract here (artifact)"),
     Flag("ISOEXEC_CONTRACT_HASH", "", (TRAIN, ENGINE), "deployment", "expected numerical_policy; a different built or loaded contract is refused"),
     Flag("ISOEXEC_HANDSHAKE_NEGATIVE_CONTROL", "0", (TRAIN,), "diagnostic", "corrupt the stamped hash so the handshake must refuse"),

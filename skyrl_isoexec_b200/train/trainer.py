@@ -241,7 +241,7 @@ class RayPPOTrainer:
         tp_e_cfg = g.inference_engine.tensor_parallel_size or self.ps.tp
         if tp_e_cfg != self.ps.tp:
             mo.setdefault("tp_invariant", True)     # two degrees, one set of bits: the K reductions use the leaf tree
-        if t.policy.parallel.sequence_parallel and self.ps.tp > 1:
+        if (t.policy.parallel.sequence_parallel or os.environ.get("SKYRL_ISOEXEC_TRAINER_SP", "0") == "1") and self.ps.tp > 1:
             mo.setdefault("sequence_parallel", True)
         mcfg = get_config(t.policy.model, **mo)
         if mcfg.sequence_parallel and (mcfg.has_moe or mcfg.has_gdn or mcfg.is_mla):
