@@ -52,7 +52,6 @@ FLAGS: tuple[Flag, ...] = (
     Flag("SKYRL_WORKER_NCCL_TIMEOUT_IN_S", "600", (TRAIN, ENGINE), "deployment", "process-group timeout"),
     Flag("NCCL_NVLS_ENABLE", "", (TRAIN, ENGINE), "deployment", "NVLS on/off for NCCL; no NCCL reduction is on the logprob path"),
     Flag("SKYRL_ISOEXEC_PIK_P2P", "1", (TRAIN, ENGINE), "deployment", "0 forces the NCCL all-gather transport for tree reductions (same bits; read by parallel/transports.py)"),
-    Flag("SKYRL_ISOEXEC_TRAINER_SP", "0", (TRAIN,), "dead", "sequence-parallel trainer variant of the reference; SP here never changes bits"),
     Flag("VLLM_BATCH_INVARIANT", "", (ENGINE,), "dead", "vLLM switch of the reference; there is no vLLM here"),
 )
 
