@@ -525,22 +525,33 @@ class LLMEngine:
             rec, self._inflight = self._inflight, None
             self._finalize(rec)
 
+    def link_samples(self, seqs: list[Sequence]) -> int:
+        """Among requests that were just added together, make every sequence whose prompt equals an earlier one's a
+        sibling of it: the n samples of a prompt then read the first one's full prompt pages instead of prefilling them
+        again (K/V rows do not depend on the batch they are computed in, so the bits are the same) and prefill only
+        the page that holds the last prompt token. Returns the number of siblings made. Models with recurrent layers are
+        left alone: a sibling would also need the leader's recurrent state at the shared boundary."""
+        if not self.cfg.share_prompt_pages or self.mcfg.has_gdn:
+            return 0
+        leaders: dict = {}
+        n = 0
+        for s in seqs:
+            if s.num_computed or s.pages or s.output_ids:
+                continue                                        # already under way
+            ld = leaders.setdefault(tuple(s.prompt_ids), s)
+            shared = ((len(s.prompt_ids) - 1) // PAGE) * PAGE
+            if ld is not s and shared > 0:
+                s.leader, s.shared_tokens = ld, shared
+                n += 1
+        return n
+
     def generate(self, prompts: list[list[int]], params: SamplingParams | list[SamplingParams]) -> list[RequestOutput]:
         """Blocking batch generation; outputs are in prompt order."""
         if self.asleep:
             raise RuntimeError("engine is asleep; call wake_up() first")
         plist = params if isinstance(params, list) else [params] * len(prompts)
         seqs = [self.add_request(p, sp, i) for i, (p, sp) in enumerate(zip(prompts, plist))]
-        if self.cfg.share_prompt_pages and not self.mcfg.has_gdn:
-            # the n samples of a prompt: K/V rows do not depend on the batch they are computed in, so the later samples
-            # read the first one's full prompt pages (same bits) and prefill only the page with the last prompt token
-            leaders: dict = {}
-            for s in seqs:
-                key = tuple(s.prompt_ids)
-                ld = leaders.setdefault(key, s)
-                shared = ((len(s.prompt_ids) - 1) // PAGE) * PAGE
-                if ld is not s and shared > 0:
-                    s.leader, s.shared_tokens = ld, shared
+        self.link_samples(seqs)
         while True:
             if self.paused:
                 time.sleep(0.001)

@@ -152,6 +152,7 @@ class InferenceServer:
             raise RuntimeError("server is paused; resume before sending requests")
         with self._lock:
             seqs = [self.llm.add_request(p, sp, i) for i, p in enumerate(prompts)]
+            self.llm.link_samples(seqs)            # n > 1 samples of a prompt share its KV pages
             pend = _Pending(seqs)
             self._pending.append(pend)
         if not pend.event.wait(timeout):

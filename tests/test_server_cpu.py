@@ -187,3 +187,22 @@ def test_router_routes_pins_sessions_fans_out_control_and_survives_a_dead_backen
     finally:
         router.shutdown()
         group.shutdown()
+
+
+def test_server_samples_of_one_prompt_share_pages():
+    """``n`` completions of one prompt through the HTTP server prefill the prompt once."""
+    e = _engine(pages=40)
+    srv = InferenceServer(e).start()
+    try:
+        import json
+        import urllib.request
+
+        prompt = torch.randint(0, 2048, (300,), generator=torch.Generator().manual_seed(3)).tolist()
+        req = urllib.request.Request(srv.url + "/v1/completions", data=json.dumps({"prompt": prompt, "n": 4, "max_tokens": 5, "temperature": 0.0}).encode(),
+                                     headers={"Content-Type": "application/json"})
+        with urllib.request.urlopen(req, timeout=120) as r:
+            out = json.loads(r.read())
+        assert len(out["choices"]) == 4 and len({tuple(c["token_ids"]) for c in out["choices"]}) == 1      # greedy: identical
+        assert e.scheduler.shared_prompt_tokens == 3 * 256 and e.stats["prefill_tokens"] == 300 + 3 * 44
+    finally:
+        srv.shutdown()
