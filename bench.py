@@ -116,6 +116,10 @@ def main():
         if int(os.environ.get("RANK", "0")) == 0:
             reference_arm(args)
         return
+    # NCCL only carries bootstrap, metrics and fallback byte movement here; the collectives on the hot paths are this
+    # framework's own peer-memory kernels. Every multi-GPU run of this code so far had NCCL's in-switch reduction off,
+    # so that stays the default (set NCCL_NVLS_ENABLE yourself to override).
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     import torch
     import torch.distributed as dist
 
@@ -240,7 +244,7 @@ def main():
                        "parallelism": (f"dp{ps.dp}" + (f"xtp{args.tp}" if args.tp > 1 else "") + (f"xep{args.ep}" if args.ep > 1 else "")) if world > 1 else "single",
                        "engine": (f"colocated, {world // args.engine_tp} engines x TP{args.engine_tp}, own layout, resharding weight sync every step"
                                   if trainer.separate_engine else f"colocated, {world // args.tp} engines x TP{args.tp} on the trainer's weights"),
-                       "pik_leaves": mo.get("pik_leaves", 0),
+                       "pik_leaves": mo.get("pik_leaves", 0), "nccl_nvls": os.environ.get("NCCL_NVLS_ENABLE", ""),
                        "scoring_forward": "skipped: rollout logprobs reused (VARIANT, not the reference's step)" if args.reuse_rollout_logprobs else "run",
                        "l2": "working set (16 GB of weights per pass) exceeds L2; no explicit flush"},
             "clocks": sampler.summary(),
