@@ -108,8 +108,9 @@ def _worker(rank, world, port, q):
         if rank == 0:
             q.put(res)
     finally:
-        dist.barrier()
-        dist.destroy_process_group()
+        from conftest import finish_rank
+
+        finish_rank(dist)
 
 
 @pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
@@ -244,8 +245,9 @@ def _tp_worker(rank, world, port, q):
         if rank == 0:
             q.put(res)
     finally:
-        dist.barrier()
-        dist.destroy_process_group()
+        from conftest import finish_rank
+
+        finish_rank(dist)
 
 
 @pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
@@ -361,8 +363,9 @@ def _ep_worker(rank, world, port, q):
         if rank == 0:
             q.put(res)
     finally:
-        dist.barrier()
-        dist.destroy_process_group()
+        from conftest import finish_rank
+
+        finish_rank(dist)
 
 
 @pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
@@ -452,8 +455,9 @@ def _tp_model_worker(rank, world, port, q):
             res["admitted"] = sorted(tp_ops.admitted_shapes().values())
             q.put(res)
     finally:
-        dist.barrier()
-        dist.destroy_process_group()
+        from conftest import finish_rank
+
+        finish_rank(dist)
 
 
 @pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
@@ -532,8 +536,9 @@ def _ep_model_worker(rank, world, port, q):
                    "status": [int(r[2]) for r in allr], "train_mismatches": [int(r[3]) for r in allr],
                    "grouped_autograd_blocks": [int(r[4]) for r in allr]})
     finally:
-        dist.barrier()
-        dist.destroy_process_group()
+        from conftest import finish_rank
+
+        finish_rank(dist)
 
 
 @pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
@@ -598,8 +603,9 @@ def _separate_engine_worker(rank, world, port, q):
         out["status"] = _native.read_status()
         q.put((rank, out))
     finally:
-        dist.barrier()
-        dist.destroy_process_group()
+        from conftest import finish_rank
+
+        finish_rank(dist)
 
 
 @pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
