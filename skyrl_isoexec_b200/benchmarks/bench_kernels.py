@@ -75,6 +75,26 @@ def main(argv=None):
         rows.append({"kernel": "gemm_decode", "case": f"{name} M={B} N={N} K={K}", "us": t, "tbs": N * K * 2 / t / 1e6,
                      "frac_of_measured": N * K * 2 / t / 1e6 / peaks["hbm_tbs"]})
         if name != "lm_head":
+            # the same decode GEMM as the device sees it inside a step: launches queued back to back over enough weight
+            # copies to exceed L2 (the row above times one call at a time and so includes the host's launch path)
+            copies = [w] + [w.clone() for _ in range(max(1, (600 << 20) // (N * K * 2)))]
+
+            def queue(fn):
+                def run():
+                    for c in copies:
+                        fn(c)
+                return run
+
+            t = timeit(queue(lambda c: F.gemm_nt(x, c)), do_flush=False) / len(copies)
+            rows.append({"kernel": "gemm_decode_queued", "case": f"{name} M={B} N={N} K={K}", "us": t, "tbs": N * K * 2 / t / 1e6,
+                         "frac_of_measured": N * K * 2 / t / 1e6 / peaks["hbm_tbs"]})
+            if name in ("o", "down") and K % 128 == 0:
+                from ..parallel import tp_fused
+
+                t = timeit(queue(lambda c: tp_fused.leaftree_gemm_fused(x, c, 2, out_f32=False)), do_flush=False) / len(copies)
+                rows.append({"kernel": "gemm_decode_queued", "case": f"{name} M={B} N={N} K={K}, 2-leaf tree (one CTA per leaf)", "us": t,
+                             "tbs": N * K * 2 / t / 1e6, "frac_of_measured": N * K * 2 / t / 1e6 / peaks["hbm_tbs"]})
+            del copies
             xl = torch.randn(M, K, device=dev).bfloat16()
             t = timeit(lambda: F.gemm_nt(xl, w), do_flush=False)
             tf = 2 * M * N * K / t / 1e6
