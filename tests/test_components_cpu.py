@@ -995,3 +995,56 @@ def test_sft_chat_records_loss_masks_eval_callbacks_export_and_cache(tmp_path):
     tr2 = SFTTrainer(SFTConfig(model="tiny-qwen3", batch_size=2, max_seq_len=64, dummy_steps=2, logger="jsonl"), [], device="cpu")
     tr2.train()
     assert tr2.global_step == 2
+
+
+def test_generator_utils_metrics_filtering_chat_masks_and_stepwise_merge(tmp_path):
+    from skyrl_isoexec_b200.train import generator_utils as GU
+
+    # trajectory- and token-level rewards
+    m = GU.get_metrics_from_generator_output({"rewards": [1.0, 0.0, -1.0, 0.0]}, ["a", "a", "b", "b"])
+    assert m == {"avg_score": 0.0, "mean_positive_reward": 0.25, "pass_at_n": 0.5}
+    m = GU.get_metrics_from_generator_output({"rewards": [[0.0, 1.0], [0.5, -0.5], [0.0, 0.0]]}, ["a", "a", "b"])
+    assert m["avg_score"] == pytest.approx(1 / 3) and m["pass_at_n"] == 0.5 and m["mean_positive_reward"] == pytest.approx(0.5)
+    with pytest.raises(ValueError):
+        GU.get_metrics_from_generator_output({"rewards": []}, [])
+    assert GU.apply_overlong_filtering([[1, 1], [1, 0, 1]], ["stop", "length"]) == [[1, 1], [0, 0, 0]]
+    assert GU.compute_turn_token_counts([[1, 1, 0, 0, 1], [0, 0], [], [0, 1, 1, 1]]) == [2, 1, 3]
+    # chat templates
+    assert "im_start" in GU.get_custom_chat_template({"source": "name", "name_or_path": "qwen3_with_thinking"})
+    f = tmp_path / "t.jinja"
+    f.write_text("{{ messages }}")
+    assert GU.get_custom_chat_template({"source": "file", "name_or_path": str(f)}) == "{{ messages }}"
+    assert GU.get_custom_chat_template(None) is None
+    with pytest.raises(ValueError):
+        GU.get_custom_chat_template({"source": "name", "name_or_path": "nope"})
+
+    class ByteTok:
+        def encode(self, text):
+            return list(text.encode())
+
+    tok = ByteTok()
+    gen = GU.get_generation_prompt_ids(tok)
+    assert bytes(gen).decode() == "<|assistant|>\n"
+    msgs = [{"role": "assistant", "content": "let me look"}, {"role": "user", "content": "<observation>4</observation>"},
+            {"role": "assistant", "content": "four"}]
+    lp = [[-0.1] * len("let me look"), [-0.2] * len("four")]
+    ids, mask, lps = GU.get_response_ids_and_loss_mask_from_messages(msgs, tok, lp)
+    text = bytes(ids).decode()
+    assert text == "<|assistant|>\nlet me look<|end|>\n<|user|>\n<observation>4</observation><|end|>\n<|assistant|>\nfour<|end|>\n"
+    trained = bytes(t for t, k in zip(ids, mask) if k).decode()
+    assert trained == "let me lookfour" and len(lps) == len(ids)
+    assert [round(x, 1) for x, k in zip(lps, mask) if k] == [-0.1] * 11 + [-0.2] * 4 and all(x == 0.0 for x, k in zip(lps, mask) if not k)
+    assert bytes(GU.encode_messages_subset([msgs[1]], tok)).decode() == "<|user|>\n<observation>4</observation><|end|>\n"
+    # step-wise rows of two trajectories back to one row each
+    so = {"trajectory_ids": ["t0", "t1", "t0"], "is_last_step": [False, True, True],
+          "prompt_token_ids": [[1, 2], [7], [1, 2, 3, 4, 9, 9]], "response_ids": [[3, 4], [8], [5]],
+          "loss_masks": [[1, 1], [1], [1]], "rewards": [0.0, 1.0, 2.0], "stop_reasons": ["stop", "stop", "length"],
+          "rollout_logprobs": [[-1.0, -2.0], [-3.0], [-4.0]]}
+    mo = GU.merge_stepwise_output(so)
+    assert mo["trajectory_ids"] == ["t0", "t1"] and mo["prompt_token_ids"] == [[1, 2], [7]]
+    assert mo["response_ids"] == [[3, 4, 9, 9, 5], [8]] and mo["loss_masks"] == [[1, 1, 0, 0, 1], [1]]
+    assert mo["rollout_logprobs"] == [[-1.0, -2.0, 0.0, 0.0, -4.0], [-3.0]] and mo["rewards"] == [2.0, 1.0]
+    assert mo["stop_reasons"] == ["length", "stop"]
+    bad = dict(so, prompt_token_ids=[[1, 2], [7], [1, 2, 5, 5, 9]])
+    with pytest.raises(ValueError):
+        GU.merge_stepwise_output(bad)
