@@ -636,6 +636,7 @@ class PolicyWorker:
         # forward is skipped)
         check_bits = bool(batch.metadata.get("check_rollout_bits")) and batch.get("rollout_logprobs") is not None
         bits = {"mismatches": 0, "abs_sum": 0.0, "abs_max": 0.0, "tokens": 0.0}
+        post = {"sum": 0.0, "sq": 0.0, "max": 0.0, "tokens": 0.0}
         dev = self.device
         mbs = self._pack(seqs, att, R)
         for mi, mb in enumerate(mbs):
@@ -663,6 +664,17 @@ class PolicyWorker:
                 old = lp2d.detach()
             loss, m = loss_fn(lp2d, old, get("advantages"), algo, loss_mask=mask, rollout_logprobs=get("rollout_logprobs"))
             ntok = mask.sum()
+            if batch.get("rollout_logprobs") is not None and self.ps.cp == 1:
+                # |logprob the loss optimises against - rollout logprob| over the trained tokens: the policy's drift since
+                # the rollout once optimizer steps have happened between mini-batches (never the forward-identity gate;
+                # R/backends/skyrl_train/workers/worker_utils.py:39-64)
+                sel = mask > 0
+                d_ = torch.where(sel, (lp2d.detach() - get("rollout_logprobs")).abs(), torch.zeros_like(lp2d))
+                s_ = torch.stack([d_.sum(), (d_ * d_).sum(), d_.max() if d_.numel() else d_.sum(), sel.sum().to(d_.dtype)]).tolist()
+                post["sum"] += s_[0]
+                post["sq"] += s_[1]
+                post["max"] = max(post["max"], s_[2])
+                post["tokens"] += s_[3]
             if check_bits:
                 from ..core.testing import count_bit_mismatches
 
@@ -701,6 +713,8 @@ class PolicyWorker:
                "policy_entropy": tot["entropy_sum"] / n, "policy_kl": tot["kl_sum"] / n}
         if check_bits:
             out["rollout_bits"] = bits
+        if post["tokens"] > 0:
+            out["post_update_diff"] = post
         return out
 
     def _overlap_ok(self) -> bool:

@@ -575,12 +575,20 @@ class RayPPOTrainer:
             return float(t.item())
         return x
 
+    def _global_max(self, x: float) -> float:
+        if self.ps.dp > 1:
+            t = torch.tensor([x], dtype=torch.float64, device=self.device if self.device.type == "cuda" else "cpu")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.ps.dp_group)
+            return float(t.item())
+        return x
+
     def train_critic_and_policy(self, batch: TrainingInputBatch) -> dict:
         t, a = self.cfg.trainer, self.cfg.trainer.algorithm
         n_samples = self.cfg.generator.n_samples_per_prompt
         mb_seqs = (t.policy_mini_batch_size * n_samples) // max(1, self.ps.dp)
         B = batch.batch_size
         out = {"policy_loss": 0.0, "ppo_clip_ratio": 0.0, "grad_norm": 0.0, "policy_entropy": 0.0, "policy_kl": 0.0}
+        post = {"sum": 0.0, "sq": 0.0, "max": 0.0, "tokens": 0.0}
         n_updates = 0
         if getattr(self, "critic", None) is not None:
             closs = 0.0
@@ -626,10 +634,21 @@ class RayPPOTrainer:
                 out["policy_kl"] += m["policy_kl"]
                 out["grad_norm"] += gn
                 n_updates += 1
+                if m.get("post_update_diff"):
+                    for k_ in ("sum", "sq", "tokens"):
+                        post[k_] += m["post_update_diff"][k_]
+                    post["max"] = max(post["max"], m["post_update_diff"]["max"])
         for k in out:
             out[k] /= max(1, n_updates)
         out["policy_loss"] = self._global_sum(out["policy_loss"])
         self.all_metrics.update({f"policy/{k}": v for k, v in out.items()})
+        ntok = self._global_sum(post["tokens"])
+        if ntok > 0:
+            mean = self._global_sum(post["sum"]) / ntok
+            var = max(0.0, self._global_sum(post["sq"]) / ntok - mean * mean)
+            self.all_metrics.update({"policy/post_update_rollout_logprobs_abs_diff_mean": mean,
+                                     "policy/post_update_rollout_logprobs_abs_diff_std": var ** 0.5,
+                                     "policy/post_update_rollout_logprobs_abs_diff_max": self._global_max(post["max"])})
         self.all_metrics["policy/policy_lr"] = self.policy.opt.lr_at(max(0, self.policy.opt.step_count - 1))
         return out
 

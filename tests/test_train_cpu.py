@@ -327,3 +327,25 @@ def test_reference_config_keys_are_wired_or_refused(tmp_path):
     with pytest.raises(ValueError):
         validate_cfg(SkyRLTrainConfig.from_cli_overrides(base + ["trainer.placement.policy_num_gpus_per_node=4",
                                                                  "trainer.policy.parallel.tensor_model_parallel_size=1"]), 2)
+
+
+def test_post_update_drift_metrics_are_zero_on_policy_and_positive_after_a_step(tmp_path):
+    """With one mini-batch per batch the training forward IS the rollout policy: the drift metrics are exactly 0. With two
+    mini-batches the second one is trained after an optimizer step and shows a positive drift."""
+    from skyrl_isoexec_b200.train.config import SkyRLTrainConfig
+    from skyrl_isoexec_b200.train.trainer import RayPPOTrainer
+
+    def run(mini):
+        ov = ["trainer.policy.model=tiny-qwen3", "trainer.train_batch_size=4", f"trainer.policy_mini_batch_size={mini}",
+              "generator.n_samples_per_prompt=2", "generator.sampling_params.max_generate_length=8", "data.synthetic_prompt_len=12",
+              "trainer.num_steps=1", "trainer.logger=jsonl", f"trainer.ckpt_path={tmp_path}/c{mini}", "trainer.ckpt_interval=0",
+              "environment.env_class=even_tokens", "trainer.policy.optimizer_config.lr=1e-2"]
+        tr = RayPPOTrainer(SkyRLTrainConfig.from_cli_overrides(ov), device="cpu")
+        tr.build_models()
+        tr.train()
+        return tr.all_metrics
+
+    m = run(4)
+    assert m["policy/post_update_rollout_logprobs_abs_diff_mean"] == 0.0 and m["policy/post_update_rollout_logprobs_abs_diff_max"] == 0.0
+    m2 = run(2)
+    assert m2["policy/post_update_rollout_logprobs_abs_diff_max"] > 0.0 and m2["policy/post_update_rollout_logprobs_abs_diff_std"] >= 0.0
