@@ -27,6 +27,8 @@
 //     that may run at the same time on the GPU (different streams without an ordering between
 //     them) race on it: order them on one stream or with events. Nothing needs clearing
 //     between calls, because a call only reads back the partials it has just written;
+//   * the array used is the one of the CURRENT device (cudaGetDevice at the time of the call): make the device that
+//     `stream` belongs to current before calling, as for any launch on that stream;
 //   * it calls no cudaMalloc / cudaFree and no allocating library routine.
 #pragma once
 
