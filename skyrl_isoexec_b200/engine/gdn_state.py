@@ -37,6 +37,10 @@ class GDNStatePool:
         self.row_of: dict[int, int] = {}
         self.epoch = 0
         self.invalidations = {"weight_sync": 0, "sleep_wake": 0}
+        # boundary states kept for the samples of one prompt: {leader seq id: [per-layer (conv tail, fp32 state), users left]}
+        # (a narrow form of the reference's prefix-keyed boundary store, ISO/ops/gdn/gdn_cpr_state.py:96-197: keyed by the
+        # request that computed the prefix, alive only while its siblings wait)
+        self.snapshots: dict[int, list] = {}
 
     def _row(self, seq_id: int) -> int:
         if seq_id not in self.row_of:
@@ -49,12 +53,36 @@ class GDNStatePool:
         r = self.row_of.pop(seq_id, None)
         if r is not None:
             self.free.append(r)
+        self.snapshots.pop(seq_id, None)
+
+    # ------------------------------------------------------------------ boundary snapshots (samples of one prompt)
+    def snapshot(self, seq_id: int, users: int) -> None:
+        """Copy the sequence's conv tail and fp32 state of every GDN layer as they stand now (called right after the step
+        that brought its prefill to a chunk boundary, where its open chunk is empty)."""
+        r = self.row_of[seq_id]
+        self.snapshots[seq_id] = [{i: (st[0][r].clone(), st[1][r].clone()) for i, st in self.states.items()}, int(users)]
+
+    def has_snapshot(self, seq_id: int) -> bool:
+        return seq_id in self.snapshots
+
+    def adopt(self, seq_id: int, leader_id: int) -> None:
+        """Start ``seq_id`` from the leader's boundary state: its row gets the snapshot's bits."""
+        snap = self.snapshots[leader_id]
+        r = self._row(seq_id)
+        for i, st in self.states.items():
+            conv, ssm = snap[0][i]
+            st[0][r].copy_(conv)
+            st[1][r].copy_(ssm)
+        snap[1] -= 1
+        if snap[1] <= 0:
+            del self.snapshots[leader_id]
 
     def invalidate(self, event: str) -> None:
         """Drop every sequence's state (``weight_sync`` / ``sleep_wake``)."""
         assert event in ("weight_sync", "sleep_wake")
         self.free = list(range(self.rows - 1, 0, -1))
         self.row_of.clear()
+        self.snapshots.clear()
         self.epoch += 1
         self.invalidations[event] += 1
 

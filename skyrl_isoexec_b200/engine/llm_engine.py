@@ -35,6 +35,8 @@ class EngineConfig:
     enable_prefix_caching: bool = False  # the contract pins this off (state claim engine_prefix_cache)
     use_cuda_graph: bool = True
     share_prompt_pages: bool = True      # samples of one prompt share its full KV pages (not a cache: freed with the requests)
+    share_recurrent_state: bool = False  # models with GatedDeltaNet layers: siblings also start from the leader's recurrent
+                                         # state at the shared boundary (a snapshot taken when its prefill gets there)
 
 
 @dataclass
@@ -54,6 +56,8 @@ class Sequence:
     # leader's full prompt pages (all but the page holding the last prompt token) instead of recomputing them.
     leader: "Sequence | None" = None
     shared_tokens: int = 0
+    snapshot_at: int = 0           # leader of a model with recurrent layers: its prefill stops here once, for a state snapshot
+    snapshot_users: int = 0
 
     @property
     def tokens(self) -> list[int]:
@@ -86,6 +90,8 @@ class Scheduler:
         self.running: list[Sequence] = []
         self.preemptions = 0
         self.shared_prompt_tokens = 0       # prompt tokens taken from a leader's pages instead of being prefilled
+        self.can_adopt = None               # engine hooks for models with recurrent state: (sibling, leader) -> bool / None
+        self.adopt_hook = None
 
     def add(self, seq: Sequence) -> None:
         self.waiting.append(seq)
@@ -108,6 +114,14 @@ class Scheduler:
         seq.num_computed = 0
         seq.leader = None
         self.waiting.appendleft(seq)
+
+    @staticmethod
+    def _chunk(s: Sequence, budget: int) -> int:
+        """Tokens of ``s`` to prefill now: what is left, within the budget, and not across a pending snapshot boundary."""
+        n = min(s.length - s.num_computed, budget)
+        if s.snapshot_at and s.num_computed < s.snapshot_at:
+            n = min(n, s.snapshot_at - s.num_computed)
+        return n
 
     def schedule(self):
         """Returns (decode_seqs, prefill list of (seq, start, n))."""
@@ -139,7 +153,7 @@ class Scheduler:
         for s in still_prefilling:
             if budget <= 0:
                 break
-            n = min(s.length - s.num_computed, budget)
+            n = self._chunk(s, budget)
             if not self._ensure_pages(s, s.num_computed + n):
                 continue
             prefill.append((s, s.num_computed, n))
@@ -154,13 +168,18 @@ class Scheduler:
                 elif ld.num_computed < s.shared_tokens:
                     i += 1                               # the shared prompt pages are not written yet: later sequences first
                     continue
+                elif self.can_adopt is not None and not self.can_adopt(s, ld):
+                    i += 1                               # the leader's recurrent state at the boundary is not snapshotted yet
+                    continue
                 else:
                     s.pages = list(ld.pages[:s.shared_tokens // PAGE])
                     self.cache.allocator.share(s.pages)
                     s.num_computed = s.shared_tokens
                     s.leader = None
                     self.shared_prompt_tokens += s.shared_tokens
-            n = min(s.length - s.num_computed, budget)
+                    if self.adopt_hook is not None:
+                        self.adopt_hook(s, ld)
+            n = self._chunk(s, budget)
             if not self._ensure_pages(s, s.num_computed + n):
                 break
             del self.waiting[i]
@@ -209,6 +228,9 @@ class LLMEngine:
             from .gdn_state import GDNStatePool
 
             self.gdn_state = GDNStatePool(self.mcfg, self.cfg.max_num_seqs, self.device, tp=model.ps.tp)
+            if self.cfg.share_prompt_pages and self.cfg.share_recurrent_state:
+                self.scheduler.can_adopt = lambda s, ld: self.gdn_state.has_snapshot(ld.seq_id)
+                self.scheduler.adopt_hook = lambda s, ld: self.gdn_state.adopt(s.seq_id, ld.seq_id)
 
     def _auto_pages(self) -> int:
         per_page = KVCache.bytes_per_page(self.mcfg, self.model.ps.tp)
@@ -353,6 +375,8 @@ class LLMEngine:
             s.num_computed += 1
         for s, start, n in prefill:
             s.num_computed = start + n
+            if s.snapshot_at and start + n == s.snapshot_at and self.gdn_state is not None and s.snapshot_users > 0:
+                self.gdn_state.snapshot(s.seq_id, s.snapshot_users)          # the siblings of this prompt start from here
         self.stats["steps"] += 1
         self.stats["tokens"] += row
         self.stats["decode_tokens"] += len(decode)
@@ -530,8 +554,10 @@ class LLMEngine:
         sibling of it: the n samples of a prompt then read the first one's full prompt pages instead of prefilling them
         again (K/V rows do not depend on the batch they are computed in, so the bits are the same) and prefill only
         the page that holds the last prompt token. Returns the number of siblings made. Models with recurrent layers are
-        left alone: a sibling would also need the leader's recurrent state at the shared boundary."""
-        if not self.cfg.share_prompt_pages or self.mcfg.has_gdn:
+        linked only with ``share_recurrent_state``: the leader's prefill then stops once at the shared boundary, its
+        recurrent state is snapshotted there, and a sibling starts from the snapshot."""
+        recurrent = self.mcfg.has_gdn
+        if not self.cfg.share_prompt_pages or (recurrent and not self.cfg.share_recurrent_state):
             return 0
         leaders: dict = {}
         n = 0
@@ -539,9 +565,11 @@ class LLMEngine:
             if s.num_computed or s.pages or s.output_ids:
                 continue                                        # already under way
             ld = leaders.setdefault(tuple(s.prompt_ids), s)
-            shared = ((len(s.prompt_ids) - 1) // PAGE) * PAGE
+            shared = ((len(s.prompt_ids) - 1) // PAGE) * PAGE   # a multiple of the GatedDeltaNet chunk too: no open chunk there
             if ld is not s and shared > 0:
                 s.leader, s.shared_tokens = ld, shared
+                if recurrent:
+                    ld.snapshot_at, ld.snapshot_users = shared, ld.snapshot_users + 1
                 n += 1
         return n
 

@@ -86,6 +86,7 @@ class InferenceEngineConfig:
     enforce_eager: bool = False
     enable_prefix_caching: bool = False
     share_prompt_pages: bool = True     # the n samples of a prompt read one copy of its full KV pages (same bits; not a cache)
+    share_recurrent_state: bool = False # GatedDeltaNet models: the samples also start from one snapshot of the recurrent state
     weight_sync_backend: str = "nccl"   # nccl | gloo | cuda_ipc | shared
     run_engines_locally: bool = True
 

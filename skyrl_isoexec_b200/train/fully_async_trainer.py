@@ -277,7 +277,7 @@ class FullyAsyncTrainerSim(FullyAsyncTrainer):
         ecfg = EngineConfig(max_num_seqs=ie.max_num_seqs, max_num_batched_tokens=ie.max_num_batched_tokens,
                             num_kv_pages=ie.num_kv_pages, gpu_memory_utilization=ie.gpu_memory_utilization,
                             seed=t.seed + 7919 * self.ps.dp_rank, enable_prefix_caching=ie.enable_prefix_caching,
-                            use_cuda_graph=not ie.enforce_eager, share_prompt_pages=ie.share_prompt_pages,
+                            use_cuda_graph=not ie.enforce_eager, share_prompt_pages=ie.share_prompt_pages, share_recurrent_state=ie.share_recurrent_state,
                             max_model_len=min(mcfg.max_position, t.max_prompt_length + g.sampling_params.max_generate_length + 1))
         self.engine = LLMEngine(model, ecfg)
         self.infer = NativeInferenceEngine(self.engine, self.tokenizer)

@@ -311,7 +311,7 @@ class RayPPOTrainer:
                             # one sampler stream per engine; the ranks of one engine share it
                             seed=t.seed + 7919 * self._engine_index(),
                             enable_prefix_caching=ie.enable_prefix_caching,
-                            use_cuda_graph=not ie.enforce_eager, share_prompt_pages=ie.share_prompt_pages,
+                            use_cuda_graph=not ie.enforce_eager, share_prompt_pages=ie.share_prompt_pages, share_recurrent_state=ie.share_recurrent_state,
                             max_model_len=min(mcfg.max_position, t.max_prompt_length + g.sampling_params.max_generate_length + 1))
         if self.separate_engine:
             # engines of their own layout: a second set of (sharded) weights per GPU, filled by the resharding sync

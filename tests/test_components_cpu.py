@@ -1048,3 +1048,45 @@ def test_generator_utils_metrics_filtering_chat_masks_and_stepwise_merge(tmp_pat
     bad = dict(so, prompt_token_ids=[[1, 2], [7], [1, 2, 5, 5, 9]])
     with pytest.raises(ValueError):
         GU.merge_stepwise_output(bad)
+
+
+def test_samples_of_one_prompt_share_recurrent_state_in_a_hybrid_model():
+    """GatedDeltaNet layers: the siblings of a prompt start from the leader's recurrent state, snapshotted when its
+    prefill reaches the shared boundary. Greedy outputs and logprobs equal the unshared run, the sampled run's logprobs
+    equal the trainer's forward, snapshots and state rows are all given back."""
+    from skyrl_isoexec_b200.core.testing import count_bit_mismatches
+    from skyrl_isoexec_b200.engine.llm_engine import EngineConfig, LLMEngine
+    from skyrl_isoexec_b200.engine.sampler import SamplingParams
+    from skyrl_isoexec_b200.models.config import get_config
+    from skyrl_isoexec_b200.models.decoder import DecoderLM
+    from skyrl_isoexec_b200.train.batch import TrainingInputBatch, build_sequences
+    from skyrl_isoexec_b200.train.policy_worker import PolicyWorker, WorkerConfig
+
+    cfg = get_config("tiny-hybrid")
+    model = DecoderLM(cfg, device="cpu", seed=6)
+    g = torch.Generator().manual_seed(8)
+    base = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (300, 140)]
+    prompts = [p for p in base for _ in range(3)]
+
+    def run(share, sp, budget=512):
+        eng = LLMEngine(model, EngineConfig(max_num_seqs=6, num_kv_pages=30, max_num_batched_tokens=budget, share_recurrent_state=share))
+        outs = eng.generate(prompts, sp)
+        assert eng.cache.allocator.num_free == 30 and not eng.gdn_state.snapshots and not eng.gdn_state.row_of
+        return eng, outs
+
+    greedy = SamplingParams(max_generate_length=8, ignore_eos=True, temperature=0.0)
+    e0, o0 = run(False, greedy)
+    e1, o1 = run(True, greedy)
+    assert e0.scheduler.shared_prompt_tokens == 0 and e1.scheduler.shared_prompt_tokens == 2 * (256 + 128)
+    assert [o.response_ids for o in o0] == [o.response_ids for o in o1]
+    assert [o.response_logprobs for o in o0] == [o.response_logprobs for o in o1]
+    e2, o2 = run(True, greedy, budget=200)                        # the leader reaches the boundary over several chunks
+    assert [o.response_logprobs for o in o2] == [o.response_logprobs for o in o0]
+    e3, o3 = run(True, SamplingParams(max_generate_length=9, ignore_eos=True))
+    seq, att, rmask = build_sequences([o.prompt_ids for o in o3], [o.response_ids for o in o3])
+    lp = PolicyWorker(model, WorkerConfig(max_tokens_per_microbatch=1024)).forward(
+        TrainingInputBatch({"sequences": seq, "attention_mask": att, "response_mask": rmask}))
+    ro = torch.zeros_like(lp)
+    for i, o in enumerate(o3):
+        ro[i, :len(o.response_logprobs)] = torch.tensor(o.response_logprobs)
+    assert count_bit_mismatches((lp * rmask).contiguous(), (ro * rmask).contiguous()) == 0
