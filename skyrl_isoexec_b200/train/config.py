@@ -174,6 +174,8 @@ class TrainerConfig:
     seed: int = 42
     recompute_old_logprobs_per_minibatch: bool = False
     dump_data_batch: bool = False
+    balance_dp_by_length: bool = False   # after generation, deal whole prompt groups out over the data-parallel ranks so that
+                                         # every rank scores and trains on about the same number of tokens
     num_steps: int = -1                 # stop after this many global steps (-1: run the epochs out)
     profiler: ProfilerConfig = field(default_factory=ProfilerConfig)    # torch.profiler over a window of steps
     nvtx: bool = False                  # NVTX range around every phase of a step (for timeline tools)

@@ -437,6 +437,39 @@ class RayPPOTrainer:
                                                         [merged["env_metrics"][i] for i in sel] if merged.get("env_metrics") else None)
         return merged
 
+    def balance_rollouts(self, go: GeneratorOutput, uids: list[str]):
+        """Length-balanced data parallelism (reference: B/utils/ep_balance.py, DP row striping by length): the rollouts of
+        all data-parallel ranks are pooled, whole prompt groups (the samples of one prompt stay together, as the group
+        statistics of the advantage need them) are dealt out longest first in a serpentine, and every rank continues
+        with its share: same number of groups everywhere, nearly the same number of tokens. Returns (go, uids)."""
+        from .moe_utils import balanced_dp_assignment, imbalance
+
+        ps = self.ps
+        if ps.dp == 1 or go.get("step_source") is not None:
+            return go, uids
+        B = len(uids)
+        cols = {k: v for k, v in go.items() if isinstance(v, list) and len(v) == B}
+        pooled: list = [None] * ps.dp
+        dist.all_gather_object(pooled, (cols, list(uids)), group=ps.dp_group)
+        groups: dict = {}
+        for r, (c, u) in enumerate(pooled):
+            for i, uid in enumerate(u):
+                groups.setdefault((r, uid), []).append((r, i))                 # uids repeat across ranks: keep the origin
+        keys = list(groups)
+        lens = [sum(len(pooled[r][0]["prompt_token_ids"][i]) + len(pooled[r][0]["response_ids"][i]) for r, i in groups[k]) for k in keys]
+        if len(keys) % ps.dp:
+            return go, uids
+        assign = balanced_dp_assignment(lens, ps.dp)
+        before = imbalance(lens, [[j for j, k in enumerate(keys) if k[0] == r] for r in range(ps.dp)])
+        mine = sorted(assign[ps.dp_rank])
+        out = dict(go)
+        for k in cols:
+            out[k] = [pooled[r][0][k][i] for j in mine for r, i in groups[keys[j]]]
+        new_uids = [f"{keys[j][0]}:{keys[j][1]}" for j in mine for _ in groups[keys[j]]]
+        self.all_metrics["generate/dp_token_imbalance_before"] = before
+        self.all_metrics["generate/dp_token_imbalance_after"] = imbalance(lens, assign)
+        return out, new_uids
+
     def convert_to_training_input(self, go: GeneratorOutput, uids: list[str]) -> TrainingInputBatch:
         seq, att, rmask = build_sequences(go["prompt_token_ids"], go["response_ids"])
         B, R = rmask.shape
@@ -787,6 +820,8 @@ class RayPPOTrainer:
                 dec = self.tokenizer.decode if self.tokenizer is not None else str
                 log_example(dec(list(go["prompt_token_ids"][0])), dec(list(go["response_ids"][0])), go["rewards"][0])
             with Timer("convert", T):
+                if self.cfg.trainer.balance_dp_by_length:
+                    go, uids = self.balance_rollouts(go, uids)
                 batch = self.convert_to_training_input(go, uids)
             if self.cfg.trainer.dump_data_batch and self.cfg.trainer.ckpt_path:
                 d = os.path.join(self.cfg.trainer.ckpt_path, "dumped_data")
