@@ -13,6 +13,7 @@ steps, length statistics of the tokenized set, and ``dummy_steps`` for timing ru
 
 from __future__ import annotations
 
+import json
 import random
 from dataclasses import dataclass, field
 
@@ -54,6 +55,32 @@ class SFTConfig:
     export_path: str = ""
     hf_save_interval: int = 0             # every N steps; 0 with export_path set: once, at the end
     dummy_steps: int = 0                  # > 0: ignore the data, train on synthetic rows of max_seq_len tokens (timing runs)
+
+    @classmethod
+    def from_file(cls, path: str, overrides: list[str] | None = None) -> "SFTConfig":
+        """A YAML or JSON file of these fields (nested under ``optimizer:`` for the optimizer's), then ``key=value``
+        overrides with dotted keys (``optimizer.lr=3e-6``), the same forms the RL trainer's config takes."""
+        from .config import _flatten, set_by_path
+
+        with open(path, encoding="utf-8") as f:
+            text = f.read()
+        if path.endswith(".json"):
+            tree = json.loads(text)
+        else:
+            import yaml
+
+            tree = yaml.safe_load(text) or {}
+        cfg = cls()
+        for key, val in _flatten(tree):
+            if isinstance(val, (dict, list)):
+                val = json.dumps(val)
+            set_by_path(cfg, key, "none" if val is None else str(val))
+        for ov in overrides or []:
+            if "=" not in ov:
+                raise ValueError(f"override {ov!r} is not key=value")
+            key, val = ov.split("=", 1)
+            set_by_path(cfg, key.lstrip("+"), val)
+        return cfg
 
 
 class SFTTrainer:

@@ -752,6 +752,12 @@ def test_generate_sft_and_serve_entry_points(tmp_path):
                                 "response_ids": torch.randint(0, 500, (7,), generator=g).tolist()}) + "\n")
     tr = main_sft.main(["--data", str(data), "--batch-size", "3", "--num-steps", "2", "--lr", "1e-3", "--logger", "jsonl"])
     assert tr.global_step == 2
+    # a config file, a key=value override of it, and a command-line option that overrides both
+    (tmp_path / "sft.yaml").write_text("model: tiny-qwen3\nbatch_size: 2\nnum_steps: 5\nlogger: jsonl\noptimizer:\n  lr: 1.0e-3\n  weight_decay: 0.0\n")
+    tr = main_sft.main(["--data", str(data), "--config", str(tmp_path / "sft.yaml"), "--num-steps", "1", "optimizer.lr=2e-3", "batch_size=3"])
+    assert tr.global_step == 1 and tr.cfg.batch_size == 3 and tr.cfg.optimizer.lr == 2e-3 and tr.cfg.optimizer.weight_decay == 0.0
+    with pytest.raises(KeyError):
+        main_sft.SFTConfig.from_file(str(tmp_path / "sft.yaml"), ["no_such_field=1"])
     srv = serve.build(["--model", "tiny-qwen3", "--num-kv-pages", "16", "--device", "cpu"]).start()
     try:
         with urllib.request.urlopen(srv.url + "/health", timeout=10) as r:
