@@ -145,19 +145,22 @@ class Ledger:
         }
 
     def write_verdict(self, directory: str) -> str:
-        os.makedirs(directory, exist_ok=True)
-        path = os.path.join(directory, f"enforcement.{self.side}.r{self.rank}.json")
-        with open(path, "w") as f:
+        from ..utils import io as uio
+
+        path = directory.rstrip("/") + f"/enforcement.{self.side}.r{self.rank}.json"
+        with uio.open_file(path, "w") as f:               # makes the directory when local; any fsspec scheme otherwise
             json.dump(self.verdict(), f, indent=1, sort_keys=True)
         return path
 
 
 def merge_verdicts(directory: str) -> dict:
     """Fold every ``enforcement.*.json`` of a run: ok only if all are ok and all carry one hash."""
-    files = sorted(f for f in os.listdir(directory) if f.startswith("enforcement.") and f.endswith(".json"))
+    from ..utils import io as uio
+
+    files = sorted(f for f in uio.list_dir(directory) if f.startswith("enforcement.") and f.endswith(".json"))
     verdicts = []
     for f in files:
-        with open(os.path.join(directory, f)) as fh:
+        with uio.open_file(directory.rstrip("/") + "/" + f) as fh:
             verdicts.append(json.load(fh))
     hashes = {v["numerical_policy"] for v in verdicts}
     viol = [m for v in verdicts for m in v["violations"]]

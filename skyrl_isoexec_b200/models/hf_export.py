@@ -180,10 +180,12 @@ def save_hf(model: DecoderLM, path: str, write: bool = True) -> None:
     sd = to_hf_state_dict(model)
     if not write:
         return
-    os.makedirs(path, exist_ok=True)
-    save_file(sd, os.path.join(path, "model.safetensors"), metadata={"format": "pt"})
-    with open(os.path.join(path, "config.json"), "w") as f:
-        json.dump(hf_config(model.cfg), f, indent=1)
+    from ..utils import io as uio
+
+    with uio.local_work_dir(path) as d:                 # a remote ``path`` is written locally and uploaded on exit
+        save_file(sd, os.path.join(d, "model.safetensors"), metadata={"format": "pt"})
+        with open(os.path.join(d, "config.json"), "w") as f:
+            json.dump(hf_config(model.cfg), f, indent=1)
 
 
 def load_hf(model: DecoderLM, path: str) -> int:

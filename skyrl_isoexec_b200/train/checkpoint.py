@@ -16,18 +16,29 @@ shape, shard dim and sections so a checkpoint written at one TP degree loads at 
 (parameters are reassembled to full shape and re-sliced). The step directory is written under
 a temporary name and renamed, and ``latest_ckpt_global_step.txt`` is replaced last, so a crash
 mid-save never leaves a directory that ``resume_mode=latest`` would pick up.
+
+``ckpt_path`` (and ``resume_path``) may name an object store or any other fsspec scheme (``s3://``, ``gs://`` ...;
+``utils/io.py``): every rank then writes its files into a private temporary directory and uploads them, rank 0 replaces
+the remote ``latest_ckpt_global_step.txt`` after all uploads returned (a step directory without that marker pointing at it
+is never resumed from) and deletes the steps beyond ``max_to_keep``; a resume downloads the step directory once per node
+into a staging directory that lives until the process exits.
 """
 
 from __future__ import annotations
 
+import atexit
+import hashlib
 import json
 import os
 import random
 import re
 import shutil
+import tempfile
 
 import torch
 import torch.distributed as dist
+
+from ..utils import io as uio
 
 LATEST = "latest_ckpt_global_step.txt"
 _STEP_RE = re.compile(r"^global_step_(\d+)$")
@@ -46,18 +57,12 @@ def step_dir(ckpt_path: str, step: int) -> str:
     return os.path.join(ckpt_path, f"global_step_{step}")
 
 
-def save_checkpoint(ckpt_path: str, step: int, policy, data_state: dict, trainer_state: dict, ps, max_to_keep: int = -1,
-                    extra_shards: dict | None = None) -> str:
-    """``extra_shards``: ``{folder: this rank's state}`` written as ``{folder}/__{rank}_0.distcp`` beside ``policy/``."""
-    final = step_dir(ckpt_path, step)
-    tmp = final + ".tmp"
+def _write_step(tmp: str, step: int, policy, data_state: dict, trainer_state: dict, ps, extra_shards: dict | None) -> list[str]:
+    """This rank's files of one checkpoint into the directory ``tmp``; returns their paths relative to ``tmp``."""
     rank = _rank()
-    if rank == 0:
-        if os.path.isdir(tmp):
-            shutil.rmtree(tmp)
-        os.makedirs(os.path.join(tmp, "policy"), exist_ok=True)
-    _barrier()
     model = policy.model
+    wrote = []
+    os.makedirs(os.path.join(tmp, "policy"), exist_ok=True)
     shard = {
         "model": {name: t.detach().cpu().clone() for name, t in model.named_weights()},
         "optimizer": {k: (v.detach().cpu().clone() if torch.is_tensor(v) else v) for k, v in policy.opt.state_dict().items()},
@@ -67,9 +72,11 @@ def save_checkpoint(ckpt_path: str, step: int, policy, data_state: dict, trainer
         "parallel": {"tp": ps.tp, "tp_rank": ps.tp_rank, "dp_rank": ps.dp_rank, "pp_rank": ps.pp_rank, "ep_rank": ps.ep_rank},
     }
     torch.save(shard, os.path.join(tmp, "policy", f"__{rank}_0.distcp"))
+    wrote.append(f"policy/__{rank}_0.distcp")
     for folder, state in (extra_shards or {}).items():
         os.makedirs(os.path.join(tmp, folder), exist_ok=True)
         torch.save(state, os.path.join(tmp, folder, f"__{rank}_0.distcp"))
+        wrote.append(f"{folder}/__{rank}_0.distcp")
     if rank == 0:
         meta = {
             "format": "skyrl_isoexec_b200.sharded.v1", "global_step": step, "world_size": dist.get_world_size() if dist.is_initialized() else 1,
@@ -83,6 +90,37 @@ def save_checkpoint(ckpt_path: str, step: int, policy, data_state: dict, trainer
             json.dump(meta, f, indent=1, sort_keys=True)
         torch.save(data_state, os.path.join(tmp, "data.pt"))
         torch.save(trainer_state, os.path.join(tmp, "trainer_state.pt"))
+        wrote += ["policy/metadata.json", "data.pt", "trainer_state.pt"]
+    return wrote
+
+
+def save_checkpoint(ckpt_path: str, step: int, policy, data_state: dict, trainer_state: dict, ps, max_to_keep: int = -1,
+                    extra_shards: dict | None = None) -> str:
+    """``extra_shards``: ``{folder: this rank's state}`` written as ``{folder}/__{rank}_0.distcp`` beside ``policy/``."""
+    final = step_dir(ckpt_path, step)
+    rank = _rank()
+    if uio.is_cloud_path(ckpt_path):
+        final = ckpt_path.rstrip("/") + f"/global_step_{step}"
+        if rank == 0:
+            uio.remove(final)                                   # a partial upload of an earlier attempt at this step
+        _barrier()
+        with tempfile.TemporaryDirectory(prefix="isoexec-ckpt-") as tmp:
+            wrote = _write_step(tmp, step, policy, data_state, trainer_state, ps, extra_shards)
+            uio.upload_directory(tmp, final, only=wrote)
+        _barrier()                                              # every rank's files are up before the marker moves
+        if rank == 0:
+            with uio.atomic_write(ckpt_path.rstrip("/") + "/" + LATEST) as f:
+                f.write(str(step))
+            cleanup_old_checkpoints(ckpt_path, max_to_keep)
+        _barrier()
+        return final
+    tmp = final + ".tmp"
+    if rank == 0:
+        if os.path.isdir(tmp):
+            shutil.rmtree(tmp)
+        os.makedirs(os.path.join(tmp, "policy"), exist_ok=True)
+    _barrier()
+    _write_step(tmp, step, policy, data_state, trainer_state, ps, extra_shards)
     _barrier()
     if rank == 0:
         if os.path.isdir(final):
@@ -97,12 +135,12 @@ def save_checkpoint(ckpt_path: str, step: int, policy, data_state: dict, trainer
 
 
 def list_checkpoints(ckpt_path: str) -> list[int]:
-    if not os.path.isdir(ckpt_path):
+    if not uio.isdir(ckpt_path):
         return []
     steps = []
-    for d in os.listdir(ckpt_path):
+    for d in uio.list_dir(ckpt_path):
         m = _STEP_RE.match(d)
-        if m and os.path.isdir(os.path.join(ckpt_path, d)):
+        if m and uio.isdir(ckpt_path.rstrip("/") + "/" + d):
             steps.append(int(m.group(1)))
     return sorted(steps)
 
@@ -113,7 +151,10 @@ def cleanup_old_checkpoints(ckpt_path: str, max_to_keep: int) -> list[int]:
     steps = list_checkpoints(ckpt_path)
     drop = steps[:-max_to_keep] if max_to_keep > 0 else steps
     for s in drop:
-        shutil.rmtree(step_dir(ckpt_path, s), ignore_errors=True)
+        if uio.is_cloud_path(ckpt_path):
+            uio.remove(ckpt_path.rstrip("/") + f"/global_step_{s}")
+        else:
+            shutil.rmtree(step_dir(ckpt_path, s), ignore_errors=True)
     return drop
 
 
@@ -127,18 +168,52 @@ def validate_checkpoint_dir(path: str) -> None:
             raise FileNotFoundError(f"checkpoint {path} is incomplete: missing {need}")
 
 
+_STAGED: dict[str, str] = {}
+
+
+def _stage_remote(path: str) -> str:
+    """Download a remote checkpoint directory once per node (the rank with LOCAL_RANK 0 fetches, the others wait) into a
+    staging directory removed when the process exits; returns the local directory, named like the remote one."""
+    if path in _STAGED:
+        return _STAGED[path]
+    root = os.path.join(os.environ.get("SKYRL_ISOEXEC_STAGE_DIR") or tempfile.gettempdir(),
+                        "isoexec-resume-" + hashlib.sha1(path.encode()).hexdigest()[:12])
+    local = os.path.join(root, path.rstrip("/").rsplit("/", 1)[-1])
+    leader = int(os.environ.get("LOCAL_RANK", "0")) == 0
+    err = None
+    if leader:
+        try:
+            shutil.rmtree(root, ignore_errors=True)
+            if uio.download_directory(path, local) == 0:
+                raise FileNotFoundError(f"nothing under {path}")
+            atexit.register(shutil.rmtree, root, True)
+        except Exception as e:  # noqa: BLE001 - raised after the barrier so that the waiting ranks are released first
+            err = e
+    _barrier()
+    if err is not None:
+        raise err
+    _STAGED[path] = local
+    return local
+
+
 def resolve_resume_path(ckpt_path: str, resume_mode: str, resume_path: str = "") -> str | None:
+    """The LOCAL directory to resume from, or None. Remote checkpoints are downloaded first (``_stage_remote``)."""
     if resume_mode == "none":
         return None
     if resume_mode == "from_path":
+        if uio.is_cloud_path(resume_path):
+            resume_path = _stage_remote(resume_path)
         validate_checkpoint_dir(resume_path)
         return resume_path
-    latest = os.path.join(ckpt_path, LATEST)
-    if not os.path.exists(latest):
+    latest = ckpt_path.rstrip("/") + "/" + LATEST if uio.is_cloud_path(ckpt_path) else os.path.join(ckpt_path, LATEST)
+    if not uio.exists(latest):
         return None
-    with open(latest) as f:
-        step = int(f.read().strip())
-    path = step_dir(ckpt_path, step)
+    with uio.open_file(latest) as f:
+        step = int(str(f.read()).strip())
+    if uio.is_cloud_path(ckpt_path):
+        path = _stage_remote(ckpt_path.rstrip("/") + f"/global_step_{step}")
+    else:
+        path = step_dir(ckpt_path, step)
     validate_checkpoint_dir(path)
     return path
 
@@ -285,9 +360,10 @@ def load_checkpoint(path: str, policy, ps) -> tuple[dict, dict]:
 
 def save_hf_export(export_path: str, step: int, model) -> str:
     """Export full-shape weights + config as ``{export_path}/global_step_N/policy/`` (single-rank layouts)."""
-    out = os.path.join(export_path, f"global_step_{step}", "policy")
-    os.makedirs(out, exist_ok=True)
-    torch.save({n: t.detach().cpu() for n, t in model.named_weights()}, os.path.join(out, "pytorch_model.bin"))
-    with open(os.path.join(out, "config.json"), "w") as f:
-        json.dump({"architectures": [model.cfg.architecture], **model.cfg.to_dict()}, f, indent=1)
+    out = export_path.rstrip("/") + f"/global_step_{step}/policy" if uio.is_cloud_path(export_path) \
+        else os.path.join(export_path, f"global_step_{step}", "policy")
+    with uio.local_work_dir(out) as d:
+        torch.save({n: t.detach().cpu() for n, t in model.named_weights()}, os.path.join(d, "pytorch_model.bin"))
+        with open(os.path.join(d, "config.json"), "w") as f:
+            json.dump({"architectures": [model.cfg.architecture], **model.cfg.to_dict()}, f, indent=1)
     return out

@@ -94,16 +94,32 @@ def save_dcp(policy_or_model, path: str, ps, step: int = 0, with_optimizer: bool
                 sd["meta.step"] = torch.tensor(int(policy_or_model.opt.step_count))
     if writer and (ps.pp_rank == 0 or ps.pp == 1):
         sd["meta.global_step"] = torch.tensor(int(step))
+    from ..utils import io as uio
+
+    if uio.is_cloud_path(path):
+        # every rank writes into a directory of its own (its shard file; the coordinator's also holds ``.metadata``) and
+        # uploads it; the files of the ranks have distinct names
+        import tempfile
+
+        with tempfile.TemporaryDirectory(prefix="isoexec-dcp-") as tmp:
+            _save(sd, tmp)
+            uio.upload_directory(tmp, path)
+        if dist.is_initialized():
+            dist.barrier()
+        return path
+    _save(sd, path)
+    return path
+
+
+def _save(sd: dict, path: str) -> None:
     dcp = _dcp()
     if dist.is_initialized() and dist.get_world_size() > 1:
-        if dist.get_rank() == 0:
-            os.makedirs(path, exist_ok=True)
+        os.makedirs(path, exist_ok=True)
         dist.barrier()
         dcp.save(sd, checkpoint_id=path)                      # ranks that write nothing contribute an empty plan
     else:
         os.makedirs(path, exist_ok=True)
         dcp.save(sd, checkpoint_id=path, no_dist=True)
-    return path
 
 
 def _load_keys(path: str, want: dict) -> None:

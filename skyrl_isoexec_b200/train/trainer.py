@@ -824,10 +824,10 @@ class RayPPOTrainer:
                     go, uids = self.balance_rollouts(go, uids)
                 batch = self.convert_to_training_input(go, uids)
             if self.cfg.trainer.dump_data_batch and self.cfg.trainer.ckpt_path:
-                d = os.path.join(self.cfg.trainer.ckpt_path, "dumped_data")
-                os.makedirs(d, exist_ok=True)
-                torch.save({"tensors": {k: v for k, v in batch.items() if torch.is_tensor(v)}, "uids": list(uids)},
-                           os.path.join(d, f"global_step_{self.global_step}_rank{self.rank}.pt"))
+                from ..utils import io as uio
+
+                with uio.open_file(self.cfg.trainer.ckpt_path.rstrip("/") + f"/dumped_data/global_step_{self.global_step}_rank{self.rank}.pt", "wb") as f:
+                    torch.save({"tensors": {k: v for k, v in batch.items() if torch.is_tensor(v)}, "uids": list(uids)}, f)
             if self.global_step == 1 and hasattr(self, "adapter_engine"):
                 # everything the op layer ran since the models were built was the engine's (generation)
                 self.adapter_engine.on_first_forward(_observe.diff(self._census0))
@@ -962,7 +962,7 @@ class RayPPOTrainer:
         (``trainer.resume_mode=from_path`` with that directory resumes weights, optimizer and the step counter)."""
         from . import dcp_checkpoint
 
-        path = os.path.join(self.cfg.trainer.export_path, f"global_step_{self.global_step}", "dcp")
+        path = self.cfg.trainer.export_path.rstrip("/") + f"/global_step_{self.global_step}/dcp"
         return dcp_checkpoint.save_dcp(self.policy, path, self.ps, step=self.global_step)
 
     # ------------------------------------------------------------------ checkpoints
