@@ -38,8 +38,8 @@ class GDNStatePool:
         self.epoch = 0
         self.invalidations = {"weight_sync": 0, "sleep_wake": 0}
         # boundary states kept for the samples of one prompt: {leader seq id: [per-layer (conv tail, fp32 state), users left]}
-        # (a narrow form of the reference's prefix-keyed boundary store, ISO/ops/gdn/gdn_cpr_state.py:96-197: keyed by the
-        # request that computed the prefix, alive only while its siblings wait)
+        # (keyed by the request that computed the prefix, alive only while its siblings wait; the prefix-keyed store that
+        # outlives requests is engine/prefix_cache.py::BoundaryStates)
         self.snapshots: dict[int, list] = {}
 
     def _row(self, seq_id: int) -> int:
@@ -56,11 +56,24 @@ class GDNStatePool:
         self.snapshots.pop(seq_id, None)
 
     # ------------------------------------------------------------------ boundary snapshots (samples of one prompt)
+    def clone_row(self, seq_id: int) -> dict:
+        """{layer: (conv tail, fp32 state)} of the sequence as they stand now. Meaningful as a resume point only when the
+        sequence's open chunk is empty, i.e. right after a step that ended on a chunk boundary."""
+        r = self.row_of[seq_id]
+        return {i: (st[0][r].clone(), st[1][r].clone()) for i, st in self.states.items()}
+
+    def load_row(self, seq_id: int, state: dict) -> None:
+        """Start (or restart) ``seq_id`` from a cloned boundary state: its row gets the state's bits."""
+        r = self._row(seq_id)
+        for i, st in self.states.items():
+            conv, ssm = state[i]
+            st[0][r].copy_(conv)
+            st[1][r].copy_(ssm)
+
     def snapshot(self, seq_id: int, users: int) -> None:
         """Copy the sequence's conv tail and fp32 state of every GDN layer as they stand now (called right after the step
         that brought its prefill to a chunk boundary, where its open chunk is empty)."""
-        r = self.row_of[seq_id]
-        self.snapshots[seq_id] = [{i: (st[0][r].clone(), st[1][r].clone()) for i, st in self.states.items()}, int(users)]
+        self.snapshots[seq_id] = [self.clone_row(seq_id), int(users)]
 
     def has_snapshot(self, seq_id: int) -> bool:
         return seq_id in self.snapshots
@@ -68,11 +81,7 @@ class GDNStatePool:
     def adopt(self, seq_id: int, leader_id: int) -> None:
         """Start ``seq_id`` from the leader's boundary state: its row gets the snapshot's bits."""
         snap = self.snapshots[leader_id]
-        r = self._row(seq_id)
-        for i, st in self.states.items():
-            conv, ssm = snap[0][i]
-            st[0][r].copy_(conv)
-            st[1][r].copy_(ssm)
+        self.load_row(seq_id, snap[0])
         snap[1] -= 1
         if snap[1] <= 0:
             del self.snapshots[leader_id]

@@ -91,8 +91,8 @@ class KVCache:
         self.invalidations["sleep_wake"] += 1
 
     def invalidate(self, event: str) -> bool:
-        """A weight sync makes every cached key and value stale. No prefix is kept across requests, so the cache is clean
-        exactly when no page is in use at that moment. Returns whether it was, and counts clean invalidations so that
+        """A weight sync makes every cached key and value stale. Cached prefixes are dropped by the engine before this is
+        called, so the cache is clean exactly when no page is in use at that moment. Returns whether it was, and counts clean invalidations so that
         the contract ledger sees that the event really emptied the cache instead of taking it on trust. (A sync while
         paused requests keep their pages, the in-flight update mode, is counted under ``stale_syncs``.)"""
         assert event in self.invalidations

@@ -32,7 +32,9 @@ class EngineConfig:
     max_model_len: int = 0               # 0 = model max_position
     eos_token_id: int | None = None
     seed: int = 0
-    enable_prefix_caching: bool = False  # the contract pins this off (state claim engine_prefix_cache)
+    enable_prefix_caching: bool = False  # full KV pages are kept after their request and reused by later requests with the
+                                         # same leading tokens (engine/prefix_cache.py); dropped at every weight sync
+    prefix_cache_state_mb: int = 1024    # models with recurrent layers: budget of the boundary states kept beside the pages
     use_cuda_graph: bool = True
     share_prompt_pages: bool = True      # samples of one prompt share its full KV pages (not a cache: freed with the requests)
     share_recurrent_state: bool = False  # models with GatedDeltaNet layers: siblings also start from the leader's recurrent
@@ -92,6 +94,8 @@ class Scheduler:
         self.shared_prompt_tokens = 0       # prompt tokens taken from a leader's pages instead of being prefilled
         self.can_adopt = None               # engine hooks for models with recurrent state: (sibling, leader) -> bool / None
         self.adopt_hook = None
+        self.prefix = None                  # PrefixCache when prefix caching is on
+        self.prefix_hit_hook = None         # (sequence, chain key of the matched prefix): recurrent state is loaded here
 
     def add(self, seq: Sequence) -> None:
         self.waiting.append(seq)
@@ -103,12 +107,16 @@ class Scheduler:
         need = (upto + PAGE - 1) // PAGE - len(seq.pages)
         if need <= 0:
             return True
+        if not self.cache.allocator.can_alloc(need) and self.prefix is not None:
+            self.prefix.evict(need - self.cache.allocator.num_free)      # cached pages nobody reads go before a preemption
         if not self.cache.allocator.can_alloc(need):
             return False
         seq.pages += self.cache.allocator.alloc(need)
         return True
 
     def _preempt(self, seq: Sequence) -> None:
+        if self.prefix is not None:
+            self.prefix.insert(seq.tokens, seq.pages, seq.num_computed)  # the recompute may find them again
         self.cache.allocator.release(seq.pages)
         seq.pages = []
         seq.num_computed = 0
@@ -179,6 +187,12 @@ class Scheduler:
                     self.shared_prompt_tokens += s.shared_tokens
                     if self.adopt_hook is not None:
                         self.adopt_hook(s, ld)
+            if self.prefix is not None and s.leader is None and not s.pages and s.num_computed == 0:
+                pages, key = self.prefix.match(s.tokens)
+                if pages:
+                    s.pages, s.num_computed = pages, len(pages) * PAGE
+                    if self.prefix_hit_hook is not None:
+                        self.prefix_hit_hook(s, key)
             n = self._chunk(s, budget)
             if not self._ensure_pages(s, s.num_computed + n):
                 break
@@ -189,6 +203,8 @@ class Scheduler:
         return decode, prefill
 
     def finish(self, seq: Sequence) -> None:
+        if self.prefix is not None:
+            self.prefix.insert(seq.tokens, seq.pages, seq.num_computed)
         self.cache.allocator.release(seq.pages)
         seq.pages = []
         self.running.remove(seq)
@@ -200,8 +216,6 @@ class LLMEngine:
         self.mcfg = model.cfg
         self.cfg = cfg or EngineConfig()
         self.device = model.device_
-        if self.cfg.enable_prefix_caching:
-            raise ValueError("this engine keeps no prefix cache (the execution contract pins it off); set enable_prefix_caching=false")
         self.max_len = self.cfg.max_model_len or self.mcfg.max_position
         n_pages = self.cfg.num_kv_pages or self._auto_pages()
         self.cache = KVCache(self.mcfg, n_pages, self.device, tp=model.ps.tp, layer_ids=model.layer_ids)
@@ -231,6 +245,14 @@ class LLMEngine:
             if self.cfg.share_prompt_pages and self.cfg.share_recurrent_state:
                 self.scheduler.can_adopt = lambda s, ld: self.gdn_state.has_snapshot(ld.seq_id)
                 self.scheduler.adopt_hook = lambda s, ld: self.gdn_state.adopt(s.seq_id, ld.seq_id)
+        self.prefix_cache = None
+        if self.cfg.enable_prefix_caching:
+            from .prefix_cache import BoundaryStates, PrefixCache
+
+            boundary = BoundaryStates(self.cfg.prefix_cache_state_mb << 20) if self.gdn_state is not None else None
+            self.prefix_cache = self.scheduler.prefix = PrefixCache(self.cache.allocator, boundary)
+            if boundary is not None:
+                self.scheduler.prefix_hit_hook = self._resume_from_boundary
 
     def _auto_pages(self) -> int:
         per_page = KVCache.bytes_per_page(self.mcfg, self.model.ps.tp)
@@ -256,8 +278,11 @@ class LLMEngine:
         """Release the KV pools (and recurrent state). Weights stay resident."""
         self._drain_inflight()
         assert not self.scheduler.has_work(), "sleep with requests in flight"
+        self._drop_prefix_cache()
         self._graphs.clear()      # graphs hold the pool addresses; they are re-captured after wake-up
         self.cache.sleep()
+        if self.prefix_cache is not None:
+            self.prefix_cache.alloc = self.cache.allocator       # sleep starts a fresh allocator
         if self.gdn_state is not None:
             self.gdn_state.invalidate("sleep_wake")
         self.asleep = True
@@ -267,12 +292,43 @@ class LLMEngine:
         self.asleep = False
 
     def reset_prefix_cache(self) -> None:
-        """Called at every weight sync. No prefix cache is kept (pinned off by the contract): the KV cache checks that no
-        page holds old-weight state; recurrent state is dropped."""
+        """Called at every weight sync. Cached prefixes (pages and boundary states) are dropped, after which the KV cache
+        checks that no page holds old-weight state; recurrent state is dropped."""
         self._drain_inflight()
+        self._drop_prefix_cache()
         self.cache.invalidate("weight_sync")
         if self.gdn_state is not None:
             self.gdn_state.invalidate("weight_sync")
+
+    def _drop_prefix_cache(self) -> None:
+        if self.prefix_cache is not None:
+            self.prefix_cache.clear()
+            self.stats["prefix_cache_drops"] = self.stats.get("prefix_cache_drops", 0) + 1
+
+    def _resume_from_boundary(self, s: Sequence, key: bytes) -> None:
+        """A sequence of a model with recurrent layers matched a cached prefix: its state row starts from the boundary
+        state stored for that prefix. A leader whose siblings wait for a snapshot at this very boundary gives it now
+        (its prefill will not pass the boundary again)."""
+        self.gdn_state.load_row(s.seq_id, self.prefix_cache.boundary.get(key))
+        if s.snapshot_at and s.num_computed == s.snapshot_at and s.snapshot_users > 0:
+            self.gdn_state.snapshot(s.seq_id, s.snapshot_users)
+
+    def _note_progress(self, s: Sequence, prefill: bool) -> None:
+        """After a step that advanced ``s``: list its newly full pages (a later request may match them while this one
+        still runs), and for a model with recurrent layers keep the state at a page boundary the sequence stands on
+        exactly (its open chunk is empty there)."""
+        pc = self.prefix_cache
+        if pc is None or s.num_computed < PAGE or not (prefill or s.num_computed % PAGE == 0):
+            return
+        if pc.boundary is not None:
+            if s.num_computed % PAGE or s.seq_id not in self.gdn_state.row_of:
+                return
+            from .prefix_cache import chain_keys
+
+            key = chain_keys(s.tokens, s.num_computed // PAGE)[-1]
+            if key not in pc.boundary:
+                pc.boundary.put(key, self.gdn_state.clone_row(s.seq_id))
+        pc.insert(s.tokens, s.pages, s.num_computed)
 
     def invalidation_counts(self) -> dict:
         """{state id of the contract: {event: times the state was really invalidated}}."""
@@ -297,6 +353,10 @@ class LLMEngine:
             raise ValueError(f"prompt of {len(prompt_ids)} tokens exceeds max_model_len={self.max_len}")
         seq = Sequence(self._next_id, list(prompt_ids), params, request_index=request_index, arrival=time.time())
         self._next_id += 1
+        if self.prefix_cache is not None and self.prefix_cache.boundary is not None:
+            # recurrent layers: the prefill stops once at the last full page of the prompt, so that the state there can be
+            # kept for later requests that share the prompt
+            seq.snapshot_at = ((len(prompt_ids) - 1) // PAGE) * PAGE
         self.scheduler.add(seq)
         return seq
 
@@ -373,10 +433,12 @@ class LLMEngine:
         hidden = self.model(self._h2d(torch.tensor(ids, dtype=torch.int64)), fc)
         for s in decode:
             s.num_computed += 1
+            self._note_progress(s, False)
         for s, start, n in prefill:
             s.num_computed = start + n
             if s.snapshot_at and start + n == s.snapshot_at and self.gdn_state is not None and s.snapshot_users > 0:
                 self.gdn_state.snapshot(s.seq_id, s.snapshot_users)          # the siblings of this prompt start from here
+            self._note_progress(s, True)
         self.stats["steps"] += 1
         self.stats["tokens"] += row
         self.stats["decode_tokens"] += len(decode)

@@ -126,6 +126,11 @@ class InferenceServer:
                 ("isoexec_requests_running", "gauge", len(getattr(self.llm, "running", []) or [])),
                 ("isoexec_requests_waiting", "gauge", len(getattr(self.llm, "waiting", []) or [])),
                 ("isoexec_paused", "gauge", 0 if self._paused_mode in (None, "", "none") else 1)]
+        pc = getattr(self.llm, "prefix_cache", None)
+        if pc is not None:
+            rows += [("isoexec_prefix_cache_hits_total", "counter", pc.hits), ("isoexec_prefix_cache_misses_total", "counter", pc.misses),
+                     ("isoexec_prefix_cache_hit_tokens_total", "counter", pc.hit_tokens), ("isoexec_prefix_cache_evicted_total", "counter", pc.evicted),
+                     ("isoexec_prefix_cache_pages", "gauge", len(pc))]
         out = []
         for name, kind, val in rows:
             out.append(f"# TYPE {name} {kind}")

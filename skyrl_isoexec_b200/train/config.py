@@ -345,8 +345,8 @@ def validate_cfg(cfg: SkyRLTrainConfig, world_size: int = 1) -> None:
         s = g.sampling_params
         if s.temperature != 1.0 or s.top_p != 1.0 or s.top_k not in (-1, 0) or s.min_p != 0.0:
             raise ValueError("isoexec.enabled requires temperature=1.0, top_p=1.0, top_k=-1, min_p=0.0 for rollouts")
-        if g.inference_engine.enable_prefix_caching:
-            raise ValueError("isoexec.enabled pins enable_prefix_caching=false")
+        # enable_prefix_caching is allowed: this engine's reuse is page-granular and bitwise prefix-invariant, and the cached
+        # pages fall under the contract's engine_kv_cache state claim (dropped at every weight sync, which is observed)
     ie = g.inference_engine
     if ie.tensor_parallel_size < 0 or ie.num_engines < 0:
         raise ValueError("inference engine sizes must be >= 0 (0 = derived from the trainer layout)")

@@ -3,7 +3,7 @@ plane of ``engine/server.py`` (OpenAI-style ``/v1/completions``, token-level ``/
 update, ``/metrics``).
 
     python -m skyrl_isoexec_b200.train.entrypoints.serve [--model qwen3-8b] [--weights DIR_OR_FILE] [--host 127.0.0.1] [--port 8000]
-        [--max-num-seqs 64] [--num-kv-pages 0] [--seed 0]
+        [--max-num-seqs 64] [--num-kv-pages 0] [--seed 0] [--enable-prefix-caching]
 
 ``--weights``: a Hugging Face style directory written by ``models/hf_export.py`` or a ``torch.save`` file with a
 ``model`` dict; without it the server starts on the seeded random initialisation (for tests).
@@ -33,6 +33,8 @@ def build(argv=None) -> InferenceServer:
     ap.add_argument("--max-num-seqs", type=int, default=64)
     ap.add_argument("--num-kv-pages", type=int, default=0)
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--enable-prefix-caching", action="store_true",
+                    help="keep full KV pages after their request and reuse them for later requests with the same leading tokens")
     ap.add_argument("--device", default="cuda" if torch.cuda.is_available() else "cpu")
     a = ap.parse_args(argv)
     model = DecoderLM(get_config(a.model), device=a.device, seed=a.seed)
@@ -45,7 +47,7 @@ def build(argv=None) -> InferenceServer:
             from ...sync.strategies import load_weights
 
             load_weights(model, torch.load(a.weights, map_location="cpu", weights_only=False)["model"].items())
-    kw = {"max_num_seqs": a.max_num_seqs, "seed": a.seed}
+    kw = {"max_num_seqs": a.max_num_seqs, "seed": a.seed, "enable_prefix_caching": a.enable_prefix_caching}
     if a.num_kv_pages:
         kw["num_kv_pages"] = a.num_kv_pages
     eng = LLMEngine(model, EngineConfig(**kw))
