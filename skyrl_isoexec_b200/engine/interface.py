@@ -47,6 +47,11 @@ class InferenceEngineInterface(ABC):
     async def completion(self, request_payload: dict) -> dict:
         raise NotImplementedError("completion needs a tokenizer; use engine.server.OpenAIServer")
 
+    async def render_chat_completion(self, request_payload: dict) -> dict:
+        """``{"json": {"messages": [...]}}`` -> ``{"token_ids", "features"}`` (``engine/renderer.py``): the ids the engine
+        would be given for that conversation, with every image a run of placeholder tokens, and the images' patches."""
+        raise NotImplementedError("rendering needs a tokenizer and a model configuration")
+
     @abstractmethod
     async def wake_up(self, *a, **kw): ...
 
@@ -100,12 +105,25 @@ class NativeInferenceEngine(InferenceEngineInterface):
                    self.tokenizer.apply_chat_template(p, add_generation_prompt=True, tokenize=True)
                    for p in input_batch["prompts"]]
         sp = SamplingParams.from_dict(input_batch.get("sampling_params"))
-        outs = self.llm.generate(ids, sp)
+        mm = input_batch.get("mm_features")
+        if mm is not None:
+            from .renderer import decode_features
+
+            mm = [decode_features(f) for f in mm]
+        outs = self.llm.generate(ids, sp, mm=mm)
         texts = [self.tokenizer.decode(o.response_ids) if self.tokenizer is not None else "" for o in outs]
         return {"responses": texts, "response_ids": [o.response_ids for o in outs],
                 "stop_reasons": [o.stop_reason for o in outs],
                 "response_logprobs": [o.response_logprobs for o in outs], "prompt_logprobs": None,
                 "rollout_expert_indices": None}
+
+    async def render_chat_completion(self, request_payload: dict) -> dict:
+        from .renderer import render_conversation
+
+        if self.tokenizer is None:
+            raise ValueError("rendering a conversation needs a tokenizer")
+        body = request_payload.get("json", request_payload)
+        return render_conversation(body["messages"], self.tokenizer, self.llm.mcfg, body.get("add_generation_prompt", True))
 
     async def wake_up(self, *a, tags=None, **kw):
         self.llm.wake_up(tags)
@@ -172,6 +190,8 @@ class InferenceEngineClient(InferenceEngineInterface):
                 sub["prompt_token_ids"] = [ids[i] for i in idx]
             else:
                 sub["prompts"] = [prompts[i] for i in idx]
+            if input_batch.get("mm_features") is not None:
+                sub["mm_features"] = [input_batch["mm_features"][i] for i in idx]
             return idx, await self.engines[e].generate(sub)
 
         results = await asyncio.gather(*[run(e, idx) for e, idx in shards.items()])
@@ -185,6 +205,9 @@ class InferenceEngineClient(InferenceEngineInterface):
                 out["stop_reasons"][i] = r["stop_reasons"][j]
                 out["response_logprobs"][i] = r["response_logprobs"][j] if r.get("response_logprobs") else None
         return out
+
+    async def render_chat_completion(self, request_payload: dict) -> dict:
+        return await self.engines[0].render_chat_completion(request_payload)       # a pure function of the conversation
 
     async def _all(self, name, *a, **kw):
         return await asyncio.gather(*[getattr(e, name)(*a, **kw) for e in self.engines])

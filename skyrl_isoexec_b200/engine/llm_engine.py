@@ -60,6 +60,11 @@ class Sequence:
     shared_tokens: int = 0
     snapshot_at: int = 0           # leader of a model with recurrent layers: its prefill stops here once, for a state snapshot
     snapshot_users: int = 0
+    # vision-language requests: prompt positions of the image placeholder tokens, the vision tower's row for each of them
+    # (on the engine's device), and a digest of the pixels (two requests share pages only if their images are the same)
+    mm_pos: list[int] | None = None
+    mm_feats: torch.Tensor | None = None
+    mm_key: bytes | None = None
 
     @property
     def tokens(self) -> list[int]:
@@ -115,7 +120,7 @@ class Scheduler:
         return True
 
     def _preempt(self, seq: Sequence) -> None:
-        if self.prefix is not None:
+        if self.prefix is not None and seq.mm_feats is None:
             self.prefix.insert(seq.tokens, seq.pages, seq.num_computed)  # the recompute may find them again
         self.cache.allocator.release(seq.pages)
         seq.pages = []
@@ -187,7 +192,7 @@ class Scheduler:
                     self.shared_prompt_tokens += s.shared_tokens
                     if self.adopt_hook is not None:
                         self.adopt_hook(s, ld)
-            if self.prefix is not None and s.leader is None and not s.pages and s.num_computed == 0:
+            if self.prefix is not None and s.leader is None and not s.pages and s.num_computed == 0 and s.mm_feats is None:
                 pages, key = self.prefix.match(s.tokens)
                 if pages:
                     s.pages, s.num_computed = pages, len(pages) * PAGE
@@ -203,7 +208,7 @@ class Scheduler:
         return decode, prefill
 
     def finish(self, seq: Sequence) -> None:
-        if self.prefix is not None:
+        if self.prefix is not None and seq.mm_feats is None:      # pages are keyed by tokens alone: image prompts stay out
             self.prefix.insert(seq.tokens, seq.pages, seq.num_computed)
         self.cache.allocator.release(seq.pages)
         seq.pages = []
@@ -318,7 +323,7 @@ class LLMEngine:
         still runs), and for a model with recurrent layers keep the state at a page boundary the sequence stands on
         exactly (its open chunk is empty there)."""
         pc = self.prefix_cache
-        if pc is None or s.num_computed < PAGE or not (prefill or s.num_computed % PAGE == 0):
+        if pc is None or s.num_computed < PAGE or not (prefill or s.num_computed % PAGE == 0) or s.mm_feats is not None:
             return
         if pc.boundary is not None:
             if s.num_computed % PAGE or s.seq_id not in self.gdn_state.row_of:
@@ -344,7 +349,10 @@ class LLMEngine:
         self.paused = False
 
     # ------------------------------------------------------------------ requests
-    def add_request(self, prompt_ids: list[int], params: SamplingParams, request_index: int = 0) -> Sequence:
+    def add_request(self, prompt_ids: list[int], params: SamplingParams, request_index: int = 0, mm: dict | None = None) -> Sequence:
+        """``mm``: ``{"pixel_values": [patches, dim], "image_grid_thw": [images, 3], "positions": optional list}`` for a
+        prompt with image placeholder tokens (``positions``: where they are; default: every token equal to the model's
+        ``image_token_id``). The vision tower runs here, once per request."""
         if len(prompt_ids) == 0:
             raise ValueError("empty prompt")
         if getattr(params, "repetition_penalty", 1.0) not in (1.0, None):
@@ -353,12 +361,41 @@ class LLMEngine:
             raise ValueError(f"prompt of {len(prompt_ids)} tokens exceeds max_model_len={self.max_len}")
         seq = Sequence(self._next_id, list(prompt_ids), params, request_index=request_index, arrival=time.time())
         self._next_id += 1
+        if mm is not None and mm.get("pixel_values") is not None and mm["pixel_values"].shape[0]:
+            self._attach_images(seq, mm)
         if self.prefix_cache is not None and self.prefix_cache.boundary is not None:
             # recurrent layers: the prefill stops once at the last full page of the prompt, so that the state there can be
             # kept for later requests that share the prompt
             seq.snapshot_at = ((len(prompt_ids) - 1) // PAGE) * PAGE
         self.scheduler.add(seq)
         return seq
+
+    @torch.no_grad()
+    def _attach_images(self, seq: Sequence, mm: dict) -> None:
+        import hashlib
+
+        tower = getattr(self.model, "vision", None)
+        if tower is None:
+            raise ValueError(f"model {self.mcfg.name!r} has no vision tower: it cannot take image inputs")
+        pv, grid = mm["pixel_values"], mm["image_grid_thw"]
+        tok = self.mcfg.image_token_id
+        pos = list(mm["positions"]) if mm.get("positions") is not None else [i for i, t in enumerate(seq.prompt_ids) if t == tok]
+        feats = tower.encode(pv, grid)
+        if feats.shape[0] != len(pos):
+            raise ValueError(f"the prompt has {len(pos)} image placeholder tokens, the images give {feats.shape[0]} feature rows")
+        if any(seq.prompt_ids[p] != tok for p in pos) or sorted(pos) != pos:
+            raise ValueError("image positions must be ascending and point at image placeholder tokens")
+        seq.mm_pos, seq.mm_feats = pos, feats
+        seq.mm_key = hashlib.blake2b(pv.detach().cpu().contiguous().view(torch.uint8).numpy().tobytes()
+                                     + grid.detach().cpu().to(torch.int64).numpy().tobytes(), digest_size=16).digest()
+
+    @staticmethod
+    def _image_rows_of_chunk(s: Sequence, start: int, n: int, row: int):
+        """Batch rows and feature rows of the image placeholder tokens of ``s`` inside its prefill chunk [start, start+n)."""
+        import bisect
+
+        k0, k1 = bisect.bisect_left(s.mm_pos, start), bisect.bisect_left(s.mm_pos, start + n)
+        return [row + (p - start) for p in s.mm_pos[k0:k1]], s.mm_feats[k0:k1]
 
     @torch.no_grad()
     def step(self) -> list[Sequence]:
@@ -392,6 +429,7 @@ class LLMEngine:
         G = self.model.hq // self.model.hkv
         tq = PAGE // G
         ids, pos, slots, items, bt_rows, sample_rows, sample_seqs = [], [], [], [], [], [], []
+        mm_rows, mm_feats = [], []
         row = 0
         for s in decode:
             p = s.length - 1
@@ -415,6 +453,11 @@ class LLMEngine:
             if start + n == s.length:
                 sample_rows.append(row + n - 1)
                 sample_seqs.append(s)
+            if s.mm_feats is not None:
+                r, f = self._image_rows_of_chunk(s, start, n, row)
+                if r:
+                    mm_rows += r
+                    mm_feats.append(f)
             row += n
         maxp = max(len(b) for b in bt_rows)
         bt = torch.zeros(len(bt_rows), maxp, dtype=torch.int32)
@@ -430,6 +473,8 @@ class LLMEngine:
         if self.gdn_state is not None:
             fc.gdn_meta = self.gdn_state.step_meta(decode, prefill)
             fc.kv = self.gdn_state.merge_into(self.cache.pools)
+        if mm_rows:
+            fc.mm = (self._h2d(torch.tensor(mm_rows, dtype=torch.int64)), torch.cat(mm_feats, 0))
         hidden = self.model(self._h2d(torch.tensor(ids, dtype=torch.int64)), fc)
         for s in decode:
             s.num_computed += 1
@@ -626,7 +671,7 @@ class LLMEngine:
         for s in seqs:
             if s.num_computed or s.pages or s.output_ids:
                 continue                                        # already under way
-            ld = leaders.setdefault(tuple(s.prompt_ids), s)
+            ld = leaders.setdefault((tuple(s.prompt_ids), s.mm_key), s)
             shared = ((len(s.prompt_ids) - 1) // PAGE) * PAGE   # a multiple of the GatedDeltaNet chunk too: no open chunk there
             if ld is not s and shared > 0:
                 s.leader, s.shared_tokens = ld, shared
@@ -635,12 +680,14 @@ class LLMEngine:
                 n += 1
         return n
 
-    def generate(self, prompts: list[list[int]], params: SamplingParams | list[SamplingParams]) -> list[RequestOutput]:
-        """Blocking batch generation; outputs are in prompt order."""
+    def generate(self, prompts: list[list[int]], params: SamplingParams | list[SamplingParams], mm: list | None = None) -> list[RequestOutput]:
+        """Blocking batch generation; outputs are in prompt order. ``mm``: per prompt, the image inputs of ``add_request``
+        or None."""
         if self.asleep:
             raise RuntimeError("engine is asleep; call wake_up() first")
         plist = params if isinstance(params, list) else [params] * len(prompts)
-        seqs = [self.add_request(p, sp, i) for i, (p, sp) in enumerate(zip(prompts, plist))]
+        mlist = mm if mm is not None else [None] * len(prompts)
+        seqs = [self.add_request(p, sp, i, mm=m) for i, (p, sp, m) in enumerate(zip(prompts, plist, mlist))]
         self.link_samples(seqs)
         while True:
             if self.paused:

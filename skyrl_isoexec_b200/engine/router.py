@@ -29,7 +29,7 @@ from concurrent.futures import ThreadPoolExecutor
 from http.server import BaseHTTPRequestHandler, ThreadingHTTPServer
 
 _FANOUT = {"/pause", "/resume", "/update_weights", "/update_weights_layerwise", "/sleep", "/wake_up", "/reset_prefix_cache"}
-_ONE = {"/generate", "/v1/completions", "/v1/chat/completions"}
+_ONE = {"/generate", "/v1/completions", "/v1/chat/completions", "/v1/chat/completions/render"}
 
 
 class Router:
@@ -170,7 +170,8 @@ class Router:
             res = {b: f.result() for b, f in futs.items()}
             ok = all(code == 200 for code, _ in res.values())
             return (200 if ok else 502), {"ok": ok, "backends": {b: {"status": c, "reply": o} for b, (c, o) in res.items()}}
-        if path == "/generate" and session is None and isinstance(body.get("prompt_token_ids"), list) and len(body["prompt_token_ids"]) > 1:
+        if path == "/generate" and session is None and isinstance(body.get("prompt_token_ids"), list) and len(body["prompt_token_ids"]) > 1 \
+                and body.get("mm_features") is None:
             return self._split_generate(body)
         if path in _ONE:
             return self._one(path, body, session)

@@ -152,11 +152,12 @@ class InferenceServer:
             if not busy:
                 time.sleep(0.001)
 
-    def _submit(self, prompts: list[list[int]], sp: SamplingParams, timeout: float = 3600.0):
+    def _submit(self, prompts: list[list[int]], sp: SamplingParams, timeout: float = 3600.0, mm: list | None = None):
         if self._paused_mode in ("abort", "finish"):
             raise RuntimeError("server is paused; resume before sending requests")
         with self._lock:
-            seqs = [self.llm.add_request(p, sp, i) for i, p in enumerate(prompts)]
+            seqs = [self.llm.add_request(p, sp, i, **({"mm": mm[i]} if mm is not None and mm[i] is not None else {}))
+                    for i, p in enumerate(prompts)]
             self.llm.link_samples(seqs)            # n > 1 samples of a prompt share its KV pages
             pend = _Pending(seqs)
             self._pending.append(pend)
@@ -173,6 +174,8 @@ class InferenceServer:
             return 200, self._completions(body)
         if path == "/v1/chat/completions":
             return 200, self._chat(body)
+        if path == "/v1/chat/completions/render":
+            return 200, self._render(body)
         if path == "/pause":
             return 200, self.pause(body.get("mode", "keep"))
         if path == "/resume":
@@ -274,9 +277,25 @@ class InferenceServer:
     def _generate(self, body: dict) -> dict:
         ids = body["prompt_token_ids"]
         ids = ids if ids and isinstance(ids[0], list) else [ids]
-        seqs, aborted = self._submit(ids, SamplingParams.from_dict(body.get("sampling_params")))
+        mm = body.get("mm_features")
+        if mm is not None:                       # per prompt: the ``features`` of /v1/chat/completions/render, or null
+            from .renderer import decode_features
+
+            mm = [decode_features(f) for f in mm]
+        seqs, aborted = self._submit(ids, SamplingParams.from_dict(body.get("sampling_params")), mm=mm)
         return {"response_ids": [s.output_ids for s in seqs], "response_logprobs": [s.logprobs for s in seqs],
                 "stop_reasons": [s.stop_reason for s in seqs], "aborted": aborted}
+
+    def _render(self, body: dict) -> dict:
+        """Token ids of a conversation with every image a run of placeholder tokens, and the images' patches in a
+        JSON-safe form (``engine/renderer.py``); what the answer's ``features`` hold goes back in ``/generate`` as
+        ``mm_features``."""
+        from .renderer import encode_features, render_conversation
+
+        if self.tokenizer is None:
+            raise ValueError("rendering a conversation needs a tokenizer")
+        r = render_conversation(body["messages"], self.tokenizer, self.llm.mcfg, body.get("add_generation_prompt", True))
+        return {"token_ids": r["token_ids"], "features": encode_features(r["features"])}
 
     def _openai_params(self, body: dict) -> SamplingParams:
         d = {"max_generate_length": body.get("max_tokens", 16), "temperature": body.get("temperature", 1.0),
@@ -380,9 +399,17 @@ class RemoteInferenceClient(InferenceEngineInterface):
             by_url.setdefault(self._pick(s), []).append(i)
         loop = asyncio.get_running_loop()
 
+        mm = input_batch.get("mm_features")
+        if mm is not None:
+            from .renderer import encode_features
+
+            mm = [f if f is None or "kwargs_data" in f else encode_features(f) for f in mm]
+
         def call(url, idx):
-            return idx, self._post(url, "/generate", {"prompt_token_ids": [ids[i] for i in idx],
-                                                      "sampling_params": input_batch.get("sampling_params")})
+            body = {"prompt_token_ids": [ids[i] for i in idx], "sampling_params": input_batch.get("sampling_params")}
+            if mm is not None:
+                body["mm_features"] = [mm[i] for i in idx]
+            return idx, self._post(url, "/generate", body)
 
         parts = await asyncio.gather(*[loop.run_in_executor(None, call, u, ix) for u, ix in by_url.items()])
         n = len(ids)
@@ -399,6 +426,13 @@ class RemoteInferenceClient(InferenceEngineInterface):
 
     async def chat_completion(self, request_payload: dict) -> dict:
         return self._post(self._pick(request_payload.get("session_id")), "/v1/chat/completions", request_payload)
+
+    async def render_chat_completion(self, request_payload: dict) -> dict:
+        """Messages may hold images as data URLs only (the request is JSON)."""
+        from .renderer import decode_features
+
+        r = self._post(self._pick(None), "/v1/chat/completions/render", request_payload.get("json", request_payload))
+        return {"token_ids": r["token_ids"], "features": decode_features(r.get("features"))}
 
     # ------------------------------------------------------------------ control plane (fan-out)
     def _all(self, path: str, body: dict | None = None) -> list[dict]:

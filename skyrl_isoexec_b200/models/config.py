@@ -50,6 +50,14 @@ class ModelConfig:
     q_lora_rank: int = 0         # 0 = a plain query projection
     qk_rope_dim: int = 0
     v_head_dim: int = 0
+    # --- vision tower (vision_depth == 0 -> text only); models/vision.py
+    vision_depth: int = 0
+    vision_hidden: int = 0
+    vision_heads: int = 0
+    vision_patch: int = 14
+    vision_merge: int = 2          # merge x merge neighbouring patches become one placeholder token
+    vision_max_grid: int = 64      # largest image side, in patches
+    image_token_id: int = -1       # the placeholder token; its embedding rows are replaced by the tower's output
     # --- numerics pins that enter the execution contract
     logprob_leaves: int = 8
     pik_leaves: int = 8
@@ -74,6 +82,10 @@ class ModelConfig:
             return self.qk_rope_dim
         r = int(self.head_dim * self.partial_rotary_factor)
         return r - (r % 16) if r % 16 else r
+
+    @property
+    def has_vision(self) -> bool:
+        return self.vision_depth > 0
 
     @property
     def has_moe(self) -> bool:
@@ -191,6 +203,12 @@ PRESETS: dict[str, ModelConfig] = {
         name="tiny-moe", architecture="Qwen3MoeForCausalLM", vocab_size=2048, hidden_size=256, num_layers=2,
         num_q_heads=4, num_kv_heads=2, head_dim=64, ffn_size=0, num_experts=8, top_k=2, moe_ffn_size=128,
         dtype="float32", max_position=512),
+    # vision-language: the tiny Qwen3 decoder with a two-block vision tower; token 2047 is the image placeholder
+    "tiny-vl": ModelConfig(
+        name="tiny-vl", architecture="Qwen3ForCausalLM", vocab_size=2048, hidden_size=256, num_layers=2,
+        num_q_heads=4, num_kv_heads=2, head_dim=64, ffn_size=768, tie_embeddings=True, dtype="float32",
+        max_position=1024, vision_depth=2, vision_hidden=64, vision_heads=4, vision_patch=8, vision_merge=2,
+        vision_max_grid=16, image_token_id=2047),
     "tiny-hybrid": ModelConfig(
         name="tiny-hybrid", architecture="Qwen3NextForCausalLM", vocab_size=2048, hidden_size=256, num_layers=4,
         num_q_heads=4, num_kv_heads=2, head_dim=64, ffn_size=512, layer_types=_hybrid_pattern(4), gdn_k_heads=2,

@@ -241,6 +241,7 @@ class ForwardCtx:
     gdn_meta: object | None = None     # sequence layout for GDN layers (see ops/gdn.py)
     site: str = "trainer_fwd"          # trainer_fwd | trainer_score | engine_prefill | engine_decode
     sp_T: int | None = None            # set by the forward when sequence parallelism is on: total rows of the micro-batch
+    mm: tuple | None = None            # vision-language: (rows int64 [n], features [n, hidden]) that replace embedding rows
 
 
 class DecoderLM(nn.Module):
@@ -263,6 +264,11 @@ class DecoderLM(nn.Module):
             self.params[name.replace(".", "/")] = p
         self.rope = F.RopeTable(cfg.rot_dim, cfg.max_position, cfg.rope_theta, self.device_)
         self.scale = F.softmax_scale(cfg.head_dim)
+        self.vision = None
+        if getattr(cfg, "vision_depth", 0) > 0 and self.ps.is_first_pp:
+            from .vision import VisionTower
+
+            self.vision = VisionTower(cfg, self.device_, seed)       # frozen; same seed, same bits on every rank and side
         tp = self.ps.tp
         assert cfg.num_kv_heads % tp == 0 or tp % cfg.num_kv_heads == 0, "TP must divide, or be a multiple of, the KV heads"
         self.hq, self.hkv = cfg.num_q_heads // tp, max(1, cfg.num_kv_heads // tp)
@@ -280,8 +286,13 @@ class DecoderLM(nn.Module):
         for name in self.store.order:
             yield name, self.store.views[name]
 
-    def embed(self, input_ids: torch.Tensor) -> torch.Tensor:
-        return torch.nn.functional.embedding(input_ids, self.p("embed.weight"))
+    def embed(self, input_ids: torch.Tensor, mm: tuple | None = None) -> torch.Tensor:
+        """Token embeddings; ``mm = (rows, features)`` puts the vision tower's rows in place of the image placeholder
+        tokens' embeddings (out of place: the other rows keep their gradient path, the features carry none)."""
+        x = torch.nn.functional.embedding(input_ids, self.p("embed.weight"))
+        if mm is not None and mm[0].numel():
+            x = x.index_copy(0, mm[0], mm[1].to(x.dtype))
+        return x
 
     def lm_head_weight(self) -> torch.Tensor:
         if self.cfg.tie_embeddings:
@@ -385,7 +396,7 @@ class DecoderLM(nn.Module):
         """Returns the final-norm hidden states [T, hidden] on the last pipeline stage, else the
         (x, residual) pair to send to the next stage."""
         if hidden_in is None:
-            x, res = self.embed(input_ids), None
+            x, res = self.embed(input_ids, fc.mm), None
         else:
             x, res = hidden_in
         fc.sp_T = None

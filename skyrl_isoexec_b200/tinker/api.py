@@ -8,7 +8,7 @@ survive a restart of the front end) and executed in order by one engine thread; 
   POST /api/v1/forward_backward    {model_id, data, loss_fn}
   POST /api/v1/forward             {model_id, data}
   POST /api/v1/optim_step          {model_id, adam_params}
-  POST /api/v1/asample             {model_id, prompt_ids, num_samples, sampling_params}
+  POST /api/v1/asample             {model_id, prompt_ids | chunks, num_samples, sampling_params}   (chunks: encoded_text / image)
   POST /api/v1/save_weights | load_weights {model_id, path}
   POST /api/v1/retrieve_future     {request_id}
   POST /api/v1/list_checkpoints    {model_id}                            -> every completed save of the model

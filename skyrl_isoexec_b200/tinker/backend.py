@@ -2,10 +2,11 @@
 (reference: R/backends/skyrl_train_backend.py ``SkyRLTrainBackend``; R/tinker/engine.py request loop).
 
 Requests are plain dicts, processed strictly in arrival order:
-  forward_backward {data: [{prompt_ids, response_ids, advantages?, logprobs?}], loss_fn}  -> per-sequence logprobs, loss
+  forward_backward {data: [{prompt_ids | chunks, response_ids, advantages?, logprobs?}], loss_fn}  -> per-sequence logprobs, loss
+                   (``chunks``: text and image chunks of a multimodal prompt, engine/renderer.py::render_model_input)
   forward          {data}                                                                 -> per-sequence logprobs
   optim_step       {adam_params: {learning_rate}}                                         -> grad norm
-  sample           {prompt_ids, num_samples, sampling_params}                             -> sequences + logprobs
+  sample           {prompt_ids | chunks, num_samples, sampling_params}                    -> sequences + logprobs
   save_weights / load_weights {path}
 """
 
@@ -67,8 +68,19 @@ class SkyRLTrainBackend:
                          "stop_reason": "length" if c.get("finish_reason") == "length" else "stop"})
         return {"sequences": seqs}
 
+    def _render(self, item: dict) -> tuple[list[int], dict | None]:
+        """Prompt ids and image features of a request item: ``prompt_ids`` as given, or ``chunks`` (text and image chunks,
+        ``engine/renderer.py::render_model_input``)."""
+        if item.get("chunks") is None:
+            return list(item["prompt_ids"]), None
+        from ..engine.renderer import render_model_input
+
+        r = render_model_input(item["chunks"], self.model.cfg)
+        return r["token_ids"], r["features"]
+
     def _batch(self, data: list[dict]) -> TrainingInputBatch:
-        seq, att, rmask = build_sequences([d["prompt_ids"] for d in data], [d["response_ids"] for d in data])
+        rendered = [self._render(d) for d in data]
+        seq, att, rmask = build_sequences([ids for ids, _ in rendered], [d["response_ids"] for d in data])
         B, R = rmask.shape
         adv, old = torch.zeros(B, R), torch.zeros(B, R)
         lmask = rmask.clone()
@@ -80,8 +92,17 @@ class SkyRLTrainBackend:
                 old[i, :n] = torch.tensor(d["logprobs"], dtype=torch.float32)
             if d.get("loss_mask") is not None:          # multi-turn data: observation tokens carry weight 0
                 lmask[i, :n] = torch.tensor(d["loss_mask"], dtype=lmask.dtype)
-        return TrainingInputBatch({"sequences": seq, "attention_mask": att, "response_mask": rmask, "loss_mask": lmask,
-                                   "advantages": adv, "action_log_probs": old, "rollout_logprobs": old.clone()})
+        fields = {"sequences": seq, "attention_mask": att, "response_mask": rmask, "loss_mask": lmask,
+                  "advantages": adv, "action_log_probs": old, "rollout_logprobs": old.clone()}
+        feats = [f for _, f in rendered]
+        if any(f is not None for f in feats):
+            from ..train.batch import TensorList
+
+            dim = next(f["pixel_values"].shape[1] for f in feats if f is not None)
+            fields["pixel_values"] = TensorList([f["pixel_values"] if f else torch.zeros(0, dim) for f in feats])
+            fields["image_grid_thw"] = TensorList([f["image_grid_thw"] if f else torch.zeros(0, 3, dtype=torch.int64) for f in feats])
+            fields["mm_positions"] = TensorList([torch.tensor(f["positions"] if f else [], dtype=torch.int64) for f in feats])
+        return TrainingInputBatch(fields)
 
     def handle(self, req: dict) -> dict:
         kind = req["type"]
@@ -110,11 +131,14 @@ class SkyRLTrainBackend:
         if kind == "sample":
             sp = SamplingParams.from_dict(req.get("sampling_params"))
             n = int(req.get("num_samples", 1))
+            ids, feats = self._render(req)
             if self.external_url:
-                return self._sample_external(list(req["prompt_ids"]), sp, n)
+                if feats is not None:
+                    raise ValueError("image chunks cannot be sampled through an external text-completion server")
+                return self._sample_external(ids, sp, n)
             if self.engine.asleep:
                 self.engine.wake_up()
-            outs = self.engine.generate([list(req["prompt_ids"])] * n, sp)
+            outs = self.engine.generate([ids] * n, sp, mm=[feats] * n if feats is not None else None)
             return {"sequences": [{"tokens": o.response_ids, "logprobs": o.response_logprobs, "stop_reason": o.stop_reason} for o in outs]}
         if kind == "save_weights_for_sampler":
             # the sampler IS this backend's engine and reads the trainer's parameter buffer: publishing new weights is a

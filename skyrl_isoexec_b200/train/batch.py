@@ -19,6 +19,72 @@ from typing import Any, Iterable
 import torch
 
 
+class TensorList:
+    """One tensor per sample, shapes free (``pixel_values[i]`` is ``[patches of sample i, dim]``; a sample without any is a
+    tensor with zero rows). Behaves like a batch-major tensor for the container's slicing, selection, concatenation,
+    device moves and pickling (reference: B/training_batch.py:50-130)."""
+
+    def __init__(self, tensors: list[torch.Tensor]):
+        self.tensors = list(tensors)
+        for t in self.tensors:
+            if not torch.is_tensor(t):
+                raise TypeError(f"a TensorList holds tensors, got {type(t).__name__}")
+
+    @property
+    def shape(self) -> tuple:
+        return (len(self.tensors),)
+
+    def __len__(self) -> int:
+        return len(self.tensors)
+
+    def __iter__(self):
+        return iter(self.tensors)
+
+    def __getitem__(self, index):
+        if isinstance(index, slice):
+            return TensorList(self.tensors[index])
+        if torch.is_tensor(index):
+            if index.ndim == 0:
+                return self.tensors[int(index)]
+            index = index.tolist()
+        if isinstance(index, (list, tuple)):
+            return TensorList([self.tensors[int(i)] for i in index])
+        return self.tensors[index]
+
+    def to(self, device=None, dtype=None, non_blocking=False) -> "TensorList":
+        return TensorList([t.to(device=device, non_blocking=non_blocking) for t in self.tensors])
+
+    def contiguous(self) -> "TensorList":
+        return TensorList([t.contiguous() for t in self.tensors])
+
+    def pin_memory(self) -> "TensorList":
+        return TensorList([t.pin_memory() if t.numel() else t for t in self.tensors])
+
+    def detach(self) -> "TensorList":
+        return TensorList([t.detach() for t in self.tensors])
+
+    def cpu(self) -> "TensorList":
+        return TensorList([t.cpu() for t in self.tensors])
+
+    def expand_first(self, n: int) -> "TensorList":
+        return TensorList([self.tensors[0].clone() for _ in range(n)])
+
+    @staticmethod
+    def cat(lists: list["TensorList"]) -> "TensorList":
+        return TensorList([t for tl in lists for t in tl.tensors])
+
+    def __eq__(self, other) -> bool:
+        return isinstance(other, TensorList) and len(self) == len(other) and all(
+            a.shape == b.shape and torch.equal(a, b) for a, b in zip(self.tensors, other.tensors))
+
+    def __repr__(self) -> str:
+        return f"TensorList({[tuple(t.shape) for t in self.tensors]})"
+
+
+def _is_field(v) -> bool:
+    return torch.is_tensor(v) or isinstance(v, TensorList)
+
+
 class TensorBatch(dict):
     def __init__(self, *a, **kw):
         super().__init__(*a, **kw)
@@ -30,7 +96,7 @@ class TensorBatch(dict):
         for k, v in self.items():
             if v is None:
                 continue
-            if not torch.is_tensor(v):
+            if not _is_field(v):
                 raise TypeError(f"field {k!r} is {type(v).__name__}, expected a tensor")
             if n is None:
                 n = v.shape[0]
@@ -81,18 +147,23 @@ class TensorBatch(dict):
     def cat(cls, batches: Iterable["TensorBatch"]) -> "TensorBatch":
         batches = list(batches)
         keys = list(batches[0].keys())
-        out = cls({k: (None if batches[0][k] is None else torch.cat([b[k] for b in batches], 0)) for k in keys})
+        join = lambda vs: TensorList.cat(vs) if isinstance(vs[0], TensorList) else torch.cat(vs, 0)
+        out = cls({k: (None if batches[0][k] is None else join([b[k] for b in batches])) for k in keys})
         out.metadata = dict(batches[0].metadata)
         return out
 
     def __getstate__(self):
         buf = io.BytesIO()
-        torch.save({k: (None if v is None else v.detach().cpu()) for k, v in self.items()}, buf)
-        return {"tensors": buf.getvalue(), "metadata": self.metadata}
+        lists = sorted(k for k, v in self.items() if isinstance(v, TensorList))
+        torch.save({k: (None if v is None else (v.detach().cpu().tensors if k in lists else v.detach().cpu())) for k, v in self.items()}, buf)
+        return {"tensors": buf.getvalue(), "metadata": self.metadata, "lists": lists}
 
     def __setstate__(self, st):
         self.clear()
-        self.update(torch.load(io.BytesIO(st["tensors"]), weights_only=True))
+        d = torch.load(io.BytesIO(st["tensors"]), weights_only=True)
+        for k in st.get("lists", ()):
+            d[k] = TensorList(d[k])
+        self.update(d)
         self.metadata = st["metadata"]
 
     def __reduce__(self):
@@ -104,7 +175,8 @@ class TensorBatch(dict):
 
 class TrainingInputBatch(TensorBatch):
     """Fields: sequences, attention_mask, loss_mask, response_mask, action_log_probs,
-    base_action_log_probs, values, returns, advantages, kl, rewards, rollout_logprobs."""
+    base_action_log_probs, values, returns, advantages, kl, rewards, rollout_logprobs; vision-language batches add
+    ``pixel_values`` and ``image_grid_thw`` as ``TensorList`` fields (per sample: all patches / all grids of its images)."""
 
 
 def pad_training_input_batch(batch: TrainingInputBatch, multiple: int) -> TrainingInputBatch:
@@ -119,6 +191,9 @@ def pad_training_input_batch(batch: TrainingInputBatch, multiple: int) -> Traini
     for k, v in batch.items():
         if v is None:
             out[k] = None
+            continue
+        if isinstance(v, TensorList):
+            out[k] = TensorList.cat([v, v.expand_first(pad)])
             continue
         rep = v[:1].expand(pad, *v.shape[1:]).clone()
         if k in ("loss_mask", "response_mask"):

@@ -105,6 +105,8 @@ class GeneratorConfig:
     zero_reward_on_non_stop: bool = False
     apply_overlong_filtering: bool = False
     step_wise_trajectories: bool = False   # every model turn of a multi-turn trajectory is a training sample of its own
+    multimodal: bool = False               # conversations may hold images: the vision-language generator (train/vlm_generator.py)
+    append_eos_token_after_stop_str_in_multi_turn: bool = False
     rate_limit: dict = field(default_factory=dict)   # enabled / trajectories_per_second / max_concurrency (multi-turn trajectories)
 
 
@@ -313,6 +315,12 @@ def validate_cfg(cfg: SkyRLTrainConfig, world_size: int = 1) -> None:
     if world_size % mp:
         raise ValueError(f"world size {world_size} is not divisible by tp*pp*cp={mp}")
     dp = world_size // mp
+    if g.multimodal:
+        if g.batched or g.step_wise_trajectories:
+            raise ValueError("generator.multimodal renders every trajectory on its own: it needs generator.batched=false and "
+                             "generator.step_wise_trajectories=false")
+        if p.pipeline_model_parallel_size > 1 or p.context_parallel_size > 1:
+            raise ValueError("generator.multimodal is not supported with pipeline or context parallelism")
     if g.step_wise_trajectories:
         if g.batched and g.max_turns == 1:
             raise ValueError("generator.step_wise_trajectories needs the multi-turn agent loop (generator.batched=false)")

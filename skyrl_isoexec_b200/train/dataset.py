@@ -54,6 +54,11 @@ class PromptDataset:
             return True
         if isinstance(prompt, str):
             return len(self.tokenizer.encode(prompt)) <= limit
+        if any(isinstance(m.get("content"), (list, tuple)) for m in prompt):
+            # multimodal messages: the text parts are measured here; the images' placeholder tokens depend on the model and
+            # are counted by the generator against its max_input_length
+            prompt = [dict(m, content="".join(p if isinstance(p, str) else p.get("text", "") for p in m["content"]))
+                      if isinstance(m.get("content"), (list, tuple)) else m for m in prompt]
         return len(self.tokenizer.apply_chat_template(prompt, add_generation_prompt=True, tokenize=True)) <= limit
 
     def __len__(self):

@@ -134,6 +134,7 @@ class PackedMicroBatch:
     pred_rows: torch.Tensor       # int64 [Nr] hidden rows that predict a response token
     targets: torch.Tensor         # int64 [Nr]
     out_index: torch.Tensor       # int64 [Nr] flat index into [len(seq_index) * R]
+    packed_rows: list[int] | None = None   # the mini-batch row behind every entry of seq_lens (empty sequences are not packed)
 
 
 def pack_microbatches(sequences: torch.Tensor, attention_mask: torch.Tensor, num_actions: int,
@@ -162,12 +163,13 @@ def pack_microbatches(sequences: torch.Tensor, attention_mask: torch.Tensor, num
         groups[big:big] = [g[:len(g) // 2], g[len(g) // 2:]]
     out = []
     for grp in groups:
-        ids, pos, pred, tgt, oidx, seq_lens = [], [], [], [], [], []
+        ids, pos, pred, tgt, oidx, seq_lens, packed = [], [], [], [], [], [], []
         base = 0
         for j, b in enumerate(grp):
             n, f = lens[b], first[b]
             if n == 0:
                 continue
+            packed.append(b)
             ids.append(sequences[b, f:f + n])
             pos.append(torch.arange(n, dtype=torch.int32))
             plen = P - f                      # real prompt tokens
@@ -182,7 +184,7 @@ def pack_microbatches(sequences: torch.Tensor, attention_mask: torch.Tensor, num
         z = torch.zeros(0, dtype=torch.long)
         out.append(PackedMicroBatch(grp, torch.cat(ids), torch.cat(pos), seq_lens,
                                     torch.cat(pred) if pred else z, torch.cat(tgt) if tgt else z,
-                                    torch.cat(oidx) if oidx else z))
+                                    torch.cat(oidx) if oidx else z, packed))
     return out
 
 
@@ -542,9 +544,52 @@ class PolicyWorker:
             from ..ops.gdn import GDNMeta
 
             fc.gdn_meta = GDNMeta.packed(mb.seq_lens, dev)
+        fc.mm = self._image_rows(mb)
         hidden = self.model(mb.ids.to(dev, non_blocking=True), fc,
                             checkpoint_layers=self._ckpt_arg())
         return hidden
+
+    def set_images(self, batch) -> None:
+        """Remember the batch's ``pixel_values`` / ``image_grid_thw`` (per-sample lists) for the forwards that follow."""
+        pv = batch.get("pixel_values") if batch is not None else None
+        self._mm = None if pv is None else (pv, batch.get("image_grid_thw"), batch.get("mm_positions"))
+        if self._mm is not None:
+            if getattr(self.model, "vision", None) is None:
+                raise ValueError(f"the batch carries images but model {self.model.cfg.name!r} has no vision tower")
+            if self.ps.cp > 1 or self.ps.pp > 1:
+                raise ValueError("image inputs are not supported with context or pipeline parallelism")
+
+    def _image_rows(self, mb: PackedMicroBatch):
+        """(rows, features) of the micro-batch's image placeholder tokens: the tower runs image by image, without gradient,
+        exactly as the engine ran it for the rollout. Where the batch names the placeholder positions (``mm_positions``,
+        counted from the first real token of a sequence) they are used; otherwise a sequence's FIRST placeholder-id
+        tokens are taken, as many as its images give rows (a placeholder id the policy sampled later is plain text)."""
+        mm = getattr(self, "_mm", None)
+        if mm is None:
+            return None
+        tok = self.model.cfg.image_token_id
+        rows, feats, base = [], [], 0
+        for b, n in zip(mb.packed_rows if mb.packed_rows is not None else mb.seq_index, mb.seq_lens):
+            if mm[0][b].shape[0] == 0:
+                base += n
+                continue
+            f = self.model.vision.encode(mm[0][b], mm[1][b])
+            if mm[2] is not None:
+                r = mm[2][b].to(torch.long) + base
+                if r.numel() != f.shape[0] or (r.numel() and (int(r.max()) >= base + n or bool((mb.ids[r] != tok).any()))):
+                    raise ValueError(f"sample {b}: {r.numel()} image positions for {f.shape[0]} feature rows, or a position that is "
+                                     f"not an image placeholder token (a prompt truncated inside an image?)")
+            else:
+                r = (mb.ids[base:base + n] == tok).nonzero(as_tuple=True)[0][:f.shape[0]] + base
+                if r.numel() != f.shape[0]:
+                    raise ValueError(f"sample {b}: {r.numel()} image placeholder tokens but the images give {f.shape[0]} feature rows "
+                                     f"(a prompt truncated inside an image?)")
+            rows.append(r)
+            feats.append(f)
+            base += n
+        if not rows:
+            return None
+        return torch.cat(rows).to(self.device, non_blocking=True), torch.cat(feats, 0)
 
     # ---------------------------------------------------------------- context parallelism
     def _cp_span(self, mb: PackedMicroBatch) -> tuple[int, int, int]:
@@ -608,6 +653,7 @@ class PolicyWorker:
         self._arm_peak()
         R = batch["response_mask"].shape[1] if batch.get("response_mask") is not None else batch.metadata["response_length"]
         seqs, att = batch["sequences"], batch["attention_mask"]
+        self.set_images(batch)
         out = torch.zeros(seqs.shape[0], R, dtype=torch.float32)
         for mb in self._pack(seqs, att, R):
             hidden = self._run_model(mb, "trainer_score")
@@ -629,6 +675,7 @@ class PolicyWorker:
         self._arm_peak()
         R = batch["response_mask"].shape[1]
         seqs, att = batch["sequences"], batch["attention_mask"]
+        self.set_images(batch)
         loss_fn = alg.get_policy_loss(algo.policy_loss_type)
         want_ent = self.cfg.want_entropy or algo.use_entropy_loss
         tot = {"loss": 0.0, "clip_ratio_num": 0.0, "tokens": 0.0, "entropy_sum": 0.0, "kl_sum": 0.0}

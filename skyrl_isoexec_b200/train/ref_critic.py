@@ -71,6 +71,7 @@ class CriticWorker:
         R = batch["response_mask"].shape[1]
         seqs, att = batch["sequences"], batch["attention_mask"]
         out = torch.zeros(seqs.shape[0], R, dtype=torch.float32)
+        self._policy_like.set_images(batch)
         for mb in pack_microbatches(seqs, att, R, self.cfg.max_tokens_per_microbatch):
             hidden = PolicyWorker._run_model(self._policy_like, mb, "critic_score")
             v = self._values(mb, hidden)
@@ -89,6 +90,7 @@ class CriticWorker:
             dist.all_reduce(t, group=self.ps.dp_group)
             tot_mask = float(t)
         tot = {"loss": 0.0, "clip": 0.0, "n": 0}
+        self._policy_like.set_images(batch)
         for mb in pack_microbatches(seqs, att, R, self.cfg.max_tokens_per_microbatch):
             idx = torch.tensor(mb.seq_index)
             hidden = PolicyWorker._run_model(self._policy_like, mb, "critic_fwd")

@@ -321,11 +321,22 @@ class RayPPOTrainer:
             # colocated, same TP layout: the engine computes with the trainer's flat parameter buffer
             self.engine = LLMEngine(model, ecfg)
         self.infer = NativeInferenceEngine(self.engine, self.tokenizer)
-        self.generator = SkyRLGymGenerator(self.infer, self.tokenizer, max_turns=g.max_turns, batched=g.batched,
-                                           env_config=self.cfg.environment.env_kwargs,
-                                           zero_reward_on_non_stop=g.zero_reward_on_non_stop,
-                                           apply_overlong_filtering=g.apply_overlong_filtering,
-                                           rate_limit=g.rate_limit or None, step_wise=g.step_wise_trajectories)
+        if g.multimodal:
+            from .vlm_generator import SkyRLVLMGymGenerator
+
+            if not mcfg.has_vision:
+                raise ValueError(f"generator.multimodal=true but model {mcfg.name!r} has no vision tower")
+            self.generator = SkyRLVLMGymGenerator(self.infer, self.tokenizer, max_turns=g.max_turns,
+                                                  append_eos_after_stop_str=g.append_eos_token_after_stop_str_in_multi_turn,
+                                                  env_config=self.cfg.environment.env_kwargs,
+                                                  zero_reward_on_non_stop=g.zero_reward_on_non_stop,
+                                                  apply_overlong_filtering=g.apply_overlong_filtering, rate_limit=g.rate_limit or None)
+        else:
+            self.generator = SkyRLGymGenerator(self.infer, self.tokenizer, max_turns=g.max_turns, batched=g.batched,
+                                               env_config=self.cfg.environment.env_kwargs,
+                                               zero_reward_on_non_stop=g.zero_reward_on_non_stop,
+                                               apply_overlong_filtering=g.apply_overlong_filtering,
+                                               rate_limit=g.rate_limit or None, step_wise=g.step_wise_trajectories)
         if t.isoexec.enabled:
             self.adapter_trainer = ContractAdapter("trainer", model, self.rank, trainer_tp=self.ps.tp, engine_tp=tp_e, trainer_pp=self.ps.pp)
             self.adapter_trainer.run_install()
@@ -486,8 +497,21 @@ class RayPPOTrainer:
                 rewards[i, n - 1] = float(r)     # outcome reward sits on the last response token
             if go.get("rollout_logprobs") is not None:
                 rollout_lp[i, :n] = torch.tensor(go["rollout_logprobs"][i], dtype=torch.float32)
-        b = TrainingInputBatch({"sequences": seq, "attention_mask": att, "response_mask": rmask, "loss_mask": loss_mask,
-                                "rewards": rewards, "rollout_logprobs": rollout_lp})
+        fields = {"sequences": seq, "attention_mask": att, "response_mask": rmask, "loss_mask": loss_mask,
+                  "rewards": rewards, "rollout_logprobs": rollout_lp}
+        if go.get("pixel_values") is not None:
+            # vision-language rollouts: per sample, the patches and grids of its images and where the placeholder tokens
+            # are (reference: R/train/trainer.py:913-966). Positions count from the first prompt token, which is where the
+            # packed forward starts a sequence, so a prompt must not have been cut from the left
+            from .batch import TensorList
+
+            if go.get("image_grid_thw") is None or len(go["pixel_values"]) != B or len(go["image_grid_thw"]) != B:
+                raise ValueError("pixel_values and image_grid_thw must both be given, one entry per sample")
+            fields["pixel_values"] = TensorList(list(go["pixel_values"]))
+            fields["image_grid_thw"] = TensorList(list(go["image_grid_thw"]))
+            if go.get("mm_positions") is not None:
+                fields["mm_positions"] = TensorList([torch.as_tensor(p, dtype=torch.int64) for p in go["mm_positions"]])
+        b = TrainingInputBatch(fields)
         lens = rmask.sum(1)
         b.metadata = {"uids": list(uids), "response_length": R, "avg_response_length": float(lens.mean()),
                       "max_response_length": int(lens.max())}

@@ -26,6 +26,20 @@ class ByteTokenizer:
                 out += names.get(t, "").encode()
         return out.decode("utf-8", errors="replace")
 
+    def encode_rendered(self, text: str) -> list[int]:
+        """Text produced by ``apply_chat_template(tokenize=False)`` back to ids: the names of the special tokens become
+        their ids again, everything else is bytes."""
+        import re
+
+        names = {"<s>": self.BOS, "</s>": self.EOS, "<|im_start|>": self.IM_START, "<|im_end|>": self.IM_END}
+        ids: list[int] = []
+        for piece in re.split("(" + "|".join(re.escape(n) for n in names) + ")", text):
+            if piece in names:
+                ids.append(names[piece])
+            elif piece:
+                ids += self.encode(piece)
+        return ids
+
     def apply_chat_template(self, messages: list[dict], add_generation_prompt: bool = True, tokenize: bool = True):
         ids: list[int] = []
         for m in messages:
