@@ -49,6 +49,8 @@ class RefConfig:
 class PolicyConfig:
     model: str = "tiny-qwen3"           # preset name or path of a saved config
     model_overrides: dict = field(default_factory=dict)
+    tokenizer_path: str = ""            # "" = none (token-id prompts and environments); "byte" = the built-in byte tokenizer;
+                                        # else a directory transformers.AutoTokenizer loads (text prompts, chat templates, stop strings)
     optimizer_config: OptimizerConfig = field(default_factory=OptimizerConfig)
     parallel: ParallelConfig = field(default_factory=ParallelConfig)
     seed: int = 0

@@ -41,7 +41,20 @@ class BasePPOExp:
 
     # ---- hooks
     def get_tokenizer(self):
-        return None
+        """``trainer.policy.tokenizer_path``: nothing, the built-in byte tokenizer, or a Hugging Face tokenizer directory."""
+        path = self.cfg.trainer.policy.tokenizer_path
+        if not path:
+            return None
+        if getattr(self, "_tok", None) is None:
+            if path == "byte":
+                from ...utils.tokenizer import ByteTokenizer
+
+                self._tok = ByteTokenizer()
+            else:
+                from transformers import AutoTokenizer
+
+                self._tok = AutoTokenizer.from_pretrained(path)
+        return self._tok
 
     def get_train_dataset(self):
         from ..dataset import PromptDataset
