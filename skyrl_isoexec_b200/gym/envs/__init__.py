@@ -1,1 +1,1 @@
-from . import synthetic, gsm8k, multiply, aime, tool_envs, rlm, llm_judge, visual  # noqa: F401
+from . import synthetic, gsm8k, multiply, aime, sql, search, lcb, rlm, llm_judge, visual  # noqa: F401

@@ -109,6 +109,10 @@ class GeneratorConfig:
     step_wise_trajectories: bool = False   # every model turn of a multi-turn trajectory is a training sample of its own
     multimodal: bool = False               # conversations may hold images: the vision-language generator (train/vlm_generator.py)
     append_eos_token_after_stop_str_in_multi_turn: bool = False
+    rlm: bool = False                      # REPL environments whose blocks query the policy and spawn child trajectories (train/rlm_generator.py)
+    rlm_max_depth: int = 1
+    rlm_lm_max_tokens: int = 256
+    rlm_train_children: bool = False       # child trajectories become samples of their own, rewarded with their root's outcome
     rate_limit: dict = field(default_factory=dict)   # enabled / trajectories_per_second / max_concurrency (multi-turn trajectories)
 
 
@@ -323,6 +327,8 @@ def validate_cfg(cfg: SkyRLTrainConfig, world_size: int = 1) -> None:
                              "generator.step_wise_trajectories=false")
         if p.pipeline_model_parallel_size > 1 or p.context_parallel_size > 1:
             raise ValueError("generator.multimodal is not supported with pipeline or context parallelism")
+    if g.rlm and (g.multimodal or g.step_wise_trajectories):
+        raise ValueError("generator.rlm cannot be combined with generator.multimodal or generator.step_wise_trajectories")
     if g.step_wise_trajectories:
         if g.batched and g.max_turns == 1:
             raise ValueError("generator.step_wise_trajectories needs the multi-turn agent loop (generator.batched=false)")

@@ -331,6 +331,13 @@ class RayPPOTrainer:
                                                   env_config=self.cfg.environment.env_kwargs,
                                                   zero_reward_on_non_stop=g.zero_reward_on_non_stop,
                                                   apply_overlong_filtering=g.apply_overlong_filtering, rate_limit=g.rate_limit or None)
+        elif g.rlm:
+            from .rlm_generator import RLMGymGenerator
+
+            self.generator = RLMGymGenerator(self.infer, self.tokenizer, max_turns=g.max_turns, max_depth=g.rlm_max_depth,
+                                             lm_max_tokens=g.rlm_lm_max_tokens, train_children=g.rlm_train_children,
+                                             env_config=self.cfg.environment.env_kwargs, zero_reward_on_non_stop=g.zero_reward_on_non_stop,
+                                             apply_overlong_filtering=g.apply_overlong_filtering, rate_limit=g.rate_limit or None)
         else:
             self.generator = SkyRLGymGenerator(self.infer, self.tokenizer, max_turns=g.max_turns, batched=g.batched,
                                                env_config=self.cfg.environment.env_kwargs,
