@@ -114,7 +114,8 @@ class NativeInferenceEngine(InferenceEngineInterface):
         texts = [self.tokenizer.decode(o.response_ids) if self.tokenizer is not None else "" for o in outs]
         return {"responses": texts, "response_ids": [o.response_ids for o in outs],
                 "stop_reasons": [o.stop_reason for o in outs],
-                "response_logprobs": [o.response_logprobs for o in outs], "prompt_logprobs": None,
+                "response_logprobs": [o.response_logprobs for o in outs],
+                "prompt_logprobs": [o.prompt_logprobs for o in outs] if sp.prompt_logprobs is not None else None,
                 "rollout_expert_indices": None}
 
     async def render_chat_completion(self, request_payload: dict) -> dict:

@@ -21,6 +21,7 @@ from ..ops import functional as F
 from ..ops.functional import PAGE
 from .kv_cache import KVCache
 from .sampler import Sampler, SamplingParams
+from .sampler import needs_history as _needs_history
 
 
 @dataclass
@@ -65,6 +66,7 @@ class Sequence:
     mm_pos: list[int] | None = None
     mm_feats: torch.Tensor | None = None
     mm_key: bytes | None = None
+    prompt_logprobs: list | None = None     # requested with SamplingParams.prompt_logprobs: [None, lp(token 1 | token 0), ...]
 
     @property
     def tokens(self) -> list[int]:
@@ -85,6 +87,7 @@ class RequestOutput:
     response_ids: list[int]
     response_logprobs: list[float]
     stop_reason: str
+    prompt_logprobs: list | None = None
 
 
 class Scheduler:
@@ -192,7 +195,8 @@ class Scheduler:
                     self.shared_prompt_tokens += s.shared_tokens
                     if self.adopt_hook is not None:
                         self.adopt_hook(s, ld)
-            if self.prefix is not None and s.leader is None and not s.pages and s.num_computed == 0 and s.mm_feats is None:
+            if self.prefix is not None and s.leader is None and not s.pages and s.num_computed == 0 and s.mm_feats is None \
+                    and s.prompt_logprobs is None:
                 pages, key = self.prefix.match(s.tokens)
                 if pages:
                     s.pages, s.num_computed = pages, len(pages) * PAGE
@@ -355,14 +359,14 @@ class LLMEngine:
         ``image_token_id``). The vision tower runs here, once per request."""
         if len(prompt_ids) == 0:
             raise ValueError("empty prompt")
-        if getattr(params, "repetition_penalty", 1.0) not in (1.0, None):
-            raise ValueError("repetition_penalty is not implemented by this engine; leave it at 1.0")
         if len(prompt_ids) >= self.max_len:
             raise ValueError(f"prompt of {len(prompt_ids)} tokens exceeds max_model_len={self.max_len}")
         seq = Sequence(self._next_id, list(prompt_ids), params, request_index=request_index, arrival=time.time())
         self._next_id += 1
         if mm is not None and mm.get("pixel_values") is not None and mm["pixel_values"].shape[0]:
             self._attach_images(seq, mm)
+        if params.prompt_logprobs is not None:
+            seq.prompt_logprobs = [None] * len(prompt_ids)
         if self.prefix_cache is not None and self.prefix_cache.boundary is not None:
             # recurrent layers: the prefill stops once at the last full page of the prompt, so that the state there can be
             # kept for later requests that share the prompt
@@ -423,7 +427,9 @@ class LLMEngine:
         decode, prefill = self.scheduler.schedule()
         if not decode and not prefill:
             return []
-        if not prefill and self._graphs_enabled():
+        if not prefill and self._graphs_enabled() and not any(_needs_history(s.params) for s in decode):
+            # (a request whose sampling looks at its own tokens cannot run ahead of the host: the token in flight is part
+            # of that history)
             self._inflight = self._launch_decode(decode, ahead=False)
             return []
         G = self.model.hq // self.model.hkv
@@ -476,6 +482,8 @@ class LLMEngine:
         if mm_rows:
             fc.mm = (self._h2d(torch.tensor(mm_rows, dtype=torch.int64)), torch.cat(mm_feats, 0))
         hidden = self.model(self._h2d(torch.tensor(ids, dtype=torch.int64)), fc)
+        if any(s.prompt_logprobs is not None for s, _, _ in prefill):
+            self._fill_prompt_logprobs(hidden, prefill, len(decode))
         for s in decode:
             s.num_computed += 1
             self._note_progress(s, False)
@@ -494,12 +502,37 @@ class LLMEngine:
         logits = self.model.logits(hidden.index_select(0, rows))
         return self._sample_and_finish(logits, sample_seqs)
 
+    def _fill_prompt_logprobs(self, hidden: torch.Tensor, prefill: list, first_row: int, chunk_rows: int = 1024) -> None:
+        """Log-probability of every prompt token given the tokens before it, for the requests that asked: row t of a
+        prefill chunk predicts token t + 1, so the rows whose successor is still a prompt token are scored with the
+        kernel that scores sampled tokens. (A prompt cut into prefill chunks loses nothing: the row that predicts a
+        chunk's first token is the last row of the chunk before it.)"""
+        row = first_row
+        for s, start, n in prefill:
+            if s.prompt_logprobs is not None:
+                P = len(s.prompt_ids)
+                hi = min(start + n, P - 1)                      # rows start .. hi-1 predict prompt tokens start+1 .. hi
+                for lo in range(start, hi, chunk_rows):
+                    up = min(hi, lo + chunk_rows)
+                    if all(v is not None for v in s.prompt_logprobs[lo + 1:up + 1]):
+                        continue                                # a recomputed (preempted) sequence: already filled
+                    logits = self.model.logits(hidden[row + (lo - start):row + (up - start)])
+                    if self.model.ps.tp > 1:
+                        from ..parallel.tp import column_parallel_gather
+
+                        logits = column_parallel_gather(logits, self.model.ps)
+                    tg = self._h2d(torch.tensor(s.prompt_ids[lo + 1:up + 1], dtype=torch.int64))
+                    lp, _ = F.token_logprobs(logits, tg, self.mcfg.logprob_leaves)
+                    s.prompt_logprobs[lo + 1:up + 1] = lp.tolist()
+            row += n
+
     def _sample_and_finish(self, logits: torch.Tensor, sample_seqs: list[Sequence]) -> list[Sequence]:
         if self.model.ps.tp > 1:
             from ..parallel.tp import column_parallel_gather
 
             logits = column_parallel_gather(logits, self.model.ps)
-        tokens, lps = self.sampler(logits, [s.params for s in sample_seqs])
+        hist = [(s.prompt_ids, s.output_ids) for s in sample_seqs] if any(_needs_history(s.params) for s in sample_seqs) else None
+        tokens, lps = self.sampler(logits, [s.params for s in sample_seqs], histories=hist, eos_token_id=self.cfg.eos_token_id)
         self.stats["d2h_bytes"] += tokens.numel() * 8 + lps.numel() * 4
         tokens, lps = tokens.tolist(), lps.tolist()
         finished: list[Sequence] = []
@@ -671,6 +704,8 @@ class LLMEngine:
         for s in seqs:
             if s.num_computed or s.pages or s.output_ids:
                 continue                                        # already under way
+            if s.prompt_logprobs is not None:
+                continue                                        # every prompt row of such a request must be computed
             ld = leaders.setdefault((tuple(s.prompt_ids), s.mm_key), s)
             shared = ((len(s.prompt_ids) - 1) // PAGE) * PAGE   # a multiple of the GatedDeltaNet chunk too: no open chunk there
             if ld is not s and shared > 0:
@@ -698,4 +733,4 @@ class LLMEngine:
             self.step()
             if self._ep_lockstep and not self._global_work:
                 break
-        return [RequestOutput(s.prompt_ids, s.output_ids, s.logprobs, s.stop_reason or "length") for s in seqs]
+        return [RequestOutput(s.prompt_ids, s.output_ids, s.logprobs, s.stop_reason or "length", s.prompt_logprobs) for s in seqs]

@@ -24,8 +24,13 @@ class SamplingParams:
     top_p: float = 1.0
     top_k: int = -1
     min_p: float = 0.0
-    repetition_penalty: float = 1.0
+    repetition_penalty: float = 1.0     # > 1: logits of tokens seen in prompt or output are divided (if positive) or multiplied by it
+    presence_penalty: float = 0.0       # subtracted once from the logit of every token generated so far
+    frequency_penalty: float = 0.0      # subtracted per occurrence among the generated tokens
+    min_tokens: int = 0                 # end-of-sequence and stop tokens cannot be drawn before this many tokens were generated
+    logit_bias: dict | None = None      # {token id: additive bias}
     logprobs: int | None = 1
+    prompt_logprobs: int | None = None  # not None: also report the log-probability of every prompt token given the tokens before it
     stop_token_ids: tuple[int, ...] = ()
     stop: tuple[str, ...] = ()          # stop strings (need a detokenizer on the engine: ``LLMEngine.detokenize``)
     ignore_eos: bool = False
@@ -41,17 +46,28 @@ class SamplingParams:
         if "stop" in d:
             st = d.pop("stop")
             d["stop"] = () if not st else ((st,) if isinstance(st, str) else tuple(st))
+        if d.get("logit_bias"):
+            d["logit_bias"] = {int(k): float(v) for k, v in d["logit_bias"].items()}
         known = {k: v for k, v in d.items() if k in SamplingParams.__dataclass_fields__}
         if "stop_token_ids" in known and known["stop_token_ids"] is not None:
             known["stop_token_ids"] = tuple(known["stop_token_ids"])
         return SamplingParams(**known)
 
 
+def needs_history(p: SamplingParams) -> bool:
+    """Whether drawing a token for this request depends on the tokens of its own sequence (penalties, ``min_tokens``)."""
+    return bool((p.repetition_penalty not in (1.0, None)) or p.presence_penalty or p.frequency_penalty or p.min_tokens > 0)
+
+
+def shapes_logits(p: SamplingParams) -> bool:
+    return needs_history(p) or bool(p.logit_bias)
+
+
 def isoexec_sampling_constraints(p: SamplingParams) -> SamplingParams:
     """Under the execution contract the importance ratio is exactly 1 only if the behaviour policy
-    is the raw model distribution: temperature 1 and no truncation."""
-    if p.temperature != 1.0 or p.top_p != 1.0 or p.top_k not in (-1, 0) or p.min_p != 0.0:
-        raise ValueError("IsoExec rollouts require temperature=1.0, top_p=1.0, top_k=-1, min_p=0.0")
+    is the raw model distribution: temperature 1, no truncation, no penalties or biases."""
+    if p.temperature != 1.0 or p.top_p != 1.0 or p.top_k not in (-1, 0) or p.min_p != 0.0 or shapes_logits(p):
+        raise ValueError("IsoExec rollouts require temperature=1.0, top_p=1.0, top_k=-1, min_p=0.0 and no penalties, min_tokens or logit_bias")
     return p
 
 
@@ -94,18 +110,45 @@ class Sampler:
         logprobs, _ = F.token_logprobs(logits, tokens, self.leaves)
         return tokens, logprobs
 
+    @staticmethod
+    def _shape_row(row: torch.Tensor, p: SamplingParams, history, eos_token_id) -> torch.Tensor:
+        """Penalties, bias and the ``min_tokens`` mask on one row of fp32 logits (before the temperature, as vLLM does)."""
+        prompt_ids, output_ids = history if history is not None else ((), ())
+        dev = row.device
+        if p.repetition_penalty not in (1.0, None) and (prompt_ids or output_ids):
+            seen = torch.tensor(sorted(set(prompt_ids) | set(output_ids)), dtype=torch.long, device=dev)
+            v = row[seen]
+            row[seen] = torch.where(v > 0, v / p.repetition_penalty, v * p.repetition_penalty)
+        if (p.presence_penalty or p.frequency_penalty) and output_ids:
+            ids, counts = torch.tensor(output_ids, dtype=torch.long, device=dev).unique(return_counts=True)
+            row[ids] -= p.frequency_penalty * counts.to(row.dtype) + p.presence_penalty
+        if p.logit_bias:
+            ids = torch.tensor(list(p.logit_bias), dtype=torch.long, device=dev)
+            row[ids] += torch.tensor(list(p.logit_bias.values()), dtype=row.dtype, device=dev)
+        if p.min_tokens > 0 and len(output_ids) < p.min_tokens:
+            stop = set(p.stop_token_ids) | ({eos_token_id} if eos_token_id is not None and not p.ignore_eos else set())
+            if stop:
+                row[torch.tensor(sorted(stop), dtype=torch.long, device=dev)] = float("-inf")
+        return row
+
     @torch.no_grad()
-    def __call__(self, logits: torch.Tensor, params: list[SamplingParams]):
-        """logits [n, V] -> (token ids int64 [n], raw logprobs fp32 [n])."""
+    def __call__(self, logits: torch.Tensor, params: list[SamplingParams], histories: list | None = None, eos_token_id: int | None = None):
+        """logits [n, V] -> (token ids int64 [n], raw logprobs fp32 [n]). ``histories``: per row ``(prompt ids, generated
+        ids)``, needed by requests whose parameters look at their own sequence (``needs_history``)."""
         n, V = logits.shape
-        untruncated = all(p.top_p >= 1.0 and p.top_k <= 0 and p.min_p <= 0.0 for p in params)
+        shaped = [shapes_logits(p) for p in params]
+        if any(needs_history(p) for p in params) and histories is None:
+            raise ValueError("penalties and min_tokens need the sequences' token histories")
+        untruncated = all(p.top_p >= 1.0 and p.top_k <= 0 and p.min_p <= 0.0 for p in params) and not any(shaped)
         if untruncated and logits.is_cuda and logits.dtype == torch.bfloat16 and logits.stride(1) == 1 and logits.stride(0) % 8 == 0:
             return self._fused(logits, params)
         x = logits.float()
-        uniform = all(p.temperature == 1.0 and p.top_p >= 1.0 and p.top_k <= 0 and p.min_p <= 0.0 for p in params)
+        uniform = all(p.temperature == 1.0 and p.top_p >= 1.0 and p.top_k <= 0 and p.min_p <= 0.0 for p in params) and not any(shaped)
         if not uniform:
             x = x.clone()
             for i, p in enumerate(params):
+                if shaped[i]:
+                    x[i] = self._shape_row(x[i], p, histories[i] if histories is not None else None, eos_token_id)
                 if p.temperature == 0.0:
                     continue
                 row = x[i] / p.temperature

@@ -283,8 +283,11 @@ class InferenceServer:
 
             mm = [decode_features(f) for f in mm]
         seqs, aborted = self._submit(ids, SamplingParams.from_dict(body.get("sampling_params")), mm=mm)
-        return {"response_ids": [s.output_ids for s in seqs], "response_logprobs": [s.logprobs for s in seqs],
-                "stop_reasons": [s.stop_reason for s in seqs], "aborted": aborted}
+        out = {"response_ids": [s.output_ids for s in seqs], "response_logprobs": [s.logprobs for s in seqs],
+               "stop_reasons": [s.stop_reason for s in seqs], "aborted": aborted}
+        if any(s.prompt_logprobs is not None for s in seqs):
+            out["prompt_logprobs"] = [s.prompt_logprobs for s in seqs]
+        return out
 
     def _render(self, body: dict) -> dict:
         """Token ids of a conversation with every image a run of placeholder tokens, and the images' patches in a
@@ -419,6 +422,10 @@ class RemoteInferenceClient(InferenceEngineInterface):
             for j, i in enumerate(idx):
                 out["response_ids"][i], out["response_logprobs"][i] = r["response_ids"][j], r["response_logprobs"][j]
                 out["stop_reasons"][i] = r["stop_reasons"][j]
+                if r.get("prompt_logprobs") is not None:
+                    if out["prompt_logprobs"] is None:
+                        out["prompt_logprobs"] = [None] * n
+                    out["prompt_logprobs"][i] = r["prompt_logprobs"][j]
         return out
 
     async def completion(self, request_payload: dict) -> dict:

@@ -139,7 +139,10 @@ class SkyRLTrainBackend:
             if self.engine.asleep:
                 self.engine.wake_up()
             outs = self.engine.generate([ids] * n, sp, mm=[feats] * n if feats is not None else None)
-            return {"sequences": [{"tokens": o.response_ids, "logprobs": o.response_logprobs, "stop_reason": o.stop_reason} for o in outs]}
+            res = {"sequences": [{"tokens": o.response_ids, "logprobs": o.response_logprobs, "stop_reason": o.stop_reason} for o in outs]}
+            if sp.prompt_logprobs is not None:
+                res["prompt_logprobs"] = outs[0].prompt_logprobs          # the samples share the prompt
+            return res
         if kind == "save_weights_for_sampler":
             # the sampler IS this backend's engine and reads the trainer's parameter buffer: publishing new weights is a
             # version bump plus dropping what the engine cached under the old ones (optionally also a file for others)

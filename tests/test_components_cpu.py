@@ -1096,3 +1096,69 @@ def test_samples_of_one_prompt_share_recurrent_state_in_a_hybrid_model():
     for i, o in enumerate(o3):
         ro[i, :len(o.response_logprobs)] = torch.tensor(o.response_logprobs)
     assert count_bit_mismatches((lp * rmask).contiguous(), (ro * rmask).contiguous()) == 0
+
+
+def test_sampling_penalties_min_tokens_and_logit_bias():
+    from skyrl_isoexec_b200.engine.llm_engine import EngineConfig, LLMEngine
+    from skyrl_isoexec_b200.engine.sampler import Sampler, SamplingParams, isoexec_sampling_constraints, needs_history
+    from skyrl_isoexec_b200.models.config import get_config
+    from skyrl_isoexec_b200.models.decoder import DecoderLM
+
+    sam = Sampler("cpu", seed=0)
+    logits = torch.cat([torch.tensor([[2.0, 1.0, -1.0, 0.5, 0.0]]), torch.full((1, 11), -3.0)], 1)     # 16 wide: at least one token per leaf
+    greedy = lambda **kw: SamplingParams(temperature=0.0, **kw)
+    pick = lambda p, hist=None, eos=None: int(sam(logits, [p], histories=[hist] if hist is not None else None, eos_token_id=eos)[0][0])
+    assert pick(greedy()) == 0
+    assert pick(greedy(repetition_penalty=4.0), ([0], [])) == 1                       # 2.0 / 4 < 1.0
+    assert pick(greedy(repetition_penalty=4.0), ([2], [])) == 0                       # a negative logit gets more negative
+    assert pick(greedy(presence_penalty=1.5), ([0], [])) == 0                         # the prompt does not count for presence
+    assert pick(greedy(presence_penalty=1.5), ([], [0])) == 1
+    assert pick(greedy(frequency_penalty=0.6), ([], [0])) == 0 and pick(greedy(frequency_penalty=0.6), ([], [0, 0])) == 1
+    assert pick(greedy(logit_bias={3: 5.0})) == 3
+    assert pick(greedy(min_tokens=2), ([], [4]), eos=0) == 1 and pick(greedy(min_tokens=1), ([], [4]), eos=0) == 0
+    assert pick(greedy(min_tokens=2, stop_token_ids=(1,)), ([], []), eos=0) == 3
+    # the reported logprob is the raw one whatever shaped the draw
+    tok, lp = sam(logits, [greedy(logit_bias={3: 5.0})])
+    assert abs(float(lp[0]) - float(torch.log_softmax(logits[0], -1)[3])) < 1e-6
+    with pytest.raises(ValueError, match="histories"):
+        sam(logits, [greedy(repetition_penalty=2.0)])
+    assert needs_history(SamplingParams(min_tokens=1)) and not needs_history(SamplingParams(logit_bias={1: 1.0}))
+    with pytest.raises(ValueError):
+        isoexec_sampling_constraints(SamplingParams(repetition_penalty=1.1))
+    assert SamplingParams.from_dict({"logit_bias": {"7": 2}}).logit_bias == {7: 2.0}
+    # through the engine: a heavy repetition penalty makes every greedy token new; min_tokens holds the end of sequence back
+    eng = LLMEngine(DecoderLM(get_config("tiny-qwen3"), seed=0), EngineConfig(num_kv_pages=8, seed=1, eos_token_id=7))
+    prompt = [5, 6, 7, 8]
+    plain = eng.generate([prompt], SamplingParams(max_generate_length=24, temperature=0.0, ignore_eos=True))[0].response_ids
+    pen = eng.generate([prompt], SamplingParams(max_generate_length=24, temperature=0.0, ignore_eos=True, repetition_penalty=1e6))[0].response_ids
+    assert len(set(pen)) == len(pen) and not set(pen) & set(prompt) and len(set(plain)) < len(plain)
+    forced = SamplingParams(max_generate_length=12, temperature=0.0, logit_bias={7: 1e4})
+    assert eng.generate([prompt], forced)[0].response_ids == [7]                      # the biased end-of-sequence token ends it at once
+    held = SamplingParams(max_generate_length=12, temperature=0.0, logit_bias={7: 1e4}, min_tokens=5)
+    out = eng.generate([prompt], held)[0]
+    assert len(out.response_ids) == 6 and out.response_ids[-1] == 7 and 7 not in out.response_ids[:5] and out.stop_reason == "stop"
+
+
+def test_prompt_logprobs_are_the_scoring_forwards_bits_across_prefill_chunks():
+    from skyrl_isoexec_b200.engine.llm_engine import EngineConfig, LLMEngine
+    from skyrl_isoexec_b200.engine.sampler import SamplingParams
+    from skyrl_isoexec_b200.models.config import get_config
+    from skyrl_isoexec_b200.models.decoder import DecoderLM
+    from skyrl_isoexec_b200.train.batch import TrainingInputBatch, build_sequences
+    from skyrl_isoexec_b200.train.policy_worker import PolicyWorker, WorkerConfig
+
+    m = DecoderLM(get_config("tiny-qwen3"), seed=0)
+    eng = LLMEngine(m, EngineConfig(num_kv_pages=16, seed=1, max_num_batched_tokens=48))       # prompts are prefilled in pieces
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(5, 500, (n,), generator=g).tolist() for n in (130, 61, 7)]
+    outs = eng.generate(prompts + [prompts[0]], [SamplingParams(max_generate_length=3, ignore_eos=True, prompt_logprobs=1)] * 3
+                        + [SamplingParams(max_generate_length=3, ignore_eos=True)])
+    assert outs[3].prompt_logprobs is None and eng.scheduler.shared_prompt_tokens == 0           # such requests compute every prompt row
+    w = PolicyWorker(m, WorkerConfig(max_tokens_per_microbatch=4096))
+    for p, o in zip(prompts, outs):
+        assert o.prompt_logprobs[0] is None and len(o.prompt_logprobs) == len(p)
+        # score tokens 1.. of the prompt as a "response" to its first token
+        seq, att, rmask = build_sequences([p[:1]], [p[1:]])
+        lp = w.forward(TrainingInputBatch({"sequences": seq, "attention_mask": att, "response_mask": rmask}))[0]
+        got = torch.tensor(o.prompt_logprobs[1:])
+        assert torch.equal(got.view(torch.int32), lp.view(torch.int32))
