@@ -87,6 +87,8 @@ class InferenceEngineConfig:
     num_kv_pages: int = 0
     enforce_eager: bool = False
     enable_prefix_caching: bool = False
+    own_weights: bool = False           # the engine computes with a copy of the weights of its own (filled by every weight sync) even
+                                        # when its layout is the trainer's: what lets generation run WHILE the trainer updates
     share_prompt_pages: bool = True     # the n samples of a prompt read one copy of its full KV pages (same bits; not a cache)
     share_recurrent_state: bool = False # GatedDeltaNet models: the samples also start from one snapshot of the recurrent state
     weight_sync_backend: str = "nccl"   # nccl | gloo | cuda_ipc | shared

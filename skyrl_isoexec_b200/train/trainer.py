@@ -173,7 +173,7 @@ class RayPPOTrainer:
         trainer TP groups, and each sync reshards the weights (sync/reshard.py). Collective: every rank calls it."""
         ie = self.cfg.generator.inference_engine
         tp_e = ie.tensor_parallel_size or self.ps.tp
-        self.separate_engine = tp_e != self.ps.tp
+        self.separate_engine = tp_e != self.ps.tp or bool(getattr(ie, "own_weights", False))
         self.engine_ps = self.ps
         self.engines_per_replica = 1
         self.replica_group, self.replica_size, self.replica_rank = self.ps.tp_group, self.ps.tp, self.ps.tp_rank
@@ -204,8 +204,11 @@ class RayPPOTrainer:
         if self.separate_engine:
             if self.ps.tp % tp_e or self.ps.pp > 1 or self.ps.cp > 1 or self.ps.ep > 1:
                 raise ValueError(f"engine TP {tp_e} must divide trainer TP {self.ps.tp}, with pp = cp = ep = 1")
-            self.engine_ps = ParallelState.build(tp=tp_e, kv_rep=max(1, tp_e // mcfg.num_kv_heads)) if tp_e > 1 or self.world > 1 \
-                else ParallelState.single()
+            if tp_e == self.ps.tp:
+                self.engine_ps = self.ps                  # own_weights: the trainer's layout, a second copy of the shards
+            else:
+                self.engine_ps = ParallelState.build(tp=tp_e, kv_rep=max(1, tp_e // mcfg.num_kv_heads)) if tp_e > 1 or self.world > 1 \
+                    else ParallelState.single()
             self.engines_per_replica = self.ps.tp // tp_e
         return tp_e
 
