@@ -11,7 +11,9 @@ Pieces (same roles as the reference's):
                              generation between engine steps, swaps weights, bumps the version and resumes.
 
 Because trainer and engine share one flat parameter buffer when colocated, the weight "swap" is the
-optimizer step itself; the pause is what keeps an engine step from reading half-updated weights.
+optimizer step itself; the pause is what keeps an engine step from reading half-updated weights, and it then covers the
+whole scoring + update. With ``generator.inference_engine.own_weights=true`` the engine reads a copy of its own:
+generation overlaps scoring and update, and pauses only for the copy of the new weights.
 Samples generated under an older version are off-policy: their rollout logprobs are kept and the
 configured off-policy correction (TIS / masks) applies. The bitwise gate only covers version-matched samples.
 """
@@ -222,10 +224,18 @@ class FullyAsyncTrainer(RayPPOTrainer):
                 self.all_metrics = {}
                 batch = self.convert_to_training_input(go, uids)
                 staleness = [self.stale.version - g["version"] for g in groups]
-                with self._engine_lock:             # scoring + update exclude engine steps: one flat buffer, one writer
+                if getattr(self, "separate_engine", False):
+                    # the engine has weights of its own (generator.inference_engine.own_weights): generation goes on during
+                    # scoring and the update, and stops only while the new weights are copied in
                     self._run_training(batch, all(s == 0 for s in staleness))
-                    self._publish_weights()
-                    self.stale.bump_version()
+                    with self._engine_lock:
+                        self._publish_weights()
+                        self.stale.bump_version()
+                else:
+                    with self._engine_lock:         # scoring + update exclude engine steps: one flat buffer, one writer
+                        self._run_training(batch, all(s == 0 for s in staleness))
+                        self._publish_weights()
+                        self.stale.bump_version()
                 for g in groups:
                     self.source.mark_consumed(g["uid"])
                 self.all_metrics.update({"async/staleness_max": max(staleness), "async/staleness_mean": sum(staleness) / len(staleness),

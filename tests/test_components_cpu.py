@@ -156,6 +156,21 @@ def test_fully_async_trainer_runs_with_bounded_staleness(tmp_path):
     assert 0 <= tr.all_metrics["async/staleness_max"] <= 2
     assert tr.all_metrics["policy/grad_norm"] > 0
     assert len(tr.source.consumed) >= 4
+    # with weights of its own the engine keeps generating during the update: engine steps happen while the trainer trains
+    cfg = _rl_cfg(str(tmp_path / "own"), 3, "trainer.isoexec.strict=false", "generator.inference_engine.own_weights=true")
+    tr = FullyAsyncTrainer(cfg, AsyncConfig(max_staleness_steps=2, num_parallel_generation_workers=3, mini_batch_prompts=4), device="cpu")
+    during = []
+    real = tr._run_training
+
+    def spy(batch, fresh):
+        before = tr.engine.stats["steps"]
+        real(batch, fresh)
+        during.append(tr.engine.stats["steps"] - before)
+
+    tr._run_training = spy
+    tr.train()
+    assert tr.global_step == 3 and tr.separate_engine and sum(during) > 0
+    assert torch.equal(tr.engine.model.store.flat, tr.policy.model.store.flat)
 
 
 def test_entrypoint_runs_one_step(tmp_path, capsys):
