@@ -61,6 +61,27 @@ class PolicyConfig:
 
 
 @dataclass
+class CriticConfig:
+    """The value model (built when ``advantage_estimator=gae``). Empty ``model``: the policy's architecture."""
+    model: str = ""
+    model_overrides: dict = field(default_factory=dict)
+    hf_path: str = ""                   # initial weights in the Hugging Face layout (default: seeded random init)
+    optimizer_config: OptimizerConfig = field(default_factory=lambda: OptimizerConfig(lr=5e-6))
+
+
+@dataclass
+class FullyAsyncConfig:
+    """``train/fully_async_trainer.py`` (run through ``train/entrypoints/main_async.py --mode fully_async``, or implied by
+    ``enabled``)."""
+    enabled: bool = False
+    max_staleness_steps: int = 4
+    num_parallel_generation_workers: int = 768
+    simulate_training: bool = False
+    simulate_training_step_seconds: float = 0.0
+    simulate_weight_sync_seconds: float = 0.0
+
+
+@dataclass
 class SamplingConfig:
     max_generate_length: int = 1024
     repetition_penalty: float = 1.0
@@ -109,6 +130,9 @@ class GeneratorConfig:
     zero_reward_on_non_stop: bool = False
     apply_overlong_filtering: bool = False
     step_wise_trajectories: bool = False   # every model turn of a multi-turn trajectory is a training sample of its own
+    chat_template: dict = field(default_factory=dict)          # {"source": "name" | "file", "name_or_path": ...}: train/generator_utils.py
+    chat_template_kwargs: dict = field(default_factory=dict)   # passed to the tokenizer's apply_chat_template
+    merge_stepwise_output: bool = False    # step-wise rollouts are merged back into one row per trajectory before training
     multimodal: bool = False               # conversations may hold images: the vision-language generator (train/vlm_generator.py)
     append_eos_token_after_stop_str_in_multi_turn: bool = False
     rlm: bool = False                      # REPL environments whose blocks query the policy and spawn child trajectories (train/rlm_generator.py)
@@ -156,6 +180,8 @@ class TrainerConfig:
     placement: PlacementConfig = field(default_factory=PlacementConfig)
     policy: PolicyConfig = field(default_factory=PolicyConfig)
     ref: RefConfig = field(default_factory=RefConfig)
+    critic: CriticConfig = field(default_factory=CriticConfig)
+    fully_async: FullyAsyncConfig = field(default_factory=FullyAsyncConfig)
     algorithm: AlgorithmConfig = field(default_factory=AlgorithmConfig)
     isoexec: IsoExecConfig = field(default_factory=IsoExecConfig)
     strategy: str = "native"
@@ -165,6 +191,8 @@ class TrainerConfig:
     micro_train_batch_size_per_gpu: int = 1
     micro_forward_batch_size_per_gpu: int = 1
     max_tokens_per_microbatch: int = 8192
+    logprobs_chunk_size: int = 8192     # rows of the LM head scored at a time (bounds the [rows, vocabulary] logits in flight)
+    critic_mini_batch_size: int = 0     # 0 = policy_mini_batch_size
     update_epochs_per_batch: int = 1
     max_prompt_length: int = 512
     eval_batch_size: int = 1024
@@ -210,7 +238,7 @@ class SkyRLTrainConfig:
             if arg.startswith("+"):
                 raise ValueError("the '+key=value' syntax is not supported; every key already exists in the config tree")
             key, val = arg.split("=", 1)
-            set_by_path(cfg, key.strip(), val.strip())
+            _apply(cfg, LEGACY_KEYS.get(key.strip(), key.strip()), val.strip())
         return cfg
 
     @classmethod
@@ -234,12 +262,12 @@ class SkyRLTrainConfig:
             text_val = val if isinstance(val, str) else json.dumps(val)
             if text_val == "null":
                 text_val = "none"
-            set_by_path(cfg, key, text_val)
+            _apply(cfg, key, text_val)
         for arg in overrides or []:
             if "=" not in arg:
                 raise ValueError(f"override {arg!r} is not key=value")
             k, v = arg.split("=", 1)
-            set_by_path(cfg, LEGACY_KEYS.get(k.strip(), k.strip()), v.strip())
+            _apply(cfg, LEGACY_KEYS.get(k.strip(), k.strip()), v.strip())
         return cfg
 
     def to_dict(self) -> dict:
@@ -247,6 +275,157 @@ class SkyRLTrainConfig:
 
     def dumps(self) -> str:
         return json.dumps(self.to_dict(), indent=1, sort_keys=True, default=str)
+
+
+# ----------------------------------------------------------------------------- keys of the reference's config tree
+# A launch line or YAML file written for the reference names keys of its FSDP / Megatron / vLLM / Ray machinery and nests
+# some settings differently. ``translate_key`` maps those that have a counterpart here, accepts (and notes) those that
+# configure machinery this framework does not have, and refuses, with a message that says what is missing, those whose
+# value would change what is trained if it were dropped silently.
+RENAMED_KEYS = {
+    "trainer.max_training_steps": "trainer.num_steps",
+    "trainer.enable_ray_gpu_monitor": "trainer.gpu_monitor",
+    "trainer.policy.sequence_parallel_size": "trainer.policy.parallel.context_parallel_size",       # Ulysses
+    "trainer.policy.megatron_config.tensor_model_parallel_size": "trainer.policy.parallel.tensor_model_parallel_size",
+    "trainer.policy.megatron_config.pipeline_model_parallel_size": "trainer.policy.parallel.pipeline_model_parallel_size",
+    "trainer.policy.megatron_config.context_parallel_size": "trainer.policy.parallel.context_parallel_size",
+    "trainer.policy.megatron_config.expert_model_parallel_size": "trainer.policy.parallel.expert_model_parallel_size",
+    "trainer.ref.model.path": "trainer.ref.hf_path",
+    "trainer.critic.model.path": "trainer.critic.hf_path",
+    "trainer.algorithm.kl_ctrl.type": "trainer.algorithm.kl_ctrl_type",
+    "trainer.algorithm.kl_ctrl.kl_target": "trainer.algorithm.kl_target",
+    "trainer.algorithm.kl_ctrl.horizon": "trainer.algorithm.kl_horizon",
+    "trainer.algorithm.sapo.tau_pos": "trainer.algorithm.sapo_tau_pos",
+    "trainer.algorithm.sapo.tau_neg": "trainer.algorithm.sapo_tau_neg",
+    "trainer.algorithm.dynamic_sampling.type": "trainer.algorithm.dynamic_sampling_type",
+    "trainer.algorithm.dynamic_sampling.max_sample_batches": "trainer.algorithm.dynamic_sampling_max_sample_batches",
+    "trainer.algorithm.dynamic_sampling.min_replace_ratio": "trainer.algorithm.dynamic_sampling_min_replace_ratio",
+    "trainer.algorithm.clip_cov.clip_ratio": "trainer.algorithm.clip_cov_ratio",
+    "trainer.algorithm.clip_cov.clip_cov_lb": "trainer.algorithm.clip_cov_lb",
+    "trainer.algorithm.clip_cov.clip_cov_ub": "trainer.algorithm.clip_cov_ub",
+    "trainer.algorithm.kl_cov.kl_cov_frac": "trainer.algorithm.kl_cov_frac",
+    "trainer.algorithm.kl_cov.ppo_kl_coef": "trainer.algorithm.kl_cov_ppo_kl_coef",
+    "trainer.algorithm.cispo.cispo_eps_clip_low": "trainer.algorithm.cispo_eps_clip_low",
+    "trainer.algorithm.cispo.cispo_eps_clip_high": "trainer.algorithm.cispo_eps_clip_high",
+    "trainer.algorithm.dppo.dppo_type": "trainer.algorithm.dppo_type",
+    "trainer.algorithm.dppo.delta_low": "trainer.algorithm.dppo_delta_low",
+    "trainer.algorithm.dppo.delta_high": "trainer.algorithm.dppo_delta_high",
+    "trainer.algorithm.off_policy_correction.token_mask_is_threshold_low": "trainer.algorithm.off_policy_correction.outlier_token_is_threshold_low",
+    "trainer.algorithm.off_policy_correction.token_mask_is_threshold_high": "trainer.algorithm.off_policy_correction.outlier_token_is_threshold_high",
+    "trainer.algorithm.tis_imp_ratio_cap": "trainer.algorithm.off_policy_correction.token_tis_ratio_clip_high",
+    "generator.vision_language_generator": "generator.multimodal",
+    "generator.chat_template.source": "generator.chat_template.source",
+    "generator.chat_template.name_or_path": "generator.chat_template.name_or_path",
+    "environment.skyrl_gym.text2sql.db_path": "environment.env_kwargs.db_path",
+    "environment.skyrl_gym.llm_as_a_judge.model": "environment.env_kwargs.model",
+    "environment.skyrl_gym.llm_as_a_judge.base_url": "environment.env_kwargs.base_url",
+}
+# environment.skyrl_gym.<environment>.<key> -> environment.env_kwargs.<key>
+_ENV_PREFIX = "environment.skyrl_gym."
+# machinery that does not exist here: accepted, noted, without effect
+INERT_PREFIXES = (
+    "data.dataloader.", "trainer.placement.colocate_policy_ref", "trainer.placement.critic_num_", "trainer.placement.ref_num_",
+    "trainer.use_expandable_segments", "trainer.sequence_parallel_backend", "trainer.policy.fsdp_config.", "trainer.ref.fsdp_config.",
+    "trainer.critic.fsdp_config.", "trainer.policy.use_torch_compile", "trainer.policy.megatron_config.ddp_config.",
+    "trainer.policy.megatron_config.torch_profiler_config.", "trainer.policy.megatron_config.moe_token_dispatcher_type",
+    "trainer.policy.megatron_config.moe_grouped_gemm", "trainer.policy.megatron_config.moe_per_layer_logging",
+    "trainer.policy.megatron_config.moe_router_dtype", "trainer.policy.megatron_config.optimizer_config_kwargs",
+    "trainer.policy.megatron_config.transformer_config_kwargs", "trainer.policy.megatron_config.model_config_kwargs",
+    "trainer.policy.megatron_config.empty_cuda_cache", "trainer.policy.megatron_config.dist_ckpt_optim_fully_reshardable",
+    "trainer.policy.megatron_config.moe_router_load_balancing_type", "trainer.policy.megatron_config.moe_router_score_function",
+    "trainer.policy.megatron_config.moe_router_enable_expert_bias", "trainer.ref.megatron_config.", "trainer.ref.sequence_parallel_size",
+    "trainer.critic.sequence_parallel_size", "trainer.policy.model_config_kwargs", "trainer.ref.model_config_kwargs",
+    "trainer.critic.model_config_kwargs", "trainer.policy.inference_only_init", "trainer.policy.optimizer_config.offload_after_step",
+    "trainer.critic.optimizer_config.offload_after_step", "trainer.gradient_checkpointing_use_reentrant", "trainer.log_path", "trainer.tags",
+    "trainer.remove_microbatch_padding", "trainer.flash_attn", "trainer.disable_fast_tokenizer", "trainer.dump_eval_results",
+    "trainer.max_tokens_per_microbatch_forward", "trainer.fully_async.sample_full_batch", "trainer.fully_async.clear_kv_cache_on_weight_sync",
+    "trainer.algorithm.value_head_prefix", "trainer.algorithm.zero_variance_filter_tol", "trainer.policy.megatron_config.lora_config.",
+    "generator.inference_engine.model_dtype",
+    "generator.inference_engine.weight_transfer_threshold_cuda_ipc_GB", "generator.inference_engine.async_engine",
+    "generator.inference_engine.vllm_v1_disable_multiproc", "generator.inference_engine.enable_chunked_prefill",
+    "generator.inference_engine.fully_sharded_loras", "generator.inference_engine.enable_ray_prometheus_stats",
+    "generator.inference_engine.use_expandable_segments", "generator.inference_engine.distributed_executor_backend",
+    "generator.inference_engine.engine_init_kwargs", "generator.inference_engine.override_existing_update_group",
+    "generator.inference_engine.router_init_kwargs", "generator.inference_engine.served_model_name",
+    "generator.inference_engine.http_endpoint_host", "generator.inference_engine.http_endpoint_port",
+    "environment.skyrl_gym.max_env_workers",
+)
+# (key or prefix, values that are fine, what is missing): a value outside the fine ones would change what is trained
+UNSUPPORTED_IF_SET = (
+    ("trainer.policy.model.lora.rank", ("0",), "LoRA adapters are not wired into the RL trainer (train/lora.py serves the Tinker backend)"),
+    ("trainer.ref.model.lora.rank", ("0",), "LoRA adapters are not wired into the RL trainer"),
+    ("trainer.critic.model.lora.rank", ("0",), "LoRA adapters are not wired into the RL trainer"),
+    ("trainer.policy.megatron_config.expert_tensor_parallel_size", ("1", "none", "null"), "experts are sharded over expert parallelism only"),
+    ("trainer.policy.megatron_config.moe_aux_loss_coeff", ("0", "0.0"), "there is no auxiliary load-balancing loss"),
+    ("trainer.policy.megatron_config.moe_enable_routing_replay", ("false",), "router replay has no consumer here: both sides route with the same kernel on the same bits"),
+    ("trainer.policy.megatron_config.freeze_moe_router", ("false",), "the router cannot be frozen separately"),
+    ("trainer.policy.language_model_only", ("false",), "the vision tower is frozen already; there is no switch"),
+    ("trainer.ref.language_model_only", ("false",), "the vision tower is frozen already; there is no switch"),
+    ("generator.inference_engine.language_model_only", ("false",), "the vision tower is frozen already; there is no switch"),
+    ("trainer.algorithm.temperature", ("1", "1.0", "none", "null"), "logprobs are always those of the raw distribution"),
+    ("trainer.algorithm.advantage_batch_normalize", ("false",), "batch-level advantage normalisation is not implemented"),
+    ("trainer.algorithm.zero_variance_filter", ("false",), "use trainer.algorithm.dynamic_sampling_type=filter instead"),
+    ("trainer.update_ref_every_epoch", ("false",), "the reference model stays frozen"),
+    ("trainer.bf16", ("true",), "compute is bf16 (or the preset's dtype); fp32 training is chosen with trainer.policy.model_overrides.dtype"),
+    ("generator.inference_engine.pipeline_parallel_size", ("1",), "engines are not pipelined"),
+    ("generator.inference_engine.expert_parallel_size", ("1",), "engine expert parallelism follows the trainer's"),
+    ("generator.inference_engine.enable_return_routed_experts", ("false",), "router replay has no consumer here"),
+    ("generator.inference_engine.enable_http_endpoint", ("false",), "serve the engine with train/entrypoints/serve.py instead"),
+    ("generator.inference_engine.enable_pd", ("false",), "prefill / decode disaggregation is not implemented"),
+    ("generator.inference_engine.num_prefill", ("0",), "prefill / decode disaggregation is not implemented"),
+    ("generator.inference_engine.remote_urls", ("[]", "none", "null", ""), "the trainer drives in-process engines; remote servers are for serving"),
+    ("generator.inference_engine.external_server_urls", ("[]", "none", "null", ""), "the trainer drives in-process engines"),
+    ("generator.inference_engine.external_proxy_url", ("none", "null", ""), "the trainer drives in-process engines"),
+)
+COMPAT_NOTES: list[str] = []
+
+
+def translate_key(key: str, val: str):
+    """(key here, value) for a key of this tree or of the reference's; None when the key is accepted without effect."""
+    low = val.strip().strip("\"'").lower() if isinstance(val, str) else str(val).lower()
+    for k, fine, why in UNSUPPORTED_IF_SET:
+        if key == k or (k.endswith(".") and key.startswith(k)):
+            if fine is None or low not in fine:
+                raise ValueError(f"config key {key}={val} cannot be honoured: {why}")
+            return None
+    if key == "trainer.algorithm.use_tis":
+        return ("trainer.algorithm.off_policy_correction.tis_ratio_type", "token") if low == "true" else None
+    if key == "trainer.gradient_checkpointing":
+        return ("trainer.policy.keep_last_layers", "0" if low == "true" else "-1")       # off = keep what fits instead of recomputing
+    if key in ("trainer.rope_theta", "generator.rope_theta"):
+        return None if low in ("none", "null") else ("trainer.policy.model_overrides.rope_theta", val)
+    if key in ("trainer.rope_scaling", "generator.rope_scaling"):
+        if low in ("none", "null", "{}"):
+            return None
+        raise ValueError(f"config key {key}={val} cannot be honoured: rotary scaling (YaRN and the like) is not implemented")
+    if key == "trainer.policy.record_memory":
+        return ("trainer.record_memory", "memory_snapshots" if low == "true" else "")
+    if key in ("trainer.policy.optimizer_config.adam_betas", "trainer.critic.optimizer_config.adam_betas"):
+        if low in ("none", "null"):
+            return None
+        b = json.loads(val.replace("(", "[").replace(")", "]"))
+        return [(key.replace("adam_betas", "beta1"), str(b[0])), (key.replace("adam_betas", "beta2"), str(b[1]))]
+    if key.startswith("trainer.policy.model.lora.") or key.startswith("trainer.ref.model.lora.") or key.startswith("trainer.critic.model.lora."):
+        return None                                          # the adapter's other settings mean nothing at rank 0
+    if key in RENAMED_KEYS:
+        return RENAMED_KEYS[key], ("" if key.endswith("dynamic_sampling.type") and low in ("none", "null") else val)
+    if key.startswith(_ENV_PREFIX) and not any(key.startswith(p) for p in INERT_PREFIXES):
+        rest = key[len(_ENV_PREFIX):].split(".", 1)
+        if len(rest) == 2:
+            return "environment.env_kwargs." + rest[1], val
+        return "environment.env_kwargs." + rest[0], val      # a whole mapping for one environment
+    if any(key == p or key.startswith(p) for p in INERT_PREFIXES):
+        note = f"{key}: accepted for compatibility, without effect here"
+        if note not in COMPAT_NOTES:
+            COMPAT_NOTES.append(note)
+        return None
+    return key, val
+
+
+def _apply(cfg, key: str, val: str) -> None:
+    tr = translate_key(key, val)
+    for k, v in ([] if tr is None else tr if isinstance(tr, list) else [tr]):
+        set_by_path(cfg, k, v)
 
 
 # old key -> current key (files written for earlier layouts of the tree keep working)
@@ -266,7 +445,9 @@ def _flatten(tree: dict, prefix: str = ""):
     instance ``trainer.policy.model_overrides``) is a leaf."""
     for k, v in tree.items():
         key = f"{prefix}{k}"
-        if isinstance(v, dict) and not key.endswith(("model_overrides", "additional_kwargs", "env_extras")):
+        if isinstance(v, dict) and not key.endswith(("model_overrides", "additional_kwargs", "env_extras", "env_kwargs", "chat_template_kwargs",
+                                                     "engine_init_kwargs", "router_init_kwargs", "optimizer_config_kwargs",
+                                                     "transformer_config_kwargs", "model_config_kwargs", "rope_scaling")):
             yield from _flatten(v, key + ".")
         else:
             yield key, v
@@ -306,13 +487,20 @@ def set_by_path(cfg, key: str, val: str) -> None:
         obj = getattr(obj, p)
     leaf = parts[-1]
     if isinstance(obj, dict):
-        obj[leaf] = json.loads(val) if val[:1] in "[{0123456789-tfn\"" else val
+        try:
+            obj[leaf] = None if val.lower() in ("none", "null") else json.loads(val)
+        except ValueError:
+            obj[leaf] = val
         return
     fmap = {f.name: f for f in fields(obj)} if is_dataclass(obj) else {}
     if leaf not in fmap:
         raise KeyError(f"unknown config key {key!r}")
     hints = typing.get_type_hints(type(obj))
-    setattr(obj, leaf, _coerce(val, hints[leaf]))
+    tp = hints[leaf]
+    optional = type(None) in typing.get_args(tp)
+    if val.lower() in ("none", "null") and not optional and tp is not str:
+        return                                  # "no value" for a field that always has one: the default stays
+    setattr(obj, leaf, _coerce(val, tp))
 
 
 def validate_cfg(cfg: SkyRLTrainConfig, world_size: int = 1) -> None:

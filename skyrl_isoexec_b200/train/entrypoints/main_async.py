@@ -26,8 +26,15 @@ class AsyncPPOExp(BasePPOExp):
         if self.mode == "fully_async":
             from ..fully_async_trainer import AsyncConfig, FullyAsyncTrainer
 
+            fa = self.cfg.trainer.fully_async
             acfg = AsyncConfig(max_staleness_steps=self.max_staleness_steps, num_parallel_generation_workers=self.generation_workers,
-                               mini_batch_prompts=self.cfg.trainer.policy_mini_batch_size)
+                               mini_batch_prompts=self.cfg.trainer.policy_mini_batch_size, simulate_training=fa.simulate_training,
+                               simulate_training_step_seconds=fa.simulate_training_step_seconds,
+                               simulate_weight_sync_seconds=fa.simulate_weight_sync_seconds)
+            if fa.simulate_training:
+                from ..fully_async_trainer import FullyAsyncTrainerSim
+
+                return FullyAsyncTrainerSim(self.cfg, acfg, **kw)
             return FullyAsyncTrainer(self.cfg, acfg, **kw)
         from ..async_trainer import AsyncRayPPOTrainer
 
@@ -37,13 +44,17 @@ class AsyncPPOExp(BasePPOExp):
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--config", default="")
-    ap.add_argument("--mode", default="one_step_off", choices=["one_step_off", "fully_async"])
-    ap.add_argument("--max-staleness-steps", type=int, default=1)
-    ap.add_argument("--generation-workers", type=int, default=4)
+    ap.add_argument("--mode", default="", choices=["", "one_step_off", "fully_async"],
+                    help="default: fully_async when trainer.fully_async.enabled, else one_step_off")
+    ap.add_argument("--max-staleness-steps", type=int, default=None, help="default: trainer.fully_async.max_staleness_steps")
+    ap.add_argument("--generation-workers", type=int, default=None, help="default: trainer.fully_async.num_parallel_generation_workers")
     ap.add_argument("overrides", nargs="*")
     a = ap.parse_args(argv)
     cfg = SkyRLTrainConfig.from_file(a.config, a.overrides) if a.config else SkyRLTrainConfig.from_cli_overrides(a.overrides)
-    exp = AsyncPPOExp(cfg, a.mode, a.max_staleness_steps, a.generation_workers)
+    fa = cfg.trainer.fully_async
+    mode = a.mode or ("fully_async" if fa.enabled else "one_step_off")
+    exp = AsyncPPOExp(cfg, mode, a.max_staleness_steps if a.max_staleness_steps is not None else fa.max_staleness_steps,
+                      a.generation_workers if a.generation_workers is not None else fa.num_parallel_generation_workers)
     return exp.run()
 
 

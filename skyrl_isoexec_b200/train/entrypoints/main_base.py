@@ -78,6 +78,15 @@ class BasePPOExp:
         return None
 
     def get_trainer(self) -> RayPPOTrainer:
+        if self.cfg.trainer.fully_async.enabled and type(self) is BasePPOExp:
+            # trainer.fully_async.enabled=true on the plain entry point means the fully asynchronous trainer, as in the reference
+            from .main_async import AsyncPPOExp
+
+            fa = self.cfg.trainer.fully_async
+            exp = AsyncPPOExp.__new__(AsyncPPOExp)
+            exp.__dict__.update(self.__dict__)
+            exp.mode, exp.max_staleness_steps, exp.generation_workers = "fully_async", fa.max_staleness_steps, fa.num_parallel_generation_workers
+            return exp.get_trainer()
         return RayPPOTrainer(self.cfg, ps=self.ps, device=self.device, dataset=self.get_train_dataset(),
                              tokenizer=self.get_tokenizer(), tracker=self.get_tracker())
 

@@ -171,7 +171,8 @@ def merge_stepwise_output(generator_output: dict) -> dict:
     for t, rows in order.items():
         first, last = rows[0], rows[-1]
         p0 = list(generator_output["prompt_token_ids"][first])
-        resp, mask, lps = [], [], []
+        resp, mask, lps, rew = [], [], [], []
+        per_token = isinstance(generator_output["rewards"][first], (list, tuple))
         pos = len(p0)
         for i in rows:
             p, r = list(generator_output["prompt_token_ids"][i]), list(generator_output["response_ids"][i])
@@ -182,11 +183,13 @@ def merge_stepwise_output(generator_output: dict) -> dict:
             mask += [0] * len(gap) + list(generator_output["loss_masks"][i])
             if "rollout_logprobs" in out:
                 lps += [0.0] * len(gap) + list(generator_output["rollout_logprobs"][i])
+            if per_token:
+                rew += [0.0] * len(gap) + list(generator_output["rewards"][i])
             pos = len(p) + len(r)
         out["prompt_token_ids"].append(p0)
         out["response_ids"].append(resp)
         out["loss_masks"].append(mask)
-        out["rewards"].append(generator_output["rewards"][last])
+        out["rewards"].append(rew if per_token else generator_output["rewards"][last])
         if "stop_reasons" in out:
             out["stop_reasons"].append(generator_output["stop_reasons"][last])
         if "rollout_logprobs" in out:

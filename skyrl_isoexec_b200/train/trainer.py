@@ -273,7 +273,13 @@ class RayPPOTrainer:
             model = DecoderLM(mcfg, self.ps, self.device, seed=t.policy.seed, flat_alloc=flat_alloc)
         wcfg = WorkerConfig(max_tokens_per_microbatch=t.max_tokens_per_microbatch, optimizer=t.policy.optimizer_config,
                             keep_last_layers=t.policy.keep_last_layers, shard_optimizer=t.policy.shard_optimizer,
-                            want_entropy=t.algorithm.use_entropy_loss)
+                            want_entropy=t.algorithm.use_entropy_loss, logprob_chunk_rows=t.logprobs_chunk_size)
+        from .config import COMPAT_NOTES
+
+        if COMPAT_NOTES and self.rank == 0 and not getattr(RayPPOTrainer, "_compat_said", False):
+            RayPPOTrainer._compat_said = True
+            print(f"[config] {len(COMPAT_NOTES)} keys of the reference's config tree were accepted without effect here "
+                  f"(machinery this framework does not have), e.g. {COMPAT_NOTES[0].split(':')[0]}")
         algo = t.algorithm
         if not algo.max_seq_len:
             algo.max_seq_len = t.max_prompt_length + g.sampling_params.max_generate_length
@@ -287,10 +293,11 @@ class RayPPOTrainer:
         if algo.use_kl_loss or algo.use_kl_in_reward:
             from .ref_critic import RefWorker
 
-            if t.ref.model:           # a different frozen model (a teacher): same vocabulary, its own weights
+            if t.ref.model or t.ref.hf_path:   # a different frozen model (a teacher): same vocabulary, its own weights
                 from ..models import hf_export
 
-                rcfg = get_config(t.ref.model, **t.ref.model_overrides)
+                rcfg = get_config(t.ref.model, **t.ref.model_overrides) if t.ref.model else \
+                    (mcfg.with_(**t.ref.model_overrides) if t.ref.model_overrides else mcfg)
                 assert rcfg.vocab_size == mcfg.vocab_size, "the reference / teacher model must share the policy's vocabulary"
                 rmodel = DecoderLM(rcfg, self.ps, self.device, seed=t.ref.seed)
                 if t.ref.hf_path:
@@ -301,7 +308,16 @@ class RayPPOTrainer:
         if algo.advantage_estimator == "gae":
             from .ref_critic import CriticWorker
 
-            self.critic = CriticWorker(DecoderLM(mcfg, self.ps, self.device, seed=t.policy.seed + 1), wcfg, algo)
+            ccfg = get_config(t.critic.model, **t.critic.model_overrides) if t.critic.model else \
+                (mcfg.with_(**t.critic.model_overrides) if t.critic.model_overrides else mcfg)
+            cmodel = DecoderLM(ccfg, self.ps, self.device, seed=t.policy.seed + 1)
+            if t.critic.hf_path:
+                from ..models import hf_export
+
+                hf_export.load_hf(cmodel, t.critic.hf_path)
+            import dataclasses as _dc
+
+            self.critic = CriticWorker(cmodel, _dc.replace(wcfg, optimizer=t.critic.optimizer_config), algo)
         # the controller drives its workers through one dispatch object (verbs + residency of optimizer state)
         from .worker_dispatch import WorkerDispatch
 
@@ -324,6 +340,14 @@ class RayPPOTrainer:
             # colocated, same TP layout: the engine computes with the trainer's flat parameter buffer
             self.engine = LLMEngine(model, ecfg)
         self.infer = NativeInferenceEngine(self.engine, self.tokenizer)
+        if g.chat_template and self.tokenizer is not None:
+            from .generator_utils import get_custom_chat_template
+
+            tpl = get_custom_chat_template(g.chat_template)
+            if tpl is not None:
+                if not hasattr(self.tokenizer, "chat_template"):
+                    raise ValueError("generator.chat_template needs a tokenizer with a settable chat template (a Hugging Face tokenizer)")
+                self.tokenizer.chat_template = tpl
         if g.multimodal:
             from .vlm_generator import SkyRLVLMGymGenerator
 
@@ -492,6 +516,20 @@ class RayPPOTrainer:
         return out, new_uids
 
     def convert_to_training_input(self, go: GeneratorOutput, uids: list[str]) -> TrainingInputBatch:
+        cfg = getattr(self, "cfg", None)
+        if go.get("step_source") is not None and cfg is not None and cfg.generator.merge_stepwise_output and cfg.generator.step_wise_trajectories:
+            # step-wise rollouts, trained as whole trajectories: the turns of a trajectory are joined again (observation
+            # tokens get loss mask 0), one row and one uid per trajectory
+            from .generator_utils import merge_stepwise_output
+
+            go = dict(go)
+            if go.get("trajectory_ids") is None:
+                go["trajectory_ids"] = list(go["step_source"])
+            first = {}
+            for tid, src in zip(go["trajectory_ids"], go["step_source"]):
+                first.setdefault(tid, src)
+            go = merge_stepwise_output(go)
+            uids = [uids[first[tid]] for tid in go["trajectory_ids"]]
         seq, att, rmask = build_sequences(go["prompt_token_ids"], go["response_ids"])
         B, R = rmask.shape
         loss_mask = torch.zeros(B, R)
@@ -659,11 +697,12 @@ class RayPPOTrainer:
         n_updates = 0
         if getattr(self, "critic", None) is not None:
             closs = 0.0
-            for lo in range(0, B, mb_seqs):
-                cm = self.dispatch.forward_backward("critic", batch.slice(lo, min(B, lo + mb_seqs)))
+            cmb = (t.critic_mini_batch_size * n_samples) // max(1, self.ps.dp) if t.critic_mini_batch_size > 0 else mb_seqs
+            for lo in range(0, B, cmb):
+                cm = self.dispatch.forward_backward("critic", batch.slice(lo, min(B, lo + cmb)))
                 self.dispatch.optim_step("critic")
                 closs += cm["critic_loss"]
-            self.all_metrics["critic/critic_loss"] = closs / max(1, (B + mb_seqs - 1) // mb_seqs)
+            self.all_metrics["critic/critic_loss"] = closs / max(1, (B + cmb - 1) // cmb)
         for _epoch in range(t.update_epochs_per_batch):
             for lo in range(0, B, mb_seqs):
                 mb = batch.slice(lo, min(B, lo + mb_seqs))

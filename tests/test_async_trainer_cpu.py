@@ -76,3 +76,65 @@ def test_async_entry_point_runs_both_modes(tmp_path):
     assert isinstance(tr, AsyncRayPPOTrainer) and tr.global_step == 2
     tr = main_async.main(["--mode", "fully_async", "--max-staleness-steps", "2", "--generation-workers", "2"] + base)
     assert isinstance(tr, FullyAsyncTrainer) and tr.global_step == 2 and tr.acfg.max_staleness_steps == 2
+
+
+def test_reference_config_keys_are_translated_accepted_or_refused_with_a_reason():
+    from skyrl_isoexec_b200.train import config as C
+
+    cfg = C.SkyRLTrainConfig.from_cli_overrides([
+        "trainer.policy.model.path=tiny-qwen3", "trainer.policy.megatron_config.tensor_model_parallel_size=2", "trainer.algorithm.kl_ctrl.type=adaptive",
+        "trainer.algorithm.dynamic_sampling.type=filter", "trainer.algorithm.use_tis=true", "trainer.algorithm.tis_imp_ratio_cap=3.0",
+        "trainer.policy.optimizer_config.adam_betas=[0.9,0.95]", "trainer.gradient_checkpointing=false", "trainer.policy.fsdp_config.cpu_offload=true",
+        "environment.skyrl_gym.search.search_url=http://127.0.0.1:8000/retrieve", "environment.skyrl_gym.search.topk=5", "trainer.rope_theta=500000",
+        "generator.chat_template.source=name", "generator.chat_template.name_or_path=qwen3_with_thinking", "trainer.max_training_steps=7",
+        "trainer.critic.optimizer_config.lr=1e-5", "trainer.fully_async.max_staleness_steps=2", "trainer.policy.model.lora.rank=0",
+        "trainer.policy.model.lora.alpha=16", "generator.vision_language_generator=false", "data.train_data=none", "trainer.policy.sequence_parallel_size=1"])
+    t = cfg.trainer
+    assert (t.policy.model, t.policy.parallel.tensor_model_parallel_size, t.algorithm.kl_ctrl_type, t.algorithm.dynamic_sampling_type) == ("tiny-qwen3", 2, "adaptive", "filter")
+    assert t.algorithm.off_policy_correction.tis_ratio_type == "token" and t.algorithm.off_policy_correction.token_tis_ratio_clip_high == 3.0
+    assert t.policy.optimizer_config.beta2 == 0.95 and t.policy.keep_last_layers == -1 and t.num_steps == 7 and cfg.data.train_data == []
+    assert cfg.environment.env_kwargs == {"search_url": "http://127.0.0.1:8000/retrieve", "topk": 5} and t.policy.model_overrides == {"rope_theta": 500000}
+    assert cfg.generator.chat_template == {"source": "name", "name_or_path": "qwen3_with_thinking"}
+    assert t.critic.optimizer_config.lr == 1e-5 and t.fully_async.max_staleness_steps == 2
+    assert any("fsdp_config.cpu_offload" in n for n in C.COMPAT_NOTES)
+    for bad, why in (("trainer.policy.model.lora.rank=8", "LoRA"), ("trainer.algorithm.advantage_batch_normalize=true", "not implemented"),
+                     ("generator.inference_engine.enable_pd=true", "disaggregation"), ('trainer.rope_scaling={"type": "yarn"}', "rotary scaling")):
+        with pytest.raises(ValueError, match=why):
+            C.SkyRLTrainConfig.from_cli_overrides([bad])
+    with pytest.raises(KeyError):
+        C.SkyRLTrainConfig.from_cli_overrides(["trainer.nope=1"])
+    # the same through a YAML file in the reference's nesting
+    import yaml
+
+    tree = {"trainer": {"policy": {"model": {"path": "tiny-qwen3", "lora": {"rank": 0}}, "fsdp_config": {"cpu_offload": False, "mixed_precision": {"param_dtype": "bf16"}}},
+                        "algorithm": {"kl_ctrl": {"type": "fixed", "kl_target": 0.2}, "sapo": {"tau_pos": 1.5}}, "fully_async": {"enabled": False}},
+            "generator": {"inference_engine": {"vllm_v1_disable_multiproc": True, "engine_init_kwargs": {"a": 1}}},
+            "environment": {"skyrl_gym": {"max_env_workers": 8, "text2sql": {"db_path": "/data/sql"}}}}
+    import tempfile
+
+    with tempfile.NamedTemporaryFile("w", suffix=".yaml", delete=False) as f:
+        yaml.safe_dump(tree, f)
+    cfg = C.SkyRLTrainConfig.from_file(f.name)
+    assert cfg.trainer.algorithm.kl_target == 0.2 and cfg.trainer.algorithm.sapo_tau_pos == 1.5 and cfg.environment.env_kwargs == {"db_path": "/data/sql"}
+
+
+def test_critic_has_its_own_config_and_the_plain_entry_point_honours_fully_async(tmp_path):
+    from skyrl_isoexec_b200.train.entrypoints import main_base
+    from skyrl_isoexec_b200.train.fully_async_trainer import FullyAsyncTrainer
+    from skyrl_isoexec_b200.train.trainer import RayPPOTrainer
+
+    base = ["trainer.policy.model=tiny-qwen3", "trainer.train_batch_size=2", "trainer.policy_mini_batch_size=2", "generator.n_samples_per_prompt=2",
+            "generator.sampling_params.max_generate_length=4", "generator.sampling_params.ignore_eos=true", "data.synthetic_prompt_len=8",
+            "data.synthetic_prompts=8", "trainer.max_prompt_length=8", "generator.inference_engine.num_kv_pages=16", "trainer.num_steps=1",
+            "trainer.logger=jsonl", f"trainer.ckpt_path={tmp_path}", "trainer.resume_mode=none"]
+    cfg = SkyRLTrainConfig.from_cli_overrides(base + ["trainer.algorithm.advantage_estimator=gae", "trainer.critic.optimizer_config.lr=3e-4",
+                                                      'trainer.critic.model_overrides={"num_layers": 1}', "trainer.critic_mini_batch_size=1",
+                                                      "trainer.logprobs_chunk_size=16"])
+    tr = RayPPOTrainer(cfg, device="cpu")
+    tr.train()
+    assert tr.critic.cfg.optimizer.lr == 3e-4 and tr.policy.cfg.optimizer.lr != 3e-4 and tr.critic.model.cfg.num_layers == 1
+    assert tr.policy.cfg.logprob_chunk_rows == 16 and tr.critic.opt.step_count == 2            # two critic mini-batches of one prompt each
+    exp = main_base.BasePPOExp(SkyRLTrainConfig.from_cli_overrides(base + ["trainer.fully_async.enabled=true", "trainer.fully_async.max_staleness_steps=3",
+                                                                           "trainer.fully_async.num_parallel_generation_workers=2"]))
+    trainer = exp.get_trainer()
+    assert isinstance(trainer, FullyAsyncTrainer) and trainer.acfg.max_staleness_steps == 3 and trainer.acfg.num_parallel_generation_workers == 2

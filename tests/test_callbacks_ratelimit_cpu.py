@@ -359,3 +359,28 @@ def test_tracking_backends_against_fake_clients(tmp_path, monkeypatch, capsys):
     monkeypatch.setitem(sys.modules, "wandb", None)                          # "import wandb" now fails
     with pytest.raises(ImportError):
         Tracking("p", "r", "wandb")
+
+
+def test_step_wise_rollouts_can_be_merged_back_into_one_row_per_trajectory(tmp_path):
+    cfg = _cfg(str(tmp_path), 1, "generator.step_wise_trajectories=true", "generator.merge_stepwise_output=true", "generator.batched=false",
+               "generator.max_turns=3", "environment.env_class=even_tokens_turns", "generator.inference_engine.num_kv_pages=32",
+               "trainer.max_prompt_length=24")
+    tr = RayPPOTrainer(cfg, device="cpu")
+    tr.build_models()
+    tr.sync_weights()
+    rows = next(iter(tr.loader))
+    gi, uids = tr.prepare_generator_input(rows)
+    tr.engine.wake_up()
+    go = tr.generate(gi)
+    tr.engine.sleep()
+    assert len(go["response_ids"]) == 12
+    batch = tr.convert_to_training_input(go, uids)
+    assert batch.batch_size == 4 and batch.metadata["uids"] == [uids[0], uids[1], uids[2], uids[3]]
+    # a merged row is the first step's prompt followed by all three turns; every generated token keeps loss and logprob
+    first_prompt = go["prompt_token_ids"][0]
+    joined = go["response_ids"][0] + go["response_ids"][1] + go["response_ids"][2]
+    n = int(batch["response_mask"][0].sum())
+    assert n == len(joined) and int(batch["loss_mask"][0].sum()) == len(joined)
+    assert batch["sequences"][0][batch["attention_mask"][0].bool()].tolist() == first_prompt + joined
+    m = tr.train_step(next(iter(tr.loader)))
+    assert m["policy/rollout_train_logprob_bit_mismatches"] == 0
