@@ -193,6 +193,7 @@ class TrainerConfig:
     max_tokens_per_microbatch: int = 8192
     logprobs_chunk_size: int = 8192     # rows of the LM head scored at a time (bounds the [rows, vocabulary] logits in flight)
     critic_mini_batch_size: int = 0     # 0 = policy_mini_batch_size
+    update_ref_every_epoch: bool = False  # the reference model takes the policy's weights at the end of every epoch
     update_epochs_per_batch: int = 1
     max_prompt_length: int = 512
     eval_batch_size: int = 1024
@@ -339,7 +340,7 @@ INERT_PREFIXES = (
     "trainer.critic.optimizer_config.offload_after_step", "trainer.gradient_checkpointing_use_reentrant", "trainer.log_path", "trainer.tags",
     "trainer.remove_microbatch_padding", "trainer.flash_attn", "trainer.disable_fast_tokenizer", "trainer.dump_eval_results",
     "trainer.max_tokens_per_microbatch_forward", "trainer.fully_async.sample_full_batch", "trainer.fully_async.clear_kv_cache_on_weight_sync",
-    "trainer.algorithm.value_head_prefix", "trainer.algorithm.zero_variance_filter_tol", "trainer.policy.megatron_config.lora_config.",
+    "trainer.algorithm.value_head_prefix", "trainer.policy.megatron_config.lora_config.",
     "generator.inference_engine.model_dtype",
     "generator.inference_engine.weight_transfer_threshold_cuda_ipc_GB", "generator.inference_engine.async_engine",
     "generator.inference_engine.vllm_v1_disable_multiproc", "generator.inference_engine.enable_chunked_prefill",
@@ -363,9 +364,6 @@ UNSUPPORTED_IF_SET = (
     ("trainer.ref.language_model_only", ("false",), "the vision tower is frozen already; there is no switch"),
     ("generator.inference_engine.language_model_only", ("false",), "the vision tower is frozen already; there is no switch"),
     ("trainer.algorithm.temperature", ("1", "1.0", "none", "null"), "logprobs are always those of the raw distribution"),
-    ("trainer.algorithm.advantage_batch_normalize", ("false",), "batch-level advantage normalisation is not implemented"),
-    ("trainer.algorithm.zero_variance_filter", ("false",), "use trainer.algorithm.dynamic_sampling_type=filter instead"),
-    ("trainer.update_ref_every_epoch", ("false",), "the reference model stays frozen"),
     ("trainer.bf16", ("true",), "compute is bf16 (or the preset's dtype); fp32 training is chosen with trainer.policy.model_overrides.dtype"),
     ("generator.inference_engine.pipeline_parallel_size", ("1",), "engines are not pipelined"),
     ("generator.inference_engine.expert_parallel_size", ("1",), "engine expert parallelism follows the trainer's"),

@@ -663,8 +663,26 @@ class RayPPOTrainer:
         else:
             adv, ret = alg.compute_advantages_and_returns(batch["rewards"], batch["response_mask"], batch.metadata["uids"],
                                                           a.advantage_estimator, a, values=batch.get("values"))
-        batch["advantages"], batch["returns"] = adv, ret
         m = batch["response_mask"]
+        if a.zero_variance_filter and last is None:
+            # groups whose samples all scored the same teach nothing under a group baseline: their loss mask goes to zero
+            # (reference: R/train/trainer.py:1123-1138)
+            tot = batch["rewards"].sum(-1)
+            by_uid: dict = {}
+            for i, u in enumerate(batch.metadata["uids"]):
+                by_uid.setdefault(u, []).append(i)
+            dead = [i for idx in by_uid.values() if len(idx) > 1 and float(tot[idx].max() - tot[idx].min()) <= a.zero_variance_filter_tol for i in idx]
+            if dead and batch.get("loss_mask") is not None:
+                batch["loss_mask"][torch.tensor(dead)] = 0
+            self.all_metrics["reward/num_zero_variance_filtered"] = len({batch.metadata["uids"][i] for i in dead})
+        if a.advantage_batch_normalize:
+            # z-score over every response token of the global batch (reference: R/train/trainer.py:1659-1664)
+            mf = m.to(adv.dtype)
+            n = max(1.0, self._global_sum(float(mf.sum())))
+            mean = self._global_sum(float((adv * mf).sum())) / n
+            var = self._global_sum(float((((adv - mean) ** 2) * mf).sum())) / n
+            adv = (adv - mean) * (max(var, 1e-8) ** -0.5) * mf
+        batch["advantages"], batch["returns"] = adv, ret
         scores = batch["rewards"].sum(-1)
         if last is not None:
             scores = scores[torch.tensor(last, dtype=torch.bool)]
@@ -672,6 +690,15 @@ class RayPPOTrainer:
                                  "reward/avg_pass_rate": float((scores > 0).float().mean()),
                                  "policy/avg_advantage_abs": float((adv.abs() * m).sum() / m.sum().clamp(min=1))})
         return batch
+
+    def update_ref_with_policy(self) -> None:
+        """The reference model takes the policy's current weights (``trainer.update_ref_every_epoch``; reference:
+        R/train/trainer.py ``update_ref_with_policy``). Both must have the same architecture and layout."""
+        src, dst = self.policy.model.store.flat, self.ref.model.store.flat
+        if src.shape != dst.shape:
+            raise ValueError("update_ref_every_epoch needs a reference model of the policy's own architecture")
+        with torch.no_grad():
+            dst.copy_(src)
 
     def _global_sum(self, x: float) -> float:
         if self.ps.dp > 1:
@@ -977,6 +1004,8 @@ class RayPPOTrainer:
                         done = True
                         break
                 self._fire("on_epoch_end")
+                if t.update_ref_every_epoch and getattr(self, "ref", None) is not None:
+                    self.update_ref_with_policy()
                 if done:
                     break
             self._fire("on_train_end")

@@ -97,7 +97,7 @@ def test_reference_config_keys_are_translated_accepted_or_refused_with_a_reason(
     assert cfg.generator.chat_template == {"source": "name", "name_or_path": "qwen3_with_thinking"}
     assert t.critic.optimizer_config.lr == 1e-5 and t.fully_async.max_staleness_steps == 2
     assert any("fsdp_config.cpu_offload" in n for n in C.COMPAT_NOTES)
-    for bad, why in (("trainer.policy.model.lora.rank=8", "LoRA"), ("trainer.algorithm.advantage_batch_normalize=true", "not implemented"),
+    for bad, why in (("trainer.policy.model.lora.rank=8", "LoRA"), ("trainer.algorithm.temperature=0.7", "raw distribution"),
                      ("generator.inference_engine.enable_pd=true", "disaggregation"), ('trainer.rope_scaling={"type": "yarn"}', "rotary scaling")):
         with pytest.raises(ValueError, match=why):
             C.SkyRLTrainConfig.from_cli_overrides([bad])
@@ -138,3 +138,31 @@ def test_critic_has_its_own_config_and_the_plain_entry_point_honours_fully_async
                                                                            "trainer.fully_async.num_parallel_generation_workers=2"]))
     trainer = exp.get_trainer()
     assert isinstance(trainer, FullyAsyncTrainer) and trainer.acfg.max_staleness_steps == 3 and trainer.acfg.num_parallel_generation_workers == 2
+
+
+def test_batch_normalised_advantages_zero_variance_filter_and_reference_refresh(tmp_path):
+    from skyrl_isoexec_b200.train.batch import TrainingInputBatch
+    from skyrl_isoexec_b200.train.trainer import RayPPOTrainer
+
+    base = ["trainer.policy.model=tiny-qwen3", "trainer.train_batch_size=2", "trainer.policy_mini_batch_size=2", "generator.n_samples_per_prompt=2",
+            "generator.sampling_params.max_generate_length=4", "generator.sampling_params.ignore_eos=true", "data.synthetic_prompt_len=8",
+            "data.synthetic_prompts=4", "trainer.max_prompt_length=8", "generator.inference_engine.num_kv_pages=16", "trainer.epochs=2",
+            "trainer.logger=jsonl", f"trainer.ckpt_path={tmp_path}", "trainer.resume_mode=none", "trainer.policy.optimizer_config.lr=1e-3"]
+    cfg = SkyRLTrainConfig.from_cli_overrides(base + ["trainer.algorithm.advantage_batch_normalize=true", "trainer.algorithm.zero_variance_filter=true",
+                                                      "trainer.algorithm.use_kl_loss=true", "trainer.update_ref_every_epoch=true"])
+    tr = RayPPOTrainer(cfg, device="cpu")
+    tr.all_metrics = {}
+    rm = torch.ones(4, 3)
+    rewards = torch.zeros(4, 3)
+    rewards[0, 2], rewards[1, 2] = 1.0, 0.0            # prompt a: the two samples differ
+    rewards[2, 2], rewards[3, 2] = 1.0, 1.0            # prompt b: no variance
+    b = TrainingInputBatch({"rewards": rewards, "response_mask": rm, "loss_mask": rm.clone()})
+    b.metadata = {"uids": ["a", "a", "b", "b"]}
+    out = tr.compute_advantages_and_returns(b)
+    adv = out["advantages"]
+    assert abs(float(adv.mean())) < 1e-6 and abs(float(adv.pow(2).mean()) - 1.0) < 1e-4           # z-scored over all response tokens
+    assert out["loss_mask"][:2].sum() == 6 and out["loss_mask"][2:].sum() == 0 and tr.all_metrics["reward/num_zero_variance_filtered"] == 1
+    # two epochs of two steps: after each epoch the reference is the policy of that moment
+    tr.train()
+    assert tr.global_step == 4
+    assert torch.equal(tr.ref.model.store.flat, tr.policy.model.store.flat)
