@@ -46,9 +46,21 @@ class RefConfig:
 
 
 @dataclass
+class LoRASettings:
+    """Low-rank adapters on the policy (``train/lora.py``): the base weights are frozen, only the factors step; the adapter is
+    merged into the weight buffer, so the engine needs no adapter-aware kernel. ``rank = 0``: full fine-tuning."""
+    rank: int = 0
+    alpha: float = 16.0
+    lr: float = 0.0                     # 0 = the policy optimizer's learning rate
+    target_modules: str = "all-linear"  # "all-linear" or a comma-separated list of parameter-name suffixes (e.g. "attn.qkv.weight")
+    seed: int = 0
+
+
+@dataclass
 class PolicyConfig:
     model: str = "tiny-qwen3"           # preset name or path of a saved config
     model_overrides: dict = field(default_factory=dict)
+    lora: LoRASettings = field(default_factory=LoRASettings)
     tokenizer_path: str = ""            # "" = none (token-id prompts and environments); "byte" = the built-in byte tokenizer;
                                         # else a directory transformers.AutoTokenizer loads (text prompts, chat templates, stop strings)
     optimizer_config: OptimizerConfig = field(default_factory=OptimizerConfig)
@@ -353,7 +365,6 @@ INERT_PREFIXES = (
 )
 # (key or prefix, values that are fine, what is missing): a value outside the fine ones would change what is trained
 UNSUPPORTED_IF_SET = (
-    ("trainer.policy.model.lora.rank", ("0",), "LoRA adapters are not wired into the RL trainer (train/lora.py serves the Tinker backend)"),
     ("trainer.ref.model.lora.rank", ("0",), "LoRA adapters are not wired into the RL trainer"),
     ("trainer.critic.model.lora.rank", ("0",), "LoRA adapters are not wired into the RL trainer"),
     ("trainer.policy.megatron_config.expert_tensor_parallel_size", ("1", "none", "null"), "experts are sharded over expert parallelism only"),
@@ -403,7 +414,14 @@ def translate_key(key: str, val: str):
             return None
         b = json.loads(val.replace("(", "[").replace(")", "]"))
         return [(key.replace("adam_betas", "beta1"), str(b[0])), (key.replace("adam_betas", "beta2"), str(b[1]))]
-    if key.startswith("trainer.policy.model.lora.") or key.startswith("trainer.ref.model.lora.") or key.startswith("trainer.critic.model.lora."):
+    if key.startswith("trainer.policy.model.lora."):
+        leaf = key.rsplit(".", 1)[1]
+        if leaf in ("rank", "alpha"):
+            return f"trainer.policy.lora.{leaf}", val
+        if leaf == "target_modules":
+            return "trainer.policy.lora.target_modules", val
+        return None                                          # dropout, init method, adapter paths: no counterpart, no effect on the maths here
+    if key.startswith("trainer.ref.model.lora.") or key.startswith("trainer.critic.model.lora."):
         return None                                          # the adapter's other settings mean nothing at rank 0
     if key in RENAMED_KEYS:
         return RENAMED_KEYS[key], ("" if key.endswith("dynamic_sampling.type") and low in ("none", "null") else val)
@@ -515,6 +533,8 @@ def validate_cfg(cfg: SkyRLTrainConfig, world_size: int = 1) -> None:
                              "generator.step_wise_trajectories=false")
         if p.pipeline_model_parallel_size > 1 or p.context_parallel_size > 1:
             raise ValueError("generator.multimodal is not supported with pipeline or context parallelism")
+    if t.policy.lora.rank > 0 and mp * p.expert_model_parallel_size > 1:
+        raise ValueError("trainer.policy.lora needs tensor-, pipeline-, context- and expert-parallel degrees of 1 (data parallelism is fine)")
     if g.rlm and (g.multimodal or g.step_wise_trajectories):
         raise ValueError("generator.rlm cannot be combined with generator.multimodal or generator.step_wise_trajectories")
     if g.step_wise_trajectories:

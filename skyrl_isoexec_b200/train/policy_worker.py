@@ -817,6 +817,10 @@ class PolicyWorker:
 
     def optim_step(self) -> float:
         self.reduce_gradients()
+        if getattr(self, "lora", None) is not None:
+            # adapters: the dense gradients are projected onto the factors, the factors step, the merged weights are
+            # rebuilt; master weights and Adam moments of the base parameters never move
+            return self.lora.optim_step()
         norm = self.opt.step(self.ps)
         out = float(norm.item())
         self._calibrate_keep()

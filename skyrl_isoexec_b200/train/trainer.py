@@ -290,6 +290,17 @@ class RayPPOTrainer:
         else:
             self.policy = PolicyWorker(model, wcfg, algo)
         self.ref = self.critic = None
+        self.lora_store = None
+        if t.policy.lora.rank > 0:
+            from .lora import DEFAULT_TARGETS, AdapterStore, LoRAAdapter, LoRAConfig, LoRATrainer
+
+            ls = t.policy.lora
+            targets = DEFAULT_TARGETS if ls.target_modules in ("all-linear", "", "all") else tuple(x.strip() for x in ls.target_modules.split(",") if x.strip())
+            self.lora_store = AdapterStore(model)
+            self.lora_store.register("policy", LoRAAdapter.init(model, LoRAConfig(rank=ls.rank, alpha=ls.alpha, targets=targets,
+                                                                                  lr=ls.lr or t.policy.optimizer_config.lr, seed=ls.seed)))
+            self.lora_store.activate("policy")
+            self.policy.lora = LoRATrainer(self.policy, self.lora_store, "policy")
         if algo.use_kl_loss or algo.use_kl_in_reward:
             from .ref_critic import RefWorker
 
@@ -1071,6 +1082,11 @@ class RayPPOTrainer:
     def save_checkpoints(self) -> str:
         t = self.cfg.trainer
         extra = {"critic": self.critic.state_dict()} if getattr(self, "critic", None) is not None else None
+        if self.lora_store is not None:
+            # the weights in the checkpoint are the MERGED ones; the factors and the rows of the base under them go beside
+            ad = self.lora_store.adapters["policy"]
+            extra = dict(extra or {}, lora={"adapter": ad.state_dict(), "base": {k: v.cpu() for k, v in self.lora_store._base.items()},
+                                            "opt": self.policy.lora.opt.state_dict()})
         path = ckpt.save_checkpoint(t.ckpt_path, self.global_step, self.policy, self.loader.state_dict(),
                                     {"global_step": self.global_step, "epoch": self.epoch, "kl_ctrl": self.kl_ctrl.state_dict(),
                                      "config": self.cfg.to_dict()}, self.ps,
@@ -1096,6 +1112,16 @@ class RayPPOTrainer:
         self.epoch = self._start_epoch = int(trainer_state.get("epoch", data_state.get("epoch", 0)))
         if trainer_state.get("kl_ctrl") is not None:
             self.kl_ctrl.load_state_dict(trainer_state["kl_ctrl"])
+        if self.lora_store is not None:
+            sd = ckpt.load_extra_shard(path, "lora")
+            if sd is None:
+                raise FileNotFoundError(f"{path} holds no adapter state: it was not written by a run with trainer.policy.lora")
+            ad = self.lora_store.adapters["policy"]
+            for k in ad.A:
+                ad.A[k].copy_(sd["adapter"]["A"][k])
+                ad.B[k].copy_(sd["adapter"]["B"][k])
+            self.lora_store._base = {k: v.to(self.device) for k, v in sd["base"].items()}       # the loaded weights are merged already
+            self.policy.lora.opt.load_state_dict(sd["opt"])
         if getattr(self, "critic", None) is not None:
             sd = ckpt.load_extra_shard(path, "critic")
             if sd is None:

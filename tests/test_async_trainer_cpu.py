@@ -166,3 +166,40 @@ def test_batch_normalised_advantages_zero_variance_filter_and_reference_refresh(
     tr.train()
     assert tr.global_step == 4
     assert torch.equal(tr.ref.model.store.flat, tr.policy.model.store.flat)
+
+
+def test_rl_with_lora_adapters_moves_only_the_factors_and_resumes(tmp_path):
+    from skyrl_isoexec_b200.train.trainer import RayPPOTrainer
+
+    base = ["trainer.policy.model=tiny-qwen3", "trainer.train_batch_size=4", "trainer.policy_mini_batch_size=4", "generator.n_samples_per_prompt=4",
+            "generator.sampling_params.max_generate_length=12", "generator.sampling_params.ignore_eos=true", "data.synthetic_prompt_len=8",
+            "data.synthetic_prompts=16", "trainer.max_prompt_length=8", "generator.inference_engine.num_kv_pages=32",
+            "trainer.logger=jsonl", f"trainer.ckpt_path={tmp_path}", "trainer.ckpt_interval=2", "trainer.policy.optimizer_config.lr=1e-2",
+            "trainer.policy.model.lora.rank=4", "trainer.policy.model.lora.alpha=8", "trainer.policy.model.lora.dropout=0.0"]      # the reference's key names
+    cfg = SkyRLTrainConfig.from_cli_overrides(base + ["trainer.num_steps=2", "trainer.resume_mode=none"])
+    assert cfg.trainer.policy.lora.rank == 4 and cfg.trainer.policy.lora.alpha == 8
+    tr = RayPPOTrainer(cfg, device="cpu")
+    tr.build_models()
+    w0 = {n: t.clone() for n, t in tr.policy.model.named_weights()}
+    tr.train()
+    ad = tr.lora_store.adapters["policy"]
+    assert tr.all_metrics["policy/rollout_train_logprob_bit_mismatches"] == 0            # the engine reads the merged weights
+    assert any(float(b.abs().sum()) > 0 for b in ad.B.values())                           # the factors moved
+    assert tr.policy.opt.step_count == 0 and float(tr.policy.opt.exp_avg.abs().sum()) == 0      # the base optimizer never stepped
+    for n, t in tr.policy.model.named_weights():
+        if n in ad.A:
+            assert torch.allclose(t, w0[n] + ad.delta(n), atol=1e-6) and not torch.equal(t, w0[n])
+        else:
+            assert torch.equal(t, w0[n]), n                                               # embeddings, norms: untouched
+    # resume: merged weights, factors, base rows and the adapter's optimizer state come back
+    tr2 = RayPPOTrainer(SkyRLTrainConfig.from_cli_overrides(base + ["trainer.num_steps=3", "trainer.resume_mode=latest"]), device="cpu")
+    tr2.build_models()
+    assert tr2.load_checkpoints() == 2
+    ad2 = tr2.lora_store.adapters["policy"]
+    assert all(torch.equal(ad2.B[k], ad.B[k]) and torch.equal(ad2.A[k], ad.A[k]) for k in ad.A)
+    assert all(torch.equal(t, dict(tr.policy.model.named_weights())[n]) for n, t in tr2.policy.model.named_weights())
+    assert all(torch.equal(tr2.lora_store._base[k], w0[k]) for k in ad.A)
+    from skyrl_isoexec_b200.train.config import validate_cfg
+
+    with pytest.raises(ValueError, match="lora"):
+        validate_cfg(SkyRLTrainConfig.from_cli_overrides(base + ["trainer.policy.parallel.tensor_model_parallel_size=2"]), world_size=2)
