@@ -97,7 +97,8 @@ def test_reference_config_keys_are_translated_accepted_or_refused_with_a_reason(
     assert cfg.generator.chat_template == {"source": "name", "name_or_path": "qwen3_with_thinking"}
     assert t.critic.optimizer_config.lr == 1e-5 and t.fully_async.max_staleness_steps == 2
     assert any("fsdp_config.cpu_offload" in n for n in C.COMPAT_NOTES)
-    for bad, why in (("trainer.policy.model.lora.rank=8", "LoRA"), ("trainer.algorithm.temperature=0.7", "raw distribution"),
+    assert C.SkyRLTrainConfig.from_cli_overrides(["trainer.policy.model.lora.rank=8"]).trainer.policy.lora.rank == 8
+    for bad, why in (("trainer.ref.model.lora.rank=8", "LoRA"), ("trainer.algorithm.temperature=0.7", "raw distribution"),
                      ("generator.inference_engine.enable_pd=true", "disaggregation"), ('trainer.rope_scaling={"type": "yarn"}', "rotary scaling")):
         with pytest.raises(ValueError, match=why):
             C.SkyRLTrainConfig.from_cli_overrides([bad])
