@@ -126,6 +126,8 @@ class InferenceEngineConfig:
     share_recurrent_state: bool = False # GatedDeltaNet models: the samples also start from one snapshot of the recurrent state
     weight_sync_backend: str = "nccl"   # nccl | gloo | cuda_ipc | shared
     run_engines_locally: bool = True
+    remote_urls: list = field(default_factory=list)   # run_engines_locally=false: base URLs of running inference servers (train/remote_engines.py)
+    remote_weights_dir: str = ""        # a directory the trainer writes and every server reads (default: ckpt_path/remote_weights)
 
 
 @dataclass
@@ -382,7 +384,6 @@ UNSUPPORTED_IF_SET = (
     ("generator.inference_engine.enable_http_endpoint", ("false",), "serve the engine with train/entrypoints/serve.py instead"),
     ("generator.inference_engine.enable_pd", ("false",), "prefill / decode disaggregation is not implemented"),
     ("generator.inference_engine.num_prefill", ("0",), "prefill / decode disaggregation is not implemented"),
-    ("generator.inference_engine.remote_urls", ("[]", "none", "null", ""), "the trainer drives in-process engines; remote servers are for serving"),
     ("generator.inference_engine.external_server_urls", ("[]", "none", "null", ""), "the trainer drives in-process engines"),
     ("generator.inference_engine.external_proxy_url", ("none", "null", ""), "the trainer drives in-process engines"),
 )
@@ -589,7 +590,15 @@ def validate_cfg(cfg: SkyRLTrainConfig, world_size: int = 1) -> None:
     if ie.data_parallel_size != 1:
         raise ValueError("inference_engine.data_parallel_size: engines are replicated by num_engines, not by an inner data-parallel degree")
     if not ie.run_engines_locally:
-        raise ValueError("run_engines_locally=false: remote engines are reached through engine/server.py + RemoteInferenceClient, not through this key")
+        if not ie.remote_urls:
+            raise ValueError("run_engines_locally=false needs generator.inference_engine.remote_urls (servers started with train/entrypoints/serve.py)")
+        if t.isoexec.enabled:
+            raise ValueError("remote engines: the execution contract's hand-shake and ledger do not reach across HTTP; set "
+                             "trainer.isoexec.enabled=false (the bit-mismatch metrics are still reported)")
+        if p.pipeline_model_parallel_size > 1 or p.context_parallel_size > 1 or p.expert_model_parallel_size > 1 or g.multimodal:
+            raise ValueError("remote engines are supported with tensor and data parallelism, text-only")
+        if not (ie.remote_weights_dir or t.ckpt_path):
+            raise ValueError("remote engines need generator.inference_engine.remote_weights_dir (or trainer.ckpt_path) for the weight files")
     if not g.use_conversation_multi_turn:
         raise ValueError("use_conversation_multi_turn=false (token-append multi-turn without re-rendering) is not supported; "
                          "observations are always appended as rendered turns")

@@ -343,14 +343,24 @@ class RayPPOTrainer:
                             enable_prefix_caching=ie.enable_prefix_caching,
                             use_cuda_graph=not ie.enforce_eager, share_prompt_pages=ie.share_prompt_pages, share_recurrent_state=ie.share_recurrent_state,
                             max_model_len=min(mcfg.max_position, t.max_prompt_length + g.sampling_params.max_generate_length + 1))
-        if self.separate_engine:
+        self.remote_engines = not ie.run_engines_locally
+        if self.remote_engines:
+            # rollouts on servers this job does not own: generation over HTTP, weights through a shared directory
+            from .remote_engines import RemoteEngines
+
+            wdir = ie.remote_weights_dir or os.path.join(t.ckpt_path, "remote_weights")
+            self.engine = RemoteEngines(list(ie.remote_urls), wdir, rank=self.rank)
+            self.infer = self.engine.client
+            self.separate_engine = False
+        elif self.separate_engine:
             # engines of their own layout: a second set of (sharded) weights per GPU, filled by the resharding sync
             emodel = DecoderLM(mcfg, self.engine_ps, self.device, seed=t.policy.seed, init=False)
             self.engine = LLMEngine(emodel, ecfg)
         else:
             # colocated, same TP layout: the engine computes with the trainer's flat parameter buffer
             self.engine = LLMEngine(model, ecfg)
-        self.infer = NativeInferenceEngine(self.engine, self.tokenizer)
+        if not self.remote_engines:
+            self.infer = NativeInferenceEngine(self.engine, self.tokenizer)
         if g.chat_template and self.tokenizer is not None:
             from .generator_utils import get_custom_chat_template
 
@@ -825,6 +835,12 @@ class RayPPOTrainer:
         """Trainer -> rollout. Same process and layout: the flat buffer is shared, so the transfer is
         the handshake, the state invalidation and the verification that the alias still holds."""
         iso = self.cfg.trainer.isoexec.enabled
+        if getattr(self, "remote_engines", False):
+            # every rank takes part in the gather of the shards; one rank writes the file and tells the servers
+            self.all_metrics["sync/bytes"] = self.engine.push_weights(self.policy.model, write=self.rank == 0)
+            if dist.is_initialized():
+                dist.barrier()
+            return
         before = self.engine.invalidation_counts()
         if self.separate_engine:
             self.all_metrics["sync/bytes"] = self.resharder.sync()
