@@ -126,6 +126,10 @@ class InferenceEngineConfig:
     share_recurrent_state: bool = False # GatedDeltaNet models: the samples also start from one snapshot of the recurrent state
     weight_sync_backend: str = "nccl"   # nccl | gloo | cuda_ipc | shared
     run_engines_locally: bool = True
+    enable_http_endpoint: bool = False  # the in-process engine also answers HTTP (OpenAI-style and token-level routes of engine/server.py) and
+                                        # the trainer's own generator goes through that endpoint; external agent harnesses can use it too
+    http_endpoint_host: str = "127.0.0.1"
+    http_endpoint_port: int = 0         # 0 = any free port (trainer.http_endpoint_url tells which)
     remote_urls: list = field(default_factory=list)   # run_engines_locally=false: base URLs of running inference servers (train/remote_engines.py)
     remote_weights_dir: str = ""        # a directory the trainer writes and every server reads (default: ckpt_path/remote_weights)
 
@@ -362,7 +366,6 @@ INERT_PREFIXES = (
     "generator.inference_engine.use_expandable_segments", "generator.inference_engine.distributed_executor_backend",
     "generator.inference_engine.engine_init_kwargs", "generator.inference_engine.override_existing_update_group",
     "generator.inference_engine.router_init_kwargs", "generator.inference_engine.served_model_name",
-    "generator.inference_engine.http_endpoint_host", "generator.inference_engine.http_endpoint_port",
     "environment.skyrl_gym.max_env_workers",
 )
 # (key or prefix, values that are fine, what is missing): a value outside the fine ones would change what is trained
@@ -381,7 +384,6 @@ UNSUPPORTED_IF_SET = (
     ("generator.inference_engine.pipeline_parallel_size", ("1",), "engines are not pipelined"),
     ("generator.inference_engine.expert_parallel_size", ("1",), "engine expert parallelism follows the trainer's"),
     ("generator.inference_engine.enable_return_routed_experts", ("false",), "router replay has no consumer here"),
-    ("generator.inference_engine.enable_http_endpoint", ("false",), "serve the engine with train/entrypoints/serve.py instead"),
     ("generator.inference_engine.enable_pd", ("false",), "prefill / decode disaggregation is not implemented"),
     ("generator.inference_engine.num_prefill", ("0",), "prefill / decode disaggregation is not implemented"),
     ("generator.inference_engine.external_server_urls", ("[]", "none", "null", ""), "the trainer drives in-process engines"),

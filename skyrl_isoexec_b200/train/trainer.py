@@ -359,8 +359,20 @@ class RayPPOTrainer:
         else:
             # colocated, same TP layout: the engine computes with the trainer's flat parameter buffer
             self.engine = LLMEngine(model, ecfg)
+        self.http_server, self.http_endpoint_url = None, ""
         if not self.remote_engines:
             self.infer = NativeInferenceEngine(self.engine, self.tokenizer)
+            if ie.enable_http_endpoint:
+                # the engine behind HTTP: a server thread steps it whenever requests are queued; the trainer's generator is
+                # one more client of that endpoint (reference: enable_http_endpoint of the inference engine client)
+                from ..engine.server import InferenceServer, RemoteInferenceClient
+
+                if self.engines_per_replica > 1 or self.engine_ps.tp > 1:
+                    raise ValueError("enable_http_endpoint serves a single-rank engine (tensor_parallel_size = 1)")
+                self.http_server = InferenceServer(self.engine, self.tokenizer, ie.http_endpoint_host, ie.http_endpoint_port,
+                                                   model_name=mcfg.name).start()
+                self.http_endpoint_url = self.http_server.url
+                self.infer = RemoteInferenceClient([self.http_endpoint_url])
         if g.chat_template and self.tokenizer is not None:
             from .generator_utils import get_custom_chat_template
 

@@ -46,3 +46,36 @@ def test_trainer_rolls_out_on_remote_servers_and_pushes_its_weights(tmp_path):
     with pytest.raises(ValueError, match="isoexec.enabled=false"):
         validate_cfg(SkyRLTrainConfig.from_cli_overrides(["generator.inference_engine.run_engines_locally=false",
                                                           'generator.inference_engine.remote_urls=["http://127.0.0.1:1"]']))
+
+
+def test_http_endpoint_in_front_of_the_trainers_engine_keeps_the_contract(tmp_path):
+    import json
+    import urllib.request
+
+    from skyrl_isoexec_b200.train.callbacks import TrainingCallback
+    from skyrl_isoexec_b200.train.trainer import RayPPOTrainer
+
+    ov = ["trainer.policy.model=tiny-qwen3", "trainer.train_batch_size=2", "trainer.policy_mini_batch_size=2", "generator.n_samples_per_prompt=2",
+          "generator.sampling_params.max_generate_length=8", "generator.sampling_params.ignore_eos=true", "data.synthetic_prompt_len=8",
+          "data.synthetic_prompts=8", "trainer.max_prompt_length=8", "generator.inference_engine.num_kv_pages=16", "trainer.num_steps=2",
+          "trainer.logger=jsonl", f"trainer.ckpt_path={tmp_path}", "trainer.resume_mode=none", "trainer.ckpt_interval=0",
+          "generator.inference_engine.enable_http_endpoint=true"]
+    seen = {}
+
+    class External(TrainingCallback):                      # an outside client of the same endpoint, between two steps
+        def on_step_end(self, trainer, inp, control):
+            trainer.engine.wake_up()
+            req = urllib.request.Request(trainer.http_endpoint_url + "/generate", data=json.dumps(
+                {"prompt_token_ids": [[5, 6, 7]], "sampling_params": {"max_generate_length": 3, "ignore_eos": True}}).encode(),
+                headers={"Content-Type": "application/json"})
+            seen[trainer.global_step] = json.loads(urllib.request.urlopen(req, timeout=60).read())["response_ids"][0]
+            trainer.engine.sleep()
+
+    tr = RayPPOTrainer(SkyRLTrainConfig.from_cli_overrides(ov), device="cpu", callbacks=[External()])
+    try:
+        tr.train()
+        assert tr.http_endpoint_url.startswith("http://127.0.0.1:") and tr.global_step == 2
+        assert tr.all_metrics["policy/rollout_train_logprob_bit_mismatches"] == 0 and tr.adapter_engine.ledger.verdict()["ok"]
+        assert len(seen[1]) == 3 and len(seen[2]) == 3 and tr.http_server.requests_served >= 2 * 4 + 2
+    finally:
+        tr.http_server.shutdown()
