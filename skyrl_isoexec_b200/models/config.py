@@ -134,7 +134,7 @@ def _hybrid_pattern(n: int) -> tuple[str, ...]:
 
 
 PRESETS: dict[str, ModelConfig] = {
-    # BASELINE config 1: tiny Qwen3-style decoder for the CPU/gloo run
+    # tiny Qwen3-style decoder for the CPU / gloo runs
     "tiny-qwen3": ModelConfig(
         name="tiny-qwen3", architecture="Qwen3ForCausalLM", vocab_size=2048, hidden_size=256, num_layers=2,
         num_q_heads=4, num_kv_heads=2, head_dim=64, ffn_size=768, tie_embeddings=True, dtype="float32",
@@ -149,7 +149,7 @@ PRESETS: dict[str, ModelConfig] = {
         name="qwen3-30b-a3b", architecture="Qwen3MoeForCausalLM", vocab_size=151936, hidden_size=2048, num_layers=48,
         num_q_heads=32, num_kv_heads=4, head_dim=128, ffn_size=0, num_experts=128, top_k=8, moe_ffn_size=768,
         max_position=40960),
-    # BASELINE config 4: hybrid [GDN, GDN, GDN, gated attention] x 8
+    # hybrid [GDN, GDN, GDN, gated attention] x 8 (the reference's Qwen3.5-style benchmark model)
     "qwen3.5-hybrid": ModelConfig(
         name="qwen3.5-hybrid", architecture="Qwen3NextForCausalLM", vocab_size=151936, hidden_size=2560,
         num_layers=32, num_q_heads=16, num_kv_heads=4, head_dim=128, ffn_size=9216,

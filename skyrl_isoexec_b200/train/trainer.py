@@ -168,7 +168,7 @@ class RayPPOTrainer:
     # ------------------------------------------------------------------ build
     def _engine_layout(self, mcfg):
         """Decide how the rollout engines are laid out. Same tensor-parallel degree as the trainer: the engine computes
-        with the trainer's own flat buffer (one engine per trainer TP group). Another degree (BASELINE-style "trainer TP4 x
+        with the trainer's own flat buffer (one engine per trainer TP group). Another degree (for instance "trainer TP4 x
         DP2 feeding four TP2 engines"): every GPU also holds a shard of an engine of that degree, engines nest inside
         trainer TP groups, and each sync reshards the weights (sync/reshard.py). Collective: every rank calls it."""
         ie = self.cfg.generator.inference_engine
