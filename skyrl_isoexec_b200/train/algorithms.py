@@ -105,6 +105,7 @@ class AlgorithmConfig:
     dynamic_sampling_max_sample_batches: int = 30
     dynamic_sampling_min_replace_ratio: float = 0.3
     max_seq_len: int = 0
+    temperature: float | None = None           # None = the rollout's sampling temperature; logprobs are taken at this temperature
     advantage_batch_normalize: bool = False    # z-score the advantages over all response tokens of the (global) batch
     zero_variance_filter: bool = False         # prompts whose samples all got the same outcome reward carry no loss
     zero_variance_filter_tol: float = 1e-6

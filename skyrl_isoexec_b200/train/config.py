@@ -379,7 +379,6 @@ UNSUPPORTED_IF_SET = (
     ("trainer.policy.language_model_only", ("false",), "the vision tower is frozen already; there is no switch"),
     ("trainer.ref.language_model_only", ("false",), "the vision tower is frozen already; there is no switch"),
     ("generator.inference_engine.language_model_only", ("false",), "the vision tower is frozen already; there is no switch"),
-    ("trainer.algorithm.temperature", ("1", "1.0", "none", "null"), "logprobs are always those of the raw distribution"),
     ("trainer.bf16", ("true",), "compute is bf16 (or the preset's dtype); fp32 training is chosen with trainer.policy.model_overrides.dtype"),
     ("generator.inference_engine.pipeline_parallel_size", ("1",), "engines are not pipelined"),
     ("generator.inference_engine.expert_parallel_size", ("1",), "engine expert parallelism follows the trainer's"),
@@ -536,6 +535,9 @@ def validate_cfg(cfg: SkyRLTrainConfig, world_size: int = 1) -> None:
                              "generator.step_wise_trajectories=false")
         if p.pipeline_model_parallel_size > 1 or p.context_parallel_size > 1:
             raise ValueError("generator.multimodal is not supported with pipeline or context parallelism")
+    temp = t.algorithm.temperature if t.algorithm.temperature is not None else g.sampling_params.temperature
+    if temp not in (1.0, 0.0) and t.isoexec.enabled:
+        raise ValueError("a training temperature other than 1 needs trainer.isoexec.enabled=false (the contract pins the raw distribution)")
     if t.policy.lora.rank > 0 and mp * p.expert_model_parallel_size > 1:
         raise ValueError("trainer.policy.lora needs tensor-, pipeline-, context- and expert-parallel degrees of 1 (data parallelism is fine)")
     if g.rlm and (g.multimodal or g.step_wise_trajectories):

@@ -41,6 +41,8 @@ class OptimizerConfig:
 class WorkerConfig:
     max_tokens_per_microbatch: int = 8192
     logprob_chunk_rows: int = 8192
+    temperature: float = 1.0           # != 1: logprobs of the distribution the rollout sampled from, softmax(logits / T): the rows
+                                       # entering the LM head are divided by T (no contract run: that pins T = 1)
     checkpoint_layers: bool = True
     keep_last_layers: int = 0          # do not recompute the last n layers (trades activation memory for one forward of
                                        # them); -1 = as many as the free HBM allows (only with a sharded optimizer)
@@ -643,7 +645,10 @@ class PolicyWorker:
             rows, tg, oi = rows[mine] - lo, tg[mine], oi[mine]
         rows = rows.to(dev, non_blocking=True)
         tg = tg.to(dev, non_blocking=True)
-        lp, ent = lm_head_logprobs(self.model, hidden.index_select(0, rows), tg, self.cfg.logprob_chunk_rows, want_entropy)
+        h = hidden.index_select(0, rows)
+        if self.cfg.temperature != 1.0:
+            h = h * (1.0 / self.cfg.temperature)            # logits are linear in these rows: (h / T) W = (h W) / T
+        lp, ent = lm_head_logprobs(self.model, h, tg, self.cfg.logprob_chunk_rows, want_entropy)
         return lp, ent, oi.to(dev)
 
     # ---------------------------------------------------------------- verbs

@@ -273,7 +273,8 @@ class RayPPOTrainer:
             model = DecoderLM(mcfg, self.ps, self.device, seed=t.policy.seed, flat_alloc=flat_alloc)
         wcfg = WorkerConfig(max_tokens_per_microbatch=t.max_tokens_per_microbatch, optimizer=t.policy.optimizer_config,
                             keep_last_layers=t.policy.keep_last_layers, shard_optimizer=t.policy.shard_optimizer,
-                            want_entropy=t.algorithm.use_entropy_loss, logprob_chunk_rows=t.logprobs_chunk_size)
+                            want_entropy=t.algorithm.use_entropy_loss, logprob_chunk_rows=t.logprobs_chunk_size,
+                            temperature=(t.algorithm.temperature if t.algorithm.temperature is not None else g.sampling_params.temperature) or 1.0)
         from .config import COMPAT_NOTES
 
         if COMPAT_NOTES and self.rank == 0 and not getattr(RayPPOTrainer, "_compat_said", False):

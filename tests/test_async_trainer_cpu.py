@@ -98,7 +98,7 @@ def test_reference_config_keys_are_translated_accepted_or_refused_with_a_reason(
     assert t.critic.optimizer_config.lr == 1e-5 and t.fully_async.max_staleness_steps == 2
     assert any("fsdp_config.cpu_offload" in n for n in C.COMPAT_NOTES)
     assert C.SkyRLTrainConfig.from_cli_overrides(["trainer.policy.model.lora.rank=8"]).trainer.policy.lora.rank == 8
-    for bad, why in (("trainer.ref.model.lora.rank=8", "LoRA"), ("trainer.algorithm.temperature=0.7", "raw distribution"),
+    for bad, why in (("trainer.ref.model.lora.rank=8", "LoRA"), ("generator.inference_engine.num_prefill=2", "disaggregation"),
                      ("generator.inference_engine.enable_pd=true", "disaggregation"), ('trainer.rope_scaling={"type": "yarn"}', "rotary scaling")):
         with pytest.raises(ValueError, match=why):
             C.SkyRLTrainConfig.from_cli_overrides([bad])
@@ -204,3 +204,33 @@ def test_rl_with_lora_adapters_moves_only_the_factors_and_resumes(tmp_path):
 
     with pytest.raises(ValueError, match="lora"):
         validate_cfg(SkyRLTrainConfig.from_cli_overrides(base + ["trainer.policy.parallel.tensor_model_parallel_size=2"]), world_size=2)
+
+
+def test_training_temperature_scales_the_logits_the_logprobs_are_taken_from(tmp_path):
+    from skyrl_isoexec_b200.models.config import get_config
+    from skyrl_isoexec_b200.models.decoder import DecoderLM
+    from skyrl_isoexec_b200.train.batch import TrainingInputBatch, build_sequences
+    from skyrl_isoexec_b200.train.config import validate_cfg
+    from skyrl_isoexec_b200.train.policy_worker import PolicyWorker, WorkerConfig
+
+    m = DecoderLM(get_config("tiny-qwen3"), seed=0)
+    g = torch.Generator().manual_seed(0)
+    p, r = torch.randint(5, 500, (12,), generator=g).tolist(), torch.randint(5, 500, (6,), generator=g).tolist()
+    seq, att, rmask = build_sequences([p], [r])
+    b = TrainingInputBatch({"sequences": seq, "attention_mask": att, "response_mask": rmask})
+    lp1 = PolicyWorker(m, WorkerConfig()).forward(b)[0]
+    lp2 = PolicyWorker(m, WorkerConfig(temperature=2.0)).forward(b)[0]
+    # the same numbers from the definition: log softmax(logits / T) at the response tokens
+    from skyrl_isoexec_b200.models.decoder import ForwardCtx
+    from skyrl_isoexec_b200.ops import functional as F
+
+    ids = torch.tensor(p + r)
+    fc = ForwardCtx(positions=torch.arange(len(ids), dtype=torch.int32), meta=F.AttnMeta.packed([len(ids)], m.hq, m.hkv, "cpu"), site="trainer_score")
+    with torch.no_grad():
+        logits = m.logits(m(ids, fc)).float()
+    want = torch.log_softmax(logits / 2.0, -1)[torch.arange(len(p) - 1, len(ids) - 1), torch.tensor(r)]
+    assert torch.allclose(lp2, want, atol=1e-5) and not torch.allclose(lp1, lp2, atol=1e-3)
+    ov = ["trainer.policy.model=tiny-qwen3", "generator.sampling_params.temperature=0.7"]
+    with pytest.raises(ValueError, match="isoexec.enabled=false"):
+        validate_cfg(SkyRLTrainConfig.from_cli_overrides(ov + ["trainer.isoexec.enabled=true", "trainer.algorithm.temperature=0.7"]))
+    validate_cfg(SkyRLTrainConfig.from_cli_overrides(ov + ["trainer.isoexec.enabled=false"]))
