@@ -20,6 +20,7 @@ class ModelConfig:
     head_dim: int
     ffn_size: int
     rope_theta: float = 1e6
+    rope_scaling: tuple = ()           # a Hugging Face rope_scaling mapping as sorted (key, value) pairs: linear | llama3 | yarn
     rms_eps: float = 1e-6
     tie_embeddings: bool = False
     qk_norm: bool = True
@@ -64,6 +65,19 @@ class ModelConfig:
     tp_invariant: bool = False  # row-parallel K reductions use the leaf tree so any TP | pik_leaves gives equal bits
     sequence_parallel: bool = False  # trainer forward: residual stream, norms and adds on T / tp rows per rank (dense attention models)
 
+    def __post_init__(self):
+        rs = self.rope_scaling
+        if isinstance(rs, dict):
+            object.__setattr__(self, "rope_scaling", tuple(sorted(rs.items())))
+        elif rs is None:
+            object.__setattr__(self, "rope_scaling", ())
+        elif isinstance(rs, list):
+            object.__setattr__(self, "rope_scaling", tuple(tuple(x) for x in rs))
+
+    @property
+    def rope_scaling_dict(self) -> dict | None:
+        return dict(self.rope_scaling) if self.rope_scaling else None
+
     @property
     def torch_dtype(self) -> torch.dtype:
         return {"bfloat16": torch.bfloat16, "float32": torch.float32}[self.dtype]
@@ -101,6 +115,7 @@ class ModelConfig:
     def to_dict(self) -> dict:
         d = asdict(self)
         d["layer_types"] = list(self.layer_types)
+        d["rope_scaling"] = dict(self.rope_scaling)
         return d
 
     @staticmethod
@@ -238,7 +253,7 @@ def config_from_hf(path: str) -> ModelConfig:
     h, L, Hq = c["hidden_size"], c["num_hidden_layers"], c["num_attention_heads"]
     kw = dict(name=os.path.basename(os.path.dirname(os.path.abspath(f))) or arch, architecture=arch, vocab_size=c["vocab_size"],
               hidden_size=h, num_layers=L, num_q_heads=Hq, num_kv_heads=c.get("num_key_value_heads", Hq),
-              head_dim=c.get("head_dim") or h // Hq, ffn_size=c.get("intermediate_size", 0), rope_theta=float(c.get("rope_theta", 1e4)),
+              head_dim=c.get("head_dim") or h // Hq, ffn_size=c.get("intermediate_size", 0), rope_theta=float(c.get("rope_theta", 1e4)), rope_scaling=c.get("rope_scaling") or (),
               rms_eps=float(c.get("rms_norm_eps", 1e-6)), tie_embeddings=bool(c.get("tie_word_embeddings", False)),
               qk_norm=arch.startswith("Qwen3"), max_position=int(c.get("max_position_embeddings", 8192)),
               dtype={"float32": "float32"}.get(str(c.get("torch_dtype", "bfloat16")), "bfloat16"))

@@ -262,7 +262,7 @@ class DecoderLM(nn.Module):
             p = nn.Parameter(self.store.views[name], requires_grad=True)
             self._p[name] = p
             self.params[name.replace(".", "/")] = p
-        self.rope = F.RopeTable(cfg.rot_dim, cfg.max_position, cfg.rope_theta, self.device_)
+        self.rope = F.RopeTable(cfg.rot_dim, cfg.max_position, cfg.rope_theta, self.device_, scaling=cfg.rope_scaling_dict)
         self.scale = F.softmax_scale(cfg.head_dim)
         self.vision = None
         if getattr(cfg, "vision_depth", 0) > 0 and self.ps.is_first_pp:

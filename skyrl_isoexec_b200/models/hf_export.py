@@ -170,6 +170,8 @@ def hf_config(cfg: ModelConfig) -> dict:
                   "linear_conv_kernel_dim": cfg.gdn_conv_kernel, "partial_rotary_factor": cfg.partial_rotary_factor})
         if cfg.has_moe:
             d["architectures"] = ["Qwen3_5MoeForCausalLM"]
+    if cfg.rope_scaling:
+        d["rope_scaling"] = dict(cfg.rope_scaling)
     return d
 
 

@@ -227,17 +227,76 @@ def rmsnorm(x, w, eps=1e-6, zero_centered=False, residual=None):
 
 
 # --------------------------------------------------------------------------- RoPE table
+def scaled_inv_freq(rot_dim: int, theta: float, scaling: dict | None, max_pos: int):
+    """(inverse frequencies fp64 [rot_dim / 2], factor on cos and sin) under a Hugging Face style ``rope_scaling`` mapping:
+
+    * ``linear``   every frequency divided by ``factor`` (positions are compressed);
+    * ``llama3``   wavelengths beyond ``original_max_position_embeddings / low_freq_factor`` are divided by ``factor``, those
+                   below ``.. / high_freq_factor`` are kept, the band between is blended linearly in the wavelength's inverse;
+    * ``yarn``     per dimension a blend of the original frequency (dimensions that turn more than ``beta_fast`` times over
+                   the original context) and the interpolated one (fewer than ``beta_slow`` turns), linear ramp between;
+                   cos and sin are multiplied by ``attention_factor`` (default ``0.1 ln(factor) + 1``, or the
+                   ``mscale`` / ``mscale_all_dim`` ratio of the DeepSeek configs)."""
+    import math
+
+    inv = 1.0 / (theta ** (torch.arange(0, rot_dim, 2, dtype=torch.float64) / rot_dim))
+    if not scaling:
+        return inv, 1.0
+    kind = scaling.get("rope_type", scaling.get("type", "default"))
+    if kind in ("default", None):
+        return inv, 1.0
+    factor = float(scaling.get("factor", 1.0))
+    if kind == "linear":
+        return inv / factor, 1.0
+    orig = float(scaling.get("original_max_position_embeddings") or max_pos)
+    if kind == "llama3":
+        lo, hi = float(scaling.get("low_freq_factor", 1.0)), float(scaling.get("high_freq_factor", 4.0))
+        wavelen = 2 * math.pi / inv
+        smooth = ((orig / wavelen) - lo) / (hi - lo)
+        blended = (1 - smooth) * inv / factor + smooth * inv
+        out = torch.where(wavelen > orig / lo, inv / factor, torch.where(wavelen < orig / hi, inv, blended))
+        return out, 1.0
+    if kind == "yarn":
+        beta_fast, beta_slow = float(scaling.get("beta_fast") or 32.0), float(scaling.get("beta_slow") or 1.0)
+
+        def dim_of(turns):                     # the (fractional) dimension pair that makes ``turns`` rotations over ``orig`` positions
+            return rot_dim * math.log(orig / (turns * 2 * math.pi)) / (2 * math.log(theta))
+
+        low, high = dim_of(beta_fast), dim_of(beta_slow)
+        if scaling.get("truncate", True):
+            low, high = math.floor(low), math.ceil(high)
+        low, high = max(low, 0), min(high, rot_dim - 1)
+        if low == high:
+            high += 0.001
+        ramp = ((torch.arange(rot_dim // 2, dtype=torch.float64) - low) / (high - low)).clamp(0, 1)
+        keep = 1 - ramp                        # 1 where the original frequency stays
+        out = (inv / factor) * (1 - keep) + inv * keep
+        att = scaling.get("attention_factor")
+        if att is None:
+            def mscale(f, m=1.0):
+                return 1.0 if f <= 1 else 0.1 * m * math.log(f) + 1.0
+
+            if scaling.get("mscale") and scaling.get("mscale_all_dim"):
+                att = mscale(factor, float(scaling["mscale"])) / mscale(factor, float(scaling["mscale_all_dim"]))
+            else:
+                att = mscale(factor)
+        return out, float(att)
+    raise ValueError(f"rope_scaling type {kind!r} is not implemented (linear | llama3 | yarn)")
+
+
 class RopeTable:
     """cos/sin of ``pos * theta^(-2i/rot_dim)`` as fp32 ``[max_pos, rot_dim/2]``, computed once in
-    fp64 on the host so trainer and engine hold byte-identical tables."""
+    fp64 on the host so trainer and engine hold byte-identical tables. ``scaling``: a ``rope_scaling`` mapping
+    (``scaled_inv_freq``); context extension changes only this table, the kernels read it as before."""
 
-    def __init__(self, rot_dim: int, max_pos: int, theta: float, device):
-        inv = 1.0 / (theta ** (torch.arange(0, rot_dim, 2, dtype=torch.float64) / rot_dim))
+    def __init__(self, rot_dim: int, max_pos: int, theta: float, device, scaling: dict | None = None):
+        inv, att = scaled_inv_freq(rot_dim, theta, scaling, max_pos)
         ang = torch.arange(max_pos, dtype=torch.float64)[:, None] * inv[None, :]
-        self.cos = ang.cos().float().to(device).contiguous()
-        self.sin = ang.sin().float().to(device).contiguous()
+        self.cos = (ang.cos() * att).float().to(device).contiguous()
+        self.sin = (ang.sin() * att).float().to(device).contiguous()
         self.rot_dim = rot_dim
         self.max_pos = max_pos
+        self.attention_factor = att
 
 
 # --------------------------------------------------------------------------- QK-norm + RoPE + KV write

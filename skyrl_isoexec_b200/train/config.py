@@ -406,9 +406,7 @@ def translate_key(key: str, val: str):
     if key in ("trainer.rope_theta", "generator.rope_theta"):
         return None if low in ("none", "null") else ("trainer.policy.model_overrides.rope_theta", val)
     if key in ("trainer.rope_scaling", "generator.rope_scaling"):
-        if low in ("none", "null", "{}"):
-            return None
-        raise ValueError(f"config key {key}={val} cannot be honoured: rotary scaling (YaRN and the like) is not implemented")
+        return None if low in ("none", "null", "{}") else ("trainer.policy.model_overrides.rope_scaling", val)
     if key == "trainer.policy.record_memory":
         return ("trainer.record_memory", "memory_snapshots" if low == "true" else "")
     if key in ("trainer.policy.optimizer_config.adam_betas", "trainer.critic.optimizer_config.adam_betas"):

@@ -1177,3 +1177,52 @@ def test_prompt_logprobs_are_the_scoring_forwards_bits_across_prefill_chunks():
         lp = w.forward(TrainingInputBatch({"sequences": seq, "attention_mask": att, "response_mask": rmask}))[0]
         got = torch.tensor(o.prompt_logprobs[1:])
         assert torch.equal(got.view(torch.int32), lp.view(torch.int32))
+
+
+def test_rope_scaling_tables_match_the_transformers_formulas_and_extend_the_context():
+    from transformers import LlamaConfig
+    from transformers.modeling_rope_utils import ROPE_INIT_FUNCTIONS
+
+    from skyrl_isoexec_b200.models.config import ModelConfig, get_config
+    from skyrl_isoexec_b200.models.decoder import DecoderLM
+    from skyrl_isoexec_b200.ops.functional import RopeTable, scaled_inv_freq
+
+    D, theta, maxp = 64, 10000.0, 4096
+    cases = [{"rope_type": "linear", "factor": 4.0},
+             {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0, "original_max_position_embeddings": 1024},
+             {"rope_type": "yarn", "factor": 4.0, "original_max_position_embeddings": 1024},
+             {"rope_type": "yarn", "factor": 16.0, "original_max_position_embeddings": 1024, "beta_fast": 32, "beta_slow": 1, "mscale": 1.0, "mscale_all_dim": 0.5}]
+    for sc in cases:
+        hf = LlamaConfig(hidden_size=D * 4, num_attention_heads=4, head_dim=D, max_position_embeddings=maxp, rope_parameters=dict(sc, rope_theta=theta))
+        want_inv, want_att = ROPE_INIT_FUNCTIONS[sc["rope_type"]](hf, "cpu")
+        inv, att = scaled_inv_freq(D, theta, sc, maxp)
+        assert torch.allclose(inv.float(), want_inv.float(), rtol=1e-5, atol=1e-9), sc
+        assert abs(att - float(want_att)) < 1e-6, sc
+    plain, lin = RopeTable(D, 64, theta, "cpu"), RopeTable(D, 64, theta, "cpu", scaling={"type": "linear", "factor": 2.0})
+    assert torch.allclose(lin.cos[8], plain.cos[4], atol=1e-6) and plain.attention_factor == 1.0       # position 8 at half speed is position 4
+    yarn = RopeTable(D, 64, theta, "cpu", scaling=cases[2])
+    assert abs(float(yarn.cos[0, 0]) - yarn.attention_factor) < 1e-6 and yarn.attention_factor > 1.0  # cos(0) carries the attention factor
+    with pytest.raises(ValueError, match="not implemented"):
+        RopeTable(D, 64, theta, "cpu", scaling={"type": "dynamic", "factor": 2.0})
+    # through the model config: hashable, exported, and a rollout still scores to the trainer's bits
+    cfg = get_config("tiny-qwen3", rope_scaling=cases[2], max_position=1024)
+    assert isinstance(cfg.rope_scaling, tuple) and hash(cfg) and ModelConfig.from_dict(cfg.to_dict()) == cfg
+    from skyrl_isoexec_b200.models.hf_export import hf_config
+
+    assert hf_config(cfg)["rope_scaling"]["rope_type"] == "yarn"
+    from skyrl_isoexec_b200.engine.llm_engine import EngineConfig, LLMEngine
+    from skyrl_isoexec_b200.engine.sampler import SamplingParams
+    from skyrl_isoexec_b200.train.batch import TrainingInputBatch, build_sequences
+    from skyrl_isoexec_b200.train.policy_worker import PolicyWorker, WorkerConfig
+
+    m = DecoderLM(cfg, seed=0)
+    assert not torch.equal(m.rope.cos, DecoderLM(get_config("tiny-qwen3", max_position=1024), seed=0).rope.cos)
+    p = torch.randint(5, 500, (20,), generator=torch.Generator().manual_seed(0)).tolist()
+    o = LLMEngine(m, EngineConfig(num_kv_pages=8, seed=1)).generate([p], SamplingParams(max_generate_length=6, ignore_eos=True))[0]
+    seq, att, rmask = build_sequences([p], [o.response_ids])
+    lp = PolicyWorker(m, WorkerConfig()).forward(TrainingInputBatch({"sequences": seq, "attention_mask": att, "response_mask": rmask}))[0]
+    assert torch.equal(lp.view(torch.int32), torch.tensor(o.response_logprobs).view(torch.int32))
+    from skyrl_isoexec_b200.train.config import SkyRLTrainConfig
+
+    c = SkyRLTrainConfig.from_cli_overrides(['trainer.rope_scaling={"rope_type": "yarn", "factor": 4.0}'])
+    assert c.trainer.policy.model_overrides == {"rope_scaling": {"rope_type": "yarn", "factor": 4.0}}
