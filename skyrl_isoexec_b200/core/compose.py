@@ -73,6 +73,7 @@ class ModelProfile:
     activation_dtype: str = "bf16"
     rms_eps: float = 1e-6
     rope_theta: float = 1e6
+    rope_scaling: str = ""           # canonical JSON of the rope_scaling mapping ("" = none): it changes the cos / sin table
     rot_dim: int = 128
     logprob_leaves: int = 8
     pik_leaves: int = 8
@@ -123,7 +124,8 @@ def profile_from_model_config(cfg: ModelConfig, trainer_tp: int = 1, engine_tp: 
         family=cfg.name, architectures=(cfg.architecture,), profile_ref=f"skyrl_isoexec_b200/models/config.py::{cfg.name}",
         has_gdn=cfg.has_gdn, has_moe=cfg.has_moe, has_qk_norm=cfg.qk_norm, attn_output_gate=cfg.attn_output_gate,
         zero_centered_norms=cfg.zero_centered_norm, activation_dtype="bf16" if cfg.dtype == "bfloat16" else "fp32",
-        rms_eps=cfg.rms_eps, rope_theta=cfg.rope_theta, rot_dim=cfg.rot_dim, logprob_leaves=cfg.logprob_leaves,
+        rms_eps=cfg.rms_eps, rope_theta=cfg.rope_theta,
+        rope_scaling=__import__("json").dumps(dict(cfg.rope_scaling), sort_keys=True) if getattr(cfg, "rope_scaling", ()) else "", rot_dim=cfg.rot_dim, logprob_leaves=cfg.logprob_leaves,
         pik_leaves=G, router_score=cfg.router, router_topk=cfg.top_k, router_norm_topk=cfg.norm_topk_prob,
         gdn_kernel="cpr" if getattr(cfg, "gdn_snapshot", False) else "recurrent", gdn_chunk_size=cfg.gdn_chunk, gdn_conv_width=cfg.gdn_conv_kernel, topology=tuple(topo), states=tuple(states),
         tolerances=tol)
@@ -155,7 +157,8 @@ def derive_selections(p: ModelProfile, arch: str) -> dict[tuple[str, str], Selec
     put("attention.varlen", SITES, Selection.of(x("tcgen05_unified", "cpu_blockwise"), num_splits=1, block_n=128,
                                                 window=(-1, 0), softmax_domain="log2", p_dtype=p.activation_dtype))
     put("rope.rope", SITES, Selection.of(x("fused_qknorm_rope_kvwrite", "cpu_fused_qknorm_rope"), rounds=3,
-                                         table="fp32_from_fp64", rot_dim=p.rot_dim, theta=p.rope_theta))
+                                         table="fp32_from_fp64", rot_dim=p.rot_dim, theta=p.rope_theta,
+                                         **({"scaling": p.rope_scaling} if p.rope_scaling else {})))
     norm_pins = dict(lanes=32, vec=8, eps=p.rms_eps, zero_centered=p.zero_centered_norms, rsqrt="div_sqrt_rn")
     put("norms.rms", SITES, Selection.of(x("fused_add_rmsnorm", "cpu_add_rmsnorm"), **norm_pins))
     put("activation.swiglu", SITES, Selection.of(x("fused_swiglu", "cpu_swiglu"), rounds=2))
