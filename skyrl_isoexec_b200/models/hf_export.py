@@ -180,6 +180,8 @@ def save_hf(model: DecoderLM, path: str, write: bool = True) -> None:
     from safetensors.torch import save_file
 
     sd = to_hf_state_dict(model)
+    if getattr(model, "vision", None) is not None:
+        sd.update({k: v.contiguous() for k, v in model.vision.state_dict().items()})     # the frozen tower, under its own ``visual.*`` names
     if not write:
         return
     from ..utils import io as uio
@@ -195,6 +197,8 @@ def load_hf(model: DecoderLM, path: str) -> int:
     from safetensors.torch import load_file
 
     sd = load_file(os.path.join(path, "model.safetensors"))
+    if getattr(model, "vision", None) is not None and any(k.startswith("visual.") for k in sd):
+        model.vision.load_state_dict({k: v for k, v in sd.items() if k.startswith("visual.")})
     cfg = model.cfg
     n = 0
     with torch.no_grad():

@@ -341,3 +341,14 @@ def test_tinker_backend_takes_image_chunks_for_sampling_and_training():
         be.handle({"type": "sample", "chunks": [dict(chunks[1], expected_tokens=7)], "num_samples": 1})
     with pytest.raises(ValueError, match="no vision tower"):
         SkyRLTrainBackend("tiny-qwen3", device="cpu").handle({"type": "sample", "chunks": chunks, "num_samples": 1})
+
+
+def test_hf_export_carries_the_vision_tower(tmp_path):
+    from skyrl_isoexec_b200.models import hf_export
+
+    a, b = DecoderLM(CFG, seed=0), DecoderLM(CFG, seed=7)
+    pv, grid = patchify(torch.rand(3, 32, 32, generator=torch.Generator().manual_seed(0)), CFG.vision_patch, CFG.vision_merge)
+    assert not torch.equal(a.vision.encode(pv, grid), b.vision.encode(pv, grid))
+    hf_export.save_hf(a, str(tmp_path / "m"))
+    hf_export.load_hf(b, str(tmp_path / "m"))
+    assert torch.equal(a.vision.encode(pv, grid), b.vision.encode(pv, grid)) and torch.equal(a.store.flat, b.store.flat)
