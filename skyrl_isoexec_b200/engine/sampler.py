@@ -91,12 +91,16 @@ class Sampler:
         from ..ops import _native
 
         n, V = logits.shape
-        key = tuple(p.temperature for p in params)
+        p0 = params[0]
+        # the usual batch shares one parameter object: one identity pass instead of reading every request's temperature
+        same = all(p is p0 for p in params)
+        key = ("same", p0.temperature, n) if same else tuple(p.temperature for p in params)
         inv = self._temp_cache.get(key)
         if inv is None:
             if len(self._temp_cache) > 64:
                 self._temp_cache.clear()
-            inv = torch.tensor([0.0 if t == 0.0 else 1.0 / t for t in key], dtype=torch.float32, device=logits.device)
+            temps = [p0.temperature] * n if same else [p.temperature for p in params]
+            inv = torch.tensor([0.0 if t == 0.0 else 1.0 / t for t in temps], dtype=torch.float32, device=logits.device)
             self._temp_cache[key] = inv
         L = _native.lib()
         m = L.ix_sampler_scratch_elems(n)
@@ -136,6 +140,11 @@ class Sampler:
         """logits [n, V] -> (token ids int64 [n], raw logprobs fp32 [n]). ``histories``: per row ``(prompt ids, generated
         ids)``, needed by requests whose parameters look at their own sequence (``needs_history``)."""
         n, V = logits.shape
+        p0 = params[0]
+        if all(p is p0 for p in params):                     # one shared parameter object: decide once, not per request
+            plain = p0.top_p >= 1.0 and p0.top_k <= 0 and p0.min_p <= 0.0 and not shapes_logits(p0)
+            if plain and logits.is_cuda and logits.dtype == torch.bfloat16 and logits.stride(1) == 1 and logits.stride(0) % 8 == 0:
+                return self._fused(logits, params)
         shaped = [shapes_logits(p) for p in params]
         if any(needs_history(p) for p in params) and histories is None:
             raise ValueError("penalties and min_tokens need the sequences' token histories")
