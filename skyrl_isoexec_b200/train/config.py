@@ -211,6 +211,7 @@ class TrainerConfig:
     max_tokens_per_microbatch: int = 8192
     logprobs_chunk_size: int = 8192     # rows of the LM head scored at a time (bounds the [rows, vocabulary] logits in flight)
     critic_mini_batch_size: int = 0     # 0 = policy_mini_batch_size
+    dump_eval_results: bool = False     # every evaluation also writes its samples to export_path (or ckpt_path)/dumped_evals/global_step_N.jsonl
     update_ref_every_epoch: bool = False  # the reference model takes the policy's weights at the end of every epoch
     update_epochs_per_batch: int = 1
     max_prompt_length: int = 512
@@ -356,7 +357,7 @@ INERT_PREFIXES = (
     "trainer.critic.sequence_parallel_size", "trainer.policy.model_config_kwargs", "trainer.ref.model_config_kwargs",
     "trainer.critic.model_config_kwargs", "trainer.policy.inference_only_init", "trainer.policy.optimizer_config.offload_after_step",
     "trainer.critic.optimizer_config.offload_after_step", "trainer.gradient_checkpointing_use_reentrant", "trainer.log_path", "trainer.tags",
-    "trainer.remove_microbatch_padding", "trainer.flash_attn", "trainer.disable_fast_tokenizer", "trainer.dump_eval_results",
+    "trainer.remove_microbatch_padding", "trainer.flash_attn", "trainer.disable_fast_tokenizer",
     "trainer.max_tokens_per_microbatch_forward", "trainer.fully_async.sample_full_batch", "trainer.fully_async.clear_kv_cache_on_weight_sync",
     "trainer.algorithm.value_head_prefix", "trainer.policy.megatron_config.lora_config.",
     "generator.inference_engine.model_dtype",

@@ -1075,7 +1075,12 @@ class RayPPOTrainer:
             self.engine.wake_up()
         n = max(1, g.eval_n_samples_per_prompt)
         self._fire("on_eval_start")
-        out = evaluate(self.generator, rows, params, n_samples=n, ks=tuple(sorted({1, n})))
+        t = self.cfg.trainer
+        dump = ""
+        if t.dump_eval_results and (t.export_path or t.ckpt_path) and self.rank == 0:
+            dump = (t.export_path or t.ckpt_path).rstrip("/") + f"/dumped_evals/global_step_{self.global_step}.jsonl"
+        out = evaluate(self.generator, rows, params, n_samples=n, ks=tuple(sorted({1, n})), dump_path=dump,
+                       decode=self.tokenizer.decode if self.tokenizer is not None else None)
         if was_asleep:
             self.engine.sleep()
         if self.tracker is not None:

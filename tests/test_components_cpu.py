@@ -101,8 +101,15 @@ def _rl_cfg(tmp, steps, *extra):
 
 
 def test_evaluate_reports_reward_and_pass_at_k(tmp_path):
-    tr = RayPPOTrainer(_rl_cfg(str(tmp_path), 1), device="cpu")
+    tr = RayPPOTrainer(_rl_cfg(str(tmp_path), 1, "trainer.dump_eval_results=true", "trainer.eval_batch_size=3"), device="cpu")
     tr.build_models()
+    tr.sync_weights()
+    ev = tr.eval()
+    import json as _json
+
+    lines = [_json.loads(x) for x in open(tmp_path / "dumped_evals" / "global_step_0.jsonl")]
+    assert len(lines) == 3 * max(1, tr.cfg.generator.eval_n_samples_per_prompt) and {"uid", "env_class", "prompt_ids", "response_ids", "reward", "stop_reason"} <= set(lines[0])
+    assert abs(sum(x["reward"] for x in lines) / len(lines) - ev["eval/avg_reward"]) < 1e-9
     tr.engine.wake_up()
     rows = [tr.dataset[i] for i in range(3)]
     out = evaluate(tr.generator, rows, {"max_generate_length": 8, "ignore_eos": True}, n_samples=4, ks=(1, 4))
