@@ -99,7 +99,7 @@ def test_reference_config_keys_are_translated_accepted_or_refused_with_a_reason(
     assert any("fsdp_config.cpu_offload" in n for n in C.COMPAT_NOTES)
     assert C.SkyRLTrainConfig.from_cli_overrides(["trainer.policy.model.lora.rank=8"]).trainer.policy.lora.rank == 8
     for bad, why in (("trainer.ref.model.lora.rank=8", "LoRA"), ("generator.inference_engine.num_prefill=2", "disaggregation"),
-                     ("generator.inference_engine.enable_pd=true", "disaggregation"), ('trainer.rope_scaling={"type": "yarn"}', "rotary scaling")):
+                     ("generator.inference_engine.enable_pd=true", "disaggregation"), ("trainer.policy.megatron_config.expert_tensor_parallel_size=2", "expert parallelism only")):
         with pytest.raises(ValueError, match=why):
             C.SkyRLTrainConfig.from_cli_overrides([bad])
     with pytest.raises(KeyError):
