@@ -79,6 +79,46 @@ def route(logits, k, bias=None, sigmoid_bias=False, norm_topk=True):
     return idx, w
 
 
+# ------------------------------------------------------------------------------------ auxiliary load-balancing loss
+# Switch-style balance term of a MoE layer, aux = E * sum_e f_e * P_e (f_e: share of the routed (token, slot) pairs that
+# went to expert e; P_e: mean router probability of e), as in the reference's Megatron path (``moe_aux_loss_coeff``). It is
+# not added to the policy loss: its gradient is INJECTED where the routing weights enter the block (``_AuxGrad``), which is
+# what survives activation recomputation (the recomputed layer rebuilds the injection). The trainer sets ``coeff`` and,
+# per micro-batch, ``scale`` (the micro-batch's share of the global loss normalisation); ``sum`` / ``layers`` feed a metric.
+AUX_LOSS = {"coeff": 0.0, "scale": 1.0, "sum": 0.0, "layers": 0}
+
+
+class _AuxGrad(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, w, aux, scale):
+        ctx.scale = scale
+        ctx.aux_shape = aux.shape
+        return w.view_as(w)
+
+    @staticmethod
+    def backward(ctx, g):
+        return g, torch.full(ctx.aux_shape, ctx.scale, dtype=g.dtype, device=g.device), None
+
+
+def _with_aux_loss(logits: torch.Tensor, idx: torch.Tensor, w: torch.Tensor, cfg) -> torch.Tensor:
+    if AUX_LOSS["coeff"] <= 0 or not (torch.is_grad_enabled() and logits.requires_grad and w.requires_grad) or logits.shape[0] == 0:
+        return w
+    T, E = logits.shape
+    if cfg.router == "sigmoid_bias":
+        s = torch.sigmoid(logits)
+        probs = s / s.sum(-1, keepdim=True).clamp_min(1e-20)
+    else:
+        probs = torch.softmax(logits, -1)
+    with torch.no_grad():
+        f = torch.zeros(E, dtype=torch.float32, device=logits.device)
+        f.index_add_(0, idx.reshape(-1).long(), torch.ones(idx.numel(), dtype=torch.float32, device=logits.device))
+        f /= float(idx.numel())
+    aux = E * (f * probs.mean(0)).sum()
+    AUX_LOSS["sum"] += float(aux.detach())
+    AUX_LOSS["layers"] += 1
+    return _AuxGrad.apply(w, aux, AUX_LOSS["coeff"] * AUX_LOSS["scale"])
+
+
 # ------------------------------------------------------------------------------------ dispatch / combine
 def build_dispatch(idx: torch.Tensor, num_experts: int):
     """Integer routing mechanics. idx int32 [T, k]. Returns
@@ -365,6 +405,7 @@ def moe_block(y: torch.Tensor, model, i: int) -> torch.Tensor:
     logits = F.linear(y, model.p(pfx + "router.weight"), out_f32=True).float()
     bias = model.p(pfx + "router.expert_bias").float() if cfg.router == "sigmoid_bias" else None
     idx, w = route(logits, k, bias, cfg.router == "sigmoid_bias", cfg.norm_topk_prob)
+    w = _with_aux_loss(logits, idx, w, cfg)
     gate_up, down = model.p(pfx + "experts.gate_up"), model.p(pfx + "experts.down")
     if ps.ep == 1 and _experts_fn_ok(y, gate_up, down):
         # single-rank experts on a GPU: routing tables, expert GEMMs and (with autograd) their VJPs are all kernels,

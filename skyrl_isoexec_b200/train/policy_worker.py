@@ -41,6 +41,7 @@ class OptimizerConfig:
 class WorkerConfig:
     max_tokens_per_microbatch: int = 8192
     logprob_chunk_rows: int = 8192
+    moe_aux_loss_coeff: float = 0.0    # > 0: every MoE layer's load-balancing term enters the gradient with this weight (ops/moe.py)
     temperature: float = 1.0           # != 1: logprobs of the distribution the rollout sampled from, softmax(logits / T): the rows
                                        # entering the LM head are divided by T (no contract run: that pins T = 1)
     checkpoint_layers: bool = True
@@ -695,6 +696,16 @@ class PolicyWorker:
             if mi == len(mbs) - 1 and self._overlap_ok():
                 self.opt.begin_overlap()          # gradients of this backward are final: reduce them bucket by bucket
             idx = torch.tensor(mb.seq_index)
+            if self.cfg.moe_aux_loss_coeff > 0 and self.model.cfg.has_moe:
+                from ..ops import moe as _moe
+
+                # the policy loss is a sum pre-divided by the global token count; the balance term of a micro-batch gets
+                # the share of that count its own loss tokens have, so that the total is a token-weighted mean over micro-batches
+                share = float(batch.metadata.get("aux_loss_scale", 0.0)) * float((batch["loss_mask"] if batch.get("loss_mask") is not None
+                                                                                    else batch["response_mask"])[idx].sum())
+                _moe.AUX_LOSS.update(coeff=self.cfg.moe_aux_loss_coeff, scale=share if share > 0 else 1.0 / max(1, len(mbs)))
+                if mi == 0:
+                    _moe.AUX_LOSS.update(sum=0.0, layers=0)
             hidden = self._run_model(mb, "trainer_fwd")
             lp_flat, ent_flat, oi = self._logprobs(mb, hidden, want_ent)
             nb = len(mb.seq_index)
@@ -763,6 +774,11 @@ class PolicyWorker:
         n = max(1.0, tot["tokens"])
         out = {"policy_loss": tot["loss"], "ppo_clip_ratio": tot["clip_ratio_num"] / n, "loss_tokens": tot["tokens"],
                "policy_entropy": tot["entropy_sum"] / n, "policy_kl": tot["kl_sum"] / n}
+        if self.cfg.moe_aux_loss_coeff > 0 and self.model.cfg.has_moe:
+            from ..ops import moe as _moe
+
+            out["moe_aux_loss"] = _moe.AUX_LOSS["sum"] / max(1, _moe.AUX_LOSS["layers"])      # mean balance term per layer and micro-batch
+            _moe.AUX_LOSS.update(coeff=0.0)                                                    # forwards outside the update carry none
         if check_bits:
             out["rollout_bits"] = bits
         if post["tokens"] > 0:

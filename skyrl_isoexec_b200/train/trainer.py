@@ -274,6 +274,7 @@ class RayPPOTrainer:
         wcfg = WorkerConfig(max_tokens_per_microbatch=t.max_tokens_per_microbatch, optimizer=t.policy.optimizer_config,
                             keep_last_layers=t.policy.keep_last_layers, shard_optimizer=t.policy.shard_optimizer,
                             want_entropy=t.algorithm.use_entropy_loss, logprob_chunk_rows=t.logprobs_chunk_size,
+                            moe_aux_loss_coeff=t.policy.moe_aux_loss_coeff,
                             temperature=(t.algorithm.temperature if t.algorithm.temperature is not None else g.sampling_params.temperature) or 1.0)
         from .config import COMPAT_NOTES
 
@@ -801,6 +802,8 @@ class RayPPOTrainer:
                 out["policy_kl"] += m["policy_kl"]
                 out["grad_norm"] += gn
                 n_updates += 1
+                if "moe_aux_loss" in m:
+                    out["moe_aux_loss"] = out.get("moe_aux_loss", 0.0) + m["moe_aux_loss"]
                 if m.get("post_update_diff"):
                     for k_ in ("sum", "sq", "tokens"):
                         post[k_] += m["post_update_diff"][k_]

@@ -234,3 +234,53 @@ def test_training_temperature_scales_the_logits_the_logprobs_are_taken_from(tmp_
     with pytest.raises(ValueError, match="isoexec.enabled=false"):
         validate_cfg(SkyRLTrainConfig.from_cli_overrides(ov + ["trainer.isoexec.enabled=true", "trainer.algorithm.temperature=0.7"]))
     validate_cfg(SkyRLTrainConfig.from_cli_overrides(ov + ["trainer.isoexec.enabled=false"]))
+
+
+def test_moe_balance_term_reaches_the_router_gradient_through_recomputed_layers(tmp_path):
+    from skyrl_isoexec_b200.models.config import get_config
+    from skyrl_isoexec_b200.models.decoder import DecoderLM
+    from skyrl_isoexec_b200.ops import moe as moe_ops
+    from skyrl_isoexec_b200.train.batch import TrainingInputBatch, build_sequences
+    from skyrl_isoexec_b200.train.policy_worker import PolicyWorker, WorkerConfig
+    from skyrl_isoexec_b200.train.trainer import RayPPOTrainer
+
+    # the injected gradient equals d(coeff * scale * aux) / d(logits) computed by plain autograd
+    torch.manual_seed(0)
+    logits = torch.randn(12, 8, requires_grad=True)
+    idx, w = moe_ops.route(logits, 2, None, False, True)
+    moe_ops.AUX_LOSS.update(coeff=0.5, scale=0.25, sum=0.0, layers=0)
+    w2 = moe_ops._with_aux_loss(logits, idx, w, get_config("tiny-moe"))
+    (w2 * 0.0).sum().backward()                                  # nothing but the injection reaches the logits
+    f = torch.zeros(8).index_add_(0, idx.reshape(-1).long(), torch.ones(idx.numel())) / idx.numel()
+    lg = logits.detach().clone().requires_grad_(True)
+    (0.5 * 0.25 * 8 * (f * torch.softmax(lg, -1).mean(0)).sum()).backward()
+    assert torch.allclose(logits.grad, lg.grad, atol=1e-7) and float(logits.grad.abs().sum()) > 0
+    moe_ops.AUX_LOSS.update(coeff=0.0)
+    # with zero advantages the policy gradient vanishes; what is left on the router is the balance term, also with every
+    # layer recomputed in the backward
+    m = DecoderLM(get_config("tiny-moe"), seed=0)
+    g = torch.Generator().manual_seed(1)
+    seq, att, rmask = build_sequences([torch.randint(5, 500, (10,), generator=g).tolist() for _ in range(3)],
+                                      [torch.randint(5, 500, (6,), generator=g).tolist() for _ in range(3)])
+    def batch():
+        b = TrainingInputBatch({"sequences": seq, "attention_mask": att, "response_mask": rmask, "loss_mask": rmask.clone(),
+                                "advantages": torch.zeros_like(rmask)})
+        b.metadata["aux_loss_scale"] = 1.0 / float(rmask.sum())
+        return b
+
+    def router_grad(worker):
+        s = worker.model.store.specs["layers.0.moe.router.weight"]
+        n = s.shape[0] * s.shape[1]
+        return worker.opt.main_grad[s.offset:s.offset + n].clone()
+
+    w0 = PolicyWorker(m, WorkerConfig(max_tokens_per_microbatch=4096))
+    w0.forward_backward(batch())
+    assert float(router_grad(w0).abs().sum()) == 0.0
+    w1 = PolicyWorker(DecoderLM(get_config("tiny-moe"), seed=0), WorkerConfig(max_tokens_per_microbatch=4096, moe_aux_loss_coeff=0.1, checkpoint_layers=True))
+    out = w1.forward_backward(batch())
+    assert float(router_grad(w1).abs().sum()) > 0 and out["moe_aux_loss"] >= 1.0 - 1e-6          # E * sum f P >= 1, = 1 when balanced
+    w2_ = PolicyWorker(DecoderLM(get_config("tiny-moe"), seed=0), WorkerConfig(max_tokens_per_microbatch=4096, moe_aux_loss_coeff=0.1, keep_last_layers=2))
+    w2_.forward_backward(batch())
+    assert torch.allclose(router_grad(w2_), router_grad(w1), atol=1e-7)                            # recomputed or kept: the same gradient
+    cfg = SkyRLTrainConfig.from_cli_overrides(["trainer.policy.model=tiny-moe", "trainer.policy.megatron_config.moe_aux_loss_coeff=0.01"])
+    assert cfg.trainer.policy.moe_aux_loss_coeff == 0.01 and RayPPOTrainer is not None
