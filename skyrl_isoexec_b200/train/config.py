@@ -61,6 +61,7 @@ class PolicyConfig:
     model: str = "tiny-qwen3"           # preset name or path of a saved config
     model_overrides: dict = field(default_factory=dict)
     lora: LoRASettings = field(default_factory=LoRASettings)
+    freeze_moe_router: bool = False     # MoE models: the routers do not train
     moe_aux_loss_coeff: float = 0.0     # MoE models: weight of the router's load-balancing term in the update (0 = none)
     tokenizer_path: str = ""            # "" = none (token-id prompts and environments); "byte" = the built-in byte tokenizer;
                                         # else a directory transformers.AutoTokenizer loads (text prompts, chat templates, stop strings)
@@ -312,6 +313,7 @@ RENAMED_KEYS = {
     "trainer.policy.megatron_config.context_parallel_size": "trainer.policy.parallel.context_parallel_size",
     "trainer.policy.megatron_config.expert_model_parallel_size": "trainer.policy.parallel.expert_model_parallel_size",
     "trainer.policy.megatron_config.moe_aux_loss_coeff": "trainer.policy.moe_aux_loss_coeff",
+    "trainer.policy.megatron_config.freeze_moe_router": "trainer.policy.freeze_moe_router",
     "trainer.ref.model.path": "trainer.ref.hf_path",
     "trainer.critic.model.path": "trainer.critic.hf_path",
     "trainer.algorithm.kl_ctrl.type": "trainer.algorithm.kl_ctrl_type",
@@ -377,7 +379,6 @@ UNSUPPORTED_IF_SET = (
     ("trainer.critic.model.lora.rank", ("0",), "LoRA adapters are not wired into the RL trainer"),
     ("trainer.policy.megatron_config.expert_tensor_parallel_size", ("1", "none", "null"), "experts are sharded over expert parallelism only"),
     ("trainer.policy.megatron_config.moe_enable_routing_replay", ("false",), "router replay has no consumer here: both sides route with the same kernel on the same bits"),
-    ("trainer.policy.megatron_config.freeze_moe_router", ("false",), "the router cannot be frozen separately"),
     ("trainer.policy.language_model_only", ("false",), "the vision tower is frozen already; there is no switch"),
     ("trainer.ref.language_model_only", ("false",), "the vision tower is frozen already; there is no switch"),
     ("generator.inference_engine.language_model_only", ("false",), "the vision tower is frozen already; there is no switch"),

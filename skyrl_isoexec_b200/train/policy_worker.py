@@ -41,6 +41,7 @@ class OptimizerConfig:
 class WorkerConfig:
     max_tokens_per_microbatch: int = 8192
     logprob_chunk_rows: int = 8192
+    freeze_moe_router: bool = False    # the routers' weights (and selection biases) are put back after every optimizer step
     moe_aux_loss_coeff: float = 0.0    # > 0: every MoE layer's load-balancing term enters the gradient with this weight (ops/moe.py)
     temperature: float = 1.0           # != 1: logprobs of the distribution the rollout sampled from, softmax(logits / T): the rows
                                        # entering the LM head are divided by T (no contract run: that pins T = 1)
@@ -842,7 +843,21 @@ class PolicyWorker:
             # adapters: the dense gradients are projected onto the factors, the factors step, the merged weights are
             # rebuilt; master weights and Adam moments of the base parameters never move
             return self.lora.optim_step()
+        frozen = None
+        if self.cfg.freeze_moe_router and self.model.cfg.has_moe:
+            frozen = [(t, t.detach().clone()) for n, t in self.model.named_weights() if ".moe.router." in n]
         norm = self.opt.step(self.ps)
+        if frozen:
+            with torch.no_grad():
+                for t, old in frozen:
+                    t.copy_(old)
+                if self.opt.low_precision:          # the fp32 master copy follows, or the next step would bring the change back
+                    for n, t in self.model.named_weights():
+                        if ".moe.router." in n:
+                            sp = self.model.store.specs[n]
+                            a, b = max(self.opt.lo, sp.offset), min(self.opt.hi, sp.offset + t.numel())
+                            if a < b:
+                                self.opt.master[a - self.opt.lo:b - self.opt.lo].copy_(t.reshape(-1)[a - sp.offset:b - sp.offset].float())
         out = float(norm.item())
         self._calibrate_keep()
         return out

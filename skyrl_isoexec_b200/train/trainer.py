@@ -274,7 +274,7 @@ class RayPPOTrainer:
         wcfg = WorkerConfig(max_tokens_per_microbatch=t.max_tokens_per_microbatch, optimizer=t.policy.optimizer_config,
                             keep_last_layers=t.policy.keep_last_layers, shard_optimizer=t.policy.shard_optimizer,
                             want_entropy=t.algorithm.use_entropy_loss, logprob_chunk_rows=t.logprobs_chunk_size,
-                            moe_aux_loss_coeff=t.policy.moe_aux_loss_coeff,
+                            moe_aux_loss_coeff=t.policy.moe_aux_loss_coeff, freeze_moe_router=t.policy.freeze_moe_router,
                             temperature=(t.algorithm.temperature if t.algorithm.temperature is not None else g.sampling_params.temperature) or 1.0)
         from .config import COMPAT_NOTES
 

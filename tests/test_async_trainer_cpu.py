@@ -284,3 +284,21 @@ def test_moe_balance_term_reaches_the_router_gradient_through_recomputed_layers(
     assert torch.allclose(router_grad(w2_), router_grad(w1), atol=1e-7)                            # recomputed or kept: the same gradient
     cfg = SkyRLTrainConfig.from_cli_overrides(["trainer.policy.model=tiny-moe", "trainer.policy.megatron_config.moe_aux_loss_coeff=0.01"])
     assert cfg.trainer.policy.moe_aux_loss_coeff == 0.01 and RayPPOTrainer is not None
+
+
+def test_frozen_moe_router_does_not_move_while_the_experts_train(tmp_path):
+    from skyrl_isoexec_b200.train.trainer import RayPPOTrainer
+
+    ov = ["trainer.policy.model=tiny-moe", "trainer.train_batch_size=4", "trainer.policy_mini_batch_size=4", "generator.n_samples_per_prompt=4",
+          "generator.sampling_params.max_generate_length=8", "generator.sampling_params.ignore_eos=true", "data.synthetic_prompt_len=8",
+          "data.synthetic_prompts=16", "trainer.max_prompt_length=8", "generator.inference_engine.num_kv_pages=32", "trainer.num_steps=2",
+          "trainer.logger=jsonl", f"trainer.ckpt_path={tmp_path}", "trainer.resume_mode=none", "trainer.ckpt_interval=0",
+          "trainer.policy.optimizer_config.lr=1e-2", "trainer.policy.megatron_config.freeze_moe_router=true",
+          "trainer.policy.megatron_config.moe_aux_loss_coeff=0.01"]
+    tr = RayPPOTrainer(SkyRLTrainConfig.from_cli_overrides(ov), device="cpu")
+    tr.build_models()
+    w0 = {n: t.clone() for n, t in tr.policy.model.named_weights()}
+    tr.train()
+    moved = {n for n, t in tr.policy.model.named_weights() if not torch.equal(t, w0[n])}
+    assert not any(".moe.router." in n for n in moved) and any(".moe.experts." in n for n in moved)
+    assert tr.all_metrics["policy/moe_aux_loss"] >= 1.0 - 1e-6 and tr.all_metrics["policy/rollout_train_logprob_bit_mismatches"] == 0
