@@ -388,8 +388,6 @@ UNSUPPORTED_IF_SET = (
     ("generator.inference_engine.enable_return_routed_experts", ("false",), "router replay has no consumer here"),
     ("generator.inference_engine.enable_pd", ("false",), "prefill / decode disaggregation is not implemented"),
     ("generator.inference_engine.num_prefill", ("0",), "prefill / decode disaggregation is not implemented"),
-    ("generator.inference_engine.external_server_urls", ("[]", "none", "null", ""), "the trainer drives in-process engines"),
-    ("generator.inference_engine.external_proxy_url", ("none", "null", ""), "the trainer drives in-process engines"),
 )
 COMPAT_NOTES: list[str] = []
 
@@ -410,6 +408,10 @@ def translate_key(key: str, val: str):
         return None if low in ("none", "null") else ("trainer.policy.model_overrides.rope_theta", val)
     if key in ("trainer.rope_scaling", "generator.rope_scaling"):
         return None if low in ("none", "null", "{}") else ("trainer.policy.model_overrides.rope_scaling", val)
+    if key == "generator.inference_engine.external_server_urls":
+        return None if low in ("[]", "none", "null", "") else ("generator.inference_engine.remote_urls", val)
+    if key == "generator.inference_engine.external_proxy_url":      # one router in front of the servers (engine/router.py) is one URL
+        return None if low in ("none", "null", "") else ("generator.inference_engine.remote_urls", json.dumps([val.strip().strip("\"'")]))
     if key == "trainer.policy.record_memory":
         return ("trainer.record_memory", "memory_snapshots" if low == "true" else "")
     if key in ("trainer.policy.optimizer_config.adam_betas", "trainer.critic.optimizer_config.adam_betas"):
