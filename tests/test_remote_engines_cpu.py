@@ -79,3 +79,30 @@ def test_http_endpoint_in_front_of_the_trainers_engine_keeps_the_contract(tmp_pa
         assert len(seen[1]) == 3 and len(seen[2]) == 3 and tr.http_server.requests_served >= 2 * 4 + 2
     finally:
         tr.http_server.shutdown()
+
+
+def test_trainer_through_a_router_in_front_of_two_servers(tmp_path):
+    from skyrl_isoexec_b200.engine.llm_engine import EngineConfig, LLMEngine
+    from skyrl_isoexec_b200.engine.router import Router
+    from skyrl_isoexec_b200.engine.server import ServerGroup
+    from skyrl_isoexec_b200.models.config import get_config
+    from skyrl_isoexec_b200.models.decoder import DecoderLM
+    from skyrl_isoexec_b200.train.trainer import RayPPOTrainer
+
+    engines = [LLMEngine(DecoderLM(get_config("tiny-qwen3"), seed=70 + i), EngineConfig(num_kv_pages=32, seed=9 + i)) for i in range(2)]
+    group = ServerGroup(engines)
+    router = Router(group.start()).start()
+    try:
+        ov = ["trainer.policy.model=tiny-qwen3", "trainer.train_batch_size=4", "trainer.policy_mini_batch_size=4", "generator.n_samples_per_prompt=2",
+              "generator.sampling_params.max_generate_length=6", "generator.sampling_params.ignore_eos=true", "data.synthetic_prompt_len=8",
+              "data.synthetic_prompts=16", "trainer.max_prompt_length=8", "trainer.num_steps=1", "trainer.logger=jsonl", f"trainer.ckpt_path={tmp_path}",
+              "trainer.resume_mode=none", "trainer.ckpt_interval=0", "trainer.isoexec.enabled=false",
+              "generator.inference_engine.run_engines_locally=false", f"generator.inference_engine.external_proxy_url={router.url}"]
+        tr = RayPPOTrainer(SkyRLTrainConfig.from_cli_overrides(ov), device="cpu")
+        tr.train()
+        assert tr.all_metrics["policy/rollout_train_logprob_bit_mismatches"] == 0
+        assert all(torch.equal(e.model.store.flat, tr.policy.model.store.flat) for e in engines)       # the push fanned out to both
+        assert all(e.stats["tokens"] > 0 for e in engines)                                              # and so did the requests
+    finally:
+        router.shutdown()
+        group.shutdown()
