@@ -375,8 +375,8 @@ INERT_PREFIXES = (
 )
 # (key or prefix, values that are fine, what is missing): a value outside the fine ones would change what is trained
 UNSUPPORTED_IF_SET = (
-    ("trainer.ref.model.lora.rank", ("0",), "LoRA adapters are not wired into the RL trainer"),
-    ("trainer.critic.model.lora.rank", ("0",), "LoRA adapters are not wired into the RL trainer"),
+    ("trainer.ref.model.lora.rank", ("0",), "LoRA adapters exist for the policy only (trainer.policy.lora); the reference model is frozen"),
+    ("trainer.critic.model.lora.rank", ("0",), "LoRA adapters exist for the policy only (trainer.policy.lora); the critic trains in full"),
     ("trainer.policy.megatron_config.expert_tensor_parallel_size", ("1", "none", "null"), "experts are sharded over expert parallelism only"),
     ("trainer.policy.megatron_config.moe_enable_routing_replay", ("false",), "router replay has no consumer here: both sides route with the same kernel on the same bits"),
     ("trainer.policy.language_model_only", ("false",), "the vision tower is frozen already; there is no switch"),
