@@ -191,3 +191,57 @@ def test_rl_steps_with_prefix_caching_stay_bitwise_and_the_sync_is_seen_to_empty
     assert pc is not None and pc.stored >= 4 and tr.engine.stats["prefix_cache_drops"] >= 2
     verdict = tr.adapter_engine.ledger.verdict()
     assert verdict["ok"], verdict
+
+
+def test_random_request_streams_keep_the_page_accounting_exact():
+    """Property test: whatever the order of inserts, matches, releases and evictions, every page is either free or
+    referenced, reference counts equal the number of holders, and a match only ever returns pages whose tokens are the
+    request's own prefix."""
+    from hypothesis import given, settings
+    from hypothesis import strategies as st
+
+    @settings(max_examples=60, deadline=None)
+    @given(st.lists(st.tuples(st.integers(0, 5), st.integers(1, 3), st.integers(0, PAGE - 1), st.sampled_from(["finish", "evict", "hold"])), min_size=1, max_size=25))
+    def run(ops):
+        al = PageAllocator(12)
+        pc = PrefixCache(al)
+        held: list[tuple[list[int], list[int]]] = []                       # (tokens, pages) of requests still running
+        content: dict[int, tuple] = {}                                      # page -> the tokens written into it
+        for family, n_pages, extra, what in ops:
+            # prompts of one family share their first pages: family f, page k holds tokens f * 1000 + k
+            tokens = [family * 1000 + k for k in range(n_pages) for _ in range(PAGE)] + [7] * extra + [9]
+            got, _key = pc.match(tokens)
+            for k, p in enumerate(got):
+                assert content[p] == tuple(tokens[k * PAGE:(k + 1) * PAGE])
+            need = (len(tokens) + PAGE - 1) // PAGE - len(got)
+            if not al.can_alloc(need):
+                pc.evict(need - al.num_free)
+            if not al.can_alloc(need):
+                al.release(got)
+                continue
+            pages = got + al.alloc(need)
+            for k in range(len(got), len(pages)):
+                content[pages[k]] = tuple(tokens[k * PAGE:(k + 1) * PAGE])
+            if what == "hold":
+                held.append((tokens, pages))
+            else:
+                pc.insert(tokens, pages, len(tokens))
+                al.release(pages)
+                if what == "evict":
+                    pc.evict(2)
+            # invariants
+            holders = [0] * al.num_pages
+            for _t, ps_ in held:
+                for p in ps_:
+                    holders[p] += 1
+            for page, _par, _tok in pc.table.values():
+                holders[page] += 1
+            assert holders == al.refs
+            assert sorted(al.free) == [p for p in range(al.num_pages) if al.refs[p] == 0] and len(set(al.free)) == len(al.free)
+        for tokens, pages in held:
+            pc.insert(tokens, pages, len(tokens))
+            al.release(pages)
+        pc.clear()
+        assert al.num_free == al.num_pages and all(r == 0 for r in al.refs)
+
+    run()
