@@ -245,3 +245,23 @@ def test_random_request_streams_keep_the_page_accounting_exact():
         assert al.num_free == al.num_pages and all(r == 0 for r in al.refs)
 
     run()
+
+
+@pytest.mark.parametrize("preset", ["tiny-qwen3", "tiny-hybrid"])
+def test_prefix_cache_under_page_pressure_and_preemption_still_gives_the_plain_engines_bits(preset):
+    """A pool too small for the running batch: sequences are preempted and recomputed, cached pages are evicted and found
+    again, and every answer is still the answer of an engine without a cache and with room to spare."""
+    sp = SamplingParams(max_generate_length=140, temperature=0.0, ignore_eos=True)
+    roomy = _engine(preset, False, pages=64)
+    tight = _engine(preset, True, pages=7)
+    fam = [_toks(PAGE + 5, 100 + f) for f in range(3)]
+    g = torch.Generator().manual_seed(0)
+    for rnd in range(4):
+        prompts = []
+        for _ in range(4):
+            f = int(torch.randint(0, 3, (1,), generator=g))
+            prompts.append(fam[f] + _toks(int(torch.randint(3, 60, (1,), generator=g)), 1000 + rnd * 10 + len(prompts)))
+        assert _same(roomy.generate(prompts, sp), tight.generate(prompts, sp)), rnd
+    pc, al = tight.prefix_cache, tight.cache.allocator
+    assert tight.scheduler.preemptions > 0 and pc.hits > 0 and pc.evicted > 0
+    assert al.num_free + len(pc) == al.num_pages and pc.evictable() == len(pc)
