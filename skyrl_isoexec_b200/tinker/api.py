@@ -4,7 +4,9 @@ Every mutating call returns a ``request_id`` at once; the work is queued in a SQ
 survive a restart of the front end) and executed in order by one engine thread; ``/api/v1/retrieve_future`` returns
 ``{status: pending|completed|failed, result}``.
 
-  POST /api/v1/create_model        {base_model, model_overrides?, lr?}   -> {model_id}
+  POST /api/v1/create_model        {base_model, model_overrides?, lr?, lora_config?: {rank, alpha}}   -> {model_id}
+                                   (with ``lora_config`` the model is an ADAPTER: models created on the same base with the same
+                                   overrides share one set of base weights, which never train; each trains its own factors)
   POST /api/v1/forward_backward    {model_id, data, loss_fn}
   POST /api/v1/forward             {model_id, data}
   POST /api/v1/optim_step          {model_id, adam_params}
@@ -65,6 +67,8 @@ class TinkerServer:
         self._dblock = threading.Lock()
         self.device = device
         self.models: dict[str, SkyRLTrainBackend] = {}
+        self.shared_bases: dict[str, SkyRLTrainBackend] = {}     # (base model, overrides, seed) -> the backend its adapters share
+        self.adapter_of: dict[str, str] = {}                     # adapter model id -> key of its shared base
         self._stop = threading.Event()
         self._wake = threading.Event()
         self._seq = int(self.db.execute("select coalesce(max(seq), 0) from futures").fetchone()[0])
@@ -152,11 +156,15 @@ class TinkerServer:
         for mid, spec in self.db.execute("select id, spec from models").fetchall():
             sp = json.loads(spec)
             try:
-                b = SkyRLTrainBackend(sp["base_model"], sp["model_overrides"], self.device, sp["lr"], sp["seed"])
+                if sp.get("lora_config"):
+                    self._add_adapter(mid, sp)
+                    b = self.models[mid]
+                else:
+                    b = SkyRLTrainBackend(sp["base_model"], sp["model_overrides"], self.device, sp["lr"], sp["seed"])
                 last = self.db.execute("select path from checkpoints where model_id = ? and kind = 'save_weights' order by created desc limit 1",
                                        (mid,)).fetchone()
                 if last and os.path.exists(last[0]):
-                    b.handle({"type": "load_weights", "path": last[0]})
+                    b.handle({"type": "load_weights", "path": last[0], **({"tenant": mid} if sp.get("lora_config") else {})})
                 self.models[mid] = b
                 out["models"].append(mid)
             except Exception as e:  # noqa: BLE001
@@ -325,7 +333,12 @@ class TinkerServer:
             mid = "model-" + uuid.uuid4().hex[:10]
             spec = {"base_model": body.get("base_model", "tiny-qwen3"), "model_overrides": body.get("model_overrides") or {},
                     "lr": body.get("lr", 1e-5), "seed": body.get("seed", 0)}
-            self.models[mid] = SkyRLTrainBackend(spec["base_model"], spec["model_overrides"], self.device, spec["lr"], spec["seed"])
+            lora = body.get("lora_config") or None
+            if lora and int(lora.get("rank", 0)) > 0:
+                spec["lora_config"] = {"rank": int(lora["rank"]), "alpha": float(lora.get("alpha", 16.0))}
+                self._add_adapter(mid, spec)
+            else:
+                self.models[mid] = SkyRLTrainBackend(spec["base_model"], spec["model_overrides"], self.device, spec["lr"], spec["seed"])
             with self._dblock:
                 self.db.execute("insert into models values (?, ?)", (mid, json.dumps(spec)))
                 self.db.commit()
@@ -342,6 +355,8 @@ class TinkerServer:
             raise KeyError(f"model_id {body.get('model_id')!r}")
         rid = "req-" + uuid.uuid4().hex[:12]
         payload = dict(body, type=_ROUTES[verb])
+        if body["model_id"] in self.adapter_of:
+            payload["tenant"] = body["model_id"]
         with self._dblock:
             self._seq += 1
             self.db.execute("insert into futures (id, seq, model_id, payload, status, result, created) values (?, ?, ?, ?, 'pending', null, ?)",
@@ -349,6 +364,16 @@ class TinkerServer:
             self.db.commit()
         self._wake.set()
         return {"request_id": rid}
+
+    def _add_adapter(self, mid: str, spec: dict) -> None:
+        """An adapter model: it lives on the shared backend of its (base model, overrides, seed); the first one builds it."""
+        key = json.dumps([spec["base_model"], spec["model_overrides"], spec["seed"]], sort_keys=True)
+        if key not in self.shared_bases:
+            self.shared_bases[key] = SkyRLTrainBackend(spec["base_model"], spec["model_overrides"], self.device, spec["lr"], spec["seed"])
+        be = self.shared_bases[key]
+        be.add_tenant(mid, spec["lora_config"]["rank"], spec["lora_config"]["alpha"], lr=spec["lr"], seed=len(be.tenants))
+        self.models[mid] = be
+        self.adapter_of[mid] = key
 
     # ------------------------------------------------------------------ engine loop: strictly in arrival order
     def _loop(self) -> None:

@@ -42,6 +42,33 @@ class SkyRLTrainBackend:
         self.worker = PolicyWorker(self.model, WorkerConfig(optimizer=OptimizerConfig(lr=lr, num_warmup_steps=0)), self.algo)
         self.engine = LLMEngine(self.model, EngineConfig(max_num_seqs=64, num_kv_pages=num_kv_pages, seed=seed + 1))
         self.step_count = 0
+        # multi-tenant LoRA (reference: docs/content/docs/tinker/multi_tenancy.mdx, B/workers/megatron/adapter_store.py): several
+        # model ids share this backend's base weights, each with an adapter of its own that is merged in while its requests
+        # run; the base never trains
+        self.store = None
+        self.tenants: dict = {}             # tenant -> {"trainer": LoRATrainer, "step": int}
+
+    def add_tenant(self, tenant: str, rank: int, alpha: float = 16.0, lr: float = 1e-4, seed: int = 0) -> None:
+        from ..train.lora import AdapterStore, LoRAAdapter, LoRAConfig, LoRATrainer
+
+        if self.store is None:
+            self.store = AdapterStore(self.model)
+        self.store.deactivate()                          # a new adapter is sized on the base weights
+        self.store.register(tenant, LoRAAdapter.init(self.model, LoRAConfig(rank=rank, alpha=alpha, lr=lr, seed=seed)))
+        self.tenants[tenant] = {"trainer": LoRATrainer(self.worker, self.store, tenant), "step": 0}
+
+    def _switch(self, tenant: str | None) -> None:
+        """Merge the adapter of the request's tenant (dropping what the engine cached under another one)."""
+        if self.store is None:
+            return
+        if tenant is not None and tenant not in self.tenants:
+            raise KeyError(f"unknown adapter {tenant!r}")
+        if self.store.active != tenant:
+            if tenant is None:
+                self.store.deactivate()
+            else:
+                self.store.activate(tenant)
+            self.engine.reset_prefix_cache()
 
     def _sample_external(self, prompt_ids: list[int], sp, n: int) -> dict:
         import json
@@ -106,6 +133,34 @@ class SkyRLTrainBackend:
 
     def handle(self, req: dict) -> dict:
         kind = req["type"]
+        tenant = req.get("tenant")
+        self._switch(tenant)
+        if tenant is not None and kind == "optim_step":
+            t = self.tenants[tenant]
+            lr = (req.get("adam_params") or {}).get("learning_rate")
+            if lr is not None:
+                for gparam in t["trainer"].opt.param_groups:
+                    gparam["lr"] = float(lr)
+            self.worker.reduce_gradients()
+            gn = t["trainer"].optim_step()
+            t["step"] += 1
+            self.engine.reset_prefix_cache()
+            return {"grad_norm": gn, "step": t["step"]}
+        if tenant is not None and kind in ("save_weights", "load_weights"):
+            ad = self.store.adapters[tenant]
+            if kind == "save_weights":
+                os.makedirs(os.path.dirname(req["path"]) or ".", exist_ok=True)
+                torch.save({"adapter": ad.state_dict(), "step": self.tenants[tenant]["step"], "opt": self.tenants[tenant]["trainer"].opt.state_dict()}, req["path"])
+                return {"path": req["path"]}
+            sd = torch.load(req["path"], weights_only=False, map_location="cpu")
+            for k in ad.A:
+                ad.A[k].copy_(sd["adapter"]["A"][k])
+                ad.B[k].copy_(sd["adapter"]["B"][k])
+            self.tenants[tenant]["trainer"].opt.load_state_dict(sd["opt"])
+            self.tenants[tenant]["step"] = int(sd.get("step", 0))
+            self.store.refresh()
+            self.engine.reset_prefix_cache()
+            return {"step": self.tenants[tenant]["step"]}
         if kind in ("forward", "forward_backward"):
             b = self._batch(req["data"])
             lens = [len(d["response_ids"]) for d in req["data"]]

@@ -151,3 +151,58 @@ def test_tinker_rest_paths_of_the_reference(tmp_path):
         assert get("/api/v1/telemetry")["client_events"] == {"step": 2, "error": 1}
     finally:
         srv.shutdown()
+
+
+def test_tinker_adapters_share_one_base_and_train_apart(tmp_path):
+    """Multi-tenant LoRA: two adapter models on one base. Each trains its own factors, each samples under its own merged
+    weights, the base never moves, and an adapter's save / load brings its factors back."""
+    srv = TinkerServer(db_path=str(tmp_path / "q.db"), device="cpu").start()
+    try:
+        cl = TinkerClient(srv.url)
+        a = cl.create_model(base_model="tiny-qwen3", lr=2e-2, lora_config={"rank": 4, "alpha": 8})
+        b = cl.create_model(base_model="tiny-qwen3", lr=2e-2, lora_config={"rank": 2})
+        full = cl.create_model(base_model="tiny-qwen3", lr=1e-3)                        # an ordinary model beside them
+        be = srv.models[a]
+        assert srv.models[b] is be and srv.models[full] is not be and set(be.tenants) == {a, b}
+        base0 = {n: t.clone() for n, t in be.model.named_weights()}
+        g = torch.Generator().manual_seed(0)
+        data = [{"prompt_ids": torch.randint(0, 500, (5,), generator=g).tolist(),
+                 "response_ids": torch.randint(0, 500, (8,), generator=g).tolist()} for _ in range(4)]
+        prompt = data[0]["prompt_ids"]
+        sp = {"max_generate_length": 5, "ignore_eos": True, "temperature": 0.0}
+        before = cl.call("asample", model_id=a, prompt_ids=prompt, num_samples=1, sampling_params=sp)["sequences"][0]
+        losses = []
+        for _ in range(4):                                                              # only adapter a trains
+            losses.append(cl.call("forward_backward", model_id=a, data=data, loss_fn="cross_entropy")["loss"])
+            assert cl.call("optim_step", model_id=a, adam_params={})["step"] == len(losses)
+        assert losses[-1] < losses[0]
+        after_a = cl.call("asample", model_id=a, prompt_ids=prompt, num_samples=1, sampling_params=sp)["sequences"][0]
+        same_b = cl.call("asample", model_id=b, prompt_ids=prompt, num_samples=1, sampling_params=sp)["sequences"][0]
+        assert after_a["logprobs"] != before["logprobs"]                                # a's policy moved
+        assert same_b["logprobs"] == before["logprobs"]                                 # b still is the base (its B factors are zero)
+        # sampling under an adapter and scoring under it agree bit for bit (the adapter is merged for both)
+        fwd = cl.call("forward", model_id=a, data=[{"prompt_ids": prompt, "response_ids": after_a["tokens"]}])
+        assert fwd["logprobs"][0] == after_a["logprobs"]
+        # the base weights are untouched once no adapter is merged
+        be.store.deactivate()
+        assert all(torch.equal(t, base0[n]) for n, t in be.model.named_weights())
+        # save, train on, load: the factors come back
+        path = str(tmp_path / "a.pt")
+        cl.call("save_weights", model_id=a, path=path)
+        cl.call("forward_backward", model_id=a, data=data, loss_fn="cross_entropy")
+        cl.call("optim_step", model_id=a, adam_params={"learning_rate": 5e-2})
+        moved = cl.call("asample", model_id=a, prompt_ids=prompt, num_samples=1, sampling_params=sp)["sequences"][0]
+        assert cl.call("load_weights", model_id=a, path=path)["step"] == 4
+        back = cl.call("asample", model_id=a, prompt_ids=prompt, num_samples=1, sampling_params=sp)["sequences"][0]
+        assert back["logprobs"] == after_a["logprobs"] and moved["logprobs"] != after_a["logprobs"]
+    finally:
+        srv.shutdown()
+    # a restarted front end rebuilds the shared base and both adapters, with a's last save applied
+    srv2 = TinkerServer(db_path=str(tmp_path / "q.db"), device="cpu").start()
+    try:
+        assert srv2.models[a] is srv2.models[b] and set(srv2.models[a].tenants) == {a, b}
+        cl2 = TinkerClient(srv2.url)
+        again = cl2.call("asample", model_id=a, prompt_ids=prompt, num_samples=1, sampling_params=sp)["sequences"][0]
+        assert again["logprobs"] == after_a["logprobs"]
+    finally:
+        srv2.shutdown()
