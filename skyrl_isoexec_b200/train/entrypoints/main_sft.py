@@ -3,7 +3,8 @@
     python -m skyrl_isoexec_b200.train.entrypoints.main_sft --data sft.jsonl [--model qwen3-8b] [--batch-size 32] [--epochs 1]
         [--lr 1e-5] [--ckpt-path DIR --ckpt-interval N] [--max-tokens 8192] [--num-steps N]
         [--eval-data eval.jsonl --eval-interval N] [--tokenizer DIR --train-on last|all --cache-dir DIR]
-        [--export-path DIR --hf-save-interval N] [--dummy-steps N] [--config sft.yaml] [key=value ...]
+        [--export-path DIR --hf-save-interval N] [--dummy-steps N] [--lora-rank R --lora-alpha A] [--hf-path DIR]
+        [--config sft.yaml] [key=value ...]
 
 ``--data`` is a JSONL file with one record per line: ``{"prompt_ids": [...], "response_ids": [...]}`` (token ids), an
 alpaca record (``instruction`` / ``input`` / ``output``) or a chat record (``messages`` with optional ``tool_calls`` and
@@ -38,7 +39,8 @@ def main(argv=None) -> SFTTrainer:
             "ckpt_path": ("--ckpt-path", str), "ckpt_interval": ("--ckpt-interval", int), "resume_mode": ("--resume-mode", str),
             "logger": ("--logger", str), "eval_interval": ("--eval-interval", int), "train_on": ("--train-on", str),
             "tokenize_cache_dir": ("--cache-dir", str), "export_path": ("--export-path", str),
-            "hf_save_interval": ("--hf-save-interval", int), "dummy_steps": ("--dummy-steps", int)}
+            "hf_save_interval": ("--hf-save-interval", int), "dummy_steps": ("--dummy-steps", int), "lora_rank": ("--lora-rank", int),
+            "lora_alpha": ("--lora-alpha", float), "hf_path": ("--hf-path", str)}
     for key, (flag, tp) in opts.items():
         ap.add_argument(flag, type=tp, default=None, dest="f_" + key.replace(".", "__"),
                         **({"choices": ["last", "all"]} if key == "train_on" else {}))

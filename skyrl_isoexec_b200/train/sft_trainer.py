@@ -54,6 +54,9 @@ class SFTConfig:
     eval_batch_size: int = 32
     export_path: str = ""
     hf_save_interval: int = 0             # every N steps; 0 with export_path set: once, at the end
+    lora_rank: int = 0                    # > 0: train low-rank adapters (train/lora.py), the base weights stay as they are
+    lora_alpha: float = 16.0
+    hf_path: str = ""                     # initial weights: a Hugging Face style directory (models/hf_export.py); default: random init
     dummy_steps: int = 0                  # > 0: ignore the data, train on synthetic rows of max_seq_len tokens (timing runs)
 
     @classmethod
@@ -103,6 +106,23 @@ class SFTTrainer:
         algo = alg.AlgorithmConfig(policy_loss_type="cross_entropy", loss_reduction=cfg.loss_reduction)
         self.worker = PolicyWorker(self.model, WorkerConfig(max_tokens_per_microbatch=cfg.max_tokens_per_microbatch,
                                                             optimizer=cfg.optimizer), algo)
+        if cfg.hf_path:
+            from ..models import hf_export
+
+            hf_export.load_hf(self.model, cfg.hf_path)
+            if self.worker.opt.low_precision:
+                self.worker.opt.master.copy_(self.model.store.flat[self.worker.opt.lo:self.worker.opt.hi].float())
+        self.lora_store = None
+        if cfg.lora_rank > 0:
+            from .lora import AdapterStore, LoRAAdapter, LoRAConfig, LoRATrainer
+
+            if self.ps.tp > 1 or self.ps.pp > 1:
+                raise ValueError("LoRA fine-tuning needs tensor- and pipeline-parallel degrees of 1")
+            self.lora_store = AdapterStore(self.model)
+            self.lora_store.register("sft", LoRAAdapter.init(self.model, LoRAConfig(rank=cfg.lora_rank, alpha=cfg.lora_alpha, lr=cfg.optimizer.lr,
+                                                                                    seed=cfg.seed)))
+            self.lora_store.activate("sft")
+            self.worker.lora = LoRATrainer(self.worker, self.lora_store, "sft")
         self.examples = examples
         self.global_step = 0
         self.tracker = Tracking(cfg.project_name, cfg.run_name, cfg.logger) if self.rank == 0 else None

@@ -1233,3 +1233,37 @@ def test_rope_scaling_tables_match_the_transformers_formulas_and_extend_the_cont
 
     c = SkyRLTrainConfig.from_cli_overrides(['trainer.rope_scaling={"rope_type": "yarn", "factor": 4.0}'])
     assert c.trainer.policy.model_overrides == {"rope_scaling": {"rope_type": "yarn", "factor": 4.0}}
+
+
+def test_sft_with_lora_lowers_the_loss_and_leaves_the_base_alone(tmp_path):
+    from skyrl_isoexec_b200.models import hf_export
+    from skyrl_isoexec_b200.models.config import get_config
+    from skyrl_isoexec_b200.models.decoder import DecoderLM
+
+    g = torch.Generator().manual_seed(0)
+    ex = [{"prompt_ids": torch.randint(0, 200, (6,), generator=g).tolist(), "response_ids": torch.randint(0, 200, (10,), generator=g).tolist()} for _ in range(8)]
+    donor = DecoderLM(get_config("tiny-qwen3"), seed=5)
+    hf_export.save_hf(donor, str(tmp_path / "init"))
+    cfg = SFTConfig(model="tiny-qwen3", batch_size=8, logger="jsonl", num_steps=6, epochs=6, lora_rank=4, lora_alpha=8.0, hf_path=str(tmp_path / "init"),
+                    export_path=str(tmp_path / "out"))
+    cfg.optimizer.lr = 2e-2
+    tr = SFTTrainer(cfg, ex, device="cpu")
+    assert torch.equal(tr.model.store.flat, donor.store.flat)                  # started from the given weights
+    first = tr.evaluate_rows(ex) if hasattr(tr, "evaluate_rows") else None
+    tr.eval_examples = tr.examples
+    before = tr.evaluate()
+    tr.train()
+    after = tr.evaluate()
+    assert list(after.values())[0] < list(before.values())[0] and first is None          # mean negative log-likelihood went down
+    ad = tr.lora_store.adapters["sft"]
+    assert tr.global_step == 6 and any(float(b.abs().sum()) > 0 for b in ad.B.values()) and tr.worker.opt.step_count == 0
+    merged = dict(tr.model.named_weights())
+    for n, t in donor.named_weights():
+        if n in ad.A:
+            assert torch.allclose(merged[n], t + ad.delta(n), atol=1e-6)
+        else:
+            assert torch.equal(merged[n], t)
+    # the export holds the merged weights
+    back = DecoderLM(get_config("tiny-qwen3"), seed=99)
+    hf_export.load_hf(back, str(tmp_path / "out" / f"global_step_{tr.global_step}"))
+    assert torch.equal(back.store.flat, tr.model.store.flat)
