@@ -192,13 +192,72 @@ def save_hf(model: DecoderLM, path: str, write: bool = True) -> None:
             json.dump(hf_config(model.cfg), f, indent=1)
 
 
-def load_hf(model: DecoderLM, path: str) -> int:
-    """Load ``model.safetensors`` written by ``save_hf`` (or any checkpoint with the same names) into ``model``."""
-    from safetensors.torch import load_file
+class _LazyCheckpoint:
+    """Tensors of a Hugging Face checkpoint directory, read one at a time: a single ``model.safetensors``, or the shards a
+    released model comes in (``model.safetensors.index.json`` names the file of every tensor, or every ``*.safetensors`` file
+    of the directory is looked through). Nothing but the tensor asked for is held, so a 64 GB checkpoint loads into a
+    sharded model without a 64 GB host copy. Tied checkpoints without ``lm_head.weight`` answer it with the embedding."""
 
-    sd = load_file(os.path.join(path, "model.safetensors"))
+    def __init__(self, path: str):
+        from safetensors import safe_open
+
+        self._open = safe_open
+        self.where: dict[str, str] = {}
+        index = os.path.join(path, "model.safetensors.index.json")
+        if os.path.exists(index):
+            with open(index) as f:
+                self.where = {k: os.path.join(path, v) for k, v in json.load(f)["weight_map"].items()}
+        else:
+            files = sorted(fn for fn in os.listdir(path) if fn.endswith(".safetensors"))
+            if not files:
+                raise FileNotFoundError(f"{path} holds no .safetensors file")
+            for fn in files:
+                with safe_open(os.path.join(path, fn), framework="pt", device="cpu") as f:
+                    for k in f.keys():
+                        self.where[k] = os.path.join(path, fn)
+        self._handles: dict = {}
+
+    def keys(self):
+        return self.where.keys()
+
+    def __iter__(self):
+        return iter(self.where)
+
+    def __contains__(self, k) -> bool:
+        return k in self.where
+
+    def __getitem__(self, k: str) -> torch.Tensor:
+        if k not in self.where and k == "lm_head.weight" and "model.embed_tokens.weight" in self.where:
+            k = "model.embed_tokens.weight"
+        fn = self.where[k]
+        h = self._handles.get(fn)
+        if h is None:
+            h = self._handles[fn] = self._open(fn, framework="pt", device="cpu").__enter__()
+        return h.get_tensor(k)
+
+    def close(self) -> None:
+        for h in self._handles.values():
+            h.__exit__(None, None, None)
+        self._handles.clear()
+
+
+def has_hf_weights(path: str) -> bool:
+    return os.path.isdir(path) and any(fn.endswith(".safetensors") for fn in os.listdir(path))
+
+
+def load_hf(model: DecoderLM, path: str) -> int:
+    """Load a Hugging Face style checkpoint directory (one ``model.safetensors`` as ``save_hf`` writes it, or the sharded
+    files of a released model) into ``model``: tensors are read one at a time and cut to this rank's shard."""
+    sd = _LazyCheckpoint(path)
+    try:
+        return _load_from(model, sd)
+    finally:
+        sd.close()
+
+
+def _load_from(model: DecoderLM, sd) -> int:
     if getattr(model, "vision", None) is not None and any(k.startswith("visual.") for k in sd):
-        model.vision.load_state_dict({k: v for k, v in sd.items() if k.startswith("visual.")})
+        model.vision.load_state_dict({k: sd[k] for k in sd if k.startswith("visual.")})
     cfg = model.cfg
     n = 0
     with torch.no_grad():

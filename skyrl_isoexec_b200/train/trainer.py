@@ -271,6 +271,13 @@ class RayPPOTrainer:
             model = build_stage_model(mcfg, self.ps, self.device, seed=t.policy.seed)
         else:
             model = DecoderLM(mcfg, self.ps, self.device, seed=t.policy.seed, flat_alloc=flat_alloc)
+        if os.path.isdir(t.policy.model) and self.ps.pp == 1:
+            # trainer.policy.model names a checkpoint directory: its config.json gave the architecture, its weights are the
+            # starting point (a directory with a config only starts from the seeded random init)
+            from ..models import hf_export
+
+            if hf_export.has_hf_weights(t.policy.model):
+                hf_export.load_hf(model, t.policy.model)
         wcfg = WorkerConfig(max_tokens_per_microbatch=t.max_tokens_per_microbatch, optimizer=t.policy.optimizer_config,
                             keep_last_layers=t.policy.keep_last_layers, shard_optimizer=t.policy.shard_optimizer,
                             want_entropy=t.algorithm.use_entropy_loss, logprob_chunk_rows=t.logprobs_chunk_size,

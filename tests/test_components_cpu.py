@@ -1267,3 +1267,38 @@ def test_sft_with_lora_lowers_the_loss_and_leaves_the_base_alone(tmp_path):
     back = DecoderLM(get_config("tiny-qwen3"), seed=99)
     hf_export.load_hf(back, str(tmp_path / "out" / f"global_step_{tr.global_step}"))
     assert torch.equal(back.store.flat, tr.model.store.flat)
+
+
+def test_policy_starts_from_a_sharded_hugging_face_checkpoint_directory(tmp_path):
+    import json as _json
+
+    from safetensors.torch import save_file
+
+    from skyrl_isoexec_b200.models import hf_export
+    from skyrl_isoexec_b200.models.config import get_config
+    from skyrl_isoexec_b200.models.decoder import DecoderLM
+
+    donor = DecoderLM(get_config("tiny-qwen3", tie_embeddings=False), seed=21)
+    d = tmp_path / "ckpt"
+    hf_export.save_hf(donor, str(d))
+    # re-cut the single file into two shards with an index, as released checkpoints come
+    from safetensors.torch import load_file
+
+    sd = load_file(str(d / "model.safetensors"))
+    (d / "model.safetensors").unlink()
+    keys = sorted(sd)
+    parts = {"model-00001-of-00002.safetensors": keys[: len(keys) // 2], "model-00002-of-00002.safetensors": keys[len(keys) // 2:]}
+    for fn, ks in parts.items():
+        save_file({k: sd[k].contiguous() for k in ks}, str(d / fn), metadata={"format": "pt"})
+    (d / "model.safetensors.index.json").write_text(_json.dumps({"metadata": {}, "weight_map": {k: fn for fn, ks in parts.items() for k in ks}}))
+    assert hf_export.has_hf_weights(str(d))
+    fresh = DecoderLM(get_config(str(d)), seed=0)
+    assert hf_export.load_hf(fresh, str(d)) > 0 and torch.equal(fresh.store.flat, donor.store.flat)
+    (d / "model.safetensors.index.json").unlink()                           # without an index the shard files are looked through
+    again = DecoderLM(get_config(str(d)), seed=1)
+    hf_export.load_hf(again, str(d))
+    assert torch.equal(again.store.flat, donor.store.flat)
+    # the trainer: the directory is the model name; config and weights both come from it
+    tr = RayPPOTrainer(_rl_cfg(str(tmp_path / "run"), 1, f"trainer.policy.model={d}", "trainer.policy.optimizer_config.lr=0.0"), device="cpu")
+    tr.build_models()
+    assert torch.equal(tr.policy.model.store.flat, donor.store.flat) and torch.equal(tr.policy.opt.master, donor.store.flat)
