@@ -94,6 +94,9 @@ class NativeInferenceEngine(InferenceEngineInterface):
         self.tokenizer = tokenizer
         if tokenizer is not None and llm.detokenize is None:
             llm.detokenize = tokenizer.decode          # stop strings are matched on decoded text
+        eos = getattr(tokenizer, "eos_token_id", None)
+        if eos is not None and llm.cfg.eos_token_id is None:
+            llm.cfg.eos_token_id = int(eos)            # a sequence ends at the tokenizer's end-of-sequence token (unless ignore_eos)
         self.receiver = None
 
     async def generate(self, input_batch: InferenceEngineInput) -> InferenceEngineOutput:

@@ -43,6 +43,9 @@ class _Pending:
 class InferenceServer:
     def __init__(self, llm, tokenizer=None, host: str = "127.0.0.1", port: int = 0, model_name: str = "policy"):
         self.llm, self.tokenizer, self.model_name = llm, tokenizer, model_name
+        eos = getattr(tokenizer, "eos_token_id", None)
+        if eos is not None and getattr(getattr(llm, "cfg", None), "eos_token_id", 0) is None:
+            llm.cfg.eos_token_id = int(eos)
         self._lock = threading.Lock()          # guards the engine (steps, admissions, control verbs)
         self._pending: list[_Pending] = []
         self._stop = threading.Event()

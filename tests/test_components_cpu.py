@@ -1302,3 +1302,26 @@ def test_policy_starts_from_a_sharded_hugging_face_checkpoint_directory(tmp_path
     tr = RayPPOTrainer(_rl_cfg(str(tmp_path / "run"), 1, f"trainer.policy.model={d}", "trainer.policy.optimizer_config.lr=0.0"), device="cpu")
     tr.build_models()
     assert torch.equal(tr.policy.model.store.flat, donor.store.flat) and torch.equal(tr.policy.opt.master, donor.store.flat)
+
+
+def test_engine_stops_at_the_tokenizers_end_of_sequence_token():
+    from skyrl_isoexec_b200.engine.interface import NativeInferenceEngine
+    from skyrl_isoexec_b200.engine.llm_engine import EngineConfig, LLMEngine
+    from skyrl_isoexec_b200.engine.sampler import SamplingParams
+    from skyrl_isoexec_b200.models.config import get_config
+    from skyrl_isoexec_b200.models.decoder import DecoderLM
+
+    class Tok:
+        eos_token_id = 42
+
+        def decode(self, ids, **kw):
+            return " ".join(map(str, ids))
+
+    eng = LLMEngine(DecoderLM(get_config("tiny-qwen3"), seed=0), EngineConfig(num_kv_pages=8, seed=1))
+    assert eng.cfg.eos_token_id is None
+    NativeInferenceEngine(eng, Tok())
+    assert eng.cfg.eos_token_id == 42
+    out = eng.generate([[5, 6, 7]], SamplingParams(max_generate_length=20, temperature=0.0, logit_bias={42: 1e4}))[0]
+    assert out.response_ids == [42] and out.stop_reason == "stop"
+    out = eng.generate([[5, 6, 7]], SamplingParams(max_generate_length=4, temperature=0.0, logit_bias={42: 1e4}, ignore_eos=True))[0]
+    assert out.response_ids == [42] * 4 and out.stop_reason == "length"
