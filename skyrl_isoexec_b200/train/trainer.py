@@ -390,6 +390,9 @@ class RayPPOTrainer:
                 if not hasattr(self.tokenizer, "chat_template"):
                     raise ValueError("generator.chat_template needs a tokenizer with a settable chat template (a Hugging Face tokenizer)")
                 self.tokenizer.chat_template = tpl
+        # a multi-turn trajectory stops taking turns once its context reaches this many tokens (stop reason "length"): the
+        # configured bound, but never more than the engine can hold
+        mil = min(max(g.max_input_length, t.max_prompt_length), int(getattr(self.engine, "max_len", 1 << 30)) - 1)
         if g.multimodal:
             from .vlm_generator import SkyRLVLMGymGenerator
 
@@ -399,20 +402,20 @@ class RayPPOTrainer:
                                                   append_eos_after_stop_str=g.append_eos_token_after_stop_str_in_multi_turn,
                                                   env_config=self.cfg.environment.env_kwargs,
                                                   zero_reward_on_non_stop=g.zero_reward_on_non_stop,
-                                                  apply_overlong_filtering=g.apply_overlong_filtering, rate_limit=g.rate_limit or None)
+                                                  apply_overlong_filtering=g.apply_overlong_filtering, rate_limit=g.rate_limit or None, max_input_length=mil)
         elif g.rlm:
             from .rlm_generator import RLMGymGenerator
 
             self.generator = RLMGymGenerator(self.infer, self.tokenizer, max_turns=g.max_turns, max_depth=g.rlm_max_depth,
                                              lm_max_tokens=g.rlm_lm_max_tokens, train_children=g.rlm_train_children,
                                              env_config=self.cfg.environment.env_kwargs, zero_reward_on_non_stop=g.zero_reward_on_non_stop,
-                                             apply_overlong_filtering=g.apply_overlong_filtering, rate_limit=g.rate_limit or None)
+                                             apply_overlong_filtering=g.apply_overlong_filtering, rate_limit=g.rate_limit or None, max_input_length=mil)
         else:
             self.generator = SkyRLGymGenerator(self.infer, self.tokenizer, max_turns=g.max_turns, batched=g.batched,
                                                env_config=self.cfg.environment.env_kwargs,
                                                zero_reward_on_non_stop=g.zero_reward_on_non_stop,
                                                apply_overlong_filtering=g.apply_overlong_filtering,
-                                               rate_limit=g.rate_limit or None, step_wise=g.step_wise_trajectories)
+                                               rate_limit=g.rate_limit or None, max_input_length=mil, step_wise=g.step_wise_trajectories)
         if t.isoexec.enabled:
             self.adapter_trainer = ContractAdapter("trainer", model, self.rank, trainer_tp=self.ps.tp, engine_tp=tp_e, trainer_pp=self.ps.pp)
             self.adapter_trainer.run_install()
