@@ -351,7 +351,9 @@ class RayPPOTrainer:
                             seed=t.seed + 7919 * self._engine_index(),
                             enable_prefix_caching=ie.enable_prefix_caching,
                             use_cuda_graph=not ie.enforce_eager, share_prompt_pages=ie.share_prompt_pages, share_recurrent_state=ie.share_recurrent_state,
-                            max_model_len=min(mcfg.max_position, t.max_prompt_length + g.sampling_params.max_generate_length + 1))
+                            # a multi-turn context grows to generator.max_input_length before its last turn
+                            max_model_len=min(mcfg.max_position, (max(t.max_prompt_length, g.max_input_length) if (g.max_turns > 1 or not g.batched)
+                                                                  else t.max_prompt_length) + g.sampling_params.max_generate_length + 1))
         self.remote_engines = not ie.run_engines_locally
         if self.remote_engines:
             # rollouts on servers this job does not own: generation over HTTP, weights through a shared directory
