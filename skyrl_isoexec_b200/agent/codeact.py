@@ -13,6 +13,8 @@ in front of the next one, which gives notebook-like persistence without a long-l
 
 from __future__ import annotations
 
+from ..utils.tokenizer import chat_ids
+
 import json
 import re
 import time
@@ -47,7 +49,7 @@ class CodeActAgent:
         t0 = time.time()
         tr = Trajectory(instance_id)
         msgs = [{"role": "system", "content": self.SYSTEM}, {"role": "user", "content": task}]
-        tr.prompt_ids = list(self.tok.apply_chat_template(msgs, add_generation_prompt=True, tokenize=True))
+        tr.prompt_ids = chat_ids(self.tok, msgs)
         ctx, prelude = list(tr.prompt_ids), []
         for _ in range(self.max_turns):
             if len(ctx) >= self.max_context:
@@ -84,8 +86,7 @@ class CodeActAgent:
                 obs = "bash is not available here; use <execute_python>."
             else:
                 obs = "No <execute_python> block or <finish> found."
-            obs_ids = list(self.tok.apply_chat_template([{"role": "tool", "content": obs[:self.max_obs]}], add_generation_prompt=True,
-                                                        tokenize=True))
+            obs_ids = chat_ids(self.tok, [{"role": "tool", "content": obs[:self.max_obs]}])
             tr.response_ids += obs_ids
             tr.loss_mask += [0] * len(obs_ids)
             tr.logprobs += [0.0] * len(obs_ids)

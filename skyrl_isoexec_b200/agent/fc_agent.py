@@ -16,6 +16,8 @@ sample; the outcome reward is given to every segment.
 
 from __future__ import annotations
 
+from ..utils.tokenizer import chat_ids
+
 import time
 
 from . import function_calling as fc
@@ -39,7 +41,7 @@ class FunctionCallAgent:
             self.sp["stop"] = list(fc.STOP_WORDS)
 
     def _encode(self, messages: list[dict]) -> list[int]:
-        return list(self.tok.apply_chat_template(messages, add_generation_prompt=True, tokenize=True))
+        return chat_ids(self.tok, messages)
 
     def _count(self, messages: list[dict]) -> int:
         return len(self._encode(messages))

@@ -9,6 +9,8 @@ trajectories concurrently against one engine (continuous batching does the rest)
 
 from __future__ import annotations
 
+from ..utils.tokenizer import chat_ids
+
 import asyncio
 import json
 import re
@@ -68,7 +70,7 @@ class ReActAgent:
         t0 = time.time()
         tr = Trajectory(instance_id)
         msgs = [{"role": "system", "content": self.SYSTEM + self.tools.describe()}, {"role": "user", "content": task}]
-        tr.prompt_ids = list(self.tok.apply_chat_template(msgs, add_generation_prompt=True, tokenize=True))
+        tr.prompt_ids = chat_ids(self.tok, msgs)
         ctx = list(tr.prompt_ids)
         for _ in range(self.max_turns):
             if len(ctx) >= self.max_context:
@@ -99,7 +101,7 @@ class ReActAgent:
                 except json.JSONDecodeError as e:
                     res = {"error": f"tool call is not valid JSON: {e}"}
                 obs = json.dumps(res, default=str)[:4000]
-            obs_ids = list(self.tok.apply_chat_template([{"role": "tool", "content": obs}], add_generation_prompt=True, tokenize=True))
+            obs_ids = chat_ids(self.tok, [{"role": "tool", "content": obs}])
             tr.response_ids += obs_ids
             tr.loss_mask += [0] * len(obs_ids)
             tr.logprobs += [0.0] * len(obs_ids)

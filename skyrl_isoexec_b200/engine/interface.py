@@ -12,6 +12,7 @@ import asyncio
 from abc import ABC, abstractmethod
 from typing import Any, TypedDict
 
+from ..utils.tokenizer import chat_ids
 from .llm_engine import EngineConfig, LLMEngine
 from .sampler import SamplingParams
 
@@ -105,7 +106,7 @@ class NativeInferenceEngine(InferenceEngineInterface):
             if self.tokenizer is None:
                 raise ValueError("text prompts need a tokenizer; pass prompt_token_ids")
             ids = [self.tokenizer.encode(p) if isinstance(p, str) else
-                   self.tokenizer.apply_chat_template(p, add_generation_prompt=True, tokenize=True)
+                   chat_ids(self.tokenizer, p)
                    for p in input_batch["prompts"]]
         sp = SamplingParams.from_dict(input_batch.get("sampling_params"))
         mm = input_batch.get("mm_features")

@@ -22,6 +22,8 @@ template is prefix-stable; the vision-language generator relies on that to find 
 
 from __future__ import annotations
 
+from ..utils.tokenizer import chat_ids
+
 import base64
 import io
 
@@ -87,7 +89,7 @@ def split_content(messages: list[dict]) -> tuple[list[dict], list[torch.Tensor]]
 def render_conversation(messages: list[dict], tokenizer, cfg, add_generation_prompt: bool = True) -> dict:
     flat, images = split_content(messages)
     if not images:
-        ids = list(tokenizer.apply_chat_template(flat, add_generation_prompt=add_generation_prompt, tokenize=True))
+        ids = chat_ids(tokenizer, flat, add_generation_prompt)
         return {"token_ids": ids, "features": None}
     if not getattr(cfg, "has_vision", False):
         raise ValueError(f"model {cfg.name!r} has no vision tower: the conversation must not contain images")

@@ -18,6 +18,8 @@ exponential backoff. While servers are paused in ``keep`` mode, data-plane calls
 
 from __future__ import annotations
 
+from ..utils.tokenizer import chat_ids
+
 import asyncio
 import json
 import threading
@@ -275,7 +277,7 @@ class InferenceServer:
             raise ValueError("text prompts need a tokenizer; send token ids")
         if isinstance(prompt, str):
             return self.tokenizer.encode(prompt)
-        return self.tokenizer.apply_chat_template(prompt, add_generation_prompt=True, tokenize=True)
+        return chat_ids(self.tokenizer, prompt)
 
     def _generate(self, body: dict) -> dict:
         ids = body["prompt_token_ids"]

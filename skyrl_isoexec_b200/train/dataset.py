@@ -9,6 +9,8 @@
 
 from __future__ import annotations
 
+from ..utils.tokenizer import chat_ids
+
 import json
 import random
 from collections import deque
@@ -59,7 +61,7 @@ class PromptDataset:
             # are counted by the generator against its max_input_length
             prompt = [dict(m, content="".join(p if isinstance(p, str) else p.get("text", "") for p in m["content"]))
                       if isinstance(m.get("content"), (list, tuple)) else m for m in prompt]
-        return len(self.tokenizer.apply_chat_template(prompt, add_generation_prompt=True, tokenize=True)) <= limit
+        return len(chat_ids(self.tokenizer, prompt)) <= limit
 
     def __len__(self):
         return len(self.rows)

@@ -10,6 +10,8 @@ multi-turn agent loop (R/train/generators/skyrl_gym_generator.py:273,713,808).
 
 from __future__ import annotations
 
+from ..utils.tokenizer import chat_ids
+
 import asyncio
 import time
 from abc import ABC, abstractmethod
@@ -97,6 +99,7 @@ class SkyRLGymGenerator(GeneratorInterface):
         self.env_config = env_config or {}
         self.zero_reward_on_non_stop = zero_reward_on_non_stop
         self.apply_overlong_filtering = apply_overlong_filtering
+        self.chat_template_kwargs: dict = {}                     # extra arguments of the tokenizer's chat template (the trainer sets them)
 
     # ------------------------------------------------------------------ helpers
     def _encode_prompt(self, prompt) -> list[int]:
@@ -106,7 +109,7 @@ class SkyRLGymGenerator(GeneratorInterface):
             raise ValueError("string / chat prompts need a tokenizer")
         if isinstance(prompt, str):
             return list(self.tokenizer.encode(prompt))
-        return list(self.tokenizer.apply_chat_template(prompt, add_generation_prompt=True, tokenize=True))
+        return chat_ids(self.tokenizer, prompt, **self.chat_template_kwargs)
 
     def _decode(self, ids: list[int]) -> str:
         return self.tokenizer.decode(ids) if self.tokenizer is not None else ""
@@ -182,7 +185,7 @@ class SkyRLGymGenerator(GeneratorInterface):
             if obs:
                 if self.tokenizer is None:
                     raise ValueError("text observations need a tokenizer")
-                obs_ids = list(self.tokenizer.apply_chat_template(obs, add_generation_prompt=True, tokenize=True))
+                obs_ids = chat_ids(self.tokenizer, obs, **self.chat_template_kwargs)
                 resp += obs_ids
                 mask += [0] * len(obs_ids)
                 lps += [0.0] * len(obs_ids)

@@ -8,6 +8,8 @@ Everything here is host-side list processing; tokenizers are duck-typed (``encod
 
 from __future__ import annotations
 
+from ..utils.tokenizer import chat_ids
+
 import os
 from collections import defaultdict
 
@@ -106,8 +108,8 @@ def get_generation_prompt_ids(tokenizer) -> list[int]:
     if not hasattr(tokenizer, "apply_chat_template"):
         return list(tokenizer.encode("<|assistant|>\n"))
     msgs = [{"role": "user", "content": ""}]
-    a = list(tokenizer.apply_chat_template(msgs, tokenize=True, add_generation_prompt=False))
-    b = list(tokenizer.apply_chat_template(msgs, tokenize=True, add_generation_prompt=True))
+    a = chat_ids(tokenizer, msgs, False)
+    b = chat_ids(tokenizer, msgs, True)
     if b[:len(a)] != a:
         raise ValueError("the tokenizer's template is not prefix-stable under add_generation_prompt")
     return b[len(a):]

@@ -20,6 +20,8 @@ made while an event loop is running in this thread is carried out on a helper th
 
 from __future__ import annotations
 
+from ..utils.tokenizer import chat_ids
+
 import asyncio
 import threading
 
@@ -63,7 +65,7 @@ class RLMGymGenerator(SkyRLGymGenerator):
     def _complete(self, prompts: list[str], sampling_params: dict | None) -> list[str]:
         sp = dict(sampling_params or {})
         sp["max_generate_length"] = self.lm_max_tokens
-        ids = [list(self.tokenizer.apply_chat_template([{"role": "user", "content": p}], add_generation_prompt=True, tokenize=True))
+        ids = [chat_ids(self.tokenizer, [{"role": "user", "content": p}])
                for p in prompts]
         out = _run_sync(self.engine.generate({"prompt_token_ids": ids, "sampling_params": sp}))
         return [self._decode(r) for r in out["response_ids"]]

@@ -18,6 +18,8 @@ record whose template breaks it is dropped with a count), which is what lets the
 
 from __future__ import annotations
 
+from ..utils.tokenizer import chat_ids
+
 import hashlib
 import json
 import os
@@ -40,7 +42,7 @@ def _render(messages: list[dict], tools=None) -> str:
 def _ids(tokenizer, messages: list[dict], tools=None) -> list[int]:
     if hasattr(tokenizer, "apply_chat_template"):
         kw = {"tools": tools} if tools else {}
-        return list(tokenizer.apply_chat_template(messages, tokenize=True, add_generation_prompt=False, **kw))
+        return chat_ids(tokenizer, messages, False, **kw)
     return list(tokenizer.encode(_render(messages, tools)))
 
 

@@ -418,6 +418,7 @@ class RayPPOTrainer:
                                                zero_reward_on_non_stop=g.zero_reward_on_non_stop,
                                                apply_overlong_filtering=g.apply_overlong_filtering,
                                                rate_limit=g.rate_limit or None, max_input_length=mil, step_wise=g.step_wise_trajectories)
+        self.generator.chat_template_kwargs = dict(g.chat_template_kwargs or {})
         if t.isoexec.enabled:
             self.adapter_trainer = ContractAdapter("trainer", model, self.rank, trainer_tp=self.ps.tp, engine_tp=tp_e, trainer_pp=self.ps.pp)
             self.adapter_trainer.run_install()

@@ -4,6 +4,21 @@ no pretrained tokenizer files are available (there is no network here). Ids 0..2
 from __future__ import annotations
 
 
+def chat_ids(tokenizer, messages, add_generation_prompt: bool = True, **kw) -> list[int]:
+    """Token ids of a conversation through the tokenizer's chat template. Tokenizers differ in what ``tokenize=True``
+    returns (a list of ids; or, in recent ``transformers``, a mapping with ``input_ids``; possibly batched): this gives
+    the flat list either way."""
+    out = tokenizer.apply_chat_template(messages, add_generation_prompt=add_generation_prompt, tokenize=True, **kw)
+    if hasattr(out, "keys") and "input_ids" in out:
+        out = out["input_ids"]
+    if hasattr(out, "tolist"):
+        out = out.tolist()
+    out = list(out)
+    if out and isinstance(out[0], (list, tuple)):
+        out = list(out[0])
+    return [int(t) for t in out]
+
+
 class ByteTokenizer:
     BOS, EOS, IM_START, IM_END, PAD = 256, 257, 258, 259, 260
     vocab_size = 261
@@ -40,7 +55,7 @@ class ByteTokenizer:
                 ids += self.encode(piece)
         return ids
 
-    def apply_chat_template(self, messages: list[dict], add_generation_prompt: bool = True, tokenize: bool = True):
+    def apply_chat_template(self, messages: list[dict], add_generation_prompt: bool = True, tokenize: bool = True, **_):
         ids: list[int] = []
         for m in messages:
             ids += [self.IM_START] + self.encode(f"{m['role']}\n{m['content']}") + [self.IM_END] + self.encode("\n")

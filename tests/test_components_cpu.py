@@ -1325,3 +1325,38 @@ def test_engine_stops_at_the_tokenizers_end_of_sequence_token():
     assert out.response_ids == [42] and out.stop_reason == "stop"
     out = eng.generate([[5, 6, 7]], SamplingParams(max_generate_length=4, temperature=0.0, logit_bias={42: 1e4}, ignore_eos=True))[0]
     assert out.response_ids == [42] * 4 and out.stop_reason == "length"
+
+
+def _hf_fast_tokenizer():
+    """A Hugging Face fast tokenizer built in memory (word level, with a chat template)."""
+    from tokenizers import Tokenizer, models, pre_tokenizers
+    from transformers import PreTrainedTokenizerFast
+
+    words = ["<unk>", "<eos>", "<|user|>", "<|assistant|>", "<|system|>", "hello", "world", "two", "plus", "four", "is"]
+    tk = Tokenizer(models.WordLevel({w: i for i, w in enumerate(words)}, unk_token="<unk>"))
+    tk.pre_tokenizer = pre_tokenizers.WhitespaceSplit()
+    t = PreTrainedTokenizerFast(tokenizer_object=tk, unk_token="<unk>", eos_token="<eos>")
+    t.chat_template = ("{% for m in messages %}<|{{ m['role'] }}|> {{ m['content'] }} <eos> {% endfor %}"
+                       "{% if add_generation_prompt %}<|assistant|> {% endif %}")
+    return t
+
+
+def test_chat_ids_with_a_hugging_face_tokenizer():
+    """``apply_chat_template(tokenize=True)`` of recent transformers returns a mapping, not a list: every place that
+    tokenises a conversation must still get the flat id list."""
+    from skyrl_isoexec_b200.engine.renderer import render_conversation
+    from skyrl_isoexec_b200.models.config import get_config
+    from skyrl_isoexec_b200.train.generator_utils import get_generation_prompt_ids
+    from skyrl_isoexec_b200.train.sft_data import tokenize_record
+    from skyrl_isoexec_b200.utils.tokenizer import chat_ids
+
+    t = _hf_fast_tokenizer()
+    msgs = [{"role": "user", "content": "two plus two"}]
+    ids = chat_ids(t, msgs)
+    assert ids == [2, 7, 8, 7, 1, 3] and all(isinstance(i, int) for i in ids)
+    assert chat_ids(t, msgs, False) == [2, 7, 8, 7, 1]
+    assert get_generation_prompt_ids(t) == [3]
+    r = render_conversation(msgs, t, get_config("tiny-qwen3"))
+    assert list(r["token_ids"]) == ids and r["features"] is None
+    ex = tokenize_record({"messages": msgs + [{"role": "assistant", "content": "is four"}]}, t, max_length=64)
+    assert ex is not None and ex["prompt_ids"] == [2, 7, 8, 7, 1] and ex["response_ids"] == [3, 10, 9, 1] and sum(ex["loss_mask"]) == 4
