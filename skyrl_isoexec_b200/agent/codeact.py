@@ -13,7 +13,7 @@ in front of the next one, which gives notebook-like persistence without a long-l
 
 from __future__ import annotations
 
-from ..utils.tokenizer import chat_ids
+from ..utils.tokenizer import chat_ids, chat_ids_continuation
 
 import json
 import re
@@ -86,7 +86,7 @@ class CodeActAgent:
                 obs = "bash is not available here; use <execute_python>."
             else:
                 obs = "No <execute_python> block or <finish> found."
-            obs_ids = chat_ids(self.tok, [{"role": "tool", "content": obs[:self.max_obs]}])
+            obs_ids = chat_ids_continuation(self.tok, [{"role": "tool", "content": obs[:self.max_obs]}])
             tr.response_ids += obs_ids
             tr.loss_mask += [0] * len(obs_ids)
             tr.logprobs += [0.0] * len(obs_ids)

@@ -9,7 +9,7 @@ trajectories concurrently against one engine (continuous batching does the rest)
 
 from __future__ import annotations
 
-from ..utils.tokenizer import chat_ids
+from ..utils.tokenizer import chat_ids, chat_ids_continuation
 
 import asyncio
 import json
@@ -101,7 +101,7 @@ class ReActAgent:
                 except json.JSONDecodeError as e:
                     res = {"error": f"tool call is not valid JSON: {e}"}
                 obs = json.dumps(res, default=str)[:4000]
-            obs_ids = chat_ids(self.tok, [{"role": "tool", "content": obs}])
+            obs_ids = chat_ids_continuation(self.tok, [{"role": "tool", "content": obs}])
             tr.response_ids += obs_ids
             tr.loss_mask += [0] * len(obs_ids)
             tr.logprobs += [0.0] * len(obs_ids)

@@ -10,7 +10,7 @@ multi-turn agent loop (R/train/generators/skyrl_gym_generator.py:273,713,808).
 
 from __future__ import annotations
 
-from ..utils.tokenizer import chat_ids
+from ..utils.tokenizer import chat_ids, chat_ids_continuation
 
 import asyncio
 import time
@@ -185,7 +185,7 @@ class SkyRLGymGenerator(GeneratorInterface):
             if obs:
                 if self.tokenizer is None:
                     raise ValueError("text observations need a tokenizer")
-                obs_ids = chat_ids(self.tokenizer, obs, **self.chat_template_kwargs)
+                obs_ids = chat_ids_continuation(self.tokenizer, obs, **self.chat_template_kwargs)
                 resp += obs_ids
                 mask += [0] * len(obs_ids)
                 lps += [0.0] * len(obs_ids)

@@ -19,6 +19,20 @@ def chat_ids(tokenizer, messages, add_generation_prompt: bool = True, **kw) -> l
     return [int(t) for t in out]
 
 
+def chat_ids_continuation(tokenizer, messages, **kw) -> list[int]:
+    """Ids of ``messages`` (environment observations, tool results) as they appear INSIDE a running conversation, ending
+    with the generation prompt of the next assistant turn. Rendered alone, many templates would open with a preamble
+    (a default system prompt, a begin-of-text token) that must not be repeated in mid-context: the messages are rendered
+    after a fixed dummy turn whose ids are cut off again. A template that is not prefix-stable under that falls back to
+    the stand-alone rendering (reference: skyrl/train/generators/utils.py ``encode_messages_subset``)."""
+    base = [{"role": "user", "content": "."}]
+    head = chat_ids(tokenizer, base, False, **kw)
+    full = chat_ids(tokenizer, base + list(messages), True, **kw)
+    if head and full[:len(head)] == head:
+        return full[len(head):]
+    return chat_ids(tokenizer, messages, True, **kw)
+
+
 class ByteTokenizer:
     BOS, EOS, IM_START, IM_END, PAD = 256, 257, 258, 259, 260
     vocab_size = 261

@@ -1360,3 +1360,19 @@ def test_chat_ids_with_a_hugging_face_tokenizer():
     assert list(r["token_ids"]) == ids and r["features"] is None
     ex = tokenize_record({"messages": msgs + [{"role": "assistant", "content": "is four"}]}, t, max_length=64)
     assert ex is not None and ex["prompt_ids"] == [2, 7, 8, 7, 1] and ex["response_ids"] == [3, 10, 9, 1] and sum(ex["loss_mask"]) == 4
+
+
+def test_observations_in_mid_context_do_not_repeat_the_template_preamble():
+    from skyrl_isoexec_b200.utils.tokenizer import ByteTokenizer, chat_ids, chat_ids_continuation
+
+    t = _hf_fast_tokenizer()
+    # a template that injects a default system turn when the conversation does not start with one (as Qwen's does)
+    t.chat_template = ("{% if messages[0]['role'] != 'system' %}<|system|> hello world <eos> {% endif %}"
+                       "{% for m in messages %}<|{{ m['role'] }}|> {{ m['content'] }} <eos> {% endfor %}"
+                       "{% if add_generation_prompt %}<|assistant|> {% endif %}")
+    obs = [{"role": "user", "content": "is four"}]
+    alone = chat_ids(t, obs)
+    assert alone[:4] == [4, 5, 6, 1]                                   # the preamble
+    assert chat_ids_continuation(t, obs) == [2, 10, 9, 1, 3]           # the turn and the generation prompt only
+    b = ByteTokenizer()
+    assert chat_ids_continuation(b, obs) == chat_ids(b, obs)           # no preamble: the same ids as before
