@@ -494,7 +494,14 @@ def _coerce(val: str, tp):
     if tp is str:
         return val.strip("\"'")
     if tp in (list, dict) or origin in (list, dict, tuple):
-        out = json.loads(val.replace("'", '"'))
+        try:
+            out = json.loads(val.replace("'", '"'))
+        except json.JSONDecodeError:
+            if tp is dict or origin is dict:
+                raise
+            out = [v.strip().strip("\"'") for v in val.strip("[]()").split(",") if v.strip()]   # a bare value or a, b, c: a list of strings
+        if (tp is list or origin in (list, tuple)) and not isinstance(out, (list, tuple)):
+            out = [out]
         return tuple(out) if origin is tuple else out
     return val
 

@@ -1376,3 +1376,27 @@ def test_observations_in_mid_context_do_not_repeat_the_template_preamble():
     assert chat_ids_continuation(t, obs) == [2, 10, 9, 1, 3]           # the turn and the generation prompt only
     b = ByteTokenizer()
     assert chat_ids_continuation(b, obs) == chat_ids(b, obs)           # no preamble: the same ids as before
+
+
+def test_rl_step_with_a_hugging_face_tokenizer_directory(tmp_path):
+    """``trainer.policy.tokenizer_path=<dir>``: chat prompts from a JSONL file are rendered by the directory's chat template,
+    a multi-turn environment's observations are appended as conversation turns, and the step stays bitwise on-policy."""
+    import json
+
+    from skyrl_isoexec_b200.train.entrypoints import main_base
+
+    tok_dir = tmp_path / "tok"
+    _hf_fast_tokenizer().save_pretrained(str(tok_dir))
+    data = tmp_path / "train.jsonl"
+    with open(data, "w") as f:
+        for _ in range(8):
+            f.write(json.dumps({"prompt": [{"role": "user", "content": "two plus two"}], "env_class": "gsm8k_multi_turn",
+                                "reward_spec": {"ground_truth": "4"}}) + "\n")
+    ov = ["trainer.policy.model=tiny-qwen3", f"trainer.policy.tokenizer_path={tok_dir}", f"data.train_data={data}",
+          "environment.env_class=gsm8k_multi_turn", "generator.batched=false", "generator.max_turns=2",
+          "trainer.train_batch_size=2", "trainer.policy_mini_batch_size=2", "generator.n_samples_per_prompt=2",
+          "generator.sampling_params.max_generate_length=4", "trainer.max_prompt_length=32", "generator.max_input_length=64",
+          "generator.inference_engine.num_kv_pages=16", "trainer.num_steps=1", "trainer.ckpt_interval=0"]
+    tr = main_base.BasePPOExp(SkyRLTrainConfig.from_cli_overrides(ov)).run()
+    assert tr.global_step == 1
+    assert tr.all_metrics["policy/rollout_train_logprob_bit_mismatches"] == 0
